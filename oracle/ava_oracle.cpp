@@ -1,0 +1,1091 @@
+// CPU oracle for the per-token block step of the Ava spiking language model.
+// TEST INFRASTRUCTURE ONLY: see ava_oracle.h for what it is, what it follows and who may load it.
+//
+// Build with -ffp-contract=off: every multiply-add that the reference fuses is written std::fmaf here, and every
+// one it does not fuse must stay two roundings.
+
+#include "ava_oracle.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <functional>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+#if defined(__AVX2__) && defined(__FMA__)
+#include <immintrin.h>
+#define ORC_HAVE_AVX2 1
+#else
+#define ORC_HAVE_AVX2 0
+#endif
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+namespace {
+
+// ------------------------------------------------------------------------------------------------ math hooks
+float libm_exp(float x) { return std::exp(x); }
+float libm_log(float x) { return std::log(x); }
+// Rust's f32::powf(-0.5) is the platform powf
+float libm_rsqrt(float x) { return std::pow(x, -0.5f); }
+
+orc_fn1 g_exp = libm_exp, g_log = libm_log, g_rsqrt = libm_rsqrt;
+int g_threads = 1;
+int g_simd = 1;
+double g_event_max = 0.5;  // int8.rs:459
+thread_local int g_last_event_rows = 0;
+
+constexpr int TILE = 64;       // int8.rs:41
+constexpr float NORM_EPS = 1e-5f;  // model.rs:36
+
+// ------------------------------------------------------------------------------------------------ A0 quantiser
+// quant.rs:18-31: scale[c] = max_r |w[r][c]| / 127 (1 when the column is all zero); q = round(w / scale)
+// clamped to +-127, round = half away from zero (Rust f32::round).
+void quantize_int8(const float* w, int rows, int cols, int8_t* q, float* scale) {
+    for (int c = 0; c < cols; ++c) scale[c] = 0.f;
+    for (int r = 0; r < rows; ++r)
+        for (int c = 0; c < cols; ++c) scale[c] = std::max(scale[c], std::fabs(w[(size_t)r * cols + c]));
+    for (int c = 0; c < cols; ++c) scale[c] = scale[c] > 0.f ? scale[c] / 127.0f : 1.0f;
+    for (size_t i = 0; i < (size_t)rows * cols; ++i) {
+        float v = std::round(w[i] / scale[i % cols]);  // roundf: half away from zero
+        v = std::min(std::max(v, -127.0f), 127.0f);
+        q[i] = (int8_t)v;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ A1 int8 products
+// One weight matrix W [din, dout] in int8 with one f32 scale per output column, packed in column tiles of 64
+// (int8.rs:46-72): q[(tile * din + j) * 64 + cc], columns past dout are 0 with scale 1.
+struct QW {
+    int din = 0, dout = 0, tiles = 0;
+    std::vector<int8_t> q;
+    std::vector<float> scale;
+
+    void from_q(const int8_t* qr, const float* sc, int din_, int dout_) {
+        din = din_;
+        dout = dout_;
+        tiles = (dout + TILE - 1) / TILE;
+        q.assign((size_t)tiles * din * TILE, 0);
+        scale.assign((size_t)tiles * TILE, 1.0f);
+        std::copy(sc, sc + dout, scale.begin());
+        for (int j = 0; j < din; ++j)
+            for (int c = 0; c < dout; ++c) q[((size_t)(c / TILE) * din + j) * TILE + c % TILE] = qr[(size_t)j * dout + c];
+    }
+    bool ok() const { return din > 0; }
+};
+
+// -0 counts as zero, NaN as non-zero (int8.rs:261-269)
+inline bool nonzero(float v) { return v != 0.0f; }
+
+// int8.rs:315-331: acc from +0, fma(x[j], (f32) q[j][c], acc) over every j or the listed non-zero j, increasing;
+// then acc * scale.
+void tile_scalar(const float* x, int din, const int* idx, int nidx, const int8_t* qt, const float* sc, float* out, int n_out) {
+    float acc[TILE];
+    for (int c = 0; c < TILE; ++c) acc[c] = 0.f;
+    auto add = [&](int j) {
+        const float xj = x[j];
+        const int8_t* row = qt + (size_t)j * TILE;
+        for (int c = 0; c < TILE; ++c) acc[c] = std::fmaf(xj, (float)row[c], acc[c]);
+    };
+    if (idx)
+        for (int i = 0; i < nidx; ++i) add(idx[i]);
+    else
+        for (int j = 0; j < din; ++j) add(j);
+    for (int c = 0; c < n_out; ++c) out[c] = acc[c] * sc[c];
+}
+
+#if ORC_HAVE_AVX2
+// The reference's AVX2 kernel (int8.rs:389-435) keeps 8 accumulators of 8 lanes over one 64-column tile row; each
+// lane is the same fma chain as the scalar code, so the same bits.
+inline __m256 w8(const int8_t* p) { return _mm256_cvtepi32_ps(_mm256_cvtepi8_epi32(_mm_loadl_epi64((const __m128i*)p))); }
+
+void tile_avx2(const float* x, int din, const int* idx, int nidx, const int8_t* qt, const float* sc, float* out, int n_out) {
+    __m256 a[8];
+    for (auto& v : a) v = _mm256_setzero_ps();
+    auto add = [&](int j) {
+        const __m256 xb = _mm256_set1_ps(x[j]);
+        const int8_t* p = qt + (size_t)j * TILE;
+        for (int v = 0; v < 8; ++v) a[v] = _mm256_fmadd_ps(xb, w8(p + 8 * v), a[v]);
+    };
+    if (idx)
+        for (int i = 0; i < nidx; ++i) add(idx[i]);
+    else
+        for (int j = 0; j < din; ++j) add(j);
+    alignas(32) float buf[TILE];
+    for (int v = 0; v < 8; ++v) _mm256_store_ps(buf + 8 * v, _mm256_mul_ps(a[v], _mm256_loadu_ps(sc + 8 * v)));
+    std::memcpy(out, buf, sizeof(float) * n_out);
+}
+#endif
+
+void tile_any(const float* x, int din, const int* idx, int nidx, const int8_t* qt, const float* sc, float* out, int n_out) {
+#if ORC_HAVE_AVX2
+    if (g_simd) return tile_avx2(x, din, idx, nidx, qt, sc, out, n_out);
+#endif
+    tile_scalar(x, din, idx, nidx, qt, sc, out, n_out);
+}
+
+// int8.rs:166-211 without the row-blocked kernel (which changes the speed only): per row its non-zero count, an event
+// list when the count is at most event_max * din, then one (tile, row) unit after another.
+void q8_matmul(const QW& w, const float* x, int m, float* y) {
+    const int din = w.din;
+    std::vector<int> off(m + 1, 0);
+    std::vector<char> ev(m, 0);
+    std::vector<int> cnt(m, 0);
+    const double lim = g_event_max * (double)din;
+    for (int r = 0; r < m; ++r) {
+        int c = 0;
+        for (int j = 0; j < din; ++j) c += nonzero(x[(size_t)r * din + j]);
+        cnt[r] = c;
+        ev[r] = (double)c <= lim;
+        off[r + 1] = off[r] + (ev[r] ? c : 0);
+    }
+    std::vector<int> idx(off[m]);
+    int nev = 0;
+    for (int r = 0; r < m; ++r) {
+        if (!ev[r]) continue;
+        ++nev;
+        int n = off[r];
+        for (int j = 0; j < din; ++j)
+            if (nonzero(x[(size_t)r * din + j])) idx[n++] = j;
+    }
+    g_last_event_rows = nev;
+    const int units = m * w.tiles;
+    // unit u: tile u / m, row u % m (int8.rs:184-195)
+    auto run = [&](int u) {
+        const int t = u / m, r = u % m;
+        const int c0 = t * TILE;
+        const int n_out = std::min(TILE, w.dout - c0);
+        tile_any(x + (size_t)r * din, din, ev[r] ? idx.data() + off[r] : nullptr, off[r + 1] - off[r], w.q.data() + (size_t)t * din * TILE,
+                 w.scale.data() + c0, y + (size_t)r * w.dout + c0, n_out);
+    };
+    size_t work = 0;
+    for (int r = 0; r < m; ++r) work += ev[r] ? cnt[r] : din;
+    work *= (size_t)w.tiles * TILE;
+    const int want = (int)std::min<size_t>({(size_t)g_threads, work / (1u << 16), (size_t)units});  // PAR_MIN, int8.rs:44
+    if (want <= 1) {
+        for (int u = 0; u < units; ++u) run(u);
+    } else {
+#pragma omp parallel for num_threads(want) schedule(static)
+        for (int u = 0; u < units; ++u) run(u);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ A2 small ops
+// fstep.rs:212-220: squares summed one after another from 0, the mean's affine (sum * (1/n) + 0), affine(1, eps),
+// powf(-0.5).
+float inv_rms(const float* x, int n) {
+    float s = 0.f;
+    for (int i = 0; i < n; ++i) s += x[i] * x[i];
+    const float ms = s * (float)(1.0 / (double)n) + 0.0f;
+    return g_rsqrt(ms * 1.0f + NORM_EPS);
+}
+
+void rmsnorm(const float* x, const float* gain, int n, float* y) {
+    const float inv = inv_rms(x, n);
+    for (int i = 0; i < n; ++i) y[i] = (x[i] * inv) * gain[i];
+}
+
+// fstep.rs:271-282
+void l2_heads(float* x, int n, int hs) {
+    for (int h = 0; h + hs <= n; h += hs) {
+        float s = 0.f;
+        for (int i = 0; i < hs; ++i) s += x[h + i] * x[h + i];
+        const float inv = g_rsqrt(s * 1.0f + (float)1e-6);
+        for (int i = 0; i < hs; ++i) x[h + i] = x[h + i] * inv;
+    }
+}
+
+// fstep.rs:285-292
+void head_norm(float* y, int n, int hs) {
+    for (int h = 0; h + hs <= n; h += hs) {
+        const float inv = inv_rms(y + h, hs);
+        for (int i = 0; i < hs; ++i) y[h + i] = y[h + i] * inv;
+    }
+}
+
+// fstep.rs:260-262: (exp(-x) * 1 + 1)^-1
+float sigmoid(float x) { return 1.0f / (g_exp(-x) * 1.0f + 1.0f); }
+
+// fstep.rs:265-268: -(relu(-x) + ln(exp(-|x|) * 1 + 1))
+float log_sigmoid(float x) {
+    const float soft = g_log(g_exp(-std::fabs(x)) * 1.0f + 1.0f);
+    return -(std::max(-x, 0.0f) + soft);
+}
+
+// fstep.rs:222-257: the one-row f32 product in gemm's order: out = w0 * x0, then fma(w_j, x_j, out); 2 inputs:
+// (w1 * x1) + (w0 * x0); 1 input: the product.
+void gemv(const float* x, int k, const float* w, int n, float* out) {
+    if (k == 0) {
+        for (int c = 0; c < n; ++c) out[c] = 0.f;
+    } else if (k == 1) {
+        for (int c = 0; c < n; ++c) out[c] = w[c] * x[0];
+    } else if (k == 2) {
+        for (int c = 0; c < n; ++c) out[c] = w[n + c] * x[1] + w[c] * x[0];
+    } else {
+        for (int c = 0; c < n; ++c) out[c] = w[c] * x[0];
+        for (int j = 1; j < k; ++j) {
+            const float xj = x[j];
+            const float* wr = w + (size_t)j * n;
+            for (int c = 0; c < n; ++c) out[c] = std::fmaf(wr[c], xj, out[c]);
+        }
+    }
+}
+
+void add_into(float* x, const float* o, int n) {
+    for (int i = 0; i < n; ++i) x[i] = x[i] + o[i];
+}
+
+bool all_finite(const float* x, int n) {
+    for (int i = 0; i < n; ++i)
+        if (!std::isfinite(x[i])) return false;
+    return true;
+}
+
+// ------------------------------------------------------------------------------------------------ A3 LIF
+// fstep/arch.rs:173-228.  theta NULL: 1.0 for every channel; rho/gain NULL: no adaptive threshold.
+void lif(const float* cur, const float* beta, const float* theta, const float* rho, const float* gain, int spikes, float slope,
+         const float* v0, const float* s0, const float* a0, int d, float* s, float* v, float* a) {
+    auto th = [&](int c) { return theta ? theta[c] : 1.0f; };
+    const bool alif = rho && gain;
+    if (spikes == 0 && !alif) {
+        // state::lif_infer form: v = beta v + I - th s; s = H(v - th)
+        for (int c = 0; c < d; ++c) {
+            const float vv = beta[c] * v0[c] + cur[c] - th(c) * s0[c];
+            v[c] = vv;
+            s[c] = (vv - th(c) >= 0.0f) ? 1.0f : 0.0f;
+        }
+        return;
+    }
+    auto soft_step = [&](float u) { return u / (std::fabs(u) * slope + 1.0f); };
+    auto heav = [](float u) { return u >= 0.0f ? 1.0f : 0.0f; };
+    const int levels = spikes == 2 ? 2 : 1;
+    for (int c = 0; c < d; ++c) {
+        float th_prev, th_t;
+        if (alif) {
+            const float a_prev = a0 ? a0[c] : 0.0f;
+            th_prev = th(c) + a_prev * gain[c];
+            const float an = a_prev * rho[c] + std::fabs(s0[c]) * (rho[c] * -1.0f + 1.0f);
+            a[c] = an;
+            th_t = th(c) + an * gain[c];
+        } else {
+            th_prev = th_t = th(c);
+        }
+        const float vv = v0[c] * beta[c] + cur[c] - s0[c] * th_prev;
+        v[c] = vv;
+        if (spikes == 0) {
+            const float u = vv - th_t;
+            const float sg = soft_step(u);
+            s[c] = sg + (heav(u) - sg);
+        } else {
+            float soft = 0.f, hard = 0.f;
+            for (int k = 1; k <= levels; ++k) {
+                const float kth = th_t * (float)k + 0.0f;
+                const float up = vv - kth, down = -vv - kth;
+                const float s1 = soft_step(up) - soft_step(down);
+                const float h1 = heav(up) - heav(down);
+                if (k == 1) {
+                    soft = s1;
+                    hard = h1;
+                } else {
+                    soft = soft + s1;
+                    hard = hard + h1;
+                }
+            }
+            s[c] = soft + (hard - soft);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ A5 fast-weight head
+// fstep/arch.rs:256-337 (head_rows): F, S [hs, hs] (row = key dim, col = value dim).
+//     rr = (e F + r0) + p2 S
+//     y  = ((q alpha) F + (q.w) v) - (q.ah) rr + (q M) S
+//     F' = ((F * alpha_row + w v^T) - ah rr^T) + S * M
+//     S' = ((S * M + 0) + w v^T) - ah rr^T
+void head_rows(int hs, const float* e, const float* v, const float* w, const float* ah, const float* qg, const float* ex, float qw, float qa,
+               float ke, float tinv, bool mom, float m, const float* qs, const float* p2, const float* f0, const float* s0, float* y, float* f1,
+               float* s1) {
+    std::vector<float> rr(hs), t1(hs), tq;
+    for (int a = 0; a < hs; ++a) {
+        const float* frow = f0 + (size_t)a * hs;
+        const float pa = e[a], ga = qg[a];
+        if (a == 0) {
+            for (int b = 0; b < hs; ++b) {
+                rr[b] = frow[b] * pa;
+                t1[b] = frow[b] * ga;
+            }
+        } else {
+            for (int b = 0; b < hs; ++b) {
+                rr[b] = std::fmaf(frow[b], pa, rr[b]);
+                t1[b] = std::fmaf(frow[b], ga, t1[b]);
+            }
+        }
+    }
+    for (int b = 0; b < hs; ++b) rr[b] = rr[b] + tinv * (ke * v[b]);
+    if (mom) {
+        std::vector<float> z(hs);
+        tq.assign(hs, 0.f);
+        for (int a = 0; a < hs; ++a) {
+            const float* srow = s0 + (size_t)a * hs;
+            const float pa = p2[a], q_a = qs[a];
+            if (a == 0) {
+                for (int b = 0; b < hs; ++b) {
+                    z[b] = srow[b] * pa;
+                    tq[b] = srow[b] * q_a;
+                }
+            } else {
+                for (int b = 0; b < hs; ++b) {
+                    z[b] = std::fmaf(srow[b], pa, z[b]);
+                    tq[b] = std::fmaf(srow[b], q_a, tq[b]);
+                }
+            }
+        }
+        for (int b = 0; b < hs; ++b) rr[b] = rr[b] + z[b];
+    }
+    for (int b = 0; b < hs; ++b) y[b] = (t1[b] + qw * v[b]) - qa * rr[b];
+    if (mom)
+        for (int b = 0; b < hs; ++b) y[b] = y[b] + tq[b];
+    if (mom) {
+        for (int a = 0; a < hs; ++a) {
+            const float wa = w[a], aa = ah[a], xa = ex[a];
+            const float* frow = f0 + (size_t)a * hs;
+            const float* srow = s0 + (size_t)a * hs;
+            for (int b = 0; b < hs; ++b) {
+                const float wv = wa * v[b], ar = aa * rr[b];
+                f1[(size_t)a * hs + b] = ((frow[b] * xa + wv) - ar) + srow[b] * m;
+                s1[(size_t)a * hs + b] = ((srow[b] * m + 0.0f) + wv) - ar;
+            }
+        }
+    } else {
+        for (int a = 0; a < hs; ++a) {
+            const float wa = w[a], aa = ah[a], xa = ex[a];
+            const float* frow = f0 + (size_t)a * hs;
+            for (int b = 0; b < hs; ++b) f1[(size_t)a * hs + b] = (frow[b] * xa + wa * v[b]) - aa * rr[b];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ A6 plain delta rule
+// fstep.rs:397-436 (fw_rows, Rule::Delta) with p = k^T F by gemv (fstep.rs:592-595).
+void delta_plain(int hs, const float* f0, const float* k, const float* v, const float* q, float al, float b, float* f1, float* y) {
+    std::vector<float> p(hs);
+    gemv(k, hs, f0, hs, p.data());
+    for (int a = 0; a < hs; ++a) {
+        const float ka = k[a], qa = q[a];
+        for (int c = 0; c < hs; ++c) {
+            const float corr = (ka * p[c]) * b;
+            const float r = ((f0[(size_t)a * hs + c] - corr) * al) + ((ka * v[c]) * b);
+            f1[(size_t)a * hs + c] = r;
+            y[c] = a == 0 ? r * qa : std::fmaf(r, qa, y[c]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ A7 kWTA
+// fstep.rs:295-299: the k-th largest value (selection; ties give the same value).
+float kth_largest(const float* u, int n, int k) {
+    std::vector<float> b(u, u + n);
+    std::nth_element(b.begin(), b.begin() + (k - 1), b.end(), [](float a, float c) { return a > c; });
+    return b[k - 1];
+}
+
+// fstep/arch.rs:982-989
+void kwta(const float* u, int n, int k, bool relu2, float* a) {
+    if (k >= n) {
+        for (int i = 0; i < n; ++i) a[i] = std::max(u[i] * 1.0f, 0.0f);
+    } else {
+        const float kth = kth_largest(u, n, k);
+        for (int i = 0; i < n; ++i) a[i] = std::max(u[i] * ((u[i] - kth >= 0.0f) ? 1.0f : 0.0f), 0.0f);
+    }
+    if (relu2)
+        for (int i = 0; i < n; ++i) a[i] = a[i] * a[i];
+}
+
+// ------------------------------------------------------------------------------------------------ A8 engram read
+// fstep.rs:303-356: per key the score chain K[j][0] q0, then fma(K[j][a], q[a], .), times scale plus 0; softmax with
+// the max found by "replace while mx < s", exp(s - mx), the sum from 0, each divided; then the one-row product p . V.
+void attend(const float* q, const float* kc, const float* vc, int n, int hs, float scale, float* out) {
+    std::vector<float> sc(n);
+    for (int j = 0; j < n; ++j) {
+        const float* kr = kc + (size_t)j * hs;
+        float s = kr[0] * q[0];
+        for (int a = 1; a < hs; ++a) s = std::fmaf(kr[a], q[a], s);
+        sc[j] = s * scale + 0.0f;
+    }
+    float mx = sc[0];
+    for (int j = 0; j < n; ++j)
+        if (mx < sc[j]) mx = sc[j];
+    float den = 0.f;
+    for (int j = 0; j < n; ++j) {
+        sc[j] = g_exp(sc[j] - mx);
+        den += sc[j];
+    }
+    for (int j = 0; j < n; ++j) sc[j] = sc[j] / den;
+    gemv(sc.data(), n, vc, hs, out);
+}
+
+float bf16_round(float x) {
+    uint32_t u;
+    std::memcpy(&u, &x, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) {  // NaN stays NaN
+        u |= 0x00400000u;
+        u &= 0xffff0000u;
+    } else {
+        u += 0x7fffu + ((u >> 16) & 1u);
+        u &= 0xffff0000u;
+    }
+    float r;
+    std::memcpy(&r, &u, 4);
+    return r;
+}
+
+// ------------------------------------------------------------------------------------------------ trace
+struct Trace {
+    bool on = false;
+    std::map<std::pair<std::string, int>, std::vector<float>> t;
+    void put(const char* name, int block, const float* p, size_t n) {
+        if (on) t[{name, block}] = std::vector<float>(p, p + n);
+    }
+    void put(const char* name, int block, const std::vector<float>& v) { put(name, block, v.data(), v.size()); }
+};
+Trace g_trace;
+
+}  // namespace
+
+// ================================================================================================ model level
+struct Block {
+    // the spiking memory
+    std::vector<float> mem_norm, beta_param, theta, arho, again;
+    QW win, wout;
+    // the fast-weight memory
+    std::vector<float> hebb_norm, wa, wb, ba, bb, wa1, wa2, wb1, wb2, off, vres;
+    QW wq, wk, wv, we, wg, wo;
+    // the engram
+    std::vector<float> eng_norm;
+    QW ewq, ewk, ewv, ewo;
+    // the MLP
+    std::vector<float> mlp_norm;
+    QW w1, w2;
+    std::vector<float> dense;
+    // derived once: sigmoid(beta_param), sigmoid(arho)
+    std::vector<float> beta, rho;
+    bool derived = false;
+};
+
+struct orc_model {
+    orc_config cfg;
+    std::vector<float> tok_emb, final_norm;
+    QW head;
+    std::vector<Block> blocks;
+    int nh() const { return cfg.d / cfg.head_size; }
+    int enh() const { return cfg.d / cfg.eng_head_size; }
+};
+
+struct RowState {
+    std::vector<std::vector<float>> v, s, a;    // per block [d]
+    std::vector<std::vector<float>> f, ms;      // per block [nh, hs, hs]
+    std::vector<float> ek, evv;                 // engram [enh, n, ehs]
+    int eng_n = 0;
+    int64_t seen = 0;
+};
+
+struct orc_state {
+    const orc_model* m;
+    std::vector<RowState> rows;
+};
+
+namespace {
+
+std::vector<float>* f32_slot(orc_model* m, const std::string& name, int64_t* want) {
+    const orc_config& c = m->cfg;
+    const int d = c.d, nh = m->nh(), r = c.gate_rank;
+    if (name == "tok_emb") { *want = (int64_t)c.vocab * d; return &m->tok_emb; }
+    if (name == "final.norm") { *want = d; return &m->final_norm; }
+    if (name.size() < 3 || name[0] != 'b') return nullptr;
+    const size_t dot = name.find('.');
+    if (dot == std::string::npos) return nullptr;
+    const int i = std::atoi(name.substr(1, dot - 1).c_str());
+    if (i < 0 || i >= c.n_blocks) return nullptr;
+    Block& b = m->blocks[i];
+    b.derived = false;
+    const std::string rest = name.substr(dot + 1);
+    struct E { const char* n; std::vector<float>* p; int64_t len; };
+    const E table[] = {
+        {"mem.norm", &b.mem_norm, d}, {"mem.beta", &b.beta_param, d}, {"mem.theta", &b.theta, d}, {"mem.arho", &b.arho, d},
+        {"mem.again", &b.again, d}, {"hebb.norm", &b.hebb_norm, d}, {"hebb.wa", &b.wa, (int64_t)d * nh}, {"hebb.wb", &b.wb, (int64_t)d * nh},
+        {"hebb.ba", &b.ba, nh}, {"hebb.bb", &b.bb, nh}, {"hebb.wa1", &b.wa1, (int64_t)d * r}, {"hebb.wa2", &b.wa2, (int64_t)r * d},
+        {"hebb.wb1", &b.wb1, (int64_t)d * r}, {"hebb.wb2", &b.wb2, (int64_t)r * d}, {"hebb.off", &b.off, d}, {"hebb.vres", &b.vres, 2},
+        {"eng.norm", &b.eng_norm, d}, {"mlp.norm", &b.mlp_norm, d}, {"dense", &b.dense, i + 2},
+    };
+    for (const E& e : table)
+        if (rest == e.n) { *want = e.len; return e.p; }
+    return nullptr;
+}
+
+QW* q8_slot(orc_model* m, const std::string& name, int* din, int* dout) {
+    const orc_config& c = m->cfg;
+    const int d = c.d;
+    if (name == "head") { *din = d; *dout = c.vocab; return &m->head; }
+    if (name.size() < 3 || name[0] != 'b') return nullptr;
+    const size_t dot = name.find('.');
+    if (dot == std::string::npos) return nullptr;
+    const int i = std::atoi(name.substr(1, dot - 1).c_str());
+    if (i < 0 || i >= c.n_blocks) return nullptr;
+    Block& b = m->blocks[i];
+    const std::string rest = name.substr(dot + 1);
+    struct E { const char* n; QW* p; int din, dout; };
+    const E table[] = {
+        {"mem.win", &b.win, d, d}, {"mem.wout", &b.wout, d, d}, {"hebb.wq", &b.wq, d, d}, {"hebb.wk", &b.wk, d, d}, {"hebb.wv", &b.wv, d, d},
+        {"hebb.we", &b.we, d, d}, {"hebb.wg", &b.wg, d, d}, {"hebb.wo", &b.wo, d, d}, {"eng.wq", &b.ewq, d, d}, {"eng.wk", &b.ewk, d, d},
+        {"eng.wv", &b.ewv, d, d}, {"eng.wo", &b.ewo, d, d}, {"mlp.w1", &b.w1, d, c.hidden}, {"mlp.w2", &b.w2, c.hidden, d},
+    };
+    for (const E& e : table)
+        if (rest == e.n) { *din = e.din; *dout = e.dout; return e.p; }
+    return nullptr;
+}
+
+void derive(const orc_model* mc) {
+    orc_model* m = const_cast<orc_model*>(mc);
+    for (Block& b : m->blocks) {
+        if (b.derived) continue;
+        b.beta.resize(b.beta_param.size());
+        for (size_t c = 0; c < b.beta.size(); ++c) b.beta[c] = sigmoid(b.beta_param[c]);  // fstep/arch.rs:640
+        b.rho.resize(b.arho.size());
+        for (size_t c = 0; c < b.rho.size(); ++c) b.rho[c] = sigmoid(b.arho[c]);  // fstep/arch.rs:660
+        b.derived = true;
+    }
+}
+
+// fstep/arch.rs:525-1073 for R rows at once (one token each; the rows are independent, state.rs:13-15).  The int8
+// products take the R rows as one batch, as the reference's batched path does (each row's outputs are the bits of the
+// row alone, int8.rs:7-8); everything else runs row by row.  Returns 0, or 1 when the reference's fused step would
+// refuse a token (non-finite gates or keys): such a row is left uncommitted.
+int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, float* logits, size_t logit_stride, bool trace) {
+    const orc_config& cfg = m->cfg;
+    const int d = cfg.d, hs = cfg.head_size, nh = m->nh(), H = cfg.hidden, L = cfg.n_blocks;
+    for (int r = 0; r < R; ++r)
+        if (tok[r] >= (uint32_t)cfg.vocab) return -2;
+    const bool mom = cfg.mem_momentum > 0.0f;
+    const float mf = cfg.mem_momentum;
+    auto T = [&](const char* n, int blk, const float* p, size_t len) { if (trace) g_trace.put(n, blk, p, len); };
+    const int nt = std::max(1, std::min(g_threads, R));
+    (void)nt;
+
+    std::vector<float> x((size_t)R * d), h((size_t)R * d), tmp((size_t)R * d);
+    for (int r = 0; r < R; ++r) std::copy(m->tok_emb.begin() + (size_t)tok[r] * d, m->tok_emb.begin() + (size_t)(tok[r] + 1) * d, x.begin() + (size_t)r * d);
+    T("x_in", -1, x.data(), d);
+    std::vector<std::vector<float>> streams;
+    if (cfg.dense) streams.push_back(x);
+    std::vector<float> v_first;
+    bool have_v_first = false;
+
+    std::vector<RowState> nw(R);  // the new states, committed at the end
+    for (RowState& n : nw) {
+        n.v.resize(L); n.s.resize(L); n.a.resize(L); n.f.resize(L); n.ms.resize(L);
+    }
+    std::vector<char> bad(R, 0);
+    bool eng_written = false;
+
+    for (int i = 0; i < L; ++i) {
+        const Block& b = m->blocks[i];
+        // ---- the spiking memory (fstep/arch.rs:636-677)
+#pragma omp parallel for num_threads(nt) schedule(static)
+        for (int r = 0; r < R; ++r) rmsnorm(&x[(size_t)r * d], b.mem_norm.data(), d, &h[(size_t)r * d]);
+        T("h_lif", i, h.data(), d);
+        std::vector<float> cur((size_t)R * d), sp((size_t)R * d);
+        q8_matmul(b.win, h.data(), R, cur.data());
+#pragma omp parallel for num_threads(nt) schedule(static)
+        for (int r = 0; r < R; ++r) {
+            float* c_ = &cur[(size_t)r * d];
+            if (cfg.lif_scale)
+                for (int c = 0; c < d; ++c) c_[c] = c_[c] * (b.beta[c] * -1.0f + 1.0f);
+            RowState& st = *rows[r];
+            nw[r].v[i].resize(d);
+            nw[r].a[i].resize(cfg.alif ? d : 0);
+            lif(c_, b.beta.data(), cfg.theta ? b.theta.data() : nullptr, cfg.alif ? b.rho.data() : nullptr, cfg.alif ? b.again.data() : nullptr,
+                cfg.spikes, cfg.slope, st.v[i].data(), st.s[i].data(), cfg.alif ? st.a[i].data() : nullptr, d, &sp[(size_t)r * d],
+                nw[r].v[i].data(), cfg.alif ? nw[r].a[i].data() : nullptr);
+            nw[r].s[i].assign(&sp[(size_t)r * d], &sp[(size_t)r * d] + d);
+        }
+        T("cur", i, cur.data(), d);
+        T("spikes", i, sp.data(), d);
+        q8_matmul(b.wout, sp.data(), R, tmp.data());
+        add_into(x.data(), tmp.data(), R * d);
+        T("x_lif", i, x.data(), d);
+
+        // ---- the fast-weight memory (fstep/arch.rs:679-907)
+#pragma omp parallel for num_threads(nt) schedule(static)
+        for (int r = 0; r < R; ++r) rmsnorm(&x[(size_t)r * d], b.hebb_norm.data(), d, &h[(size_t)r * d]);
+        T("h_mem", i, h.data(), d);
+        std::vector<float> q((size_t)R * d), kraw((size_t)R * d), v((size_t)R * d), weo((size_t)R * d), gq(cfg.out_gate ? (size_t)R * d : 0);
+        q8_matmul(b.wq, h.data(), R, q.data());
+        q8_matmul(b.wk, h.data(), R, kraw.data());
+        q8_matmul(b.wv, h.data(), R, v.data());
+        q8_matmul(b.we, h.data(), R, weo.data());
+        if (cfg.out_gate) q8_matmul(b.wg, h.data(), R, gq.data());
+        if (trace) {
+            std::vector<float> all;
+            for (auto* p : {&q, &kraw, &v, &weo, &gq})
+                if (!p->empty()) all.insert(all.end(), p->begin(), p->begin() + d);
+            T("qkveg", i, all.data(), all.size());
+        }
+        if (cfg.value_residual && !have_v_first) {
+            v_first = v;  // block 0's values, before any mixing (fstep/arch.rs:695)
+            have_v_first = true;
+        }
+        const bool mix_v = cfg.value_residual && i > 0 && !b.vres.empty();
+        std::vector<float> y((size_t)R * d);
+        struct Tr { std::vector<float> k, ek, w, ah, qg, ex, yraw, qw, qa; } tr;
+#pragma omp parallel for num_threads(nt) schedule(static)
+        for (int r = 0; r < R; ++r) {
+            float* qr = &q[(size_t)r * d];
+            float* vr = &v[(size_t)r * d];
+            const float* hr = &h[(size_t)r * d];
+            const float* kr = &kraw[(size_t)r * d];
+            l2_heads(qr, d, hs);
+            std::vector<float> k(kr, kr + d);
+            l2_heads(k.data(), d, hs);
+            if (mix_v) {
+                const float p0 = b.vres[0] * 1.0f + 1.0f;
+                const float* vf = &v_first[(size_t)r * d];
+                for (int c = 0; c < d; ++c) vr[c] = vr[c] * p0 + vf[c] * b.vres[1];
+            }
+            const int rk = cfg.gate_rank;
+            std::vector<float> za(nh), zb(nh), z1(rk), lra(d), lrb(d);
+            gemv(hr, d, b.wa.data(), nh, za.data());
+            gemv(hr, d, b.wb.data(), nh, zb.data());
+            add_into(za.data(), b.ba.data(), nh);
+            add_into(zb.data(), b.bb.data(), nh);
+            gemv(hr, d, b.wa1.data(), rk, z1.data());
+            gemv(z1.data(), rk, b.wa2.data(), d, lra.data());
+            gemv(hr, d, b.wb1.data(), rk, z1.data());
+            gemv(z1.data(), rk, b.wb2.data(), d, lrb.data());
+
+            RowState& st = *rows[r];
+            std::vector<float> fnew((size_t)nh * hs * hs), snew(mom ? (size_t)nh * hs * hs : 0);
+            std::vector<float> ek(d), ex(d), w(d), ah(d), qg(d), yraw(d), qwv(nh), qav(nh);
+            float* yr = &y[(size_t)r * d];
+            bool bad_row = false;
+            for (int e = 0; e < nh && !bad_row; ++e) {
+                const int o = e * hs;
+                std::vector<float> la(hs), be(hs), qs, p2, e0(hs);
+                for (int c = 0; c < hs; ++c) {
+                    la[c] = log_sigmoid((za[e] + b.off[o + c]) + lra[o + c]);
+                    be[c] = sigmoid(zb[e] + lrb[o + c]) * 2.0f + 0.0f;
+                }
+                for (int c = 0; c < hs; ++c) ek[o + c] = kr[o + c] + weo[(size_t)r * d + o + c];
+                l2_heads(ek.data() + o, hs, hs);
+                for (int c = 0; c < hs; ++c) {
+                    ex[o + c] = g_exp(la[c]);
+                    w[o + c] = k[o + c] * be[c];
+                    ah[o + c] = ek[o + c] * (be[c] * ex[o + c]);
+                    qg[o + c] = qr[o + c] * ex[o + c];
+                }
+                if (!all_finite(la.data(), hs) || !all_finite(ek.data() + o, hs) || !all_finite(w.data() + o, hs) ||
+                    !all_finite(ah.data() + o, hs) || !all_finite(qr + o, hs) || !all_finite(vr + o, hs)) {
+                    bad_row = true;
+                    break;
+                }
+                if (mom) {
+                    qs.resize(hs);
+                    p2.resize(hs);
+                    const float gsx = 0.0f * mf + 0.0f;
+                    for (int c = 0; c < hs; ++c) {
+                        qs[c] = qr[o + c] * (1.0f * mf + 0.0f);
+                        p2[c] = ek[o + c] * gsx;
+                    }
+                }
+                auto sum0 = [&](const float* a, const float* c2) {
+                    float s = 0.f;
+                    for (int c = 0; c < hs; ++c) s += a[c] * c2[c];
+                    return s;
+                };
+                for (int c = 0; c < hs; ++c) e0[c] = ek[o + c] * 0.0f;
+                const float qw = sum0(qr + o, w.data() + o), qa = sum0(qr + o, ah.data() + o);
+                const float ke = sum0(e0.data(), w.data() + o), ae = sum0(e0.data(), ah.data() + o);
+                const float tinv = -(ae * 0.0f) + 1.0f;
+                if (tinv != 1.0f) {
+                    bad_row = true;
+                    break;
+                }
+                qwv[e] = qw;
+                qav[e] = qa;
+                head_rows(hs, ek.data() + o, vr + o, w.data() + o, ah.data() + o, qg.data() + o, ex.data() + o, qw, qa, ke, tinv, mom, mf,
+                          mom ? qs.data() : nullptr, mom ? p2.data() : nullptr, st.f[i].data() + (size_t)e * hs * hs,
+                          mom ? st.ms[i].data() + (size_t)e * hs * hs : nullptr, yr + o, fnew.data() + (size_t)e * hs * hs,
+                          mom ? snew.data() + (size_t)e * hs * hs : nullptr);
+                std::copy(yr + o, yr + o + hs, yraw.begin() + o);
+                head_norm(yr + o, hs, hs);
+                if (cfg.out_gate)
+                    for (int c = 0; c < hs; ++c) {
+                        const float g = gq[(size_t)r * d + o + c];
+                        yr[o + c] = yr[o + c] * (g / (1.0f + g_exp(-g)));
+                    }
+            }
+            if (bad_row) {
+                bad[r] = 1;
+                std::fill(yr, yr + d, 0.f);
+            }
+            nw[r].f[i] = std::move(fnew);
+            nw[r].ms[i] = std::move(snew);
+            if (trace && r == 0) {
+                tr.k = k; tr.ek = ek; tr.w = w; tr.ah = ah; tr.qg = qg; tr.ex = ex; tr.yraw = yraw; tr.qw = qwv; tr.qa = qav;
+            }
+        }
+        if (trace) {
+            T("q", i, q.data(), d); T("k", i, tr.k.data(), d); T("v", i, v.data(), d); T("ek", i, tr.ek.data(), d); T("w", i, tr.w.data(), d);
+            T("ah", i, tr.ah.data(), d); T("qg", i, tr.qg.data(), d); T("ex", i, tr.ex.data(), d); T("qw", i, tr.qw.data(), nh);
+            T("qa", i, tr.qa.data(), nh); T("y_raw", i, tr.yraw.data(), d); T("y", i, y.data(), d);
+        }
+        q8_matmul(b.wo, y.data(), R, tmp.data());
+        add_into(x.data(), tmp.data(), R * d);
+        T("x_mem", i, x.data(), d);
+
+        // ---- the engram (fstep/arch.rs:909-974)
+        if (i == cfg.eng_block) {
+            const int ehs = cfg.eng_head_size, enh = m->enh();
+#pragma omp parallel for num_threads(nt) schedule(static)
+            for (int r = 0; r < R; ++r) rmsnorm(&x[(size_t)r * d], b.eng_norm.data(), d, &h[(size_t)r * d]);
+            T("h_eng", i, h.data(), d);
+            std::vector<float> eq((size_t)R * d), ekk((size_t)R * d), evv((size_t)R * d), o((size_t)R * d);
+            q8_matmul(b.ewq, h.data(), R, eq.data());
+            q8_matmul(b.ewk, h.data(), R, ekk.data());
+            q8_matmul(b.ewv, h.data(), R, evv.data());
+            if (trace) {
+                std::vector<float> all;
+                for (auto* p : {&eq, &ekk, &evv}) all.insert(all.end(), p->begin(), p->begin() + d);
+                T("eng_qkv", i, all.data(), all.size());
+            }
+            const float scale = (float)(1.0 / std::sqrt((double)ehs));
+#pragma omp parallel for num_threads(nt) schedule(static)
+            for (int r = 0; r < R; ++r) {
+                float* kk = &ekk[(size_t)r * d];
+                float* vv = &evv[(size_t)r * d];
+                if (cfg.eng_store_bf16)
+                    for (int c = 0; c < d; ++c) {
+                        kk[c] = bf16_round(kk[c]);
+                        vv[c] = bf16_round(vv[c]);
+                    }
+                const RowState& st = *rows[r];
+                const int n0 = st.eng_n, n = n0 + 1;
+                // [enh, n, ehs] with this token's row appended per head (fstep.rs:449-459)
+                std::vector<float> kc((size_t)enh * n * ehs), vc((size_t)enh * n * ehs);
+                for (int hh = 0; hh < enh; ++hh) {
+                    std::copy(st.ek.begin() + (size_t)hh * n0 * ehs, st.ek.begin() + (size_t)(hh + 1) * n0 * ehs, kc.begin() + (size_t)hh * n * ehs);
+                    std::copy(st.evv.begin() + (size_t)hh * n0 * ehs, st.evv.begin() + (size_t)(hh + 1) * n0 * ehs, vc.begin() + (size_t)hh * n * ehs);
+                    std::copy(kk + hh * ehs, kk + (hh + 1) * ehs, kc.begin() + ((size_t)hh * n + n0) * ehs);
+                    std::copy(vv + hh * ehs, vv + (hh + 1) * ehs, vc.begin() + ((size_t)hh * n + n0) * ehs);
+                }
+                for (int hh = 0; hh < enh; ++hh)
+                    attend(&eq[(size_t)r * d + hh * ehs], kc.data() + (size_t)hh * n * ehs, vc.data() + (size_t)hh * n * ehs, n, ehs, scale,
+                           &o[(size_t)r * d + hh * ehs]);
+                // the oldest-first cap (state.rs:526-538)
+                int keep = n;
+                if (cfg.eng_cap > 0 && n > cfg.eng_cap) keep = cfg.eng_cap;
+                nw[r].ek.resize((size_t)enh * keep * ehs);
+                nw[r].evv.resize((size_t)enh * keep * ehs);
+                for (int hh = 0; hh < enh; ++hh) {
+                    std::copy(kc.begin() + ((size_t)hh * n + (n - keep)) * ehs, kc.begin() + (size_t)(hh + 1) * n * ehs,
+                              nw[r].ek.begin() + (size_t)hh * keep * ehs);
+                    std::copy(vc.begin() + ((size_t)hh * n + (n - keep)) * ehs, vc.begin() + (size_t)(hh + 1) * n * ehs,
+                              nw[r].evv.begin() + (size_t)hh * keep * ehs);
+                }
+                nw[r].eng_n = keep;
+            }
+            eng_written = true;
+            T("eng_o", i, o.data(), d);
+            q8_matmul(b.ewo, o.data(), R, tmp.data());
+            add_into(x.data(), tmp.data(), R * d);
+            T("x_eng", i, x.data(), d);
+        }
+
+        // ---- the sparse MLP (fstep/arch.rs:976-999)
+#pragma omp parallel for num_threads(nt) schedule(static)
+        for (int r = 0; r < R; ++r) rmsnorm(&x[(size_t)r * d], b.mlp_norm.data(), d, &h[(size_t)r * d]);
+        T("h_mlp", i, h.data(), d);
+        std::vector<float> u((size_t)R * H), a((size_t)R * H);
+        q8_matmul(b.w1, h.data(), R, u.data());
+        T("u", i, u.data(), H);
+#pragma omp parallel for num_threads(nt) schedule(static)
+        for (int r = 0; r < R; ++r) kwta(&u[(size_t)r * H], H, cfg.kwta_k, cfg.relu2 != 0, &a[(size_t)r * H]);
+        T("a", i, a.data(), H);
+        q8_matmul(b.w2, a.data(), R, tmp.data());
+        add_into(x.data(), tmp.data(), R * d);
+
+        // ---- the dense residual mix (fstep/arch.rs:1014-1024)
+        if (cfg.dense) {
+            streams.push_back(x);
+            std::vector<float> mix = x;
+            for (size_t j = 0; j < streams.size(); ++j)
+                for (size_t c = 0; c < (size_t)R * d; ++c) mix[c] = mix[c] + streams[j][c] * b.dense[j];
+            x = mix;
+        }
+        T("x_out", i, x.data(), d);
+    }
+#pragma omp parallel for num_threads(nt) schedule(static)
+    for (int r = 0; r < R; ++r) rmsnorm(&x[(size_t)r * d], m->final_norm.data(), d, &h[(size_t)r * d]);
+    T("x_final", -1, h.data(), d);
+    if (logit_stride == (size_t)cfg.vocab) {
+        q8_matmul(m->head, h.data(), R, logits);
+    } else {
+        std::vector<float> lg((size_t)R * cfg.vocab);
+        q8_matmul(m->head, h.data(), R, lg.data());
+        for (int r = 0; r < R; ++r) std::copy(lg.begin() + (size_t)r * cfg.vocab, lg.begin() + (size_t)(r + 1) * cfg.vocab, logits + r * logit_stride);
+    }
+
+    // everything computed: the states move on (fstep/arch.rs:1059-1069); a refused row keeps its state
+    int rc = 0;
+    for (int r = 0; r < R; ++r) {
+        if (bad[r]) {
+            rc = 1;
+            continue;
+        }
+        RowState& st = *rows[r];
+        st.v = std::move(nw[r].v); st.s = std::move(nw[r].s); st.a = std::move(nw[r].a);
+        st.f = std::move(nw[r].f); st.ms = std::move(nw[r].ms);
+        if (eng_written) {
+            st.ek = std::move(nw[r].ek);
+            st.evv = std::move(nw[r].evv);
+            st.eng_n = nw[r].eng_n;
+        }
+        st.seen += 1;
+    }
+    return rc;
+}
+
+bool parse_state_name(const orc_state* s, int row, const std::string& name, const std::vector<float>** out) {
+    const RowState& r = s->rows[row];
+    if (name == "eng.k") { *out = &r.ek; return true; }
+    if (name == "eng.v") { *out = &r.evv; return true; }
+    const size_t d1 = name.find('.'), d2 = name.rfind('.');
+    if (d1 == std::string::npos || d2 == d1) return false;
+    const std::string kind = name.substr(0, d1), what = name.substr(d2 + 1);
+    const int i = std::atoi(name.substr(d1 + 1, d2 - d1 - 1).c_str());
+    if (i < 0 || i >= s->m->cfg.n_blocks) return false;
+    if (kind == "lif") {
+        if (what == "v") { *out = &r.v[i]; return true; }
+        if (what == "s") { *out = &r.s[i]; return true; }
+        if (what == "a") { *out = &r.a[i]; return true; }
+    } else if (kind == "mem") {
+        if (what == "f") { *out = &r.f[i]; return true; }
+        if (what == "s") { *out = &r.ms[i]; return true; }
+    }
+    return false;
+}
+
+}  // namespace
+
+// ================================================================================================ C API
+extern "C" {
+
+void orc_set_math(orc_fn1 e, orc_fn1 l, orc_fn1 r) {
+    if (e) g_exp = e;
+    if (l) g_log = l;
+    if (r) g_rsqrt = r;
+}
+void orc_reset_math(void) { g_exp = libm_exp; g_log = libm_log; g_rsqrt = libm_rsqrt; }
+void orc_set_threads(int n) { g_threads = n < 1 ? 1 : n; }
+void orc_set_simd(int on) { g_simd = on; }
+void orc_set_event_max(double v) { g_event_max = v; }
+
+void orc_quantize_int8(const float* w, int rows, int cols, int8_t* q, float* scale) { quantize_int8(w, rows, cols, q, scale); }
+
+void orc_q8_matmul(const float* x, int m, const int8_t* q, const float* scale, int din, int dout, float* y) {
+    QW w;
+    w.from_q(q, scale, din, dout);
+    q8_matmul(w, x, m, y);
+}
+int orc_last_event_rows(void) { return g_last_event_rows; }
+void orc_rmsnorm(const float* x, const float* gain, int n, float* y) { rmsnorm(x, gain, n, y); }
+void orc_l2_heads(float* x, int n, int hs) { l2_heads(x, n, hs); }
+void orc_head_norm(float* y, int n, int hs) { head_norm(y, n, hs); }
+float orc_sigmoid(float x) { return sigmoid(x); }
+float orc_log_sigmoid(float x) { return log_sigmoid(x); }
+void orc_gemv(const float* x, int k, const float* w, int n, float* out) { gemv(x, k, w, n, out); }
+void orc_lif(const float* cur, const float* beta, const float* theta, const float* rho, const float* gain, int spikes, float slope,
+             const float* v0, const float* s0, const float* a0, int d, float* s1, float* v1, float* a1) {
+    lif(cur, beta, theta, rho, gain, spikes, slope, v0, s0, a0, d, s1, v1, a1);
+}
+float orc_kth_largest(const float* u, int n, int k) { return kth_largest(u, n, k); }
+void orc_kwta(const float* u, int n, int k, int relu2, float* a) { kwta(u, n, k, relu2 != 0, a); }
+void orc_attend(const float* q, const float* kc, const float* vc, int n, int hs, float scale, float* out) { attend(q, kc, vc, n, hs, scale, out); }
+void orc_head_rows(int hs, const float* e, const float* v, const float* w, const float* ah, const float* qg, const float* ex, float qw, float qa,
+                   float ke, float tinv, float mom, const float* qs, const float* p2, const float* f0, const float* s0, float* y, float* f1,
+                   float* s1) {
+    head_rows(hs, e, v, w, ah, qg, ex, qw, qa, ke, tinv, mom > 0.0f, mom, qs, p2, f0, s0, y, f1, s1);
+}
+void orc_delta_plain(int hs, const float* f0, const float* k, const float* v, const float* q, float al, float b, float* f1, float* y) {
+    delta_plain(hs, f0, k, v, q, al, b, f1, y);
+}
+float orc_bf16_round(float x) { return bf16_round(x); }
+
+orc_model* orc_model_new(const orc_config* cfg) {
+    if (!cfg || cfg->d <= 0 || cfg->head_size <= 0 || cfg->d % cfg->head_size != 0) return nullptr;
+    if (cfg->eng_block >= 0 && (cfg->eng_head_size <= 0 || cfg->d % cfg->eng_head_size != 0)) return nullptr;
+    orc_model* m = new orc_model();
+    m->cfg = *cfg;
+    m->blocks.resize(cfg->n_blocks);
+    return m;
+}
+void orc_model_free(orc_model* m) { delete m; }
+
+int orc_model_set_f32(orc_model* m, const char* name, const float* data, int64_t n) {
+    int64_t want = 0;
+    std::vector<float>* slot = f32_slot(m, name, &want);
+    if (!slot || want != n) return -1;
+    slot->assign(data, data + n);
+    return 0;
+}
+int orc_model_set_q8(orc_model* m, const char* name, const int8_t* q, const float* scale, int din, int dout) {
+    int wi = 0, wo = 0;
+    QW* slot = q8_slot(m, name, &wi, &wo);
+    if (!slot || wi != din || wo != dout) return -1;
+    slot->from_q(q, scale, din, dout);
+    return 0;
+}
+int orc_model_set_q8_from_f32(orc_model* m, const char* name, const float* w, int din, int dout) {
+    std::vector<int8_t> q((size_t)din * dout);
+    std::vector<float> sc(dout);
+    quantize_int8(w, din, dout, q.data(), sc.data());
+    return orc_model_set_q8(m, name, q.data(), sc.data(), din, dout);
+}
+int orc_model_check(orc_model* m, char* missing, int cap) {
+    const orc_config& c = m->cfg;
+    auto fail = [&](const std::string& n) {
+        if (missing && cap > 0) std::snprintf(missing, cap, "%s", n.c_str());
+        return -1;
+    };
+    if (m->tok_emb.empty()) return fail("tok_emb");
+    if (m->final_norm.empty()) return fail("final.norm");
+    if (!m->head.ok()) return fail("head");
+    for (int i = 0; i < c.n_blocks; ++i) {
+        const Block& b = m->blocks[i];
+        const std::string p = "b" + std::to_string(i) + ".";
+        struct F { const char* n; const std::vector<float>* v; bool need; };
+        const F fs[] = {{"mem.norm", &b.mem_norm, true}, {"mem.beta", &b.beta_param, true}, {"mem.theta", &b.theta, c.theta != 0},
+                        {"mem.arho", &b.arho, c.alif != 0}, {"mem.again", &b.again, c.alif != 0}, {"hebb.norm", &b.hebb_norm, true},
+                        {"hebb.wa", &b.wa, true}, {"hebb.wb", &b.wb, true}, {"hebb.ba", &b.ba, true}, {"hebb.bb", &b.bb, true},
+                        {"hebb.wa1", &b.wa1, true}, {"hebb.wa2", &b.wa2, true}, {"hebb.wb1", &b.wb1, true}, {"hebb.wb2", &b.wb2, true},
+                        {"hebb.off", &b.off, true}, {"hebb.vres", &b.vres, c.value_residual && i > 0}, {"eng.norm", &b.eng_norm, i == c.eng_block},
+                        {"mlp.norm", &b.mlp_norm, true}, {"dense", &b.dense, c.dense != 0}};
+        for (const F& f : fs)
+            if (f.need && f.v->empty()) return fail(p + f.n);
+        struct Q { const char* n; const QW* q; bool need; };
+        const Q qs[] = {{"mem.win", &b.win, true}, {"mem.wout", &b.wout, true}, {"hebb.wq", &b.wq, true}, {"hebb.wk", &b.wk, true},
+                        {"hebb.wv", &b.wv, true}, {"hebb.we", &b.we, true}, {"hebb.wg", &b.wg, c.out_gate != 0}, {"hebb.wo", &b.wo, true},
+                        {"eng.wq", &b.ewq, i == c.eng_block}, {"eng.wk", &b.ewk, i == c.eng_block}, {"eng.wv", &b.ewv, i == c.eng_block},
+                        {"eng.wo", &b.ewo, i == c.eng_block}, {"mlp.w1", &b.w1, true}, {"mlp.w2", &b.w2, true}};
+        for (const Q& q : qs)
+            if (q.need && !q.q->ok()) return fail(p + q.n);
+    }
+    derive(m);
+    return 0;
+}
+
+orc_state* orc_state_new(const orc_model* m, int rows) {
+    orc_state* s = new orc_state();
+    s->m = m;
+    s->rows.resize(rows);
+    const orc_config& c = m->cfg;
+    const size_t fl = (size_t)m->nh() * c.head_size * c.head_size;
+    for (RowState& r : s->rows) {
+        r.v.assign(c.n_blocks, std::vector<float>(c.d, 0.f));
+        r.s.assign(c.n_blocks, std::vector<float>(c.d, 0.f));
+        r.a.assign(c.n_blocks, std::vector<float>(c.alif ? c.d : 0, 0.f));
+        r.f.assign(c.n_blocks, std::vector<float>(fl, 0.f));
+        r.ms.assign(c.n_blocks, std::vector<float>(c.mem_momentum > 0.f ? fl : 0, 0.f));
+    }
+    return s;
+}
+void orc_state_free(orc_state* s) { delete s; }
+int orc_state_rows(const orc_state* s) { return (int)s->rows.size(); }
+orc_state* orc_state_select(const orc_state* s, const int32_t* idx, int n) {
+    orc_state* o = new orc_state();
+    o->m = s->m;
+    for (int i = 0; i < n; ++i) {
+        if (idx[i] < 0 || idx[i] >= (int)s->rows.size()) {
+            delete o;
+            return nullptr;
+        }
+        o->rows.push_back(s->rows[idx[i]]);
+    }
+    return o;
+}
+int64_t orc_state_len(const orc_state* s, int row, const char* name) {
+    const std::vector<float>* v = nullptr;
+    if (row < 0 || row >= (int)s->rows.size() || !parse_state_name(s, row, name, &v)) return -1;
+    return (int64_t)v->size();
+}
+int orc_state_get(const orc_state* s, int row, const char* name, float* out) {
+    const std::vector<float>* v = nullptr;
+    if (row < 0 || row >= (int)s->rows.size() || !parse_state_name(s, row, name, &v)) return -1;
+    std::copy(v->begin(), v->end(), out);
+    return 0;
+}
+int orc_state_put(orc_state* s, int row, const char* name, const float* in, int64_t n) {
+    const std::vector<float>* v = nullptr;
+    if (row < 0 || row >= (int)s->rows.size() || !parse_state_name(s, row, name, &v)) return -1;
+    std::vector<float>* w = const_cast<std::vector<float>*>(v);
+    const std::string nm = name;
+    if (nm == "eng.k" || nm == "eng.v") {
+        const int per = s->m->enh() * s->m->cfg.eng_head_size;
+        if (n % per != 0) return -1;
+        w->assign(in, in + n);
+        s->rows[row].eng_n = (int)(n / per);
+        return 0;
+    }
+    if ((int64_t)w->size() != n) return -1;
+    std::copy(in, in + n, w->begin());
+    return 0;
+}
+int64_t orc_state_seen(const orc_state* s, int row) { return s->rows[row].seen; }
+
+int orc_step(const orc_model* m, orc_state* s, const uint32_t* tok, float* logits) {
+    derive(m);
+    const int rows = (int)s->rows.size();
+    std::vector<RowState*> rp(rows);
+    for (int r = 0; r < rows; ++r) rp[r] = &s->rows[r];
+    return step_rows(m, rp.data(), rows, tok, logits, m->cfg.vocab, g_trace.on);
+}
+
+int orc_forward(const orc_model* m, orc_state* s, const uint32_t* ids, int t, int last_only, float* logits) {
+    derive(m);
+    const int rows = (int)s->rows.size(), V = m->cfg.vocab;
+    std::vector<RowState*> rp(rows);
+    for (int r = 0; r < rows; ++r) rp[r] = &s->rows[r];
+    std::vector<float> scratch(last_only ? (size_t)rows * V : 0);
+    std::vector<uint32_t> tk(rows);
+    int rc = 0;
+    for (int j = 0; j < t; ++j) {
+        for (int r = 0; r < rows; ++r) tk[r] = ids[(size_t)r * t + j];
+        int one;
+        if (last_only)
+            one = step_rows(m, rp.data(), rows, tk.data(), j == t - 1 ? logits : scratch.data(), V, false);
+        else
+            one = step_rows(m, rp.data(), rows, tk.data(), logits + (size_t)j * V, (size_t)t * V, false);
+        if (one < 0) return one;
+        rc = std::max(rc, one);
+    }
+    return rc;
+}
+
+void orc_trace_enable(int on) {
+    g_trace.on = on != 0;
+    if (!on) g_trace.t.clear();
+}
+int64_t orc_trace_len(const char* name, int block) {
+    auto it = g_trace.t.find({name, block});
+    return it == g_trace.t.end() ? -1 : (int64_t)it->second.size();
+}
+int orc_trace_get(const char* name, int block, float* out) {
+    auto it = g_trace.t.find({name, block});
+    if (it == g_trace.t.end()) return -1;
+    std::copy(it->second.begin(), it->second.end(), out);
+    return 0;
+}
+
+}  // extern "C"
