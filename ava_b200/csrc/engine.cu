@@ -1,0 +1,1029 @@
+// Host side of the B200 engine for Ava's per-token block step: the model's weights and the carried state in device
+// memory, the launch sequence of one step, and the C ABI of include/ava_engine.h.
+//
+// The step follows the reference's fused one-token step (design-tests/nn/gpu/src/model/fstep/arch.rs:525-1073) for
+// every row of a state at once; the rows are independent (src/state.rs:13-15).  Unlike the reference, which computes
+// everything and commits at the end (arch.rs:1059-1069), the state is updated in place as the step goes: a step that
+// reports a non-finite gate or key (AVA_ERR_NONFINITE) has already moved the state.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/ava_engine.h"
+#include "ava_math.h"
+#include "kernels.cuh"
+
+namespace {
+
+using namespace ava;
+
+thread_local std::string g_create_error;
+
+// ------------------------------------------------------------------------------------------------ device memory
+struct Dev {
+    void* p = nullptr;
+    size_t bytes = 0;
+    Dev() = default;
+    Dev(const Dev&) = delete;
+    Dev& operator=(const Dev&) = delete;
+    ~Dev() { release(); }
+    void release() {
+        if (p) cudaFree(p);
+        p = nullptr;
+        bytes = 0;
+    }
+    cudaError_t alloc(size_t n) {
+        release();
+        if (n == 0) return cudaSuccess;
+        const cudaError_t e = cudaMalloc(&p, n);
+        if (e == cudaSuccess) bytes = n;
+        return e;
+    }
+    template <typename T>
+    T* as() const { return reinterpret_cast<T*>(p); }
+};
+
+struct QMat {
+    int din = 0, dout = 0;
+    Dev q, scale;
+    const int8_t* qp() const { return q.as<int8_t>(); }
+    const float* sp() const { return scale.as<float>(); }
+};
+
+struct HostQ {
+    int din = 0, dout = 0;
+    std::vector<int8_t> q;
+    std::vector<float> scale;
+};
+
+struct BlockDev {
+    Dev mem_norm, beta, theta, rho, again, hebb_norm, wa, wb, ba, bb, wa1, wa2, wb1, wb2, off, vres, eng_norm, mlp_norm, dense;
+    QMat win, wout, proj, wo, eqkv, ewo, w1, w2;
+};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// the fast weights [rows_total, hs] f32 as a 2-D tiled tensor map with boxes of [cw columns, rb rows]
+bool make_state_tmap(CUtensorMap* map, void* base, uint64_t rows_total, int hs, int cw, int rb) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)hs, (cuuint64_t)rows_total};
+    const cuuint64_t strides[1] = {(cuuint64_t)hs * sizeof(float)};
+    const cuuint32_t box[2] = {(cuuint32_t)cw, (cuuint32_t)rb};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// nn/parts/src/quant.rs:18-31
+void quantize_int8(const float* w, int rows, int cols, int8_t* q, float* scale) {
+    for (int c = 0; c < cols; ++c) scale[c] = 0.f;
+    for (int r = 0; r < rows; ++r)
+        for (int c = 0; c < cols; ++c) scale[c] = std::max(scale[c], std::fabs(w[(size_t)r * cols + c]));
+    for (int c = 0; c < cols; ++c) scale[c] = scale[c] > 0.f ? scale[c] / 127.0f : 1.0f;
+    for (size_t i = 0; i < (size_t)rows * cols; ++i) {
+        float v = std::round(w[i] / scale[i % cols]);
+        q[i] = (int8_t)std::min(std::max(v, -127.0f), 127.0f);
+    }
+}
+
+}  // namespace
+
+// ================================================================================================ engine
+struct ava_engine {
+    ava_config cfg{};
+    int device = 0;
+    int sm_count = 148;
+    cudaStream_t stream = nullptr;
+    bool finalized = false;
+    mutable std::string err;
+    std::string blocker;
+    int64_t launches = 0;
+
+    std::map<std::string, std::vector<float>> host_f32;
+    std::map<std::string, HostQ> host_q8;
+
+    Dev tok_emb, final_norm;
+    QMat head;
+    std::vector<std::unique_ptr<BlockDev>> blocks;
+    int cw = 0, rb = 0;  // fast-weight slice width and rows per TMA box
+
+    // work buffers for `ws_rows` rows
+    int ws_rows = 0;
+    Dev x, h, proj, ve, vv, vw, vah, vqg, vex, qw, qa, yraw, y, eqkv, eo, u, act, streams, v_first, logits, tok, next, status;
+    uint32_t* status_host = nullptr;  // pinned
+
+    bool keep = false;
+    std::map<std::pair<std::string, int>, std::unique_ptr<Dev>> debug;
+    std::map<std::string, int64_t> debug_width;
+    int debug_rows = 0;
+
+    int nh() const { return cfg.d / cfg.head_size; }
+    int proj_w() const { return (cfg.out_gate ? 5 : 4) * cfg.d; }
+
+    int fail(int code, const char* fmt, ...) const {
+        char buf[512];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, sizeof buf, fmt, ap);
+        va_end(ap);
+        err = buf;
+        return code;
+    }
+    int cuda_fail(cudaError_t e, const char* what) const { return fail(AVA_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e)); }
+};
+
+struct ava_state {
+    ava_engine* e = nullptr;
+    int rows = 0;
+    int ring = 0;   // engram slots per head
+    int keep = 0;   // tokens kept after a read
+    Dev lif_v, lif_s, lif_a;  // [L][rows][d]
+    Dev mem_f;                // [L][rows][nh][hs][hs]
+    Dev eng_k, eng_v;         // [rows][enh][ring][ehs]
+    Dev eng_n, eng_start;     // [rows] i32
+    std::vector<int32_t> n_host, start_host;
+    std::vector<int64_t> seen;
+    CUtensorMap tmap{};
+    size_t kv_elem() const { return e->cfg.eng_store_bf16 ? 2 : 4; }
+};
+
+namespace {
+
+#define CK(call)                                                   \
+    do {                                                           \
+        const cudaError_t e__ = (call);                            \
+        if (e__ != cudaSuccess) return e->cuda_fail(e__, #call);   \
+    } while (0)
+
+bool split_block_name(const std::string& name, int n_blocks, int* block, std::string* rest) {
+    if (name.size() < 3 || name[0] != 'b') return false;
+    const size_t dot = name.find('.');
+    if (dot == std::string::npos || dot < 2) return false;
+    for (size_t i = 1; i < dot; ++i)
+        if (name[i] < '0' || name[i] > '9') return false;
+    *block = std::atoi(name.substr(1, dot - 1).c_str());
+    *rest = name.substr(dot + 1);
+    return *block >= 0 && *block < n_blocks;
+}
+
+// expected float count of an f32 tensor, or -1 for an unknown name
+int64_t f32_len(const ava_config& c, const std::string& name) {
+    const int64_t d = c.d, nh = c.d / c.head_size, r = c.gate_rank;
+    if (name == "tok_emb") return (int64_t)c.vocab * d;
+    if (name == "final.norm") return d;
+    int b;
+    std::string rest;
+    if (!split_block_name(name, c.n_blocks, &b, &rest)) return -1;
+    static const char* vec_d[] = {"mem.norm", "mem.beta", "mem.theta", "mem.arho", "mem.again", "hebb.norm", "hebb.off", "eng.norm", "mlp.norm"};
+    for (const char* n : vec_d)
+        if (rest == n) return d;
+    if (rest == "hebb.wa" || rest == "hebb.wb") return d * nh;
+    if (rest == "hebb.ba" || rest == "hebb.bb") return nh;
+    if (rest == "hebb.wa1" || rest == "hebb.wb1" || rest == "hebb.wa2" || rest == "hebb.wb2") return d * r;
+    if (rest == "hebb.vres") return 2;
+    if (rest == "dense") return b + 2;
+    return -1;
+}
+
+bool q8_dims(const ava_config& c, const std::string& name, int* din, int* dout) {
+    if (name == "head") {
+        *din = c.d;
+        *dout = c.vocab;
+        return true;
+    }
+    int b;
+    std::string rest;
+    if (!split_block_name(name, c.n_blocks, &b, &rest)) return false;
+    static const char* sq[] = {"mem.win", "mem.wout", "hebb.wq", "hebb.wk", "hebb.wv", "hebb.we", "hebb.wg", "hebb.wo", "eng.wq", "eng.wk", "eng.wv", "eng.wo"};
+    for (const char* n : sq)
+        if (rest == n) {
+            *din = *dout = c.d;
+            return true;
+        }
+    if (rest == "mlp.w1") {
+        *din = c.d;
+        *dout = c.hidden;
+        return true;
+    }
+    if (rest == "mlp.w2") {
+        *din = c.hidden;
+        *dout = c.d;
+        return true;
+    }
+    return false;
+}
+
+int upload(ava_engine* e, Dev& dst, const void* src, size_t bytes) {
+    CK(dst.alloc(bytes));
+    CK(cudaMemcpy(dst.p, src, bytes, cudaMemcpyHostToDevice));
+    return AVA_OK;
+}
+
+int upload_f32(ava_engine* e, Dev& dst, const std::string& name, bool need) {
+    auto it = e->host_f32.find(name);
+    if (it == e->host_f32.end()) return need ? e->fail(AVA_ERR_MISSING, "missing tensor %s", name.c_str()) : AVA_OK;
+    return upload(e, dst, it->second.data(), it->second.size() * sizeof(float));
+}
+
+// the int8 copies of `names` side by side [din, sum of douts] (src/int8.rs:86-102)
+int upload_q8(ava_engine* e, QMat& dst, const std::vector<std::string>& names) {
+    int din = 0, dout = 0;
+    for (const std::string& n : names) {
+        auto it = e->host_q8.find(n);
+        if (it == e->host_q8.end()) return e->fail(AVA_ERR_MISSING, "missing int8 matrix %s", n.c_str());
+        if (din && it->second.din != din) return e->fail(AVA_ERR_ARG, "%s: input width differs from its neighbours", n.c_str());
+        din = it->second.din;
+        dout += it->second.dout;
+    }
+    std::vector<int8_t> q((size_t)din * dout);
+    std::vector<float> sc(dout);
+    int c0 = 0;
+    for (const std::string& n : names) {
+        const HostQ& hq = e->host_q8[n];
+        for (int j = 0; j < din; ++j) std::memcpy(&q[(size_t)j * dout + c0], &hq.q[(size_t)j * hq.dout], hq.dout);
+        std::copy(hq.scale.begin(), hq.scale.end(), sc.begin() + c0);
+        c0 += hq.dout;
+    }
+    dst.din = din;
+    dst.dout = dout;
+    int rc = upload(e, dst.q, q.data(), q.size());
+    if (rc) return rc;
+    return upload(e, dst.scale, sc.data(), sc.size() * sizeof(float));
+}
+
+const char* find_blocker(const ava_config& c, int* cw, int* rb) {
+    if (c.d <= 0 || c.n_blocks <= 0 || c.vocab <= 0 || c.hidden <= 0 || c.head_size <= 0 || c.d % c.head_size) return "bad shape";
+    if (c.d % 16 || c.hidden % 16) return "widths must be multiples of 16 (the product kernel's k step)";
+    if (c.vocab % 4) return "vocabulary must be a multiple of 4";
+    if (c.mem_momentum > 0.0f) return "--mem-momentum: the second state matrix is not in the engine yet";
+    if (c.gate_rank < 1) return "gate rank must be at least 1";
+    if (c.eng_block >= 0 && (c.eng_head_size <= 0 || c.d % c.eng_head_size)) return "bad engram head size";
+    if (c.spikes < 0 || c.spikes > 2) return "unknown spike kind";
+    if (c.head_size % 16 || !mem_heads_tiling(c.head_size, cw, rb)) return "memory head size not covered (multiples of 16; up to 256 or a multiple of 256 up to 2048)";
+    return nullptr;
+}
+
+int ensure_workspace(ava_engine* e, int rows) {
+    if (rows <= e->ws_rows) return AVA_OK;
+    const ava_config& c = e->cfg;
+    const size_t M = rows, d = c.d, f = sizeof(float);
+    CK(e->x.alloc(M * d * f));
+    CK(e->h.alloc(M * d * f));
+    CK(e->proj.alloc(M * e->proj_w() * f));
+    for (Dev* b : {&e->ve, &e->vv, &e->vw, &e->vah, &e->vqg, &e->vex, &e->yraw, &e->y, &e->eo, &e->v_first}) CK(b->alloc(M * d * f));
+    CK(e->qw.alloc(M * e->nh() * f));
+    CK(e->qa.alloc(M * e->nh() * f));
+    CK(e->eqkv.alloc(M * 3 * d * f));
+    CK(e->u.alloc(M * c.hidden * f));
+    CK(e->act.alloc(M * c.hidden * f));
+    CK(e->streams.alloc(c.dense ? (size_t)(c.n_blocks + 1) * M * d * f : 0));
+    CK(e->logits.alloc(M * c.vocab * f));
+    CK(e->tok.alloc(M * sizeof(uint32_t)));
+    CK(e->next.alloc(M * sizeof(uint32_t)));
+    e->ws_rows = rows;
+    return AVA_OK;
+}
+
+void dbg(ava_engine* e, const char* name, int block, const float* src, int rows, int64_t width) {
+    if (!e->keep) return;
+    auto& slot = e->debug[{name, block}];
+    if (!slot) slot.reset(new Dev());
+    const size_t bytes = (size_t)rows * width * sizeof(float);
+    if (slot->bytes != bytes) slot->alloc(bytes);
+    cudaMemcpyAsync(slot->p, src, bytes, cudaMemcpyDeviceToDevice, e->stream);
+    e->debug_width[name] = width;
+    e->debug_rows = rows;
+}
+
+int gemm(ava_engine* e, const float* A, int lda, const QMat& w, float* C, int ldc, int M, GemmEpilogue epi, const LifParams* lif = nullptr) {
+    GemmArgs g{};
+    g.A = A;
+    g.lda = lda;
+    g.W = w.qp();
+    g.ldw = w.dout;
+    g.scale = w.sp();
+    g.C = C;
+    g.ldc = ldc;
+    g.M = M;
+    g.N = w.dout;
+    g.K = w.din;
+    if (lif) g.lif = *lif;
+    launch_q8_gemm(e->stream, g, epi, e->sm_count);
+    e->launches++;
+    return AVA_OK;
+}
+
+// One token per row, everything queued on the engine's stream.  tok/logits/next are device pointers.
+int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits, uint32_t* next, bool want_logits) {
+    const ava_config& c = e->cfg;
+    const int M = s->rows, d = c.d, L = c.n_blocks, nh = e->nh(), hs = c.head_size, H = c.hidden;
+    cudaStream_t st = e->stream;
+    float* x = e->x.as<float>();
+    float* h = e->h.as<float>();
+    float* streams = c.dense ? e->streams.as<float>() : nullptr;
+    const size_t Md = (size_t)M * d;
+
+    // the engram's capacity is checked on the host's mirror of the counts before anything moves
+    int n_max = 0;
+    if (c.eng_block >= 0) {
+        for (int r = 0; r < M; ++r) {
+            if (s->n_host[r] >= s->ring) return e->fail(AVA_ERR_CAPACITY, "engram store of row %d is full (%d tokens)", r, s->ring);
+            n_max = std::max(n_max, s->n_host[r] + 1);
+        }
+    }
+
+    launch_embed(st, e->tok_emb.as<float>(), tok, M, d, c.vocab, x, streams, e->status.as<uint32_t>());
+    e->launches++;
+    dbg(e, "x_in", -1, x, M, d);
+    for (int i = 0; i < L; ++i) {
+        BlockDev& b = *e->blocks[i];
+        // ---- the spiking memory
+        launch_rmsnorm(st, x, b.mem_norm.as<float>(), M, d, h);
+        e->launches++;
+        dbg(e, "h_lif", i, h, M, d);
+        LifParams lp{};
+        lp.beta = b.beta.as<float>();
+        lp.theta = c.theta ? b.theta.as<float>() : nullptr;
+        lp.rho = c.alif ? b.rho.as<float>() : nullptr;
+        lp.gain = c.alif ? b.again.as<float>() : nullptr;
+        lp.v = s->lif_v.as<float>() + (size_t)i * Md;
+        lp.s = s->lif_s.as<float>() + (size_t)i * Md;
+        lp.a = c.alif ? s->lif_a.as<float>() + (size_t)i * Md : nullptr;
+        lp.spikes = c.spikes;
+        lp.lif_scale = c.lif_scale;
+        gemm(e, h, d, b.win, nullptr, 0, M, EPI_LIF, &lp);
+        dbg(e, "spikes", i, lp.s, M, d);
+        gemm(e, lp.s, d, b.wout, x, d, M, EPI_ADD);
+        dbg(e, "x_lif", i, x, M, d);
+
+        // ---- the fast-weight memory
+        launch_rmsnorm(st, x, b.hebb_norm.as<float>(), M, d, h);
+        e->launches++;
+        dbg(e, "h_mem", i, h, M, d);
+        const int pw = e->proj_w();
+        gemm(e, h, d, b.proj, e->proj.as<float>(), pw, M, EPI_STORE);
+        dbg(e, "qkveg", i, e->proj.as<float>(), M, pw);
+        MemPrepArgs mp{};
+        mp.h = h;
+        mp.proj = e->proj.as<float>();
+        mp.ldp = pw;
+        mp.wa = b.wa.as<float>(); mp.wb = b.wb.as<float>(); mp.ba = b.ba.as<float>(); mp.bb = b.bb.as<float>();
+        mp.wa1 = b.wa1.as<float>(); mp.wa2 = b.wa2.as<float>(); mp.wb1 = b.wb1.as<float>(); mp.wb2 = b.wb2.as<float>();
+        mp.off = b.off.as<float>();
+        mp.vres = (c.value_residual && i > 0 && b.vres.p) ? b.vres.as<float>() : nullptr;
+        mp.v_first = e->v_first.as<float>();
+        mp.first = c.value_residual && i == 0;
+        mp.M = M; mp.d = d; mp.hs = hs; mp.rank = c.gate_rank;
+        mp.e = e->ve.as<float>(); mp.v = e->vv.as<float>(); mp.w = e->vw.as<float>(); mp.ah = e->vah.as<float>();
+        mp.qg = e->vqg.as<float>(); mp.ex = e->vex.as<float>(); mp.qw = e->qw.as<float>(); mp.qa = e->qa.as<float>();
+        mp.status = e->status.as<uint32_t>();
+        launch_mem_prep(st, mp);
+        e->launches++;
+        dbg(e, "ek", i, mp.e, M, d); dbg(e, "v", i, mp.v, M, d); dbg(e, "w", i, mp.w, M, d); dbg(e, "ah", i, mp.ah, M, d);
+        dbg(e, "qg", i, mp.qg, M, d); dbg(e, "ex", i, mp.ex, M, d); dbg(e, "qw", i, mp.qw, M, nh); dbg(e, "qa", i, mp.qa, M, nh);
+        MemHeadsArgs mh{};
+        mh.tmap = s->tmap;
+        mh.row0 = (int64_t)i * M * nh * hs;
+        mh.M = M; mh.nh = nh; mh.hs = hs; mh.cw = e->cw; mh.rb = e->rb;
+        mh.e = mp.e; mh.v = mp.v; mh.w = mp.w; mh.ah = mp.ah; mh.qg = mp.qg; mh.ex = mp.ex; mh.qw = mp.qw; mh.qa = mp.qa;
+        mh.y = e->yraw.as<float>();
+        mh.status = e->status.as<uint32_t>();
+        launch_mem_heads(st, mh);
+        e->launches++;
+        dbg(e, "y_raw", i, mh.y, M, d);
+        launch_mem_post(st, mh.y, c.out_gate ? e->proj.as<float>() + 4 * d : nullptr, pw, M, d, hs, e->y.as<float>());
+        e->launches++;
+        dbg(e, "y", i, e->y.as<float>(), M, d);
+        gemm(e, e->y.as<float>(), d, b.wo, x, d, M, EPI_ADD);
+        dbg(e, "x_mem", i, x, M, d);
+
+        // ---- the engram
+        if (i == c.eng_block) {
+            launch_rmsnorm(st, x, b.eng_norm.as<float>(), M, d, h);
+            e->launches++;
+            gemm(e, h, d, b.eqkv, e->eqkv.as<float>(), 3 * d, M, EPI_STORE);
+            dbg(e, "eng_qkv", i, e->eqkv.as<float>(), M, 3 * d);
+            EngramArgs ea{};
+            ea.qkv = e->eqkv.as<float>();
+            ea.k = s->eng_k.p; ea.v = s->eng_v.p;
+            ea.n = s->eng_n.as<int32_t>(); ea.start = s->eng_start.as<int32_t>();
+            ea.M = M; ea.d = d; ea.hs = c.eng_head_size; ea.cap = s->ring; ea.keep = s->keep; ea.bf16 = c.eng_store_bf16;
+            ea.o = e->eo.as<float>();
+            ea.status = e->status.as<uint32_t>();
+            if (!launch_engram(st, ea, n_max))
+                return e->fail(AVA_ERR_CAPACITY, "engram read over %d tokens does not fit this kernel's shared memory", n_max);
+            e->launches++;
+            dbg(e, "eng_o", i, ea.o, M, d);
+            gemm(e, ea.o, d, b.ewo, x, d, M, EPI_ADD);
+            dbg(e, "x_eng", i, x, M, d);
+        }
+
+        // ---- the sparse MLP
+        launch_rmsnorm(st, x, b.mlp_norm.as<float>(), M, d, h);
+        e->launches++;
+        gemm(e, h, d, b.w1, e->u.as<float>(), H, M, EPI_STORE);
+        dbg(e, "u", i, e->u.as<float>(), M, H);
+        launch_kwta(st, e->u.as<float>(), M, H, c.kwta_k, c.relu2, e->act.as<float>());
+        e->launches++;
+        dbg(e, "a", i, e->act.as<float>(), M, H);
+        gemm(e, e->act.as<float>(), H, b.w2, x, d, M, EPI_ADD);
+        if (c.dense) {
+            launch_dense_mix(st, x, streams, b.dense.as<float>(), i + 2, (int64_t)Md);
+            e->launches++;
+        }
+        dbg(e, "x_out", i, x, M, d);
+    }
+    if (want_logits || next) {
+        launch_rmsnorm(st, x, e->final_norm.as<float>(), M, d, h);
+        e->launches++;
+        dbg(e, "x_final", -1, h, M, d);
+        float* lg = logits ? logits : e->logits.as<float>();
+        gemm(e, h, d, e->head, lg, c.vocab, M, EPI_STORE);
+        if (next) {
+            launch_argmax(st, lg, M, c.vocab, next);
+            e->launches++;
+        }
+    }
+    // the host's mirror of the engram counts moves as the kernel moves them
+    if (c.eng_block >= 0)
+        for (int r = 0; r < M; ++r) {
+            const int n = s->n_host[r] + 1;
+            if (n > s->keep) {
+                s->start_host[r] = (s->start_host[r] + (n - s->keep)) % s->ring;
+                s->n_host[r] = s->keep;
+            } else {
+                s->n_host[r] = n;
+            }
+        }
+    for (int r = 0; r < M; ++r) s->seen[r] += 1;
+    const cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) return e->cuda_fail(le, "kernel launch");
+    return AVA_OK;
+}
+
+// waits for the stream and turns the device status word into a return code (clearing it)
+int finish(ava_engine* e) {
+    CK(cudaMemcpyAsync(e->status_host, e->status.p, sizeof(uint32_t), cudaMemcpyDeviceToHost, e->stream));
+    CK(cudaMemsetAsync(e->status.p, 0, sizeof(uint32_t), e->stream));
+    CK(cudaStreamSynchronize(e->stream));
+    const uint32_t st = *e->status_host;
+    if (st & ST_WAIT_TIMEOUT) return e->fail(AVA_ERR_CUDA, "a bounded wait on a TMA barrier ran out inside the memory kernel");
+    if (st & ST_BAD_TOKEN) return e->fail(AVA_ERR_ARG, "a token id outside the vocabulary");
+    if (st & ST_ENGRAM_FULL) return e->fail(AVA_ERR_CAPACITY, "the engram store had no room for a token");
+    if (st & ST_NONFINITE) return e->fail(AVA_ERR_NONFINITE, "a gate, key or value of the fast-weight memory was not finite (the state has moved)");
+    return AVA_OK;
+}
+
+int check_pair(ava_engine* e, ava_state* s) {
+    if (!e) return AVA_ERR_ARG;
+    if (!s || s->e != e) return e->fail(AVA_ERR_STATE, "the state belongs to another engine");
+    if (!e->finalized) return e->fail(AVA_ERR_ARG, "engine not finalized");
+    if (!e->blocker.empty()) return AVA_NOT_APPLICABLE;
+    CK(cudaSetDevice(e->device));
+    return ensure_workspace(e, s->rows);
+}
+
+struct StateSlice {
+    Dev* buf = nullptr;
+    size_t off = 0, count = 0;  // elements (floats, or store elements for the engram)
+    bool eng = false;
+};
+
+// where row `row`'s tensor `name` lives; for the engram the count is the tokens held times the row width
+bool locate(const ava_state* s, int row, const std::string& name, StateSlice* out) {
+    const ava_config& c = s->e->cfg;
+    ava_state* ms = const_cast<ava_state*>(s);
+    const size_t d = c.d, M = s->rows;
+    if (name == "eng.k" || name == "eng.v") {
+        if (c.eng_block < 0) return false;
+        out->buf = name == "eng.k" ? &ms->eng_k : &ms->eng_v;
+        out->eng = true;
+        out->count = (size_t)s->n_host[row] * d;
+        return true;
+    }
+    const size_t d1 = name.find('.'), d2 = name.rfind('.');
+    if (d1 == std::string::npos || d2 == d1) return false;
+    const std::string kind = name.substr(0, d1), what = name.substr(d2 + 1);
+    const int i = std::atoi(name.substr(d1 + 1, d2 - d1 - 1).c_str());
+    if (i < 0 || i >= c.n_blocks) return false;
+    if (kind == "lif") {
+        out->buf = what == "v" ? &ms->lif_v : what == "s" ? &ms->lif_s : what == "a" && c.alif ? &ms->lif_a : nullptr;
+        out->off = ((size_t)i * M + row) * d;
+        out->count = d;
+        return out->buf != nullptr;
+    }
+    if (kind == "mem" && what == "f") {
+        const size_t per = (size_t)d * c.head_size;  // nh * hs * hs
+        out->buf = &ms->mem_f;
+        out->off = ((size_t)i * M + row) * per;
+        out->count = per;
+        return true;
+    }
+    return false;
+}
+
+int alloc_state(ava_engine* e, int rows, int ring, int keep, ava_state** out) {
+    const ava_config& c = e->cfg;
+    std::unique_ptr<ava_state> s(new ava_state());
+    s->e = e;
+    s->rows = rows;
+    s->ring = ring;
+    s->keep = keep;
+    const size_t M = rows, d = c.d, L = c.n_blocks, f = sizeof(float);
+    CK(s->lif_v.alloc(L * M * d * f));
+    CK(s->lif_s.alloc(L * M * d * f));
+    if (c.alif) CK(s->lif_a.alloc(L * M * d * f));
+    CK(s->mem_f.alloc(L * M * d * c.head_size * f));
+    if (c.eng_block >= 0) {
+        CK(s->eng_k.alloc(M * d * ring * s->kv_elem()));
+        CK(s->eng_v.alloc(M * d * ring * s->kv_elem()));
+        CK(s->eng_n.alloc(M * sizeof(int32_t)));
+        CK(s->eng_start.alloc(M * sizeof(int32_t)));
+    }
+    s->n_host.assign(rows, 0);
+    s->start_host.assign(rows, 0);
+    s->seen.assign(rows, 0);
+    if (!make_state_tmap(&s->tmap, s->mem_f.p, (uint64_t)L * M * (d / c.head_size) * c.head_size, c.head_size, e->cw, e->rb))
+        return e->fail(AVA_ERR_CUDA, "cuTensorMapEncodeTiled failed for the fast-weight state");
+    *out = s.release();
+    return AVA_OK;
+}
+
+int zero_state(ava_engine* e, ava_state* s) {
+    for (Dev* b : {&s->lif_v, &s->lif_s, &s->lif_a, &s->mem_f, &s->eng_n, &s->eng_start})
+        if (b->p) CK(cudaMemsetAsync(b->p, 0, b->bytes, e->stream));
+    CK(cudaStreamSynchronize(e->stream));
+    return AVA_OK;
+}
+
+// copies row `src_row` of `src` into row `dst_row` of `dst` (same engine, same ring)
+int copy_row(ava_engine* e, const ava_state* src, int src_row, ava_state* dst, int dst_row) {
+    const ava_config& c = e->cfg;
+    const size_t d = c.d, per = d * c.head_size, f = sizeof(float);
+    for (int i = 0; i < c.n_blocks; ++i) {
+        const size_t so = (size_t)i * src->rows + src_row, dn = (size_t)i * dst->rows + dst_row;
+        CK(cudaMemcpyAsync(dst->lif_v.as<float>() + dn * d, src->lif_v.as<float>() + so * d, d * f, cudaMemcpyDeviceToDevice, e->stream));
+        CK(cudaMemcpyAsync(dst->lif_s.as<float>() + dn * d, src->lif_s.as<float>() + so * d, d * f, cudaMemcpyDeviceToDevice, e->stream));
+        if (c.alif)
+            CK(cudaMemcpyAsync(dst->lif_a.as<float>() + dn * d, src->lif_a.as<float>() + so * d, d * f, cudaMemcpyDeviceToDevice, e->stream));
+        CK(cudaMemcpyAsync(dst->mem_f.as<float>() + dn * per, src->mem_f.as<float>() + so * per, per * f, cudaMemcpyDeviceToDevice, e->stream));
+    }
+    if (c.eng_block >= 0) {
+        const size_t rowb = d * src->ring * src->kv_elem();
+        CK(cudaMemcpyAsync((char*)dst->eng_k.p + dst_row * rowb, (char*)src->eng_k.p + src_row * rowb, rowb, cudaMemcpyDeviceToDevice, e->stream));
+        CK(cudaMemcpyAsync((char*)dst->eng_v.p + dst_row * rowb, (char*)src->eng_v.p + src_row * rowb, rowb, cudaMemcpyDeviceToDevice, e->stream));
+        dst->n_host[dst_row] = src->n_host[src_row];
+        dst->start_host[dst_row] = src->start_host[src_row];
+    }
+    dst->seen[dst_row] = src->seen[src_row];
+    return AVA_OK;
+}
+
+int push_counts(ava_engine* e, ava_state* s) {
+    if (e->cfg.eng_block < 0) return AVA_OK;
+    CK(cudaMemcpyAsync(s->eng_n.p, s->n_host.data(), s->rows * sizeof(int32_t), cudaMemcpyHostToDevice, e->stream));
+    CK(cudaMemcpyAsync(s->eng_start.p, s->start_host.data(), s->rows * sizeof(int32_t), cudaMemcpyHostToDevice, e->stream));
+    CK(cudaStreamSynchronize(e->stream));
+    return AVA_OK;
+}
+
+}  // namespace
+
+// ================================================================================================ C ABI
+extern "C" {
+
+int ava_engine_create(const ava_config* cfg, int device, ava_engine** out) {
+    if (!cfg || !out) return AVA_ERR_ARG;
+    int count = 0;
+    cudaError_t ce = cudaGetDeviceCount(&count);
+    if (ce != cudaSuccess || count == 0) {
+        g_create_error = std::string("no CUDA device: ") + cudaGetErrorString(ce) + " (this library has no CPU path)";
+        return AVA_ERR_CUDA;
+    }
+    if (device < 0 || device >= count) {
+        g_create_error = "device index out of range";
+        return AVA_ERR_ARG;
+    }
+    std::unique_ptr<ava_engine> e(new ava_engine());
+    e->cfg = *cfg;
+    e->device = device;
+    cudaSetDevice(device);
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) e->sm_count = prop.multiProcessorCount;
+    if ((ce = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking)) != cudaSuccess ||
+        (ce = cudaMallocHost((void**)&e->status_host, sizeof(uint32_t))) != cudaSuccess || (ce = e->status.alloc(sizeof(uint32_t))) != cudaSuccess ||
+        (ce = cudaMemset(e->status.p, 0, sizeof(uint32_t))) != cudaSuccess) {
+        g_create_error = std::string("engine set-up: ") + cudaGetErrorString(ce);
+        return AVA_ERR_CUDA;
+    }
+    const char* why = find_blocker(e->cfg, &e->cw, &e->rb);
+    if (why) e->blocker = why;
+    *out = e.release();
+    return AVA_OK;
+}
+
+void ava_engine_destroy(ava_engine* e) {
+    if (!e) return;
+    cudaSetDevice(e->device);
+    if (e->stream) {
+        cudaStreamSynchronize(e->stream);
+        cudaStreamDestroy(e->stream);
+    }
+    if (e->status_host) cudaFreeHost(e->status_host);
+    delete e;
+}
+
+const char* ava_last_error(const ava_engine* e) { return e ? e->err.c_str() : g_create_error.c_str(); }
+const char* ava_engine_blocker(const ava_engine* e) { return (e && !e->blocker.empty()) ? e->blocker.c_str() : nullptr; }
+
+int ava_engine_set_f32(ava_engine* e, const char* name, const float* data, int64_t n) {
+    if (!e || !name || !data) return AVA_ERR_ARG;
+    const int64_t want = f32_len(e->cfg, name);
+    if (want < 0) return e->fail(AVA_ERR_ARG, "unknown tensor %s", name);
+    if (want != n) return e->fail(AVA_ERR_ARG, "%s: %lld values, want %lld", name, (long long)n, (long long)want);
+    e->host_f32[name].assign(data, data + n);
+    e->finalized = false;
+    return AVA_OK;
+}
+
+int ava_engine_set_q8(ava_engine* e, const char* name, const int8_t* q, const float* scale, int32_t din, int32_t dout) {
+    if (!e || !name || !q || !scale) return AVA_ERR_ARG;
+    int wi, wo;
+    if (!q8_dims(e->cfg, name, &wi, &wo)) return e->fail(AVA_ERR_ARG, "unknown int8 matrix %s", name);
+    if (wi != din || wo != dout) return e->fail(AVA_ERR_ARG, "%s: [%d, %d], want [%d, %d]", name, din, dout, wi, wo);
+    HostQ& h = e->host_q8[name];
+    h.din = din;
+    h.dout = dout;
+    h.q.assign(q, q + (size_t)din * dout);
+    h.scale.assign(scale, scale + dout);
+    e->finalized = false;
+    return AVA_OK;
+}
+
+int ava_engine_set_q8_from_f32(ava_engine* e, const char* name, const float* w, int32_t din, int32_t dout) {
+    if (!e || !name || !w || din <= 0 || dout <= 0) return AVA_ERR_ARG;
+    std::vector<int8_t> q((size_t)din * dout);
+    std::vector<float> sc(dout);
+    quantize_int8(w, din, dout, q.data(), sc.data());
+    return ava_engine_set_q8(e, name, q.data(), sc.data(), din, dout);
+}
+
+int ava_engine_finalize(ava_engine* e) {
+    if (!e) return AVA_ERR_ARG;
+    if (!e->blocker.empty()) {
+        e->finalized = true;
+        return AVA_NOT_APPLICABLE;
+    }
+    CK(cudaSetDevice(e->device));
+    const ava_config& c = e->cfg;
+    int rc;
+    if ((rc = upload_f32(e, e->tok_emb, "tok_emb", true))) return rc;
+    if ((rc = upload_f32(e, e->final_norm, "final.norm", true))) return rc;
+    if (!e->host_q8.count("head")) {
+        // the tied head: tok_emb^T quantised, one scale per vocabulary row (src/int8.rs:82-84)
+        const std::vector<float>& emb = e->host_f32["tok_emb"];
+        std::vector<float> et((size_t)c.d * c.vocab);
+        for (int v = 0; v < c.vocab; ++v)
+            for (int j = 0; j < c.d; ++j) et[(size_t)j * c.vocab + v] = emb[(size_t)v * c.d + j];
+        if ((rc = ava_engine_set_q8_from_f32(e, "head", et.data(), c.d, c.vocab))) return rc;
+    }
+    if ((rc = upload_q8(e, e->head, {"head"}))) return rc;
+    e->blocks.clear();
+    for (int i = 0; i < c.n_blocks; ++i) {
+        e->blocks.emplace_back(new BlockDev());
+        BlockDev& b = *e->blocks.back();
+        const std::string p = "b" + std::to_string(i) + ".";
+        if ((rc = upload_f32(e, b.mem_norm, p + "mem.norm", true))) return rc;
+        {
+            // leak and adaptation rate are sigmoids of their parameters (src/model/fstep/arch.rs:640,660)
+            auto it = e->host_f32.find(p + "mem.beta");
+            if (it == e->host_f32.end()) return e->fail(AVA_ERR_MISSING, "missing tensor %smem.beta", p.c_str());
+            std::vector<float> beta(it->second.size());
+            for (size_t k = 0; k < beta.size(); ++k) beta[k] = ava::sigmoid(it->second[k]);
+            if ((rc = upload(e, b.beta, beta.data(), beta.size() * sizeof(float)))) return rc;
+            if (c.alif) {
+                auto ir = e->host_f32.find(p + "mem.arho");
+                if (ir == e->host_f32.end()) return e->fail(AVA_ERR_MISSING, "missing tensor %smem.arho", p.c_str());
+                std::vector<float> rho(ir->second.size());
+                for (size_t k = 0; k < rho.size(); ++k) rho[k] = ava::sigmoid(ir->second[k]);
+                if ((rc = upload(e, b.rho, rho.data(), rho.size() * sizeof(float)))) return rc;
+                if ((rc = upload_f32(e, b.again, p + "mem.again", true))) return rc;
+            }
+        }
+        if ((rc = upload_f32(e, b.theta, p + "mem.theta", c.theta != 0))) return rc;
+        if ((rc = upload_f32(e, b.hebb_norm, p + "hebb.norm", true))) return rc;
+        struct F { Dev* d; const char* n; };
+        for (const F& f : {F{&b.wa, "hebb.wa"}, F{&b.wb, "hebb.wb"}, F{&b.ba, "hebb.ba"}, F{&b.bb, "hebb.bb"}, F{&b.wa1, "hebb.wa1"},
+                           F{&b.wa2, "hebb.wa2"}, F{&b.wb1, "hebb.wb1"}, F{&b.wb2, "hebb.wb2"}, F{&b.off, "hebb.off"}, F{&b.mlp_norm, "mlp.norm"}})
+            if ((rc = upload_f32(e, *f.d, p + f.n, true))) return rc;
+        if ((rc = upload_f32(e, b.vres, p + "hebb.vres", c.value_residual && i > 0))) return rc;
+        if ((rc = upload_f32(e, b.dense, p + "dense", c.dense != 0))) return rc;
+        if ((rc = upload_q8(e, b.win, {p + "mem.win"}))) return rc;
+        if ((rc = upload_q8(e, b.wout, {p + "mem.wout"}))) return rc;
+        std::vector<std::string> pj = {p + "hebb.wq", p + "hebb.wk", p + "hebb.wv", p + "hebb.we"};
+        if (c.out_gate) pj.push_back(p + "hebb.wg");
+        if ((rc = upload_q8(e, b.proj, pj))) return rc;
+        if ((rc = upload_q8(e, b.wo, {p + "hebb.wo"}))) return rc;
+        if (i == c.eng_block) {
+            if ((rc = upload_f32(e, b.eng_norm, p + "eng.norm", true))) return rc;
+            if ((rc = upload_q8(e, b.eqkv, {p + "eng.wq", p + "eng.wk", p + "eng.wv"}))) return rc;
+            if ((rc = upload_q8(e, b.ewo, {p + "eng.wo"}))) return rc;
+        }
+        if ((rc = upload_q8(e, b.w1, {p + "mlp.w1"}))) return rc;
+        if ((rc = upload_q8(e, b.w2, {p + "mlp.w2"}))) return rc;
+    }
+    // the host copies are no longer needed
+    e->host_f32.clear();
+    e->host_q8.clear();
+    e->finalized = true;
+    return AVA_OK;
+}
+
+int ava_state_new(ava_engine* e, int32_t rows, int32_t max_ctx, ava_state** out) {
+    if (!e || !out || rows <= 0) return AVA_ERR_ARG;
+    if (!e->finalized) return e->fail(AVA_ERR_ARG, "engine not finalized");
+    if (!e->blocker.empty()) return AVA_NOT_APPLICABLE;
+    CK(cudaSetDevice(e->device));
+    const ava_config& c = e->cfg;
+    // a capped store reads cap + 1 tokens before it drops the oldest (src/model/fstep/arch.rs:962-964)
+    const int ring = c.eng_block < 0 ? 0 : (c.eng_cap > 0 ? c.eng_cap + 1 : std::max(1, max_ctx));
+    const int keep = c.eng_cap > 0 ? c.eng_cap : ring;
+    ava_state* s = nullptr;
+    int rc = alloc_state(e, rows, ring, keep, &s);
+    if (rc) return rc;
+    if ((rc = zero_state(e, s))) {
+        delete s;
+        return rc;
+    }
+    *out = s;
+    return AVA_OK;
+}
+
+void ava_state_destroy(ava_state* s) {
+    if (!s) return;
+    cudaSetDevice(s->e->device);
+    cudaStreamSynchronize(s->e->stream);
+    delete s;
+}
+
+int32_t ava_state_rows(const ava_state* s) { return s ? s->rows : 0; }
+
+int ava_state_select(const ava_state* s, const int32_t* idx, int32_t n, ava_state** out) {
+    if (!s || !idx || !out || n <= 0) return AVA_ERR_ARG;
+    ava_engine* e = s->e;
+    for (int i = 0; i < n; ++i)
+        if (idx[i] < 0 || idx[i] >= s->rows) return e->fail(AVA_ERR_ARG, "select: row %d of %d", idx[i], s->rows);
+    CK(cudaSetDevice(e->device));
+    ava_state* o = nullptr;
+    int rc = alloc_state(e, n, s->ring, s->keep, &o);
+    if (rc) return rc;
+    for (int i = 0; i < n && !rc; ++i) rc = copy_row(e, s, idx[i], o, i);
+    if (!rc) rc = push_counts(e, o);
+    if (rc) {
+        delete o;
+        return rc;
+    }
+    *out = o;
+    return AVA_OK;
+}
+
+int ava_state_cat(const ava_state* const* parts, int32_t n, ava_state** out) {
+    if (!parts || n <= 0 || !out || !parts[0]) return AVA_ERR_ARG;
+    ava_engine* e = parts[0]->e;
+    int rows = 0;
+    for (int i = 0; i < n; ++i) {
+        if (!parts[i] || parts[i]->e != e) return e->fail(AVA_ERR_STATE, "cat: states of different engines");
+        if (parts[i]->ring != parts[0]->ring) return e->fail(AVA_ERR_STATE, "cat: states with different engram capacities");
+        rows += parts[i]->rows;
+    }
+    CK(cudaSetDevice(e->device));
+    ava_state* o = nullptr;
+    int rc = alloc_state(e, rows, parts[0]->ring, parts[0]->keep, &o);
+    if (rc) return rc;
+    int at = 0;
+    for (int i = 0; i < n && !rc; ++i)
+        for (int r = 0; r < parts[i]->rows && !rc; ++r) rc = copy_row(e, parts[i], r, o, at++);
+    if (!rc) rc = push_counts(e, o);
+    if (rc) {
+        delete o;
+        return rc;
+    }
+    *out = o;
+    return AVA_OK;
+}
+
+int64_t ava_state_seen(const ava_state* s, int32_t row) { return (s && row >= 0 && row < s->rows) ? s->seen[row] : -1; }
+
+int64_t ava_state_len(const ava_state* s, int32_t row, const char* name) {
+    StateSlice sl;
+    if (!s || !name || row < 0 || row >= s->rows || !locate(s, row, name, &sl)) return -1;
+    return (int64_t)sl.count;
+}
+
+int ava_state_export(const ava_state* s, int32_t row, const char* name, float* out) {
+    if (!s || !name || !out) return AVA_ERR_ARG;
+    ava_engine* e = s->e;
+    StateSlice sl;
+    if (row < 0 || row >= s->rows || !locate(s, row, name, &sl)) return e->fail(AVA_ERR_ARG, "no state tensor %s of row %d", name, row);
+    CK(cudaSetDevice(e->device));
+    CK(cudaStreamSynchronize(e->stream));
+    if (!sl.eng) {
+        CK(cudaMemcpy(out, sl.buf->as<float>() + sl.off, sl.count * sizeof(float), cudaMemcpyDeviceToHost));
+        return AVA_OK;
+    }
+    // the ring [heads, ring, hs] unrolled oldest first into [heads, n, hs], widened to f32
+    const ava_config& c = e->cfg;
+    const int ehs = c.eng_head_size, enh = c.d / ehs, n = s->n_host[row], ring = s->ring, start = s->start_host[row];
+    const size_t rowe = (size_t)c.d * ring;
+    std::vector<unsigned char> raw(rowe * s->kv_elem());
+    CK(cudaMemcpy(raw.data(), (char*)sl.buf->p + row * rowe * s->kv_elem(), raw.size(), cudaMemcpyDeviceToHost));
+    for (int hh = 0; hh < enh; ++hh)
+        for (int j = 0; j < n; ++j)
+            for (int x = 0; x < ehs; ++x) {
+                const size_t src = ((size_t)hh * ring + (start + j) % ring) * ehs + x;
+                out[((size_t)hh * n + j) * ehs + x] = c.eng_store_bf16 ? ava::bf16_to_f(reinterpret_cast<uint16_t*>(raw.data())[src])
+                                                                      : reinterpret_cast<float*>(raw.data())[src];
+            }
+    return AVA_OK;
+}
+
+int ava_state_import(ava_state* s, int32_t row, const char* name, const float* in, int64_t n) {
+    if (!s || !name || !in) return AVA_ERR_ARG;
+    ava_engine* e = s->e;
+    StateSlice sl;
+    if (row < 0 || row >= s->rows || !locate(s, row, name, &sl)) return e->fail(AVA_ERR_ARG, "no state tensor %s of row %d", name, row);
+    CK(cudaSetDevice(e->device));
+    CK(cudaStreamSynchronize(e->stream));
+    if (!sl.eng) {
+        if ((int64_t)sl.count != n) return e->fail(AVA_ERR_ARG, "%s: %lld values, want %lld", name, (long long)n, (long long)sl.count);
+        CK(cudaMemcpy(sl.buf->as<float>() + sl.off, in, n * sizeof(float), cudaMemcpyHostToDevice));
+        return AVA_OK;
+    }
+    const ava_config& c = e->cfg;
+    const int ehs = c.eng_head_size, enh = c.d / ehs, ring = s->ring;
+    if (n % c.d) return e->fail(AVA_ERR_ARG, "%s: not whole tokens", name);
+    const int tokens = (int)(n / c.d);
+    if (tokens > s->keep) return e->fail(AVA_ERR_CAPACITY, "%s: %d tokens, room for %d", name, tokens, s->keep);
+    const size_t rowe = (size_t)c.d * ring;
+    std::vector<unsigned char> raw(rowe * s->kv_elem(), 0);
+    for (int hh = 0; hh < enh; ++hh)
+        for (int j = 0; j < tokens; ++j)
+            for (int x = 0; x < ehs; ++x) {
+                const float v = in[((size_t)hh * tokens + j) * ehs + x];
+                const size_t dst = ((size_t)hh * ring + j) * ehs + x;
+                if (c.eng_store_bf16)
+                    reinterpret_cast<uint16_t*>(raw.data())[dst] = ava::f_to_bf16(v);
+                else
+                    reinterpret_cast<float*>(raw.data())[dst] = v;
+            }
+    CK(cudaMemcpy((char*)sl.buf->p + row * rowe * s->kv_elem(), raw.data(), raw.size(), cudaMemcpyHostToDevice));
+    // keys and values are imported one after the other: the count follows whichever came last
+    s->n_host[row] = tokens;
+    s->start_host[row] = 0;
+    return push_counts(e, s);
+}
+
+int ava_step_device(ava_engine* e, ava_state* s, const uint32_t* tok_device, float* logits_device, uint32_t* next_device) {
+    int rc = check_pair(e, s);
+    if (rc) return rc;
+    if (!tok_device) return e->fail(AVA_ERR_ARG, "no tokens");
+    return step_device(e, s, tok_device, logits_device, next_device, logits_device != nullptr);
+}
+
+int ava_sync(ava_engine* e) {
+    if (!e) return AVA_ERR_ARG;
+    CK(cudaSetDevice(e->device));
+    return finish(e);
+}
+
+int ava_step(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits) {
+    int rc = check_pair(e, s);
+    if (rc) return rc;
+    if (!tok || !logits) return e->fail(AVA_ERR_ARG, "null buffer");
+    for (int r = 0; r < s->rows; ++r)
+        if (tok[r] >= (uint32_t)e->cfg.vocab) return e->fail(AVA_ERR_ARG, "token %u of row %d outside the vocabulary", tok[r], r);
+    CK(cudaMemcpyAsync(e->tok.p, tok, s->rows * sizeof(uint32_t), cudaMemcpyHostToDevice, e->stream));
+    if ((rc = step_device(e, s, e->tok.as<uint32_t>(), e->logits.as<float>(), nullptr, true))) return rc;
+    CK(cudaMemcpyAsync(logits, e->logits.p, (size_t)s->rows * e->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost, e->stream));
+    return finish(e);
+}
+
+int ava_step_greedy(ava_engine* e, ava_state* s, const uint32_t* tok, uint32_t* next) {
+    int rc = check_pair(e, s);
+    if (rc) return rc;
+    if (!tok || !next) return e->fail(AVA_ERR_ARG, "null buffer");
+    for (int r = 0; r < s->rows; ++r)
+        if (tok[r] >= (uint32_t)e->cfg.vocab) return e->fail(AVA_ERR_ARG, "token %u of row %d outside the vocabulary", tok[r], r);
+    CK(cudaMemcpyAsync(e->tok.p, tok, s->rows * sizeof(uint32_t), cudaMemcpyHostToDevice, e->stream));
+    if ((rc = step_device(e, s, e->tok.as<uint32_t>(), nullptr, e->next.as<uint32_t>(), false))) return rc;
+    CK(cudaMemcpyAsync(next, e->next.p, s->rows * sizeof(uint32_t), cudaMemcpyDeviceToHost, e->stream));
+    return finish(e);
+}
+
+int ava_forward_with_state(ava_engine* e, ava_state* s, const uint32_t* ids, int32_t t, int32_t last_only, float* logits) {
+    int rc = check_pair(e, s);
+    if (rc) return rc;
+    if (!ids || !logits || t <= 0) return e->fail(AVA_ERR_ARG, "bad arguments");
+    const int M = s->rows, V = e->cfg.vocab;
+    for (size_t i = 0; i < (size_t)M * t; ++i)
+        if (ids[i] >= (uint32_t)V) return e->fail(AVA_ERR_ARG, "token %u outside the vocabulary", ids[i]);
+    // the ids column by column: position j of every row is one step
+    std::vector<uint32_t> col((size_t)t * M);
+    for (int r = 0; r < M; ++r)
+        for (int j = 0; j < t; ++j) col[(size_t)j * M + r] = ids[(size_t)r * t + j];
+    Dev dcol;
+    CK(dcol.alloc(col.size() * sizeof(uint32_t)));
+    CK(cudaMemcpyAsync(dcol.p, col.data(), col.size() * sizeof(uint32_t), cudaMemcpyHostToDevice, e->stream));
+    for (int j = 0; j < t; ++j) {
+        const bool want = !last_only || j == t - 1;
+        if ((rc = step_device(e, s, dcol.as<uint32_t>() + (size_t)j * M, want ? e->logits.as<float>() : nullptr, nullptr, want))) return rc;
+        if (want) {
+            if (last_only) {
+                CK(cudaMemcpyAsync(logits, e->logits.p, (size_t)M * V * sizeof(float), cudaMemcpyDeviceToHost, e->stream));
+            } else {
+                // [rows, t, vocab]: row r's position j
+                CK(cudaMemcpy2DAsync(logits + (size_t)j * V, (size_t)t * V * sizeof(float), e->logits.p, (size_t)V * sizeof(float),
+                                     (size_t)V * sizeof(float), M, cudaMemcpyDeviceToHost, e->stream));
+            }
+        }
+    }
+    return finish(e);
+}
+
+void* ava_engine_stream(ava_engine* e) { return e ? (void*)e->stream : nullptr; }
+int64_t ava_engine_launches(const ava_engine* e) { return e ? e->launches : 0; }
+
+int64_t ava_engine_bytes(const ava_engine* e) {
+    if (!e) return 0;
+    int64_t n = e->tok_emb.bytes + e->final_norm.bytes + e->head.q.bytes + e->head.scale.bytes;
+    for (const auto& bp : e->blocks) {
+        const BlockDev& b = *bp;
+        for (const Dev* d : {&b.mem_norm, &b.beta, &b.theta, &b.rho, &b.again, &b.hebb_norm, &b.wa, &b.wb, &b.ba, &b.bb, &b.wa1, &b.wa2, &b.wb1, &b.wb2,
+                             &b.off, &b.vres, &b.eng_norm, &b.mlp_norm, &b.dense})
+            n += d->bytes;
+        for (const QMat* q : {&b.win, &b.wout, &b.proj, &b.wo, &b.eqkv, &b.ewo, &b.w1, &b.w2}) n += q->q.bytes + q->scale.bytes;
+    }
+    for (const Dev* d : {&e->x, &e->h, &e->proj, &e->ve, &e->vv, &e->vw, &e->vah, &e->vqg, &e->vex, &e->qw, &e->qa, &e->yraw, &e->y, &e->eqkv, &e->eo,
+                         &e->u, &e->act, &e->streams, &e->v_first, &e->logits, &e->tok, &e->next})
+        n += d->bytes;
+    return n;
+}
+
+int64_t ava_state_bytes(const ava_state* s) {
+    if (!s) return 0;
+    int64_t n = 0;
+    for (const Dev* d : {&s->lif_v, &s->lif_s, &s->lif_a, &s->mem_f, &s->eng_k, &s->eng_v, &s->eng_n, &s->eng_start}) n += d->bytes;
+    return n;
+}
+
+int ava_debug_keep(ava_engine* e, int32_t on) {
+    if (!e) return AVA_ERR_ARG;
+    e->keep = on != 0;
+    if (!on) e->debug.clear();
+    return AVA_OK;
+}
+
+int64_t ava_debug_width(const ava_engine* e, const char* name) {
+    if (!e || !name) return -1;
+    auto it = e->debug_width.find(name);
+    return it == e->debug_width.end() ? -1 : it->second;
+}
+
+int ava_debug_get(ava_engine* e, const char* name, int32_t block, float* out) {
+    if (!e || !name || !out) return AVA_ERR_ARG;
+    auto it = e->debug.find({name, block});
+    if (it == e->debug.end()) return e->fail(AVA_ERR_ARG, "no kept tensor %s of block %d", name, block);
+    CK(cudaSetDevice(e->device));
+    CK(cudaStreamSynchronize(e->stream));
+    CK(cudaMemcpy(out, it->second->p, it->second->bytes, cudaMemcpyDeviceToHost));
+    return AVA_OK;
+}
+
+float ava_host_expf(float x) { return ava::expf_(x); }
+float ava_host_logf(float x) { return ava::logf_(x); }
+float ava_host_rsqrtf(float x) { return ava::rsqrtf_(x); }
+
+}  // extern "C"

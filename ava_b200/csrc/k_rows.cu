@@ -1,0 +1,376 @@
+// The per-row kernels of the block step (sm_100a): embedding gather, RMS norm, the memory's gate preparation and
+// head norm + output gate, k-winners-take-all, the dense residual mix, greedy argmax.
+//
+// Sums that the reference takes "one value after another from 0" (design-tests/nn/gpu/src/model/fstep.rs:12-14) are
+// taken in that order by one thread, and the small f32 products follow gemm's one-row order (fstep.rs:17-23,222-257):
+// out = w0 * x0, then fma(w_j, x_j, out).  The chains are short next to the memory traffic of the step, and keeping
+// them makes every value the bits of the reference's arithmetic.
+#include "ava_math.h"
+#include "kernels.cuh"
+
+namespace ava {
+
+namespace {
+
+constexpr float NORM_EPS = 1e-5f;  // src/model.rs:36
+
+// (mean(x^2) + eps)^-1/2 with the squares summed in order (src/model/fstep.rs:212-220); x in shared memory
+__device__ __forceinline__ float inv_rms_seq(const float* x, int n) {
+    float s = 0.0f;
+    for (int i = 0; i < n; ++i) s = add(s, mul(x[i], x[i]));
+    const float ms = add(mul(s, (float)(1.0 / (double)n)), 0.0f);
+    return rsqrtf_(add(mul(ms, 1.0f), NORM_EPS));
+}
+
+// (sum(x^2) + 1e-6)^-1/2 (src/model/fstep.rs:271-282)
+__device__ __forceinline__ float inv_l2_seq(const float* x, int n) {
+    float s = 0.0f;
+    for (int i = 0; i < n; ++i) s = add(s, mul(x[i], x[i]));
+    return rsqrtf_(add(mul(s, 1.0f), (float)1e-6));
+}
+
+// gemm's one-row product for one output: x [k] (shared), w[j * stride] the column's weights
+__device__ __forceinline__ float gemv_col(const float* x, int k, const float* w, int stride) {
+    if (k == 0) return 0.0f;
+    if (k == 1) return mul(w[0], x[0]);
+    if (k == 2) return add(mul(w[stride], x[1]), mul(w[0], x[0]));
+    float out = mul(w[0], x[0]);
+    for (int j = 1; j < k; ++j) out = fma(w[(size_t)j * stride], x[j], out);
+    return out;
+}
+
+__device__ __forceinline__ bool finite_f(float v) { return (f_to_bits(v) & 0x7f800000u) != 0x7f800000u; }
+
+// ---------------------------------------------------------------------------------------------------- embedding
+__global__ void embed_kernel(const float* __restrict__ tok_emb, const uint32_t* __restrict__ tok, int M, int d, int vocab, float* x, float* stream0,
+                             uint32_t* status) {
+    const int r = blockIdx.x;
+    uint32_t t = tok[r];
+    if (t >= (uint32_t)vocab) {  // stay in bounds; the host reports the token
+        if (threadIdx.x == 0) atomicOr(status, ST_BAD_TOKEN);
+        t = 0;
+    }
+    const float4* src = reinterpret_cast<const float4*>(tok_emb + (size_t)t * d);
+    float4* dst = reinterpret_cast<float4*>(x + (size_t)r * d);
+    float4* dst2 = stream0 ? reinterpret_cast<float4*>(stream0 + (size_t)r * d) : nullptr;
+    for (int i = threadIdx.x; i < d / 4; i += blockDim.x) {
+        const float4 v = src[i];
+        dst[i] = v;
+        if (dst2) dst2[i] = v;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------- RMS norm
+// One warp per row: the row is staged in shared memory, lane 0 takes the ordered sum, every lane scales.
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain, int M, int n, float* __restrict__ y) {
+    extern __shared__ float sm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (r >= M) return;
+    float* xs = sm + (size_t)warp * n;
+    const float* xr = x + (size_t)r * n;
+    for (int i = lane; i < n; i += 32) xs[i] = xr[i];
+    __syncwarp();
+    float inv = 0.0f;
+    if (lane == 0) inv = inv_rms_seq(xs, n);
+    inv = __shfl_sync(0xffffffffu, inv, 0);
+    float* yr = y + (size_t)r * n;
+    for (int i = lane; i < n; i += 32) yr[i] = mul(mul(xs[i], inv), gain[i]);
+}
+
+// ---------------------------------------------------------------------------------------------------- memory: gates
+// src/model/fstep/arch.rs:685-803 for one row per block of threads.
+__global__ void mem_prep_kernel(const MemPrepArgs a) {
+    extern __shared__ float sm[];
+    const int d = a.d, hs = a.hs, nh = d / hs, rk = a.rank;
+    const int r = blockIdx.x, tid = threadIdx.x, T = blockDim.x;
+    float* h = sm;            // [d]
+    float* q = h + d;         // [d] raw, then unit
+    float* kr = q + d;        // [d] raw key
+    float* ek = kr + d;       // [d] raw erase key, then unit
+    float* wv = ek + d;       // [d] w = k b
+    float* ahv = wv + d;      // [d] ah = e (b alpha)
+    float* lra = ahv + d;     // [d]
+    float* lrb = lra + d;     // [d]
+    float* inv_q = lrb + d;   // [nh]
+    float* inv_k = inv_q + nh;
+    float* inv_e = inv_k + nh;
+    float* za = inv_e + nh;
+    float* zb = za + nh;
+    float* z1a = zb + nh;     // [rk]
+    float* z1b = z1a + rk;    // [rk]
+
+    const float* pr = a.proj + (size_t)r * a.ldp;
+    for (int c = tid; c < d; c += T) {
+        h[c] = a.h[(size_t)r * d + c];
+        q[c] = pr[c];
+        const float kk = pr[d + c];
+        kr[c] = kk;
+        ek[c] = add(kk, pr[3 * d + c]);
+    }
+    __syncthreads();
+    // the independent ordered chains, one per thread
+    const int nroles = 5 * nh + 2 * rk;
+    for (int role = tid; role < nroles; role += T) {
+        if (role < nh) {
+            inv_q[role] = inv_l2_seq(q + role * hs, hs);
+        } else if (role < 2 * nh) {
+            inv_k[role - nh] = inv_l2_seq(kr + (role - nh) * hs, hs);
+        } else if (role < 3 * nh) {
+            inv_e[role - 2 * nh] = inv_l2_seq(ek + (role - 2 * nh) * hs, hs);
+        } else if (role < 4 * nh) {
+            const int e = role - 3 * nh;
+            za[e] = add(gemv_col(h, d, a.wa + e, nh), a.ba[e]);
+        } else if (role < 5 * nh) {
+            const int e = role - 4 * nh;
+            zb[e] = add(gemv_col(h, d, a.wb + e, nh), a.bb[e]);
+        } else if (role < 5 * nh + rk) {
+            const int i = role - 5 * nh;
+            z1a[i] = gemv_col(h, d, a.wa1 + i, rk);
+        } else {
+            const int i = role - 5 * nh - rk;
+            z1b[i] = gemv_col(h, d, a.wb1 + i, rk);
+        }
+    }
+    __syncthreads();
+    for (int c = tid; c < d; c += T) {
+        lra[c] = gemv_col(z1a, rk, a.wa2 + c, d);
+        lrb[c] = gemv_col(z1b, rk, a.wb2 + c, d);
+    }
+    __syncthreads();
+    bool bad = false;
+    for (int c = tid; c < d; c += T) {
+        const int e = c / hs;
+        const size_t o = (size_t)r * d + c;
+        const float la = log_sigmoid(add(add(za[e], a.off[c]), lra[c]));
+        const float be = add(mul(sigmoid(add(zb[e], lrb[c])), 2.0f), 0.0f);
+        const float ex = expf_(la);
+        const float qn = mul(q[c], inv_q[e]);
+        const float kn = mul(kr[c], inv_k[e]);
+        const float en = mul(ek[c], inv_e[e]);
+        float v = pr[2 * d + c];
+        if (a.first) {
+            a.v_first[o] = v;
+        } else if (a.vres) {
+            // (1 + p0) v + p1 v0 (src/model/fstep/arch.rs:697-702)
+            const float p0 = add(mul(a.vres[0], 1.0f), 1.0f);
+            v = add(mul(v, p0), mul(a.v_first[o], a.vres[1]));
+        }
+        const float w = mul(kn, be);
+        const float ah = mul(en, mul(be, ex));
+        const float qg = mul(qn, ex);
+        bad |= !(finite_f(la) && finite_f(en) && finite_f(w) && finite_f(ah) && finite_f(qn) && finite_f(v));
+        a.e[o] = en;
+        a.v[o] = v;
+        a.w[o] = w;
+        a.ah[o] = ah;
+        a.qg[o] = qg;
+        a.ex[o] = ex;
+        q[c] = qn;
+        wv[c] = w;
+        ahv[c] = ah;
+    }
+    if (bad) atomicOr(a.status, ST_NONFINITE);
+    __syncthreads();
+    // q.w and q.ah, each summed in order from 0 (src/model/fstep/arch.rs:789-797)
+    for (int role = tid; role < 2 * nh; role += T) {
+        const int e = role % nh;
+        const float* b = role < nh ? wv : ahv;
+        float s = 0.0f;
+        for (int c = e * hs; c < (e + 1) * hs; ++c) s = add(s, mul(q[c], b[c]));
+        (role < nh ? a.qw : a.qa)[(size_t)r * nh + e] = s;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------- memory: output
+// head norm, then the silu output gate (src/model/fstep/arch.rs:842-852)
+__global__ void mem_post_kernel(const float* __restrict__ y_raw, const float* __restrict__ gate, int ldg, int M, int d, int hs, float* __restrict__ y) {
+    extern __shared__ float sm[];
+    const int nh = d / hs, r = blockIdx.x, tid = threadIdx.x, T = blockDim.x;
+    float* ys = sm;
+    float* inv = sm + d;
+    for (int c = tid; c < d; c += T) ys[c] = y_raw[(size_t)r * d + c];
+    __syncthreads();
+    for (int e = tid; e < nh; e += T) inv[e] = inv_rms_seq(ys + e * hs, hs);
+    __syncthreads();
+    for (int c = tid; c < d; c += T) {
+        float v = mul(ys[c], inv[c / hs]);
+        if (gate) {
+            const float g = gate[(size_t)r * ldg + c];
+            v = mul(v, div(g, add(1.0f, expf_(-g))));
+        }
+        y[(size_t)r * d + c] = v;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------- kWTA
+// The k-th largest value found exactly, one bit of its order-preserving key per round: T is the largest key with
+// count(keys >= T) >= k.  Every unit at or above it is kept (ties included), negatives dropped, squared on request
+// (src/model/fstep.rs:295-299, src/model/fstep/arch.rs:982-989).
+__device__ __forceinline__ uint32_t order_key(float f) {
+    const uint32_t u = f_to_bits(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_value(uint32_t k) { return bits_to_f((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k); }
+
+__global__ void kwta_kernel(const float* __restrict__ u, int M, int n, int k, int relu2, float* __restrict__ out) {
+    extern __shared__ uint32_t keys[];  // [n] keys, then [33] counters
+    __shared__ int warp_cnt[32];
+    __shared__ int total;
+    const int r = blockIdx.x, tid = threadIdx.x, T = blockDim.x, lane = tid & 31, warp = tid >> 5;
+    const float* ur = u + (size_t)r * n;
+    float* orow = out + (size_t)r * n;
+    if (k >= n) {
+        for (int i = tid; i < n; i += T) {
+            float v = fmaxf(mul(ur[i], 1.0f), 0.0f);
+            orow[i] = relu2 ? mul(v, v) : v;
+        }
+        return;
+    }
+    for (int i = tid; i < n; i += T) keys[i] = order_key(ur[i]);
+    __syncthreads();
+    uint32_t thr = 0;
+    for (int bit = 31; bit >= 0; --bit) {
+        const uint32_t cand = thr | (1u << bit);
+        int c = 0;
+        for (int i = tid; i < n; i += T) c += keys[i] >= cand;
+        for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+        if (lane == 0) warp_cnt[warp] = c;
+        __syncthreads();
+        if (tid == 0) {
+            int t = 0;
+            for (int w = 0; w < (T >> 5); ++w) t += warp_cnt[w];
+            total = t;
+        }
+        __syncthreads();
+        if (total >= k) thr = cand;
+    }
+    const float kth = key_value(thr);
+    for (int i = tid; i < n; i += T) {
+        const float v = ur[i];
+        float o = fmaxf(mul(v, sub(v, kth) >= 0.0f ? 1.0f : 0.0f), 0.0f);
+        orow[i] = relu2 ? mul(o, o) : o;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------- dense mix
+// src/model/fstep/arch.rs:1014-1024: the block's output joins the streams, then x <- x + sum_j stream_j w_j in order.
+__global__ void dense_mix_kernel(float* x, float* streams, const float* __restrict__ w, int n_streams, int64_t MD) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= MD) return;
+    const float xv = x[i];
+    streams[(int64_t)(n_streams - 1) * MD + i] = xv;
+    float mix = xv;
+    for (int j = 0; j < n_streams - 1; ++j) mix = add(mix, mul(streams[(int64_t)j * MD + i], w[j]));
+    mix = add(mix, mul(xv, w[n_streams - 1]));
+    x[i] = mix;
+}
+
+// ---------------------------------------------------------------------------------------------------- argmax
+__global__ void argmax_kernel(const float* __restrict__ logits, int M, int V, uint32_t* next) {
+    __shared__ float bv[32];
+    __shared__ uint32_t bi[32];
+    const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* lr = logits + (size_t)r * V;
+    float best = -INFINITY;
+    uint32_t idx = 0xffffffffu;
+    for (int i = tid; i < V; i += blockDim.x) {
+        const float v = lr[i];
+        if (v > best || (v == best && (uint32_t)i < idx) || idx == 0xffffffffu) {
+            best = v;
+            idx = i;
+        }
+    }
+    auto better = [](float v, uint32_t i, float bv_, uint32_t bi_) { return bi_ == 0xffffffffu || (i != 0xffffffffu && (v > bv_ || (v == bv_ && i < bi_))); };
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (better(ov, oi, best, idx)) {
+            best = ov;
+            idx = oi;
+        }
+    }
+    if (lane == 0) {
+        bv[warp] = best;
+        bi[warp] = idx;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < (blockDim.x >> 5); ++w)
+            if (better(bv[w], bi[w], best, idx)) {
+                best = bv[w];
+                idx = bi[w];
+            }
+        next[r] = idx == 0xffffffffu ? 0u : idx;
+    }
+}
+
+__global__ void math_kernel(int which, const float* x, int64_t n, float* y) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    y[i] = which == 0 ? expf_(x[i]) : which == 1 ? logf_(x[i]) : rsqrtf_(x[i]);
+}
+
+__global__ void round_bf16_kernel(const float* x, int64_t n, uint16_t* y) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = f_to_bf16(x[i]);
+}
+__global__ void widen_bf16_kernel(const uint16_t* x, int64_t n, float* y) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = bf16_to_f(x[i]);
+}
+
+template <typename K>
+void opt_in_smem(K kernel, size_t bytes) {
+    if (bytes > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+}  // namespace
+
+void launch_embed(cudaStream_t st, const float* tok_emb, const uint32_t* tok, int M, int d, int vocab, float* x, float* stream0, uint32_t* status) {
+    embed_kernel<<<M, 128, 0, st>>>(tok_emb, tok, M, d, vocab, x, stream0, status);
+}
+
+void launch_rmsnorm(cudaStream_t st, const float* x, const float* gain, int M, int n, float* y) {
+    const int warps = 4;
+    const size_t smem = (size_t)warps * n * sizeof(float);
+    opt_in_smem(rmsnorm_kernel, smem);
+    rmsnorm_kernel<<<(M + warps - 1) / warps, warps * 32, smem, st>>>(x, gain, M, n, y);
+}
+
+void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a) {
+    const int nh = a.d / a.hs;
+    const size_t smem = ((size_t)8 * a.d + 5 * nh + 2 * a.rank) * sizeof(float);
+    opt_in_smem(mem_prep_kernel, smem);
+    mem_prep_kernel<<<a.M, 256, smem, st>>>(a);
+}
+
+void launch_mem_post(cudaStream_t st, const float* y_raw, const float* gate, int ldg, int M, int d, int hs, float* y) {
+    const size_t smem = ((size_t)d + d / hs) * sizeof(float);
+    opt_in_smem(mem_post_kernel, smem);
+    mem_post_kernel<<<M, 256, smem, st>>>(y_raw, gate, ldg, M, d, hs, y);
+}
+
+void launch_kwta(cudaStream_t st, const float* u, int M, int n, int k, int relu2, float* a) {
+    const size_t smem = (size_t)n * sizeof(uint32_t);
+    opt_in_smem(kwta_kernel, smem);
+    kwta_kernel<<<M, 256, smem, st>>>(u, M, n, k, relu2, a);
+}
+
+void launch_dense_mix(cudaStream_t st, float* x, float* streams, const float* w, int n_streams, int64_t MD) {
+    dense_mix_kernel<<<(unsigned)((MD + 255) / 256), 256, 0, st>>>(x, streams, w, n_streams, MD);
+}
+
+void launch_argmax(cudaStream_t st, const float* logits, int M, int V, uint32_t* next) { argmax_kernel<<<M, 256, 0, st>>>(logits, M, V, next); }
+
+void launch_math(cudaStream_t st, int which, const float* x, int64_t n, float* y) {
+    math_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(which, x, n, y);
+}
+void launch_round_bf16(cudaStream_t st, const float* x, int64_t n, uint16_t* y) {
+    round_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, n, y);
+}
+void launch_widen_bf16(cudaStream_t st, const uint16_t* x, int64_t n, float* y) {
+    widen_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, n, y);
+}
+
+}  // namespace ava

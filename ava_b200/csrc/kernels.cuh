@@ -1,0 +1,105 @@
+// Launchers of the block step's CUDA kernels (sm_100a).  Every pointer is device memory.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ava {
+
+// Status word in device memory that kernels OR bits into; the host reads it when it reads the step's results.
+enum : uint32_t {
+    ST_NONFINITE = 1u,     // a gate, key or value of the fast-weight memory was not finite
+    ST_WAIT_TIMEOUT = 2u,  // a bounded wait on a copy barrier ran out
+    ST_ENGRAM_FULL = 4u,   // the engram store had no room for this token
+    ST_BAD_TOKEN = 8u,     // a token id outside the vocabulary
+};
+
+// ---- int8-weight products -----------------------------------------------------------------------------------
+enum GemmEpilogue { EPI_STORE = 0, EPI_ADD = 1, EPI_LIF = 2 };
+
+struct LifParams {
+    const float* beta;   // [d] leak (already sigmoid of the parameter)
+    const float* theta;  // [d] or nullptr (1.0)
+    const float* rho;    // [d] or nullptr: no adaptive threshold
+    const float* gain;   // [d] or nullptr
+    float* v;            // [M, d] membranes, updated in place
+    float* s;            // [M, d] spikes, updated in place (this step's spikes are what W_out reads)
+    float* a;            // [M, d] adaptation trace or nullptr
+    int spikes;          // 0 binary, 1 ternary, 2 int2
+    int lif_scale;       // current times (1 - beta)
+};
+
+struct GemmArgs {
+    const float* A;      // [M, K] activations, row stride lda
+    int lda;
+    const int8_t* W;     // [K, N] int8 weights, row stride ldw
+    int ldw;
+    const float* scale;  // [N]
+    float* C;            // [M, N] output (EPI_STORE / EPI_ADD), row stride ldc
+    int ldc;
+    int M, N, K;
+    LifParams lif;       // EPI_LIF only (N == d)
+};
+
+// C = A . W with f32 activations, int8 weights, one fused multiply-add per term in the order k = 0, 1, ... from +0,
+// the sum then times scale[n]: the bits of the reference's int8 product (src/int8.rs:315-331).  K % 16 == 0, N % 4 == 0.
+void launch_q8_gemm(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int sm_count);
+
+// ---- row kernels ----------------------------------------------------------------------------------------------
+void launch_embed(cudaStream_t st, const float* tok_emb, const uint32_t* tok, int M, int d, int vocab, float* x, float* stream0, uint32_t* status);
+void launch_rmsnorm(cudaStream_t st, const float* x, const float* gain, int M, int n, float* y);
+void launch_lif(cudaStream_t st, const float* cur, const LifParams& p, int M, int d);
+
+struct MemPrepArgs {
+    const float* h;      // [M, d] normed input
+    const float* proj;   // [M, ldp]: q | k | v | e | (g)
+    int ldp;
+    const float *wa, *wb, *ba, *bb, *wa1, *wa2, *wb1, *wb2, *off;
+    const float* vres;   // [2] or nullptr
+    float* v_first;      // [M, d]: written when first, read when vres
+    int first;           // 1: this block's values become v_first
+    int M, d, hs, rank;
+    // outputs [M, d] each, qw/qa [M, d / hs]
+    float *e, *v, *w, *ah, *qg, *ex, *qw, *qa;
+    uint32_t* status;
+};
+void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a);
+
+struct MemHeadsArgs {
+    CUtensorMap tmap;    // the fast weights as a 2-D tensor [rows_total, hs] f32, box [cw, rb]
+    int64_t row0;        // first tensor row of this launch's (row 0, head 0)
+    int M, nh, hs, cw, rb;
+    const float *e, *v, *w, *ah, *qg, *ex;  // [M, nh * hs]
+    const float *qw, *qa;                    // [M, nh]
+    float* y;                                // [M, nh * hs]
+    uint32_t* status;
+};
+void launch_mem_heads(cudaStream_t st, const MemHeadsArgs& a);
+// the column-slice width and rows-per-box the kernel uses for a head size; false: head size not covered
+bool mem_heads_tiling(int hs, int* cw, int* rb);
+
+void launch_mem_post(cudaStream_t st, const float* y_raw, const float* gate, int ldg, int M, int d, int hs, float* y);
+
+struct EngramArgs {
+    const float* qkv;    // [M, 3 d]
+    void* k;             // [M, heads, cap, hs] bf16 or f32
+    void* v;
+    int32_t* n;          // [M] tokens held
+    int32_t* start;      // [M] ring start
+    int M, d, hs, cap, keep, bf16;   // cap: ring slots per head; keep: tokens kept after the read (oldest dropped)
+    float* o;            // [M, d]
+    uint32_t* status;
+};
+// returns false when n_max keys do not fit the kernel's shared memory
+bool launch_engram(cudaStream_t st, const EngramArgs& a, int n_max);
+
+void launch_kwta(cudaStream_t st, const float* u, int M, int n, int k, int relu2, float* a);
+// x <- x + sum_j streams[j] * w[j] over the n_streams streams (the last one is x itself, stored first)
+void launch_dense_mix(cudaStream_t st, float* x, float* streams, const float* w, int n_streams, int64_t MD);
+void launch_argmax(cudaStream_t st, const float* logits, int M, int V, uint32_t* next);
+void launch_math(cudaStream_t st, int which, const float* x, int64_t n, float* y);
+void launch_round_bf16(cudaStream_t st, const float* x, int64_t n, uint16_t* y);
+void launch_widen_bf16(cudaStream_t st, const uint16_t* x, int64_t n, float* y);
+
+}  // namespace ava

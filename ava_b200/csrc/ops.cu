@@ -1,0 +1,232 @@
+// Single operators of the block step on host buffers: the kernels behind the step, callable one at a time so that a
+// parity test can feed an operator exactly the inputs the reference's code would see (teacher forcing).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <vector>
+
+#include "../../include/ava_engine.h"
+#include "ava_math.h"
+#include "kernels.cuh"
+
+namespace {
+
+using namespace ava;
+
+struct Tmp {
+    void* p = nullptr;
+    ~Tmp() {
+        if (p) cudaFree(p);
+    }
+    template <typename T>
+    T* as() { return reinterpret_cast<T*>(p); }
+};
+
+#define OCK(call)                                   \
+    do {                                            \
+        if ((call) != cudaSuccess) return AVA_ERR_CUDA; \
+    } while (0)
+
+cudaError_t up(Tmp& t, const void* src, size_t bytes) {
+    cudaError_t e = cudaMalloc(&t.p, bytes ? bytes : 1);
+    if (e != cudaSuccess) return e;
+    return src && bytes ? cudaMemcpy(t.p, src, bytes, cudaMemcpyHostToDevice) : cudaSuccess;
+}
+
+int begin(int device) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || device < 0 || device >= n) return AVA_ERR_CUDA;
+    return cudaSetDevice(device) == cudaSuccess ? AVA_OK : AVA_ERR_CUDA;
+}
+
+int end_() {
+    if (cudaGetLastError() != cudaSuccess) return AVA_ERR_CUDA;
+    return cudaDeviceSynchronize() == cudaSuccess ? AVA_OK : AVA_ERR_CUDA;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ava_op_q8_matmul(int device, const float* x, int32_t m, const int8_t* q, const float* scale, int32_t din, int32_t dout, float* y) {
+    if (!x || !q || !scale || !y || m <= 0 || din <= 0 || dout <= 0) return AVA_ERR_ARG;
+    if (din % 16 || dout % 4) return AVA_NOT_APPLICABLE;
+    int rc = begin(device);
+    if (rc) return rc;
+    Tmp dx, dq, ds, dy;
+    OCK(up(dx, x, (size_t)m * din * 4));
+    OCK(up(dq, q, (size_t)din * dout));
+    OCK(up(ds, scale, (size_t)dout * 4));
+    OCK(up(dy, nullptr, (size_t)m * dout * 4));
+    GemmArgs g{};
+    g.A = dx.as<float>(); g.lda = din; g.W = dq.as<int8_t>(); g.ldw = dout; g.scale = ds.as<float>();
+    g.C = dy.as<float>(); g.ldc = dout; g.M = m; g.N = dout; g.K = din;
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    launch_q8_gemm(0, g, EPI_STORE, sms);
+    if ((rc = end_())) return rc;
+    OCK(cudaMemcpy(y, dy.p, (size_t)m * dout * 4, cudaMemcpyDeviceToHost));
+    return AVA_OK;
+}
+
+int ava_op_rmsnorm(int device, const float* x, const float* gain, int32_t m, int32_t n, float* y) {
+    if (!x || !gain || !y || m <= 0 || n <= 0) return AVA_ERR_ARG;
+    int rc = begin(device);
+    if (rc) return rc;
+    Tmp dx, dg, dy;
+    OCK(up(dx, x, (size_t)m * n * 4));
+    OCK(up(dg, gain, (size_t)n * 4));
+    OCK(up(dy, nullptr, (size_t)m * n * 4));
+    launch_rmsnorm(0, dx.as<float>(), dg.as<float>(), m, n, dy.as<float>());
+    if ((rc = end_())) return rc;
+    OCK(cudaMemcpy(y, dy.p, (size_t)m * n * 4, cudaMemcpyDeviceToHost));
+    return AVA_OK;
+}
+
+int ava_op_lif(int device, const float* cur, const float* beta, const float* theta, const float* rho, const float* gain, int32_t spikes,
+               const float* v0, const float* s0, const float* a0, int32_t m, int32_t d, float* s1, float* v1, float* a1) {
+    if (!cur || !beta || !v0 || !s0 || !s1 || !v1 || m <= 0 || d <= 0) return AVA_ERR_ARG;
+    const bool alif = rho && gain;
+    if (alif && (!a0 || !a1)) return AVA_ERR_ARG;
+    int rc = begin(device);
+    if (rc) return rc;
+    const size_t md = (size_t)m * d * 4, dd = (size_t)d * 4;
+    Tmp dc, db, dt, dr, dg, dv, ds, da;
+    OCK(up(dc, cur, md));
+    OCK(up(db, beta, dd));
+    if (theta) OCK(up(dt, theta, dd));
+    if (alif) {
+        OCK(up(dr, rho, dd));
+        OCK(up(dg, gain, dd));
+        OCK(up(da, a0, md));
+    }
+    OCK(up(dv, v0, md));
+    OCK(up(ds, s0, md));
+    LifParams p{};
+    p.beta = db.as<float>(); p.theta = theta ? dt.as<float>() : nullptr; p.rho = alif ? dr.as<float>() : nullptr;
+    p.gain = alif ? dg.as<float>() : nullptr; p.v = dv.as<float>(); p.s = ds.as<float>(); p.a = alif ? da.as<float>() : nullptr;
+    p.spikes = spikes; p.lif_scale = 0;
+    launch_lif(0, dc.as<float>(), p, m, d);
+    if ((rc = end_())) return rc;
+    OCK(cudaMemcpy(s1, ds.p, md, cudaMemcpyDeviceToHost));
+    OCK(cudaMemcpy(v1, dv.p, md, cudaMemcpyDeviceToHost));
+    if (alif) OCK(cudaMemcpy(a1, da.p, md, cudaMemcpyDeviceToHost));
+    return AVA_OK;
+}
+
+int ava_op_kwta(int device, const float* u, int32_t m, int32_t n, int32_t k, int32_t relu2, float* a) {
+    if (!u || !a || m <= 0 || n <= 0 || k <= 0) return AVA_ERR_ARG;
+    int rc = begin(device);
+    if (rc) return rc;
+    Tmp du, da;
+    OCK(up(du, u, (size_t)m * n * 4));
+    OCK(up(da, nullptr, (size_t)m * n * 4));
+    launch_kwta(0, du.as<float>(), m, n, k, relu2, da.as<float>());
+    if ((rc = end_())) return rc;
+    OCK(cudaMemcpy(a, da.p, (size_t)m * n * 4, cudaMemcpyDeviceToHost));
+    return AVA_OK;
+}
+
+int ava_op_mem_heads(int device, int32_t m, int32_t hs, const float* e, const float* v, const float* w, const float* ah, const float* qg,
+                     const float* ex, const float* qw, const float* qa, float* f, float* y) {
+    if (!e || !v || !w || !ah || !qg || !ex || !qw || !qa || !f || !y || m <= 0 || hs <= 0) return AVA_ERR_ARG;
+    int cw, rb;
+    if (hs % 16 || !mem_heads_tiling(hs, &cw, &rb)) return AVA_NOT_APPLICABLE;
+    int rc = begin(device);
+    if (rc) return rc;
+    const size_t vb = (size_t)m * hs * 4, fb = (size_t)m * hs * hs * 4;
+    Tmp de, dv, dw, dah, dqg, dex, dqw, dqa, df, dy, dst;
+    OCK(up(de, e, vb)); OCK(up(dv, v, vb)); OCK(up(dw, w, vb)); OCK(up(dah, ah, vb)); OCK(up(dqg, qg, vb)); OCK(up(dex, ex, vb));
+    OCK(up(dqw, qw, (size_t)m * 4)); OCK(up(dqa, qa, (size_t)m * 4));
+    OCK(up(df, f, fb));
+    OCK(up(dy, nullptr, vb));
+    OCK(up(dst, nullptr, 4));
+    OCK(cudaMemset(dst.p, 0, 4));
+    MemHeadsArgs a{};
+    {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) != cudaSuccess || qr != cudaDriverEntryPointSuccess) return AVA_ERR_CUDA;
+        typedef CUresult (*Fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                               const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+        const cuuint64_t dims[2] = {(cuuint64_t)hs, (cuuint64_t)m * hs};
+        const cuuint64_t strides[1] = {(cuuint64_t)hs * 4};
+        const cuuint32_t box[2] = {(cuuint32_t)cw, (cuuint32_t)rb};
+        const cuuint32_t es[2] = {1, 1};
+        if (((Fn)fn)(&a.tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, df.p, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return AVA_ERR_CUDA;
+    }
+    a.row0 = 0; a.M = m; a.nh = 1; a.hs = hs; a.cw = cw; a.rb = rb;
+    a.e = de.as<float>(); a.v = dv.as<float>(); a.w = dw.as<float>(); a.ah = dah.as<float>(); a.qg = dqg.as<float>(); a.ex = dex.as<float>();
+    a.qw = dqw.as<float>(); a.qa = dqa.as<float>(); a.y = dy.as<float>(); a.status = dst.as<uint32_t>();
+    launch_mem_heads(0, a);
+    if ((rc = end_())) return rc;
+    uint32_t st = 0;
+    OCK(cudaMemcpy(&st, dst.p, 4, cudaMemcpyDeviceToHost));
+    if (st) return AVA_ERR_CUDA;
+    OCK(cudaMemcpy(f, df.p, fb, cudaMemcpyDeviceToHost));
+    OCK(cudaMemcpy(y, dy.p, vb, cudaMemcpyDeviceToHost));
+    return AVA_OK;
+}
+
+int ava_op_attend(int device, int32_t m, int32_t n, int32_t hs, int32_t bf16_store, const float* q, const float* kc, const float* vc, float* out) {
+    if (!q || !kc || !vc || !out || m <= 0 || n <= 0 || hs <= 0) return AVA_ERR_ARG;
+    int rc = begin(device);
+    if (rc) return rc;
+    // m heads as one row of width d = m * hs; the first n - 1 keys/values are laid in the store, the last one arrives
+    // as this token's key and value
+    const int d = m * hs;
+    const size_t el = bf16_store ? 2 : 4;
+    std::vector<float> qkv((size_t)3 * d);
+    for (int hh = 0; hh < m; ++hh)
+        for (int x = 0; x < hs; ++x) {
+            qkv[hh * hs + x] = q[(size_t)hh * hs + x];
+            qkv[d + hh * hs + x] = kc[((size_t)hh * n + (n - 1)) * hs + x];
+            qkv[2 * d + hh * hs + x] = vc[((size_t)hh * n + (n - 1)) * hs + x];
+        }
+    std::vector<unsigned char> ks((size_t)d * n * el, 0), vs((size_t)d * n * el, 0);
+    for (int hh = 0; hh < m; ++hh)
+        for (int j = 0; j + 1 < n; ++j)
+            for (int x = 0; x < hs; ++x) {
+                const size_t i = ((size_t)hh * n + j) * hs + x;
+                if (bf16_store) {
+                    reinterpret_cast<uint16_t*>(ks.data())[i] = f_to_bf16(kc[i]);
+                    reinterpret_cast<uint16_t*>(vs.data())[i] = f_to_bf16(vc[i]);
+                } else {
+                    reinterpret_cast<float*>(ks.data())[i] = kc[i];
+                    reinterpret_cast<float*>(vs.data())[i] = vc[i];
+                }
+            }
+    const int32_t n0 = n - 1, zero = 0;
+    Tmp dq, dk, dv, dn, dstart, dout, dst;
+    OCK(up(dq, qkv.data(), qkv.size() * 4));
+    OCK(up(dk, ks.data(), ks.size()));
+    OCK(up(dv, vs.data(), vs.size()));
+    OCK(up(dn, &n0, 4));
+    OCK(up(dstart, &zero, 4));
+    OCK(up(dout, nullptr, (size_t)d * 4));
+    OCK(up(dst, &zero, 4));
+    EngramArgs a{};
+    a.qkv = dq.as<float>(); a.k = dk.p; a.v = dv.p; a.n = dn.as<int32_t>(); a.start = dstart.as<int32_t>();
+    a.M = 1; a.d = d; a.hs = hs; a.cap = n; a.keep = n; a.bf16 = bf16_store; a.o = dout.as<float>(); a.status = dst.as<uint32_t>();
+    if (!launch_engram(0, a, n)) return AVA_ERR_CAPACITY;
+    if ((rc = end_())) return rc;
+    OCK(cudaMemcpy(out, dout.p, (size_t)d * 4, cudaMemcpyDeviceToHost));
+    return AVA_OK;
+}
+
+int ava_op_math(int device, int32_t which, const float* x, int64_t n, float* y) {
+    if (!x || !y || n <= 0 || which < 0 || which > 2) return AVA_ERR_ARG;
+    int rc = begin(device);
+    if (rc) return rc;
+    Tmp dx, dy;
+    OCK(up(dx, x, (size_t)n * 4));
+    OCK(up(dy, nullptr, (size_t)n * 4));
+    launch_math(0, which, dx.as<float>(), n, dy.as<float>());
+    if ((rc = end_())) return rc;
+    OCK(cudaMemcpy(y, dy.p, (size_t)n * 4, cudaMemcpyDeviceToHost));
+    return AVA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,358 @@
+"""Python mirror of the reference's model/engine interface over the C ABI (include/ava_engine.h).
+
+`Model` / `State` carry the reference's method names (`Model::state`, `Model::step`, `Model::forward_with_state`,
+`State::select`, `State::cat`; design-tests/nn/gpu/src/model.rs:1260, src/state.rs:129,207,593,684).  Everything goes
+through libava_engine.so with ctypes; there is no other compute path: without the library or without a CUDA device
+these calls raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import config as _config
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libava_engine.so")
+
+OK, NOT_APPLICABLE = 0, 1
+ERR_ARG, ERR_CUDA, ERR_STATE, ERR_NONFINITE, ERR_MISSING, ERR_CAPACITY = -1, -2, -3, -4, -5, -6
+
+
+class AvaConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in _config.FIELDS_I32] + [(n, C.c_float) for n in _config.FIELDS_F32]
+
+
+class EngineError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__(f"ava engine error {code}: {msg}")
+        self.code = code
+
+
+class NotApplicable(RuntimeError):
+    """The engine does not cover this configuration (the reference's `Ok(None)` convention)."""
+
+
+_lib = None
+fp = C.POINTER(C.c_float)
+i8p = C.POINTER(C.c_int8)
+u32p = C.POINTER(C.c_uint32)
+i32p = C.POINTER(C.c_int32)
+
+
+def lib() -> C.CDLL:
+    """The C-ABI library.  Raises when it has not been built: there is no fallback."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m ava_b200.build` (no CPU fallback exists)")
+    L = C.CDLL(LIB_PATH)
+    vp = C.c_void_p
+    sig = {
+        "ava_engine_create": ([C.POINTER(AvaConfig), C.c_int, C.POINTER(vp)], C.c_int),
+        "ava_engine_destroy": ([vp], None),
+        "ava_last_error": ([vp], C.c_char_p),
+        "ava_engine_set_f32": ([vp, C.c_char_p, fp, C.c_int64], C.c_int),
+        "ava_engine_set_q8": ([vp, C.c_char_p, i8p, fp, C.c_int32, C.c_int32], C.c_int),
+        "ava_engine_set_q8_from_f32": ([vp, C.c_char_p, fp, C.c_int32, C.c_int32], C.c_int),
+        "ava_engine_finalize": ([vp], C.c_int),
+        "ava_engine_blocker": ([vp], C.c_char_p),
+        "ava_state_new": ([vp, C.c_int32, C.c_int32, C.POINTER(vp)], C.c_int),
+        "ava_state_destroy": ([vp], None),
+        "ava_state_rows": ([vp], C.c_int32),
+        "ava_state_select": ([vp, i32p, C.c_int32, C.POINTER(vp)], C.c_int),
+        "ava_state_cat": ([C.POINTER(vp), C.c_int32, C.POINTER(vp)], C.c_int),
+        "ava_state_seen": ([vp, C.c_int32], C.c_int64),
+        "ava_state_len": ([vp, C.c_int32, C.c_char_p], C.c_int64),
+        "ava_state_export": ([vp, C.c_int32, C.c_char_p, fp], C.c_int),
+        "ava_state_import": ([vp, C.c_int32, C.c_char_p, fp, C.c_int64], C.c_int),
+        "ava_step": ([vp, vp, u32p, fp], C.c_int),
+        "ava_step_greedy": ([vp, vp, u32p, u32p], C.c_int),
+        "ava_forward_with_state": ([vp, vp, u32p, C.c_int32, C.c_int32, fp], C.c_int),
+        "ava_step_device": ([vp, vp, vp, vp, vp], C.c_int),
+        "ava_sync": ([vp], C.c_int),
+        "ava_engine_stream": ([vp], vp),
+        "ava_engine_launches": ([vp], C.c_int64),
+        "ava_engine_bytes": ([vp], C.c_int64),
+        "ava_state_bytes": ([vp], C.c_int64),
+        "ava_debug_keep": ([vp, C.c_int32], C.c_int),
+        "ava_debug_width": ([vp, C.c_char_p], C.c_int64),
+        "ava_debug_get": ([vp, C.c_char_p, C.c_int32, fp], C.c_int),
+        "ava_op_q8_matmul": ([C.c_int, fp, C.c_int32, i8p, fp, C.c_int32, C.c_int32, fp], C.c_int),
+        "ava_op_rmsnorm": ([C.c_int, fp, fp, C.c_int32, C.c_int32, fp], C.c_int),
+        "ava_op_lif": ([C.c_int, fp, fp, fp, fp, fp, C.c_int32, fp, fp, fp, C.c_int32, C.c_int32, fp, fp, fp], C.c_int),
+        "ava_op_kwta": ([C.c_int, fp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, fp], C.c_int),
+        "ava_op_mem_heads": ([C.c_int, C.c_int32, C.c_int32, fp, fp, fp, fp, fp, fp, fp, fp, fp, fp], C.c_int),
+        "ava_op_attend": ([C.c_int, C.c_int32, C.c_int32, C.c_int32, C.c_int32, fp, fp, fp, fp], C.c_int),
+        "ava_host_expf": ([C.c_float], C.c_float),
+        "ava_host_logf": ([C.c_float], C.c_float),
+        "ava_host_rsqrtf": ([C.c_float], C.c_float),
+        "ava_op_math": ([C.c_int, C.c_int32, fp, C.c_int64, fp], C.c_int),
+    }
+    for name, (args, res) in sig.items():
+        f = getattr(L, name)
+        f.argtypes = args
+        f.restype = res
+    _lib = L
+    return L
+
+
+EXPORTS = ("ava_engine_create ava_engine_destroy ava_last_error ava_engine_set_f32 ava_engine_set_q8 "
+           "ava_engine_set_q8_from_f32 ava_engine_finalize ava_engine_blocker ava_state_new ava_state_destroy "
+           "ava_state_rows ava_state_select ava_state_cat ava_state_seen ava_state_len ava_state_export "
+           "ava_state_import ava_step ava_step_greedy ava_forward_with_state ava_step_device ava_sync "
+           "ava_engine_stream ava_engine_launches ava_engine_bytes ava_state_bytes ava_debug_keep ava_debug_width "
+           "ava_debug_get ava_op_q8_matmul ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_op_attend "
+           "ava_host_expf ava_host_logf ava_host_rsqrtf ava_op_math").split()
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, np.float32)
+
+
+def _p(a, t=fp):
+    return a.ctypes.data_as(t) if a is not None else None
+
+
+def host_math():
+    """(expf, logf, rsqrtf) of the engine as C function addresses, for a checker that wants the same arithmetic."""
+    L = lib()
+    return tuple(C.cast(getattr(L, n), C.c_void_p) for n in ("ava_host_expf", "ava_host_logf", "ava_host_rsqrtf"))
+
+
+class Model:
+    """`Model` of the reference for the one-token step: configuration + weights on one GPU."""
+
+    def __init__(self, cfg: dict, weights: dict | None = None, device: int = 0):
+        self.cfg = dict(cfg)
+        self.device = device
+        c = AvaConfig(**{k: cfg[k] for k in _config.FIELDS_I32 + _config.FIELDS_F32})
+        h = C.c_void_p()
+        rc = lib().ava_engine_create(C.byref(c), device, C.byref(h))
+        if rc != OK:
+            raise EngineError(rc, lib().ava_last_error(None).decode())
+        self.h = h
+        if weights is not None:
+            self.load(weights)
+
+    def _check(self, rc):
+        if rc == NOT_APPLICABLE:
+            why = lib().ava_engine_blocker(self.h)
+            raise NotApplicable(why.decode() if why else "not applicable")
+        if rc != OK:
+            raise EngineError(rc, lib().ava_last_error(self.h).decode())
+
+    def load(self, weights: dict):
+        """weights: name -> f32 array, or (int8 [din, dout], f32 scale [dout]); then `set_int8` + `set_fused`."""
+        L = lib()
+        for name, w in weights.items():
+            if isinstance(w, tuple):
+                q = np.ascontiguousarray(w[0], np.int8)
+                sc = _f32(w[1])
+                self._check(L.ava_engine_set_q8(self.h, name.encode(), _p(q, i8p), _p(sc), q.shape[0], q.shape[1]))
+            else:
+                a = _f32(w)
+                self._check(L.ava_engine_set_f32(self.h, name.encode(), _p(a), a.size))
+        self._check(L.ava_engine_finalize(self.h))
+
+    def fused_blocker(self):
+        why = lib().ava_engine_blocker(self.h)
+        return why.decode() if why else None
+
+    def state(self, rows: int, max_ctx: int = 4096) -> "State":
+        h = C.c_void_p()
+        self._check(lib().ava_state_new(self.h, rows, max_ctx, C.byref(h)))
+        return State(self, h)
+
+    def step(self, st: "State", tok) -> np.ndarray:
+        tok = np.ascontiguousarray(tok, np.uint32).reshape(-1)
+        assert tok.size == st.rows
+        logits = np.empty((st.rows, self.cfg["vocab"]), np.float32)
+        self._check(lib().ava_step(self.h, st.h, _p(tok, u32p), _p(logits)))
+        return logits
+
+    def step_greedy(self, st: "State", tok) -> np.ndarray:
+        tok = np.ascontiguousarray(tok, np.uint32).reshape(-1)
+        nxt = np.empty(st.rows, np.uint32)
+        self._check(lib().ava_step_greedy(self.h, st.h, _p(tok, u32p), _p(nxt, u32p)))
+        return nxt
+
+    def forward_with_state(self, ids, st: "State", last_only: bool = False) -> np.ndarray:
+        ids = np.ascontiguousarray(ids, np.uint32)
+        rows, t = ids.shape
+        assert rows == st.rows
+        V = self.cfg["vocab"]
+        logits = np.empty((rows, V) if last_only else (rows, t, V), np.float32)
+        self._check(lib().ava_forward_with_state(self.h, st.h, _p(ids, u32p), t, int(last_only), _p(logits)))
+        return logits
+
+    # device-resident form: raw device addresses (ints), nothing copied, nothing synchronised
+    def step_device(self, st: "State", tok_ptr: int, logits_ptr: int | None, next_ptr: int | None):
+        self._check(lib().ava_step_device(self.h, st.h, tok_ptr, logits_ptr, next_ptr))
+
+    def sync(self):
+        self._check(lib().ava_sync(self.h))
+
+    @property
+    def stream(self) -> int:
+        return lib().ava_engine_stream(self.h)
+
+    @property
+    def launches(self) -> int:
+        return lib().ava_engine_launches(self.h)
+
+    @property
+    def nbytes(self) -> int:
+        return lib().ava_engine_bytes(self.h)
+
+    def debug_keep(self, on: bool):
+        self._check(lib().ava_debug_keep(self.h, int(on)))
+
+    def debug_get(self, name: str, block: int, rows: int) -> np.ndarray:
+        w = lib().ava_debug_width(self.h, name.encode())
+        if w < 0:
+            raise KeyError(name)
+        out = np.empty((rows, w), np.float32)
+        self._check(lib().ava_debug_get(self.h, name.encode(), block, _p(out)))
+        return out
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib().ava_engine_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class State:
+    """`State` of the reference: the carried membranes, traces, fast weights and engram store of `rows` rows."""
+
+    def __init__(self, model: Model, h):
+        self.m = model
+        self.h = h
+
+    @property
+    def rows(self) -> int:
+        return lib().ava_state_rows(self.h)
+
+    @property
+    def nbytes(self) -> int:
+        return lib().ava_state_bytes(self.h)
+
+    def select(self, idx) -> "State":
+        idx = np.ascontiguousarray(idx, np.int32)
+        h = C.c_void_p()
+        self.m._check(lib().ava_state_select(self.h, _p(idx, i32p), idx.size, C.byref(h)))
+        return State(self.m, h)
+
+    @staticmethod
+    def cat(parts) -> "State":
+        arr = (C.c_void_p * len(parts))(*[p.h for p in parts])
+        h = C.c_void_p()
+        parts[0].m._check(lib().ava_state_cat(arr, len(parts), C.byref(h)))
+        return State(parts[0].m, h)
+
+    def seen(self, row: int) -> int:
+        return lib().ava_state_seen(self.h, row)
+
+    def get(self, row: int, name: str) -> np.ndarray:
+        n = lib().ava_state_len(self.h, row, name.encode())
+        if n < 0:
+            raise KeyError(name)
+        out = np.empty(n, np.float32)
+        if n:
+            self.m._check(lib().ava_state_export(self.h, row, name.encode(), _p(out)))
+        return out
+
+    def put(self, row: int, name: str, a):
+        a = _f32(a)
+        self.m._check(lib().ava_state_import(self.h, row, name.encode(), _p(a), a.size))
+
+    def close(self):
+        if getattr(self, "h", None) and getattr(self.m, "h", None):
+            lib().ava_state_destroy(self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# ---------------------------------------------------------------------------------------------- single operators
+def _rc(rc):
+    if rc == NOT_APPLICABLE:
+        raise NotApplicable("operator shape not covered")
+    if rc != OK:
+        raise EngineError(rc, "operator failed")
+
+
+def op_q8_matmul(x, q, scale, device=0):
+    x = _f32(x)
+    x2 = x.reshape(-1, x.shape[-1])
+    q = np.ascontiguousarray(q, np.int8)
+    scale = _f32(scale)
+    y = np.empty((x2.shape[0], q.shape[1]), np.float32)
+    _rc(lib().ava_op_q8_matmul(device, _p(x2), x2.shape[0], _p(q, i8p), _p(scale), q.shape[0], q.shape[1], _p(y)))
+    return y.reshape(x.shape[:-1] + (q.shape[1],))
+
+
+def op_rmsnorm(x, gain, device=0):
+    x = _f32(x)
+    x2 = x.reshape(-1, x.shape[-1])
+    y = np.empty_like(x2)
+    g = _f32(gain)
+    _rc(lib().ava_op_rmsnorm(device, _p(x2), _p(g), x2.shape[0], x2.shape[1], _p(y)))
+    return y.reshape(x.shape)
+
+
+def op_lif(cur, beta, v0, s0, theta=None, rho=None, gain=None, a0=None, spikes=2, device=0):
+    cur = _f32(cur)
+    m, d = cur.shape
+    arrs = [_f32(a) if a is not None else None for a in (beta, theta, rho, gain, v0, s0, a0)]
+    beta, theta, rho, gain, v0, s0, a0 = arrs
+    s1, v1 = np.empty((m, d), np.float32), np.empty((m, d), np.float32)
+    a1 = np.empty((m, d), np.float32) if rho is not None else None
+    _rc(lib().ava_op_lif(device, _p(cur), _p(beta), _p(theta), _p(rho), _p(gain), spikes, _p(v0), _p(s0), _p(a0), m, d,
+                         _p(s1), _p(v1), _p(a1)))
+    return s1, v1, a1
+
+
+def op_kwta(u, k, relu2, device=0):
+    u = _f32(u)
+    m, n = u.shape
+    a = np.empty_like(u)
+    _rc(lib().ava_op_kwta(device, _p(u), m, n, k, int(relu2), _p(a)))
+    return a
+
+
+def op_mem_heads(e, v, w, ah, qg, ex, qw, qa, f, device=0):
+    e, v, w, ah, qg, ex, qw, qa = map(_f32, (e, v, w, ah, qg, ex, qw, qa))
+    m, hs = e.shape
+    f = np.array(f, np.float32, copy=True).reshape(m, hs, hs)
+    y = np.empty((m, hs), np.float32)
+    _rc(lib().ava_op_mem_heads(device, m, hs, _p(e), _p(v), _p(w), _p(ah), _p(qg), _p(ex), _p(qw), _p(qa), _p(f), _p(y)))
+    return y, f
+
+
+def op_attend(q, kc, vc, bf16_store=False, device=0):
+    q, kc, vc = _f32(q), _f32(kc), _f32(vc)
+    m, n, hs = kc.shape
+    out = np.empty((m, hs), np.float32)
+    _rc(lib().ava_op_attend(device, m, n, hs, int(bf16_store), _p(q), _p(kc), _p(vc), _p(out)))
+    return out
+
+
+def op_math(which, x, device=0):
+    x = _f32(x).reshape(-1)
+    y = np.empty_like(x)
+    _rc(lib().ava_op_math(device, which, _p(x), x.size, _p(y)))
+    return y

@@ -1,0 +1,170 @@
+/* ava_engine.h — C ABI of the B200 engine for Ava's per-token block step.
+ *
+ * The reference (nochallenge/ava, crate design-tests/nn/gpu) has no FFI of its own: its seams are Rust-internal.
+ * Each entry point below names the reference interface it stands in for (file:line inside the reference project),
+ * so that a Rust `extern "C"` block can bind them one to one (see bindings/ava_engine.rs and INTEGRATION.md).
+ *
+ * Conventions
+ *   - plain pointers and sizes only; every buffer is HOST memory unless the name says `_device`;
+ *   - return value: 0 = done; 1 = AVA_NOT_APPLICABLE, the reference's `Ok(None)` convention ("this fast path does not
+ *     cover the model or state as it is set; nothing was changed", src/model/fstep.rs:61-101, fstep/arch.rs:42-129);
+ *     < 0 = error, text in ava_last_error();
+ *   - one host thread drives an engine (the reference's `Model` is !Sync, src/model.rs:398-423); the engine owns its
+ *     CUDA stream; states belong to the engine that made them;
+ *   - the library has no CPU fallback: without a CUDA device every compute call fails with AVA_ERR_CUDA.
+ */
+#ifndef AVA_ENGINE_H
+#define AVA_ENGINE_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AVA_OK 0
+#define AVA_NOT_APPLICABLE 1
+#define AVA_ERR_ARG (-1)
+#define AVA_ERR_CUDA (-2)
+#define AVA_ERR_STATE (-3)
+#define AVA_ERR_NONFINITE (-4)
+#define AVA_ERR_MISSING (-5)
+#define AVA_ERR_CAPACITY (-6)
+
+/* Shape and block options: the fields of the reference's `Config` (src/model.rs:158-177) and of `Arch`
+ * (src/arch.rs:149-197) that the one-token step reads. */
+typedef struct ava_config {
+    int32_t vocab;
+    int32_t d;              /* model width */
+    int32_t n_blocks;
+    int32_t hidden;         /* wide layer */
+    int32_t kwta_k;         /* units the k-winners-take-all keeps (hidden / kwta_div, src/model.rs:265-267) */
+    int32_t head_size;      /* fast-weight memory head size (--head-size); heads = d / head_size */
+    int32_t eng_block;      /* block with the engram read (Config::engram); -1: none */
+    int32_t eng_head_size;  /* engram head size (HEAD_SIZE = 32 in the reference, src/model.rs:43) */
+    int32_t eng_store_bf16; /* 1: keys and values are stored as bf16 (the reference stores f32) */
+    int32_t eng_cap;        /* EngramCap { max, rule: Oldest } (src/state.rs:46-49); 0: no cap */
+    int32_t gate_rank;      /* GATE_RANK (src/arch.rs:80) */
+    int32_t spikes;         /* Spikes: 0 binary, 1 ternary, 2 int2 */
+    int32_t alif;           /* --alif */
+    int32_t theta;          /* per-neuron thresholds present (--homeostasis) */
+    int32_t lif_scale;      /* --lif-scale */
+    int32_t value_residual; /* --value-residual */
+    int32_t relu2;          /* --mlp-act relu2 */
+    int32_t dense;          /* --residual dense */
+    int32_t out_gate;       /* 1: silu(h Wg) output gate (OutGate::Silu) */
+    float   mem_momentum;   /* --mem-momentum (0: off) */
+    float   slope;          /* --surrogate-slope (does not change forward values) */
+} ava_config;
+
+typedef struct ava_engine ava_engine;
+typedef struct ava_state ava_state;
+
+/* ---- model ------------------------------------------------------------------------------------------------ */
+
+/* `Model::new` for inference (src/model.rs:805-918): an engine for this configuration on CUDA device `device`. */
+int ava_engine_create(const ava_config* cfg, int device, ava_engine** out);
+void ava_engine_destroy(ava_engine* e);
+/* Text of the last error of this engine (never NULL). `e` NULL: the last error of engine creation on this thread. */
+const char* ava_last_error(const ava_engine* e);
+
+/* Weights by the reference's tensor names (src/model.rs:805-918, src/arch.rs:809-886): "tok_emb" [vocab, d],
+ * "final.norm" [d], "b{i}.mem.{norm,beta,theta,arho,again}" [d], "b{i}.hebb.{norm,off}" [d], "b{i}.hebb.{wa,wb}"
+ * [d, heads], "b{i}.hebb.{ba,bb}" [heads], "b{i}.hebb.{wa1,wb1}" [d, rank], "b{i}.hebb.{wa2,wb2}" [rank, d],
+ * "b{i}.hebb.vres" [2], "b{i}.eng.norm", "b{i}.mlp.norm" [d], "b{i}.dense" [i + 2].  `n` = number of floats. */
+int ava_engine_set_f32(ava_engine* e, const char* name, const float* data, int64_t n);
+/* An int8 matrix W [din, dout] row-major (applied x . W) with one f32 scale per output column — the product of
+ * `Model::set_int8` (src/model.rs:949-991) given directly: "b{i}.mem.{win,wout}", "b{i}.hebb.{wq,wk,wv,we,wg,wo}",
+ * "b{i}.eng.{wq,wk,wv,wo}", "b{i}.mlp.{w1,w2}", "head" [d, vocab]. */
+int ava_engine_set_q8(ava_engine* e, const char* name, const int8_t* q, const float* scale, int32_t din, int32_t dout);
+/* The same from f32 weights: quantised as `ava_parts::quant::quantize_int8` does (nn/parts/src/quant.rs:18-31). */
+int ava_engine_set_q8_from_f32(ava_engine* e, const char* name, const float* w, int32_t din, int32_t dout);
+/* `Model::set_int8(true)` + `set_fused(true)`: checks that every tensor is there, builds the output head from
+ * tok_emb^T when none was given (src/int8.rs:82-84), lays the weights out in device memory.  AVA_NOT_APPLICABLE when
+ * the configuration has an option the engine does not cover (`Model::fused_blocker`, src/model/fstep.rs:61-101). */
+int ava_engine_finalize(ava_engine* e);
+/* `Model::fused_blocker`: why the engine does not cover this configuration, or NULL. */
+const char* ava_engine_blocker(const ava_engine* e);
+
+/* ---- carried state (src/state.rs:94-116) --------------------------------------------------------------------- */
+
+/* `Model::state(rows)` (src/state.rs:593): zero membranes, spikes, traces and fast weights, empty engram store with
+ * room for `max_ctx` tokens per row (the oldest-first cap, when set, bounds it instead). */
+int ava_state_new(ava_engine* e, int32_t rows, int32_t max_ctx, ava_state** out);
+void ava_state_destroy(ava_state* s);
+int32_t ava_state_rows(const ava_state* s);
+/* `State::select` (src/state.rs:129-203): rows idx[0..n) as a new state; a repeated row is a fork. */
+int ava_state_select(const ava_state* s, const int32_t* idx, int32_t n, ava_state** out);
+/* `State::cat` (src/state.rs:207-328): the rows of `parts` one after another as a new state. */
+int ava_state_cat(const ava_state* const* parts, int32_t n, ava_state** out);
+/* Tokens row `row` has read (`State::seen`). */
+int64_t ava_state_seen(const ava_state* s, int32_t row);
+/* Tensors of one row by the reference's saved-state names (src/state.rs:1150-1202): "lif.{i}.v|s|a" [d],
+ * "mem.{i}.f|s" [heads, hs, hs], "eng.k|v" [eng heads, n, eng hs] (f32 values; a bf16 store is widened). */
+int64_t ava_state_len(const ava_state* s, int32_t row, const char* name);
+int ava_state_export(const ava_state* s, int32_t row, const char* name, float* out);
+int ava_state_import(ava_state* s, int32_t row, const char* name, const float* in, int64_t n);
+
+/* ---- the hot path --------------------------------------------------------------------------------------------- */
+
+/* `Model::step(&mut Stream, tok)` (src/model.rs:1260-1272 -> fstep::arch::step, src/model/fstep/arch.rs:478) for every
+ * row of `s` at once: one token per row, logits [rows, vocab].  The rows are independent (src/state.rs:13-15). */
+int ava_step(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits);
+/* The same, returning only each row's greedy next token (lowest index on ties). */
+int ava_step_greedy(ava_engine* e, ava_state* s, const uint32_t* tok, uint32_t* next);
+/* `Model::forward_with_state(ids [rows, t], &mut State)` (src/state.rs:684): t tokens per row.  logits [rows, t,
+ * vocab], or [rows, vocab] of the last position when last_only (what `Model::feed` keeps, src/model.rs:1218-1227). */
+int ava_forward_with_state(ava_engine* e, ava_state* s, const uint32_t* ids, int32_t t, int32_t last_only, float* logits);
+
+/* Device-resident forms for callers that keep tokens and logits in GPU memory (no host copies, no synchronise):
+ * tok_device [rows] u32, logits_device [rows, vocab] f32 or NULL, next_device [rows] u32 or NULL.  Work is queued on
+ * the engine's stream; ava_sync waits for it and returns the step's status. */
+int ava_step_device(ava_engine* e, ava_state* s, const uint32_t* tok_device, float* logits_device, uint32_t* next_device);
+int ava_sync(ava_engine* e);
+/* The engine's cudaStream_t (for timing with CUDA events on the launching stream). */
+void* ava_engine_stream(ava_engine* e);
+/* Kernels launched by this engine since it was made. */
+int64_t ava_engine_launches(const ava_engine* e);
+/* Bytes of device memory the engine (weights, work buffers) and a state hold. */
+int64_t ava_engine_bytes(const ava_engine* e);
+int64_t ava_state_bytes(const ava_state* s);
+
+/* Per-block intermediates of the last step (row-major [rows, width] f32 copied to host), for teacher-forced parity
+ * checks — the side-band of `Model::step_trace` (src/model/fstep/arch.rs:420-450).  Names: "h_lif", "spikes",
+ * "x_lif", "h_mem", "qkveg", "y_raw", "y", "x_mem", "eng_qkv", "eng_o", "u", "a", "x_out".  Call ava_debug_keep(e, 1)
+ * before the step; widths via ava_debug_width. */
+int ava_debug_keep(ava_engine* e, int32_t on);
+int64_t ava_debug_width(const ava_engine* e, const char* name);
+int ava_debug_get(ava_engine* e, const char* name, int32_t block, float* out);
+
+/* ---- single operators on host buffers (the S1 operator seam and the per-op kernels, for parity tests) ---------- */
+
+/* `QW::matmul_rows` (src/int8.rs:124): y [m, dout] = x [m, din] . W.  Same bits as the reference's ordered sum. */
+int ava_op_q8_matmul(int device, const float* x, int32_t m, const int8_t* q, const float* scale, int32_t din, int32_t dout, float* y);
+/* `fstep::rmsnorm` (src/model/fstep.rs:207-220) on m rows of n. */
+int ava_op_rmsnorm(int device, const float* x, const float* gain, int32_t m, int32_t n, float* y);
+/* `fstep::arch::lif` (src/model/fstep/arch.rs:173-228) on m rows of d; theta/rho/gain/a0/a1 may be NULL. */
+int ava_op_lif(int device, const float* cur, const float* beta, const float* theta, const float* rho, const float* gain,
+               int32_t spikes, const float* v0, const float* s0, const float* a0, int32_t m, int32_t d, float* s1, float* v1,
+               float* a1);
+/* kth_largest + mask + relu(^2) (src/model/fstep.rs:295-299, src/model/fstep/arch.rs:982-989) on m rows of n. */
+int ava_op_kwta(int device, const float* u, int32_t m, int32_t n, int32_t k, int32_t relu2, float* a);
+/* `head_rows` without momentum (src/model/fstep/arch.rs:256-337) for m independent heads of size hs:
+ * e, v, w, ah, qg, ex [m, hs]; qw, qa [m]; f [m, hs, hs] updated in place; y [m, hs]. */
+int ava_op_mem_heads(int device, int32_t m, int32_t hs, const float* e, const float* v, const float* w, const float* ah,
+                     const float* qg, const float* ex, const float* qw, const float* qa, float* f, float* y);
+/* `attend` (src/model/fstep.rs:303-327) for m heads over n keys/values of hs (f32, or rounded to bf16 first). */
+int ava_op_attend(int device, int32_t m, int32_t n, int32_t hs, int32_t bf16_store, const float* q, const float* kc,
+                  const float* vc, float* out);
+
+/* The engine's exp / ln / x^-1/2, evaluated on the host with the operation sequence the kernels use (same bits). */
+float ava_host_expf(float x);
+float ava_host_logf(float x);
+float ava_host_rsqrtf(float x);
+/* The same evaluated on the device, n values (tests that host and device agree bit for bit). which: 0 exp, 1 ln, 2 x^-1/2. */
+int ava_op_math(int device, int32_t which, const float* x, int64_t n, float* y);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

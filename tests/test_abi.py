@@ -1,0 +1,99 @@
+"""CPU checks of the C-ABI library: it loads, exports every symbol the header declares, its host arithmetic is what the
+kernels use, and without a GPU it fails loudly instead of falling back to anything."""
+import ctypes as C
+import math
+import os
+import re
+
+import numpy as np
+import pytest
+
+from ava_b200 import build, config, engine
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def L():
+    build.build()
+    return engine.lib()
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "ava_engine.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ava_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(L):
+    names = declared_symbols()
+    assert len(names) >= 35
+    for n in names:
+        assert hasattr(L, n), n
+    assert set(names) == set(engine.EXPORTS)
+
+
+def test_each_entry_point_cites_the_reference():
+    text = open(os.path.join(ROOT, "include", "ava_engine.h")).read()
+    assert text.count("src/") >= 20
+
+
+def test_host_math_is_close_to_libm(L):
+    xs = np.concatenate([np.linspace(-100, 88, 4001), np.array([0.0, -0.0, 1e-30, -1e-30, 88.7, -103.9])]).astype(np.float32)
+    for x in xs:
+        got, want = L.ava_host_expf(float(x)), math.exp(float(x))
+        if want > 1e-37:
+            assert abs(got - want) <= 2.5e-7 * want, (x, got, want)
+        else:
+            assert abs(got - want) < 1e-38
+    assert L.ava_host_expf(float("inf")) == float("inf") and L.ava_host_expf(float("-inf")) == 0.0
+    assert math.isnan(L.ava_host_expf(float("nan")))
+    for x in np.concatenate([np.logspace(-38, 38, 3001), np.linspace(0.5, 2.5, 2001)]).astype(np.float32):
+        got, want = L.ava_host_logf(float(x)), math.log(float(x))
+        assert abs(got - want) <= 2.5e-7 * max(abs(want), 0.3), (x, got, want)
+    assert L.ava_host_logf(1.0) == 0.0 and L.ava_host_logf(0.0) == float("-inf") and math.isnan(L.ava_host_logf(-1.0))
+    for x in np.logspace(-30, 30, 2001).astype(np.float32):
+        got, want = L.ava_host_rsqrtf(float(x)), float(x) ** -0.5
+        assert abs(got - want) <= 1.3e-7 * want
+
+
+def test_oracle_accepts_the_engines_math(L, orc):
+    """The checker can run on the engine's exp / ln / x^-1/2, and doing so only moves results by rounding."""
+    cfg = config.tiny()
+    from ava_b200 import synth
+    m = orc.OracleModel(cfg, synth.model(cfg, 0, "awake"))
+    ids = synth.token_ids(cfg["vocab"], 1, 4)
+    a = m.state(1).forward(ids)
+    try:
+        orc.set_math(*engine.host_math())
+        m2 = orc.OracleModel(cfg, synth.model(cfg, 0, "awake"))
+        b = m2.state(1).forward(ids)
+    finally:
+        orc.reset_math()
+    np.testing.assert_allclose(a[0, 0], b[0, 0], rtol=0, atol=1e-5)
+
+
+def test_no_gpu_means_an_error_not_a_fallback(L):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(engine.EngineError) as ei:
+        engine.Model(config.tiny())
+    assert ei.value.code == engine.ERR_CUDA and "no CPU path" in str(ei.value)
+    x = np.zeros((1, 16), np.float32)
+    with pytest.raises(engine.EngineError):
+        engine.op_q8_matmul(x, np.zeros((16, 4), np.int8), np.ones(4, np.float32))
+
+
+def test_product_does_not_touch_the_oracle():
+    """Nothing under the package may import, link or name the oracle."""
+    pkg = os.path.join(ROOT, "ava_b200")
+    for dp, _, files in os.walk(pkg):
+        if os.path.basename(dp) == "build":
+            continue
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dp, f)).read()
+                assert "oracle" not in text.lower().replace("a checker", ""), os.path.join(dp, f)
+    out = os.popen(f"ldd {engine.LIB_PATH}").read()
+    assert "oracle" not in out

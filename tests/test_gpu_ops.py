@@ -1,0 +1,178 @@
+"""Each CUDA kernel against the CPU oracle on the same seeded inputs, through the C ABI (teacher-forced: the kernel gets
+exactly the inputs the oracle's function gets).  Integer and ordered-sum work must agree bit for bit; where exp / ln /
+x^-1/2 enter, the oracle is run on the engine's own host arithmetic, which makes those bit-exact too."""
+import numpy as np
+import pytest
+
+from ava_b200 import build, config, engine
+
+pytestmark = pytest.mark.gpu
+
+
+def bits(a):
+    return np.ascontiguousarray(a, np.float32).view(np.uint32)
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _lib():
+    build.build()
+    engine.lib()
+
+
+@pytest.fixture()
+def orc_same_math(orc):
+    orc.set_math(*engine.host_math())
+    yield orc
+    orc.reset_math()
+
+
+def test_device_math_equals_host_math():
+    L = engine.lib()
+    rng = np.random.default_rng(0)
+    x = np.concatenate([rng.uniform(-104, 89, 200000), rng.normal(0, 1, 100000), [0.0, -0.0, np.inf, -np.inf, np.nan, 88.72, -103.9]]).astype(np.float32)
+    got = engine.op_math(0, x)
+    want = np.array([L.ava_host_expf(float(v)) for v in x[:5000]], np.float32)
+    assert np.array_equal(bits(got[:5000]), bits(want))
+    tail = np.array([L.ava_host_expf(float(v)) for v in x[-7:]], np.float32)
+    assert np.array_equal(bits(got[-7:]), bits(tail))
+    y = np.abs(np.concatenate([rng.lognormal(0, 20, 100000), rng.uniform(0.4, 2.6, 100000), [0.0, 1.0, np.inf, 1e-40]])).astype(np.float32)
+    got = engine.op_math(1, y)
+    idx = np.r_[0:3000, 100000:103000, y.size - 4:y.size]
+    want = np.array([L.ava_host_logf(float(v)) for v in y[idx]], np.float32)
+    assert np.array_equal(bits(got[idx]), bits(want))
+    got = engine.op_math(2, y[:100000] + np.float32(1e-30))
+    want = np.array([L.ava_host_rsqrtf(float(v)) for v in (y[:3000] + np.float32(1e-30))], np.float32)
+    assert np.array_equal(bits(got[:3000]), bits(want))
+
+
+@pytest.mark.parametrize("m,din,dout", [(1, 128, 64), (5, 768, 768), (70, 768, 3840), (256, 3072, 768), (33, 128, 320), (256, 768, 4112)])
+def test_q8_matmul_bits(orc, m, din, dout):
+    rng = np.random.default_rng(m * 7 + dout)
+    q = rng.integers(-127, 128, (din, dout)).astype(np.int8)
+    sc = (rng.uniform(0.5, 1.5, dout) / 127).astype(np.float32)
+    x = rng.normal(size=(m, din)).astype(np.float32)
+    if m > 2:
+        x[1] = 0.0
+        x[2] = rng.integers(-2, 3, din)   # spikes: the sum is an exact integer
+        x[0, ::5] = -0.0
+    orc.set_threads(8)
+    try:
+        want = orc.q8_matmul(x, q, sc)
+    finally:
+        orc.set_threads(1)
+    got = engine.op_q8_matmul(x, q, sc)
+    assert np.array_equal(bits(got), bits(want))
+    if m > 2:
+        exact = (x[2].astype(np.int64) @ q.astype(np.int64)).astype(np.float32) * sc
+        assert np.array_equal(bits(got[2]), bits(exact))
+
+
+@pytest.mark.parametrize("m,n", [(1, 64), (7, 768), (300, 2048)])
+def test_rmsnorm_bits(orc_same_math, m, n):
+    rng = np.random.default_rng(n)
+    x = (rng.normal(size=(m, n)) * rng.uniform(0.01, 30, (m, 1))).astype(np.float32)
+    g = rng.uniform(0.5, 1.5, n).astype(np.float32)
+    want = np.stack([orc_same_math.rmsnorm(x[r], g) for r in range(m)])
+    assert np.array_equal(bits(engine.op_rmsnorm(x, g)), bits(want))
+
+
+@pytest.mark.parametrize("spikes", [0, 1, 2])
+@pytest.mark.parametrize("alif", [False, True])
+def test_lif_exact(orc, spikes, alif):
+    rng = np.random.default_rng(spikes * 2 + alif)
+    m, d = 9, 768
+    cur = rng.normal(0, 1.2, (m, d)).astype(np.float32)
+    beta = rng.uniform(0.8, 0.99, d).astype(np.float32)
+    th = rng.uniform(0.8, 1.2, d).astype(np.float32)
+    v0 = rng.normal(0, 1, (m, d)).astype(np.float32)
+    s0 = rng.integers(-2, 3, (m, d)).astype(np.float32) if spikes == 2 else rng.integers(0, 2, (m, d)).astype(np.float32)
+    kw = {}
+    if alif:
+        kw = dict(rho=rng.uniform(0.9, 0.99, d).astype(np.float32), gain=rng.uniform(0.5, 1.5, d).astype(np.float32))
+        a0 = rng.uniform(0, 1, (m, d)).astype(np.float32)
+    # some membranes exactly on a threshold
+    cur[0, :8] = 0.0
+    v0[0, :8] = 0.0
+    s1, v1, a1 = engine.op_lif(cur, beta, v0, s0, theta=th, a0=a0 if alif else None, spikes=spikes, **kw)
+    for r in range(m):
+        ws, wv, wa = orc.lif(cur[r], beta, v0[r], s0[r], theta=th, a0=a0[r] if alif else None, spikes=spikes, **kw)
+        assert np.array_equal(s1[r], ws)
+        assert np.array_equal(bits(v1[r]), bits(wv))
+        if alif:
+            assert np.array_equal(bits(a1[r]), bits(wa))
+
+
+def test_lif_hand_vectors():
+    """The reference's hand-worked spikes (arch/tests.rs:431-445) through the kernel."""
+    cur = [2.5, -1.2, 0.3, -3.0, 1.0, 0.99]
+    for spikes, want in ((1, [1, -1, 1, -1, 1, 0]), (2, [2, -2, 2, -2, 2, -1]), (0, [1, 0, 0, 0, 1, 0])):
+        v = np.zeros((1, 1), np.float32)
+        s = np.zeros((1, 1), np.float32)
+        got = []
+        for i in cur:
+            s, v, _ = engine.op_lif(np.array([[i]], np.float32), np.zeros(1, np.float32), v, s, spikes=spikes)
+            got.append(float(s[0, 0]))
+        assert got == [float(w) for w in want]
+
+
+@pytest.mark.parametrize("n,k", [(256, 64), (3072, 768), (8192, 2048), (1000, 999), (64, 64)])
+@pytest.mark.parametrize("relu2", [0, 1])
+def test_kwta_exact(orc, n, k, relu2):
+    rng = np.random.default_rng(n + k)
+    m = 6
+    u = rng.normal(size=(m, n)).astype(np.float32)
+    u[1, : n // 2] = u[1, 0]            # a big tie
+    u[2] = -np.abs(u[2])                # all negative
+    u[3, ::3] = 0.0
+    u[3, 1::3] = -0.0
+    u[4] = np.round(u[4] * 4) / 4       # many ties at the threshold
+    got = engine.op_kwta(u, k, relu2)
+    for r in range(m):
+        want = orc.kwta(u[r], k, relu2)
+        assert np.array_equal(got[r] != 0, want != 0), r
+        assert np.array_equal(got[r], want), r
+
+
+@pytest.mark.parametrize("hs,m", [(32, 5), (64, 12), (128, 3), (256, 2), (768, 3)])
+def test_mem_heads_bits(orc, hs, m):
+    rng = np.random.default_rng(hs)
+    unit = lambda x: (x / np.sqrt((x * x).sum(-1, keepdims=True))).astype(np.float32)
+    e = unit(rng.normal(size=(m, hs)))
+    k = unit(rng.normal(size=(m, hs)))
+    q = unit(rng.normal(size=(m, hs)))
+    v = rng.normal(size=(m, hs)).astype(np.float32)
+    ex = rng.uniform(0.9, 1.0, (m, hs)).astype(np.float32)
+    be = rng.uniform(0.05, 1.5, (m, hs)).astype(np.float32)
+    w, ah, qg = k * be, e * (be * ex), q * ex
+    qw = rng.normal(size=m).astype(np.float32)
+    qa = rng.normal(size=m).astype(np.float32)
+    f = rng.normal(0, 0.3, (m, hs, hs)).astype(np.float32)
+    f[0] = 0.0
+    y, f1 = engine.op_mem_heads(e, v, w, ah, qg, ex, qw, qa, f)
+    for i in range(m):
+        wy, wf, _ = orc.head_rows(e[i], v[i], w[i], ah[i], qg[i], ex[i], float(qw[i]), float(qa[i]), f[i])
+        assert np.array_equal(bits(y[i]), bits(wy)), i
+        assert np.array_equal(bits(f1[i]), bits(wf)), i
+    # twice over the same state: the second call reads what the first wrote
+    y2, f2 = engine.op_mem_heads(e, v, w, ah, qg, ex, qw, qa, f1)
+    wy, wf, _ = orc.head_rows(e[1], v[1], w[1], ah[1], qg[1], ex[1], float(qw[1]), float(qa[1]), f1[1])
+    assert np.array_equal(bits(f2[1]), bits(wf)) and np.array_equal(bits(y2[1]), bits(wy))
+
+
+@pytest.mark.parametrize("n", [1, 2, 3, 70, 1500])
+@pytest.mark.parametrize("bf16", [False, True])
+def test_attend_bits(orc_same_math, n, bf16):
+    orc = orc_same_math
+    rng = np.random.default_rng(n)
+    m, hs = 12, 64
+    q = rng.normal(size=(m, hs)).astype(np.float32)
+    kc = rng.normal(size=(m, n, hs)).astype(np.float32)
+    vc = rng.normal(size=(m, n, hs)).astype(np.float32)
+    got = engine.op_attend(q, kc, vc, bf16)
+    if bf16:
+        rb = np.vectorize(orc.bf16_round, otypes=[np.float32])
+        kc, vc = rb(kc), rb(vc)
+    scale = np.float32(1.0 / np.sqrt(float(hs)))
+    for hh in range(m):
+        want = orc.attend(q[hh], kc[hh], vc[hh], scale)
+        assert np.array_equal(bits(got[hh]), bits(want)), hh

@@ -1,0 +1,265 @@
+"""The whole block step on the GPU against the CPU oracle, through the C ABI, in the manner of the reference's own
+tests (design-tests/nn/gpu/src/model/fstep/arch_tests.rs:72-135: every logit and the whole state over hundreds of
+tokens; src/state/tests.rs:146-197: rows independent, select forks, cat joins).
+
+With the oracle on the engine's exp / ln / x^-1/2 every value must be the same bits: logits, membranes, spikes, traces,
+fast weights, engram store.  With the oracle on libm the first token must agree to 1e-5 (later tokens of a spiking
+model may part ways at a threshold tie, which the reference documents: int8/tests.rs:276-283)."""
+import numpy as np
+import pytest
+
+from ava_b200 import build, config, engine, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def bits(a):
+    return np.ascontiguousarray(a, np.float32).view(np.uint32)
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _lib():
+    build.build()
+    engine.lib()
+
+
+@pytest.fixture()
+def orc_same_math(orc):
+    orc.set_math(*engine.host_math())
+    yield orc
+    orc.reset_math()
+
+
+STATE_NAMES = lambda cfg: [f"lif.{i}.{k}" for i in range(cfg["n_blocks"]) for k in (("v", "s", "a") if cfg["alif"] else ("v", "s"))] + \
+    [f"mem.{i}.f" for i in range(cfg["n_blocks"])] + (["eng.k", "eng.v"] if cfg["eng_block"] >= 0 else [])
+
+
+def assert_same_state(cfg, gs, os_, rows):
+    for r in range(rows):
+        for name in STATE_NAMES(cfg):
+            a, b = gs.get(r, name), os_.get(r, name)
+            assert a.shape == b.shape, (name, a.shape, b.shape)
+            assert np.array_equal(bits(a), bits(b)), (r, name, float(np.abs(a - b).max()))
+
+
+def pair(orc, cfg, seed=0, recipe="awake"):
+    w = synth.model(cfg, seed, recipe)
+    return engine.Model(cfg, w), orc.OracleModel(cfg, w)
+
+
+CONFIGS = {
+    "ava04_small": dict(),                                                            # 4 heads of 32, engram 4 x 32 f32
+    "one_head_bf16": dict(head_size=128, eng_head_size=64, eng_store_bf16=1),         # the benchmark's corner
+    "binary_plain": dict(spikes=0, alif=0, theta=0, value_residual=0, dense=0, relu2=0, lif_scale=0, out_gate=0),
+    "ternary_no_engram": dict(spikes=1, eng_block=-1, head_size=64),
+    "wide_rank2": dict(d=256, head_size=256, gate_rank=2, eng_block=0, hidden=512, kwta_k=64),
+}
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_step_is_the_oracles_bits(orc_same_math, name):
+    orc = orc_same_math
+    cfg = config.tiny(**CONFIGS[name])
+    gm, om = pair(orc, cfg)
+    rows, T = 3, 60
+    ids = synth.token_ids(cfg["vocab"], rows, T, seed0=11)
+    gs, os_ = gm.state(rows, max_ctx=T + 4), om.state(rows)
+    for t in range(T):
+        lg = gm.step(gs, ids[:, t])
+        lo = os_.step(ids[:, t])
+        assert np.array_equal(bits(lg), bits(lo)), (t, float(np.abs(lg - lo).max()))
+    assert_same_state(cfg, gs, os_, rows)
+    assert [gs.seen(r) for r in range(rows)] == [T] * rows
+    # spikes were really signed integers and the k-WTA really sparse
+    s = gs.get(0, "lif.1.s")
+    assert set(np.unique(s)).issubset({-2.0, -1.0, 0.0, 1.0, 2.0}) and (s != 0).any()
+
+
+def test_intermediates_match_teacher_forced(orc_same_math):
+    orc = orc_same_math
+    cfg = config.tiny()
+    gm, om = pair(orc, cfg, seed=3)
+    ids = synth.token_ids(cfg["vocab"], 2, 12, seed0=5)
+    gs, os_ = gm.state(2, 32), om.state(2)
+    gm.debug_keep(True)
+    orc.trace_enable(True)
+    try:
+        for t in range(12):
+            gm.step(gs, ids[:, t])
+            os_.step(ids[:, t])
+        for blk in range(cfg["n_blocks"]):
+            for name in ("h_lif", "spikes", "x_lif", "h_mem", "qkveg", "ek", "w", "ah", "qg", "ex", "qw", "qa", "y_raw", "y", "x_mem", "u", "a", "x_out"):
+                got = gm.debug_get(name, blk, 2)[0]
+                want = orc.trace(name, blk)
+                assert np.array_equal(bits(got), bits(want)), (blk, name)
+            a = gm.debug_get("a", blk, 2)[0]
+            assert (a != 0).sum() <= cfg["kwta_k"] + 8 and (a >= 0).all()
+        assert np.array_equal(bits(gm.debug_get("eng_o", cfg["eng_block"], 2)[0]), bits(orc.trace("eng_o", cfg["eng_block"])))
+    finally:
+        orc.trace_enable(False)
+        gm.debug_keep(False)
+
+
+def test_first_token_against_libm_oracle(orc):
+    """The oracle on the platform's libm, as the reference runs: agreement to rounding on a fresh state."""
+    cfg = config.tiny()
+    gm, om = pair(orc, cfg, seed=1)
+    ids = synth.token_ids(cfg["vocab"], 4, 1, seed0=2)
+    lg = gm.step(gm.state(4, 8), ids[:, 0])
+    lo = om.state(4).step(ids[:, 0])
+    np.testing.assert_allclose(lg, lo, rtol=0, atol=1e-5 * max(1.0, float(np.abs(lo).max())))
+
+
+def test_forward_with_state_equals_steps(orc_same_math):
+    orc = orc_same_math
+    cfg = config.tiny()
+    gm, om = pair(orc, cfg, seed=2)
+    ids = synth.token_ids(cfg["vocab"], 3, 17, seed0=9)
+    gs = gm.state(3, 64)
+    all_logits = gm.forward_with_state(ids, gs)
+    want = om.state(3).forward(ids)
+    assert np.array_equal(bits(all_logits), bits(want))
+    gs2 = gm.state(3, 64)
+    last = gm.forward_with_state(ids, gs2, last_only=True)
+    assert np.array_equal(bits(last), bits(want[:, -1]))
+    # pieces == one pass (src/state/tests.rs:105-123)
+    gs3 = gm.state(3, 64)
+    gm.forward_with_state(ids[:, :6], gs3)
+    tail = gm.forward_with_state(ids[:, 6:], gs3)
+    assert np.array_equal(bits(tail), bits(want[:, 6:]))
+
+
+def test_rows_independent_select_forks_cat_joins(orc_same_math):
+    orc = orc_same_math
+    cfg = config.tiny()
+    gm, om = pair(orc, cfg, seed=4)
+    ids = synth.token_ids(cfg["vocab"], 3, 10, seed0=1)
+    gs = gm.state(3, 64)
+    batch = gm.forward_with_state(ids, gs)
+    for r in range(3):
+        one = gm.forward_with_state(ids[r:r + 1], gm.state(1, 64))
+        assert np.array_equal(bits(one[0]), bits(batch[r]))
+    # select(&[0, 0]) forks one prompt state into two continuations
+    two = gs.select([0, 0])
+    a = gm.step(two, np.array([5, 9], np.uint32))
+    b = gm.step(gs.select([0]), np.array([9], np.uint32))
+    assert np.array_equal(bits(a[1]), bits(b[0])) and not np.array_equal(a[0], a[1])
+    # cat of rows with different lengths continues each row correctly
+    s_short, s_long = gm.state(1, 64), gm.state(1, 64)
+    gm.forward_with_state(ids[0:1, :4], s_short)
+    gm.forward_with_state(ids[1:2, :9], s_long)
+    joined = engine.State.cat([s_short, s_long])
+    assert joined.rows == 2 and [joined.seen(0), joined.seen(1)] == [4, 9]
+    nxt = np.array([7, 8], np.uint32)
+    lj = gm.step(joined, nxt)
+    assert np.array_equal(bits(lj[0]), bits(gm.step(s_short, nxt[:1])[0]))
+    assert np.array_equal(bits(lj[1]), bits(gm.step(s_long, nxt[1:])[0]))
+    # the oracle agrees on the joined rows
+    o = om.state(1)
+    o.forward(ids[1:2, :9])
+    assert np.array_equal(bits(lj[1]), bits(o.step(nxt[1:])[0]))
+
+
+def test_engram_cap_drops_the_oldest(orc_same_math):
+    orc = orc_same_math
+    cfg = config.tiny(eng_cap=6)
+    gm, om = pair(orc, cfg, seed=6)
+    ids = synth.token_ids(cfg["vocab"], 2, 20, seed0=3)
+    gs, os_ = gm.state(2, 0), om.state(2)
+    lg = gm.forward_with_state(ids, gs)
+    lo = os_.forward(ids)
+    assert np.array_equal(bits(lg), bits(lo))
+    assert gs.get(0, "eng.k").size == cfg["d"] * 6
+    assert_same_state(cfg, gs, os_, 2)
+
+
+def test_state_export_import_round_trip(orc_same_math):
+    orc = orc_same_math
+    cfg = config.tiny(eng_store_bf16=1)
+    gm, om = pair(orc, cfg, seed=8)
+    ids = synth.token_ids(cfg["vocab"], 1, 9, seed0=4)
+    gs = gm.state(1, 32)
+    gm.forward_with_state(ids, gs)
+    fresh = gm.state(1, 32)
+    for name in STATE_NAMES(cfg):
+        fresh.put(0, name, gs.get(0, name))
+    nxt = np.array([3], np.uint32)
+    assert np.array_equal(bits(gm.step(fresh, nxt)), bits(gm.step(gs, nxt)))
+
+
+def test_greedy_is_the_lowest_argmax(orc_same_math):
+    cfg = config.tiny()
+    gm, om = pair(orc_same_math, cfg, seed=5)
+    ids = synth.token_ids(cfg["vocab"], 4, 3, seed0=6)
+    g1, g2 = gm.state(4, 16), gm.state(4, 16)
+    for t in range(3):
+        lg = gm.step(g1, ids[:, t])
+        nx = gm.step_greedy(g2, ids[:, t])
+        assert np.array_equal(nx, lg.argmax(1).astype(np.uint32))
+
+
+def test_errors_and_not_applicable(orc):
+    cfg = config.tiny()
+    w = synth.model(cfg, 0, "awake")
+    gm = engine.Model(cfg, w)
+    st = gm.state(2, 4)
+    with pytest.raises(engine.EngineError) as ei:
+        gm.step(st, np.array([1, cfg["vocab"]], np.uint32))
+    assert ei.value.code == engine.ERR_ARG
+    other = engine.Model(cfg, w)
+    with pytest.raises(engine.EngineError) as ei:
+        other.step(st, np.array([1, 2], np.uint32))
+    assert ei.value.code == engine.ERR_STATE
+    for t in range(4):
+        gm.step(st, np.array([1, 2], np.uint32))
+    with pytest.raises(engine.EngineError) as ei:          # the engram store is full: refused before anything moves
+        gm.step(st, np.array([1, 2], np.uint32))
+    assert ei.value.code == engine.ERR_CAPACITY and st.seen(0) == 4
+    missing = dict(w)
+    del missing["b1.mlp.w2"]
+    with pytest.raises(engine.EngineError) as ei:
+        engine.Model(cfg, missing)
+    assert ei.value.code == engine.ERR_MISSING and "b1.mlp.w2" in str(ei.value)
+    # an option outside the engine: the reference's "does not apply" answer, with the reason
+    mom = config.tiny(mem_momentum=0.5)
+    with pytest.raises(engine.NotApplicable) as ei:
+        engine.Model(mom, synth.model(mom, 0, "awake"))
+    assert "momentum" in str(ei.value)
+
+
+def test_nonfinite_gate_is_reported(orc):
+    cfg = config.tiny()
+    w = synth.model(cfg, 0, "awake")
+    w["b1.hebb.off"] = np.full(cfg["d"], np.nan, np.float32)
+    gm = engine.Model(cfg, w)
+    with pytest.raises(engine.EngineError) as ei:
+        gm.step(gm.state(1, 4), np.array([1], np.uint32))
+    assert ei.value.code == engine.ERR_NONFINITE
+    om = orc.OracleModel(cfg, w)
+    os_ = om.state(1)
+    os_.step(np.array([1], np.uint32))
+    assert os_.last_status == 1 and os_.seen(0) == 0
+
+
+@pytest.mark.parametrize("rows", [1, 40])
+def test_benchmark_shape_bits(orc_same_math, rows):
+    """The Ava-0.4-shaped benchmark model itself (12 blocks, d 768, one 768x768 fast-synapse matrix per block, engram of
+    12 x 64 in bf16), a few tokens, every bit."""
+    orc = orc_same_math
+    cfg = config.ava04_shaped()
+    w = synth.model(cfg, 0, "bench")
+    gm, om = engine.Model(cfg, w), orc.OracleModel(cfg, w)
+    orc.set_threads(8)
+    try:
+        T = 6 if rows == 1 else 3
+        ids = synth.token_ids(cfg["vocab"], rows, T)
+        gs, os_ = gm.state(rows, 16), om.state(rows)
+        for t in range(T):
+            lg = gm.step(gs, ids[:, t])
+            lo = os_.step(ids[:, t])
+            assert np.array_equal(bits(lg), bits(lo)), (t, float(np.abs(lg - lo).max()))
+        for r in (0, rows - 1):
+            for name in ("lif.0.v", "lif.11.s", "lif.6.a", "mem.0.f", "mem.11.f", "eng.k", "eng.v"):
+                assert np.array_equal(bits(gs.get(r, name)), bits(os_.get(r, name))), (r, name)
+    finally:
+        orc.set_threads(1)
