@@ -90,7 +90,7 @@ AVA_HD float pow2i(int n) { return bits_to_f((uint32_t)(n + 127) << 23); }
 // e^x: x = n ln2 + r, |r| <= ln2/2, a degree-6 polynomial in r, then two exact scalings by powers of two (two, so
 // that results in the subnormal range round once, at the last multiply).
 AVA_HD float expf_(float x) {
-    if (x != x) return add(x, x);
+    if (x != x) return bits_to_f(0x7fc00000u);
     if (x > 88.72283935546875f) return bits_to_f(0x7f800000u);
     if (x < -103.972076416015625f) return 0.0f;
     const float n = ::rintf(mul(x, 1.44269504088896341f));
@@ -113,7 +113,7 @@ AVA_HD float expf_(float x) {
 // ln x for finite x > 0 (else the IEEE special values): x = m 2^e with m in [sqrt(1/2), sqrt 2), a degree-8
 // polynomial in m - 1.
 AVA_HD float logf_(float x) {
-    if (x != x) return add(x, x);
+    if (x != x) return bits_to_f(0x7fc00000u);
     if (x < 0.0f) return bits_to_f(0x7fc00000u);
     if (x == 0.0f) return bits_to_f(0xff800000u);
     uint32_t u = f_to_bits(x);
