@@ -135,6 +135,11 @@ struct ava_engine {
     Dev x, h, proj, ve, vv, vw, vah, vqg, vex, qw, qa, yraw, y, eqkv, eo, u, act, streams, v_first, logits, tok, next, status;
     uint32_t* status_host = nullptr;  // pinned
 
+    bool prof = false;
+    struct Pending { const char* cls; cudaEvent_t a, b; };
+    std::vector<Pending> prof_pending;
+    std::map<std::string, std::pair<int64_t, double>> prof_total;  // kernel -> (launches, milliseconds)
+
     bool keep = false;
     std::map<std::pair<std::string, int>, std::unique_ptr<Dev>> debug;
     std::map<std::string, int64_t> debug_width;
@@ -307,6 +312,21 @@ int ensure_workspace(ava_engine* e, int rows) {
     return AVA_OK;
 }
 
+// Section clock (the reference's fused step has one too: src/model/fstep/arch.rs:131-165): with profiling on, every
+// kernel launch is bracketed by CUDA events on the engine's stream; ava_prof_read folds them into per-kernel totals.
+void prof_begin(ava_engine* e, const char* cls) {
+    if (!e->prof) return;
+    cudaEvent_t a, b;
+    if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
+    cudaEventRecord(a, e->stream);
+    e->prof_pending.push_back({cls, a, b});
+}
+void prof_end(ava_engine* e) {
+    e->launches++;
+    if (!e->prof || e->prof_pending.empty()) return;
+    cudaEventRecord(e->prof_pending.back().b, e->stream);
+}
+
 void dbg(ava_engine* e, const char* name, int block, const float* src, int rows, int64_t width) {
     if (!e->keep) return;
     auto& slot = e->debug[{name, block}];
@@ -318,7 +338,7 @@ void dbg(ava_engine* e, const char* name, int block, const float* src, int rows,
     e->debug_rows = rows;
 }
 
-int gemm(ava_engine* e, const float* A, int lda, const QMat& w, float* C, int ldc, int M, GemmEpilogue epi, const LifParams* lif = nullptr) {
+int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w, float* C, int ldc, int M, GemmEpilogue epi, const LifParams* lif = nullptr) {
     GemmArgs g{};
     g.A = A;
     g.lda = lda;
@@ -331,8 +351,9 @@ int gemm(ava_engine* e, const float* A, int lda, const QMat& w, float* C, int ld
     g.N = w.dout;
     g.K = w.din;
     if (lif) g.lif = *lif;
+    prof_begin(e, cls);
     launch_q8_gemm(e->stream, g, epi, e->sm_count);
-    e->launches++;
+    prof_end(e);
     return AVA_OK;
 }
 
@@ -355,14 +376,16 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         }
     }
 
+    prof_begin(e, "embed");
     launch_embed(st, e->tok_emb.as<float>(), tok, M, d, c.vocab, x, streams, e->status.as<uint32_t>());
-    e->launches++;
+    prof_end(e);
     dbg(e, "x_in", -1, x, M, d);
     for (int i = 0; i < L; ++i) {
         BlockDev& b = *e->blocks[i];
         // ---- the spiking memory
+        prof_begin(e, "rmsnorm");
         launch_rmsnorm(st, x, b.mem_norm.as<float>(), M, d, h);
-        e->launches++;
+        prof_end(e);
         dbg(e, "h_lif", i, h, M, d);
         LifParams lp{};
         lp.beta = b.beta.as<float>();
@@ -374,17 +397,18 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         lp.a = c.alif ? s->lif_a.as<float>() + (size_t)i * Md : nullptr;
         lp.spikes = c.spikes;
         lp.lif_scale = c.lif_scale;
-        gemm(e, h, d, b.win, nullptr, 0, M, EPI_LIF, &lp);
+        gemm(e, "gemm.win_lif", h, d, b.win, nullptr, 0, M, EPI_LIF, &lp);
         dbg(e, "spikes", i, lp.s, M, d);
-        gemm(e, lp.s, d, b.wout, x, d, M, EPI_ADD);
+        gemm(e, "gemm.wout", lp.s, d, b.wout, x, d, M, EPI_ADD);
         dbg(e, "x_lif", i, x, M, d);
 
         // ---- the fast-weight memory
+        prof_begin(e, "rmsnorm");
         launch_rmsnorm(st, x, b.hebb_norm.as<float>(), M, d, h);
-        e->launches++;
+        prof_end(e);
         dbg(e, "h_mem", i, h, M, d);
         const int pw = e->proj_w();
-        gemm(e, h, d, b.proj, e->proj.as<float>(), pw, M, EPI_STORE);
+        gemm(e, "gemm.qkveg", h, d, b.proj, e->proj.as<float>(), pw, M, EPI_STORE);
         dbg(e, "qkveg", i, e->proj.as<float>(), M, pw);
         MemPrepArgs mp{};
         mp.h = h;
@@ -400,8 +424,9 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         mp.e = e->ve.as<float>(); mp.v = e->vv.as<float>(); mp.w = e->vw.as<float>(); mp.ah = e->vah.as<float>();
         mp.qg = e->vqg.as<float>(); mp.ex = e->vex.as<float>(); mp.qw = e->qw.as<float>(); mp.qa = e->qa.as<float>();
         mp.status = e->status.as<uint32_t>();
+        prof_begin(e, "mem_prep");
         launch_mem_prep(st, mp);
-        e->launches++;
+        prof_end(e);
         dbg(e, "ek", i, mp.e, M, d); dbg(e, "v", i, mp.v, M, d); dbg(e, "w", i, mp.w, M, d); dbg(e, "ah", i, mp.ah, M, d);
         dbg(e, "qg", i, mp.qg, M, d); dbg(e, "ex", i, mp.ex, M, d); dbg(e, "qw", i, mp.qw, M, nh); dbg(e, "qa", i, mp.qa, M, nh);
         MemHeadsArgs mh{};
@@ -411,20 +436,23 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         mh.e = mp.e; mh.v = mp.v; mh.w = mp.w; mh.ah = mp.ah; mh.qg = mp.qg; mh.ex = mp.ex; mh.qw = mp.qw; mh.qa = mp.qa;
         mh.y = e->yraw.as<float>();
         mh.status = e->status.as<uint32_t>();
+        prof_begin(e, "mem_heads");
         launch_mem_heads(st, mh);
-        e->launches++;
+        prof_end(e);
         dbg(e, "y_raw", i, mh.y, M, d);
+        prof_begin(e, "mem_post");
         launch_mem_post(st, mh.y, c.out_gate ? e->proj.as<float>() + 4 * d : nullptr, pw, M, d, hs, e->y.as<float>());
-        e->launches++;
+        prof_end(e);
         dbg(e, "y", i, e->y.as<float>(), M, d);
-        gemm(e, e->y.as<float>(), d, b.wo, x, d, M, EPI_ADD);
+        gemm(e, "gemm.wo", e->y.as<float>(), d, b.wo, x, d, M, EPI_ADD);
         dbg(e, "x_mem", i, x, M, d);
 
         // ---- the engram
         if (i == c.eng_block) {
+            prof_begin(e, "rmsnorm");
             launch_rmsnorm(st, x, b.eng_norm.as<float>(), M, d, h);
-            e->launches++;
-            gemm(e, h, d, b.eqkv, e->eqkv.as<float>(), 3 * d, M, EPI_STORE);
+            prof_end(e);
+            gemm(e, "gemm.eng_qkv", h, d, b.eqkv, e->eqkv.as<float>(), 3 * d, M, EPI_STORE);
             dbg(e, "eng_qkv", i, e->eqkv.as<float>(), M, 3 * d);
             EngramArgs ea{};
             ea.qkv = e->eqkv.as<float>();
@@ -433,38 +461,44 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
             ea.M = M; ea.d = d; ea.hs = c.eng_head_size; ea.cap = s->ring; ea.keep = s->keep; ea.bf16 = c.eng_store_bf16;
             ea.o = e->eo.as<float>();
             ea.status = e->status.as<uint32_t>();
+            prof_begin(e, "engram");
             if (!launch_engram(st, ea, n_max))
                 return e->fail(AVA_ERR_CAPACITY, "engram read over %d tokens does not fit this kernel's shared memory", n_max);
-            e->launches++;
+            prof_end(e);
             dbg(e, "eng_o", i, ea.o, M, d);
-            gemm(e, ea.o, d, b.ewo, x, d, M, EPI_ADD);
+            gemm(e, "gemm.eng_wo", ea.o, d, b.ewo, x, d, M, EPI_ADD);
             dbg(e, "x_eng", i, x, M, d);
         }
 
         // ---- the sparse MLP
+        prof_begin(e, "rmsnorm");
         launch_rmsnorm(st, x, b.mlp_norm.as<float>(), M, d, h);
-        e->launches++;
-        gemm(e, h, d, b.w1, e->u.as<float>(), H, M, EPI_STORE);
+        prof_end(e);
+        gemm(e, "gemm.w1", h, d, b.w1, e->u.as<float>(), H, M, EPI_STORE);
         dbg(e, "u", i, e->u.as<float>(), M, H);
+        prof_begin(e, "kwta");
         launch_kwta(st, e->u.as<float>(), M, H, c.kwta_k, c.relu2, e->act.as<float>());
-        e->launches++;
+        prof_end(e);
         dbg(e, "a", i, e->act.as<float>(), M, H);
-        gemm(e, e->act.as<float>(), H, b.w2, x, d, M, EPI_ADD);
+        gemm(e, "gemm.w2", e->act.as<float>(), H, b.w2, x, d, M, EPI_ADD);
         if (c.dense) {
+            prof_begin(e, "dense_mix");
             launch_dense_mix(st, x, streams, b.dense.as<float>(), i + 2, (int64_t)Md);
-            e->launches++;
+            prof_end(e);
         }
         dbg(e, "x_out", i, x, M, d);
     }
     if (want_logits || next) {
+        prof_begin(e, "rmsnorm");
         launch_rmsnorm(st, x, e->final_norm.as<float>(), M, d, h);
-        e->launches++;
+        prof_end(e);
         dbg(e, "x_final", -1, h, M, d);
         float* lg = logits ? logits : e->logits.as<float>();
-        gemm(e, h, d, e->head, lg, c.vocab, M, EPI_STORE);
+        gemm(e, "gemm.head", h, d, e->head, lg, c.vocab, M, EPI_STORE);
         if (next) {
+            prof_begin(e, "argmax");
             launch_argmax(st, lg, M, c.vocab, next);
-            e->launches++;
+            prof_end(e);
         }
     }
     // the host's mirror of the engram counts moves as the kernel moves them
@@ -1019,6 +1053,50 @@ int ava_debug_get(ava_engine* e, const char* name, int32_t block, float* out) {
     CK(cudaSetDevice(e->device));
     CK(cudaStreamSynchronize(e->stream));
     CK(cudaMemcpy(out, it->second->p, it->second->bytes, cudaMemcpyDeviceToHost));
+    return AVA_OK;
+}
+
+int ava_prof_enable(ava_engine* e, int32_t on) {
+    if (!e) return AVA_ERR_ARG;
+    CK(cudaSetDevice(e->device));
+    CK(cudaStreamSynchronize(e->stream));
+    for (auto& p : e->prof_pending) {
+        cudaEventDestroy(p.a);
+        cudaEventDestroy(p.b);
+    }
+    e->prof_pending.clear();
+    e->prof_total.clear();
+    e->prof = on != 0;
+    return AVA_OK;
+}
+
+int ava_prof_read(ava_engine* e, const char* kernel, int64_t* launches, double* ms) {
+    if (!e || !kernel) return AVA_ERR_ARG;
+    CK(cudaSetDevice(e->device));
+    CK(cudaStreamSynchronize(e->stream));
+    for (auto& p : e->prof_pending) {
+        float t = 0.f;
+        if (cudaEventElapsedTime(&t, p.a, p.b) == cudaSuccess) {
+            auto& slot = e->prof_total[p.cls];
+            slot.first += 1;
+            slot.second += t;
+        }
+        cudaEventDestroy(p.a);
+        cudaEventDestroy(p.b);
+    }
+    e->prof_pending.clear();
+    auto it = e->prof_total.find(kernel);
+    if (launches) *launches = it == e->prof_total.end() ? 0 : it->second.first;
+    if (ms) *ms = it == e->prof_total.end() ? 0.0 : it->second.second;
+    return AVA_OK;
+}
+
+int ava_prof_names(ava_engine* e, char* out, int32_t cap) {
+    if (!e || !out || cap <= 0) return AVA_ERR_ARG;
+    std::string all;
+    for (auto& p : e->prof_pending) e->prof_total[p.cls];
+    for (auto& kv : e->prof_total) all += kv.first + "\n";
+    snprintf(out, cap, "%s", all.c_str());
     return AVA_OK;
 }
 

@@ -1,0 +1,292 @@
+"""Benchmark of the block step: batch-256 decode of the Ava-0.4-shaped model on N B200s.
+
+A "step" is one decoded token for every resident sequence (256 per GPU; sequences are independent, so each rank steps
+its own 256 with no data-path collective: weak scaling).  Workload = BASELINE configuration 1: each sequence has read a
+prompt and is decoding with its membranes, thresholds, 12 fast-synapse 768x768 f32 matrices and the block-6 bf16 KV
+store resident in HBM.  The KV length over the timed steps is centred on the configuration's mean decode context
+(1024-token prompt + 1024 decode tokens: mean 1535.5), reached by untimed steps.
+
+  value      tokens/s over all ranks, inputs resident in HBM, CUDA events on the engine's stream, max over ranks
+  e2e        the same through ava_step (host token ids in, host logits out, copies inside the timed region)
+  roofline   the fast-weight state pass (mem_heads kernel): algorithmic bytes per launch / its mean launch time
+  cpu_baseline / --impl reference
+             the CPU oracle (a restatement of the reference's int8 CPU engine; the reference itself needs a Rust tool
+             chain and cannot be built here) on the host cores, on a bounded sample of the same workload
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode tokens/s (batch 256 per GPU, Ava-0.4-shaped int8 model)"
+UNIT = "tokens/s"
+ROWS_PER_GPU = 256
+MEAN_CTX = 1536  # mean KV length of the decode phase of configuration 1 (1024 prompt + 1024 decode)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class Clocks:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.p = None
+
+    def start(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.gpu)],
+                                      stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.p = None
+
+    def stop(self) -> dict:
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        try:
+            out, _ = self.p.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+            out, _ = self.p.communicate()
+        sm, mx, reasons = [], [], set()
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------- CPU baseline
+def cpu_reference(cfg, weights, steps: int, warmup: int, rows: int, threads: int):
+    """The CPU oracle stepping `rows` sequences of the workload from a fresh state: tokens/s and what was run."""
+    from oracle import oracle
+    from ava_b200 import synth
+    oracle.build()
+    oracle.set_threads(threads)
+    oracle.set_simd(True)
+    m = oracle.OracleModel(cfg, weights)
+    st = m.state(rows)
+    ids = synth.token_ids(cfg["vocab"], rows, warmup + steps)
+    for t in range(warmup):
+        st.step(ids[:, t])
+    t0 = time.perf_counter()
+    for t in range(warmup, warmup + steps):
+        st.step(ids[:, t])
+    dt = time.perf_counter() - t0
+    sample = (f"{rows} of the {ROWS_PER_GPU} sequences, {steps} steps after {warmup} warm-up steps from a fresh state "
+              f"(KV length {warmup}..{warmup + steps}), AVX2+FMA tile kernel, {threads} threads")
+    return rows * steps / dt, dt / steps * 1e3, sample
+
+
+def run_reference(args, cfg, rank):
+    if rank != 0:
+        return
+    from ava_b200 import synth
+    threads = os.cpu_count() or 1
+    rows = 16
+    w = synth.model(cfg, 0, "bench")
+    val, ms, sample = cpu_reference(cfg, w, args.steps, args.warmup, rows, threads)
+    line = {"metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations x int8 weights",
+            "data": "synthetic", "impl": "reference",
+            "config": {"workload": "BASELINE config 1 (Ava-0.4-shaped decode), bounded CPU sample", "rows": rows},
+            "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------- GPU arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--rows", type=int, default=ROWS_PER_GPU, help="sequences per GPU")
+    ap.add_argument("--ctx", type=int, default=MEAN_CTX, help="KV length the timed steps are centred on")
+    ap.add_argument("--small", action="store_true", help="a small model and batch (profiling captures, not a bench value)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    from ava_b200 import config, synth
+    cfg = config.ava04_shaped()
+    if args.small:
+        cfg = config.make(4096, 768, 2, head_size=768, eng_block=1, eng_head_size=64, eng_store_bf16=1)
+
+    if args.impl == "reference":
+        run_reference(args, cfg, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from ava_b200 import engine
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the engine has no CPU path)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    weights = synth.model(cfg, 0, "bench")
+    model = engine.Model(cfg, weights, device=local)
+    rows, K, W = args.rows, args.steps, args.warmup
+    e2e_steps = K
+    # untimed steps bring the KV length to ctx - K/2, so that the timed steps straddle the mean decode context
+    prompt = max(1, args.ctx - K // 2 - W)
+    max_ctx = prompt + W + K + e2e_steps + W + 16
+    state = model.state(rows, max_ctx)
+    stream = torch.cuda.ExternalStream(model.stream, device=local)
+
+    ids = synth.token_ids(cfg["vocab"], rows, prompt, seed0=rank * rows)           # seeds 0..255 per rank
+    ids_dev = torch.from_numpy(np.ascontiguousarray(ids.T).astype(np.int32)).to(f"cuda:{local}")  # [prompt, rows]
+    tok = [torch.zeros(rows, dtype=torch.int32, device=f"cuda:{local}") for _ in range(2)]
+    logits_dev = torch.empty(rows, cfg["vocab"], dtype=torch.float32, device=f"cuda:{local}")
+    torch.cuda.synchronize()
+
+    # the prompt, token by token (untimed; no output head)
+    for t in range(prompt - 1):
+        model.step_device(state, ids_dev[t].data_ptr(), None, None)
+    model.step_device(state, ids_dev[prompt - 1].data_ptr(), logits_dev.data_ptr(), tok[0].data_ptr())
+    model.sync()
+
+    def decode(n, cur):
+        for _ in range(n):
+            model.step_device(state, tok[cur].data_ptr(), logits_dev.data_ptr(), tok[cur ^ 1].data_ptr())
+            cur ^= 1
+        return cur
+
+    cur = decode(W, 0)
+    model.sync()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    clocks = Clocks(local)
+    clocks.start()
+    l0 = model.launches
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    cur = decode(K, cur)
+    ev1.record(stream)
+    model.sync()
+    torch.cuda.synchronize()
+    launches = model.launches - l0
+    ms = ev0.elapsed_time(ev1)
+    clk = clocks.stop()
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.barrier()
+        ms = float(t.item())
+    value = world * rows * K / (ms * 1e-3)
+
+    # ---- end to end: the reference-facing call with host buffers (pinned), copies inside the timed region
+    tok_host = torch.empty(rows, dtype=torch.int32).pin_memory()
+    logits_host = torch.empty(rows, cfg["vocab"], dtype=torch.float32).pin_memory()
+    tok_host.copy_(tok[cur].cpu())
+    L = engine.lib()
+    import ctypes as C
+
+    def host_step():
+        rc = L.ava_step(model.h, state.h, C.cast(tok_host.data_ptr(), engine.u32p), C.cast(logits_host.data_ptr(), engine.fp))
+        if rc != 0:
+            raise RuntimeError(L.ava_last_error(model.h).decode())
+        tok_host.copy_(logits_host.argmax(1).to(torch.int32))
+
+    for _ in range(W):
+        host_step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        host_step()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], dtype=torch.float64, device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_val = world * rows * e2e_steps / e2e_s
+
+    # ---- the dominant kernel under the section clock: a few more steps with every launch bracketed by events
+    model.prof_enable(True)
+    cur2 = decode(4, cur)
+    prof = model.prof_read()
+    model.prof_enable(False)
+    total_ms = sum(v[1] for v in prof.values()) or 1.0
+    n_mh, ms_mh = prof.get("mem_heads", (0, 0.0))
+    state_bytes = rows * 2 * 4 * cfg["d"] * cfg["head_size"]        # read once + written once, f32, per launch
+    peak, peak_src = peaks()
+    achieved = state_bytes / (ms_mh / max(n_mh, 1) * 1e-3) / 1e9 if n_mh else 0.0
+    # the whole step against the HBM roofline: algorithmic bytes per decoded token (state + weights/rows + KV + LIF)
+    kv_bytes = args.ctx * 2 * cfg["d"] * 2 if cfg["eng_block"] >= 0 else 0
+    tok_bytes = (2 * 4 * cfg["n_blocks"] * cfg["d"] * cfg["head_size"] + synth.weight_bytes(cfg) / rows + kv_bytes
+                 + 2 * 4 * 3 * cfg["n_blocks"] * cfg["d"])
+    step_frac = (value / world) * tok_bytes / 1e9 / peak
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations x int8 weights, f32 state, bf16 KV",
+        "data": "synthetic",
+        "config": {"workload": "BASELINE config 1: Ava-0.4-shaped decode (12 blocks, d 768, wide 3072, kWTA 768, vocab 16384, one 768x768 f32 "
+                               "fast-synapse matrix per block, bf16 engram of 12x64 in block 6)" if not args.small else "small profiling case",
+                   "rows_per_gpu": rows, "kv_len_timed": [prompt + W, prompt + W + K], "l2": "per-step inputs (state "
+                   f"{state.nbytes / 1e9:.2f} GB per GPU) are larger than L2", "sequences": "independent, sharded by rank, no collective"},
+        "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": rows * 4, "d2h_bytes_per_step": rows * cfg["vocab"] * 4,
+                "steps": e2e_steps, "call": "ava_step (host token ids in, host logits out, pinned buffers)"},
+        "gpu_launches": int(launches),
+        "clocks": clk,
+        "roofline": {"bound": "hbm", "kernel": "mem_heads (fast-weight state pass)", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "of": peak_src, "traffic": None, "bytes_per_launch": state_bytes,
+                     "mean_launch_ms": ms_mh / max(n_mh, 1), "launches_timed": n_mh,
+                     "step_bytes_per_token": tok_bytes, "step_frac_of_hbm_roofline": step_frac},
+        "kernel_share": {k: round(v[1] / total_ms, 4) for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])},
+    }
+    if rank == 0 and not args.no_cpu and not args.small:
+        threads = os.cpu_count() or 1
+        val, _, sample = cpu_reference(cfg, weights, 128, 4, 16, threads)
+        line["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
+    elif rank == 0:
+        line["cpu_baseline"] = None
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    del cur2
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -129,6 +129,14 @@ int64_t ava_engine_launches(const ava_engine* e);
 int64_t ava_engine_bytes(const ava_engine* e);
 int64_t ava_state_bytes(const ava_state* s);
 
+/* Section clock, as the reference's fused step keeps one (`take_secs`, src/model/fstep/arch.rs:131-165, switched by
+ * `int8::set_mm_prof`, src/int8.rs:635-640): with it on, every kernel launch is bracketed by CUDA events on the
+ * engine's stream.  ava_prof_read waits for the stream and returns one kernel's launches and total milliseconds since
+ * the clock was switched on; ava_prof_names lists the kernels seen, one per line. */
+int ava_prof_enable(ava_engine* e, int32_t on);
+int ava_prof_read(ava_engine* e, const char* kernel, int64_t* launches, double* ms);
+int ava_prof_names(ava_engine* e, char* out, int32_t cap);
+
 /* Per-block intermediates of the last step (row-major [rows, width] f32 copied to host), for teacher-forced parity
  * checks — the side-band of `Model::step_trace` (src/model/fstep/arch.rs:420-450).  Names: "h_lif", "spikes",
  * "x_lif", "h_mem", "qkveg", "y_raw", "y", "x_mem", "eng_qkv", "eng_o", "u", "a", "x_out".  Call ava_debug_keep(e, 1)
