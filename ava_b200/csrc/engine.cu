@@ -70,33 +70,6 @@ struct BlockDev {
     QMat win, wout, proj, wo, eqkv, ewo, w1, w2;
 };
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
-// the fast weights [rows_total, hs] f32 as a 2-D tiled tensor map with boxes of [cw columns, rb rows]
-bool make_state_tmap(CUtensorMap* map, void* base, uint64_t rows_total, int hs, int cw, int rb) {
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (!fn) return false;
-    const cuuint64_t dims[2] = {(cuuint64_t)hs, (cuuint64_t)rows_total};
-    const cuuint64_t strides[1] = {(cuuint64_t)hs * sizeof(float)};
-    const cuuint32_t box[2] = {(cuuint32_t)cw, (cuuint32_t)rb};
-    const cuuint32_t estr[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 // nn/parts/src/quant.rs:18-31
 void quantize_int8(const float* w, int rows, int cols, int8_t* q, float* scale) {
     for (int c = 0; c < cols; ++c) scale[c] = 0.f;
@@ -128,7 +101,7 @@ struct ava_engine {
     Dev tok_emb, final_norm;
     QMat head;
     std::vector<std::unique_ptr<BlockDev>> blocks;
-    int cw = 0, rb = 0;  // fast-weight slice width and rows per TMA box
+    int cw = 0, rb = 0;  // fast-weight slice width and rows per bulk copy
 
     // work buffers for `ws_rows` rows
     int ws_rows = 0;
@@ -166,12 +139,11 @@ struct ava_state {
     int ring = 0;   // engram slots per head
     int keep = 0;   // tokens kept after a read
     Dev lif_v, lif_s, lif_a;  // [L][rows][d]
-    Dev mem_f;                // [L][rows][nh][hs][hs]
+    Dev mem_f;                // [L][rows][nh][hs / cw][hs][cw]: slice-major, a block of threads owns one contiguous slice
     Dev eng_k, eng_v;         // [rows][enh][ring][ehs]
     Dev eng_n, eng_start;     // [rows] i32
     std::vector<int32_t> n_host, start_host;
     std::vector<int64_t> seen;
-    CUtensorMap tmap{};
     size_t kv_elem() const { return e->cfg.eng_store_bf16 ? 2 : 4; }
 };
 
@@ -287,7 +259,7 @@ const char* find_blocker(const ava_config& c, int* cw, int* rb) {
     if (c.gate_rank < 1) return "gate rank must be at least 1";
     if (c.eng_block >= 0 && (c.eng_head_size <= 0 || c.d % c.eng_head_size)) return "bad engram head size";
     if (c.spikes < 0 || c.spikes > 2) return "unknown spike kind";
-    if (c.head_size % 16 || !mem_heads_tiling(c.head_size, cw, rb)) return "memory head size not covered (multiples of 16; up to 256 or a multiple of 256 up to 2048)";
+    if (c.head_size % 16 || !mem_heads_tiling(c.head_size, cw, rb)) return "memory head size not covered (a multiple of 16 whose column slice fits shared memory)";
     return nullptr;
 }
 
@@ -338,7 +310,7 @@ void dbg(ava_engine* e, const char* name, int block, const float* src, int rows,
     e->debug_rows = rows;
 }
 
-int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w, float* C, int ldc, int M, GemmEpilogue epi, const LifParams* lif = nullptr) {
+int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w, float* C, int ldc, int M, GemmEpilogue epi, const LifParams* lif = nullptr, bool sparse = false) {
     GemmArgs g{};
     g.A = A;
     g.lda = lda;
@@ -352,7 +324,7 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
     g.K = w.din;
     if (lif) g.lif = *lif;
     prof_begin(e, cls);
-    launch_q8_gemm(e->stream, g, epi, e->sm_count);
+    if (!(sparse && launch_q8_event(e->stream, g, epi))) launch_q8_gemm(e->stream, g, epi, e->sm_count);
     prof_end(e);
     return AVA_OK;
 }
@@ -399,7 +371,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         lp.lif_scale = c.lif_scale;
         gemm(e, "gemm.win_lif", h, d, b.win, nullptr, 0, M, EPI_LIF, &lp);
         dbg(e, "spikes", i, lp.s, M, d);
-        gemm(e, "gemm.wout", lp.s, d, b.wout, x, d, M, EPI_ADD);
+        gemm(e, "gemm.wout", lp.s, d, b.wout, x, d, M, EPI_ADD, nullptr, true);
         dbg(e, "x_lif", i, x, M, d);
 
         // ---- the fast-weight memory
@@ -430,9 +402,8 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         dbg(e, "ek", i, mp.e, M, d); dbg(e, "v", i, mp.v, M, d); dbg(e, "w", i, mp.w, M, d); dbg(e, "ah", i, mp.ah, M, d);
         dbg(e, "qg", i, mp.qg, M, d); dbg(e, "ex", i, mp.ex, M, d); dbg(e, "qw", i, mp.qw, M, nh); dbg(e, "qa", i, mp.qa, M, nh);
         MemHeadsArgs mh{};
-        mh.tmap = s->tmap;
-        mh.row0 = (int64_t)i * M * nh * hs;
-        mh.M = M; mh.nh = nh; mh.hs = hs; mh.cw = e->cw; mh.rb = e->rb;
+        mh.f = s->mem_f.as<float>() + (size_t)i * Md * hs;
+        mh.M = M; mh.nh = nh; mh.hs = hs; mh.cw = e->cw; mh.chunk_rows = e->rb;
         mh.e = mp.e; mh.v = mp.v; mh.w = mp.w; mh.ah = mp.ah; mh.qg = mp.qg; mh.ex = mp.ex; mh.qw = mp.qw; mh.qa = mp.qa;
         mh.y = e->yraw.as<float>();
         mh.status = e->status.as<uint32_t>();
@@ -465,6 +436,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
             if (!launch_engram(st, ea, n_max))
                 return e->fail(AVA_ERR_CAPACITY, "engram read over %d tokens does not fit this kernel's shared memory", n_max);
             prof_end(e);
+            e->launches++;  // the small kernel that moves the counts on
             dbg(e, "eng_o", i, ea.o, M, d);
             gemm(e, "gemm.eng_wo", ea.o, d, b.ewo, x, d, M, EPI_ADD);
             dbg(e, "x_eng", i, x, M, d);
@@ -480,7 +452,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         launch_kwta(st, e->u.as<float>(), M, H, c.kwta_k, c.relu2, e->act.as<float>());
         prof_end(e);
         dbg(e, "a", i, e->act.as<float>(), M, H);
-        gemm(e, "gemm.w2", e->act.as<float>(), H, b.w2, x, d, M, EPI_ADD);
+        gemm(e, "gemm.w2", e->act.as<float>(), H, b.w2, x, d, M, EPI_ADD, nullptr, true);
         if (c.dense) {
             prof_begin(e, "dense_mix");
             launch_dense_mix(st, x, streams, b.dense.as<float>(), i + 2, (int64_t)Md);
@@ -524,7 +496,7 @@ int finish(ava_engine* e) {
     CK(cudaMemsetAsync(e->status.p, 0, sizeof(uint32_t), e->stream));
     CK(cudaStreamSynchronize(e->stream));
     const uint32_t st = *e->status_host;
-    if (st & ST_WAIT_TIMEOUT) return e->fail(AVA_ERR_CUDA, "a bounded wait on a TMA barrier ran out inside the memory kernel");
+    if (st & ST_WAIT_TIMEOUT) return e->fail(AVA_ERR_CUDA, "a bounded wait on a bulk-copy barrier ran out inside the memory kernel");
     if (st & ST_BAD_TOKEN) return e->fail(AVA_ERR_ARG, "a token id outside the vocabulary");
     if (st & ST_ENGRAM_FULL) return e->fail(AVA_ERR_CAPACITY, "the engram store had no room for a token");
     if (st & ST_NONFINITE) return e->fail(AVA_ERR_NONFINITE, "a gate, key or value of the fast-weight memory was not finite (the state has moved)");
@@ -544,6 +516,7 @@ struct StateSlice {
     Dev* buf = nullptr;
     size_t off = 0, count = 0;  // elements (floats, or store elements for the engram)
     bool eng = false;
+    bool tiled = false;         // the fast weights: slice-major in device memory, natural [heads, hs, hs] outside
 };
 
 // where row `row`'s tensor `name` lives; for the engram the count is the tokens held times the row width
@@ -574,6 +547,7 @@ bool locate(const ava_state* s, int row, const std::string& name, StateSlice* ou
         out->buf = &ms->mem_f;
         out->off = ((size_t)i * M + row) * per;
         out->count = per;
+        out->tiled = true;
         return true;
     }
     return false;
@@ -600,8 +574,6 @@ int alloc_state(ava_engine* e, int rows, int ring, int keep, ava_state** out) {
     s->n_host.assign(rows, 0);
     s->start_host.assign(rows, 0);
     s->seen.assign(rows, 0);
-    if (!make_state_tmap(&s->tmap, s->mem_f.p, (uint64_t)L * M * (d / c.head_size) * c.head_size, c.head_size, e->cw, e->rb))
-        return e->fail(AVA_ERR_CUDA, "cuTensorMapEncodeTiled failed for the fast-weight state");
     *out = s.release();
     return AVA_OK;
 }
@@ -884,6 +856,14 @@ int ava_state_export(const ava_state* s, int32_t row, const char* name, float* o
     if (row < 0 || row >= s->rows || !locate(s, row, name, &sl)) return e->fail(AVA_ERR_ARG, "no state tensor %s of row %d", name, row);
     CK(cudaSetDevice(e->device));
     CK(cudaStreamSynchronize(e->stream));
+    if (sl.tiled) {
+        Dev tmp;
+        CK(tmp.alloc(sl.count * sizeof(float)));
+        launch_retile(e->stream, sl.buf->as<float>() + sl.off, tmp.as<float>(), e->nh(), e->cfg.head_size, e->cw, 0);
+        CK(cudaStreamSynchronize(e->stream));
+        CK(cudaMemcpy(out, tmp.p, sl.count * sizeof(float), cudaMemcpyDeviceToHost));
+        return AVA_OK;
+    }
     if (!sl.eng) {
         CK(cudaMemcpy(out, sl.buf->as<float>() + sl.off, sl.count * sizeof(float), cudaMemcpyDeviceToHost));
         return AVA_OK;
@@ -913,6 +893,14 @@ int ava_state_import(ava_state* s, int32_t row, const char* name, const float* i
     CK(cudaStreamSynchronize(e->stream));
     if (!sl.eng) {
         if ((int64_t)sl.count != n) return e->fail(AVA_ERR_ARG, "%s: %lld values, want %lld", name, (long long)n, (long long)sl.count);
+        if (sl.tiled) {
+            Dev tmp;
+            CK(tmp.alloc(sl.count * sizeof(float)));
+            CK(cudaMemcpy(tmp.p, in, n * sizeof(float), cudaMemcpyHostToDevice));
+            launch_retile(e->stream, tmp.as<float>(), sl.buf->as<float>() + sl.off, e->nh(), e->cfg.head_size, e->cw, 1);
+            CK(cudaStreamSynchronize(e->stream));
+            return AVA_OK;
+        }
         CK(cudaMemcpy(sl.buf->as<float>() + sl.off, in, n * sizeof(float), cudaMemcpyHostToDevice));
         return AVA_OK;
     }

@@ -6,11 +6,12 @@
 //     t1  = (q alpha)^T F
 //     y   = (t1 + (q.w) v) - (q.ah) rr
 //     F'  = (F * alpha_row + w v^T) - ah rr^T
-// Columns are independent, so one block of threads owns a slice of CW columns of one head: the [hs, CW] slice is
-// brought into shared memory once by TMA (2-D tiled bulk copies, one mbarrier per box of rows), the column sums run
-// down the rows as the boxes land, the slice is updated in place in shared memory and written back once by TMA.  Per
-// token the state is read once and written once: 8 bytes per state element, the kernel's whole DRAM traffic apart
-// from the per-head vectors.
+// Columns are independent, so one block of threads owns a slice of CW columns of one head.  The state is kept
+// SLICE-MAJOR in HBM: [row][head][slice][hs][CW], so a block's slice is one contiguous run of hs * CW * 4 bytes.  It
+// comes into shared memory as a few large bulk copies (cp.async.bulk, one mbarrier per chunk of rows), the column sums
+// run down the rows as the chunks land, the slice is updated in place in shared memory and each chunk is written back
+// with a bulk store as soon as it is done.  Per token the state is read once and written once: 8 bytes per state
+// element is the kernel's whole DRAM traffic apart from the per-head vectors.
 #include "ava_math.h"
 #include "kernels.cuh"
 
@@ -18,9 +19,9 @@ namespace ava {
 
 namespace {
 
-constexpr int MAX_BOXES = 8;
+constexpr int MAX_CHUNKS = 16;
 constexpr int THREADS = 256;
-constexpr uint32_t WAIT_LIMIT = 1u << 22;  // polls (each backs off ~64 ns) before a wait gives up: about a quarter second
+constexpr uint32_t WAIT_LIMIT = 1u << 22;  // polls (most back off ~64 ns) before a wait gives up: about a quarter second
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -43,27 +44,26 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
-        if (i > 64) __nanosleep(64);
+        if (i > 256) __nanosleep(64);
     }
     return false;
 }
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(dst)),
-        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
-        : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, const void* src) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y), "r"(smem_u32(src))
+// global -> shared, completion counted in bytes on the mbarrier; addresses and size multiples of 16
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)), "l"(src),
+                 "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
+__device__ __forceinline__ void bulk_store(void* dst, const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)), "r"(bytes) : "memory");
+}
 
-// One block: row m, head e, columns [c0, c0 + CW).  Shared memory: the slice [hs][CW], then e, qg, ex, w, ah [hs]
-// each, then v, rr, t1 [CW] each, then the barriers.
+// One block: row m, head e, slice s.  Shared memory: the slice [hs][CW], then e, qg, ex, w, ah [hs] each, then v, rr,
+// t1 [CW] each, then the barriers.
 template <int CW>
-__global__ void __launch_bounds__(THREADS) mem_heads_kernel(const __grid_constant__ MemHeadsArgs a) {
+__global__ void __launch_bounds__(THREADS) mem_heads_kernel(const MemHeadsArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    const int hs = a.hs, rb = a.rb, nbox = hs / rb;
+    const int hs = a.hs, cr = a.chunk_rows, nchunk = hs / cr;
     float* tile = reinterpret_cast<float*>(smem_raw);
     float* ve = tile + (size_t)hs * CW;
     float* vqg = ve + hs;
@@ -81,50 +81,64 @@ __global__ void __launch_bounds__(THREADS) mem_heads_kernel(const __grid_constan
     const int head = (blockIdx.x / slices) % a.nh;
     const int m = blockIdx.x / (slices * a.nh);
     const int c0 = slice * CW;
-    const int64_t trow = a.row0 + ((int64_t)m * a.nh + head) * hs;  // first tensor row of this head
-    const size_t vo = ((size_t)m * a.nh + head) * hs;                // offset of this head's vectors
+    const size_t vo = ((size_t)m * a.nh + head) * hs;  // offset of this head's vectors
+    float* gslice = a.f + (vo * hs) + (size_t)slice * hs * CW;  // this block's contiguous slice in HBM
+    const uint32_t chunk_bytes = (uint32_t)(cr * CW * sizeof(float));
+    // optional phase clock of thread 0 (nanoseconds, 6 marks per block) for tuning; nullptr in normal runs
+    unsigned long long* tl = a.timeline ? a.timeline + (size_t)blockIdx.x * 6 : nullptr;
+    auto mark = [&](int i) {
+        if (tl && tid == 0) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+            tl[i] = t;
+        }
+    };
+    mark(0);
 
+    uint64_t* vbar = &bars[nchunk];  // the per-head vectors arrive on their own barrier
     if (tid == 0) {
-        for (int b = 0; b < nbox; ++b) mbar_init(&bars[b], 1);
+        for (int c = 0; c <= nchunk; ++c) mbar_init(&bars[c], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
     if (tid == 0) {
-        for (int b = 0; b < nbox; ++b) {
-            mbar_expect_tx(&bars[b], (uint32_t)(rb * CW * sizeof(float)));
-            tma_load_2d(tile + (size_t)b * rb * CW, &a.tmap, c0, (int)(trow + (int64_t)b * rb), &bars[b]);
+        const uint32_t vb = (uint32_t)(hs * sizeof(float));
+        mbar_expect_tx(vbar, 5 * vb + (uint32_t)(CW * sizeof(float)));
+        bulk_load(ve, a.e + vo, vb, vbar);
+        bulk_load(vqg, a.qg + vo, vb, vbar);
+        for (int c = 0; c < nchunk; ++c) {
+            mbar_expect_tx(&bars[c], chunk_bytes);
+            bulk_load(tile + (size_t)c * cr * CW, gslice + (size_t)c * cr * CW, chunk_bytes, &bars[c]);
         }
+        bulk_load(vex, a.ex + vo, vb, vbar);
+        bulk_load(vw, a.w + vo, vb, vbar);
+        bulk_load(vah, a.ah + vo, vb, vbar);
+        bulk_load(vv, a.v + vo + c0, (uint32_t)(CW * sizeof(float)), vbar);
     }
-    for (int i = tid; i < hs; i += THREADS) {
-        ve[i] = a.e[vo + i];
-        vqg[i] = a.qg[vo + i];
-        vex[i] = a.ex[vo + i];
-        vw[i] = a.w[vo + i];
-        vah[i] = a.ah[vo + i];
-    }
-    if (tid < CW) vv[tid] = a.v[vo + c0 + tid];
-    __syncthreads();
+    bool ok = mbar_wait(vbar, 0);
+    mark(1);
 
-    // pass 1: the column sums, rows in order as their boxes land (the first CW threads, one column each)
-    bool ok = true;
+    // pass 1: the column sums, rows in order as their chunks land (the first CW threads, one column each).  The chain
+    // starts from -0: fma(f, e, -0) is the rounded product with its own sign, i.e. row 0's plain product.
     if (tid < CW) {
-        float r = 0.0f, t = 0.0f;
-        for (int b = 0; b < nbox; ++b) {
-            ok = ok && mbar_wait(&bars[b], 0);
-            const float* p = tile + (size_t)b * rb * CW + tid;
-            int row = b * rb;
-            if (b == 0) {
-                const float f = p[0];
-                r = mul(f, ve[0]);
-                t = mul(f, vqg[0]);
-                p += CW;
-                row = 1;
-            }
-#pragma unroll 8
-            for (; row < (b + 1) * rb; ++row, p += CW) {
-                const float f = *p;
-                r = fma(f, ve[row], r);
-                t = fma(f, vqg[row], t);
+        float r = -0.0f, t = -0.0f;
+        for (int c = 0; c < nchunk; ++c) {
+            ok = mbar_wait(&bars[c], 0) && ok;
+            const float* p = tile + (size_t)c * cr * CW + tid;
+            const int end = (c + 1) * cr;
+            for (int row = c * cr; row < end; row += 8, p += 8 * CW) {
+                float f[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] = p[i * CW];
+                const float4 e0 = *reinterpret_cast<const float4*>(ve + row), e1 = *reinterpret_cast<const float4*>(ve + row + 4);
+                const float4 g0 = *reinterpret_cast<const float4*>(vqg + row), g1 = *reinterpret_cast<const float4*>(vqg + row + 4);
+                const float ev[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
+                const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    r = fma(f[i], ev[i], r);
+                    t = fma(f[i], gv[i], t);
+                }
             }
         }
         // the recall's term from inside the one-token chunk is an exact zero (arch.rs:277-280): kept for the sign of zero
@@ -132,53 +146,68 @@ __global__ void __launch_bounds__(THREADS) mem_heads_kernel(const __grid_constan
         rr[tid] = r;
         t1[tid] = t;
     }
-    if (!ok) atomicOr(a.status, ST_WAIT_TIMEOUT);
+    mark(2);
     __syncthreads();
-    // every thread must see the boxes' bytes: a wait that succeeded makes them visible to its thread only
-    bool ok2 = true;
+    // a wait that succeeded makes the copied bytes visible to its own thread only: every other thread waits too
     if (tid >= CW)
-        for (int b = 0; b < nbox; ++b) ok2 = ok2 && mbar_wait(&bars[b], 0);
-    if (!ok2) atomicOr(a.status, ST_WAIT_TIMEOUT);
+        for (int c = 0; c < nchunk; ++c) ok = mbar_wait(&bars[c], 0) && ok;
+    if (!ok) atomicOr(a.status, ST_WAIT_TIMEOUT);
 
     // the read
     if (tid < CW) {
         const float qw = a.qw[(size_t)m * a.nh + head], qa = a.qa[(size_t)m * a.nh + head];
         a.y[vo + c0 + tid] = sub(add(t1[tid], mul(qw, vv[tid])), mul(qa, rr[tid]));
     }
-    // pass 2: the update, in place; thread -> (row group, column) so that a warp covers whole rows
+    // pass 2: the update in place, four columns per thread, chunk by chunk; each chunk goes back to HBM as soon as
+    // it is done
     {
-        const int col = tid % CW, rg = tid / CW, rgs = THREADS / CW;
-        const float vb = vv[col], rb_ = rr[col];
-        for (int row = rg; row < hs; row += rgs) {
-            float* p = tile + (size_t)row * CW + col;
-            *p = sub(add(mul(*p, vex[row]), mul(vw[row], vb)), mul(vah[row], rb_));
+        constexpr int QW = CW / 4, RPP = THREADS / QW;  // threads per row, rows per sweep
+        const int q4 = tid % QW, rg = tid / QW;
+        const float4 vb = *reinterpret_cast<const float4*>(vv + 4 * q4), rb4 = *reinterpret_cast<const float4*>(rr + 4 * q4);
+        for (int c = 0; c < nchunk; ++c) {
+            const int end = (c + 1) * cr;
+#pragma unroll 2
+            for (int row = c * cr + rg; row < end; row += RPP) {
+                float4* p = reinterpret_cast<float4*>(tile + (size_t)row * CW) + q4;
+                float4 f = *p;
+                const float x = vex[row], w = vw[row], ah = vah[row];
+                f.x = sub(add(mul(f.x, x), mul(w, vb.x)), mul(ah, rb4.x));
+                f.y = sub(add(mul(f.y, x), mul(w, vb.y)), mul(ah, rb4.y));
+                f.z = sub(add(mul(f.z, x), mul(w, vb.z)), mul(ah, rb4.z));
+                f.w = sub(add(mul(f.w, x), mul(w, vb.w)), mul(ah, rb4.w));
+                *p = f;
+            }
+            // generic-proxy writes must be visible to the bulk-copy engine before it reads the chunk
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncthreads();
+            if (tid == 0) {
+                bulk_store(gslice + (size_t)c * cr * CW, tile + (size_t)c * cr * CW, chunk_bytes);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
         }
     }
-    // make the generic-proxy writes visible to the TMA engine, then write the slice back
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
-    if (tid == 0) {
-        for (int b = 0; b < nbox; ++b) tma_store_2d(&a.tmap, c0, (int)(trow + (int64_t)b * rb), tile + (size_t)b * rb * CW);
-        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        // the shared memory must stay until the engine has read it
-        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-    }
+    mark(3);
+    // the shared memory must stay until the engine has read it
+    if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    mark(4);
 }
 
-size_t smem_bytes(int hs, int cw) { return ((size_t)hs * cw + 5 * (size_t)hs + 3 * (size_t)cw) * sizeof(float) + MAX_BOXES * sizeof(uint64_t); }
+size_t smem_bytes(int hs, int cw) { return ((size_t)hs * cw + 5 * (size_t)hs + 3 * (size_t)cw) * sizeof(float) + (MAX_CHUNKS + 1) * sizeof(uint64_t); }
 
 }  // namespace
 
-bool mem_heads_tiling(int hs, int* cw, int* rb) {
-    // rows per TMA box: at most 256; the head's rows must be whole boxes, at most MAX_BOXES of them
-    int r = hs <= 256 ? hs : 256;
-    if (hs % r != 0 || hs / r > MAX_BOXES) return false;
+bool mem_heads_tiling(int hs, int* cw, int* chunk_rows) {
+    if (hs % 16 != 0) return false;
     // the widest slice (128-byte rows) that leaves room for two blocks per SM, else 64-byte rows
     int w = 32;
     if (hs % w != 0 || smem_bytes(hs, w) > 113 * 1024) w = 16;
     if (hs % w != 0 || smem_bytes(hs, w) > 227 * 1024) return false;
+    // chunks of at least 64 rows, at most MAX_CHUNKS of them, dividing the head
+    int cr = hs <= 128 ? hs : 128;
+    while (hs / cr > MAX_CHUNKS) cr *= 2;
+    if (hs % cr != 0) return false;
     *cw = w;
-    *rb = r;
+    *chunk_rows = cr;
     return true;
 }
 
@@ -192,6 +221,24 @@ void launch_mem_heads(cudaStream_t st, const MemHeadsArgs& a) {
         cudaFuncSetAttribute(mem_heads_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         mem_heads_kernel<16><<<grid, THREADS, smem, st>>>(a);
     }
+}
+
+// natural [heads_total][hs][hs] <-> slice-major [heads_total][hs / cw][hs][cw]
+__global__ void retile_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t heads, int hs, int cw, int to_slices) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // index in the natural layout
+    if (i >= heads * hs * hs) return;
+    const int b = (int)(i % hs), a = (int)((i / hs) % hs);
+    const int64_t h = i / ((int64_t)hs * hs);
+    const int64_t j = (h * (hs / cw) + b / cw) * (int64_t)hs * cw + (int64_t)a * cw + b % cw;
+    if (to_slices)
+        dst[j] = src[i];
+    else
+        dst[i] = src[j];
+}
+
+void launch_retile(cudaStream_t st, const float* src, float* dst, int64_t heads, int hs, int cw, int to_slices) {
+    const int64_t n = heads * hs * hs;
+    retile_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(src, dst, heads, hs, cw, to_slices);
 }
 
 }  // namespace ava

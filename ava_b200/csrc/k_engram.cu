@@ -4,8 +4,10 @@
 // src/model/fstep/arch.rs:909-974): this token's key and value join the store first, then per head the scores
 // K_j . q (row 0's product, then fma over the head's dimensions) times 1/sqrt(hs), the maximum, exp(s - max), the
 // sum taken in key order from 0, each weight divided by it, and the mix p . V in gemm's one-row order over the keys.
-// One block of threads per row; the scores of all heads live in shared memory.  The store is a ring per row so that
-// an oldest-first cap (src/state.rs:526-538) drops a token by moving the start.
+// One block of threads per (row, group of heads); the group's scores live in shared memory.  Key rows are read with
+// 16-byte loads, values sixteen keys at a time ahead of the chain, so the loads overlap while every sum keeps the
+// reference's order.  The store is a ring per row so that an oldest-first cap (src/state.rs:526-538) drops a token by
+// moving the start.
 #include "ava_math.h"
 #include "kernels.cuh"
 
@@ -13,10 +15,12 @@ namespace ava {
 
 namespace {
 
+constexpr int ENG_THREADS = 256;
+
 template <bool BF16>
 __device__ __forceinline__ float kv_load(const void* base, size_t i) {
-    if (BF16) return bf16_to_f(reinterpret_cast<const uint16_t*>(base)[i]);
-    return reinterpret_cast<const float*>(base)[i];
+    if (BF16) return bf16_to_f(__ldg(reinterpret_cast<const uint16_t*>(base) + i));
+    return __ldg(reinterpret_cast<const float*>(base) + i);
 }
 template <bool BF16>
 __device__ __forceinline__ void kv_store(void* base, size_t i, float v) {
@@ -26,75 +30,110 @@ __device__ __forceinline__ void kv_store(void* base, size_t i, float v) {
         reinterpret_cast<float*>(base)[i] = v;
 }
 
+// eight consecutive stored elements starting at element i (i a multiple of 8), widened to f32
 template <bool BF16>
-__global__ void engram_kernel(const EngramArgs a) {
+__device__ __forceinline__ void kv_load8(const void* base, size_t i, float* out) {
+    if (BF16) {
+        const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + i);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            out[2 * k] = bits_to_f(w[k] << 16);
+            out[2 * k + 1] = bits_to_f(w[k] & 0xffff0000u);
+        }
+    } else {
+        const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + i);
+        const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + i + 4);
+        out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+        out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+    }
+}
+
+// hg heads per block; grid = M * (nh / hg)
+template <bool BF16>
+__global__ void __launch_bounds__(ENG_THREADS) engram_kernel(const EngramArgs a, int hg) {
     extern __shared__ float sm[];
-    __shared__ int s_n, s_start;
     const int d = a.d, hs = a.hs, nh = d / hs, cap = a.cap;
-    const int r = blockIdx.x, tid = threadIdx.x, T = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarp = T >> 5;
+    const int groups = nh / hg;
+    const int r = blockIdx.x / groups, h0 = (blockIdx.x % groups) * hg;
+    const int tid = threadIdx.x, T = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarp = T >> 5;
     const float* qkv = a.qkv + (size_t)r * 3 * d;
     const size_t row_base = (size_t)r * nh * cap * hs;
+    const int gd = hg * hs;  // channels of this group
 
+    // the counts are read by every block of the row and written by none: a second small kernel moves them afterwards
+    int n0 = a.n[r];
+    const int start = a.start[r];
+    if (n0 >= cap) {
+        if (tid == 0) atomicOr(a.status, ST_ENGRAM_FULL);
+        n0 = cap - 1;  // keep the kernel in bounds; the host reports the error
+    }
+    const int n = n0 + 1;
+    int slot = start + n0;
+    if (slot >= cap) slot -= cap;
     // this token's key and value join the store
-    if (tid == 0) {
-        int n = a.n[r];
-        if (n >= cap) {
-            atomicOr(a.status, ST_ENGRAM_FULL);
-            n = cap - 1;  // keep the kernel in bounds; the host reports the error
-        }
-        s_n = n;
-        s_start = a.start[r];
-    }
-    __syncthreads();
-    const int n0 = s_n, start = s_start, n = n0 + 1;
-    const int slot = (start + n0) % cap;
-    for (int c = tid; c < d; c += T) {
-        const int hh = c / hs, dd = c % hs;
+    for (int c = tid; c < gd; c += T) {
+        const int hh = h0 + c / hs, dd = c % hs;
         const size_t o = row_base + ((size_t)hh * cap + slot) * hs + dd;
-        kv_store<BF16>(a.k, o, qkv[d + c]);
-        kv_store<BF16>(a.v, o, qkv[2 * d + c]);
+        kv_store<BF16>(a.k, o, qkv[d + h0 * hs + c]);
+        kv_store<BF16>(a.v, o, qkv[2 * d + h0 * hs + c]);
     }
-    float* q = sm;              // [d]
-    float* mx = q + d;          // [nh]
-    float* den = mx + nh;       // [nh]
-    float* sc = den + nh;       // [nh][n]
-    for (int c = tid; c < d; c += T) q[c] = qkv[c];
+    float* q = sm;              // [gd]
+    float* mx = q + gd;         // [hg]
+    float* den = mx + hg;       // [hg]
+    float* sc = den + hg;       // [hg][n]
+    for (int c = tid; c < gd; c += T) q[c] = qkv[h0 * hs + c];
     __syncthreads();  // the stores above are visible to this block's loads below
 
     const float scale = (float)(1.0 / sqrt((double)hs));
-    for (int idx = tid; idx < nh * n; idx += T) {
-        const int hh = idx / n, j = idx % n;
-        const size_t o = row_base + ((size_t)hh * cap + (start + j) % cap) * hs;
-        const float* qh = q + hh * hs;
-        float s = mul(kv_load<BF16>(a.k, o), qh[0]);
-        for (int x = 1; x < hs; ++x) s = fma(kv_load<BF16>(a.k, o + x), qh[x], s);
-        sc[(size_t)hh * n + j] = add(mul(s, scale), 0.0f);
-    }
-    __syncthreads();
-    for (int hh = warp; hh < nh; hh += nwarp) {
-        float m = -INFINITY;
-        for (int j = lane; j < n; j += 32) m = fmaxf(m, sc[(size_t)hh * n + j]);
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        if (lane == 0) mx[hh] = m;
-    }
-    __syncthreads();
-    for (int idx = tid; idx < nh * n; idx += T) sc[idx] = expf_(sub(sc[idx], mx[idx / n]));
-    __syncthreads();
-    for (int hh = tid; hh < nh; hh += T) {
+    for (int idx = tid; idx < hg * n; idx += T) {
+        const int g = idx / n, j = idx % n;
+        int pj = start + j;
+        if (pj >= cap) pj -= cap;
+        const size_t o = row_base + ((size_t)(h0 + g) * cap + pj) * hs;
+        const float* qh = q + g * hs;
         float s = 0.0f;
-        const float* p = sc + (size_t)hh * n;
-        for (int j = 0; j < n; ++j) s = add(s, p[j]);
-        den[hh] = s;
+        for (int x0 = 0; x0 < hs; x0 += 32) {
+            float kv[32];
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+                if (x0 + 8 * b < hs) kv_load8<BF16>(a.k, o + x0 + 8 * b, kv + 8 * b);
+#pragma unroll
+            for (int x = 0; x < 32; ++x) {
+                if (x0 + x < hs) s = (x0 + x == 0) ? mul(kv[0], qh[0]) : fma(kv[x], qh[x0 + x], s);
+            }
+        }
+        sc[(size_t)g * n + j] = add(mul(s, scale), 0.0f);
     }
     __syncthreads();
-    for (int idx = tid; idx < nh * n; idx += T) sc[idx] = div(sc[idx], den[idx / n]);
+    for (int g = warp; g < hg; g += nwarp) {
+        float m = -INFINITY;
+        for (int j = lane; j < n; j += 32) m = fmaxf(m, sc[(size_t)g * n + j]);
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) mx[g] = m;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < hg * n; idx += T) sc[idx] = expf_(sub(sc[idx], mx[idx / n]));
+    __syncthreads();
+    for (int g = tid; g < hg; g += T) {
+        float s = 0.0f;
+        const float* p = sc + (size_t)g * n;
+        for (int j = 0; j < n; ++j) s = add(s, p[j]);
+        den[g] = s;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < hg * n; idx += T) sc[idx] = div(sc[idx], den[idx / n]);
     __syncthreads();
     // o = p . V: per output the chain over the keys (src/model/fstep.rs:222-257 with k = n)
-    for (int c = tid; c < d; c += T) {
-        const int hh = c / hs, dd = c % hs;
-        const float* p = sc + (size_t)hh * n;
-        const size_t hb = row_base + (size_t)hh * cap * hs + dd;
-        auto V = [&](int j) { return kv_load<BF16>(a.v, hb + (size_t)((start + j) % cap) * hs); };
+    for (int c = tid; c < gd; c += T) {
+        const int g = c / hs, dd = c % hs;
+        const float* p = sc + (size_t)g * n;
+        const size_t hb = row_base + (size_t)(h0 + g) * cap * hs + dd;
+        auto V = [&](int j) {
+            int pj = start + j;
+            if (pj >= cap) pj -= cap;
+            return kv_load<BF16>(a.v, hb + (size_t)pj * hs);
+        };
         float out;
         if (n == 1) {
             out = mul(V(0), p[0]);
@@ -102,18 +141,32 @@ __global__ void engram_kernel(const EngramArgs a) {
             out = add(mul(V(1), p[1]), mul(V(0), p[0]));
         } else {
             out = mul(V(0), p[0]);
-            for (int j = 1; j < n; ++j) out = fma(V(j), p[j], out);
+            int j = 1;
+            for (; j + 16 <= n; j += 16) {
+                float t[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) t[i] = V(j + i);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) out = fma(t[i], p[j + i], out);
+            }
+            for (; j < n; ++j) out = fma(V(j), p[j], out);
         }
-        a.o[(size_t)r * d + c] = out;
+        a.o[(size_t)r * d + h0 * hs + c] = out;
     }
-    // the read saw every token including the oldest; a capped store then drops the oldest (src/state.rs:526-538)
-    if (tid == 0) {
-        if (n > a.keep) {
-            a.n[r] = a.keep;
-            a.start[r] = (start + (n - a.keep)) % cap;
-        } else {
-            a.n[r] = n;
-        }
+}
+
+// after the read: the count moves on; a capped store drops its oldest tokens (src/state.rs:526-538)
+__global__ void engram_advance_kernel(int32_t* n, int32_t* start, int M, int cap, int keep) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= M) return;
+    int n0 = n[r];
+    if (n0 >= cap) n0 = cap - 1;
+    const int nn = n0 + 1;
+    if (nn > keep) {
+        n[r] = keep;
+        start[r] = (start[r] + (nn - keep)) % cap;
+    } else {
+        n[r] = nn;
     }
 }
 
@@ -121,18 +174,23 @@ __global__ void engram_kernel(const EngramArgs a) {
 
 bool launch_engram(cudaStream_t st, const EngramArgs& a, int n_max) {
     const int nh = a.d / a.hs;
-    const size_t smem = ((size_t)a.d + 2 * nh + (size_t)nh * n_max) * sizeof(float);
+    if (a.hs % 8 != 0) return false;
+    // heads per block: as many as give each thread one output channel, dividing the head count
+    int hg = ENG_THREADS / a.hs;
+    if (hg < 1) hg = 1;
+    if (hg > nh) hg = nh;
+    while (nh % hg != 0) --hg;
+    const size_t smem = ((size_t)hg * a.hs + 2 * hg + (size_t)hg * n_max) * sizeof(float);
     if (smem > 227 * 1024 - 64) return false;
-    int threads = ((a.d + 31) / 32) * 32;
-    if (threads > 1024) threads = 1024;
-    if (threads < 128) threads = 128;
+    const unsigned grid = (unsigned)(a.M * (nh / hg));
     if (a.bf16) {
         cudaFuncSetAttribute(engram_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        engram_kernel<true><<<a.M, threads, smem, st>>>(a);
+        engram_kernel<true><<<grid, ENG_THREADS, smem, st>>>(a, hg);
     } else {
         cudaFuncSetAttribute(engram_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        engram_kernel<false><<<a.M, threads, smem, st>>>(a);
+        engram_kernel<false><<<grid, ENG_THREADS, smem, st>>>(a, hg);
     }
+    engram_advance_kernel<<<(a.M + 127) / 128, 128, 0, st>>>(a.n, a.start, a.M, a.cap, a.keep);
     return true;
 }
 

@@ -14,28 +14,68 @@ namespace {
 
 constexpr float NORM_EPS = 1e-5f;  // src/model.rs:36
 
+// sum of x[i]^2 one after another from 0; x in shared memory, 16-byte aligned.  Eight values are fetched ahead of the
+// chain so that the loads overlap; the order of the additions is the reference's.
+__device__ __forceinline__ float sumsq_seq(const float* x, int n) {
+    float s = 0.0f;
+    int i = 0;
+    for (; i + 8 <= n; i += 8) {
+        const float4 a = *reinterpret_cast<const float4*>(x + i), b = *reinterpret_cast<const float4*>(x + i + 4);
+        const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        float p[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) p[k] = mul(v[k], v[k]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) s = add(s, p[k]);
+    }
+    for (; i < n; ++i) s = add(s, mul(x[i], x[i]));
+    return s;
+}
+
+// sum of a[i] * b[i] one after another from 0 (shared memory, 16-byte aligned)
+__device__ __forceinline__ float dot_seq(const float* a, const float* b, int n) {
+    float s = 0.0f;
+    int i = 0;
+    for (; i + 8 <= n; i += 8) {
+        const float4 a0 = *reinterpret_cast<const float4*>(a + i), a1 = *reinterpret_cast<const float4*>(a + i + 4);
+        const float4 b0 = *reinterpret_cast<const float4*>(b + i), b1 = *reinterpret_cast<const float4*>(b + i + 4);
+        const float p[8] = {mul(a0.x, b0.x), mul(a0.y, b0.y), mul(a0.z, b0.z), mul(a0.w, b0.w),
+                            mul(a1.x, b1.x), mul(a1.y, b1.y), mul(a1.z, b1.z), mul(a1.w, b1.w)};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) s = add(s, p[k]);
+    }
+    for (; i < n; ++i) s = add(s, mul(a[i], b[i]));
+    return s;
+}
+
 // (mean(x^2) + eps)^-1/2 with the squares summed in order (src/model/fstep.rs:212-220); x in shared memory
 __device__ __forceinline__ float inv_rms_seq(const float* x, int n) {
-    float s = 0.0f;
-    for (int i = 0; i < n; ++i) s = add(s, mul(x[i], x[i]));
+    const float s = sumsq_seq(x, n);
     const float ms = add(mul(s, (float)(1.0 / (double)n)), 0.0f);
     return rsqrtf_(add(mul(ms, 1.0f), NORM_EPS));
 }
 
 // (sum(x^2) + 1e-6)^-1/2 (src/model/fstep.rs:271-282)
 __device__ __forceinline__ float inv_l2_seq(const float* x, int n) {
-    float s = 0.0f;
-    for (int i = 0; i < n; ++i) s = add(s, mul(x[i], x[i]));
+    const float s = sumsq_seq(x, n);
     return rsqrtf_(add(mul(s, 1.0f), (float)1e-6));
 }
 
-// gemm's one-row product for one output: x [k] (shared), w[j * stride] the column's weights
-__device__ __forceinline__ float gemv_col(const float* x, int k, const float* w, int stride) {
+// gemm's one-row product for one output: x [k] (shared), w[j * stride] the column's weights (global).  The weights are
+// fetched sixteen at a time ahead of the chain so that their latency overlaps; the chain's order is untouched.
+__device__ __forceinline__ float gemv_col(const float* x, int k, const float* __restrict__ w, int stride) {
     if (k == 0) return 0.0f;
     if (k == 1) return mul(w[0], x[0]);
     if (k == 2) return add(mul(w[stride], x[1]), mul(w[0], x[0]));
     float out = mul(w[0], x[0]);
-    for (int j = 1; j < k; ++j) out = fma(w[(size_t)j * stride], x[j], out);
+    for (int j = 1; j < k; j += 16) {
+        float t[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) t[i] = (j + i < k) ? __ldg(w + (size_t)(j + i) * stride) : 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (j + i < k) out = fma(t[i], x[j + i], out);
+    }
     return out;
 }
 
@@ -63,7 +103,7 @@ __global__ void embed_kernel(const float* __restrict__ tok_emb, const uint32_t* 
 // ---------------------------------------------------------------------------------------------------- RMS norm
 // One warp per row: the row is staged in shared memory, lane 0 takes the ordered sum, every lane scales.
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain, int M, int n, float* __restrict__ y) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x * (blockDim.x >> 5) + warp;
     if (r >= M) return;
@@ -81,7 +121,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 // ---------------------------------------------------------------------------------------------------- memory: gates
 // src/model/fstep/arch.rs:685-803 for one row per block of threads.
 __global__ void mem_prep_kernel(const MemPrepArgs a) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     const int d = a.d, hs = a.hs, nh = d / hs, rk = a.rank;
     const int r = blockIdx.x, tid = threadIdx.x, T = blockDim.x;
     float* h = sm;            // [d]
@@ -109,27 +149,29 @@ __global__ void mem_prep_kernel(const MemPrepArgs a) {
         ek[c] = add(kk, pr[3 * d + c]);
     }
     __syncthreads();
-    // the independent ordered chains, one per thread
-    const int nroles = 5 * nh + 2 * rk;
-    for (int role = tid; role < nroles; role += T) {
-        if (role < nh) {
-            inv_q[role] = inv_l2_seq(q + role * hs, hs);
-        } else if (role < 2 * nh) {
-            inv_k[role - nh] = inv_l2_seq(kr + (role - nh) * hs, hs);
-        } else if (role < 3 * nh) {
-            inv_e[role - 2 * nh] = inv_l2_seq(ek + (role - 2 * nh) * hs, hs);
-        } else if (role < 4 * nh) {
-            const int e = role - 3 * nh;
-            za[e] = add(gemv_col(h, d, a.wa + e, nh), a.ba[e]);
-        } else if (role < 5 * nh) {
-            const int e = role - 4 * nh;
-            zb[e] = add(gemv_col(h, d, a.wb + e, nh), a.bb[e]);
-        } else if (role < 5 * nh + rk) {
-            const int i = role - 5 * nh;
-            z1a[i] = gemv_col(h, d, a.wa1 + i, rk);
+    // the independent ordered chains, one per thread.  Chains of one kind run the same code, so each kind gets its own
+    // warps (a warp whose lanes ran different kinds would run them one after another): warps 0-1 the three sums of
+    // squares per head, warps 2-3 the per-head gate projections, warps 4.. the low-rank projections.
+    {
+        const int warp = tid >> 5, lane = tid & 31, nwarp = T >> 5;
+        if (warp < 2) {
+            for (int it = warp * 32 + lane; it < 3 * nh; it += 64) {
+                const int which = it / nh, e = it % nh;
+                const float* src = (which == 0 ? q : which == 1 ? kr : ek) + e * hs;
+                (which == 0 ? inv_q : which == 1 ? inv_k : inv_e)[e] = inv_l2_seq(src, hs);
+            }
+        } else if (warp < 4) {
+            for (int it = (warp - 2) * 32 + lane; it < 2 * nh; it += 64) {
+                const int which = it / nh, e = it % nh;
+                const float z = gemv_col(h, d, (which ? a.wb : a.wa) + e, nh);
+                (which ? zb : za)[e] = add(z, (which ? a.bb : a.ba)[e]);
+            }
         } else {
-            const int i = role - 5 * nh - rk;
-            z1b[i] = gemv_col(h, d, a.wb1 + i, rk);
+            const int cw = nwarp - 4;
+            for (int it = (warp - 4) * 32 + lane; it < 2 * rk; it += cw * 32) {
+                const int which = it / rk, i = it % rk;
+                (which ? z1b : z1a)[i] = gemv_col(h, d, (which ? a.wb1 : a.wa1) + i, rk);
+            }
         }
     }
     __syncthreads();
@@ -176,16 +218,14 @@ __global__ void mem_prep_kernel(const MemPrepArgs a) {
     for (int role = tid; role < 2 * nh; role += T) {
         const int e = role % nh;
         const float* b = role < nh ? wv : ahv;
-        float s = 0.0f;
-        for (int c = e * hs; c < (e + 1) * hs; ++c) s = add(s, mul(q[c], b[c]));
-        (role < nh ? a.qw : a.qa)[(size_t)r * nh + e] = s;
+        (role < nh ? a.qw : a.qa)[(size_t)r * nh + e] = dot_seq(q + e * hs, b + e * hs, hs);
     }
 }
 
 // ---------------------------------------------------------------------------------------------------- memory: output
 // head norm, then the silu output gate (src/model/fstep/arch.rs:842-852)
 __global__ void mem_post_kernel(const float* __restrict__ y_raw, const float* __restrict__ gate, int ldg, int M, int d, int hs, float* __restrict__ y) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     const int nh = d / hs, r = blockIdx.x, tid = threadIdx.x, T = blockDim.x;
     float* ys = sm;
     float* inv = sm + d;

@@ -46,6 +46,10 @@ struct GemmArgs {
 // the sum then times scale[n]: the bits of the reference's int8 product (src/int8.rs:315-331).  K % 16 == 0, N % 4 == 0.
 void launch_q8_gemm(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int sm_count);
 
+// The same product for rows that are mostly zeros (spikes, k-WTA'd units): summed over the non-zero inputs only, in
+// order, which gives the dense sum's bits (src/int8.rs:10-13).  false: shape not covered, use launch_q8_gemm.
+bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi);
+
 // ---- row kernels ----------------------------------------------------------------------------------------------
 void launch_embed(cudaStream_t st, const float* tok_emb, const uint32_t* tok, int M, int d, int vocab, float* x, float* stream0, uint32_t* status);
 void launch_rmsnorm(cudaStream_t st, const float* x, const float* gain, int M, int n, float* y);
@@ -67,17 +71,19 @@ struct MemPrepArgs {
 void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a);
 
 struct MemHeadsArgs {
-    CUtensorMap tmap;    // the fast weights as a 2-D tensor [rows_total, hs] f32, box [cw, rb]
-    int64_t row0;        // first tensor row of this launch's (row 0, head 0)
-    int M, nh, hs, cw, rb;
+    float* f;            // this block's fast weights, slice-major: [M][nh][hs / cw][hs][cw] f32, updated in place
+    int M, nh, hs, cw, chunk_rows;
     const float *e, *v, *w, *ah, *qg, *ex;  // [M, nh * hs]
     const float *qw, *qa;                    // [M, nh]
     float* y;                                // [M, nh * hs]
     uint32_t* status;
+    unsigned long long* timeline;            // nullptr, or [blocks][6] phase marks in ns (tuning aid)
 };
 void launch_mem_heads(cudaStream_t st, const MemHeadsArgs& a);
-// the column-slice width and rows-per-box the kernel uses for a head size; false: head size not covered
-bool mem_heads_tiling(int hs, int* cw, int* rb);
+// the column-slice width and the rows per bulk copy the kernel uses for a head size; false: head size not covered
+bool mem_heads_tiling(int hs, int* cw, int* chunk_rows);
+// natural [heads][hs][hs] to slice-major [heads][hs / cw][hs][cw] (to_slices 1) or back (0)
+void launch_retile(cudaStream_t st, const float* src, float* dst, int64_t heads, int hs, int cw, int to_slices);
 
 void launch_mem_post(cudaStream_t st, const float* y_raw, const float* gate, int ldg, int M, int d, int hs, float* y);
 

@@ -48,7 +48,16 @@ int end_() {
 
 extern "C" {
 
+static int q8_matmul_impl(int device, const float* x, int32_t m, const int8_t* q, const float* scale, int32_t din, int32_t dout, float* y, bool event);
+
 int ava_op_q8_matmul(int device, const float* x, int32_t m, const int8_t* q, const float* scale, int32_t din, int32_t dout, float* y) {
+    return q8_matmul_impl(device, x, m, q, scale, din, dout, y, false);
+}
+int ava_op_q8_event_matmul(int device, const float* x, int32_t m, const int8_t* q, const float* scale, int32_t din, int32_t dout, float* y) {
+    return q8_matmul_impl(device, x, m, q, scale, din, dout, y, true);
+}
+
+static int q8_matmul_impl(int device, const float* x, int32_t m, const int8_t* q, const float* scale, int32_t din, int32_t dout, float* y, bool event) {
     if (!x || !q || !scale || !y || m <= 0 || din <= 0 || dout <= 0) return AVA_ERR_ARG;
     if (din % 16 || dout % 4) return AVA_NOT_APPLICABLE;
     int rc = begin(device);
@@ -63,7 +72,11 @@ int ava_op_q8_matmul(int device, const float* x, int32_t m, const int8_t* q, con
     g.C = dy.as<float>(); g.ldc = dout; g.M = m; g.N = dout; g.K = din;
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    launch_q8_gemm(0, g, EPI_STORE, sms);
+    if (event) {
+        if (!launch_q8_event(0, g, EPI_STORE)) return AVA_NOT_APPLICABLE;
+    } else {
+        launch_q8_gemm(0, g, EPI_STORE, sms);
+    }
     if ((rc = end_())) return rc;
     OCK(cudaMemcpy(y, dy.p, (size_t)m * dout * 4, cudaMemcpyDeviceToHost));
     return AVA_OK;
@@ -143,24 +156,14 @@ int ava_op_mem_heads(int device, int32_t m, int32_t hs, const float* e, const fl
     OCK(up(dst, nullptr, 4));
     OCK(cudaMemset(dst.p, 0, 4));
     MemHeadsArgs a{};
-    {
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult qr;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) != cudaSuccess || qr != cudaDriverEntryPointSuccess) return AVA_ERR_CUDA;
-        typedef CUresult (*Fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                               const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-        const cuuint64_t dims[2] = {(cuuint64_t)hs, (cuuint64_t)m * hs};
-        const cuuint64_t strides[1] = {(cuuint64_t)hs * 4};
-        const cuuint32_t box[2] = {(cuuint32_t)cw, (cuuint32_t)rb};
-        const cuuint32_t es[2] = {1, 1};
-        if (((Fn)fn)(&a.tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, df.p, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-            return AVA_ERR_CUDA;
-    }
-    a.row0 = 0; a.M = m; a.nh = 1; a.hs = hs; a.cw = cw; a.rb = rb;
+    Tmp dft;  // the slice-major copy the kernel works on
+    OCK(up(dft, nullptr, fb));
+    launch_retile(0, df.as<float>(), dft.as<float>(), m, hs, cw, 1);
+    a.f = dft.as<float>(); a.M = m; a.nh = 1; a.hs = hs; a.cw = cw; a.chunk_rows = rb;
     a.e = de.as<float>(); a.v = dv.as<float>(); a.w = dw.as<float>(); a.ah = dah.as<float>(); a.qg = dqg.as<float>(); a.ex = dex.as<float>();
     a.qw = dqw.as<float>(); a.qa = dqa.as<float>(); a.y = dy.as<float>(); a.status = dst.as<uint32_t>();
     launch_mem_heads(0, a);
+    launch_retile(0, dft.as<float>(), df.as<float>(), m, hs, cw, 0);
     if ((rc = end_())) return rc;
     uint32_t st = 0;
     OCK(cudaMemcpy(&st, dst.p, 4, cudaMemcpyDeviceToHost));
@@ -168,6 +171,32 @@ int ava_op_mem_heads(int device, int32_t m, int32_t hs, const float* e, const fl
     OCK(cudaMemcpy(f, df.p, fb, cudaMemcpyDeviceToHost));
     OCK(cudaMemcpy(y, dy.p, vb, cudaMemcpyDeviceToHost));
     return AVA_OK;
+}
+
+/* Tuning aid: the fast-weight kernel on m zeroed heads of size hs with the phase clock on; out [blocks][6] ns marks
+ * (start, vectors staged, column sums done, update done and stores issued, stores read out), returns the block count. */
+int ava_debug_mem_heads_timeline(int device, int32_t m, int32_t hs, uint64_t* out, int64_t cap) {
+    int cw, rb;
+    if (!out || m <= 0 || hs % 16 || !mem_heads_tiling(hs, &cw, &rb)) return AVA_ERR_ARG;
+    int rc = begin(device);
+    if (rc) return rc;
+    const int64_t blocks = (int64_t)m * (hs / cw);
+    if (cap < blocks * 6) return AVA_ERR_ARG;
+    const size_t vb = (size_t)m * hs * 4, fb = (size_t)m * hs * hs * 4;
+    Tmp dv, dq, df, dy, dst, dtl;
+    OCK(up(dv, nullptr, vb)); OCK(up(dq, nullptr, (size_t)m * 4)); OCK(up(df, nullptr, fb)); OCK(up(dy, nullptr, vb)); OCK(up(dst, nullptr, 4));
+    OCK(up(dtl, nullptr, (size_t)blocks * 6 * 8));
+    OCK(cudaMemset(dv.p, 0, vb)); OCK(cudaMemset(dq.p, 0, (size_t)m * 4)); OCK(cudaMemset(df.p, 0, fb)); OCK(cudaMemset(dst.p, 0, 4));
+    MemHeadsArgs a{};
+    a.f = df.as<float>(); a.M = m; a.nh = 1; a.hs = hs; a.cw = cw; a.chunk_rows = rb;
+    a.e = a.v = a.w = a.ah = a.qg = a.ex = dv.as<float>(); a.qw = a.qa = dq.as<float>(); a.y = dy.as<float>(); a.status = dst.as<uint32_t>();
+    launch_mem_heads(0, a);  // warm
+    a.timeline = dtl.as<unsigned long long>();
+    OCK(cudaMemset(dtl.p, 0, (size_t)blocks * 6 * 8));
+    launch_mem_heads(0, a);
+    if ((rc = end_())) return rc;
+    OCK(cudaMemcpy(out, dtl.p, (size_t)blocks * 6 * 8, cudaMemcpyDeviceToHost));
+    return (int)blocks;
 }
 
 int ava_op_attend(int device, int32_t m, int32_t n, int32_t hs, int32_t bf16_store, const float* q, const float* kc, const float* vc, float* out) {

@@ -85,6 +85,8 @@ def lib() -> C.CDLL:
         "ava_debug_width": ([vp, C.c_char_p], C.c_int64),
         "ava_debug_get": ([vp, C.c_char_p, C.c_int32, fp], C.c_int),
         "ava_op_q8_matmul": ([C.c_int, fp, C.c_int32, i8p, fp, C.c_int32, C.c_int32, fp], C.c_int),
+        "ava_op_q8_event_matmul": ([C.c_int, fp, C.c_int32, i8p, fp, C.c_int32, C.c_int32, fp], C.c_int),
+        "ava_debug_mem_heads_timeline": ([C.c_int, C.c_int32, C.c_int32, C.POINTER(C.c_uint64), C.c_int64], C.c_int),
         "ava_op_rmsnorm": ([C.c_int, fp, fp, C.c_int32, C.c_int32, fp], C.c_int),
         "ava_op_lif": ([C.c_int, fp, fp, fp, fp, fp, C.c_int32, fp, fp, fp, C.c_int32, C.c_int32, fp, fp, fp], C.c_int),
         "ava_op_kwta": ([C.c_int, fp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, fp], C.c_int),
@@ -108,7 +110,7 @@ EXPORTS = ("ava_engine_create ava_engine_destroy ava_last_error ava_engine_set_f
            "ava_state_rows ava_state_select ava_state_cat ava_state_seen ava_state_len ava_state_export "
            "ava_state_import ava_step ava_step_greedy ava_forward_with_state ava_step_device ava_sync "
            "ava_engine_stream ava_engine_launches ava_engine_bytes ava_state_bytes ava_debug_keep ava_debug_width "
-           "ava_debug_get ava_prof_enable ava_prof_read ava_prof_names ava_op_q8_matmul ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_op_attend "
+           "ava_debug_get ava_prof_enable ava_prof_read ava_prof_names ava_op_q8_matmul ava_op_q8_event_matmul ava_debug_mem_heads_timeline ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_op_attend "
            "ava_host_expf ava_host_logf ava_host_rsqrtf ava_op_math").split()
 
 
@@ -312,13 +314,14 @@ def _rc(rc):
         raise EngineError(rc, "operator failed")
 
 
-def op_q8_matmul(x, q, scale, device=0):
+def op_q8_matmul(x, q, scale, device=0, event=False):
     x = _f32(x)
     x2 = x.reshape(-1, x.shape[-1])
     q = np.ascontiguousarray(q, np.int8)
     scale = _f32(scale)
     y = np.empty((x2.shape[0], q.shape[1]), np.float32)
-    _rc(lib().ava_op_q8_matmul(device, _p(x2), x2.shape[0], _p(q, i8p), _p(scale), q.shape[0], q.shape[1], _p(y)))
+    f = lib().ava_op_q8_event_matmul if event else lib().ava_op_q8_matmul
+    _rc(f(device, _p(x2), x2.shape[0], _p(q, i8p), _p(scale), q.shape[0], q.shape[1], _p(y)))
     return y.reshape(x.shape[:-1] + (q.shape[1],))
 
 

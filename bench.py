@@ -274,6 +274,7 @@ def main():
                      "mean_launch_ms": ms_mh / max(n_mh, 1), "launches_timed": n_mh,
                      "step_bytes_per_token": tok_bytes, "step_frac_of_hbm_roofline": step_frac},
         "kernel_share": {k: round(v[1] / total_ms, 4) for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])},
+        "kernel_ms_per_step": {k: round(v[1] / 4, 4) for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])},
     }
     if rank == 0 and not args.no_cpu and not args.small:
         threads = os.cpu_count() or 1

@@ -149,6 +149,9 @@ int ava_debug_get(ava_engine* e, const char* name, int32_t block, float* out);
 
 /* `QW::matmul_rows` (src/int8.rs:124): y [m, dout] = x [m, din] . W.  Same bits as the reference's ordered sum. */
 int ava_op_q8_matmul(int device, const float* x, int32_t m, const int8_t* q, const float* scale, int32_t din, int32_t dout, float* y);
+/* The same through the event-sum kernel (E2, src/int8.rs:10-13,142-163): only the non-zero inputs of each row are
+ * summed, in order; the same bits as the dense sum for any input. */
+int ava_op_q8_event_matmul(int device, const float* x, int32_t m, const int8_t* q, const float* scale, int32_t din, int32_t dout, float* y);
 /* `fstep::rmsnorm` (src/model/fstep.rs:207-220) on m rows of n. */
 int ava_op_rmsnorm(int device, const float* x, const float* gain, int32_t m, int32_t n, float* y);
 /* `fstep::arch::lif` (src/model/fstep/arch.rs:173-228) on m rows of d; theta/rho/gain/a0/a1 may be NULL. */
@@ -164,6 +167,10 @@ int ava_op_mem_heads(int device, int32_t m, int32_t hs, const float* e, const fl
 /* `attend` (src/model/fstep.rs:303-327) for m heads over n keys/values of hs (f32, or rounded to bf16 first). */
 int ava_op_attend(int device, int32_t m, int32_t n, int32_t hs, int32_t bf16_store, const float* q, const float* kc,
                   const float* vc, float* out);
+
+/* Tuning aid with no counterpart in the reference: the fast-weight kernel on m zeroed heads of size hs with its phase
+ * clock on; out [blocks][6] nanosecond marks, returns the number of blocks (or < 0). */
+int ava_debug_mem_heads_timeline(int device, int32_t m, int32_t hs, uint64_t* out, int64_t cap);
 
 /* The engine's exp / ln / x^-1/2, evaluated on the host with the operation sequence the kernels use (same bits). */
 float ava_host_expf(float x);

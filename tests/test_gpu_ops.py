@@ -67,6 +67,25 @@ def test_q8_matmul_bits(orc, m, din, dout):
         assert np.array_equal(bits(got[2]), bits(exact))
 
 
+@pytest.mark.parametrize("density", [0.0, 0.02, 0.25, 0.6, 1.0])
+@pytest.mark.parametrize("din,dout", [(768, 768), (3072, 768), (128, 320)])
+def test_event_sum_bits(orc, density, din, dout):
+    """The event-sum kernel (non-zero inputs only, in order) gives the dense sum's bits at any density."""
+    rng = np.random.default_rng(int(density * 100) + din)
+    m = 9
+    q = rng.integers(-127, 128, (din, dout)).astype(np.int8)
+    sc = (rng.uniform(0.5, 1.5, dout) / 127).astype(np.float32)
+    x = np.zeros((m, din), np.float32)
+    on = rng.random((m, din)) < density
+    x[on] = rng.normal(size=on.sum())
+    x[0][on[0]] = rng.integers(-2, 3, on[0].sum())   # spikes
+    x[1, ::7] = -0.0
+    want = orc.q8_matmul(x, q, sc)
+    got = engine.op_q8_matmul(x, q, sc, event=True)
+    assert np.array_equal(bits(got), bits(want))
+    assert np.array_equal(bits(engine.op_q8_matmul(x, q, sc)), bits(want))
+
+
 @pytest.mark.parametrize("m,n", [(1, 64), (7, 768), (300, 2048)])
 def test_rmsnorm_bits(orc_same_math, m, n):
     rng = np.random.default_rng(n)
