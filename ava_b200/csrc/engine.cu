@@ -66,7 +66,7 @@ struct HostQ {
 };
 
 struct BlockDev {
-    Dev mem_norm, beta, theta, rho, again, hebb_norm, wa, wb, ba, bb, wa1, wa2, wb1, wb2, off, vres, eng_norm, mlp_norm, dense;
+    Dev mem_norm, beta, theta, rho, again, hebb_norm, gate_w, ba, bb, wa2, wb2, off, vres, eng_norm, mlp_norm, dense;
     QMat win, wout, proj, wo, eqkv, ewo, w1, w2;
 };
 
@@ -102,6 +102,7 @@ struct ava_engine {
     QMat head;
     std::vector<std::unique_ptr<BlockDev>> blocks;
     int cw = 0, rb = 0;  // fast-weight slice width and rows per bulk copy
+    int gate_cols = 0, gate_chunk = 0;  // the gates' projection matrix: padded columns, rows per staged chunk
 
     // work buffers for `ws_rows` rows
     int ws_rows = 0;
@@ -386,8 +387,8 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         mp.h = h;
         mp.proj = e->proj.as<float>();
         mp.ldp = pw;
-        mp.wa = b.wa.as<float>(); mp.wb = b.wb.as<float>(); mp.ba = b.ba.as<float>(); mp.bb = b.bb.as<float>();
-        mp.wa1 = b.wa1.as<float>(); mp.wa2 = b.wa2.as<float>(); mp.wb1 = b.wb1.as<float>(); mp.wb2 = b.wb2.as<float>();
+        mp.gate_w = b.gate_w.as<float>(); mp.gate_cols = e->gate_cols; mp.gate_chunk = e->gate_chunk;
+        mp.ba = b.ba.as<float>(); mp.bb = b.bb.as<float>(); mp.wa2 = b.wa2.as<float>(); mp.wb2 = b.wb2.as<float>();
         mp.off = b.off.as<float>();
         mp.vres = (c.value_residual && i > 0 && b.vres.p) ? b.vres.as<float>() : nullptr;
         mp.v_first = e->v_first.as<float>();
@@ -647,6 +648,12 @@ int ava_engine_create(const ava_config* cfg, int device, ava_engine** out) {
     }
     const char* why = find_blocker(e->cfg, &e->cw, &e->rb);
     if (why) e->blocker = why;
+    if (!why) {
+        e->gate_cols = ((2 * e->nh() + 2 * cfg->gate_rank + 3) / 4) * 4;
+        e->gate_chunk = 128;
+        while (cfg->d % e->gate_chunk) e->gate_chunk /= 2;
+        if (e->gate_cols > 224) e->blocker = "too many gate projection columns (heads and gate rank) for the gate kernel";
+    }
     *out = e.release();
     return AVA_OK;
 }
@@ -742,9 +749,24 @@ int ava_engine_finalize(ava_engine* e) {
         if ((rc = upload_f32(e, b.theta, p + "mem.theta", c.theta != 0))) return rc;
         if ((rc = upload_f32(e, b.hebb_norm, p + "hebb.norm", true))) return rc;
         struct F { Dev* d; const char* n; };
-        for (const F& f : {F{&b.wa, "hebb.wa"}, F{&b.wb, "hebb.wb"}, F{&b.ba, "hebb.ba"}, F{&b.bb, "hebb.bb"}, F{&b.wa1, "hebb.wa1"},
-                           F{&b.wa2, "hebb.wa2"}, F{&b.wb1, "hebb.wb1"}, F{&b.wb2, "hebb.wb2"}, F{&b.off, "hebb.off"}, F{&b.mlp_norm, "mlp.norm"}})
+        for (const F& f : {F{&b.ba, "hebb.ba"}, F{&b.bb, "hebb.bb"}, F{&b.wa2, "hebb.wa2"}, F{&b.wb2, "hebb.wb2"}, F{&b.off, "hebb.off"},
+                           F{&b.mlp_norm, "mlp.norm"}})
             if ((rc = upload_f32(e, *f.d, p + f.n, true))) return rc;
+        {
+            // the gates' first-stage projections side by side [d][wa | wb | wa1 | wb1 | zero padding]: one staged stream
+            const int nh = e->nh(), rk = c.gate_rank, ncp = e->gate_cols;
+            std::vector<float> gw((size_t)c.d * ncp, 0.0f);
+            struct G { const char* n; int w; };
+            int c0 = 0;
+            for (const G& gpart : {G{"hebb.wa", nh}, G{"hebb.wb", nh}, G{"hebb.wa1", rk}, G{"hebb.wb1", rk}}) {
+                auto it = e->host_f32.find(p + gpart.n);
+                if (it == e->host_f32.end()) return e->fail(AVA_ERR_MISSING, "missing tensor %s%s", p.c_str(), gpart.n);
+                for (int j = 0; j < c.d; ++j)
+                    for (int k = 0; k < gpart.w; ++k) gw[(size_t)j * ncp + c0 + k] = it->second[(size_t)j * gpart.w + k];
+                c0 += gpart.w;
+            }
+            if ((rc = upload(e, b.gate_w, gw.data(), gw.size() * sizeof(float)))) return rc;
+        }
         if ((rc = upload_f32(e, b.vres, p + "hebb.vres", c.value_residual && i > 0))) return rc;
         if ((rc = upload_f32(e, b.dense, p + "dense", c.dense != 0))) return rc;
         if ((rc = upload_q8(e, b.win, {p + "mem.win"}))) return rc;
@@ -1003,7 +1025,7 @@ int64_t ava_engine_bytes(const ava_engine* e) {
     int64_t n = e->tok_emb.bytes + e->final_norm.bytes + e->head.q.bytes + e->head.scale.bytes;
     for (const auto& bp : e->blocks) {
         const BlockDev& b = *bp;
-        for (const Dev* d : {&b.mem_norm, &b.beta, &b.theta, &b.rho, &b.again, &b.hebb_norm, &b.wa, &b.wb, &b.ba, &b.bb, &b.wa1, &b.wa2, &b.wb1, &b.wb2,
+        for (const Dev* d : {&b.mem_norm, &b.beta, &b.theta, &b.rho, &b.again, &b.hebb_norm, &b.gate_w, &b.ba, &b.bb, &b.wa2, &b.wb2,
                              &b.off, &b.vres, &b.eng_norm, &b.mlp_norm, &b.dense})
             n += d->bytes;
         for (const QMat* q : {&b.win, &b.wout, &b.proj, &b.wo, &b.eqkv, &b.ewo, &b.w1, &b.w2}) n += q->q.bytes + q->scale.bytes;

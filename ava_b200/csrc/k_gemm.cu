@@ -15,6 +15,16 @@ namespace {
 
 constexpr int BK = 16;
 
+// Four int8 weights packed in a word, widened to f32 without the (quarter-rate) integer-to-float unit: a byte b + 128
+// placed in the mantissa of 2^23 is the float 8388608 + b + 128 exactly, and subtracting 8388736 leaves b.
+__device__ __forceinline__ void widen4(int w, float* f) {
+    const unsigned u = (unsigned)w ^ 0x80808080u;
+    f[0] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7440)) - 8388736.0f;
+    f[1] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7441)) - 8388736.0f;
+    f[2] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7442)) - 8388736.0f;
+    f[3] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7443)) - 8388736.0f;
+}
+
 __device__ __forceinline__ void lif_update(const LifParams& p, int r, int c, int d, float cur) {
     // src/model/fstep/arch.rs:173-228 with the hard spike count taken directly (as the reference's own GPU kernel
     // does; the CPU's soft + (hard - soft) equals it).
@@ -49,20 +59,26 @@ __device__ __forceinline__ void lif_update(const LifParams& p, int r, int c, int
     p.s[i] = s;
 }
 
-template <int BM, int BN, int EPI>
-__global__ void __launch_bounds__((BM / 4) * (BN / 4)) q8_gemm_kernel(const GemmArgs g) {
-    constexpr int T = (BM / 4) * (BN / 4);
+// Tile BM x BN per block, TM x TN outputs per thread (TM = 4; TN = 4 or 2).  Wide products use 64x64 tiles of 4x4; the
+// narrow ones (N = d) use 32x64 tiles of 4x2 so that twice the warps share the same work and cover each other's
+// shared-memory latency.
+template <int BM, int BN, int TM, int TN, int EPI>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN)) q8_gemm_kernel(const GemmArgs g) {
+    static_assert((TM == 4 || TM == 8) && (TN == 8 || TN == 4 || TN == 2), "micro-tile");
+    constexpr int T = (BM / TM) * (BN / TN);
     constexpr int AS = BM + 4;  // padded row length of the k-major A tile
     __shared__ __align__(16) float As[2][BK][AS];
     __shared__ __align__(16) float Ws[2][BK][BN];
 
     const int tid = threadIdx.x;
-    const int tx = tid % (BN / 4), ty = tid / (BN / 4);
+    const int tx = tid % (BN / TN), ty = tid / (BN / TN);
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int nk = g.K / BK;
 
-    constexpr int A_LOADS = (BM * 4 + T - 1) / T;   // float4 per thread
-    constexpr int W_LOADS = (BN * 4 + T - 1) / T;   // char4 per thread
+    constexpr int KQ = BK / 4;                      // float4 per A-tile row
+    constexpr int A_N = BM * KQ, W_N = BK * BN / 4; // float4 of the A tile, words of the W tile
+    constexpr int A_LOADS = (A_N + T - 1) / T;      // float4 per thread
+    constexpr int W_LOADS = (W_N + T - 1) / T;      // char4 per thread
     constexpr int PF = 4;                           // tiles fetched ahead into registers (global latency cover)
     float4 ra[PF][A_LOADS];
     int rw[PF][W_LOADS];
@@ -71,9 +87,9 @@ __global__ void __launch_bounds__((BM / 4) * (BN / 4)) q8_gemm_kernel(const Gemm
 #pragma unroll
         for (int i = 0; i < A_LOADS; ++i) {
             const int idx = tid + i * T;
-            const int row = idx >> 2, kq = idx & 3;
+            const int row = idx / KQ, kq = idx % KQ;
             fa[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (kt < nk && idx < BM * 4 && m0 + row < g.M)
+            if (kt < nk && idx < A_N && m0 + row < g.M)
                 fa[i] = *reinterpret_cast<const float4*>(g.A + (size_t)(m0 + row) * g.lda + kt * BK + kq * 4);
         }
 #pragma unroll
@@ -81,7 +97,7 @@ __global__ void __launch_bounds__((BM / 4) * (BN / 4)) q8_gemm_kernel(const Gemm
             const int idx = tid + i * T;
             const int k = idx / (BN / 4), n4 = idx % (BN / 4);
             fw[i] = 0;
-            if (kt < nk && idx < BN * 4 && n0 + n4 * 4 < g.N)
+            if (kt < nk && idx < W_N && n0 + n4 * 4 < g.N)
                 fw[i] = __ldg(reinterpret_cast<const int*>(g.W + (size_t)(kt * BK + k) * g.ldw + n0 + n4 * 4));
         }
     };
@@ -89,8 +105,8 @@ __global__ void __launch_bounds__((BM / 4) * (BN / 4)) q8_gemm_kernel(const Gemm
 #pragma unroll
         for (int i = 0; i < A_LOADS; ++i) {
             const int idx = tid + i * T;
-            const int row = idx >> 2, kq = idx & 3;
-            if (idx < BM * 4) {
+            const int row = idx / KQ, kq = idx % KQ;
+            if (idx < A_N) {
                 As[buf][kq * 4 + 0][row] = fa[i].x;
                 As[buf][kq * 4 + 1][row] = fa[i].y;
                 As[buf][kq * 4 + 2][row] = fa[i].z;
@@ -101,23 +117,36 @@ __global__ void __launch_bounds__((BM / 4) * (BN / 4)) q8_gemm_kernel(const Gemm
         for (int i = 0; i < W_LOADS; ++i) {
             const int idx = tid + i * T;
             const int k = idx / (BN / 4), n4 = idx % (BN / 4);
-            if (idx < BN * 4) {
-                const int w = fw[i];
-                float4 f;
-                f.x = (float)(int8_t)(w & 0xff);
-                f.y = (float)(int8_t)((w >> 8) & 0xff);
-                f.z = (float)(int8_t)((w >> 16) & 0xff);
-                f.w = (float)(int8_t)((w >> 24) & 0xff);
-                *reinterpret_cast<float4*>(&Ws[buf][k][n4 * 4]) = f;
+            if (idx < W_N) {
+                float f[4];
+                widen4(fw[i], f);
+                *reinterpret_cast<float4*>(&Ws[buf][k][n4 * 4]) = make_float4(f[0], f[1], f[2], f[3]);
             }
         }
     };
+    auto frag = [&](int buf, int k, float* av, float* bv) {
+#pragma unroll
+        for (int i = 0; i < TM; i += 4) {
+            const float4 a = *reinterpret_cast<const float4*>(&As[buf][k][ty * TM + i]);
+            av[i] = a.x; av[i + 1] = a.y; av[i + 2] = a.z; av[i + 3] = a.w;
+        }
+        if (TN >= 4) {
+#pragma unroll
+            for (int j = 0; j < TN; j += 4) {
+                const float4 b = *reinterpret_cast<const float4*>(&Ws[buf][k][tx * TN + j]);
+                bv[j] = b.x; bv[j + 1] = b.y; bv[j + 2] = b.z; bv[j + 3] = b.w;
+            }
+        } else {
+            const float2 b = *reinterpret_cast<const float2*>(&Ws[buf][k][tx * TN]);
+            bv[0] = b.x; bv[1] = b.y;
+        }
+    };
 
-    float acc[4][4];
+    float acc[TM][TN];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
 
 #pragma unroll
     for (int s = 0; s < PF; ++s) load_global(s, ra[s], rw[s]);
@@ -130,16 +159,16 @@ __global__ void __launch_bounds__((BM / 4) * (BN / 4)) q8_gemm_kernel(const Gemm
             const int kt = kt0 + s;
             if (kt < nk) {
                 load_global(kt + PF, ra[s], rw[s]);
+                // the fragments of step k + 1 are fetched before the multiply-adds of step k
+                float av[2][TM], bv[2][TN];
+                frag(s & 1, 0, av[0], bv[0]);
 #pragma unroll
                 for (int k = 0; k < BK; ++k) {
-                    const float4 a = *reinterpret_cast<const float4*>(&As[s & 1][k][ty * 4]);
-                    const float4 b = *reinterpret_cast<const float4*>(&Ws[s & 1][k][tx * 4]);
-                    const float av[4] = {a.x, a.y, a.z, a.w};
-                    const float bv[4] = {b.x, b.y, b.z, b.w};
+                    if (k + 1 < BK) frag(s & 1, k + 1, av[(k + 1) & 1], bv[(k + 1) & 1]);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
+                    for (int i = 0; i < TM; ++i)
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) acc[i][j] = fma(av[i], bv[j], acc[i][j]);
+                        for (int j = 0; j < TN; ++j) acc[i][j] = fma(av[k & 1][i], bv[k & 1][j], acc[i][j]);
                 }
                 if (kt + 1 < nk) store_smem((s + 1) & 1, ra[(s + 1) % PF], rw[(s + 1) % PF]);
                 __syncthreads();
@@ -147,30 +176,41 @@ __global__ void __launch_bounds__((BM / 4) * (BN / 4)) q8_gemm_kernel(const Gemm
         }
     }
 
-    const int c0 = n0 + tx * 4;
+    const int c0 = n0 + tx * TN;
     if (c0 >= g.N) return;
-    const float4 sc = *reinterpret_cast<const float4*>(g.scale + c0);
-    const float scv[4] = {sc.x, sc.y, sc.z, sc.w};
+    float scv[TN];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int r = m0 + ty * 4 + i;
+    for (int j = 0; j < TN; ++j) scv[j] = g.scale[c0 + j];
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int r = m0 + ty * TM + i;
         if (r >= g.M) continue;
-        float o[4];
+        float o[TN];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) o[j] = mul(acc[i][j], scv[j]);
+        for (int j = 0; j < TN; ++j) o[j] = mul(acc[i][j], scv[j]);
         if (EPI == EPI_LIF) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) lif_update(g.lif, r, c0 + j, g.N, o[j]);
+            for (int j = 0; j < TN; ++j) lif_update(g.lif, r, c0 + j, g.N, o[j]);
         } else {
-            float4* dst = reinterpret_cast<float4*>(g.C + (size_t)r * g.ldc + c0);
-            if (EPI == EPI_ADD) {
-                const float4 x = *dst;
-                o[0] = add(x.x, o[0]);
-                o[1] = add(x.y, o[1]);
-                o[2] = add(x.z, o[2]);
-                o[3] = add(x.w, o[3]);
+            float* dst = g.C + (size_t)r * g.ldc + c0;
+            if (TN >= 4) {
+#pragma unroll
+                for (int j = 0; j < TN; j += 4) {
+                    float4* d4 = reinterpret_cast<float4*>(dst + j);
+                    if (EPI == EPI_ADD) {
+                        const float4 x = *d4;
+                        o[j] = add(x.x, o[j]); o[j + 1] = add(x.y, o[j + 1]); o[j + 2] = add(x.z, o[j + 2]); o[j + 3] = add(x.w, o[j + 3]);
+                    }
+                    *d4 = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+                }
+            } else {
+                float2* d2 = reinterpret_cast<float2*>(dst);
+                if (EPI == EPI_ADD) {
+                    const float2 x = *d2;
+                    o[0] = add(x.x, o[0]); o[1] = add(x.y, o[1]);
+                }
+                *d2 = make_float2(o[0], o[1]);
             }
-            *dst = make_float4(o[0], o[1], o[2], o[3]);
         }
     }
 }
@@ -223,10 +263,12 @@ __global__ void __launch_bounds__(EV_THREADS) q8_event_kernel(const GemmArgs g) 
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     const int8_t* wp = g.W + c0;
     auto step = [&](int w, float x) {
-        acc[0] = fma(x, (float)(int8_t)(w & 0xff), acc[0]);
-        acc[1] = fma(x, (float)(int8_t)((w >> 8) & 0xff), acc[1]);
-        acc[2] = fma(x, (float)(int8_t)((w >> 16) & 0xff), acc[2]);
-        acc[3] = fma(x, (float)(int8_t)((w >> 24) & 0xff), acc[3]);
+        float f[4];
+        widen4(w, f);
+        acc[0] = fma(x, f[0], acc[0]);
+        acc[1] = fma(x, f[1], acc[1]);
+        acc[2] = fma(x, f[2], acc[2]);
+        acc[3] = fma(x, f[3], acc[3]);
     };
     int i = 0;
     for (; i + 32 <= nnz; i += 32) {
@@ -257,14 +299,14 @@ __global__ void __launch_bounds__(EV_THREADS) q8_event_kernel(const GemmArgs g) 
     *dst = make_float4(o[0], o[1], o[2], o[3]);
 }
 
-template <int BM, int BN>
+template <int BM, int BN, int TM, int TN>
 void launch_tile(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {
     dim3 grid((a.N + BN - 1) / BN, (a.M + BM - 1) / BM);
-    dim3 block((BM / 4) * (BN / 4));
+    dim3 block((BM / TM) * (BN / TN));
     switch (epi) {
-        case EPI_STORE: q8_gemm_kernel<BM, BN, EPI_STORE><<<grid, block, 0, st>>>(a); break;
-        case EPI_ADD: q8_gemm_kernel<BM, BN, EPI_ADD><<<grid, block, 0, st>>>(a); break;
-        case EPI_LIF: q8_gemm_kernel<BM, BN, EPI_LIF><<<grid, block, 0, st>>>(a); break;
+        case EPI_STORE: q8_gemm_kernel<BM, BN, TM, TN, EPI_STORE><<<grid, block, 0, st>>>(a); break;
+        case EPI_ADD: q8_gemm_kernel<BM, BN, TM, TN, EPI_ADD><<<grid, block, 0, st>>>(a); break;
+        case EPI_LIF: q8_gemm_kernel<BM, BN, TM, TN, EPI_LIF><<<grid, block, 0, st>>>(a); break;
     }
 }
 
@@ -276,13 +318,27 @@ __global__ void lif_kernel(const float* cur, const LifParams p, int M, int d) {
 
 }  // namespace
 
+int g_gemm_force = 0;  // tuning override (0: choose by shape)
+
 void launch_q8_gemm(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int sm_count) {
-    // 64x64 tiles when they fill the SMs, else 32x64 so that a narrow product still spreads out
+    switch (g_gemm_force) {
+        case 1: return launch_tile<64, 64, 4, 4>(st, a, epi);
+        case 2: return launch_tile<64, 64, 8, 4>(st, a, epi);
+        case 3: return launch_tile<32, 64, 4, 4>(st, a, epi);
+        case 4: return launch_tile<32, 64, 4, 2>(st, a, epi);
+        default: break;
+    }
+    // Measured on B200 at 256 rows (the machine is short of warps at this batch, so the choice is about filling SMs):
+    // very wide products take 64x64 tiles of 8x4, wide ones 64x64 of 4x4, then 32x64 of 4x4, narrow ones 32x64 of 4x2.
     const long tiles64 = (long)((a.N + 63) / 64) * ((a.M + 63) / 64);
-    if (tiles64 >= sm_count)
-        launch_tile<64, 64>(st, a, epi);
+    if (tiles64 >= 4L * sm_count)
+        launch_tile<64, 64, 8, 4>(st, a, epi);
+    else if (2 * tiles64 >= 3L * sm_count)
+        launch_tile<64, 64, 4, 4>(st, a, epi);
+    else if (tiles64 >= sm_count)
+        launch_tile<32, 64, 4, 4>(st, a, epi);
     else
-        launch_tile<32, 64>(st, a, epi);
+        launch_tile<32, 64, 4, 2>(st, a, epi);
 }
 
 bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {

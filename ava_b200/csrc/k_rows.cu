@@ -149,30 +149,59 @@ __global__ void mem_prep_kernel(const MemPrepArgs a) {
         ek[c] = add(kk, pr[3 * d + c]);
     }
     __syncthreads();
-    // the independent ordered chains, one per thread.  Chains of one kind run the same code, so each kind gets its own
-    // warps (a warp whose lanes ran different kinds would run them one after another): warps 0-1 the three sums of
-    // squares per head, warps 2-3 the per-head gate projections, warps 4.. the low-rank projections.
+    // The ordered chains.  The gate projections h . [wa | wb | wa1 | wb1] (gemm's one-row order: row 0's product,
+    // then fma down the rows) take one thread per output column; their weights come through shared memory a chunk of
+    // rows at a time (every thread copies, cp.async, double buffered), so a chain never waits on global memory.  The
+    // three sums of squares per head run in the warps after them while the first chunk is in flight.
     {
-        const int warp = tid >> 5, lane = tid & 31, nwarp = T >> 5;
-        if (warp < 2) {
-            for (int it = warp * 32 + lane; it < 3 * nh; it += 64) {
-                const int which = it / nh, e = it % nh;
-                const float* src = (which == 0 ? q : which == 1 ? kr : ek) + e * hs;
-                (which == 0 ? inv_q : which == 1 ? inv_k : inv_e)[e] = inv_l2_seq(src, hs);
+        const int ncols = 2 * nh + 2 * rk, ncp = a.gate_cols;  // real and padded column count
+        const int CR = a.gate_chunk, nchunk = d / CR;
+        float* stage = z1b + rk;                               // [2][CR * ncp], 16-byte aligned (see the launcher)
+        stage += (4 - ((5 * nh + 2 * rk) & 3)) & 3;
+        const int per_chunk4 = CR * ncp / 4;
+        auto fetch = [&](int c) {
+            float* dst = stage + (size_t)(c & 1) * CR * ncp;
+            const float* src = a.gate_w + (size_t)c * CR * ncp;
+            for (int i = tid; i < per_chunk4; i += T)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst + 4 * i)), "l"(src + 4 * i) : "memory");
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        fetch(0);
+        float out = -0.0f;  // fma(w, x, -0) is the plain rounded product: the chain's first term
+        const int first_sq = ((ncols + 31) / 32) * 32;         // sums of squares start at a warp boundary
+        for (int c = 0; c < nchunk; ++c) {
+            if (c + 1 < nchunk) {
+                fetch(c + 1);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
             }
-        } else if (warp < 4) {
-            for (int it = (warp - 2) * 32 + lane; it < 2 * nh; it += 64) {
-                const int which = it / nh, e = it % nh;
-                const float z = gemv_col(h, d, (which ? a.wb : a.wa) + e, nh);
-                (which ? zb : za)[e] = add(z, (which ? a.bb : a.ba)[e]);
+            __syncthreads();
+            if (tid < ncols) {
+                const float* wcol = stage + (size_t)(c & 1) * CR * ncp + tid;
+                const float* hx = h + c * CR;
+                for (int r0 = 0; r0 < CR; r0 += 8) {
+                    float w8[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) w8[i] = wcol[(size_t)(r0 + i) * ncp];
+                    const float4 x0 = *reinterpret_cast<const float4*>(hx + r0), x1 = *reinterpret_cast<const float4*>(hx + r0 + 4);
+                    const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) out = fma(w8[i], xv[i], out);
+                }
+            } else if (c == 0) {
+                for (int it = tid - first_sq; it >= 0 && it < 3 * nh; it += T - first_sq) {
+                    const int which = it / nh, e = it % nh;
+                    const float* src = (which == 0 ? q : which == 1 ? kr : ek) + e * hs;
+                    (which == 0 ? inv_q : which == 1 ? inv_k : inv_e)[e] = inv_l2_seq(src, hs);
+                }
             }
-        } else {
-            const int cw = nwarp - 4;
-            for (int it = (warp - 4) * 32 + lane; it < 2 * rk; it += cw * 32) {
-                const int which = it / rk, i = it % rk;
-                (which ? z1b : z1a)[i] = gemv_col(h, d, (which ? a.wb1 : a.wa1) + i, rk);
-            }
+            __syncthreads();
         }
+        if (tid < nh) za[tid] = add(out, a.ba[tid]);
+        else if (tid < 2 * nh) zb[tid - nh] = add(out, a.bb[tid - nh]);
+        else if (tid < 2 * nh + rk) z1a[tid - 2 * nh] = out;
+        else if (tid < ncols) z1b[tid - 2 * nh - rk] = out;
     }
     __syncthreads();
     for (int c = tid; c < d; c += T) {
@@ -380,7 +409,7 @@ void launch_rmsnorm(cudaStream_t st, const float* x, const float* gain, int M, i
 
 void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a) {
     const int nh = a.d / a.hs;
-    const size_t smem = ((size_t)8 * a.d + 5 * nh + 2 * a.rank) * sizeof(float);
+    const size_t smem = ((size_t)8 * a.d + 5 * nh + 2 * a.rank + 4 + 2 * (size_t)a.gate_chunk * a.gate_cols) * sizeof(float);
     opt_in_smem(mem_prep_kernel, smem);
     mem_prep_kernel<<<a.M, 256, smem, st>>>(a);
 }

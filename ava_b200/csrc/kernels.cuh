@@ -59,7 +59,10 @@ struct MemPrepArgs {
     const float* h;      // [M, d] normed input
     const float* proj;   // [M, ldp]: q | k | v | e | (g)
     int ldp;
-    const float *wa, *wb, *ba, *bb, *wa1, *wa2, *wb1, *wb2, *off;
+    const float* gate_w; // [d][gate_cols]: wa | wb | wa1 | wb1 side by side, columns padded with zeros to a multiple of 4
+    int gate_cols;       // padded column count (at most 256: one chain per thread)
+    int gate_chunk;      // rows staged per copy; divides d, a multiple of 8
+    const float *ba, *bb, *wa2, *wb2, *off;
     const float* vres;   // [2] or nullptr
     float* v_first;      // [M, d]: written when first, read when vres
     int first;           // 1: this block's values become v_first
