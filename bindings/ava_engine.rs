@@ -1,0 +1,174 @@
+//! Rust binding of libava_engine.so (include/ava_engine.h) for the reference's crate `ava_gpu`
+//! (design-tests/nn/gpu).  NOT COMPILED in the environment this repository was built in (no Rust tool chain there):
+//! it is the text a maintainer would add as `src/b200.rs`, written against the C header line by line.
+//!
+//! It gives the engine the reference's own method names so that the callers of the one-token path
+//! (`ava_live`, `generate_gpu`, `talk_bench`, `int8_bench`, `state::generate`) switch by changing a type:
+//!   Model::state(rows)                  -> B200Model::state(rows, max_ctx)
+//!   Model::step(&mut Stream, tok)       -> B200Model::step(&mut B200State, &[tok]) (one token per row)
+//!   Model::forward_with_state(ids, st)  -> B200Model::forward_with_state(ids, t, &mut st, last_only)
+//!   State::select / State::cat          -> B200State::select / B200State::cat
+//! `Ok(None)` of the reference's fused step ("this fast path does not apply") is status 1 here.
+
+use std::ffi::{c_char, c_int, c_void, CStr, CString};
+
+#[repr(C)]
+#[derive(Clone, Copy, Debug, Default)]
+pub struct AvaConfig {
+    pub vocab: i32,
+    pub d: i32,
+    pub n_blocks: i32,
+    pub hidden: i32,
+    pub kwta_k: i32,
+    pub head_size: i32,
+    pub eng_block: i32,
+    pub eng_head_size: i32,
+    pub eng_store_bf16: i32,
+    pub eng_cap: i32,
+    pub gate_rank: i32,
+    pub spikes: i32,
+    pub alif: i32,
+    pub theta: i32,
+    pub lif_scale: i32,
+    pub value_residual: i32,
+    pub relu2: i32,
+    pub dense: i32,
+    pub out_gate: i32,
+    pub mem_momentum: f32,
+    pub slope: f32,
+}
+
+#[repr(C)]
+pub struct AvaEngine { _p: [u8; 0] }
+#[repr(C)]
+pub struct AvaState { _p: [u8; 0] }
+
+#[link(name = "ava_engine")]
+extern "C" {
+    pub fn ava_engine_create(cfg: *const AvaConfig, device: c_int, out: *mut *mut AvaEngine) -> c_int;
+    pub fn ava_engine_destroy(e: *mut AvaEngine);
+    pub fn ava_last_error(e: *const AvaEngine) -> *const c_char;
+    pub fn ava_engine_set_f32(e: *mut AvaEngine, name: *const c_char, data: *const f32, n: i64) -> c_int;
+    pub fn ava_engine_set_q8(e: *mut AvaEngine, name: *const c_char, q: *const i8, scale: *const f32, din: i32, dout: i32) -> c_int;
+    pub fn ava_engine_set_q8_from_f32(e: *mut AvaEngine, name: *const c_char, w: *const f32, din: i32, dout: i32) -> c_int;
+    pub fn ava_engine_finalize(e: *mut AvaEngine) -> c_int;
+    pub fn ava_engine_blocker(e: *const AvaEngine) -> *const c_char;
+    pub fn ava_state_new(e: *mut AvaEngine, rows: i32, max_ctx: i32, out: *mut *mut AvaState) -> c_int;
+    pub fn ava_state_destroy(s: *mut AvaState);
+    pub fn ava_state_rows(s: *const AvaState) -> i32;
+    pub fn ava_state_select(s: *const AvaState, idx: *const i32, n: i32, out: *mut *mut AvaState) -> c_int;
+    pub fn ava_state_cat(parts: *const *const AvaState, n: i32, out: *mut *mut AvaState) -> c_int;
+    pub fn ava_state_seen(s: *const AvaState, row: i32) -> i64;
+    pub fn ava_state_len(s: *const AvaState, row: i32, name: *const c_char) -> i64;
+    pub fn ava_state_export(s: *const AvaState, row: i32, name: *const c_char, out: *mut f32) -> c_int;
+    pub fn ava_state_import(s: *mut AvaState, row: i32, name: *const c_char, data: *const f32, n: i64) -> c_int;
+    pub fn ava_step(e: *mut AvaEngine, s: *mut AvaState, tok: *const u32, logits: *mut f32) -> c_int;
+    pub fn ava_step_greedy(e: *mut AvaEngine, s: *mut AvaState, tok: *const u32, next: *mut u32) -> c_int;
+    pub fn ava_forward_with_state(e: *mut AvaEngine, s: *mut AvaState, ids: *const u32, t: i32, last_only: i32, logits: *mut f32) -> c_int;
+    pub fn ava_step_device(e: *mut AvaEngine, s: *mut AvaState, tok: *const u32, logits: *mut f32, next: *mut u32) -> c_int;
+    pub fn ava_sync(e: *mut AvaEngine) -> c_int;
+    pub fn ava_engine_stream(e: *mut AvaEngine) -> *mut c_void;
+}
+
+#[derive(Debug)]
+pub enum B200Error {
+    /// status 1: the engine does not cover this configuration (the reference's `Ok(None)`), with the reason
+    NotApplicable(String),
+    Failed(i32, String),
+}
+
+pub struct B200Model {
+    h: *mut AvaEngine,
+    pub vocab: usize,
+}
+pub struct B200State {
+    h: *mut AvaState,
+}
+
+impl B200Model {
+    fn check(&self, rc: c_int) -> Result<(), B200Error> {
+        match rc {
+            0 => Ok(()),
+            1 => {
+                let p = unsafe { ava_engine_blocker(self.h) };
+                let why = if p.is_null() { String::new() } else { unsafe { CStr::from_ptr(p) }.to_string_lossy().into_owned() };
+                Err(B200Error::NotApplicable(why))
+            }
+            rc => Err(B200Error::Failed(rc, unsafe { CStr::from_ptr(ava_last_error(self.h)) }.to_string_lossy().into_owned())),
+        }
+    }
+
+    /// `Model::new` + `set_int8(true)` + `set_fused(true)`: `f32s` are (tensor name, values), `q8s` (name, W [din, dout]
+    /// f32 row-major) are quantised by the engine exactly as `ava_parts::quant::quantize_int8`.
+    pub fn new(cfg: &AvaConfig, device: i32, f32s: &[(&str, &[f32])], q8s: &[(&str, &[f32], usize, usize)]) -> Result<B200Model, B200Error> {
+        let mut h = std::ptr::null_mut();
+        let rc = unsafe { ava_engine_create(cfg, device, &mut h) };
+        if rc != 0 {
+            return Err(B200Error::Failed(rc, unsafe { CStr::from_ptr(ava_last_error(std::ptr::null())) }.to_string_lossy().into_owned()));
+        }
+        let m = B200Model { h, vocab: cfg.vocab as usize };
+        for (name, v) in f32s {
+            let n = CString::new(*name).unwrap();
+            m.check(unsafe { ava_engine_set_f32(m.h, n.as_ptr(), v.as_ptr(), v.len() as i64) })?;
+        }
+        for (name, w, din, dout) in q8s {
+            let n = CString::new(*name).unwrap();
+            m.check(unsafe { ava_engine_set_q8_from_f32(m.h, n.as_ptr(), w.as_ptr(), *din as i32, *dout as i32) })?;
+        }
+        m.check(unsafe { ava_engine_finalize(m.h) })?;
+        Ok(m)
+    }
+
+    /// `Model::state(rows)`
+    pub fn state(&self, rows: usize, max_ctx: usize) -> Result<B200State, B200Error> {
+        let mut s = std::ptr::null_mut();
+        self.check(unsafe { ava_state_new(self.h, rows as i32, max_ctx as i32, &mut s) })?;
+        Ok(B200State { h: s })
+    }
+
+    /// `Model::step`: one token per row, logits [rows, vocab]
+    pub fn step(&self, st: &mut B200State, tok: &[u32]) -> Result<Vec<f32>, B200Error> {
+        let rows = unsafe { ava_state_rows(st.h) } as usize;
+        assert_eq!(tok.len(), rows);
+        let mut logits = vec![0f32; rows * self.vocab];
+        self.check(unsafe { ava_step(self.h, st.h, tok.as_ptr(), logits.as_mut_ptr()) })?;
+        Ok(logits)
+    }
+
+    /// `Model::forward_with_state(ids [rows, t], &mut State)`
+    pub fn forward_with_state(&self, ids: &[u32], t: usize, st: &mut B200State, last_only: bool) -> Result<Vec<f32>, B200Error> {
+        let rows = unsafe { ava_state_rows(st.h) } as usize;
+        assert_eq!(ids.len(), rows * t);
+        let mut logits = vec![0f32; rows * self.vocab * if last_only { 1 } else { t }];
+        self.check(unsafe { ava_forward_with_state(self.h, st.h, ids.as_ptr(), t as i32, last_only as i32, logits.as_mut_ptr()) })?;
+        Ok(logits)
+    }
+}
+
+impl B200State {
+    /// `State::select`
+    pub fn select(&self, idx: &[i32]) -> Option<B200State> {
+        let mut s = std::ptr::null_mut();
+        (unsafe { ava_state_select(self.h, idx.as_ptr(), idx.len() as i32, &mut s) } == 0).then_some(B200State { h: s })
+    }
+    /// `State::cat`
+    pub fn cat(parts: &[&B200State]) -> Option<B200State> {
+        let ps: Vec<*const AvaState> = parts.iter().map(|p| p.h as *const AvaState).collect();
+        let mut s = std::ptr::null_mut();
+        (unsafe { ava_state_cat(ps.as_ptr(), ps.len() as i32, &mut s) } == 0).then_some(B200State { h: s })
+    }
+    pub fn seen(&self, row: usize) -> i64 {
+        unsafe { ava_state_seen(self.h, row as i32) }
+    }
+}
+
+impl Drop for B200State {
+    fn drop(&mut self) {
+        unsafe { ava_state_destroy(self.h) }
+    }
+}
+impl Drop for B200Model {
+    fn drop(&mut self) {
+        unsafe { ava_engine_destroy(self.h) }
+    }
+}
