@@ -170,7 +170,10 @@ def main():
     state = model.state(rows, max_ctx)
     stream = torch.cuda.ExternalStream(model.stream, device=local)
 
-    ids = synth.token_ids(cfg["vocab"], rows, prompt, seed0=rank * rows)           # seeds 0..255 per rank
+    from ava_b200 import shard
+    first, last = shard.block(world * rows, world, rank)                           # this rank's sequences (weak scaling)
+    assert last - first == rows
+    ids = synth.token_ids(cfg["vocab"], rows, prompt, seed0=first)                 # sequence r reads SplitMix64(r)
     ids_dev = torch.from_numpy(np.ascontiguousarray(ids.T).astype(np.int32)).to(f"cuda:{local}")  # [prompt, rows]
     tok = [torch.zeros(rows, dtype=torch.int32, device=f"cuda:{local}") for _ in range(2)]
     logits_dev = torch.empty(rows, cfg["vocab"], dtype=torch.float32, device=f"cuda:{local}")
