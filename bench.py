@@ -254,6 +254,9 @@ def main():
     state_bytes = rows * 2 * 4 * cfg["d"] * cfg["head_size"]        # read once + written once, f32, per launch
     peak, peak_src = peaks()
     achieved = state_bytes / (ms_mh / max(n_mh, 1) * 1e-3) / 1e9 if n_mh else 0.0
+    # DRAM bytes one launch moved under ncu (dram__bytes_read.sum + dram__bytes_write.sum, 256 rows of one 768x768
+    # matrix: profiles/mem_heads_bulk_slice_major_small_case.md); it grows in proportion to the state a launch streams
+    traffic = 1154.7e6 * state_bytes / 1207959552.0
     # the whole step against the HBM roofline: algorithmic bytes per decoded token (state + weights/rows + KV + LIF)
     kv_bytes = args.ctx * 2 * cfg["d"] * 2 if cfg["eng_block"] >= 0 else 0
     tok_bytes = (2 * 4 * cfg["n_blocks"] * cfg["d"] * cfg["head_size"] + synth.weight_bytes(cfg) / rows + kv_bytes
@@ -273,7 +276,8 @@ def main():
         "gpu_launches": int(launches),
         "clocks": clk,
         "roofline": {"bound": "hbm", "kernel": "mem_heads (fast-weight state pass)", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "of": peak_src, "traffic": None, "bytes_per_launch": state_bytes,
+                     "frac": achieved / peak, "of": peak_src, "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram read + write)",
+                     "bytes_per_launch": state_bytes,
                      "mean_launch_ms": ms_mh / max(n_mh, 1), "launches_timed": n_mh,
                      "step_bytes_per_token": tok_bytes, "step_frac_of_hbm_roofline": step_frac},
         "kernel_share": {k: round(v[1] / total_ms, 4) for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])},
