@@ -91,6 +91,8 @@ def lib() -> C.CDLL:
         "ava_op_lif": ([C.c_int, fp, fp, fp, fp, fp, C.c_int32, fp, fp, fp, C.c_int32, C.c_int32, fp, fp, fp], C.c_int),
         "ava_op_kwta": ([C.c_int, fp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, fp], C.c_int),
         "ava_op_mem_heads": ([C.c_int, C.c_int32, C.c_int32, fp, fp, fp, fp, fp, fp, fp, fp, fp, fp], C.c_int),
+        "ava_mem_heads_static": ([C.c_int, vp, C.c_int32, C.c_int32] + [vp] * 10, C.c_int),
+        "ava_static_last_error": ([], C.c_char_p),
         "ava_op_attend": ([C.c_int, C.c_int32, C.c_int32, C.c_int32, C.c_int32, fp, fp, fp, fp], C.c_int),
         "ava_host_expf": ([C.c_float], C.c_float),
         "ava_host_logf": ([C.c_float], C.c_float),
@@ -110,7 +112,7 @@ EXPORTS = ("ava_engine_create ava_engine_destroy ava_last_error ava_engine_set_f
            "ava_state_rows ava_state_select ava_state_cat ava_state_seen ava_state_len ava_state_export "
            "ava_state_import ava_step ava_step_greedy ava_forward_with_state ava_step_device ava_sync "
            "ava_engine_stream ava_engine_launches ava_engine_bytes ava_state_bytes ava_debug_keep ava_debug_width "
-           "ava_debug_get ava_prof_enable ava_prof_read ava_prof_names ava_op_q8_matmul ava_op_q8_event_matmul ava_debug_mem_heads_timeline ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_op_attend "
+           "ava_debug_get ava_prof_enable ava_prof_read ava_prof_names ava_op_q8_matmul ava_op_q8_event_matmul ava_debug_mem_heads_timeline ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
            "ava_host_expf ava_host_logf ava_host_rsqrtf ava_op_math").split()
 
 

@@ -164,6 +164,20 @@ int ava_op_kwta(int device, const float* u, int32_t m, int32_t n, int32_t k, int
  * e, v, w, ah, qg, ex [m, hs]; qw, qa [m]; f [m, hs, hs] updated in place; y [m, hs]. */
 int ava_op_mem_heads(int device, int32_t m, int32_t hs, const float* e, const float* v, const float* w, const float* ah,
                      const float* qg, const float* ex, const float* qw, const float* qa, float* f, float* y);
+/* No counterpart in the reference.  ava_op_mem_heads for callers that cannot allocate device memory (code inside a
+ * host callback or a latency-critical thread that must not take the allocator's lock, a process whose GPU memory was
+ * handed out in full at start-up, a program region that may not allocate until a capture it began earlier ends): every
+ * pointer is DEVICE memory, `stream` is a cudaStream_t (NULL: the default stream), f [m, hs, hs] is updated in place
+ * and y [m, hs] written.  The kernel's scratch is a built-in device array of AVA_STATIC_SCRATCH_BYTES that every GPU
+ * loading the library holds until exit; m * hs * hs above AVA_STATIC_SCRATCH_FLOATS is refused with AVA_ERR_CAPACITY
+ * (text from ava_static_last_error).  All calls on a device share that array: calls that overlap on the GPU race.  The
+ * first call on a device looks the array's address up; make it before any stream capture.  Returns after the stream
+ * has drained. */
+#define AVA_STATIC_SCRATCH_FLOATS 4194304
+#define AVA_STATIC_SCRATCH_BYTES (4 * AVA_STATIC_SCRATCH_FLOATS)
+int ava_mem_heads_static(int device, void* stream, int32_t m, int32_t hs, const float* e, const float* v, const float* w, const float* ah,
+                         const float* qg, const float* ex, const float* qw, const float* qa, float* f, float* y);
+const char* ava_static_last_error(void);
 /* `attend` (src/model/fstep.rs:303-327) for m heads over n keys/values of hs (f32, or rounded to bf16 first). */
 int ava_op_attend(int device, int32_t m, int32_t n, int32_t hs, int32_t bf16_store, const float* q, const float* kc,
                   const float* vc, float* out);
