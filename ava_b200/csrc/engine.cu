@@ -105,7 +105,7 @@ struct ava_engine {
     int gate_cols = 0, gate_chunk = 0;  // the gates' projection matrix: padded columns, rows per staged chunk
 
     // work buffers for `ws_rows` rows
-    int ws_rows = 0;
+    int ws_rows = 0, ws_logit_rows = 0;
     Dev x, h, proj, ve, vv, vw, vah, vqg, vex, qw, qa, yraw, y, eqkv, eo, u, act, streams, v_first, logits, tok, next, status;
     uint32_t* status_host = nullptr;  // pinned
 
@@ -264,7 +264,11 @@ const char* find_blocker(const ava_config& c, int* cw, int* rb) {
     return nullptr;
 }
 
-int ensure_workspace(ava_engine* e, int rows) {
+int ensure_workspace(ava_engine* e, int rows, int logit_rows = 0) {
+    if (logit_rows > e->ws_logit_rows) {
+        CK(e->logits.alloc((size_t)logit_rows * e->cfg.vocab * sizeof(float)));
+        e->ws_logit_rows = logit_rows;
+    }
     if (rows <= e->ws_rows) return AVA_OK;
     const ava_config& c = e->cfg;
     const size_t M = rows, d = c.d, f = sizeof(float);
@@ -278,7 +282,6 @@ int ensure_workspace(ava_engine* e, int rows) {
     CK(e->u.alloc(M * c.hidden * f));
     CK(e->act.alloc(M * c.hidden * f));
     CK(e->streams.alloc(c.dense ? (size_t)(c.n_blocks + 1) * M * d * f : 0));
-    CK(e->logits.alloc(M * c.vocab * f));
     CK(e->tok.alloc(M * sizeof(uint32_t)));
     CK(e->next.alloc(M * sizeof(uint32_t)));
     e->ws_rows = rows;
@@ -330,22 +333,29 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
     return AVA_OK;
 }
 
-// One token per row, everything queued on the engine's stream.  tok/logits/next are device pointers.
-int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits, uint32_t* next, bool want_logits) {
+// T tokens per row (T = 1: the decode step), everything queued on the engine's stream.  tok is [T][rows] on the
+// device; logits/next (device, may be null) get the LAST token's [rows, vocab] / [rows], or with all_logits every
+// token's [T][rows][vocab].  With T > 1 the products, norms, gates and the MLP run over all T x rows token-rows at
+// once, and the three recurrences walk the chunk in order inside their kernels: the LIF scan, the fast-weight pass
+// with its slice resident in shared memory, the engram read token by token.  Every value is the one T single steps give.
+int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits, uint32_t* next, bool want_logits, int T = 1, bool all_logits = false) {
     const ava_config& c = e->cfg;
-    const int M = s->rows, d = c.d, L = c.n_blocks, nh = e->nh(), hs = c.head_size, H = c.hidden;
+    const int rows = s->rows, d = c.d, L = c.n_blocks, nh = e->nh(), hs = c.head_size, H = c.hidden;
+    const int M = rows * T;  // token-rows, time-major: token t of row r is token-row t * rows + r
     cudaStream_t st = e->stream;
     float* x = e->x.as<float>();
     float* h = e->h.as<float>();
     float* streams = c.dense ? e->streams.as<float>() : nullptr;
-    const size_t Md = (size_t)M * d;
+    const size_t Md = (size_t)M * d;        // one activation buffer of the chunk
+    const size_t Rd = (size_t)rows * d;     // one block's carried LIF state
 
     // the engram's capacity is checked on the host's mirror of the counts before anything moves
     int n_max = 0;
     if (c.eng_block >= 0) {
-        for (int r = 0; r < M; ++r) {
-            if (s->n_host[r] >= s->ring) return e->fail(AVA_ERR_CAPACITY, "engram store of row %d is full (%d tokens)", r, s->ring);
-            n_max = std::max(n_max, s->n_host[r] + 1);
+        for (int r = 0; r < rows; ++r) {
+            if (s->keep == s->ring && s->n_host[r] + T > s->ring)
+                return e->fail(AVA_ERR_CAPACITY, "engram store of row %d is full (%d tokens)", r, s->ring);
+            n_max = std::max(n_max, std::min(s->n_host[r] + T - 1, s->keep) + 1);
         }
     }
 
@@ -365,14 +375,24 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         lp.theta = c.theta ? b.theta.as<float>() : nullptr;
         lp.rho = c.alif ? b.rho.as<float>() : nullptr;
         lp.gain = c.alif ? b.again.as<float>() : nullptr;
-        lp.v = s->lif_v.as<float>() + (size_t)i * Md;
-        lp.s = s->lif_s.as<float>() + (size_t)i * Md;
-        lp.a = c.alif ? s->lif_a.as<float>() + (size_t)i * Md : nullptr;
+        lp.v = s->lif_v.as<float>() + (size_t)i * Rd;
+        lp.s = s->lif_s.as<float>() + (size_t)i * Rd;
+        lp.a = c.alif ? s->lif_a.as<float>() + (size_t)i * Rd : nullptr;
         lp.spikes = c.spikes;
         lp.lif_scale = c.lif_scale;
-        gemm(e, "gemm.win_lif", h, d, b.win, nullptr, 0, M, EPI_LIF, &lp);
-        dbg(e, "spikes", i, lp.s, M, d);
-        gemm(e, "gemm.wout", lp.s, d, b.wout, x, d, M, EPI_ADD, nullptr, true);
+        const float* spikes = lp.s;
+        if (T == 1) {
+            gemm(e, "gemm.win_lif", h, d, b.win, nullptr, 0, M, EPI_LIF, &lp);
+        } else {
+            // currents of the whole chunk, then the scan in time (buffers free at this point of the block are borrowed)
+            gemm(e, "gemm.win", h, d, b.win, e->yraw.as<float>(), d, M, EPI_STORE);
+            prof_begin(e, "lif_scan");
+            launch_lif_scan(st, e->yraw.as<float>(), lp, rows, d, T, e->eo.as<float>());
+            prof_end(e);
+            spikes = e->eo.as<float>();
+        }
+        dbg(e, "spikes", i, spikes, M, d);
+        gemm(e, "gemm.wout", spikes, d, b.wout, x, d, M, EPI_ADD, nullptr, true);
         dbg(e, "x_lif", i, x, M, d);
 
         // ---- the fast-weight memory
@@ -403,13 +423,16 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         dbg(e, "ek", i, mp.e, M, d); dbg(e, "v", i, mp.v, M, d); dbg(e, "w", i, mp.w, M, d); dbg(e, "ah", i, mp.ah, M, d);
         dbg(e, "qg", i, mp.qg, M, d); dbg(e, "ex", i, mp.ex, M, d); dbg(e, "qw", i, mp.qw, M, nh); dbg(e, "qa", i, mp.qa, M, nh);
         MemHeadsArgs mh{};
-        mh.f = s->mem_f.as<float>() + (size_t)i * Md * hs;
-        mh.M = M; mh.nh = nh; mh.hs = hs; mh.cw = e->cw; mh.chunk_rows = e->rb;
+        mh.f = s->mem_f.as<float>() + (size_t)i * Rd * hs;
+        mh.M = rows; mh.nh = nh; mh.hs = hs; mh.cw = e->cw; mh.chunk_rows = e->rb;
         mh.e = mp.e; mh.v = mp.v; mh.w = mp.w; mh.ah = mp.ah; mh.qg = mp.qg; mh.ex = mp.ex; mh.qw = mp.qw; mh.qa = mp.qa;
         mh.y = e->yraw.as<float>();
         mh.status = e->status.as<uint32_t>();
         prof_begin(e, "mem_heads");
-        launch_mem_heads(st, mh);
+        if (T == 1)
+            launch_mem_heads(st, mh);
+        else
+            launch_mem_heads_seq(st, mh, T);
         prof_end(e);
         dbg(e, "y_raw", i, mh.y, M, d);
         prof_begin(e, "mem_post");
@@ -430,14 +453,19 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
             ea.qkv = e->eqkv.as<float>();
             ea.k = s->eng_k.p; ea.v = s->eng_v.p;
             ea.n = s->eng_n.as<int32_t>(); ea.start = s->eng_start.as<int32_t>();
-            ea.M = M; ea.d = d; ea.hs = c.eng_head_size; ea.cap = s->ring; ea.keep = s->keep; ea.bf16 = c.eng_store_bf16;
-            ea.o = e->eo.as<float>();
+            ea.M = rows; ea.d = d; ea.hs = c.eng_head_size; ea.cap = s->ring; ea.keep = s->keep; ea.bf16 = c.eng_store_bf16;
             ea.status = e->status.as<uint32_t>();
-            prof_begin(e, "engram");
-            if (!launch_engram(st, ea, n_max))
-                return e->fail(AVA_ERR_CAPACITY, "engram read over %d tokens does not fit this kernel's shared memory", n_max);
-            prof_end(e);
-            e->launches++;  // the small kernel that moves the counts on
+            // the read is causal: token t sees the store as tokens 0..t left it, so the chunk goes token by token
+            for (int t = 0; t < T; ++t) {
+                ea.qkv = e->eqkv.as<float>() + (size_t)t * rows * 3 * d;
+                ea.o = e->eo.as<float>() + (size_t)t * Rd;
+                prof_begin(e, "engram");
+                if (!launch_engram(st, ea, n_max))
+                    return e->fail(AVA_ERR_CAPACITY, "engram read over %d tokens does not fit this kernel's shared memory", n_max);
+                prof_end(e);
+                e->launches++;  // the small kernel that moves the counts on
+            }
+            ea.o = e->eo.as<float>();
             dbg(e, "eng_o", i, ea.o, M, d);
             gemm(e, "gemm.eng_wo", ea.o, d, b.ewo, x, d, M, EPI_ADD);
             dbg(e, "x_eng", i, x, M, d);
@@ -462,30 +490,33 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         dbg(e, "x_out", i, x, M, d);
     }
     if (want_logits || next) {
+        // the head reads the last token's rows only, unless every position's logits were asked for
+        const int first_row = all_logits ? 0 : (T - 1) * rows, head_rows = all_logits ? M : rows;
         prof_begin(e, "rmsnorm");
-        launch_rmsnorm(st, x, e->final_norm.as<float>(), M, d, h);
+        launch_rmsnorm(st, x + (size_t)first_row * d, e->final_norm.as<float>(), head_rows, d, h);
         prof_end(e);
-        dbg(e, "x_final", -1, h, M, d);
+        dbg(e, "x_final", -1, h, head_rows, d);
         float* lg = logits ? logits : e->logits.as<float>();
-        gemm(e, "gemm.head", h, d, e->head, lg, c.vocab, M, EPI_STORE);
+        gemm(e, "gemm.head", h, d, e->head, lg, c.vocab, head_rows, EPI_STORE);
         if (next) {
             prof_begin(e, "argmax");
-            launch_argmax(st, lg, M, c.vocab, next);
+            launch_argmax(st, lg + (all_logits ? (size_t)(T - 1) * rows * c.vocab : 0), rows, c.vocab, next);
             prof_end(e);
         }
     }
-    // the host's mirror of the engram counts moves as the kernel moves them
+    // the host's mirror of the engram counts moves as the kernels move them
     if (c.eng_block >= 0)
-        for (int r = 0; r < M; ++r) {
-            const int n = s->n_host[r] + 1;
-            if (n > s->keep) {
-                s->start_host[r] = (s->start_host[r] + (n - s->keep)) % s->ring;
-                s->n_host[r] = s->keep;
-            } else {
-                s->n_host[r] = n;
+        for (int r = 0; r < rows; ++r)
+            for (int t = 0; t < T; ++t) {
+                const int n = s->n_host[r] + 1;
+                if (n > s->keep) {
+                    s->start_host[r] = (s->start_host[r] + (n - s->keep)) % s->ring;
+                    s->n_host[r] = s->keep;
+                } else {
+                    s->n_host[r] = n;
+                }
             }
-        }
-    for (int r = 0; r < M; ++r) s->seen[r] += 1;
+    for (int r = 0; r < rows; ++r) s->seen[r] += T;
     const cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) return e->cuda_fail(le, "kernel launch");
     return AVA_OK;
@@ -510,7 +541,7 @@ int check_pair(ava_engine* e, ava_state* s) {
     if (!e->finalized) return e->fail(AVA_ERR_ARG, "engine not finalized");
     if (!e->blocker.empty()) return AVA_NOT_APPLICABLE;
     CK(cudaSetDevice(e->device));
-    return ensure_workspace(e, s->rows);
+    return ensure_workspace(e, s->rows, s->rows);
 }
 
 struct StateSlice {
@@ -1001,20 +1032,46 @@ int ava_forward_with_state(ava_engine* e, ava_state* s, const uint32_t* ids, int
     Dev dcol;
     CK(dcol.alloc(col.size() * sizeof(uint32_t)));
     CK(cudaMemcpyAsync(dcol.p, col.data(), col.size() * sizeof(uint32_t), cudaMemcpyHostToDevice, e->stream));
-    for (int j = 0; j < t; ++j) {
-        const bool want = !last_only || j == t - 1;
-        if ((rc = step_device(e, s, dcol.as<uint32_t>() + (size_t)j * M, want ? e->logits.as<float>() : nullptr, nullptr, want))) return rc;
-        if (want) {
-            if (last_only) {
-                CK(cudaMemcpyAsync(logits, e->logits.p, (size_t)M * V * sizeof(float), cudaMemcpyDeviceToHost, e->stream));
-            } else {
-                // [rows, t, vocab]: row r's position j
-                CK(cudaMemcpy2DAsync(logits + (size_t)j * V, (size_t)t * V * sizeof(float), e->logits.p, (size_t)V * sizeof(float),
-                                     (size_t)V * sizeof(float), M, cudaMemcpyDeviceToHost, e->stream));
-            }
+    // the prompt goes in chunks of Tc tokens per row: token-parallel work over Tc x rows token-rows at once, the
+    // recurrences in order inside their kernels (step_device).  The chunk is sized to a bounded work space.
+    int64_t max_rows = 16384;
+    if (!last_only) max_rows = std::min<int64_t>(max_rows, std::max<int64_t>(M, ((int64_t)1 << 28) / V));  // logits of a chunk <= 1 GiB
+    const int Tc = (int)std::max<int64_t>(1, std::min<int64_t>(t, max_rows / M));
+    if ((rc = ensure_workspace(e, M * Tc, last_only ? M : M * Tc))) return rc;
+    for (int j0 = 0; j0 < t; j0 += Tc) {
+        const int T = std::min(Tc, t - j0);
+        const bool last_chunk = j0 + T == t;
+        const bool want = !last_only || last_chunk;
+        if ((rc = step_device(e, s, dcol.as<uint32_t>() + (size_t)j0 * M, want ? e->logits.as<float>() : nullptr, nullptr, want, T, !last_only))) return rc;
+        if (!want) continue;
+        if (last_only) {
+            CK(cudaMemcpyAsync(logits, e->logits.p, (size_t)M * V * sizeof(float), cudaMemcpyDeviceToHost, e->stream));
+        } else {
+            // device [T][rows][vocab] -> host [rows][t][vocab]: position j0 + k of every row
+            for (int k = 0; k < T; ++k)
+                CK(cudaMemcpy2DAsync(logits + (size_t)(j0 + k) * V, (size_t)t * V * sizeof(float), e->logits.as<float>() + (size_t)k * M * V,
+                                     (size_t)V * sizeof(float), (size_t)V * sizeof(float), M, cudaMemcpyDeviceToHost, e->stream));
+            CK(cudaStreamSynchronize(e->stream));  // the logits buffer is reused by the next chunk
         }
     }
     return finish(e);
+}
+
+int ava_prefill_device(ava_engine* e, ava_state* s, const uint32_t* tok_device, int32_t t, int32_t chunk, float* logits_device, uint32_t* next_device) {
+    int rc = check_pair(e, s);
+    if (rc) return rc;
+    if (!tok_device || t <= 0 || chunk <= 0) return e->fail(AVA_ERR_ARG, "bad arguments");
+    const int M = s->rows;
+    const int Tc = std::min(chunk, t);
+    if ((rc = ensure_workspace(e, M * Tc, M))) return rc;
+    for (int j0 = 0; j0 < t; j0 += Tc) {
+        const int T = std::min(Tc, t - j0);
+        const bool last_chunk = j0 + T == t;
+        const bool want = last_chunk && (logits_device || next_device);
+        if ((rc = step_device(e, s, tok_device + (size_t)j0 * M, want ? logits_device : nullptr, want ? next_device : nullptr, want && logits_device, T, false)))
+            return rc;
+    }
+    return AVA_OK;
 }
 
 void* ava_engine_stream(ava_engine* e) { return e ? (void*)e->stream : nullptr; }

@@ -192,6 +192,130 @@ __global__ void __launch_bounds__(THREADS) mem_heads_kernel(const MemHeadsArgs a
     mark(4);
 }
 
+// The same update + read for T tokens in a row (chunked prompt reading): the block's slice comes into shared memory
+// once, every token of the chunk updates it there in order, and it goes back to HBM once: the state traffic of a chunk
+// is that of one token.  Per token the block needs the head's vectors (time-major [T][M][nh * hs]): e and q*alpha for
+// the column sums and the value slice arrive by bulk copy one token ahead (two buffers, one mbarrier each, used with
+// alternating parity); alpha, w and ah are read through the cache during the update, where a warp covers whole rows.
+template <int CW>
+__global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsArgs a, int T) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int hs = a.hs, cr = a.chunk_rows, nchunk = hs / cr, d = a.nh * hs;
+    float* tile = reinterpret_cast<float*>(smem_raw);
+    float* vbuf = tile + (size_t)hs * CW;          // [2][2 * hs + CW]: e, q*alpha, v slice
+    const int vstride = 2 * hs + CW;
+    float* rr = vbuf + 2 * vstride;
+    float* t1 = rr + CW;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(t1 + CW);  // nchunk for the slice, then 2 for the vectors
+    uint64_t* vbar = &bars[nchunk];
+
+    const int tid = threadIdx.x;
+    const int slices = hs / CW;
+    const int slice = blockIdx.x % slices;
+    const int head = (blockIdx.x / slices) % a.nh;
+    const int m = blockIdx.x / (slices * a.nh);
+    const int c0 = slice * CW;
+    const size_t ho = (size_t)head * hs;
+    float* gslice = a.f + (((size_t)m * a.nh + head) * hs * hs) + (size_t)slice * hs * CW;
+    const uint32_t chunk_bytes = (uint32_t)(cr * CW * sizeof(float));
+    const uint32_t vb = (uint32_t)(hs * sizeof(float));
+    const size_t Md = (size_t)a.M * d;
+
+    auto fetch_vectors = [&](int t) {  // thread 0 only
+        float* dst = vbuf + (size_t)(t & 1) * vstride;
+        const size_t o = (size_t)t * Md + (size_t)m * d + ho;
+        mbar_expect_tx(&vbar[t & 1], 2 * vb + (uint32_t)(CW * sizeof(float)));
+        bulk_load(dst, a.e + o, vb, &vbar[t & 1]);
+        bulk_load(dst + hs, a.qg + o, vb, &vbar[t & 1]);
+        bulk_load(dst + 2 * hs, a.v + o + c0, (uint32_t)(CW * sizeof(float)), &vbar[t & 1]);
+    };
+
+    if (tid == 0) {
+        for (int c = 0; c < nchunk + 2; ++c) mbar_init(&bars[c], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (tid == 0) {
+        fetch_vectors(0);
+        for (int c = 0; c < nchunk; ++c) {
+            mbar_expect_tx(&bars[c], chunk_bytes);
+            bulk_load(tile + (size_t)c * cr * CW, gslice + (size_t)c * cr * CW, chunk_bytes, &bars[c]);
+        }
+    }
+    bool ok = true;
+    constexpr int QW = CW / 4, RPP = THREADS / QW;
+    const int q4 = tid % QW, rg = tid / QW;
+    for (int t = 0; t < T; ++t) {
+        // the buffer of token t + 1 was last read during token t - 1, which every thread has left (barrier below)
+        if (tid == 0 && t + 1 < T) fetch_vectors(t + 1);
+        ok = mbar_wait(&vbar[t & 1], (uint32_t)((t >> 1) & 1)) && ok;
+        const float* ve = vbuf + (size_t)(t & 1) * vstride;
+        const float* vqg = ve + hs;
+        const float* vv = ve + 2 * hs;
+        if (tid < CW) {
+            float r = -0.0f, s1 = -0.0f;
+            for (int c = 0; c < nchunk; ++c) {
+                if (t == 0) ok = mbar_wait(&bars[c], 0) && ok;
+                const float* p = tile + (size_t)c * cr * CW + tid;
+                const int end = (c + 1) * cr;
+                for (int row = c * cr; row < end; row += 8, p += 8 * CW) {
+                    float f[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) f[i] = p[i * CW];
+                    const float4 e0 = *reinterpret_cast<const float4*>(ve + row), e1 = *reinterpret_cast<const float4*>(ve + row + 4);
+                    const float4 g0 = *reinterpret_cast<const float4*>(vqg + row), g1 = *reinterpret_cast<const float4*>(vqg + row + 4);
+                    const float ev[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
+                    const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        r = fma(f[i], ev[i], r);
+                        s1 = fma(f[i], gv[i], s1);
+                    }
+                }
+            }
+            r = add(r, mul(1.0f, mul(0.0f, vv[tid])));
+            rr[tid] = r;
+            t1[tid] = s1;
+        }
+        __syncthreads();
+        if (t == 0 && tid >= CW)
+            for (int c = 0; c < nchunk; ++c) ok = mbar_wait(&bars[c], 0) && ok;
+        const size_t row_o = (size_t)t * Md + (size_t)m * d + ho;  // this token's vectors of this head
+        if (tid < CW) {
+            const size_t qo = ((size_t)t * a.M + m) * a.nh + head;
+            a.y[row_o + c0 + tid] = sub(add(t1[tid], mul(a.qw[qo], vv[tid])), mul(a.qa[qo], rr[tid]));
+        }
+        {
+            const float4 vb4 = *reinterpret_cast<const float4*>(vv + 4 * q4), rb4 = *reinterpret_cast<const float4*>(rr + 4 * q4);
+            const float* gx = a.ex + row_o;
+            const float* gw = a.w + row_o;
+            const float* ga = a.ah + row_o;
+#pragma unroll 4
+            for (int row = rg; row < hs; row += RPP) {
+                float4* p = reinterpret_cast<float4*>(tile + (size_t)row * CW) + q4;
+                float4 f = *p;
+                const float x = __ldg(gx + row), w = __ldg(gw + row), ah = __ldg(ga + row);
+                f.x = sub(add(mul(f.x, x), mul(w, vb4.x)), mul(ah, rb4.x));
+                f.y = sub(add(mul(f.y, x), mul(w, vb4.y)), mul(ah, rb4.y));
+                f.z = sub(add(mul(f.z, x), mul(w, vb4.z)), mul(ah, rb4.z));
+                f.w = sub(add(mul(f.w, x), mul(w, vb4.w)), mul(ah, rb4.w));
+                *p = f;
+            }
+        }
+        __syncthreads();
+    }
+    if (!ok) atomicOr(a.status, ST_WAIT_TIMEOUT);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (tid == 0) {
+        for (int c = 0; c < nchunk; ++c) bulk_store(gslice + (size_t)c * cr * CW, tile + (size_t)c * cr * CW, chunk_bytes);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    }
+}
+
+size_t smem_bytes_seq(int hs, int cw) { return ((size_t)hs * cw + 2 * (2 * (size_t)hs + cw) + 2 * (size_t)cw) * sizeof(float) + (MAX_CHUNKS + 2) * sizeof(uint64_t); }
+
 size_t smem_bytes(int hs, int cw) { return ((size_t)hs * cw + 5 * (size_t)hs + 3 * (size_t)cw) * sizeof(float) + (MAX_CHUNKS + 1) * sizeof(uint64_t); }
 
 }  // namespace
@@ -220,6 +344,18 @@ void launch_mem_heads(cudaStream_t st, const MemHeadsArgs& a) {
     } else {
         cudaFuncSetAttribute(mem_heads_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         mem_heads_kernel<16><<<grid, THREADS, smem, st>>>(a);
+    }
+}
+
+void launch_mem_heads_seq(cudaStream_t st, const MemHeadsArgs& a, int T) {
+    const size_t smem = smem_bytes_seq(a.hs, a.cw);
+    const unsigned grid = (unsigned)((size_t)a.M * a.nh * (a.hs / a.cw));
+    if (a.cw == 32) {
+        cudaFuncSetAttribute(mem_heads_seq_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        mem_heads_seq_kernel<32><<<grid, THREADS, smem, st>>>(a, T);
+    } else {
+        cudaFuncSetAttribute(mem_heads_seq_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        mem_heads_seq_kernel<16><<<grid, THREADS, smem, st>>>(a, T);
     }
 }
 

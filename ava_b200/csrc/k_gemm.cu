@@ -25,38 +25,63 @@ __device__ __forceinline__ void widen4(int w, float* f) {
     f[3] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7443)) - 8388736.0f;
 }
 
-__device__ __forceinline__ void lif_update(const LifParams& p, int r, int c, int d, float cur) {
-    // src/model/fstep/arch.rs:173-228 with the hard spike count taken directly (as the reference's own GPU kernel
-    // does; the CPU's soft + (hard - soft) equals it).
+// One LIF update of one channel (src/model/fstep/arch.rs:173-228) with the hard spike count taken directly (as the
+// reference's own GPU kernel does; the CPU's soft + (hard - soft) equals it).  v, s, a: the carried state, in and out.
+__device__ __forceinline__ void lif_core(const LifParams& p, int c, float cur, float& v, float& s, float& a) {
     const float beta = p.beta[c];
     if (p.lif_scale) cur = mul(cur, add(mul(beta, -1.0f), 1.0f));
-    const size_t i = (size_t)r * d + c;
     const float th = p.theta ? p.theta[c] : 1.0f;
-    const float v0 = p.v[i], s0 = p.s[i];
     float th_prev = th, th_t = th;
     if (p.rho) {
-        const float a_prev = p.a[i];
         const float rho = p.rho[c], gain = p.gain[c];
-        th_prev = add(th, mul(a_prev, gain));
-        const float an = add(mul(a_prev, rho), mul(fabsf(s0), add(mul(rho, -1.0f), 1.0f)));
-        p.a[i] = an;
-        th_t = add(th, mul(an, gain));
+        th_prev = add(th, mul(a, gain));
+        a = add(mul(a, rho), mul(fabsf(s), add(mul(rho, -1.0f), 1.0f)));
+        th_t = add(th, mul(a, gain));
     }
-    const float vv = sub(add(mul(v0, beta), cur), mul(s0, th_prev));
-    p.v[i] = vv;
-    float s;
+    const float vv = sub(add(mul(v, beta), cur), mul(s, th_prev));
+    v = vv;
     if (p.spikes == 0) {
         s = sub(vv, th_t) >= 0.0f ? 1.0f : 0.0f;
     } else {
         const int levels = p.spikes == 2 ? 2 : 1;
-        s = 0.0f;
+        float n = 0.0f;
         for (int k = 1; k <= levels; ++k) {
             const float kth = add(mul(th_t, (float)k), 0.0f);
             const float up = sub(vv, kth), down = sub(-vv, kth);
-            s += (up >= 0.0f ? 1.0f : 0.0f) - (down >= 0.0f ? 1.0f : 0.0f);
+            n += (up >= 0.0f ? 1.0f : 0.0f) - (down >= 0.0f ? 1.0f : 0.0f);
         }
+        s = n;
     }
+}
+
+__device__ __forceinline__ void lif_update(const LifParams& p, int r, int c, int d, float cur) {
+    const size_t i = (size_t)r * d + c;
+    float v = p.v[i], s = p.s[i], a = p.rho ? p.a[i] : 0.0f;
+    lif_core(p, c, cur, v, s, a);
+    p.v[i] = v;
     p.s[i] = s;
+    if (p.rho) p.a[i] = a;
+}
+
+// The LIF over a chunk of T tokens: one thread per (row, channel) walks the tokens in order with the membrane, last
+// spike and trace in registers (the reset makes the recurrence nonlinear, so time stays sequential; the parallelism is
+// rows x channels).  cur and spikes are time-major [T][M][d].
+__global__ void lif_scan_kernel(const float* __restrict__ cur, const LifParams p, int M, int d, int T, float* __restrict__ spikes) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t Md = (size_t)M * d;
+    if (i >= Md) return;
+    const int c = (int)(i % d);
+    float v = p.v[i], s = p.s[i], a = p.rho ? p.a[i] : 0.0f;
+    float nxt = cur[i];
+    for (int t = 0; t < T; ++t) {
+        const float x = nxt;
+        if (t + 1 < T) nxt = cur[(size_t)(t + 1) * Md + i];
+        lif_core(p, c, x, v, s, a);
+        spikes[(size_t)t * Md + i] = s;
+    }
+    p.v[i] = v;
+    p.s[i] = s;
+    if (p.rho) p.a[i] = a;
 }
 
 // Tile BM x BN per block, TM x TN outputs per thread (TM = 4; TN = 4 or 2).  Wide products use 64x64 tiles of 4x4; the
@@ -354,6 +379,11 @@ bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {
         q8_event_kernel<EPI_STORE><<<grid, EV_THREADS, smem, st>>>(a);
     }
     return true;
+}
+
+void launch_lif_scan(cudaStream_t st, const float* cur, const LifParams& p, int M, int d, int T, float* spikes) {
+    const size_t n = (size_t)M * d;
+    lif_scan_kernel<<<(unsigned)((n + 127) / 128), 128, 0, st>>>(cur, p, M, d, T, spikes);
 }
 
 void launch_lif(cudaStream_t st, const float* cur, const LifParams& p, int M, int d) {

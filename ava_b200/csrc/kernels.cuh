@@ -54,6 +54,8 @@ bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi);
 void launch_embed(cudaStream_t st, const float* tok_emb, const uint32_t* tok, int M, int d, int vocab, float* x, float* stream0, uint32_t* status);
 void launch_rmsnorm(cudaStream_t st, const float* x, const float* gain, int M, int n, float* y);
 void launch_lif(cudaStream_t st, const float* cur, const LifParams& p, int M, int d);
+// T tokens of M rows in time order: cur, spikes [T][M][d]; the state in p moves T steps
+void launch_lif_scan(cudaStream_t st, const float* cur, const LifParams& p, int M, int d, int T, float* spikes);
 
 struct MemPrepArgs {
     const float* h;      // [M, d] normed input
@@ -83,6 +85,9 @@ struct MemHeadsArgs {
     unsigned long long* timeline;            // nullptr, or [blocks][6] phase marks in ns (tuning aid)
 };
 void launch_mem_heads(cudaStream_t st, const MemHeadsArgs& a);
+// The same for T tokens in time order with the slice resident in shared memory between them: the vectors and y are
+// time-major [T][M][nh * hs], qw/qa [T][M][nh]; the state is read and written once for the whole chunk.
+void launch_mem_heads_seq(cudaStream_t st, const MemHeadsArgs& a, int T);
 // the column-slice width and the rows per bulk copy the kernel uses for a head size; false: head size not covered
 bool mem_heads_tiling(int hs, int* cw, int* chunk_rows);
 // natural [heads][hs][hs] to slice-major [heads][hs / cw][hs][cw] (to_slices 1) or back (0)

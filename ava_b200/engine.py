@@ -73,6 +73,7 @@ def lib() -> C.CDLL:
         "ava_step_greedy": ([vp, vp, u32p, u32p], C.c_int),
         "ava_forward_with_state": ([vp, vp, u32p, C.c_int32, C.c_int32, fp], C.c_int),
         "ava_step_device": ([vp, vp, vp, vp, vp], C.c_int),
+        "ava_prefill_device": ([vp, vp, vp, C.c_int32, C.c_int32, vp, vp], C.c_int),
         "ava_sync": ([vp], C.c_int),
         "ava_engine_stream": ([vp], vp),
         "ava_engine_launches": ([vp], C.c_int64),
@@ -110,7 +111,7 @@ def lib() -> C.CDLL:
 EXPORTS = ("ava_engine_create ava_engine_destroy ava_last_error ava_engine_set_f32 ava_engine_set_q8 "
            "ava_engine_set_q8_from_f32 ava_engine_finalize ava_engine_blocker ava_state_new ava_state_destroy "
            "ava_state_rows ava_state_select ava_state_cat ava_state_seen ava_state_len ava_state_export "
-           "ava_state_import ava_step ava_step_greedy ava_forward_with_state ava_step_device ava_sync "
+           "ava_state_import ava_step ava_step_greedy ava_forward_with_state ava_step_device ava_prefill_device ava_sync "
            "ava_engine_stream ava_engine_launches ava_engine_bytes ava_state_bytes ava_debug_keep ava_debug_width "
            "ava_debug_get ava_prof_enable ava_prof_read ava_prof_names ava_op_q8_matmul ava_op_q8_event_matmul ava_debug_mem_heads_timeline ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
            "ava_host_expf ava_host_logf ava_host_rsqrtf ava_op_math").split()
@@ -199,6 +200,10 @@ class Model:
     # device-resident form: raw device addresses (ints), nothing copied, nothing synchronised
     def step_device(self, st: "State", tok_ptr: int, logits_ptr: int | None, next_ptr: int | None):
         self._check(lib().ava_step_device(self.h, st.h, tok_ptr, logits_ptr, next_ptr))
+
+    def prefill_device(self, st: "State", tok_ptr: int, t: int, chunk: int, logits_ptr: int | None, next_ptr: int | None):
+        """tok_ptr: device u32 [t][rows] (time-major); queued on the engine's stream."""
+        self._check(lib().ava_prefill_device(self.h, st.h, tok_ptr, t, chunk, logits_ptr, next_ptr))
 
     def sync(self):
         self._check(lib().ava_sync(self.h))

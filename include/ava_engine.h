@@ -120,6 +120,10 @@ int ava_forward_with_state(ava_engine* e, ava_state* s, const uint32_t* ids, int
  * tok_device [rows] u32, logits_device [rows, vocab] f32 or NULL, next_device [rows] u32 or NULL.  Work is queued on
  * the engine's stream; ava_sync waits for it and returns the step's status. */
 int ava_step_device(ava_engine* e, ava_state* s, const uint32_t* tok_device, float* logits_device, uint32_t* next_device);
+/* Prompt reading with device-resident ids (`Model::feed`, src/model.rs:1218-1227, without host copies): tok_device
+ * [t][rows] u32 (time-major), processed `chunk` tokens per row at a time; logits_device [rows, vocab] and next_device
+ * [rows] (either may be NULL) receive the last position's logits / greedy token.  Queued on the engine's stream. */
+int ava_prefill_device(ava_engine* e, ava_state* s, const uint32_t* tok_device, int32_t t, int32_t chunk, float* logits_device, uint32_t* next_device);
 int ava_sync(ava_engine* e);
 /* The engine's cudaStream_t (for timing with CUDA events on the launching stream). */
 void* ava_engine_stream(ava_engine* e);

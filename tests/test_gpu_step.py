@@ -129,6 +129,37 @@ def test_forward_with_state_equals_steps(orc_same_math):
     assert np.array_equal(bits(tail), bits(want[:, 6:]))
 
 
+@pytest.mark.parametrize("name", ["ava04_small", "one_head_bf16", "binary_plain"])
+@pytest.mark.parametrize("chunk", [1, 5, 64])
+def test_chunked_prompt_equals_steps(orc_same_math, name, chunk):
+    """Reading a prompt in chunks (token-parallel products, the recurrences in order inside their kernels) gives the
+    bits of reading it token by token: last logits and the whole state, for chunks that do and do not divide t."""
+    import torch
+    orc = orc_same_math
+    cfg = config.tiny(**CONFIGS[name])
+    gm, om = pair(orc, cfg, seed=7)
+    rows, t = 3, 23
+    ids = synth.token_ids(cfg["vocab"], rows, t, seed0=21)
+    os_ = om.state(rows)
+    want = os_.forward(ids, last_only=True)
+    gs = gm.state(rows, 64)
+    dev = torch.device("cuda", 0)
+    tok = torch.from_numpy(np.ascontiguousarray(ids.T).astype(np.int32)).to(dev)
+    logits = torch.empty(rows, cfg["vocab"], dtype=torch.float32, device=dev)
+    nxt = torch.empty(rows, dtype=torch.int32, device=dev)
+    torch.cuda.synchronize()
+    gm.prefill_device(gs, tok.data_ptr(), t, chunk, logits.data_ptr(), nxt.data_ptr())
+    gm.sync()
+    got = logits.cpu().numpy()
+    assert np.array_equal(bits(got), bits(want)), float(np.abs(got - want).max())
+    assert np.array_equal(nxt.cpu().numpy().astype(np.int64), want.argmax(1))
+    assert_same_state(cfg, gs, os_, rows)
+    assert gs.seen(0) == t
+    # and the next single step continues from it
+    nx = np.array([1, 2, 3], np.uint32)
+    assert np.array_equal(bits(gm.step(gs, nx)), bits(os_.step(nx)))
+
+
 def test_rows_independent_select_forks_cat_joins(orc_same_math):
     orc = orc_same_math
     cfg = config.tiny()
