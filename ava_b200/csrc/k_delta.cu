@@ -194,20 +194,25 @@ __global__ void __launch_bounds__(THREADS) mem_heads_kernel(const MemHeadsArgs a
 
 // The same update + read for T tokens in a row (chunked prompt reading): the block's slice comes into shared memory
 // once, every token of the chunk updates it there in order, and it goes back to HBM once: the state traffic of a chunk
-// is that of one token.  Per token the block needs the head's vectors (time-major [T][M][nh * hs]): e and q*alpha for
-// the column sums and the value slice arrive by bulk copy one token ahead (two buffers, one mbarrier each, used with
-// alternating parity); alpha, w and ah are read through the cache during the update, where a warp covers whole rows.
+// is that of one token.  Per token the block needs the head's vectors (time-major [T][M][nh * hs]), all brought by
+// bulk copies that overlap the other pass: alpha, w and ah of token t land while its column sums run; e, q*alpha of
+// token t + 1 land while token t's update runs (the value slice is double-buffered: both passes read it).
 template <int CW>
 __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsArgs a, int T) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int hs = a.hs, cr = a.chunk_rows, nchunk = hs / cr, d = a.nh * hs;
     float* tile = reinterpret_cast<float*>(smem_raw);
-    float* vbuf = tile + (size_t)hs * CW;          // [2][2 * hs + CW]: e, q*alpha, v slice
-    const int vstride = 2 * hs + CW;
-    float* rr = vbuf + 2 * vstride;
+    float* ve = tile + (size_t)hs * CW;
+    float* vqg = ve + hs;
+    float* vex = vqg + hs;
+    float* vw = vex + hs;
+    float* vah = vw + hs;
+    float* vvb = vah + hs;                          // [2][CW]
+    float* rr = vvb + 2 * CW;
     float* t1 = rr + CW;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(t1 + CW);  // nchunk for the slice, then 2 for the vectors
-    uint64_t* vbar = &bars[nchunk];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(t1 + CW);  // nchunk for the slice, then A (sums' vectors), B (update's)
+    uint64_t* barA = &bars[nchunk];
+    uint64_t* barB = &bars[nchunk + 1];
 
     const int tid = threadIdx.x;
     const int slices = hs / CW;
@@ -220,14 +225,21 @@ __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsAr
     const uint32_t chunk_bytes = (uint32_t)(cr * CW * sizeof(float));
     const uint32_t vb = (uint32_t)(hs * sizeof(float));
     const size_t Md = (size_t)a.M * d;
+    auto row_off = [&](int t) { return (size_t)t * Md + (size_t)m * d + ho; };
 
-    auto fetch_vectors = [&](int t) {  // thread 0 only
-        float* dst = vbuf + (size_t)(t & 1) * vstride;
-        const size_t o = (size_t)t * Md + (size_t)m * d + ho;
-        mbar_expect_tx(&vbar[t & 1], 2 * vb + (uint32_t)(CW * sizeof(float)));
-        bulk_load(dst, a.e + o, vb, &vbar[t & 1]);
-        bulk_load(dst + hs, a.qg + o, vb, &vbar[t & 1]);
-        bulk_load(dst + 2 * hs, a.v + o + c0, (uint32_t)(CW * sizeof(float)), &vbar[t & 1]);
+    auto fetch_a = [&](int t) {  // thread 0: what the column sums of token t read (+ its value slice)
+        const size_t o = row_off(t);
+        mbar_expect_tx(barA, 2 * vb + (uint32_t)(CW * sizeof(float)));
+        bulk_load(ve, a.e + o, vb, barA);
+        bulk_load(vqg, a.qg + o, vb, barA);
+        bulk_load(vvb + (t & 1) * CW, a.v + o + c0, (uint32_t)(CW * sizeof(float)), barA);
+    };
+    auto fetch_b = [&](int t) {  // thread 0: what the update of token t reads
+        const size_t o = row_off(t);
+        mbar_expect_tx(barB, 3 * vb);
+        bulk_load(vex, a.ex + o, vb, barB);
+        bulk_load(vw, a.w + o, vb, barB);
+        bulk_load(vah, a.ah + o, vb, barB);
     };
 
     if (tid == 0) {
@@ -236,41 +248,49 @@ __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsAr
     }
     __syncthreads();
     if (tid == 0) {
-        fetch_vectors(0);
+        fetch_a(0);
         for (int c = 0; c < nchunk; ++c) {
             mbar_expect_tx(&bars[c], chunk_bytes);
             bulk_load(tile + (size_t)c * cr * CW, gslice + (size_t)c * cr * CW, chunk_bytes, &bars[c]);
         }
     }
     bool ok = true;
+    for (int c = 0; c < nchunk; ++c) ok = mbar_wait(&bars[c], 0) && ok;  // the slice is resident from here on
     constexpr int QW = CW / 4, RPP = THREADS / QW;
     const int q4 = tid % QW, rg = tid / QW;
     for (int t = 0; t < T; ++t) {
-        // the buffer of token t + 1 was last read during token t - 1, which every thread has left (barrier below)
-        if (tid == 0 && t + 1 < T) fetch_vectors(t + 1);
-        ok = mbar_wait(&vbar[t & 1], (uint32_t)((t >> 1) & 1)) && ok;
-        const float* ve = vbuf + (size_t)(t & 1) * vstride;
-        const float* vqg = ve + hs;
-        const float* vv = ve + 2 * hs;
+        const uint32_t par = (uint32_t)(t & 1);
+        // alpha, w, ah of this token: their buffers were last read by the update of token t - 1 (barrier at its end)
+        if (tid == 0) fetch_b(t);
+        ok = mbar_wait(barA, par) && ok;
+        const float* vv = vvb + (t & 1) * CW;
         if (tid < CW) {
+            // the column sums, eight rows fetched one batch ahead of the two chains (chains start from -0: see above)
             float r = -0.0f, s1 = -0.0f;
-            for (int c = 0; c < nchunk; ++c) {
-                if (t == 0) ok = mbar_wait(&bars[c], 0) && ok;
-                const float* p = tile + (size_t)c * cr * CW + tid;
-                const int end = (c + 1) * cr;
-                for (int row = c * cr; row < end; row += 8, p += 8 * CW) {
-                    float f[8];
+            const float* p = tile + tid;
+            float f[8], ev[8], gv[8];
+            auto load8 = [&](int row, float* ff, float* ee, float* gg) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) f[i] = p[i * CW];
-                    const float4 e0 = *reinterpret_cast<const float4*>(ve + row), e1 = *reinterpret_cast<const float4*>(ve + row + 4);
-                    const float4 g0 = *reinterpret_cast<const float4*>(vqg + row), g1 = *reinterpret_cast<const float4*>(vqg + row + 4);
-                    const float ev[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
-                    const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+                for (int i = 0; i < 8; ++i) ff[i] = p[(size_t)(row + i) * CW];
+                const float4 e0 = *reinterpret_cast<const float4*>(ve + row), e1 = *reinterpret_cast<const float4*>(ve + row + 4);
+                const float4 g0 = *reinterpret_cast<const float4*>(vqg + row), g1 = *reinterpret_cast<const float4*>(vqg + row + 4);
+                ee[0] = e0.x; ee[1] = e0.y; ee[2] = e0.z; ee[3] = e0.w; ee[4] = e1.x; ee[5] = e1.y; ee[6] = e1.z; ee[7] = e1.w;
+                gg[0] = g0.x; gg[1] = g0.y; gg[2] = g0.z; gg[3] = g0.w; gg[4] = g1.x; gg[5] = g1.y; gg[6] = g1.z; gg[7] = g1.w;
+            };
+            load8(0, f, ev, gv);
+            for (int row = 0; row < hs; row += 8) {
+                float nf[8], ne[8], ng[8];
+                if (row + 8 < hs) load8(row + 8, nf, ne, ng);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        r = fma(f[i], ev[i], r);
-                        s1 = fma(f[i], gv[i], s1);
-                    }
+                for (int i = 0; i < 8; ++i) {
+                    r = fma(f[i], ev[i], r);
+                    s1 = fma(f[i], gv[i], s1);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    f[i] = nf[i];
+                    ev[i] = ne[i];
+                    gv[i] = ng[i];
                 }
             }
             r = add(r, mul(1.0f, mul(0.0f, vv[tid])));
@@ -278,23 +298,21 @@ __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsAr
             t1[tid] = s1;
         }
         __syncthreads();
-        if (t == 0 && tid >= CW)
-            for (int c = 0; c < nchunk; ++c) ok = mbar_wait(&bars[c], 0) && ok;
-        const size_t row_o = (size_t)t * Md + (size_t)m * d + ho;  // this token's vectors of this head
+        // e, q*alpha of the next token: the sums above were their last readers
+        if (tid == 0 && t + 1 < T) fetch_a(t + 1);
+        const size_t ro = row_off(t);
         if (tid < CW) {
             const size_t qo = ((size_t)t * a.M + m) * a.nh + head;
-            a.y[row_o + c0 + tid] = sub(add(t1[tid], mul(a.qw[qo], vv[tid])), mul(a.qa[qo], rr[tid]));
+            a.y[ro + c0 + tid] = sub(add(t1[tid], mul(a.qw[qo], vv[tid])), mul(a.qa[qo], rr[tid]));
         }
+        ok = mbar_wait(barB, par) && ok;
         {
             const float4 vb4 = *reinterpret_cast<const float4*>(vv + 4 * q4), rb4 = *reinterpret_cast<const float4*>(rr + 4 * q4);
-            const float* gx = a.ex + row_o;
-            const float* gw = a.w + row_o;
-            const float* ga = a.ah + row_o;
 #pragma unroll 4
             for (int row = rg; row < hs; row += RPP) {
                 float4* p = reinterpret_cast<float4*>(tile + (size_t)row * CW) + q4;
                 float4 f = *p;
-                const float x = __ldg(gx + row), w = __ldg(gw + row), ah = __ldg(ga + row);
+                const float x = vex[row], w = vw[row], ah = vah[row];
                 f.x = sub(add(mul(f.x, x), mul(w, vb4.x)), mul(ah, rb4.x));
                 f.y = sub(add(mul(f.y, x), mul(w, vb4.y)), mul(ah, rb4.y));
                 f.z = sub(add(mul(f.z, x), mul(w, vb4.z)), mul(ah, rb4.z));
@@ -314,7 +332,7 @@ __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsAr
     }
 }
 
-size_t smem_bytes_seq(int hs, int cw) { return ((size_t)hs * cw + 2 * (2 * (size_t)hs + cw) + 2 * (size_t)cw) * sizeof(float) + (MAX_CHUNKS + 2) * sizeof(uint64_t); }
+size_t smem_bytes_seq(int hs, int cw) { return ((size_t)hs * cw + 5 * (size_t)hs + 4 * (size_t)cw) * sizeof(float) + (MAX_CHUNKS + 2) * sizeof(uint64_t); }
 
 size_t smem_bytes(int hs, int cw) { return ((size_t)hs * cw + 5 * (size_t)hs + 3 * (size_t)cw) * sizeof(float) + (MAX_CHUNKS + 1) * sizeof(uint64_t); }
 

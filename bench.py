@@ -123,6 +123,41 @@ def run_reference(args, cfg, rank):
     print(json.dumps(line), flush=True)
 
 
+def measure_prefill(model, cfg, local, world, dist, rows, tokens, chunk, seed0):
+    """Chunked prompt reading through ava_prefill_device: tokens/s over all ranks, device-timed, ids resident."""
+    import torch
+    from ava_b200 import synth
+    ids = synth.token_ids(cfg["vocab"], rows, tokens, seed0=seed0)
+    tok = torch.from_numpy(np.ascontiguousarray(ids.T).astype(np.int32)).to(f"cuda:{local}")
+    logits = torch.empty(rows, cfg["vocab"], dtype=torch.float32, device=f"cuda:{local}")
+    stream = torch.cuda.ExternalStream(model.stream, device=local)
+    warm = model.state(rows, chunk + 8)
+    model.prefill_device(warm, tok.data_ptr(), chunk, chunk, logits.data_ptr(), None)
+    model.sync()
+    warm.close()
+    st = model.state(rows, tokens + 8)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    l0 = model.launches
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    model.prefill_device(st, tok.data_ptr(), tokens, chunk, logits.data_ptr(), None)
+    ev1.record(stream)
+    model.sync()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    st.close()
+    return {"value": world * rows * tokens / (ms * 1e-3), "unit": "tokens/s", "rows_per_gpu": rows, "tokens_per_row": tokens, "chunk": chunk,
+            "ms": ms, "gpu_launches": int(model.launches - l0),
+            "what": "chunked prompt reading, bit-identical to stepping (CUDA-core products in k order, LIF time scan, fast-weight slice "
+                    "resident in shared memory per chunk, engram read token by token); config 2 is 8192 tokens per row, this is its first part"}
+
+
 # ------------------------------------------------------------------------------------------------- GPU arm
 def main():
     ap = argparse.ArgumentParser()
@@ -134,6 +169,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=MEAN_CTX, help="KV length the timed steps are centred on")
     ap.add_argument("--small", action="store_true", help="a small model and batch (profiling captures, not a bench value)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--prefill-tokens", type=int, default=1024, help="tokens per row of the prompt-reading sample (config 2: 8192)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
 
@@ -286,6 +322,9 @@ def main():
         "kernel_share": {k: round(v[1] / total_ms, 4) for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])},
         "kernel_ms_per_step": {k: round(v[1] / 4, 4) for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])},
     }
+    # ---- prompt reading (BASELINE config 2's shape: 64 rows per GPU, chunks of 256 tokens), a bounded sample of it
+    if not args.small:
+        line["prefill"] = measure_prefill(model, cfg, local, world, dist, rows=64, tokens=args.prefill_tokens, chunk=256, seed0=50_000 + first)
     if rank == 0 and not args.no_cpu and not args.small:
         threads = os.cpu_count() or 1
         val, _, sample = cpu_reference(cfg, weights, 128, 4, 16, threads)
