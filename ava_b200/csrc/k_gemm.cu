@@ -372,10 +372,10 @@ bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {
     if (smem > 200 * 1024) return false;
     dim3 grid((a.N + EV_COLS - 1) / EV_COLS, a.M);
     if (epi == EPI_ADD) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(q8_event_kernel<EPI_ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem > 32 * 1024) cudaFuncSetAttribute(q8_event_kernel<EPI_ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         q8_event_kernel<EPI_ADD><<<grid, EV_THREADS, smem, st>>>(a);
     } else {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(q8_event_kernel<EPI_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem > 32 * 1024) cudaFuncSetAttribute(q8_event_kernel<EPI_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         q8_event_kernel<EPI_STORE><<<grid, EV_THREADS, smem, st>>>(a);
     }
     return true;

@@ -391,7 +391,7 @@ __global__ void widen_bf16_kernel(const uint16_t* x, int64_t n, float* y) {
 
 template <typename K>
 void opt_in_smem(K kernel, size_t bytes) {
-    if (bytes > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (bytes > 32 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 }
 
 }  // namespace

@@ -168,6 +168,7 @@ def main():
     ap.add_argument("--rows", type=int, default=ROWS_PER_GPU, help="sequences per GPU")
     ap.add_argument("--ctx", type=int, default=MEAN_CTX, help="KV length the timed steps are centred on")
     ap.add_argument("--small", action="store_true", help="a small model and batch (profiling captures, not a bench value)")
+    ap.add_argument("--scaled", action="store_true", help="BASELINE config 3: 24 blocks, d 2048, wide 8192, vocab 32768 (use --rows 128: an 8-GPU share of 1024 sequences)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--prefill-tokens", type=int, default=1024, help="tokens per row of the prompt-reading sample (config 2: 8192)")
     args = ap.parse_args()
@@ -181,6 +182,8 @@ def main():
     cfg = config.ava04_shaped()
     if args.small:
         cfg = config.make(4096, 768, 2, head_size=768, eng_block=1, eng_head_size=64, eng_store_bf16=1)
+    if args.scaled:
+        cfg = config.ava04_shaped(scaled=True)
 
     if args.impl == "reference":
         run_reference(args, cfg, rank)
@@ -307,7 +310,9 @@ def main():
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations x int8 weights, f32 state, bf16 KV",
         "data": "synthetic",
         "config": {"workload": "BASELINE config 1: Ava-0.4-shaped decode (12 blocks, d 768, wide 3072, kWTA 768, vocab 16384, one 768x768 f32 "
-                               "fast-synapse matrix per block, bf16 engram of 12x64 in block 6)" if not args.small else "small profiling case",
+                               "fast-synapse matrix per block, bf16 engram of 12x64 in block 6)" if not (args.small or args.scaled) else
+                   ("small profiling case" if args.small else "BASELINE config 3: scaled Ava (24 blocks, d 2048, wide 8192, kWTA 2048, vocab 32768, one "
+                    "2048x2048 f32 fast-synapse matrix per block)"),
                    "rows_per_gpu": rows, "kv_len_timed": [prompt + W, prompt + W + K], "l2": "per-step inputs (state "
                    f"{state.nbytes / 1e9:.2f} GB per GPU) are larger than L2", "sequences": "independent, sharded by rank, no collective"},
         "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": rows * 4, "d2h_bytes_per_step": rows * cfg["vocab"] * 4,
@@ -323,7 +328,7 @@ def main():
         "kernel_ms_per_step": {k: round(v[1] / 4, 4) for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])},
     }
     # ---- prompt reading (BASELINE config 2's shape: 64 rows per GPU, chunks of 256 tokens), a bounded sample of it
-    if not args.small:
+    if not args.small and not args.scaled:
         line["prefill"] = measure_prefill(model, cfg, local, world, dist, rows=64, tokens=args.prefill_tokens, chunk=256, seed0=50_000 + first)
     if rank == 0 and not args.no_cpu and not args.small:
         threads = os.cpu_count() or 1

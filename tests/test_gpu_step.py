@@ -272,6 +272,31 @@ def test_nonfinite_gate_is_reported(orc):
     assert os_.last_status == 1 and os_.seen(0) == 0
 
 
+def test_scaled_block_bits(orc_same_math):
+    """One block of the scaled model (d 2048, wide 8192, kWTA 2048, one 2048x2048 fast-synapse matrix, vocab cut to 2048):
+    the 64-byte column slices and the 16-chunk bulk copies of the big head, every bit."""
+    orc = orc_same_math
+    cfg = config.make(2048, 2048, 1, head_size=2048, eng_block=0, eng_head_size=64, eng_store_bf16=1)
+    w = synth.model(cfg, 0, "awake")
+    gm, om = engine.Model(cfg, w), orc.OracleModel(cfg, w)
+    orc.set_threads(8)
+    try:
+        rows, T = 3, 4
+        ids = synth.token_ids(cfg["vocab"], rows, T)
+        gs, os_ = gm.state(rows, 16), om.state(rows)
+        for t in range(T):
+            lg = gm.step(gs, ids[:, t])
+            lo = os_.step(ids[:, t])
+            assert np.array_equal(bits(lg), bits(lo)), (t, float(np.abs(lg - lo).max()))
+        assert_same_state(cfg, gs, os_, rows)
+        # and the chunked prompt path at this size
+        gs2 = gm.state(rows, 16)
+        last = gm.forward_with_state(ids, gs2, last_only=True)
+        assert np.array_equal(bits(last), bits(lg))
+    finally:
+        orc.set_threads(1)
+
+
 @pytest.mark.parametrize("rows", [1, 40])
 def test_benchmark_shape_bits(orc_same_math, rows):
     """The Ava-0.4-shaped benchmark model itself (12 blocks, d 768, one 768x768 fast-synapse matrix per block, engram of
