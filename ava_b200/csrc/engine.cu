@@ -106,7 +106,7 @@ struct ava_engine {
 
     // work buffers for `ws_rows` rows
     int ws_rows = 0, ws_logit_rows = 0;
-    Dev x, h, proj, ve, vv, vw, vah, vqg, vex, qw, qa, yraw, y, eqkv, eo, u, act, streams, v_first, logits, tok, next, status;
+    Dev x, h, proj, ve, vv, vw, vah, vqg, vex, vqs, qw, qa, yraw, y, eqkv, eo, u, act, streams, v_first, logits, tok, next, status;
     uint32_t* status_host = nullptr;  // pinned
 
     bool prof = false;
@@ -141,6 +141,7 @@ struct ava_state {
     int keep = 0;   // tokens kept after a read
     Dev lif_v, lif_s, lif_a;  // [L][rows][d]
     Dev mem_f;                // [L][rows][nh][hs / cw][hs][cw]: slice-major, a block of threads owns one contiguous slice
+    Dev mem_s;                // the momentum matrix, same layout (only with --mem-momentum)
     Dev eng_k, eng_v;         // [rows][enh][ring][ehs]
     Dev eng_n, eng_start;     // [rows] i32
     std::vector<int32_t> n_host, start_host;
@@ -256,11 +257,10 @@ const char* find_blocker(const ava_config& c, int* cw, int* rb) {
     if (c.d <= 0 || c.n_blocks <= 0 || c.vocab <= 0 || c.hidden <= 0 || c.head_size <= 0 || c.d % c.head_size) return "bad shape";
     if (c.d % 16 || c.hidden % 16) return "widths must be multiples of 16 (the product kernel's k step)";
     if (c.vocab % 4) return "vocabulary must be a multiple of 4";
-    if (c.mem_momentum > 0.0f) return "--mem-momentum: the second state matrix is not in the engine yet";
     if (c.gate_rank < 1) return "gate rank must be at least 1";
     if (c.eng_block >= 0 && (c.eng_head_size <= 0 || c.d % c.eng_head_size)) return "bad engram head size";
     if (c.spikes < 0 || c.spikes > 2) return "unknown spike kind";
-    if (c.head_size % 16 || !mem_heads_tiling(c.head_size, cw, rb)) return "memory head size not covered (a multiple of 16 whose column slice fits shared memory)";
+    if (c.head_size % 16 || !mem_heads_tiling(c.head_size, cw, rb, c.mem_momentum > 0.0f)) return "memory head size not covered (a multiple of 16 whose column slice fits shared memory)";
     return nullptr;
 }
 
@@ -276,6 +276,7 @@ int ensure_workspace(ava_engine* e, int rows, int logit_rows = 0) {
     CK(e->h.alloc(M * d * f));
     CK(e->proj.alloc(M * e->proj_w() * f));
     for (Dev* b : {&e->ve, &e->vv, &e->vw, &e->vah, &e->vqg, &e->vex, &e->yraw, &e->y, &e->eo, &e->v_first}) CK(b->alloc(M * d * f));
+    if (c.mem_momentum > 0.0f) CK(e->vqs.alloc(M * d * f));
     CK(e->qw.alloc(M * e->nh() * f));
     CK(e->qa.alloc(M * e->nh() * f));
     CK(e->eqkv.alloc(M * 3 * d * f));
@@ -416,6 +417,8 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         mp.M = M; mp.d = d; mp.hs = hs; mp.rank = c.gate_rank;
         mp.e = e->ve.as<float>(); mp.v = e->vv.as<float>(); mp.w = e->vw.as<float>(); mp.ah = e->vah.as<float>();
         mp.qg = e->vqg.as<float>(); mp.ex = e->vex.as<float>(); mp.qw = e->qw.as<float>(); mp.qa = e->qa.as<float>();
+        mp.qs = c.mem_momentum > 0.0f ? e->vqs.as<float>() : nullptr;
+        mp.mom = c.mem_momentum;
         mp.status = e->status.as<uint32_t>();
         prof_begin(e, "mem_prep");
         launch_mem_prep(st, mp);
@@ -424,12 +427,15 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         dbg(e, "qg", i, mp.qg, M, d); dbg(e, "ex", i, mp.ex, M, d); dbg(e, "qw", i, mp.qw, M, nh); dbg(e, "qa", i, mp.qa, M, nh);
         MemHeadsArgs mh{};
         mh.f = s->mem_f.as<float>() + (size_t)i * Rd * hs;
+        mh.s = c.mem_momentum > 0.0f ? s->mem_s.as<float>() + (size_t)i * Rd * hs : nullptr;
+        mh.qs = mp.qs;
+        mh.mom = c.mem_momentum;
         mh.M = rows; mh.nh = nh; mh.hs = hs; mh.cw = e->cw; mh.chunk_rows = e->rb;
         mh.e = mp.e; mh.v = mp.v; mh.w = mp.w; mh.ah = mp.ah; mh.qg = mp.qg; mh.ex = mp.ex; mh.qw = mp.qw; mh.qa = mp.qa;
         mh.y = e->yraw.as<float>();
         mh.status = e->status.as<uint32_t>();
         prof_begin(e, "mem_heads");
-        if (T == 1)
+        if (T == 1 && !mh.s)
             launch_mem_heads(st, mh);
         else
             launch_mem_heads_seq(st, mh, T);
@@ -574,9 +580,9 @@ bool locate(const ava_state* s, int row, const std::string& name, StateSlice* ou
         out->count = d;
         return out->buf != nullptr;
     }
-    if (kind == "mem" && what == "f") {
+    if (kind == "mem" && (what == "f" || (what == "s" && c.mem_momentum > 0.0f))) {
         const size_t per = (size_t)d * c.head_size;  // nh * hs * hs
-        out->buf = &ms->mem_f;
+        out->buf = what == "f" ? &ms->mem_f : &ms->mem_s;
         out->off = ((size_t)i * M + row) * per;
         out->count = per;
         out->tiled = true;
@@ -597,6 +603,7 @@ int alloc_state(ava_engine* e, int rows, int ring, int keep, ava_state** out) {
     CK(s->lif_s.alloc(L * M * d * f));
     if (c.alif) CK(s->lif_a.alloc(L * M * d * f));
     CK(s->mem_f.alloc(L * M * d * c.head_size * f));
+    if (c.mem_momentum > 0.0f) CK(s->mem_s.alloc(L * M * d * c.head_size * f));
     if (c.eng_block >= 0) {
         CK(s->eng_k.alloc(M * d * ring * s->kv_elem()));
         CK(s->eng_v.alloc(M * d * ring * s->kv_elem()));
@@ -611,7 +618,7 @@ int alloc_state(ava_engine* e, int rows, int ring, int keep, ava_state** out) {
 }
 
 int zero_state(ava_engine* e, ava_state* s) {
-    for (Dev* b : {&s->lif_v, &s->lif_s, &s->lif_a, &s->mem_f, &s->eng_n, &s->eng_start})
+    for (Dev* b : {&s->lif_v, &s->lif_s, &s->lif_a, &s->mem_f, &s->mem_s, &s->eng_n, &s->eng_start})
         if (b->p) CK(cudaMemsetAsync(b->p, 0, b->bytes, e->stream));
     CK(cudaStreamSynchronize(e->stream));
     return AVA_OK;
@@ -628,6 +635,8 @@ int copy_row(ava_engine* e, const ava_state* src, int src_row, ava_state* dst, i
         if (c.alif)
             CK(cudaMemcpyAsync(dst->lif_a.as<float>() + dn * d, src->lif_a.as<float>() + so * d, d * f, cudaMemcpyDeviceToDevice, e->stream));
         CK(cudaMemcpyAsync(dst->mem_f.as<float>() + dn * per, src->mem_f.as<float>() + so * per, per * f, cudaMemcpyDeviceToDevice, e->stream));
+        if (c.mem_momentum > 0.0f)
+            CK(cudaMemcpyAsync(dst->mem_s.as<float>() + dn * per, src->mem_s.as<float>() + so * per, per * f, cudaMemcpyDeviceToDevice, e->stream));
     }
     if (c.eng_block >= 0) {
         const size_t rowb = d * src->ring * src->kv_elem();
@@ -1096,7 +1105,7 @@ int64_t ava_engine_bytes(const ava_engine* e) {
 int64_t ava_state_bytes(const ava_state* s) {
     if (!s) return 0;
     int64_t n = 0;
-    for (const Dev* d : {&s->lif_v, &s->lif_s, &s->lif_a, &s->mem_f, &s->eng_k, &s->eng_v, &s->eng_n, &s->eng_start}) n += d->bytes;
+    for (const Dev* d : {&s->lif_v, &s->lif_s, &s->lif_a, &s->mem_f, &s->mem_s, &s->eng_k, &s->eng_v, &s->eng_n, &s->eng_start}) n += d->bytes;
     return n;
 }
 

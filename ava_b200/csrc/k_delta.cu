@@ -197,7 +197,9 @@ __global__ void __launch_bounds__(THREADS) mem_heads_kernel(const MemHeadsArgs a
 // is that of one token.  Per token the block needs the head's vectors (time-major [T][M][nh * hs]), all brought by
 // bulk copies that overlap the other pass: alpha, w and ah of token t land while its column sums run; e, q*alpha of
 // token t + 1 land while token t's update runs (the value slice is double-buffered: both passes read it).
-template <int CW>
+// MOM: the memory's momentum (second matrix S, src/model/fstep/arch.rs:281-323): rr gains p2 S (an exact zero kept for
+// the sign of zero), y gains (q M) S, F' = ((F alpha + w v^T) - ah rr^T) + S M, S' = ((S M + 0) + w v^T) - ah rr^T.
+template <int CW, bool MOM>
 __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsArgs a, int T) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int hs = a.hs, cr = a.chunk_rows, nchunk = hs / cr, d = a.nh * hs;
@@ -207,10 +209,13 @@ __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsAr
     float* vex = vqg + hs;
     float* vw = vex + hs;
     float* vah = vw + hs;
-    float* vvb = vah + hs;                          // [2][CW]
+    float* vqs = vah + hs;                          // [hs] q * M (momentum only)
+    float* vvb = vqs + (MOM ? hs : 0);              // [2][CW]
     float* rr = vvb + 2 * CW;
     float* t1 = rr + CW;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(t1 + CW);  // nchunk for the slice, then A (sums' vectors), B (update's)
+    float* tqv = t1 + CW;                           // [CW] (q M) S (momentum only)
+    float* tileS = tqv + CW;                        // [hs][CW] the momentum matrix's slice (momentum only)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tileS + (MOM ? (size_t)hs * CW : 0));  // slice chunks, then A, B
     uint64_t* barA = &bars[nchunk];
     uint64_t* barB = &bars[nchunk + 1];
 
@@ -221,7 +226,9 @@ __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsAr
     const int m = blockIdx.x / (slices * a.nh);
     const int c0 = slice * CW;
     const size_t ho = (size_t)head * hs;
-    float* gslice = a.f + (((size_t)m * a.nh + head) * hs * hs) + (size_t)slice * hs * CW;
+    const size_t goff = (((size_t)m * a.nh + head) * hs * hs) + (size_t)slice * hs * CW;
+    float* gslice = a.f + goff;
+    float* gsliceS = MOM ? a.s + goff : nullptr;
     const uint32_t chunk_bytes = (uint32_t)(cr * CW * sizeof(float));
     const uint32_t vb = (uint32_t)(hs * sizeof(float));
     const size_t Md = (size_t)a.M * d;
@@ -229,9 +236,10 @@ __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsAr
 
     auto fetch_a = [&](int t) {  // thread 0: what the column sums of token t read (+ its value slice)
         const size_t o = row_off(t);
-        mbar_expect_tx(barA, 2 * vb + (uint32_t)(CW * sizeof(float)));
+        mbar_expect_tx(barA, (MOM ? 3 : 2) * vb + (uint32_t)(CW * sizeof(float)));
         bulk_load(ve, a.e + o, vb, barA);
         bulk_load(vqg, a.qg + o, vb, barA);
+        if (MOM) bulk_load(vqs, a.qs + o, vb, barA);
         bulk_load(vvb + (t & 1) * CW, a.v + o + c0, (uint32_t)(CW * sizeof(float)), barA);
     };
     auto fetch_b = [&](int t) {  // thread 0: what the update of token t reads
@@ -250,11 +258,14 @@ __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsAr
     if (tid == 0) {
         fetch_a(0);
         for (int c = 0; c < nchunk; ++c) {
-            mbar_expect_tx(&bars[c], chunk_bytes);
+            mbar_expect_tx(&bars[c], (MOM ? 2 : 1) * chunk_bytes);
             bulk_load(tile + (size_t)c * cr * CW, gslice + (size_t)c * cr * CW, chunk_bytes, &bars[c]);
+            if (MOM) bulk_load(tileS + (size_t)c * cr * CW, gsliceS + (size_t)c * cr * CW, chunk_bytes, &bars[c]);
         }
     }
     bool ok = true;
+    const float mf = a.mom;
+    const float gsx = add(mul(0.0f, mf), 0.0f);  // the factor of the recall's zero row p2 = e * (0 * M + 0)
     for (int c = 0; c < nchunk; ++c) ok = mbar_wait(&bars[c], 0) && ok;  // the slice is resident from here on
     constexpr int QW = CW / 4, RPP = THREADS / QW;
     const int q4 = tid % QW, rg = tid / QW;
@@ -266,8 +277,9 @@ __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsAr
         const float* vv = vvb + (t & 1) * CW;
         if (tid < CW) {
             // the column sums, eight rows fetched one batch ahead of the two chains (chains start from -0: see above)
-            float r = -0.0f, s1 = -0.0f;
+            float r = -0.0f, s1 = -0.0f, z = -0.0f, tq = -0.0f;
             const float* p = tile + tid;
+            const float* ps = tileS + tid;
             float f[8], ev[8], gv[8];
             auto load8 = [&](int row, float* ff, float* ee, float* gg) {
 #pragma unroll
@@ -286,6 +298,14 @@ __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsAr
                     r = fma(f[i], ev[i], r);
                     s1 = fma(f[i], gv[i], s1);
                 }
+                if (MOM) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float sv = ps[(size_t)(row + i) * CW];
+                        z = fma(sv, mul(ev[i], gsx), z);
+                        tq = fma(sv, vqs[row + i], tq);
+                    }
+                }
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     f[i] = nf[i];
@@ -294,6 +314,10 @@ __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsAr
                 }
             }
             r = add(r, mul(1.0f, mul(0.0f, vv[tid])));
+            if (MOM) {
+                r = add(r, z);
+                tqv[tid] = tq;
+            }
             rr[tid] = r;
             t1[tid] = s1;
         }
@@ -303,7 +327,9 @@ __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsAr
         const size_t ro = row_off(t);
         if (tid < CW) {
             const size_t qo = ((size_t)t * a.M + m) * a.nh + head;
-            a.y[ro + c0 + tid] = sub(add(t1[tid], mul(a.qw[qo], vv[tid])), mul(a.qa[qo], rr[tid]));
+            float yv = sub(add(t1[tid], mul(a.qw[qo], vv[tid])), mul(a.qa[qo], rr[tid]));
+            if (MOM) yv = add(yv, tqv[tid]);
+            a.y[ro + c0 + tid] = yv;
         }
         ok = mbar_wait(barB, par) && ok;
         {
@@ -313,10 +339,26 @@ __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsAr
                 float4* p = reinterpret_cast<float4*>(tile + (size_t)row * CW) + q4;
                 float4 f = *p;
                 const float x = vex[row], w = vw[row], ah = vah[row];
-                f.x = sub(add(mul(f.x, x), mul(w, vb4.x)), mul(ah, rb4.x));
-                f.y = sub(add(mul(f.y, x), mul(w, vb4.y)), mul(ah, rb4.y));
-                f.z = sub(add(mul(f.z, x), mul(w, vb4.z)), mul(ah, rb4.z));
-                f.w = sub(add(mul(f.w, x), mul(w, vb4.w)), mul(ah, rb4.w));
+                if (!MOM) {
+                    f.x = sub(add(mul(f.x, x), mul(w, vb4.x)), mul(ah, rb4.x));
+                    f.y = sub(add(mul(f.y, x), mul(w, vb4.y)), mul(ah, rb4.y));
+                    f.z = sub(add(mul(f.z, x), mul(w, vb4.z)), mul(ah, rb4.z));
+                    f.w = sub(add(mul(f.w, x), mul(w, vb4.w)), mul(ah, rb4.w));
+                } else {
+                    float4* q = reinterpret_cast<float4*>(tileS + (size_t)row * CW) + q4;
+                    float4 sv = *q;
+                    const float fv[4] = {f.x, f.y, f.z, f.w}, s4[4] = {sv.x, sv.y, sv.z, sv.w};
+                    const float v4[4] = {vb4.x, vb4.y, vb4.z, vb4.w}, r4[4] = {rb4.x, rb4.y, rb4.z, rb4.w};
+                    float fo[4], so[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float wv = mul(w, v4[k]), ar = mul(ah, r4[k]), sm = mul(s4[k], mf);
+                        fo[k] = add(sub(add(mul(fv[k], x), wv), ar), sm);
+                        so[k] = sub(add(add(sm, 0.0f), wv), ar);
+                    }
+                    f = make_float4(fo[0], fo[1], fo[2], fo[3]);
+                    *q = make_float4(so[0], so[1], so[2], so[3]);
+                }
                 *p = f;
             }
         }
@@ -326,24 +368,35 @@ __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsAr
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
     if (tid == 0) {
-        for (int c = 0; c < nchunk; ++c) bulk_store(gslice + (size_t)c * cr * CW, tile + (size_t)c * cr * CW, chunk_bytes);
+        for (int c = 0; c < nchunk; ++c) {
+            bulk_store(gslice + (size_t)c * cr * CW, tile + (size_t)c * cr * CW, chunk_bytes);
+            if (MOM) bulk_store(gsliceS + (size_t)c * cr * CW, tileS + (size_t)c * cr * CW, chunk_bytes);
+        }
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     }
 }
 
-size_t smem_bytes_seq(int hs, int cw) { return ((size_t)hs * cw + 5 * (size_t)hs + 4 * (size_t)cw) * sizeof(float) + (MAX_CHUNKS + 2) * sizeof(uint64_t); }
+size_t smem_bytes_seq(int hs, int cw, bool mom = false) {
+    return ((size_t)hs * cw * (mom ? 2 : 1) + (mom ? 6 : 5) * (size_t)hs + 5 * (size_t)cw) * sizeof(float) + (MAX_CHUNKS + 2) * sizeof(uint64_t);
+}
 
 size_t smem_bytes(int hs, int cw) { return ((size_t)hs * cw + 5 * (size_t)hs + 3 * (size_t)cw) * sizeof(float) + (MAX_CHUNKS + 1) * sizeof(uint64_t); }
 
 }  // namespace
 
-bool mem_heads_tiling(int hs, int* cw, int* chunk_rows) {
+bool mem_heads_tiling(int hs, int* cw, int* chunk_rows, bool momentum) {
     if (hs % 16 != 0) return false;
-    // the widest slice (128-byte rows) that leaves room for two blocks per SM, else 64-byte rows
+    // the widest slice (128-byte rows) that leaves room for two blocks per SM, else 64-byte rows; with momentum two
+    // matrices' slices share the block and the slice only has to fit
     int w = 32;
-    if (hs % w != 0 || smem_bytes(hs, w) > 113 * 1024) w = 16;
-    if (hs % w != 0 || smem_bytes(hs, w) > 227 * 1024) return false;
+    if (momentum) {
+        if (hs % w != 0 || smem_bytes_seq(hs, w, true) > 227 * 1024) w = 16;
+        if (hs % w != 0 || smem_bytes_seq(hs, w, true) > 227 * 1024) return false;
+    } else {
+        if (hs % w != 0 || smem_bytes(hs, w) > 113 * 1024) w = 16;
+        if (hs % w != 0 || smem_bytes(hs, w) > 227 * 1024) return false;
+    }
     // chunks of at least 64 rows, at most MAX_CHUNKS of them, dividing the head
     int cr = hs <= 128 ? hs : 128;
     while (hs / cr > MAX_CHUNKS) cr *= 2;
@@ -365,15 +418,20 @@ void launch_mem_heads(cudaStream_t st, const MemHeadsArgs& a) {
     }
 }
 
+template <int CW, bool MOM>
+void launch_seq(cudaStream_t st, const MemHeadsArgs& a, int T, size_t smem, unsigned grid) {
+    cudaFuncSetAttribute(mem_heads_seq_kernel<CW, MOM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    mem_heads_seq_kernel<CW, MOM><<<grid, THREADS, smem, st>>>(a, T);
+}
+
 void launch_mem_heads_seq(cudaStream_t st, const MemHeadsArgs& a, int T) {
-    const size_t smem = smem_bytes_seq(a.hs, a.cw);
+    const bool mom = a.s != nullptr;
+    const size_t smem = smem_bytes_seq(a.hs, a.cw, mom);
     const unsigned grid = (unsigned)((size_t)a.M * a.nh * (a.hs / a.cw));
     if (a.cw == 32) {
-        cudaFuncSetAttribute(mem_heads_seq_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        mem_heads_seq_kernel<32><<<grid, THREADS, smem, st>>>(a, T);
+        if (mom) launch_seq<32, true>(st, a, T, smem, grid); else launch_seq<32, false>(st, a, T, smem, grid);
     } else {
-        cudaFuncSetAttribute(mem_heads_seq_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        mem_heads_seq_kernel<16><<<grid, THREADS, smem, st>>>(a, T);
+        if (mom) launch_seq<16, true>(st, a, T, smem, grid); else launch_seq<16, false>(st, a, T, smem, grid);
     }
 }
 

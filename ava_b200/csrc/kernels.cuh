@@ -71,12 +71,17 @@ struct MemPrepArgs {
     int M, d, hs, rank;
     // outputs [M, d] each, qw/qa [M, d / hs]
     float *e, *v, *w, *ah, *qg, *ex, *qw, *qa;
+    float* qs;           // [M, d] q * M when the memory has momentum, else nullptr
+    float mom;
     uint32_t* status;
 };
 void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a);
 
 struct MemHeadsArgs {
     float* f;            // this block's fast weights, slice-major: [M][nh][hs / cw][hs][cw] f32, updated in place
+    float* s;            // the momentum matrix, same layout, or nullptr (multi-token kernel only)
+    const float* qs;     // [M, nh * hs] q * M (momentum only)
+    float mom;           // M
     int M, nh, hs, cw, chunk_rows;
     const float *e, *v, *w, *ah, *qg, *ex;  // [M, nh * hs]
     const float *qw, *qa;                    // [M, nh]
@@ -89,7 +94,7 @@ void launch_mem_heads(cudaStream_t st, const MemHeadsArgs& a);
 // time-major [T][M][nh * hs], qw/qa [T][M][nh]; the state is read and written once for the whole chunk.
 void launch_mem_heads_seq(cudaStream_t st, const MemHeadsArgs& a, int T);
 // the column-slice width and the rows per bulk copy the kernel uses for a head size; false: head size not covered
-bool mem_heads_tiling(int hs, int* cw, int* chunk_rows);
+bool mem_heads_tiling(int hs, int* cw, int* chunk_rows, bool momentum = false);
 // natural [heads][hs][hs] to slice-major [heads][hs / cw][hs][cw] (to_slices 1) or back (0)
 void launch_retile(cudaStream_t st, const float* src, float* dst, int64_t heads, int hs, int cw, int to_slices);
 

@@ -159,7 +159,7 @@ int ava_op_mem_heads(int device, int32_t m, int32_t hs, const float* e, const fl
     Tmp dft;  // the slice-major copy the kernel works on
     OCK(up(dft, nullptr, fb));
     launch_retile(0, df.as<float>(), dft.as<float>(), m, hs, cw, 1);
-    a.f = dft.as<float>(); a.M = m; a.nh = 1; a.hs = hs; a.cw = cw; a.chunk_rows = rb;
+    a.f = dft.as<float>(); a.s = nullptr; a.qs = nullptr; a.mom = 0.0f; a.M = m; a.nh = 1; a.hs = hs; a.cw = cw; a.chunk_rows = rb;
     a.e = de.as<float>(); a.v = dv.as<float>(); a.w = dw.as<float>(); a.ah = dah.as<float>(); a.qg = dqg.as<float>(); a.ex = dex.as<float>();
     a.qw = dqw.as<float>(); a.qa = dqa.as<float>(); a.y = dy.as<float>(); a.status = dst.as<uint32_t>();
     launch_mem_heads(0, a);
@@ -188,7 +188,7 @@ int ava_debug_mem_heads_timeline(int device, int32_t m, int32_t hs, uint64_t* ou
     OCK(up(dtl, nullptr, (size_t)blocks * 6 * 8));
     OCK(cudaMemset(dv.p, 0, vb)); OCK(cudaMemset(dq.p, 0, (size_t)m * 4)); OCK(cudaMemset(df.p, 0, fb)); OCK(cudaMemset(dst.p, 0, 4));
     MemHeadsArgs a{};
-    a.f = df.as<float>(); a.M = m; a.nh = 1; a.hs = hs; a.cw = cw; a.chunk_rows = rb;
+    a.f = df.as<float>(); a.s = nullptr; a.qs = nullptr; a.mom = 0.0f; a.M = m; a.nh = 1; a.hs = hs; a.cw = cw; a.chunk_rows = rb;
     a.e = a.v = a.w = a.ah = a.qg = a.ex = dv.as<float>(); a.qw = a.qa = dq.as<float>(); a.y = dy.as<float>(); a.status = dst.as<uint32_t>();
     launch_mem_heads(0, a);  // warm
     a.timeline = dtl.as<unsigned long long>();

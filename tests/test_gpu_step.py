@@ -31,7 +31,7 @@ def orc_same_math(orc):
 
 
 STATE_NAMES = lambda cfg: [f"lif.{i}.{k}" for i in range(cfg["n_blocks"]) for k in (("v", "s", "a") if cfg["alif"] else ("v", "s"))] + \
-    [f"mem.{i}.f" for i in range(cfg["n_blocks"])] + (["eng.k", "eng.v"] if cfg["eng_block"] >= 0 else [])
+    [f"mem.{i}.{k}" for i in range(cfg["n_blocks"]) for k in (("f", "s") if cfg["mem_momentum"] > 0 else ("f",))] + (["eng.k", "eng.v"] if cfg["eng_block"] >= 0 else [])
 
 
 def assert_same_state(cfg, gs, os_, rows):
@@ -52,6 +52,7 @@ CONFIGS = {
     "one_head_bf16": dict(head_size=128, eng_head_size=64, eng_store_bf16=1),         # the benchmark's corner
     "binary_plain": dict(spikes=0, alif=0, theta=0, value_residual=0, dense=0, relu2=0, lif_scale=0, out_gate=0),
     "ternary_no_engram": dict(spikes=1, eng_block=-1, head_size=64),
+    "momentum": dict(mem_momentum=0.5, head_size=64),                                   # the released recipe's --mem-momentum
     "wide_rank2": dict(d=256, head_size=256, gate_rank=2, eng_block=0, hidden=512, kwta_k=64),
 }
 
@@ -129,7 +130,7 @@ def test_forward_with_state_equals_steps(orc_same_math):
     assert np.array_equal(bits(tail), bits(want[:, 6:]))
 
 
-@pytest.mark.parametrize("name", ["ava04_small", "one_head_bf16", "binary_plain"])
+@pytest.mark.parametrize("name", ["ava04_small", "one_head_bf16", "binary_plain", "momentum"])
 @pytest.mark.parametrize("chunk", [1, 5, 64])
 def test_chunked_prompt_equals_steps(orc_same_math, name, chunk):
     """Reading a prompt in chunks (token-parallel products, the recurrences in order inside their kernels) gives the
@@ -251,11 +252,11 @@ def test_errors_and_not_applicable(orc):
     with pytest.raises(engine.EngineError) as ei:
         engine.Model(cfg, missing)
     assert ei.value.code == engine.ERR_MISSING and "b1.mlp.w2" in str(ei.value)
-    # an option outside the engine: the reference's "does not apply" answer, with the reason
-    mom = config.tiny(mem_momentum=0.5)
+    # a shape outside the engine: the reference's "does not apply" answer, with the reason
+    odd = config.make(320, 120, 1, head_size=24, hidden=240, kwta_k=60)
     with pytest.raises(engine.NotApplicable) as ei:
-        engine.Model(mom, synth.model(mom, 0, "awake"))
-    assert "momentum" in str(ei.value)
+        engine.Model(odd, None).load({})
+    assert "multiples of 16" in str(ei.value)
 
 
 def test_nonfinite_gate_is_reported(orc):
