@@ -114,6 +114,9 @@ struct ava_engine {
     std::vector<Pending> prof_pending;
     std::map<std::string, std::pair<int64_t, double>> prof_total;  // kernel -> (launches, milliseconds)
 
+    int long_seg = 0;      // > 0: the engram is always read in segments of this many keys (else only when it must be)
+    Dev eng_partial;       // [rows][heads][segments][2 + hs] partial softmax statistics of the segmented read
+
     bool keep = false;
     std::map<std::pair<std::string, int>, std::unique_ptr<Dev>> debug;
     std::map<std::string, int64_t> debug_width;
@@ -461,15 +464,40 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
             ea.n = s->eng_n.as<int32_t>(); ea.start = s->eng_start.as<int32_t>();
             ea.M = rows; ea.d = d; ea.hs = c.eng_head_size; ea.cap = s->ring; ea.keep = s->keep; ea.bf16 = c.eng_store_bf16;
             ea.status = e->status.as<uint32_t>();
-            // the read is causal: token t sees the store as tokens 0..t left it, so the chunk goes token by token
+            // the read is causal: token t sees the store as tokens 0..t left it, so the chunk goes token by token.  A
+            // store that one block's shared memory can hold is read in one pass (the reference's order, bit for bit);
+            // a longer one, or any store when the segmented read is switched on, in segments merged afterwards.
+            const int enh = d / c.eng_head_size;
+            const bool segmented = e->long_seg > 0 || !engram_fits_one_block(d, c.eng_head_size, n_max);
+            const int seg_len = e->long_seg > 0 ? e->long_seg : 2048;
+            const int n_seg = engram_segments(n_max, seg_len);
+            if (segmented) {
+                const size_t need = (size_t)rows * enh * n_seg * (2 + c.eng_head_size) * sizeof(float);
+                if (e->eng_partial.bytes < need) CK(e->eng_partial.alloc(need));
+            }
             for (int t = 0; t < T; ++t) {
                 ea.qkv = e->eqkv.as<float>() + (size_t)t * rows * 3 * d;
                 ea.o = e->eo.as<float>() + (size_t)t * Rd;
-                prof_begin(e, "engram");
-                if (!launch_engram(st, ea, n_max))
-                    return e->fail(AVA_ERR_CAPACITY, "engram read over %d tokens does not fit this kernel's shared memory", n_max);
-                prof_end(e);
-                e->launches++;  // the small kernel that moves the counts on
+                if (!segmented) {
+                    prof_begin(e, "engram");
+                    if (!launch_engram(st, ea, n_max))
+                        return e->fail(AVA_ERR_CAPACITY, "engram read over %d tokens does not fit this kernel's shared memory", n_max);
+                    prof_end(e);
+                    e->launches++;  // the small kernel that moves the counts on
+                } else {
+                    prof_begin(e, "engram.append");
+                    launch_engram_append(st, ea);
+                    prof_end(e);
+                    prof_begin(e, "engram.partial");
+                    if (!launch_engram_partial(st, ea, seg_len, n_seg, e->eng_partial.as<float>()))
+                        return e->fail(AVA_ERR_CAPACITY, "engram segments of %d keys do not fit shared memory", seg_len);
+                    prof_end(e);
+                    prof_begin(e, "engram.combine");
+                    launch_engram_combine(st, e->eng_partial.as<float>(), rows, enh, c.eng_head_size, n_seg, ea.o);
+                    prof_end(e);
+                    launch_engram_trim(st, ea);
+                    e->launches += 2;
+                }
             }
             ea.o = e->eo.as<float>();
             dbg(e, "eng_o", i, ea.o, M, d);
@@ -1107,6 +1135,12 @@ int64_t ava_state_bytes(const ava_state* s) {
     int64_t n = 0;
     for (const Dev* d : {&s->lif_v, &s->lif_s, &s->lif_a, &s->mem_f, &s->mem_s, &s->eng_k, &s->eng_v, &s->eng_n, &s->eng_start}) n += d->bytes;
     return n;
+}
+
+int ava_engine_set_segmented_read(ava_engine* e, int32_t seg_len) {
+    if (!e || seg_len < 0 || (seg_len > 0 && seg_len < 8)) return AVA_ERR_ARG;
+    e->long_seg = seg_len;
+    return AVA_OK;
 }
 
 int ava_debug_keep(ava_engine* e, int32_t on) {

@@ -155,6 +155,152 @@ __global__ void __launch_bounds__(ENG_THREADS) engram_kernel(const EngramArgs a,
     }
 }
 
+// ---------------------------------------------------------------------------------------------------- long stores
+// For a store too long for one block's shared memory, or split by position over several GPUs, the read is taken in
+// segments: each block takes one (row, head group, segment of keys) and leaves per head the partial softmax statistics
+// (m, l, o[hs]): m the segment's largest score, l = sum exp(s - m), o = sum exp(s - m) v.  A second kernel merges the
+// partials of all segments (of all GPUs, once gathered) in position order:
+//     m = max m_p,  l = sum l_p e^(m_p - m),  o = sum o_p e^(m_p - m) / l.
+// Within a segment the sums keep the reference's order; across segments the order of additions differs from the
+// reference's single pass, so this path agrees with it to rounding (1e-6 relative), not bit for bit.
+// partial layout: [row][head][segment][2 + hs] f32.
+template <bool BF16>
+__global__ void __launch_bounds__(ENG_THREADS) engram_partial_kernel(const EngramArgs a, int hg, int seg_len, int n_seg_max, float* partial) {
+    extern __shared__ float sm[];
+    const int d = a.d, hs = a.hs, nh = d / hs, cap = a.cap;
+    const int groups = nh / hg;
+    const int seg = blockIdx.x % n_seg_max;
+    const int r = (blockIdx.x / n_seg_max) / groups, h0 = ((blockIdx.x / n_seg_max) % groups) * hg;
+    const int tid = threadIdx.x, T = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarp = T >> 5;
+    const float* qkv = a.qkv + (size_t)r * 3 * d;
+    const size_t row_base = (size_t)r * nh * cap * hs;
+    const int gd = hg * hs;
+    const int n_all = min(a.n[r], cap), start = a.start[r];
+    const int j0 = seg * seg_len, n = min(seg_len, n_all - j0);  // this segment's keys: logical positions j0 .. j0 + n
+    float* q = sm;          // [gd]
+    float* mx = q + gd;     // [hg]
+    float* sc = mx + hg;    // [hg][n]
+    auto out = [&](int g) { return partial + ((((size_t)r * nh + h0 + g) * n_seg_max + seg) * (2 + hs)); };
+    if (n <= 0) {           // an empty segment contributes nothing: m = -inf, l = 0
+        for (int c = tid; c < hg * (2 + hs); c += T) out(c / (2 + hs))[c % (2 + hs)] = (c % (2 + hs)) == 0 ? -INFINITY : 0.0f;
+        return;
+    }
+    for (int c = tid; c < gd; c += T) q[c] = qkv[h0 * hs + c];
+    __syncthreads();
+    const float scale = (float)(1.0 / sqrt((double)hs));
+    for (int idx = tid; idx < hg * n; idx += T) {
+        const int g = idx / n, j = idx % n;
+        int pj = start + j0 + j;
+        if (pj >= cap) pj -= cap;
+        const size_t o = row_base + ((size_t)(h0 + g) * cap + pj) * hs;
+        const float* qh = q + g * hs;
+        float s = 0.0f;
+        for (int x0 = 0; x0 < hs; x0 += 32) {
+            float kv[32];
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+                if (x0 + 8 * b < hs) kv_load8<BF16>(a.k, o + x0 + 8 * b, kv + 8 * b);
+#pragma unroll
+            for (int x = 0; x < 32; ++x) {
+                if (x0 + x < hs) s = (x0 + x == 0) ? mul(kv[0], qh[0]) : fma(kv[x], qh[x0 + x], s);
+            }
+        }
+        sc[(size_t)g * n + j] = add(mul(s, scale), 0.0f);
+    }
+    __syncthreads();
+    for (int g = warp; g < hg; g += nwarp) {
+        float m = -INFINITY;
+        for (int j = lane; j < n; j += 32) m = fmaxf(m, sc[(size_t)g * n + j]);
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) mx[g] = m;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < hg * n; idx += T) sc[idx] = expf_(sub(sc[idx], mx[idx / n]));
+    __syncthreads();
+    for (int g = tid; g < hg; g += T) {
+        float s = 0.0f;
+        const float* p = sc + (size_t)g * n;
+        for (int j = 0; j < n; ++j) s = add(s, p[j]);
+        out(g)[0] = mx[g];
+        out(g)[1] = s;
+    }
+    for (int c = tid; c < gd; c += T) {
+        const int g = c / hs, dd = c % hs;
+        const float* p = sc + (size_t)g * n;
+        const size_t hb = row_base + (size_t)(h0 + g) * cap * hs + dd;
+        auto V = [&](int j) {
+            int pj = start + j0 + j;
+            if (pj >= cap) pj -= cap;
+            return kv_load<BF16>(a.v, hb + (size_t)pj * hs);
+        };
+        float o = -0.0f;
+        int j = 0;
+        for (; j + 16 <= n; j += 16) {
+            float t[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) t[i] = V(j + i);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o = fma(t[i], p[j + i], o);
+        }
+        for (; j < n; ++j) o = fma(V(j), p[j], o);
+        out(g)[2 + dd] = o;
+    }
+}
+
+// partial [row][head][n_part][2 + hs] -> o [row][nh * hs]; one thread per output channel walks the parts in order
+__global__ void engram_combine_kernel(const float* __restrict__ partial, int M, int nh, int hs, int n_part, float* __restrict__ o) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= M * nh * hs) return;
+    const int dd = i % hs, rh = i / hs;  // rh = row * nh + head
+    const float* p = partial + (size_t)rh * n_part * (2 + hs);
+    float m = -INFINITY;
+    for (int k = 0; k < n_part; ++k) m = fmaxf(m, p[(size_t)k * (2 + hs)]);
+    float l = 0.0f, acc = 0.0f;
+    for (int k = 0; k < n_part; ++k) {
+        const float* pk = p + (size_t)k * (2 + hs);
+        if (pk[1] == 0.0f) continue;  // an empty part
+        const float w = expf_(sub(pk[0], m));
+        l = add(l, mul(pk[1], w));
+        acc = add(acc, mul(pk[2 + dd], w));
+    }
+    o[i] = div(acc, l);
+}
+
+// this token's key and value join the store (the long path appends first, then reads every segment)
+template <bool BF16>
+__global__ void engram_append_kernel(const EngramArgs a) {
+    const int d = a.d, hs = a.hs, nh = d / hs, cap = a.cap;
+    const int r = blockIdx.x;
+    const int n0 = a.n[r];
+    if (n0 >= cap) {
+        if (threadIdx.x == 0) atomicOr(a.status, ST_ENGRAM_FULL);
+        return;
+    }
+    int slot = a.start[r] + n0;
+    if (slot >= cap) slot -= cap;
+    const float* qkv = a.qkv + (size_t)r * 3 * d;
+    const size_t row_base = (size_t)r * nh * cap * hs;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        const size_t o = row_base + ((size_t)(c / hs) * cap + slot) * hs + c % hs;
+        kv_store<BF16>(a.k, o, qkv[d + c]);
+        kv_store<BF16>(a.v, o, qkv[2 * d + c]);
+    }
+}
+// n <- n + 1 after an append (the partial kernels read n as the number of keys present)
+__global__ void engram_count_kernel(int32_t* n, int M, int cap) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < M && n[r] < cap) n[r] += 1;
+}
+// a capped store drops its oldest tokens after the read
+__global__ void engram_trim_kernel(int32_t* n, int32_t* start, int M, int cap, int keep) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= M) return;
+    if (n[r] > keep) {
+        start[r] = (start[r] + (n[r] - keep)) % cap;
+        n[r] = keep;
+    }
+}
+
 // after the read: the count moves on; a capped store drops its oldest tokens (src/state.rs:526-538)
 __global__ void engram_advance_kernel(int32_t* n, int32_t* start, int M, int cap, int keep) {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
@@ -172,14 +318,13 @@ __global__ void engram_advance_kernel(int32_t* n, int32_t* start, int M, int cap
 
 }  // namespace
 
+static int head_group(int nh, int hs);
+
 bool launch_engram(cudaStream_t st, const EngramArgs& a, int n_max) {
     const int nh = a.d / a.hs;
     if (a.hs % 8 != 0) return false;
     // heads per block: as many as give each thread one output channel, dividing the head count
-    int hg = ENG_THREADS / a.hs;
-    if (hg < 1) hg = 1;
-    if (hg > nh) hg = nh;
-    while (nh % hg != 0) --hg;
+    const int hg = head_group(nh, a.hs);
     const size_t smem = ((size_t)hg * a.hs + 2 * hg + (size_t)hg * n_max) * sizeof(float);
     if (smem > 227 * 1024 - 64) return false;
     const unsigned grid = (unsigned)(a.M * (nh / hg));
@@ -192,6 +337,52 @@ bool launch_engram(cudaStream_t st, const EngramArgs& a, int n_max) {
     }
     engram_advance_kernel<<<(a.M + 127) / 128, 128, 0, st>>>(a.n, a.start, a.M, a.cap, a.keep);
     return true;
+}
+
+static int head_group(int nh, int hs) {
+    int hg = ENG_THREADS / hs;
+    if (hg < 1) hg = 1;
+    if (hg > nh) hg = nh;
+    while (nh % hg != 0) --hg;
+    return hg;
+}
+
+void launch_engram_append(cudaStream_t st, const EngramArgs& a) {
+    if (a.bf16) engram_append_kernel<true><<<a.M, 256, 0, st>>>(a); else engram_append_kernel<false><<<a.M, 256, 0, st>>>(a);
+    engram_count_kernel<<<(a.M + 127) / 128, 128, 0, st>>>(a.n, a.M, a.cap);
+}
+
+void launch_engram_trim(cudaStream_t st, const EngramArgs& a) {
+    engram_trim_kernel<<<(a.M + 127) / 128, 128, 0, st>>>(a.n, a.start, a.M, a.cap, a.keep);
+}
+
+bool engram_fits_one_block(int d, int hs, int n_max) {
+    const int hg = head_group(d / hs, hs);
+    return ((size_t)hg * hs + 2 * hg + (size_t)hg * n_max) * sizeof(float) <= 227 * 1024 - 64;
+}
+
+int engram_segments(int n_max, int seg_len) { return (n_max + seg_len - 1) / seg_len; }
+
+bool launch_engram_partial(cudaStream_t st, const EngramArgs& a, int seg_len, int n_seg, float* partial) {
+    const int nh = a.d / a.hs;
+    if (a.hs % 8 != 0 || n_seg <= 0) return false;
+    const int hg = head_group(nh, a.hs);
+    const size_t smem = ((size_t)hg * a.hs + hg + (size_t)hg * seg_len) * sizeof(float);
+    if (smem > 227 * 1024 - 64) return false;
+    const unsigned grid = (unsigned)((size_t)a.M * (nh / hg) * n_seg);
+    if (a.bf16) {
+        cudaFuncSetAttribute(engram_partial_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        engram_partial_kernel<true><<<grid, ENG_THREADS, smem, st>>>(a, hg, seg_len, n_seg, partial);
+    } else {
+        cudaFuncSetAttribute(engram_partial_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        engram_partial_kernel<false><<<grid, ENG_THREADS, smem, st>>>(a, hg, seg_len, n_seg, partial);
+    }
+    return true;
+}
+
+void launch_engram_combine(cudaStream_t st, const float* partial, int M, int nh, int hs, int n_part, float* o) {
+    const int n = M * nh * hs;
+    engram_combine_kernel<<<(n + 127) / 128, 128, 0, st>>>(partial, M, nh, hs, n_part, o);
 }
 
 }  // namespace ava

@@ -113,6 +113,16 @@ struct EngramArgs {
 // returns false when n_max keys do not fit the kernel's shared memory
 bool launch_engram(cudaStream_t st, const EngramArgs& a, int n_max);
 
+// The long-store form: append, then per (row, head, segment of seg_len keys) partial softmax statistics
+// [row][head][n_seg][2 + hs] = (max, sum, unnormalised mix), merged in position order by the combine kernel (which
+// also merges the parts gathered from several GPUs).  Agrees with the single-pass read to rounding, not bit for bit.
+void launch_engram_append(cudaStream_t st, const EngramArgs& a);
+void launch_engram_trim(cudaStream_t st, const EngramArgs& a);
+int engram_segments(int n_max, int seg_len);
+bool engram_fits_one_block(int d, int hs, int n_max);
+bool launch_engram_partial(cudaStream_t st, const EngramArgs& a, int seg_len, int n_seg, float* partial);
+void launch_engram_combine(cudaStream_t st, const float* partial, int M, int nh, int hs, int n_part, float* o);
+
 void launch_kwta(cudaStream_t st, const float* u, int M, int n, int k, int relu2, float* a);
 // x <- x + sum_j streams[j] * w[j] over the n_streams streams (the last one is x itself, stored first)
 void launch_dense_mix(cudaStream_t st, float* x, float* streams, const float* w, int n_streams, int64_t MD);

@@ -79,6 +79,7 @@ def lib() -> C.CDLL:
         "ava_engine_launches": ([vp], C.c_int64),
         "ava_engine_bytes": ([vp], C.c_int64),
         "ava_state_bytes": ([vp], C.c_int64),
+        "ava_engine_set_segmented_read": ([vp, C.c_int32], C.c_int),
         "ava_prof_enable": ([vp, C.c_int32], C.c_int),
         "ava_prof_read": ([vp, C.c_char_p, C.POINTER(C.c_int64), C.POINTER(C.c_double)], C.c_int),
         "ava_prof_names": ([vp, C.c_char_p, C.c_int32], C.c_int),
@@ -113,7 +114,7 @@ EXPORTS = ("ava_engine_create ava_engine_destroy ava_last_error ava_engine_set_f
            "ava_state_rows ava_state_select ava_state_cat ava_state_seen ava_state_len ava_state_export "
            "ava_state_import ava_step ava_step_greedy ava_forward_with_state ava_step_device ava_prefill_device ava_sync "
            "ava_engine_stream ava_engine_launches ava_engine_bytes ava_state_bytes ava_debug_keep ava_debug_width "
-           "ava_debug_get ava_prof_enable ava_prof_read ava_prof_names ava_op_q8_matmul ava_op_q8_event_matmul ava_debug_mem_heads_timeline ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
+           "ava_debug_get ava_engine_set_segmented_read ava_prof_enable ava_prof_read ava_prof_names ava_op_q8_matmul ava_op_q8_event_matmul ava_debug_mem_heads_timeline ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
            "ava_host_expf ava_host_logf ava_host_rsqrtf ava_op_math").split()
 
 
@@ -219,6 +220,10 @@ class Model:
     @property
     def nbytes(self) -> int:
         return lib().ava_engine_bytes(self.h)
+
+    def set_segmented_read(self, seg_len: int):
+        """seg_len > 0: the engram is always read in segments of that many keys (the long-context / split-store path)."""
+        self._check(lib().ava_engine_set_segmented_read(self.h, seg_len))
 
     def prof_enable(self, on: bool):
         self._check(lib().ava_prof_enable(self.h, int(on)))

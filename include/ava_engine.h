@@ -133,6 +133,13 @@ int64_t ava_engine_launches(const ava_engine* e);
 int64_t ava_engine_bytes(const ava_engine* e);
 int64_t ava_state_bytes(const ava_state* s);
 
+/* No counterpart in the reference (its engram read materialises all scores on the CPU, src/memory.rs:664-692).  A
+ * store too long for one block's shared memory (about 14 k tokens at 12 heads of 64) is read in segments whose partial
+ * softmax statistics (max, sum, mix) are merged afterwards; seg_len > 0 makes every read take that path with segments
+ * of seg_len keys (0: only when it must).  The segmented read agrees with the one-pass read to rounding, not bit for
+ * bit. */
+int ava_engine_set_segmented_read(ava_engine* e, int32_t seg_len);
+
 /* Section clock, as the reference's fused step keeps one (`take_secs`, src/model/fstep/arch.rs:131-165, switched by
  * `int8::set_mm_prof`, src/int8.rs:635-640): with it on, every kernel launch is bracketed by CUDA events on the
  * engine's stream.  ava_prof_read waits for the stream and returns one kernel's launches and total milliseconds since
