@@ -149,6 +149,9 @@ struct ava_state {
     Dev eng_n, eng_start;     // [rows] i32
     std::vector<int32_t> n_host, start_host;
     std::vector<int64_t> seen;
+    // a store split by position over several GPUs: this state keeps the tokens rank `shard_rank` owns
+    int shard_world = 0, shard_rank = 0;
+    int64_t shard_block = 0, shard_pos = 0;
     size_t kv_elem() const { return e->cfg.eng_store_bf16 ? 2 : 4; }
 };
 
@@ -342,7 +345,10 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
 // token's [T][rows][vocab].  With T > 1 the products, norms, gates and the MLP run over all T x rows token-rows at
 // once, and the three recurrences walk the chunk in order inside their kernels: the LIF scan, the fast-weight pass
 // with its slice resident in shared memory, the engram read token by token.  Every value is the one T single steps give.
-int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits, uint32_t* next, bool want_logits, int T = 1, bool all_logits = false) {
+enum StepPhase { PHASE_ALL = 0, PHASE_BEGIN = 1, PHASE_END = 2 };  // BEGIN stops once the engram's q,k,v exist; END resumes after its read
+
+int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits, uint32_t* next, bool want_logits, int T = 1, bool all_logits = false,
+                StepPhase phase = PHASE_ALL) {
     const ava_config& c = e->cfg;
     const int rows = s->rows, d = c.d, L = c.n_blocks, nh = e->nh(), hs = c.head_size, H = c.hidden;
     const int M = rows * T;  // token-rows, time-major: token t of row r is token-row t * rows + r
@@ -355,7 +361,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
 
     // the engram's capacity is checked on the host's mirror of the counts before anything moves
     int n_max = 0;
-    if (c.eng_block >= 0) {
+    if (c.eng_block >= 0 && phase == PHASE_ALL) {
         for (int r = 0; r < rows; ++r) {
             if (s->keep == s->ring && s->n_host[r] + T > s->ring)
                 return e->fail(AVA_ERR_CAPACITY, "engram store of row %d is full (%d tokens)", r, s->ring);
@@ -363,12 +369,15 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         }
     }
 
-    prof_begin(e, "embed");
-    launch_embed(st, e->tok_emb.as<float>(), tok, M, d, c.vocab, x, streams, e->status.as<uint32_t>());
-    prof_end(e);
-    dbg(e, "x_in", -1, x, M, d);
-    for (int i = 0; i < L; ++i) {
+    if (phase != PHASE_END) {
+        prof_begin(e, "embed");
+        launch_embed(st, e->tok_emb.as<float>(), tok, M, d, c.vocab, x, streams, e->status.as<uint32_t>());
+        prof_end(e);
+        dbg(e, "x_in", -1, x, M, d);
+    }
+    for (int i = phase == PHASE_END ? c.eng_block : 0; i < L; ++i) {
         BlockDev& b = *e->blocks[i];
+        if (!(phase == PHASE_END && i == c.eng_block)) {
         // ---- the spiking memory
         prof_begin(e, "rmsnorm");
         launch_rmsnorm(st, x, b.mem_norm.as<float>(), M, d, h);
@@ -450,14 +459,22 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         dbg(e, "y", i, e->y.as<float>(), M, d);
         gemm(e, "gemm.wo", e->y.as<float>(), d, b.wo, x, d, M, EPI_ADD);
         dbg(e, "x_mem", i, x, M, d);
+        }
 
         // ---- the engram
         if (i == c.eng_block) {
-            prof_begin(e, "rmsnorm");
-            launch_rmsnorm(st, x, b.eng_norm.as<float>(), M, d, h);
-            prof_end(e);
-            gemm(e, "gemm.eng_qkv", h, d, b.eqkv, e->eqkv.as<float>(), 3 * d, M, EPI_STORE);
-            dbg(e, "eng_qkv", i, e->eqkv.as<float>(), M, 3 * d);
+            if (phase != PHASE_END) {
+                prof_begin(e, "rmsnorm");
+                launch_rmsnorm(st, x, b.eng_norm.as<float>(), M, d, h);
+                prof_end(e);
+                gemm(e, "gemm.eng_qkv", h, d, b.eqkv, e->eqkv.as<float>(), 3 * d, M, EPI_STORE);
+                dbg(e, "eng_qkv", i, e->eqkv.as<float>(), M, 3 * d);
+            }
+            if (phase == PHASE_BEGIN) {
+                const cudaError_t le0 = cudaGetLastError();
+                if (le0 != cudaSuccess) return e->cuda_fail(le0, "kernel launch");
+                return AVA_OK;
+            }
             EngramArgs ea{};
             ea.qkv = e->eqkv.as<float>();
             ea.k = s->eng_k.p; ea.v = s->eng_v.p;
@@ -475,7 +492,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
                 const size_t need = (size_t)rows * enh * n_seg * (2 + c.eng_head_size) * sizeof(float);
                 if (e->eng_partial.bytes < need) CK(e->eng_partial.alloc(need));
             }
-            for (int t = 0; t < T; ++t) {
+            for (int t = 0; t < T && phase == PHASE_ALL; ++t) {
                 ea.qkv = e->eqkv.as<float>() + (size_t)t * rows * 3 * d;
                 ea.o = e->eo.as<float>() + (size_t)t * Rd;
                 if (!segmented) {
@@ -539,7 +556,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         }
     }
     // the host's mirror of the engram counts moves as the kernels move them
-    if (c.eng_block >= 0)
+    if (c.eng_block >= 0 && phase == PHASE_ALL)
         for (int r = 0; r < rows; ++r)
             for (int t = 0; t < T; ++t) {
                 const int n = s->n_host[r] + 1;
@@ -1109,6 +1126,78 @@ int ava_prefill_device(ava_engine* e, ava_state* s, const uint32_t* tok_device, 
             return rc;
     }
     return AVA_OK;
+}
+
+// ---- the engram store split by position over several GPUs (one long sequence) ---------------------------------
+int ava_state_set_kv_shard(ava_state* s, int32_t rank, int32_t world, int64_t block, int64_t position) {
+    if (!s || world < 1 || rank < 0 || rank >= world || block < 1 || position < 0) return AVA_ERR_ARG;
+    if (s->e->cfg.eng_block < 0) return s->e->fail(AVA_ERR_ARG, "the model has no engram");
+    if (s->e->cfg.eng_cap > 0) return s->e->fail(AVA_NOT_APPLICABLE, "a capped store is not split");
+    s->shard_world = world;
+    s->shard_rank = rank;
+    s->shard_block = block;
+    s->shard_pos = position;
+    return AVA_OK;
+}
+
+int32_t ava_shard_parts(const ava_engine* e, const ava_state* s) {
+    if (!e || !s) return -1;
+    return engram_segments(s->ring, e->long_seg > 0 ? e->long_seg : 2048);
+}
+
+int ava_split_step_begin(ava_engine* e, ava_state* s, const uint32_t* tok_device, float* qkv_device) {
+    int rc = check_pair(e, s);
+    if (rc) return rc;
+    if (!tok_device || !qkv_device || e->cfg.eng_block < 0) return e->fail(AVA_ERR_ARG, "bad arguments");
+    if ((rc = step_device(e, s, tok_device, nullptr, nullptr, false, 1, false, PHASE_BEGIN))) return rc;
+    CK(cudaMemcpyAsync(qkv_device, e->eqkv.p, (size_t)s->rows * 3 * e->cfg.d * sizeof(float), cudaMemcpyDeviceToDevice, e->stream));
+    return AVA_OK;
+}
+
+int ava_shard_partial(ava_engine* e, ava_state* s, const float* qkv_device, float* partial_device) {
+    int rc = check_pair(e, s);
+    if (rc) return rc;
+    if (!qkv_device || !partial_device || s->shard_world < 1) return e->fail(AVA_ERR_ARG, "the state has no shard set");
+    const ava_config& c = e->cfg;
+    const int rows = s->rows, d = c.d;
+    EngramArgs ea{};
+    ea.qkv = qkv_device;
+    ea.k = s->eng_k.p; ea.v = s->eng_v.p;
+    ea.n = s->eng_n.as<int32_t>(); ea.start = s->eng_start.as<int32_t>();
+    ea.M = rows; ea.d = d; ea.hs = c.eng_head_size; ea.cap = s->ring; ea.keep = s->keep; ea.bf16 = c.eng_store_bf16;
+    ea.status = e->status.as<uint32_t>();
+    const int owner = (int)std::min<int64_t>(s->shard_pos / s->shard_block, s->shard_world - 1);
+    if (owner == s->shard_rank) {
+        for (int r = 0; r < rows; ++r)
+            if (s->n_host[r] >= s->ring) return e->fail(AVA_ERR_CAPACITY, "this rank's part of the engram store is full (%d tokens)", s->ring);
+        prof_begin(e, "engram.append");
+        launch_engram_append(e->stream, ea);
+        prof_end(e);
+        e->launches++;
+        for (int r = 0; r < rows; ++r) s->n_host[r] += 1;
+    }
+    s->shard_pos += 1;
+    const int seg_len = e->long_seg > 0 ? e->long_seg : 2048;
+    const int n_seg = engram_segments(s->ring, seg_len);
+    prof_begin(e, "engram.partial");
+    if (!launch_engram_partial(e->stream, ea, seg_len, n_seg, partial_device))
+        return e->fail(AVA_ERR_CAPACITY, "engram segments of %d keys do not fit shared memory", seg_len);
+    prof_end(e);
+    const cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) return e->cuda_fail(le, "kernel launch");
+    return AVA_OK;
+}
+
+int ava_split_step_end(ava_engine* e, ava_state* s, const float* gathered_device, int32_t world, float* logits_device, uint32_t* next_device) {
+    int rc = check_pair(e, s);
+    if (rc) return rc;
+    if (!gathered_device || world < 1) return e->fail(AVA_ERR_ARG, "bad arguments");
+    const ava_config& c = e->cfg;
+    const int seg_len = e->long_seg > 0 ? e->long_seg : 2048;
+    prof_begin(e, "engram.combine");
+    launch_engram_combine(e->stream, gathered_device, s->rows, c.d / c.eng_head_size, c.eng_head_size, engram_segments(s->ring, seg_len), e->eo.as<float>(), world);
+    prof_end(e);
+    return step_device(e, s, nullptr, logits_device, next_device, logits_device != nullptr, 1, false, PHASE_END);
 }
 
 void* ava_engine_stream(ava_engine* e) { return e ? (void*)e->stream : nullptr; }

@@ -247,22 +247,26 @@ __global__ void __launch_bounds__(ENG_THREADS) engram_partial_kernel(const Engra
     }
 }
 
-// partial [row][head][n_part][2 + hs] -> o [row][nh * hs]; one thread per output channel walks the parts in order
-__global__ void engram_combine_kernel(const float* __restrict__ partial, int M, int nh, int hs, int n_part, float* __restrict__ o) {
+// partial [group][row][head][n_part][2 + hs] -> o [row][nh * hs]; one thread per output channel walks the groups (the
+// GPUs a store is split over, in position order) and within each its parts in order
+__global__ void engram_combine_kernel(const float* __restrict__ partial, int M, int nh, int hs, int n_part, int n_groups, float* __restrict__ o) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= M * nh * hs) return;
     const int dd = i % hs, rh = i / hs;  // rh = row * nh + head
-    const float* p = partial + (size_t)rh * n_part * (2 + hs);
+    const size_t part = 2 + hs, gstride = (size_t)M * nh * n_part * part;
+    const float* p = partial + (size_t)rh * n_part * part;
     float m = -INFINITY;
-    for (int k = 0; k < n_part; ++k) m = fmaxf(m, p[(size_t)k * (2 + hs)]);
+    for (int g = 0; g < n_groups; ++g)
+        for (int k = 0; k < n_part; ++k) m = fmaxf(m, p[g * gstride + (size_t)k * part]);
     float l = 0.0f, acc = 0.0f;
-    for (int k = 0; k < n_part; ++k) {
-        const float* pk = p + (size_t)k * (2 + hs);
-        if (pk[1] == 0.0f) continue;  // an empty part
-        const float w = expf_(sub(pk[0], m));
-        l = add(l, mul(pk[1], w));
-        acc = add(acc, mul(pk[2 + dd], w));
-    }
+    for (int g = 0; g < n_groups; ++g)
+        for (int k = 0; k < n_part; ++k) {
+            const float* pk = p + g * gstride + (size_t)k * part;
+            if (pk[1] == 0.0f) continue;  // an empty part
+            const float w = expf_(sub(pk[0], m));
+            l = add(l, mul(pk[1], w));
+            acc = add(acc, mul(pk[2 + dd], w));
+        }
     o[i] = div(acc, l);
 }
 
@@ -380,9 +384,9 @@ bool launch_engram_partial(cudaStream_t st, const EngramArgs& a, int seg_len, in
     return true;
 }
 
-void launch_engram_combine(cudaStream_t st, const float* partial, int M, int nh, int hs, int n_part, float* o) {
+void launch_engram_combine(cudaStream_t st, const float* partial, int M, int nh, int hs, int n_part, float* o, int n_groups) {
     const int n = M * nh * hs;
-    engram_combine_kernel<<<(n + 127) / 128, 128, 0, st>>>(partial, M, nh, hs, n_part, o);
+    engram_combine_kernel<<<(n + 127) / 128, 128, 0, st>>>(partial, M, nh, hs, n_part, n_groups, o);
 }
 
 }  // namespace ava

@@ -121,7 +121,7 @@ void launch_engram_trim(cudaStream_t st, const EngramArgs& a);
 int engram_segments(int n_max, int seg_len);
 bool engram_fits_one_block(int d, int hs, int n_max);
 bool launch_engram_partial(cudaStream_t st, const EngramArgs& a, int seg_len, int n_seg, float* partial);
-void launch_engram_combine(cudaStream_t st, const float* partial, int M, int nh, int hs, int n_part, float* o);
+void launch_engram_combine(cudaStream_t st, const float* partial, int M, int nh, int hs, int n_part, float* o, int n_groups = 1);
 
 void launch_kwta(cudaStream_t st, const float* u, int M, int n, int k, int relu2, float* a);
 // x <- x + sum_j streams[j] * w[j] over the n_streams streams (the last one is x itself, stored first)

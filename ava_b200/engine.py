@@ -74,6 +74,11 @@ def lib() -> C.CDLL:
         "ava_forward_with_state": ([vp, vp, u32p, C.c_int32, C.c_int32, fp], C.c_int),
         "ava_step_device": ([vp, vp, vp, vp, vp], C.c_int),
         "ava_prefill_device": ([vp, vp, vp, C.c_int32, C.c_int32, vp, vp], C.c_int),
+        "ava_state_set_kv_shard": ([vp, C.c_int32, C.c_int32, C.c_int64, C.c_int64], C.c_int),
+        "ava_shard_parts": ([vp, vp], C.c_int32),
+        "ava_split_step_begin": ([vp, vp, vp, vp], C.c_int),
+        "ava_shard_partial": ([vp, vp, vp, vp], C.c_int),
+        "ava_split_step_end": ([vp, vp, vp, C.c_int32, vp, vp], C.c_int),
         "ava_sync": ([vp], C.c_int),
         "ava_engine_stream": ([vp], vp),
         "ava_engine_launches": ([vp], C.c_int64),
@@ -112,7 +117,7 @@ def lib() -> C.CDLL:
 EXPORTS = ("ava_engine_create ava_engine_destroy ava_last_error ava_engine_set_f32 ava_engine_set_q8 "
            "ava_engine_set_q8_from_f32 ava_engine_finalize ava_engine_blocker ava_state_new ava_state_destroy "
            "ava_state_rows ava_state_select ava_state_cat ava_state_seen ava_state_len ava_state_export "
-           "ava_state_import ava_step ava_step_greedy ava_forward_with_state ava_step_device ava_prefill_device ava_sync "
+           "ava_state_import ava_step ava_step_greedy ava_forward_with_state ava_step_device ava_prefill_device ava_state_set_kv_shard ava_shard_parts ava_split_step_begin ava_shard_partial ava_split_step_end ava_sync "
            "ava_engine_stream ava_engine_launches ava_engine_bytes ava_state_bytes ava_debug_keep ava_debug_width "
            "ava_debug_get ava_engine_set_segmented_read ava_prof_enable ava_prof_read ava_prof_names ava_op_q8_matmul ava_op_q8_event_matmul ava_debug_mem_heads_timeline ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
            "ava_host_expf ava_host_logf ava_host_rsqrtf ava_op_math").split()

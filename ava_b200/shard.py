@@ -34,3 +34,9 @@ def max_over_ranks(value: float, dist=None, device=None) -> float:
     t = torch.tensor([value], dtype=torch.float64, device=device or "cpu")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
+
+
+def kv_owner(position: int, block: int, world: int) -> int:
+    """The rank that keeps token `position` of one long sequence whose engram store is split by position: contiguous
+    blocks of `block` positions, the tail (the decoded tokens) on the last rank."""
+    return min(position // block, world - 1)

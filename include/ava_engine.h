@@ -140,6 +140,24 @@ int64_t ava_state_bytes(const ava_state* s);
  * bit. */
 int ava_engine_set_segmented_read(ava_engine* e, int32_t seg_len);
 
+/* ---- one long sequence with its engram store split by position over several GPUs ------------------------------
+ * No counterpart in the reference (one device, src/memory.rs:664-692).  Each GPU runs one process with its own engine
+ * and a state whose store keeps only the tokens it owns: position p belongs to rank min(p / block, world - 1).  The
+ * membranes and fast weights are stepped on rank 0 only.  Per token:
+ *   rank 0     ava_split_step_begin   blocks up to the engram's q,k,v; copies them [rows, 3 d] to qkv_device
+ *   (caller)   broadcast qkv from rank 0 (NCCL)
+ *   all ranks  ava_shard_partial      the owner appends k,v; every rank leaves the partial softmax statistics of its
+ *                                     part: [rows][heads][ava_shard_parts()][2 + head size] f32 (max, sum, mix)
+ *   (caller)   all-gather the partials (NCCL) into [world][...]
+ *   rank 0     ava_split_step_end     merges them in position order and finishes the step
+ * The merged read agrees with the one-pass read to rounding (the additions are grouped differently), not bit for bit.
+ * Every pointer is device memory; work is queued on the engine's stream (the caller orders its NCCL calls after it). */
+int ava_state_set_kv_shard(ava_state* s, int32_t rank, int32_t world, int64_t block, int64_t position);
+int32_t ava_shard_parts(const ava_engine* e, const ava_state* s);
+int ava_split_step_begin(ava_engine* e, ava_state* s, const uint32_t* tok_device, float* qkv_device);
+int ava_shard_partial(ava_engine* e, ava_state* s, const float* qkv_device, float* partial_device);
+int ava_split_step_end(ava_engine* e, ava_state* s, const float* gathered_device, int32_t world, float* logits_device, uint32_t* next_device);
+
 /* Section clock, as the reference's fused step keeps one (`take_secs`, src/model/fstep/arch.rs:131-165, switched by
  * `int8::set_mm_prof`, src/int8.rs:635-640): with it on, every kernel launch is bracketed by CUDA events on the
  * engine's stream.  ava_prof_read waits for the stream and returns one kernel's launches and total milliseconds since
