@@ -55,6 +55,7 @@ struct Dev {
 struct QMat {
     int din = 0, dout = 0;
     Dev q, scale;
+    Dev wt;  // fast-products mode only: the weights as bf16 [dout][din]
     const int8_t* qp() const { return q.as<int8_t>(); }
     const float* sp() const { return scale.as<float>(); }
 };
@@ -113,6 +114,9 @@ struct ava_engine {
     struct Pending { const char* cls; cudaEvent_t a, b; };
     std::vector<Pending> prof_pending;
     std::map<std::string, std::pair<int64_t, double>> prof_total;  // kernel -> (launches, milliseconds)
+
+    bool fast = false;     // dense products on the tensor cores (exact products, the tensor core's summation order)
+    Dev limbs;             // [3][rows][d] bf16 limbs of the current product's input
 
     int long_seg = 0;      // > 0: the engram is always read in segments of this many keys (else only when it must be)
     Dev eng_partial;       // [rows][heads][segments][2 + hs] partial softmax statistics of the segmented read
@@ -334,6 +338,34 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
     g.N = w.dout;
     g.K = w.din;
     if (lif) g.lif = *lif;
+    if (e->fast && !sparse && w.wt.p && lda == w.din && w.din % 64 == 0 && w.dout % 4 == 0) {
+        const size_t need = (size_t)3 * M * w.din * sizeof(uint16_t);
+        if (e->limbs.bytes < need) CK(e->limbs.alloc(need));
+        prof_begin(e, "tc.split3");
+        launch_split3(e->stream, A, (int64_t)M * w.din, e->limbs.as<uint16_t>());
+        prof_end(e);
+        TcGemmArgs t{};
+        t.a_limbs = e->limbs.as<uint16_t>();
+        t.w_bf16 = w.wt.as<uint16_t>();
+        t.scale = w.sp();
+        t.C = epi == EPI_LIF ? e->yraw.as<float>() : C;  // the currents' buffer is free while the LIF layer runs
+        t.ldc = epi == EPI_LIF ? w.dout : ldc;
+        t.M = M;
+        t.N = w.dout;
+        t.K = w.din;
+        t.status = e->status.as<uint32_t>();
+        prof_begin(e, cls);
+        const bool launched = launch_tc_gemm(e->stream, t, epi == EPI_LIF ? EPI_STORE : epi);
+        prof_end(e);
+        if (launched) {
+            if (epi == EPI_LIF) {
+                prof_begin(e, "lif");
+                launch_lif(e->stream, e->yraw.as<float>(), *lif, M, w.dout);
+                prof_end(e);
+            }
+            return AVA_OK;
+        }
+    }
     prof_begin(e, cls);
     if (!(sparse && launch_q8_event(e->stream, g, epi))) launch_q8_gemm(e->stream, g, epi, e->sm_count);
     prof_end(e);
@@ -579,7 +611,7 @@ int finish(ava_engine* e) {
     CK(cudaMemsetAsync(e->status.p, 0, sizeof(uint32_t), e->stream));
     CK(cudaStreamSynchronize(e->stream));
     const uint32_t st = *e->status_host;
-    if (st & ST_WAIT_TIMEOUT) return e->fail(AVA_ERR_CUDA, "a bounded wait on a bulk-copy barrier ran out inside the memory kernel");
+    if (st & ST_WAIT_TIMEOUT) return e->fail(AVA_ERR_CUDA, "a bounded wait on a copy barrier ran out inside a kernel");
     if (st & ST_BAD_TOKEN) return e->fail(AVA_ERR_ARG, "a token id outside the vocabulary");
     if (st & ST_ENGRAM_FULL) return e->fail(AVA_ERR_CAPACITY, "the engram store had no room for a token");
     if (st & ST_NONFINITE) return e->fail(AVA_ERR_NONFINITE, "a gate, key or value of the fast-weight memory was not finite (the state has moved)");
@@ -1229,6 +1261,26 @@ int64_t ava_state_bytes(const ava_state* s) {
 int ava_engine_set_segmented_read(ava_engine* e, int32_t seg_len) {
     if (!e || seg_len < 0 || (seg_len > 0 && seg_len < 8)) return AVA_ERR_ARG;
     e->long_seg = seg_len;
+    return AVA_OK;
+}
+
+int ava_engine_set_fast_products(ava_engine* e, int32_t on) {
+    if (!e) return AVA_ERR_ARG;
+    if (!e->finalized) return e->fail(AVA_ERR_ARG, "engine not finalized");
+    CK(cudaSetDevice(e->device));
+    if (on) {
+        // bf16 [dout][din] copies of the dense matrices (the spike-driven ones keep the exact event sum)
+        std::vector<QMat*> mats{&e->head};
+        for (auto& b : e->blocks)
+            for (QMat* m : {&b->win, &b->proj, &b->wo, &b->eqkv, &b->ewo, &b->w1}) mats.push_back(m);
+        for (QMat* m : mats) {
+            if (!m->q.p || m->wt.p || m->din % 64 || m->dout % 4) continue;
+            CK(m->wt.alloc((size_t)m->din * m->dout * sizeof(uint16_t)));
+            launch_widen_transpose(e->stream, m->qp(), m->din, m->dout, m->wt.as<uint16_t>());
+        }
+        CK(cudaStreamSynchronize(e->stream));
+    }
+    e->fast = on != 0;
     return AVA_OK;
 }
 

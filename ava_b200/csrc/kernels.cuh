@@ -50,6 +50,24 @@ void launch_q8_gemm(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int sm
 // order, which gives the dense sum's bits (src/int8.rs:10-13).  false: shape not covered, use launch_q8_gemm.
 bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi);
 
+// The dense product on the tensor cores (tcgen05, f32 accumulate in tensor memory), for the optional fast-products
+// mode: exact products (three bf16 limbs of each activation times a bf16 copy of the int8 weight), the sum in the
+// tensor core's order instead of the reference's, so results agree with launch_q8_gemm to about 1e-6 of the sum of
+// magnitudes and not bit for bit.
+struct TcGemmArgs {
+    const uint16_t* a_limbs;  // bf16 [3][M][K] from launch_split3
+    const uint16_t* w_bf16;   // bf16 [N][K] from launch_widen_transpose
+    const float* scale;       // [N]
+    float* C;                 // [M, N], row stride ldc (a multiple of 4)
+    int ldc;
+    int M, N, K;
+    uint32_t* status;         // ST_WAIT_TIMEOUT when a bounded wait ran out (the tile is then not written)
+};
+// false: shape or epilogue not covered (K % 64, N % 4, EPI_LIF) or no tensor-map encoder; nothing was launched
+bool launch_tc_gemm(cudaStream_t st, const TcGemmArgs& a, GemmEpilogue epi);
+void launch_split3(cudaStream_t st, const float* x, int64_t n, uint16_t* out);
+void launch_widen_transpose(cudaStream_t st, const int8_t* q, int K, int N, uint16_t* out);
+
 // ---- row kernels ----------------------------------------------------------------------------------------------
 void launch_embed(cudaStream_t st, const float* tok_emb, const uint32_t* tok, int M, int d, int vocab, float* x, float* stream0, uint32_t* status);
 void launch_rmsnorm(cudaStream_t st, const float* x, const float* gain, int M, int n, float* y);

@@ -82,6 +82,49 @@ static int q8_matmul_impl(int device, const float* x, int32_t m, const int8_t* q
     return AVA_OK;
 }
 
+int ava_op_q8_tc_matmul(int device, const float* x, int32_t m, const int8_t* q, const float* scale, int32_t din, int32_t dout, float* y,
+                        int32_t reps, float* ms_per_launch) {
+    if (!x || !q || !scale || !y || m <= 0 || din <= 0 || dout <= 0 || reps < 0) return AVA_ERR_ARG;
+    if (din % 64 || dout % 4) return AVA_NOT_APPLICABLE;
+    int rc = begin(device);
+    if (rc) return rc;
+    Tmp dx, dq, ds, dy, dl, dw, dst;
+    OCK(up(dx, x, (size_t)m * din * 4));
+    OCK(up(dq, q, (size_t)din * dout));
+    OCK(up(ds, scale, (size_t)dout * 4));
+    OCK(up(dy, nullptr, (size_t)m * dout * 4));
+    OCK(up(dl, nullptr, (size_t)3 * m * din * 2));
+    OCK(up(dw, nullptr, (size_t)din * dout * 2));
+    OCK(up(dst, nullptr, 4));
+    OCK(cudaMemset(dst.p, 0, 4));
+    launch_widen_transpose(0, dq.as<int8_t>(), din, dout, dw.as<uint16_t>());
+    launch_split3(0, dx.as<float>(), (int64_t)m * din, dl.as<uint16_t>());
+    TcGemmArgs g{};
+    g.a_limbs = dl.as<uint16_t>(); g.w_bf16 = dw.as<uint16_t>(); g.scale = ds.as<float>();
+    g.C = dy.as<float>(); g.ldc = dout; g.M = m; g.N = dout; g.K = din; g.status = dst.as<uint32_t>();
+    if (!launch_tc_gemm(0, g, EPI_STORE)) return AVA_NOT_APPLICABLE;
+    if ((rc = end_())) return rc;
+    uint32_t st = 0;
+    OCK(cudaMemcpy(&st, dst.p, 4, cudaMemcpyDeviceToHost));
+    if (st) return AVA_ERR_STATE;
+    OCK(cudaMemcpy(y, dy.p, (size_t)m * dout * 4, cudaMemcpyDeviceToHost));
+    if (reps > 0 && ms_per_launch) {  // the product alone, inputs resident, back to back
+        cudaEvent_t e0, e1;
+        OCK(cudaEventCreate(&e0));
+        OCK(cudaEventCreate(&e1));
+        OCK(cudaEventRecord(e0, 0));
+        for (int i = 0; i < reps; ++i) launch_tc_gemm(0, g, EPI_STORE);
+        OCK(cudaEventRecord(e1, 0));
+        if ((rc = end_())) return rc;
+        float ms = 0.0f;
+        OCK(cudaEventElapsedTime(&ms, e0, e1));
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        *ms_per_launch = ms / (float)reps;
+    }
+    return AVA_OK;
+}
+
 int ava_op_rmsnorm(int device, const float* x, const float* gain, int32_t m, int32_t n, float* y) {
     if (!x || !gain || !y || m <= 0 || n <= 0) return AVA_ERR_ARG;
     int rc = begin(device);

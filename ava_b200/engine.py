@@ -85,6 +85,7 @@ def lib() -> C.CDLL:
         "ava_engine_bytes": ([vp], C.c_int64),
         "ava_state_bytes": ([vp], C.c_int64),
         "ava_engine_set_segmented_read": ([vp, C.c_int32], C.c_int),
+        "ava_engine_set_fast_products": ([vp, C.c_int32], C.c_int),
         "ava_prof_enable": ([vp, C.c_int32], C.c_int),
         "ava_prof_read": ([vp, C.c_char_p, C.POINTER(C.c_int64), C.POINTER(C.c_double)], C.c_int),
         "ava_prof_names": ([vp, C.c_char_p, C.c_int32], C.c_int),
@@ -93,6 +94,7 @@ def lib() -> C.CDLL:
         "ava_debug_get": ([vp, C.c_char_p, C.c_int32, fp], C.c_int),
         "ava_op_q8_matmul": ([C.c_int, fp, C.c_int32, i8p, fp, C.c_int32, C.c_int32, fp], C.c_int),
         "ava_op_q8_event_matmul": ([C.c_int, fp, C.c_int32, i8p, fp, C.c_int32, C.c_int32, fp], C.c_int),
+        "ava_op_q8_tc_matmul": ([C.c_int, fp, C.c_int32, i8p, fp, C.c_int32, C.c_int32, fp, C.c_int32, fp], C.c_int),
         "ava_debug_mem_heads_timeline": ([C.c_int, C.c_int32, C.c_int32, C.POINTER(C.c_uint64), C.c_int64], C.c_int),
         "ava_op_rmsnorm": ([C.c_int, fp, fp, C.c_int32, C.c_int32, fp], C.c_int),
         "ava_op_lif": ([C.c_int, fp, fp, fp, fp, fp, C.c_int32, fp, fp, fp, C.c_int32, C.c_int32, fp, fp, fp], C.c_int),
@@ -119,7 +121,7 @@ EXPORTS = ("ava_engine_create ava_engine_destroy ava_last_error ava_engine_set_f
            "ava_state_rows ava_state_select ava_state_cat ava_state_seen ava_state_len ava_state_export "
            "ava_state_import ava_step ava_step_greedy ava_forward_with_state ava_step_device ava_prefill_device ava_state_set_kv_shard ava_shard_parts ava_split_step_begin ava_shard_partial ava_split_step_end ava_sync "
            "ava_engine_stream ava_engine_launches ava_engine_bytes ava_state_bytes ava_debug_keep ava_debug_width "
-           "ava_debug_get ava_engine_set_segmented_read ava_prof_enable ava_prof_read ava_prof_names ava_op_q8_matmul ava_op_q8_event_matmul ava_debug_mem_heads_timeline ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
+           "ava_debug_get ava_engine_set_segmented_read ava_engine_set_fast_products ava_prof_enable ava_prof_read ava_prof_names ava_op_q8_matmul ava_op_q8_event_matmul ava_op_q8_tc_matmul ava_debug_mem_heads_timeline ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
            "ava_host_expf ava_host_logf ava_host_rsqrtf ava_op_math").split()
 
 
@@ -229,6 +231,11 @@ class Model:
     def set_segmented_read(self, seg_len: int):
         """seg_len > 0: the engram is always read in segments of that many keys (the long-context / split-store path)."""
         self._check(lib().ava_engine_set_segmented_read(self.h, seg_len))
+
+    def set_fast_products(self, on: bool):
+        """Dense products on the tensor cores: exact products, the tensor core's summation order (about 1e-6 of each
+        sum's magnitudes from the reference's ordered sums; off by default)."""
+        self._check(lib().ava_engine_set_fast_products(self.h, int(on)))
 
     def prof_enable(self, on: bool):
         self._check(lib().ava_prof_enable(self.h, int(on)))
@@ -340,6 +347,21 @@ def op_q8_matmul(x, q, scale, device=0, event=False):
     f = lib().ava_op_q8_event_matmul if event else lib().ava_op_q8_matmul
     _rc(f(device, _p(x2), x2.shape[0], _p(q, i8p), _p(scale), q.shape[0], q.shape[1], _p(y)))
     return y.reshape(x.shape[:-1] + (q.shape[1],))
+
+
+def op_q8_tc_matmul(x, q, scale, device=0, reps=0):
+    """The product on the tensor cores (exact products, the tensor core's summation order).  With reps > 0 also
+    returns the milliseconds per launch of the product kernel alone: (y, ms)."""
+    x = _f32(x)
+    x2 = x.reshape(-1, x.shape[-1])
+    q = np.ascontiguousarray(q, np.int8)
+    scale = _f32(scale)
+    y = np.empty((x2.shape[0], q.shape[1]), np.float32)
+    ms = C.c_float(0.0)
+    _rc(lib().ava_op_q8_tc_matmul(device, _p(x2), x2.shape[0], _p(q, i8p), _p(scale), q.shape[0], q.shape[1], _p(y), reps,
+                                  C.cast(C.byref(ms), fp)))
+    y = y.reshape(x.shape[:-1] + (q.shape[1],))
+    return (y, ms.value) if reps > 0 else y
 
 
 def op_rmsnorm(x, gain, device=0):

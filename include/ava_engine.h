@@ -140,6 +140,15 @@ int64_t ava_state_bytes(const ava_state* s);
  * bit. */
 int ava_engine_set_segmented_read(ava_engine* e, int32_t seg_len);
 
+/* Fast products (no counterpart in the reference; off by default).  on != 0: the dense int8-weight products of the step
+ * (W_in, the q|k|v|e|g projection, W_o, the engram's projections, W_1 and the output head) run on the tensor cores:
+ * every product exact (the f32 activation as three bf16 limbs, the int8 weight exact in bf16), the f32 sum in the
+ * tensor core's order instead of k = 0, 1, ...  The step's results then agree with the reference's to about 1e-6 of
+ * each sum's magnitudes instead of bit for bit, and a membrane within that distance of its threshold can spike
+ * differently.  The spike-driven products (W_out, W_2) keep the exact event sum.  Costs 2 bytes per dense weight of
+ * device memory on first use.  Call after ava_engine_finalize, between steps. */
+int ava_engine_set_fast_products(ava_engine* e, int32_t on);
+
 /* ---- one long sequence with its engram store split by position over several GPUs ------------------------------
  * No counterpart in the reference (one device, src/memory.rs:664-692).  Each GPU runs one process with its own engine
  * and a state whose store keeps only the tokens it owns: position p belongs to rank min(p / block, world - 1).  The
@@ -181,6 +190,12 @@ int ava_op_q8_matmul(int device, const float* x, int32_t m, const int8_t* q, con
 /* The same through the event-sum kernel (E2, src/int8.rs:10-13,142-163): only the non-zero inputs of each row are
  * summed, in order; the same bits as the dense sum for any input. */
 int ava_op_q8_event_matmul(int device, const float* x, int32_t m, const int8_t* q, const float* scale, int32_t din, int32_t dout, float* y);
+/* The same product on the tensor cores (no counterpart in the reference): every product exact (three bf16 limbs of
+ * each activation, the int8 weight exact in bf16), the f32 sum in the tensor core's order, so y agrees with
+ * ava_op_q8_matmul to about 1e-6 of the sum of magnitudes, not bit for bit.  din % 64 == 0, dout % 4 == 0, else
+ * AVA_NOT_APPLICABLE.  reps > 0 and ms_per_launch != NULL: also times reps launches of the product kernel. */
+int ava_op_q8_tc_matmul(int device, const float* x, int32_t m, const int8_t* q, const float* scale, int32_t din, int32_t dout, float* y,
+                        int32_t reps, float* ms_per_launch);
 /* `fstep::rmsnorm` (src/model/fstep.rs:207-220) on m rows of n. */
 int ava_op_rmsnorm(int device, const float* x, const float* gain, int32_t m, int32_t n, float* y);
 /* `fstep::arch::lif` (src/model/fstep/arch.rs:173-228) on m rows of d; theta/rho/gain/a0/a1 may be NULL. */

@@ -67,6 +67,33 @@ def test_q8_matmul_bits(orc, m, din, dout):
         assert np.array_equal(bits(got[2]), bits(exact))
 
 
+@pytest.mark.parametrize("m,din,dout", [(1, 64, 64), (5, 128, 132), (70, 768, 3840), (256, 3072, 768), (130, 768, 16384), (300, 2048, 196)])
+def test_tensor_core_product_agrees_to_rounding(orc, m, din, dout):
+    """The tcgen05 form of the product: exact products, the tensor core's summation order.  Against the reference's
+    ordered sum it may differ by the rounding of the additions only: at most 4e-6 of the sum of the terms' magnitudes
+    (measured: 1.3e-6 to 2.3e-6), and spike rows (small integers) come out exact."""
+    rng = np.random.default_rng(m + dout)
+    q = rng.integers(-127, 128, (din, dout)).astype(np.int8)
+    sc = (rng.uniform(0.5, 1.5, dout) / 127).astype(np.float32)
+    x = (rng.normal(size=(m, din)) * np.exp(rng.normal(size=(m, din)))).astype(np.float32)
+    if m > 2:
+        x[1] = 0.0
+        x[2] = rng.integers(-2, 3, din)
+    orc.set_threads(8)
+    try:
+        want = orc.q8_matmul(x, q, sc)
+    finally:
+        orc.set_threads(1)
+    got = engine.op_q8_tc_matmul(x, q, sc)
+    mag = (np.abs(x).astype(np.float64) @ np.abs(q).astype(np.float64)) * sc + 1e-30
+    assert float(np.max(np.abs(got.astype(np.float64) - want) / mag)) <= 4e-6
+    if m > 2:
+        assert not got[1].any()
+        assert np.array_equal(bits(got[2]), bits(want[2]))   # integer sums below 2^24: exact in any order
+    with pytest.raises(engine.NotApplicable):
+        engine.op_q8_tc_matmul(x[:, :48], q[:48], sc)
+
+
 @pytest.mark.parametrize("density", [0.0, 0.02, 0.25, 0.6, 1.0])
 @pytest.mark.parametrize("din,dout", [(768, 768), (3072, 768), (128, 320)])
 def test_event_sum_bits(orc, density, din, dout):
