@@ -117,6 +117,8 @@ struct ava_engine {
 
     bool fast = false;     // dense products on the tensor cores (exact products, the tensor core's summation order)
     Dev limbs;             // [3][rows][d] bf16 limbs of the current product's input
+    const float* limbs_src = nullptr;  // the f32 buffer whose limbs the producing kernel has just written there
+    int limbs_rows = 0;
 
     int long_seg = 0;      // > 0: the engram is always read in segments of this many keys (else only when it must be)
     Dev eng_partial;       // [rows][heads][segments][2 + hs] partial softmax statistics of the segmented read
@@ -325,6 +327,16 @@ void dbg(ava_engine* e, const char* name, int block, const float* src, int rows,
     e->debug_rows = rows;
 }
 
+// fast products: where the kernel that writes `dst` [M, K] should also leave its bf16 limbs (null when the mode is off)
+uint16_t* limbs_for(ava_engine* e, const float* dst, int M, int K) {
+    if (!e->fast || K % 64) return nullptr;
+    const size_t need = (size_t)3 * M * K * sizeof(uint16_t);
+    if (e->limbs.bytes < need && e->limbs.alloc(need) != cudaSuccess) return nullptr;
+    e->limbs_src = dst;
+    e->limbs_rows = M;
+    return e->limbs.as<uint16_t>();
+}
+
 int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w, float* C, int ldc, int M, GemmEpilogue epi, const LifParams* lif = nullptr, bool sparse = false) {
     GemmArgs g{};
     g.A = A;
@@ -340,10 +352,16 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
     if (lif) g.lif = *lif;
     if (e->fast && !sparse && w.wt.p && lda == w.din && w.din % 64 == 0 && w.dout % 4 == 0) {
         const size_t need = (size_t)3 * M * w.din * sizeof(uint16_t);
-        if (e->limbs.bytes < need) CK(e->limbs.alloc(need));
-        prof_begin(e, "tc.split3");
-        launch_split3(e->stream, A, (int64_t)M * w.din, e->limbs.as<uint16_t>());
-        prof_end(e);
+        if (e->limbs.bytes < need) {
+            CK(e->limbs.alloc(need));
+            e->limbs_src = nullptr;
+        }
+        if (!(e->limbs_src == A && e->limbs_rows == M)) {  // the producer did not leave them
+            prof_begin(e, "tc.split3");
+            launch_split3(e->stream, A, (int64_t)M * w.din, e->limbs.as<uint16_t>());
+            prof_end(e);
+        }
+        e->limbs_src = nullptr;  // one product per set of limbs
         TcGemmArgs t{};
         t.a_limbs = e->limbs.as<uint16_t>();
         t.w_bf16 = w.wt.as<uint16_t>();
@@ -412,7 +430,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         if (!(phase == PHASE_END && i == c.eng_block)) {
         // ---- the spiking memory
         prof_begin(e, "rmsnorm");
-        launch_rmsnorm(st, x, b.mem_norm.as<float>(), M, d, h);
+        launch_rmsnorm(st, x, b.mem_norm.as<float>(), M, d, h, limbs_for(e, h, M, d));
         prof_end(e);
         dbg(e, "h_lif", i, h, M, d);
         LifParams lp{};
@@ -442,7 +460,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
 
         // ---- the fast-weight memory
         prof_begin(e, "rmsnorm");
-        launch_rmsnorm(st, x, b.hebb_norm.as<float>(), M, d, h);
+        launch_rmsnorm(st, x, b.hebb_norm.as<float>(), M, d, h, limbs_for(e, h, M, d));
         prof_end(e);
         dbg(e, "h_mem", i, h, M, d);
         const int pw = e->proj_w();
@@ -486,7 +504,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         prof_end(e);
         dbg(e, "y_raw", i, mh.y, M, d);
         prof_begin(e, "mem_post");
-        launch_mem_post(st, mh.y, c.out_gate ? e->proj.as<float>() + 4 * d : nullptr, pw, M, d, hs, e->y.as<float>());
+        launch_mem_post(st, mh.y, c.out_gate ? e->proj.as<float>() + 4 * d : nullptr, pw, M, d, hs, e->y.as<float>(), limbs_for(e, e->y.as<float>(), M, d));
         prof_end(e);
         dbg(e, "y", i, e->y.as<float>(), M, d);
         gemm(e, "gemm.wo", e->y.as<float>(), d, b.wo, x, d, M, EPI_ADD);
@@ -497,7 +515,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         if (i == c.eng_block) {
             if (phase != PHASE_END) {
                 prof_begin(e, "rmsnorm");
-                launch_rmsnorm(st, x, b.eng_norm.as<float>(), M, d, h);
+                launch_rmsnorm(st, x, b.eng_norm.as<float>(), M, d, h, limbs_for(e, h, M, d));
                 prof_end(e);
                 gemm(e, "gemm.eng_qkv", h, d, b.eqkv, e->eqkv.as<float>(), 3 * d, M, EPI_STORE);
                 dbg(e, "eng_qkv", i, e->eqkv.as<float>(), M, 3 * d);
@@ -556,7 +574,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
 
         // ---- the sparse MLP
         prof_begin(e, "rmsnorm");
-        launch_rmsnorm(st, x, b.mlp_norm.as<float>(), M, d, h);
+        launch_rmsnorm(st, x, b.mlp_norm.as<float>(), M, d, h, limbs_for(e, h, M, d));
         prof_end(e);
         gemm(e, "gemm.w1", h, d, b.w1, e->u.as<float>(), H, M, EPI_STORE);
         dbg(e, "u", i, e->u.as<float>(), M, H);
@@ -576,7 +594,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         // the head reads the last token's rows only, unless every position's logits were asked for
         const int first_row = all_logits ? 0 : (T - 1) * rows, head_rows = all_logits ? M : rows;
         prof_begin(e, "rmsnorm");
-        launch_rmsnorm(st, x + (size_t)first_row * d, e->final_norm.as<float>(), head_rows, d, h);
+        launch_rmsnorm(st, x + (size_t)first_row * d, e->final_norm.as<float>(), head_rows, d, h, limbs_for(e, h, head_rows, d));
         prof_end(e);
         dbg(e, "x_final", -1, h, head_rows, d);
         float* lg = logits ? logits : e->logits.as<float>();

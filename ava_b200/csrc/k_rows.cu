@@ -102,7 +102,18 @@ __global__ void embed_kernel(const float* __restrict__ tok_emb, const uint32_t* 
 
 // ---------------------------------------------------------------------------------------------------- RMS norm
 // One warp per row: the row is staged in shared memory, lane 0 takes the ordered sum, every lane scales.
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain, int M, int n, float* __restrict__ y) {
+// three bf16 limbs of v (their sum is v exactly) into planes [3][plane], for the tensor-core products
+__device__ __forceinline__ void store_limbs(uint16_t* limbs, int64_t plane, int64_t i, float v) {
+    const uint16_t hi = f_to_bf16(v);
+    const float r1 = sub(v, bf16_to_f(hi));
+    const uint16_t mid = f_to_bf16(r1);
+    limbs[i] = hi;
+    limbs[plane + i] = mid;
+    limbs[2 * plane + i] = f_to_bf16(sub(r1, bf16_to_f(mid)));
+}
+
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain, int M, int n, float* __restrict__ y,
+                               uint16_t* __restrict__ limbs) {
     extern __shared__ __align__(16) float sm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -115,7 +126,11 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     if (lane == 0) inv = inv_rms_seq(xs, n);
     inv = __shfl_sync(0xffffffffu, inv, 0);
     float* yr = y + (size_t)r * n;
-    for (int i = lane; i < n; i += 32) yr[i] = mul(mul(xs[i], inv), gain[i]);
+    for (int i = lane; i < n; i += 32) {
+        const float v = mul(mul(xs[i], inv), gain[i]);
+        yr[i] = v;
+        if (limbs) store_limbs(limbs, (int64_t)M * n, (int64_t)r * n + i, v);
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------- memory: gates
@@ -254,7 +269,8 @@ __global__ void mem_prep_kernel(const MemPrepArgs a) {
 
 // ---------------------------------------------------------------------------------------------------- memory: output
 // head norm, then the silu output gate (src/model/fstep/arch.rs:842-852)
-__global__ void mem_post_kernel(const float* __restrict__ y_raw, const float* __restrict__ gate, int ldg, int M, int d, int hs, float* __restrict__ y) {
+__global__ void mem_post_kernel(const float* __restrict__ y_raw, const float* __restrict__ gate, int ldg, int M, int d, int hs, float* __restrict__ y,
+                                uint16_t* __restrict__ limbs) {
     extern __shared__ __align__(16) float sm[];
     const int nh = d / hs, r = blockIdx.x, tid = threadIdx.x, T = blockDim.x;
     float* ys = sm;
@@ -270,6 +286,7 @@ __global__ void mem_post_kernel(const float* __restrict__ y_raw, const float* __
             v = mul(v, div(g, add(1.0f, expf_(-g))));
         }
         y[(size_t)r * d + c] = v;
+        if (limbs) store_limbs(limbs, (int64_t)M * d, (int64_t)r * d + c, v);
     }
 }
 
@@ -401,11 +418,11 @@ void launch_embed(cudaStream_t st, const float* tok_emb, const uint32_t* tok, in
     embed_kernel<<<M, 128, 0, st>>>(tok_emb, tok, M, d, vocab, x, stream0, status);
 }
 
-void launch_rmsnorm(cudaStream_t st, const float* x, const float* gain, int M, int n, float* y) {
+void launch_rmsnorm(cudaStream_t st, const float* x, const float* gain, int M, int n, float* y, uint16_t* limbs) {
     const int warps = 4;
     const size_t smem = (size_t)warps * n * sizeof(float);
     opt_in_smem(rmsnorm_kernel, smem);
-    rmsnorm_kernel<<<(M + warps - 1) / warps, warps * 32, smem, st>>>(x, gain, M, n, y);
+    rmsnorm_kernel<<<(M + warps - 1) / warps, warps * 32, smem, st>>>(x, gain, M, n, y, limbs);
 }
 
 void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a) {
@@ -415,10 +432,10 @@ void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a) {
     mem_prep_kernel<<<a.M, 256, smem, st>>>(a);
 }
 
-void launch_mem_post(cudaStream_t st, const float* y_raw, const float* gate, int ldg, int M, int d, int hs, float* y) {
+void launch_mem_post(cudaStream_t st, const float* y_raw, const float* gate, int ldg, int M, int d, int hs, float* y, uint16_t* limbs) {
     const size_t smem = ((size_t)d + d / hs) * sizeof(float);
     opt_in_smem(mem_post_kernel, smem);
-    mem_post_kernel<<<M, 256, smem, st>>>(y_raw, gate, ldg, M, d, hs, y);
+    mem_post_kernel<<<M, 256, smem, st>>>(y_raw, gate, ldg, M, d, hs, y, limbs);
 }
 
 void launch_kwta(cudaStream_t st, const float* u, int M, int n, int k, int relu2, float* a) {

@@ -70,7 +70,8 @@ void launch_widen_transpose(cudaStream_t st, const int8_t* q, int K, int N, uint
 
 // ---- row kernels ----------------------------------------------------------------------------------------------
 void launch_embed(cudaStream_t st, const float* tok_emb, const uint32_t* tok, int M, int d, int vocab, float* x, float* stream0, uint32_t* status);
-void launch_rmsnorm(cudaStream_t st, const float* x, const float* gain, int M, int n, float* y);
+// limbs (may be null): also the three bf16 limbs of y, planes [3][M * n], for launch_tc_gemm
+void launch_rmsnorm(cudaStream_t st, const float* x, const float* gain, int M, int n, float* y, uint16_t* limbs = nullptr);
 void launch_lif(cudaStream_t st, const float* cur, const LifParams& p, int M, int d);
 // T tokens of M rows in time order: cur, spikes [T][M][d]; the state in p moves T steps
 void launch_lif_scan(cudaStream_t st, const float* cur, const LifParams& p, int M, int d, int T, float* spikes);
@@ -116,7 +117,7 @@ bool mem_heads_tiling(int hs, int* cw, int* chunk_rows, bool momentum = false);
 // natural [heads][hs][hs] to slice-major [heads][hs / cw][hs][cw] (to_slices 1) or back (0)
 void launch_retile(cudaStream_t st, const float* src, float* dst, int64_t heads, int hs, int cw, int to_slices);
 
-void launch_mem_post(cudaStream_t st, const float* y_raw, const float* gate, int ldg, int M, int d, int hs, float* y);
+void launch_mem_post(cudaStream_t st, const float* y_raw, const float* gate, int ldg, int M, int d, int hs, float* y, uint16_t* limbs = nullptr);
 
 struct EngramArgs {
     const float* qkv;    // [M, 3 d]
