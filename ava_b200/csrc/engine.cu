@@ -272,7 +272,7 @@ const char* find_blocker(const ava_config& c, int* cw, int* rb) {
     if (c.gate_rank < 1) return "gate rank must be at least 1";
     if (c.eng_block >= 0 && (c.eng_head_size <= 0 || c.d % c.eng_head_size)) return "bad engram head size";
     if (c.spikes < 0 || c.spikes > 2) return "unknown spike kind";
-    if (c.head_size % 16 || !mem_heads_tiling(c.head_size, cw, rb, c.mem_momentum > 0.0f)) return "memory head size not covered (a multiple of 16 whose column slice fits shared memory)";
+    if (c.fast_mem && (c.head_size % 16 || !mem_heads_tiling(c.head_size, cw, rb, c.mem_momentum > 0.0f))) return "memory head size not covered (a multiple of 16 whose column slice fits shared memory)";
     return nullptr;
 }
 
@@ -458,7 +458,8 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         gemm(e, "gemm.wout", spikes, d, b.wout, x, d, M, EPI_ADD, nullptr, true);
         dbg(e, "x_lif", i, x, M, d);
 
-        // ---- the fast-weight memory
+        // ---- the fast-weight memory (kinds D and A; a kind-S block goes on to its MLP)
+        if (c.fast_mem) {
         prof_begin(e, "rmsnorm");
         launch_rmsnorm(st, x, b.hebb_norm.as<float>(), M, d, h, limbs_for(e, h, M, d));
         prof_end(e);
@@ -509,6 +510,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         dbg(e, "y", i, e->y.as<float>(), M, d);
         gemm(e, "gemm.wo", e->y.as<float>(), d, b.wo, x, d, M, EPI_ADD);
         dbg(e, "x_mem", i, x, M, d);
+        }
         }
 
         // ---- the engram
@@ -675,7 +677,7 @@ bool locate(const ava_state* s, int row, const std::string& name, StateSlice* ou
         out->count = d;
         return out->buf != nullptr;
     }
-    if (kind == "mem" && (what == "f" || (what == "s" && c.mem_momentum > 0.0f))) {
+    if (kind == "mem" && c.fast_mem && (what == "f" || (what == "s" && c.mem_momentum > 0.0f))) {
         const size_t per = (size_t)d * c.head_size;  // nh * hs * hs
         out->buf = what == "f" ? &ms->mem_f : &ms->mem_s;
         out->off = ((size_t)i * M + row) * per;
@@ -697,8 +699,8 @@ int alloc_state(ava_engine* e, int rows, int ring, int keep, ava_state** out) {
     CK(s->lif_v.alloc(L * M * d * f));
     CK(s->lif_s.alloc(L * M * d * f));
     if (c.alif) CK(s->lif_a.alloc(L * M * d * f));
-    CK(s->mem_f.alloc(L * M * d * c.head_size * f));
-    if (c.mem_momentum > 0.0f) CK(s->mem_s.alloc(L * M * d * c.head_size * f));
+    if (c.fast_mem) CK(s->mem_f.alloc(L * M * d * c.head_size * f));
+    if (c.fast_mem && c.mem_momentum > 0.0f) CK(s->mem_s.alloc(L * M * d * c.head_size * f));
     if (c.eng_block >= 0) {
         CK(s->eng_k.alloc(M * d * ring * s->kv_elem()));
         CK(s->eng_v.alloc(M * d * ring * s->kv_elem()));
@@ -729,8 +731,9 @@ int copy_row(ava_engine* e, const ava_state* src, int src_row, ava_state* dst, i
         CK(cudaMemcpyAsync(dst->lif_s.as<float>() + dn * d, src->lif_s.as<float>() + so * d, d * f, cudaMemcpyDeviceToDevice, e->stream));
         if (c.alif)
             CK(cudaMemcpyAsync(dst->lif_a.as<float>() + dn * d, src->lif_a.as<float>() + so * d, d * f, cudaMemcpyDeviceToDevice, e->stream));
-        CK(cudaMemcpyAsync(dst->mem_f.as<float>() + dn * per, src->mem_f.as<float>() + so * per, per * f, cudaMemcpyDeviceToDevice, e->stream));
-        if (c.mem_momentum > 0.0f)
+        if (c.fast_mem)
+            CK(cudaMemcpyAsync(dst->mem_f.as<float>() + dn * per, src->mem_f.as<float>() + so * per, per * f, cudaMemcpyDeviceToDevice, e->stream));
+        if (c.fast_mem && c.mem_momentum > 0.0f)
             CK(cudaMemcpyAsync(dst->mem_s.as<float>() + dn * per, src->mem_s.as<float>() + so * per, per * f, cudaMemcpyDeviceToDevice, e->stream));
     }
     if (c.eng_block >= 0) {
@@ -882,10 +885,11 @@ int ava_engine_finalize(ava_engine* e) {
             }
         }
         if ((rc = upload_f32(e, b.theta, p + "mem.theta", c.theta != 0))) return rc;
+        if ((rc = upload_f32(e, b.mlp_norm, p + "mlp.norm", true))) return rc;
+        if (c.fast_mem) {
         if ((rc = upload_f32(e, b.hebb_norm, p + "hebb.norm", true))) return rc;
         struct F { Dev* d; const char* n; };
-        for (const F& f : {F{&b.ba, "hebb.ba"}, F{&b.bb, "hebb.bb"}, F{&b.wa2, "hebb.wa2"}, F{&b.wb2, "hebb.wb2"}, F{&b.off, "hebb.off"},
-                           F{&b.mlp_norm, "mlp.norm"}})
+        for (const F& f : {F{&b.ba, "hebb.ba"}, F{&b.bb, "hebb.bb"}, F{&b.wa2, "hebb.wa2"}, F{&b.wb2, "hebb.wb2"}, F{&b.off, "hebb.off"}})
             if ((rc = upload_f32(e, *f.d, p + f.n, true))) return rc;
         {
             // the gates' first-stage projections side by side [d][wa | wb | wa1 | wb1 | zero padding]: one staged stream
@@ -903,13 +907,14 @@ int ava_engine_finalize(ava_engine* e) {
             if ((rc = upload(e, b.gate_w, gw.data(), gw.size() * sizeof(float)))) return rc;
         }
         if ((rc = upload_f32(e, b.vres, p + "hebb.vres", c.value_residual && i > 0))) return rc;
-        if ((rc = upload_f32(e, b.dense, p + "dense", c.dense != 0))) return rc;
-        if ((rc = upload_q8(e, b.win, {p + "mem.win"}))) return rc;
-        if ((rc = upload_q8(e, b.wout, {p + "mem.wout"}))) return rc;
         std::vector<std::string> pj = {p + "hebb.wq", p + "hebb.wk", p + "hebb.wv", p + "hebb.we"};
         if (c.out_gate) pj.push_back(p + "hebb.wg");
         if ((rc = upload_q8(e, b.proj, pj))) return rc;
         if ((rc = upload_q8(e, b.wo, {p + "hebb.wo"}))) return rc;
+        }
+        if ((rc = upload_f32(e, b.dense, p + "dense", c.dense != 0))) return rc;
+        if ((rc = upload_q8(e, b.win, {p + "mem.win"}))) return rc;
+        if ((rc = upload_q8(e, b.wout, {p + "mem.wout"}))) return rc;
         if (i == c.eng_block) {
             if ((rc = upload_f32(e, b.eng_norm, p + "eng.norm", true))) return rc;
             if ((rc = upload_q8(e, b.eqkv, {p + "eng.wq", p + "eng.wk", p + "eng.wv"}))) return rc;

@@ -93,6 +93,16 @@ def lib() -> C.CDLL:
         "ava_debug_width": ([vp, C.c_char_p], C.c_int64),
         "ava_debug_get": ([vp, C.c_char_p, C.c_int32, fp], C.c_int),
         "ava_op_q8_matmul": ([C.c_int, fp, C.c_int32, i8p, fp, C.c_int32, C.c_int32, fp], C.c_int),
+        "ava_loader_error": ([], C.c_char_p),
+        "ava_ckpt_open": ([C.c_char_p, C.POINTER(vp)], C.c_int),
+        "ava_ckpt_close": ([vp], None),
+        "ava_ckpt_count": ([vp], C.c_int32),
+        "ava_ckpt_find": ([vp, C.c_char_p], C.c_int32),
+        "ava_ckpt_tensor": ([vp, C.c_int32, C.POINTER(C.c_char_p), C.POINTER(C.c_char_p), C.POINTER(C.c_int32), C.POINTER(C.c_int64)], C.c_int),
+        "ava_ckpt_read_f32": ([vp, C.c_int32, fp, C.c_int64], C.c_int),
+        "ava_arch_flags": ([C.c_char_p, C.POINTER(AvaConfig)], C.c_int),
+        "ava_config_from_ckpt": ([vp, C.c_char_p, C.c_char_p, C.POINTER(AvaConfig)], C.c_int),
+        "ava_engine_load_ckpt": ([vp, vp], C.c_int),
         "ava_op_q8_event_matmul": ([C.c_int, fp, C.c_int32, i8p, fp, C.c_int32, C.c_int32, fp], C.c_int),
         "ava_op_q8_tc_matmul": ([C.c_int, fp, C.c_int32, i8p, fp, C.c_int32, C.c_int32, fp, C.c_int32, fp], C.c_int),
         "ava_debug_mem_heads_timeline": ([C.c_int, C.c_int32, C.c_int32, C.POINTER(C.c_uint64), C.c_int64], C.c_int),
@@ -121,7 +131,7 @@ EXPORTS = ("ava_engine_create ava_engine_destroy ava_last_error ava_engine_set_f
            "ava_state_rows ava_state_select ava_state_cat ava_state_seen ava_state_len ava_state_export "
            "ava_state_import ava_step ava_step_greedy ava_forward_with_state ava_step_device ava_prefill_device ava_state_set_kv_shard ava_shard_parts ava_split_step_begin ava_shard_partial ava_split_step_end ava_sync "
            "ava_engine_stream ava_engine_launches ava_engine_bytes ava_state_bytes ava_debug_keep ava_debug_width "
-           "ava_debug_get ava_engine_set_segmented_read ava_engine_set_fast_products ava_prof_enable ava_prof_read ava_prof_names ava_op_q8_matmul ava_op_q8_event_matmul ava_op_q8_tc_matmul ava_debug_mem_heads_timeline ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
+           "ava_debug_get ava_engine_set_segmented_read ava_engine_set_fast_products ava_prof_enable ava_prof_read ava_prof_names ava_loader_error ava_ckpt_open ava_ckpt_close ava_ckpt_count ava_ckpt_find ava_ckpt_tensor ava_ckpt_read_f32 ava_arch_flags ava_config_from_ckpt ava_engine_load_ckpt ava_op_q8_matmul ava_op_q8_event_matmul ava_op_q8_tc_matmul ava_debug_mem_heads_timeline ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
            "ava_host_expf ava_host_logf ava_host_rsqrtf ava_op_math").split()
 
 
@@ -137,6 +147,71 @@ def host_math():
     """(expf, logf, rsqrtf) of the engine as C function addresses, for a checker that wants the same arithmetic."""
     L = lib()
     return tuple(C.cast(getattr(L, n), C.c_void_p) for n in ("ava_host_expf", "ava_host_logf", "ava_host_rsqrtf"))
+
+
+def _loader_check(rc):
+    if rc == NOT_APPLICABLE:
+        raise NotApplicable(lib().ava_loader_error().decode())
+    if rc != OK:
+        raise EngineError(rc, lib().ava_loader_error().decode())
+
+
+def _config_dict(c: "AvaConfig") -> dict:
+    return {k: (float(getattr(c, k)) if k in _config.FIELDS_F32 else int(getattr(c, k))) for k in _config.FIELDS_I32 + _config.FIELDS_F32}
+
+
+def arch_flags(flags: str, cfg: dict) -> dict:
+    """`Arch::from_flags` on top of cfg: the configuration with an arch.txt line applied."""
+    c = AvaConfig(**{k: cfg[k] for k in _config.FIELDS_I32 + _config.FIELDS_F32})
+    _loader_check(lib().ava_arch_flags(flags.encode(), C.byref(c)))
+    return _config_dict(c)
+
+
+class Checkpoint:
+    """A .safetensors file opened by the library's loader (host side; needs no GPU)."""
+
+    def __init__(self, path: str):
+        h = C.c_void_p()
+        _loader_check(lib().ava_ckpt_open(str(path).encode(), C.byref(h)))
+        self.h = h
+
+    def close(self):
+        if self.h:
+            lib().ava_ckpt_close(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __len__(self):
+        return lib().ava_ckpt_count(self.h)
+
+    def info(self, i: int):
+        name, dt, rank = C.c_char_p(), C.c_char_p(), C.c_int32()
+        dims = (C.c_int64 * 4)()
+        _loader_check(lib().ava_ckpt_tensor(self.h, i, C.byref(name), C.byref(dt), C.byref(rank), dims))
+        return name.value.decode(), dt.value.decode(), tuple(dims[k] for k in range(rank.value))
+
+    def names(self):
+        return [self.info(i)[0] for i in range(len(self))]
+
+    def get(self, name: str) -> np.ndarray:
+        i = lib().ava_ckpt_find(self.h, name.encode())
+        if i < 0:
+            raise KeyError(name)
+        _, _, shape = self.info(i)
+        out = np.empty(shape, np.float32)
+        _loader_check(lib().ava_ckpt_read_f32(self.h, i, _p(out), out.size))
+        return out
+
+    def config(self, kind: str, flags: str | None = None) -> dict:
+        """`ckpt::detect` + the arch.txt line: the configuration the file was saved with."""
+        c = AvaConfig()
+        _loader_check(lib().ava_config_from_ckpt(self.h, kind.encode(), (flags or "").encode(), C.byref(c)))
+        return _config_dict(c)
 
 
 class Model:
@@ -173,6 +248,23 @@ class Model:
                 a = _f32(w)
                 self._check(L.ava_engine_set_f32(self.h, name.encode(), _p(a), a.size))
         self._check(L.ava_engine_finalize(self.h))
+
+    @classmethod
+    def from_checkpoint(cls, path: str, kind: str, flags: str | None = None, device: int = 0, **overrides) -> "Model":
+        """`ckpt::load_auto` + `set_int8` + `set_fused`: the model a .safetensors file holds (`flags`: the arch.txt line
+        beside it).  overrides: configuration fields the file does not fix (eng_cap, eng_store_bf16, ...)."""
+        ck = Checkpoint(path)
+        try:
+            cfg = ck.config(kind, flags)
+            cfg.update(overrides)
+            m = cls(cfg, None, device)
+            rc = lib().ava_engine_load_ckpt(m.h, ck.h)
+            if rc != OK:
+                _loader_check(rc)
+            m._check(lib().ava_engine_finalize(m.h))
+            return m
+        finally:
+            ck.close()
 
     def fused_blocker(self):
         why = lib().ava_engine_blocker(self.h)

@@ -130,39 +130,40 @@ def model(cfg: dict, seed: int = 0, recipe: str = "bench", unit_gain: bool = Tru
             jitter = g.n(p + "mem.arho", (d,), 0.2) if awake else np.zeros(d, np.float32)
             w[p + "mem.arho"] = (logit(rho) + jitter).astype(np.float32)
             w[p + "mem.again"] = g.u(p + "mem.again", (d,), 0.5, 1.5) if awake else np.ones(d, np.float32)
-        # the fast-weight memory
-        w[p + "hebb.norm"] = ones("hebb.norm")
-        for nm in ("wq", "wk", "wv", "wo"):
-            w[p + "hebb." + nm] = g.q8(p + "hebb." + nm, d, d, gain(d, 0.5 if nm == "wo" else 1.0))
-        if cfg["out_gate"]:
-            w[p + "hebb.wg"] = g.q8(p + "hebb.wg", d, d, gain(d))
-        if awake:
-            w[p + "hebb.we"] = g.q8(p + "hebb.we", d, d, gain(d, 0.3))
-            w[p + "hebb.wa"] = g.n(p + "hebb.wa", (d, nh), 0.02)
-            w[p + "hebb.wb"] = g.n(p + "hebb.wb", (d, nh), 0.02)
-            w[p + "hebb.ba"] = g.n(p + "hebb.ba", (nh,), 0.1)
-            w[p + "hebb.bb"] = g.n(p + "hebb.bb", (nh,), 0.1)
-            w[p + "hebb.wa1"] = g.n(p + "hebb.wa1", (d, r), 0.02)
-            w[p + "hebb.wa2"] = g.n(p + "hebb.wa2", (r, d), 0.1)
-            w[p + "hebb.wb1"] = g.n(p + "hebb.wb1", (d, r), 0.02)
-            w[p + "hebb.wb2"] = g.n(p + "hebb.wb2", (r, d), 0.1)
-            # per-channel keep offsets: logit of a decay in (0.9, 0.999)
-            ga = g.u(p + "hebb.off", (d,), 0.9, 0.999).astype(np.float64)
-            w[p + "hebb.off"] = np.log(ga / (1 - ga)).astype(np.float32)
-        else:
-            # alpha = 1 (log_sigmoid of a large offset is -0), write strength 2 sigmoid(bb) = 0.1, erase key = key
-            w[p + "hebb.we"] = (np.zeros((d, d), np.int8), g.q8(p + "hebb.we", d, d, gain(d))[1])
-            w[p + "hebb.wa"] = np.zeros((d, nh), np.float32)
-            w[p + "hebb.wb"] = np.zeros((d, nh), np.float32)
-            w[p + "hebb.ba"] = np.zeros(nh, np.float32)
-            w[p + "hebb.bb"] = np.full(nh, logit(0.05), np.float32)
-            w[p + "hebb.wa1"] = np.zeros((d, r), np.float32)
-            w[p + "hebb.wa2"] = np.zeros((r, d), np.float32)
-            w[p + "hebb.wb1"] = np.zeros((d, r), np.float32)
-            w[p + "hebb.wb2"] = np.zeros((r, d), np.float32)
-            w[p + "hebb.off"] = np.full(d, 40.0, np.float32)
-        if cfg["value_residual"] and i > 0:
-            w[p + "hebb.vres"] = g.n(p + "hebb.vres", (2,), 0.1) if awake else np.zeros(2, np.float32)
+        # the fast-weight memory (kinds D and A; kind S has none)
+        if cfg["fast_mem"]:
+            w[p + "hebb.norm"] = ones("hebb.norm")
+            for nm in ("wq", "wk", "wv", "wo"):
+                w[p + "hebb." + nm] = g.q8(p + "hebb." + nm, d, d, gain(d, 0.5 if nm == "wo" else 1.0))
+            if cfg["out_gate"]:
+                w[p + "hebb.wg"] = g.q8(p + "hebb.wg", d, d, gain(d))
+            if awake:
+                w[p + "hebb.we"] = g.q8(p + "hebb.we", d, d, gain(d, 0.3))
+                w[p + "hebb.wa"] = g.n(p + "hebb.wa", (d, nh), 0.02)
+                w[p + "hebb.wb"] = g.n(p + "hebb.wb", (d, nh), 0.02)
+                w[p + "hebb.ba"] = g.n(p + "hebb.ba", (nh,), 0.1)
+                w[p + "hebb.bb"] = g.n(p + "hebb.bb", (nh,), 0.1)
+                w[p + "hebb.wa1"] = g.n(p + "hebb.wa1", (d, r), 0.02)
+                w[p + "hebb.wa2"] = g.n(p + "hebb.wa2", (r, d), 0.1)
+                w[p + "hebb.wb1"] = g.n(p + "hebb.wb1", (d, r), 0.02)
+                w[p + "hebb.wb2"] = g.n(p + "hebb.wb2", (r, d), 0.1)
+                # per-channel keep offsets: logit of a decay in (0.9, 0.999)
+                ga = g.u(p + "hebb.off", (d,), 0.9, 0.999).astype(np.float64)
+                w[p + "hebb.off"] = np.log(ga / (1 - ga)).astype(np.float32)
+            else:
+                # alpha = 1 (log_sigmoid of a large offset is -0), write strength 2 sigmoid(bb) = 0.1, erase key = key
+                w[p + "hebb.we"] = (np.zeros((d, d), np.int8), g.q8(p + "hebb.we", d, d, gain(d))[1])
+                w[p + "hebb.wa"] = np.zeros((d, nh), np.float32)
+                w[p + "hebb.wb"] = np.zeros((d, nh), np.float32)
+                w[p + "hebb.ba"] = np.zeros(nh, np.float32)
+                w[p + "hebb.bb"] = np.full(nh, logit(0.05), np.float32)
+                w[p + "hebb.wa1"] = np.zeros((d, r), np.float32)
+                w[p + "hebb.wa2"] = np.zeros((r, d), np.float32)
+                w[p + "hebb.wb1"] = np.zeros((d, r), np.float32)
+                w[p + "hebb.wb2"] = np.zeros((r, d), np.float32)
+                w[p + "hebb.off"] = np.full(d, 40.0, np.float32)
+            if cfg["value_residual"] and i > 0:
+                w[p + "hebb.vres"] = g.n(p + "hebb.vres", (2,), 0.1) if awake else np.zeros(2, np.float32)
         if i == cfg["eng_block"]:
             w[p + "eng.norm"] = ones("eng.norm")
             for nm in ("wq", "wk", "wv", "wo"):
@@ -186,6 +187,6 @@ def token_ids(vocab: int, rows: int, t: int, seed0: int = 0) -> np.ndarray:
 def weight_bytes(cfg: dict) -> int:
     """int8 weight bytes one step streams: every block's matrices and the head (scales not counted)."""
     d, H, V, L = cfg["d"], cfg["hidden"], cfg["vocab"], cfg["n_blocks"]
-    per_block = (7 + (1 if cfg["out_gate"] else 0)) * d * d + 2 * d * H
+    per_block = (2 + ((5 + (1 if cfg["out_gate"] else 0)) if cfg["fast_mem"] else 0)) * d * d + 2 * d * H
     eng = 4 * d * d if cfg["eng_block"] >= 0 else 0
     return L * per_block + eng + V * d

@@ -34,6 +34,7 @@ pub struct AvaConfig {
     pub relu2: i32,
     pub dense: i32,
     pub out_gate: i32,
+    pub fast_mem: i32,
     pub mem_momentum: f32,
     pub slope: f32,
 }

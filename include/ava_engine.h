@@ -53,6 +53,8 @@ typedef struct ava_config {
     int32_t relu2;          /* --mlp-act relu2 */
     int32_t dense;          /* --residual dense */
     int32_t out_gate;       /* 1: silu(h Wg) output gate (OutGate::Silu) */
+    int32_t fast_mem;       /* 1: every block has the fast-weight memory (Kind::D / A, src/model.rs:110-118); 0: Kind::S,
+                               the spiking memory and the sparse MLP only (the step of src/model/fstep.rs:461-688) */
     float   mem_momentum;   /* --mem-momentum (0: off) */
     float   slope;          /* --surrogate-slope (does not change forward values) */
 } ava_config;
@@ -182,6 +184,36 @@ int ava_prof_names(ava_engine* e, char* out, int32_t cap);
 int ava_debug_keep(ava_engine* e, int32_t on);
 int64_t ava_debug_width(const ava_engine* e, const char* name);
 int ava_debug_get(ava_engine* e, const char* name, int32_t block, float* out);
+
+/* ---- checkpoints: the loader either side of the engine (src/ckpt.rs, src/arch.rs `Arch::from_flags`) --------------- */
+
+typedef struct ava_ckpt ava_ckpt;
+
+/* Text of the last loader error on this thread (never NULL). */
+const char* ava_loader_error(void);
+/* `ckpt::read` (src/ckpt.rs:16-18): opens a .safetensors file and checks its header (names, dtypes F32 / F16 / BF16,
+ * shapes of at most 4 dimensions, data offsets that match).  The file is read into host memory once. */
+int ava_ckpt_open(const char* path, ava_ckpt** out);
+void ava_ckpt_close(ava_ckpt* c);
+int32_t ava_ckpt_count(const ava_ckpt* c);
+/* index of the tensor called `name`, or -1 */
+int32_t ava_ckpt_find(const ava_ckpt* c, const char* name);
+/* name, dtype text, rank and dims (4 slots, unused ones 1) of tensor i; any out pointer may be NULL */
+int ava_ckpt_tensor(const ava_ckpt* c, int32_t i, const char** name, const char** dtype, int32_t* rank, int64_t* dims);
+/* tensor i as f32 (n = its element count) */
+int ava_ckpt_read_f32(const ava_ckpt* c, int32_t i, float* out, int64_t n);
+/* `Arch::from_flags` (src/arch.rs:273-420,596-607) on top of `cfg`: the one-line block options of an arch.txt.  Options
+ * that only shape training or initial values are accepted and ignored; an option that adds a part the engine does not
+ * have gives AVA_NOT_APPLICABLE with its name in ava_loader_error (the `fused_blocker` convention). */
+int ava_arch_flags(const char* flags, ava_config* cfg);
+/* `ckpt::detect` + `Config::with_arch` (src/ckpt.rs:21-60): the configuration a file was saved with.  vocab and d from
+ * tok_emb, the block count from the highest b{i}, the engram's block from b{i}.eng.wq, the wide layer from b0.mlp.w1,
+ * per-neuron thresholds from b{i}.mem.theta; `kind` ("S" or "D") and the arch.txt line (NULL or "" for none) are not
+ * in the file and are given, as in the reference. */
+int ava_config_from_ckpt(const ava_ckpt* c, const char* kind, const char* arch_flags, ava_config* out);
+/* `load_auto` + `Model::set_int8` (src/ckpt.rs:51-76, src/model.rs:949-991): every tensor of the file into the engine,
+ * the matrices quantised per output column as they go; call ava_engine_finalize afterwards. */
+int ava_engine_load_ckpt(ava_engine* e, const ava_ckpt* c);
 
 /* ---- single operators on host buffers (the S1 operator seam and the per-op kernels, for parity tests) ---------- */
 

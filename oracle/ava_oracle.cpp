@@ -617,7 +617,8 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
         add_into(x.data(), tmp.data(), R * d);
         T("x_lif", i, x.data(), d);
 
-        // ---- the fast-weight memory (fstep/arch.rs:679-907)
+        // ---- the fast-weight memory (fstep/arch.rs:679-907); a kind-S block has none (fstep.rs:536-548, then :673)
+        if (cfg.fast_mem) {
 #pragma omp parallel for num_threads(nt) schedule(static)
         for (int r = 0; r < R; ++r) rmsnorm(&x[(size_t)r * d], b.hebb_norm.data(), d, &h[(size_t)r * d]);
         T("h_mem", i, h.data(), d);
@@ -744,6 +745,7 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
         q8_matmul(b.wo, y.data(), R, tmp.data());
         add_into(x.data(), tmp.data(), R * d);
         T("x_mem", i, x.data(), d);
+        }
 
         // ---- the engram (fstep/arch.rs:909-974)
         if (i == cfg.eng_block) {
@@ -870,7 +872,7 @@ bool parse_state_name(const orc_state* s, int row, const std::string& name, cons
         if (what == "v") { *out = &r.v[i]; return true; }
         if (what == "s") { *out = &r.s[i]; return true; }
         if (what == "a") { *out = &r.a[i]; return true; }
-    } else if (kind == "mem") {
+    } else if (kind == "mem" && s->m->cfg.fast_mem) {
         if (what == "f") { *out = &r.f[i]; return true; }
         if (what == "s") { *out = &r.ms[i]; return true; }
     }
@@ -967,16 +969,16 @@ int orc_model_check(orc_model* m, char* missing, int cap) {
         const std::string p = "b" + std::to_string(i) + ".";
         struct F { const char* n; const std::vector<float>* v; bool need; };
         const F fs[] = {{"mem.norm", &b.mem_norm, true}, {"mem.beta", &b.beta_param, true}, {"mem.theta", &b.theta, c.theta != 0},
-                        {"mem.arho", &b.arho, c.alif != 0}, {"mem.again", &b.again, c.alif != 0}, {"hebb.norm", &b.hebb_norm, true},
-                        {"hebb.wa", &b.wa, true}, {"hebb.wb", &b.wb, true}, {"hebb.ba", &b.ba, true}, {"hebb.bb", &b.bb, true},
-                        {"hebb.wa1", &b.wa1, true}, {"hebb.wa2", &b.wa2, true}, {"hebb.wb1", &b.wb1, true}, {"hebb.wb2", &b.wb2, true},
-                        {"hebb.off", &b.off, true}, {"hebb.vres", &b.vres, c.value_residual && i > 0}, {"eng.norm", &b.eng_norm, i == c.eng_block},
+                        {"mem.arho", &b.arho, c.alif != 0}, {"mem.again", &b.again, c.alif != 0}, {"hebb.norm", &b.hebb_norm, c.fast_mem != 0},
+                        {"hebb.wa", &b.wa, c.fast_mem != 0}, {"hebb.wb", &b.wb, c.fast_mem != 0}, {"hebb.ba", &b.ba, c.fast_mem != 0}, {"hebb.bb", &b.bb, c.fast_mem != 0},
+                        {"hebb.wa1", &b.wa1, c.fast_mem != 0}, {"hebb.wa2", &b.wa2, c.fast_mem != 0}, {"hebb.wb1", &b.wb1, c.fast_mem != 0}, {"hebb.wb2", &b.wb2, c.fast_mem != 0},
+                        {"hebb.off", &b.off, c.fast_mem != 0}, {"hebb.vres", &b.vres, c.fast_mem && c.value_residual && i > 0}, {"eng.norm", &b.eng_norm, i == c.eng_block},
                         {"mlp.norm", &b.mlp_norm, true}, {"dense", &b.dense, c.dense != 0}};
         for (const F& f : fs)
             if (f.need && f.v->empty()) return fail(p + f.n);
         struct Q { const char* n; const QW* q; bool need; };
-        const Q qs[] = {{"mem.win", &b.win, true}, {"mem.wout", &b.wout, true}, {"hebb.wq", &b.wq, true}, {"hebb.wk", &b.wk, true},
-                        {"hebb.wv", &b.wv, true}, {"hebb.we", &b.we, true}, {"hebb.wg", &b.wg, c.out_gate != 0}, {"hebb.wo", &b.wo, true},
+        const Q qs[] = {{"mem.win", &b.win, true}, {"mem.wout", &b.wout, true}, {"hebb.wq", &b.wq, c.fast_mem != 0}, {"hebb.wk", &b.wk, c.fast_mem != 0},
+                        {"hebb.wv", &b.wv, c.fast_mem != 0}, {"hebb.we", &b.we, c.fast_mem != 0}, {"hebb.wg", &b.wg, c.fast_mem && c.out_gate}, {"hebb.wo", &b.wo, c.fast_mem != 0},
                         {"eng.wq", &b.ewq, i == c.eng_block}, {"eng.wk", &b.ewk, i == c.eng_block}, {"eng.wv", &b.ewv, i == c.eng_block},
                         {"eng.wo", &b.ewo, i == c.eng_block}, {"mlp.w1", &b.w1, true}, {"mlp.w2", &b.w2, true}};
         for (const Q& q : qs)
@@ -991,7 +993,7 @@ orc_state* orc_state_new(const orc_model* m, int rows) {
     s->m = m;
     s->rows.resize(rows);
     const orc_config& c = m->cfg;
-    const size_t fl = (size_t)m->nh() * c.head_size * c.head_size;
+    const size_t fl = c.fast_mem ? (size_t)m->nh() * c.head_size * c.head_size : 0;
     for (RowState& r : s->rows) {
         r.v.assign(c.n_blocks, std::vector<float>(c.d, 0.f));
         r.s.assign(c.n_blocks, std::vector<float>(c.d, 0.f));

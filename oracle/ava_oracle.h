@@ -57,6 +57,7 @@ typedef struct orc_config {
     int32_t relu2;          /* square the kept MLP units */
     int32_t dense;          /* dense residual mixes */
     int32_t out_gate;       /* 1: silu(h Wg) output gate on the memory read */
+    int32_t fast_mem;       /* 1: blocks have the fast-weight memory; 0: kind S (src/model/fstep.rs:461-688) */
     float   mem_momentum;   /* 0: off */
     float   slope;          /* surrogate slope (forward value cancels; kept for the literal op order) */
 } orc_config;

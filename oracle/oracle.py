@@ -21,7 +21,7 @@ class OrcConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "vocab", "d", "n_blocks", "hidden", "kwta_k", "head_size", "eng_block", "eng_head_size", "eng_store_bf16",
         "eng_cap", "gate_rank", "spikes", "alif", "theta", "lif_scale", "value_residual", "relu2", "dense",
-        "out_gate")] + [("mem_momentum", C.c_float), ("slope", C.c_float)]
+        "out_gate", "fast_mem")] + [("mem_momentum", C.c_float), ("slope", C.c_float)]
 
 
 def build(force: bool = False) -> str:
@@ -267,6 +267,9 @@ class OracleModel:
             else:
                 w = np.ascontiguousarray(w, np.float32)
                 rc = L.orc_model_set_f32(self.h, name.encode(), _fp(w), w.size)
+                if rc != 0 and w.ndim == 2:
+                    # an f32 matrix of a checkpoint: quantised per output column (nn/parts/src/quant.rs:18-31)
+                    rc = L.orc_model_set_q8_from_f32(self.h, name.encode(), _fp(w), w.shape[0], w.shape[1])
             if rc != 0:
                 raise ValueError(f"oracle: tensor {name!r} refused (unknown name or wrong size)")
         if "head" not in weights:
