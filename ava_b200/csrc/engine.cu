@@ -1287,6 +1287,8 @@ int ava_engine_set_segmented_read(ava_engine* e, int32_t seg_len) {
     return AVA_OK;
 }
 
+const ava_config* ava_engine_config(const ava_engine* e) { return e ? &e->cfg : nullptr; }
+
 int ava_engine_set_fast_products(ava_engine* e, int32_t on) {
     if (!e) return AVA_ERR_ARG;
     if (!e->finalized) return e->fail(AVA_ERR_ARG, "engine not finalized");

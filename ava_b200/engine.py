@@ -40,6 +40,8 @@ fp = C.POINTER(C.c_float)
 i8p = C.POINTER(C.c_int8)
 u32p = C.POINTER(C.c_uint32)
 i32p = C.POINTER(C.c_int32)
+PICK_FN = C.CFUNCTYPE(C.c_uint32, C.c_void_p, C.c_int32, fp, C.c_int32)
+STOP_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int32, u32p, C.c_int32)
 
 
 def lib() -> C.CDLL:
@@ -93,6 +95,11 @@ def lib() -> C.CDLL:
         "ava_debug_width": ([vp, C.c_char_p], C.c_int64),
         "ava_debug_get": ([vp, C.c_char_p, C.c_int32, fp], C.c_int),
         "ava_op_q8_matmul": ([C.c_int, fp, C.c_int32, i8p, fp, C.c_int32, C.c_int32, fp], C.c_int),
+        "ava_engine_config": ([vp], C.POINTER(AvaConfig)),
+        "ava_splitmix64_next": ([C.POINTER(C.c_uint64)], C.c_uint64),
+        "ava_pick": ([fp, C.c_int32, C.c_float, C.c_int32, C.POINTER(C.c_uint64), u32p, fp, fp], C.c_int),
+        "ava_generate": ([vp, u32p, C.POINTER(C.c_int32), C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_uint32, PICK_FN, STOP_FN, vp, u32p,
+                          C.POINTER(C.c_int32)], C.c_int),
         "ava_loader_error": ([], C.c_char_p),
         "ava_ckpt_open": ([C.c_char_p, C.POINTER(vp)], C.c_int),
         "ava_ckpt_close": ([vp], None),
@@ -131,7 +138,7 @@ EXPORTS = ("ava_engine_create ava_engine_destroy ava_last_error ava_engine_set_f
            "ava_state_rows ava_state_select ava_state_cat ava_state_seen ava_state_len ava_state_export "
            "ava_state_import ava_step ava_step_greedy ava_forward_with_state ava_step_device ava_prefill_device ava_state_set_kv_shard ava_shard_parts ava_split_step_begin ava_shard_partial ava_split_step_end ava_sync "
            "ava_engine_stream ava_engine_launches ava_engine_bytes ava_state_bytes ava_debug_keep ava_debug_width "
-           "ava_debug_get ava_engine_set_segmented_read ava_engine_set_fast_products ava_prof_enable ava_prof_read ava_prof_names ava_loader_error ava_ckpt_open ava_ckpt_close ava_ckpt_count ava_ckpt_find ava_ckpt_tensor ava_ckpt_read_f32 ava_arch_flags ava_config_from_ckpt ava_engine_load_ckpt ava_op_q8_matmul ava_op_q8_event_matmul ava_op_q8_tc_matmul ava_debug_mem_heads_timeline ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
+           "ava_debug_get ava_engine_set_segmented_read ava_engine_set_fast_products ava_prof_enable ava_prof_read ava_prof_names ava_engine_config ava_splitmix64_next ava_pick ava_generate ava_loader_error ava_ckpt_open ava_ckpt_close ava_ckpt_count ava_ckpt_find ava_ckpt_tensor ava_ckpt_read_f32 ava_arch_flags ava_config_from_ckpt ava_engine_load_ckpt ava_op_q8_matmul ava_op_q8_event_matmul ava_op_q8_tc_matmul ava_debug_mem_heads_timeline ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
            "ava_host_expf ava_host_logf ava_host_rsqrtf ava_op_math").split()
 
 
@@ -147,6 +154,27 @@ def host_math():
     """(expf, logf, rsqrtf) of the engine as C function addresses, for a checker that wants the same arithmetic."""
     L = lib()
     return tuple(C.cast(getattr(L, n), C.c_void_p) for n in ("ava_host_expf", "ava_host_logf", "ava_host_rsqrtf"))
+
+
+class Rng:
+    """SplitMix64 as the reference's tools use it (design-tests/nn/data/src/rng.rs:7-31), stepped by the library."""
+
+    def __init__(self, seed: int):
+        self.state = C.c_uint64(seed)
+
+    def next_u64(self) -> int:
+        return int(lib().ava_splitmix64_next(C.byref(self.state)))
+
+
+def pick(logits, temperature: float, top_k: int, rng: Rng | None, traced: bool = False):
+    """`diary::pick` on one row of logits; traced: (token, ln p under the model, ln p under the sampler)."""
+    a = _f32(logits).reshape(-1)
+    tok, lp, slp = C.c_uint32(), C.c_float(), C.c_float()
+    rc = lib().ava_pick(_p(a), a.size, temperature, top_k, C.byref(rng.state) if rng is not None else None, C.cast(C.byref(tok), u32p),
+                        C.cast(C.byref(lp), fp), C.cast(C.byref(slp), fp))
+    if rc != OK:
+        raise EngineError(rc, "ava_pick: bad argument")
+    return (tok.value, lp.value, slp.value) if traced else tok.value
 
 
 def _loader_check(rc):
@@ -265,6 +293,40 @@ class Model:
             return m
         finally:
             ck.close()
+
+    def generate(self, prompts, max_new: int, batch_rows: int = 256, eos: int = 256, pick_fn=None, stop_fn=None, max_ctx: int = 0):
+        """`state::generate`: continuations of every prompt (lists of ids).  pick_fn(prompt_index, logits) -> token
+        (None: greedy, taken on the device); stop_fn(prompt_index, tokens) -> bool.  Returns one list of ids per prompt."""
+        lens = np.array([len(p) for p in prompts], np.int32)
+        flat = np.ascontiguousarray(np.concatenate([np.asarray(p, np.uint32) for p in prompts]) if len(prompts) else np.zeros(0, np.uint32))
+        out = np.zeros((len(prompts), max(max_new, 1)), np.uint32)
+        out_len = np.zeros(len(prompts), np.int32)
+        V = self.cfg["vocab"]
+        errors = []
+
+        def _pick(_user, r, lg, n):
+            try:
+                return int(pick_fn(r, np.ctypeslib.as_array(lg, shape=(n,)))) & 0xFFFFFFFF
+            except Exception as ex:   # an exception must not cross the C frames
+                errors.append(ex)
+                return eos
+
+        def _stop(_user, r, toks, n):
+            try:
+                return int(bool(stop_fn(r, [int(toks[i]) for i in range(n)])))
+            except Exception as ex:
+                errors.append(ex)
+                return 1
+
+        cp = PICK_FN(_pick) if pick_fn is not None else C.cast(None, PICK_FN)
+        cs = STOP_FN(_stop) if stop_fn is not None else C.cast(None, STOP_FN)
+        rc = lib().ava_generate(self.h, _p(flat, u32p), _p(lens, i32p), len(prompts), max_new, batch_rows, max_ctx, eos, cp, cs, None,
+                                _p(out, u32p), _p(out_len, i32p))
+        if errors:
+            raise errors[0]
+        self._check(rc)
+        assert V > 0
+        return [out[r, :out_len[r]].tolist() for r in range(len(prompts))]
 
     def fused_blocker(self):
         why = lib().ava_engine_blocker(self.h)

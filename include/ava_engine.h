@@ -215,6 +215,31 @@ int ava_config_from_ckpt(const ava_ckpt* c, const char* kind, const char* arch_f
  * the matrices quantised per output column as they go; call ava_engine_finalize afterwards. */
 int ava_engine_load_ckpt(ava_engine* e, const ava_ckpt* c);
 
+/* ---- the step's callers: sampler and batched generation (src/diary.rs:686-744, src/state.rs:1388-1458) ----------- */
+
+/* The configuration the engine was created with (valid while the engine lives). */
+const ava_config* ava_engine_config(const ava_engine* e);
+/* `SplitMix64::next_u64` (nn/data/src/rng.rs:24-28): advances *state and returns the next 64 bits. */
+uint64_t ava_splitmix64_next(uint64_t* state);
+/* `diary::pick` / `pick_traced` (src/diary.rs:686-744) on one row of host logits: the most likely token (lowest index
+ * among equals) when temperature <= 0, else softmax(logits / temperature) in f32, the top_k most likely kept (ties in
+ * index order), one draw of *rng_state over their mass.  logp (may be NULL): ln p(token) under the model at
+ * temperature 1; sample_logp (may be NULL): ln p(token) under the sampler, 0 for a greedy pick. */
+int ava_pick(const float* logits, int32_t vocab, float temperature, int32_t top_k, uint64_t* rng_state, uint32_t* token, float* logp,
+             float* sample_logp);
+/* The reference's `pick` and `stop` closures: the token for prompt `prompt_index` given its logits; whether the row
+ * stops after the tokens written so far. */
+typedef uint32_t (*ava_pick_fn)(void* user, int32_t prompt_index, const float* logits, int32_t vocab);
+typedef int (*ava_stop_fn)(void* user, int32_t prompt_index, const uint32_t* tokens, int32_t n);
+/* `state::generate` (src/state.rs:1388-1458): continuations of every prompt with carried state.  prompts: the ids of
+ * all prompts one after another, prompt_len [n_prompts] (none empty).  The prompts are read in groups of at most
+ * batch_rows rows, rows of one length in one chunked pass; then the group steps together, one token per pass, and a
+ * row leaves at `eos` (not written), when `stop` says so, or after max_new tokens.  pick NULL: greedy, taken on the
+ * device (no logits leave it); stop may be NULL.  max_ctx <= 0: longest prompt + max_new + 1 (the engram ring's
+ * length).  out [n_prompts][max_new], out_len [n_prompts]. */
+int ava_generate(ava_engine* e, const uint32_t* prompts, const int32_t* prompt_len, int32_t n_prompts, int32_t max_new, int32_t batch_rows,
+                 int32_t max_ctx, uint32_t eos, ava_pick_fn pick, ava_stop_fn stop, void* user, uint32_t* out, int32_t* out_len);
+
 /* ---- single operators on host buffers (the S1 operator seam and the per-op kernels, for parity tests) ---------- */
 
 /* `QW::matmul_rows` (src/int8.rs:124): y [m, dout] = x [m, din] . W.  Same bits as the reference's ordered sum. */
