@@ -95,6 +95,7 @@ struct ava_engine {
     mutable std::string err;
     std::string blocker;
     int64_t launches = 0;
+    uint64_t fingerprint = 0;
 
     std::map<std::string, std::vector<float>> host_f32;
     std::map<std::string, HostQ> host_q8;
@@ -923,6 +924,28 @@ int ava_engine_finalize(ava_engine* e) {
         if ((rc = upload_q8(e, b.w1, {p + "mlp.w1"}))) return rc;
         if ((rc = upload_q8(e, b.w2, {p + "mlp.w2"}))) return rc;
     }
+    {
+        // what `Model::fingerprint` hashes (src/state.rs:1075-1091): the configuration, every 97th value of tok_emb, final.norm,
+        // every 101st value of each block's w2, FNV-1a over their bytes.  The reference hashes the Debug text of its Config
+        // and the f32 w2; here the configuration's fields and the int8 w2 with its scales, so the two values differ: a state
+        // file is tied to the engine's model, not exchangeable with the reference's check (see ava_state_save).
+        uint64_t h = 0xcbf29ce484222325ull;
+        auto bytes = [&](const void* p, size_t n) {
+            const unsigned char* b = static_cast<const unsigned char*>(p);
+            for (size_t k = 0; k < n; ++k) h = (h ^ b[k]) * 0x100000001b3ull;
+        };
+        bytes(&e->cfg, sizeof(ava_config));
+        const auto& te = e->host_f32["tok_emb"];
+        for (size_t k = 0; k < te.size(); k += 97) bytes(&te[k], 4);
+        const auto& fn = e->host_f32["final.norm"];
+        for (size_t k = 0; k < fn.size(); ++k) bytes(&fn[k], 4);
+        for (int i = 0; i < c.n_blocks; ++i) {
+            const HostQ& w2 = e->host_q8["b" + std::to_string(i) + ".mlp.w2"];
+            for (size_t k = 0; k < w2.q.size(); k += 101) bytes(&w2.q[k], 1);
+            bytes(w2.scale.data(), w2.scale.size() * 4);
+        }
+        e->fingerprint = h;
+    }
     // the host copies are no longer needed
     e->host_f32.clear();
     e->host_q8.clear();
@@ -1000,6 +1023,14 @@ int ava_state_cat(const ava_state* const* parts, int32_t n, ava_state** out) {
         return rc;
     }
     *out = o;
+    return AVA_OK;
+}
+
+uint64_t ava_engine_fingerprint(const ava_engine* e) { return e ? e->fingerprint : 0; }
+ava_engine* ava_state_engine(const ava_state* s) { return s ? s->e : nullptr; }
+int ava_state_set_seen(ava_state* s, int32_t row, int64_t seen) {
+    if (!s || row < 0 || row >= s->rows || seen < 0) return AVA_ERR_ARG;
+    s->seen[row] = seen;
     return AVA_OK;
 }
 

@@ -167,7 +167,7 @@ bool parse_header(const char* text, size_t n, std::vector<Entry>* out) {
 }
 
 int dtype_size(const std::string& d) {
-    if (d == "F32") return 4;
+    if (d == "F32" || d == "U32") return 4;
     if (d == "F16" || d == "BF16") return 2;
     return 0;
 }
@@ -279,7 +279,7 @@ int ava_ckpt_open(const char* path, ava_ckpt** out) {
     for (size_t i = 0; i < c->entries.size(); ++i) {
         const Entry& e = c->entries[i];
         const int es = dtype_size(e.dtype);
-        if (!es) return fail(AVA_NOT_APPLICABLE, e.name + ": dtype " + e.dtype + " (F32, F16 and BF16 are read)");
+        if (!es) return fail(AVA_NOT_APPLICABLE, e.name + ": dtype " + e.dtype + " (F32, F16, BF16 and U32 are read)");
         if (e.shape.size() > 4) return fail(AVA_NOT_APPLICABLE, e.name + ": more than 4 dimensions");
         for (int64_t s : e.shape)
             if (s < 0) return fail(AVA_ERR_ARG, e.name + ": negative dimension");
@@ -313,8 +313,18 @@ int ava_ckpt_tensor(const ava_ckpt* c, int32_t i, const char** name, const char*
     return AVA_OK;
 }
 
+int ava_ckpt_read_u32(const ava_ckpt* c, int32_t i, uint32_t* out, int64_t n) {
+    if (!c || !out || i < 0 || i >= (int32_t)c->entries.size()) return fail(AVA_ERR_ARG, "tensor index out of range");
+    const Entry& e = c->entries[i];
+    if (e.dtype != "U32") return fail(AVA_ERR_ARG, e.name + ": not a U32 tensor");
+    if (n != e.count()) return fail(AVA_ERR_ARG, e.name + ": element count differs");
+    std::memcpy(out, c->data.data() + e.begin, (size_t)n * 4);
+    return AVA_OK;
+}
+
 int ava_ckpt_read_f32(const ava_ckpt* c, int32_t i, float* out, int64_t n) {
     if (!c || !out || i < 0 || i >= (int32_t)c->entries.size()) return fail(AVA_ERR_ARG, "tensor index out of range");
+    if (c->entries[i].dtype == "U32") return fail(AVA_ERR_ARG, c->entries[i].name + ": an integer tensor (ava_ckpt_read_u32)");
     if (n != c->entries[i].count()) return fail(AVA_ERR_ARG, c->entries[i].name + ": element count differs");
     std::memcpy(out, tensor_f32(c, i), (size_t)n * 4);
     return AVA_OK;
@@ -462,6 +472,7 @@ int ava_engine_load_ckpt(ava_engine* e, const ava_ckpt* c) {
         const Entry& t = c->entries[i];
         int b;
         std::string rest;
+        if (t.dtype == "U32") return fail(AVA_ERR_ARG, t.name + ": an integer tensor in a model file");
         const float* w = tensor_f32(c, (int)i);
         int rc;
         if (block_name(t.name, &b, &rest) && is_matrix(rest)) {

@@ -95,6 +95,12 @@ def lib() -> C.CDLL:
         "ava_debug_width": ([vp, C.c_char_p], C.c_int64),
         "ava_debug_get": ([vp, C.c_char_p, C.c_int32, fp], C.c_int),
         "ava_op_q8_matmul": ([C.c_int, fp, C.c_int32, i8p, fp, C.c_int32, C.c_int32, fp], C.c_int),
+        "ava_engine_fingerprint": ([vp], C.c_uint64),
+        "ava_state_engine": ([vp], vp),
+        "ava_state_set_seen": ([vp, C.c_int32, C.c_int64], C.c_int),
+        "ava_state_save": ([vp, C.c_char_p], C.c_int),
+        "ava_state_load": ([vp, C.c_char_p, C.c_int32, C.POINTER(vp)], C.c_int),
+        "ava_ckpt_read_u32": ([vp, C.c_int32, u32p, C.c_int64], C.c_int),
         "ava_engine_config": ([vp], C.POINTER(AvaConfig)),
         "ava_splitmix64_next": ([C.POINTER(C.c_uint64)], C.c_uint64),
         "ava_pick": ([fp, C.c_int32, C.c_float, C.c_int32, C.POINTER(C.c_uint64), u32p, fp, fp], C.c_int),
@@ -138,7 +144,7 @@ EXPORTS = ("ava_engine_create ava_engine_destroy ava_last_error ava_engine_set_f
            "ava_state_rows ava_state_select ava_state_cat ava_state_seen ava_state_len ava_state_export "
            "ava_state_import ava_step ava_step_greedy ava_forward_with_state ava_step_device ava_prefill_device ava_state_set_kv_shard ava_shard_parts ava_split_step_begin ava_shard_partial ava_split_step_end ava_sync "
            "ava_engine_stream ava_engine_launches ava_engine_bytes ava_state_bytes ava_debug_keep ava_debug_width "
-           "ava_debug_get ava_engine_set_segmented_read ava_engine_set_fast_products ava_prof_enable ava_prof_read ava_prof_names ava_engine_config ava_splitmix64_next ava_pick ava_generate ava_loader_error ava_ckpt_open ava_ckpt_close ava_ckpt_count ava_ckpt_find ava_ckpt_tensor ava_ckpt_read_f32 ava_arch_flags ava_config_from_ckpt ava_engine_load_ckpt ava_op_q8_matmul ava_op_q8_event_matmul ava_op_q8_tc_matmul ava_debug_mem_heads_timeline ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
+           "ava_debug_get ava_engine_set_segmented_read ava_engine_set_fast_products ava_prof_enable ava_prof_read ava_prof_names ava_engine_fingerprint ava_state_engine ava_state_set_seen ava_state_save ava_state_load ava_ckpt_read_u32 ava_engine_config ava_splitmix64_next ava_pick ava_generate ava_loader_error ava_ckpt_open ava_ckpt_close ava_ckpt_count ava_ckpt_find ava_ckpt_tensor ava_ckpt_read_f32 ava_arch_flags ava_config_from_ckpt ava_engine_load_ckpt ava_op_q8_matmul ava_op_q8_event_matmul ava_op_q8_tc_matmul ava_debug_mem_heads_timeline ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
            "ava_host_expf ava_host_logf ava_host_rsqrtf ava_op_math").split()
 
 
@@ -230,7 +236,11 @@ class Checkpoint:
         i = lib().ava_ckpt_find(self.h, name.encode())
         if i < 0:
             raise KeyError(name)
-        _, _, shape = self.info(i)
+        _, dt, shape = self.info(i)
+        if dt == "U32":
+            out = np.empty(shape, np.uint32)
+            _loader_check(lib().ava_ckpt_read_u32(self.h, i, _p(out, u32p), out.size))
+            return out
         out = np.empty(shape, np.float32)
         _loader_check(lib().ava_ckpt_read_f32(self.h, i, _p(out), out.size))
         return out
@@ -327,6 +337,18 @@ class Model:
         self._check(rc)
         assert V > 0
         return [out[r, :out_len[r]].tolist() for r in range(len(prompts))]
+
+    @property
+    def fingerprint(self) -> int:
+        return int(lib().ava_engine_fingerprint(self.h))
+
+    def load_state(self, path: str, max_ctx: int = 4096) -> "State":
+        """`State::load`: a state `State.save` wrote for this model."""
+        h = C.c_void_p()
+        rc = lib().ava_state_load(self.h, str(path).encode(), max_ctx, C.byref(h))
+        if rc != OK:
+            raise EngineError(rc, lib().ava_last_error(self.h).decode() or lib().ava_loader_error().decode() or "not a state of this model")
+        return State(self, h)
 
     def fused_blocker(self):
         why = lib().ava_engine_blocker(self.h)
@@ -455,6 +477,10 @@ class State:
         h = C.c_void_p()
         parts[0].m._check(lib().ava_state_cat(arr, len(parts), C.byref(h)))
         return State(parts[0].m, h)
+
+    def save(self, path: str):
+        """`State::save`: a safetensors file under the reference's tensor names (whole or absent: tmp + rename)."""
+        self.m._check(lib().ava_state_save(self.h, str(path).encode()))
 
     def seen(self, row: int) -> int:
         return lib().ava_state_seen(self.h, row)

@@ -200,8 +200,9 @@ int32_t ava_ckpt_count(const ava_ckpt* c);
 int32_t ava_ckpt_find(const ava_ckpt* c, const char* name);
 /* name, dtype text, rank and dims (4 slots, unused ones 1) of tensor i; any out pointer may be NULL */
 int ava_ckpt_tensor(const ava_ckpt* c, int32_t i, const char** name, const char** dtype, int32_t* rank, int64_t* dims);
-/* tensor i as f32 (n = its element count) */
+/* tensor i as f32 (n = its element count); integer tensors (U32: the counters of a state file) through read_u32 */
 int ava_ckpt_read_f32(const ava_ckpt* c, int32_t i, float* out, int64_t n);
+int ava_ckpt_read_u32(const ava_ckpt* c, int32_t i, uint32_t* out, int64_t n);
 /* `Arch::from_flags` (src/arch.rs:273-420,596-607) on top of `cfg`: the one-line block options of an arch.txt.  Options
  * that only shape training or initial values are accepted and ignored; an option that adds a part the engine does not
  * have gives AVA_NOT_APPLICABLE with its name in ava_loader_error (the `fused_blocker` convention). */
@@ -214,6 +215,26 @@ int ava_config_from_ckpt(const ava_ckpt* c, const char* kind, const char* arch_f
 /* `load_auto` + `Model::set_int8` (src/ckpt.rs:51-76, src/model.rs:949-991): every tensor of the file into the engine,
  * the matrices quantised per output column as they go; call ava_engine_finalize afterwards. */
 int ava_engine_load_ckpt(ava_engine* e, const ava_ckpt* c);
+
+/* ---- carried state on disk (`State::save` / `State::load`, src/state.rs:1114-1329) ------------------------------- */
+
+/* `Model::fingerprint` (src/state.rs:1075-1091) for the engine's model: FNV-1a over the configuration, every 97th value
+ * of tok_emb, final.norm, and every 101st int8 weight of each block's w2 with its scales.  NOT the reference's value
+ * (that one hashes the Debug text of its Rust Config and the f32 w2), so a state file is tied to this engine's model. */
+uint64_t ava_engine_fingerprint(const ava_engine* e);
+/* the engine a state belongs to */
+ava_engine* ava_state_engine(const ava_state* s);
+/* tokens read so far of a row (`State::seen`), set when a state is rebuilt from a file */
+int ava_state_set_seen(ava_state* s, int32_t row, int64_t seen);
+/* `State::save`: the state as a safetensors file under the reference's tensor names and shapes (meta.seen, meta.model,
+ * meta.blocks, meta.cap, meta.hist, meta.hist_len, lif.{i}.{v,s,a} [rows, d], mem.{i}.{f,s} [rows * heads, hs, hs],
+ * eng.{k,v} [rows, heads, S, hs] left-padded with eng.valid and eng.pad), written through PATH.tmp and a rename.
+ * meta.hist is written empty: the token history feeds the reference's glance and magnitude codes, which the engine
+ * does not have. */
+int ava_state_save(const ava_state* s, const char* path);
+/* `State::load`: a state that ava_state_save wrote for this engine's model (AVA_ERR_STATE when the file is not one, or
+ * its fingerprint, block count or cap differ).  max_ctx: the engram ring's length, at least the stored length. */
+int ava_state_load(ava_engine* e, const char* path, int32_t max_ctx, ava_state** out);
 
 /* ---- the step's callers: sampler and batched generation (src/diary.rs:686-744, src/state.rs:1388-1458) ----------- */
 
