@@ -18,6 +18,9 @@
 #include <string>
 #include <vector>
 
+#include <cerrno>
+#include <sys/stat.h>
+
 #include "../../include/ava_engine.h"
 
 namespace {
@@ -243,6 +246,60 @@ int ava_state_load(ava_engine* e, const char* path, int32_t max_ctx, ava_state**
     for (int r = 0; r < rows; ++r) ava_state_set_seen(st, r, seen[r]);
     guard.s = nullptr;
     *out = st;
+    return AVA_OK;
+}
+
+// ---- one saved state per conversation, in a folder (`ConvStore`, src/state.rs:1334-1384)
+
+int ava_conv_path(const char* dir, const char* id, char* out, int64_t n) {
+    if (!dir || !id || !out || n <= 0) return AVA_ERR_ARG;
+    // the id itself when it is short and plain (letters, digits, '-', '_'), else its FNV-1a hash
+    const size_t len = std::strlen(id);
+    bool plain = len > 0 && len <= 64;
+    for (size_t k = 0; k < len && plain; ++k) {
+        const unsigned char ch = (unsigned char)id[k];
+        plain = (ch >= '0' && ch <= '9') || (ch >= 'a' && ch <= 'z') || (ch >= 'A' && ch <= 'Z') || ch == '-' || ch == '_';
+    }
+    std::string name;
+    if (plain) {
+        name = id;
+    } else {
+        uint64_t h = 0xcbf29ce484222325ull;
+        for (size_t k = 0; k < len; ++k) h = (h ^ (unsigned char)id[k]) * 0x100000001b3ull;
+        char buf[24];
+        std::snprintf(buf, sizeof buf, "h%016llx", (unsigned long long)h);
+        name = buf;
+    }
+    std::string path = dir;
+    if (!path.empty() && path.back() != '/') path += '/';
+    path += "state-" + name + ".safetensors";
+    if ((int64_t)path.size() + 1 > n) return AVA_ERR_CAPACITY;
+    std::memcpy(out, path.c_str(), path.size() + 1);
+    return AVA_OK;
+}
+
+int ava_conv_save(const char* dir, const char* id, const ava_state* s) {
+    char path[4096];
+    int rc = ava_conv_path(dir, id, path, sizeof path);
+    if (rc) return rc;
+    // the folder is made on first use (one level, as `create_dir_all` of a folder beside the model file)
+    std::string cmd_dir = dir;
+    if (::mkdir(cmd_dir.c_str(), 0777) != 0 && errno != EEXIST) return AVA_ERR_ARG;
+    return ava_state_save(s, path);
+}
+
+int ava_conv_load(ava_engine* e, const char* dir, const char* id, int32_t max_ctx, ava_state** out, int32_t* found) {
+    if (!out || !found) return AVA_ERR_ARG;
+    *out = nullptr;
+    *found = AVA_CONV_FRESH;
+    char path[4096];
+    int rc = ava_conv_path(dir, id, path, sizeof path);
+    if (rc) return rc;
+    FILE* f = std::fopen(path, "rb");
+    if (!f) return AVA_OK;  // no saved state for this conversation: start fresh
+    std::fclose(f);
+    rc = ava_state_load(e, path, max_ctx, out);
+    *found = rc == AVA_OK ? AVA_CONV_RESUMED : AVA_CONV_STALE;  // stale: saved by another model, or unreadable
     return AVA_OK;
 }
 

@@ -43,6 +43,8 @@ pub struct AvaConfig {
 pub struct AvaEngine { _p: [u8; 0] }
 #[repr(C)]
 pub struct AvaState { _p: [u8; 0] }
+#[repr(C)]
+pub struct AvaCkpt { _p: [u8; 0] }
 
 #[link(name = "ava_engine")]
 extern "C" {
@@ -69,6 +71,31 @@ extern "C" {
     pub fn ava_step_device(e: *mut AvaEngine, s: *mut AvaState, tok: *const u32, logits: *mut f32, next: *mut u32) -> c_int;
     pub fn ava_sync(e: *mut AvaEngine) -> c_int;
     pub fn ava_engine_stream(e: *mut AvaEngine) -> *mut c_void;
+    pub fn ava_engine_set_fast_products(e: *mut AvaEngine, on: i32) -> c_int;
+    pub fn ava_engine_config(e: *const AvaEngine) -> *const AvaConfig;
+    pub fn ava_engine_fingerprint(e: *const AvaEngine) -> u64;
+    // files: src/ckpt.rs, src/arch.rs `from_flags`
+    pub fn ava_loader_error() -> *const c_char;
+    pub fn ava_ckpt_open(path: *const c_char, out: *mut *mut AvaCkpt) -> c_int;
+    pub fn ava_ckpt_close(c: *mut AvaCkpt);
+    pub fn ava_ckpt_count(c: *const AvaCkpt) -> i32;
+    pub fn ava_ckpt_find(c: *const AvaCkpt, name: *const c_char) -> i32;
+    pub fn ava_ckpt_read_f32(c: *const AvaCkpt, i: i32, out: *mut f32, n: i64) -> c_int;
+    pub fn ava_arch_flags(flags: *const c_char, cfg: *mut AvaConfig) -> c_int;
+    pub fn ava_config_from_ckpt(c: *const AvaCkpt, kind: *const c_char, arch_flags: *const c_char, out: *mut AvaConfig) -> c_int;
+    pub fn ava_engine_load_ckpt(e: *mut AvaEngine, c: *const AvaCkpt) -> c_int;
+    // carried state on disk: `State::save` / `State::load`, `ConvStore`
+    pub fn ava_state_save(s: *const AvaState, path: *const c_char) -> c_int;
+    pub fn ava_state_load(e: *mut AvaEngine, path: *const c_char, max_ctx: i32, out: *mut *mut AvaState) -> c_int;
+    pub fn ava_conv_save(dir: *const c_char, id: *const c_char, s: *const AvaState) -> c_int;
+    pub fn ava_conv_load(e: *mut AvaEngine, dir: *const c_char, id: *const c_char, max_ctx: i32, out: *mut *mut AvaState, found: *mut i32) -> c_int;
+    // `diary::pick`, `state::generate`
+    pub fn ava_pick(logits: *const f32, vocab: i32, temperature: f32, top_k: i32, rng_state: *mut u64, token: *mut u32, logp: *mut f32,
+                    sample_logp: *mut f32) -> c_int;
+    pub fn ava_generate(e: *mut AvaEngine, prompts: *const u32, prompt_len: *const i32, n_prompts: i32, max_new: i32, batch_rows: i32, max_ctx: i32,
+                        eos: u32, pick: Option<extern "C" fn(*mut c_void, i32, *const f32, i32) -> u32>,
+                        stop: Option<extern "C" fn(*mut c_void, i32, *const u32, i32) -> c_int>, user: *mut c_void, out: *mut u32,
+                        out_len: *mut i32) -> c_int;
 }
 
 #[derive(Debug)]

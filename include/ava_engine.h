@@ -235,6 +235,17 @@ int ava_state_save(const ava_state* s, const char* path);
 /* `State::load`: a state that ava_state_save wrote for this engine's model (AVA_ERR_STATE when the file is not one, or
  * its fingerprint, block count or cap differ).  max_ctx: the engram ring's length, at least the stored length. */
 int ava_state_load(ava_engine* e, const char* path, int32_t max_ctx, ava_state** out);
+/* `ConvStore` (src/state.rs:1334-1384): one saved state per conversation in a folder.  The file of conversation `id` is
+ * DIR/state-ID.safetensors when the id is short and plain (at most 64 letters, digits, '-' and '_'), else
+ * DIR/state-hXXXXXXXXXXXXXXXX.safetensors with the FNV-1a hash of the id. */
+int ava_conv_path(const char* dir, const char* id, char* out, int64_t n);
+int ava_conv_save(const char* dir, const char* id, const ava_state* s);
+/* `ConvStore::load`: *found = AVA_CONV_FRESH (no file; *out NULL), AVA_CONV_RESUMED (*out is the state) or
+ * AVA_CONV_STALE (a file of another model, or unreadable: start fresh; *out NULL). */
+#define AVA_CONV_FRESH 0
+#define AVA_CONV_RESUMED 1
+#define AVA_CONV_STALE 2
+int ava_conv_load(ava_engine* e, const char* dir, const char* id, int32_t max_ctx, ava_state** out, int32_t* found);
 
 /* ---- the step's callers: sampler and batched generation (src/diary.rs:686-744, src/state.rs:1388-1458) ----------- */
 

@@ -88,3 +88,24 @@ def test_fresh_state_has_no_store_in_the_file(tmp_path):
     back = m.load_state(path, 16)
     tok = np.array([3, 4], np.uint32)
     assert np.array_equal(bits(m.step(st, tok)), bits(m.step(back, tok)))
+
+
+def test_conversation_store(tmp_path):
+    cfg = config.kind_s(320, 128, 2)
+    m = engine.Model(cfg, synth.model(cfg, 1, "awake"))
+    other = engine.Model(cfg, synth.model(cfg, 2, "awake"))
+    store = engine.ConvStore(str(tmp_path / "conversations"))
+    assert store.path("anna-2") == str(tmp_path / "conversations" / "state-anna-2.safetensors")
+    odd = store.path("who is there?")
+    assert odd.endswith(".safetensors") and "state-h" in odd and len(odd.split("state-h")[1]) == 16 + len(".safetensors")
+    assert store.load("anna-2", m) == ("fresh", None)
+    st = m.state(1, 32)
+    m.step(st, np.array([7], np.uint32))
+    store.save("anna-2", st)
+    store.save("who is there?", st)
+    kind, back = store.load("anna-2", m, 32)
+    assert kind == "resumed" and back.seen(0) == 1
+    tok = np.array([9], np.uint32)
+    assert np.array_equal(bits(m.step(st, tok)), bits(m.step(back, tok)))
+    assert store.load("anna-2", other) == ("stale", None)
+    assert store.load("who is there?", m, 32)[0] == "resumed"
