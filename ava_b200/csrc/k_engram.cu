@@ -49,11 +49,42 @@ __device__ __forceinline__ void kv_load8(const void* base, size_t i, float* out)
     }
 }
 
-// hg heads per block; grid = M * (nh / hg)
-template <bool BF16>
-__global__ void __launch_bounds__(ENG_THREADS) engram_kernel(const EngramArgs a, int hg) {
+// out = fma(V_j, p_j, out) for the keys j0 .. j1 - 1, which sit hs elements apart from element `first`; sixteen values
+// are fetched ahead of the chain, and the next sixteen while the chain runs.  HS > 0: hs known at compile time.
+template <bool BF16, int HS>
+__device__ __forceinline__ float pv_run(const void* v, size_t first, int hs_rt, const float* p, int j0, int j1, float out) {
+    const int hs = HS ? HS : hs_rt;
+    int j = j0;
+    size_t at = first;
+    if (j + 16 <= j1) {
+        float t[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) t[i] = kv_load<BF16>(v, at + (size_t)i * hs);
+        for (; j + 32 <= j1; j += 16) {
+            at += (size_t)16 * hs;
+            float u[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) u[i] = kv_load<BF16>(v, at + (size_t)i * hs);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) out = fma(t[i], p[j + i], out);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) t[i] = u[i];
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) out = fma(t[i], p[j + i], out);
+        j += 16;
+        at += (size_t)16 * hs;
+    }
+    for (; j < j1; ++j, at += hs) out = fma(kv_load<BF16>(v, at), p[j], out);
+    return out;
+}
+
+// hg heads per block; grid = M * (nh / hg).  HS > 0: the head size, known at compile time (the loops unroll without
+// bounds checks); HS == 0: any head size that is a multiple of 8.
+template <bool BF16, int HS>
+__global__ void __launch_bounds__(ENG_THREADS, HS ? 4 : 1) engram_kernel(const EngramArgs a, int hg) {
     extern __shared__ float sm[];
-    const int d = a.d, hs = a.hs, nh = d / hs, cap = a.cap;
+    const int d = a.d, hs = HS ? HS : a.hs, nh = d / hs, cap = a.cap;
     const int groups = nh / hg;
     const int r = blockIdx.x / groups, h0 = (blockIdx.x % groups) * hg;
     const int tid = threadIdx.x, T = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarp = T >> 5;
@@ -85,25 +116,36 @@ __global__ void __launch_bounds__(ENG_THREADS) engram_kernel(const EngramArgs a,
     for (int c = tid; c < gd; c += T) q[c] = qkv[h0 * hs + c];
     __syncthreads();  // the stores above are visible to this block's loads below
 
+    // the ring as two straight runs: keys j < n1 sit at slots start + j, the others at slots j - n1
+    const int n1 = min(n, cap - start);
     const float scale = (float)(1.0 / sqrt((double)hs));
-    for (int idx = tid; idx < hg * n; idx += T) {
-        const int g = idx / n, j = idx % n;
-        int pj = start + j;
-        if (pj >= cap) pj -= cap;
-        const size_t o = row_base + ((size_t)(h0 + g) * cap + pj) * hs;
+    for (int g = 0; g < hg; ++g) {
         const float* qh = q + g * hs;
-        float s = 0.0f;
-        for (int x0 = 0; x0 < hs; x0 += 32) {
-            float kv[32];
+        const size_t head_base = row_base + (size_t)(h0 + g) * cap * hs;
+        for (int j = tid; j < n; j += T) {
+            const size_t o = head_base + (size_t)(j < n1 ? start + j : j - n1) * hs;
+            float s = 0.0f;
+            if (HS) {
 #pragma unroll
-            for (int b = 0; b < 4; ++b)
-                if (x0 + 8 * b < hs) kv_load8<BF16>(a.k, o + x0 + 8 * b, kv + 8 * b);
+                for (int x0 = 0; x0 < (HS ? HS : 8); x0 += 32) {
+                    float kv[32];
 #pragma unroll
-            for (int x = 0; x < 32; ++x) {
-                if (x0 + x < hs) s = (x0 + x == 0) ? mul(kv[0], qh[0]) : fma(kv[x], qh[x0 + x], s);
+                    for (int b = 0; b < 4; ++b)
+                        if (x0 + 8 * b < HS) kv_load8<BF16>(a.k, o + x0 + 8 * b, kv + 8 * b);
+#pragma unroll
+                    for (int x = 0; x < 32; ++x)
+                        if (x0 + x < HS) s = (x0 + x == 0) ? mul(kv[0], qh[0]) : fma(kv[x], qh[x0 + x], s);
+                }
+            } else {
+                for (int x0 = 0; x0 < hs; x0 += 8) {
+                    float kv[8];
+                    kv_load8<BF16>(a.k, o + x0, kv);
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) s = (x0 + x == 0) ? mul(kv[0], qh[0]) : fma(kv[x], qh[x0 + x], s);
+                }
             }
+            sc[(size_t)g * n + j] = add(mul(s, scale), 0.0f);
         }
-        sc[(size_t)g * n + j] = add(mul(s, scale), 0.0f);
     }
     __syncthreads();
     for (int g = warp; g < hg; g += nwarp) {
@@ -113,7 +155,10 @@ __global__ void __launch_bounds__(ENG_THREADS) engram_kernel(const EngramArgs a,
         if (lane == 0) mx[g] = m;
     }
     __syncthreads();
-    for (int idx = tid; idx < hg * n; idx += T) sc[idx] = expf_(sub(sc[idx], mx[idx / n]));
+    for (int g = 0; g < hg; ++g) {
+        const float m = mx[g];
+        for (int j = tid; j < n; j += T) sc[(size_t)g * n + j] = expf_(sub(sc[(size_t)g * n + j], m));
+    }
     __syncthreads();
     for (int g = tid; g < hg; g += T) {
         float s = 0.0f;
@@ -122,34 +167,27 @@ __global__ void __launch_bounds__(ENG_THREADS) engram_kernel(const EngramArgs a,
         den[g] = s;
     }
     __syncthreads();
-    for (int idx = tid; idx < hg * n; idx += T) sc[idx] = div(sc[idx], den[idx / n]);
+    for (int g = 0; g < hg; ++g) {
+        const float dn = den[g];
+        for (int j = tid; j < n; j += T) sc[(size_t)g * n + j] = div(sc[(size_t)g * n + j], dn);
+    }
     __syncthreads();
     // o = p . V: per output the chain over the keys (src/model/fstep.rs:222-257 with k = n)
     for (int c = tid; c < gd; c += T) {
         const int g = c / hs, dd = c % hs;
         const float* p = sc + (size_t)g * n;
         const size_t hb = row_base + (size_t)(h0 + g) * cap * hs + dd;
-        auto V = [&](int j) {
-            int pj = start + j;
-            if (pj >= cap) pj -= cap;
-            return kv_load<BF16>(a.v, hb + (size_t)pj * hs);
-        };
+        auto at = [&](int j) { return hb + (size_t)(j < n1 ? start + j : j - n1) * hs; };
         float out;
         if (n == 1) {
-            out = mul(V(0), p[0]);
+            out = mul(kv_load<BF16>(a.v, at(0)), p[0]);
         } else if (n == 2) {
-            out = add(mul(V(1), p[1]), mul(V(0), p[0]));
+            out = add(mul(kv_load<BF16>(a.v, at(1)), p[1]), mul(kv_load<BF16>(a.v, at(0)), p[0]));
         } else {
-            out = mul(V(0), p[0]);
-            int j = 1;
-            for (; j + 16 <= n; j += 16) {
-                float t[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) t[i] = V(j + i);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) out = fma(t[i], p[j + i], out);
-            }
-            for (; j < n; ++j) out = fma(V(j), p[j], out);
+            out = mul(kv_load<BF16>(a.v, at(0)), p[0]);
+            if (n1 > 1) out = pv_run<BF16, HS>(a.v, at(1), hs, p, 1, n1, out);
+            const int j2 = max(n1, 1);
+            if (j2 < n) out = pv_run<BF16, HS>(a.v, at(j2), hs, p, j2, n, out);
         }
         a.o[(size_t)r * d + h0 * hs + c] = out;
     }
@@ -332,12 +370,18 @@ bool launch_engram(cudaStream_t st, const EngramArgs& a, int n_max) {
     const size_t smem = ((size_t)hg * a.hs + 2 * hg + (size_t)hg * n_max) * sizeof(float);
     if (smem > 227 * 1024 - 64) return false;
     const unsigned grid = (unsigned)(a.M * (nh / hg));
+    auto go = [&](auto kernel) {
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kernel<<<grid, ENG_THREADS, smem, st>>>(a, hg);
+    };
     if (a.bf16) {
-        cudaFuncSetAttribute(engram_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        engram_kernel<true><<<grid, ENG_THREADS, smem, st>>>(a, hg);
+        if (a.hs == 64) go(engram_kernel<true, 64>);
+        else if (a.hs == 32) go(engram_kernel<true, 32>);
+        else go(engram_kernel<true, 0>);
     } else {
-        cudaFuncSetAttribute(engram_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        engram_kernel<false><<<grid, ENG_THREADS, smem, st>>>(a, hg);
+        if (a.hs == 64) go(engram_kernel<false, 64>);
+        else if (a.hs == 32) go(engram_kernel<false, 32>);
+        else go(engram_kernel<false, 0>);
     }
     engram_advance_kernel<<<(a.M + 127) / 128, 128, 0, st>>>(a.n, a.start, a.M, a.cap, a.keep);
     return true;

@@ -101,7 +101,6 @@ __global__ void embed_kernel(const float* __restrict__ tok_emb, const uint32_t* 
 }
 
 // ---------------------------------------------------------------------------------------------------- RMS norm
-// One warp per row: the row is staged in shared memory, lane 0 takes the ordered sum, every lane scales.
 // three bf16 limbs of v (their sum is v exactly) into planes [3][plane], for the tensor-core products
 __device__ __forceinline__ void store_limbs(uint16_t* limbs, int64_t plane, int64_t i, float v) {
     const uint16_t hi = f_to_bf16(v);
@@ -112,6 +111,7 @@ __device__ __forceinline__ void store_limbs(uint16_t* limbs, int64_t plane, int6
     limbs[2 * plane + i] = f_to_bf16(sub(r1, bf16_to_f(mid)));
 }
 
+// One warp per row: the row is staged in shared memory, lane 0 takes the ordered sum, every lane scales.
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain, int M, int n, float* __restrict__ y,
                                uint16_t* __restrict__ limbs) {
     extern __shared__ __align__(16) float sm[];
@@ -291,8 +291,8 @@ __global__ void mem_post_kernel(const float* __restrict__ y_raw, const float* __
 }
 
 // ---------------------------------------------------------------------------------------------------- kWTA
-// The k-th largest value found exactly, one bit of its order-preserving key per round: T is the largest key with
-// count(keys >= T) >= k.  Every unit at or above it is kept (ties included), negatives dropped, squared on request
+// The k-th largest value found exactly, one byte of its order-preserving key per round (256 threads, one per
+// histogram bin): the result is the largest key T with count(keys >= T) >= k.  Every unit at or above it is kept (ties included), negatives dropped, squared on request
 // (src/model/fstep.rs:295-299, src/model/fstep/arch.rs:982-989).
 __device__ __forceinline__ uint32_t order_key(float f) {
     const uint32_t u = f_to_bits(f);
@@ -301,9 +301,7 @@ __device__ __forceinline__ uint32_t order_key(float f) {
 __device__ __forceinline__ float key_value(uint32_t k) { return bits_to_f((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k); }
 
 __global__ void kwta_kernel(const float* __restrict__ u, int M, int n, int k, int relu2, float* __restrict__ out) {
-    extern __shared__ uint32_t keys[];  // [n] keys, then [33] counters
-    __shared__ int warp_cnt[32];
-    __shared__ int total;
+    extern __shared__ uint32_t keys[];  // [n] keys
     const int r = blockIdx.x, tid = threadIdx.x, T = blockDim.x, lane = tid & 31, warp = tid >> 5;
     const float* ur = u + (size_t)r * n;
     float* orow = out + (size_t)r * n;
@@ -315,22 +313,39 @@ __global__ void kwta_kernel(const float* __restrict__ u, int M, int n, int k, in
         return;
     }
     for (int i = tid; i < n; i += T) keys[i] = order_key(ur[i]);
-    __syncthreads();
+    // radix select, one byte of the key per pass from the top: a 256-bin histogram of the keys that share the prefix
+    // found so far, a suffix sum over the bins (one bin per thread), and the bin that holds the k-th largest
+    __shared__ int hist[256];
+    __shared__ int warp_sum[8];
+    __shared__ uint32_t sel_prefix;
+    __shared__ int sel_k;
     uint32_t thr = 0;
-    for (int bit = 31; bit >= 0; --bit) {
-        const uint32_t cand = thr | (1u << bit);
-        int c = 0;
-        for (int i = tid; i < n; i += T) c += keys[i] >= cand;
-        for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
-        if (lane == 0) warp_cnt[warp] = c;
+    int k_rem = k;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        hist[tid] = 0;
         __syncthreads();
-        if (tid == 0) {
-            int t = 0;
-            for (int w = 0; w < (T >> 5); ++w) t += warp_cnt[w];
-            total = t;
+        const uint32_t mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+        for (int i = tid; i < n; i += T) {
+            const uint32_t key = keys[i];
+            if ((key & mask) == thr) atomicAdd(&hist[(key >> shift) & 255u], 1);
         }
         __syncthreads();
-        if (total >= k) thr = cand;
+        const int h = hist[tid];
+        int sfx = h;  // keys in bins tid .. 255
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_down_sync(0xffffffffu, sfx, o);
+            if (lane + o < 32) sfx += up;
+        }
+        if (lane == 0) warp_sum[warp] = sfx;
+        __syncthreads();
+        for (int w = warp + 1; w < 8; ++w) sfx += warp_sum[w];
+        if (sfx >= k_rem && sfx - h < k_rem) {  // exactly one bin: the suffix sums fall as the bin index rises
+            sel_prefix = thr | ((uint32_t)tid << shift);
+            sel_k = k_rem - (sfx - h);
+        }
+        __syncthreads();
+        thr = sel_prefix;
+        k_rem = sel_k;
     }
     const float kth = key_value(thr);
     for (int i = tid; i < n; i += T) {
