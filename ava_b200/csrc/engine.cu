@@ -12,6 +12,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <memory>
@@ -785,6 +786,7 @@ int ava_engine_create(const ava_config* cfg, int device, ava_engine** out) {
         g_create_error = std::string("engine set-up: ") + cudaGetErrorString(ce);
         return AVA_ERR_CUDA;
     }
+    if (const char* v = std::getenv("AVA_PDL")) g_pdl = std::atoi(v) != 0;
     const char* why = find_blocker(e->cfg, &e->cw, &e->rb);
     if (why) e->blocker = why;
     if (!why) {

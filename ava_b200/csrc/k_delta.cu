@@ -62,6 +62,7 @@ __device__ __forceinline__ void bulk_store(void* dst, const void* src, uint32_t 
 // t1 [CW] each, then the barriers.
 template <int CW>
 __global__ void __launch_bounds__(THREADS) mem_heads_kernel(const MemHeadsArgs a) {
+    pdl_enter();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int hs = a.hs, cr = a.chunk_rows, nchunk = hs / cr;
     float* tile = reinterpret_cast<float*>(smem_raw);
@@ -201,6 +202,7 @@ __global__ void __launch_bounds__(THREADS) mem_heads_kernel(const MemHeadsArgs a
 // the sign of zero), y gains (q M) S, F' = ((F alpha + w v^T) - ah rr^T) + S M, S' = ((S M + 0) + w v^T) - ah rr^T.
 template <int CW, bool MOM>
 __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsArgs a, int T) {
+    pdl_enter();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int hs = a.hs, cr = a.chunk_rows, nchunk = hs / cr, d = a.nh * hs;
     float* tile = reinterpret_cast<float*>(smem_raw);
@@ -411,17 +413,17 @@ void launch_mem_heads(cudaStream_t st, const MemHeadsArgs& a) {
     const unsigned grid = (unsigned)((size_t)a.M * a.nh * (a.hs / a.cw));
     if (a.cw == 32) {
         cudaFuncSetAttribute(mem_heads_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        mem_heads_kernel<32><<<grid, THREADS, smem, st>>>(a);
+        launch_k(mem_heads_kernel<32>, dim3(grid), dim3(THREADS), smem, st, a);
     } else {
         cudaFuncSetAttribute(mem_heads_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        mem_heads_kernel<16><<<grid, THREADS, smem, st>>>(a);
+        launch_k(mem_heads_kernel<16>, dim3(grid), dim3(THREADS), smem, st, a);
     }
 }
 
 template <int CW, bool MOM>
 void launch_seq(cudaStream_t st, const MemHeadsArgs& a, int T, size_t smem, unsigned grid) {
     cudaFuncSetAttribute(mem_heads_seq_kernel<CW, MOM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    mem_heads_seq_kernel<CW, MOM><<<grid, THREADS, smem, st>>>(a, T);
+    launch_k(mem_heads_seq_kernel<CW, MOM>, dim3(grid), dim3(THREADS), smem, st, a, T);
 }
 
 void launch_mem_heads_seq(cudaStream_t st, const MemHeadsArgs& a, int T) {
@@ -437,6 +439,7 @@ void launch_mem_heads_seq(cudaStream_t st, const MemHeadsArgs& a, int T) {
 
 // natural [heads_total][hs][hs] <-> slice-major [heads_total][hs / cw][hs][cw]
 __global__ void retile_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t heads, int hs, int cw, int to_slices) {
+    pdl_enter();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // index in the natural layout
     if (i >= heads * hs * hs) return;
     const int b = (int)(i % hs), a = (int)((i / hs) % hs);
@@ -450,7 +453,7 @@ __global__ void retile_kernel(const float* __restrict__ src, float* __restrict__
 
 void launch_retile(cudaStream_t st, const float* src, float* dst, int64_t heads, int hs, int cw, int to_slices) {
     const int64_t n = heads * hs * hs;
-    retile_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(src, dst, heads, hs, cw, to_slices);
+    launch_k(retile_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, src, dst, heads, hs, cw, to_slices);
 }
 
 }  // namespace ava

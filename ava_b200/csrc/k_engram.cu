@@ -83,6 +83,7 @@ __device__ __forceinline__ float pv_run(const void* v, size_t first, int hs_rt, 
 // bounds checks); HS == 0: any head size that is a multiple of 8.
 template <bool BF16, int HS>
 __global__ void __launch_bounds__(ENG_THREADS, HS ? 4 : 1) engram_kernel(const EngramArgs a, int hg) {
+    pdl_enter();
     extern __shared__ float sm[];
     const int d = a.d, hs = HS ? HS : a.hs, nh = d / hs, cap = a.cap;
     const int groups = nh / hg;
@@ -204,6 +205,7 @@ __global__ void __launch_bounds__(ENG_THREADS, HS ? 4 : 1) engram_kernel(const E
 // partial layout: [row][head][segment][2 + hs] f32.
 template <bool BF16>
 __global__ void __launch_bounds__(ENG_THREADS) engram_partial_kernel(const EngramArgs a, int hg, int seg_len, int n_seg_max, float* partial) {
+    pdl_enter();
     extern __shared__ float sm[];
     const int d = a.d, hs = a.hs, nh = d / hs, cap = a.cap;
     const int groups = nh / hg;
@@ -288,6 +290,7 @@ __global__ void __launch_bounds__(ENG_THREADS) engram_partial_kernel(const Engra
 // partial [group][row][head][n_part][2 + hs] -> o [row][nh * hs]; one thread per output channel walks the groups (the
 // GPUs a store is split over, in position order) and within each its parts in order
 __global__ void engram_combine_kernel(const float* __restrict__ partial, int M, int nh, int hs, int n_part, int n_groups, float* __restrict__ o) {
+    pdl_enter();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= M * nh * hs) return;
     const int dd = i % hs, rh = i / hs;  // rh = row * nh + head
@@ -311,6 +314,7 @@ __global__ void engram_combine_kernel(const float* __restrict__ partial, int M, 
 // this token's key and value join the store (the long path appends first, then reads every segment)
 template <bool BF16>
 __global__ void engram_append_kernel(const EngramArgs a) {
+    pdl_enter();
     const int d = a.d, hs = a.hs, nh = d / hs, cap = a.cap;
     const int r = blockIdx.x;
     const int n0 = a.n[r];
@@ -330,11 +334,13 @@ __global__ void engram_append_kernel(const EngramArgs a) {
 }
 // n <- n + 1 after an append (the partial kernels read n as the number of keys present)
 __global__ void engram_count_kernel(int32_t* n, int M, int cap) {
+    pdl_enter();
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r < M && n[r] < cap) n[r] += 1;
 }
 // a capped store drops its oldest tokens after the read
 __global__ void engram_trim_kernel(int32_t* n, int32_t* start, int M, int cap, int keep) {
+    pdl_enter();
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= M) return;
     if (n[r] > keep) {
@@ -345,6 +351,7 @@ __global__ void engram_trim_kernel(int32_t* n, int32_t* start, int M, int cap, i
 
 // after the read: the count moves on; a capped store drops its oldest tokens (src/state.rs:526-538)
 __global__ void engram_advance_kernel(int32_t* n, int32_t* start, int M, int cap, int keep) {
+    pdl_enter();
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= M) return;
     int n0 = n[r];
@@ -372,7 +379,7 @@ bool launch_engram(cudaStream_t st, const EngramArgs& a, int n_max) {
     const unsigned grid = (unsigned)(a.M * (nh / hg));
     auto go = [&](auto kernel) {
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kernel<<<grid, ENG_THREADS, smem, st>>>(a, hg);
+        launch_k(kernel, dim3(grid), dim3(ENG_THREADS), smem, st, a, hg);
     };
     if (a.bf16) {
         if (a.hs == 64) go(engram_kernel<true, 64>);
@@ -383,7 +390,7 @@ bool launch_engram(cudaStream_t st, const EngramArgs& a, int n_max) {
         else if (a.hs == 32) go(engram_kernel<false, 32>);
         else go(engram_kernel<false, 0>);
     }
-    engram_advance_kernel<<<(a.M + 127) / 128, 128, 0, st>>>(a.n, a.start, a.M, a.cap, a.keep);
+    launch_k(engram_advance_kernel, dim3((a.M + 127) / 128), dim3(128), 0, st, a.n, a.start, a.M, a.cap, a.keep);
     return true;
 }
 
@@ -396,12 +403,12 @@ static int head_group(int nh, int hs) {
 }
 
 void launch_engram_append(cudaStream_t st, const EngramArgs& a) {
-    if (a.bf16) engram_append_kernel<true><<<a.M, 256, 0, st>>>(a); else engram_append_kernel<false><<<a.M, 256, 0, st>>>(a);
-    engram_count_kernel<<<(a.M + 127) / 128, 128, 0, st>>>(a.n, a.M, a.cap);
+    if (a.bf16) launch_k(engram_append_kernel<true>, dim3(a.M), dim3(256), 0, st, a); else launch_k(engram_append_kernel<false>, dim3(a.M), dim3(256), 0, st, a);
+    launch_k(engram_count_kernel, dim3((a.M + 127) / 128), dim3(128), 0, st, a.n, a.M, a.cap);
 }
 
 void launch_engram_trim(cudaStream_t st, const EngramArgs& a) {
-    engram_trim_kernel<<<(a.M + 127) / 128, 128, 0, st>>>(a.n, a.start, a.M, a.cap, a.keep);
+    launch_k(engram_trim_kernel, dim3((a.M + 127) / 128), dim3(128), 0, st, a.n, a.start, a.M, a.cap, a.keep);
 }
 
 bool engram_fits_one_block(int d, int hs, int n_max) {
@@ -420,17 +427,17 @@ bool launch_engram_partial(cudaStream_t st, const EngramArgs& a, int seg_len, in
     const unsigned grid = (unsigned)((size_t)a.M * (nh / hg) * n_seg);
     if (a.bf16) {
         cudaFuncSetAttribute(engram_partial_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        engram_partial_kernel<true><<<grid, ENG_THREADS, smem, st>>>(a, hg, seg_len, n_seg, partial);
+        launch_k(engram_partial_kernel<true>, dim3(grid), dim3(ENG_THREADS), smem, st, a, hg, seg_len, n_seg, partial);
     } else {
         cudaFuncSetAttribute(engram_partial_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        engram_partial_kernel<false><<<grid, ENG_THREADS, smem, st>>>(a, hg, seg_len, n_seg, partial);
+        launch_k(engram_partial_kernel<false>, dim3(grid), dim3(ENG_THREADS), smem, st, a, hg, seg_len, n_seg, partial);
     }
     return true;
 }
 
 void launch_engram_combine(cudaStream_t st, const float* partial, int M, int nh, int hs, int n_part, float* o, int n_groups) {
     const int n = M * nh * hs;
-    engram_combine_kernel<<<(n + 127) / 128, 128, 0, st>>>(partial, M, nh, hs, n_part, n_groups, o);
+    launch_k(engram_combine_kernel, dim3((n + 127) / 128), dim3(128), 0, st, partial, M, nh, hs, n_part, n_groups, o);
 }
 
 }  // namespace ava

@@ -67,6 +67,7 @@ __device__ __forceinline__ void lif_update(const LifParams& p, int r, int c, int
 // spike and trace in registers (the reset makes the recurrence nonlinear, so time stays sequential; the parallelism is
 // rows x channels).  cur and spikes are time-major [T][M][d].
 __global__ void lif_scan_kernel(const float* __restrict__ cur, const LifParams p, int M, int d, int T, float* __restrict__ spikes) {
+    pdl_enter();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t Md = (size_t)M * d;
     if (i >= Md) return;
@@ -89,6 +90,7 @@ __global__ void lif_scan_kernel(const float* __restrict__ cur, const LifParams p
 // shared-memory latency.
 template <int BM, int BN, int TM, int TN, int EPI>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN)) q8_gemm_kernel(const GemmArgs g) {
+    pdl_enter();
     static_assert((TM == 4 || TM == 8) && (TN == 8 || TN == 4 || TN == 2), "micro-tile");
     constexpr int T = (BM / TM) * (BN / TN);
     constexpr int AS = BM + 4;  // padded row length of the k-major A tile
@@ -249,6 +251,7 @@ constexpr int EV_THREADS = 64, EV_COLS = EV_THREADS * 4;
 
 template <int EPI>
 __global__ void __launch_bounds__(EV_THREADS) q8_event_kernel(const GemmArgs g) {
+    pdl_enter();
     extern __shared__ unsigned char ev_smem[];
     float* vals = reinterpret_cast<float*>(ev_smem);                  // [K]
     unsigned short* idx = reinterpret_cast<unsigned short*>(vals + g.K);  // [K]
@@ -296,12 +299,23 @@ __global__ void __launch_bounds__(EV_THREADS) q8_event_kernel(const GemmArgs g) 
         acc[3] = fma(x, f[3], acc[3]);
     };
     int i = 0;
-    for (; i + 32 <= nnz; i += 32) {
+    if (nnz >= 32) {
+        // thirty-two weight words in flight while the thirty-two before them are summed
         int w[32];
 #pragma unroll
-        for (int u = 0; u < 32; ++u) w[u] = __ldg(reinterpret_cast<const int*>(wp + (size_t)idx[i + u] * g.ldw));
+        for (int u = 0; u < 32; ++u) w[u] = __ldg(reinterpret_cast<const int*>(wp + (size_t)idx[u] * g.ldw));
+        for (; i + 64 <= nnz; i += 32) {
+            int nx[32];
+#pragma unroll
+            for (int u = 0; u < 32; ++u) nx[u] = __ldg(reinterpret_cast<const int*>(wp + (size_t)idx[i + 32 + u] * g.ldw));
+#pragma unroll
+            for (int u = 0; u < 32; ++u) step(w[u], vals[i + u]);
+#pragma unroll
+            for (int u = 0; u < 32; ++u) w[u] = nx[u];
+        }
 #pragma unroll
         for (int u = 0; u < 32; ++u) step(w[u], vals[i + u]);
+        i += 32;
     }
     for (; i + 4 <= nnz; i += 4) {
         int w[4];
@@ -329,13 +343,14 @@ void launch_tile(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {
     dim3 grid((a.N + BN - 1) / BN, (a.M + BM - 1) / BM);
     dim3 block((BM / TM) * (BN / TN));
     switch (epi) {
-        case EPI_STORE: q8_gemm_kernel<BM, BN, TM, TN, EPI_STORE><<<grid, block, 0, st>>>(a); break;
-        case EPI_ADD: q8_gemm_kernel<BM, BN, TM, TN, EPI_ADD><<<grid, block, 0, st>>>(a); break;
-        case EPI_LIF: q8_gemm_kernel<BM, BN, TM, TN, EPI_LIF><<<grid, block, 0, st>>>(a); break;
+        case EPI_STORE: launch_k(q8_gemm_kernel<BM, BN, TM, TN, EPI_STORE>, dim3(grid), dim3(block), 0, st, a); break;
+        case EPI_ADD: launch_k(q8_gemm_kernel<BM, BN, TM, TN, EPI_ADD>, dim3(grid), dim3(block), 0, st, a); break;
+        case EPI_LIF: launch_k(q8_gemm_kernel<BM, BN, TM, TN, EPI_LIF>, dim3(grid), dim3(block), 0, st, a); break;
     }
 }
 
 __global__ void lif_kernel(const float* cur, const LifParams p, int M, int d) {
+    pdl_enter();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)M * d) return;
     lif_update(p, (int)(i / d), (int)(i % d), d, cur[i]);
@@ -344,6 +359,7 @@ __global__ void lif_kernel(const float* cur, const LifParams p, int M, int d) {
 }  // namespace
 
 int g_gemm_force = 0;  // tuning override (0: choose by shape)
+int g_pdl = 1;         // programmatic dependent launch on every kernel of the step (kernels.cuh)
 
 void launch_q8_gemm(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int sm_count) {
     switch (g_gemm_force) {
@@ -373,22 +389,22 @@ bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {
     dim3 grid((a.N + EV_COLS - 1) / EV_COLS, a.M);
     if (epi == EPI_ADD) {
         if (smem > 32 * 1024) cudaFuncSetAttribute(q8_event_kernel<EPI_ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        q8_event_kernel<EPI_ADD><<<grid, EV_THREADS, smem, st>>>(a);
+        launch_k(q8_event_kernel<EPI_ADD>, dim3(grid), dim3(EV_THREADS), smem, st, a);
     } else {
         if (smem > 32 * 1024) cudaFuncSetAttribute(q8_event_kernel<EPI_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        q8_event_kernel<EPI_STORE><<<grid, EV_THREADS, smem, st>>>(a);
+        launch_k(q8_event_kernel<EPI_STORE>, dim3(grid), dim3(EV_THREADS), smem, st, a);
     }
     return true;
 }
 
 void launch_lif_scan(cudaStream_t st, const float* cur, const LifParams& p, int M, int d, int T, float* spikes) {
     const size_t n = (size_t)M * d;
-    lif_scan_kernel<<<(unsigned)((n + 127) / 128), 128, 0, st>>>(cur, p, M, d, T, spikes);
+    launch_k(lif_scan_kernel, dim3((unsigned)((n + 127) / 128)), dim3(128), 0, st, cur, p, M, d, T, spikes);
 }
 
 void launch_lif(cudaStream_t st, const float* cur, const LifParams& p, int M, int d) {
     const size_t n = (size_t)M * d;
-    lif_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(cur, p, M, d);
+    launch_k(lif_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, cur, p, M, d);
 }
 
 }  // namespace ava

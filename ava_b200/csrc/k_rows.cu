@@ -84,6 +84,7 @@ __device__ __forceinline__ bool finite_f(float v) { return (f_to_bits(v) & 0x7f8
 // ---------------------------------------------------------------------------------------------------- embedding
 __global__ void embed_kernel(const float* __restrict__ tok_emb, const uint32_t* __restrict__ tok, int M, int d, int vocab, float* x, float* stream0,
                              uint32_t* status) {
+    pdl_enter();
     const int r = blockIdx.x;
     uint32_t t = tok[r];
     if (t >= (uint32_t)vocab) {  // stay in bounds; the host reports the token
@@ -114,6 +115,7 @@ __device__ __forceinline__ void store_limbs(uint16_t* limbs, int64_t plane, int6
 // One warp per row: the row is staged in shared memory, lane 0 takes the ordered sum, every lane scales.
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain, int M, int n, float* __restrict__ y,
                                uint16_t* __restrict__ limbs) {
+    pdl_enter();
     extern __shared__ __align__(16) float sm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -136,6 +138,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 // ---------------------------------------------------------------------------------------------------- memory: gates
 // src/model/fstep/arch.rs:685-803 for one row per block of threads.
 __global__ void mem_prep_kernel(const MemPrepArgs a) {
+    pdl_enter();
     extern __shared__ __align__(16) float sm[];
     const int d = a.d, hs = a.hs, nh = d / hs, rk = a.rank;
     const int r = blockIdx.x, tid = threadIdx.x, T = blockDim.x;
@@ -271,6 +274,7 @@ __global__ void mem_prep_kernel(const MemPrepArgs a) {
 // head norm, then the silu output gate (src/model/fstep/arch.rs:842-852)
 __global__ void mem_post_kernel(const float* __restrict__ y_raw, const float* __restrict__ gate, int ldg, int M, int d, int hs, float* __restrict__ y,
                                 uint16_t* __restrict__ limbs) {
+    pdl_enter();
     extern __shared__ __align__(16) float sm[];
     const int nh = d / hs, r = blockIdx.x, tid = threadIdx.x, T = blockDim.x;
     float* ys = sm;
@@ -301,6 +305,7 @@ __device__ __forceinline__ uint32_t order_key(float f) {
 __device__ __forceinline__ float key_value(uint32_t k) { return bits_to_f((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k); }
 
 __global__ void kwta_kernel(const float* __restrict__ u, int M, int n, int k, int relu2, float* __restrict__ out) {
+    pdl_enter();
     extern __shared__ uint32_t keys[];  // [n] keys
     const int r = blockIdx.x, tid = threadIdx.x, T = blockDim.x, lane = tid & 31, warp = tid >> 5;
     const float* ur = u + (size_t)r * n;
@@ -358,6 +363,7 @@ __global__ void kwta_kernel(const float* __restrict__ u, int M, int n, int k, in
 // ---------------------------------------------------------------------------------------------------- dense mix
 // src/model/fstep/arch.rs:1014-1024: the block's output joins the streams, then x <- x + sum_j stream_j w_j in order.
 __global__ void dense_mix_kernel(float* x, float* streams, const float* __restrict__ w, int n_streams, int64_t MD) {
+    pdl_enter();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= MD) return;
     const float xv = x[i];
@@ -370,6 +376,7 @@ __global__ void dense_mix_kernel(float* x, float* streams, const float* __restri
 
 // ---------------------------------------------------------------------------------------------------- argmax
 __global__ void argmax_kernel(const float* __restrict__ logits, int M, int V, uint32_t* next) {
+    pdl_enter();
     __shared__ float bv[32];
     __shared__ uint32_t bi[32];
     const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -408,16 +415,19 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int M, int V, ui
 }
 
 __global__ void math_kernel(int which, const float* x, int64_t n, float* y) {
+    pdl_enter();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     y[i] = which == 0 ? expf_(x[i]) : which == 1 ? logf_(x[i]) : rsqrtf_(x[i]);
 }
 
 __global__ void round_bf16_kernel(const float* x, int64_t n, uint16_t* y) {
+    pdl_enter();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) y[i] = f_to_bf16(x[i]);
 }
 __global__ void widen_bf16_kernel(const uint16_t* x, int64_t n, float* y) {
+    pdl_enter();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) y[i] = bf16_to_f(x[i]);
 }
@@ -430,49 +440,49 @@ void opt_in_smem(K kernel, size_t bytes) {
 }  // namespace
 
 void launch_embed(cudaStream_t st, const float* tok_emb, const uint32_t* tok, int M, int d, int vocab, float* x, float* stream0, uint32_t* status) {
-    embed_kernel<<<M, 128, 0, st>>>(tok_emb, tok, M, d, vocab, x, stream0, status);
+    launch_k(embed_kernel, dim3(M), dim3(128), 0, st, tok_emb, tok, M, d, vocab, x, stream0, status);
 }
 
 void launch_rmsnorm(cudaStream_t st, const float* x, const float* gain, int M, int n, float* y, uint16_t* limbs) {
     const int warps = 4;
     const size_t smem = (size_t)warps * n * sizeof(float);
     opt_in_smem(rmsnorm_kernel, smem);
-    rmsnorm_kernel<<<(M + warps - 1) / warps, warps * 32, smem, st>>>(x, gain, M, n, y, limbs);
+    launch_k(rmsnorm_kernel, dim3((M + warps - 1) / warps), dim3(warps * 32), smem, st, x, gain, M, n, y, limbs);
 }
 
 void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a) {
     const int nh = a.d / a.hs;
     const size_t smem = ((size_t)8 * a.d + 5 * nh + 2 * a.rank + 4 + 2 * (size_t)a.gate_chunk * a.gate_cols) * sizeof(float);
     opt_in_smem(mem_prep_kernel, smem);
-    mem_prep_kernel<<<a.M, 256, smem, st>>>(a);
+    launch_k(mem_prep_kernel, dim3(a.M), dim3(256), smem, st, a);
 }
 
 void launch_mem_post(cudaStream_t st, const float* y_raw, const float* gate, int ldg, int M, int d, int hs, float* y, uint16_t* limbs) {
     const size_t smem = ((size_t)d + d / hs) * sizeof(float);
     opt_in_smem(mem_post_kernel, smem);
-    mem_post_kernel<<<M, 256, smem, st>>>(y_raw, gate, ldg, M, d, hs, y, limbs);
+    launch_k(mem_post_kernel, dim3(M), dim3(256), smem, st, y_raw, gate, ldg, M, d, hs, y, limbs);
 }
 
 void launch_kwta(cudaStream_t st, const float* u, int M, int n, int k, int relu2, float* a) {
     const size_t smem = (size_t)n * sizeof(uint32_t);
     opt_in_smem(kwta_kernel, smem);
-    kwta_kernel<<<M, 256, smem, st>>>(u, M, n, k, relu2, a);
+    launch_k(kwta_kernel, dim3(M), dim3(256), smem, st, u, M, n, k, relu2, a);
 }
 
 void launch_dense_mix(cudaStream_t st, float* x, float* streams, const float* w, int n_streams, int64_t MD) {
-    dense_mix_kernel<<<(unsigned)((MD + 255) / 256), 256, 0, st>>>(x, streams, w, n_streams, MD);
+    launch_k(dense_mix_kernel, dim3((unsigned)((MD + 255) / 256)), dim3(256), 0, st, x, streams, w, n_streams, MD);
 }
 
-void launch_argmax(cudaStream_t st, const float* logits, int M, int V, uint32_t* next) { argmax_kernel<<<M, 256, 0, st>>>(logits, M, V, next); }
+void launch_argmax(cudaStream_t st, const float* logits, int M, int V, uint32_t* next) { launch_k(argmax_kernel, dim3(M), dim3(256), 0, st, logits, M, V, next); }
 
 void launch_math(cudaStream_t st, int which, const float* x, int64_t n, float* y) {
-    math_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(which, x, n, y);
+    launch_k(math_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, which, x, n, y);
 }
 void launch_round_bf16(cudaStream_t st, const float* x, int64_t n, uint16_t* y) {
-    round_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, n, y);
+    launch_k(round_bf16_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, x, n, y);
 }
 void launch_widen_bf16(cudaStream_t st, const uint16_t* x, int64_t n, float* y) {
-    widen_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, n, y);
+    launch_k(widen_bf16_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, x, n, y);
 }
 
 }  // namespace ava

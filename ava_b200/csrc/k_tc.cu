@@ -80,6 +80,7 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(TC_THREADS) tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                                                              const float* __restrict__ scale, float* C, int ldc, int M, int N, int K,
                                                              uint32_t* status) {
+    pdl_enter();
     extern __shared__ unsigned char smem_raw[];
     // the swizzled tiles want a 1024-byte boundary, which the dynamic shared-memory base does not promise
     unsigned char* smem = smem_raw + ((1024u - (s32(smem_raw) & 1023u)) & 1023u);
@@ -205,6 +206,7 @@ __global__ void __launch_bounds__(TC_THREADS) tc_gemm_kernel(const __grid_consta
 
 // x f32 [n] -> three bf16 planes [3][n] whose sum is x exactly
 __global__ void split3_kernel(const float* __restrict__ x, int64_t n, uint16_t* __restrict__ out) {
+    pdl_enter();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const float v = x[i];
@@ -219,6 +221,7 @@ __global__ void split3_kernel(const float* __restrict__ x, int64_t n, uint16_t* 
 
 // int8 [K][N] -> bf16 [N][K] (exact)
 __global__ void widen_transpose_kernel(const int8_t* __restrict__ q, int K, int N, uint16_t* __restrict__ out) {
+    pdl_enter();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (int64_t)K * N) return;
     const int k = (int)(i % K), n = (int)(i / K);
@@ -267,9 +270,9 @@ bool launch_bn(cudaStream_t st, const TcGemmArgs& a, GemmEpilogue epi) {
         opted = true;
     }
     if (epi == EPI_ADD) {
-        tc_gemm_kernel<BN, EPI_ADD><<<grid, TC_THREADS, smem, st>>>(ma, mw, a.scale, a.C, a.ldc, a.M, a.N, a.K, a.status);
+        launch_k(tc_gemm_kernel<BN, EPI_ADD>, dim3(grid), dim3(TC_THREADS), smem, st, ma, mw, a.scale, a.C, a.ldc, a.M, a.N, a.K, a.status);
     } else {
-        tc_gemm_kernel<BN, EPI_STORE><<<grid, TC_THREADS, smem, st>>>(ma, mw, a.scale, a.C, a.ldc, a.M, a.N, a.K, a.status);
+        launch_k(tc_gemm_kernel<BN, EPI_STORE>, dim3(grid), dim3(TC_THREADS), smem, st, ma, mw, a.scale, a.C, a.ldc, a.M, a.N, a.K, a.status);
     }
     return true;
 }
@@ -284,12 +287,12 @@ bool launch_tc_gemm(cudaStream_t st, const TcGemmArgs& a, GemmEpilogue epi) {
 }
 
 void launch_split3(cudaStream_t st, const float* x, int64_t n, uint16_t* out) {
-    split3_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, n, out);
+    launch_k(split3_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, x, n, out);
 }
 
 void launch_widen_transpose(cudaStream_t st, const int8_t* q, int K, int N, uint16_t* out) {
     const int64_t n = (int64_t)K * N;
-    widen_transpose_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(q, K, N, out);
+    launch_k(widen_transpose_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, q, K, N, out);
 }
 
 }  // namespace ava

@@ -7,6 +7,37 @@
 
 namespace ava {
 
+// ---- launches with programmatic dependent launch -----------------------------------------------------------------
+// Every kernel of the step starts with pdl_enter(): it lets the next kernel in the stream be scheduled early
+// (griddepcontrol.launch_dependents) and then waits until the kernel before it has completed and its writes are
+// visible (griddepcontrol.wait), so the order of the work is that of plain stream launches while launch latency and
+// block scheduling overlap the tail of the kernel before.  Without the launch attribute both instructions do nothing.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_enter() {
+#ifdef AVA_PDL_EARLY_TRIGGER
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+#endif
+
+extern int g_pdl;  // 1: launch with the programmatic-serialization attribute (default; AVA_PDL=0 in the environment turns it off)
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Status word in device memory that kernels OR bits into; the host reads it when it reads the step's results.
 enum : uint32_t {
     ST_NONFINITE = 1u,     // a gate, key or value of the fast-weight memory was not finite
