@@ -110,6 +110,7 @@ struct ava_engine {
     // work buffers for `ws_rows` rows
     int ws_rows = 0, ws_logit_rows = 0;
     Dev x, h, proj, ve, vv, vw, vah, vqg, vex, vqs, qw, qa, yraw, y, eqkv, eo, u, act, streams, v_first, logits, tok, next, status;
+    Dev gz, lra, lrb;  // the gates' stages: [rows][gate_cols], [rows][d] twice
     uint32_t* status_host = nullptr;  // pinned
 
     bool prof = false;
@@ -291,6 +292,9 @@ int ensure_workspace(ava_engine* e, int rows, int logit_rows = 0) {
     CK(e->proj.alloc(M * e->proj_w() * f));
     for (Dev* b : {&e->ve, &e->vv, &e->vw, &e->vah, &e->vqg, &e->vex, &e->yraw, &e->y, &e->eo, &e->v_first}) CK(b->alloc(M * d * f));
     if (c.mem_momentum > 0.0f) CK(e->vqs.alloc(M * d * f));
+    CK(e->gz.alloc(M * std::max(e->gate_cols, 4) * f));
+    CK(e->lra.alloc(M * d * f));
+    CK(e->lrb.alloc(M * d * f));
     CK(e->qw.alloc(M * e->nh() * f));
     CK(e->qa.alloc(M * e->nh() * f));
     CK(e->eqkv.alloc(M * 3 * d * f));
@@ -474,6 +478,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         mp.proj = e->proj.as<float>();
         mp.ldp = pw;
         mp.gate_w = b.gate_w.as<float>(); mp.gate_cols = e->gate_cols; mp.gate_chunk = e->gate_chunk;
+        mp.z = e->gz.as<float>(); mp.lra = e->lra.as<float>(); mp.lrb = e->lrb.as<float>();
         mp.ba = b.ba.as<float>(); mp.bb = b.bb.as<float>(); mp.wa2 = b.wa2.as<float>(); mp.wb2 = b.wb2.as<float>();
         mp.off = b.off.as<float>();
         mp.vres = (c.value_residual && i > 0 && b.vres.p) ? b.vres.as<float>() : nullptr;
@@ -488,6 +493,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         prof_begin(e, "mem_prep");
         launch_mem_prep(st, mp);
         prof_end(e);
+        e->launches += 2;  // the two stages of the gate projections before it
         dbg(e, "ek", i, mp.e, M, d); dbg(e, "v", i, mp.v, M, d); dbg(e, "w", i, mp.w, M, d); dbg(e, "ah", i, mp.ah, M, d);
         dbg(e, "qg", i, mp.qg, M, d); dbg(e, "ex", i, mp.ex, M, d); dbg(e, "qw", i, mp.qw, M, nh); dbg(e, "qa", i, mp.qa, M, nh);
         MemHeadsArgs mh{};
@@ -895,12 +901,13 @@ int ava_engine_finalize(ava_engine* e) {
         for (const F& f : {F{&b.ba, "hebb.ba"}, F{&b.bb, "hebb.bb"}, F{&b.wa2, "hebb.wa2"}, F{&b.wb2, "hebb.wb2"}, F{&b.off, "hebb.off"}})
             if ((rc = upload_f32(e, *f.d, p + f.n, true))) return rc;
         {
-            // the gates' first-stage projections side by side [d][wa | wb | wa1 | wb1 | zero padding]: one staged stream
+            // the gates' first-stage projections side by side [d][wa1 | wb1 | wa | wb | zero padding]: one staged stream
+            // (the low-rank parts first, so that each row's z1 values start on a 16-byte boundary)
             const int nh = e->nh(), rk = c.gate_rank, ncp = e->gate_cols;
             std::vector<float> gw((size_t)c.d * ncp, 0.0f);
             struct G { const char* n; int w; };
             int c0 = 0;
-            for (const G& gpart : {G{"hebb.wa", nh}, G{"hebb.wb", nh}, G{"hebb.wa1", rk}, G{"hebb.wb1", rk}}) {
+            for (const G& gpart : {G{"hebb.wa1", rk}, G{"hebb.wb1", rk}, G{"hebb.wa", nh}, G{"hebb.wb", nh}}) {
                 auto it = e->host_f32.find(p + gpart.n);
                 if (it == e->host_f32.end()) return e->fail(AVA_ERR_MISSING, "missing tensor %s%s", p.c_str(), gpart.n);
                 for (int j = 0; j < c.d; ++j)

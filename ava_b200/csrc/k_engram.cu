@@ -17,10 +17,19 @@ namespace {
 
 constexpr int ENG_THREADS = 256;
 
+// Loads written as volatile asm stay where the source puts them: the compiler otherwise sinks a batch of loads down to
+// their uses (to save registers) and an ordered chain then waits for each load in turn.  Plain ld.global, not the
+// read-only path: the block reads the slot it has just written.
 template <bool BF16>
 __device__ __forceinline__ float kv_load(const void* base, size_t i) {
-    if (BF16) return bf16_to_f(__ldg(reinterpret_cast<const uint16_t*>(base) + i));
-    return __ldg(reinterpret_cast<const float*>(base) + i);
+    if (BF16) {
+        unsigned short h;
+        asm volatile("ld.global.u16 %0, [%1];" : "=h"(h) : "l"(reinterpret_cast<const uint16_t*>(base) + i));
+        return bf16_to_f(h);
+    }
+    float v;
+    asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(reinterpret_cast<const float*>(base) + i));
+    return v;
 }
 template <bool BF16>
 __device__ __forceinline__ void kv_store(void* base, size_t i, float v) {
@@ -34,7 +43,8 @@ __device__ __forceinline__ void kv_store(void* base, size_t i, float v) {
 template <bool BF16>
 __device__ __forceinline__ void kv_load8(const void* base, size_t i, float* out) {
     if (BF16) {
-        const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + i);
+        uint4 u;
+        asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "l"(reinterpret_cast<const uint16_t*>(base) + i));
         const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -42,8 +52,9 @@ __device__ __forceinline__ void kv_load8(const void* base, size_t i, float* out)
             out[2 * k + 1] = bits_to_f(w[k] & 0xffff0000u);
         }
     } else {
-        const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + i);
-        const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + i + 4);
+        float4 a, b;
+        asm volatile("ld.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w) : "l"(reinterpret_cast<const float*>(base) + i));
+        asm volatile("ld.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w) : "l"(reinterpret_cast<const float*>(base) + i + 4));
         out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
         out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
     }
@@ -82,7 +93,7 @@ __device__ __forceinline__ float pv_run(const void* v, size_t first, int hs_rt, 
 // hg heads per block; grid = M * (nh / hg).  HS > 0: the head size, known at compile time (the loops unroll without
 // bounds checks); HS == 0: any head size that is a multiple of 8.
 template <bool BF16, int HS>
-__global__ void __launch_bounds__(ENG_THREADS, HS ? 4 : 1) engram_kernel(const EngramArgs a, int hg) {
+__global__ void __launch_bounds__(ENG_THREADS, HS ? 3 : 1) engram_kernel(const EngramArgs a, int hg) {
     pdl_enter();
     extern __shared__ float sm[];
     const int d = a.d, hs = HS ? HS : a.hs, nh = d / hs, cap = a.cap;

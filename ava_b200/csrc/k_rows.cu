@@ -5,6 +5,8 @@
 // taken in that order by one thread, and the small f32 products follow gemm's one-row order (fstep.rs:17-23,222-257):
 // out = w0 * x0, then fma(w_j, x_j, out).  The chains are short next to the memory traffic of the step, and keeping
 // them makes every value the bits of the reference's arithmetic.
+#include <algorithm>
+
 #include "ava_math.h"
 #include "kernels.cuh"
 
@@ -14,35 +16,67 @@ namespace {
 
 constexpr float NORM_EPS = 1e-5f;  // src/model.rs:36
 
+// Shared-memory loads that stay where they are written: the compiler otherwise sinks a prefetch down to its use and the
+// ordered chains below then wait for every load in turn.
+__device__ __forceinline__ float lds1(const float* p) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+    return v;
+}
+__device__ __forceinline__ float4 lds4(const float* p) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+    return v;
+}
+
 // sum of x[i]^2 one after another from 0; x in shared memory, 16-byte aligned.  Eight values are fetched ahead of the
 // chain so that the loads overlap; the order of the additions is the reference's.
 __device__ __forceinline__ float sumsq_seq(const float* x, int n) {
     float s = 0.0f;
     int i = 0;
-    for (; i + 8 <= n; i += 8) {
-        const float4 a = *reinterpret_cast<const float4*>(x + i), b = *reinterpret_cast<const float4*>(x + i + 4);
-        const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-        float p[8];
+    if (n >= 8) {
+        float4 a = lds4(x), b = lds4(x + 4);
+        for (; i + 16 <= n; i += 8) {
+            const float4 na = lds4(x + i + 8), nb = lds4(x + i + 12);
+            const float p[8] = {mul(a.x, a.x), mul(a.y, a.y), mul(a.z, a.z), mul(a.w, a.w), mul(b.x, b.x), mul(b.y, b.y), mul(b.z, b.z), mul(b.w, b.w)};
 #pragma unroll
-        for (int k = 0; k < 8; ++k) p[k] = mul(v[k], v[k]);
+            for (int k = 0; k < 8; ++k) s = add(s, p[k]);
+            a = na;
+            b = nb;
+        }
+        const float p[8] = {mul(a.x, a.x), mul(a.y, a.y), mul(a.z, a.z), mul(a.w, a.w), mul(b.x, b.x), mul(b.y, b.y), mul(b.z, b.z), mul(b.w, b.w)};
 #pragma unroll
         for (int k = 0; k < 8; ++k) s = add(s, p[k]);
+        i += 8;
     }
     for (; i < n; ++i) s = add(s, mul(x[i], x[i]));
     return s;
 }
 
-// sum of a[i] * b[i] one after another from 0 (shared memory, 16-byte aligned)
+// sum of a[i] * b[i] one after another from 0 (shared memory, 16-byte aligned); the next eight products are formed
+// while the chain adds the eight before
 __device__ __forceinline__ float dot_seq(const float* a, const float* b, int n) {
     float s = 0.0f;
     int i = 0;
-    for (; i + 8 <= n; i += 8) {
-        const float4 a0 = *reinterpret_cast<const float4*>(a + i), a1 = *reinterpret_cast<const float4*>(a + i + 4);
-        const float4 b0 = *reinterpret_cast<const float4*>(b + i), b1 = *reinterpret_cast<const float4*>(b + i + 4);
-        const float p[8] = {mul(a0.x, b0.x), mul(a0.y, b0.y), mul(a0.z, b0.z), mul(a0.w, b0.w),
-                            mul(a1.x, b1.x), mul(a1.y, b1.y), mul(a1.z, b1.z), mul(a1.w, b1.w)};
+    if (n >= 8) {
+        auto prods = [&](int at, float* p) {
+            const float4 a0 = lds4(a + at), a1 = lds4(a + at + 4), b0 = lds4(b + at), b1 = lds4(b + at + 4);
+            p[0] = mul(a0.x, b0.x); p[1] = mul(a0.y, b0.y); p[2] = mul(a0.z, b0.z); p[3] = mul(a0.w, b0.w);
+            p[4] = mul(a1.x, b1.x); p[5] = mul(a1.y, b1.y); p[6] = mul(a1.z, b1.z); p[7] = mul(a1.w, b1.w);
+        };
+        float p[8];
+        prods(0, p);
+        for (; i + 16 <= n; i += 8) {
+            float np[8];
+            prods(i + 8, np);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) s = add(s, p[k]);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) p[k] = np[k];
+        }
 #pragma unroll
         for (int k = 0; k < 8; ++k) s = add(s, p[k]);
+        i += 8;
     }
     for (; i < n; ++i) s = add(s, mul(a[i], b[i]));
     return s;
@@ -137,113 +171,231 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 
 // ---------------------------------------------------------------------------------------------------- memory: gates
 // src/model/fstep/arch.rs:685-803 for one row per block of threads.
+// Stage one of the gates: z [M][ncp] = h . [wa1 | wb1 | wa | wb] in gemm's one-row order (row 0's product, then fma
+// down the rows: an fma chain from -0).  One thread per (row, column), a few rows per block so that the block's copy of
+// the weights serves them all.  The weights come through a ring of S chunks of CR rows in shared memory (cp.async, every
+// thread copies); all S are requested before the first is used, so the chain meets the memory latency once.
+__global__ void gate_z_kernel(const float* __restrict__ hin, const float* __restrict__ gate_w, int M, int d, int ncp, int CR, int RB, int S,
+                              float* __restrict__ z) {
+    pdl_enter();
+    extern __shared__ __align__(16) float sm[];
+    float* h = sm;                       // [RB][d]
+    float* stage = sm + (size_t)RB * d;  // [S][CR * ncp]
+    const int tid = threadIdx.x, T = blockDim.x;
+    const int row0 = blockIdx.x * RB, rows = min(RB, M - row0);
+    const int nchunk = d / CR, per_chunk4 = CR * ncp / 4;
+    auto fetch = [&](int c) {  // one commit group per chunk, empty past the end so that the group count stays in step
+        if (c < nchunk) {
+            float* dst = stage + (size_t)(c % S) * CR * ncp;
+            const float* src = gate_w + (size_t)c * CR * ncp;
+            for (int i = tid; i < per_chunk4; i += T)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst + 4 * i)), "l"(src + 4 * i) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    for (int c = 0; c < S; ++c) fetch(c);
+    for (int i = tid; i < rows * d / 4; i += T)
+        reinterpret_cast<float4*>(h)[i] = reinterpret_cast<const float4*>(hin + (size_t)row0 * d)[i];
+    const int rb = tid / ncp, col = tid - rb * ncp;
+    const bool live = rb < rows;
+    float out = -0.0f;  // fma(w, x, -0) is the plain rounded product: the chain's first term
+    for (int c = 0; c < nchunk; ++c) {
+        // groups are committed in chunk order; at most S - 1 newer ones may still be in flight
+        switch (S - 1) {
+            case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+            case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+            case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+            case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+            case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+            case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+            case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+            default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
+        }
+        __syncthreads();
+        if (live) {
+            const float* wcol = stage + (size_t)(c % S) * CR * ncp + col;
+            const float* hx = h + (size_t)rb * d + c * CR;
+            float w8[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w8[i] = lds1(wcol + (size_t)i * ncp);
+            float4 x0 = lds4(hx), x1 = lds4(hx + 4);
+            for (int r0 = 0; r0 < CR; r0 += 8) {
+                // the next eight rows' weights and inputs are on their way while this eight joins the chain
+                float nx[8];
+                const int nr = r0 + 8 < CR ? r0 + 8 : r0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) nx[i] = lds1(wcol + (size_t)(nr + i) * ncp);
+                const float4 y0 = lds4(hx + nr), y1 = lds4(hx + nr + 4);
+                const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) out = fma(w8[i], xv[i], out);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) w8[i] = nx[i];
+                x0 = y0;
+                x1 = y1;
+            }
+        }
+        __syncthreads();
+        fetch(c + S);  // the slot just read takes the chunk S further on
+    }
+    if (live) z[(size_t)(row0 + rb) * ncp + col] = out;
+}
+
+// gemm's one-row product of k terms, the terms given by functions of j (src/model/fstep.rs:222-257)
+template <typename W, typename X>
+__device__ __forceinline__ float chain_k(int k, W w, X x) {
+    if (k == 0) return 0.0f;
+    if (k == 1) return mul(w(0), x(0));
+    if (k == 2) return add(mul(w(1), x(1)), mul(w(0), x(0)));
+    float out = mul(w(0), x(0));
+    for (int j = 1; j < k; ++j) out = fma(w(j), x(j), out);
+    return out;
+}
+
+// Stage two: lra [M][d] = z1a . wa2, lrb = z1b . wb2 (rank-long chains).  A block owns 16 columns of both matrices:
+// each thread keeps its column's weights in registers (RK > 0: the rank, known at compile time) and walks the rows,
+// sixteen threads side by side on different rows; the z1 values of the block's tile of rows sit in shared memory.
+constexpr int LR_COLS = 16, LR_LANES = 16, LR_ROWS = 256;
+template <int RK>
+__global__ void __launch_bounds__(LR_COLS* LR_LANES) lowrank_kernel(const float* __restrict__ z, int ncp, int za_col, int zb_col, int rk_rt,
+                                                                     const float* __restrict__ wa2, const float* __restrict__ wb2, int M_all, int d,
+                                                                     float* __restrict__ lra, float* __restrict__ lrb) {
+    pdl_enter();
+    extern __shared__ __align__(16) float sm[];
+    const int rk = RK ? RK : rk_rt;
+    // this block's tile of rows
+    const int row0 = blockIdx.y * LR_ROWS, M = min(LR_ROWS, M_all - row0);
+    z += (size_t)row0 * ncp;
+    lra += (size_t)row0 * d;
+    lrb += (size_t)row0 * d;
+    float* zs = sm;  // [M][2 rk]: z1a | z1b of every row of the tile
+    const int tid = threadIdx.x, col = tid % LR_COLS, lane_r = tid / LR_COLS;
+    const int c = blockIdx.x * LR_COLS + col;
+    if ((2 * rk) % 4 == 0 && za_col == 0 && zb_col == rk) {
+        // z1a | z1b are the first 2 rk values of each row of z (rows are 16-byte aligned): every copy in flight at once
+        const int per_row4 = 2 * rk / 4;
+        for (int i = tid; i < M * per_row4; i += blockDim.x) {
+            const int r = i / per_row4, j4 = i - r * per_row4;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(zs + 4 * i)), "l"(z + (size_t)r * ncp + 4 * j4)
+                         : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else {
+        for (int i = tid; i < M * 2 * rk; i += blockDim.x) {
+            const int r = i / (2 * rk), j = i - r * 2 * rk;
+            zs[i] = z[(size_t)r * ncp + (j < rk ? za_col + j : zb_col + j - rk)];
+        }
+    }
+    __syncthreads();
+    if (c >= d) return;
+    if (RK >= 4 && RK % 4 == 0) {
+        float wa[RK ? RK : 1], wb[RK ? RK : 1];
+#pragma unroll
+        for (int j = 0; j < RK; ++j) {
+            wa[j] = __ldg(wa2 + (size_t)j * d + c);
+            wb[j] = __ldg(wb2 + (size_t)j * d + c);
+        }
+        for (int r = lane_r; r < M; r += 2 * LR_LANES) {
+            // two rows and both gates at once: four independent chains
+            const int r2 = r + LR_LANES;
+            const float* z0 = zs + (size_t)r * 2 * RK;
+            const float* z1 = zs + (size_t)(r2 < M ? r2 : r) * 2 * RK;
+            float a0 = -0.0f, b0 = -0.0f, a1 = -0.0f, b1 = -0.0f;  // fma from -0: the chain's first term is the plain product
+#pragma unroll
+            for (int j = 0; j < RK; j += 4) {
+                const float4 za0 = lds4(z0 + j), zb0 = lds4(z0 + RK + j), za1 = lds4(z1 + j), zb1 = lds4(z1 + RK + j);
+                const float xa0[4] = {za0.x, za0.y, za0.z, za0.w}, xb0[4] = {zb0.x, zb0.y, zb0.z, zb0.w};
+                const float xa1[4] = {za1.x, za1.y, za1.z, za1.w}, xb1[4] = {zb1.x, zb1.y, zb1.z, zb1.w};
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    a0 = fma(wa[j + u], xa0[u], a0);
+                    b0 = fma(wb[j + u], xb0[u], b0);
+                    a1 = fma(wa[j + u], xa1[u], a1);
+                    b1 = fma(wb[j + u], xb1[u], b1);
+                }
+            }
+            lra[(size_t)r * d + c] = a0;
+            lrb[(size_t)r * d + c] = b0;
+            if (r2 < M) {
+                lra[(size_t)r2 * d + c] = a1;
+                lrb[(size_t)r2 * d + c] = b1;
+            }
+        }
+    } else {
+        for (int r = lane_r; r < M; r += LR_LANES) {
+            const float* zr = zs + (size_t)r * 2 * rk;
+            lra[(size_t)r * d + c] = chain_k(rk, [&](int j) { return __ldg(wa2 + (size_t)j * d + c); }, [&](int j) { return zr[j]; });
+            lrb[(size_t)r * d + c] = chain_k(rk, [&](int j) { return __ldg(wb2 + (size_t)j * d + c); }, [&](int j) { return zr[rk + j]; });
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------- memory: gates
+// src/model/fstep/arch.rs:685-803 for one row per block of threads, after the two stages of the gate projections.
 __global__ void mem_prep_kernel(const MemPrepArgs a) {
     pdl_enter();
     extern __shared__ __align__(16) float sm[];
-    const int d = a.d, hs = a.hs, nh = d / hs, rk = a.rank;
+    const int d = a.d, hs = a.hs, nh = d / hs;
     const int r = blockIdx.x, tid = threadIdx.x, T = blockDim.x;
-    float* h = sm;            // [d]
-    float* q = h + d;         // [d] raw, then unit
+    float* q = sm;            // [d] raw, then unit
     float* kr = q + d;        // [d] raw key
     float* ek = kr + d;       // [d] raw erase key, then unit
     float* wv = ek + d;       // [d] w = k b
     float* ahv = wv + d;      // [d] ah = e (b alpha)
-    float* lra = ahv + d;     // [d]
-    float* lrb = lra + d;     // [d]
-    float* inv_q = lrb + d;   // [nh]
+    float* inv_q = ahv + d;   // [nh]
     float* inv_k = inv_q + nh;
     float* inv_e = inv_k + nh;
-    float* za = inv_e + nh;
-    float* zb = za + nh;
-    float* z1a = zb + nh;     // [rk]
-    float* z1b = z1a + rk;    // [rk]
 
     const float* pr = a.proj + (size_t)r * a.ldp;
     for (int c = tid; c < d; c += T) {
-        h[c] = a.h[(size_t)r * d + c];
         q[c] = pr[c];
         const float kk = pr[d + c];
         kr[c] = kk;
         ek[c] = add(kk, pr[3 * d + c]);
     }
     __syncthreads();
-    // The ordered chains.  The gate projections h . [wa | wb | wa1 | wb1] (gemm's one-row order: row 0's product,
-    // then fma down the rows) take one thread per output column; their weights come through shared memory a chunk of
-    // rows at a time (every thread copies, cp.async, double buffered), so a chain never waits on global memory.  The
-    // three sums of squares per head run in the warps after them while the first chunk is in flight.
-    {
-        const int ncols = 2 * nh + 2 * rk, ncp = a.gate_cols;  // real and padded column count
-        const int CR = a.gate_chunk, nchunk = d / CR;
-        float* stage = z1b + rk;                               // [2][CR * ncp], 16-byte aligned (see the launcher)
-        stage += (4 - ((5 * nh + 2 * rk) & 3)) & 3;
-        const int per_chunk4 = CR * ncp / 4;
-        auto fetch = [&](int c) {
-            float* dst = stage + (size_t)(c & 1) * CR * ncp;
-            const float* src = a.gate_w + (size_t)c * CR * ncp;
-            for (int i = tid; i < per_chunk4; i += T)
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst + 4 * i)), "l"(src + 4 * i) : "memory");
-            asm volatile("cp.async.commit_group;" ::: "memory");
-        };
-        fetch(0);
-        float out = -0.0f;  // fma(w, x, -0) is the plain rounded product: the chain's first term
-        const int first_sq = ((ncols + 31) / 32) * 32;         // sums of squares start at a warp boundary
-        for (int c = 0; c < nchunk; ++c) {
-            if (c + 1 < nchunk) {
-                fetch(c + 1);
-                asm volatile("cp.async.wait_group 1;" ::: "memory");
-            } else {
-                asm volatile("cp.async.wait_group 0;" ::: "memory");
-            }
-            __syncthreads();
-            if (tid < ncols) {
-                const float* wcol = stage + (size_t)(c & 1) * CR * ncp + tid;
-                const float* hx = h + c * CR;
-                for (int r0 = 0; r0 < CR; r0 += 8) {
-                    float w8[8];
+    // the gate phase's inputs for this thread's first channels are requested now, so that their latency passes while the
+    // sums of squares run
+    constexpr int PRE = 3;
+    float p_lra[PRE], p_lrb[PRE], p_off[PRE], p_v[PRE], p_v0[PRE];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) w8[i] = wcol[(size_t)(r0 + i) * ncp];
-                    const float4 x0 = *reinterpret_cast<const float4*>(hx + r0), x1 = *reinterpret_cast<const float4*>(hx + r0 + 4);
-                    const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) out = fma(w8[i], xv[i], out);
-                }
-            } else if (c == 0) {
-                for (int it = tid - first_sq; it >= 0 && it < 3 * nh; it += T - first_sq) {
-                    const int which = it / nh, e = it % nh;
-                    const float* src = (which == 0 ? q : which == 1 ? kr : ek) + e * hs;
-                    (which == 0 ? inv_q : which == 1 ? inv_k : inv_e)[e] = inv_l2_seq(src, hs);
-                }
-            }
-            __syncthreads();
-        }
-        if (tid < nh) za[tid] = add(out, a.ba[tid]);
-        else if (tid < 2 * nh) zb[tid - nh] = add(out, a.bb[tid - nh]);
-        else if (tid < 2 * nh + rk) z1a[tid - 2 * nh] = out;
-        else if (tid < ncols) z1b[tid - 2 * nh - rk] = out;
+    for (int u = 0; u < PRE; ++u) {
+        const int c = tid + u * T;
+        const bool in = c < d;
+        const size_t o = (size_t)r * d + (in ? c : 0);
+        p_lra[u] = in ? __ldg(a.lra + o) : 0.0f;
+        p_lrb[u] = in ? __ldg(a.lrb + o) : 0.0f;
+        p_off[u] = in ? __ldg(a.off + c) : 0.0f;
+        p_v[u] = in ? pr[2 * d + c] : 0.0f;
+        p_v0[u] = (in && !a.first && a.vres) ? a.v_first[o] : 0.0f;
+    }
+    // the three sums of squares per head, each in order by one thread; spread over the warps
+    for (int it = tid; it < 3 * nh * 32; it += T) {
+        if (it & 31) continue;
+        const int which = (it >> 5) / nh, e = (it >> 5) % nh;
+        const float* src = (which == 0 ? q : which == 1 ? kr : ek) + e * hs;
+        (which == 0 ? inv_q : which == 1 ? inv_k : inv_e)[e] = inv_l2_seq(src, hs);
     }
     __syncthreads();
-    for (int c = tid; c < d; c += T) {
-        lra[c] = gemv_col(z1a, rk, a.wa2 + c, d);
-        lrb[c] = gemv_col(z1b, rk, a.wb2 + c, d);
-    }
-    __syncthreads();
+    const float* zr = a.z + (size_t)r * a.gate_cols;
     bool bad = false;
-    for (int c = tid; c < d; c += T) {
+    auto gates = [&](int c, float in_lra, float in_lrb, float in_off, float v, float v0) {
         const int e = c / hs;
         const size_t o = (size_t)r * d + c;
-        const float la = log_sigmoid(add(add(za[e], a.off[c]), lra[c]));
-        const float be = add(mul(sigmoid(add(zb[e], lrb[c])), 2.0f), 0.0f);
+        const float za = add(zr[2 * a.rank + e], a.ba[e]), zb = add(zr[2 * a.rank + nh + e], a.bb[e]);
+        const float la = log_sigmoid(add(add(za, in_off), in_lra));
+        const float be = add(mul(sigmoid(add(zb, in_lrb)), 2.0f), 0.0f);
         const float ex = expf_(la);
         const float qn = mul(q[c], inv_q[e]);
         const float kn = mul(kr[c], inv_k[e]);
         const float en = mul(ek[c], inv_e[e]);
-        float v = pr[2 * d + c];
         if (a.first) {
             a.v_first[o] = v;
         } else if (a.vres) {
             // (1 + p0) v + p1 v0 (src/model/fstep/arch.rs:697-702)
             const float p0 = add(mul(a.vres[0], 1.0f), 1.0f);
-            v = add(mul(v, p0), mul(a.v_first[o], a.vres[1]));
+            v = add(mul(v, p0), mul(v0, a.vres[1]));
         }
         const float w = mul(kn, be);
         const float ah = mul(en, mul(be, ex));
@@ -259,16 +411,27 @@ __global__ void mem_prep_kernel(const MemPrepArgs a) {
         q[c] = qn;
         wv[c] = w;
         ahv[c] = ah;
+    };
+#pragma unroll
+    for (int u = 0; u < PRE; ++u) {
+        const int c = tid + u * T;
+        if (c < d) gates(c, p_lra[u], p_lrb[u], p_off[u], p_v[u], p_v0[u]);
+    }
+    for (int c = tid + PRE * T; c < d; c += T) {
+        const size_t o = (size_t)r * d + c;
+        gates(c, a.lra[o], a.lrb[o], a.off[c], pr[2 * d + c], (!a.first && a.vres) ? a.v_first[o] : 0.0f);
     }
     if (bad) atomicOr(a.status, ST_NONFINITE);
     __syncthreads();
-    // q.w and q.ah, each summed in order from 0 (src/model/fstep/arch.rs:789-797)
-    for (int role = tid; role < 2 * nh; role += T) {
-        const int e = role % nh;
-        const float* b = role < nh ? wv : ahv;
-        (role < nh ? a.qw : a.qa)[(size_t)r * nh + e] = dot_seq(q + e * hs, b + e * hs, hs);
+    // q.w and q.ah, each summed in order from 0 (src/model/fstep/arch.rs:789-797); one thread per sum, in separate warps
+    for (int it = tid; it < 2 * nh * 32; it += T) {
+        if (it & 31) continue;
+        const int role = it >> 5, e = role % nh;
+        const float* bvec = role < nh ? wv : ahv;
+        (role < nh ? a.qw : a.qa)[(size_t)r * nh + e] = dot_seq(q + e * hs, bvec + e * hs, hs);
     }
 }
+
 
 // ---------------------------------------------------------------------------------------------------- memory: output
 // head norm, then the silu output gate (src/model/fstep/arch.rs:842-852)
@@ -452,7 +615,29 @@ void launch_rmsnorm(cudaStream_t st, const float* x, const float* gain, int M, i
 
 void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a) {
     const int nh = a.d / a.hs;
-    const size_t smem = ((size_t)8 * a.d + 5 * nh + 2 * a.rank + 4 + 2 * (size_t)a.gate_chunk * a.gate_cols) * sizeof(float);
+    // stage one: a few rows per block share the staged weights
+    {
+        const int RB = std::max(1, 256 / a.gate_cols), threads = ((RB * a.gate_cols + 31) / 32) * 32;
+        // as many chunks of the weights in flight as shared memory holds (all of them at d = 768)
+        const size_t chunk = (size_t)a.gate_chunk * a.gate_cols * sizeof(float), rows_b = (size_t)RB * a.d * sizeof(float);
+        const int S = (int)std::max<size_t>(1, std::min<size_t>({(size_t)(a.d / a.gate_chunk), (size_t)8, (220 * 1024 - rows_b) / chunk}));
+        const size_t smem = rows_b + S * chunk;
+        opt_in_smem(gate_z_kernel, smem);
+        launch_k(gate_z_kernel, dim3((a.M + RB - 1) / RB), dim3(threads), smem, st, a.h, a.gate_w, a.M, a.d, a.gate_cols, a.gate_chunk, RB, S, a.z);
+    }
+    // stage two
+    {
+        const size_t smem = (size_t)std::min(a.M, LR_ROWS) * 2 * a.rank * sizeof(float);
+        const dim3 grid((a.d + LR_COLS - 1) / LR_COLS, (a.M + LR_ROWS - 1) / LR_ROWS), block(LR_COLS * LR_LANES);
+        if (a.rank == 32) {
+            opt_in_smem(lowrank_kernel<32>, smem);
+            launch_k(lowrank_kernel<32>, grid, block, smem, st, a.z, a.gate_cols, 0, a.rank, a.rank, a.wa2, a.wb2, a.M, a.d, a.lra, a.lrb);
+        } else {
+            opt_in_smem(lowrank_kernel<0>, smem);
+            launch_k(lowrank_kernel<0>, grid, block, smem, st, a.z, a.gate_cols, 0, a.rank, a.rank, a.wa2, a.wb2, a.M, a.d, a.lra, a.lrb);
+        }
+    }
+    const size_t smem = ((size_t)5 * a.d + 3 * nh + 4) * sizeof(float);
     opt_in_smem(mem_prep_kernel, smem);
     launch_k(mem_prep_kernel, dim3(a.M), dim3(256), smem, st, a);
 }

@@ -111,9 +111,11 @@ struct MemPrepArgs {
     const float* h;      // [M, d] normed input
     const float* proj;   // [M, ldp]: q | k | v | e | (g)
     int ldp;
-    const float* gate_w; // [d][gate_cols]: wa | wb | wa1 | wb1 side by side, columns padded with zeros to a multiple of 4
+    const float* gate_w; // [d][gate_cols]: wa1 | wb1 | wa | wb side by side, columns padded with zeros to a multiple of 4
     int gate_cols;       // padded column count (at most 256: one chain per thread)
     int gate_chunk;      // rows staged per copy; divides d, a multiple of 8
+    float* z;            // [M][gate_cols] work: h . gate_w (stage one)
+    float *lra, *lrb;    // [M, d] work: the low-rank parts of the two gates (stage two)
     const float *ba, *bb, *wa2, *wb2, *off;
     const float* vres;   // [2] or nullptr
     float* v_first;      // [M, d]: written when first, read when vres
@@ -125,6 +127,7 @@ struct MemPrepArgs {
     float mom;
     uint32_t* status;
 };
+// three launches: the gates' first projection, their low-rank second stage, then everything per row
 void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a);
 
 struct MemHeadsArgs {
