@@ -242,6 +242,127 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) q8_gemm_kernel(const Ge
     }
 }
 
+// ---------------------------------------------------------------------------------------------------- few rows
+// The same product when there are only a few rows (one sequence talking, a handful generating): the tiled kernel above
+// then spends its time on 48 rounds of load-sync-multiply per output, one after another.  Here a block takes 64 output
+// columns and ALL K rows of their weights: the K x 64 int8 tile is requested at once (cp.async, every thread copies, one
+// latency for the lot) and sits in shared memory; then one thread per (row pair, four columns) walks k = 0, 1, ... with
+// its 8 accumulators, weights read from shared memory, inputs from a staged copy of the rows.  The sums are the same
+// fma chains in the same order, so the same bits.
+constexpr int RT_COLS = 64, RT_THREADS = 256, RT_ROWS = 32;  // rows per block: 16 row lanes x 2 rows
+
+template <int EPI>
+__global__ void __launch_bounds__(RT_THREADS) q8_resident_kernel(const GemmArgs g) {
+    pdl_enter();
+    extern __shared__ __align__(16) unsigned char rt_smem[];
+    int8_t* wt = reinterpret_cast<int8_t*>(rt_smem);                            // [K][64]
+    float* xs = reinterpret_cast<float*>(rt_smem + (size_t)g.K * RT_COLS);      // [rows][K]
+    const int tid = threadIdx.x;
+    const int n0 = blockIdx.x * RT_COLS, m0 = blockIdx.y * RT_ROWS;
+    const int rows = min(RT_ROWS, g.M - m0);
+    // the weights: K rows of 64 bytes, 16 bytes per copy
+    for (int i = tid; i < g.K * 4; i += RT_THREADS) {
+        const int k = i >> 2, q = i & 3;
+        if (n0 + q * 16 < g.N)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(wt + (size_t)k * RT_COLS + q * 16)),
+                         "l"(g.W + (size_t)k * g.ldw + n0 + q * 16)
+                         : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    // the rows' inputs
+    for (int i = tid; i < rows * (g.K / 4); i += RT_THREADS) {
+        const int r = i / (g.K / 4), k4 = i - r * (g.K / 4);
+        reinterpret_cast<float4*>(xs + (size_t)r * g.K)[k4] = *reinterpret_cast<const float4*>(g.A + (size_t)(m0 + r) * g.lda + 4 * k4);
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    const int cg = tid & 15, rl = tid >> 4;  // four columns cg * 4 .., rows rl and rl + 16
+    const int c0 = n0 + cg * 4;
+    if (c0 >= g.N || rl >= rows) return;
+    const bool two = rl + 16 < rows;
+    const float* x0 = xs + (size_t)rl * g.K;
+    const float* x1 = xs + (size_t)(two ? rl + 16 : rl) * g.K;
+    const int* wp = reinterpret_cast<const int*>(wt + cg * 4);
+    float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+    auto lds_w = [&](int k) {
+        int w;
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w) : "r"((uint32_t)__cvta_generic_to_shared(wp + (size_t)k * (RT_COLS / 4))));
+        return w;
+    };
+    auto lds_x = [&](const float* p) {
+        float4 v;
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+        return v;
+    };
+    // four k at a time, the next four on their way
+    int w[4];
+    float4 xa = lds_x(x0), xb = lds_x(x1);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) w[u] = lds_w(u);
+    for (int k = 0; k < g.K; k += 4) {
+        const int kn = k + 4 < g.K ? k + 4 : k;
+        int nw[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) nw[u] = lds_w(kn + u);
+        const float4 nxa = lds_x(x0 + kn), nxb = lds_x(x1 + kn);
+        const float va[4] = {xa.x, xa.y, xa.z, xa.w}, vb[4] = {xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            float f[4];
+            widen4(w[u], f);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                a0[j] = fma(va[u], f[j], a0[j]);
+                a1[j] = fma(vb[u], f[j], a1[j]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) w[u] = nw[u];
+        xa = nxa;
+        xb = nxb;
+    }
+    const float4 sc = *reinterpret_cast<const float4*>(g.scale + c0);
+    const float scv[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        if (h == 1 && !two) break;
+        const int r = m0 + rl + 16 * h;
+        const float* acc = h ? a1 : a0;
+        float o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = mul(acc[j], scv[j]);
+        if (EPI == EPI_LIF) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) lif_update(g.lif, r, c0 + j, g.N, o[j]);
+        } else {
+            float4* d4 = reinterpret_cast<float4*>(g.C + (size_t)r * g.ldc + c0);
+            if (EPI == EPI_ADD) {
+                const float4 x = *d4;
+                o[0] = add(x.x, o[0]); o[1] = add(x.y, o[1]); o[2] = add(x.z, o[2]); o[3] = add(x.w, o[3]);
+            }
+            *d4 = make_float4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
+// false: shape not covered (the tile and the rows must fit shared memory; N a multiple of 16; 16-byte aligned rows)
+bool launch_resident(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {
+    const int rows = a.M < RT_ROWS ? a.M : RT_ROWS;
+    const size_t smem = (size_t)a.K * RT_COLS + (size_t)rows * a.K * sizeof(float);
+    if (smem > 220 * 1024 || a.N % 16 || a.K % 4 || a.ldw % 16 || a.lda % 4) return false;
+    dim3 grid((a.N + RT_COLS - 1) / RT_COLS, (a.M + RT_ROWS - 1) / RT_ROWS);
+    auto go = [&](auto kernel) {
+        if (smem > 32 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch_k(kernel, grid, dim3(RT_THREADS), smem, st, a);
+    };
+    switch (epi) {
+        case EPI_STORE: go(q8_resident_kernel<EPI_STORE>); break;
+        case EPI_ADD: go(q8_resident_kernel<EPI_ADD>); break;
+        case EPI_LIF: go(q8_resident_kernel<EPI_LIF>); break;
+    }
+    return true;
+}
+
 // ---------------------------------------------------------------------------------------------------- event sums
 // A mostly-zero row (the LIF spikes, the k-WTA'd MLP units) sums over its non-zero inputs only, in increasing order:
 // fma(0, q, acc) = acc exactly, so this is the dense sum bit for bit (src/int8.rs:10-13; -0 counts as zero, NaN does
@@ -359,6 +480,8 @@ __global__ void lif_kernel(const float* cur, const LifParams p, int M, int d) {
 }  // namespace
 
 int g_gemm_force = 0;  // tuning override (0: choose by shape)
+int g_resident_max_rows = 16;  // up to this many rows the resident-tile kernel takes the dense products (measured: 19-21 us
+                                // against 23 us for the tiled kernel at 1-8 rows, slower from 32 rows on)
 int g_pdl = 1;         // programmatic dependent launch on every kernel of the step (kernels.cuh)
 
 void launch_q8_gemm(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int sm_count) {
@@ -367,8 +490,13 @@ void launch_q8_gemm(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int sm
         case 2: return launch_tile<64, 64, 8, 4>(st, a, epi);
         case 3: return launch_tile<32, 64, 4, 4>(st, a, epi);
         case 4: return launch_tile<32, 64, 4, 2>(st, a, epi);
+        case 6:
+            if (launch_resident(st, a, epi)) return;
+            break;
         default: break;
     }
+    // a few rows: the whole-K tile in shared memory, one latency instead of one per k-tile
+    if (g_gemm_force == 0 && a.M <= g_resident_max_rows && launch_resident(st, a, epi)) return;
     // Measured on B200 at 256 rows (the machine is short of warps at this batch, so the choice is about filling SMs):
     // very wide products take 64x64 tiles of 8x4, wide ones 64x64 of 4x4, then 32x64 of 4x4, narrow ones 32x64 of 4x2.
     const long tiles64 = (long)((a.N + 63) / 64) * ((a.M + 63) / 64);
