@@ -1,4 +1,4 @@
-"""One long sequence with its engram store split by position over several GPUs (BASELINE configuration 4).
+"""One long sequence with its engram store split by position over several GPUs (benchmark configuration 4).
 
 One process per GPU, each with its own engine (replicated weights).  The membranes and the fast-synapse state live on
 rank 0 and are stepped there; every rank keeps the keys and values of the positions it owns and, per decoded token,

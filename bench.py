@@ -1,7 +1,7 @@
 """Benchmark of the block step: batch-256 decode of the Ava-0.4-shaped model on N B200s.
 
 A "step" is one decoded token for every resident sequence (256 per GPU; sequences are independent, so each rank steps
-its own 256 with no data-path collective: weak scaling).  Workload = BASELINE configuration 1: each sequence has read a
+its own 256 with no data-path collective: weak scaling).  Workload = benchmark configuration 1: each sequence has read a
 prompt and is decoding with its membranes, thresholds, 12 fast-synapse 768x768 f32 matrices and the block-6 bf16 KV
 store resident in HBM.  The KV length over the timed steps is centred on the configuration's mean decode context
 (1024-token prompt + 1024 decode tokens: mean 1535.5), reached by untimed steps.
@@ -116,7 +116,7 @@ def run_reference(args, cfg, rank):
     line = {"metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations x int8 weights",
             "data": "synthetic", "impl": "reference",
-            "config": {"workload": "BASELINE config 1 (Ava-0.4-shaped decode), bounded CPU sample", "rows": rows},
+            "config": {"workload": "benchmark configuration 1 (Ava-0.4-shaped decode), bounded CPU sample", "rows": rows},
             "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -170,7 +170,7 @@ def main():
     ap.add_argument("--rows", type=int, default=ROWS_PER_GPU, help="sequences per GPU")
     ap.add_argument("--ctx", type=int, default=MEAN_CTX, help="KV length the timed steps are centred on")
     ap.add_argument("--small", action="store_true", help="a small model and batch (profiling captures, not a bench value)")
-    ap.add_argument("--scaled", action="store_true", help="BASELINE config 3: 24 blocks, d 2048, wide 8192, vocab 32768 (use --rows 128: an 8-GPU share of 1024 sequences)")
+    ap.add_argument("--scaled", action="store_true", help="benchmark configuration 3: 24 blocks, d 2048, wide 8192, vocab 32768 (use --rows 128: an 8-GPU share of 1024 sequences)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--prefill-tokens", type=int, default=1024, help="tokens per row of the prompt-reading sample (config 2: 8192)")
     args = ap.parse_args()
@@ -311,9 +311,9 @@ def main():
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations x int8 weights, f32 state, bf16 KV",
         "data": "synthetic",
-        "config": {"workload": "BASELINE config 1: Ava-0.4-shaped decode (12 blocks, d 768, wide 3072, kWTA 768, vocab 16384, one 768x768 f32 "
+        "config": {"workload": "benchmark configuration 1: Ava-0.4-shaped decode (12 blocks, d 768, wide 3072, kWTA 768, vocab 16384, one 768x768 f32 "
                                "fast-synapse matrix per block, bf16 engram of 12x64 in block 6)" if not (args.small or args.scaled) else
-                   ("small profiling case" if args.small else "BASELINE config 3: scaled Ava (24 blocks, d 2048, wide 8192, kWTA 2048, vocab 32768, one "
+                   ("small profiling case" if args.small else "benchmark configuration 3: scaled Ava (24 blocks, d 2048, wide 8192, kWTA 2048, vocab 32768, one "
                     "2048x2048 f32 fast-synapse matrix per block)"),
                    "rows_per_gpu": rows, "kv_len_timed": [prompt + W, prompt + W + K], "l2": "per-step inputs (state "
                    f"{state.nbytes / 1e9:.2f} GB per GPU) are larger than L2", "sequences": "independent, sharded by rank, no collective"},
@@ -361,7 +361,7 @@ def main():
                              "parity": "dense products on tcgen05 tensor cores: exact products (3 bf16 limbs x bf16 weights), f32 sums in the "
                                        "tensor core's order; agrees with the reference to ~2e-6 of each sum's magnitudes, not bit for bit",
                              "kernel_ms_per_step": {k: round(v[1] / 4, 4) for k, v in sorted(fprof.items(), key=lambda kv: -kv[1][1])}}
-    # ---- prompt reading (BASELINE config 2's shape: 64 rows per GPU, chunks of 256 tokens), a bounded sample of it
+    # ---- prompt reading (benchmark configuration 2's shape: 64 rows per GPU, chunks of 256 tokens), a bounded sample of it
     if not args.small and not args.scaled:
         line["prefill"] = measure_prefill(model, cfg, local, world, dist, rows=64, tokens=args.prefill_tokens, chunk=256, seed0=50_000 + first)
     if rank == 0 and not args.no_cpu and not args.small:

@@ -3,7 +3,7 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29533 \
         tests/multi_gpu_split_kv.py [--prompt 2048] [--decode 32]
 
-One long sequence (BASELINE configuration 4 at a reduced prompt length): rank 0 reads the prompt, the engram store is
+One long sequence (benchmark configuration 4 at a reduced prompt length): rank 0 reads the prompt, the engram store is
 dealt out by position, then every decoded token takes a broadcast of q,k,v and an all-gather of the partial softmax
 statistics.  Rank 0 checks its logits against the CPU oracle's one-pass read (1e-4 relative) and prints a JSON line
 with the decode rate.  Not collected by pytest (no test_ prefix): the single-GPU emulation of the same path is

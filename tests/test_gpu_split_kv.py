@@ -1,4 +1,4 @@
-"""The engram store of one long sequence split by position over several ranks (BASELINE configuration 4), checked on
+"""The engram store of one long sequence split by position over several ranks (benchmark configuration 4), checked on
 ONE GPU: two ranks are two engines in this process on the same device, and the two collectives (broadcast of q,k,v,
 all-gather of the partial softmax statistics) are plain copies between their buffers.  The kernels of the two ranks run
 one after another, never waiting on each other.  The real NCCL run on 2+ GPUs is tests/multi_gpu_split_kv.py."""

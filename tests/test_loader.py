@@ -115,7 +115,9 @@ def test_damaged_files_are_refused(tmp_path, damage):
         engine.Checkpoint(str(tmp_path / "absent.safetensors"))
 
 
-REF_AVA_M = "/root/reference/release/ava-m"
+# the reference project, when it is mounted beside this repository (or where AVA_REFERENCE_DIR says)
+REF_AVA_M = os.path.join(os.environ.get("AVA_REFERENCE_DIR", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "..", "reference")),
+                         "release", "ava-m")
 
 
 @pytest.mark.skipif(not os.path.isfile(os.path.join(REF_AVA_M, "model.safetensors")), reason="the reference's released Ava-M is not on this machine")
