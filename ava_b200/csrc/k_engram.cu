@@ -205,6 +205,188 @@ __global__ void __launch_bounds__(ENG_THREADS, HS ? 3 : 1) engram_kernel(const E
     }
 }
 
+// ---------------------------------------------------------------------------------------------------- streamed read
+// The same read for the benchmark's store (bf16, heads of 64) with the keys and values streamed through shared memory:
+// tiles are requested with cp.async one tile ahead of the arithmetic, so the chains never wait on global memory and the
+// kernel runs at the rate the store can be read.  Keys: 256 per tile (one per thread), each key's eight 16-byte pieces
+// stored at piece ^ (key & 7) so that a thread reading its own key's 128 bytes meets no bank conflict.  Values: 64 keys
+// of all four heads per tile, read by one thread per output channel.  Every sum is the one the kernel above takes, in
+// the same order: the same bits.
+constexpr int ES_KT = 256;            // keys per key tile (one head)
+constexpr int ES_VT = 64;             // keys per value tile (four heads)
+constexpr int ES_TILE = ES_KT * 128;  // bytes of a tile: 256 keys x 128 B = 4 heads x 64 keys x 128 B
+
+__device__ __forceinline__ void cp16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint4 lds_u4(const void* p) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+    return v;
+}
+__device__ __forceinline__ float lds_bf16(const uint16_t* p) {
+    unsigned short h;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+    return bf16_to_f(h);
+}
+
+__global__ void __launch_bounds__(ENG_THREADS, 2) engram_stream_kernel(const EngramArgs a) {
+    pdl_enter();
+    extern __shared__ __align__(16) unsigned char es_smem[];
+    constexpr int HS = 64, HG = 4;
+    const int d = a.d, nh = d / HS, cap = a.cap, groups = nh / HG;
+    const int r = blockIdx.x / groups, h0 = (blockIdx.x % groups) * HG;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* qkv = a.qkv + (size_t)r * 3 * d;
+    const size_t row_base = (size_t)r * nh * cap * HS;
+    uint16_t* Kst = reinterpret_cast<uint16_t*>(a.k);
+    uint16_t* Vst = reinterpret_cast<uint16_t*>(a.v);
+
+    int n0 = a.n[r];
+    const int start = a.start[r];
+    if (n0 >= cap) {
+        if (tid == 0) atomicOr(a.status, ST_ENGRAM_FULL);
+        n0 = cap - 1;
+    }
+    const int n = n0 + 1;
+    int slot = start + n0;
+    if (slot >= cap) slot -= cap;
+    {   // this token's key and value join the store: thread = (head, channel)
+        const int hh = h0 + (tid >> 6), dd = tid & 63;
+        const size_t o = row_base + ((size_t)hh * cap + slot) * HS + dd;
+        Kst[o] = f_to_bf16(qkv[d + h0 * HS + tid]);
+        Vst[o] = f_to_bf16(qkv[2 * d + h0 * HS + tid]);
+    }
+    unsigned char* tile0 = es_smem;                       // two tiles
+    float* q = reinterpret_cast<float*>(es_smem + 2 * ES_TILE);  // [256]
+    float* mx = q + HG * HS;                              // [4]
+    float* den = mx + HG;                                 // [4]
+    float* sc = den + HG;                                 // [4][n]
+    q[tid] = qkv[h0 * HS + tid];
+    __syncthreads();  // the stores above are visible to this block's copies below
+
+    const int n1 = min(n, cap - start);  // keys j < n1 sit at slots start + j, the others at slots j - n1
+    auto slot_of = [&](int j) { return j < n1 ? start + j : j - n1; };
+
+    // ---- scores: tiles of 256 keys of one head; tile index t = head * tiles_k + tile
+    const int tiles_k = (n + ES_KT - 1) / ES_KT, total_k = HG * tiles_k;
+    auto fetch_k = [&](int t) {
+        unsigned char* dst = tile0 + (size_t)(t & 1) * ES_TILE;
+        const int g = t / tiles_k, j0 = (t % tiles_k) * ES_KT;
+        const uint16_t* head = Kst + row_base + (size_t)(h0 + g) * cap * HS;
+        // 256 keys x 8 pieces: thread copies piece (i & 7) of key (i >> 3)
+        for (int i = tid; i < ES_KT * 8; i += ENG_THREADS) {
+            const int kk = i >> 3, c = i & 7, j = j0 + kk;
+            if (j < n) cp16(dst + kk * 128 + ((c ^ (kk & 7)) << 4), head + (size_t)slot_of(j) * HS + c * 8);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const float scale = (float)(1.0 / sqrt((double)HS));
+    fetch_k(0);
+    for (int t = 0; t < total_k; ++t) {
+        if (t + 1 < total_k) {
+            fetch_k(t + 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const int g = t / tiles_k, j = (t % tiles_k) * ES_KT + tid;
+        if (j < n) {
+            const unsigned char* key = tile0 + (size_t)(t & 1) * ES_TILE + tid * 128;
+            const float* qh = q + g * HS;
+            uint4 u[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) u[c] = lds_u4(key + ((c ^ (tid & 7)) << 4));
+            float s = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint32_t w[4] = {u[c].x, u[c].y, u[c].z, u[c].w};
+#pragma unroll
+                for (int k2 = 0; k2 < 4; ++k2) {
+                    const float lo = bits_to_f(w[k2] << 16), hi = bits_to_f(w[k2] & 0xffff0000u);
+                    const int x = c * 8 + 2 * k2;
+                    s = x == 0 ? mul(lo, qh[0]) : fma(lo, qh[x], s);
+                    s = fma(hi, qh[x + 1], s);
+                }
+            }
+            sc[(size_t)g * n + j] = add(mul(s, scale), 0.0f);
+        }
+        __syncthreads();
+    }
+    // ---- softmax per head, as above
+    for (int g = warp; g < HG; g += ENG_THREADS / 32) {
+        float m = -INFINITY;
+        for (int j = lane; j < n; j += 32) m = fmaxf(m, sc[(size_t)g * n + j]);
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) mx[g] = m;
+    }
+    __syncthreads();
+    // the first value tile is requested now, so that it arrives while the weights are formed
+    const int tiles_v = (n + ES_VT - 1) / ES_VT;
+    auto fetch_v = [&](int t) {
+        unsigned char* dst = tile0 + (size_t)(t & 1) * ES_TILE;
+        const int j0 = t * ES_VT;
+        // 4 heads x 64 keys x 8 pieces
+        for (int i = tid; i < HG * ES_VT * 8; i += ENG_THREADS) {
+            const int c = i & 7, kk = (i >> 3) & (ES_VT - 1), g = i >> 9, j = j0 + kk;
+            if (j < n) cp16(dst + ((size_t)(g * ES_VT + kk) * 128) + (c << 4), Vst + row_base + ((size_t)(h0 + g) * cap + slot_of(j)) * HS + c * 8);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch_v(0);
+    for (int g = 0; g < HG; ++g) {
+        const float m = mx[g];
+        for (int j = tid; j < n; j += ENG_THREADS) sc[(size_t)g * n + j] = expf_(sub(sc[(size_t)g * n + j], m));
+    }
+    __syncthreads();
+    if (tid < HG) {
+        float s = 0.0f;
+        const float* p = sc + (size_t)tid * n;
+        for (int j = 0; j < n; ++j) s = add(s, p[j]);
+        den[tid] = s;
+    }
+    __syncthreads();
+    for (int g = 0; g < HG; ++g) {
+        const float dn = den[g];
+        for (int j = tid; j < n; j += ENG_THREADS) sc[(size_t)g * n + j] = div(sc[(size_t)g * n + j], dn);
+    }
+    __syncthreads();
+    // ---- o = p . V: thread = (head, channel), the chain over the keys in order (src/model/fstep.rs:222-257 with k = n)
+    const int g = tid >> 6, dd = tid & 63;
+    const float* p = sc + (size_t)g * n;
+    float out = 0.0f, first = 0.0f, second = 0.0f;
+    for (int t = 0; t < tiles_v; ++t) {
+        if (t + 1 < tiles_v) {
+            fetch_v(t + 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const uint16_t* vt = reinterpret_cast<const uint16_t*>(tile0 + (size_t)(t & 1) * ES_TILE) + (size_t)g * ES_VT * HS + dd;
+        const int j0 = t * ES_VT, cnt = min(ES_VT, n - j0);
+        float v16[16];
+        for (int b = 0; b < cnt; b += 16) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v16[i] = lds_bf16(vt + (size_t)(b + i < cnt ? b + i : b) * HS);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int j = j0 + b + i;
+                if (b + i < cnt) {
+                    if (j == 0) first = v16[i];
+                    else if (j == 1) second = v16[i];
+                    if (n > 2) out = j == 0 ? mul(v16[i], p[0]) : fma(v16[i], p[j], out);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (n == 1) out = mul(first, p[0]);
+    else if (n == 2) out = add(mul(second, p[1]), mul(first, p[0]));
+    a.o[(size_t)r * d + h0 * HS + tid] = out;
+}
+
 // ---------------------------------------------------------------------------------------------------- long stores
 // For a store too long for one block's shared memory, or split by position over several GPUs, the read is taken in
 // segments: each block takes one (row, head group, segment of keys) and leaves per head the partial softmax statistics
@@ -388,6 +570,16 @@ bool launch_engram(cudaStream_t st, const EngramArgs& a, int n_max) {
     const size_t smem = ((size_t)hg * a.hs + 2 * hg + (size_t)hg * n_max) * sizeof(float);
     if (smem > 227 * 1024 - 64) return false;
     const unsigned grid = (unsigned)(a.M * (nh / hg));
+    if (a.bf16 && a.hs == 64 && hg == 4) {
+        // the streamed form: two tiles of 32 KB beside the scores
+        const size_t ssmem = 2 * (size_t)ES_TILE + ((size_t)hg * a.hs + 2 * hg + (size_t)hg * n_max) * sizeof(float);
+        if (ssmem <= 227 * 1024 - 64) {
+            cudaFuncSetAttribute(engram_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ssmem);
+            launch_k(engram_stream_kernel, dim3(grid), dim3(ENG_THREADS), ssmem, st, a);
+            launch_k(engram_advance_kernel, dim3((a.M + 127) / 128), dim3(128), 0, st, a.n, a.start, a.M, a.cap, a.keep);
+            return true;
+        }
+    }
     auto go = [&](auto kernel) {
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         launch_k(kernel, dim3(grid), dim3(ENG_THREADS), smem, st, a, hg);

@@ -400,3 +400,29 @@ def test_fast_products_agree_to_rounding(orc_same_math, shape):
         assert np.array_equal(bits(gm.step(gs2, ids[:, 0])), bits(os2.step(ids[:, 0])))
     finally:
         orc.set_threads(1)
+
+
+@pytest.mark.parametrize("cap", [0, 300])
+def test_streamed_engram_read_bits(orc_same_math, cap):
+    """The streamed form of the engram read (bf16 store, four heads of 64 per block: the benchmark's kind of store) over
+    several tiles of keys, with and without the oldest-first cap (the ring then wraps): every logit and the store bit
+    for bit against the oracle."""
+    orc = orc_same_math
+    cfg = config.make(320, 256, 2, head_size=64, eng_block=1, eng_head_size=64, eng_store_bf16=1, eng_cap=cap, hidden=512)
+    gm, om = pair(orc, cfg, seed=5)
+    rows, T = 2, 700
+    ids = synth.token_ids(cfg["vocab"], rows, T, seed0=3)
+    gs, os_ = gm.state(rows, max_ctx=T + 4), om.state(rows)
+    orc.set_threads(4)
+    try:
+        for t in range(T):
+            lg = gm.step(gs, ids[:, t])
+            lo = os_.step(ids[:, t])
+            if t % 50 == 0 or t > T - 4 or t in (255, 256, 257, 299, 300, 301, 302):
+                assert np.array_equal(bits(lg), bits(lo)), (t, float(np.abs(lg - lo).max()))
+    finally:
+        orc.set_threads(1)
+    assert np.array_equal(bits(lg), bits(lo))
+    for name in ("eng.k", "eng.v", "lif.1.v"):
+        assert np.array_equal(bits(gs.get(1, name)), bits(os_.get(1, name))), name
+    assert gs.get(0, "eng.k").size == (cap if cap else T) * cfg["d"]
