@@ -270,14 +270,24 @@ __global__ void __launch_bounds__(ENG_THREADS, 2) engram_stream_kernel(const Eng
 
     // ---- scores: tiles of 256 keys of one head; tile index t = head * tiles_k + tile
     const int tiles_k = (n + ES_KT - 1) / ES_KT, total_k = HG * tiles_k;
+    const int pc = tid & 7, pk = tid >> 3;  // a thread copies piece pc of the keys pk, pk + 32, ... of a tile
     auto fetch_k = [&](int t) {
-        unsigned char* dst = tile0 + (size_t)(t & 1) * ES_TILE;
+        unsigned char* dst = tile0 + (size_t)(t & 1) * ES_TILE + pk * 128 + ((pc ^ (pk & 7)) << 4);  // (pk + 32 i) & 7 == pk & 7
         const int g = t / tiles_k, j0 = (t % tiles_k) * ES_KT;
-        const uint16_t* head = Kst + row_base + (size_t)(h0 + g) * cap * HS;
-        // 256 keys x 8 pieces: thread copies piece (i & 7) of key (i >> 3)
-        for (int i = tid; i < ES_KT * 8; i += ENG_THREADS) {
-            const int kk = i >> 3, c = i & 7, j = j0 + kk;
-            if (j < n) cp16(dst + kk * 128 + ((c ^ (kk & 7)) << 4), head + (size_t)slot_of(j) * HS + c * 8);
+        const uint16_t* head = Kst + row_base + (size_t)(h0 + g) * cap * HS + pc * 8;
+        const int last = min(j0 + ES_KT, n) - 1;
+        if (j0 >= n1 || last < n1) {
+            // the tile's keys sit in one straight run of slots
+            const uint16_t* src = head + (size_t)(slot_of(j0) + pk) * HS;
+#pragma unroll
+            for (int i = 0; i < ES_KT / 32; ++i)
+                if (j0 + pk + 32 * i <= last) cp16(dst + i * 32 * 128, src + (size_t)i * 32 * HS);
+        } else {
+#pragma unroll
+            for (int i = 0; i < ES_KT / 32; ++i) {
+                const int j = j0 + pk + 32 * i;
+                if (j <= last) cp16(dst + i * 32 * 128, head + (size_t)slot_of(j) * HS);
+            }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -298,16 +308,16 @@ __global__ void __launch_bounds__(ENG_THREADS, 2) engram_stream_kernel(const Eng
             uint4 u[8];
 #pragma unroll
             for (int c = 0; c < 8; ++c) u[c] = lds_u4(key + ((c ^ (tid & 7)) << 4));
-            float s = 0.0f;
+            float s = -0.0f;  // fma(k, q, -0) is the plain rounded product: the chain's first term
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 const uint32_t w[4] = {u[c].x, u[c].y, u[c].z, u[c].w};
+                const float4 qa = *reinterpret_cast<const float4*>(qh + c * 8), qb = *reinterpret_cast<const float4*>(qh + c * 8 + 4);
+                const float qv[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
 #pragma unroll
                 for (int k2 = 0; k2 < 4; ++k2) {
-                    const float lo = bits_to_f(w[k2] << 16), hi = bits_to_f(w[k2] & 0xffff0000u);
-                    const int x = c * 8 + 2 * k2;
-                    s = x == 0 ? mul(lo, qh[0]) : fma(lo, qh[x], s);
-                    s = fma(hi, qh[x + 1], s);
+                    s = fma(bits_to_f(w[k2] << 16), qv[2 * k2], s);
+                    s = fma(bits_to_f(w[k2] & 0xffff0000u), qv[2 * k2 + 1], s);
                 }
             }
             sc[(size_t)g * n + j] = add(mul(s, scale), 0.0f);
@@ -324,13 +334,18 @@ __global__ void __launch_bounds__(ENG_THREADS, 2) engram_stream_kernel(const Eng
     __syncthreads();
     // the first value tile is requested now, so that it arrives while the weights are formed
     const int tiles_v = (n + ES_VT - 1) / ES_VT;
+    const size_t head_stride = (size_t)cap * HS;
     auto fetch_v = [&](int t) {
-        unsigned char* dst = tile0 + (size_t)(t & 1) * ES_TILE;
-        const int j0 = t * ES_VT;
-        // 4 heads x 64 keys x 8 pieces
-        for (int i = tid; i < HG * ES_VT * 8; i += ENG_THREADS) {
-            const int c = i & 7, kk = (i >> 3) & (ES_VT - 1), g = i >> 9, j = j0 + kk;
-            if (j < n) cp16(dst + ((size_t)(g * ES_VT + kk) * 128) + (c << 4), Vst + row_base + ((size_t)(h0 + g) * cap + slot_of(j)) * HS + c * 8);
+        // 4 heads x 64 keys x 8 pieces: a thread copies piece pc of the keys pk and pk + 32 of every head
+        unsigned char* dst = tile0 + (size_t)(t & 1) * ES_TILE + pk * 128 + (pc << 4);
+        const int j0 = t * ES_VT, last = min(j0 + ES_VT, n) - 1;
+        const uint16_t* base = Vst + row_base + (size_t)h0 * head_stride + pc * 8;
+        const bool straight = j0 >= n1 || last < n1;
+        const int s0 = slot_of(j0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int gg = i >> 1, kk = pk + 32 * (i & 1), j = j0 + kk;
+            if (j <= last) cp16(dst + (gg * ES_VT + 32 * (i & 1)) * 128, base + gg * head_stride + (size_t)(straight ? s0 + kk : slot_of(j)) * HS);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -352,10 +367,12 @@ __global__ void __launch_bounds__(ENG_THREADS, 2) engram_stream_kernel(const Eng
         for (int j = tid; j < n; j += ENG_THREADS) sc[(size_t)g * n + j] = div(sc[(size_t)g * n + j], dn);
     }
     __syncthreads();
-    // ---- o = p . V: thread = (head, channel), the chain over the keys in order (src/model/fstep.rs:222-257 with k = n)
-    const int g = tid >> 6, dd = tid & 63;
-    const float* p = sc + (size_t)g * n;
-    float out = 0.0f, first = 0.0f, second = 0.0f;
+    // ---- o = p . V: the chain over the keys in order per output channel (src/model/fstep.rs:222-257 with k = n).  The
+    // first 128 threads take two channels each (one 32-bit load per key); all threads keep the tiles coming.
+    const int g = tid >> 5, pair = tid & 31;  // head and channel pair of a working thread (tid < 128)
+    const bool works = tid < 128;
+    const float* p = sc + (size_t)(works ? g : 0) * n;
+    float o0 = -0.0f, o1 = -0.0f;  // fma from -0: the first term is the plain product (n >= 3; n of 1 and 2 below)
     for (int t = 0; t < tiles_v; ++t) {
         if (t + 1 < tiles_v) {
             fetch_v(t + 1);
@@ -364,27 +381,55 @@ __global__ void __launch_bounds__(ENG_THREADS, 2) engram_stream_kernel(const Eng
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
-        const uint16_t* vt = reinterpret_cast<const uint16_t*>(tile0 + (size_t)(t & 1) * ES_TILE) + (size_t)g * ES_VT * HS + dd;
-        const int j0 = t * ES_VT, cnt = min(ES_VT, n - j0);
-        float v16[16];
-        for (int b = 0; b < cnt; b += 16) {
+        if (works) {
+            const uint32_t* vt = reinterpret_cast<const uint32_t*>(tile0 + (size_t)(t & 1) * ES_TILE) + (size_t)g * ES_VT * 32 + pair;
+            const int j0 = t * ES_VT, cnt = min(ES_VT, n - j0);
+            auto ldv = [&](int k) {
+                uint32_t w;
+                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w) : "r"((uint32_t)__cvta_generic_to_shared(vt + (size_t)k * 32)));
+                return w;
+            };
+            auto ldp = [&](int j) {
+                float v;
+                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"((uint32_t)__cvta_generic_to_shared(p + j)));
+                return v;
+            };
+            int b = 0;
+            for (; b + 16 <= cnt; b += 16) {
+                uint32_t w[16];
+                float pj[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v16[i] = lds_bf16(vt + (size_t)(b + i < cnt ? b + i : b) * HS);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const int j = j0 + b + i;
-                if (b + i < cnt) {
-                    if (j == 0) first = v16[i];
-                    else if (j == 1) second = v16[i];
-                    if (n > 2) out = j == 0 ? mul(v16[i], p[0]) : fma(v16[i], p[j], out);
+                for (int i = 0; i < 16; ++i) {
+                    w[i] = ldv(b + i);
+                    pj[i] = ldp(j0 + b + i);
                 }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    o0 = fma(bits_to_f(w[i] << 16), pj[i], o0);
+                    o1 = fma(bits_to_f(w[i] & 0xffff0000u), pj[i], o1);
+                }
+            }
+            for (; b < cnt; ++b) {
+                const uint32_t w = ldv(b);
+                const float pj = ldp(j0 + b);
+                o0 = fma(bits_to_f(w << 16), pj, o0);
+                o1 = fma(bits_to_f(w & 0xffff0000u), pj, o1);
             }
         }
         __syncthreads();
     }
-    if (n == 1) out = mul(first, p[0]);
-    else if (n == 2) out = add(mul(second, p[1]), mul(first, p[0]));
-    a.o[(size_t)r * d + h0 * HS + tid] = out;
+    if (works) {
+        if (n == 2) {
+            // two keys: (v1 p1) + (v0 p0), each product rounded (the reference's two-term form)
+            const uint16_t* v0 = Vst + row_base + ((size_t)(h0 + g) * cap + slot_of(0)) * HS + 2 * pair;
+            const uint16_t* v1 = Vst + row_base + ((size_t)(h0 + g) * cap + slot_of(1)) * HS + 2 * pair;
+            o0 = add(mul(bf16_to_f(v1[0]), p[1]), mul(bf16_to_f(v0[0]), p[0]));
+            o1 = add(mul(bf16_to_f(v1[1]), p[1]), mul(bf16_to_f(v0[1]), p[0]));
+        }
+        float* dst = a.o + (size_t)r * d + (h0 + g) * HS + 2 * pair;
+        dst[0] = o0;
+        dst[1] = o1;
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------- long stores
