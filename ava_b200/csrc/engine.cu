@@ -111,6 +111,7 @@ struct ava_engine {
     int ws_rows = 0, ws_logit_rows = 0;
     Dev x, h, proj, ve, vv, vw, vah, vqg, vex, vqs, qw, qa, yraw, y, eqkv, eo, u, act, streams, v_first, logits, tok, next, status;
     Dev gz, lra, lrb;  // the gates' stages: [rows][gate_cols], [rows][d] twice
+    Dev uniform;       // [rows] f64: the sampler's draws of one step
     uint32_t* status_host = nullptr;  // pinned
 
     bool prof = false;
@@ -303,6 +304,7 @@ int ensure_workspace(ava_engine* e, int rows, int logit_rows = 0) {
     CK(e->streams.alloc(c.dense ? (size_t)(c.n_blocks + 1) * M * d * f : 0));
     CK(e->tok.alloc(M * sizeof(uint32_t)));
     CK(e->next.alloc(M * sizeof(uint32_t)));
+    CK(e->uniform.alloc(M * sizeof(double)));
     e->ws_rows = rows;
     return AVA_OK;
 }
@@ -1163,6 +1165,25 @@ int ava_step_greedy(ava_engine* e, ava_state* s, const uint32_t* tok, uint32_t* 
         if (tok[r] >= (uint32_t)e->cfg.vocab) return e->fail(AVA_ERR_ARG, "token %u of row %d outside the vocabulary", tok[r], r);
     CK(cudaMemcpyAsync(e->tok.p, tok, s->rows * sizeof(uint32_t), cudaMemcpyHostToDevice, e->stream));
     if ((rc = step_device(e, s, e->tok.as<uint32_t>(), nullptr, e->next.as<uint32_t>(), false))) return rc;
+    CK(cudaMemcpyAsync(next, e->next.p, s->rows * sizeof(uint32_t), cudaMemcpyDeviceToHost, e->stream));
+    return finish(e);
+}
+
+int ava_step_sample(ava_engine* e, ava_state* s, const uint32_t* tok, float temperature, int32_t top_k, const double* uniform, uint32_t* next) {
+    if (!(temperature > 0.0f)) return ava_step_greedy(e, s, tok, next);
+    int rc = check_pair(e, s);
+    if (rc) return rc;
+    if (!tok || !next || !uniform) return e->fail(AVA_ERR_ARG, "null buffer");
+    for (int r = 0; r < s->rows; ++r)
+        if (tok[r] >= (uint32_t)e->cfg.vocab) return e->fail(AVA_ERR_ARG, "token %u of row %d outside the vocabulary", tok[r], r);
+    const int k = top_k < 1 ? 1 : top_k;
+    if (k > 1024 && k < e->cfg.vocab) return e->fail(AVA_NOT_APPLICABLE, "top_k above 1024: pick on the host (ava_step + ava_pick)");
+    CK(cudaMemcpyAsync(e->tok.p, tok, s->rows * sizeof(uint32_t), cudaMemcpyHostToDevice, e->stream));
+    CK(cudaMemcpyAsync(e->uniform.p, uniform, s->rows * sizeof(double), cudaMemcpyHostToDevice, e->stream));
+    if ((rc = step_device(e, s, e->tok.as<uint32_t>(), e->logits.as<float>(), nullptr, true))) return rc;
+    if (!launch_sample(e->stream, e->logits.as<float>(), s->rows, e->cfg.vocab, temperature, top_k, e->uniform.as<double>(), e->next.as<uint32_t>()))
+        return e->fail(AVA_NOT_APPLICABLE, "the sampler does not cover this vocabulary or top_k: pick on the host (ava_step + ava_pick)");
+    e->launches++;
     CK(cudaMemcpyAsync(next, e->next.p, s->rows * sizeof(uint32_t), cudaMemcpyDeviceToHost, e->stream));
     return finish(e);
 }

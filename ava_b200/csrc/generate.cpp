@@ -113,8 +113,17 @@ int ava_pick(const float* logits, int32_t vocab, float temperature, int32_t top_
     return AVA_OK;
 }
 
-int ava_generate(ava_engine* e, const uint32_t* prompts, const int32_t* prompt_len, int32_t n_prompts, int32_t max_new, int32_t batch_rows,
-                 int32_t max_ctx, uint32_t eos, ava_pick_fn pick, ava_stop_fn stop, void* user, uint32_t* out, int32_t* out_len) {
+namespace {
+struct Sampler {
+    float temperature;
+    int32_t top_k;
+    uint64_t* rng;
+};
+}  // namespace
+
+static int generate_impl(ava_engine* e, const uint32_t* prompts, const int32_t* prompt_len, int32_t n_prompts, int32_t max_new, int32_t batch_rows,
+                         int32_t max_ctx, uint32_t eos, ava_pick_fn pick, const Sampler* smp, ava_stop_fn stop, void* user, uint32_t* out,
+                         int32_t* out_len) {
     if (!e || !prompts || !prompt_len || n_prompts <= 0 || max_new < 0 || !out || !out_len) return AVA_ERR_ARG;
     std::vector<size_t> start((size_t)n_prompts);
     size_t at = 0;
@@ -141,7 +150,8 @@ int ava_generate(ava_engine* e, const uint32_t* prompts, const int32_t* prompt_l
         const std::vector<int> group(order.begin() + i, order.begin() + std::min(order.size(), i + (size_t)br));
         i += group.size();
         std::vector<StateOwner> parts;
-        std::vector<float> last((size_t)group.size() * (pick ? V : 0));
+        std::vector<float> last((size_t)group.size() * ((pick || smp) ? V : 0));
+        bool first_pick = smp != nullptr;  // the sampler's first token of a group comes from the prompt's logits on the host
         std::vector<uint32_t> greedy(group.size());
         for (size_t j = 0; j < group.size();) {
             const int len = prompt_len[group[j]];
@@ -156,7 +166,7 @@ int ava_generate(ava_engine* e, const uint32_t* prompts, const int32_t* prompt_l
             logits.resize(run * (size_t)V);
             if ((rc = ava_forward_with_state(e, st, ids.data(), len, 1, logits.data()))) return rc;
             for (size_t k = 0; k < run; ++k) {
-                if (pick) std::memcpy(&last[(j + k) * V], &logits[k * V], (size_t)V * sizeof(float));
+                if (pick || smp) std::memcpy(&last[(j + k) * V], &logits[k * V], (size_t)V * sizeof(float));
                 else greedy[j + k] = argmax_lowest(&logits[k * V], V);
             }
             j += run;
@@ -179,13 +189,22 @@ int ava_generate(ava_engine* e, const uint32_t* prompts, const int32_t* prompt_l
             std::vector<uint32_t> next;
             for (size_t k = 0; k < live.size(); ++k) {
                 const int r = live[k];
-                const uint32_t tok = pick ? pick(user, r, &last[k * V], V) : greedy[k];
+                uint32_t tok;
+                if (pick) {
+                    tok = pick(user, r, &last[k * V], V);
+                } else if (first_pick) {
+                    const int prc = ava_pick(&last[k * V], V, smp->temperature, smp->top_k, smp->rng, &tok, nullptr, nullptr);
+                    if (prc) return prc;
+                } else {
+                    tok = greedy[k];
+                }
                 if (tok == eos) continue;
                 out[(size_t)r * max_new + out_len[r]++] = tok;
                 if (stop && stop(user, r, out + (size_t)r * max_new, out_len[r])) continue;
                 keep.push_back((int32_t)k);
                 next.push_back(tok);
             }
+            first_pick = false;
             if (keep.empty() || step + 1 == max_new) break;
             if (keep.size() != live.size()) {
                 ava_state* sel = nullptr;
@@ -200,6 +219,12 @@ int ava_generate(ava_engine* e, const uint32_t* prompts, const int32_t* prompt_l
             if (pick) {
                 last.resize(next.size() * (size_t)V);
                 rc = ava_step(e, st.s, next.data(), last.data());
+            } else if (smp && smp->temperature > 0.0f) {
+                // the next pass picks for the live rows in order: their draws are taken now, in that order
+                std::vector<double> u(next.size());
+                for (double& v : u) v = (double)(splitmix_next(smp->rng) >> 11) / (double)(1ull << 53);
+                greedy.resize(next.size());
+                rc = ava_step_sample(e, st.s, next.data(), smp->temperature, smp->top_k, u.data(), greedy.data());
             } else {
                 greedy.resize(next.size());
                 rc = ava_step_greedy(e, st.s, next.data(), greedy.data());  // the arg-max is taken on the device
@@ -208,6 +233,19 @@ int ava_generate(ava_engine* e, const uint32_t* prompts, const int32_t* prompt_l
         }
     }
     return AVA_OK;
+}
+
+int ava_generate(ava_engine* e, const uint32_t* prompts, const int32_t* prompt_len, int32_t n_prompts, int32_t max_new, int32_t batch_rows,
+                 int32_t max_ctx, uint32_t eos, ava_pick_fn pick, ava_stop_fn stop, void* user, uint32_t* out, int32_t* out_len) {
+    return generate_impl(e, prompts, prompt_len, n_prompts, max_new, batch_rows, max_ctx, eos, pick, nullptr, stop, user, out, out_len);
+}
+
+int ava_generate_sampled(ava_engine* e, const uint32_t* prompts, const int32_t* prompt_len, int32_t n_prompts, int32_t max_new, int32_t batch_rows,
+                         int32_t max_ctx, uint32_t eos, float temperature, int32_t top_k, uint64_t* rng_state, ava_stop_fn stop, void* user,
+                         uint32_t* out, int32_t* out_len) {
+    if (!rng_state) return AVA_ERR_ARG;
+    const Sampler smp{temperature, top_k, rng_state};
+    return generate_impl(e, prompts, prompt_len, n_prompts, max_new, batch_rows, max_ctx, eos, nullptr, &smp, stop, user, out, out_len);
 }
 
 }  // extern "C"

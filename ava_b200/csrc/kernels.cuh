@@ -179,6 +179,9 @@ void launch_engram_combine(cudaStream_t st, const float* partial, int M, int nh,
 void launch_kwta(cudaStream_t st, const float* u, int M, int n, int k, int relu2, float* a);
 // x <- x + sum_j streams[j] * w[j] over the n_streams streams (the last one is x itself, stored first)
 void launch_dense_mix(cudaStream_t st, float* x, float* streams, const float* w, int n_streams, int64_t MD);
+// `diary::pick` for every row: softmax(logits / temperature), the top_k most likely, one draw with the row's uniform
+// number in [0, 1).  false: not covered (top_k above 1024, a vocabulary too large for shared memory, temperature <= 0).
+bool launch_sample(cudaStream_t st, const float* logits, int M, int V, float temperature, int top_k, const double* uniform, uint32_t* next);
 void launch_argmax(cudaStream_t st, const float* logits, int M, int V, uint32_t* next);
 void launch_math(cudaStream_t st, int which, const float* x, int64_t n, float* y);
 void launch_round_bf16(cudaStream_t st, const float* x, int64_t n, uint16_t* y);

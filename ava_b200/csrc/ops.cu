@@ -125,6 +125,20 @@ int ava_op_q8_tc_matmul(int device, const float* x, int32_t m, const int8_t* q, 
     return AVA_OK;
 }
 
+int ava_op_sample(int device, const float* logits, int32_t m, int32_t vocab, float temperature, int32_t top_k, const double* uniform, uint32_t* next) {
+    if (!logits || !uniform || !next || m <= 0 || vocab <= 0) return AVA_ERR_ARG;
+    int rc = begin(device);
+    if (rc) return rc;
+    Tmp dl, du, dn;
+    OCK(up(dl, logits, (size_t)m * vocab * 4));
+    OCK(up(du, uniform, (size_t)m * 8));
+    OCK(up(dn, nullptr, (size_t)m * 4));
+    if (!launch_sample(0, dl.as<float>(), m, vocab, temperature, top_k, du.as<double>(), dn.as<uint32_t>())) return AVA_NOT_APPLICABLE;
+    if ((rc = end_())) return rc;
+    OCK(cudaMemcpy(next, dn.p, (size_t)m * 4, cudaMemcpyDeviceToHost));
+    return AVA_OK;
+}
+
 int ava_op_rmsnorm(int device, const float* x, const float* gain, int32_t m, int32_t n, float* y) {
     if (!x || !gain || !y || m <= 0 || n <= 0) return AVA_ERR_ARG;
     int rc = begin(device);

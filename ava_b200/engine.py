@@ -104,6 +104,10 @@ def lib() -> C.CDLL:
         "ava_conv_path": ([C.c_char_p, C.c_char_p, C.c_char_p, C.c_int64], C.c_int),
         "ava_conv_save": ([C.c_char_p, C.c_char_p, vp], C.c_int),
         "ava_conv_load": ([vp, C.c_char_p, C.c_char_p, C.c_int32, C.POINTER(vp), i32p], C.c_int),
+        "ava_step_sample": ([vp, vp, u32p, C.c_float, C.c_int32, C.POINTER(C.c_double), u32p], C.c_int),
+        "ava_generate_sampled": ([vp, u32p, C.POINTER(C.c_int32), C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_uint32, C.c_float, C.c_int32,
+                                  C.POINTER(C.c_uint64), STOP_FN, vp, u32p, C.POINTER(C.c_int32)], C.c_int),
+        "ava_op_sample": ([C.c_int, fp, C.c_int32, C.c_int32, C.c_float, C.c_int32, C.POINTER(C.c_double), u32p], C.c_int),
         "ava_engine_config": ([vp], C.POINTER(AvaConfig)),
         "ava_splitmix64_next": ([C.POINTER(C.c_uint64)], C.c_uint64),
         "ava_pick": ([fp, C.c_int32, C.c_float, C.c_int32, C.POINTER(C.c_uint64), u32p, fp, fp], C.c_int),
@@ -147,7 +151,7 @@ EXPORTS = ("ava_engine_create ava_engine_destroy ava_last_error ava_engine_set_f
            "ava_state_rows ava_state_select ava_state_cat ava_state_seen ava_state_len ava_state_export "
            "ava_state_import ava_step ava_step_greedy ava_forward_with_state ava_step_device ava_prefill_device ava_state_set_kv_shard ava_shard_parts ava_split_step_begin ava_shard_partial ava_split_step_end ava_sync "
            "ava_engine_stream ava_engine_launches ava_engine_bytes ava_state_bytes ava_debug_keep ava_debug_width "
-           "ava_debug_get ava_engine_set_segmented_read ava_engine_set_fast_products ava_prof_enable ava_prof_read ava_prof_names ava_engine_fingerprint ava_state_engine ava_state_set_seen ava_state_save ava_state_load ava_ckpt_read_u32 ava_conv_path ava_conv_save ava_conv_load ava_engine_config ava_splitmix64_next ava_pick ava_generate ava_loader_error ava_ckpt_open ava_ckpt_close ava_ckpt_count ava_ckpt_find ava_ckpt_tensor ava_ckpt_read_f32 ava_arch_flags ava_config_from_ckpt ava_engine_load_ckpt ava_op_q8_matmul ava_op_q8_event_matmul ava_op_q8_tc_matmul ava_debug_mem_heads_timeline ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
+           "ava_debug_get ava_engine_set_segmented_read ava_engine_set_fast_products ava_prof_enable ava_prof_read ava_prof_names ava_engine_fingerprint ava_state_engine ava_state_set_seen ava_state_save ava_state_load ava_ckpt_read_u32 ava_conv_path ava_conv_save ava_conv_load ava_step_sample ava_generate_sampled ava_op_sample ava_engine_config ava_splitmix64_next ava_pick ava_generate ava_loader_error ava_ckpt_open ava_ckpt_close ava_ckpt_count ava_ckpt_find ava_ckpt_tensor ava_ckpt_read_f32 ava_arch_flags ava_config_from_ckpt ava_engine_load_ckpt ava_op_q8_matmul ava_op_q8_event_matmul ava_op_q8_tc_matmul ava_debug_mem_heads_timeline ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
            "ava_host_expf ava_host_logf ava_host_rsqrtf ava_op_math").split()
 
 
@@ -184,6 +188,16 @@ def pick(logits, temperature: float, top_k: int, rng: Rng | None, traced: bool =
     if rc != OK:
         raise EngineError(rc, "ava_pick: bad argument")
     return (tok.value, lp.value, slp.value) if traced else tok.value
+
+
+def op_sample(logits, temperature: float, top_k: int, uniform, device: int = 0) -> np.ndarray:
+    """The device sampler on rows of host logits (one uniform number per row)."""
+    a = _f32(logits)
+    a2 = a.reshape(-1, a.shape[-1])
+    u = np.ascontiguousarray(uniform, np.float64).reshape(-1)
+    out = np.empty(a2.shape[0], np.uint32)
+    _rc(lib().ava_op_sample(device, _p(a2), a2.shape[0], a2.shape[1], temperature, top_k, _p(u, C.POINTER(C.c_double)), _p(out, u32p)))
+    return out
 
 
 def _loader_check(rc):
@@ -391,6 +405,39 @@ class Model:
         logits = np.empty((st.rows, self.cfg["vocab"]), np.float32)
         self._check(lib().ava_step(self.h, st.h, _p(tok, u32p), _p(logits)))
         return logits
+
+    def step_sample(self, st: "State", tok, temperature: float, top_k: int, uniform) -> np.ndarray:
+        """One step with every row's next token drawn on the device (`diary::pick` with the row's uniform number)."""
+        tok = np.ascontiguousarray(tok, np.uint32).reshape(-1)
+        u = np.ascontiguousarray(uniform, np.float64).reshape(-1)
+        assert tok.size == st.rows == u.size
+        nxt = np.empty(st.rows, np.uint32)
+        self._check(lib().ava_step_sample(self.h, st.h, _p(tok, u32p), temperature, top_k, _p(u, C.POINTER(C.c_double)), _p(nxt, u32p)))
+        return nxt
+
+    def generate_sampled(self, prompts, max_new: int, temperature: float, top_k: int, rng: "Rng", batch_rows: int = 256, eos: int = 256,
+                         stop_fn=None, max_ctx: int = 0):
+        """`state::generate` with `diary::pick(logits, temperature, top_k, rng)` as the pick, the draws taken on the device."""
+        lens = np.array([len(p) for p in prompts], np.int32)
+        flat = np.ascontiguousarray(np.concatenate([np.asarray(p, np.uint32) for p in prompts]))
+        out = np.zeros((len(prompts), max(max_new, 1)), np.uint32)
+        out_len = np.zeros(len(prompts), np.int32)
+        errors = []
+
+        def _stop(_user, r, toks, n):
+            try:
+                return int(bool(stop_fn(r, [int(toks[i]) for i in range(n)])))
+            except Exception as ex:
+                errors.append(ex)
+                return 1
+
+        cs = STOP_FN(_stop) if stop_fn is not None else C.cast(None, STOP_FN)
+        rc = lib().ava_generate_sampled(self.h, _p(flat, u32p), _p(lens, i32p), len(prompts), max_new, batch_rows, max_ctx, eos, temperature, top_k,
+                                        C.byref(rng.state), cs, None, _p(out, u32p), _p(out_len, i32p))
+        if errors:
+            raise errors[0]
+        self._check(rc)
+        return [out[r, :out_len[r]].tolist() for r in range(len(prompts))]
 
     def step_greedy(self, st: "State", tok) -> np.ndarray:
         tok = np.ascontiguousarray(tok, np.uint32).reshape(-1)

@@ -259,6 +259,11 @@ uint64_t ava_splitmix64_next(uint64_t* state);
  * temperature 1; sample_logp (may be NULL): ln p(token) under the sampler, 0 for a greedy pick. */
 int ava_pick(const float* logits, int32_t vocab, float temperature, int32_t top_k, uint64_t* rng_state, uint32_t* token, float* logp,
              float* sample_logp);
+/* One step with the next token of every row drawn on the device: `diary::pick` with the row's uniform number
+ * uniform[r] in [0, 1) (what `(next_u64 >> 11) / 2^53` gives), the same token ava_pick draws from the same logits and
+ * number.  No logits leave the device.  temperature <= 0: the greedy step.  AVA_NOT_APPLICABLE when top_k is above
+ * 1024 (and below the vocabulary) or the vocabulary does not fit the sampler's shared memory (about 50,000). */
+int ava_step_sample(ava_engine* e, ava_state* s, const uint32_t* tok, float temperature, int32_t top_k, const double* uniform, uint32_t* next);
 /* The reference's `pick` and `stop` closures: the token for prompt `prompt_index` given its logits; whether the row
  * stops after the tokens written so far. */
 typedef uint32_t (*ava_pick_fn)(void* user, int32_t prompt_index, const float* logits, int32_t vocab);
@@ -271,6 +276,12 @@ typedef int (*ava_stop_fn)(void* user, int32_t prompt_index, const uint32_t* tok
  * length).  out [n_prompts][max_new], out_len [n_prompts]. */
 int ava_generate(ava_engine* e, const uint32_t* prompts, const int32_t* prompt_len, int32_t n_prompts, int32_t max_new, int32_t batch_rows,
                  int32_t max_ctx, uint32_t eos, ava_pick_fn pick, ava_stop_fn stop, void* user, uint32_t* out, int32_t* out_len);
+/* The same loop with `diary::pick(logits, temperature, top_k, rng)` as the pick, one generator for all rows stepped in
+ * the order the reference's loop calls it (the live rows of a group in order, every step): the tokens are those of
+ * ava_generate with such a callback, but after the prompt the draws are taken on the device (ava_step_sample). */
+int ava_generate_sampled(ava_engine* e, const uint32_t* prompts, const int32_t* prompt_len, int32_t n_prompts, int32_t max_new, int32_t batch_rows,
+                         int32_t max_ctx, uint32_t eos, float temperature, int32_t top_k, uint64_t* rng_state, ava_stop_fn stop, void* user,
+                         uint32_t* out, int32_t* out_len);
 
 /* ---- single operators on host buffers (the S1 operator seam and the per-op kernels, for parity tests) ---------- */
 
@@ -285,6 +296,9 @@ int ava_op_q8_event_matmul(int device, const float* x, int32_t m, const int8_t* 
  * AVA_NOT_APPLICABLE.  reps > 0 and ms_per_launch != NULL: also times reps launches of the product kernel. */
 int ava_op_q8_tc_matmul(int device, const float* x, int32_t m, const int8_t* q, const float* scale, int32_t din, int32_t dout, float* y,
                         int32_t reps, float* ms_per_launch);
+/* The device sampler alone (the kernel behind ava_step_sample) on m rows of host logits: next[r] is the token ava_pick
+ * draws from logits[r] with the uniform number uniform[r].  temperature > 0. */
+int ava_op_sample(int device, const float* logits, int32_t m, int32_t vocab, float temperature, int32_t top_k, const double* uniform, uint32_t* next);
 /* `fstep::rmsnorm` (src/model/fstep.rs:207-220) on m rows of n. */
 int ava_op_rmsnorm(int device, const float* x, const float* gain, int32_t m, int32_t n, float* y);
 /* `fstep::arch::lif` (src/model/fstep/arch.rs:173-228) on m rows of d; theta/rho/gain/a0/a1 may be NULL. */

@@ -88,3 +88,44 @@ def test_arguments(model):
         raise KeyError("from the callback")
     with pytest.raises(KeyError):
         model.generate([[1, 2, 3]], 4, pick_fn=boom)
+
+
+@pytest.mark.parametrize("temperature,top_k,vocab", [(1.0, 40, 16384), (0.7, 5, 4096), (1.3, 1, 500), (1.0, 1024, 2000), (0.9, 100000, 700), (0.02, 40, 16384)])
+def test_device_sampler_draws_what_the_host_sampler_draws(temperature, top_k, vocab):
+    """The sampler kernel against ava_pick on the same logits and the same uniform numbers: the same tokens, ties at the
+    top and at the cut included."""
+    rng = np.random.default_rng(top_k + vocab)
+    rows = 24
+    lg = (rng.normal(size=(rows, vocab)) * 3).astype(np.float32)
+    lg[1, 10:14] = lg[1].max() + 1.0                       # ties among the most likely
+    lg[2] = np.round(lg[2])                                # many ties everywhere (and at the top_k cut)
+    lg[3] = 0.0                                            # all equal: index order decides
+    lg[4, 7] = 80.0                                        # one token takes all the mass
+    gen = engine.Rng(77)
+    states, u = [], []
+    for r in range(rows):
+        states.append(gen.state.value)
+        u.append((gen.next_u64() >> 11) / float(1 << 53))
+    got = engine.op_sample(lg, temperature, top_k, u)
+    for r in range(rows):
+        want = engine.pick(lg[r], temperature, top_k, engine.Rng(states[r]))
+        assert got[r] == want, (r, int(got[r]), want)
+
+
+def test_generate_sampled_equals_the_callback_form(model):
+    prompts = prompts_of(model.cfg, [6, 6, 3, 9, 6])
+    for batch_rows in (8, 2):
+        rng = engine.Rng(5)
+        want = model.generate(prompts, 12, batch_rows=batch_rows, eos=1 << 30, pick_fn=lambda r, lg: engine.pick(lg, 0.8, 16, rng))
+        rng2 = engine.Rng(5)
+        got = model.generate_sampled(prompts, 12, 0.8, 16, rng2, batch_rows=batch_rows, eos=1 << 30)
+        assert got == want
+        assert rng2.state.value == rng.state.value       # the same number of draws
+    # an EOS that rows meet on the way, and a stop rule
+    eos = want[0][4]
+    rng, rng2 = engine.Rng(9), engine.Rng(9)
+    stop = lambda r, toks: len(toks) >= 3 + r
+    want = model.generate(prompts, 12, eos=eos, pick_fn=lambda r, lg: engine.pick(lg, 0.8, 16, rng), stop_fn=stop)
+    assert model.generate_sampled(prompts, 12, 0.8, 16, rng2, eos=eos, stop_fn=stop) == want
+    # temperature 0 is the greedy loop
+    assert model.generate_sampled(prompts, 6, 0.0, 16, engine.Rng(1), eos=1 << 30) == model.generate(prompts, 6, eos=1 << 30)
