@@ -1349,6 +1349,7 @@ int ava_engine_set_segmented_read(ava_engine* e, int32_t seg_len) {
 }
 
 const ava_config* ava_engine_config(const ava_engine* e) { return e ? &e->cfg : nullptr; }
+int ava_engine_device(const ava_engine* e) { return e ? e->device : -1; }
 
 int ava_engine_set_fast_products(ava_engine* e, int32_t on) {
     if (!e) return AVA_ERR_ARG;

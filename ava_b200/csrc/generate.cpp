@@ -184,6 +184,17 @@ static int generate_impl(ava_engine* e, const uint32_t* prompts, const int32_t* 
         }
         parts.clear();
         std::vector<int> live(group);  // prompt index of each state row
+        if (first_pick && smp->temperature > 0.0f && max_new > 0) {
+            // the first tokens, from the prompts' logits: drawn on the device too when the sampler covers the case (the
+            // uniform numbers in the rows' order, as the loop below would draw them)
+            uint64_t saved = *smp->rng;
+            std::vector<double> u(live.size());
+            for (double& v : u) v = (double)(splitmix_next(smp->rng) >> 11) / (double)(1ull << 53);
+            if (ava_op_sample(ava_engine_device(e), last.data(), (int32_t)live.size(), V, smp->temperature, smp->top_k, u.data(), greedy.data()) == AVA_OK)
+                first_pick = false;
+            else
+                *smp->rng = saved;  // not covered: the host sampler takes them, from the same generator state
+        }
         for (int step = 0; step < max_new; ++step) {
             std::vector<int32_t> keep;
             std::vector<uint32_t> next;

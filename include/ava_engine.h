@@ -251,6 +251,8 @@ int ava_conv_load(ava_engine* e, const char* dir, const char* id, int32_t max_ct
 
 /* The configuration the engine was created with (valid while the engine lives). */
 const ava_config* ava_engine_config(const ava_engine* e);
+/* The CUDA device the engine runs on. */
+int ava_engine_device(const ava_engine* e);
 /* `SplitMix64::next_u64` (nn/data/src/rng.rs:24-28): advances *state and returns the next 64 bits. */
 uint64_t ava_splitmix64_next(uint64_t* state);
 /* `diary::pick` / `pick_traced` (src/diary.rs:686-744) on one row of host logits: the most likely token (lowest index
