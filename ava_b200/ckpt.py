@@ -67,6 +67,8 @@ def flags_of(cfg: dict) -> str:
         f.append("--alif")
     if cfg["theta"]:
         f.append("--homeostasis 0.1")
+    if cfg.get("stp"):
+        f.append("--stp")
     return " ".join(f)
 
 

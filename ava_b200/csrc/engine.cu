@@ -69,6 +69,7 @@ struct HostQ {
 
 struct BlockDev {
     Dev mem_norm, beta, theta, rho, again, hebb_norm, gate_w, ba, bb, wa2, wb2, off, vres, eng_norm, mlp_norm, dense;
+    Dev stp_U, stp_F, stp_D, stp_mix;  // --stp: sigmoids of the synapse's parameters, and its mix
     QMat win, wout, proj, wo, eqkv, ewo, w1, w2;
 };
 
@@ -155,6 +156,7 @@ struct ava_state {
     Dev lif_v, lif_s, lif_a;  // [L][rows][d]
     Dev mem_f;                // [L][rows][nh][hs / cw][hs][cw]: slice-major, a block of threads owns one contiguous slice
     Dev mem_s;                // the momentum matrix, same layout (only with --mem-momentum)
+    Dev stp_u, stp_x;         // [L][rows][d]: the synapse's (u, x) (only with --stp; a fresh state has u = 0, x = 1)
     Dev eng_k, eng_v;         // [rows][enh][ring][ehs]
     Dev eng_n, eng_start;     // [rows] i32
     std::vector<int32_t> n_host, start_host;
@@ -192,7 +194,8 @@ int64_t f32_len(const ava_config& c, const std::string& name) {
     int b;
     std::string rest;
     if (!split_block_name(name, c.n_blocks, &b, &rest)) return -1;
-    static const char* vec_d[] = {"mem.norm", "mem.beta", "mem.theta", "mem.arho", "mem.again", "hebb.norm", "hebb.off", "eng.norm", "mlp.norm"};
+    static const char* vec_d[] = {"mem.norm", "mem.beta", "mem.theta", "mem.arho", "mem.again", "hebb.norm", "hebb.off", "eng.norm", "mlp.norm",
+                                  "parts.stp.u_param", "parts.stp.f_param", "parts.stp.d_param", "parts.stp.mix"};
     for (const char* n : vec_d)
         if (rest == n) return d;
     if (rest == "hebb.wa" || rest == "hebb.wb") return d * nh;
@@ -463,6 +466,15 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
             spikes = e->eo.as<float>();
         }
         dbg(e, "spikes", i, spikes, M, d);
+        if (c.stp) {
+            // the LIF keeps its spikes; what reaches W_out goes through the short-term-plastic synapse
+            prof_begin(e, "stp");
+            launch_stp(st, spikes, b.stp_U.as<float>(), b.stp_F.as<float>(), b.stp_D.as<float>(), b.stp_mix.as<float>(),
+                       s->stp_u.as<float>() + (size_t)i * Rd, s->stp_x.as<float>() + (size_t)i * Rd, rows, d, T, e->eo.as<float>());
+            prof_end(e);
+            spikes = e->eo.as<float>();
+            dbg(e, "stp_out", i, spikes, M, d);
+        }
         gemm(e, "gemm.wout", spikes, d, b.wout, x, d, M, EPI_ADD, nullptr, true);
         dbg(e, "x_lif", i, x, M, d);
 
@@ -687,6 +699,12 @@ bool locate(const ava_state* s, int row, const std::string& name, StateSlice* ou
         out->count = d;
         return out->buf != nullptr;
     }
+    if (kind == "parts" && c.stp && (what == "stp_u" || what == "stp_x")) {
+        out->buf = what == "stp_u" ? &ms->stp_u : &ms->stp_x;
+        out->off = ((size_t)i * M + row) * d;
+        out->count = d;
+        return true;
+    }
     if (kind == "mem" && c.fast_mem && (what == "f" || (what == "s" && c.mem_momentum > 0.0f))) {
         const size_t per = (size_t)d * c.head_size;  // nh * hs * hs
         out->buf = what == "f" ? &ms->mem_f : &ms->mem_s;
@@ -709,6 +727,10 @@ int alloc_state(ava_engine* e, int rows, int ring, int keep, ava_state** out) {
     CK(s->lif_v.alloc(L * M * d * f));
     CK(s->lif_s.alloc(L * M * d * f));
     if (c.alif) CK(s->lif_a.alloc(L * M * d * f));
+    if (c.stp) {
+        CK(s->stp_u.alloc(L * M * d * f));
+        CK(s->stp_x.alloc(L * M * d * f));
+    }
     if (c.fast_mem) CK(s->mem_f.alloc(L * M * d * c.head_size * f));
     if (c.fast_mem && c.mem_momentum > 0.0f) CK(s->mem_s.alloc(L * M * d * c.head_size * f));
     if (c.eng_block >= 0) {
@@ -725,8 +747,9 @@ int alloc_state(ava_engine* e, int rows, int ring, int keep, ava_state** out) {
 }
 
 int zero_state(ava_engine* e, ava_state* s) {
-    for (Dev* b : {&s->lif_v, &s->lif_s, &s->lif_a, &s->mem_f, &s->mem_s, &s->eng_n, &s->eng_start})
+    for (Dev* b : {&s->lif_v, &s->lif_s, &s->lif_a, &s->mem_f, &s->mem_s, &s->stp_u, &s->eng_n, &s->eng_start})
         if (b->p) CK(cudaMemsetAsync(b->p, 0, b->bytes, e->stream));
+    if (s->stp_x.p) launch_fill(e->stream, s->stp_x.as<float>(), (int64_t)(s->stp_x.bytes / sizeof(float)), 1.0f);  // x starts at 1
     CK(cudaStreamSynchronize(e->stream));
     return AVA_OK;
 }
@@ -741,6 +764,10 @@ int copy_row(ava_engine* e, const ava_state* src, int src_row, ava_state* dst, i
         CK(cudaMemcpyAsync(dst->lif_s.as<float>() + dn * d, src->lif_s.as<float>() + so * d, d * f, cudaMemcpyDeviceToDevice, e->stream));
         if (c.alif)
             CK(cudaMemcpyAsync(dst->lif_a.as<float>() + dn * d, src->lif_a.as<float>() + so * d, d * f, cudaMemcpyDeviceToDevice, e->stream));
+        if (c.stp) {
+            CK(cudaMemcpyAsync(dst->stp_u.as<float>() + dn * d, src->stp_u.as<float>() + so * d, d * f, cudaMemcpyDeviceToDevice, e->stream));
+            CK(cudaMemcpyAsync(dst->stp_x.as<float>() + dn * d, src->stp_x.as<float>() + so * d, d * f, cudaMemcpyDeviceToDevice, e->stream));
+        }
         if (c.fast_mem)
             CK(cudaMemcpyAsync(dst->mem_f.as<float>() + dn * per, src->mem_f.as<float>() + so * per, per * f, cudaMemcpyDeviceToDevice, e->stream));
         if (c.fast_mem && c.mem_momentum > 0.0f)
@@ -896,6 +923,19 @@ int ava_engine_finalize(ava_engine* e) {
             }
         }
         if ((rc = upload_f32(e, b.theta, p + "mem.theta", c.theta != 0))) return rc;
+        if (c.stp) {
+            // U, F, D are sigmoids of their parameters (src/model/fstep/arch_f3.rs:82)
+            struct P { Dev* d; const char* n; bool sig; };
+            for (const P& q : {P{&b.stp_U, "parts.stp.u_param", true}, P{&b.stp_F, "parts.stp.f_param", true}, P{&b.stp_D, "parts.stp.d_param", true},
+                               P{&b.stp_mix, "parts.stp.mix", false}}) {
+                auto it = e->host_f32.find(p + q.n);
+                if (it == e->host_f32.end()) return e->fail(AVA_ERR_MISSING, "missing tensor %s%s", p.c_str(), q.n);
+                std::vector<float> v(it->second);
+                if (q.sig)
+                    for (float& t : v) t = ava::sigmoid(t);
+                if ((rc = upload(e, *q.d, v.data(), v.size() * sizeof(float)))) return rc;
+            }
+        }
         if ((rc = upload_f32(e, b.mlp_norm, p + "mlp.norm", true))) return rc;
         if (c.fast_mem) {
         if ((rc = upload_f32(e, b.hebb_norm, p + "hebb.norm", true))) return rc;
@@ -1338,7 +1378,8 @@ int64_t ava_engine_bytes(const ava_engine* e) {
 int64_t ava_state_bytes(const ava_state* s) {
     if (!s) return 0;
     int64_t n = 0;
-    for (const Dev* d : {&s->lif_v, &s->lif_s, &s->lif_a, &s->mem_f, &s->mem_s, &s->eng_k, &s->eng_v, &s->eng_n, &s->eng_start}) n += d->bytes;
+    for (const Dev* d : {&s->lif_v, &s->lif_s, &s->lif_a, &s->mem_f, &s->mem_s, &s->stp_u, &s->stp_x, &s->eng_k, &s->eng_v, &s->eng_n, &s->eng_start})
+        n += d->bytes;
     return n;
 }
 

@@ -470,6 +470,41 @@ void launch_tile(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {
     }
 }
 
+// --stp: the spikes through the synapse, one thread per (row, channel), the tokens of a chunk in order
+__global__ void stp_kernel(const float* spikes, const float* __restrict__ U, const float* __restrict__ F, const float* __restrict__ D,
+                           const float* __restrict__ mix, float* u_st, float* x_st, int M, int d, int T, float* out) {
+    pdl_enter();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t Md = (size_t)M * d;
+    if (i >= Md) return;
+    const int c = (int)(i % d);
+    const float uu = U[c], df = F[c], dd = D[c], mx = mix[c];
+    float u = u_st[i], x = x_st[i];
+    for (int t = 0; t < T; ++t) {
+        const float sv = spikes[(size_t)t * Md + i];
+        // the event size: s k + (clamp(|s|, 0, 1) - s k), k = 1 on [0, 1], -1 on [-1, 0), 0 beyond (nn/parts/src/stp.rs:42-54)
+        const float k = ((sv >= 0.0f && sv <= 1.0f) ? 1.0f : 0.0f) - ((sv < 0.0f && sv >= -1.0f) ? 1.0f : 0.0f);
+        const float sk = mul(sv, k);
+        const float a = fminf(fmaxf(fabsf(sv), 0.0f), 1.0f);
+        const float ev = add(sk, sub(a, sk));
+        const float u_plus = add(u, mul(mul(add(mul(u, -1.0f), 1.0f), uu), ev));
+        const float e = mul(u_plus, x);
+        const float eff = div(e, uu);
+        const float x_used = sub(x, mul(e, ev));
+        u = mul(u_plus, df);
+        x = add(mul(mul(add(mul(x_used, -1.0f), 1.0f), dd), -1.0f), 1.0f);
+        out[(size_t)t * Md + i] = add(sv, mul(sub(mul(sv, eff), sv), mx));
+    }
+    u_st[i] = u;
+    x_st[i] = x;
+}
+
+__global__ void fill_kernel(float* p, int64_t n, float v) {
+    pdl_enter();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = v;
+}
+
 __global__ void lif_kernel(const float* cur, const LifParams p, int M, int d) {
     pdl_enter();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -528,6 +563,16 @@ bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {
 void launch_lif_scan(cudaStream_t st, const float* cur, const LifParams& p, int M, int d, int T, float* spikes) {
     const size_t n = (size_t)M * d;
     launch_k(lif_scan_kernel, dim3((unsigned)((n + 127) / 128)), dim3(128), 0, st, cur, p, M, d, T, spikes);
+}
+
+void launch_stp(cudaStream_t st, const float* spikes, const float* U, const float* F, const float* D, const float* mix, float* u, float* x, int M, int d,
+                int T, float* out) {
+    const size_t n = (size_t)M * d;
+    launch_k(stp_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, spikes, U, F, D, mix, u, x, M, d, T, out);
+}
+
+void launch_fill(cudaStream_t st, float* p, int64_t n, float v) {
+    launch_k(fill_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, p, n, v);
 }
 
 void launch_lif(cudaStream_t st, const float* cur, const LifParams& p, int M, int d) {

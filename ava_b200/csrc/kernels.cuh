@@ -105,6 +105,11 @@ void launch_embed(cudaStream_t st, const float* tok_emb, const uint32_t* tok, in
 void launch_rmsnorm(cudaStream_t st, const float* x, const float* gain, int M, int n, float* y, uint16_t* limbs = nullptr);
 void launch_lif(cudaStream_t st, const float* cur, const LifParams& p, int M, int d);
 // T tokens of M rows in time order: cur, spikes [T][M][d]; the state in p moves T steps
+// --stp (src/model/fstep/arch_f3.rs:72-106): T tokens of M rows in time order, spikes and out [T][M][d] (out may be
+// the spikes' own buffer), the synapse's state (u, x) [M][d] moves T steps
+void launch_stp(cudaStream_t st, const float* spikes, const float* U, const float* F, const float* D, const float* mix, float* u, float* x, int M, int d,
+                int T, float* out);
+void launch_fill(cudaStream_t st, float* p, int64_t n, float v);
 void launch_lif_scan(cudaStream_t st, const float* cur, const LifParams& p, int M, int d, int T, float* spikes);
 
 struct MemPrepArgs {

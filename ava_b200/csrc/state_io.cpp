@@ -2,7 +2,7 @@
 // is a safetensors file under the reference's tensor names and shapes:
 //   meta.seen U32 [rows], meta.model U32 [2] (fingerprint high, low), meta.blocks U32 [1], meta.cap U32 [2] (max, rule;
 //   0 0: no cap), meta.hist U32 [rows, 17], meta.hist_len U32 [rows],
-//   lif.{i}.v / .s / .a F32 [rows, d], mem.{i}.f / .s F32 [rows * heads, hs, hs],
+//   lif.{i}.v / .s / .a F32 [rows, d], mem.{i}.f / .s F32 [rows * heads, hs, hs], parts.{i}.stp_u / .stp_x F32 [rows, d],
 //   eng.k / eng.v F32 [rows, heads, S, hs] with S the longest row's store and shorter rows padded on the left
 //   (src/state.rs:207-328), eng.valid U32 [rows], eng.pad F32 [rows, S] (0 for a slot, -1e9 for padding) when rows differ.
 // Written through PATH.tmp and a rename, so the file is whole or absent.  Host code over the C ABI.
@@ -115,6 +115,13 @@ int ava_state_save(const ava_state* s, const char* path) {
             if (!rows_of(li + k, d, &v)) return rc;
             put_f32(&outs, li + k, {rows, d}, v);
         }
+        if (c.stp) {
+            const std::string pi = "parts." + std::to_string(i) + ".";
+            for (const char* k : {"stp_u", "stp_x"}) {
+                if (!rows_of(pi + k, d, &v)) return rc;
+                put_f32(&outs, pi + k, {rows, d}, v);
+            }
+        }
         if (!c.fast_mem) continue;
         const int hs = c.head_size, nh = d / hs;
         for (const char* k : {"f", "s"}) {
@@ -220,6 +227,11 @@ int ava_state_load(ava_engine* e, const char* path, int32_t max_ctx, ava_state**
         for (const char* k : {"v", "s", "a"}) {
             if (k[0] == 'a' && !c.alif) continue;
             if ((rc = rows_in(li + k, d))) return rc;
+        }
+        if (c.stp) {
+            const std::string pi = "parts." + std::to_string(i) + ".";
+            for (const char* k : {"stp_u", "stp_x"})
+                if ((rc = rows_in(pi + k, d))) return rc;
         }
         if (!c.fast_mem) continue;
         for (const char* k : {"f", "s"}) {

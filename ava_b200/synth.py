@@ -130,6 +130,12 @@ def model(cfg: dict, seed: int = 0, recipe: str = "bench", unit_gain: bool = Tru
             jitter = g.n(p + "mem.arho", (d,), 0.2) if awake else np.zeros(d, np.float32)
             w[p + "mem.arho"] = (logit(rho) + jitter).astype(np.float32)
             w[p + "mem.again"] = g.u(p + "mem.again", (d,), 0.5, 1.5) if awake else np.ones(d, np.float32)
+        if cfg["stp"]:
+            # the synapse of the spikes: U around 0.2, facilitation and recovery of a few tokens, a real mix
+            for nm, lo, hi in (("u_param", 0.1, 0.5), ("f_param", 0.5, 0.98), ("d_param", 0.5, 0.95)):
+                pv = g.u(p + "parts.stp." + nm, (d,), lo, hi).astype(np.float64)
+                w[p + "parts.stp." + nm] = np.log(pv / (1.0 - pv)).astype(np.float32)
+            w[p + "parts.stp.mix"] = g.u(p + "parts.stp.mix", (d,), 0.0, 1.0) if awake else np.full(d, 0.5, np.float32)
         # the fast-weight memory (kinds D and A; kind S has none)
         if cfg["fast_mem"]:
             w[p + "hebb.norm"] = ones("hebb.norm")

@@ -207,7 +207,7 @@ def main():
     e2e_steps = K
     # untimed steps bring the KV length to ctx - K/2, so that the timed steps straddle the mean decode context
     prompt = max(1, args.ctx - K // 2 - W)
-    max_ctx = prompt + W + K + e2e_steps + W + 16 + K + W + 8   # decode, end to end, section clock, fast-products leg
+    max_ctx = prompt + W + K + 2 * (e2e_steps + W) + 16 + K + W + 8   # decode, end to end (two calls), section clock, fast-products leg
     state = model.state(rows, max_ctx)
     stream = torch.cuda.ExternalStream(model.stream, device=local)
 
@@ -288,6 +288,32 @@ def main():
         e2e_s = float(t.item())
     e2e_val = world * rows * e2e_steps / e2e_s
 
+    # the same through the greedy call (host token ids in, host token ids out: what a generation loop moves per step)
+    nxt_host = torch.empty(rows, dtype=torch.int32).pin_memory()
+    cur_host = e2e_ids[0].clone().pin_memory()
+
+    def greedy_step():
+        rc = L.ava_step_greedy(model.h, state.h, C.cast(cur_host.data_ptr(), engine.u32p), C.cast(nxt_host.data_ptr(), engine.u32p))
+        if rc != 0:
+            raise RuntimeError(L.ava_last_error(model.h).decode())
+        cur_host.copy_(nxt_host)
+
+    for _ in range(W):
+        greedy_step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        greedy_step()
+    torch.cuda.synchronize()
+    greedy_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([greedy_s], dtype=torch.float64, device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        greedy_s = float(t.item())
+    e2e_greedy = world * rows * e2e_steps / greedy_s
+
     # ---- the dominant kernel under the section clock: a few more steps with every launch bracketed by events
     model.prof_enable(True)
     cur2 = decode(4, cur)
@@ -318,7 +344,9 @@ def main():
                    "rows_per_gpu": rows, "kv_len_timed": [prompt + W, prompt + W + K], "l2": "per-step inputs (state "
                    f"{state.nbytes / 1e9:.2f} GB per GPU) are larger than L2", "sequences": "independent, sharded by rank, no collective"},
         "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": rows * 4, "d2h_bytes_per_step": rows * cfg["vocab"] * 4,
-                "steps": e2e_steps, "call": "ava_step (host token ids in, host logits out, pinned buffers)"},
+                "steps": e2e_steps, "call": "ava_step (host token ids in, host logits out, pinned buffers)",
+                "greedy": {"value": e2e_greedy, "unit": UNIT, "h2d_bytes_per_step": rows * 4, "d2h_bytes_per_step": rows * 4,
+                           "call": "ava_step_greedy (host token ids in, host token ids out; the arg-max on the device)"}},
         "gpu_launches": int(launches),
         "clocks": clk,
         "roofline": {"bound": "hbm", "kernel": "mem_heads (fast-weight state pass)", "achieved": achieved, "peak": peak, "unit": "GB/s",

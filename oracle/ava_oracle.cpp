@@ -461,6 +461,8 @@ struct Block {
     // the spiking memory
     std::vector<float> mem_norm, beta_param, theta, arho, again;
     QW win, wout;
+    // short-term plasticity of the spikes' synapse (--stp): parameters and their sigmoids
+    std::vector<float> stp_u, stp_f, stp_d, stp_mix, stp_U, stp_F, stp_D;
     // the fast-weight memory
     std::vector<float> hebb_norm, wa, wb, ba, bb, wa1, wa2, wb1, wb2, off, vres;
     QW wq, wk, wv, we, wg, wo;
@@ -488,6 +490,7 @@ struct orc_model {
 struct RowState {
     std::vector<std::vector<float>> v, s, a;    // per block [d]
     std::vector<std::vector<float>> f, ms;      // per block [nh, hs, hs]
+    std::vector<std::vector<float>> su, sx;     // per block [d]: the synapse's (u, x) with --stp
     std::vector<float> ek, evv;                 // engram [enh, n, ehs]
     int eng_n = 0;
     int64_t seen = 0;
@@ -516,7 +519,8 @@ std::vector<float>* f32_slot(orc_model* m, const std::string& name, int64_t* wan
     struct E { const char* n; std::vector<float>* p; int64_t len; };
     const E table[] = {
         {"mem.norm", &b.mem_norm, d}, {"mem.beta", &b.beta_param, d}, {"mem.theta", &b.theta, d}, {"mem.arho", &b.arho, d},
-        {"mem.again", &b.again, d}, {"hebb.norm", &b.hebb_norm, d}, {"hebb.wa", &b.wa, (int64_t)d * nh}, {"hebb.wb", &b.wb, (int64_t)d * nh},
+        {"mem.again", &b.again, d}, {"parts.stp.u_param", &b.stp_u, d}, {"parts.stp.f_param", &b.stp_f, d}, {"parts.stp.d_param", &b.stp_d, d},
+        {"parts.stp.mix", &b.stp_mix, d}, {"hebb.norm", &b.hebb_norm, d}, {"hebb.wa", &b.wa, (int64_t)d * nh}, {"hebb.wb", &b.wb, (int64_t)d * nh},
         {"hebb.ba", &b.ba, nh}, {"hebb.bb", &b.bb, nh}, {"hebb.wa1", &b.wa1, (int64_t)d * r}, {"hebb.wa2", &b.wa2, (int64_t)r * d},
         {"hebb.wb1", &b.wb1, (int64_t)d * r}, {"hebb.wb2", &b.wb2, (int64_t)r * d}, {"hebb.off", &b.off, d}, {"hebb.vres", &b.vres, 2},
         {"eng.norm", &b.eng_norm, d}, {"mlp.norm", &b.mlp_norm, d}, {"dense", &b.dense, i + 2},
@@ -556,7 +560,41 @@ void derive(const orc_model* mc) {
         for (size_t c = 0; c < b.beta.size(); ++c) b.beta[c] = sigmoid(b.beta_param[c]);  // fstep/arch.rs:640
         b.rho.resize(b.arho.size());
         for (size_t c = 0; c < b.rho.size(); ++c) b.rho[c] = sigmoid(b.arho[c]);  // fstep/arch.rs:660
+        b.stp_U.resize(b.stp_u.size());
+        b.stp_F.resize(b.stp_f.size());
+        b.stp_D.resize(b.stp_d.size());
+        for (size_t c = 0; c < b.stp_u.size(); ++c) {  // fstep/arch_f3.rs:82
+            b.stp_U[c] = sigmoid(b.stp_u[c]);
+            b.stp_F[c] = sigmoid(b.stp_f[c]);
+            b.stp_D[c] = sigmoid(b.stp_d[c]);
+        }
         b.derived = true;
+    }
+}
+
+// S: the spikes s [d] through the synapse from its carried (u, x) (fstep/arch_f3.rs:72-106; the part itself:
+// nn/parts/src/stp.rs:42-85): what reaches W_out, the new (u, x), and the efficacy e / U of each channel.
+void stp_step(const float* s, const float* U, const float* F, const float* D, const float* mix, const float* u0, const float* x0, int d,
+              float* out, float* u1, float* x1, float* eff_out) {
+    for (int c = 0; c < d; ++c) {
+        const float uu = U[c], df = F[c], dd = D[c], sv = s[c];
+        // ava_parts::stp::events: k = (s >= 0)(s <= 1) - (s < 0)(s >= -1), s k + (clamp(|s|, 0, 1) - s k)
+        auto f = [](bool b) { return b ? 1.0f : 0.0f; };
+        const float k = f(sv >= 0.0f) * f(sv <= 1.0f) - f(sv < 0.0f) * f(sv >= -1.0f);
+        const float sk = sv * k;
+        float a = std::fabs(sv);
+        a = a < 0.0f ? 0.0f : a;
+        a = a > 1.0f ? 1.0f : a;
+        const float ev = sk + (a - sk);
+        const float u = u0[c], x = x0[c];
+        const float u_plus = u + ((u * -1.0f + 1.0f) * uu) * ev;
+        const float e = u_plus * x;
+        const float eff = e / uu;
+        const float x_used = x - e * ev;
+        u1[c] = u_plus * df;
+        x1[c] = ((x_used * -1.0f + 1.0f) * dd) * -1.0f + 1.0f;
+        out[c] = sv + ((sv * eff) - sv) * mix[c];
+        if (eff_out) eff_out[c] = eff;
     }
 }
 
@@ -585,7 +623,7 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
 
     std::vector<RowState> nw(R);  // the new states, committed at the end
     for (RowState& n : nw) {
-        n.v.resize(L); n.s.resize(L); n.a.resize(L); n.f.resize(L); n.ms.resize(L);
+        n.v.resize(L); n.s.resize(L); n.a.resize(L); n.f.resize(L); n.ms.resize(L); n.su.resize(L); n.sx.resize(L);
     }
     std::vector<char> bad(R, 0);
     bool eng_written = false;
@@ -613,6 +651,16 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
         }
         T("cur", i, cur.data(), d);
         T("spikes", i, sp.data(), d);
+        if (cfg.stp) {
+            // the LIF keeps its spikes; what reaches W_out went through the synapse
+            for (int r = 0; r < R; ++r) {
+                nw[r].su[i].resize(d);
+                nw[r].sx[i].resize(d);
+                stp_step(&sp[(size_t)r * d], b.stp_U.data(), b.stp_F.data(), b.stp_D.data(), b.stp_mix.data(), rows[r]->su[i].data(),
+                         rows[r]->sx[i].data(), d, &sp[(size_t)r * d], nw[r].su[i].data(), nw[r].sx[i].data(), nullptr);
+            }
+            T("stp_out", i, sp.data(), d);
+        }
         q8_matmul(b.wout, sp.data(), R, tmp.data());
         add_into(x.data(), tmp.data(), R * d);
         T("x_lif", i, x.data(), d);
@@ -849,6 +897,10 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
         RowState& st = *rows[r];
         st.v = std::move(nw[r].v); st.s = std::move(nw[r].s); st.a = std::move(nw[r].a);
         st.f = std::move(nw[r].f); st.ms = std::move(nw[r].ms);
+        if (cfg.stp) {
+            st.su = std::move(nw[r].su);
+            st.sx = std::move(nw[r].sx);
+        }
         if (eng_written) {
             st.ek = std::move(nw[r].ek);
             st.evv = std::move(nw[r].evv);
@@ -872,6 +924,9 @@ bool parse_state_name(const orc_state* s, int row, const std::string& name, cons
         if (what == "v") { *out = &r.v[i]; return true; }
         if (what == "s") { *out = &r.s[i]; return true; }
         if (what == "a") { *out = &r.a[i]; return true; }
+    } else if (kind == "parts" && s->m->cfg.stp) {
+        if (what == "stp_u") { *out = &r.su[i]; return true; }
+        if (what == "stp_x") { *out = &r.sx[i]; return true; }
     } else if (kind == "mem" && s->m->cfg.fast_mem) {
         if (what == "f") { *out = &r.f[i]; return true; }
         if (what == "s") { *out = &r.ms[i]; return true; }
@@ -911,6 +966,16 @@ void orc_gemv(const float* x, int k, const float* w, int n, float* out) { gemv(x
 void orc_lif(const float* cur, const float* beta, const float* theta, const float* rho, const float* gain, int spikes, float slope,
              const float* v0, const float* s0, const float* a0, int d, float* s1, float* v1, float* a1) {
     lif(cur, beta, theta, rho, gain, spikes, slope, v0, s0, a0, d, s1, v1, a1);
+}
+void orc_stp(const float* s, const float* u_param, const float* f_param, const float* d_param, const float* mix, const float* u0, const float* x0,
+             int d, float* out, float* u1, float* x1, float* eff) {
+    std::vector<float> U(d), F(d), D(d);
+    for (int c = 0; c < d; ++c) {
+        U[c] = sigmoid(u_param[c]);
+        F[c] = sigmoid(f_param[c]);
+        D[c] = sigmoid(d_param[c]);
+    }
+    stp_step(s, U.data(), F.data(), D.data(), mix, u0, x0, d, out, u1, x1, eff);
 }
 float orc_kth_largest(const float* u, int n, int k) { return kth_largest(u, n, k); }
 void orc_kwta(const float* u, int n, int k, int relu2, float* a) { kwta(u, n, k, relu2 != 0, a); }
@@ -973,7 +1038,9 @@ int orc_model_check(orc_model* m, char* missing, int cap) {
                         {"hebb.wa", &b.wa, c.fast_mem != 0}, {"hebb.wb", &b.wb, c.fast_mem != 0}, {"hebb.ba", &b.ba, c.fast_mem != 0}, {"hebb.bb", &b.bb, c.fast_mem != 0},
                         {"hebb.wa1", &b.wa1, c.fast_mem != 0}, {"hebb.wa2", &b.wa2, c.fast_mem != 0}, {"hebb.wb1", &b.wb1, c.fast_mem != 0}, {"hebb.wb2", &b.wb2, c.fast_mem != 0},
                         {"hebb.off", &b.off, c.fast_mem != 0}, {"hebb.vres", &b.vres, c.fast_mem && c.value_residual && i > 0}, {"eng.norm", &b.eng_norm, i == c.eng_block},
-                        {"mlp.norm", &b.mlp_norm, true}, {"dense", &b.dense, c.dense != 0}};
+                        {"mlp.norm", &b.mlp_norm, true}, {"dense", &b.dense, c.dense != 0},
+                        {"parts.stp.u_param", &b.stp_u, c.stp != 0}, {"parts.stp.f_param", &b.stp_f, c.stp != 0},
+                        {"parts.stp.d_param", &b.stp_d, c.stp != 0}, {"parts.stp.mix", &b.stp_mix, c.stp != 0}};
         for (const F& f : fs)
             if (f.need && f.v->empty()) return fail(p + f.n);
         struct Q { const char* n; const QW* q; bool need; };
@@ -1000,6 +1067,8 @@ orc_state* orc_state_new(const orc_model* m, int rows) {
         r.a.assign(c.n_blocks, std::vector<float>(c.alif ? c.d : 0, 0.f));
         r.f.assign(c.n_blocks, std::vector<float>(fl, 0.f));
         r.ms.assign(c.n_blocks, std::vector<float>(c.mem_momentum > 0.f ? fl : 0, 0.f));
+        r.su.assign(c.n_blocks, std::vector<float>(c.stp ? c.d : 0, 0.f));  // u = 0, x = 1 (nn/parts/src/stp.rs:69-70)
+        r.sx.assign(c.n_blocks, std::vector<float>(c.stp ? c.d : 0, 1.f));
     }
     return s;
 }

@@ -58,6 +58,7 @@ typedef struct orc_config {
     int32_t dense;          /* dense residual mixes */
     int32_t out_gate;       /* 1: silu(h Wg) output gate on the memory read */
     int32_t fast_mem;       /* 1: blocks have the fast-weight memory; 0: kind S (src/model/fstep.rs:461-688) */
+    int32_t stp;            /* --stp: the spikes reach W_out through a short-term-plastic synapse (fstep/arch_f3.rs:72-106) */
     float   mem_momentum;   /* 0: off */
     float   slope;          /* surrogate slope (forward value cancels; kept for the literal op order) */
 } orc_config;
@@ -90,6 +91,11 @@ void orc_gemv(const float* x, int k, const float* w, int n, float* out);
 void orc_lif(const float* cur, const float* beta, const float* theta, const float* rho, const float* gain,
              int spikes, float slope, const float* v0, const float* s0, const float* a0, int d, float* s1,
              float* v1, float* a1);
+/* S (--stp): the spikes through the short-term-plastic synapse (fstep/arch_f3.rs:72-106, nn/parts/src/stp.rs:42-85):
+ * out [d] what reaches W_out, (u1, x1) the synapse's new state, eff (may be NULL) the efficacy e / U.  The parameters
+ * are the raw ones (their sigmoids are taken inside). */
+void orc_stp(const float* s, const float* u_param, const float* f_param, const float* d_param, const float* mix, const float* u0, const float* x0,
+             int d, float* out, float* u1, float* x1, float* eff);
 float orc_kth_largest(const float* u, int n, int k);
 /* A7: a = max(u * [u - kth >= 0], 0), squared when relu2. */
 void orc_kwta(const float* u, int n, int k, int relu2, float* a);

@@ -21,7 +21,7 @@ class OrcConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "vocab", "d", "n_blocks", "hidden", "kwta_k", "head_size", "eng_block", "eng_head_size", "eng_store_bf16",
         "eng_cap", "gate_rank", "spikes", "alif", "theta", "lif_scale", "value_residual", "relu2", "dense",
-        "out_gate", "fast_mem")] + [("mem_momentum", C.c_float), ("slope", C.c_float)]
+        "out_gate", "fast_mem", "stp")] + [("mem_momentum", C.c_float), ("slope", C.c_float)]
 
 
 def build(force: bool = False) -> str:
@@ -63,6 +63,8 @@ def lib() -> C.CDLL:
     L.orc_log_sigmoid.argtypes = [C.c_float]
     L.orc_log_sigmoid.restype = C.c_float
     L.orc_gemv.argtypes = [fp, C.c_int, fp, C.c_int, fp]
+    L.orc_stp.argtypes = [fp] * 7 + [C.c_int] + [fp] * 4
+    L.orc_stp.restype = None
     L.orc_lif.argtypes = [fp, fp, fp, fp, fp, C.c_int, C.c_float, fp, fp, fp, C.c_int, fp, fp, fp]
     L.orc_kth_largest.argtypes = [fp, C.c_int, C.c_int]
     L.orc_kth_largest.restype = C.c_float
@@ -188,6 +190,16 @@ def lif(cur, beta, v0, s0, theta=None, rho=None, gain=None, a0=None, spikes=2, s
     lib().orc_lif(cp, _fp(beta), _fp(theta), _fp(rho), _fp(gain), spikes, slope, _fp(v0), _fp(s0), _fp(a0), d,
                   _fp(s1), _fp(v1), _fp(a1))
     return s1, v1, a1
+
+
+def stp(s, u_param, f_param, d_param, mix, u0, x0):
+    """(out, u1, x1, efficacy) of one step of the short-term-plastic synapse."""
+    s, sp = _f(s)
+    arrs = [_f(a) for a in (u_param, f_param, d_param, mix, u0, x0)]
+    out, u1, x1, eff = (np.empty_like(s) for _ in range(4))
+    L = lib()
+    L.orc_stp(sp, *[a[1] for a in arrs], s.size, _fp(out), _fp(u1), _fp(x1), _fp(eff))
+    return out, u1, x1, eff
 
 
 def kth_largest(u, k):

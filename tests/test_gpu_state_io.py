@@ -20,7 +20,7 @@ def _lib():
 
 
 @pytest.mark.parametrize("name,kw", [("ava04_small", dict()), ("momentum_bf16", dict(mem_momentum=0.5, head_size=64, eng_store_bf16=1)),
-                                     ("capped", dict(eng_cap=6)), ("kind_s", None)])
+                                     ("capped", dict(eng_cap=6)), ("stp", dict(stp=1)), ("kind_s", None)])
 def test_saved_state_continues_bit_for_bit(tmp_path, name, kw):
     cfg = config.kind_s(320, 128, 3) if kw is None else config.tiny(**kw)
     m = engine.Model(cfg, synth.model(cfg, 1, "awake"))
@@ -45,6 +45,8 @@ def test_saved_state_continues_bit_for_bit(tmp_path, name, kw):
     fp = ck.get("meta.model")
     assert (int(fp[0]) << 32 | int(fp[1])) == m.fingerprint
     assert ck.get("lif.1.v").shape == (rows, d) and ck.get("meta.hist").shape == (rows, 17)
+    if cfg["stp"]:
+        assert ck.get("parts.0.stp_u").shape == (rows, d) and (ck.get("parts.1.stp_x") != 1.0).any()
     if cfg["fast_mem"]:
         hs = cfg["head_size"]
         assert ck.get("mem.0.f").shape == (rows * d // hs, hs, hs)

@@ -32,6 +32,7 @@ def orc_same_math(orc):
 
 STATE_NAMES = lambda cfg: [f"lif.{i}.{k}" for i in range(cfg["n_blocks"]) for k in (("v", "s", "a") if cfg["alif"] else ("v", "s"))] + \
     ([f"mem.{i}.{k}" for i in range(cfg["n_blocks"]) for k in (("f", "s") if cfg["mem_momentum"] > 0 else ("f",))] if cfg["fast_mem"] else []) + \
+    ([f"parts.{i}.{k}" for i in range(cfg["n_blocks"]) for k in ("stp_u", "stp_x")] if cfg["stp"] else []) + \
     (["eng.k", "eng.v"] if cfg["eng_block"] >= 0 else [])
 
 
@@ -55,6 +56,7 @@ CONFIGS = {
     "ternary_no_engram": dict(spikes=1, eng_block=-1, head_size=64),
     "momentum": dict(mem_momentum=0.5, head_size=64),                                   # the released recipe's --mem-momentum
     "wide_rank2": dict(d=256, head_size=256, gate_rank=2, eng_block=0, hidden=512, kwta_k=64),
+    "stp": dict(stp=1, head_size=64),                                                   # --stp: the spikes through the plastic synapse
     # the reference's kind S (Ava-M's): spiking memory + sparse MLP only, binary spikes, relu
     "kind_s": dict(head_size=128, eng_block=-1, spikes=0, alif=0, theta=0, lif_scale=0, value_residual=0, relu2=0, dense=0, out_gate=0,
                    fast_mem=0),
@@ -134,7 +136,7 @@ def test_forward_with_state_equals_steps(orc_same_math):
     assert np.array_equal(bits(tail), bits(want[:, 6:]))
 
 
-@pytest.mark.parametrize("name", ["ava04_small", "one_head_bf16", "binary_plain", "momentum", "kind_s"])
+@pytest.mark.parametrize("name", ["ava04_small", "one_head_bf16", "binary_plain", "momentum", "kind_s", "stp"])
 @pytest.mark.parametrize("chunk", [1, 5, 64])
 def test_chunked_prompt_equals_steps(orc_same_math, name, chunk):
     """Reading a prompt in chunks (token-parallel products, the recurrences in order inside their kernels) gives the

@@ -59,7 +59,8 @@ def test_arch_flag_words():
             got["theta"]) == (64, 1, 384, 1, 1, 1, 2, 1, 1)
     assert got["mem_momentum"] == 0.5
     # the released Ava 0.4 adds nine parts the engine does not have: the first of them is named
-    with pytest.raises(engine.NotApplicable, match="--stp"):
+    assert engine.arch_flags(AVA04_FLAGS + " --stp", base)["stp"] == 1
+    with pytest.raises(engine.NotApplicable, match="--neuromod"):
         engine.arch_flags(AVA04_FLAGS + " --stp --neuromod 3 --dendrite", base)
     with pytest.raises(engine.NotApplicable, match="gates"):
         engine.arch_flags("--head-size 64", base)

@@ -419,3 +419,40 @@ def test_benchmark_recipe_is_the_stated_corner(orc):
         assert np.array_equal(k, np.array([orc.bf16_round(v) for v in k], np.float32))
     finally:
         orc.trace_enable(False)
+
+
+def _stp_efficacies(orc, U, F, D, spikes, mix=0.0):
+    lg = lambda p: np.float32(np.log(p / (1 - p)))
+    u, x, effs, outs = np.zeros(1, np.float32), np.ones(1, np.float32), [], []
+    for sv in spikes:
+        o, u, x, e = orc.stp(np.array([sv], np.float32), [lg(U)], [lg(F)], [lg(D)], [mix], u, x)
+        effs.append(float(e[0]))
+        outs.append(float(o[0]))
+    return effs, outs
+
+
+def test_stp_depresses_facilitates_and_starts_as_no_change(orc):
+    """design-tests/nn/parts/src/stp.rs `depresses_facilitates_and_starts_as_no_change`: with mix 0 the spikes pass
+    unchanged; a depressing synapse (U 0.8, no facilitation memory, slow recovery) weakens each spike of a train, the
+    first at efficacy 1; a facilitating one (U 0.1, long facilitation, fast recovery) strengthens them past 2 by the
+    fifth; with mix 1 the output is the efficacy-weighted spike."""
+    rng = np.random.default_rng(4)
+    s = (rng.normal(size=9) >= 0.3).astype(np.float32)
+    _, outs = _stp_efficacies(orc, 0.2, float(np.exp(-1 / 20)), float(np.exp(-1 / 5)), s, mix=0.0)
+    assert np.allclose(outs, s, atol=1e-7)
+    e, _ = _stp_efficacies(orc, 0.8, 1e-4, 0.99, [1.0] * 5)
+    assert abs(e[0] - 1.0) < 1e-4 and all(b < a for a, b in zip(e, e[1:]))
+    e, _ = _stp_efficacies(orc, 0.1, 0.95, 1e-4, [1.0] * 5)
+    assert abs(e[0] - 1.0) < 1e-4 and all(b > a for a, b in zip(e, e[1:])) and e[4] > 2.0
+    e, outs = _stp_efficacies(orc, 0.1, 0.95, 1e-4, s, mix=1.0)
+    assert np.allclose(outs, s * np.array(e, np.float32), atol=1e-6)
+
+
+def test_stp_signed_multilevel_spikes_stay_bounded(orc):
+    """stp.rs `signed_multilevel_spikes_keep_the_rule_bounded`: int2 spikes (-2..2), also a sustained run of -2, keep
+    every efficacy finite and at most 1 / U."""
+    rng = np.random.default_rng(8)
+    rnd = np.clip(np.round(rng.normal(size=600) * 1.5), -2, 2).astype(np.float32)
+    for spikes in (rnd, np.full(300, -2.0, np.float32)):
+        e, _ = _stp_efficacies(orc, 0.05, 0.99, 0.5, spikes)
+        assert np.isfinite(e).all() and np.abs(e).max() <= 1.0 / 0.05 + 1e-3
