@@ -54,6 +54,17 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                  "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
+// shared-memory loads as volatile asm: they keep their place ahead of the chains that use them
+__device__ __forceinline__ float lds_f(const float* p) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(smem_u32(p)));
+    return v;
+}
+__device__ __forceinline__ float4 lds_f4(const float* p) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(smem_u32(p)));
+    return v;
+}
 __device__ __forceinline__ void bulk_store(void* dst, const void* src, uint32_t bytes) {
     asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)), "r"(bytes) : "memory");
 }
@@ -283,11 +294,12 @@ __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsAr
             const float* p = tile + tid;
             const float* ps = tileS + tid;
             float f[8], ev[8], gv[8];
+            // loads as volatile asm: here the slice is resident and the chains are the whole critical path, so the eight
+            // rows fetched ahead must really be ahead (the compiler otherwise sinks them down to the multiply-adds)
             auto load8 = [&](int row, float* ff, float* ee, float* gg) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) ff[i] = p[(size_t)(row + i) * CW];
-                const float4 e0 = *reinterpret_cast<const float4*>(ve + row), e1 = *reinterpret_cast<const float4*>(ve + row + 4);
-                const float4 g0 = *reinterpret_cast<const float4*>(vqg + row), g1 = *reinterpret_cast<const float4*>(vqg + row + 4);
+                for (int i = 0; i < 8; ++i) ff[i] = lds_f(p + (size_t)(row + i) * CW);
+                const float4 e0 = lds_f4(ve + row), e1 = lds_f4(ve + row + 4), g0 = lds_f4(vqg + row), g1 = lds_f4(vqg + row + 4);
                 ee[0] = e0.x; ee[1] = e0.y; ee[2] = e0.z; ee[3] = e0.w; ee[4] = e1.x; ee[5] = e1.y; ee[6] = e1.z; ee[7] = e1.w;
                 gg[0] = g0.x; gg[1] = g0.y; gg[2] = g0.z; gg[3] = g0.w; gg[4] = g1.x; gg[5] = g1.y; gg[6] = g1.z; gg[7] = g1.w;
             };
