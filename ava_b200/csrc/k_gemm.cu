@@ -27,23 +27,21 @@ __device__ __forceinline__ void widen4(int w, float* f) {
 
 // One LIF update of one channel (src/model/fstep/arch.rs:173-228) with the hard spike count taken directly (as the
 // reference's own GPU kernel does; the CPU's soft + (hard - soft) equals it).  v, s, a: the carried state, in and out.
-__device__ __forceinline__ void lif_core(const LifParams& p, int c, float cur, float& v, float& s, float& a) {
-    const float beta = p.beta[c];
-    if (p.lif_scale) cur = mul(cur, add(mul(beta, -1.0f), 1.0f));
-    const float th = p.theta ? p.theta[c] : 1.0f;
+__device__ __forceinline__ void lif_math(int spikes, int lif_scale, bool adaptive, float beta, float th, float rho, float gain, float cur, float& v,
+                                         float& s, float& a) {
+    if (lif_scale) cur = mul(cur, add(mul(beta, -1.0f), 1.0f));
     float th_prev = th, th_t = th;
-    if (p.rho) {
-        const float rho = p.rho[c], gain = p.gain[c];
+    if (adaptive) {
         th_prev = add(th, mul(a, gain));
         a = add(mul(a, rho), mul(fabsf(s), add(mul(rho, -1.0f), 1.0f)));
         th_t = add(th, mul(a, gain));
     }
     const float vv = sub(add(mul(v, beta), cur), mul(s, th_prev));
     v = vv;
-    if (p.spikes == 0) {
+    if (spikes == 0) {
         s = sub(vv, th_t) >= 0.0f ? 1.0f : 0.0f;
     } else {
-        const int levels = p.spikes == 2 ? 2 : 1;
+        const int levels = spikes == 2 ? 2 : 1;
         float n = 0.0f;
         for (int k = 1; k <= levels; ++k) {
             const float kth = add(mul(th_t, (float)k), 0.0f);
@@ -52,6 +50,11 @@ __device__ __forceinline__ void lif_core(const LifParams& p, int c, float cur, f
         }
         s = n;
     }
+}
+
+__device__ __forceinline__ void lif_core(const LifParams& p, int c, float cur, float& v, float& s, float& a) {
+    lif_math(p.spikes, p.lif_scale, p.rho != nullptr, p.beta[c], p.theta ? p.theta[c] : 1.0f, p.rho ? p.rho[c] : 0.0f, p.rho ? p.gain[c] : 0.0f, cur, v, s,
+             a);
 }
 
 __device__ __forceinline__ void lif_update(const LifParams& p, int r, int c, int d, float cur) {
@@ -208,6 +211,51 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) q8_gemm_kernel(const Ge
     float scv[TN];
 #pragma unroll
     for (int j = 0; j < TN; ++j) scv[j] = g.scale[c0 + j];
+    float lbeta[TN], lth[TN], lrho[TN], lgain[TN];  // the LIF's per-channel parameters of this thread's columns
+    if (EPI == EPI_LIF) {
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            lbeta[j] = g.lif.beta[c0 + j];
+            lth[j] = g.lif.theta ? g.lif.theta[c0 + j] : 1.0f;
+            lrho[j] = g.lif.rho ? g.lif.rho[c0 + j] : 0.0f;
+            lgain[j] = g.lif.rho ? g.lif.gain[c0 + j] : 0.0f;
+        }
+    }
+    if (EPI == EPI_LIF) {
+        // The carried state of the whole micro-tile is read before any of it is written: the stores would otherwise
+        // fence the next element's loads, and every element would wait a memory round trip of its own.
+        const LifParams& p = g.lif;
+        float v[TM][TN], sp[TM][TN], tr[TM][TN];
+#pragma unroll
+        for (int i = 0; i < TM; ++i) {
+            const int r = m0 + ty * TM + i;
+#pragma unroll
+            for (int j = 0; j < TN; ++j) {
+                const size_t at = (size_t)(r < g.M ? r : 0) * g.N + c0 + j;
+                v[i][j] = p.v[at];
+                sp[i][j] = p.s[at];
+                tr[i][j] = p.rho ? p.a[at] : 0.0f;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < TM; ++i)
+#pragma unroll
+            for (int j = 0; j < TN; ++j)
+                lif_math(p.spikes, p.lif_scale, p.rho != nullptr, lbeta[j], lth[j], lrho[j], lgain[j], mul(acc[i][j], scv[j]), v[i][j], sp[i][j], tr[i][j]);
+#pragma unroll
+        for (int i = 0; i < TM; ++i) {
+            const int r = m0 + ty * TM + i;
+            if (r >= g.M) continue;
+#pragma unroll
+            for (int j = 0; j < TN; ++j) {
+                const size_t at = (size_t)r * g.N + c0 + j;
+                p.v[at] = v[i][j];
+                p.s[at] = sp[i][j];
+                if (p.rho) p.a[at] = tr[i][j];
+            }
+        }
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < TM; ++i) {
         const int r = m0 + ty * TM + i;
@@ -216,8 +264,7 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) q8_gemm_kernel(const Ge
 #pragma unroll
         for (int j = 0; j < TN; ++j) o[j] = mul(acc[i][j], scv[j]);
         if (EPI == EPI_LIF) {
-#pragma unroll
-            for (int j = 0; j < TN; ++j) lif_update(g.lif, r, c0 + j, g.N, o[j]);
+            // handled above for the whole micro-tile
         } else {
             float* dst = g.C + (size_t)r * g.ldc + c0;
             if (TN >= 4) {
