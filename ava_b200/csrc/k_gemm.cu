@@ -221,6 +221,24 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) q8_gemm_kernel(const Ge
             lgain[j] = g.lif.rho ? g.lif.gain[c0 + j] : 0.0f;
         }
     }
+    float resid[TM][TN];  // EPI_ADD: what the product is added to, read for the whole micro-tile before any row is written
+    if (EPI == EPI_ADD) {
+#pragma unroll
+        for (int i = 0; i < TM; ++i) {
+            const int r = m0 + ty * TM + i;
+            const float* src = g.C + (size_t)(r < g.M ? r : 0) * g.ldc + c0;
+            if (TN >= 4) {
+#pragma unroll
+                for (int j = 0; j < TN; j += 4) {
+                    const float4 x = *reinterpret_cast<const float4*>(src + j);
+                    resid[i][j] = x.x; resid[i][j + 1] = x.y; resid[i][j + 2] = x.z; resid[i][j + 3] = x.w;
+                }
+            } else {
+                const float2 x = *reinterpret_cast<const float2*>(src);
+                resid[i][0] = x.x; resid[i][1] = x.y;
+            }
+        }
+    }
     if (EPI == EPI_LIF) {
         // The carried state of the whole micro-tile is read before any of it is written: the stores would otherwise
         // fence the next element's loads, and every element would wait a memory round trip of its own.
@@ -272,16 +290,15 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) q8_gemm_kernel(const Ge
                 for (int j = 0; j < TN; j += 4) {
                     float4* d4 = reinterpret_cast<float4*>(dst + j);
                     if (EPI == EPI_ADD) {
-                        const float4 x = *d4;
-                        o[j] = add(x.x, o[j]); o[j + 1] = add(x.y, o[j + 1]); o[j + 2] = add(x.z, o[j + 2]); o[j + 3] = add(x.w, o[j + 3]);
+                        o[j] = add(resid[i][j], o[j]); o[j + 1] = add(resid[i][j + 1], o[j + 1]);
+                        o[j + 2] = add(resid[i][j + 2], o[j + 2]); o[j + 3] = add(resid[i][j + 3], o[j + 3]);
                     }
                     *d4 = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
                 }
             } else {
                 float2* d2 = reinterpret_cast<float2*>(dst);
                 if (EPI == EPI_ADD) {
-                    const float2 x = *d2;
-                    o[0] = add(x.x, o[0]); o[1] = add(x.y, o[1]);
+                    o[0] = add(resid[i][0], o[0]); o[1] = add(resid[i][1], o[1]);
                 }
                 *d2 = make_float2(o[0], o[1]);
             }

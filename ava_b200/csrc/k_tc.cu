@@ -182,6 +182,16 @@ __global__ void __launch_bounds__(TC_THREADS) tc_gemm_kernel(const __grid_consta
             : "r"(taddr));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (row < M && acc_ok) {
+            // EPI_ADD: the 32 values the products are added to are read before any is written (a store would fence the
+            // loads after it, one memory round trip per group of four)
+            float4 prev[8];
+            if (EPI == EPI_ADD) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    const int c = n0 + c0 + j;
+                    prev[j / 4] = c < N ? *reinterpret_cast<const float4*>(C + (size_t)row * ldc + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
                 const int c = n0 + c0 + j;
@@ -189,12 +199,11 @@ __global__ void __launch_bounds__(TC_THREADS) tc_gemm_kernel(const __grid_consta
                     const float4 sc = *reinterpret_cast<const float4*>(scale + c);
                     float4 o = make_float4(mul(__uint_as_float(r[j]), sc.x), mul(__uint_as_float(r[j + 1]), sc.y),
                                            mul(__uint_as_float(r[j + 2]), sc.z), mul(__uint_as_float(r[j + 3]), sc.w));
-                    float4* dst = reinterpret_cast<float4*>(C + (size_t)row * ldc + c);
                     if (EPI == EPI_ADD) {
-                        const float4 x = *dst;
+                        const float4 x = prev[j / 4];
                         o = make_float4(add(x.x, o.x), add(x.y, o.y), add(x.z, o.z), add(x.w, o.w));
                     }
-                    *dst = o;
+                    *reinterpret_cast<float4*>(C + (size_t)row * ldc + c) = o;
                 }
             }
         }
