@@ -358,12 +358,17 @@ __global__ void mem_prep_kernel(const MemPrepArgs a) {
     // the gate phase's inputs for this thread's first channels are requested now, so that their latency passes while the
     // sums of squares run
     constexpr int PRE = 3;
-    float p_lra[PRE], p_lrb[PRE], p_off[PRE], p_v[PRE], p_v0[PRE];
+    float p_lra[PRE], p_lrb[PRE], p_off[PRE], p_v[PRE], p_v0[PRE], p_za[PRE], p_zb[PRE];
+    const float* zr = a.z + (size_t)r * a.gate_cols;
+    const float vres0 = a.vres ? a.vres[0] : 0.0f, vres1 = a.vres ? a.vres[1] : 0.0f;
 #pragma unroll
     for (int u = 0; u < PRE; ++u) {
         const int c = tid + u * T;
         const bool in = c < d;
         const size_t o = (size_t)r * d + (in ? c : 0);
+        const int e = (in ? c : 0) / hs;
+        p_za[u] = add(zr[2 * a.rank + e], a.ba[e]);
+        p_zb[u] = add(zr[2 * a.rank + nh + e], a.bb[e]);
         p_lra[u] = in ? __ldg(a.lra + o) : 0.0f;
         p_lrb[u] = in ? __ldg(a.lrb + o) : 0.0f;
         p_off[u] = in ? __ldg(a.off + c) : 0.0f;
@@ -378,12 +383,10 @@ __global__ void mem_prep_kernel(const MemPrepArgs a) {
         (which == 0 ? inv_q : which == 1 ? inv_k : inv_e)[e] = inv_l2_seq(src, hs);
     }
     __syncthreads();
-    const float* zr = a.z + (size_t)r * a.gate_cols;
     bool bad = false;
-    auto gates = [&](int c, float in_lra, float in_lrb, float in_off, float v, float v0) {
+    auto gates = [&](int c, float in_lra, float in_lrb, float in_off, float v, float v0, float za, float zb) {
         const int e = c / hs;
         const size_t o = (size_t)r * d + c;
-        const float za = add(zr[2 * a.rank + e], a.ba[e]), zb = add(zr[2 * a.rank + nh + e], a.bb[e]);
         const float la = log_sigmoid(add(add(za, in_off), in_lra));
         const float be = add(mul(sigmoid(add(zb, in_lrb)), 2.0f), 0.0f);
         const float ex = expf_(la);
@@ -394,8 +397,8 @@ __global__ void mem_prep_kernel(const MemPrepArgs a) {
             a.v_first[o] = v;
         } else if (a.vres) {
             // (1 + p0) v + p1 v0 (src/model/fstep/arch.rs:697-702)
-            const float p0 = add(mul(a.vres[0], 1.0f), 1.0f);
-            v = add(mul(v, p0), mul(v0, a.vres[1]));
+            const float p0 = add(mul(vres0, 1.0f), 1.0f);
+            v = add(mul(v, p0), mul(v0, vres1));
         }
         const float w = mul(kn, be);
         const float ah = mul(en, mul(be, ex));
@@ -415,11 +418,13 @@ __global__ void mem_prep_kernel(const MemPrepArgs a) {
 #pragma unroll
     for (int u = 0; u < PRE; ++u) {
         const int c = tid + u * T;
-        if (c < d) gates(c, p_lra[u], p_lrb[u], p_off[u], p_v[u], p_v0[u]);
+        if (c < d) gates(c, p_lra[u], p_lrb[u], p_off[u], p_v[u], p_v0[u], p_za[u], p_zb[u]);
     }
     for (int c = tid + PRE * T; c < d; c += T) {
         const size_t o = (size_t)r * d + c;
-        gates(c, a.lra[o], a.lrb[o], a.off[c], pr[2 * d + c], (!a.first && a.vres) ? a.v_first[o] : 0.0f);
+        const int e = c / hs;
+        gates(c, a.lra[o], a.lrb[o], a.off[c], pr[2 * d + c], (!a.first && a.vres) ? a.v_first[o] : 0.0f, add(zr[2 * a.rank + e], a.ba[e]),
+              add(zr[2 * a.rank + nh + e], a.bb[e]));
     }
     if (bad) atomicOr(a.status, ST_NONFINITE);
     __syncthreads();
@@ -530,10 +535,10 @@ __global__ void dense_mix_kernel(float* x, float* streams, const float* __restri
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= MD) return;
     const float xv = x[i];
-    streams[(int64_t)(n_streams - 1) * MD + i] = xv;
     float mix = xv;
-    for (int j = 0; j < n_streams - 1; ++j) mix = add(mix, mul(streams[(int64_t)j * MD + i], w[j]));
+    for (int j = 0; j < n_streams - 1; ++j) mix = add(mix, mul(streams[(int64_t)j * MD + i], w[j]));  // every load before the first store
     mix = add(mix, mul(xv, w[n_streams - 1]));
+    streams[(int64_t)(n_streams - 1) * MD + i] = xv;
     x[i] = mix;
 }
 
