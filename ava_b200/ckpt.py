@@ -69,6 +69,8 @@ def flags_of(cfg: dict) -> str:
         f.append("--homeostasis 0.1")
     if cfg.get("stp"):
         f.append("--stp")
+    if cfg.get("dendrite"):
+        f.append("--dendrite")
     return " ".join(f)
 
 

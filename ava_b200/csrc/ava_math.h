@@ -161,6 +161,18 @@ AVA_HD float log_sigmoid(float x) {
     return -add(fmaxf(-x, 0.0f), soft);
 }
 
+// tanh from the shared exp: (1 - e^(-2|x|)) / (1 + e^(-2|x|)) with the sign of x; x itself below 2^-12 (the cubic term is
+// under half an ulp there), +-1 above 9.5.  The gains of the dendrites are 1 + tanh (src/model/fstep/arch_f4.rs:34-37).
+AVA_HD float tanhf_(float x) {
+    const float ax = fabsf(x);
+    if (!(ax == ax)) return bits_to_f(0x7fc00000u);
+    if (ax < 2.44140625e-4f) return x;
+    if (ax > 9.5f) return x > 0.0f ? 1.0f : -1.0f;
+    const float t = expf_(mul(ax, -2.0f));
+    const float r = div(sub(1.0f, t), add(1.0f, t));
+    return x < 0.0f ? -r : r;
+}
+
 // float -> bf16 bits, round to nearest even; NaN stays NaN
 AVA_HD uint16_t f_to_bf16(float x) {
     uint32_t u = f_to_bits(x);

@@ -70,6 +70,7 @@ struct HostQ {
 struct BlockDev {
     Dev mem_norm, beta, theta, rho, again, hebb_norm, gate_w, ba, bb, wa2, wb2, off, vres, eng_norm, mlp_norm, dense;
     Dev stp_U, stp_F, stp_D, stp_mix;  // --stp: sigmoids of the synapse's parameters, and its mix
+    Dev dend_a, dend_b;                // --dendrite: A [d][32], B [32][hidden]
     QMat win, wout, proj, wo, eqkv, ewo, w1, w2;
 };
 
@@ -113,6 +114,7 @@ struct ava_engine {
     Dev x, h, proj, ve, vv, vw, vah, vqg, vex, vqs, qw, qa, yraw, y, eqkv, eo, u, act, streams, v_first, logits, tok, next, status;
     Dev gz, lra, lrb;  // the gates' stages: [rows][gate_cols], [rows][d] twice
     Dev uniform;       // [rows] f64: the sampler's draws of one step
+    Dev ctx, dz1, ones;  // --dendrite: the block's memory read [rows][d], its projection [rows][32], a vector of ones [d]
     uint32_t* status_host = nullptr;  // pinned
 
     bool prof = false;
@@ -198,6 +200,8 @@ int64_t f32_len(const ava_config& c, const std::string& name) {
                                   "parts.stp.u_param", "parts.stp.f_param", "parts.stp.d_param", "parts.stp.mix"};
     for (const char* n : vec_d)
         if (rest == n) return d;
+    if (rest == "v51.dend_a") return d * 32;  // DEND_RANK (src/v51.rs:52)
+    if (rest == "v51.dend_b") return (int64_t)32 * c.hidden;
     if (rest == "hebb.wa" || rest == "hebb.wb") return d * nh;
     if (rest == "hebb.ba" || rest == "hebb.bb") return nh;
     if (rest == "hebb.wa1" || rest == "hebb.wb1" || rest == "hebb.wa2" || rest == "hebb.wb2") return d * r;
@@ -308,6 +312,10 @@ int ensure_workspace(ava_engine* e, int rows, int logit_rows = 0) {
     CK(e->tok.alloc(M * sizeof(uint32_t)));
     CK(e->next.alloc(M * sizeof(uint32_t)));
     CK(e->uniform.alloc(M * sizeof(double)));
+    if (c.dendrite && c.fast_mem) {
+        CK(e->ctx.alloc(M * d * f));
+        CK(e->dz1.alloc(M * 32 * f));
+    }
     e->ws_rows = rows;
     return AVA_OK;
 }
@@ -530,7 +538,15 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         launch_mem_post(st, mh.y, c.out_gate ? e->proj.as<float>() + 4 * d : nullptr, pw, M, d, hs, e->y.as<float>(), limbs_for(e, e->y.as<float>(), M, d));
         prof_end(e);
         dbg(e, "y", i, e->y.as<float>(), M, d);
-        gemm(e, "gemm.wo", e->y.as<float>(), d, b.wo, x, d, M, EPI_ADD);
+        if (c.dendrite) {
+            // P: the read after W_o is kept, the context of this block's dendrites
+            gemm(e, "gemm.wo", e->y.as<float>(), d, b.wo, e->ctx.as<float>(), d, M, EPI_STORE);
+            prof_begin(e, "add");
+            launch_add_into(st, x, e->ctx.as<float>(), (int64_t)Md);
+            prof_end(e);
+        } else {
+            gemm(e, "gemm.wo", e->y.as<float>(), d, b.wo, x, d, M, EPI_ADD);
+        }
         dbg(e, "x_mem", i, x, M, d);
         }
         }
@@ -606,6 +622,16 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         launch_kwta(st, e->u.as<float>(), M, H, c.kwta_k, c.relu2, e->act.as<float>());
         prof_end(e);
         dbg(e, "a", i, e->act.as<float>(), M, H);
+        if (c.dendrite && c.fast_mem) {
+            // P: the units times 1 + tanh(head_norm(ctx) A B); h is free here
+            prof_begin(e, "dendrite");
+            launch_rmsnorm(st, e->ctx.as<float>(), e->ones.as<float>(), M, d, h);
+            launch_chain_gemv(st, h, b.dend_a.as<float>(), M, d, 32, e->gate_chunk, e->dz1.as<float>());
+            launch_dend_gain(st, e->dz1.as<float>(), 32, b.dend_b.as<float>(), M, H, e->act.as<float>());
+            prof_end(e);
+            e->launches += 2;
+            dbg(e, "a_dend", i, e->act.as<float>(), M, H);
+        }
         gemm(e, "gemm.w2", e->act.as<float>(), H, b.w2, x, d, M, EPI_ADD, nullptr, true);
         if (c.dense) {
             prof_begin(e, "dense_mix");
@@ -923,6 +949,10 @@ int ava_engine_finalize(ava_engine* e) {
             }
         }
         if ((rc = upload_f32(e, b.theta, p + "mem.theta", c.theta != 0))) return rc;
+        if (c.dendrite && c.fast_mem) {
+            if ((rc = upload_f32(e, b.dend_a, p + "v51.dend_a", true))) return rc;
+            if ((rc = upload_f32(e, b.dend_b, p + "v51.dend_b", true))) return rc;
+        }
         if (c.stp) {
             // U, F, D are sigmoids of their parameters (src/model/fstep/arch_f3.rs:82)
             struct P { Dev* d; const char* n; bool sig; };
@@ -974,6 +1004,10 @@ int ava_engine_finalize(ava_engine* e) {
         }
         if ((rc = upload_q8(e, b.w1, {p + "mlp.w1"}))) return rc;
         if ((rc = upload_q8(e, b.w2, {p + "mlp.w2"}))) return rc;
+    }
+    if (c.dendrite && c.fast_mem) {
+        const std::vector<float> one((size_t)c.d, 1.0f);
+        if ((rc = upload(e, e->ones, one.data(), one.size() * sizeof(float)))) return rc;
     }
     {
         // what `Model::fingerprint` hashes (src/state.rs:1075-1091): the configuration, every 97th value of tok_emb, final.norm,

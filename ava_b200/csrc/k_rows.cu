@@ -331,6 +331,52 @@ __global__ void __launch_bounds__(LR_COLS* LR_LANES) lowrank_kernel(const float*
     }
 }
 
+// --dendrite: act [M][H] *= 1 + tanh(z1 . B) (src/model/fstep/arch_f4.rs:120-141).  Laid out like the stage above: a block
+// owns 16 units (columns of B, in registers per thread when the rank is known), the z1 values of its tile of rows sit
+// in shared memory, sixteen threads side by side on different rows.
+template <int RK>
+__global__ void __launch_bounds__(LR_COLS* LR_LANES) dend_gain_kernel(const float* __restrict__ z1, int rk_rt, const float* __restrict__ B, int M_all, int H,
+                                                                       float* act) {
+    pdl_enter();
+    extern __shared__ __align__(16) float sm[];
+    const int rk = RK ? RK : rk_rt;
+    const int row0 = blockIdx.y * LR_ROWS, M = min(LR_ROWS, M_all - row0);
+    const int tid = threadIdx.x, col = tid % LR_COLS, lane_r = tid / LR_COLS;
+    const int c = blockIdx.x * LR_COLS + col;
+    for (int i = tid; i < M * rk; i += blockDim.x) sm[i] = z1[(size_t)row0 * rk + i];
+    __syncthreads();
+    if (c >= H) return;
+    float w[RK ? RK : 1];
+    if (RK) {
+#pragma unroll
+        for (int j = 0; j < RK; ++j) w[j] = __ldg(B + (size_t)j * H + c);
+    }
+    for (int r = lane_r; r < M; r += LR_LANES) {
+        const float* zr = sm + (size_t)r * rk;
+        float z;
+        if (RK >= 3) {
+            z = mul(w[0], zr[0]);
+#pragma unroll
+            for (int j = 1; j < RK; ++j) z = fma(w[j], zr[j], z);
+        } else {
+            z = chain_k(rk, [&](int j) { return __ldg(B + (size_t)j * H + c); }, [&](int j) { return zr[j]; });
+        }
+        float* ap = act + (size_t)(row0 + r) * H + c;
+        *ap = mul(*ap, add(mul(tanhf_(z), 1.0f), 1.0f));
+    }
+}
+
+__global__ void add_into_kernel(float* x, const float* __restrict__ y, int64_t n) {
+    pdl_enter();
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i + 4 <= n) {
+        const float4 a = *reinterpret_cast<const float4*>(x + i), b = *reinterpret_cast<const float4*>(y + i);
+        *reinterpret_cast<float4*>(x + i) = make_float4(add(a.x, b.x), add(a.y, b.y), add(a.z, b.z), add(a.w, b.w));
+    } else {
+        for (int64_t k = i; k < n; ++k) x[k] = add(x[k], y[k]);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------- memory: gates
 // src/model/fstep/arch.rs:685-803 for one row per block of threads, after the two stages of the gate projections.
 __global__ void mem_prep_kernel(const MemPrepArgs a) {
@@ -618,18 +664,37 @@ void launch_rmsnorm(cudaStream_t st, const float* x, const float* gain, int M, i
     launch_k(rmsnorm_kernel, dim3((M + warps - 1) / warps), dim3(warps * 32), smem, st, x, gain, M, n, y, limbs);
 }
 
+void launch_chain_gemv(cudaStream_t st, const float* x, const float* W, int M, int d, int n, int chunk_rows, float* out) {
+    // a few rows per block share the staged weights
+    const int RB = std::max(1, 256 / n), threads = ((RB * n + 31) / 32) * 32;
+    // as many chunks of the weights in flight as shared memory holds (all of them at d = 768)
+    const size_t chunk = (size_t)chunk_rows * n * sizeof(float), rows_b = (size_t)RB * d * sizeof(float);
+    const int S = (int)std::max<size_t>(1, std::min<size_t>({(size_t)(d / chunk_rows), (size_t)8, (220 * 1024 - rows_b) / chunk}));
+    const size_t smem = rows_b + S * chunk;
+    opt_in_smem(gate_z_kernel, smem);
+    launch_k(gate_z_kernel, dim3((M + RB - 1) / RB), dim3(threads), smem, st, x, W, M, d, n, chunk_rows, RB, S, out);
+}
+
+void launch_dend_gain(cudaStream_t st, const float* z1, int rank, const float* B, int M, int H, float* act) {
+    const size_t smem = (size_t)std::min(M, LR_ROWS) * rank * sizeof(float);
+    const dim3 grid((H + LR_COLS - 1) / LR_COLS, (M + LR_ROWS - 1) / LR_ROWS), block(LR_COLS * LR_LANES);
+    if (rank == 32) {
+        opt_in_smem(dend_gain_kernel<32>, smem);
+        launch_k(dend_gain_kernel<32>, grid, block, smem, st, z1, rank, B, M, H, act);
+    } else {
+        opt_in_smem(dend_gain_kernel<0>, smem);
+        launch_k(dend_gain_kernel<0>, grid, block, smem, st, z1, rank, B, M, H, act);
+    }
+}
+
+void launch_add_into(cudaStream_t st, float* x, const float* y, int64_t n) {
+    launch_k(add_into_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, st, x, y, n);
+}
+
 void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a) {
     const int nh = a.d / a.hs;
-    // stage one: a few rows per block share the staged weights
-    {
-        const int RB = std::max(1, 256 / a.gate_cols), threads = ((RB * a.gate_cols + 31) / 32) * 32;
-        // as many chunks of the weights in flight as shared memory holds (all of them at d = 768)
-        const size_t chunk = (size_t)a.gate_chunk * a.gate_cols * sizeof(float), rows_b = (size_t)RB * a.d * sizeof(float);
-        const int S = (int)std::max<size_t>(1, std::min<size_t>({(size_t)(a.d / a.gate_chunk), (size_t)8, (220 * 1024 - rows_b) / chunk}));
-        const size_t smem = rows_b + S * chunk;
-        opt_in_smem(gate_z_kernel, smem);
-        launch_k(gate_z_kernel, dim3((a.M + RB - 1) / RB), dim3(threads), smem, st, a.h, a.gate_w, a.M, a.d, a.gate_cols, a.gate_chunk, RB, S, a.z);
-    }
+    // stage one
+    launch_chain_gemv(st, a.h, a.gate_w, a.M, a.d, a.gate_cols, a.gate_chunk, a.z);
     // stage two
     {
         const size_t smem = (size_t)std::min(a.M, LR_ROWS) * 2 * a.rank * sizeof(float);

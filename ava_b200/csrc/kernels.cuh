@@ -132,6 +132,14 @@ struct MemPrepArgs {
     float mom;
     uint32_t* status;
 };
+// out [M][n] = x [M][d] . W [d][n] in gemm's one-row order (an fma chain down the rows from the first product), the weights
+// staged through shared memory for a few rows at a time; n a multiple of 4 (at most 224), d a multiple of chunk
+void launch_chain_gemv(cudaStream_t st, const float* x, const float* W, int M, int d, int n, int chunk, float* out);
+// --dendrite (src/model/fstep/arch_f4.rs:120-141): act [M][H] *= 1 + tanh(z1 [M][rank] . B [rank][H]), the product in gemm's
+// one-row order
+void launch_dend_gain(cudaStream_t st, const float* z1, int rank, const float* B, int M, int H, float* act);
+// x += y, elementwise
+void launch_add_into(cudaStream_t st, float* x, const float* y, int64_t n);
 // three launches: the gates' first projection, their low-rank second stage, then everything per row
 void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a);
 

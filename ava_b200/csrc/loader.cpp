@@ -350,6 +350,7 @@ int ava_arch_flags(const char* flags, ava_config* cfg) {
         else if (k == "--lif-scale") cfg->lif_scale = 1;
         else if (k == "--alif") cfg->alif = 1;
         else if (k == "--stp") cfg->stp = 1;
+        else if (k == "--dendrite") cfg->dendrite = 1;
         // switches that shape training or initial values only (src/arch.rs:159-169, src/model.rs:269-275)
         else if (k == "--resid-fix" || k == "--lif-reset-grad") {}
         else if (k == "--timescales" || k == "--lif-init") {

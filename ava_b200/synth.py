@@ -174,6 +174,9 @@ def model(cfg: dict, seed: int = 0, recipe: str = "bench", unit_gain: bool = Tru
             w[p + "eng.norm"] = ones("eng.norm")
             for nm in ("wq", "wk", "wv", "wo"):
                 w[p + "eng." + nm] = g.q8(p + "eng." + nm, d, d, gain(d, 0.5 if nm == "wo" else 1.0))
+        if cfg.get("dendrite") and cfg["fast_mem"]:
+            w[p + "v51.dend_a"] = g.n(p + "v51.dend_a", (d, 32), 1.0 / math.sqrt(d))
+            w[p + "v51.dend_b"] = g.n(p + "v51.dend_b", (32, H), 0.3) if awake else np.zeros((32, H), np.float32)
         w[p + "mlp.norm"] = ones("mlp.norm")
         w[p + "mlp.w1"] = g.q8(p + "mlp.w1", d, H, gain(d))
         w[p + "mlp.w2"] = g.q8(p + "mlp.w2", H, d, gain(cfg["kwta_k"], 0.25))

@@ -55,6 +55,8 @@ typedef struct ava_config {
     int32_t out_gate;       /* 1: silu(h Wg) output gate (OutGate::Silu) */
     int32_t fast_mem;       /* 1: every block has the fast-weight memory (Kind::D / A, src/model.rs:110-118); 0: Kind::S,
                                the spiking memory and the sparse MLP only (the step of src/model/fstep.rs:461-688) */
+    int32_t dendrite;       /* --dendrite: each MLP unit times 1 + tanh(head_norm(c) A B), c the block's memory read after W_o
+                               (src/model/fstep/arch_f4.rs:120-141, src/v51.rs:8-10) */
     int32_t stp;            /* --stp: the spikes reach W_out through a short-term-plastic synapse with carried (u, x)
                                (src/model/fstep/arch_f3.rs:72-106, nn/parts/src/stp.rs) */
     float   mem_momentum;   /* --mem-momentum (0: off) */

@@ -8,6 +8,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <limits>
 #include <cstdio>
 #include <cstring>
 #include <functional>
@@ -205,6 +206,19 @@ void head_norm(float* y, int n, int hs) {
         const float inv = inv_rms(y + h, hs);
         for (int i = 0; i < hs; ++i) y[h + i] = y[h + i] * inv;
     }
+}
+
+// tanh as Rust's f32::tanh (the platform's libm), or, when another exp has been plugged in (orc_set_math), the
+// composite from that exp that the engine's kernels use: the two sides then agree bit for bit.
+float tanh_f(float x) {
+    if (g_exp == libm_exp) return std::tanh(x);
+    const float ax = std::fabs(x);
+    if (!(ax == ax)) return std::numeric_limits<float>::quiet_NaN();
+    if (ax < 2.44140625e-4f) return x;
+    if (ax > 9.5f) return x > 0.0f ? 1.0f : -1.0f;
+    const float t = g_exp(ax * -2.0f);
+    const float r = (1.0f - t) / (1.0f + t);
+    return x < 0.0f ? -r : r;
 }
 
 // fstep.rs:260-262: (exp(-x) * 1 + 1)^-1
@@ -463,6 +477,8 @@ struct Block {
     QW win, wout;
     // short-term plasticity of the spikes' synapse (--stp): parameters and their sigmoids
     std::vector<float> stp_u, stp_f, stp_d, stp_mix, stp_U, stp_F, stp_D;
+    // the dendrites of the MLP's units (--dendrite): A [d, 32], B [32, hidden]
+    std::vector<float> dend_a, dend_b;
     // the fast-weight memory
     std::vector<float> hebb_norm, wa, wb, ba, bb, wa1, wa2, wb1, wb2, off, vres;
     QW wq, wk, wv, we, wg, wo;
@@ -520,7 +536,8 @@ std::vector<float>* f32_slot(orc_model* m, const std::string& name, int64_t* wan
     const E table[] = {
         {"mem.norm", &b.mem_norm, d}, {"mem.beta", &b.beta_param, d}, {"mem.theta", &b.theta, d}, {"mem.arho", &b.arho, d},
         {"mem.again", &b.again, d}, {"parts.stp.u_param", &b.stp_u, d}, {"parts.stp.f_param", &b.stp_f, d}, {"parts.stp.d_param", &b.stp_d, d},
-        {"parts.stp.mix", &b.stp_mix, d}, {"hebb.norm", &b.hebb_norm, d}, {"hebb.wa", &b.wa, (int64_t)d * nh}, {"hebb.wb", &b.wb, (int64_t)d * nh},
+        {"parts.stp.mix", &b.stp_mix, d}, {"v51.dend_a", &b.dend_a, (int64_t)d * 32}, {"v51.dend_b", &b.dend_b, (int64_t)32 * c.hidden},
+        {"hebb.norm", &b.hebb_norm, d}, {"hebb.wa", &b.wa, (int64_t)d * nh}, {"hebb.wb", &b.wb, (int64_t)d * nh},
         {"hebb.ba", &b.ba, nh}, {"hebb.bb", &b.bb, nh}, {"hebb.wa1", &b.wa1, (int64_t)d * r}, {"hebb.wa2", &b.wa2, (int64_t)r * d},
         {"hebb.wb1", &b.wb1, (int64_t)d * r}, {"hebb.wb2", &b.wb2, (int64_t)r * d}, {"hebb.off", &b.off, d}, {"hebb.vres", &b.vres, 2},
         {"eng.norm", &b.eng_norm, d}, {"mlp.norm", &b.mlp_norm, d}, {"dense", &b.dense, i + 2},
@@ -628,6 +645,7 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
     std::vector<char> bad(R, 0);
     bool eng_written = false;
 
+    std::vector<float> ctx;  // P: the block's memory read [R, d]
     for (int i = 0; i < L; ++i) {
         const Block& b = m->blocks[i];
         // ---- the spiking memory (fstep/arch.rs:636-677)
@@ -791,6 +809,7 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
             T("qa", i, tr.qa.data(), nh); T("y_raw", i, tr.yraw.data(), d); T("y", i, y.data(), d);
         }
         q8_matmul(b.wo, y.data(), R, tmp.data());
+        if (cfg.dendrite) ctx.assign(tmp.begin(), tmp.begin() + (size_t)R * d);  // P: the memory's read, the dendrites' context
         add_into(x.data(), tmp.data(), R * d);
         T("x_mem", i, x.data(), d);
         }
@@ -863,6 +882,20 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
 #pragma omp parallel for num_threads(nt) schedule(static)
         for (int r = 0; r < R; ++r) kwta(&u[(size_t)r * H], H, cfg.kwta_k, cfg.relu2 != 0, &a[(size_t)r * H]);
         T("a", i, a.data(), H);
+        if (cfg.dendrite && cfg.fast_mem) {
+            // P (fstep/arch_f4.rs:120-141): the units times 1 + tanh(head_norm(ctx) A B), the two products in gemm's one-row order
+            const int rk = 32;
+#pragma omp parallel for num_threads(nt) schedule(static)
+            for (int r = 0; r < R; ++r) {
+                std::vector<float> hn(ctx.begin() + (size_t)r * d, ctx.begin() + (size_t)(r + 1) * d), z1(rk), z(H);
+                head_norm(hn.data(), d, d);
+                gemv(hn.data(), d, b.dend_a.data(), rk, z1.data());
+                gemv(z1.data(), rk, b.dend_b.data(), H, z.data());
+                float* ar = &a[(size_t)r * H];
+                for (int j = 0; j < H; ++j) ar[j] = ar[j] * (tanh_f(z[j]) * 1.0f + 1.0f);
+            }
+            T("a_dend", i, a.data(), H);
+        }
         q8_matmul(b.w2, a.data(), R, tmp.data());
         add_into(x.data(), tmp.data(), R * d);
 
@@ -1040,7 +1073,8 @@ int orc_model_check(orc_model* m, char* missing, int cap) {
                         {"hebb.off", &b.off, c.fast_mem != 0}, {"hebb.vres", &b.vres, c.fast_mem && c.value_residual && i > 0}, {"eng.norm", &b.eng_norm, i == c.eng_block},
                         {"mlp.norm", &b.mlp_norm, true}, {"dense", &b.dense, c.dense != 0},
                         {"parts.stp.u_param", &b.stp_u, c.stp != 0}, {"parts.stp.f_param", &b.stp_f, c.stp != 0},
-                        {"parts.stp.d_param", &b.stp_d, c.stp != 0}, {"parts.stp.mix", &b.stp_mix, c.stp != 0}};
+                        {"parts.stp.d_param", &b.stp_d, c.stp != 0}, {"parts.stp.mix", &b.stp_mix, c.stp != 0},
+                        {"v51.dend_a", &b.dend_a, c.dendrite && c.fast_mem}, {"v51.dend_b", &b.dend_b, c.dendrite && c.fast_mem}};
         for (const F& f : fs)
             if (f.need && f.v->empty()) return fail(p + f.n);
         struct Q { const char* n; const QW* q; bool need; };

@@ -60,6 +60,8 @@ def test_arch_flag_words():
     assert got["mem_momentum"] == 0.5
     # the released Ava 0.4 adds nine parts the engine does not have: the first of them is named
     assert engine.arch_flags(AVA04_FLAGS + " --stp", base)["stp"] == 1
+    got = engine.arch_flags(AVA04_FLAGS + " --stp --dendrite", base)
+    assert (got["stp"], got["dendrite"]) == (1, 1)
     with pytest.raises(engine.NotApplicable, match="--neuromod"):
         engine.arch_flags(AVA04_FLAGS + " --stp --neuromod 3 --dendrite", base)
     with pytest.raises(engine.NotApplicable, match="gates"):

@@ -456,3 +456,23 @@ def test_stp_signed_multilevel_spikes_stay_bounded(orc):
     for spikes in (rnd, np.full(300, -2.0, np.float32)):
         e, _ = _stp_efficacies(orc, 0.05, 0.99, 0.5, spikes)
         assert np.isfinite(e).all() and np.abs(e).max() <= 1.0 / 0.05 + 1e-3
+
+
+def test_new_parts_start_as_no_change(orc):
+    """The reference initialises the synapse's mix and the dendrites' B to zero so that a model with the parts starts
+    as the model without them (nn/parts/src/stp.rs:61, src/v51.rs:399): the whole step must then give the same bits."""
+    from ava_b200 import config, synth
+    base = config.tiny(head_size=64)
+    full = config.tiny(head_size=64, stp=1, dendrite=1)
+    w0 = synth.model(base, 3, "awake")
+    w1 = synth.model(full, 3, "awake")
+    for k in w1:
+        if k.endswith("parts.stp.mix") or k.endswith("v51.dend_b"):
+            w1[k] = np.zeros_like(w1[k])
+    m0, m1 = orc.OracleModel(base, w0), orc.OracleModel(full, w1)
+    s0, s1 = m0.state(2), m1.state(2)
+    ids = synth.token_ids(base["vocab"], 2, 12)
+    for t in range(12):
+        a, b = s0.step(ids[:, t]), s1.step(ids[:, t])
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), t
+    assert (s1.get(0, "parts.1.stp_x") != 1.0).any()          # the synapse's state moved all the same
