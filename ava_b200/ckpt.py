@@ -71,6 +71,8 @@ def flags_of(cfg: dict) -> str:
         f.append("--stp")
     if cfg.get("dendrite"):
         f.append("--dendrite")
+    if cfg.get("neuromod"):
+        f.append(f"--neuromod {cfg['neuromod']}")
     return " ".join(f)
 
 

@@ -104,6 +104,7 @@ struct ava_engine {
     std::map<std::string, HostQ> host_q8;
 
     Dev tok_emb, final_norm;
+    Dev nm_norm, nm_wn, nm_bn;  // --neuromod: the nucleus (gain [d], read-out padded to [d][4], bias [k])
     QMat head;
     std::vector<std::unique_ptr<BlockDev>> blocks;
     int cw = 0, rb = 0;  // fast-weight slice width and rows per bulk copy
@@ -114,6 +115,7 @@ struct ava_engine {
     Dev x, h, proj, ve, vv, vw, vah, vqg, vex, vqs, qw, qa, yraw, y, eqkv, eo, u, act, streams, v_first, logits, tok, next, status;
     Dev gz, lra, lrb;  // the gates' stages: [rows][gate_cols], [rows][d] twice
     Dev uniform;       // [rows] f64: the sampler's draws of one step
+    Dev sig;           // --neuromod: [rows][4] NE, ACh, DA (and one unused) of the step's token-rows
     Dev ctx, dz1, ones;  // --dendrite: the block's memory read [rows][d], its projection [rows][32], a vector of ones [d]
     uint32_t* status_host = nullptr;  // pinned
 
@@ -193,6 +195,9 @@ int64_t f32_len(const ava_config& c, const std::string& name) {
     const int64_t d = c.d, nh = c.d / c.head_size, r = c.gate_rank;
     if (name == "tok_emb") return (int64_t)c.vocab * d;
     if (name == "final.norm") return d;
+    if (name == "nm.norm" && c.neuromod > 0) return d;
+    if (name == "nm.wn" && c.neuromod > 0) return d * c.neuromod;
+    if (name == "nm.bn" && c.neuromod > 0) return c.neuromod;
     int b;
     std::string rest;
     if (!split_block_name(name, c.n_blocks, &b, &rest)) return -1;
@@ -283,6 +288,7 @@ const char* find_blocker(const ava_config& c, int* cw, int* rb) {
     if (c.gate_rank < 1) return "gate rank must be at least 1";
     if (c.eng_block >= 0 && (c.eng_head_size <= 0 || c.d % c.eng_head_size)) return "bad engram head size";
     if (c.spikes < 0 || c.spikes > 2) return "unknown spike kind";
+    if (c.neuromod != 0 && (c.neuromod < 2 || c.neuromod > 4)) return "neuromod: 2 to 4 signals";
     if (c.fast_mem && (c.head_size % 16 || !mem_heads_tiling(c.head_size, cw, rb, c.mem_momentum > 0.0f))) return "memory head size not covered (a multiple of 16 whose column slice fits shared memory)";
     return nullptr;
 }
@@ -312,6 +318,7 @@ int ensure_workspace(ava_engine* e, int rows, int logit_rows = 0) {
     CK(e->tok.alloc(M * sizeof(uint32_t)));
     CK(e->next.alloc(M * sizeof(uint32_t)));
     CK(e->uniform.alloc(M * sizeof(double)));
+    if (c.neuromod > 0) CK(e->sig.alloc(M * 4 * f));
     if (c.dendrite && c.fast_mem) {
         CK(e->ctx.alloc(M * d * f));
         CK(e->dz1.alloc(M * 32 * f));
@@ -356,8 +363,11 @@ uint16_t* limbs_for(ava_engine* e, const float* dst, int M, int K) {
     return e->limbs.as<uint16_t>();
 }
 
-int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w, float* C, int ldc, int M, GemmEpilogue epi, const LifParams* lif = nullptr, bool sparse = false) {
+int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w, float* C, int ldc, int M, GemmEpilogue epi, const LifParams* lif = nullptr, bool sparse = false,
+         const float* row_gain = nullptr, int row_gain_stride = 0) {
     GemmArgs g{};
+    g.row_gain = row_gain;
+    g.row_gain_stride = row_gain_stride;
     g.A = A;
     g.lda = lda;
     g.W = w.qp();
@@ -462,6 +472,9 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         lp.a = c.alif ? s->lif_a.as<float>() + (size_t)i * Rd : nullptr;
         lp.spikes = c.spikes;
         lp.lif_scale = c.lif_scale;
+        const float* nm = (c.neuromod > 0 && i > 0) ? e->sig.as<float>() : nullptr;  // the nucleus's signals reach the later blocks
+        lp.ne = nm;
+        lp.ne_stride = 4;
         const float* spikes = lp.s;
         if (T == 1) {
             gemm(e, "gemm.win_lif", h, d, b.win, nullptr, 0, M, EPI_LIF, &lp);
@@ -511,6 +524,8 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         mp.qg = e->vqg.as<float>(); mp.ex = e->vex.as<float>(); mp.qw = e->qw.as<float>(); mp.qa = e->qa.as<float>();
         mp.qs = c.mem_momentum > 0.0f ? e->vqs.as<float>() : nullptr;
         mp.mom = c.mem_momentum;
+        mp.ach = (c.neuromod > 0 && i > 0) ? e->sig.as<float>() + 1 : nullptr;
+        mp.ach_stride = 4;
         mp.status = e->status.as<uint32_t>();
         prof_begin(e, "mem_prep");
         launch_mem_prep(st, mp);
@@ -632,13 +647,23 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
             e->launches += 2;
             dbg(e, "a_dend", i, e->act.as<float>(), M, H);
         }
-        gemm(e, "gemm.w2", e->act.as<float>(), H, b.w2, x, d, M, EPI_ADD, nullptr, true);
+        gemm(e, "gemm.w2", e->act.as<float>(), H, b.w2, x, d, M, EPI_ADD, nullptr, true, (c.neuromod > 0 && i > 0) ? e->sig.as<float>() + 2 : nullptr, 4);
         if (c.dense) {
             prof_begin(e, "dense_mix");
             launch_dense_mix(st, x, streams, b.dense.as<float>(), i + 2, (int64_t)Md);
             prof_end(e);
         }
         dbg(e, "x_out", i, x, M, d);
+        if (i == 0 && c.neuromod > 0) {
+            // the nucleus reads block 0's output: 2 sigmoid(rmsnorm(x, g) W + b) per token-row (h and the gates' scratch are free)
+            prof_begin(e, "nucleus");
+            launch_rmsnorm(st, x, e->nm_norm.as<float>(), M, d, h);
+            launch_chain_gemv(st, h, e->nm_wn.as<float>(), M, d, 4, e->gate_chunk, e->gz.as<float>());
+            launch_nucleus(st, e->gz.as<float>(), e->nm_bn.as<float>(), c.neuromod, M, e->sig.as<float>());
+            prof_end(e);
+            e->launches += 2;
+            dbg(e, "nm_sig", 0, e->sig.as<float>(), M, 4);
+        }
     }
     if (want_logits || next) {
         // the head reads the last token's rows only, unless every position's logits were asked for
@@ -1004,6 +1029,16 @@ int ava_engine_finalize(ava_engine* e) {
         }
         if ((rc = upload_q8(e, b.w1, {p + "mlp.w1"}))) return rc;
         if ((rc = upload_q8(e, b.w2, {p + "mlp.w2"}))) return rc;
+    }
+    if (c.neuromod > 0) {
+        if ((rc = upload_f32(e, e->nm_norm, "nm.norm", true))) return rc;
+        if ((rc = upload_f32(e, e->nm_bn, "nm.bn", true))) return rc;
+        auto it = e->host_f32.find("nm.wn");
+        if (it == e->host_f32.end()) return e->fail(AVA_ERR_MISSING, "missing tensor nm.wn");
+        std::vector<float> w4((size_t)c.d * 4, 0.0f);  // [d][k] with the columns padded to four
+        for (int j = 0; j < c.d; ++j)
+            for (int k = 0; k < c.neuromod; ++k) w4[(size_t)j * 4 + k] = it->second[(size_t)j * c.neuromod + k];
+        if ((rc = upload(e, e->nm_wn, w4.data(), w4.size() * sizeof(float)))) return rc;
     }
     if (c.dendrite && c.fast_mem) {
         const std::vector<float> one((size_t)c.d, 1.0f);

@@ -27,9 +27,11 @@ __device__ __forceinline__ void widen4(int w, float* f) {
 
 // One LIF update of one channel (src/model/fstep/arch.rs:173-228) with the hard spike count taken directly (as the
 // reference's own GPU kernel does; the CPU's soft + (hard - soft) equals it).  v, s, a: the carried state, in and out.
-__device__ __forceinline__ void lif_math(int spikes, int lif_scale, bool adaptive, float beta, float th, float rho, float gain, float cur, float& v,
-                                         float& s, float& a) {
+// ne: --neuromod's NE signal of the row (1 without it: a product with 1 is exact), applied after --lif-scale.
+__device__ __forceinline__ void lif_math(int spikes, int lif_scale, bool adaptive, float beta, float th, float rho, float gain, float ne, float cur,
+                                         float& v, float& s, float& a) {
     if (lif_scale) cur = mul(cur, add(mul(beta, -1.0f), 1.0f));
+    cur = mul(cur, ne);
     float th_prev = th, th_t = th;
     if (adaptive) {
         th_prev = add(th, mul(a, gain));
@@ -52,15 +54,15 @@ __device__ __forceinline__ void lif_math(int spikes, int lif_scale, bool adaptiv
     }
 }
 
-__device__ __forceinline__ void lif_core(const LifParams& p, int c, float cur, float& v, float& s, float& a) {
-    lif_math(p.spikes, p.lif_scale, p.rho != nullptr, p.beta[c], p.theta ? p.theta[c] : 1.0f, p.rho ? p.rho[c] : 0.0f, p.rho ? p.gain[c] : 0.0f, cur, v, s,
-             a);
+__device__ __forceinline__ void lif_core(const LifParams& p, int c, float ne, float cur, float& v, float& s, float& a) {
+    lif_math(p.spikes, p.lif_scale, p.rho != nullptr, p.beta[c], p.theta ? p.theta[c] : 1.0f, p.rho ? p.rho[c] : 0.0f, p.rho ? p.gain[c] : 0.0f, ne, cur,
+             v, s, a);
 }
 
 __device__ __forceinline__ void lif_update(const LifParams& p, int r, int c, int d, float cur) {
     const size_t i = (size_t)r * d + c;
     float v = p.v[i], s = p.s[i], a = p.rho ? p.a[i] : 0.0f;
-    lif_core(p, c, cur, v, s, a);
+    lif_core(p, c, p.ne ? p.ne[(size_t)r * p.ne_stride] : 1.0f, cur, v, s, a);
     p.v[i] = v;
     p.s[i] = s;
     if (p.rho) p.a[i] = a;
@@ -80,7 +82,8 @@ __global__ void lif_scan_kernel(const float* __restrict__ cur, const LifParams p
     for (int t = 0; t < T; ++t) {
         const float x = nxt;
         if (t + 1 < T) nxt = cur[(size_t)(t + 1) * Md + i];
-        lif_core(p, c, x, v, s, a);
+        // the NE signal belongs to the token-row: row (t, i / d) of the chunk
+        lif_core(p, c, p.ne ? p.ne[((size_t)t * M + i / d) * p.ne_stride] : 1.0f, x, v, s, a);
         spikes[(size_t)t * Md + i] = s;
     }
     p.v[i] = v;
@@ -243,10 +246,11 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) q8_gemm_kernel(const Ge
         // The carried state of the whole micro-tile is read before any of it is written: the stores would otherwise
         // fence the next element's loads, and every element would wait a memory round trip of its own.
         const LifParams& p = g.lif;
-        float v[TM][TN], sp[TM][TN], tr[TM][TN];
+        float v[TM][TN], sp[TM][TN], tr[TM][TN], lne[TM];
 #pragma unroll
         for (int i = 0; i < TM; ++i) {
             const int r = m0 + ty * TM + i;
+            lne[i] = p.ne ? p.ne[(size_t)(r < g.M ? r : 0) * p.ne_stride] : 1.0f;
 #pragma unroll
             for (int j = 0; j < TN; ++j) {
                 const size_t at = (size_t)(r < g.M ? r : 0) * g.N + c0 + j;
@@ -259,7 +263,8 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) q8_gemm_kernel(const Ge
         for (int i = 0; i < TM; ++i)
 #pragma unroll
             for (int j = 0; j < TN; ++j)
-                lif_math(p.spikes, p.lif_scale, p.rho != nullptr, lbeta[j], lth[j], lrho[j], lgain[j], mul(acc[i][j], scv[j]), v[i][j], sp[i][j], tr[i][j]);
+                lif_math(p.spikes, p.lif_scale, p.rho != nullptr, lbeta[j], lth[j], lrho[j], lgain[j], lne[i], mul(acc[i][j], scv[j]), v[i][j], sp[i][j],
+                         tr[i][j]);
 #pragma unroll
         for (int i = 0; i < TM; ++i) {
             const int r = m0 + ty * TM + i;
@@ -281,6 +286,11 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) q8_gemm_kernel(const Ge
         float o[TN];
 #pragma unroll
         for (int j = 0; j < TN; ++j) o[j] = mul(acc[i][j], scv[j]);
+        if (EPI == EPI_ADD && g.row_gain) {
+            const float rg = g.row_gain[(size_t)r * g.row_gain_stride];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) o[j] = mul(o[j], rg);
+        }
         if (EPI == EPI_LIF) {
             // handled above for the whole micro-tile
         } else {
@@ -395,6 +405,11 @@ __global__ void __launch_bounds__(RT_THREADS) q8_resident_kernel(const GemmArgs 
         float o[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) o[j] = mul(acc[j], scv[j]);
+        if (EPI == EPI_ADD && g.row_gain) {
+            const float rg = g.row_gain[(size_t)r * g.row_gain_stride];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o[j] = mul(o[j], rg);
+        }
         if (EPI == EPI_LIF) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) lif_update(g.lif, r, c0 + j, g.N, o[j]);
@@ -512,6 +527,11 @@ __global__ void __launch_bounds__(EV_THREADS) q8_event_kernel(const GemmArgs g) 
     for (; i < nnz; ++i) step(__ldg(reinterpret_cast<const int*>(wp + (size_t)idx[i] * g.ldw)), vals[i]);
     const float4 sc = *reinterpret_cast<const float4*>(g.scale + c0);
     float o[4] = {mul(acc[0], sc.x), mul(acc[1], sc.y), mul(acc[2], sc.z), mul(acc[3], sc.w)};
+    if (EPI == EPI_ADD && g.row_gain) {
+        const float rg = g.row_gain[(size_t)r * g.row_gain_stride];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = mul(o[j], rg);
+    }
     float4* dst = reinterpret_cast<float4*>(g.C + (size_t)r * g.ldc + c0);
     if (EPI == EPI_ADD) {
         const float4 x = *dst;

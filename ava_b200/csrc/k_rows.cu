@@ -366,6 +366,15 @@ __global__ void __launch_bounds__(LR_COLS* LR_LANES) dend_gain_kernel(const floa
     }
 }
 
+// --neuromod: the nucleus's signals 2 sigmoid(z + b) (src/model/fstep/arch.rs:1108-1119); z and sig are [M][4], k <= 4 used
+__global__ void nucleus_kernel(const float* __restrict__ z, const float* __restrict__ bias, int k, int M, float* __restrict__ sig) {
+    pdl_enter();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= M * 4) return;
+    const int j = i & 3;
+    sig[i] = j < k ? add(mul(sigmoid(add(z[i], bias[j])), 2.0f), 0.0f) : 1.0f;
+}
+
 __global__ void add_into_kernel(float* x, const float* __restrict__ y, int64_t n) {
     pdl_enter();
     const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
@@ -430,11 +439,17 @@ __global__ void mem_prep_kernel(const MemPrepArgs a) {
     }
     __syncthreads();
     bool bad = false;
+    const float ach = a.ach ? a.ach[(size_t)r * a.ach_stride] : 1.0f;
     auto gates = [&](int c, float in_lra, float in_lrb, float in_off, float v, float v0, float za, float zb) {
         const int e = c / hs;
         const size_t o = (size_t)r * d + c;
         const float la = log_sigmoid(add(add(za, in_off), in_lra));
-        const float be = add(mul(sigmoid(add(zb, in_lrb)), 2.0f), 0.0f);
+        float be = add(mul(sigmoid(add(zb, in_lrb)), 2.0f), 0.0f);
+        if (a.ach) {  // --neuromod ACh: times its signal, kept in [0, 2] (maximum, then minimum: src/model/fstep/arch.rs:1121-1129)
+            be = mul(be, ach);
+            be = be < 0.0f ? 0.0f : be;
+            be = be > 2.0f ? 2.0f : be;
+        }
         const float ex = expf_(la);
         const float qn = mul(q[c], inv_q[e]);
         const float kn = mul(kr[c], inv_k[e]);
@@ -666,7 +681,8 @@ void launch_rmsnorm(cudaStream_t st, const float* x, const float* gain, int M, i
 
 void launch_chain_gemv(cudaStream_t st, const float* x, const float* W, int M, int d, int n, int chunk_rows, float* out) {
     // a few rows per block share the staged weights
-    const int RB = std::max(1, 256 / n), threads = ((RB * n + 31) / 32) * 32;
+    // rows per block: one thread per (row, column), the rows' inputs within about 96 KB of shared memory
+    const int RB = std::max(1, std::min(256 / n, (int)((96 * 1024) / ((size_t)d * sizeof(float))))), threads = ((RB * n + 31) / 32) * 32;
     // as many chunks of the weights in flight as shared memory holds (all of them at d = 768)
     const size_t chunk = (size_t)chunk_rows * n * sizeof(float), rows_b = (size_t)RB * d * sizeof(float);
     const int S = (int)std::max<size_t>(1, std::min<size_t>({(size_t)(d / chunk_rows), (size_t)8, (220 * 1024 - rows_b) / chunk}));
@@ -685,6 +701,10 @@ void launch_dend_gain(cudaStream_t st, const float* z1, int rank, const float* B
         opt_in_smem(dend_gain_kernel<0>, smem);
         launch_k(dend_gain_kernel<0>, grid, block, smem, st, z1, rank, B, M, H, act);
     }
+}
+
+void launch_nucleus(cudaStream_t st, const float* z, const float* bias, int k, int M, float* sig) {
+    launch_k(nucleus_kernel, dim3((M * 4 + 255) / 256), dim3(256), 0, st, z, bias, k, M, sig);
 }
 
 void launch_add_into(cudaStream_t st, float* x, const float* y, int64_t n) {

@@ -59,6 +59,8 @@ struct LifParams {
     float* a;            // [M, d] adaptation trace or nullptr
     int spikes;          // 0 binary, 1 ternary, 2 int2
     int lif_scale;       // current times (1 - beta)
+    const float* ne;     // --neuromod NE: the current (after lif_scale) times ne[row * ne_stride], or nullptr
+    int ne_stride;
 };
 
 struct GemmArgs {
@@ -71,6 +73,8 @@ struct GemmArgs {
     int ldc;
     int M, N, K;
     LifParams lif;       // EPI_LIF only (N == d)
+    const float* row_gain;  // EPI_ADD only, or nullptr: the product's row r times row_gain[r * row_gain_stride] before the add
+    int row_gain_stride;    // (--neuromod DA on the MLP's output)
 };
 
 // C = A . W with f32 activations, int8 weights, one fused multiply-add per term in the order k = 0, 1, ... from +0,
@@ -119,6 +123,8 @@ struct MemPrepArgs {
     const float* gate_w; // [d][gate_cols]: wa1 | wb1 | wa | wb side by side, columns padded with zeros to a multiple of 4
     int gate_cols;       // padded column count (at most 256: one chain per thread)
     int gate_chunk;      // rows staged per copy; divides d, a multiple of 8
+    const float* ach;    // --neuromod ACh: the write strength times ach[row * ach_stride], kept in [0, 2]; or nullptr
+    int ach_stride;
     float* z;            // [M][gate_cols] work: h . gate_w (stage one)
     float *lra, *lrb;    // [M, d] work: the low-rank parts of the two gates (stage two)
     const float *ba, *bb, *wa2, *wb2, *off;
@@ -138,6 +144,8 @@ void launch_chain_gemv(cudaStream_t st, const float* x, const float* W, int M, i
 // --dendrite (src/model/fstep/arch_f4.rs:120-141): act [M][H] *= 1 + tanh(z1 [M][rank] . B [rank][H]), the product in gemm's
 // one-row order
 void launch_dend_gain(cudaStream_t st, const float* z1, int rank, const float* B, int M, int H, float* act);
+// --neuromod: sig [M][4] = 2 sigmoid(z [M][4] + bias [k]) for the first k of each row's four
+void launch_nucleus(cudaStream_t st, const float* z, const float* bias, int k, int M, float* sig);
 // x += y, elementwise
 void launch_add_into(cudaStream_t st, float* x, const float* y, int64_t n);
 // three launches: the gates' first projection, their low-rank second stage, then everything per row

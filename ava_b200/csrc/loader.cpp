@@ -351,6 +351,12 @@ int ava_arch_flags(const char* flags, ava_config* cfg) {
         else if (k == "--alif") cfg->alif = 1;
         else if (k == "--stp") cfg->stp = 1;
         else if (k == "--dendrite") cfg->dendrite = 1;
+        else if (k == "--neuromod") {
+            if (!value(&v)) return fail(AVA_ERR_ARG, "--neuromod needs a value");
+            const int n = std::atoi(v.c_str());
+            if (n != 0 && (n < 2 || n > 4)) return fail(AVA_NOT_APPLICABLE, "--neuromod " + v + ": the engine covers 2 to 4 signals");
+            cfg->neuromod = n;
+        }
         // switches that shape training or initial values only (src/arch.rs:159-169, src/model.rs:269-275)
         else if (k == "--resid-fix" || k == "--lif-reset-grad") {}
         else if (k == "--timescales" || k == "--lif-init") {
@@ -430,7 +436,7 @@ int ava_config_from_ckpt(const ava_ckpt* c, const char* kind, const char* arch_f
         int b;
         std::string rest;
         if (!block_name(e.name, &b, &rest)) {
-            if (e.name != "tok_emb" && e.name != "final.norm")
+            if (e.name != "tok_emb" && e.name != "final.norm" && e.name != "nm.norm" && e.name != "nm.wn" && e.name != "nm.bn")
                 return fail(AVA_NOT_APPLICABLE, e.name + ": a tensor of a part the engine does not cover (glance, magnitude code, order head)");
             continue;
         }

@@ -112,6 +112,11 @@ def model(cfg: dict, seed: int = 0, recipe: str = "bench", unit_gain: bool = Tru
 
     w["tok_emb"] = g.n("tok_emb", (V, d), 0.02)
     w["final.norm"] = 1.0 + g.n("final.norm", (d,), 0.05) if awake else np.ones(d, np.float32)
+    if cfg.get("neuromod"):
+        k = cfg["neuromod"]
+        w["nm.norm"] = (1.0 + g.n("nm.norm", (d,), 0.05)).astype(np.float32) if awake else np.ones(d, np.float32)
+        w["nm.wn"] = g.n("nm.wn", (d, k), 0.05) if awake else np.zeros((d, k), np.float32)
+        w["nm.bn"] = g.n("nm.bn", (k,), 0.3) if awake else np.zeros(k, np.float32)
     for i in range(L):
         p = f"b{i}."
         ones = lambda nm: (1.0 + g.n(p + nm, (d,), 0.05)).astype(np.float32) if awake else np.ones(d, np.float32)

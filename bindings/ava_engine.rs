@@ -36,6 +36,7 @@ pub struct AvaConfig {
     pub out_gate: i32,
     pub fast_mem: i32,
     pub dendrite: i32,
+    pub neuromod: i32,
     pub stp: i32,
     pub mem_momentum: f32,
     pub slope: f32,

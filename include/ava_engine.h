@@ -57,6 +57,9 @@ typedef struct ava_config {
                                the spiking memory and the sparse MLP only (the step of src/model/fstep.rs:461-688) */
     int32_t dendrite;       /* --dendrite: each MLP unit times 1 + tanh(head_norm(c) A B), c the block's memory read after W_o
                                (src/model/fstep/arch_f4.rs:120-141, src/v51.rs:8-10) */
+    int32_t neuromod;       /* --neuromod k (2..4; Ava 0.4: 3): a nucleus reads block 0's output and sends every later block three
+                               signals 2 sigmoid(.): NE scales the LIF's input current, ACh the memory's write strength (kept in
+                               [0, 2]), DA the MLP's output (src/v50.rs:20-29, src/model/fstep/arch.rs:616-651,765,996,1029) */
     int32_t stp;            /* --stp: the spikes reach W_out through a short-term-plastic synapse with carried (u, x)
                                (src/model/fstep/arch_f3.rs:72-106, nn/parts/src/stp.rs) */
     float   mem_momentum;   /* --mem-momentum (0: off) */

@@ -497,6 +497,7 @@ struct Block {
 struct orc_model {
     orc_config cfg;
     std::vector<float> tok_emb, final_norm;
+    std::vector<float> nm_norm, nm_wn, nm_bn;  // --neuromod: the nucleus (gain [d], read-out [d, k], bias [k])
     QW head;
     std::vector<Block> blocks;
     int nh() const { return cfg.d / cfg.head_size; }
@@ -523,6 +524,9 @@ std::vector<float>* f32_slot(orc_model* m, const std::string& name, int64_t* wan
     const orc_config& c = m->cfg;
     const int d = c.d, nh = m->nh(), r = c.gate_rank;
     if (name == "tok_emb") { *want = (int64_t)c.vocab * d; return &m->tok_emb; }
+    if (name == "nm.norm") { *want = d; return &m->nm_norm; }
+    if (name == "nm.wn") { *want = (int64_t)d * c.neuromod; return &m->nm_wn; }
+    if (name == "nm.bn") { *want = c.neuromod; return &m->nm_bn; }
     if (name == "final.norm") { *want = d; return &m->final_norm; }
     if (name.size() < 3 || name[0] != 'b') return nullptr;
     const size_t dot = name.find('.');
@@ -646,6 +650,9 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
     bool eng_written = false;
 
     std::vector<float> ctx;  // P: the block's memory read [R, d]
+    // --neuromod (fstep/arch.rs:616,1029,1108-1119; src/v50.rs:20-29): three signals per row after block 0, for the later blocks
+    const int NM_NE = 0, NM_ACH = 1, NM_DA = 2, nk = cfg.neuromod;
+    std::vector<float> sig;  // [R][nk], empty in block 0
     for (int i = 0; i < L; ++i) {
         const Block& b = m->blocks[i];
         // ---- the spiking memory (fstep/arch.rs:636-677)
@@ -659,6 +666,8 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
             float* c_ = &cur[(size_t)r * d];
             if (cfg.lif_scale)
                 for (int c = 0; c < d; ++c) c_[c] = c_[c] * (b.beta[c] * -1.0f + 1.0f);
+            if (!sig.empty())  // NE: the input current times its signal, after --lif-scale
+                for (int c = 0; c < d; ++c) c_[c] = c_[c] * sig[(size_t)r * nk + NM_NE];
             RowState& st = *rows[r];
             nw[r].v[i].resize(d);
             nw[r].a[i].resize(cfg.alif ? d : 0);
@@ -743,6 +752,11 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
                 for (int c = 0; c < hs; ++c) {
                     la[c] = log_sigmoid((za[e] + b.off[o + c]) + lra[o + c]);
                     be[c] = sigmoid(zb[e] + lrb[o + c]) * 2.0f + 0.0f;
+                    if (!sig.empty()) {  // ACh: the write strength times its signal, kept in [0, 2] (maximum, then minimum)
+                        float v = be[c] * sig[(size_t)r * nk + NM_ACH];
+                        v = v < 0.0f ? 0.0f : v;
+                        be[c] = v > 2.0f ? 2.0f : v;
+                    }
                 }
                 for (int c = 0; c < hs; ++c) ek[o + c] = kr[o + c] + weo[(size_t)r * d + o + c];
                 l2_heads(ek.data() + o, hs, hs);
@@ -897,6 +911,9 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
             T("a_dend", i, a.data(), H);
         }
         q8_matmul(b.w2, a.data(), R, tmp.data());
+        if (!sig.empty())  // DA: the MLP's output times its signal
+            for (int r = 0; r < R; ++r)
+                for (int c = 0; c < d; ++c) tmp[(size_t)r * d + c] = tmp[(size_t)r * d + c] * sig[(size_t)r * nk + NM_DA];
         add_into(x.data(), tmp.data(), R * d);
 
         // ---- the dense residual mix (fstep/arch.rs:1014-1024)
@@ -908,6 +925,17 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
             x = mix;
         }
         T("x_out", i, x.data(), d);
+        if (i == 0 && nk > 0) {
+            // the nucleus reads block 0's output: 2 sigmoid(rmsnorm(x, g) W + b)
+            sig.assign((size_t)R * nk, 0.f);
+            for (int r = 0; r < R; ++r) {
+                std::vector<float> hn(d), z(nk);
+                rmsnorm(&x[(size_t)r * d], m->nm_norm.data(), d, hn.data());
+                gemv(hn.data(), d, m->nm_wn.data(), nk, z.data());
+                for (int k = 0; k < nk; ++k) sig[(size_t)r * nk + k] = sigmoid(z[k] + m->nm_bn[k]) * 2.0f + 0.0f;
+            }
+            T("nm_sig", 0, sig.data(), nk);
+        }
     }
 #pragma omp parallel for num_threads(nt) schedule(static)
     for (int r = 0; r < R; ++r) rmsnorm(&x[(size_t)r * d], m->final_norm.data(), d, &h[(size_t)r * d]);
@@ -1061,6 +1089,7 @@ int orc_model_check(orc_model* m, char* missing, int cap) {
     };
     if (m->tok_emb.empty()) return fail("tok_emb");
     if (m->final_norm.empty()) return fail("final.norm");
+    if (c.neuromod > 0 && (m->nm_norm.empty() || m->nm_wn.empty() || m->nm_bn.empty())) return fail("nm.norm / nm.wn / nm.bn");
     if (!m->head.ok()) return fail("head");
     for (int i = 0; i < c.n_blocks; ++i) {
         const Block& b = m->blocks[i];

@@ -62,8 +62,10 @@ def test_arch_flag_words():
     assert engine.arch_flags(AVA04_FLAGS + " --stp", base)["stp"] == 1
     got = engine.arch_flags(AVA04_FLAGS + " --stp --dendrite", base)
     assert (got["stp"], got["dendrite"]) == (1, 1)
-    with pytest.raises(engine.NotApplicable, match="--neuromod"):
-        engine.arch_flags(AVA04_FLAGS + " --stp --neuromod 3 --dendrite", base)
+    got = engine.arch_flags(AVA04_FLAGS + " --stp --neuromod 3 --dendrite", base)
+    assert (got["stp"], got["neuromod"], got["dendrite"]) == (1, 3, 1)
+    with pytest.raises(engine.NotApplicable, match="--letters"):
+        engine.arch_flags(AVA04_FLAGS + " --stp --neuromod 3 --dendrite --letters --dopamine", base)
     with pytest.raises(engine.NotApplicable, match="gates"):
         engine.arch_flags("--head-size 64", base)
     with pytest.raises(engine.NotApplicable, match="sigmoid"):

@@ -459,15 +459,16 @@ def test_stp_signed_multilevel_spikes_stay_bounded(orc):
 
 
 def test_new_parts_start_as_no_change(orc):
-    """The reference initialises the synapse's mix and the dendrites' B to zero so that a model with the parts starts
-    as the model without them (nn/parts/src/stp.rs:61, src/v51.rs:399): the whole step must then give the same bits."""
+    """The reference initialises the synapse's mix and the dendrites' B to zero and the nucleus's read-out
+    and bias too, so that a model with the parts starts as the model without them (nn/parts/src/stp.rs:61, src/v51.rs:399,
+    src/v50.rs:20-22): the whole step must then give the same bits."""
     from ava_b200 import config, synth
     base = config.tiny(head_size=64)
-    full = config.tiny(head_size=64, stp=1, dendrite=1)
+    full = config.tiny(head_size=64, stp=1, dendrite=1, neuromod=3)
     w0 = synth.model(base, 3, "awake")
     w1 = synth.model(full, 3, "awake")
     for k in w1:
-        if k.endswith("parts.stp.mix") or k.endswith("v51.dend_b"):
+        if k.endswith("parts.stp.mix") or k.endswith("v51.dend_b") or k in ("nm.wn", "nm.bn"):  # the nucleus then sends 2 sigmoid(0) = 1
             w1[k] = np.zeros_like(w1[k])
     m0, m1 = orc.OracleModel(base, w0), orc.OracleModel(full, w1)
     s0, s1 = m0.state(2), m1.state(2)
