@@ -364,10 +364,8 @@ uint16_t* limbs_for(ava_engine* e, const float* dst, int M, int K) {
 }
 
 int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w, float* C, int ldc, int M, GemmEpilogue epi, const LifParams* lif = nullptr, bool sparse = false,
-         const float* row_gain = nullptr, int row_gain_stride = 0) {
+         const float* row_gain = nullptr) {
     GemmArgs g{};
-    g.row_gain = row_gain;
-    g.row_gain_stride = row_gain_stride;
     g.A = A;
     g.lda = lda;
     g.W = w.qp();
@@ -379,6 +377,7 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
     g.N = w.dout;
     g.K = w.din;
     if (lif) g.lif = *lif;
+    if (epi == EPI_ADD) g.lif.ne = row_gain;  // [rows][NM_STRIDE]
     if (e->fast && !sparse && w.wt.p && lda == w.din && w.din % 64 == 0 && w.dout % 4 == 0) {
         const size_t need = (size_t)3 * M * w.din * sizeof(uint16_t);
         if (e->limbs.bytes < need) {
@@ -474,7 +473,6 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         lp.lif_scale = c.lif_scale;
         const float* nm = (c.neuromod > 0 && i > 0) ? e->sig.as<float>() : nullptr;  // the nucleus's signals reach the later blocks
         lp.ne = nm;
-        lp.ne_stride = 4;
         const float* spikes = lp.s;
         if (T == 1) {
             gemm(e, "gemm.win_lif", h, d, b.win, nullptr, 0, M, EPI_LIF, &lp);
@@ -647,7 +645,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
             e->launches += 2;
             dbg(e, "a_dend", i, e->act.as<float>(), M, H);
         }
-        gemm(e, "gemm.w2", e->act.as<float>(), H, b.w2, x, d, M, EPI_ADD, nullptr, true, (c.neuromod > 0 && i > 0) ? e->sig.as<float>() + 2 : nullptr, 4);
+        gemm(e, "gemm.w2", e->act.as<float>(), H, b.w2, x, d, M, EPI_ADD, nullptr, true, (c.neuromod > 0 && i > 0) ? e->sig.as<float>() + 2 : nullptr);
         if (c.dense) {
             prof_begin(e, "dense_mix");
             launch_dense_mix(st, x, streams, b.dense.as<float>(), i + 2, (int64_t)Md);

@@ -62,7 +62,7 @@ __device__ __forceinline__ void lif_core(const LifParams& p, int c, float ne, fl
 __device__ __forceinline__ void lif_update(const LifParams& p, int r, int c, int d, float cur) {
     const size_t i = (size_t)r * d + c;
     float v = p.v[i], s = p.s[i], a = p.rho ? p.a[i] : 0.0f;
-    lif_core(p, c, p.ne ? p.ne[(size_t)r * p.ne_stride] : 1.0f, cur, v, s, a);
+    lif_core(p, c, p.ne ? p.ne[(size_t)r * NM_STRIDE] : 1.0f, cur, v, s, a);
     p.v[i] = v;
     p.s[i] = s;
     if (p.rho) p.a[i] = a;
@@ -83,7 +83,7 @@ __global__ void lif_scan_kernel(const float* __restrict__ cur, const LifParams p
         const float x = nxt;
         if (t + 1 < T) nxt = cur[(size_t)(t + 1) * Md + i];
         // the NE signal belongs to the token-row: row (t, i / d) of the chunk
-        lif_core(p, c, p.ne ? p.ne[((size_t)t * M + i / d) * p.ne_stride] : 1.0f, x, v, s, a);
+        lif_core(p, c, p.ne ? p.ne[((size_t)t * M + i / d) * NM_STRIDE] : 1.0f, x, v, s, a);
         spikes[(size_t)t * Md + i] = s;
     }
     p.v[i] = v;
@@ -250,7 +250,7 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) q8_gemm_kernel(const Ge
 #pragma unroll
         for (int i = 0; i < TM; ++i) {
             const int r = m0 + ty * TM + i;
-            lne[i] = p.ne ? p.ne[(size_t)(r < g.M ? r : 0) * p.ne_stride] : 1.0f;
+            lne[i] = p.ne ? p.ne[(size_t)(r < g.M ? r : 0) * NM_STRIDE] : 1.0f;
 #pragma unroll
             for (int j = 0; j < TN; ++j) {
                 const size_t at = (size_t)(r < g.M ? r : 0) * g.N + c0 + j;
@@ -286,8 +286,8 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) q8_gemm_kernel(const Ge
         float o[TN];
 #pragma unroll
         for (int j = 0; j < TN; ++j) o[j] = mul(acc[i][j], scv[j]);
-        if (EPI == EPI_ADD && g.row_gain) {
-            const float rg = g.row_gain[(size_t)r * g.row_gain_stride];
+        if (EPI == EPI_ADD && g.lif.ne) {
+            const float rg = g.lif.ne[(size_t)r * NM_STRIDE];
 #pragma unroll
             for (int j = 0; j < TN; ++j) o[j] = mul(o[j], rg);
         }
@@ -405,8 +405,8 @@ __global__ void __launch_bounds__(RT_THREADS) q8_resident_kernel(const GemmArgs 
         float o[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) o[j] = mul(acc[j], scv[j]);
-        if (EPI == EPI_ADD && g.row_gain) {
-            const float rg = g.row_gain[(size_t)r * g.row_gain_stride];
+        if (EPI == EPI_ADD && g.lif.ne) {
+            const float rg = g.lif.ne[(size_t)r * NM_STRIDE];
 #pragma unroll
             for (int j = 0; j < 4; ++j) o[j] = mul(o[j], rg);
         }
@@ -449,7 +449,7 @@ bool launch_resident(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {
 // shared memory, then every thread walks the list with four columns' accumulators, eight weight loads in flight.
 constexpr int EV_THREADS = 64, EV_COLS = EV_THREADS * 4;
 
-template <int EPI>
+template <int EPI, bool GAIN>
 __global__ void __launch_bounds__(EV_THREADS) q8_event_kernel(const GemmArgs g) {
     pdl_enter();
     extern __shared__ unsigned char ev_smem[];
@@ -527,8 +527,8 @@ __global__ void __launch_bounds__(EV_THREADS) q8_event_kernel(const GemmArgs g) 
     for (; i < nnz; ++i) step(__ldg(reinterpret_cast<const int*>(wp + (size_t)idx[i] * g.ldw)), vals[i]);
     const float4 sc = *reinterpret_cast<const float4*>(g.scale + c0);
     float o[4] = {mul(acc[0], sc.x), mul(acc[1], sc.y), mul(acc[2], sc.z), mul(acc[3], sc.w)};
-    if (EPI == EPI_ADD && g.row_gain) {
-        const float rg = g.row_gain[(size_t)r * g.row_gain_stride];
+    if (GAIN) {
+        const float rg = g.lif.ne[(size_t)r * NM_STRIDE];
 #pragma unroll
         for (int j = 0; j < 4; ++j) o[j] = mul(o[j], rg);
     }
@@ -634,13 +634,16 @@ bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {
     const size_t smem = (size_t)a.K * (sizeof(float) + sizeof(unsigned short));
     if (smem > 200 * 1024) return false;
     dim3 grid((a.N + EV_COLS - 1) / EV_COLS, a.M);
-    if (epi == EPI_ADD) {
-        if (smem > 32 * 1024) cudaFuncSetAttribute(q8_event_kernel<EPI_ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_k(q8_event_kernel<EPI_ADD>, dim3(grid), dim3(EV_THREADS), smem, st, a);
-    } else {
-        if (smem > 32 * 1024) cudaFuncSetAttribute(q8_event_kernel<EPI_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_k(q8_event_kernel<EPI_STORE>, dim3(grid), dim3(EV_THREADS), smem, st, a);
-    }
+    auto go = [&](auto kernel) {
+        if (smem > 32 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch_k(kernel, dim3(grid), dim3(EV_THREADS), smem, st, a);
+    };
+    if (epi == EPI_ADD && a.lif.ne)
+        go(q8_event_kernel<EPI_ADD, true>);
+    else if (epi == EPI_ADD)
+        go(q8_event_kernel<EPI_ADD, false>);
+    else
+        go(q8_event_kernel<EPI_STORE, false>);
     return true;
 }
 

@@ -49,6 +49,9 @@ enum : uint32_t {
 // ---- int8-weight products -----------------------------------------------------------------------------------
 enum GemmEpilogue { EPI_STORE = 0, EPI_ADD = 1, EPI_LIF = 2 };
 
+// The --neuromod signals of a step lie as [rows][NM_STRIDE] floats (NE, ACh, DA, one unused).
+constexpr int NM_STRIDE = 4;
+
 struct LifParams {
     const float* beta;   // [d] leak (already sigmoid of the parameter)
     const float* theta;  // [d] or nullptr (1.0)
@@ -57,25 +60,25 @@ struct LifParams {
     float* v;            // [M, d] membranes, updated in place
     float* s;            // [M, d] spikes, updated in place (this step's spikes are what W_out reads)
     float* a;            // [M, d] adaptation trace or nullptr
+    const float* ne;     // --neuromod NE: the current (after lif_scale) times ne[row * NM_STRIDE], or nullptr
     int spikes;          // 0 binary, 1 ternary, 2 int2
     int lif_scale;       // current times (1 - beta)
-    const float* ne;     // --neuromod NE: the current (after lif_scale) times ne[row * ne_stride], or nullptr
-    int ne_stride;
 };
 
+// The product kernels take this struct by value.  It is kept at 128 bytes (pointers first, no padding): with a larger
+// parameter block the compiler gave the 64x64 tile kernel 80 registers instead of 64, three resident blocks per SM
+// instead of four, and the widest product of the step lost 7%.
 struct GemmArgs {
     const float* A;      // [M, K] activations, row stride lda
-    int lda;
     const int8_t* W;     // [K, N] int8 weights, row stride ldw
-    int ldw;
     const float* scale;  // [N]
     float* C;            // [M, N] output (EPI_STORE / EPI_ADD), row stride ldc
-    int ldc;
+    int lda, ldw, ldc;
     int M, N, K;
-    LifParams lif;       // EPI_LIF only (N == d)
-    const float* row_gain;  // EPI_ADD only, or nullptr: the product's row r times row_gain[r * row_gain_stride] before the add
-    int row_gain_stride;    // (--neuromod DA on the MLP's output)
+    LifParams lif;       // EPI_LIF (N == d).  EPI_ADD reads only lif.ne: when not null, the product's row r is multiplied
+                         // by lif.ne[r * NM_STRIDE] before the add (--neuromod DA on the MLP's output)
 };
+static_assert(sizeof(GemmArgs) == 128, "parameter block of the product kernels");
 
 // C = A . W with f32 activations, int8 weights, one fused multiply-add per term in the order k = 0, 1, ... from +0,
 // the sum then times scale[n]: the bits of the reference's int8 product (src/int8.rs:315-331).  K % 16 == 0, N % 4 == 0.
