@@ -73,6 +73,8 @@ def flags_of(cfg: dict) -> str:
         f.append("--dendrite")
     if cfg.get("neuromod"):
         f.append(f"--neuromod {cfg['neuromod']}")
+    if cfg.get("thalamus"):
+        f.append("--thalamus")
     return " ".join(f)
 
 

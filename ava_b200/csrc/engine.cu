@@ -105,6 +105,7 @@ struct ava_engine {
 
     Dev tok_emb, final_norm;
     Dev nm_norm, nm_wn, nm_bn;  // --neuromod: the nucleus (gain [d], read-out padded to [d][4], bias [k])
+    Dev th_read, th_gate, th_bias;  // --thalamus: reads [blocks][d][16], gates [blocks][16][2], biases [blocks][2]
     QMat head;
     std::vector<std::unique_ptr<BlockDev>> blocks;
     int cw = 0, rb = 0;  // fast-weight slice width and rows per bulk copy
@@ -116,6 +117,7 @@ struct ava_engine {
     Dev gz, lra, lrb;  // the gates' stages: [rows][gate_cols], [rows][d] twice
     Dev uniform;       // [rows] f64: the sampler's draws of one step
     Dev sig;           // --neuromod: [rows][4] NE, ACh, DA (and one unused) of the step's token-rows
+    Dev th_acc, th_g, x_in;  // --thalamus: the relay's sum [rows][16], the block's gates [rows][4], the block's input [rows][d]
     Dev ctx, dz1, ones;  // --dendrite: the block's memory read [rows][d], its projection [rows][32], a vector of ones [d]
     uint32_t* status_host = nullptr;  // pinned
 
@@ -198,6 +200,9 @@ int64_t f32_len(const ava_config& c, const std::string& name) {
     if (name == "nm.norm" && c.neuromod > 0) return d;
     if (name == "nm.wn" && c.neuromod > 0) return d * c.neuromod;
     if (name == "nm.bn" && c.neuromod > 0) return c.neuromod;
+    if (name == "th.read" && c.thalamus) return (int64_t)c.n_blocks * d * 16;  // TH_K (src/v51b.rs:45)
+    if (name == "th.gate" && c.thalamus) return (int64_t)c.n_blocks * 16 * 2;
+    if (name == "th.bias" && c.thalamus) return (int64_t)c.n_blocks * 2;
     int b;
     std::string rest;
     if (!split_block_name(name, c.n_blocks, &b, &rest)) return -1;
@@ -289,6 +294,7 @@ const char* find_blocker(const ava_config& c, int* cw, int* rb) {
     if (c.eng_block >= 0 && (c.eng_head_size <= 0 || c.d % c.eng_head_size)) return "bad engram head size";
     if (c.spikes < 0 || c.spikes > 2) return "unknown spike kind";
     if (c.neuromod != 0 && (c.neuromod < 2 || c.neuromod > 4)) return "neuromod: 2 to 4 signals";
+    if (c.thalamus && !c.fast_mem) return "thalamus: a part of the blocks with the fast-weight memory";
     if (c.fast_mem && (c.head_size % 16 || !mem_heads_tiling(c.head_size, cw, rb, c.mem_momentum > 0.0f))) return "memory head size not covered (a multiple of 16 whose column slice fits shared memory)";
     return nullptr;
 }
@@ -306,7 +312,7 @@ int ensure_workspace(ava_engine* e, int rows, int logit_rows = 0) {
     CK(e->proj.alloc(M * e->proj_w() * f));
     for (Dev* b : {&e->ve, &e->vv, &e->vw, &e->vah, &e->vqg, &e->vex, &e->yraw, &e->y, &e->eo, &e->v_first}) CK(b->alloc(M * d * f));
     if (c.mem_momentum > 0.0f) CK(e->vqs.alloc(M * d * f));
-    CK(e->gz.alloc(M * std::max(e->gate_cols, 4) * f));
+    CK(e->gz.alloc(M * std::max(e->gate_cols, 16) * f));
     CK(e->lra.alloc(M * d * f));
     CK(e->lrb.alloc(M * d * f));
     CK(e->qw.alloc(M * e->nh() * f));
@@ -319,6 +325,11 @@ int ensure_workspace(ava_engine* e, int rows, int logit_rows = 0) {
     CK(e->next.alloc(M * sizeof(uint32_t)));
     CK(e->uniform.alloc(M * sizeof(double)));
     if (c.neuromod > 0) CK(e->sig.alloc(M * 4 * f));
+    if (c.thalamus) {
+        CK(e->th_acc.alloc(M * 16 * f));
+        CK(e->th_g.alloc(M * 4 * f));
+        CK(e->x_in.alloc(M * d * f));
+    }
     if (c.dendrite && c.fast_mem) {
         CK(e->ctx.alloc(M * d * f));
         CK(e->dz1.alloc(M * 32 * f));
@@ -378,7 +389,7 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
     g.K = w.din;
     if (lif) g.lif = *lif;
     if (epi == EPI_ADD) g.lif.ne = row_gain;  // [rows][NM_STRIDE]
-    if (e->fast && !sparse && w.wt.p && lda == w.din && w.din % 64 == 0 && w.dout % 4 == 0) {
+    if (e->fast && !sparse && !row_gain && w.wt.p && lda == w.din && w.din % 64 == 0 && w.dout % 4 == 0) {
         const size_t need = (size_t)3 * M * w.din * sizeof(uint16_t);
         if (e->limbs.bytes < need) {
             CK(e->limbs.alloc(need));
@@ -453,8 +464,24 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         prof_end(e);
         dbg(e, "x_in", -1, x, M, d);
     }
+    // TH: the relay reads the stream (16 numbers per token-row) into its sum and sets block j's gates; h and the gates'
+    // scratch are free at both places it is called from
+    auto relay_read = [&](int j) {
+        prof_begin(e, "relay");
+        launch_rmsnorm(st, x, e->ones.as<float>(), M, d, h);
+        launch_chain_gemv(st, h, e->th_read.as<float>() + (size_t)j * d * 16, M, d, 16, e->gate_chunk, e->gz.as<float>());
+        launch_relay(st, e->gz.as<float>(), e->th_acc.as<float>(), j == 0, j + 1, e->th_gate.as<float>() + (size_t)j * 32,
+                     e->th_bias.as<float>() + (size_t)j * 2, M, e->th_g.as<float>());
+        prof_end(e);
+        e->launches += 2;
+        dbg(e, "th_g", j, e->th_g.as<float>(), M, 4);
+    };
+    if (c.thalamus && phase != PHASE_END) relay_read(0);
     for (int i = phase == PHASE_END ? c.eng_block : 0; i < L; ++i) {
         BlockDev& b = *e->blocks[i];
+        if (c.thalamus && !(phase == PHASE_END && i == c.eng_block))
+            CK(cudaMemcpyAsync(e->x_in.p, x, Md * sizeof(float), cudaMemcpyDeviceToDevice, st));  // the residual rule's x_in
+        const float* th_mem = c.thalamus ? e->th_g.as<float>() + 1 : nullptr;
         if (!(phase == PHASE_END && i == c.eng_block)) {
         // ---- the spiking memory
         prof_begin(e, "rmsnorm");
@@ -555,10 +582,10 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
             // P: the read after W_o is kept, the context of this block's dendrites
             gemm(e, "gemm.wo", e->y.as<float>(), d, b.wo, e->ctx.as<float>(), d, M, EPI_STORE);
             prof_begin(e, "add");
-            launch_add_into(st, x, e->ctx.as<float>(), (int64_t)Md);
+            launch_add_into(st, x, e->ctx.as<float>(), (int64_t)Md, th_mem, d);
             prof_end(e);
         } else {
-            gemm(e, "gemm.wo", e->y.as<float>(), d, b.wo, x, d, M, EPI_ADD);
+            gemm(e, "gemm.wo", e->y.as<float>(), d, b.wo, x, d, M, EPI_ADD, nullptr, false, th_mem);
         }
         dbg(e, "x_mem", i, x, M, d);
         }
@@ -646,12 +673,18 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
             dbg(e, "a_dend", i, e->act.as<float>(), M, H);
         }
         gemm(e, "gemm.w2", e->act.as<float>(), H, b.w2, x, d, M, EPI_ADD, nullptr, true, (c.neuromod > 0 && i > 0) ? e->sig.as<float>() + 2 : nullptr);
+        if (c.thalamus) {
+            prof_begin(e, "relay");
+            launch_relay_res(st, x, e->x_in.as<float>(), e->th_g.as<float>(), M, d);
+            prof_end(e);
+        }
         if (c.dense) {
             prof_begin(e, "dense_mix");
             launch_dense_mix(st, x, streams, b.dense.as<float>(), i + 2, (int64_t)Md);
             prof_end(e);
         }
         dbg(e, "x_out", i, x, M, d);
+        if (c.thalamus && i + 1 < L) relay_read(i + 1);
         if (i == 0 && c.neuromod > 0) {
             // the nucleus reads block 0's output: 2 sigmoid(rmsnorm(x, g) W + b) per token-row (h and the gates' scratch are free)
             prof_begin(e, "nucleus");
@@ -1038,7 +1071,12 @@ int ava_engine_finalize(ava_engine* e) {
             for (int k = 0; k < c.neuromod; ++k) w4[(size_t)j * 4 + k] = it->second[(size_t)j * c.neuromod + k];
         if ((rc = upload(e, e->nm_wn, w4.data(), w4.size() * sizeof(float)))) return rc;
     }
-    if (c.dendrite && c.fast_mem) {
+    if (c.thalamus) {
+        if ((rc = upload_f32(e, e->th_read, "th.read", true))) return rc;
+        if ((rc = upload_f32(e, e->th_gate, "th.gate", true))) return rc;
+        if ((rc = upload_f32(e, e->th_bias, "th.bias", true))) return rc;
+    }
+    if ((c.dendrite && c.fast_mem) || c.thalamus) {
         const std::vector<float> one((size_t)c.d, 1.0f);
         if ((rc = upload(e, e->ones, one.data(), one.size() * sizeof(float)))) return rc;
     }

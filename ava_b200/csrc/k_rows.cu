@@ -375,15 +375,71 @@ __global__ void nucleus_kernel(const float* __restrict__ z, const float* __restr
     sig[i] = j < k ? add(mul(sigmoid(add(z[i], bias[j])), 2.0f), 0.0f) : 1.0f;
 }
 
-__global__ void add_into_kernel(float* x, const float* __restrict__ y, int64_t n) {
+// x += y, or with a row gain x += y * gain[row * NM_STRIDE] (rows of d, d % 4 == 0)
+__global__ void add_into_kernel(float* x, const float* __restrict__ y, int64_t n, const float* __restrict__ gain, int d) {
     pdl_enter();
     const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i + 4 <= n) {
-        const float4 a = *reinterpret_cast<const float4*>(x + i), b = *reinterpret_cast<const float4*>(y + i);
+        const float4 a = *reinterpret_cast<const float4*>(x + i);
+        float4 b = *reinterpret_cast<const float4*>(y + i);
+        if (gain) {
+            const float g = gain[(i / d) * NM_STRIDE];
+            b = make_float4(mul(b.x, g), mul(b.y, g), mul(b.z, g), mul(b.w, g));
+        }
         *reinterpret_cast<float4*>(x + i) = make_float4(add(a.x, b.x), add(a.y, b.y), add(a.z, b.z), add(a.w, b.w));
     } else {
-        for (int64_t k = i; k < n; ++k) x[k] = add(x[k], y[k]);
+        for (int64_t k = i; k < n; ++k) x[k] = add(x[k], gain ? mul(y[k], gain[(k / d) * NM_STRIDE]) : y[k]);
     }
+}
+
+// --thalamus, one thread per token-row (src/model/fstep/arch_f2.rs:93-118, src/v51b.rs:312-321): the relay's sum takes
+// this read (thr [M][16]; the first read starts the sum), then the next block's gates are
+// 2 sigmoid(tanh(acc * (1 / sqrt(reads)) + 0) G + c) with the 16-term product as an ordered chain from G[0] f[0].
+// g is [M][NM_STRIDE]: [0] the residual's gate, [1] the memory read's.
+__global__ void relay_kernel(const float* __restrict__ thr, float* __restrict__ acc, int first, float mulf, const float* __restrict__ G,
+                             const float* __restrict__ bias, int M, float* __restrict__ g) {
+    pdl_enter();
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= M) return;
+    float z0 = -0.0f, z1 = -0.0f;
+#pragma unroll
+    for (int k4 = 0; k4 < 16; k4 += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(thr + (size_t)r * 16 + k4);
+        float4 a = t;
+        if (!first) {
+            const float4 o = *reinterpret_cast<const float4*>(acc + (size_t)r * 16 + k4);
+            a = make_float4(add(o.x, t.x), add(o.y, t.y), add(o.z, t.z), add(o.w, t.w));
+        }
+        *reinterpret_cast<float4*>(acc + (size_t)r * 16 + k4) = a;
+        const float av[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float f = tanhf_(add(mul(av[u], mulf), 0.0f));
+            const int k = k4 + u;
+            if (k == 0) {
+                z0 = mul(G[0], f);
+                z1 = mul(G[1], f);
+            } else {
+                z0 = fma(G[k * 2], f, z0);
+                z1 = fma(G[k * 2 + 1], f, z1);
+            }
+        }
+    }
+    g[(size_t)r * NM_STRIDE] = add(mul(sigmoid(add(z0, bias[0])), 2.0f), 0.0f);
+    g[(size_t)r * NM_STRIDE + 1] = add(mul(sigmoid(add(z1, bias[1])), 2.0f), 0.0f);
+    g[(size_t)r * NM_STRIDE + 2] = 1.0f;
+    g[(size_t)r * NM_STRIDE + 3] = 1.0f;
+}
+
+// --thalamus: the residual rule x + (x - x_in)(g * 1 + -1) on a block's whole change (src/v51b.rs:323-325)
+__global__ void relay_res_kernel(float* x, const float* __restrict__ x_in, const float* __restrict__ g, int64_t n, int d) {
+    pdl_enter();
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= n) return;
+    const float gm1 = add(mul(g[(i / d) * NM_STRIDE], 1.0f), -1.0f);
+    const float4 a = *reinterpret_cast<const float4*>(x + i), b = *reinterpret_cast<const float4*>(x_in + i);
+    *reinterpret_cast<float4*>(x + i) = make_float4(add(a.x, mul(sub(a.x, b.x), gm1)), add(a.y, mul(sub(a.y, b.y), gm1)),
+                                                    add(a.z, mul(sub(a.z, b.z), gm1)), add(a.w, mul(sub(a.w, b.w), gm1)));
 }
 
 // ---------------------------------------------------------------------------------------------------- memory: gates
@@ -707,8 +763,18 @@ void launch_nucleus(cudaStream_t st, const float* z, const float* bias, int k, i
     launch_k(nucleus_kernel, dim3((M * 4 + 255) / 256), dim3(256), 0, st, z, bias, k, M, sig);
 }
 
-void launch_add_into(cudaStream_t st, float* x, const float* y, int64_t n) {
-    launch_k(add_into_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, st, x, y, n);
+void launch_add_into(cudaStream_t st, float* x, const float* y, int64_t n, const float* row_gain, int d) {
+    launch_k(add_into_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, st, x, y, n, row_gain, d);
+}
+
+void launch_relay(cudaStream_t st, const float* thr, float* acc, bool first, int reads, const float* G, const float* bias, int M, float* g) {
+    const float mulf = (float)(1.0 / std::sqrt((double)reads));
+    launch_k(relay_kernel, dim3((M + 127) / 128), dim3(128), 0, st, thr, acc, first ? 1 : 0, mulf, G, bias, M, g);
+}
+
+void launch_relay_res(cudaStream_t st, float* x, const float* x_in, const float* g, int M, int d) {
+    const int64_t n = (int64_t)M * d;
+    launch_k(relay_res_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, st, x, x_in, g, n, d);
 }
 
 void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a) {

@@ -150,7 +150,11 @@ void launch_dend_gain(cudaStream_t st, const float* z1, int rank, const float* B
 // --neuromod: sig [M][4] = 2 sigmoid(z [M][4] + bias [k]) for the first k of each row's four
 void launch_nucleus(cudaStream_t st, const float* z, const float* bias, int k, int M, float* sig);
 // x += y, elementwise
-void launch_add_into(cudaStream_t st, float* x, const float* y, int64_t n);
+void launch_add_into(cudaStream_t st, float* x, const float* y, int64_t n, const float* row_gain = nullptr, int d = 0);
+// --thalamus: the relay takes one 16-wide read per token-row into its sum and gives the next block's gates [M][NM_STRIDE]
+// ([0] residual, [1] memory read); then the residual rule on a block's whole change (src/model/fstep/arch_f2.rs:62-153)
+void launch_relay(cudaStream_t st, const float* thr, float* acc, bool first, int reads, const float* G, const float* bias, int M, float* g);
+void launch_relay_res(cudaStream_t st, float* x, const float* x_in, const float* g, int M, int d);
 // three launches: the gates' first projection, their low-rank second stage, then everything per row
 void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a);
 

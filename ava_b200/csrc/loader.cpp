@@ -351,6 +351,7 @@ int ava_arch_flags(const char* flags, ava_config* cfg) {
         else if (k == "--alif") cfg->alif = 1;
         else if (k == "--stp") cfg->stp = 1;
         else if (k == "--dendrite") cfg->dendrite = 1;
+        else if (k == "--thalamus") cfg->thalamus = 1;
         else if (k == "--neuromod") {
             if (!value(&v)) return fail(AVA_ERR_ARG, "--neuromod needs a value");
             const int n = std::atoi(v.c_str());
@@ -436,7 +437,7 @@ int ava_config_from_ckpt(const ava_ckpt* c, const char* kind, const char* arch_f
         int b;
         std::string rest;
         if (!block_name(e.name, &b, &rest)) {
-            if (e.name != "tok_emb" && e.name != "final.norm" && e.name != "nm.norm" && e.name != "nm.wn" && e.name != "nm.bn")
+            if (e.name != "tok_emb" && e.name != "final.norm" && e.name != "nm.norm" && e.name != "nm.wn" && e.name != "nm.bn" && e.name != "th.read" && e.name != "th.gate" && e.name != "th.bias")
                 return fail(AVA_NOT_APPLICABLE, e.name + ": a tensor of a part the engine does not cover (glance, magnitude code, order head)");
             continue;
         }

@@ -117,6 +117,11 @@ def model(cfg: dict, seed: int = 0, recipe: str = "bench", unit_gain: bool = Tru
         w["nm.norm"] = (1.0 + g.n("nm.norm", (d,), 0.05)).astype(np.float32) if awake else np.ones(d, np.float32)
         w["nm.wn"] = g.n("nm.wn", (d, k), 0.05) if awake else np.zeros((d, k), np.float32)
         w["nm.bn"] = g.n("nm.bn", (k,), 0.3) if awake else np.zeros(k, np.float32)
+    if cfg.get("thalamus"):
+        # the reference starts the reads as seeded noise / sqrt(d) and the gates at zero (every gate exactly 1)
+        w["th.read"] = g.n("th.read", (L, d, 16), 1.0 / math.sqrt(d))
+        w["th.gate"] = g.n("th.gate", (L, 16, 2), 0.5) if awake else np.zeros((L, 16, 2), np.float32)
+        w["th.bias"] = g.n("th.bias", (L, 2), 0.3) if awake else np.zeros((L, 2), np.float32)
     for i in range(L):
         p = f"b{i}."
         ones = lambda nm: (1.0 + g.n(p + nm, (d,), 0.05)).astype(np.float32) if awake else np.ones(d, np.float32)

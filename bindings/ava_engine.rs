@@ -38,6 +38,7 @@ pub struct AvaConfig {
     pub dendrite: i32,
     pub neuromod: i32,
     pub stp: i32,
+    pub thalamus: i32,
     pub mem_momentum: f32,
     pub slope: f32,
 }

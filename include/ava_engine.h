@@ -62,6 +62,10 @@ typedef struct ava_config {
                                [0, 2]), DA the MLP's output (src/v50.rs:20-29, src/model/fstep/arch.rs:616-651,765,996,1029) */
     int32_t stp;            /* --stp: the spikes reach W_out through a short-term-plastic synapse with carried (u, x)
                                (src/model/fstep/arch_f3.rs:72-106, nn/parts/src/stp.rs) */
+    int32_t thalamus;       /* --thalamus: a relay sums 16-wide reads rmsnorm(x) R_j of the blocks' input and of every block's
+                               output; block i's two gates 2 sigmoid(tanh(sum / sqrt(reads)) G_i + c_i) scale its memory read
+                               and its whole change of the stream (src/model/fstep/arch_f2.rs:62-153, src/v51b.rs:312-325);
+                               weights th.read [blocks, d, 16], th.gate [blocks, 16, 2], th.bias [blocks, 2]; needs fast_mem */
     float   mem_momentum;   /* --mem-momentum (0: off) */
     float   slope;          /* --surrogate-slope (does not change forward values) */
 } ava_config;

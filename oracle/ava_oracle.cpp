@@ -498,6 +498,7 @@ struct orc_model {
     orc_config cfg;
     std::vector<float> tok_emb, final_norm;
     std::vector<float> nm_norm, nm_wn, nm_bn;  // --neuromod: the nucleus (gain [d], read-out [d, k], bias [k])
+    std::vector<float> th_read, th_gate, th_bias;  // --thalamus: reads [L, d, 16], gates [L, 16, 2], biases [L, 2]
     QW head;
     std::vector<Block> blocks;
     int nh() const { return cfg.d / cfg.head_size; }
@@ -527,6 +528,9 @@ std::vector<float>* f32_slot(orc_model* m, const std::string& name, int64_t* wan
     if (name == "nm.norm") { *want = d; return &m->nm_norm; }
     if (name == "nm.wn") { *want = (int64_t)d * c.neuromod; return &m->nm_wn; }
     if (name == "nm.bn") { *want = c.neuromod; return &m->nm_bn; }
+    if (name == "th.read") { *want = (int64_t)c.n_blocks * d * 16; return &m->th_read; }
+    if (name == "th.gate") { *want = (int64_t)c.n_blocks * 16 * 2; return &m->th_gate; }
+    if (name == "th.bias") { *want = (int64_t)c.n_blocks * 2; return &m->th_bias; }
     if (name == "final.norm") { *want = d; return &m->final_norm; }
     if (name.size() < 3 || name[0] != 'b') return nullptr;
     const size_t dot = name.find('.');
@@ -653,8 +657,37 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
     // --neuromod (fstep/arch.rs:616,1029,1108-1119; src/v50.rs:20-29): three signals per row after block 0, for the later blocks
     const int NM_NE = 0, NM_ACH = 1, NM_DA = 2, nk = cfg.neuromod;
     std::vector<float> sig;  // [R][nk], empty in block 0
+    // --thalamus (fstep/arch_f2.rs:62-153; src/v51b.rs:312-325): the relay's running sum of reads rmsnorm(x) R_j [R][16],
+    // each block's two gates 2 sigmoid(tanh(acc / sqrt(reads)) G_i + c_i): [0] the residual's, [1] the memory read's
+    const int TK = 16;
+    std::vector<float> th_acc, th_g, x_in;
+    int th_reads = 0;
+    const std::vector<float> th_ones(cfg.thalamus ? d : 0, 1.0f);
+    auto relay_read = [&](int j) {
+        if (th_acc.empty()) th_acc.assign((size_t)R * TK, 0.f);
+        for (int r = 0; r < R; ++r) {
+            std::vector<float> xn(d), z(TK);
+            rmsnorm(&x[(size_t)r * d], th_ones.data(), d, xn.data());
+            gemv(xn.data(), d, &m->th_read[(size_t)j * d * TK], TK, z.data());
+            for (int k = 0; k < TK; ++k) th_acc[(size_t)r * TK + k] = j == 0 ? z[k] : th_acc[(size_t)r * TK + k] + z[k];
+        }
+        ++th_reads;
+    };
+    if (cfg.thalamus) relay_read(0);
     for (int i = 0; i < L; ++i) {
         const Block& b = m->blocks[i];
+        if (cfg.thalamus) {
+            x_in = x;
+            th_g.assign((size_t)R * 2, 1.0f);
+            const float mulf = (float)(1.0 / std::sqrt((double)th_reads));
+            for (int r = 0; r < R; ++r) {
+                float f[TK], z[2];
+                for (int k = 0; k < TK; ++k) f[k] = tanh_f(th_acc[(size_t)r * TK + k] * mulf + 0.0f);
+                gemv(f, TK, &m->th_gate[(size_t)i * TK * 2], 2, z);
+                for (int c = 0; c < 2; ++c) th_g[(size_t)r * 2 + c] = sigmoid(z[c] + m->th_bias[(size_t)i * 2 + c]) * 2.0f + 0.0f;
+            }
+            T("th_g", i, th_g.data(), 2);
+        }
         // ---- the spiking memory (fstep/arch.rs:636-677)
 #pragma omp parallel for num_threads(nt) schedule(static)
         for (int r = 0; r < R; ++r) rmsnorm(&x[(size_t)r * d], b.mem_norm.data(), d, &h[(size_t)r * d]);
@@ -824,6 +857,9 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
         }
         q8_matmul(b.wo, y.data(), R, tmp.data());
         if (cfg.dendrite) ctx.assign(tmp.begin(), tmp.begin() + (size_t)R * d);  // P: the memory's read, the dendrites' context
+        if (cfg.thalamus)  // TH: the memory gate (after the dendrites' copy)
+            for (int r = 0; r < R; ++r)
+                for (int c = 0; c < d; ++c) tmp[(size_t)r * d + c] = tmp[(size_t)r * d + c] * th_g[(size_t)r * 2 + 1];
         add_into(x.data(), tmp.data(), R * d);
         T("x_mem", i, x.data(), d);
         }
@@ -915,6 +951,14 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
             for (int r = 0; r < R; ++r)
                 for (int c = 0; c < d; ++c) tmp[(size_t)r * d + c] = tmp[(size_t)r * d + c] * sig[(size_t)r * nk + NM_DA];
         add_into(x.data(), tmp.data(), R * d);
+        if (cfg.thalamus)  // TH: the residual rule x + (x - x_in)(g_res 1 + -1) on the block's whole change
+            for (int r = 0; r < R; ++r) {
+                const float gm1 = th_g[(size_t)r * 2] * 1.0f + -1.0f;
+                for (int c = 0; c < d; ++c) {
+                    const size_t at = (size_t)r * d + c;
+                    x[at] = x[at] + (x[at] - x_in[at]) * gm1;
+                }
+            }
 
         // ---- the dense residual mix (fstep/arch.rs:1014-1024)
         if (cfg.dense) {
@@ -925,6 +969,7 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
             x = mix;
         }
         T("x_out", i, x.data(), d);
+        if (cfg.thalamus && i + 1 < L) relay_read(i + 1);  // the relay reads this block's output for the later gates
         if (i == 0 && nk > 0) {
             // the nucleus reads block 0's output: 2 sigmoid(rmsnorm(x, g) W + b)
             sig.assign((size_t)R * nk, 0.f);
@@ -1090,6 +1135,7 @@ int orc_model_check(orc_model* m, char* missing, int cap) {
     if (m->tok_emb.empty()) return fail("tok_emb");
     if (m->final_norm.empty()) return fail("final.norm");
     if (c.neuromod > 0 && (m->nm_norm.empty() || m->nm_wn.empty() || m->nm_bn.empty())) return fail("nm.norm / nm.wn / nm.bn");
+    if (c.thalamus && (m->th_read.empty() || m->th_gate.empty() || m->th_bias.empty())) return fail("th.read / th.gate / th.bias");
     if (!m->head.ok()) return fail("head");
     for (int i = 0; i < c.n_blocks; ++i) {
         const Block& b = m->blocks[i];

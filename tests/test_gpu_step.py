@@ -59,6 +59,8 @@ CONFIGS = {
     "stp": dict(stp=1, head_size=64),
     "dendrite": dict(dendrite=1, stp=1, head_size=64, mem_momentum=0.5),               # --dendrite (with --stp and momentum, as Ava 0.4 has them)                                                   # --stp: the spikes through the plastic synapse
     "neuromod": dict(neuromod=3, stp=1, dendrite=1, head_size=64),                       # --neuromod 3 with the two parts above
+    "thalamus": dict(thalamus=1, neuromod=3, stp=1, dendrite=1, head_size=64, mem_momentum=0.5),  # --thalamus with the three parts above
+    "thalamus_alone": dict(thalamus=1, head_size=64),                                    # its gates on the fused W_o epilogue
     # the reference's kind S (Ava-M's): spiking memory + sparse MLP only, binary spikes, relu
     "kind_s": dict(head_size=128, eng_block=-1, spikes=0, alif=0, theta=0, lif_scale=0, value_residual=0, relu2=0, dense=0, out_gate=0,
                    fast_mem=0),
@@ -138,7 +140,7 @@ def test_forward_with_state_equals_steps(orc_same_math):
     assert np.array_equal(bits(tail), bits(want[:, 6:]))
 
 
-@pytest.mark.parametrize("name", ["ava04_small", "one_head_bf16", "binary_plain", "momentum", "kind_s", "stp", "dendrite", "neuromod"])
+@pytest.mark.parametrize("name", ["ava04_small", "one_head_bf16", "binary_plain", "momentum", "kind_s", "stp", "dendrite", "neuromod", "thalamus", "thalamus_alone"])
 @pytest.mark.parametrize("chunk", [1, 5, 64])
 def test_chunked_prompt_equals_steps(orc_same_math, name, chunk):
     """Reading a prompt in chunks (token-parallel products, the recurrences in order inside their kernels) gives the

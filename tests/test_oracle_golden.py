@@ -461,14 +461,15 @@ def test_stp_signed_multilevel_spikes_stay_bounded(orc):
 def test_new_parts_start_as_no_change(orc):
     """The reference initialises the synapse's mix and the dendrites' B to zero and the nucleus's read-out
     and bias too, so that a model with the parts starts as the model without them (nn/parts/src/stp.rs:61, src/v51.rs:399,
-    src/v50.rs:20-22): the whole step must then give the same bits."""
+    src/v50.rs:20-22), and the relay's gate matrices and biases (src/v51b.rs:282-283): the whole step must then give the
+    same bits."""
     from ava_b200 import config, synth
     base = config.tiny(head_size=64)
-    full = config.tiny(head_size=64, stp=1, dendrite=1, neuromod=3)
+    full = config.tiny(head_size=64, stp=1, dendrite=1, neuromod=3, thalamus=1)
     w0 = synth.model(base, 3, "awake")
     w1 = synth.model(full, 3, "awake")
     for k in w1:
-        if k.endswith("parts.stp.mix") or k.endswith("v51.dend_b") or k in ("nm.wn", "nm.bn"):  # the nucleus then sends 2 sigmoid(0) = 1
+        if k.endswith("parts.stp.mix") or k.endswith("v51.dend_b") or k in ("nm.wn", "nm.bn", "th.gate", "th.bias"):  # nucleus and relay then send 2 sigmoid(0) = 1
             w1[k] = np.zeros_like(w1[k])
     m0, m1 = orc.OracleModel(base, w0), orc.OracleModel(full, w1)
     s0, s1 = m0.state(2), m1.state(2)
@@ -477,3 +478,37 @@ def test_new_parts_start_as_no_change(orc):
         a, b = s0.step(ids[:, t]), s1.step(ids[:, t])
         assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), t
     assert (s1.get(0, "parts.1.stp_x") != 1.0).any()          # the synapse's state moved all the same
+
+
+def test_relay_gates_follow_their_formula(orc):
+    """--thalamus (src/v51b.rs:312-321): block i's gates are 2 sigmoid(tanh(acc / sqrt(i + 1)) G_i + c_i), acc the sum of the
+    reads rmsnorm(x_j) R_j of the blocks' input and of the outputs of the blocks before i.  Checked in f64 on the
+    oracle's own traces of the stream, and that the gates move the logits."""
+    from ava_b200 import config, synth
+    cfg = config.tiny(head_size=64, thalamus=1)
+    w = synth.model(cfg, 11, "awake")
+    m = orc.OracleModel(cfg, w)
+    s = m.state(1)
+    ids = synth.token_ids(cfg["vocab"], 1, 4)
+    orc.trace_enable(True)
+    try:
+        for t in range(4):
+            with_gates = s.step(ids[:, t]).copy()
+        d, L = cfg["d"], cfg["n_blocks"]
+        xs = [orc.trace("x_in", -1)[:d]] + [orc.trace("x_out", i)[:d] for i in range(L - 1)]
+        acc = np.zeros(16)
+        for i in range(L):
+            x = xs[i].astype(np.float64)
+            acc = acc + (x / np.sqrt((x * x).mean() + 1e-5)) @ w["th.read"][i].astype(np.float64)
+            z = np.tanh(acc / np.sqrt(i + 1.0)) @ w["th.gate"][i].astype(np.float64) + w["th.bias"][i]
+            want = 2.0 / (1.0 + np.exp(-z))
+            got = orc.trace("th_g", i)[:2]
+            assert np.allclose(got, want, rtol=0, atol=2e-5), (i, got, want)
+            assert (np.abs(got - 1.0) > 1e-3).all()
+    finally:
+        orc.trace_enable(False)
+    plain = dict(cfg, thalamus=0)
+    s0 = orc.OracleModel(plain, {k: v for k, v in w.items() if not k.startswith("th.")}).state(1)
+    for t in range(4):
+        without = s0.step(ids[:, t])
+    assert np.abs(with_gates - without).max() > 1e-3
