@@ -75,6 +75,10 @@ def flags_of(cfg: dict) -> str:
         f.append(f"--neuromod {cfg['neuromod']}")
     if cfg.get("thalamus"):
         f.append("--thalamus")
+    if cfg.get("dopamine"):
+        f.append("--dopamine")
+    if cfg.get("mood"):
+        f.append("--mood" if cfg["mood"] == 4 else f"--mood-units {cfg['mood']}")
     return " ".join(f)
 
 

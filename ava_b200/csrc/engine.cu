@@ -71,6 +71,7 @@ struct BlockDev {
     Dev mem_norm, beta, theta, rho, again, hebb_norm, gate_w, ba, bb, wa2, wb2, off, vres, eng_norm, mlp_norm, dense;
     Dev stp_U, stp_F, stp_D, stp_mix;  // --stp: sigmoids of the synapse's parameters, and its mix
     Dev dend_a, dend_b;                // --dendrite: A [d][32], B [32][hidden]
+    Dev da_w, da_c, mood_g;            // --dopamine: gate [d] twice; --mood: gain [k][d] (blocks after the first)
     QMat win, wout, proj, wo, eqkv, ewo, w1, w2;
 };
 
@@ -105,6 +106,7 @@ struct ava_engine {
 
     Dev tok_emb, final_norm;
     Dev nm_norm, nm_wn, nm_bn;  // --neuromod: the nucleus (gain [d], read-out padded to [d][4], bias [k])
+    Dev mood_lam, mood_win, mood_bin;  // --mood: decay, input weight and bias [k]
     Dev th_read, th_gate, th_bias;  // --thalamus: reads [blocks][d][16], gates [blocks][16][2], biases [blocks][2]
     QMat head;
     std::vector<std::unique_ptr<BlockDev>> blocks;
@@ -117,6 +119,9 @@ struct ava_engine {
     Dev gz, lra, lrb;  // the gates' stages: [rows][gate_cols], [rows][d] twice
     Dev uniform;       // [rows] f64: the sampler's draws of one step
     Dev sig;           // --neuromod: [rows][4] NE, ACh, DA (and one unused) of the step's token-rows
+    // --dopamine / --mood: block 0's normed output [rows][d], the rows the head reads (the position before each), the
+    // head's logits for them [rows][vocab], surprise s and z [rows], moods [rows][k], the current's gain and the MLP's output [rows][d]
+    Dev sur_xf, sur_in, sur_logits, sur_s, sur_z, mood_all, mood_gain, y2;
     Dev th_acc, th_g, x_in;  // --thalamus: the relay's sum [rows][16], the block's gates [rows][4], the block's input [rows][d]
     Dev ctx, dz1, ones;  // --dendrite: the block's memory read [rows][d], its projection [rows][32], a vector of ones [d]
     uint32_t* status_host = nullptr;  // pinned
@@ -163,6 +168,8 @@ struct ava_state {
     Dev mem_f;                // [L][rows][nh][hs / cw][hs][cw]: slice-major, a block of threads owns one contiguous slice
     Dev mem_s;                // the momentum matrix, same layout (only with --mem-momentum)
     Dev stp_u, stp_x;         // [L][rows][d]: the synapse's (u, x) (only with --stp; a fresh state has u = 0, x = 1)
+    Dev sur_prev, sur_valid, sur_last, mood;  // --dopamine / --mood: block 0's last normed output [rows][d], whether there is one
+                                              // [rows], the last surprise [rows], the mood [rows][k] (all zero in a fresh state)
     Dev eng_k, eng_v;         // [rows][enh][ring][ehs]
     Dev eng_n, eng_start;     // [rows] i32
     std::vector<int32_t> n_host, start_host;
@@ -200,6 +207,7 @@ int64_t f32_len(const ava_config& c, const std::string& name) {
     if (name == "nm.norm" && c.neuromod > 0) return d;
     if (name == "nm.wn" && c.neuromod > 0) return d * c.neuromod;
     if (name == "nm.bn" && c.neuromod > 0) return c.neuromod;
+    if (c.mood > 0 && (name == "v51.mood.lam" || name == "v51.mood.win" || name == "v51.mood.bin")) return c.mood;
     if (name == "th.read" && c.thalamus) return (int64_t)c.n_blocks * d * 16;  // TH_K (src/v51b.rs:45)
     if (name == "th.gate" && c.thalamus) return (int64_t)c.n_blocks * 16 * 2;
     if (name == "th.bias" && c.thalamus) return (int64_t)c.n_blocks * 2;
@@ -210,6 +218,8 @@ int64_t f32_len(const ava_config& c, const std::string& name) {
                                   "parts.stp.u_param", "parts.stp.f_param", "parts.stp.d_param", "parts.stp.mix"};
     for (const char* n : vec_d)
         if (rest == n) return d;
+    if ((rest == "v51.da_w" || rest == "v51.da_c") && c.dopamine && b > 0) return d;
+    if (rest == "v51.mood_g" && c.mood > 0 && b > 0) return (int64_t)c.mood * d;
     if (rest == "v51.dend_a") return d * 32;  // DEND_RANK (src/v51.rs:52)
     if (rest == "v51.dend_b") return (int64_t)32 * c.hidden;
     if (rest == "hebb.wa" || rest == "hebb.wb") return d * nh;
@@ -294,6 +304,7 @@ const char* find_blocker(const ava_config& c, int* cw, int* rb) {
     if (c.eng_block >= 0 && (c.eng_head_size <= 0 || c.d % c.eng_head_size)) return "bad engram head size";
     if (c.spikes < 0 || c.spikes > 2) return "unknown spike kind";
     if (c.neuromod != 0 && (c.neuromod < 2 || c.neuromod > 4)) return "neuromod: 2 to 4 signals";
+    if (c.mood < 0 || c.mood > 16) return "mood: up to 16 units";
     if (c.thalamus && !c.fast_mem) return "thalamus: a part of the blocks with the fast-weight memory";
     if (c.fast_mem && (c.head_size % 16 || !mem_heads_tiling(c.head_size, cw, rb, c.mem_momentum > 0.0f))) return "memory head size not covered (a multiple of 16 whose column slice fits shared memory)";
     return nullptr;
@@ -325,6 +336,18 @@ int ensure_workspace(ava_engine* e, int rows, int logit_rows = 0) {
     CK(e->next.alloc(M * sizeof(uint32_t)));
     CK(e->uniform.alloc(M * sizeof(double)));
     if (c.neuromod > 0) CK(e->sig.alloc(M * 4 * f));
+    if (c.dopamine || c.mood > 0) {
+        CK(e->sur_xf.alloc(M * d * f));
+        CK(e->sur_in.alloc(M * d * f));
+        CK(e->sur_logits.alloc(M * c.vocab * f));
+        CK(e->sur_s.alloc(M * f));
+        CK(e->sur_z.alloc(M * f));
+        if (c.mood > 0) {
+            CK(e->mood_all.alloc(M * c.mood * f));
+            CK(e->mood_gain.alloc(M * d * f));
+        }
+        if (c.dopamine) CK(e->y2.alloc(M * d * f));
+    }
     if (c.thalamus) {
         CK(e->th_acc.alloc(M * 16 * f));
         CK(e->th_g.alloc(M * 4 * f));
@@ -501,13 +524,21 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         const float* nm = (c.neuromod > 0 && i > 0) ? e->sig.as<float>() : nullptr;  // the nucleus's signals reach the later blocks
         lp.ne = nm;
         const float* spikes = lp.s;
-        if (T == 1) {
+        const float* cur_gain = nullptr;
+        if (c.mood > 0 && i > 0) {
+            // M: the current times 1 + tanh(mood G) per token-row and channel, after NE
+            prof_begin(e, "mood");
+            launch_mood_gain(st, e->mood_all.as<float>(), c.mood, b.mood_g.as<float>(), M, d, e->mood_gain.as<float>());
+            prof_end(e);
+            cur_gain = e->mood_gain.as<float>();
+        }
+        if (T == 1 && !cur_gain) {
             gemm(e, "gemm.win_lif", h, d, b.win, nullptr, 0, M, EPI_LIF, &lp);
         } else {
             // currents of the whole chunk, then the scan in time (buffers free at this point of the block are borrowed)
             gemm(e, "gemm.win", h, d, b.win, e->yraw.as<float>(), d, M, EPI_STORE);
             prof_begin(e, "lif_scan");
-            launch_lif_scan(st, e->yraw.as<float>(), lp, rows, d, T, e->eo.as<float>());
+            launch_lif_scan(st, e->yraw.as<float>(), lp, rows, d, T, e->eo.as<float>(), cur_gain);
             prof_end(e);
             spikes = e->eo.as<float>();
         }
@@ -672,7 +703,16 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
             e->launches += 2;
             dbg(e, "a_dend", i, e->act.as<float>(), M, H);
         }
-        gemm(e, "gemm.w2", e->act.as<float>(), H, b.w2, x, d, M, EPI_ADD, nullptr, true, (c.neuromod > 0 && i > 0) ? e->sig.as<float>() + 2 : nullptr);
+        const float* nm_da = (c.neuromod > 0 && i > 0) ? e->sig.as<float>() + 2 : nullptr;
+        if (c.dopamine && i > 0) {
+            // DA: the MLP's output times 1 + tanh(z w + c), z the token's surprise / ln V, before the nucleus's DA signal
+            gemm(e, "gemm.w2", e->act.as<float>(), H, b.w2, e->y2.as<float>(), d, M, EPI_STORE, nullptr, true);
+            prof_begin(e, "dopamine");
+            launch_da_add(st, x, e->y2.as<float>(), e->sur_z.as<float>(), b.da_w.as<float>(), b.da_c.as<float>(), nm_da, M, d);
+            prof_end(e);
+        } else {
+            gemm(e, "gemm.w2", e->act.as<float>(), H, b.w2, x, d, M, EPI_ADD, nullptr, true, nm_da);
+        }
         if (c.thalamus) {
             prof_begin(e, "relay");
             launch_relay_res(st, x, e->x_in.as<float>(), e->th_g.as<float>(), M, d);
@@ -685,6 +725,29 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         }
         dbg(e, "x_out", i, x, M, d);
         if (c.thalamus && i + 1 < L) relay_read(i + 1);
+        if (i == 0 && (c.dopamine || c.mood > 0)) {
+            // DA / M: the surprise at each token, from the head's logits for block 0's normed output at the position before
+            // it (the carried one for a chunk's first token), then the mood's scan; the carried values move on
+            prof_begin(e, "surprise");
+            launch_rmsnorm(st, x, e->final_norm.as<float>(), M, d, e->sur_xf.as<float>());
+            CK(cudaMemcpyAsync(e->sur_in.p, s->sur_prev.p, Rd * sizeof(float), cudaMemcpyDeviceToDevice, st));
+            if (T > 1)
+                CK(cudaMemcpyAsync(e->sur_in.as<float>() + Rd, e->sur_xf.p, (size_t)(T - 1) * Rd * sizeof(float), cudaMemcpyDeviceToDevice, st));
+            prof_end(e);
+            gemm(e, "gemm.sur_head", e->sur_in.as<float>(), d, e->head, e->sur_logits.as<float>(), c.vocab, M, EPI_STORE);
+            prof_begin(e, "surprise");
+            if (!launch_surprise(st, e->sur_logits.as<float>(), c.vocab, tok, s->sur_valid.as<float>(), rows, T, e->sur_s.as<float>(), e->sur_z.as<float>()))
+                return e->fail(AVA_ERR_CAPACITY, "the surprise kernel holds a vocabulary of up to 56320 in shared memory");
+            if (c.mood > 0)
+                launch_mood(st, e->sur_z.as<float>(), rows, T, c.mood, e->mood_lam.as<float>(), e->mood_win.as<float>(), e->mood_bin.as<float>(),
+                            s->mood.as<float>(), e->mood_all.as<float>());
+            CK(cudaMemcpyAsync(s->sur_prev.p, e->sur_xf.as<float>() + (size_t)(T - 1) * Rd, Rd * sizeof(float), cudaMemcpyDeviceToDevice, st));
+            CK(cudaMemcpyAsync(s->sur_last.p, e->sur_s.as<float>() + (size_t)(T - 1) * rows, rows * sizeof(float), cudaMemcpyDeviceToDevice, st));
+            launch_fill(st, s->sur_valid.as<float>(), rows, 1.0f);
+            prof_end(e);
+            e->launches += 3;
+            dbg(e, "sur_z", 0, e->sur_z.as<float>(), M, 1);
+        }
         if (i == 0 && c.neuromod > 0) {
             // the nucleus reads block 0's output: 2 sigmoid(rmsnorm(x, g) W + b) per token-row (h and the gates' scratch are free)
             prof_begin(e, "nucleus");
@@ -770,6 +833,15 @@ bool locate(const ava_state* s, int row, const std::string& name, StateSlice* ou
         out->count = (size_t)s->n_host[row] * d;
         return true;
     }
+    if (name.rfind("v51.", 0) == 0 && (c.dopamine || c.mood > 0)) {
+        const std::string what = name.substr(4);
+        const size_t k = what == "prev" ? d : what == "mood" ? (size_t)c.mood : 1;
+        out->buf = what == "prev" ? &ms->sur_prev : what == "pvalid" ? &ms->sur_valid : what == "last_s" ? &ms->sur_last
+                   : what == "mood" && c.mood > 0 ? &ms->mood : nullptr;
+        out->off = (size_t)row * k;
+        out->count = k;
+        return out->buf != nullptr;
+    }
     const size_t d1 = name.find('.'), d2 = name.rfind('.');
     if (d1 == std::string::npos || d2 == d1) return false;
     const std::string kind = name.substr(0, d1), what = name.substr(d2 + 1);
@@ -813,6 +885,12 @@ int alloc_state(ava_engine* e, int rows, int ring, int keep, ava_state** out) {
         CK(s->stp_u.alloc(L * M * d * f));
         CK(s->stp_x.alloc(L * M * d * f));
     }
+    if (c.dopamine || c.mood > 0) {
+        CK(s->sur_prev.alloc(M * d * f));
+        CK(s->sur_valid.alloc(M * f));
+        CK(s->sur_last.alloc(M * f));
+        if (c.mood > 0) CK(s->mood.alloc(M * c.mood * f));
+    }
     if (c.fast_mem) CK(s->mem_f.alloc(L * M * d * c.head_size * f));
     if (c.fast_mem && c.mem_momentum > 0.0f) CK(s->mem_s.alloc(L * M * d * c.head_size * f));
     if (c.eng_block >= 0) {
@@ -829,7 +907,8 @@ int alloc_state(ava_engine* e, int rows, int ring, int keep, ava_state** out) {
 }
 
 int zero_state(ava_engine* e, ava_state* s) {
-    for (Dev* b : {&s->lif_v, &s->lif_s, &s->lif_a, &s->mem_f, &s->mem_s, &s->stp_u, &s->eng_n, &s->eng_start})
+    for (Dev* b : {&s->lif_v, &s->lif_s, &s->lif_a, &s->mem_f, &s->mem_s, &s->stp_u, &s->sur_prev, &s->sur_valid, &s->sur_last, &s->mood, &s->eng_n,
+                   &s->eng_start})
         if (b->p) CK(cudaMemsetAsync(b->p, 0, b->bytes, e->stream));
     if (s->stp_x.p) launch_fill(e->stream, s->stp_x.as<float>(), (int64_t)(s->stp_x.bytes / sizeof(float)), 1.0f);  // x starts at 1
     CK(cudaStreamSynchronize(e->stream));
@@ -854,6 +933,14 @@ int copy_row(ava_engine* e, const ava_state* src, int src_row, ava_state* dst, i
             CK(cudaMemcpyAsync(dst->mem_f.as<float>() + dn * per, src->mem_f.as<float>() + so * per, per * f, cudaMemcpyDeviceToDevice, e->stream));
         if (c.fast_mem && c.mem_momentum > 0.0f)
             CK(cudaMemcpyAsync(dst->mem_s.as<float>() + dn * per, src->mem_s.as<float>() + so * per, per * f, cudaMemcpyDeviceToDevice, e->stream));
+    }
+    if (c.dopamine || c.mood > 0) {
+        CK(cudaMemcpyAsync(dst->sur_prev.as<float>() + dst_row * d, src->sur_prev.as<float>() + src_row * d, d * f, cudaMemcpyDeviceToDevice, e->stream));
+        CK(cudaMemcpyAsync(dst->sur_valid.as<float>() + dst_row, src->sur_valid.as<float>() + src_row, f, cudaMemcpyDeviceToDevice, e->stream));
+        CK(cudaMemcpyAsync(dst->sur_last.as<float>() + dst_row, src->sur_last.as<float>() + src_row, f, cudaMemcpyDeviceToDevice, e->stream));
+        if (c.mood > 0)
+            CK(cudaMemcpyAsync(dst->mood.as<float>() + (size_t)dst_row * c.mood, src->mood.as<float>() + (size_t)src_row * c.mood, c.mood * f,
+                               cudaMemcpyDeviceToDevice, e->stream));
     }
     if (c.eng_block >= 0) {
         const size_t rowb = d * src->ring * src->kv_elem();
@@ -1009,6 +1096,11 @@ int ava_engine_finalize(ava_engine* e) {
             if ((rc = upload_f32(e, b.dend_a, p + "v51.dend_a", true))) return rc;
             if ((rc = upload_f32(e, b.dend_b, p + "v51.dend_b", true))) return rc;
         }
+        if (c.dopamine && i > 0) {
+            if ((rc = upload_f32(e, b.da_w, p + "v51.da_w", true))) return rc;
+            if ((rc = upload_f32(e, b.da_c, p + "v51.da_c", true))) return rc;
+        }
+        if (c.mood > 0 && i > 0 && (rc = upload_f32(e, b.mood_g, p + "v51.mood_g", true))) return rc;
         if (c.stp) {
             // U, F, D are sigmoids of their parameters (src/model/fstep/arch_f3.rs:82)
             struct P { Dev* d; const char* n; bool sig; };
@@ -1070,6 +1162,11 @@ int ava_engine_finalize(ava_engine* e) {
         for (int j = 0; j < c.d; ++j)
             for (int k = 0; k < c.neuromod; ++k) w4[(size_t)j * 4 + k] = it->second[(size_t)j * c.neuromod + k];
         if ((rc = upload(e, e->nm_wn, w4.data(), w4.size() * sizeof(float)))) return rc;
+    }
+    if (c.mood > 0) {
+        if ((rc = upload_f32(e, e->mood_lam, "v51.mood.lam", true))) return rc;
+        if ((rc = upload_f32(e, e->mood_win, "v51.mood.win", true))) return rc;
+        if ((rc = upload_f32(e, e->mood_bin, "v51.mood.bin", true))) return rc;
     }
     if (c.thalamus) {
         if ((rc = upload_f32(e, e->th_read, "th.read", true))) return rc;
@@ -1483,7 +1580,7 @@ int64_t ava_engine_bytes(const ava_engine* e) {
 int64_t ava_state_bytes(const ava_state* s) {
     if (!s) return 0;
     int64_t n = 0;
-    for (const Dev* d : {&s->lif_v, &s->lif_s, &s->lif_a, &s->mem_f, &s->mem_s, &s->stp_u, &s->stp_x, &s->eng_k, &s->eng_v, &s->eng_n, &s->eng_start})
+    for (const Dev* d : {&s->lif_v, &s->lif_s, &s->lif_a, &s->mem_f, &s->mem_s, &s->stp_u, &s->stp_x, &s->sur_prev, &s->sur_valid, &s->sur_last, &s->mood, &s->eng_k, &s->eng_v, &s->eng_n, &s->eng_start})
         n += d->bytes;
     return n;
 }

@@ -28,10 +28,13 @@ __device__ __forceinline__ void widen4(int w, float* f) {
 // One LIF update of one channel (src/model/fstep/arch.rs:173-228) with the hard spike count taken directly (as the
 // reference's own GPU kernel does; the CPU's soft + (hard - soft) equals it).  v, s, a: the carried state, in and out.
 // ne: --neuromod's NE signal of the row (1 without it: a product with 1 is exact), applied after --lif-scale.
+// MG: --mood's gain of this (token-row, channel) after NE (src/model/fstep/arch.rs:646-650); only the scan kernel has it.
+template <bool MG = false>
 __device__ __forceinline__ void lif_math(int spikes, int lif_scale, bool adaptive, float beta, float th, float rho, float gain, float ne, float cur,
-                                         float& v, float& s, float& a) {
+                                         float& v, float& s, float& a, float mg = 1.0f) {
     if (lif_scale) cur = mul(cur, add(mul(beta, -1.0f), 1.0f));
     cur = mul(cur, ne);
+    if (MG) cur = mul(cur, mg);
     float th_prev = th, th_t = th;
     if (adaptive) {
         th_prev = add(th, mul(a, gain));
@@ -54,9 +57,10 @@ __device__ __forceinline__ void lif_math(int spikes, int lif_scale, bool adaptiv
     }
 }
 
-__device__ __forceinline__ void lif_core(const LifParams& p, int c, float ne, float cur, float& v, float& s, float& a) {
-    lif_math(p.spikes, p.lif_scale, p.rho != nullptr, p.beta[c], p.theta ? p.theta[c] : 1.0f, p.rho ? p.rho[c] : 0.0f, p.rho ? p.gain[c] : 0.0f, ne, cur,
-             v, s, a);
+template <bool MG = false>
+__device__ __forceinline__ void lif_core(const LifParams& p, int c, float ne, float cur, float& v, float& s, float& a, float mg = 1.0f) {
+    lif_math<MG>(p.spikes, p.lif_scale, p.rho != nullptr, p.beta[c], p.theta ? p.theta[c] : 1.0f, p.rho ? p.rho[c] : 0.0f, p.rho ? p.gain[c] : 0.0f, ne,
+                 cur, v, s, a, mg);
 }
 
 __device__ __forceinline__ void lif_update(const LifParams& p, int r, int c, int d, float cur) {
@@ -70,8 +74,9 @@ __device__ __forceinline__ void lif_update(const LifParams& p, int r, int c, int
 
 // The LIF over a chunk of T tokens: one thread per (row, channel) walks the tokens in order with the membrane, last
 // spike and trace in registers (the reset makes the recurrence nonlinear, so time stays sequential; the parallelism is
-// rows x channels).  cur and spikes are time-major [T][M][d].
-__global__ void lif_scan_kernel(const float* __restrict__ cur, const LifParams p, int M, int d, int T, float* __restrict__ spikes) {
+// rows x channels).  cur and spikes are time-major [T][M][d]; so is cur_gain (--mood's gain of the current, or nullptr).
+__global__ void lif_scan_kernel(const float* __restrict__ cur, const LifParams p, int M, int d, int T, float* __restrict__ spikes,
+                                const float* __restrict__ cur_gain) {
     pdl_enter();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t Md = (size_t)M * d;
@@ -83,7 +88,11 @@ __global__ void lif_scan_kernel(const float* __restrict__ cur, const LifParams p
         const float x = nxt;
         if (t + 1 < T) nxt = cur[(size_t)(t + 1) * Md + i];
         // the NE signal belongs to the token-row: row (t, i / d) of the chunk
-        lif_core(p, c, p.ne ? p.ne[((size_t)t * M + i / d) * NM_STRIDE] : 1.0f, x, v, s, a);
+        const float ne = p.ne ? p.ne[((size_t)t * M + i / d) * NM_STRIDE] : 1.0f;
+        if (cur_gain)
+            lif_core<true>(p, c, ne, x, v, s, a, cur_gain[(size_t)t * Md + i]);
+        else
+            lif_core(p, c, ne, x, v, s, a);
         spikes[(size_t)t * Md + i] = s;
     }
     p.v[i] = v;
@@ -647,9 +656,9 @@ bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {
     return true;
 }
 
-void launch_lif_scan(cudaStream_t st, const float* cur, const LifParams& p, int M, int d, int T, float* spikes) {
+void launch_lif_scan(cudaStream_t st, const float* cur, const LifParams& p, int M, int d, int T, float* spikes, const float* cur_gain) {
     const size_t n = (size_t)M * d;
-    launch_k(lif_scan_kernel, dim3((unsigned)((n + 127) / 128)), dim3(128), 0, st, cur, p, M, d, T, spikes);
+    launch_k(lif_scan_kernel, dim3((unsigned)((n + 127) / 128)), dim3(128), 0, st, cur, p, M, d, T, spikes, cur_gain);
 }
 
 void launch_stp(cudaStream_t st, const float* spikes, const float* U, const float* F, const float* D, const float* mix, float* u, float* x, int M, int d,

@@ -117,7 +117,20 @@ void launch_lif(cudaStream_t st, const float* cur, const LifParams& p, int M, in
 void launch_stp(cudaStream_t st, const float* spikes, const float* U, const float* F, const float* D, const float* mix, float* u, float* x, int M, int d,
                 int T, float* out);
 void launch_fill(cudaStream_t st, float* p, int64_t n, float v);
-void launch_lif_scan(cudaStream_t st, const float* cur, const LifParams& p, int M, int d, int T, float* spikes);
+void launch_lif_scan(cudaStream_t st, const float* cur, const LifParams& p, int M, int d, int T, float* spikes, const float* cur_gain = nullptr);
+
+// --dopamine / --mood (src/model/fstep/arch_f3.rs:106-186, arch_f4.rs:131-143), token-rows time-major [T][rows]:
+// the surprise of every token-row from the head's logits of the position before it: s = (lse - logit[token]) * valid
+// (valid: the carried flag for a chunk's first token, 1 after it), z = s * (1 / ln V) + 0.  false: vocabulary too large
+// for the kernel's shared memory.
+bool launch_surprise(cudaStream_t st, const float* logits, int V, const uint32_t* tok, const float* valid, int rows, int T, float* s, float* z);
+// the mood's scan over a chunk's tokens from the carried mood [rows][k] (updated in place); all [T][rows][k] moods out
+void launch_mood(cudaStream_t st, const float* z, int rows, int T, int k, const float* lam, const float* win, const float* bin, float* mood_state,
+                 float* mood_all);
+// gain [M][d] = 1 + tanh(mood [M][k] . G [k][d]) (the product in the one-row order), the LIF current's factor
+void launch_mood_gain(cudaStream_t st, const float* mood_all, int k, const float* G, int M, int d, float* gain);
+// x += (y * (1 + tanh(z[row] w + c))) [* row_gain[row * NM_STRIDE]]: the MLP's output under --dopamine (then --neuromod's DA)
+void launch_da_add(cudaStream_t st, float* x, const float* y, const float* z, const float* w, const float* c, const float* row_gain, int M, int d);
 
 struct MemPrepArgs {
     const float* h;      // [M, d] normed input

@@ -352,6 +352,12 @@ int ava_arch_flags(const char* flags, ava_config* cfg) {
         else if (k == "--stp") cfg->stp = 1;
         else if (k == "--dendrite") cfg->dendrite = 1;
         else if (k == "--thalamus") cfg->thalamus = 1;
+        else if (k == "--dopamine") cfg->dopamine = 1;
+        else if (k == "--mood") cfg->mood = 4;  // MOOD_UNITS (src/v51.rs:53)
+        else if (k == "--mood-units") {
+            if (!value(&v) || std::atoi(v.c_str()) < 1 || std::atoi(v.c_str()) > 16) return fail(AVA_ERR_ARG, "--mood-units needs an integer from 1 to 16");
+            cfg->mood = std::atoi(v.c_str());
+        }
         else if (k == "--neuromod") {
             if (!value(&v)) return fail(AVA_ERR_ARG, "--neuromod needs a value");
             const int n = std::atoi(v.c_str());
@@ -437,7 +443,7 @@ int ava_config_from_ckpt(const ava_ckpt* c, const char* kind, const char* arch_f
         int b;
         std::string rest;
         if (!block_name(e.name, &b, &rest)) {
-            if (e.name != "tok_emb" && e.name != "final.norm" && e.name != "nm.norm" && e.name != "nm.wn" && e.name != "nm.bn" && e.name != "th.read" && e.name != "th.gate" && e.name != "th.bias")
+            if (e.name != "tok_emb" && e.name != "final.norm" && e.name != "nm.norm" && e.name != "nm.wn" && e.name != "nm.bn" && e.name != "th.read" && e.name != "th.gate" && e.name != "th.bias" && e.name.rfind("v51.mood.", 0) != 0)
                 return fail(AVA_NOT_APPLICABLE, e.name + ": a tensor of a part the engine does not cover (glance, magnitude code, order head)");
             continue;
         }

@@ -117,6 +117,11 @@ def model(cfg: dict, seed: int = 0, recipe: str = "bench", unit_gain: bool = Tru
         w["nm.norm"] = (1.0 + g.n("nm.norm", (d,), 0.05)).astype(np.float32) if awake else np.ones(d, np.float32)
         w["nm.wn"] = g.n("nm.wn", (d, k), 0.05) if awake else np.zeros((d, k), np.float32)
         w["nm.bn"] = g.n("nm.bn", (k,), 0.3) if awake else np.zeros(k, np.float32)
+    if cfg.get("mood"):
+        k = cfg["mood"]
+        w["v51.mood.lam"] = g.n("v51.mood.lam", (k,), 1.0) + 2.0
+        w["v51.mood.win"] = (1.0 + g.n("v51.mood.win", (k,), 0.3)).astype(np.float32)
+        w["v51.mood.bin"] = g.n("v51.mood.bin", (k,), 0.1) if awake else np.zeros(k, np.float32)
     if cfg.get("thalamus"):
         # the reference starts the reads as seeded noise / sqrt(d) and the gates at zero (every gate exactly 1)
         w["th.read"] = g.n("th.read", (L, d, 16), 1.0 / math.sqrt(d))
@@ -187,6 +192,11 @@ def model(cfg: dict, seed: int = 0, recipe: str = "bench", unit_gain: bool = Tru
         if cfg.get("dendrite") and cfg["fast_mem"]:
             w[p + "v51.dend_a"] = g.n(p + "v51.dend_a", (d, 32), 1.0 / math.sqrt(d))
             w[p + "v51.dend_b"] = g.n(p + "v51.dend_b", (32, H), 0.3) if awake else np.zeros((32, H), np.float32)
+        if cfg.get("dopamine") and i > 0:
+            w[p + "v51.da_w"] = g.n(p + "v51.da_w", (d,), 0.5) if awake else np.zeros(d, np.float32)
+            w[p + "v51.da_c"] = g.n(p + "v51.da_c", (d,), 0.1) if awake else np.zeros(d, np.float32)
+        if cfg.get("mood") and i > 0:
+            w[p + "v51.mood_g"] = g.n(p + "v51.mood_g", (cfg["mood"], d), 0.3) if awake else np.zeros((cfg["mood"], d), np.float32)
         w[p + "mlp.norm"] = ones("mlp.norm")
         w[p + "mlp.w1"] = g.q8(p + "mlp.w1", d, H, gain(d))
         w[p + "mlp.w2"] = g.q8(p + "mlp.w2", H, d, gain(cfg["kwta_k"], 0.25))

@@ -39,6 +39,8 @@ pub struct AvaConfig {
     pub neuromod: i32,
     pub stp: i32,
     pub thalamus: i32,
+    pub dopamine: i32,
+    pub mood: i32,
     pub mem_momentum: f32,
     pub slope: f32,
 }

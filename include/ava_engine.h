@@ -66,6 +66,15 @@ typedef struct ava_config {
                                output; block i's two gates 2 sigmoid(tanh(sum / sqrt(reads)) G_i + c_i) scale its memory read
                                and its whole change of the stream (src/model/fstep/arch_f2.rs:62-153, src/v51b.rs:312-325);
                                weights th.read [blocks, d, 16], th.gate [blocks, 16, 2], th.bias [blocks, 2]; needs fast_mem */
+    int32_t dopamine;       /* --dopamine: after block 0 the surprise at this token, s = CE(head(prev), token) with prev block 0's
+                               normed output at the token before (0 at the start of a stream), z = s / ln(vocab); every later
+                               block's MLP output times 1 + tanh(z w + c) per channel, before --neuromod's DA
+                               (src/model/fstep/arch_f3.rs:106-150, arch_f4.rs:131-143); weights b{i}.v51.da_w / da_c [d], i > 0;
+                               carried per row: v51.prev [d], v51.pvalid [1], v51.last_s [1] */
+    int32_t mood;           /* --mood (4 units; --mood-units k): m = (z win + bin) sigmoid(-lam) + m exp(log_sigmoid(lam)) after
+                               block 0; every later block's LIF current times 1 + tanh(m G) per channel, after --neuromod's NE
+                               (src/model/fstep/arch_f3.rs:150-186); weights v51.mood.lam / win / bin [k], b{i}.v51.mood_g [k, d],
+                               i > 0; carried per row: v51.mood [k] (and the surprise's three tensors) */
     float   mem_momentum;   /* --mem-momentum (0: off) */
     float   slope;          /* --surrogate-slope (does not change forward values) */
 } ava_config;

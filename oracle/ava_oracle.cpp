@@ -477,6 +477,7 @@ struct Block {
     QW win, wout;
     // short-term plasticity of the spikes' synapse (--stp): parameters and their sigmoids
     std::vector<float> stp_u, stp_f, stp_d, stp_mix, stp_U, stp_F, stp_D;
+    std::vector<float> da_w, da_c, mood_g;  // --dopamine: gate [d] twice; --mood: gain [k, d] (blocks after the first)
     // the dendrites of the MLP's units (--dendrite): A [d, 32], B [32, hidden]
     std::vector<float> dend_a, dend_b;
     // the fast-weight memory
@@ -498,6 +499,7 @@ struct orc_model {
     orc_config cfg;
     std::vector<float> tok_emb, final_norm;
     std::vector<float> nm_norm, nm_wn, nm_bn;  // --neuromod: the nucleus (gain [d], read-out [d, k], bias [k])
+    std::vector<float> mood_lam, mood_win, mood_bin;  // --mood: decay, input weight and bias [k]
     std::vector<float> th_read, th_gate, th_bias;  // --thalamus: reads [L, d, 16], gates [L, 16, 2], biases [L, 2]
     QW head;
     std::vector<Block> blocks;
@@ -509,6 +511,8 @@ struct RowState {
     std::vector<std::vector<float>> v, s, a;    // per block [d]
     std::vector<std::vector<float>> f, ms;      // per block [nh, hs, hs]
     std::vector<std::vector<float>> su, sx;     // per block [d]: the synapse's (u, x) with --stp
+    std::vector<float> prev, mood;              // --dopamine / --mood: block 0's last normed output [d], the mood [k]
+    std::vector<float> pvalid, last_s;          // [1] each: whether there is a prev, the last surprise
     std::vector<float> ek, evv;                 // engram [enh, n, ehs]
     int eng_n = 0;
     int64_t seen = 0;
@@ -528,6 +532,9 @@ std::vector<float>* f32_slot(orc_model* m, const std::string& name, int64_t* wan
     if (name == "nm.norm") { *want = d; return &m->nm_norm; }
     if (name == "nm.wn") { *want = (int64_t)d * c.neuromod; return &m->nm_wn; }
     if (name == "nm.bn") { *want = c.neuromod; return &m->nm_bn; }
+    if (name == "v51.mood.lam") { *want = c.mood; return &m->mood_lam; }
+    if (name == "v51.mood.win") { *want = c.mood; return &m->mood_win; }
+    if (name == "v51.mood.bin") { *want = c.mood; return &m->mood_bin; }
     if (name == "th.read") { *want = (int64_t)c.n_blocks * d * 16; return &m->th_read; }
     if (name == "th.gate") { *want = (int64_t)c.n_blocks * 16 * 2; return &m->th_gate; }
     if (name == "th.bias") { *want = (int64_t)c.n_blocks * 2; return &m->th_bias; }
@@ -549,6 +556,7 @@ std::vector<float>* f32_slot(orc_model* m, const std::string& name, int64_t* wan
         {"hebb.ba", &b.ba, nh}, {"hebb.bb", &b.bb, nh}, {"hebb.wa1", &b.wa1, (int64_t)d * r}, {"hebb.wa2", &b.wa2, (int64_t)r * d},
         {"hebb.wb1", &b.wb1, (int64_t)d * r}, {"hebb.wb2", &b.wb2, (int64_t)r * d}, {"hebb.off", &b.off, d}, {"hebb.vres", &b.vres, 2},
         {"eng.norm", &b.eng_norm, d}, {"mlp.norm", &b.mlp_norm, d}, {"dense", &b.dense, i + 2},
+        {"v51.da_w", &b.da_w, d}, {"v51.da_c", &b.da_c, d}, {"v51.mood_g", &b.mood_g, (int64_t)c.mood * d},
     };
     for (const E& e : table)
         if (rest == e.n) { *want = e.len; return e.p; }
@@ -657,6 +665,11 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
     // --neuromod (fstep/arch.rs:616,1029,1108-1119; src/v50.rs:20-29): three signals per row after block 0, for the later blocks
     const int NM_NE = 0, NM_ACH = 1, NM_DA = 2, nk = cfg.neuromod;
     std::vector<float> sig;  // [R][nk], empty in block 0
+    // --dopamine / --mood (fstep/arch_f3.rs:106-186): after block 0 the surprise at this token, CE(head(prev), tok) * valid
+    // with prev block 0's normed output of the token before; z = s / ln V; the mood's one-step scan
+    const bool surprise = cfg.dopamine || cfg.mood > 0;
+    bool have_surprise = false;
+    std::vector<float> sur_prev, sur_s, sur_z, mood_now;
     // --thalamus (fstep/arch_f2.rs:62-153; src/v51b.rs:312-325): the relay's running sum of reads rmsnorm(x) R_j [R][16],
     // each block's two gates 2 sigmoid(tanh(acc / sqrt(reads)) G_i + c_i): [0] the residual's, [1] the memory read's
     const int TK = 16;
@@ -701,6 +714,11 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
                 for (int c = 0; c < d; ++c) c_[c] = c_[c] * (b.beta[c] * -1.0f + 1.0f);
             if (!sig.empty())  // NE: the input current times its signal, after --lif-scale
                 for (int c = 0; c < d; ++c) c_[c] = c_[c] * sig[(size_t)r * nk + NM_NE];
+            if (have_surprise && cfg.mood > 0 && i > 0) {  // M: the current times tanh(mood G)·1 + 1, after NE (fstep/arch_f3.rs:176-186)
+                std::vector<float> z(d);
+                gemv(&mood_now[(size_t)r * cfg.mood], cfg.mood, b.mood_g.data(), d, z.data());
+                for (int c = 0; c < d; ++c) c_[c] = c_[c] * (tanh_f(z[c]) * 1.0f + 1.0f);
+            }
             RowState& st = *rows[r];
             nw[r].v[i].resize(d);
             nw[r].a[i].resize(cfg.alif ? d : 0);
@@ -947,6 +965,10 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
             T("a_dend", i, a.data(), H);
         }
         q8_matmul(b.w2, a.data(), R, tmp.data());
+        if (have_surprise && cfg.dopamine && i > 0)  // DA: the output times tanh(z w + c)·1 + 1, z the surprise / ln V (fstep/arch_f4.rs:131-143)
+            for (int r = 0; r < R; ++r)
+                for (int c = 0; c < d; ++c)
+                    tmp[(size_t)r * d + c] = tmp[(size_t)r * d + c] * (tanh_f(sur_z[r] * b.da_w[c] + b.da_c[c]) * 1.0f + 1.0f);
         if (!sig.empty())  // DA: the MLP's output times its signal
             for (int r = 0; r < R; ++r)
                 for (int c = 0; c < d; ++c) tmp[(size_t)r * d + c] = tmp[(size_t)r * d + c] * sig[(size_t)r * nk + NM_DA];
@@ -970,6 +992,31 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
         }
         T("x_out", i, x.data(), d);
         if (cfg.thalamus && i + 1 < L) relay_read(i + 1);  // the relay reads this block's output for the later gates
+        if (i == 0 && surprise) {
+            sur_prev.resize((size_t)R * d); sur_s.assign(R, 0.f); sur_z.assign(R, 0.f); mood_now.assign((size_t)R * cfg.mood, 0.f);
+            std::vector<float> row(cfg.vocab);
+            for (int r = 0; r < R; ++r) {
+                rmsnorm(&x[(size_t)r * d], m->final_norm.data(), d, &sur_prev[(size_t)r * d]);
+                const RowState& st = *rows[r];
+                q8_matmul(m->head, st.prev.data(), 1, row.data());
+                float mx = -std::numeric_limits<float>::infinity();
+                for (float v : row) mx = std::max(mx, v);
+                float se = 0.f;
+                for (float v : row) se += g_exp(v - mx);
+                const float lse = mx + g_log(se);
+                sur_s[r] = (lse - row[tok[r]]) * st.pvalid[0];
+                sur_z[r] = sur_s[r] * (float)(1.0 / std::log((double)cfg.vocab)) + 0.0f;
+                for (int j = 0; j < cfg.mood; ++j) {
+                    const float u = sur_z[r] * m->mood_win[j] + m->mood_bin[j];
+                    const float ll = log_sigmoid(m->mood_lam[j]), oml = sigmoid(-m->mood_lam[j]);
+                    const float p = g_exp(0.0f * ll) * 1.0f;
+                    mood_now[(size_t)r * cfg.mood + j] = p * (u * oml) + st.mood[j] * g_exp(1.0f * ll);
+                }
+            }
+            have_surprise = true;
+            T("sur_z", 0, sur_z.data(), 1);
+            if (cfg.mood > 0) T("mood", 0, mood_now.data(), cfg.mood);
+        }
         if (i == 0 && nk > 0) {
             // the nucleus reads block 0's output: 2 sigmoid(rmsnorm(x, g) W + b)
             sig.assign((size_t)R * nk, 0.f);
@@ -1007,6 +1054,12 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
             st.su = std::move(nw[r].su);
             st.sx = std::move(nw[r].sx);
         }
+        if (surprise) {  // fstep/arch_f3.rs:324-336
+            st.prev.assign(sur_prev.begin() + (size_t)r * d, sur_prev.begin() + (size_t)(r + 1) * d);
+            st.pvalid[0] = 1.0f;
+            st.last_s[0] = sur_s[r];
+            if (cfg.mood > 0) st.mood.assign(mood_now.begin() + (size_t)r * cfg.mood, mood_now.begin() + (size_t)(r + 1) * cfg.mood);
+        }
         if (eng_written) {
             st.ek = std::move(nw[r].ek);
             st.evv = std::move(nw[r].evv);
@@ -1021,6 +1074,10 @@ bool parse_state_name(const orc_state* s, int row, const std::string& name, cons
     const RowState& r = s->rows[row];
     if (name == "eng.k") { *out = &r.ek; return true; }
     if (name == "eng.v") { *out = &r.evv; return true; }
+    if (name == "v51.prev") { *out = &r.prev; return true; }
+    if (name == "v51.mood") { *out = &r.mood; return true; }
+    if (name == "v51.pvalid") { *out = &r.pvalid; return true; }
+    if (name == "v51.last_s") { *out = &r.last_s; return true; }
     const size_t d1 = name.find('.'), d2 = name.rfind('.');
     if (d1 == std::string::npos || d2 == d1) return false;
     const std::string kind = name.substr(0, d1), what = name.substr(d2 + 1);
@@ -1135,6 +1192,7 @@ int orc_model_check(orc_model* m, char* missing, int cap) {
     if (m->tok_emb.empty()) return fail("tok_emb");
     if (m->final_norm.empty()) return fail("final.norm");
     if (c.neuromod > 0 && (m->nm_norm.empty() || m->nm_wn.empty() || m->nm_bn.empty())) return fail("nm.norm / nm.wn / nm.bn");
+    if (c.mood > 0 && (m->mood_lam.empty() || m->mood_win.empty() || m->mood_bin.empty())) return fail("v51.mood.lam / win / bin");
     if (c.thalamus && (m->th_read.empty() || m->th_gate.empty() || m->th_bias.empty())) return fail("th.read / th.gate / th.bias");
     if (!m->head.ok()) return fail("head");
     for (int i = 0; i < c.n_blocks; ++i) {
@@ -1149,7 +1207,9 @@ int orc_model_check(orc_model* m, char* missing, int cap) {
                         {"mlp.norm", &b.mlp_norm, true}, {"dense", &b.dense, c.dense != 0},
                         {"parts.stp.u_param", &b.stp_u, c.stp != 0}, {"parts.stp.f_param", &b.stp_f, c.stp != 0},
                         {"parts.stp.d_param", &b.stp_d, c.stp != 0}, {"parts.stp.mix", &b.stp_mix, c.stp != 0},
-                        {"v51.dend_a", &b.dend_a, c.dendrite && c.fast_mem}, {"v51.dend_b", &b.dend_b, c.dendrite && c.fast_mem}};
+                        {"v51.dend_a", &b.dend_a, c.dendrite && c.fast_mem}, {"v51.dend_b", &b.dend_b, c.dendrite && c.fast_mem},
+                        {"v51.da_w", &b.da_w, c.dopamine && i > 0}, {"v51.da_c", &b.da_c, c.dopamine && i > 0},
+                        {"v51.mood_g", &b.mood_g, c.mood > 0 && i > 0}};
         for (const F& f : fs)
             if (f.need && f.v->empty()) return fail(p + f.n);
         struct Q { const char* n; const QW* q; bool need; };
@@ -1178,6 +1238,10 @@ orc_state* orc_state_new(const orc_model* m, int rows) {
         r.ms.assign(c.n_blocks, std::vector<float>(c.mem_momentum > 0.f ? fl : 0, 0.f));
         r.su.assign(c.n_blocks, std::vector<float>(c.stp ? c.d : 0, 0.f));  // u = 0, x = 1 (nn/parts/src/stp.rs:69-70)
         r.sx.assign(c.n_blocks, std::vector<float>(c.stp ? c.d : 0, 1.f));
+        r.prev.assign((c.dopamine || c.mood > 0) ? c.d : 0, 0.f);  // src/v51.rs:1029-1036
+        r.mood.assign(c.mood, 0.f);
+        r.pvalid.assign((c.dopamine || c.mood > 0) ? 1 : 0, 0.f);
+        r.last_s.assign((c.dopamine || c.mood > 0) ? 1 : 0, 0.f);
     }
     return s;
 }

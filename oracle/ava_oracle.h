@@ -61,6 +61,8 @@ typedef struct orc_config {
     int32_t dendrite;       /* --dendrite: MLP units times 1 + tanh(head_norm(memory read) A B) (fstep/arch_f4.rs:120-141) */
     int32_t neuromod;       /* --neuromod k (3): NE, ACh, DA signals from a nucleus after block 0 (src/v50.rs:20-29) */
     int32_t stp;            /* --stp: the spikes reach W_out through a short-term-plastic synapse (fstep/arch_f3.rs:72-106) */
+    int32_t dopamine;       /* --dopamine: the surprise at this token scales the later blocks' MLP output (fstep/arch_f4.rs:131-143) */
+    int32_t mood;           /* --mood (4 units): a slow trace of the surprise scales the later blocks' LIF current (fstep/arch_f3.rs:106-186) */
     int32_t thalamus;       /* --thalamus: a relay reads the stream and gates each block's memory read and residual (fstep/arch_f2.rs:62-153) */
     float   mem_momentum;   /* 0: off */
     float   slope;          /* surrogate slope (forward value cancels; kept for the literal op order) */

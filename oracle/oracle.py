@@ -21,7 +21,7 @@ class OrcConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "vocab", "d", "n_blocks", "hidden", "kwta_k", "head_size", "eng_block", "eng_head_size", "eng_store_bf16",
         "eng_cap", "gate_rank", "spikes", "alif", "theta", "lif_scale", "value_residual", "relu2", "dense",
-        "out_gate", "fast_mem", "dendrite", "neuromod", "stp", "thalamus")] + [("mem_momentum", C.c_float), ("slope", C.c_float)]
+        "out_gate", "fast_mem", "dendrite", "neuromod", "stp", "dopamine", "mood", "thalamus")] + [("mem_momentum", C.c_float), ("slope", C.c_float)]
 
 
 def build(force: bool = False) -> str:

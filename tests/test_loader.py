@@ -64,8 +64,9 @@ def test_arch_flag_words():
     assert (got["stp"], got["dendrite"]) == (1, 1)
     got = engine.arch_flags(AVA04_FLAGS + " --stp --neuromod 3 --dendrite", base)
     assert (got["stp"], got["neuromod"], got["dendrite"]) == (1, 3, 1)
-    got = engine.arch_flags(AVA04_FLAGS + " --stp --neuromod 3 --dendrite --thalamus", base)
-    assert (got["neuromod"], got["thalamus"]) == (3, 1)
+    got = engine.arch_flags(AVA04_FLAGS + " --stp --neuromod 3 --dendrite --thalamus --dopamine --mood", base)
+    assert (got["neuromod"], got["thalamus"], got["dopamine"], got["mood"]) == (3, 1, 1, 4)
+    assert engine.arch_flags(AVA04_FLAGS + " --mood-units 2", base)["mood"] == 2
     with pytest.raises(engine.NotApplicable, match="--letters"):
         engine.arch_flags(AVA04_FLAGS + " --stp --neuromod 3 --dendrite --letters --dopamine --thalamus", base)
     with pytest.raises(engine.NotApplicable, match="gates"):

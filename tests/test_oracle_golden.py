@@ -465,11 +465,12 @@ def test_new_parts_start_as_no_change(orc):
     same bits."""
     from ava_b200 import config, synth
     base = config.tiny(head_size=64)
-    full = config.tiny(head_size=64, stp=1, dendrite=1, neuromod=3, thalamus=1)
+    full = config.tiny(head_size=64, stp=1, dendrite=1, neuromod=3, thalamus=1, dopamine=1, mood=4)
     w0 = synth.model(base, 3, "awake")
     w1 = synth.model(full, 3, "awake")
     for k in w1:
-        if k.endswith("parts.stp.mix") or k.endswith("v51.dend_b") or k in ("nm.wn", "nm.bn", "th.gate", "th.bias"):  # nucleus and relay then send 2 sigmoid(0) = 1
+        if k.endswith("parts.stp.mix") or k.endswith("v51.dend_b") or k.endswith("v51.da_w") or k.endswith("v51.da_c") or k.endswith("v51.mood_g") \
+                or k in ("nm.wn", "nm.bn", "th.gate", "th.bias"):  # nucleus and relay then send 2 sigmoid(0) = 1
             w1[k] = np.zeros_like(w1[k])
     m0, m1 = orc.OracleModel(base, w0), orc.OracleModel(full, w1)
     s0, s1 = m0.state(2), m1.state(2)
@@ -512,3 +513,37 @@ def test_relay_gates_follow_their_formula(orc):
     for t in range(4):
         without = s0.step(ids[:, t])
     assert np.abs(with_gates - without).max() > 1e-3
+
+
+def test_surprise_mood_and_dopamine_follow_their_formulas(orc):
+    """--dopamine / --mood (src/model/fstep/arch_f3.rs:106-186): the surprise at token t is the cross entropy of the
+    head's logits for block 0's normed output at t - 1 (0 at the first token), z = s / ln V, the mood
+    m = (z win + bin) sigmoid(-lam) + m sigmoid(lam).  Checked in f64 on the carried tensors token by token."""
+    from ava_b200 import config, synth
+    cfg = config.tiny(head_size=64, dopamine=1, mood=4)
+    w = synth.model(cfg, 5, "awake")
+    m = orc.OracleModel(cfg, w)
+    s = m.state(1)
+    ids = synth.token_ids(cfg["vocab"], 1, 6)
+    q, sc = orc.quantize_int8(np.ascontiguousarray(w["tok_emb"].T))
+    head = q.astype(np.float64) * sc.astype(np.float64)
+    lam, win, b = (w["v51.mood." + k].astype(np.float64) for k in ("lam", "win", "bin"))
+    mood = np.zeros(4)
+    sig = lambda x: 1.0 / (1.0 + np.exp(-x))
+    for t in range(6):
+        prev, valid = s.get(0, "v51.prev").astype(np.float64), float(s.get(0, "v51.pvalid")[0])
+        assert valid == (0.0 if t == 0 else 1.0)
+        s.step(ids[:, t])
+        lg = prev @ head
+        ce = (np.log(np.exp(lg - lg.max()).sum()) + lg.max() - lg[ids[0, t]]) * valid
+        assert abs(float(s.get(0, "v51.last_s")[0]) - ce) < 1e-4, t
+        mood = (ce / np.log(cfg["vocab"]) * win + b) * sig(-lam) + mood * sig(lam)
+        assert np.allclose(s.get(0, "v51.mood"), mood, rtol=0, atol=1e-5), t
+    assert float(s.get(0, "v51.last_s")[0]) > 1.0   # an untrained model is surprised
+    # both parts move the logits
+    plain = dict(cfg, dopamine=0, mood=0)
+    s0 = orc.OracleModel(plain, {k: v for k, v in w.items() if "v51." not in k}).state(1)
+    s1 = m.state(1)
+    for t in range(3):
+        a, b2 = s0.step(ids[:, t]), s1.step(ids[:, t])
+    assert np.abs(a - b2).max() > 1e-3
