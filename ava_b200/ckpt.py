@@ -75,6 +75,8 @@ def flags_of(cfg: dict) -> str:
         f.append(f"--neuromod {cfg['neuromod']}")
     if cfg.get("thalamus"):
         f.append("--thalamus")
+    if cfg.get("cb_units"):
+        f.append(f"--cerebellum-head {cfg['cb_units']}")
     if cfg.get("dopamine"):
         f.append("--dopamine")
     if cfg.get("mood"):

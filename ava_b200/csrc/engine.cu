@@ -107,6 +107,7 @@ struct ava_engine {
     Dev tok_emb, final_norm;
     Dev nm_norm, nm_wn, nm_bn;  // --neuromod: the nucleus (gain [d], read-out padded to [d][4], bias [k])
     Dev mood_lam, mood_win, mood_bin;  // --mood: decay, input weight and bias [k]
+    Dev cb_w, cb_idx, cb_sgn;       // --cerebellum-head: read-out [G][d], wiring [G][4] (u32 inputs, f32 weights)
     Dev th_read, th_gate, th_bias;  // --thalamus: reads [blocks][d][16], gates [blocks][16][2], biases [blocks][2]
     QMat head;
     std::vector<std::unique_ptr<BlockDev>> blocks;
@@ -122,6 +123,8 @@ struct ava_engine {
     // --dopamine / --mood: block 0's normed output [rows][d], the rows the head reads (the position before each), the
     // head's logits for them [rows][vocab], surprise s and z [rows], moods [rows][k], the current's gain and the MLP's output [rows][d]
     Dev sur_xf, sur_in, sur_logits, sur_s, sur_z, mood_all, mood_gain, y2;
+    Dev cb_emb, cb_en, cb_h, cb_a, cb_lj, cb_lc, cb_n;  // --cerebellum-head: embedding rows (raw, normed) [rows][d], units and kept units
+                                                        // [rows][G], the code's list [rows][G] twice, its length [rows]
     Dev th_acc, th_g, x_in;  // --thalamus: the relay's sum [rows][16], the block's gates [rows][4], the block's input [rows][d]
     Dev ctx, dz1, ones;  // --dendrite: the block's memory read [rows][d], its projection [rows][32], a vector of ones [d]
     uint32_t* status_host = nullptr;  // pinned
@@ -208,6 +211,7 @@ int64_t f32_len(const ava_config& c, const std::string& name) {
     if (name == "nm.wn" && c.neuromod > 0) return d * c.neuromod;
     if (name == "nm.bn" && c.neuromod > 0) return c.neuromod;
     if (c.mood > 0 && (name == "v51.mood.lam" || name == "v51.mood.win" || name == "v51.mood.bin")) return c.mood;
+    if (name == "cbh.wo" && c.cb_units > 0) return (int64_t)c.cb_units * d;
     if (name == "th.read" && c.thalamus) return (int64_t)c.n_blocks * d * 16;  // TH_K (src/v51b.rs:45)
     if (name == "th.gate" && c.thalamus) return (int64_t)c.n_blocks * 16 * 2;
     if (name == "th.bias" && c.thalamus) return (int64_t)c.n_blocks * 2;
@@ -305,6 +309,7 @@ const char* find_blocker(const ava_config& c, int* cw, int* rb) {
     if (c.spikes < 0 || c.spikes > 2) return "unknown spike kind";
     if (c.neuromod != 0 && (c.neuromod < 2 || c.neuromod > 4)) return "neuromod: 2 to 4 signals";
     if (c.mood < 0 || c.mood > 16) return "mood: up to 16 units";
+    if (c.cb_units < 0 || c.cb_units % 32) return "cerebellum head: a multiple of 32 units";
     if (c.thalamus && !c.fast_mem) return "thalamus: a part of the blocks with the fast-weight memory";
     if (c.fast_mem && (c.head_size % 16 || !mem_heads_tiling(c.head_size, cw, rb, c.mem_momentum > 0.0f))) return "memory head size not covered (a multiple of 16 whose column slice fits shared memory)";
     return nullptr;
@@ -347,6 +352,16 @@ int ensure_workspace(ava_engine* e, int rows, int logit_rows = 0) {
             CK(e->mood_gain.alloc(M * d * f));
         }
         if (c.dopamine) CK(e->y2.alloc(M * d * f));
+    }
+    if (c.cb_units > 0) {
+        const size_t G = c.cb_units;
+        CK(e->cb_emb.alloc(M * d * f));
+        CK(e->cb_en.alloc(M * d * f));
+        CK(e->cb_h.alloc(M * G * f));
+        CK(e->cb_a.alloc(M * G * f));
+        CK(e->cb_lj.alloc(M * G * sizeof(int)));
+        CK(e->cb_lc.alloc(M * G * f));
+        CK(e->cb_n.alloc(M * sizeof(int)));
     }
     if (c.thalamus) {
         CK(e->th_acc.alloc(M * 16 * f));
@@ -763,9 +778,22 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         // the head reads the last token's rows only, unless every position's logits were asked for
         const int first_row = all_logits ? 0 : (T - 1) * rows, head_rows = all_logits ? M : rows;
         prof_begin(e, "rmsnorm");
-        launch_rmsnorm(st, x + (size_t)first_row * d, e->final_norm.as<float>(), head_rows, d, h, limbs_for(e, h, head_rows, d));
+        launch_rmsnorm(st, x + (size_t)first_row * d, e->final_norm.as<float>(), head_rows, d, h, c.cb_units > 0 ? nullptr : limbs_for(e, h, head_rows, d));
         prof_end(e);
         dbg(e, "x_final", -1, h, head_rows, d);
+        if (c.cb_units > 0) {
+            // CB: the final normed state plus the read-out of the sparse code of it and the token's embedding
+            const int G = c.cb_units;
+            prof_begin(e, "cerebellum");
+            launch_cb_inputs(st, e->tok_emb.as<float>(), tok + first_row, head_rows, d, c.vocab, e->cb_emb.as<float>());
+            launch_rmsnorm(st, e->cb_emb.as<float>(), e->ones.as<float>(), head_rows, d, e->cb_en.as<float>());
+            launch_cb_units(st, h, e->cb_en.as<float>(), e->cb_idx.as<uint32_t>(), e->cb_sgn.as<float>(), G, d, head_rows, e->cb_h.as<float>());
+            launch_kwta(st, e->cb_h.as<float>(), head_rows, G, G / 32, 0, e->cb_a.as<float>());
+            launch_cb_read(st, e->cb_a.as<float>(), G, e->cb_lj.as<int>(), e->cb_lc.as<float>(), e->cb_n.as<int>(), e->cb_w.as<float>(), head_rows, d, h);
+            prof_end(e);
+            e->launches += 5;
+            dbg(e, "x_cb", -1, h, head_rows, d);
+        }
         float* lg = logits ? logits : e->logits.as<float>();
         gemm(e, "gemm.head", h, d, e->head, lg, c.vocab, head_rows, EPI_STORE);
         if (next) {
@@ -1173,7 +1201,40 @@ int ava_engine_finalize(ava_engine* e) {
         if ((rc = upload_f32(e, e->th_gate, "th.gate", true))) return rc;
         if ((rc = upload_f32(e, e->th_bias, "th.bias", true))) return rc;
     }
-    if ((c.dendrite && c.fast_mem) || c.thalamus) {
+    if (c.cb_units > 0) {
+        if ((rc = upload_f32(e, e->cb_w, "cbh.wo", true))) return rc;
+        // the fixed wiring (src/v51b.rs:241-266, seed and fan-in :47-49): Marsaglia's xorshift64 (13, 7, 17) from seed | 1;
+        // per unit four distinct inputs of the 2 d (a draw modulo 2 d, redrawn while already picked), then per input one more
+        // draw whose lowest bit gives the sign of 1/2
+        const int G = c.cb_units, inputs = 2 * c.d, fan = 4;
+        std::vector<uint32_t> idx;
+        std::vector<float> sg;
+        uint64_t sd = 0x51B0CE7Eull | 1;
+        auto next = [&]() {
+            sd ^= sd << 13;
+            sd ^= sd >> 7;
+            sd ^= sd << 17;
+            return sd;
+        };
+        const float amp = 1.0f / std::sqrt((float)fan);
+        for (int u = 0; u < G; ++u) {
+            uint32_t picked[4];
+            int np = 0;
+            while (np < std::min(fan, inputs)) {
+                const uint32_t r = (uint32_t)(next() % (uint64_t)inputs);
+                bool seen = false;
+                for (int q = 0; q < np; ++q) seen |= picked[q] == r;
+                if (!seen) picked[np++] = r;
+            }
+            for (int q = 0; q < np; ++q) {
+                idx.push_back(picked[q]);
+                sg.push_back((next() & 1) == 0 ? amp : -amp);
+            }
+        }
+        if ((rc = upload(e, e->cb_idx, idx.data(), idx.size() * sizeof(uint32_t)))) return rc;
+        if ((rc = upload(e, e->cb_sgn, sg.data(), sg.size() * sizeof(float)))) return rc;
+    }
+    if ((c.dendrite && c.fast_mem) || c.thalamus || c.cb_units > 0) {
         const std::vector<float> one((size_t)c.d, 1.0f);
         if ((rc = upload(e, e->ones, one.data(), one.size() * sizeof(float)))) return rc;
     }

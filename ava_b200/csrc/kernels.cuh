@@ -129,6 +129,12 @@ void launch_mood(cudaStream_t st, const float* z, int rows, int T, int k, const 
                  float* mood_all);
 // gain [M][d] = 1 + tanh(mood [M][k] . G [k][d]) (the product in the one-row order), the LIF current's factor
 void launch_mood_gain(cudaStream_t st, const float* mood_all, int k, const float* G, int M, int d, float* gain);
+// --cerebellum-head (src/model/fstep/arch_f3.rs:207-283): the tokens' embedding rows gathered; the G units' sums of their
+// four wired inputs of [xf, en] (en: the normed embedding rows); after the k-WTA kernel has kept the top G/32 of h into a:
+// the code's list per token-row (scratch list_j, list_c [R][G], count [R]) and xf += the read-out's rows in unit order
+void launch_cb_inputs(cudaStream_t st, const float* tok_emb, const uint32_t* tok, int R, int d, int V, float* emb_rows);
+void launch_cb_units(cudaStream_t st, const float* xf, const float* en, const uint32_t* idx, const float* sgn, int g, int d, int R, float* h);
+void launch_cb_read(cudaStream_t st, const float* a, int g, int* list_j, float* list_c, int* count, const float* W, int R, int d, float* xf);
 // x += (y * (1 + tanh(z[row] w + c))) [* row_gain[row * NM_STRIDE]]: the MLP's output under --dopamine (then --neuromod's DA)
 void launch_da_add(cudaStream_t st, float* x, const float* y, const float* z, const float* w, const float* c, const float* row_gain, int M, int d);
 

@@ -353,6 +353,12 @@ int ava_arch_flags(const char* flags, ava_config* cfg) {
         else if (k == "--dendrite") cfg->dendrite = 1;
         else if (k == "--thalamus") cfg->thalamus = 1;
         else if (k == "--dopamine") cfg->dopamine = 1;
+        else if (k == "--cerebellum-head") {
+            if (!value(&v)) return fail(AVA_ERR_ARG, "--cerebellum-head needs a value");
+            const int g = std::atoi(v.c_str());
+            if (g < 0 || g % 32) return fail(AVA_ERR_ARG, "--cerebellum-head " + v + ": a multiple of 32 (src/v51b.rs:110-112)");
+            cfg->cb_units = g;
+        }
         else if (k == "--mood") cfg->mood = 4;  // MOOD_UNITS (src/v51.rs:53)
         else if (k == "--mood-units") {
             if (!value(&v) || std::atoi(v.c_str()) < 1 || std::atoi(v.c_str()) > 16) return fail(AVA_ERR_ARG, "--mood-units needs an integer from 1 to 16");
@@ -443,7 +449,7 @@ int ava_config_from_ckpt(const ava_ckpt* c, const char* kind, const char* arch_f
         int b;
         std::string rest;
         if (!block_name(e.name, &b, &rest)) {
-            if (e.name != "tok_emb" && e.name != "final.norm" && e.name != "nm.norm" && e.name != "nm.wn" && e.name != "nm.bn" && e.name != "th.read" && e.name != "th.gate" && e.name != "th.bias" && e.name.rfind("v51.mood.", 0) != 0)
+            if (e.name != "tok_emb" && e.name != "final.norm" && e.name != "nm.norm" && e.name != "nm.wn" && e.name != "nm.bn" && e.name != "th.read" && e.name != "th.gate" && e.name != "th.bias" && e.name.rfind("v51.mood.", 0) != 0 && e.name != "cbh.wo")
                 return fail(AVA_NOT_APPLICABLE, e.name + ": a tensor of a part the engine does not cover (glance, magnitude code, order head)");
             continue;
         }

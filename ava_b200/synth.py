@@ -122,6 +122,8 @@ def model(cfg: dict, seed: int = 0, recipe: str = "bench", unit_gain: bool = Tru
         w["v51.mood.lam"] = g.n("v51.mood.lam", (k,), 1.0) + 2.0
         w["v51.mood.win"] = (1.0 + g.n("v51.mood.win", (k,), 0.3)).astype(np.float32)
         w["v51.mood.bin"] = g.n("v51.mood.bin", (k,), 0.1) if awake else np.zeros(k, np.float32)
+    if cfg.get("cb_units"):
+        w["cbh.wo"] = g.n("cbh.wo", (cfg["cb_units"], d), 0.05) if awake else np.zeros((cfg["cb_units"], d), np.float32)
     if cfg.get("thalamus"):
         # the reference starts the reads as seeded noise / sqrt(d) and the gates at zero (every gate exactly 1)
         w["th.read"] = g.n("th.read", (L, d, 16), 1.0 / math.sqrt(d))

@@ -75,6 +75,11 @@ typedef struct ava_config {
                                block 0; every later block's LIF current times 1 + tanh(m G) per channel, after --neuromod's NE
                                (src/model/fstep/arch_f3.rs:150-186); weights v51.mood.lam / win / bin [k], b{i}.v51.mood_g [k, d],
                                i > 0; carried per row: v51.mood [k] (and the surprise's three tensors) */
+    int32_t cb_units;       /* --cerebellum-head G (a multiple of 32; Ava 0.4: 12288): G granule units each sum 4 fixed inputs of
+                               [final normed state, rmsnorm(the token's embedding)] with weights +-1/2 (wiring from the
+                               reference's seed), the top G/32 are kept, rectified and brought to unit length, and their rows of
+                               cbh.wo [G, d], summed in unit order, are added to the final normed state before the head
+                               (src/model/fstep/arch_f3.rs:207-283, src/v51b.rs:241-266,327-360) */
     float   mem_momentum;   /* --mem-momentum (0: off) */
     float   slope;          /* --surrogate-slope (does not change forward values) */
 } ava_config;

@@ -419,6 +419,34 @@ void kwta(const float* u, int n, int k, bool relu2, float* a) {
         for (int i = 0; i < n; ++i) a[i] = a[i] * a[i];
 }
 
+// --cerebellum-head's fixed wiring (src/v51b.rs:241-266): Marsaglia's xorshift64 (13, 7, 17) from seed | 1; per unit
+// `fan_in` distinct inputs (a draw modulo the input count, redrawn while already picked), then per input one more
+// draw whose lowest bit gives the sign of 1 / sqrt(fan_in).
+void cb_wiring(int inputs, int g, int fan_in, uint64_t seed, std::vector<uint32_t>* idx, std::vector<float>* w) {
+    uint64_t s = seed | 1;
+    auto next = [&]() {
+        s ^= s << 13;
+        s ^= s >> 7;
+        s ^= s << 17;
+        return s;
+    };
+    const float amp = 1.0f / std::sqrt((float)fan_in);
+    idx->clear();
+    w->clear();
+    std::vector<uint32_t> picked;
+    for (int u = 0; u < g; ++u) {
+        picked.clear();
+        while ((int)picked.size() < std::min(fan_in, inputs)) {
+            const uint32_t r = (uint32_t)(next() % (uint64_t)inputs);
+            if (std::find(picked.begin(), picked.end(), r) == picked.end()) picked.push_back(r);
+        }
+        for (uint32_t r : picked) {
+            idx->push_back(r);
+            w->push_back((next() & 1) == 0 ? amp : -amp);
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ A8 engram read
 // fstep.rs:303-356: per key the score chain K[j][0] q0, then fma(K[j][a], q[a], .), times scale plus 0; softmax with
 // the max found by "replace while mx < s", exp(s - mx), the sum from 0, each divided; then the one-row product p . V.
@@ -500,6 +528,9 @@ struct orc_model {
     std::vector<float> tok_emb, final_norm;
     std::vector<float> nm_norm, nm_wn, nm_bn;  // --neuromod: the nucleus (gain [d], read-out [d, k], bias [k])
     std::vector<float> mood_lam, mood_win, mood_bin;  // --mood: decay, input weight and bias [k]
+    std::vector<float> cb_w;     // --cerebellum-head: the read-out [G, d]
+    std::vector<uint32_t> cb_idx;  // its fixed wiring: 4 inputs of [xf, rmsnorm(emb)] per unit, weights +-1/2
+    std::vector<float> cb_sgn;
     std::vector<float> th_read, th_gate, th_bias;  // --thalamus: reads [L, d, 16], gates [L, 16, 2], biases [L, 2]
     QW head;
     std::vector<Block> blocks;
@@ -535,6 +566,7 @@ std::vector<float>* f32_slot(orc_model* m, const std::string& name, int64_t* wan
     if (name == "v51.mood.lam") { *want = c.mood; return &m->mood_lam; }
     if (name == "v51.mood.win") { *want = c.mood; return &m->mood_win; }
     if (name == "v51.mood.bin") { *want = c.mood; return &m->mood_bin; }
+    if (name == "cbh.wo") { *want = (int64_t)c.cb_units * d; return &m->cb_w; }
     if (name == "th.read") { *want = (int64_t)c.n_blocks * d * 16; return &m->th_read; }
     if (name == "th.gate") { *want = (int64_t)c.n_blocks * 16 * 2; return &m->th_gate; }
     if (name == "th.bias") { *want = (int64_t)c.n_blocks * 2; return &m->th_bias; }
@@ -635,6 +667,33 @@ void stp_step(const float* s, const float* U, const float* F, const float* D, co
 // products take the R rows as one batch, as the reference's batched path does (each row's outputs are the bits of the
 // row alone, int8.rs:7-8); everything else runs row by row.  Returns 0, or 1 when the reference's fused step would
 // refuse a token (non-finite gates or keys): such a row is left uncommitted.
+// fstep/arch_f3.rs:207-283 on one row: xf [d] plus the read-out of the sparse code of [xf, rmsnorm(emb, 1)]
+void cb_correct(const orc_model* m, const float* emb, float* xf) {
+    const int d = m->cfg.d, g = m->cfg.cb_units, k = g / 32;
+    std::vector<float> u(xf, xf + d), ones(d, 1.0f), en(d), h(g), a(g);
+    rmsnorm(emb, ones.data(), d, en.data());
+    u.insert(u.end(), en.begin(), en.end());
+    for (int j = 0; j < g; ++j) {
+        float s = 0.f;
+        for (int q = 0; q < 4; ++q) s += u[m->cb_idx[(size_t)j * 4 + q]] * m->cb_sgn[(size_t)j * 4 + q];
+        h[j] = s;
+    }
+    kwta(h.data(), g, k, false, a.data());
+    float s2 = 0.f;
+    for (int j = 0; j < g; ++j) s2 += a[j] * a[j];
+    const float len = std::sqrt(s2) * 1.0f + (float)1e-6;
+    std::vector<std::pair<int, float>> act;
+    for (int j = 0; j < g; ++j) {
+        const float c = a[j] / len;
+        if (c != 0.0f) act.emplace_back(j, c);
+    }
+    if (act.empty()) act.emplace_back(0, 0.0f);
+    std::vector<float> corr(d, 0.f);
+    for (const auto& e : act)
+        for (int c = 0; c < d; ++c) corr[c] += m->cb_w[(size_t)e.first * d + c] * e.second;
+    for (int c = 0; c < d; ++c) xf[c] = xf[c] + corr[c];
+}
+
 int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, float* logits, size_t logit_stride, bool trace) {
     const orc_config& cfg = m->cfg;
     const int d = cfg.d, hs = cfg.head_size, nh = m->nh(), H = cfg.hidden, L = cfg.n_blocks;
@@ -1032,6 +1091,10 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
 #pragma omp parallel for num_threads(nt) schedule(static)
     for (int r = 0; r < R; ++r) rmsnorm(&x[(size_t)r * d], m->final_norm.data(), d, &h[(size_t)r * d]);
     T("x_final", -1, h.data(), d);
+    if (cfg.cb_units > 0) {  // CB: the cerebellum's correction of the final normed state, from it and the token's embedding
+        for (int r = 0; r < R; ++r) cb_correct(m, &m->tok_emb[(size_t)tok[r] * d], &h[(size_t)r * d]);
+        T("x_cb", -1, h.data(), d);
+    }
     if (logit_stride == (size_t)cfg.vocab) {
         q8_matmul(m->head, h.data(), R, logits);
     } else {
@@ -1140,6 +1203,13 @@ void orc_stp(const float* s, const float* u_param, const float* f_param, const f
     }
     stp_step(s, U.data(), F.data(), D.data(), mix, u0, x0, d, out, u1, x1, eff);
 }
+void orc_cb_wiring(int inputs, int g, uint32_t* idx, float* w) {
+    std::vector<uint32_t> i;
+    std::vector<float> s;
+    cb_wiring(inputs, g, 4, 0x51B0CE7Eull, &i, &s);
+    std::copy(i.begin(), i.end(), idx);
+    std::copy(s.begin(), s.end(), w);
+}
 float orc_kth_largest(const float* u, int n, int k) { return kth_largest(u, n, k); }
 void orc_kwta(const float* u, int n, int k, int relu2, float* a) { kwta(u, n, k, relu2 != 0, a); }
 void orc_attend(const float* q, const float* kc, const float* vc, int n, int hs, float scale, float* out) { attend(q, kc, vc, n, hs, scale, out); }
@@ -1159,6 +1229,7 @@ orc_model* orc_model_new(const orc_config* cfg) {
     orc_model* m = new orc_model();
     m->cfg = *cfg;
     m->blocks.resize(cfg->n_blocks);
+    if (cfg->cb_units > 0) cb_wiring(2 * cfg->d, cfg->cb_units, 4, 0x51B0CE7Eull, &m->cb_idx, &m->cb_sgn);  // src/v51b.rs:47-49,292
     return m;
 }
 void orc_model_free(orc_model* m) { delete m; }
@@ -1193,6 +1264,7 @@ int orc_model_check(orc_model* m, char* missing, int cap) {
     if (m->final_norm.empty()) return fail("final.norm");
     if (c.neuromod > 0 && (m->nm_norm.empty() || m->nm_wn.empty() || m->nm_bn.empty())) return fail("nm.norm / nm.wn / nm.bn");
     if (c.mood > 0 && (m->mood_lam.empty() || m->mood_win.empty() || m->mood_bin.empty())) return fail("v51.mood.lam / win / bin");
+    if (c.cb_units > 0 && m->cb_w.empty()) return fail("cbh.wo");
     if (c.thalamus && (m->th_read.empty() || m->th_gate.empty() || m->th_bias.empty())) return fail("th.read / th.gate / th.bias");
     if (!m->head.ok()) return fail("head");
     for (int i = 0; i < c.n_blocks; ++i) {

@@ -63,6 +63,7 @@ typedef struct orc_config {
     int32_t stp;            /* --stp: the spikes reach W_out through a short-term-plastic synapse (fstep/arch_f3.rs:72-106) */
     int32_t dopamine;       /* --dopamine: the surprise at this token scales the later blocks' MLP output (fstep/arch_f4.rs:131-143) */
     int32_t mood;           /* --mood (4 units): a slow trace of the surprise scales the later blocks' LIF current (fstep/arch_f3.rs:106-186) */
+    int32_t cb_units;       /* --cerebellum-head G: G sparse granule units correct the final normed state (fstep/arch_f3.rs:207-283) */
     int32_t thalamus;       /* --thalamus: a relay reads the stream and gates each block's memory read and residual (fstep/arch_f2.rs:62-153) */
     float   mem_momentum;   /* 0: off */
     float   slope;          /* surrogate slope (forward value cancels; kept for the literal op order) */
@@ -99,6 +100,8 @@ void orc_lif(const float* cur, const float* beta, const float* theta, const floa
 /* S (--stp): the spikes through the short-term-plastic synapse (fstep/arch_f3.rs:72-106, nn/parts/src/stp.rs:42-85):
  * out [d] what reaches W_out, (u1, x1) the synapse's new state, eff (may be NULL) the efficacy e / U.  The parameters
  * are the raw ones (their sigmoids are taken inside). */
+/* --cerebellum-head's wiring for `inputs` inputs and g units of fan-in 4 from the reference's seed: idx [g * 4], w [g * 4] */
+void orc_cb_wiring(int inputs, int g, uint32_t* idx, float* w);
 void orc_stp(const float* s, const float* u_param, const float* f_param, const float* d_param, const float* mix, const float* u0, const float* x0,
              int d, float* out, float* u1, float* x1, float* eff);
 float orc_kth_largest(const float* u, int n, int k);

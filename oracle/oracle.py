@@ -21,7 +21,7 @@ class OrcConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "vocab", "d", "n_blocks", "hidden", "kwta_k", "head_size", "eng_block", "eng_head_size", "eng_store_bf16",
         "eng_cap", "gate_rank", "spikes", "alif", "theta", "lif_scale", "value_residual", "relu2", "dense",
-        "out_gate", "fast_mem", "dendrite", "neuromod", "stp", "dopamine", "mood", "thalamus")] + [("mem_momentum", C.c_float), ("slope", C.c_float)]
+        "out_gate", "fast_mem", "dendrite", "neuromod", "stp", "dopamine", "mood", "cb_units", "thalamus")] + [("mem_momentum", C.c_float), ("slope", C.c_float)]
 
 
 def build(force: bool = False) -> str:
@@ -65,6 +65,8 @@ def lib() -> C.CDLL:
     L.orc_gemv.argtypes = [fp, C.c_int, fp, C.c_int, fp]
     L.orc_stp.argtypes = [fp] * 7 + [C.c_int] + [fp] * 4
     L.orc_stp.restype = None
+    L.orc_cb_wiring.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_uint32), fp]
+    L.orc_cb_wiring.restype = None
     L.orc_lif.argtypes = [fp, fp, fp, fp, fp, C.c_int, C.c_float, fp, fp, fp, C.c_int, fp, fp, fp]
     L.orc_kth_largest.argtypes = [fp, C.c_int, C.c_int]
     L.orc_kth_largest.restype = C.c_float
@@ -200,6 +202,12 @@ def stp(s, u_param, f_param, d_param, mix, u0, x0):
     L = lib()
     L.orc_stp(sp, *[a[1] for a in arrs], s.size, _fp(out), _fp(u1), _fp(x1), _fp(eff))
     return out, u1, x1, eff
+
+
+def cb_wiring(inputs: int, g: int):
+    idx, w = np.empty(g * 4, np.uint32), np.empty(g * 4, np.float32)
+    lib().orc_cb_wiring(inputs, g, idx.ctypes.data_as(C.POINTER(C.c_uint32)), _fp(w))
+    return idx.reshape(g, 4), w.reshape(g, 4)
 
 
 def kth_largest(u, k):

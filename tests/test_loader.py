@@ -67,6 +67,9 @@ def test_arch_flag_words():
     got = engine.arch_flags(AVA04_FLAGS + " --stp --neuromod 3 --dendrite --thalamus --dopamine --mood", base)
     assert (got["neuromod"], got["thalamus"], got["dopamine"], got["mood"]) == (3, 1, 1, 4)
     assert engine.arch_flags(AVA04_FLAGS + " --mood-units 2", base)["mood"] == 2
+    assert engine.arch_flags(AVA04_FLAGS + " --cerebellum-head 12288", base)["cb_units"] == 12288
+    with pytest.raises(engine.EngineError, match="multiple of 32"):
+        engine.arch_flags(AVA04_FLAGS + " --cerebellum-head 100", base)
     with pytest.raises(engine.NotApplicable, match="--letters"):
         engine.arch_flags(AVA04_FLAGS + " --stp --neuromod 3 --dendrite --letters --dopamine --thalamus", base)
     with pytest.raises(engine.NotApplicable, match="gates"):

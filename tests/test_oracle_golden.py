@@ -465,12 +465,12 @@ def test_new_parts_start_as_no_change(orc):
     same bits."""
     from ava_b200 import config, synth
     base = config.tiny(head_size=64)
-    full = config.tiny(head_size=64, stp=1, dendrite=1, neuromod=3, thalamus=1, dopamine=1, mood=4)
+    full = config.tiny(head_size=64, stp=1, dendrite=1, neuromod=3, thalamus=1, dopamine=1, mood=4, cb_units=512)
     w0 = synth.model(base, 3, "awake")
     w1 = synth.model(full, 3, "awake")
     for k in w1:
         if k.endswith("parts.stp.mix") or k.endswith("v51.dend_b") or k.endswith("v51.da_w") or k.endswith("v51.da_c") or k.endswith("v51.mood_g") \
-                or k in ("nm.wn", "nm.bn", "th.gate", "th.bias"):  # nucleus and relay then send 2 sigmoid(0) = 1
+                or k in ("nm.wn", "nm.bn", "th.gate", "th.bias", "cbh.wo"):  # nucleus and relay then send 2 sigmoid(0) = 1
             w1[k] = np.zeros_like(w1[k])
     m0, m1 = orc.OracleModel(base, w0), orc.OracleModel(full, w1)
     s0, s1 = m0.state(2), m1.state(2)
@@ -547,3 +547,39 @@ def test_surprise_mood_and_dopamine_follow_their_formulas(orc):
     for t in range(3):
         a, b2 = s0.step(ids[:, t]), s1.step(ids[:, t])
     assert np.abs(a - b2).max() > 1e-3
+
+
+def test_cerebellum_wiring_and_correction(orc):
+    """--cerebellum-head: the wiring's properties the reference's own test asks for (src/v51b/tests.rs:94-102: four
+    distinct inputs per unit, weights +-1/2), the generator's first draw by hand, and the correction against a numpy
+    restatement of src/model/fstep/arch_f3.rs:207-283 (top G/32 units, rectified, unit length, read out)."""
+    from ava_b200 import config, synth
+    idx, w = orc.cb_wiring(256, 1024)
+    assert idx.shape == (1024, 4) and all(len(set(r)) == 4 for r in idx.tolist()) and idx.max() < 256
+    assert set(np.unique(w).tolist()) == {-0.5, 0.5}
+    s = 0x51B0CE7E | 1                      # xorshift64 (13, 7, 17), by hand
+    s ^= (s << 13) & (2**64 - 1); s ^= s >> 7; s ^= (s << 17) & (2**64 - 1)
+    assert idx[0, 0] == s % 256
+    cfg = config.tiny(head_size=64, cb_units=512)
+    wts = synth.model(cfg, 9, "awake")
+    st = orc.OracleModel(cfg, wts).state(1)
+    ids = synth.token_ids(cfg["vocab"], 1, 3)
+    d, g = cfg["d"], 512
+    ix, sg = orc.cb_wiring(2 * d, g)
+    orc.trace_enable(True)
+    try:
+        for t in range(3):
+            st.step(ids[:, t])
+            xf, got = orc.trace("x_final", -1)[:d].astype(np.float64), orc.trace("x_cb", -1)[:d]
+            e = wts["tok_emb"][ids[0, t]].astype(np.float64)
+            u = np.concatenate([xf, e / np.sqrt((e * e).mean() + 1e-5)])
+            h = (u[ix] * sg).sum(1)
+            kth = np.sort(h)[-g // 32]
+            a = np.maximum(np.where(h >= kth, h, 0.0), 0.0)
+            code = a / (np.sqrt((a * a).sum()) + 1e-6)
+            assert (code != 0).sum() <= g // 32
+            want = xf + code @ wts["cbh.wo"].astype(np.float64)
+            assert np.allclose(got, want, rtol=0, atol=2e-5), t
+            assert np.abs(got - xf).max() > 1e-3
+    finally:
+        orc.trace_enable(False)
