@@ -18,6 +18,8 @@ def dequantised(weights: dict) -> dict:
     |q| in every column is 127."""
     out = {}
     for name, w in weights.items():
+        if name == "token_bytes":   # the tokenizer's, not the model file's
+            continue
         if isinstance(w, tuple):
             q, sc = w
             out[name] = (q.astype(np.float32) * np.asarray(sc, np.float32)[None, :]).astype(np.float32)
@@ -77,6 +79,8 @@ def flags_of(cfg: dict) -> str:
         f.append("--thalamus")
     if cfg.get("cb_units"):
         f.append(f"--cerebellum-head {cfg['cb_units']}")
+    if cfg.get("letters"):
+        f.append("--letters")
     if cfg.get("dopamine"):
         f.append("--dopamine")
     if cfg.get("mood"):

@@ -107,6 +107,9 @@ struct ava_engine {
     Dev tok_emb, final_norm;
     Dev nm_norm, nm_wn, nm_bn;  // --neuromod: the nucleus (gain [d], read-out padded to [d][4], bias [k])
     Dev mood_lam, mood_win, mood_bin;  // --mood: decay, input weight and bias [k]
+    Dev letters;                    // --letters: every token's share of its input [vocab][d], built when the engine is finalized
+    std::vector<uint8_t> tok_bytes;  // the tokens' spellings, bytes[tok_off[t] .. tok_off[t + 1])
+    std::vector<int64_t> tok_off;
     Dev cb_w, cb_idx, cb_sgn;       // --cerebellum-head: read-out [G][d], wiring [G][4] (u32 inputs, f32 weights)
     Dev th_read, th_gate, th_bias;  // --thalamus: reads [blocks][d][16], gates [blocks][16][2], biases [blocks][2]
     QMat head;
@@ -211,6 +214,11 @@ int64_t f32_len(const ava_config& c, const std::string& name) {
     if (name == "nm.wn" && c.neuromod > 0) return d * c.neuromod;
     if (name == "nm.bn" && c.neuromod > 0) return c.neuromod;
     if (c.mood > 0 && (name == "v51.mood.lam" || name == "v51.mood.win" || name == "v51.mood.bin")) return c.mood;
+    if (c.letters) {  // LETTER_DIM 64, LETTER_MAX 16 (src/v51.rs:54-55)
+        if (name == "v51.letters.byte") return 256 * 64;
+        if (name == "v51.letters.pos" || name == "v51.letters.end") return 16 * 64;
+        if (name == "v51.letters.wo") return 64 * d;
+    }
     if (name == "cbh.wo" && c.cb_units > 0) return (int64_t)c.cb_units * d;
     if (name == "th.read" && c.thalamus) return (int64_t)c.n_blocks * d * 16;  // TH_K (src/v51b.rs:45)
     if (name == "th.gate" && c.thalamus) return (int64_t)c.n_blocks * 16 * 2;
@@ -498,7 +506,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
 
     if (phase != PHASE_END) {
         prof_begin(e, "embed");
-        launch_embed(st, e->tok_emb.as<float>(), tok, M, d, c.vocab, x, streams, e->status.as<uint32_t>());
+        launch_embed(st, e->tok_emb.as<float>(), tok, M, d, c.vocab, x, streams, e->status.as<uint32_t>(), c.letters ? e->letters.as<float>() : nullptr);
         prof_end(e);
         dbg(e, "x_in", -1, x, M, d);
     }
@@ -1055,6 +1063,18 @@ int ava_engine_set_f32(ava_engine* e, const char* name, const float* data, int64
     return AVA_OK;
 }
 
+int ava_engine_set_token_bytes(ava_engine* e, const uint8_t* bytes, const int64_t* offsets) {
+    if (!e || !offsets) return AVA_ERR_ARG;
+    const int V = e->cfg.vocab;
+    for (int t = 0; t < V; ++t)
+        if (offsets[t + 1] < offsets[t] || offsets[0] != 0) return e->fail(AVA_ERR_ARG, "token %d: offsets must start at 0 and not decrease", t);
+    if (offsets[V] > 0 && !bytes) return AVA_ERR_ARG;
+    e->tok_off.assign(offsets, offsets + V + 1);
+    e->tok_bytes.assign(bytes, bytes + offsets[V]);
+    e->finalized = false;
+    return AVA_OK;
+}
+
 int ava_engine_set_q8(ava_engine* e, const char* name, const int8_t* q, const float* scale, int32_t din, int32_t dout) {
     if (!e || !name || !q || !scale) return AVA_ERR_ARG;
     int wi, wo;
@@ -1200,6 +1220,47 @@ int ava_engine_finalize(ava_engine* e) {
         if ((rc = upload_f32(e, e->th_read, "th.read", true))) return rc;
         if ((rc = upload_f32(e, e->th_gate, "th.gate", true))) return rc;
         if ((rc = upload_f32(e, e->th_bias, "th.bias", true))) return rc;
+    }
+    if (c.letters) {
+        // R (src/model/fstep/arch_f2.rs:34-60, src/v51.rs:449-469): a token's share of its input depends on the token alone,
+        // so the whole table is built here, once, with the arithmetic the kernels share with the host: per token
+        // l = (0 + m_0 tanh((E[b_0] + Q[e_0]) + P[0]) + ... over 16 places) * inv, b the bytes of its spelling, e their
+        // places counted from the end, m = 1 for a place in use, inv = 1 / sqrt(places in use); then l Wo in the one-row
+        // order (Wo[0] l_0, then one fused multiply-add per further input)
+        if (e->tok_off.size() != (size_t)c.vocab + 1) return e->fail(AVA_ERR_MISSING, "--letters: the tokens' spellings are not set (ava_engine_set_token_bytes)");
+        const char* names[4] = {"v51.letters.byte", "v51.letters.pos", "v51.letters.end", "v51.letters.wo"};
+        const std::vector<float>* w[4];
+        for (int q = 0; q < 4; ++q) {
+            auto it = e->host_f32.find(names[q]);
+            if (it == e->host_f32.end()) return e->fail(AVA_ERR_MISSING, "missing tensor %s", names[q]);
+            w[q] = &it->second;
+        }
+        const float *E = w[0]->data(), *P = w[1]->data(), *Q = w[2]->data(), *Wo = w[3]->data();
+        constexpr int DL = 64, LM = 16;
+        const int d = c.d;
+        std::vector<float> table((size_t)c.vocab * d);
+        for (int t = 0; t < c.vocab; ++t) {
+            const int64_t len = e->tok_off[t + 1] - e->tok_off[t];
+            const int used = (int)std::min<int64_t>(len, LM);
+            const float inv = used > 0 ? ava::div(1.0f, ava::root((float)used)) : 0.0f;
+            float l[DL];
+            for (int cc = 0; cc < DL; ++cc) l[cc] = 0.0f;
+            for (int j = 0; j < LM; ++j) {
+                const int b = j < used ? e->tok_bytes[e->tok_off[t] + j] : 0;
+                const int k = j < used ? (int)std::min<int64_t>(len - 1 - j, LM - 1) : 0;
+                const float m = j < used ? 1.0f : 0.0f;
+                for (int cc = 0; cc < DL; ++cc) {
+                    const float sv = ava::tanhf_(ava::add(ava::add(E[b * DL + cc], Q[k * DL + cc]), P[j * DL + cc]));
+                    l[cc] = ava::add(l[cc], ava::mul(sv, m));
+                }
+            }
+            for (int cc = 0; cc < DL; ++cc) l[cc] = ava::mul(l[cc], inv);
+            float* out = &table[(size_t)t * d];
+            for (int cc = 0; cc < d; ++cc) out[cc] = ava::mul(Wo[cc], l[0]);
+            for (int j = 1; j < DL; ++j)
+                for (int cc = 0; cc < d; ++cc) out[cc] = ava::fma(Wo[(size_t)j * d + cc], l[j], out[cc]);
+        }
+        if ((rc = upload(e, e->letters, table.data(), table.size() * sizeof(float)))) return rc;
     }
     if (c.cb_units > 0) {
         if ((rc = upload_f32(e, e->cb_w, "cbh.wo", true))) return rc;

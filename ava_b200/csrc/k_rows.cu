@@ -116,8 +116,9 @@ __device__ __forceinline__ float gemv_col(const float* x, int k, const float* __
 __device__ __forceinline__ bool finite_f(float v) { return (f_to_bits(v) & 0x7f800000u) != 0x7f800000u; }
 
 // ---------------------------------------------------------------------------------------------------- embedding
+// letters: --letters' table [vocab][d] or nullptr; a token's row of it is added to its embedding
 __global__ void embed_kernel(const float* __restrict__ tok_emb, const uint32_t* __restrict__ tok, int M, int d, int vocab, float* x, float* stream0,
-                             uint32_t* status) {
+                             uint32_t* status, const float* __restrict__ letters) {
     pdl_enter();
     const int r = blockIdx.x;
     uint32_t t = tok[r];
@@ -128,8 +129,13 @@ __global__ void embed_kernel(const float* __restrict__ tok_emb, const uint32_t* 
     const float4* src = reinterpret_cast<const float4*>(tok_emb + (size_t)t * d);
     float4* dst = reinterpret_cast<float4*>(x + (size_t)r * d);
     float4* dst2 = stream0 ? reinterpret_cast<float4*>(stream0 + (size_t)r * d) : nullptr;
+    const float4* let = letters ? reinterpret_cast<const float4*>(letters + (size_t)t * d) : nullptr;
     for (int i = threadIdx.x; i < d / 4; i += blockDim.x) {
-        const float4 v = src[i];
+        float4 v = src[i];
+        if (let) {
+            const float4 o = let[i];
+            v = make_float4(add(v.x, o.x), add(v.y, o.y), add(v.z, o.z), add(v.w, o.w));
+        }
         dst[i] = v;
         if (dst2) dst2[i] = v;
     }
@@ -724,8 +730,9 @@ void opt_in_smem(K kernel, size_t bytes) {
 
 }  // namespace
 
-void launch_embed(cudaStream_t st, const float* tok_emb, const uint32_t* tok, int M, int d, int vocab, float* x, float* stream0, uint32_t* status) {
-    launch_k(embed_kernel, dim3(M), dim3(128), 0, st, tok_emb, tok, M, d, vocab, x, stream0, status);
+void launch_embed(cudaStream_t st, const float* tok_emb, const uint32_t* tok, int M, int d, int vocab, float* x, float* stream0, uint32_t* status,
+                  const float* letters) {
+    launch_k(embed_kernel, dim3(M), dim3(128), 0, st, tok_emb, tok, M, d, vocab, x, stream0, status, letters);
 }
 
 void launch_rmsnorm(cudaStream_t st, const float* x, const float* gain, int M, int n, float* y, uint16_t* limbs) {

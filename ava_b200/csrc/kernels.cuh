@@ -107,7 +107,8 @@ void launch_split3(cudaStream_t st, const float* x, int64_t n, uint16_t* out);
 void launch_widen_transpose(cudaStream_t st, const int8_t* q, int K, int N, uint16_t* out);
 
 // ---- row kernels ----------------------------------------------------------------------------------------------
-void launch_embed(cudaStream_t st, const float* tok_emb, const uint32_t* tok, int M, int d, int vocab, float* x, float* stream0, uint32_t* status);
+void launch_embed(cudaStream_t st, const float* tok_emb, const uint32_t* tok, int M, int d, int vocab, float* x, float* stream0, uint32_t* status,
+                  const float* letters = nullptr);
 // limbs (may be null): also the three bf16 limbs of y, planes [3][M * n], for launch_tc_gemm
 void launch_rmsnorm(cudaStream_t st, const float* x, const float* gain, int M, int n, float* y, uint16_t* limbs = nullptr);
 void launch_lif(cudaStream_t st, const float* cur, const LifParams& p, int M, int d);

@@ -58,6 +58,7 @@ def lib() -> C.CDLL:
         "ava_engine_destroy": ([vp], None),
         "ava_last_error": ([vp], C.c_char_p),
         "ava_engine_set_f32": ([vp, C.c_char_p, fp, C.c_int64], C.c_int),
+        "ava_engine_set_token_bytes": ([vp, C.POINTER(C.c_uint8), C.POINTER(C.c_int64)], C.c_int),
         "ava_engine_set_q8": ([vp, C.c_char_p, i8p, fp, C.c_int32, C.c_int32], C.c_int),
         "ava_engine_set_q8_from_f32": ([vp, C.c_char_p, fp, C.c_int32, C.c_int32], C.c_int),
         "ava_engine_finalize": ([vp], C.c_int),
@@ -147,7 +148,7 @@ def lib() -> C.CDLL:
     return L
 
 
-EXPORTS = ("ava_engine_create ava_engine_destroy ava_last_error ava_engine_set_f32 ava_engine_set_q8 "
+EXPORTS = ("ava_engine_create ava_engine_destroy ava_last_error ava_engine_set_f32 ava_engine_set_token_bytes ava_engine_set_q8 "
            "ava_engine_set_q8_from_f32 ava_engine_finalize ava_engine_blocker ava_state_new ava_state_destroy "
            "ava_state_rows ava_state_select ava_state_cat ava_state_seen ava_state_len ava_state_export "
            "ava_state_import ava_step ava_step_greedy ava_forward_with_state ava_step_device ava_prefill_device ava_state_set_kv_shard ava_shard_parts ava_split_step_begin ava_shard_partial ava_split_step_end ava_sync "
@@ -319,7 +320,9 @@ class Model:
         """weights: name -> f32 array, or (int8 [din, dout], f32 scale [dout]); then `set_int8` + `set_fused`."""
         L = lib()
         for name, w in weights.items():
-            if isinstance(w, tuple):
+            if name == "token_bytes":   # --letters: the tokens' spellings (data u8, offsets i64 [vocab + 1])
+                self.set_token_bytes(*w)
+            elif isinstance(w, tuple):
                 q = np.ascontiguousarray(w[0], np.int8)
                 sc = _f32(w[1])
                 self._check(L.ava_engine_set_q8(self.h, name.encode(), _p(q, i8p), _p(sc), q.shape[0], q.shape[1]))
@@ -328,8 +331,16 @@ class Model:
                 self._check(L.ava_engine_set_f32(self.h, name.encode(), _p(a), a.size))
         self._check(L.ava_engine_finalize(self.h))
 
+    def set_token_bytes(self, data, offsets):
+        """--letters: every token's spelling, data[offsets[t]:offsets[t + 1]] (the reference reads its tokenizer's file)."""
+        data = np.ascontiguousarray(data, np.uint8)
+        offsets = np.ascontiguousarray(offsets, np.int64)
+        if offsets.size != self.cfg["vocab"] + 1:
+            raise ValueError("offsets: vocab + 1 values")
+        self._check(lib().ava_engine_set_token_bytes(self.h, data.ctypes.data_as(C.POINTER(C.c_uint8)), offsets.ctypes.data_as(C.POINTER(C.c_int64))))
+
     @classmethod
-    def from_checkpoint(cls, path: str, kind: str, flags: str | None = None, device: int = 0, **overrides) -> "Model":
+    def from_checkpoint(cls, path: str, kind: str, flags: str | None = None, device: int = 0, token_bytes=None, **overrides) -> "Model":
         """`ckpt::load_auto` + `set_int8` + `set_fused`: the model a .safetensors file holds (`flags`: the arch.txt line
         beside it).  overrides: configuration fields the file does not fix (eng_cap, eng_store_bf16, ...)."""
         ck = Checkpoint(path)
@@ -337,6 +348,8 @@ class Model:
             cfg = ck.config(kind, flags)
             cfg.update(overrides)
             m = cls(cfg, None, device)
+            if token_bytes is not None:
+                m.set_token_bytes(*token_bytes)
             rc = lib().ava_engine_load_ckpt(m.h, ck.h)
             if rc != OK:
                 _loader_check(rc)

@@ -122,6 +122,19 @@ def model(cfg: dict, seed: int = 0, recipe: str = "bench", unit_gain: bool = Tru
         w["v51.mood.lam"] = g.n("v51.mood.lam", (k,), 1.0) + 2.0
         w["v51.mood.win"] = (1.0 + g.n("v51.mood.win", (k,), 0.3)).astype(np.float32)
         w["v51.mood.bin"] = g.n("v51.mood.bin", (k,), 0.1) if awake else np.zeros(k, np.float32)
+    if cfg.get("letters"):
+        # spellings of 0 to 20 bytes (longer than the 16 places the part reads, and one empty), seeded
+        rng = np.random.default_rng(seed * 7919 + 17)
+        lens = rng.integers(1, 21, size=V)
+        lens[min(3, V - 1)] = 0
+        off = np.zeros(V + 1, np.int64)
+        off[1:] = np.cumsum(lens)
+        w["token_bytes"] = (rng.integers(0, 256, size=int(off[-1]), dtype=np.uint8), off)
+        s3 = 1.0 / math.sqrt(3.0)
+        w["v51.letters.byte"] = g.n("v51.letters.byte", (256, 64), s3)
+        w["v51.letters.pos"] = g.n("v51.letters.pos", (16, 64), s3)
+        w["v51.letters.end"] = g.n("v51.letters.end", (16, 64), s3)
+        w["v51.letters.wo"] = g.n("v51.letters.wo", (64, d), 0.02) if awake else np.zeros((64, d), np.float32)
     if cfg.get("cb_units"):
         w["cbh.wo"] = g.n("cbh.wo", (cfg["cb_units"], d), 0.05) if awake else np.zeros((cfg["cb_units"], d), np.float32)
     if cfg.get("thalamus"):

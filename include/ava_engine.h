@@ -80,6 +80,10 @@ typedef struct ava_config {
                                reference's seed), the top G/32 are kept, rectified and brought to unit length, and their rows of
                                cbh.wo [G, d], summed in unit order, are added to the final normed state before the head
                                (src/model/fstep/arch_f3.rs:207-283, src/v51b.rs:241-266,327-360) */
+    int32_t letters;        /* --letters: a token's input also takes l Wo, l the mean-like sum over up to 16 of its bytes of
+                               tanh(byte[b] + end[place from the end] + pos[place]) / sqrt(bytes used) (64 wide; src/v51.rs:492-501,
+                               src/model/fstep/arch_f2.rs:34-60); weights v51.letters.byte [256, 64] / .pos [16, 64] / .end [16, 64] /
+                               .wo [64, d] and the tokens' spellings (ava_engine_set_token_bytes) */
     float   mem_momentum;   /* --mem-momentum (0: off) */
     float   slope;          /* --surrogate-slope (does not change forward values) */
 } ava_config;
@@ -100,6 +104,10 @@ const char* ava_last_error(const ava_engine* e);
  * [d, heads], "b{i}.hebb.{ba,bb}" [heads], "b{i}.hebb.{wa1,wb1}" [d, rank], "b{i}.hebb.{wa2,wb2}" [rank, d],
  * "b{i}.hebb.vres" [2], "b{i}.eng.norm", "b{i}.mlp.norm" [d], "b{i}.dense" [i + 2].  `n` = number of floats. */
 int ava_engine_set_f32(ava_engine* e, const char* name, const float* data, int64_t n);
+/* --letters: the spelling of every token, bytes[offsets[t] .. offsets[t + 1]) for t in 0 .. vocab - 1 (offsets[0] = 0; vocab + 1
+ * offsets).  The reference reads them from its tokenizer's merge file (src/v51.rs:449-469, `set_letters_from_bpe`); here the
+ * host that owns the tokenizer passes them in, before ava_engine_finalize. */
+int ava_engine_set_token_bytes(ava_engine* e, const uint8_t* bytes, const int64_t* offsets);
 /* An int8 matrix W [din, dout] row-major (applied x . W) with one f32 scale per output column — the product of
  * `Model::set_int8` (src/model.rs:949-991) given directly: "b{i}.mem.{win,wout}", "b{i}.hebb.{wq,wk,wv,we,wg,wo}",
  * "b{i}.eng.{wq,wk,wv,wo}", "b{i}.mlp.{w1,w2}", "head" [d, vocab]. */

@@ -528,6 +528,10 @@ struct orc_model {
     std::vector<float> tok_emb, final_norm;
     std::vector<float> nm_norm, nm_wn, nm_bn;  // --neuromod: the nucleus (gain [d], read-out [d, k], bias [k])
     std::vector<float> mood_lam, mood_win, mood_bin;  // --mood: decay, input weight and bias [k]
+    // --letters (src/v51.rs:449-482): per token 16 byte ids, their places counted from the end, a mask and 1 / sqrt(used);
+    // byte [256, 64], pos [16, 64], end [16, 64] embeddings and the read-out [64, d]
+    std::vector<uint32_t> let_ids, let_eidx;
+    std::vector<float> let_mask, let_inv, let_byte, let_pos, let_end, let_wo;
     std::vector<float> cb_w;     // --cerebellum-head: the read-out [G, d]
     std::vector<uint32_t> cb_idx;  // its fixed wiring: 4 inputs of [xf, rmsnorm(emb)] per unit, weights +-1/2
     std::vector<float> cb_sgn;
@@ -566,6 +570,10 @@ std::vector<float>* f32_slot(orc_model* m, const std::string& name, int64_t* wan
     if (name == "v51.mood.lam") { *want = c.mood; return &m->mood_lam; }
     if (name == "v51.mood.win") { *want = c.mood; return &m->mood_win; }
     if (name == "v51.mood.bin") { *want = c.mood; return &m->mood_bin; }
+    if (name == "v51.letters.byte") { *want = 256 * 64; return &m->let_byte; }
+    if (name == "v51.letters.pos") { *want = 16 * 64; return &m->let_pos; }
+    if (name == "v51.letters.end") { *want = 16 * 64; return &m->let_end; }
+    if (name == "v51.letters.wo") { *want = (int64_t)64 * d; return &m->let_wo; }
     if (name == "cbh.wo") { *want = (int64_t)c.cb_units * d; return &m->cb_w; }
     if (name == "th.read") { *want = (int64_t)c.n_blocks * d * 16; return &m->th_read; }
     if (name == "th.gate") { *want = (int64_t)c.n_blocks * 16 * 2; return &m->th_gate; }
@@ -708,6 +716,25 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
     std::vector<float> x((size_t)R * d), h((size_t)R * d), tmp((size_t)R * d);
     for (int r = 0; r < R; ++r) std::copy(m->tok_emb.begin() + (size_t)tok[r] * d, m->tok_emb.begin() + (size_t)(tok[r] + 1) * d, x.begin() + (size_t)r * d);
     T("x_in", -1, x.data(), d);
+    if (cfg.letters) {
+        // R (fstep/arch_f2.rs:34-60): l = (0 + m_0 tanh((E[b_0] + Q[e_0]) + P[0]) + ...) inv, then l Wo in the one-row order
+        const int DL = 64, LM = 16;
+        for (int r = 0; r < R; ++r) {
+            const size_t t = tok[r];
+            std::vector<float> l(DL, 0.f), o(d);
+            for (int j = 0; j < LM; ++j) {
+                const uint32_t bb = m->let_ids[t * LM + j], kk = m->let_eidx[t * LM + j];
+                for (int c = 0; c < DL; ++c) {
+                    const float s = tanh_f((m->let_byte[(size_t)bb * DL + c] + m->let_end[(size_t)kk * DL + c]) + m->let_pos[(size_t)j * DL + c]);
+                    l[c] += s * m->let_mask[t * LM + j];
+                }
+            }
+            for (int c = 0; c < DL; ++c) l[c] *= m->let_inv[t];
+            gemv(l.data(), DL, m->let_wo.data(), d, o.data());
+            add_into(&x[(size_t)r * d], o.data(), d);
+        }
+        T("x_let", -1, x.data(), d);
+    }
     std::vector<std::vector<float>> streams;
     if (cfg.dense) streams.push_back(x);
     std::vector<float> v_first;
@@ -1203,6 +1230,26 @@ void orc_stp(const float* s, const float* u_param, const float* f_param, const f
     }
     stp_step(s, U.data(), F.data(), D.data(), mix, u0, x0, d, out, u1, x1, eff);
 }
+int orc_model_set_token_bytes(orc_model* m, const uint8_t* bytes, const int64_t* offsets) {
+    // src/v51.rs:455-469
+    const int V = m->cfg.vocab, LM = 16;
+    m->let_ids.assign((size_t)V * LM, 0);
+    m->let_eidx.assign((size_t)V * LM, 0);
+    m->let_mask.assign((size_t)V * LM, 0.f);
+    m->let_inv.assign(V, 0.f);
+    for (int t = 0; t < V; ++t) {
+        const int64_t len = offsets[t + 1] - offsets[t];
+        if (len < 0) return -1;
+        const int used = (int)std::min<int64_t>(len, LM);
+        for (int j = 0; j < used; ++j) {
+            m->let_ids[(size_t)t * LM + j] = bytes[offsets[t] + j];
+            m->let_eidx[(size_t)t * LM + j] = (uint32_t)std::min<int64_t>(len - 1 - j, LM - 1);
+            m->let_mask[(size_t)t * LM + j] = 1.0f;
+        }
+        if (used > 0) m->let_inv[t] = 1.0f / std::sqrt((float)used);
+    }
+    return 0;
+}
 void orc_cb_wiring(int inputs, int g, uint32_t* idx, float* w) {
     std::vector<uint32_t> i;
     std::vector<float> s;
@@ -1265,6 +1312,8 @@ int orc_model_check(orc_model* m, char* missing, int cap) {
     if (c.neuromod > 0 && (m->nm_norm.empty() || m->nm_wn.empty() || m->nm_bn.empty())) return fail("nm.norm / nm.wn / nm.bn");
     if (c.mood > 0 && (m->mood_lam.empty() || m->mood_win.empty() || m->mood_bin.empty())) return fail("v51.mood.lam / win / bin");
     if (c.cb_units > 0 && m->cb_w.empty()) return fail("cbh.wo");
+    if (c.letters && (m->let_byte.empty() || m->let_pos.empty() || m->let_end.empty() || m->let_wo.empty())) return fail("v51.letters.byte / pos / end / wo");
+    if (c.letters && m->let_ids.empty()) return fail("the tokens' spellings (orc_model_set_token_bytes)");
     if (c.thalamus && (m->th_read.empty() || m->th_gate.empty() || m->th_bias.empty())) return fail("th.read / th.gate / th.bias");
     if (!m->head.ok()) return fail("head");
     for (int i = 0; i < c.n_blocks; ++i) {

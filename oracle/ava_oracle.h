@@ -64,6 +64,7 @@ typedef struct orc_config {
     int32_t dopamine;       /* --dopamine: the surprise at this token scales the later blocks' MLP output (fstep/arch_f4.rs:131-143) */
     int32_t mood;           /* --mood (4 units): a slow trace of the surprise scales the later blocks' LIF current (fstep/arch_f3.rs:106-186) */
     int32_t cb_units;       /* --cerebellum-head G: G sparse granule units correct the final normed state (fstep/arch_f3.rs:207-283) */
+    int32_t letters;        /* --letters: each token's spelling adds a vector to its input (fstep/arch_f2.rs:34-60) */
     int32_t thalamus;       /* --thalamus: a relay reads the stream and gates each block's memory read and residual (fstep/arch_f2.rs:62-153) */
     float   mem_momentum;   /* 0: off */
     float   slope;          /* surrogate slope (forward value cancels; kept for the literal op order) */
@@ -126,6 +127,8 @@ typedef struct orc_state orc_state;
 orc_model* orc_model_new(const orc_config* cfg);
 void orc_model_free(orc_model* m);
 /* f32 tensor by its reference name ("tok_emb", "b3.mem.beta", "final.norm", ...). Returns 0, or -1 (unknown / size). */
+/* --letters: the spelling of every token, bytes[offsets[t] .. offsets[t + 1]) for t in 0 .. vocab - 1 */
+int orc_model_set_token_bytes(orc_model* m, const uint8_t* bytes, const int64_t* offsets);
 int orc_model_set_f32(orc_model* m, const char* name, const float* data, int64_t n);
 /* an int8 matrix [din, dout] with its per-output scales, by name ("b3.hebb.wq", "head"). */
 int orc_model_set_q8(orc_model* m, const char* name, const int8_t* q, const float* scale, int din, int dout);

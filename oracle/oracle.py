@@ -21,7 +21,7 @@ class OrcConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "vocab", "d", "n_blocks", "hidden", "kwta_k", "head_size", "eng_block", "eng_head_size", "eng_store_bf16",
         "eng_cap", "gate_rank", "spikes", "alif", "theta", "lif_scale", "value_residual", "relu2", "dense",
-        "out_gate", "fast_mem", "dendrite", "neuromod", "stp", "dopamine", "mood", "cb_units", "thalamus")] + [("mem_momentum", C.c_float), ("slope", C.c_float)]
+        "out_gate", "fast_mem", "dendrite", "neuromod", "stp", "dopamine", "mood", "cb_units", "letters", "thalamus")] + [("mem_momentum", C.c_float), ("slope", C.c_float)]
 
 
 def build(force: bool = False) -> str:
@@ -65,6 +65,8 @@ def lib() -> C.CDLL:
     L.orc_gemv.argtypes = [fp, C.c_int, fp, C.c_int, fp]
     L.orc_stp.argtypes = [fp] * 7 + [C.c_int] + [fp] * 4
     L.orc_stp.restype = None
+    L.orc_model_set_token_bytes.argtypes = [C.c_void_p, C.POINTER(C.c_uint8), C.POINTER(C.c_int64)]
+    L.orc_model_set_token_bytes.restype = C.c_int
     L.orc_cb_wiring.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_uint32), fp]
     L.orc_cb_wiring.restype = None
     L.orc_lif.argtypes = [fp, fp, fp, fp, fp, C.c_int, C.c_float, fp, fp, fp, C.c_int, fp, fp, fp]
@@ -278,7 +280,10 @@ class OracleModel:
         """weights: name -> f32 array, or name -> (int8 [din, dout], f32 scale [dout])."""
         L = lib()
         for name, w in weights.items():
-            if isinstance(w, tuple):
+            if name == "token_bytes":
+                data, off = np.ascontiguousarray(w[0], np.uint8), np.ascontiguousarray(w[1], np.int64)
+                rc = L.orc_model_set_token_bytes(self.h, data.ctypes.data_as(C.POINTER(C.c_uint8)), off.ctypes.data_as(C.POINTER(C.c_int64)))
+            elif isinstance(w, tuple):
                 q, sc = w
                 q = np.ascontiguousarray(q, np.int8)
                 sc = np.ascontiguousarray(sc, np.float32)

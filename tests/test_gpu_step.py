@@ -64,8 +64,9 @@ CONFIGS = {
     "dopamine": dict(dopamine=1, neuromod=3, head_size=64),                              # --dopamine: the surprise scales the MLP's output, before DA
     "mood": dict(mood=4, neuromod=3, head_size=64),                                      # --mood: the surprise's slow trace scales the current, after NE
     "six_parts": dict(stp=1, neuromod=3, dendrite=1, dopamine=1, mood=4, thalamus=1, head_size=64, mem_momentum=0.5),
+    "letters": dict(letters=1, thalamus=1, head_size=64),                                # --letters: the token's spelling in its input (the relay reads it)
     "cerebellum": dict(cb_units=512, head_size=64),                                      # --cerebellum-head: the correction before the head
-    "all_parts": dict(stp=1, neuromod=3, dendrite=1, dopamine=1, mood=4, thalamus=1, cb_units=1024, head_size=64, mem_momentum=0.5),
+    "all_parts": dict(stp=1, neuromod=3, dendrite=1, dopamine=1, mood=4, thalamus=1, cb_units=1024, letters=1, head_size=64, mem_momentum=0.5),
     "thalamus_alone": dict(thalamus=1, head_size=64),                                    # its gates on the fused W_o epilogue
     # the reference's kind S (Ava-M's): spiking memory + sparse MLP only, binary spikes, relu
     "kind_s": dict(head_size=128, eng_block=-1, spikes=0, alif=0, theta=0, lif_scale=0, value_residual=0, relu2=0, dense=0, out_gate=0,
@@ -146,7 +147,7 @@ def test_forward_with_state_equals_steps(orc_same_math):
     assert np.array_equal(bits(tail), bits(want[:, 6:]))
 
 
-@pytest.mark.parametrize("name", ["ava04_small", "one_head_bf16", "binary_plain", "momentum", "kind_s", "stp", "dendrite", "neuromod", "thalamus", "thalamus_alone", "dopamine", "mood", "six_parts", "cerebellum", "all_parts"])
+@pytest.mark.parametrize("name", ["ava04_small", "one_head_bf16", "binary_plain", "momentum", "kind_s", "stp", "dendrite", "neuromod", "thalamus", "thalamus_alone", "dopamine", "mood", "six_parts", "cerebellum", "letters", "all_parts"])
 @pytest.mark.parametrize("chunk", [1, 5, 64])
 def test_chunked_prompt_equals_steps(orc_same_math, name, chunk):
     """Reading a prompt in chunks (token-parallel products, the recurrences in order inside their kernels) gives the

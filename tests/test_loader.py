@@ -70,8 +70,9 @@ def test_arch_flag_words():
     assert engine.arch_flags(AVA04_FLAGS + " --cerebellum-head 12288", base)["cb_units"] == 12288
     with pytest.raises(engine.EngineError, match="multiple of 32"):
         engine.arch_flags(AVA04_FLAGS + " --cerebellum-head 100", base)
-    with pytest.raises(engine.NotApplicable, match="--letters"):
-        engine.arch_flags(AVA04_FLAGS + " --stp --neuromod 3 --dendrite --letters --dopamine --thalamus", base)
+    assert engine.arch_flags(AVA04_FLAGS + " --letters", base)["letters"] == 1
+    with pytest.raises(engine.NotApplicable, match="--rhythm"):
+        engine.arch_flags(AVA04_FLAGS + " --stp --neuromod 3 --dendrite --letters --dopamine --rhythm --thalamus", base)
     with pytest.raises(engine.NotApplicable, match="gates"):
         engine.arch_flags("--head-size 64", base)
     with pytest.raises(engine.NotApplicable, match="sigmoid"):

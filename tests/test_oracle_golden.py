@@ -465,12 +465,12 @@ def test_new_parts_start_as_no_change(orc):
     same bits."""
     from ava_b200 import config, synth
     base = config.tiny(head_size=64)
-    full = config.tiny(head_size=64, stp=1, dendrite=1, neuromod=3, thalamus=1, dopamine=1, mood=4, cb_units=512)
+    full = config.tiny(head_size=64, stp=1, dendrite=1, neuromod=3, thalamus=1, dopamine=1, mood=4, cb_units=512, letters=1)
     w0 = synth.model(base, 3, "awake")
     w1 = synth.model(full, 3, "awake")
     for k in w1:
         if k.endswith("parts.stp.mix") or k.endswith("v51.dend_b") or k.endswith("v51.da_w") or k.endswith("v51.da_c") or k.endswith("v51.mood_g") \
-                or k in ("nm.wn", "nm.bn", "th.gate", "th.bias", "cbh.wo"):  # nucleus and relay then send 2 sigmoid(0) = 1
+                or k in ("nm.wn", "nm.bn", "th.gate", "th.bias", "cbh.wo", "v51.letters.wo"):  # nucleus and relay then send 2 sigmoid(0) = 1
             w1[k] = np.zeros_like(w1[k])
     m0, m1 = orc.OracleModel(base, w0), orc.OracleModel(full, w1)
     s0, s1 = m0.state(2), m1.state(2)
@@ -581,5 +581,32 @@ def test_cerebellum_wiring_and_correction(orc):
             want = xf + code @ wts["cbh.wo"].astype(np.float64)
             assert np.allclose(got, want, rtol=0, atol=2e-5), t
             assert np.abs(got - xf).max() > 1e-3
+    finally:
+        orc.trace_enable(False)
+
+
+def test_letters_follow_their_formula(orc):
+    """--letters (src/v51.rs:455-469,492-501): a token's input is its embedding plus l Wo with
+    l = sum over its first 16 bytes of tanh(byte[b] + end[min(len - 1 - j, 15)] + pos[j]) / sqrt(min(len, 16));
+    a token without bytes adds nothing.  Checked in f64 against the oracle's trace of the input."""
+    from ava_b200 import config, synth
+    cfg = config.tiny(head_size=64, letters=1)
+    w = synth.model(cfg, 2, "awake")
+    data, off = w["token_bytes"]
+    st = orc.OracleModel(cfg, w).state(1)
+    E, P, Q, Wo = (w["v51.letters." + k].astype(np.float64) for k in ("byte", "pos", "end", "wo"))
+    orc.trace_enable(True)
+    try:
+        for tok in (0, 3, 7, int(np.argmax(np.diff(off)))):   # token 3 has no bytes; the last is a longest one
+            st.step(np.array([tok], np.uint32))
+            b = data[off[tok]:off[tok + 1]]
+            used = min(len(b), 16)
+            l = np.zeros(64)
+            for j in range(used):
+                l += np.tanh(E[b[j]] + Q[min(len(b) - 1 - j, 15)] + P[j])
+            want = w["tok_emb"][tok].astype(np.float64) + (l / np.sqrt(used) if used else l) @ Wo
+            got = orc.trace("x_let", -1)[: cfg["d"]]
+            assert np.allclose(got, want, rtol=0, atol=1e-5), tok
+            assert (np.abs(got - w["tok_emb"][tok]).max() > 1e-4) == (used > 0)
     finally:
         orc.trace_enable(False)
