@@ -79,6 +79,8 @@ def flags_of(cfg: dict) -> str:
         f.append("--thalamus")
     if cfg.get("cb_units"):
         f.append(f"--cerebellum-head {cfg['cb_units']}")
+    if cfg.get("rhythm"):
+        f.append("--rhythm")
     if cfg.get("letters"):
         f.append("--letters")
     if cfg.get("dopamine"):

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 FIELDS_I32 = ("vocab", "d", "n_blocks", "hidden", "kwta_k", "head_size", "eng_block", "eng_head_size",
               "eng_store_bf16", "eng_cap", "gate_rank", "spikes", "alif", "theta", "lif_scale", "value_residual",
-              "relu2", "dense", "out_gate", "fast_mem", "dendrite", "neuromod", "stp", "thalamus", "dopamine", "mood", "cb_units", "letters")
+              "relu2", "dense", "out_gate", "fast_mem", "dendrite", "neuromod", "stp", "thalamus", "dopamine", "mood", "cb_units", "letters", "rhythm")
 FIELDS_F32 = ("mem_momentum", "slope")
 
 SPIKES_BINARY, SPIKES_TERNARY, SPIKES_INT2 = 0, 1, 2
@@ -16,13 +16,13 @@ SPIKES_BINARY, SPIKES_TERNARY, SPIKES_INT2 = 0, 1, 2
 
 def make(vocab, d, n_blocks, *, hidden=None, kwta_k=None, head_size=64, eng_block=-1, eng_head_size=32,
          eng_store_bf16=0, eng_cap=0, gate_rank=32, spikes=SPIKES_INT2, alif=1, theta=1, lif_scale=1,
-         value_residual=1, relu2=1, dense=1, out_gate=1, fast_mem=1, dendrite=0, neuromod=0, stp=0, thalamus=0, dopamine=0, mood=0, cb_units=0, letters=0, mem_momentum=0.0, slope=4.0) -> dict:
+         value_residual=1, relu2=1, dense=1, out_gate=1, fast_mem=1, dendrite=0, neuromod=0, stp=0, thalamus=0, dopamine=0, mood=0, cb_units=0, letters=0, rhythm=0, mem_momentum=0.0, slope=4.0) -> dict:
     hidden = 4 * d if hidden is None else hidden
     kwta_k = hidden // 4 if kwta_k is None else kwta_k
     cfg = dict(vocab=vocab, d=d, n_blocks=n_blocks, hidden=hidden, kwta_k=kwta_k, head_size=head_size,
                eng_block=eng_block, eng_head_size=eng_head_size, eng_store_bf16=eng_store_bf16, eng_cap=eng_cap,
                gate_rank=gate_rank, spikes=spikes, alif=alif, theta=theta, lif_scale=lif_scale,
-               value_residual=value_residual, relu2=relu2, dense=dense, out_gate=out_gate, fast_mem=fast_mem, dendrite=dendrite, neuromod=neuromod, stp=stp, thalamus=thalamus, dopamine=dopamine, mood=mood, cb_units=cb_units, letters=letters,
+               value_residual=value_residual, relu2=relu2, dense=dense, out_gate=out_gate, fast_mem=fast_mem, dendrite=dendrite, neuromod=neuromod, stp=stp, thalamus=thalamus, dopamine=dopamine, mood=mood, cb_units=cb_units, letters=letters, rhythm=rhythm,
                mem_momentum=float(mem_momentum), slope=float(slope))
     assert d % head_size == 0
     assert eng_block < n_blocks

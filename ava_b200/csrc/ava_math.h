@@ -183,3 +183,90 @@ AVA_HD uint16_t f_to_bf16(float x) {
 AVA_HD float bf16_to_f(uint16_t h) { return bits_to_f((uint32_t)h << 16); }
 
 }  // namespace ava
+
+namespace ava {
+
+// sine and cosine of a float, computed in IEEE double operations only (multiply, add, fused multiply-add, round to
+// integer) and rounded to float once at the end, so that host and device give the same bits.  --rhythm's phases are
+// the one place the step needs them (design-tests/nn/gpu/src/model/fstep/arch_f4.rs:84-89, where the reference calls
+// the platform's cosf / sinf).  The argument is reduced by the nearest multiple n of pi/2, pi/2 split into three parts
+// whose first two have 33 significant bits (n * part is exact for |n| < 2^20, i.e. |x| below about 1.6e6; beyond that
+// the reduction loses accuracy gradually, still the same on both sides); on |r| <= pi/4 the Taylor series to r^19 and
+// r^18 (the next terms are below 1e-19).
+AVA_HD double dmul(double a, double b) {
+#if defined(__CUDA_ARCH__)
+    return __dmul_rn(a, b);
+#else
+    return a * b;
+#endif
+}
+AVA_HD double dadd(double a, double b) {
+#if defined(__CUDA_ARCH__)
+    return __dadd_rn(a, b);
+#else
+    return a + b;
+#endif
+}
+AVA_HD double dfma(double a, double b, double c) {
+#if defined(__CUDA_ARCH__)
+    return __fma_rn(a, b, c);
+#else
+    return ::fma(a, b, c);
+#endif
+}
+
+// quadrant (n mod 4) and sin(r), cos(r) of the reduced argument
+AVA_HD void sincos_parts(float xf, int* quad, double* s, double* c) {
+    const double x = (double)xf;
+    const double n = rint(dmul(x, 0.63661977236758134308));  // 2 / pi
+    // pi/2 = P1 + P2 + P3 (+ ...), P1 and P2 with 33 significant bits
+    const double P1 = 1.57079632673412561417, P2 = 6.07710050630396597660e-11, P3 = 2.02226624879595063154e-21;
+    double r = dfma(-n, P1, x);
+    r = dfma(-n, P2, r);
+    r = dfma(-n, P3, r);
+    const double r2 = dmul(r, r);
+    // sin r = r (1 - r2/3! + r2^2/5! - ... + r2^9/19!), cos r = 1 - r2/2! + ... + r2^9/18!, by Horner's rule
+    double ps = -1.0 / 121645100408832000.0;                  // -1/19!
+    ps = dfma(ps, r2, 1.0 / 355687428096000.0);              // 1/17!
+    ps = dfma(ps, r2, -1.0 / 1307674368000.0);               // -1/15!
+    ps = dfma(ps, r2, 1.0 / 6227020800.0);                   // 1/13!
+    ps = dfma(ps, r2, -1.0 / 39916800.0);                    // -1/11!
+    ps = dfma(ps, r2, 1.0 / 362880.0);                       // 1/9!
+    ps = dfma(ps, r2, -1.0 / 5040.0);                        // -1/7!
+    ps = dfma(ps, r2, 1.0 / 120.0);                          // 1/5!
+    ps = dfma(ps, r2, -1.0 / 6.0);                           // -1/3!
+    ps = dfma(ps, r2, 1.0);
+    double pc = -1.0 / 6402373705728000.0;                   // -1/18!
+    pc = dfma(pc, r2, 1.0 / 20922789888000.0);               // 1/16!
+    pc = dfma(pc, r2, -1.0 / 87178291200.0);                 // -1/14!
+    pc = dfma(pc, r2, 1.0 / 479001600.0);                    // 1/12!
+    pc = dfma(pc, r2, -1.0 / 3628800.0);                     // -1/10!
+    pc = dfma(pc, r2, 1.0 / 40320.0);                        // 1/8!
+    pc = dfma(pc, r2, -1.0 / 720.0);                         // -1/6!
+    pc = dfma(pc, r2, 1.0 / 24.0);                           // 1/4!
+    pc = dfma(pc, r2, -0.5);
+    pc = dfma(pc, r2, 1.0);
+    *s = dmul(r, ps);
+    *c = pc;
+    *quad = (int)((long long)n & 3);
+}
+
+AVA_HD float sinf_(float x) {
+    if (!(fabsf(x) < 3.0e38f)) return bits_to_f(0x7fc00000u);  // infinities and NaN
+    int q;
+    double s, c;
+    sincos_parts(x, &q, &s, &c);
+    const double v = q == 0 ? s : q == 1 ? c : q == 2 ? -s : -c;
+    return (float)v;
+}
+
+AVA_HD float cosf_(float x) {
+    if (!(fabsf(x) < 3.0e38f)) return bits_to_f(0x7fc00000u);
+    int q;
+    double s, c;
+    sincos_parts(x, &q, &s, &c);
+    const double v = q == 0 ? c : q == 1 ? -s : q == 2 ? -c : s;
+    return (float)v;
+}
+
+}  // namespace ava

@@ -71,6 +71,7 @@ struct BlockDev {
     Dev mem_norm, beta, theta, rho, again, hebb_norm, gate_w, ba, bb, wa2, wb2, off, vres, eng_norm, mlp_norm, dense;
     Dev stp_U, stp_F, stp_D, stp_mix;  // --stp: sigmoids of the synapse's parameters, and its mix
     Dev dend_a, dend_b;                // --dendrite: A [d][32], B [32][hidden]
+    Dev rh_w, rh_r;                    // --rhythm: the write strength's and the read's gates [4][heads]
     Dev da_w, da_c, mood_g;            // --dopamine: gate [d] twice; --mood: gain [k][d] (blocks after the first)
     QMat win, wout, proj, wo, eqkv, ewo, w1, w2;
 };
@@ -106,6 +107,7 @@ struct ava_engine {
 
     Dev tok_emb, final_norm;
     Dev nm_norm, nm_wn, nm_bn;  // --neuromod: the nucleus (gain [d], read-out padded to [d][4], bias [k])
+    Dev rhy_lw, rhy_wr, rhy_br;        // --rhythm: log frequencies [2], reset read-out padded to [d][4], bias [2]
     Dev mood_lam, mood_win, mood_bin;  // --mood: decay, input weight and bias [k]
     Dev letters;                    // --letters: every token's share of its input [vocab][d], built when the engine is finalized
     std::vector<uint8_t> tok_bytes;  // the tokens' spellings, bytes[tok_off[t] .. tok_off[t + 1])
@@ -128,6 +130,7 @@ struct ava_engine {
     Dev sur_xf, sur_in, sur_logits, sur_s, sur_z, mood_all, mood_gain, y2;
     Dev cb_emb, cb_en, cb_h, cb_a, cb_lj, cb_lc, cb_n;  // --cerebellum-head: embedding rows (raw, normed) [rows][d], units and kept units
                                                         // [rows][G], the code's list [rows][G] twice, its length [rows]
+    Dev rh_f, rh_gw, rh_gr;  // --rhythm: phase features [rows][4], the block's gains per head [rows][heads] twice
     Dev th_acc, th_g, x_in;  // --thalamus: the relay's sum [rows][16], the block's gates [rows][4], the block's input [rows][d]
     Dev ctx, dz1, ones;  // --dendrite: the block's memory read [rows][d], its projection [rows][32], a vector of ones [d]
     uint32_t* status_host = nullptr;  // pinned
@@ -174,6 +177,7 @@ struct ava_state {
     Dev mem_f;                // [L][rows][nh][hs / cw][hs][cw]: slice-major, a block of threads owns one contiguous slice
     Dev mem_s;                // the momentum matrix, same layout (only with --mem-momentum)
     Dev stp_u, stp_x;         // [L][rows][d]: the synapse's (u, x) (only with --stp; a fresh state has u = 0, x = 1)
+    Dev rh;                                   // --rhythm: the time since each clock's last reset [rows][2]
     Dev sur_prev, sur_valid, sur_last, mood;  // --dopamine / --mood: block 0's last normed output [rows][d], whether there is one
                                               // [rows], the last surprise [rows], the mood [rows][k] (all zero in a fresh state)
     Dev eng_k, eng_v;         // [rows][enh][ring][ehs]
@@ -213,6 +217,8 @@ int64_t f32_len(const ava_config& c, const std::string& name) {
     if (name == "nm.norm" && c.neuromod > 0) return d;
     if (name == "nm.wn" && c.neuromod > 0) return d * c.neuromod;
     if (name == "nm.bn" && c.neuromod > 0) return c.neuromod;
+    if (c.rhythm && (name == "v51.rhythm.lw" || name == "v51.rhythm.br")) return 2;
+    if (c.rhythm && name == "v51.rhythm.wr") return d * 2;
     if (c.mood > 0 && (name == "v51.mood.lam" || name == "v51.mood.win" || name == "v51.mood.bin")) return c.mood;
     if (c.letters) {  // LETTER_DIM 64, LETTER_MAX 16 (src/v51.rs:54-55)
         if (name == "v51.letters.byte") return 256 * 64;
@@ -232,6 +238,7 @@ int64_t f32_len(const ava_config& c, const std::string& name) {
         if (rest == n) return d;
     if ((rest == "v51.da_w" || rest == "v51.da_c") && c.dopamine && b > 0) return d;
     if (rest == "v51.mood_g" && c.mood > 0 && b > 0) return (int64_t)c.mood * d;
+    if ((rest == "v51.rh_w" || rest == "v51.rh_r") && c.rhythm && c.fast_mem) return 4 * nh;
     if (rest == "v51.dend_a") return d * 32;  // DEND_RANK (src/v51.rs:52)
     if (rest == "v51.dend_b") return (int64_t)32 * c.hidden;
     if (rest == "hebb.wa" || rest == "hebb.wb") return d * nh;
@@ -318,6 +325,7 @@ const char* find_blocker(const ava_config& c, int* cw, int* rb) {
     if (c.neuromod != 0 && (c.neuromod < 2 || c.neuromod > 4)) return "neuromod: 2 to 4 signals";
     if (c.mood < 0 || c.mood > 16) return "mood: up to 16 units";
     if (c.cb_units < 0 || c.cb_units % 32) return "cerebellum head: a multiple of 32 units";
+    if (c.rhythm && !c.fast_mem) return "rhythm: a part of the blocks with the fast-weight memory";
     if (c.thalamus && !c.fast_mem) return "thalamus: a part of the blocks with the fast-weight memory";
     if (c.fast_mem && (c.head_size % 16 || !mem_heads_tiling(c.head_size, cw, rb, c.mem_momentum > 0.0f))) return "memory head size not covered (a multiple of 16 whose column slice fits shared memory)";
     return nullptr;
@@ -370,6 +378,11 @@ int ensure_workspace(ava_engine* e, int rows, int logit_rows = 0) {
         CK(e->cb_lj.alloc(M * G * sizeof(int)));
         CK(e->cb_lc.alloc(M * G * f));
         CK(e->cb_n.alloc(M * sizeof(int)));
+    }
+    if (c.rhythm) {
+        CK(e->rh_f.alloc(M * 4 * f));
+        CK(e->rh_gw.alloc(M * e->nh() * f));
+        CK(e->rh_gr.alloc(M * e->nh() * f));
     }
     if (c.thalamus) {
         CK(e->th_acc.alloc(M * 16 * f));
@@ -522,6 +535,16 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         e->launches += 2;
         dbg(e, "th_g", j, e->th_g.as<float>(), M, 4);
     };
+    if (c.rhythm && phase != PHASE_END) {
+        // Y: the clocks at every token of the chunk, from the input (after the letters): reset read-out, times, phase features
+        prof_begin(e, "rhythm");
+        launch_rmsnorm(st, x, e->ones.as<float>(), M, d, h);
+        launch_chain_gemv(st, h, e->rhy_wr.as<float>(), M, d, 4, e->gate_chunk, e->gz.as<float>());
+        launch_rhythm(st, e->gz.as<float>(), e->rhy_br.as<float>(), e->rhy_lw.as<float>(), rows, T, s->rh.as<float>(), e->rh_f.as<float>());
+        prof_end(e);
+        e->launches += 2;
+        dbg(e, "rh_f", -1, e->rh_f.as<float>(), M, 4);
+    }
     if (c.thalamus && phase != PHASE_END) relay_read(0);
     for (int i = phase == PHASE_END ? c.eng_block : 0; i < L; ++i) {
         BlockDev& b = *e->blocks[i];
@@ -603,6 +626,12 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         mp.qg = e->vqg.as<float>(); mp.ex = e->vex.as<float>(); mp.qw = e->qw.as<float>(); mp.qa = e->qa.as<float>();
         mp.qs = c.mem_momentum > 0.0f ? e->vqs.as<float>() : nullptr;
         mp.mom = c.mem_momentum;
+        if (c.rhythm) {
+            prof_begin(e, "rhythm");
+            launch_rhythm_gates(st, e->rh_f.as<float>(), b.rh_w.as<float>(), b.rh_r.as<float>(), M, nh, e->rh_gw.as<float>(), e->rh_gr.as<float>());
+            prof_end(e);
+            mp.rh_w = e->rh_gw.as<float>();
+        }
         mp.ach = (c.neuromod > 0 && i > 0) ? e->sig.as<float>() + 1 : nullptr;
         mp.ach_stride = 4;
         mp.status = e->status.as<uint32_t>();
@@ -629,7 +658,8 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         prof_end(e);
         dbg(e, "y_raw", i, mh.y, M, d);
         prof_begin(e, "mem_post");
-        launch_mem_post(st, mh.y, c.out_gate ? e->proj.as<float>() + 4 * d : nullptr, pw, M, d, hs, e->y.as<float>(), limbs_for(e, e->y.as<float>(), M, d));
+        launch_mem_post(st, mh.y, c.out_gate ? e->proj.as<float>() + 4 * d : nullptr, pw, M, d, hs, e->y.as<float>(), limbs_for(e, e->y.as<float>(), M, d),
+                        c.rhythm ? e->rh_gr.as<float>() : nullptr);
         prof_end(e);
         dbg(e, "y", i, e->y.as<float>(), M, d);
         if (c.dendrite) {
@@ -869,6 +899,13 @@ bool locate(const ava_state* s, int row, const std::string& name, StateSlice* ou
         out->count = (size_t)s->n_host[row] * d;
         return true;
     }
+    if (name == "v51.rh") {
+        if (!c.rhythm) return false;
+        out->buf = &ms->rh;
+        out->off = (size_t)row * 2;
+        out->count = 2;
+        return true;
+    }
     if (name.rfind("v51.", 0) == 0 && (c.dopamine || c.mood > 0)) {
         const std::string what = name.substr(4);
         const size_t k = what == "prev" ? d : what == "mood" ? (size_t)c.mood : 1;
@@ -921,6 +958,7 @@ int alloc_state(ava_engine* e, int rows, int ring, int keep, ava_state** out) {
         CK(s->stp_u.alloc(L * M * d * f));
         CK(s->stp_x.alloc(L * M * d * f));
     }
+    if (c.rhythm) CK(s->rh.alloc(M * 2 * f));
     if (c.dopamine || c.mood > 0) {
         CK(s->sur_prev.alloc(M * d * f));
         CK(s->sur_valid.alloc(M * f));
@@ -943,7 +981,7 @@ int alloc_state(ava_engine* e, int rows, int ring, int keep, ava_state** out) {
 }
 
 int zero_state(ava_engine* e, ava_state* s) {
-    for (Dev* b : {&s->lif_v, &s->lif_s, &s->lif_a, &s->mem_f, &s->mem_s, &s->stp_u, &s->sur_prev, &s->sur_valid, &s->sur_last, &s->mood, &s->eng_n,
+    for (Dev* b : {&s->lif_v, &s->lif_s, &s->lif_a, &s->mem_f, &s->mem_s, &s->stp_u, &s->sur_prev, &s->sur_valid, &s->sur_last, &s->mood, &s->rh, &s->eng_n,
                    &s->eng_start})
         if (b->p) CK(cudaMemsetAsync(b->p, 0, b->bytes, e->stream));
     if (s->stp_x.p) launch_fill(e->stream, s->stp_x.as<float>(), (int64_t)(s->stp_x.bytes / sizeof(float)), 1.0f);  // x starts at 1
@@ -970,6 +1008,8 @@ int copy_row(ava_engine* e, const ava_state* src, int src_row, ava_state* dst, i
         if (c.fast_mem && c.mem_momentum > 0.0f)
             CK(cudaMemcpyAsync(dst->mem_s.as<float>() + dn * per, src->mem_s.as<float>() + so * per, per * f, cudaMemcpyDeviceToDevice, e->stream));
     }
+    if (c.rhythm)
+        CK(cudaMemcpyAsync(dst->rh.as<float>() + (size_t)dst_row * 2, src->rh.as<float>() + (size_t)src_row * 2, 2 * f, cudaMemcpyDeviceToDevice, e->stream));
     if (c.dopamine || c.mood > 0) {
         CK(cudaMemcpyAsync(dst->sur_prev.as<float>() + dst_row * d, src->sur_prev.as<float>() + src_row * d, d * f, cudaMemcpyDeviceToDevice, e->stream));
         CK(cudaMemcpyAsync(dst->sur_valid.as<float>() + dst_row, src->sur_valid.as<float>() + src_row, f, cudaMemcpyDeviceToDevice, e->stream));
@@ -1149,6 +1189,10 @@ int ava_engine_finalize(ava_engine* e) {
             if ((rc = upload_f32(e, b.da_c, p + "v51.da_c", true))) return rc;
         }
         if (c.mood > 0 && i > 0 && (rc = upload_f32(e, b.mood_g, p + "v51.mood_g", true))) return rc;
+        if (c.rhythm) {
+            if ((rc = upload_f32(e, b.rh_w, p + "v51.rh_w", true))) return rc;
+            if ((rc = upload_f32(e, b.rh_r, p + "v51.rh_r", true))) return rc;
+        }
         if (c.stp) {
             // U, F, D are sigmoids of their parameters (src/model/fstep/arch_f3.rs:82)
             struct P { Dev* d; const char* n; bool sig; };
@@ -1210,6 +1254,16 @@ int ava_engine_finalize(ava_engine* e) {
         for (int j = 0; j < c.d; ++j)
             for (int k = 0; k < c.neuromod; ++k) w4[(size_t)j * 4 + k] = it->second[(size_t)j * c.neuromod + k];
         if ((rc = upload(e, e->nm_wn, w4.data(), w4.size() * sizeof(float)))) return rc;
+    }
+    if (c.rhythm) {
+        if ((rc = upload_f32(e, e->rhy_lw, "v51.rhythm.lw", true))) return rc;
+        if ((rc = upload_f32(e, e->rhy_br, "v51.rhythm.br", true))) return rc;
+        auto it = e->host_f32.find("v51.rhythm.wr");
+        if (it == e->host_f32.end()) return e->fail(AVA_ERR_MISSING, "missing tensor v51.rhythm.wr");
+        std::vector<float> w4((size_t)c.d * 4, 0.0f);  // [d][2] with the columns padded to four
+        for (int j = 0; j < c.d; ++j)
+            for (int k = 0; k < 2; ++k) w4[(size_t)j * 4 + k] = it->second[(size_t)j * 2 + k];
+        if ((rc = upload(e, e->rhy_wr, w4.data(), w4.size() * sizeof(float)))) return rc;
     }
     if (c.mood > 0) {
         if ((rc = upload_f32(e, e->mood_lam, "v51.mood.lam", true))) return rc;
@@ -1295,7 +1349,7 @@ int ava_engine_finalize(ava_engine* e) {
         if ((rc = upload(e, e->cb_idx, idx.data(), idx.size() * sizeof(uint32_t)))) return rc;
         if ((rc = upload(e, e->cb_sgn, sg.data(), sg.size() * sizeof(float)))) return rc;
     }
-    if ((c.dendrite && c.fast_mem) || c.thalamus || c.cb_units > 0) {
+    if ((c.dendrite && c.fast_mem) || c.thalamus || c.cb_units > 0 || c.rhythm) {
         const std::vector<float> one((size_t)c.d, 1.0f);
         if ((rc = upload(e, e->ones, one.data(), one.size() * sizeof(float)))) return rc;
     }
@@ -1702,7 +1756,7 @@ int64_t ava_engine_bytes(const ava_engine* e) {
 int64_t ava_state_bytes(const ava_state* s) {
     if (!s) return 0;
     int64_t n = 0;
-    for (const Dev* d : {&s->lif_v, &s->lif_s, &s->lif_a, &s->mem_f, &s->mem_s, &s->stp_u, &s->stp_x, &s->sur_prev, &s->sur_valid, &s->sur_last, &s->mood, &s->eng_k, &s->eng_v, &s->eng_n, &s->eng_start})
+    for (const Dev* d : {&s->lif_v, &s->lif_s, &s->lif_a, &s->mem_f, &s->mem_s, &s->stp_u, &s->stp_x, &s->sur_prev, &s->sur_valid, &s->sur_last, &s->mood, &s->rh, &s->eng_k, &s->eng_v, &s->eng_n, &s->eng_start})
         n += d->bytes;
     return n;
 }
@@ -1806,5 +1860,7 @@ int ava_prof_names(ava_engine* e, char* out, int32_t cap) {
 float ava_host_expf(float x) { return ava::expf_(x); }
 float ava_host_logf(float x) { return ava::logf_(x); }
 float ava_host_rsqrtf(float x) { return ava::rsqrtf_(x); }
+float ava_host_sinf(float x) { return ava::sinf_(x); }
+float ava_host_cosf(float x) { return ava::cosf_(x); }
 
 }  // extern "C"

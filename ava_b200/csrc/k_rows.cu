@@ -507,6 +507,7 @@ __global__ void mem_prep_kernel(const MemPrepArgs a) {
         const size_t o = (size_t)r * d + c;
         const float la = log_sigmoid(add(add(za, in_off), in_lra));
         float be = add(mul(sigmoid(add(zb, in_lrb)), 2.0f), 0.0f);
+        if (a.rh_w) be = mul(be, a.rh_w[(size_t)r * nh + e]);  // --rhythm: the write gate, before ACh's clamp
         if (a.ach) {  // --neuromod ACh: times its signal, kept in [0, 2] (maximum, then minimum: src/model/fstep/arch.rs:1121-1129)
             be = mul(be, ach);
             be = be < 0.0f ? 0.0f : be;
@@ -564,7 +565,7 @@ __global__ void mem_prep_kernel(const MemPrepArgs a) {
 // ---------------------------------------------------------------------------------------------------- memory: output
 // head norm, then the silu output gate (src/model/fstep/arch.rs:842-852)
 __global__ void mem_post_kernel(const float* __restrict__ y_raw, const float* __restrict__ gate, int ldg, int M, int d, int hs, float* __restrict__ y,
-                                uint16_t* __restrict__ limbs) {
+                                uint16_t* __restrict__ limbs, const float* __restrict__ rh_r) {
     pdl_enter();
     extern __shared__ __align__(16) float sm[];
     const int nh = d / hs, r = blockIdx.x, tid = threadIdx.x, T = blockDim.x;
@@ -576,6 +577,7 @@ __global__ void mem_post_kernel(const float* __restrict__ y_raw, const float* __
     __syncthreads();
     for (int c = tid; c < d; c += T) {
         float v = mul(ys[c], inv[c / hs]);
+        if (rh_r) v = mul(v, rh_r[(size_t)r * nh + c / hs]);
         if (gate) {
             const float g = gate[(size_t)r * ldg + c];
             v = mul(v, div(g, add(1.0f, expf_(-g))));
@@ -805,10 +807,11 @@ void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a) {
     launch_k(mem_prep_kernel, dim3(a.M), dim3(256), smem, st, a);
 }
 
-void launch_mem_post(cudaStream_t st, const float* y_raw, const float* gate, int ldg, int M, int d, int hs, float* y, uint16_t* limbs) {
+void launch_mem_post(cudaStream_t st, const float* y_raw, const float* gate, int ldg, int M, int d, int hs, float* y, uint16_t* limbs,
+                     const float* rh_r) {
     const size_t smem = ((size_t)d + d / hs) * sizeof(float);
     opt_in_smem(mem_post_kernel, smem);
-    launch_k(mem_post_kernel, dim3(M), dim3(256), smem, st, y_raw, gate, ldg, M, d, hs, y, limbs);
+    launch_k(mem_post_kernel, dim3(M), dim3(256), smem, st, y_raw, gate, ldg, M, d, hs, y, limbs, rh_r);
 }
 
 void launch_kwta(cudaStream_t st, const float* u, int M, int n, int k, int relu2, float* a) {

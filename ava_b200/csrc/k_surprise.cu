@@ -115,7 +115,58 @@ __global__ void da_add_kernel(float* x, const float* __restrict__ y, const float
     x[i] = add(x[i], o);
 }
 
+// --rhythm, one thread per (row, clock): l = log_sigmoid(-(pre + br)) = ln(1 - reset), the one-step scan written as the
+// reference's chunk form at one token (big = l 1, before = big - l, diff = big - before, w = exp(min(diff, 0)) 1,
+// time = w + exp(big) time), phase = time exp(lw), features cos and sin
+__global__ void rhythm_kernel(const float* __restrict__ pre, const float* __restrict__ br, const float* __restrict__ lw, int rows, int T,
+                              float* __restrict__ times, float* __restrict__ f) {
+    pdl_enter();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * 2) return;
+    const int r = i >> 1, o = i & 1;
+    const float b = br[o], w_ph = expf_(lw[o]);
+    float a = times[i];
+    for (int t = 0; t < T; ++t) {
+        const size_t row = (size_t)t * rows + r;
+        const float p = add(pre[row * 4 + o], b);
+        const float l = log_sigmoid(-p);
+        const float big = mul(l, 1.0f), before = sub(big, l), diff = sub(big, before);
+        const float w = mul(expf_(diff > 0.0f ? 0.0f : diff), 1.0f);
+        a = add(w, mul(expf_(big), a));
+        const float ph = mul(a, w_ph);
+        f[row * 4 + 2 * o] = cosf_(ph);
+        f[row * 4 + 2 * o + 1] = sinf_(ph);
+    }
+    times[i] = a;
+}
+
+__global__ void rhythm_gates_kernel(const float* __restrict__ f, const float* __restrict__ Gw, const float* __restrict__ Gr, int M, int nh,
+                                    float* __restrict__ gw, float* __restrict__ gr) {
+    pdl_enter();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= M * nh) return;
+    const int r = i / nh, e = i % nh;
+    const float4 fv = *reinterpret_cast<const float4*>(f + (size_t)r * 4);
+    float zw = mul(Gw[e], fv.x), zr = mul(Gr[e], fv.x);
+    zw = fma(Gw[nh + e], fv.y, zw);
+    zr = fma(Gr[nh + e], fv.y, zr);
+    zw = fma(Gw[2 * nh + e], fv.z, zw);
+    zr = fma(Gr[2 * nh + e], fv.z, zr);
+    zw = fma(Gw[3 * nh + e], fv.w, zw);
+    zr = fma(Gr[3 * nh + e], fv.w, zr);
+    gw[i] = add(mul(tanhf_(zw), 1.0f), 1.0f);
+    gr[i] = add(mul(tanhf_(zr), 1.0f), 1.0f);
+}
+
 }  // namespace
+
+void launch_rhythm(cudaStream_t st, const float* pre, const float* br, const float* lw, int rows, int T, float* times, float* f) {
+    launch_k(rhythm_kernel, dim3((rows * 2 + 127) / 128), dim3(128), 0, st, pre, br, lw, rows, T, times, f);
+}
+
+void launch_rhythm_gates(cudaStream_t st, const float* f, const float* Gw, const float* Gr, int M, int nh, float* gw, float* gr) {
+    launch_k(rhythm_gates_kernel, dim3((M * nh + 127) / 128), dim3(128), 0, st, f, Gw, Gr, M, nh, gw, gr);
+}
 
 bool launch_surprise(cudaStream_t st, const float* logits, int V, const uint32_t* tok, const float* valid, int rows, int T, float* s, float* z) {
     const size_t smem = (size_t)((V + 3) & ~3) * sizeof(float);

@@ -146,6 +146,7 @@ struct MemPrepArgs {
     const float* gate_w; // [d][gate_cols]: wa1 | wb1 | wa | wb side by side, columns padded with zeros to a multiple of 4
     int gate_cols;       // padded column count (at most 256: one chain per thread)
     int gate_chunk;      // rows staged per copy; divides d, a multiple of 8
+    const float* rh_w;   // --rhythm: the write strength times rh_w[row * heads + head] before ACh; or nullptr
     const float* ach;    // --neuromod ACh: the write strength times ach[row * ach_stride], kept in [0, 2]; or nullptr
     int ach_stride;
     float* z;            // [M][gate_cols] work: h . gate_w (stage one)
@@ -199,7 +200,14 @@ bool mem_heads_tiling(int hs, int* cw, int* chunk_rows, bool momentum = false);
 // natural [heads][hs][hs] to slice-major [heads][hs / cw][hs][cw] (to_slices 1) or back (0)
 void launch_retile(cudaStream_t st, const float* src, float* dst, int64_t heads, int hs, int cw, int to_slices);
 
-void launch_mem_post(cudaStream_t st, const float* y_raw, const float* gate, int ldg, int M, int d, int hs, float* y, uint16_t* limbs = nullptr);
+// rh_r: --rhythm's gain of the read [M][heads], after the head norm and before the output gate; or nullptr
+void launch_mem_post(cudaStream_t st, const float* y_raw, const float* gate, int ldg, int M, int d, int hs, float* y, uint16_t* limbs = nullptr,
+                     const float* rh_r = nullptr);
+// --rhythm (src/model/fstep/arch_f4.rs:47-107), token-rows time-major [T][rows]: from the reset read-outs pre [M][4] (two
+// used, bias not yet added) the clocks' times token after token from the carried ones [rows][2] (updated in place) and
+// the phase features f [M][4] = cos, sin of time * exp(lw); then a block's gains per head 1 + tanh(f G) [M][heads] twice
+void launch_rhythm(cudaStream_t st, const float* pre, const float* br, const float* lw, int rows, int T, float* times, float* f);
+void launch_rhythm_gates(cudaStream_t st, const float* f, const float* Gw, const float* Gr, int M, int nh, float* gw, float* gr);
 
 struct EngramArgs {
     const float* qkv;    // [M, 3 d]

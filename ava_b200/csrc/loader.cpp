@@ -354,6 +354,7 @@ int ava_arch_flags(const char* flags, ava_config* cfg) {
         else if (k == "--thalamus") cfg->thalamus = 1;
         else if (k == "--dopamine") cfg->dopamine = 1;
         else if (k == "--letters") cfg->letters = 1;
+        else if (k == "--rhythm") cfg->rhythm = 1;
         else if (k == "--cerebellum-head") {
             if (!value(&v)) return fail(AVA_ERR_ARG, "--cerebellum-head needs a value");
             const int g = std::atoi(v.c_str());
@@ -450,7 +451,7 @@ int ava_config_from_ckpt(const ava_ckpt* c, const char* kind, const char* arch_f
         int b;
         std::string rest;
         if (!block_name(e.name, &b, &rest)) {
-            if (e.name != "tok_emb" && e.name != "final.norm" && e.name != "nm.norm" && e.name != "nm.wn" && e.name != "nm.bn" && e.name != "th.read" && e.name != "th.gate" && e.name != "th.bias" && e.name.rfind("v51.mood.", 0) != 0 && e.name != "cbh.wo" && e.name.rfind("v51.letters.", 0) != 0)
+            if (e.name != "tok_emb" && e.name != "final.norm" && e.name != "nm.norm" && e.name != "nm.wn" && e.name != "nm.bn" && e.name != "th.read" && e.name != "th.gate" && e.name != "th.bias" && e.name.rfind("v51.mood.", 0) != 0 && e.name != "cbh.wo" && e.name.rfind("v51.letters.", 0) != 0 && e.name.rfind("v51.rhythm.", 0) != 0)
                 return fail(AVA_NOT_APPLICABLE, e.name + ": a tensor of a part the engine does not cover (glance, magnitude code, order head)");
             continue;
         }

@@ -2,7 +2,7 @@
 // is a safetensors file under the reference's tensor names and shapes:
 //   meta.seen U32 [rows], meta.model U32 [2] (fingerprint high, low), meta.blocks U32 [1], meta.cap U32 [2] (max, rule;
 //   0 0: no cap), meta.hist U32 [rows, 17], meta.hist_len U32 [rows],
-//   lif.{i}.v / .s / .a F32 [rows, d], mem.{i}.f / .s F32 [rows * heads, hs, hs], parts.{i}.stp_u / .stp_x F32 [rows, d], v51.prev [rows, d] / .pvalid [rows] / .last_s [rows] / .mood [rows, k],
+//   lif.{i}.v / .s / .a F32 [rows, d], mem.{i}.f / .s F32 [rows * heads, hs, hs], parts.{i}.stp_u / .stp_x F32 [rows, d], v51.prev [rows, d] / .pvalid [rows] / .last_s [rows] / .mood [rows, k] / .rh [rows, 2],
 //   eng.k / eng.v F32 [rows, heads, S, hs] with S the longest row's store and shorter rows padded on the left
 //   (src/state.rs:207-328), eng.valid U32 [rows], eng.pad F32 [rows, S] (0 for a slot, -1e9 for padding) when rows differ.
 // Written through PATH.tmp and a rename, so the file is whole or absent.  Host code over the C ABI.
@@ -130,6 +130,10 @@ int ava_state_save(const ava_state* s, const char* path) {
             put_f32(&outs, mi + k, {(int64_t)rows * nh, hs, hs}, v);
         }
     }
+    if (c.rhythm) {
+        if (!rows_of("v51.rh", 2, &v)) return rc;
+        put_f32(&outs, "v51.rh", {rows, 2}, v);
+    }
     if (c.dopamine || c.mood > 0) {  // src/v51.rs:1012,1068-1076: [rows, d], [rows], [rows], [rows, k]
         if (!rows_of("v51.prev", d, &v)) return rc;
         put_f32(&outs, "v51.prev", {rows, d}, v);
@@ -251,6 +255,7 @@ int ava_state_load(ava_engine* e, const char* path, int32_t max_ctx, ava_state**
             if ((rc = rows_in(mi + k, (int64_t)d * c.head_size))) return rc;
         }
     }
+    if (c.rhythm && (rc = rows_in("v51.rh", 2))) return rc;
     if (c.dopamine || c.mood > 0) {
         if ((rc = rows_in("v51.prev", d)) || (rc = rows_in("v51.pvalid", 1)) || (rc = rows_in("v51.last_s", 1))) return rc;
         if (c.mood > 0 && (rc = rows_in("v51.mood", c.mood))) return rc;

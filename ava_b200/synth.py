@@ -117,6 +117,11 @@ def model(cfg: dict, seed: int = 0, recipe: str = "bench", unit_gain: bool = Tru
         w["nm.norm"] = (1.0 + g.n("nm.norm", (d,), 0.05)).astype(np.float32) if awake else np.ones(d, np.float32)
         w["nm.wn"] = g.n("nm.wn", (d, k), 0.05) if awake else np.zeros((d, k), np.float32)
         w["nm.bn"] = g.n("nm.bn", (k,), 0.3) if awake else np.zeros(k, np.float32)
+    if cfg.get("rhythm"):
+        # the reference's start: periods of 16 and 3.2 tokens, a reset bias of -10 (never); the awake recipe resets now and then
+        w["v51.rhythm.lw"] = np.log(2.0 * np.pi / np.array([16.0, 3.2])).astype(np.float32)
+        w["v51.rhythm.wr"] = g.n("v51.rhythm.wr", (d, 2), 2.0 / math.sqrt(d)) if awake else np.zeros((d, 2), np.float32)
+        w["v51.rhythm.br"] = np.array([-2.0, -1.0], np.float32) if awake else np.full(2, -10.0, np.float32)
     if cfg.get("mood"):
         k = cfg["mood"]
         w["v51.mood.lam"] = g.n("v51.mood.lam", (k,), 1.0) + 2.0
@@ -207,6 +212,9 @@ def model(cfg: dict, seed: int = 0, recipe: str = "bench", unit_gain: bool = Tru
         if cfg.get("dendrite") and cfg["fast_mem"]:
             w[p + "v51.dend_a"] = g.n(p + "v51.dend_a", (d, 32), 1.0 / math.sqrt(d))
             w[p + "v51.dend_b"] = g.n(p + "v51.dend_b", (32, H), 0.3) if awake else np.zeros((32, H), np.float32)
+        if cfg.get("rhythm") and cfg["fast_mem"]:
+            w[p + "v51.rh_w"] = g.n(p + "v51.rh_w", (4, nh), 0.3) if awake else np.zeros((4, nh), np.float32)
+            w[p + "v51.rh_r"] = g.n(p + "v51.rh_r", (4, nh), 0.3) if awake else np.zeros((4, nh), np.float32)
         if cfg.get("dopamine") and i > 0:
             w[p + "v51.da_w"] = g.n(p + "v51.da_w", (d,), 0.5) if awake else np.zeros(d, np.float32)
             w[p + "v51.da_c"] = g.n(p + "v51.da_c", (d,), 0.1) if awake else np.zeros(d, np.float32)

@@ -43,6 +43,7 @@ pub struct AvaConfig {
     pub mood: i32,
     pub cb_units: i32,
     pub letters: i32,
+    pub rhythm: i32,
     pub mem_momentum: f32,
     pub slope: f32,
 }

@@ -84,6 +84,12 @@ typedef struct ava_config {
                                tanh(byte[b] + end[place from the end] + pos[place]) / sqrt(bytes used) (64 wide; src/v51.rs:492-501,
                                src/model/fstep/arch_f2.rs:34-60); weights v51.letters.byte [256, 64] / .pos [16, 64] / .end [16, 64] /
                                .wo [64, d] and the tokens' spellings (ava_engine_set_token_bytes) */
+    int32_t rhythm;         /* --rhythm: two clocks count the tokens since their last reset (reset read from the input: time =
+                               (1 - reset)(1 + time)), their phases time * exp(lw) give four features cos / sin, and every block's
+                               write strength (before ACh's clamp) and head-normed read (before the output gate) are scaled per head
+                               by 1 + tanh(f G) (src/model/fstep/arch_f4.rs:39-108); weights v51.rhythm.lw / br [2], .wr [d, 2],
+                               b{i}.v51.rh_w / rh_r [4, heads]; carried per row: v51.rh [2]; needs fast_mem.  Sine and cosine are
+                               the library's own (ava_host_sinf / ava_host_cosf), the same bits on host and device */
     float   mem_momentum;   /* --mem-momentum (0: off) */
     float   slope;          /* --surrogate-slope (does not change forward values) */
 } ava_config;
@@ -372,6 +378,8 @@ int ava_debug_mem_heads_timeline(int device, int32_t m, int32_t hs, uint64_t* ou
 float ava_host_expf(float x);
 float ava_host_logf(float x);
 float ava_host_rsqrtf(float x);
+float ava_host_sinf(float x);
+float ava_host_cosf(float x);
 /* The same evaluated on the device, n values (tests that host and device agree bit for bit). which: 0 exp, 1 ln, 2 x^-1/2. */
 int ava_op_math(int device, int32_t which, const float* x, int64_t n, float* y);
 

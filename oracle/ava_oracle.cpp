@@ -34,7 +34,9 @@ float libm_log(float x) { return std::log(x); }
 // Rust's f32::powf(-0.5) is the platform powf
 float libm_rsqrt(float x) { return std::pow(x, -0.5f); }
 
-orc_fn1 g_exp = libm_exp, g_log = libm_log, g_rsqrt = libm_rsqrt;
+float libm_sin(float x) { return std::sin(x); }
+float libm_cos(float x) { return std::cos(x); }
+orc_fn1 g_exp = libm_exp, g_log = libm_log, g_rsqrt = libm_rsqrt, g_sin = libm_sin, g_cos = libm_cos;
 int g_threads = 1;
 int g_simd = 1;
 double g_event_max = 0.5;  // int8.rs:459
@@ -505,6 +507,7 @@ struct Block {
     QW win, wout;
     // short-term plasticity of the spikes' synapse (--stp): parameters and their sigmoids
     std::vector<float> stp_u, stp_f, stp_d, stp_mix, stp_U, stp_F, stp_D;
+    std::vector<float> rh_w, rh_r;          // --rhythm: the write strength's and the read's gates [4, heads]
     std::vector<float> da_w, da_c, mood_g;  // --dopamine: gate [d] twice; --mood: gain [k, d] (blocks after the first)
     // the dendrites of the MLP's units (--dendrite): A [d, 32], B [32, hidden]
     std::vector<float> dend_a, dend_b;
@@ -527,6 +530,7 @@ struct orc_model {
     orc_config cfg;
     std::vector<float> tok_emb, final_norm;
     std::vector<float> nm_norm, nm_wn, nm_bn;  // --neuromod: the nucleus (gain [d], read-out [d, k], bias [k])
+    std::vector<float> rhy_lw, rhy_wr, rhy_br;  // --rhythm: log frequencies [2], reset read-out [d, 2] and bias [2]
     std::vector<float> mood_lam, mood_win, mood_bin;  // --mood: decay, input weight and bias [k]
     // --letters (src/v51.rs:449-482): per token 16 byte ids, their places counted from the end, a mask and 1 / sqrt(used);
     // byte [256, 64], pos [16, 64], end [16, 64] embeddings and the read-out [64, d]
@@ -546,6 +550,7 @@ struct RowState {
     std::vector<std::vector<float>> v, s, a;    // per block [d]
     std::vector<std::vector<float>> f, ms;      // per block [nh, hs, hs]
     std::vector<std::vector<float>> su, sx;     // per block [d]: the synapse's (u, x) with --stp
+    std::vector<float> rh;                      // --rhythm: the time since each clock's last reset [2]
     std::vector<float> prev, mood;              // --dopamine / --mood: block 0's last normed output [d], the mood [k]
     std::vector<float> pvalid, last_s;          // [1] each: whether there is a prev, the last surprise
     std::vector<float> ek, evv;                 // engram [enh, n, ehs]
@@ -567,6 +572,9 @@ std::vector<float>* f32_slot(orc_model* m, const std::string& name, int64_t* wan
     if (name == "nm.norm") { *want = d; return &m->nm_norm; }
     if (name == "nm.wn") { *want = (int64_t)d * c.neuromod; return &m->nm_wn; }
     if (name == "nm.bn") { *want = c.neuromod; return &m->nm_bn; }
+    if (name == "v51.rhythm.lw") { *want = 2; return &m->rhy_lw; }
+    if (name == "v51.rhythm.wr") { *want = (int64_t)d * 2; return &m->rhy_wr; }
+    if (name == "v51.rhythm.br") { *want = 2; return &m->rhy_br; }
     if (name == "v51.mood.lam") { *want = c.mood; return &m->mood_lam; }
     if (name == "v51.mood.win") { *want = c.mood; return &m->mood_win; }
     if (name == "v51.mood.bin") { *want = c.mood; return &m->mood_bin; }
@@ -596,7 +604,7 @@ std::vector<float>* f32_slot(orc_model* m, const std::string& name, int64_t* wan
         {"hebb.ba", &b.ba, nh}, {"hebb.bb", &b.bb, nh}, {"hebb.wa1", &b.wa1, (int64_t)d * r}, {"hebb.wa2", &b.wa2, (int64_t)r * d},
         {"hebb.wb1", &b.wb1, (int64_t)d * r}, {"hebb.wb2", &b.wb2, (int64_t)r * d}, {"hebb.off", &b.off, d}, {"hebb.vres", &b.vres, 2},
         {"eng.norm", &b.eng_norm, d}, {"mlp.norm", &b.mlp_norm, d}, {"dense", &b.dense, i + 2},
-        {"v51.da_w", &b.da_w, d}, {"v51.da_c", &b.da_c, d}, {"v51.mood_g", &b.mood_g, (int64_t)c.mood * d},
+        {"v51.rh_w", &b.rh_w, (int64_t)4 * nh}, {"v51.rh_r", &b.rh_r, (int64_t)4 * nh}, {"v51.da_w", &b.da_w, d}, {"v51.da_c", &b.da_c, d}, {"v51.mood_g", &b.mood_g, (int64_t)c.mood * d},
     };
     for (const E& e : table)
         if (rest == e.n) { *want = e.len; return e.p; }
@@ -734,6 +742,30 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
             add_into(&x[(size_t)r * d], o.data(), d);
         }
         T("x_let", -1, x.data(), d);
+    }
+    // Y (fstep/arch_f4.rs:47-92): before the blocks, from the input after the letters: the clocks' times and phase features
+    std::vector<float> rh_f, rh_a;  // [R][4] cos, sin of each phase; [R][2] the new times
+    if (cfg.rhythm) {
+        rh_f.resize((size_t)R * 4);
+        rh_a.resize((size_t)R * 2);
+        for (int r = 0; r < R; ++r) {
+            std::vector<float> hn(x.begin() + (size_t)r * d, x.begin() + (size_t)(r + 1) * d);
+            head_norm(hn.data(), d, d);
+            float pre[2];
+            gemv(hn.data(), d, m->rhy_wr.data(), 2, pre);
+            for (int o = 0; o < 2; ++o) {
+                pre[o] = pre[o] + m->rhy_br[o];
+                const float l = log_sigmoid(-pre[o]);  // ln(1 - r)
+                const float big = l * 1.0f, before = big - l, diff = big - before;
+                const float w = g_exp(diff > 0.0f ? 0.0f : diff) * 1.0f;
+                const float a = w + g_exp(big) * rows[r]->rh[o];
+                rh_a[(size_t)r * 2 + o] = a;
+                const float ph = a * g_exp(m->rhy_lw[o]);
+                rh_f[(size_t)r * 4 + 2 * o] = g_cos(ph);
+                rh_f[(size_t)r * 4 + 2 * o + 1] = g_sin(ph);
+            }
+        }
+        T("rh_f", -1, rh_f.data(), 4);
     }
     std::vector<std::vector<float>> streams;
     if (cfg.dense) streams.push_back(x);
@@ -878,6 +910,17 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
             gemv(hr, d, b.wb1.data(), rk, z1.data());
             gemv(z1.data(), rk, b.wb2.data(), d, lrb.data());
 
+            // Y: this block's gains per head from the token's phase features, 1 + tanh(f G) (fstep/arch_f4.rs:94-107)
+            std::vector<float> rgw, rgr;
+            if (cfg.rhythm) {
+                rgw.resize(nh); rgr.resize(nh);
+                gemv(&rh_f[(size_t)r * 4], 4, b.rh_w.data(), nh, rgw.data());
+                gemv(&rh_f[(size_t)r * 4], 4, b.rh_r.data(), nh, rgr.data());
+                for (int e = 0; e < nh; ++e) {
+                    rgw[e] = tanh_f(rgw[e]) * 1.0f + 1.0f;
+                    rgr[e] = tanh_f(rgr[e]) * 1.0f + 1.0f;
+                }
+            }
             RowState& st = *rows[r];
             std::vector<float> fnew((size_t)nh * hs * hs), snew(mom ? (size_t)nh * hs * hs : 0);
             std::vector<float> ek(d), ex(d), w(d), ah(d), qg(d), yraw(d), qwv(nh), qav(nh);
@@ -889,6 +932,7 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
                 for (int c = 0; c < hs; ++c) {
                     la[c] = log_sigmoid((za[e] + b.off[o + c]) + lra[o + c]);
                     be[c] = sigmoid(zb[e] + lrb[o + c]) * 2.0f + 0.0f;
+                    if (cfg.rhythm) be[c] = be[c] * rgw[e];  // Y: before ACh's clamp
                     if (!sig.empty()) {  // ACh: the write strength times its signal, kept in [0, 2] (maximum, then minimum)
                         float v = be[c] * sig[(size_t)r * nk + NM_ACH];
                         v = v < 0.0f ? 0.0f : v;
@@ -938,6 +982,8 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
                           mom ? snew.data() + (size_t)e * hs * hs : nullptr);
                 std::copy(yr + o, yr + o + hs, yraw.begin() + o);
                 head_norm(yr + o, hs, hs);
+                if (cfg.rhythm)  // Y: the read's gain, after the head norm and before the output gate
+                    for (int c = 0; c < hs; ++c) yr[o + c] = yr[o + c] * rgr[e];
                 if (cfg.out_gate)
                     for (int c = 0; c < hs; ++c) {
                         const float g = gq[(size_t)r * d + o + c];
@@ -1144,6 +1190,7 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
             st.su = std::move(nw[r].su);
             st.sx = std::move(nw[r].sx);
         }
+        if (cfg.rhythm) st.rh.assign(rh_a.begin() + (size_t)r * 2, rh_a.begin() + (size_t)(r + 1) * 2);
         if (surprise) {  // fstep/arch_f3.rs:324-336
             st.prev.assign(sur_prev.begin() + (size_t)r * d, sur_prev.begin() + (size_t)(r + 1) * d);
             st.pvalid[0] = 1.0f;
@@ -1166,6 +1213,7 @@ bool parse_state_name(const orc_state* s, int row, const std::string& name, cons
     if (name == "eng.v") { *out = &r.evv; return true; }
     if (name == "v51.prev") { *out = &r.prev; return true; }
     if (name == "v51.mood") { *out = &r.mood; return true; }
+    if (name == "v51.rh") { *out = &r.rh; return true; }
     if (name == "v51.pvalid") { *out = &r.pvalid; return true; }
     if (name == "v51.last_s") { *out = &r.last_s; return true; }
     const size_t d1 = name.find('.'), d2 = name.rfind('.');
@@ -1197,7 +1245,11 @@ void orc_set_math(orc_fn1 e, orc_fn1 l, orc_fn1 r) {
     if (l) g_log = l;
     if (r) g_rsqrt = r;
 }
-void orc_reset_math(void) { g_exp = libm_exp; g_log = libm_log; g_rsqrt = libm_rsqrt; }
+void orc_reset_math(void) { g_exp = libm_exp; g_log = libm_log; g_rsqrt = libm_rsqrt; g_sin = libm_sin; g_cos = libm_cos; }
+void orc_set_trig(orc_fn1 s, orc_fn1 c) {
+    if (s) g_sin = s;
+    if (c) g_cos = c;
+}
 void orc_set_threads(int n) { g_threads = n < 1 ? 1 : n; }
 void orc_set_simd(int on) { g_simd = on; }
 void orc_set_event_max(double v) { g_event_max = v; }
@@ -1310,6 +1362,7 @@ int orc_model_check(orc_model* m, char* missing, int cap) {
     if (m->tok_emb.empty()) return fail("tok_emb");
     if (m->final_norm.empty()) return fail("final.norm");
     if (c.neuromod > 0 && (m->nm_norm.empty() || m->nm_wn.empty() || m->nm_bn.empty())) return fail("nm.norm / nm.wn / nm.bn");
+    if (c.rhythm && (m->rhy_lw.empty() || m->rhy_wr.empty() || m->rhy_br.empty())) return fail("v51.rhythm.lw / wr / br");
     if (c.mood > 0 && (m->mood_lam.empty() || m->mood_win.empty() || m->mood_bin.empty())) return fail("v51.mood.lam / win / bin");
     if (c.cb_units > 0 && m->cb_w.empty()) return fail("cbh.wo");
     if (c.letters && (m->let_byte.empty() || m->let_pos.empty() || m->let_end.empty() || m->let_wo.empty())) return fail("v51.letters.byte / pos / end / wo");
@@ -1329,6 +1382,7 @@ int orc_model_check(orc_model* m, char* missing, int cap) {
                         {"parts.stp.u_param", &b.stp_u, c.stp != 0}, {"parts.stp.f_param", &b.stp_f, c.stp != 0},
                         {"parts.stp.d_param", &b.stp_d, c.stp != 0}, {"parts.stp.mix", &b.stp_mix, c.stp != 0},
                         {"v51.dend_a", &b.dend_a, c.dendrite && c.fast_mem}, {"v51.dend_b", &b.dend_b, c.dendrite && c.fast_mem},
+                        {"v51.rh_w", &b.rh_w, c.rhythm && c.fast_mem}, {"v51.rh_r", &b.rh_r, c.rhythm && c.fast_mem},
                         {"v51.da_w", &b.da_w, c.dopamine && i > 0}, {"v51.da_c", &b.da_c, c.dopamine && i > 0},
                         {"v51.mood_g", &b.mood_g, c.mood > 0 && i > 0}};
         for (const F& f : fs)
@@ -1361,6 +1415,7 @@ orc_state* orc_state_new(const orc_model* m, int rows) {
         r.sx.assign(c.n_blocks, std::vector<float>(c.stp ? c.d : 0, 1.f));
         r.prev.assign((c.dopamine || c.mood > 0) ? c.d : 0, 0.f);  // src/v51.rs:1029-1036
         r.mood.assign(c.mood, 0.f);
+        r.rh.assign(c.rhythm ? 2 : 0, 0.f);
         r.pvalid.assign((c.dopamine || c.mood > 0) ? 1 : 0, 0.f);
         r.last_s.assign((c.dopamine || c.mood > 0) ? 1 : 0, 0.f);
     }

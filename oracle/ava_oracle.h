@@ -65,6 +65,7 @@ typedef struct orc_config {
     int32_t mood;           /* --mood (4 units): a slow trace of the surprise scales the later blocks' LIF current (fstep/arch_f3.rs:106-186) */
     int32_t cb_units;       /* --cerebellum-head G: G sparse granule units correct the final normed state (fstep/arch_f3.rs:207-283) */
     int32_t letters;        /* --letters: each token's spelling adds a vector to its input (fstep/arch_f2.rs:34-60) */
+    int32_t rhythm;         /* --rhythm: two resettable clocks' phases scale the memory's write strength and read per head (fstep/arch_f4.rs:39-108) */
     int32_t thalamus;       /* --thalamus: a relay reads the stream and gates each block's memory read and residual (fstep/arch_f2.rs:62-153) */
     float   mem_momentum;   /* 0: off */
     float   slope;          /* surrogate slope (forward value cancels; kept for the literal op order) */
@@ -75,6 +76,8 @@ typedef float (*orc_fn1)(float);
 /* Replace exp / ln / x^-0.5 (NULL keeps the current one).  Process-wide. */
 void orc_set_math(orc_fn1 expf_, orc_fn1 logf_, orc_fn1 rsqrtf_);
 void orc_reset_math(void);
+/* Replace sine and cosine (--rhythm's phases; NULL keeps the current one).  orc_reset_math puts the platform's back. */
+void orc_set_trig(orc_fn1 sinf_, orc_fn1 cosf_);
 void orc_set_threads(int n);
 /* 1: AVX2+FMA tile kernel for the int8 products (same bits as scalar); 0: scalar. */
 void orc_set_simd(int on);

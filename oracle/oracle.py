@@ -21,7 +21,7 @@ class OrcConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "vocab", "d", "n_blocks", "hidden", "kwta_k", "head_size", "eng_block", "eng_head_size", "eng_store_bf16",
         "eng_cap", "gate_rank", "spikes", "alif", "theta", "lif_scale", "value_residual", "relu2", "dense",
-        "out_gate", "fast_mem", "dendrite", "neuromod", "stp", "dopamine", "mood", "cb_units", "letters", "thalamus")] + [("mem_momentum", C.c_float), ("slope", C.c_float)]
+        "out_gate", "fast_mem", "dendrite", "neuromod", "stp", "dopamine", "mood", "cb_units", "letters", "rhythm", "thalamus")] + [("mem_momentum", C.c_float), ("slope", C.c_float)]
 
 
 def build(force: bool = False) -> str:
@@ -49,6 +49,7 @@ def lib() -> C.CDLL:
     fp = C.POINTER(C.c_float)
     i8p = C.POINTER(C.c_int8)
     L.orc_set_math.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+    L.orc_set_trig.argtypes = [C.c_void_p, C.c_void_p]
     L.orc_set_threads.argtypes = [C.c_int]
     L.orc_set_simd.argtypes = [C.c_int]
     L.orc_set_event_max.argtypes = [C.c_double]
@@ -120,14 +121,15 @@ def _fp(a):
 _keep_math = []
 
 
-def set_math(expf=None, logf=None, rsqrtf=None):
-    """Plug in other exp / ln / x^-0.5 (ctypes function pointers or addresses); None keeps the current one."""
+def set_math(expf=None, logf=None, rsqrtf=None, sinf=None, cosf=None):
+    """Plug in other exp / ln / x^-0.5 / sin / cos (ctypes function pointers or addresses); None keeps the current one."""
     def addr(f):
         if f is None:
             return None
         _keep_math.append(f)
         return C.cast(f, C.c_void_p)
     lib().orc_set_math(addr(expf), addr(logf), addr(rsqrtf))
+    lib().orc_set_trig(addr(sinf), addr(cosf))
 
 
 def reset_math():

@@ -33,7 +33,7 @@ def orc_same_math(orc):
 STATE_NAMES = lambda cfg: [f"lif.{i}.{k}" for i in range(cfg["n_blocks"]) for k in (("v", "s", "a") if cfg["alif"] else ("v", "s"))] + \
     ([f"mem.{i}.{k}" for i in range(cfg["n_blocks"]) for k in (("f", "s") if cfg["mem_momentum"] > 0 else ("f",))] if cfg["fast_mem"] else []) + \
     ([f"parts.{i}.{k}" for i in range(cfg["n_blocks"]) for k in ("stp_u", "stp_x")] if cfg["stp"] else []) + \
-    (["v51.prev", "v51.pvalid", "v51.last_s"] if cfg["dopamine"] or cfg["mood"] else []) + (["v51.mood"] if cfg["mood"] else []) + \
+    (["v51.rh"] if cfg["rhythm"] else []) + (["v51.prev", "v51.pvalid", "v51.last_s"] if cfg["dopamine"] or cfg["mood"] else []) + (["v51.mood"] if cfg["mood"] else []) + \
     (["eng.k", "eng.v"] if cfg["eng_block"] >= 0 else [])
 
 
@@ -65,8 +65,9 @@ CONFIGS = {
     "mood": dict(mood=4, neuromod=3, head_size=64),                                      # --mood: the surprise's slow trace scales the current, after NE
     "six_parts": dict(stp=1, neuromod=3, dendrite=1, dopamine=1, mood=4, thalamus=1, head_size=64, mem_momentum=0.5),
     "letters": dict(letters=1, thalamus=1, head_size=64),                                # --letters: the token's spelling in its input (the relay reads it)
+    "rhythm": dict(rhythm=1, neuromod=3, head_size=64, mem_momentum=0.5),                # --rhythm: the clocks' phases gate the write strength (before ACh) and the read
     "cerebellum": dict(cb_units=512, head_size=64),                                      # --cerebellum-head: the correction before the head
-    "all_parts": dict(stp=1, neuromod=3, dendrite=1, dopamine=1, mood=4, thalamus=1, cb_units=1024, letters=1, head_size=64, mem_momentum=0.5),
+    "all_parts": dict(stp=1, neuromod=3, dendrite=1, dopamine=1, mood=4, thalamus=1, cb_units=1024, letters=1, rhythm=1, head_size=64, mem_momentum=0.5),
     "thalamus_alone": dict(thalamus=1, head_size=64),                                    # its gates on the fused W_o epilogue
     # the reference's kind S (Ava-M's): spiking memory + sparse MLP only, binary spikes, relu
     "kind_s": dict(head_size=128, eng_block=-1, spikes=0, alif=0, theta=0, lif_scale=0, value_residual=0, relu2=0, dense=0, out_gate=0,
@@ -147,7 +148,7 @@ def test_forward_with_state_equals_steps(orc_same_math):
     assert np.array_equal(bits(tail), bits(want[:, 6:]))
 
 
-@pytest.mark.parametrize("name", ["ava04_small", "one_head_bf16", "binary_plain", "momentum", "kind_s", "stp", "dendrite", "neuromod", "thalamus", "thalamus_alone", "dopamine", "mood", "six_parts", "cerebellum", "letters", "all_parts"])
+@pytest.mark.parametrize("name", ["ava04_small", "one_head_bf16", "binary_plain", "momentum", "kind_s", "stp", "dendrite", "neuromod", "thalamus", "thalamus_alone", "dopamine", "mood", "six_parts", "cerebellum", "letters", "rhythm", "all_parts"])
 @pytest.mark.parametrize("chunk", [1, 5, 64])
 def test_chunked_prompt_equals_steps(orc_same_math, name, chunk):
     """Reading a prompt in chunks (token-parallel products, the recurrences in order inside their kernels) gives the

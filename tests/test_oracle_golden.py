@@ -465,12 +465,12 @@ def test_new_parts_start_as_no_change(orc):
     same bits."""
     from ava_b200 import config, synth
     base = config.tiny(head_size=64)
-    full = config.tiny(head_size=64, stp=1, dendrite=1, neuromod=3, thalamus=1, dopamine=1, mood=4, cb_units=512, letters=1)
+    full = config.tiny(head_size=64, stp=1, dendrite=1, neuromod=3, thalamus=1, dopamine=1, mood=4, cb_units=512, letters=1, rhythm=1)
     w0 = synth.model(base, 3, "awake")
     w1 = synth.model(full, 3, "awake")
     for k in w1:
         if k.endswith("parts.stp.mix") or k.endswith("v51.dend_b") or k.endswith("v51.da_w") or k.endswith("v51.da_c") or k.endswith("v51.mood_g") \
-                or k in ("nm.wn", "nm.bn", "th.gate", "th.bias", "cbh.wo", "v51.letters.wo"):  # nucleus and relay then send 2 sigmoid(0) = 1
+                or k in ("nm.wn", "nm.bn", "th.gate", "th.bias", "cbh.wo", "v51.letters.wo") or k.endswith("v51.rh_w") or k.endswith("v51.rh_r"):  # nucleus and relay then send 2 sigmoid(0) = 1
             w1[k] = np.zeros_like(w1[k])
     m0, m1 = orc.OracleModel(base, w0), orc.OracleModel(full, w1)
     s0, s1 = m0.state(2), m1.state(2)
@@ -610,3 +610,48 @@ def test_letters_follow_their_formula(orc):
             assert (np.abs(got - w["tok_emb"][tok]).max() > 1e-4) == (used > 0)
     finally:
         orc.trace_enable(False)
+
+
+def test_rhythm_clocks_follow_their_formula(orc):
+    """--rhythm (src/model/fstep/arch_f4.rs:47-92): each clock's time is (1 - reset) * (1 + time) with reset =
+    sigmoid(head_norm(x) wr + br), its phase time * exp(lw), the features cos and sin of the phases.  In f64 on the
+    carried times; with the reference's start (reset bias -10) the times count the tokens."""
+    from ava_b200 import config, synth
+    cfg = config.tiny(head_size=64, rhythm=1)
+    w = synth.model(cfg, 4, "awake")
+    st = orc.OracleModel(cfg, w).state(1)
+    ids = synth.token_ids(cfg["vocab"], 1, 8)
+    times = np.zeros(2)
+    orc.trace_enable(True)
+    try:
+        for t in range(8):
+            st.step(ids[:, t])
+            x = w["tok_emb"][ids[0, t]].astype(np.float64)
+            pre = (x / np.sqrt((x * x).mean() + 1e-5)) @ w["v51.rhythm.wr"].astype(np.float64) + w["v51.rhythm.br"]
+            times = (1.0 + times) / (1.0 + np.exp(pre))            # 1 - sigmoid(pre) = sigmoid(-pre)
+            assert np.allclose(st.get(0, "v51.rh"), times, rtol=2e-5, atol=0), t
+            ph = times * np.exp(w["v51.rhythm.lw"].astype(np.float64))
+            want = np.array([np.cos(ph[0]), np.sin(ph[0]), np.cos(ph[1]), np.sin(ph[1])])
+            assert np.allclose(orc.trace("rh_f", -1)[:4], want, rtol=0, atol=1e-4), t
+    finally:
+        orc.trace_enable(False)
+    quiet = dict(w)
+    quiet["v51.rhythm.wr"] = np.zeros_like(w["v51.rhythm.wr"])
+    quiet["v51.rhythm.br"] = np.full(2, -10.0, np.float32)
+    s2 = orc.OracleModel(cfg, quiet).state(1)
+    for t in range(8):
+        s2.step(ids[:, t])
+    assert np.allclose(s2.get(0, "v51.rh"), [8.0, 8.0], atol=2e-3)
+
+
+def test_shared_sine_and_cosine_are_correctly_rounded():
+    """The library's sine and cosine (double arithmetic, one rounding to float) against numpy's double results rounded to
+    float, over the range the phases take."""
+    from ava_b200 import engine
+    L = engine.lib()
+    rng = np.random.default_rng(0)
+    for scale in (1.0, 100.0, 1e4, 1e6):
+        for x in (rng.uniform(-scale, scale, 2000).astype(np.float32)):
+            assert L.ava_host_sinf(float(x)) == float(np.float32(np.sin(np.float64(x))))
+            assert L.ava_host_cosf(float(x)) == float(np.float32(np.cos(np.float64(x))))
+    assert L.ava_host_sinf(0.0) == 0.0 and L.ava_host_cosf(0.0) == 1.0 and np.isnan(L.ava_host_sinf(float("inf")))
