@@ -1683,7 +1683,10 @@ int ava_split_step_begin(ava_engine* e, ava_state* s, const uint32_t* tok_device
     int rc = check_pair(e, s);
     if (rc) return rc;
     if (!tok_device || !qkv_device || e->cfg.eng_block < 0) return e->fail(AVA_ERR_ARG, "bad arguments");
-    if ((rc = step_device(e, s, tok_device, nullptr, nullptr, false, 1, false, PHASE_BEGIN))) return rc;
+    // the second half of the step reads the token ids again (the surprise, the cerebellum's input): they are kept
+    if (tok_device != e->tok.as<uint32_t>())
+        CK(cudaMemcpyAsync(e->tok.p, tok_device, (size_t)s->rows * sizeof(uint32_t), cudaMemcpyDeviceToDevice, e->stream));
+    if ((rc = step_device(e, s, e->tok.as<uint32_t>(), nullptr, nullptr, false, 1, false, PHASE_BEGIN))) return rc;
     CK(cudaMemcpyAsync(qkv_device, e->eqkv.p, (size_t)s->rows * 3 * e->cfg.d * sizeof(float), cudaMemcpyDeviceToDevice, e->stream));
     return AVA_OK;
 }
@@ -1731,7 +1734,7 @@ int ava_split_step_end(ava_engine* e, ava_state* s, const float* gathered_device
     prof_begin(e, "engram.combine");
     launch_engram_combine(e->stream, gathered_device, s->rows, c.d / c.eng_head_size, c.eng_head_size, engram_segments(s->ring, seg_len), e->eo.as<float>(), world);
     prof_end(e);
-    return step_device(e, s, nullptr, logits_device, next_device, logits_device != nullptr, 1, false, PHASE_END);
+    return step_device(e, s, e->tok.as<uint32_t>(), logits_device, next_device, logits_device != nullptr, 1, false, PHASE_END);
 }
 
 void* ava_engine_stream(ava_engine* e) { return e ? (void*)e->stream : nullptr; }

@@ -14,13 +14,20 @@ def test_kv_owner_rule():
     assert [shard.kv_owner(p, 4, 3) for p in range(14)] == [0, 0, 0, 0, 1, 1, 1, 1, 2, 2, 2, 2, 2, 2]
 
 
-@pytest.mark.parametrize("world", [1, 2, 3])
-def test_split_store_decode_matches_the_oracle(orc, world):
+NINE_PARTS = dict(stp=1, neuromod=3, dendrite=1, dopamine=1, mood=4, thalamus=1, cb_units=512, letters=1, rhythm=1)
+
+
+@pytest.mark.parametrize("world,parts", [(1, False), (2, False), (3, False), (2, True)])
+def test_split_store_decode_matches_the_oracle(orc, world, parts):
     import torch
     build.build()
     orc.set_math(*engine.host_math())
     try:
-        cfg = config.tiny(eng_head_size=64, eng_store_bf16=1)
+        cfg = config.tiny(eng_head_size=64, eng_store_bf16=1, **(NINE_PARTS if parts else {}))
+        carried = [f"lif.{i}.{k}" for i in range(cfg["n_blocks"]) for k in "vsa"] + [f"mem.{i}.f" for i in range(cfg["n_blocks"])]
+        if parts:   # the step is cut in two at the engram: what the parts carry must survive the cut as well
+            carried += [f"parts.{i}.{k}" for i in range(cfg["n_blocks"]) for k in ("stp_u", "stp_x")]
+            carried += ["v51.prev", "v51.pvalid", "v51.last_s", "v51.mood", "v51.rh"]
         w = synth.model(cfg, 0, "awake")
         om = orc.OracleModel(cfg, w)
         prompt_len, decode = 37, 12
@@ -38,7 +45,7 @@ def test_split_store_decode_matches_the_oracle(orc, world):
         for sk in ranks:
             sk.take_prompt_store(k_full, v_full, prompt_len, block)
         # rank 0 continues from the prompt's membranes and fast weights
-        for name in [f"lif.{i}.{k}" for i in range(cfg["n_blocks"]) for k in "vsa"] + [f"mem.{i}.f" for i in range(cfg["n_blocks"])]:
+        for name in carried:
             ranks[0].state.put(0, name, full.get(0, name))
         dev = torch.device("cuda", 0)
         logits = torch.empty(1, cfg["vocab"], dtype=torch.float32, device=dev)
@@ -61,7 +68,7 @@ def test_split_store_decode_matches_the_oracle(orc, world):
             got = logits.cpu().numpy()
             np.testing.assert_allclose(got, want, rtol=0, atol=1e-4 * max(1.0, float(np.abs(want).max())), err_msg=f"token {t}")
             # keep both on one trajectory: rounding differences may flip a spike later on
-            for name in [f"lif.{i}.{k}" for i in range(cfg["n_blocks"]) for k in "vsa"] + [f"mem.{i}.f" for i in range(cfg["n_blocks"])]:
+            for name in carried:
                 ranks[0].state.put(0, name, os_.get(0, name))
         # every position is on exactly one rank, the decoded ones on the last
         counts = [sk.state.get(0, "eng.k").size // cfg["d"] for sk in ranks]
