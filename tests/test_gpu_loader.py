@@ -43,20 +43,36 @@ def run_both(orc, gm, om, cfg, rows, T, names):
     return gs
 
 
-@pytest.mark.parametrize("kind", ["S", "D"])
+NINE_PARTS = dict(stp=1, neuromod=3, dendrite=1, dopamine=1, mood=4, thalamus=1, cb_units=512, letters=1, rhythm=1)
+
+
+@pytest.mark.parametrize("kind", ["S", "D", "D with the nine Ava-0.4 parts"])
 def test_synthetic_checkpoint_runs_to_the_oracles_bits(orc_same_math, tmp_path, kind):
     orc = orc_same_math
-    cfg = config.kind_s(320, 128, 3) if kind == "S" else config.tiny(mem_momentum=0.5, head_size=64)
-    path = ckpt.save(str(tmp_path), cfg, synth.model(cfg, 2, "awake"))
+    parts = kind.startswith("D with")
+    kind = kind[0]
+    cfg = config.kind_s(320, 128, 3) if kind == "S" else config.tiny(mem_momentum=0.5, head_size=64, **(NINE_PARTS if parts else {}))
+    weights = synth.model(cfg, 2, "awake")
+    path = ckpt.save(str(tmp_path), cfg, weights)
     flags = ckpt.flags_of(cfg)
-    gm = engine.Model.from_checkpoint(path, kind, flags)
+    if parts:   # the model file has the parts' tensors under the reference's names; the spellings come from the tokenizer
+        assert all(w in flags for w in ("--stp", "--neuromod 3", "--dendrite", "--letters", "--dopamine", "--mood", "--rhythm", "--thalamus",
+                                        "--cerebellum-head 512"))
+    gm = engine.Model.from_checkpoint(path, kind, flags, token_bytes=weights.get("token_bytes"))
+    for k in NINE_PARTS:
+        assert gm.cfg[k] == cfg[k], k
     for k in ("d", "n_blocks", "hidden", "kwta_k", "head_size", "eng_block", "spikes", "alif", "theta", "fast_mem"):
         assert gm.cfg[k] == cfg[k], k
     ck = engine.Checkpoint(path)
-    om = orc.OracleModel(gm.cfg, {n: ck.get(n) for n in ck.names()})
+    ow = {n: ck.get(n) for n in ck.names()}
+    if parts:
+        ow["token_bytes"] = weights["token_bytes"]
+    om = orc.OracleModel(gm.cfg, ow)
     names = [f"lif.{i}.{k}" for i in range(cfg["n_blocks"]) for k in ("v", "s")]
     if kind == "D":
         names += ["mem.0.f", "mem.2.s", "eng.k"]
+    if parts:
+        names += ["parts.1.stp_x", "v51.prev", "v51.last_s", "v51.mood", "v51.rh"]
     gs = run_both(orc, gm, om, gm.cfg, rows=3, T=40, names=names)
     assert (gs.get(0, "lif.1.s") != 0).any()
 

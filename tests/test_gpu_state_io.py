@@ -20,7 +20,9 @@ def _lib():
 
 
 @pytest.mark.parametrize("name,kw", [("ava04_small", dict()), ("momentum_bf16", dict(mem_momentum=0.5, head_size=64, eng_store_bf16=1)),
-                                     ("capped", dict(eng_cap=6)), ("stp", dict(stp=1)), ("kind_s", None)])
+                                     ("capped", dict(eng_cap=6)), ("stp", dict(stp=1)), ("kind_s", None),
+                                     ("nine_parts", dict(stp=1, neuromod=3, dendrite=1, dopamine=1, mood=4, thalamus=1, cb_units=512, letters=1,
+                                                         rhythm=1, head_size=64, mem_momentum=0.5))])
 def test_saved_state_continues_bit_for_bit(tmp_path, name, kw):
     cfg = config.kind_s(320, 128, 3) if kw is None else config.tiny(**kw)
     m = engine.Model(cfg, synth.model(cfg, 1, "awake"))
@@ -47,6 +49,9 @@ def test_saved_state_continues_bit_for_bit(tmp_path, name, kw):
     assert ck.get("lif.1.v").shape == (rows, d) and ck.get("meta.hist").shape == (rows, 17)
     if cfg["stp"]:
         assert ck.get("parts.0.stp_u").shape == (rows, d) and (ck.get("parts.1.stp_x") != 1.0).any()
+    if cfg["mood"]:   # the reference's names and shapes for what the surprise, the mood and the clocks carry (src/v51.rs:1012)
+        assert ck.get("v51.prev").shape == (rows, d) and ck.get("v51.pvalid").tolist() == [1.0] * rows and ck.get("v51.last_s").shape == (rows,)
+        assert ck.get("v51.mood").shape == (rows, cfg["mood"]) and ck.get("v51.rh").shape == (rows, 2) and (ck.get("v51.rh") > 0).all()
     if cfg["fast_mem"]:
         hs = cfg["head_size"]
         assert ck.get("mem.0.f").shape == (rows * d // hs, hs, hs)
