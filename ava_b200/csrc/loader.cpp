@@ -451,7 +451,14 @@ int ava_config_from_ckpt(const ava_ckpt* c, const char* kind, const char* arch_f
         int b;
         std::string rest;
         if (!block_name(e.name, &b, &rest)) {
-            if (e.name != "tok_emb" && e.name != "final.norm" && e.name != "nm.norm" && e.name != "nm.wn" && e.name != "nm.bn" && e.name != "th.read" && e.name != "th.gate" && e.name != "th.bias" && e.name.rfind("v51.mood.", 0) != 0 && e.name != "cbh.wo" && e.name.rfind("v51.letters.", 0) != 0 && e.name.rfind("v51.rhythm.", 0) != 0)
+            // tensors outside the blocks: the embedding and final norm, and the covered parts' own (nucleus, relay,
+            // cerebellum read-out, mood, letters, rhythm)
+            static const char* const whole[] = {"tok_emb", "final.norm", "nm.norm", "nm.wn", "nm.bn", "th.read", "th.gate", "th.bias", "cbh.wo"};
+            static const char* const prefix[] = {"v51.mood.", "v51.letters.", "v51.rhythm."};
+            bool known = false;
+            for (const char* n : whole) known |= e.name == n;
+            for (const char* p : prefix) known |= e.name.rfind(p, 0) == 0;
+            if (!known)
                 return fail(AVA_NOT_APPLICABLE, e.name + ": a tensor of a part the engine does not cover (glance, magnitude code, order head)");
             continue;
         }

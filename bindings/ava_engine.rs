@@ -61,6 +61,8 @@ extern "C" {
     pub fn ava_engine_destroy(e: *mut AvaEngine);
     pub fn ava_last_error(e: *const AvaEngine) -> *const c_char;
     pub fn ava_engine_set_f32(e: *mut AvaEngine, name: *const c_char, data: *const f32, n: i64) -> c_int;
+    /// --letters: every token's spelling, bytes[offsets[t]..offsets[t + 1]] (vocab + 1 offsets), before finalize
+    pub fn ava_engine_set_token_bytes(e: *mut AvaEngine, bytes: *const u8, offsets: *const i64) -> c_int;
     pub fn ava_engine_set_q8(e: *mut AvaEngine, name: *const c_char, q: *const i8, scale: *const f32, din: i32, dout: i32) -> c_int;
     pub fn ava_engine_set_q8_from_f32(e: *mut AvaEngine, name: *const c_char, w: *const f32, din: i32, dout: i32) -> c_int;
     pub fn ava_engine_finalize(e: *mut AvaEngine) -> c_int;
