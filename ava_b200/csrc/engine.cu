@@ -130,6 +130,7 @@ struct ava_engine {
     Dev sur_xf, sur_in, sur_logits, sur_s, sur_z, mood_all, mood_gain, y2;
     Dev cb_emb, cb_en, cb_h, cb_a, cb_lj, cb_lc, cb_n;  // --cerebellum-head: embedding rows (raw, normed) [rows][d], units and kept units
                                                         // [rows][G], the code's list [rows][G] twice, its length [rows]
+    Dev side;                // [rows][d] scratch of the token trace's side-band (only while intermediates are kept)
     Dev rh_f, rh_gw, rh_gr;  // --rhythm: phase features [rows][4], the block's gains per head [rows][heads] twice
     Dev th_acc, th_g, x_in;  // --thalamus: the relay's sum [rows][16], the block's gates [rows][4], the block's input [rows][d]
     Dev ctx, dz1, ones;  // --dendrite: the block's memory read [rows][d], its projection [rows][32], a vector of ones [d]
@@ -635,9 +636,14 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         mp.ach = (c.neuromod > 0 && i > 0) ? e->sig.as<float>() + 1 : nullptr;
         mp.ach_stride = 4;
         mp.status = e->status.as<uint32_t>();
+        if (e->keep) {
+            if (e->side.bytes < Md * sizeof(float)) CK(e->side.alloc(Md * sizeof(float)));
+            mp.be_out = e->side.as<float>();
+        }
         prof_begin(e, "mem_prep");
         launch_mem_prep(st, mp);
         prof_end(e);
+        if (e->keep) dbg(e, "be", i, e->side.as<float>(), M, d);
         e->launches += 2;  // the two stages of the gate projections before it
         dbg(e, "ek", i, mp.e, M, d); dbg(e, "v", i, mp.v, M, d); dbg(e, "w", i, mp.w, M, d); dbg(e, "ah", i, mp.ah, M, d);
         dbg(e, "qg", i, mp.qg, M, d); dbg(e, "ex", i, mp.ex, M, d); dbg(e, "qw", i, mp.qw, M, nh); dbg(e, "qa", i, mp.qa, M, nh);
@@ -732,7 +738,15 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
             }
             ea.o = e->eo.as<float>();
             dbg(e, "eng_o", i, ea.o, M, d);
-            gemm(e, "gemm.eng_wo", ea.o, d, b.ewo, x, d, M, EPI_ADD);
+            if (e->keep) {
+                // the read as it is added (the token trace shows it): the same product stored, then the same addition
+                if (e->side.bytes < Md * sizeof(float)) CK(e->side.alloc(Md * sizeof(float)));
+                gemm(e, "gemm.eng_wo", ea.o, d, b.ewo, e->side.as<float>(), d, M, EPI_STORE);
+                dbg(e, "eng_r", i, e->side.as<float>(), M, d);
+                launch_add_into(st, x, e->side.as<float>(), (int64_t)Md);
+            } else {
+                gemm(e, "gemm.eng_wo", ea.o, d, b.ewo, x, d, M, EPI_ADD);
+            }
             dbg(e, "x_eng", i, x, M, d);
         }
 

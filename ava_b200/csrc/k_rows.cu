@@ -534,6 +534,7 @@ __global__ void mem_prep_kernel(const MemPrepArgs a) {
         a.ah[o] = ah;
         a.qg[o] = qg;
         a.ex[o] = ex;
+        if (a.be_out) a.be_out[o] = be;
         if (a.qs) a.qs[o] = mul(qn, add(mul(1.0f, a.mom), 0.0f));  // q * (1 * M + 0) (src/model/fstep/arch.rs:784)
         q[c] = qn;
         wv[c] = w;

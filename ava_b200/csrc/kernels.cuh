@@ -146,6 +146,7 @@ struct MemPrepArgs {
     const float* gate_w; // [d][gate_cols]: wa1 | wb1 | wa | wb side by side, columns padded with zeros to a multiple of 4
     int gate_cols;       // padded column count (at most 256: one chain per thread)
     int gate_chunk;      // rows staged per copy; divides d, a multiple of 8
+    float* be_out;       // the write strength b [M, d] as the update uses it (the token trace's side-band), or nullptr
     const float* rh_w;   // --rhythm: the write strength times rh_w[row * heads + head] before ACh; or nullptr
     const float* ach;    // --neuromod ACh: the write strength times ach[row * ach_stride], kept in [0, 2]; or nullptr
     int ach_stride;

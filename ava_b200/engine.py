@@ -89,6 +89,9 @@ def lib() -> C.CDLL:
         "ava_state_bytes": ([vp], C.c_int64),
         "ava_engine_set_segmented_read": ([vp, C.c_int32], C.c_int),
         "ava_engine_set_fast_products": ([vp, C.c_int32], C.c_int),
+        "ava_step_trace": ([vp, vp, C.c_uint32, fp, C.POINTER(vp)], C.c_int),
+        "ava_trace_get": ([vp, C.c_char_p, C.c_int32, fp, C.c_int64], C.c_int64),
+        "ava_trace_free": ([vp], None),
         "ava_prof_enable": ([vp, C.c_int32], C.c_int),
         "ava_prof_read": ([vp, C.c_char_p, C.POINTER(C.c_int64), C.POINTER(C.c_double)], C.c_int),
         "ava_prof_names": ([vp, C.c_char_p, C.c_int32], C.c_int),
@@ -156,7 +159,7 @@ EXPORTS = ("ava_engine_create ava_engine_destroy ava_last_error ava_engine_set_f
            "ava_state_import ava_step ava_step_greedy ava_forward_with_state ava_step_device ava_prefill_device ava_state_set_kv_shard ava_shard_parts ava_split_step_begin ava_shard_partial ava_split_step_end ava_sync "
            "ava_engine_stream ava_engine_launches ava_engine_bytes ava_state_bytes ava_debug_keep ava_debug_width "
            "ava_debug_get ava_engine_set_segmented_read ava_engine_set_fast_products ava_prof_enable ava_prof_read ava_prof_names ava_engine_fingerprint ava_state_engine ava_state_set_seen ava_state_save ava_state_load ava_ckpt_read_u32 ava_conv_path ava_conv_save ava_conv_load ava_step_sample ava_generate_sampled ava_op_sample ava_engine_device ava_engine_config ava_splitmix64_next ava_pick ava_generate ava_loader_error ava_ckpt_open ava_ckpt_close ava_ckpt_count ava_ckpt_find ava_ckpt_tensor ava_ckpt_read_f32 ava_arch_flags ava_config_from_ckpt ava_engine_load_ckpt ava_op_q8_matmul ava_op_q8_event_matmul ava_op_q8_tc_matmul ava_debug_mem_heads_timeline ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
-           "ava_host_expf ava_host_logf ava_host_rsqrtf ava_host_sinf ava_host_cosf ava_op_math").split()
+           "ava_host_expf ava_host_logf ava_host_rsqrtf ava_host_sinf ava_host_cosf ava_op_math ava_step_trace ava_trace_get ava_trace_free").split()
 
 
 def _f32(a):
@@ -454,6 +457,32 @@ class Model:
             raise errors[0]
         self._check(rc)
         return [out[r, :out_len[r]].tolist() for r in range(len(prompts))]
+
+    def step_trace(self, st: "State", tok: int):
+        """`Model::step_trace`: one token of a one-row state; (logits [vocab], get(name, block) -> f32 array)."""
+        L = lib()
+        logits = np.empty(self.cfg["vocab"], np.float32)
+        h = C.c_void_p()
+        self._check(L.ava_step_trace(self.h, st.h, int(tok), _p(logits), C.byref(h)))
+        rec = {}
+
+        def get(name: str, block: int) -> np.ndarray:
+            n = L.ava_trace_get(h, name.encode(), block, None, 0)
+            if n < 0:
+                raise KeyError((name, block))
+            a = np.empty(n, np.float32)
+            L.ava_trace_get(h, name.encode(), block, _p(a), n)
+            return a
+        try:
+            for blk in range(-1, self.cfg["n_blocks"]):
+                for name in ("input_rms", "spikes", "winners", "hidden", "mem_write", "mem_read", "mem_keep", "mem_gate", "engram_attn", "engram_read"):
+                    try:
+                        rec[(name, blk)] = get(name, blk)
+                    except KeyError:
+                        pass
+        finally:
+            L.ava_trace_free(h)
+        return logits, rec
 
     def step_greedy(self, st: "State", tok) -> np.ndarray:
         tok = np.ascontiguousarray(tok, np.uint32).reshape(-1)

@@ -208,6 +208,18 @@ int ava_split_step_begin(ava_engine* e, ava_state* s, const uint32_t* tok_device
 int ava_shard_partial(ava_engine* e, ava_state* s, const float* qkv_device, float* partial_device);
 int ava_split_step_end(ava_engine* e, ava_state* s, const float* gathered_device, int32_t world, float* logits_device, uint32_t* next_device);
 
+/* One traced token of a one-row state: `Model::step_trace` (src/model.rs, record built in src/model/fstep/arch.rs:420-476,
+ * the chat app's event feed).  The step is the plain one (same logits, same state); the record holds copies of what it
+ * computed and sizes taken from those copies on the host.  ava_trace_get(name, block): per block "spikes" [d] as they reach
+ * W_out, "winners" [hidden] 0/1, "hidden" [hidden] as it reaches W2, and per memory head "mem_write" (|F' - alpha F|),
+ * "mem_read" (|y| before its norm), "mem_keep" (mean alpha), "mem_gate" (mean write strength); at the engram's block
+ * "engram_attn" [heads, keys] (this token's key last) and "engram_read" [d]; block -1 "input_rms" [1].  Returns the
+ * value count (copying up to cap floats when out is not NULL) or -1.  AVA_NOT_APPLICABLE with a capped engram store. */
+typedef struct ava_trace ava_trace;
+int ava_step_trace(ava_engine* e, ava_state* s, uint32_t tok, float* logits, ava_trace** out);
+int64_t ava_trace_get(const ava_trace* t, const char* name, int32_t block, float* out, int64_t cap);
+void ava_trace_free(ava_trace* t);
+
 /* Section clock, as the reference's fused step keeps one (`take_secs`, src/model/fstep/arch.rs:131-165, switched by
  * `int8::set_mm_prof`, src/int8.rs:635-640): with it on, every kernel launch is bracketed by CUDA events on the
  * engine's stream.  ava_prof_read waits for the stream and returns one kernel's launches and total milliseconds since

@@ -884,7 +884,7 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
         }
         const bool mix_v = cfg.value_residual && i > 0 && !b.vres.empty();
         std::vector<float> y((size_t)R * d);
-        struct Tr { std::vector<float> k, ek, w, ah, qg, ex, yraw, qw, qa; } tr;
+        struct Tr { std::vector<float> k, ek, w, ah, qg, ex, yraw, qw, qa, be; } tr;
 #pragma omp parallel for num_threads(nt) schedule(static)
         for (int r = 0; r < R; ++r) {
             float* qr = &q[(size_t)r * d];
@@ -929,6 +929,7 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
             for (int e = 0; e < nh && !bad_row; ++e) {
                 const int o = e * hs;
                 std::vector<float> la(hs), be(hs), qs, p2, e0(hs);
+                if (trace && r == 0 && e == 0) tr.be.assign(d, 0.f);
                 for (int c = 0; c < hs; ++c) {
                     la[c] = log_sigmoid((za[e] + b.off[o + c]) + lra[o + c]);
                     be[c] = sigmoid(zb[e] + lrb[o + c]) * 2.0f + 0.0f;
@@ -939,6 +940,7 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
                         be[c] = v > 2.0f ? 2.0f : v;
                     }
                 }
+                if (trace && r == 0) std::copy(be.begin(), be.end(), tr.be.begin() + o);
                 for (int c = 0; c < hs; ++c) ek[o + c] = kr[o + c] + weo[(size_t)r * d + o + c];
                 l2_heads(ek.data() + o, hs, hs);
                 for (int c = 0; c < hs; ++c) {
@@ -1003,7 +1005,7 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
         if (trace) {
             T("q", i, q.data(), d); T("k", i, tr.k.data(), d); T("v", i, v.data(), d); T("ek", i, tr.ek.data(), d); T("w", i, tr.w.data(), d);
             T("ah", i, tr.ah.data(), d); T("qg", i, tr.qg.data(), d); T("ex", i, tr.ex.data(), d); T("qw", i, tr.qw.data(), nh);
-            T("qa", i, tr.qa.data(), nh); T("y_raw", i, tr.yraw.data(), d); T("y", i, y.data(), d);
+            T("qa", i, tr.qa.data(), nh); T("y_raw", i, tr.yraw.data(), d); T("y", i, y.data(), d); T("be", i, tr.be.data(), d);
         }
         q8_matmul(b.wo, y.data(), R, tmp.data());
         if (cfg.dendrite) ctx.assign(tmp.begin(), tmp.begin() + (size_t)R * d);  // P: the memory's read, the dendrites' context
@@ -1068,6 +1070,7 @@ int step_rows(const orc_model* m, RowState** rows, int R, const uint32_t* tok, f
             eng_written = true;
             T("eng_o", i, o.data(), d);
             q8_matmul(b.ewo, o.data(), R, tmp.data());
+            T("eng_r", i, tmp.data(), d);
             add_into(x.data(), tmp.data(), R * d);
             T("x_eng", i, x.data(), d);
         }
