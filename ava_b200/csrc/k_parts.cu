@@ -1,7 +1,8 @@
-// --dopamine and --mood: the surprise at each token and what follows from it (src/model/fstep/arch_f3.rs:106-186,
-// src/model/fstep/arch_f4.rs:131-143).  Every value is the one the reference's one-token step computes: the cross
+// Kernels of the Ava-0.4 parts that hang off the surprise and the clocks: --dopamine and --mood (the surprise at each
+// token and what follows from it: src/model/fstep/arch_f3.rs:106-186, src/model/fstep/arch_f4.rs:131-143) and --rhythm
+// (src/model/fstep/arch_f4.rs:39-108).  Every value is the one the reference's one-token step computes: the cross
 // entropy of the head's logits for block 0's normed output at the position before, with the exponentials summed in
-// index order by one thread (the reference's loop), the mood's one-step scan token after token.
+// index order by one thread (the reference's loop); the mood's and the clocks' one-step scans token after token.
 #include <cmath>
 
 #include "ava_math.h"
