@@ -172,6 +172,7 @@ def main():
     ap.add_argument("--small", action="store_true", help="a small model and batch (profiling captures, not a bench value)")
     ap.add_argument("--scaled", action="store_true", help="benchmark configuration 3: 24 blocks, d 2048, wide 8192, vocab 32768 (use --rows 128: an 8-GPU share of 1024 sequences)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--parts", action="store_true", help="the same workload with the nine Ava-0.4 parts switched on (their cost; not the headline configuration)")
     ap.add_argument("--prefill-tokens", type=int, default=1024, help="tokens per row of the prompt-reading sample (config 2: 8192)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
@@ -186,6 +187,8 @@ def main():
         cfg = config.make(4096, 768, 2, head_size=768, eng_block=1, eng_head_size=64, eng_store_bf16=1)
     if args.scaled:
         cfg = config.ava04_shaped(scaled=True)
+    if args.parts:
+        cfg = dict(cfg, stp=1, neuromod=3, dendrite=1, letters=1, dopamine=1, mood=4, rhythm=1, thalamus=1, cb_units=12288)
 
     if args.impl == "reference":
         run_reference(args, cfg, rank)
@@ -341,6 +344,7 @@ def main():
                                "fast-synapse matrix per block, bf16 engram of 12x64 in block 6)" if not (args.small or args.scaled) else
                    ("small profiling case" if args.small else "benchmark configuration 3: scaled Ava (24 blocks, d 2048, wide 8192, kWTA 2048, vocab 32768, one "
                     "2048x2048 f32 fast-synapse matrix per block)"),
+                   "parts": "the nine Ava-0.4 parts on (stp, neuromod 3, dendrite, letters, dopamine, mood, rhythm, thalamus, cerebellum head 12288)" if args.parts else "none",
                    "rows_per_gpu": rows, "kv_len_timed": [prompt + W, prompt + W + K], "l2": "per-step inputs (state "
                    f"{state.nbytes / 1e9:.2f} GB per GPU) are larger than L2", "sequences": "independent, sharded by rank, no collective"},
         "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": rows * 4, "d2h_bytes_per_step": rows * cfg["vocab"] * 4,
