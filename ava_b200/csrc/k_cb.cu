@@ -94,12 +94,21 @@ __global__ void cb_read_kernel(const int* __restrict__ list_j, const float* __re
     const float* lc = list_c + r * g;
     float corr = 0.0f;
     bool any = false;
-    for (int e = 0; e < n; ++e) {
-        const float c = lc[e];
-        if (c != 0.0f) {
-            corr = add(corr, mul(W[(size_t)lj[e] * d + ch], c));
-            any = true;
+    // eight rows of the read-out in flight while the chain adds the eight before them (a slot past the list has code 0)
+    for (int e0 = 0; e0 < n; e0 += 8) {
+        float c[8], w[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int e = e0 + u;
+            c[u] = e < n ? lc[e] : 0.0f;
+            w[u] = W[(size_t)(e < n ? lj[e] : 0) * d + ch];
         }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (c[u] != 0.0f) {
+                corr = add(corr, mul(w[u], c[u]));
+                any = true;
+            }
     }
     if (!any) corr = add(corr, mul(W[ch], 0.0f));
     xf[i] = add(xf[i], corr);
