@@ -91,7 +91,29 @@ void quantize_int8(const float* w, int rows, int cols, int8_t* q, float* scale) 
 }  // namespace
 
 // ================================================================================================ engine
-struct ava_engine {
+// The work buffers of one lane of rows.  The engine itself is lane 0; a decode step of a large batch may run its rows
+// as several lanes, each a contiguous window of the state's rows with buffers and a stream of its own, so that one
+// lane's latency-bound kernels run beside another lane's.
+struct Work {
+    int ws_rows = 0;
+    Dev x, h, proj, ve, vv, vw, vah, vqg, vex, vqs, qw, qa, yraw, y, eqkv, eo, u, act, streams, v_first;
+    Dev gz, lra, lrb;  // the gates' stages: [rows][gate_cols], [rows][d] twice
+    Dev sig;           // --neuromod: [rows][4] NE, ACh, DA (and one unused) of the step's token-rows
+    // --dopamine / --mood: block 0's normed output [rows][d], the rows the head reads (the position before each), the
+    // head's logits for them [rows][vocab], surprise s and z [rows], moods [rows][k], the current's gain and the MLP's output [rows][d]
+    Dev sur_xf, sur_in, sur_logits, sur_s, sur_z, mood_all, mood_gain, y2;
+    Dev cb_emb, cb_en, cb_h, cb_a, cb_lj, cb_lc, cb_n;  // --cerebellum-head: embedding rows (raw, normed) [rows][d], units and kept units
+                                                        // [rows][G], the code's list [rows][G] twice, its length [rows]
+    Dev side;                // [rows][d] scratch of the token trace's side-band (only while intermediates are kept)
+    Dev rh_f, rh_gw, rh_gr;  // --rhythm: phase features [rows][4], the block's gains per head [rows][heads] twice
+    Dev th_acc, th_g, x_in;  // --thalamus: the relay's sum [rows][16], the block's gates [rows][4], the block's input [rows][d]
+    Dev ctx, dz1;        // --dendrite: the block's memory read [rows][d], its projection [rows][32]
+    Dev eng_partial;         // [rows][heads][segments][2 + hs] partial softmax statistics of the segmented read
+    cudaStream_t lane_stream = nullptr;  // lanes after the first: the stream their kernels are queued on
+    cudaEvent_t lane_done = nullptr;
+};
+
+struct ava_engine : Work {
     ava_config cfg{};
     int device = 0;
     int sm_count = 148;
@@ -119,25 +141,20 @@ struct ava_engine {
     int cw = 0, rb = 0;  // fast-weight slice width and rows per bulk copy
     int gate_cols = 0, gate_chunk = 0;  // the gates' projection matrix: padded columns, rows per staged chunk
 
-    // work buffers for `ws_rows` rows
-    int ws_rows = 0, ws_logit_rows = 0;
-    Dev x, h, proj, ve, vv, vw, vah, vqg, vex, vqs, qw, qa, yraw, y, eqkv, eo, u, act, streams, v_first, logits, tok, next, status;
-    Dev gz, lra, lrb;  // the gates' stages: [rows][gate_cols], [rows][d] twice
+    // the engine's own (lane 0's) work buffers are the members of Work; these belong to the engine as a whole
+    int ws_logit_rows = 0;
+    Dev logits, tok, next, status;
     Dev uniform;       // [rows] f64: the sampler's draws of one step
-    Dev sig;           // --neuromod: [rows][4] NE, ACh, DA (and one unused) of the step's token-rows
-    // --dopamine / --mood: block 0's normed output [rows][d], the rows the head reads (the position before each), the
-    // head's logits for them [rows][vocab], surprise s and z [rows], moods [rows][k], the current's gain and the MLP's output [rows][d]
-    Dev sur_xf, sur_in, sur_logits, sur_s, sur_z, mood_all, mood_gain, y2;
-    Dev cb_emb, cb_en, cb_h, cb_a, cb_lj, cb_lc, cb_n;  // --cerebellum-head: embedding rows (raw, normed) [rows][d], units and kept units
-                                                        // [rows][G], the code's list [rows][G] twice, its length [rows]
-    Dev side;                // [rows][d] scratch of the token trace's side-band (only while intermediates are kept)
-    Dev rh_f, rh_gw, rh_gr;  // --rhythm: phase features [rows][4], the block's gains per head [rows][heads] twice
-    Dev th_acc, th_g, x_in;  // --thalamus: the relay's sum [rows][16], the block's gates [rows][4], the block's input [rows][d]
-    Dev ctx, dz1, ones;  // --dendrite: the block's memory read [rows][d], its projection [rows][32], a vector of ones [d]
+    Dev ones;          // a vector of ones [d] (the gain of a plain RMS norm)
+    std::vector<std::unique_ptr<Work>> more_lanes;  // lanes 1, 2, ... (lane 0 is the engine itself)
+    bool gemm2 = false;                             // dense products through the packed-weight kernel (k_gemm2.cu)
+    int n_lanes = 1;                                // lanes a decode step of enough rows is split into
+    cudaEvent_t fork_ev = nullptr;
+    cudaStream_t cur = nullptr;                     // the stream the launch helpers queue on (the lane being queued)
     uint32_t* status_host = nullptr;  // pinned
 
     bool prof = false;
-    struct Pending { const char* cls; cudaEvent_t a, b; };
+    struct Pending { const char* cls; cudaEvent_t a, b; cudaStream_t st; };
     std::vector<Pending> prof_pending;
     std::map<std::string, std::pair<int64_t, double>> prof_total;  // kernel -> (launches, milliseconds)
 
@@ -147,7 +164,6 @@ struct ava_engine {
     int limbs_rows = 0;
 
     int long_seg = 0;      // > 0: the engram is always read in segments of this many keys (else only when it must be)
-    Dev eng_partial;       // [rows][heads][segments][2 + hs] partial softmax statistics of the segmented read
 
     bool keep = false;
     std::map<std::pair<std::string, int>, std::unique_ptr<Dev>> debug;
@@ -328,73 +344,76 @@ const char* find_blocker(const ava_config& c, int* cw, int* rb) {
     if (c.cb_units < 0 || c.cb_units % 32) return "cerebellum head: a multiple of 32 units";
     if (c.rhythm && !c.fast_mem) return "rhythm: a part of the blocks with the fast-weight memory";
     if (c.thalamus && !c.fast_mem) return "thalamus: a part of the blocks with the fast-weight memory";
+    if ((c.dopamine || c.mood > 0) && c.vocab > SURPRISE_MAX_VOCAB) return "dopamine / mood: the surprise kernel holds a vocabulary of up to 56320 in shared memory";
     if (c.fast_mem && (c.head_size % 16 || !mem_heads_tiling(c.head_size, cw, rb, c.mem_momentum > 0.0f))) return "memory head size not covered (a multiple of 16 whose column slice fits shared memory)";
     return nullptr;
 }
 
-int ensure_workspace(ava_engine* e, int rows, int logit_rows = 0) {
+int ensure_workspace(ava_engine* e, Work& w, int rows, int logit_rows = 0) {
     if (logit_rows > e->ws_logit_rows) {
         CK(e->logits.alloc((size_t)logit_rows * e->cfg.vocab * sizeof(float)));
         e->ws_logit_rows = logit_rows;
     }
-    if (rows <= e->ws_rows) return AVA_OK;
+    if (rows <= w.ws_rows) return AVA_OK;
     const ava_config& c = e->cfg;
     const size_t M = rows, d = c.d, f = sizeof(float);
-    CK(e->x.alloc(M * d * f));
-    CK(e->h.alloc(M * d * f));
-    CK(e->proj.alloc(M * e->proj_w() * f));
-    for (Dev* b : {&e->ve, &e->vv, &e->vw, &e->vah, &e->vqg, &e->vex, &e->yraw, &e->y, &e->eo, &e->v_first}) CK(b->alloc(M * d * f));
-    if (c.mem_momentum > 0.0f) CK(e->vqs.alloc(M * d * f));
-    CK(e->gz.alloc(M * std::max(e->gate_cols, 16) * f));
-    CK(e->lra.alloc(M * d * f));
-    CK(e->lrb.alloc(M * d * f));
-    CK(e->qw.alloc(M * e->nh() * f));
-    CK(e->qa.alloc(M * e->nh() * f));
-    CK(e->eqkv.alloc(M * 3 * d * f));
-    CK(e->u.alloc(M * c.hidden * f));
-    CK(e->act.alloc(M * c.hidden * f));
-    CK(e->streams.alloc(c.dense ? (size_t)(c.n_blocks + 1) * M * d * f : 0));
-    CK(e->tok.alloc(M * sizeof(uint32_t)));
-    CK(e->next.alloc(M * sizeof(uint32_t)));
-    CK(e->uniform.alloc(M * sizeof(double)));
-    if (c.neuromod > 0) CK(e->sig.alloc(M * 4 * f));
+    CK(w.x.alloc(M * d * f));
+    CK(w.h.alloc(M * d * f));
+    CK(w.proj.alloc(M * e->proj_w() * f));
+    for (Dev* b : {&w.ve, &w.vv, &w.vw, &w.vah, &w.vqg, &w.vex, &w.yraw, &w.y, &w.eo, &w.v_first}) CK(b->alloc(M * d * f));
+    if (c.mem_momentum > 0.0f) CK(w.vqs.alloc(M * d * f));
+    CK(w.gz.alloc(M * std::max(e->gate_cols, 16) * f));
+    CK(w.lra.alloc(M * d * f));
+    CK(w.lrb.alloc(M * d * f));
+    CK(w.qw.alloc(M * e->nh() * f));
+    CK(w.qa.alloc(M * e->nh() * f));
+    CK(w.eqkv.alloc(M * 3 * d * f));
+    CK(w.u.alloc(M * c.hidden * f));
+    CK(w.act.alloc(M * c.hidden * f));
+    CK(w.streams.alloc(c.dense ? (size_t)(c.n_blocks + 1) * M * d * f : 0));
+    if (&w == static_cast<Work*>(e)) {  // the engine's own token, next-token and draw buffers cover all lanes' rows
+        CK(e->tok.alloc(M * sizeof(uint32_t)));
+        CK(e->next.alloc(M * sizeof(uint32_t)));
+        CK(e->uniform.alloc(M * sizeof(double)));
+    }
+    if (c.neuromod > 0) CK(w.sig.alloc(M * 4 * f));
     if (c.dopamine || c.mood > 0) {
-        CK(e->sur_xf.alloc(M * d * f));
-        CK(e->sur_in.alloc(M * d * f));
-        CK(e->sur_logits.alloc(M * c.vocab * f));
-        CK(e->sur_s.alloc(M * f));
-        CK(e->sur_z.alloc(M * f));
+        CK(w.sur_xf.alloc(M * d * f));
+        CK(w.sur_in.alloc(M * d * f));
+        CK(w.sur_logits.alloc(M * c.vocab * f));
+        CK(w.sur_s.alloc(M * f));
+        CK(w.sur_z.alloc(M * f));
         if (c.mood > 0) {
-            CK(e->mood_all.alloc(M * c.mood * f));
-            CK(e->mood_gain.alloc(M * d * f));
+            CK(w.mood_all.alloc(M * c.mood * f));
+            CK(w.mood_gain.alloc(M * d * f));
         }
-        if (c.dopamine) CK(e->y2.alloc(M * d * f));
+        if (c.dopamine) CK(w.y2.alloc(M * d * f));
     }
     if (c.cb_units > 0) {
         const size_t G = c.cb_units;
-        CK(e->cb_emb.alloc(M * d * f));
-        CK(e->cb_en.alloc(M * d * f));
-        CK(e->cb_h.alloc(M * G * f));
-        CK(e->cb_a.alloc(M * G * f));
-        CK(e->cb_lj.alloc(M * G * sizeof(int)));
-        CK(e->cb_lc.alloc(M * G * f));
-        CK(e->cb_n.alloc(M * sizeof(int)));
+        CK(w.cb_emb.alloc(M * d * f));
+        CK(w.cb_en.alloc(M * d * f));
+        CK(w.cb_h.alloc(M * G * f));
+        CK(w.cb_a.alloc(M * G * f));
+        CK(w.cb_lj.alloc(M * G * sizeof(int)));
+        CK(w.cb_lc.alloc(M * G * f));
+        CK(w.cb_n.alloc(M * sizeof(int)));
     }
     if (c.rhythm) {
-        CK(e->rh_f.alloc(M * 4 * f));
-        CK(e->rh_gw.alloc(M * e->nh() * f));
-        CK(e->rh_gr.alloc(M * e->nh() * f));
+        CK(w.rh_f.alloc(M * 4 * f));
+        CK(w.rh_gw.alloc(M * e->nh() * f));
+        CK(w.rh_gr.alloc(M * e->nh() * f));
     }
     if (c.thalamus) {
-        CK(e->th_acc.alloc(M * 16 * f));
-        CK(e->th_g.alloc(M * 4 * f));
-        CK(e->x_in.alloc(M * d * f));
+        CK(w.th_acc.alloc(M * 16 * f));
+        CK(w.th_g.alloc(M * 4 * f));
+        CK(w.x_in.alloc(M * d * f));
     }
     if (c.dendrite && c.fast_mem) {
-        CK(e->ctx.alloc(M * d * f));
-        CK(e->dz1.alloc(M * 32 * f));
+        CK(w.ctx.alloc(M * d * f));
+        CK(w.dz1.alloc(M * 32 * f));
     }
-    e->ws_rows = rows;
+    w.ws_rows = rows;
     return AVA_OK;
 }
 
@@ -404,13 +423,13 @@ void prof_begin(ava_engine* e, const char* cls) {
     if (!e->prof) return;
     cudaEvent_t a, b;
     if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
-    cudaEventRecord(a, e->stream);
-    e->prof_pending.push_back({cls, a, b});
+    cudaEventRecord(a, e->cur);
+    e->prof_pending.push_back({cls, a, b, e->cur});
 }
 void prof_end(ava_engine* e) {
     e->launches++;
     if (!e->prof || e->prof_pending.empty()) return;
-    cudaEventRecord(e->prof_pending.back().b, e->stream);
+    cudaEventRecord(e->prof_pending.back().b, e->cur);
 }
 
 void dbg(ava_engine* e, const char* name, int block, const float* src, int rows, int64_t width) {
@@ -419,7 +438,7 @@ void dbg(ava_engine* e, const char* name, int block, const float* src, int rows,
     if (!slot) slot.reset(new Dev());
     const size_t bytes = (size_t)rows * width * sizeof(float);
     if (slot->bytes != bytes) slot->alloc(bytes);
-    cudaMemcpyAsync(slot->p, src, bytes, cudaMemcpyDeviceToDevice, e->stream);
+    cudaMemcpyAsync(slot->p, src, bytes, cudaMemcpyDeviceToDevice, e->cur);
     e->debug_width[name] = width;
     e->debug_rows = rows;
 }
@@ -457,7 +476,7 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
         }
         if (!(e->limbs_src == A && e->limbs_rows == M)) {  // the producer did not leave them
             prof_begin(e, "tc.split3");
-            launch_split3(e->stream, A, (int64_t)M * w.din, e->limbs.as<uint16_t>());
+            launch_split3(e->cur, A, (int64_t)M * w.din, e->limbs.as<uint16_t>());
             prof_end(e);
         }
         e->limbs_src = nullptr;  // one product per set of limbs
@@ -472,19 +491,19 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
         t.K = w.din;
         t.status = e->status.as<uint32_t>();
         prof_begin(e, cls);
-        const bool launched = launch_tc_gemm(e->stream, t, epi == EPI_LIF ? EPI_STORE : epi);
+        const bool launched = launch_tc_gemm(e->cur, t, epi == EPI_LIF ? EPI_STORE : epi);
         prof_end(e);
         if (launched) {
             if (epi == EPI_LIF) {
                 prof_begin(e, "lif");
-                launch_lif(e->stream, e->yraw.as<float>(), *lif, M, w.dout);
+                launch_lif(e->cur, e->yraw.as<float>(), *lif, M, w.dout);
                 prof_end(e);
             }
             return AVA_OK;
         }
     }
     prof_begin(e, cls);
-    if (!(sparse && launch_q8_event(e->stream, g, epi))) launch_q8_gemm(e->stream, g, epi, e->sm_count);
+    if (!(sparse && launch_q8_event(e->cur, g, epi)) && !(e->gemm2 && launch_q8_gemm2(e->cur, g, epi, e->sm_count))) launch_q8_gemm(e->cur, g, epi, e->sm_count);
     prof_end(e);
     return AVA_OK;
 }
@@ -496,22 +515,27 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
 // with its slice resident in shared memory, the engram read token by token.  Every value is the one T single steps give.
 enum StepPhase { PHASE_ALL = 0, PHASE_BEGIN = 1, PHASE_END = 2 };  // BEGIN stops once the engram's q,k,v exist; END resumes after its read
 
-int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits, uint32_t* next, bool want_logits, int T = 1, bool all_logits = false,
-                StepPhase phase = PHASE_ALL) {
+// One lane: rows [r0, r0 + rows) of the state, with the lane's work buffers, queued on stream st.  tok, logits and next
+// are the caller's whole buffers (a lane reads and writes its own rows of them).
+int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int rows, const uint32_t* tok, float* logits, uint32_t* next, bool want_logits,
+              int T, bool all_logits, StepPhase phase) {
     const ava_config& c = e->cfg;
-    const int rows = s->rows, d = c.d, L = c.n_blocks, nh = e->nh(), hs = c.head_size, H = c.hidden;
+    const int d = c.d, L = c.n_blocks, nh = e->nh(), hs = c.head_size, H = c.hidden;
+    e->cur = st;
+    tok += r0;  // a lane other than the first exists only for T == 1: its tokens are rows r0.. of the one token
+    const size_t Sd = (size_t)s->rows * d;  // one block's carried LIF state over ALL rows of the state
+    const size_t so = (size_t)r0 * d;       // this lane's first row inside a block's state
     const int M = rows * T;  // token-rows, time-major: token t of row r is token-row t * rows + r
-    cudaStream_t st = e->stream;
-    float* x = e->x.as<float>();
-    float* h = e->h.as<float>();
-    float* streams = c.dense ? e->streams.as<float>() : nullptr;
+    float* x = w.x.as<float>();
+    float* h = w.h.as<float>();
+    float* streams = c.dense ? w.streams.as<float>() : nullptr;
     const size_t Md = (size_t)M * d;        // one activation buffer of the chunk
     const size_t Rd = (size_t)rows * d;     // one block's carried LIF state
 
     // the engram's capacity is checked on the host's mirror of the counts before anything moves
     int n_max = 0;
     if (c.eng_block >= 0 && phase == PHASE_ALL) {
-        for (int r = 0; r < rows; ++r) {
+        for (int r = r0; r < r0 + rows; ++r) {
             if (s->keep == s->ring && s->n_host[r] + T > s->ring)
                 return e->fail(AVA_ERR_CAPACITY, "engram store of row %d is full (%d tokens)", r, s->ring);
             n_max = std::max(n_max, std::min(s->n_host[r] + T - 1, s->keep) + 1);
@@ -529,29 +553,29 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
     auto relay_read = [&](int j) {
         prof_begin(e, "relay");
         launch_rmsnorm(st, x, e->ones.as<float>(), M, d, h);
-        launch_chain_gemv(st, h, e->th_read.as<float>() + (size_t)j * d * 16, M, d, 16, e->gate_chunk, e->gz.as<float>());
-        launch_relay(st, e->gz.as<float>(), e->th_acc.as<float>(), j == 0, j + 1, e->th_gate.as<float>() + (size_t)j * 32,
-                     e->th_bias.as<float>() + (size_t)j * 2, M, e->th_g.as<float>());
+        launch_chain_gemv(st, h, e->th_read.as<float>() + (size_t)j * d * 16, M, d, 16, e->gate_chunk, w.gz.as<float>());
+        launch_relay(st, w.gz.as<float>(), w.th_acc.as<float>(), j == 0, j + 1, e->th_gate.as<float>() + (size_t)j * 32,
+                     e->th_bias.as<float>() + (size_t)j * 2, M, w.th_g.as<float>());
         prof_end(e);
         e->launches += 2;
-        dbg(e, "th_g", j, e->th_g.as<float>(), M, 4);
+        dbg(e, "th_g", j, w.th_g.as<float>(), M, 4);
     };
     if (c.rhythm && phase != PHASE_END) {
         // Y: the clocks at every token of the chunk, from the input (after the letters): reset read-out, times, phase features
         prof_begin(e, "rhythm");
         launch_rmsnorm(st, x, e->ones.as<float>(), M, d, h);
-        launch_chain_gemv(st, h, e->rhy_wr.as<float>(), M, d, 4, e->gate_chunk, e->gz.as<float>());
-        launch_rhythm(st, e->gz.as<float>(), e->rhy_br.as<float>(), e->rhy_lw.as<float>(), rows, T, s->rh.as<float>(), e->rh_f.as<float>());
+        launch_chain_gemv(st, h, e->rhy_wr.as<float>(), M, d, 4, e->gate_chunk, w.gz.as<float>());
+        launch_rhythm(st, w.gz.as<float>(), e->rhy_br.as<float>(), e->rhy_lw.as<float>(), rows, T, s->rh.as<float>() + (size_t)r0 * 2, w.rh_f.as<float>());
         prof_end(e);
         e->launches += 2;
-        dbg(e, "rh_f", -1, e->rh_f.as<float>(), M, 4);
+        dbg(e, "rh_f", -1, w.rh_f.as<float>(), M, 4);
     }
     if (c.thalamus && phase != PHASE_END) relay_read(0);
     for (int i = phase == PHASE_END ? c.eng_block : 0; i < L; ++i) {
         BlockDev& b = *e->blocks[i];
         if (c.thalamus && !(phase == PHASE_END && i == c.eng_block))
-            CK(cudaMemcpyAsync(e->x_in.p, x, Md * sizeof(float), cudaMemcpyDeviceToDevice, st));  // the residual rule's x_in
-        const float* th_mem = c.thalamus ? e->th_g.as<float>() + 1 : nullptr;
+            CK(cudaMemcpyAsync(w.x_in.p, x, Md * sizeof(float), cudaMemcpyDeviceToDevice, st));  // the residual rule's x_in
+        const float* th_mem = c.thalamus ? w.th_g.as<float>() + 1 : nullptr;
         if (!(phase == PHASE_END && i == c.eng_block)) {
         // ---- the spiking memory
         prof_begin(e, "rmsnorm");
@@ -563,40 +587,40 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         lp.theta = c.theta ? b.theta.as<float>() : nullptr;
         lp.rho = c.alif ? b.rho.as<float>() : nullptr;
         lp.gain = c.alif ? b.again.as<float>() : nullptr;
-        lp.v = s->lif_v.as<float>() + (size_t)i * Rd;
-        lp.s = s->lif_s.as<float>() + (size_t)i * Rd;
-        lp.a = c.alif ? s->lif_a.as<float>() + (size_t)i * Rd : nullptr;
+        lp.v = s->lif_v.as<float>() + (size_t)i * Sd + so;
+        lp.s = s->lif_s.as<float>() + (size_t)i * Sd + so;
+        lp.a = c.alif ? s->lif_a.as<float>() + (size_t)i * Sd + so : nullptr;
         lp.spikes = c.spikes;
         lp.lif_scale = c.lif_scale;
-        const float* nm = (c.neuromod > 0 && i > 0) ? e->sig.as<float>() : nullptr;  // the nucleus's signals reach the later blocks
+        const float* nm = (c.neuromod > 0 && i > 0) ? w.sig.as<float>() : nullptr;  // the nucleus's signals reach the later blocks
         lp.ne = nm;
         const float* spikes = lp.s;
         const float* cur_gain = nullptr;
         if (c.mood > 0 && i > 0) {
             // M: the current times 1 + tanh(mood G) per token-row and channel, after NE
             prof_begin(e, "mood");
-            launch_mood_gain(st, e->mood_all.as<float>(), c.mood, b.mood_g.as<float>(), M, d, e->mood_gain.as<float>());
+            launch_mood_gain(st, w.mood_all.as<float>(), c.mood, b.mood_g.as<float>(), M, d, w.mood_gain.as<float>());
             prof_end(e);
-            cur_gain = e->mood_gain.as<float>();
+            cur_gain = w.mood_gain.as<float>();
         }
         if (T == 1 && !cur_gain) {
             gemm(e, "gemm.win_lif", h, d, b.win, nullptr, 0, M, EPI_LIF, &lp);
         } else {
             // currents of the whole chunk, then the scan in time (buffers free at this point of the block are borrowed)
-            gemm(e, "gemm.win", h, d, b.win, e->yraw.as<float>(), d, M, EPI_STORE);
+            gemm(e, "gemm.win", h, d, b.win, w.yraw.as<float>(), d, M, EPI_STORE);
             prof_begin(e, "lif_scan");
-            launch_lif_scan(st, e->yraw.as<float>(), lp, rows, d, T, e->eo.as<float>(), cur_gain);
+            launch_lif_scan(st, w.yraw.as<float>(), lp, rows, d, T, w.eo.as<float>(), cur_gain);
             prof_end(e);
-            spikes = e->eo.as<float>();
+            spikes = w.eo.as<float>();
         }
         dbg(e, "spikes", i, spikes, M, d);
         if (c.stp) {
             // the LIF keeps its spikes; what reaches W_out goes through the short-term-plastic synapse
             prof_begin(e, "stp");
             launch_stp(st, spikes, b.stp_U.as<float>(), b.stp_F.as<float>(), b.stp_D.as<float>(), b.stp_mix.as<float>(),
-                       s->stp_u.as<float>() + (size_t)i * Rd, s->stp_x.as<float>() + (size_t)i * Rd, rows, d, T, e->eo.as<float>());
+                       s->stp_u.as<float>() + (size_t)i * Sd + so, s->stp_x.as<float>() + (size_t)i * Sd + so, rows, d, T, w.eo.as<float>());
             prof_end(e);
-            spikes = e->eo.as<float>();
+            spikes = w.eo.as<float>();
             dbg(e, "stp_out", i, spikes, M, d);
         }
         gemm(e, "gemm.wout", spikes, d, b.wout, x, d, M, EPI_ADD, nullptr, true);
@@ -609,52 +633,52 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         prof_end(e);
         dbg(e, "h_mem", i, h, M, d);
         const int pw = e->proj_w();
-        gemm(e, "gemm.qkveg", h, d, b.proj, e->proj.as<float>(), pw, M, EPI_STORE);
-        dbg(e, "qkveg", i, e->proj.as<float>(), M, pw);
+        gemm(e, "gemm.qkveg", h, d, b.proj, w.proj.as<float>(), pw, M, EPI_STORE);
+        dbg(e, "qkveg", i, w.proj.as<float>(), M, pw);
         MemPrepArgs mp{};
         mp.h = h;
-        mp.proj = e->proj.as<float>();
+        mp.proj = w.proj.as<float>();
         mp.ldp = pw;
         mp.gate_w = b.gate_w.as<float>(); mp.gate_cols = e->gate_cols; mp.gate_chunk = e->gate_chunk;
-        mp.z = e->gz.as<float>(); mp.lra = e->lra.as<float>(); mp.lrb = e->lrb.as<float>();
+        mp.z = w.gz.as<float>(); mp.lra = w.lra.as<float>(); mp.lrb = w.lrb.as<float>();
         mp.ba = b.ba.as<float>(); mp.bb = b.bb.as<float>(); mp.wa2 = b.wa2.as<float>(); mp.wb2 = b.wb2.as<float>();
         mp.off = b.off.as<float>();
         mp.vres = (c.value_residual && i > 0 && b.vres.p) ? b.vres.as<float>() : nullptr;
-        mp.v_first = e->v_first.as<float>();
+        mp.v_first = w.v_first.as<float>();
         mp.first = c.value_residual && i == 0;
         mp.M = M; mp.d = d; mp.hs = hs; mp.rank = c.gate_rank;
-        mp.e = e->ve.as<float>(); mp.v = e->vv.as<float>(); mp.w = e->vw.as<float>(); mp.ah = e->vah.as<float>();
-        mp.qg = e->vqg.as<float>(); mp.ex = e->vex.as<float>(); mp.qw = e->qw.as<float>(); mp.qa = e->qa.as<float>();
-        mp.qs = c.mem_momentum > 0.0f ? e->vqs.as<float>() : nullptr;
+        mp.e = w.ve.as<float>(); mp.v = w.vv.as<float>(); mp.w = w.vw.as<float>(); mp.ah = w.vah.as<float>();
+        mp.qg = w.vqg.as<float>(); mp.ex = w.vex.as<float>(); mp.qw = w.qw.as<float>(); mp.qa = w.qa.as<float>();
+        mp.qs = c.mem_momentum > 0.0f ? w.vqs.as<float>() : nullptr;
         mp.mom = c.mem_momentum;
         if (c.rhythm) {
             prof_begin(e, "rhythm");
-            launch_rhythm_gates(st, e->rh_f.as<float>(), b.rh_w.as<float>(), b.rh_r.as<float>(), M, nh, e->rh_gw.as<float>(), e->rh_gr.as<float>());
+            launch_rhythm_gates(st, w.rh_f.as<float>(), b.rh_w.as<float>(), b.rh_r.as<float>(), M, nh, w.rh_gw.as<float>(), w.rh_gr.as<float>());
             prof_end(e);
-            mp.rh_w = e->rh_gw.as<float>();
+            mp.rh_w = w.rh_gw.as<float>();
         }
-        mp.ach = (c.neuromod > 0 && i > 0) ? e->sig.as<float>() + 1 : nullptr;
+        mp.ach = (c.neuromod > 0 && i > 0) ? w.sig.as<float>() + 1 : nullptr;
         mp.ach_stride = 4;
         mp.status = e->status.as<uint32_t>();
         if (e->keep) {
-            if (e->side.bytes < Md * sizeof(float)) CK(e->side.alloc(Md * sizeof(float)));
-            mp.be_out = e->side.as<float>();
+            if (w.side.bytes < Md * sizeof(float)) CK(w.side.alloc(Md * sizeof(float)));
+            mp.be_out = w.side.as<float>();
         }
         prof_begin(e, "mem_prep");
         launch_mem_prep(st, mp);
         prof_end(e);
-        if (e->keep) dbg(e, "be", i, e->side.as<float>(), M, d);
+        if (e->keep) dbg(e, "be", i, w.side.as<float>(), M, d);
         e->launches += 2;  // the two stages of the gate projections before it
         dbg(e, "ek", i, mp.e, M, d); dbg(e, "v", i, mp.v, M, d); dbg(e, "w", i, mp.w, M, d); dbg(e, "ah", i, mp.ah, M, d);
         dbg(e, "qg", i, mp.qg, M, d); dbg(e, "ex", i, mp.ex, M, d); dbg(e, "qw", i, mp.qw, M, nh); dbg(e, "qa", i, mp.qa, M, nh);
         MemHeadsArgs mh{};
-        mh.f = s->mem_f.as<float>() + (size_t)i * Rd * hs;
-        mh.s = c.mem_momentum > 0.0f ? s->mem_s.as<float>() + (size_t)i * Rd * hs : nullptr;
+        mh.f = s->mem_f.as<float>() + ((size_t)i * Sd + so) * hs;
+        mh.s = c.mem_momentum > 0.0f ? s->mem_s.as<float>() + ((size_t)i * Sd + so) * hs : nullptr;
         mh.qs = mp.qs;
         mh.mom = c.mem_momentum;
         mh.M = rows; mh.nh = nh; mh.hs = hs; mh.cw = e->cw; mh.chunk_rows = e->rb;
         mh.e = mp.e; mh.v = mp.v; mh.w = mp.w; mh.ah = mp.ah; mh.qg = mp.qg; mh.ex = mp.ex; mh.qw = mp.qw; mh.qa = mp.qa;
-        mh.y = e->yraw.as<float>();
+        mh.y = w.yraw.as<float>();
         mh.status = e->status.as<uint32_t>();
         prof_begin(e, "mem_heads");
         if (T == 1 && !mh.s)
@@ -664,18 +688,18 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         prof_end(e);
         dbg(e, "y_raw", i, mh.y, M, d);
         prof_begin(e, "mem_post");
-        launch_mem_post(st, mh.y, c.out_gate ? e->proj.as<float>() + 4 * d : nullptr, pw, M, d, hs, e->y.as<float>(), limbs_for(e, e->y.as<float>(), M, d),
-                        c.rhythm ? e->rh_gr.as<float>() : nullptr);
+        launch_mem_post(st, mh.y, c.out_gate ? w.proj.as<float>() + 4 * d : nullptr, pw, M, d, hs, w.y.as<float>(), limbs_for(e, w.y.as<float>(), M, d),
+                        c.rhythm ? w.rh_gr.as<float>() : nullptr);
         prof_end(e);
-        dbg(e, "y", i, e->y.as<float>(), M, d);
+        dbg(e, "y", i, w.y.as<float>(), M, d);
         if (c.dendrite) {
             // P: the read after W_o is kept, the context of this block's dendrites
-            gemm(e, "gemm.wo", e->y.as<float>(), d, b.wo, e->ctx.as<float>(), d, M, EPI_STORE);
+            gemm(e, "gemm.wo", w.y.as<float>(), d, b.wo, w.ctx.as<float>(), d, M, EPI_STORE);
             prof_begin(e, "add");
-            launch_add_into(st, x, e->ctx.as<float>(), (int64_t)Md, th_mem, d);
+            launch_add_into(st, x, w.ctx.as<float>(), (int64_t)Md, th_mem, d);
             prof_end(e);
         } else {
-            gemm(e, "gemm.wo", e->y.as<float>(), d, b.wo, x, d, M, EPI_ADD, nullptr, false, th_mem);
+            gemm(e, "gemm.wo", w.y.as<float>(), d, b.wo, x, d, M, EPI_ADD, nullptr, false, th_mem);
         }
         dbg(e, "x_mem", i, x, M, d);
         }
@@ -687,8 +711,8 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
                 prof_begin(e, "rmsnorm");
                 launch_rmsnorm(st, x, b.eng_norm.as<float>(), M, d, h, limbs_for(e, h, M, d));
                 prof_end(e);
-                gemm(e, "gemm.eng_qkv", h, d, b.eqkv, e->eqkv.as<float>(), 3 * d, M, EPI_STORE);
-                dbg(e, "eng_qkv", i, e->eqkv.as<float>(), M, 3 * d);
+                gemm(e, "gemm.eng_qkv", h, d, b.eqkv, w.eqkv.as<float>(), 3 * d, M, EPI_STORE);
+                dbg(e, "eng_qkv", i, w.eqkv.as<float>(), M, 3 * d);
             }
             if (phase == PHASE_BEGIN) {
                 const cudaError_t le0 = cudaGetLastError();
@@ -696,9 +720,10 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
                 return AVA_OK;
             }
             EngramArgs ea{};
-            ea.qkv = e->eqkv.as<float>();
-            ea.k = s->eng_k.p; ea.v = s->eng_v.p;
-            ea.n = s->eng_n.as<int32_t>(); ea.start = s->eng_start.as<int32_t>();
+            ea.qkv = w.eqkv.as<float>();
+            const size_t kv_row = (size_t)d * s->ring * s->kv_elem();  // bytes of one row's keys (or values): [heads][ring][hs]
+            ea.k = (char*)s->eng_k.p + r0 * kv_row; ea.v = (char*)s->eng_v.p + r0 * kv_row;
+            ea.n = s->eng_n.as<int32_t>() + r0; ea.start = s->eng_start.as<int32_t>() + r0;
             ea.M = rows; ea.d = d; ea.hs = c.eng_head_size; ea.cap = s->ring; ea.keep = s->keep; ea.bf16 = c.eng_store_bf16;
             ea.status = e->status.as<uint32_t>();
             // the read is causal: token t sees the store as tokens 0..t left it, so the chunk goes token by token.  A
@@ -710,11 +735,11 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
             const int n_seg = engram_segments(n_max, seg_len);
             if (segmented) {
                 const size_t need = (size_t)rows * enh * n_seg * (2 + c.eng_head_size) * sizeof(float);
-                if (e->eng_partial.bytes < need) CK(e->eng_partial.alloc(need));
+                if (w.eng_partial.bytes < need) CK(w.eng_partial.alloc(need));
             }
             for (int t = 0; t < T && phase == PHASE_ALL; ++t) {
-                ea.qkv = e->eqkv.as<float>() + (size_t)t * rows * 3 * d;
-                ea.o = e->eo.as<float>() + (size_t)t * Rd;
+                ea.qkv = w.eqkv.as<float>() + (size_t)t * rows * 3 * d;
+                ea.o = w.eo.as<float>() + (size_t)t * Rd;
                 if (!segmented) {
                     prof_begin(e, "engram");
                     if (!launch_engram(st, ea, n_max))
@@ -726,24 +751,24 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
                     launch_engram_append(st, ea);
                     prof_end(e);
                     prof_begin(e, "engram.partial");
-                    if (!launch_engram_partial(st, ea, seg_len, n_seg, e->eng_partial.as<float>()))
+                    if (!launch_engram_partial(st, ea, seg_len, n_seg, w.eng_partial.as<float>()))
                         return e->fail(AVA_ERR_CAPACITY, "engram segments of %d keys do not fit shared memory", seg_len);
                     prof_end(e);
                     prof_begin(e, "engram.combine");
-                    launch_engram_combine(st, e->eng_partial.as<float>(), rows, enh, c.eng_head_size, n_seg, ea.o);
+                    launch_engram_combine(st, w.eng_partial.as<float>(), rows, enh, c.eng_head_size, n_seg, ea.o);
                     prof_end(e);
                     launch_engram_trim(st, ea);
                     e->launches += 2;
                 }
             }
-            ea.o = e->eo.as<float>();
+            ea.o = w.eo.as<float>();
             dbg(e, "eng_o", i, ea.o, M, d);
             if (e->keep) {
                 // the read as it is added (the token trace shows it): the same product stored, then the same addition
-                if (e->side.bytes < Md * sizeof(float)) CK(e->side.alloc(Md * sizeof(float)));
-                gemm(e, "gemm.eng_wo", ea.o, d, b.ewo, e->side.as<float>(), d, M, EPI_STORE);
-                dbg(e, "eng_r", i, e->side.as<float>(), M, d);
-                launch_add_into(st, x, e->side.as<float>(), (int64_t)Md);
+                if (w.side.bytes < Md * sizeof(float)) CK(w.side.alloc(Md * sizeof(float)));
+                gemm(e, "gemm.eng_wo", ea.o, d, b.ewo, w.side.as<float>(), d, M, EPI_STORE);
+                dbg(e, "eng_r", i, w.side.as<float>(), M, d);
+                launch_add_into(st, x, w.side.as<float>(), (int64_t)Md);
             } else {
                 gemm(e, "gemm.eng_wo", ea.o, d, b.ewo, x, d, M, EPI_ADD);
             }
@@ -754,35 +779,35 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         prof_begin(e, "rmsnorm");
         launch_rmsnorm(st, x, b.mlp_norm.as<float>(), M, d, h, limbs_for(e, h, M, d));
         prof_end(e);
-        gemm(e, "gemm.w1", h, d, b.w1, e->u.as<float>(), H, M, EPI_STORE);
-        dbg(e, "u", i, e->u.as<float>(), M, H);
+        gemm(e, "gemm.w1", h, d, b.w1, w.u.as<float>(), H, M, EPI_STORE);
+        dbg(e, "u", i, w.u.as<float>(), M, H);
         prof_begin(e, "kwta");
-        launch_kwta(st, e->u.as<float>(), M, H, c.kwta_k, c.relu2, e->act.as<float>());
+        launch_kwta(st, w.u.as<float>(), M, H, c.kwta_k, c.relu2, w.act.as<float>());
         prof_end(e);
-        dbg(e, "a", i, e->act.as<float>(), M, H);
+        dbg(e, "a", i, w.act.as<float>(), M, H);
         if (c.dendrite && c.fast_mem) {
             // P: the units times 1 + tanh(head_norm(ctx) A B); h is free here
             prof_begin(e, "dendrite");
-            launch_rmsnorm(st, e->ctx.as<float>(), e->ones.as<float>(), M, d, h);
-            launch_chain_gemv(st, h, b.dend_a.as<float>(), M, d, 32, e->gate_chunk, e->dz1.as<float>());
-            launch_dend_gain(st, e->dz1.as<float>(), 32, b.dend_b.as<float>(), M, H, e->act.as<float>());
+            launch_rmsnorm(st, w.ctx.as<float>(), e->ones.as<float>(), M, d, h);
+            launch_chain_gemv(st, h, b.dend_a.as<float>(), M, d, 32, e->gate_chunk, w.dz1.as<float>());
+            launch_dend_gain(st, w.dz1.as<float>(), 32, b.dend_b.as<float>(), M, H, w.act.as<float>());
             prof_end(e);
             e->launches += 2;
-            dbg(e, "a_dend", i, e->act.as<float>(), M, H);
+            dbg(e, "a_dend", i, w.act.as<float>(), M, H);
         }
-        const float* nm_da = (c.neuromod > 0 && i > 0) ? e->sig.as<float>() + 2 : nullptr;
+        const float* nm_da = (c.neuromod > 0 && i > 0) ? w.sig.as<float>() + 2 : nullptr;
         if (c.dopamine && i > 0) {
             // DA: the MLP's output times 1 + tanh(z w + c), z the token's surprise / ln V, before the nucleus's DA signal
-            gemm(e, "gemm.w2", e->act.as<float>(), H, b.w2, e->y2.as<float>(), d, M, EPI_STORE, nullptr, true);
+            gemm(e, "gemm.w2", w.act.as<float>(), H, b.w2, w.y2.as<float>(), d, M, EPI_STORE, nullptr, true);
             prof_begin(e, "dopamine");
-            launch_da_add(st, x, e->y2.as<float>(), e->sur_z.as<float>(), b.da_w.as<float>(), b.da_c.as<float>(), nm_da, M, d);
+            launch_da_add(st, x, w.y2.as<float>(), w.sur_z.as<float>(), b.da_w.as<float>(), b.da_c.as<float>(), nm_da, M, d);
             prof_end(e);
         } else {
-            gemm(e, "gemm.w2", e->act.as<float>(), H, b.w2, x, d, M, EPI_ADD, nullptr, true, nm_da);
+            gemm(e, "gemm.w2", w.act.as<float>(), H, b.w2, x, d, M, EPI_ADD, nullptr, true, nm_da);
         }
         if (c.thalamus) {
             prof_begin(e, "relay");
-            launch_relay_res(st, x, e->x_in.as<float>(), e->th_g.as<float>(), M, d);
+            launch_relay_res(st, x, w.x_in.as<float>(), w.th_g.as<float>(), M, d);
             prof_end(e);
         }
         if (c.dense) {
@@ -796,34 +821,34 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
             // DA / M: the surprise at each token, from the head's logits for block 0's normed output at the position before
             // it (the carried one for a chunk's first token), then the mood's scan; the carried values move on
             prof_begin(e, "surprise");
-            launch_rmsnorm(st, x, e->final_norm.as<float>(), M, d, e->sur_xf.as<float>());
-            CK(cudaMemcpyAsync(e->sur_in.p, s->sur_prev.p, Rd * sizeof(float), cudaMemcpyDeviceToDevice, st));
+            launch_rmsnorm(st, x, e->final_norm.as<float>(), M, d, w.sur_xf.as<float>());
+            CK(cudaMemcpyAsync(w.sur_in.p, s->sur_prev.as<float>() + so, Rd * sizeof(float), cudaMemcpyDeviceToDevice, st));
             if (T > 1)
-                CK(cudaMemcpyAsync(e->sur_in.as<float>() + Rd, e->sur_xf.p, (size_t)(T - 1) * Rd * sizeof(float), cudaMemcpyDeviceToDevice, st));
+                CK(cudaMemcpyAsync(w.sur_in.as<float>() + Rd, w.sur_xf.p, (size_t)(T - 1) * Rd * sizeof(float), cudaMemcpyDeviceToDevice, st));
             prof_end(e);
-            gemm(e, "gemm.sur_head", e->sur_in.as<float>(), d, e->head, e->sur_logits.as<float>(), c.vocab, M, EPI_STORE);
+            gemm(e, "gemm.sur_head", w.sur_in.as<float>(), d, e->head, w.sur_logits.as<float>(), c.vocab, M, EPI_STORE);
             prof_begin(e, "surprise");
-            if (!launch_surprise(st, e->sur_logits.as<float>(), c.vocab, tok, s->sur_valid.as<float>(), rows, T, e->sur_s.as<float>(), e->sur_z.as<float>()))
+            if (!launch_surprise(st, w.sur_logits.as<float>(), c.vocab, tok, s->sur_valid.as<float>() + r0, rows, T, w.sur_s.as<float>(), w.sur_z.as<float>()))
                 return e->fail(AVA_ERR_CAPACITY, "the surprise kernel holds a vocabulary of up to 56320 in shared memory");
             if (c.mood > 0)
-                launch_mood(st, e->sur_z.as<float>(), rows, T, c.mood, e->mood_lam.as<float>(), e->mood_win.as<float>(), e->mood_bin.as<float>(),
-                            s->mood.as<float>(), e->mood_all.as<float>());
-            CK(cudaMemcpyAsync(s->sur_prev.p, e->sur_xf.as<float>() + (size_t)(T - 1) * Rd, Rd * sizeof(float), cudaMemcpyDeviceToDevice, st));
-            CK(cudaMemcpyAsync(s->sur_last.p, e->sur_s.as<float>() + (size_t)(T - 1) * rows, rows * sizeof(float), cudaMemcpyDeviceToDevice, st));
-            launch_fill(st, s->sur_valid.as<float>(), rows, 1.0f);
+                launch_mood(st, w.sur_z.as<float>(), rows, T, c.mood, e->mood_lam.as<float>(), e->mood_win.as<float>(), e->mood_bin.as<float>(),
+                            s->mood.as<float>() + (size_t)r0 * c.mood, w.mood_all.as<float>());
+            CK(cudaMemcpyAsync(s->sur_prev.as<float>() + so, w.sur_xf.as<float>() + (size_t)(T - 1) * Rd, Rd * sizeof(float), cudaMemcpyDeviceToDevice, st));
+            CK(cudaMemcpyAsync(s->sur_last.as<float>() + r0, w.sur_s.as<float>() + (size_t)(T - 1) * rows, rows * sizeof(float), cudaMemcpyDeviceToDevice, st));
+            launch_fill(st, s->sur_valid.as<float>() + r0, rows, 1.0f);
             prof_end(e);
             e->launches += 3;
-            dbg(e, "sur_z", 0, e->sur_z.as<float>(), M, 1);
+            dbg(e, "sur_z", 0, w.sur_z.as<float>(), M, 1);
         }
         if (i == 0 && c.neuromod > 0) {
             // the nucleus reads block 0's output: 2 sigmoid(rmsnorm(x, g) W + b) per token-row (h and the gates' scratch are free)
             prof_begin(e, "nucleus");
             launch_rmsnorm(st, x, e->nm_norm.as<float>(), M, d, h);
-            launch_chain_gemv(st, h, e->nm_wn.as<float>(), M, d, 4, e->gate_chunk, e->gz.as<float>());
-            launch_nucleus(st, e->gz.as<float>(), e->nm_bn.as<float>(), c.neuromod, M, e->sig.as<float>());
+            launch_chain_gemv(st, h, e->nm_wn.as<float>(), M, d, 4, e->gate_chunk, w.gz.as<float>());
+            launch_nucleus(st, w.gz.as<float>(), e->nm_bn.as<float>(), c.neuromod, M, w.sig.as<float>());
             prof_end(e);
             e->launches += 2;
-            dbg(e, "nm_sig", 0, e->sig.as<float>(), M, 4);
+            dbg(e, "nm_sig", 0, w.sig.as<float>(), M, 4);
         }
     }
     if (want_logits || next) {
@@ -837,16 +862,17 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
             // CB: the final normed state plus the read-out of the sparse code of it and the token's embedding
             const int G = c.cb_units;
             prof_begin(e, "cerebellum");
-            launch_cb_inputs(st, e->tok_emb.as<float>(), tok + first_row, head_rows, d, c.vocab, e->cb_emb.as<float>());
-            launch_rmsnorm(st, e->cb_emb.as<float>(), e->ones.as<float>(), head_rows, d, e->cb_en.as<float>());
-            launch_cb_units(st, h, e->cb_en.as<float>(), e->cb_idx.as<uint32_t>(), e->cb_sgn.as<float>(), G, d, head_rows, e->cb_h.as<float>());
-            launch_kwta(st, e->cb_h.as<float>(), head_rows, G, G / 32, 0, e->cb_a.as<float>());
-            launch_cb_read(st, e->cb_a.as<float>(), G, e->cb_lj.as<int>(), e->cb_lc.as<float>(), e->cb_n.as<int>(), e->cb_w.as<float>(), head_rows, d, h);
+            launch_cb_inputs(st, e->tok_emb.as<float>(), tok + first_row, head_rows, d, c.vocab, w.cb_emb.as<float>());
+            launch_rmsnorm(st, w.cb_emb.as<float>(), e->ones.as<float>(), head_rows, d, w.cb_en.as<float>());
+            launch_cb_units(st, h, w.cb_en.as<float>(), e->cb_idx.as<uint32_t>(), e->cb_sgn.as<float>(), G, d, head_rows, w.cb_h.as<float>());
+            launch_kwta(st, w.cb_h.as<float>(), head_rows, G, G / 32, 0, w.cb_a.as<float>());
+            launch_cb_read(st, w.cb_a.as<float>(), G, w.cb_lj.as<int>(), w.cb_lc.as<float>(), w.cb_n.as<int>(), e->cb_w.as<float>(), head_rows, d, h);
             prof_end(e);
             e->launches += 5;
             dbg(e, "x_cb", -1, h, head_rows, d);
         }
-        float* lg = logits ? logits : e->logits.as<float>();
+        float* lg = (logits ? logits : e->logits.as<float>()) + (size_t)r0 * c.vocab;
+        if (next) next += r0;
         gemm(e, "gemm.head", h, d, e->head, lg, c.vocab, head_rows, EPI_STORE);
         if (next) {
             prof_begin(e, "argmax");
@@ -856,7 +882,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
     }
     // the host's mirror of the engram counts moves as the kernels move them
     if (c.eng_block >= 0 && phase == PHASE_ALL)
-        for (int r = 0; r < rows; ++r)
+        for (int r = r0; r < r0 + rows; ++r)
             for (int t = 0; t < T; ++t) {
                 const int n = s->n_host[r] + 1;
                 if (n > s->keep) {
@@ -866,10 +892,48 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
                     s->n_host[r] = n;
                 }
             }
-    for (int r = 0; r < rows; ++r) s->seen[r] += T;
+    for (int r = r0; r < r0 + rows; ++r) s->seen[r] += T;
     const cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) return e->cuda_fail(le, "kernel launch");
     return AVA_OK;
+}
+
+// The step of a whole state.  A decode step (T == 1) of enough rows runs as `n_lanes` lanes: contiguous windows of the
+// rows, each with its own work buffers and stream, forked from the engine's stream and joined back into it, so callers
+// see one stream as before.  Rows are independent (src/state.rs:13-15), so the lanes compute the same bits.
+int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits, uint32_t* next, bool want_logits, int T = 1, bool all_logits = false,
+                StepPhase phase = PHASE_ALL) {
+    int lanes = 1;
+    if (e->n_lanes > 1 && T == 1 && phase == PHASE_ALL && !e->keep && !e->fast && s->rows >= 16 * e->n_lanes) lanes = e->n_lanes;
+    if (lanes == 1) return step_rows(e, *e, e->stream, s, 0, s->rows, tok, logits, next, want_logits, T, all_logits, phase);
+    const int per = (s->rows + lanes - 1) / lanes;
+    while ((int)e->more_lanes.size() < lanes - 1) {
+        std::unique_ptr<Work> w(new Work());
+        CK(cudaStreamCreateWithFlags(&w->lane_stream, cudaStreamNonBlocking));
+        CK(cudaEventCreateWithFlags(&w->lane_done, cudaEventDisableTiming));
+        e->more_lanes.push_back(std::move(w));
+    }
+    if (!e->fork_ev) CK(cudaEventCreateWithFlags(&e->fork_ev, cudaEventDisableTiming));
+    for (int l = 1; l < lanes; ++l) {
+        const int rc = ensure_workspace(e, *e->more_lanes[l - 1], per);
+        if (rc) return rc;
+    }
+    CK(cudaEventRecord(e->fork_ev, e->stream));
+    int rc = AVA_OK;
+    for (int l = 0; l < lanes && rc == AVA_OK; ++l) {
+        const int r0 = l * per, n = std::min(per, s->rows - r0);
+        if (n <= 0) break;
+        Work& w = l == 0 ? static_cast<Work&>(*e) : *e->more_lanes[l - 1];
+        cudaStream_t st = l == 0 ? e->stream : w.lane_stream;
+        if (l > 0) CK(cudaStreamWaitEvent(st, e->fork_ev, 0));
+        rc = step_rows(e, w, st, s, r0, n, tok, logits, next, want_logits, T, all_logits, phase);
+        if (l > 0) {
+            CK(cudaEventRecord(w.lane_done, st));
+            CK(cudaStreamWaitEvent(e->stream, w.lane_done, 0));
+        }
+    }
+    e->cur = e->stream;
+    return rc;
 }
 
 // waits for the stream and turns the device status word into a return code (clearing it)
@@ -891,7 +955,7 @@ int check_pair(ava_engine* e, ava_state* s) {
     if (!e->finalized) return e->fail(AVA_ERR_ARG, "engine not finalized");
     if (!e->blocker.empty()) return AVA_NOT_APPLICABLE;
     CK(cudaSetDevice(e->device));
-    return ensure_workspace(e, s->rows, s->rows);
+    return ensure_workspace(e, *e, s->rows, s->rows);
 }
 
 struct StateSlice {
@@ -1080,7 +1144,10 @@ int ava_engine_create(const ava_config* cfg, int device, ava_engine** out) {
         g_create_error = std::string("engine set-up: ") + cudaGetErrorString(ce);
         return AVA_ERR_CUDA;
     }
+    e->cur = e->stream;
     if (const char* v = std::getenv("AVA_PDL")) g_pdl = std::atoi(v) != 0;
+    if (const char* v = std::getenv("AVA_LANES")) e->n_lanes = std::max(1, std::min(8, std::atoi(v)));
+    if (const char* v = std::getenv("AVA_GEMM2")) e->gemm2 = std::atoi(v) != 0;
     const char* why = find_blocker(e->cfg, &e->cw, &e->rb);
     if (why) e->blocker = why;
     if (!why) {
@@ -1096,6 +1163,14 @@ int ava_engine_create(const ava_config* cfg, int device, ava_engine** out) {
 void ava_engine_destroy(ava_engine* e) {
     if (!e) return;
     cudaSetDevice(e->device);
+    for (auto& w : e->more_lanes) {
+        if (w->lane_stream) {
+            cudaStreamSynchronize(w->lane_stream);
+            cudaStreamDestroy(w->lane_stream);
+        }
+        if (w->lane_done) cudaEventDestroy(w->lane_done);
+    }
+    if (e->fork_ev) cudaEventDestroy(e->fork_ev);
     if (e->stream) {
         cudaStreamSynchronize(e->stream);
         cudaStreamDestroy(e->stream);
@@ -1608,8 +1683,9 @@ int ava_step_sample(ava_engine* e, ava_state* s, const uint32_t* tok, float temp
     if (!tok || !next || !uniform) return e->fail(AVA_ERR_ARG, "null buffer");
     for (int r = 0; r < s->rows; ++r)
         if (tok[r] >= (uint32_t)e->cfg.vocab) return e->fail(AVA_ERR_ARG, "token %u of row %d outside the vocabulary", tok[r], r);
-    const int k = top_k < 1 ? 1 : top_k;
-    if (k > 1024 && k < e->cfg.vocab) return e->fail(AVA_NOT_APPLICABLE, "top_k above 1024: pick on the host (ava_step + ava_pick)");
+    // asked before anything moves: a refusal leaves the state as it was
+    if (!sample_covered(e->cfg.vocab, top_k))
+        return e->fail(AVA_NOT_APPLICABLE, "the device sampler does not cover this vocabulary or top_k (top_k above 1024, or a vocabulary beyond its shared memory): pick on the host (ava_step + ava_pick)");
     CK(cudaMemcpyAsync(e->tok.p, tok, s->rows * sizeof(uint32_t), cudaMemcpyHostToDevice, e->stream));
     CK(cudaMemcpyAsync(e->uniform.p, uniform, s->rows * sizeof(double), cudaMemcpyHostToDevice, e->stream));
     if ((rc = step_device(e, s, e->tok.as<uint32_t>(), e->logits.as<float>(), nullptr, true))) return rc;
@@ -1639,7 +1715,7 @@ int ava_forward_with_state(ava_engine* e, ava_state* s, const uint32_t* ids, int
     int64_t max_rows = 16384;
     if (!last_only) max_rows = std::min<int64_t>(max_rows, std::max<int64_t>(M, ((int64_t)1 << 28) / V));  // logits of a chunk <= 1 GiB
     const int Tc = (int)std::max<int64_t>(1, std::min<int64_t>(t, max_rows / M));
-    if ((rc = ensure_workspace(e, M * Tc, last_only ? M : M * Tc))) return rc;
+    if ((rc = ensure_workspace(e, *e, M * Tc, last_only ? M : M * Tc))) return rc;
     for (int j0 = 0; j0 < t; j0 += Tc) {
         const int T = std::min(Tc, t - j0);
         const bool last_chunk = j0 + T == t;
@@ -1665,7 +1741,7 @@ int ava_prefill_device(ava_engine* e, ava_state* s, const uint32_t* tok_device, 
     if (!tok_device || t <= 0 || chunk <= 0) return e->fail(AVA_ERR_ARG, "bad arguments");
     const int M = s->rows;
     const int Tc = std::min(chunk, t);
-    if ((rc = ensure_workspace(e, M * Tc, M))) return rc;
+    if ((rc = ensure_workspace(e, *e, M * Tc, M))) return rc;
     for (int j0 = 0; j0 < t; j0 += Tc) {
         const int T = std::min(Tc, t - j0);
         const bool last_chunk = j0 + T == t;
@@ -1848,6 +1924,18 @@ int ava_prof_read(ava_engine* e, const char* kernel, int64_t* launches, double* 
     if (!e || !kernel) return AVA_ERR_ARG;
     CK(cudaSetDevice(e->device));
     CK(cudaStreamSynchronize(e->stream));
+    for (auto& w : e->more_lanes)
+        if (w->lane_stream) CK(cudaStreamSynchronize(w->lane_stream));
+    if (const char* path = e->prof_pending.empty() ? nullptr : std::getenv("AVA_TIMELINE")) {  // tuning aid: every bracketed launch with its start and end (ms since the first)
+        if (FILE* fp = std::fopen(path, "w")) {
+            for (auto& p : e->prof_pending) {
+                float t0 = 0.f, t1 = 0.f;
+                if (cudaEventElapsedTime(&t0, e->prof_pending.front().a, p.a) == cudaSuccess && cudaEventElapsedTime(&t1, e->prof_pending.front().a, p.b) == cudaSuccess)
+                    std::fprintf(fp, "%p %s %.4f %.4f\n", (void*)p.st, p.cls, t0, t1);
+            }
+            std::fclose(fp);
+        }
+    }
     for (auto& p : e->prof_pending) {
         float t = 0.f;
         if (cudaEventElapsedTime(&t, p.a, p.b) == cudaSuccess) {

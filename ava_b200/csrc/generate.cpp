@@ -15,6 +15,7 @@
 #include <vector>
 
 #include "../../include/ava_engine.h"
+#include "kernels.cuh"
 
 namespace {
 
@@ -139,6 +140,11 @@ static int generate_impl(ava_engine* e, const uint32_t* prompts, const int32_t* 
     if (max_ctx < longest + max_new) return AVA_ERR_CAPACITY;
     const ava_config* cfg = ava_engine_config(e);
     const int V = cfg->vocab;
+    // decided once per call: the draws are taken on the device when its sampler covers (vocabulary, top_k); when it
+    // does not, every step returns its logits and `ava_pick` draws on the host from the same generator (`diary::pick`
+    // works for any top_k, src/diary.rs:686-718)
+    const bool dev_sampler = smp && smp->temperature > 0.0f && ava::sample_covered(V, smp->top_k);
+    const bool host_sampler = smp && smp->temperature > 0.0f && !dev_sampler;
     std::vector<int> order((size_t)n_prompts);
     std::iota(order.begin(), order.end(), 0);
     std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return prompt_len[a] < prompt_len[b]; });
@@ -184,7 +190,7 @@ static int generate_impl(ava_engine* e, const uint32_t* prompts, const int32_t* 
         }
         parts.clear();
         std::vector<int> live(group);  // prompt index of each state row
-        if (first_pick && smp->temperature > 0.0f && max_new > 0) {
+        if (first_pick && dev_sampler && max_new > 0) {
             // the first tokens, from the prompts' logits: drawn on the device too when the sampler covers the case (the
             // uniform numbers in the rows' order, as the loop below would draw them)
             uint64_t saved = *smp->rng;
@@ -215,7 +221,7 @@ static int generate_impl(ava_engine* e, const uint32_t* prompts, const int32_t* 
                 keep.push_back((int32_t)k);
                 next.push_back(tok);
             }
-            first_pick = false;
+            if (!host_sampler) first_pick = false;  // a sampler the device does not cover keeps drawing on the host
             if (keep.empty() || step + 1 == max_new) break;
             if (keep.size() != live.size()) {
                 ava_state* sel = nullptr;
@@ -227,7 +233,7 @@ static int generate_impl(ava_engine* e, const uint32_t* prompts, const int32_t* 
                 live.swap(nl);
             }
             int rc;
-            if (pick) {
+            if (pick || host_sampler) {
                 last.resize(next.size() * (size_t)V);
                 rc = ava_step(e, st.s, next.data(), last.data());
             } else if (smp && smp->temperature > 0.0f) {

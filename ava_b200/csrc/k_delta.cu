@@ -48,6 +48,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     }
     return false;
 }
+// the same with the caller's limit (a testing aid shortens it)
+__device__ __forceinline__ bool mbar_wait_lim(uint64_t* bar, uint32_t parity, uint32_t limit) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < limit; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if (i > 256) __nanosleep(64);
+    }
+    return false;
+}
 // global -> shared, completion counted in bytes on the mbarrier; addresses and size multiples of 16
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)), "l"(src),
@@ -96,6 +113,7 @@ __global__ void __launch_bounds__(THREADS) mem_heads_kernel(const MemHeadsArgs a
     const size_t vo = ((size_t)m * a.nh + head) * hs;  // offset of this head's vectors
     float* gslice = a.f + (vo * hs) + (size_t)slice * hs * CW;  // this block's contiguous slice in HBM
     const uint32_t chunk_bytes = (uint32_t)(cr * CW * sizeof(float));
+    const uint32_t limit = a.wait_limit ? a.wait_limit : WAIT_LIMIT;
     // optional phase clock of thread 0 (nanoseconds, 6 marks per block) for tuning; nullptr in normal runs
     unsigned long long* tl = a.timeline ? a.timeline + (size_t)blockIdx.x * 6 : nullptr;
     auto mark = [&](int i) {
@@ -119,7 +137,8 @@ __global__ void __launch_bounds__(THREADS) mem_heads_kernel(const MemHeadsArgs a
         bulk_load(ve, a.e + vo, vb, vbar);
         bulk_load(vqg, a.qg + vo, vb, vbar);
         for (int c = 0; c < nchunk; ++c) {
-            mbar_expect_tx(&bars[c], chunk_bytes);
+            // a testing aid can over-state one chunk's byte count so that its barrier never completes
+            mbar_expect_tx(&bars[c], chunk_bytes + (a.fault_chunk_plus1 == c + 1 ? 16u : 0u));
             bulk_load(tile + (size_t)c * cr * CW, gslice + (size_t)c * cr * CW, chunk_bytes, &bars[c]);
         }
         bulk_load(vex, a.ex + vo, vb, vbar);
@@ -127,7 +146,7 @@ __global__ void __launch_bounds__(THREADS) mem_heads_kernel(const MemHeadsArgs a
         bulk_load(vah, a.ah + vo, vb, vbar);
         bulk_load(vv, a.v + vo + c0, (uint32_t)(CW * sizeof(float)), vbar);
     }
-    bool ok = mbar_wait(vbar, 0);
+    bool ok = mbar_wait_lim(vbar, 0, limit);
     mark(1);
 
     // pass 1: the column sums, rows in order as their chunks land (the first CW threads, one column each).  The chain
@@ -135,7 +154,8 @@ __global__ void __launch_bounds__(THREADS) mem_heads_kernel(const MemHeadsArgs a
     if (tid < CW) {
         float r = -0.0f, t = -0.0f;
         for (int c = 0; c < nchunk; ++c) {
-            ok = mbar_wait(&bars[c], 0) && ok;
+            ok = mbar_wait_lim(&bars[c], 0, limit) && ok;
+            if (!ok) break;
             const float* p = tile + (size_t)c * cr * CW + tid;
             const int end = (c + 1) * cr;
             for (int row = c * cr; row < end; row += 8, p += 8 * CW) {
@@ -162,8 +182,12 @@ __global__ void __launch_bounds__(THREADS) mem_heads_kernel(const MemHeadsArgs a
     __syncthreads();
     // a wait that succeeded makes the copied bytes visible to its own thread only: every other thread waits too
     if (tid >= CW)
-        for (int c = 0; c < nchunk; ++c) ok = mbar_wait(&bars[c], 0) && ok;
-    if (!ok) atomicOr(a.status, ST_WAIT_TIMEOUT);
+        for (int c = 0; c < nchunk && ok; ++c) ok = mbar_wait_lim(&bars[c], 0, limit);
+    // a wait ran out somewhere in the block: flag it and leave the state as it was (no read, no update, no store)
+    if (__syncthreads_or(!ok)) {
+        if (tid == 0) atomicOr(a.status, ST_WAIT_TIMEOUT);
+        return;
+    }
 
     // the read
     if (tid < CW) {
@@ -378,7 +402,11 @@ __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsAr
         }
         __syncthreads();
     }
-    if (!ok) atomicOr(a.status, ST_WAIT_TIMEOUT);
+    // a wait ran out somewhere in the block: flag it and store nothing (the state keeps what it held before the chunk)
+    if (__syncthreads_or(!ok)) {
+        if (tid == 0) atomicOr(a.status, ST_WAIT_TIMEOUT);
+        return;
+    }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
     if (tid == 0) {

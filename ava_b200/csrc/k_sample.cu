@@ -186,10 +186,16 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
 
 }  // namespace
 
-bool launch_sample(cudaStream_t st, const float* logits, int M, int V, float temperature, int top_k, const double* uniform, uint32_t* next) {
+static size_t sample_smem(int V) { return (size_t)((V + 3) & ~3) * sizeof(float) + SAMPLE_MAX_K * sizeof(unsigned long long); }
+
+bool sample_covered(int V, int top_k) {
     const int k = top_k < 1 ? 1 : (top_k > V ? V : top_k);
-    const size_t smem = (size_t)((V + 3) & ~3) * sizeof(float) + SAMPLE_MAX_K * sizeof(unsigned long long);
-    if (k > SAMPLE_MAX_K || smem > 220 * 1024 || !(temperature > 0.0f)) return false;
+    return V > 0 && k <= SAMPLE_MAX_K && sample_smem(V) <= 220 * 1024;
+}
+
+bool launch_sample(cudaStream_t st, const float* logits, int M, int V, float temperature, int top_k, const double* uniform, uint32_t* next) {
+    const size_t smem = sample_smem(V);
+    if (!sample_covered(V, top_k) || !(temperature > 0.0f)) return false;
     const float inv_t = (float)(1.0 / (double)temperature);
     if (smem > 32 * 1024) cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_k(sample_kernel, dim3(M), dim3(SAMPLE_THREADS), smem, st, logits, V, inv_t, top_k, uniform, next);

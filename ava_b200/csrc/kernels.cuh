@@ -84,6 +84,9 @@ static_assert(sizeof(GemmArgs) == 128, "parameter block of the product kernels")
 // the sum then times scale[n]: the bits of the reference's int8 product (src/int8.rs:315-331).  K % 16 == 0, N % 4 == 0.
 void launch_q8_gemm(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int sm_count);
 
+// The same product, same bits, with packed weights and packed multiply-adds (k_gemm2.cu).  false: shape not covered.
+bool launch_q8_gemm2(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int sm_count);
+
 // The same product for rows that are mostly zeros (spikes, k-WTA'd units): summed over the non-zero inputs only, in
 // order, which gives the dense sum's bits (src/int8.rs:10-13).  false: shape not covered, use launch_q8_gemm.
 bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi);
@@ -191,6 +194,9 @@ struct MemHeadsArgs {
     float* y;                                // [M, nh * hs]
     uint32_t* status;
     unsigned long long* timeline;            // nullptr, or [blocks][6] phase marks in ns (tuning aid)
+    uint32_t wait_limit;                     // polls before a bounded wait gives up (0: the kernel's default)
+    int fault_chunk_plus1;                   // testing aid: c + 1 makes every block expect 16 bytes too many for chunk c of its
+                                             // first item, so that barrier never completes and the wait runs out (0: off)
 };
 void launch_mem_heads(cudaStream_t st, const MemHeadsArgs& a);
 // The same for T tokens in time order with the slice resident in shared memory between them: the vectors and y are
@@ -239,6 +245,10 @@ void launch_dense_mix(cudaStream_t st, float* x, float* streams, const float* w,
 // `diary::pick` for every row: softmax(logits / temperature), the top_k most likely, one draw with the row's uniform
 // number in [0, 1).  false: not covered (top_k above 1024, a vocabulary too large for shared memory, temperature <= 0).
 bool launch_sample(cudaStream_t st, const float* logits, int M, int V, float temperature, int top_k, const double* uniform, uint32_t* next);
+// whether launch_sample covers a vocabulary and a top_k (asked before a step moves the state, and once per generation)
+bool sample_covered(int V, int top_k);
+// the largest vocabulary launch_surprise holds in shared memory
+constexpr int SURPRISE_MAX_VOCAB = 220 * 1024 / 4;
 void launch_argmax(cudaStream_t st, const float* logits, int M, int V, uint32_t* next);
 void launch_math(cudaStream_t st, int which, const float* x, int64_t n, float* y);
 void launch_round_bf16(cudaStream_t st, const float* x, int64_t n, uint16_t* y);

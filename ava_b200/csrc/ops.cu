@@ -3,6 +3,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstring>
 #include <vector>
 
 #include "../../include/ava_engine.h"
@@ -228,6 +229,38 @@ int ava_op_mem_heads(int device, int32_t m, int32_t hs, const float* e, const fl
     OCK(cudaMemcpy(f, df.p, fb, cudaMemcpyDeviceToHost));
     OCK(cudaMemcpy(y, dy.p, vb, cudaMemcpyDeviceToHost));
     return AVA_OK;
+}
+
+/* Testing aid for the kernels' bounded waits (no GPU fault involved: every copy completes, only a barrier is told to
+ * expect 16 bytes more than will ever arrive).  Runs the fast-weight update + read on m heads of size hs whose state
+ * is filled with a pattern, with chunk `chunk` of every block's first item mis-counted and a poll limit of
+ * `poll_limit`, so the wait on that chunk runs out.  Returns what a step would return for the raised status word
+ * (AVA_ERR_CUDA when the time-out was flagged, AVA_OK when it was not) and sets *state_changed to 1 when any bit of the
+ * state in device memory differs from the pattern afterwards (it must not: a block that gave up stores nothing). */
+int ava_debug_mem_heads_wait_runs_out(int device, int32_t m, int32_t hs, int32_t chunk, uint32_t poll_limit, int32_t* state_changed) {
+    int cw, rb;
+    if (!state_changed || m <= 0 || hs % 16 || !mem_heads_tiling(hs, &cw, &rb) || chunk < 0 || chunk >= hs / rb || poll_limit == 0) return AVA_ERR_ARG;
+    int rc = begin(device);
+    if (rc) return rc;
+    const size_t vn = (size_t)m * hs, fn = (size_t)m * hs * hs;
+    std::vector<float> hv(vn), hf(fn), back(fn);
+    for (size_t i = 0; i < vn; ++i) hv[i] = 0.01f * (float)((i * 37) % 101) - 0.5f;
+    for (size_t i = 0; i < fn; ++i) hf[i] = 0.001f * (float)((i * 131) % 1999) - 1.0f;
+    Tmp dv, dq, df, dy, dst;
+    OCK(up(dv, hv.data(), vn * 4)); OCK(up(dq, hv.data(), (size_t)m * 4)); OCK(up(df, hf.data(), fn * 4)); OCK(up(dy, nullptr, vn * 4)); OCK(up(dst, nullptr, 4));
+    OCK(cudaMemset(dst.p, 0, 4));
+    MemHeadsArgs a{};
+    a.f = df.as<float>(); a.M = m; a.nh = 1; a.hs = hs; a.cw = cw; a.chunk_rows = rb;
+    a.e = a.v = a.w = a.ah = a.qg = a.ex = dv.as<float>(); a.qw = a.qa = dq.as<float>(); a.y = dy.as<float>(); a.status = dst.as<uint32_t>();
+    a.wait_limit = poll_limit;
+    a.fault_chunk_plus1 = chunk + 1;
+    launch_mem_heads(0, a);
+    if ((rc = end_())) return rc;
+    uint32_t st = 0;
+    OCK(cudaMemcpy(&st, dst.p, 4, cudaMemcpyDeviceToHost));
+    OCK(cudaMemcpy(back.data(), df.p, fn * 4, cudaMemcpyDeviceToHost));
+    *state_changed = std::memcmp(back.data(), hf.data(), fn * 4) != 0;
+    return (st & ST_WAIT_TIMEOUT) ? AVA_ERR_CUDA : AVA_OK;
 }
 
 /* Tuning aid: the fast-weight kernel on m zeroed heads of size hs with the phase clock on; out [blocks][6] ns marks

@@ -1,10 +1,10 @@
 // One entry point that allocates nothing, for callers that cannot call cudaMalloc.
 //
-// Who that is: code that runs where device allocation is forbidden or would stall everything else — a host callback or
-// a latency-critical service thread that must not take the allocator's device-wide lock, a process whose memory was
-// handed out in full at start-up (a serving runtime that owns the whole GPU), or a region of a program that has begun a
-// stream capture earlier and may not allocate until it ends.  Such a caller already holds its inputs and outputs in
-// device memory and only needs the fast-weight update + read done on them.
+// Who that is: code that runs where device allocation is forbidden or would stall everything else — a latency-critical
+// service thread that must not take the allocator's device-wide lock (cudaMalloc and cudaFree synchronise the whole
+// device), or a process whose GPU memory was handed out in full at start-up (a serving runtime that owns the whole GPU
+// and gives its plug-ins fixed buffers).  Such a caller already holds its inputs and outputs in device memory and only
+// needs the fast-weight update + read done on them.
 //
 // ava_mem_heads_static is ava_op_mem_heads (update + read of m independent fast-weight heads) with two differences:
 // every pointer is DEVICE memory, and the kernel's scratch (the slice-major copy of the heads it works on, plus its
@@ -17,9 +17,15 @@
 //     all it reads and clears its status word itself, but two calls that overlap on the GPU (different streams, or
 //     different host threads) race on it.  Serialise them;
 //   * the first call on each device looks the array's device address up (cudaGetSymbolAddress, with that device
-//     current).  Make that first call before any stream capture begins.
+//     current).  Make that first call before any stream capture begins;
+//   * the kernel fetches e, v, w, ah, qg and ex with bulk copies, which need 16-byte-aligned addresses: a pointer into
+//     the middle of a larger buffer must keep that alignment, or the call is refused with AVA_ERR_ARG before anything
+//     is launched (f, y, qw and qa need only their natural 4-byte alignment);
+//   * the call makes `device` the calling thread's current device and leaves it so, and it returns only after `stream`
+//     has drained (it reads the kernel's status word back).
 #include <cuda_runtime.h>
 
+#include <cstdint>
 #include <string>
 
 #include "../../include/ava_engine.h"
@@ -82,6 +88,16 @@ int ava_mem_heads_static(int device, void* stream, int32_t m, int32_t hs, const 
         return fail(AVA_ERR_CAPACITY, "ava_mem_heads_static: " + std::to_string(m) + " heads of " + std::to_string(hs) + " x " + std::to_string(hs) +
                                           " need " + std::to_string(need) + " floats of scratch; the built-in array holds " +
                                           std::to_string(SCRATCH_FLOATS) + " (use ava_op_mem_heads or an engine state for more)");
+    // the kernel's bulk copies fault on a source that is not 16-byte aligned, and a fault would end the caller's context
+    const void* bulk[6] = {e, v, w, ah, qg, ex};
+    static const char* const bulk_name[6] = {"e", "v", "w", "ah", "qg", "ex"};
+    for (int i = 0; i < 6; ++i)
+        if (reinterpret_cast<uintptr_t>(bulk[i]) & 15)
+            return fail(AVA_ERR_ARG, std::string("ava_mem_heads_static: ") + bulk_name[i] + " must be 16-byte aligned (the kernel reads it with bulk copies)");
+    if ((hs * sizeof(float)) % 16) return fail(AVA_ERR_ARG, "ava_mem_heads_static: rows of hs floats must be a multiple of 16 bytes");
+    const void* word[4] = {qw, qa, f, y};
+    for (int i = 0; i < 4; ++i)
+        if (reinterpret_cast<uintptr_t>(word[i]) & 3) return fail(AVA_ERR_ARG, "ava_mem_heads_static: qw, qa, f and y must be 4-byte aligned");
     int count = 0;
     if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count || device >= MAX_DEVICES)
         return fail(AVA_ERR_CUDA, "no such CUDA device (this library has no CPU path)");

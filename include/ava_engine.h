@@ -364,15 +364,17 @@ int ava_op_kwta(int device, const float* u, int32_t m, int32_t n, int32_t k, int
  * e, v, w, ah, qg, ex [m, hs]; qw, qa [m]; f [m, hs, hs] updated in place; y [m, hs]. */
 int ava_op_mem_heads(int device, int32_t m, int32_t hs, const float* e, const float* v, const float* w, const float* ah,
                      const float* qg, const float* ex, const float* qw, const float* qa, float* f, float* y);
-/* No counterpart in the reference.  ava_op_mem_heads for callers that cannot allocate device memory (code inside a
- * host callback or a latency-critical thread that must not take the allocator's lock, a process whose GPU memory was
- * handed out in full at start-up, a program region that may not allocate until a capture it began earlier ends): every
- * pointer is DEVICE memory, `stream` is a cudaStream_t (NULL: the default stream), f [m, hs, hs] is updated in place
- * and y [m, hs] written.  The kernel's scratch is a built-in device array of AVA_STATIC_SCRATCH_BYTES that every GPU
- * loading the library holds until exit; m * hs * hs above AVA_STATIC_SCRATCH_FLOATS is refused with AVA_ERR_CAPACITY
- * (text from ava_static_last_error).  All calls on a device share that array: calls that overlap on the GPU race.  The
- * first call on a device looks the array's address up; make it before any stream capture.  Returns after the stream
- * has drained. */
+/* No counterpart in the reference.  ava_op_mem_heads for callers that cannot allocate device memory (a latency-critical
+ * thread that must not take the allocator's device-wide lock, a process whose GPU memory was handed out in full at
+ * start-up): every pointer is DEVICE memory, `stream` is a cudaStream_t (NULL: the default stream), f [m, hs, hs] is
+ * updated in place and y [m, hs] written.  e, v, w, ah, qg and ex must be 16-byte aligned (the kernel reads them with
+ * bulk copies; a sub-view of a larger buffer must keep that alignment), qw, qa, f and y 4-byte aligned: anything else
+ * is refused with AVA_ERR_ARG before a launch.  The kernel's scratch is a built-in device array of
+ * AVA_STATIC_SCRATCH_BYTES that every GPU loading the library holds until exit; m * hs * hs above
+ * AVA_STATIC_SCRATCH_FLOATS is refused with AVA_ERR_CAPACITY (text from ava_static_last_error).  All calls on a device
+ * share that array: calls that overlap on the GPU race.  The first call on a device looks the array's address up; make
+ * it before any stream capture.  The call makes `device` the calling thread's current device and returns after the
+ * stream has drained. */
 #define AVA_STATIC_SCRATCH_FLOATS 4194304
 #define AVA_STATIC_SCRATCH_BYTES (4 * AVA_STATIC_SCRATCH_FLOATS)
 int ava_mem_heads_static(int device, void* stream, int32_t m, int32_t hs, const float* e, const float* v, const float* w, const float* ah,
@@ -385,6 +387,12 @@ int ava_op_attend(int device, int32_t m, int32_t n, int32_t hs, int32_t bf16_sto
 /* Tuning aid with no counterpart in the reference: the fast-weight kernel on m zeroed heads of size hs with its phase
  * clock on; out [blocks][6] nanosecond marks, returns the number of blocks (or < 0). */
 int ava_debug_mem_heads_timeline(int device, int32_t m, int32_t hs, uint64_t* out, int64_t cap);
+/* Testing aid for the kernels' bounded waits; no counterpart in the reference (its waits are host-side joins).  Runs
+ * the fast-weight kernel on m pattern-filled heads of size hs with the byte count of row chunk `chunk` over-stated by
+ * 16 on every block's first item and a poll limit of `poll_limit`, so that wait runs out without any copy failing.
+ * Returns AVA_ERR_CUDA when the kernel flagged the time-out (what a step would return), AVA_OK when it did not;
+ * *state_changed = 1 if any bit of the state in device memory changed (a block that gave up must store nothing). */
+int ava_debug_mem_heads_wait_runs_out(int device, int32_t m, int32_t hs, int32_t chunk, uint32_t poll_limit, int32_t* state_changed);
 
 /* The engine's exp / ln / x^-1/2, evaluated on the host with the operation sequence the kernels use (same bits). */
 float ava_host_expf(float x);

@@ -97,3 +97,25 @@ def test_product_does_not_touch_the_oracle():
                 assert "oracle" not in text.lower().replace("a checker", ""), os.path.join(dp, f)
     out = os.popen(f"ldd {engine.LIB_PATH}").read()
     assert "oracle" not in out
+
+
+def test_static_entry_refuses_an_unaligned_vector_before_any_launch(L):
+    """ava_mem_heads_static reads six of its inputs with bulk copies, which fault on a source that is not 16-byte
+    aligned; the entry point must refuse such a pointer with AVA_ERR_ARG before it touches the device (so this runs
+    without a GPU: the check comes before the first CUDA call)."""
+    buf = (C.c_float * 4096)()
+    base = C.addressof(buf)
+    base += (-base) % 16
+    ok = C.c_void_p(base)
+    off4 = C.c_void_p(base + 4)     # a 4-byte-aligned view into the buffer, as a caller slicing a larger array would pass
+    off2 = C.c_void_p(base + 2)
+    for i in range(6):              # e, v, w, ah, qg, ex
+        args = [ok] * 10
+        args[i] = off4
+        rc = L.ava_mem_heads_static(0, None, 1, 64, *args)
+        assert rc == engine.ERR_ARG, i
+        assert b"16-byte aligned" in L.ava_static_last_error()
+    for i in range(6, 10):          # qw, qa, f, y: 4-byte alignment is enough, 2 is not
+        args = [ok] * 10
+        args[i] = off2
+        assert L.ava_mem_heads_static(0, None, 1, 64, *args) == engine.ERR_ARG

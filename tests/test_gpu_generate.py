@@ -129,3 +129,24 @@ def test_generate_sampled_equals_the_callback_form(model):
     assert model.generate_sampled(prompts, 12, 0.8, 16, rng2, eos=eos, stop_fn=stop) == want
     # temperature 0 is the greedy loop
     assert model.generate_sampled(prompts, 6, 0.0, 16, engine.Rng(1), eos=1 << 30) == model.generate(prompts, 6, eos=1 << 30)
+
+
+def test_a_top_k_the_device_sampler_does_not_cover_is_drawn_on_the_host():
+    """`diary::pick` works for any top_k (src/diary.rs:686-718); the device sampler holds at most 1024 kept tokens.  The
+    generation loop decides once per call: beyond that it steps with logits out and draws with the host sampler from the
+    same generator, so the tokens equal the callback form; the single step refuses before the state moves."""
+    cfg = config.tiny(vocab=2048)
+    m = engine.Model(cfg, synth.model(cfg, 4, "awake"))
+    prompts = prompts_of(cfg, [6, 3, 6])
+    rng, rng2 = engine.Rng(11), engine.Rng(11)
+    want = m.generate(prompts, 9, batch_rows=8, eos=1 << 30, pick_fn=lambda r, lg: engine.pick(lg, 0.9, 1500, rng))
+    got = m.generate_sampled(prompts, 9, 0.9, 1500, rng2, batch_rows=8, eos=1 << 30)
+    assert got == want and all(len(g) == 9 for g in got)
+    assert rng2.state.value == rng.state.value
+    st = m.state(2, 16)
+    m.step(st, np.array([1, 2], np.uint32))
+    before = (st.seen(0), st.get(0, "lif.0.v").copy(), st.get(1, "mem.1.f").copy())
+    with pytest.raises(engine.NotApplicable):
+        m.step_sample(st, np.array([3, 4], np.uint32), 0.9, 1500, np.array([0.25, 0.5]))
+    assert st.seen(0) == before[0]
+    assert np.array_equal(st.get(0, "lif.0.v"), before[1]) and np.array_equal(st.get(1, "mem.1.f"), before[2])

@@ -205,6 +205,46 @@ def test_mem_heads_bits(orc, hs, m):
     assert np.array_equal(bits(f2[1]), bits(wf)) and np.array_equal(bits(y2[1]), bits(wy))
 
 
+@pytest.mark.parametrize("hs,m", [(768, 40), (64, 700), (128, 200), (256, 77)])
+def test_mem_heads_bits_when_a_block_walks_several_items(orc, hs, m):
+    """The state pass keeps as many blocks as the GPU holds at once and each walks several (row, slice) items, the
+    next item's rows streaming in while the current one is updated: with more items than blocks every buffer, barrier
+    phase and hand-over between items is exercised.  Same bits as `head_rows` (src/model/fstep/arch.rs:256-337)."""
+    rng = np.random.default_rng(hs + m)
+    unit = lambda x: (x / np.sqrt((x * x).sum(-1, keepdims=True))).astype(np.float32)
+    e, k, q = (unit(rng.normal(size=(m, hs))) for _ in range(3))
+    v = rng.normal(size=(m, hs)).astype(np.float32)
+    ex = rng.uniform(0.9, 1.0, (m, hs)).astype(np.float32)
+    be = rng.uniform(0.05, 1.5, (m, hs)).astype(np.float32)
+    w, ah, qg = k * be, e * (be * ex), q * ex
+    qw, qa = rng.normal(size=m).astype(np.float32), rng.normal(size=m).astype(np.float32)
+    f = rng.normal(0, 0.3, (m, hs, hs)).astype(np.float32)
+    y, f1 = engine.op_mem_heads(e, v, w, ah, qg, ex, qw, qa, f)
+    y2, f2 = engine.op_mem_heads(e, v, w, ah, qg, ex, qw, qa, f1)
+    for i in list(range(0, m, max(1, m // 16))) + [m - 1]:
+        wy, wf, _ = orc.head_rows(e[i], v[i], w[i], ah[i], qg[i], ex[i], float(qw[i]), float(qa[i]), f[i])
+        assert np.array_equal(bits(y[i]), bits(wy)), i
+        assert np.array_equal(bits(f1[i]), bits(wf)), i
+        wy2, wf2, _ = orc.head_rows(e[i], v[i], w[i], ah[i], qg[i], ex[i], float(qw[i]), float(qa[i]), wf)
+        assert np.array_equal(bits(y2[i]), bits(wy2)) and np.array_equal(bits(f2[i]), bits(wf2)), i
+
+
+@pytest.mark.parametrize("hs,m,chunk", [(768, 20, 3), (768, 400, 0), (768, 3, 5), (64, 8, 0), (256, 50, 1)])
+def test_mem_heads_bounded_wait_runs_out_and_the_state_stays(hs, m, chunk):
+    """Every wait on a copy barrier inside the state pass is bounded.  Nothing is made to fault or hang here: all the
+    copies complete, only one barrier per block is told to expect 16 bytes more than will arrive, with a limit of a few
+    thousand polls.  The kernel must give up, raise its status bit (a step then returns AVA_ERR_CUDA) and leave every
+    bit of the state as it was: a block that gave up neither updates nor stores."""
+    import ctypes as C
+    changed = C.c_int32(-1)
+    rc = engine.lib().ava_debug_mem_heads_wait_runs_out(0, m, hs, chunk, 4000, C.byref(changed))
+    assert rc == engine.ERR_CUDA
+    assert changed.value == 0
+    # and the device is fine afterwards: the same kernel, undisturbed, gives the usual bits
+    x = np.full((1, hs), 0.01, np.float32)
+    engine.op_mem_heads(x, x, x, x, x, np.ones((1, hs), np.float32), np.ones(1, np.float32), np.ones(1, np.float32), np.zeros((1, hs, hs), np.float32))
+
+
 @pytest.mark.parametrize("n", [1, 2, 3, 70, 1500])
 @pytest.mark.parametrize("bf16", [False, True])
 def test_attend_bits(orc_same_math, n, bf16):
