@@ -147,7 +147,7 @@ struct ava_engine : Work {
     Dev uniform;       // [rows] f64: the sampler's draws of one step
     Dev ones;          // a vector of ones [d] (the gain of a plain RMS norm)
     std::vector<std::unique_ptr<Work>> more_lanes;  // lanes 1, 2, ... (lane 0 is the engine itself)
-    bool gemm2 = false;                             // dense products through the packed-weight kernel (k_gemm2.cu)
+    bool gemm2 = true;                              // dense products of more than a few rows through the packed-weight kernel (k_gemm2.cu)
     int n_lanes = 1;                                // lanes a decode step of enough rows is split into
     cudaEvent_t fork_ev = nullptr;
     cudaStream_t cur = nullptr;                     // the stream the launch helpers queue on (the lane being queued)
@@ -503,7 +503,7 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
         }
     }
     prof_begin(e, cls);
-    if (!(sparse && launch_q8_event(e->cur, g, epi)) && !(e->gemm2 && launch_q8_gemm2(e->cur, g, epi, e->sm_count))) launch_q8_gemm(e->cur, g, epi, e->sm_count);
+    if (!(sparse && launch_q8_event(e->cur, g, epi)) && !(e->gemm2 && M > 16 && launch_q8_gemm2(e->cur, g, epi, e->sm_count))) launch_q8_gemm(e->cur, g, epi, e->sm_count);
     prof_end(e);
     return AVA_OK;
 }

@@ -88,7 +88,9 @@ __device__ __forceinline__ void bulk_store(void* dst, const void* src, uint32_t 
 
 // One block: row m, head e, slice s.  Shared memory: the slice [hs][CW], then e, qg, ex, w, ah [hs] each, then v, rr,
 // t1 [CW] each, then the barriers.
-template <int CW>
+// DBG: the testing form, whose waits take the caller's poll limit and whose byte count for one chunk can be over-stated
+// so that the wait on it runs out; the production form keeps the limit a compile-time constant.
+template <int CW, bool DBG>
 __global__ void __launch_bounds__(THREADS) mem_heads_kernel(const MemHeadsArgs a) {
     pdl_enter();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -113,7 +115,6 @@ __global__ void __launch_bounds__(THREADS) mem_heads_kernel(const MemHeadsArgs a
     const size_t vo = ((size_t)m * a.nh + head) * hs;  // offset of this head's vectors
     float* gslice = a.f + (vo * hs) + (size_t)slice * hs * CW;  // this block's contiguous slice in HBM
     const uint32_t chunk_bytes = (uint32_t)(cr * CW * sizeof(float));
-    const uint32_t limit = a.wait_limit ? a.wait_limit : WAIT_LIMIT;
     // optional phase clock of thread 0 (nanoseconds, 6 marks per block) for tuning; nullptr in normal runs
     unsigned long long* tl = a.timeline ? a.timeline + (size_t)blockIdx.x * 6 : nullptr;
     auto mark = [&](int i) {
@@ -124,6 +125,7 @@ __global__ void __launch_bounds__(THREADS) mem_heads_kernel(const MemHeadsArgs a
         }
     };
     mark(0);
+    auto wait = [&](uint64_t* bar) { return DBG ? mbar_wait_lim(bar, 0, a.wait_limit ? a.wait_limit : WAIT_LIMIT) : mbar_wait(bar, 0); };
 
     uint64_t* vbar = &bars[nchunk];  // the per-head vectors arrive on their own barrier
     if (tid == 0) {
@@ -137,8 +139,7 @@ __global__ void __launch_bounds__(THREADS) mem_heads_kernel(const MemHeadsArgs a
         bulk_load(ve, a.e + vo, vb, vbar);
         bulk_load(vqg, a.qg + vo, vb, vbar);
         for (int c = 0; c < nchunk; ++c) {
-            // a testing aid can over-state one chunk's byte count so that its barrier never completes
-            mbar_expect_tx(&bars[c], chunk_bytes + (a.fault_chunk_plus1 == c + 1 ? 16u : 0u));
+            mbar_expect_tx(&bars[c], chunk_bytes + ((DBG && a.fault_chunk_plus1 == c + 1) ? 16u : 0u));
             bulk_load(tile + (size_t)c * cr * CW, gslice + (size_t)c * cr * CW, chunk_bytes, &bars[c]);
         }
         bulk_load(vex, a.ex + vo, vb, vbar);
@@ -146,7 +147,7 @@ __global__ void __launch_bounds__(THREADS) mem_heads_kernel(const MemHeadsArgs a
         bulk_load(vah, a.ah + vo, vb, vbar);
         bulk_load(vv, a.v + vo + c0, (uint32_t)(CW * sizeof(float)), vbar);
     }
-    bool ok = mbar_wait_lim(vbar, 0, limit);
+    bool ok = wait(vbar);
     mark(1);
 
     // pass 1: the column sums, rows in order as their chunks land (the first CW threads, one column each).  The chain
@@ -154,8 +155,7 @@ __global__ void __launch_bounds__(THREADS) mem_heads_kernel(const MemHeadsArgs a
     if (tid < CW) {
         float r = -0.0f, t = -0.0f;
         for (int c = 0; c < nchunk; ++c) {
-            ok = mbar_wait_lim(&bars[c], 0, limit) && ok;
-            if (!ok) break;
+            ok = wait(&bars[c]) && ok;
             const float* p = tile + (size_t)c * cr * CW + tid;
             const int end = (c + 1) * cr;
             for (int row = c * cr; row < end; row += 8, p += 8 * CW) {
@@ -182,7 +182,7 @@ __global__ void __launch_bounds__(THREADS) mem_heads_kernel(const MemHeadsArgs a
     __syncthreads();
     // a wait that succeeded makes the copied bytes visible to its own thread only: every other thread waits too
     if (tid >= CW)
-        for (int c = 0; c < nchunk && ok; ++c) ok = mbar_wait_lim(&bars[c], 0, limit);
+        for (int c = 0; c < nchunk; ++c) ok = wait(&bars[c]) && ok;
     // a wait ran out somewhere in the block: flag it and leave the state as it was (no read, no update, no store)
     if (__syncthreads_or(!ok)) {
         if (tid == 0) atomicOr(a.status, ST_WAIT_TIMEOUT);
@@ -448,15 +448,20 @@ bool mem_heads_tiling(int hs, int* cw, int* chunk_rows, bool momentum) {
     return true;
 }
 
+template <int CW, bool DBG>
+static void launch_one(cudaStream_t st, const MemHeadsArgs& a, size_t smem, unsigned grid) {
+    cudaFuncSetAttribute(mem_heads_kernel<CW, DBG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_k(mem_heads_kernel<CW, DBG>, dim3(grid), dim3(THREADS), smem, st, a);
+}
+
 void launch_mem_heads(cudaStream_t st, const MemHeadsArgs& a) {
     const size_t smem = smem_bytes(a.hs, a.cw);
     const unsigned grid = (unsigned)((size_t)a.M * a.nh * (a.hs / a.cw));
+    const bool dbg = a.wait_limit != 0 || a.fault_chunk_plus1 != 0;
     if (a.cw == 32) {
-        cudaFuncSetAttribute(mem_heads_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_k(mem_heads_kernel<32>, dim3(grid), dim3(THREADS), smem, st, a);
+        if (dbg) launch_one<32, true>(st, a, smem, grid); else launch_one<32, false>(st, a, smem, grid);
     } else {
-        cudaFuncSetAttribute(mem_heads_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_k(mem_heads_kernel<16>, dim3(grid), dim3(THREADS), smem, st, a);
+        if (dbg) launch_one<16, true>(st, a, smem, grid); else launch_one<16, false>(st, a, smem, grid);
     }
 }
 

@@ -278,7 +278,22 @@ bool launch_q8_gemm2(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int s
         default: break;
     }
     (void)sm_count;
-    launch_tile2<64, 64, 8, 4>(st, a, epi);
+    // Measured on B200 (one decode step's products are short of warps, so the choice is about filling the SMs; the
+    // wide-tile forms win once there are rows enough):
+    //   thousands of rows (a prompt chunk): 64x128 tiles of 8x8 (the LIF epilogue keeps 8x4);
+    //   129..1023 rows: very wide products 64x64 of 8x4, wide ones 128x64 of 8x4, the rest 32x64 of 4x4;
+    //   65..128 rows: wide products 64x64 of 8x4, narrow ones 32x64 of 4x4;  up to 64 rows: 32x32 of 4x4 when wide.
+    if (a.M >= 1024) {
+        if (epi == EPI_LIF) launch_tile2<64, 64, 8, 4>(st, a, epi); else launch_tile2<64, 128, 8, 8>(st, a, epi);
+    } else if (a.M > 128) {
+        if (a.N >= 8192) launch_tile2<64, 64, 8, 4>(st, a, epi);
+        else if (a.N >= 3584) launch_tile2<128, 64, 8, 4>(st, a, epi);
+        else launch_tile2<32, 64, 4, 4>(st, a, epi);
+    } else if (a.M > 64) {
+        if (a.N >= 1024) launch_tile2<64, 64, 8, 4>(st, a, epi); else launch_tile2<32, 64, 4, 4>(st, a, epi);
+    } else {
+        if (a.N >= 1024) launch_tile2<32, 32, 4, 4>(st, a, epi); else launch_tile2<32, 64, 4, 4>(st, a, epi);
+    }
     return true;
 }
 
