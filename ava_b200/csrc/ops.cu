@@ -73,9 +73,10 @@ static int q8_matmul_impl(int device, const float* x, int32_t m, const int8_t* q
     g.C = dy.as<float>(); g.ldc = dout; g.M = m; g.N = dout; g.K = din;
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    // the kernels a step of this many rows would take (the engine's own choice: see `gemm` in engine.cu)
     if (event) {
         if (!launch_q8_event(0, g, EPI_STORE)) return AVA_NOT_APPLICABLE;
-    } else {
+    } else if (!(m > 16 && launch_q8_gemm2(0, g, EPI_STORE, sms))) {
         launch_q8_gemm(0, g, EPI_STORE, sms);
     }
     if ((rc = end_())) return rc;

@@ -113,6 +113,31 @@ def test_event_sum_bits(orc, density, din, dout):
     assert np.array_equal(bits(engine.op_q8_matmul(x, q, sc)), bits(want))
 
 
+@pytest.mark.parametrize("m,din,dout,density", [(8, 64, 128, 0.5), (77, 3072, 768, 0.25), (256, 768, 768, 0.05), (19, 192, 784, 0.3), (130, 2048, 208, 0.6), (5, 128, 64, 0.2)])
+def test_event_sum_bits_many_rows(orc, m, din, dout, density):
+    """The event sum of a batch of rows: the dense sum's bits for every row, for row counts and widths that do and do not
+    fill a block's columns, with rows of all zeros, -0 (skipped) and a NaN (kept: src/int8.rs:261-269)."""
+    rng = np.random.default_rng(m + din + dout)
+    q = rng.integers(-127, 128, (din, dout)).astype(np.int8)
+    sc = (rng.uniform(0.5, 1.5, dout) / 127).astype(np.float32)
+    x = np.zeros((m, din), np.float32)
+    on = rng.random((m, din)) < density
+    x[on] = rng.normal(size=on.sum())
+    x[0][on[0]] = rng.integers(-2, 3, on[0].sum())
+    x[1, ::7] = -0.0
+    x[2] = 0.0
+    x[m - 1, din // 2] = np.nan
+    orc.set_threads(8)
+    try:
+        want = orc.q8_matmul(x, q, sc)
+    finally:
+        orc.set_threads(1)
+    got = engine.op_q8_matmul(x, q, sc, event=True)
+    assert np.array_equal(bits(got[:m - 1]), bits(want[:m - 1]))
+    assert np.isnan(got[m - 1]).all() and np.isnan(want[m - 1]).all()
+    assert not np.isnan(got[:m - 1]).any()
+
+
 @pytest.mark.parametrize("m,n", [(1, 64), (7, 768), (300, 2048)])
 def test_rmsnorm_bits(orc_same_math, m, n):
     rng = np.random.default_rng(n)
