@@ -111,6 +111,8 @@ struct Work {
     Dev eng_partial;         // [rows][heads][segments][2 + hs] partial softmax statistics of the segmented read
     cudaStream_t lane_stream = nullptr;  // lanes after the first: the stream their kernels are queued on
     cudaEvent_t lane_done = nullptr;
+    cudaStream_t side_stream = nullptr;  // the lane's side stream: the gates' projections run there beside the q|k|v|e|g product
+    cudaEvent_t side_go = nullptr, side_done = nullptr;
 };
 
 struct ava_engine : Work {
@@ -148,7 +150,7 @@ struct ava_engine : Work {
     Dev ones;          // a vector of ones [d] (the gain of a plain RMS norm)
     std::vector<std::unique_ptr<Work>> more_lanes;  // lanes 1, 2, ... (lane 0 is the engine itself)
     bool gemm2 = true;                              // dense products of more than a few rows through the packed-weight kernel (k_gemm2.cu)
-    int n_lanes = 1;                                // lanes a decode step of enough rows is split into
+    int n_lanes = 2;                                // lanes a decode step of enough rows is split into (ava_engine_set_lanes)
     cudaEvent_t fork_ev = nullptr;
     cudaStream_t cur = nullptr;                     // the stream the launch helpers queue on (the lane being queued)
     uint32_t* status_host = nullptr;  // pinned
@@ -193,6 +195,14 @@ struct ava_state {
     Dev lif_v, lif_s, lif_a;  // [L][rows][d]
     Dev mem_f;                // [L][rows][nh][hs / cw][hs][cw]: slice-major, a block of threads owns one contiguous slice
     Dev mem_s;                // the momentum matrix, same layout (only with --mem-momentum)
+    // The plain memory's decode pass (k_stream.cu) leaves each token's update pending: alpha, w, ah per row and value,
+    // rr per column of every block, [2][5][L][rows][d] (two sets that take turns: one is written by this step while the
+    // other, the step before's, is applied).  mem_f is one update behind while `pending` is set; flush_pending()
+    // brings it up to date for every other reader.
+    Dev pend;
+    bool pending = false;
+    int pend_set = 0;         // the set the LAST step wrote
+    float* pend_at(int set, int what, int block) { return pend.as<float>() + ((((size_t)set * 5 + what) * e->cfg.n_blocks + block) * rows) * e->cfg.d; }
     Dev stp_u, stp_x;         // [L][rows][d]: the synapse's (u, x) (only with --stp; a fresh state has u = 0, x = 1)
     Dev rh;                                   // --rhythm: the time since each clock's last reset [rows][2]
     Dev sur_prev, sur_valid, sur_last, mood;  // --dopamine / --mood: block 0's last normed output [rows][d], whether there is one
@@ -633,8 +643,6 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
         prof_end(e);
         dbg(e, "h_mem", i, h, M, d);
         const int pw = e->proj_w();
-        gemm(e, "gemm.qkveg", h, d, b.proj, w.proj.as<float>(), pw, M, EPI_STORE);
-        dbg(e, "qkveg", i, w.proj.as<float>(), M, pw);
         MemPrepArgs mp{};
         mp.h = h;
         mp.proj = w.proj.as<float>();
@@ -651,6 +659,13 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
         mp.qg = w.vqg.as<float>(); mp.ex = w.vex.as<float>(); mp.qw = w.qw.as<float>(); mp.qa = w.qa.as<float>();
         mp.qs = c.mem_momentum > 0.0f ? w.vqs.as<float>() : nullptr;
         mp.mom = c.mem_momentum;
+        // One token of the plain memory takes the streaming pass: this token's alpha, w, ah and values go straight into
+        // the state's pending set (the one this step writes), the pass reads the set the step before wrote.
+        const bool stream = T == 1 && !(c.mem_momentum > 0.0f);
+        const int wset = s->pend_set ^ 1;
+        if (stream) {
+            mp.ex = s->pend_at(wset, 0, i) + so; mp.w = s->pend_at(wset, 1, i) + so; mp.ah = s->pend_at(wset, 2, i) + so; mp.v = s->pend_at(wset, 3, i) + so;
+        }
         if (c.rhythm) {
             prof_begin(e, "rhythm");
             launch_rhythm_gates(st, w.rh_f.as<float>(), b.rh_w.as<float>(), b.rh_r.as<float>(), M, nh, w.rh_gw.as<float>(), w.rh_gr.as<float>());
@@ -664,8 +679,24 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
             if (w.side.bytes < Md * sizeof(float)) CK(w.side.alloc(Md * sizeof(float)));
             mp.be_out = w.side.as<float>();
         }
+        // the gates' two projection stages read the normed input alone: on the lane's side stream they run beside the
+        // q|k|v|e|g product (both are short of warps on their own); the per-row kernel then needs both
+        const bool fork = w.side_stream != nullptr && !e->prof && !e->keep;
+        if (fork) {
+            CK(cudaEventRecord(w.side_go, st));
+            CK(cudaStreamWaitEvent(w.side_stream, w.side_go, 0));
+            launch_mem_gates(w.side_stream, mp);
+            CK(cudaEventRecord(w.side_done, w.side_stream));
+        }
+        gemm(e, "gemm.qkveg", h, d, b.proj, w.proj.as<float>(), pw, M, EPI_STORE);
+        dbg(e, "qkveg", i, w.proj.as<float>(), M, pw);
         prof_begin(e, "mem_prep");
-        launch_mem_prep(st, mp);
+        if (fork) {
+            CK(cudaStreamWaitEvent(st, w.side_done, 0));
+            launch_mem_prep_rows(st, mp);
+        } else {
+            launch_mem_prep(st, mp);
+        }
         prof_end(e);
         if (e->keep) dbg(e, "be", i, w.side.as<float>(), M, d);
         e->launches += 2;  // the two stages of the gate projections before it
@@ -681,10 +712,21 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
         mh.y = w.yraw.as<float>();
         mh.status = e->status.as<uint32_t>();
         prof_begin(e, "mem_heads");
-        if (T == 1 && !mh.s)
-            launch_mem_heads(st, mh);
-        else
+        if (stream) {
+            MemStreamArgs ms{};
+            ms.f = mh.f; ms.M = rows; ms.nh = nh; ms.hs = hs; ms.cw = e->cw;
+            ms.e = mp.e; ms.qg = mp.qg; ms.v = mp.v; ms.qw = mp.qw; ms.qa = mp.qa;
+            ms.y = mh.y;
+            ms.rr_out = s->pend_at(wset, 4, i) + so;
+            if (s->pending) {
+                const int rset = s->pend_set;
+                ms.px = s->pend_at(rset, 0, i) + so; ms.pw = s->pend_at(rset, 1, i) + so; ms.pah = s->pend_at(rset, 2, i) + so;
+                ms.pv = s->pend_at(rset, 3, i) + so; ms.prr = s->pend_at(rset, 4, i) + so;
+            }
+            if (!launch_mem_stream(st, ms)) return e->fail(AVA_ERR_CAPACITY, "memory head size not covered by the streaming pass");
+        } else {
             launch_mem_heads_seq(st, mh, T);
+        }
         prof_end(e);
         dbg(e, "y_raw", i, mh.y, M, d);
         prof_begin(e, "mem_post");
@@ -898,19 +940,40 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
     return AVA_OK;
 }
 
+int flush_pending(ava_engine* e, ava_state* s);
+
 // The step of a whole state.  A decode step (T == 1) of enough rows runs as `n_lanes` lanes: contiguous windows of the
 // rows, each with its own work buffers and stream, forked from the engine's stream and joined back into it, so callers
 // see one stream as before.  Rows are independent (src/state.rs:13-15), so the lanes compute the same bits.
 int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits, uint32_t* next, bool want_logits, int T = 1, bool all_logits = false,
                 StepPhase phase = PHASE_ALL) {
+    // a token's pending set is complete once its last block is through: a step split in two (BEGIN, END) writes one set
+    // across both halves, so the sets change places after ALL or END only
+    const bool streams_state = e->cfg.fast_mem && T == 1 && !(e->cfg.mem_momentum > 0.0f) && phase != PHASE_BEGIN;
+    if (!streams_state && T > 1) {
+        const int frc = flush_pending(e, s);  // a chunk of tokens works on the state itself
+        if (frc) return frc;
+    }
     int lanes = 1;
-    if (e->n_lanes > 1 && T == 1 && phase == PHASE_ALL && !e->keep && !e->fast && s->rows >= 16 * e->n_lanes) lanes = e->n_lanes;
-    if (lanes == 1) return step_rows(e, *e, e->stream, s, 0, s->rows, tok, logits, next, want_logits, T, all_logits, phase);
+    if (e->n_lanes > 1 && T == 1 && phase == PHASE_ALL && !e->keep && !e->fast && !e->prof) lanes = std::max(1, std::min(e->n_lanes, s->rows / 48));  // a lane of fewer rows gains nothing
+    if (lanes == 1) {
+        const int rc1 = step_rows(e, *e, e->stream, s, 0, s->rows, tok, logits, next, want_logits, T, all_logits, phase);
+        if (rc1 == AVA_OK && streams_state) {
+            s->pend_set ^= 1;
+            s->pending = true;
+        }
+        return rc1;
+    }
     const int per = (s->rows + lanes - 1) / lanes;
     while ((int)e->more_lanes.size() < lanes - 1) {
         std::unique_ptr<Work> w(new Work());
         CK(cudaStreamCreateWithFlags(&w->lane_stream, cudaStreamNonBlocking));
         CK(cudaEventCreateWithFlags(&w->lane_done, cudaEventDisableTiming));
+        if (e->side_stream) {
+            CK(cudaStreamCreateWithFlags(&w->side_stream, cudaStreamNonBlocking));
+            CK(cudaEventCreateWithFlags(&w->side_go, cudaEventDisableTiming));
+            CK(cudaEventCreateWithFlags(&w->side_done, cudaEventDisableTiming));
+        }
         e->more_lanes.push_back(std::move(w));
     }
     if (!e->fork_ev) CK(cudaEventCreateWithFlags(&e->fork_ev, cudaEventDisableTiming));
@@ -933,6 +996,10 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         }
     }
     e->cur = e->stream;
+    if (rc == AVA_OK && streams_state) {
+        s->pend_set ^= 1;
+        s->pending = true;
+    }
     return rc;
 }
 
@@ -1045,6 +1112,7 @@ int alloc_state(ava_engine* e, int rows, int ring, int keep, ava_state** out) {
     }
     if (c.fast_mem) CK(s->mem_f.alloc(L * M * d * c.head_size * f));
     if (c.fast_mem && c.mem_momentum > 0.0f) CK(s->mem_s.alloc(L * M * d * c.head_size * f));
+    if (c.fast_mem && !(c.mem_momentum > 0.0f)) CK(s->pend.alloc(2 * 5 * L * M * d * f));
     if (c.eng_block >= 0) {
         CK(s->eng_k.alloc(M * d * ring * s->kv_elem()));
         CK(s->eng_v.alloc(M * d * ring * s->kv_elem()));
@@ -1064,6 +1132,22 @@ int zero_state(ava_engine* e, ava_state* s) {
         if (b->p) CK(cudaMemsetAsync(b->p, 0, b->bytes, e->stream));
     if (s->stp_x.p) launch_fill(e->stream, s->stp_x.as<float>(), (int64_t)(s->stp_x.bytes / sizeof(float)), 1.0f);  // x starts at 1
     CK(cudaStreamSynchronize(e->stream));
+    return AVA_OK;
+}
+
+// Applies the update the last decode step left pending to the fast weights, so that mem_f is the state every reader
+// other than the next streaming pass expects (queued on the engine's stream; callers that read next synchronise anyway).
+int flush_pending(ava_engine* e, ava_state* s) {
+    if (!s->pending) return AVA_OK;
+    const ava_config& c = e->cfg;
+    CK(cudaSetDevice(e->device));
+    for (int i = 0; i < c.n_blocks; ++i)
+        launch_mem_flush(e->stream, s->mem_f.as<float>() + (size_t)i * s->rows * c.d * c.head_size, s->pend_at(s->pend_set, 0, i), s->pend_at(s->pend_set, 1, i),
+                         s->pend_at(s->pend_set, 2, i), s->pend_at(s->pend_set, 3, i), s->pend_at(s->pend_set, 4, i), (int64_t)s->rows * e->nh(), c.head_size, e->cw);
+    e->launches += c.n_blocks;
+    s->pending = false;
+    const cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) return e->cuda_fail(le, "kernel launch");
     return AVA_OK;
 }
 
@@ -1145,6 +1229,11 @@ int ava_engine_create(const ava_config* cfg, int device, ava_engine** out) {
         return AVA_ERR_CUDA;
     }
     e->cur = e->stream;
+    if (!std::getenv("AVA_NO_SIDE")) {
+        cudaStreamCreateWithFlags(&e->side_stream, cudaStreamNonBlocking);
+        cudaEventCreateWithFlags(&e->side_go, cudaEventDisableTiming);
+        cudaEventCreateWithFlags(&e->side_done, cudaEventDisableTiming);
+    }
     if (const char* v = std::getenv("AVA_PDL")) g_pdl = std::atoi(v) != 0;
     if (const char* v = std::getenv("AVA_LANES")) e->n_lanes = std::max(1, std::min(8, std::atoi(v)));
     if (const char* v = std::getenv("AVA_GEMM2")) e->gemm2 = std::atoi(v) != 0;
@@ -1169,7 +1258,13 @@ void ava_engine_destroy(ava_engine* e) {
             cudaStreamDestroy(w->lane_stream);
         }
         if (w->lane_done) cudaEventDestroy(w->lane_done);
+        if (w->side_stream) cudaStreamDestroy(w->side_stream);
+        if (w->side_go) cudaEventDestroy(w->side_go);
+        if (w->side_done) cudaEventDestroy(w->side_done);
     }
+    if (e->side_stream) cudaStreamDestroy(e->side_stream);
+    if (e->side_go) cudaEventDestroy(e->side_go);
+    if (e->side_done) cudaEventDestroy(e->side_done);
     if (e->fork_ev) cudaEventDestroy(e->fork_ev);
     if (e->stream) {
         cudaStreamSynchronize(e->stream);
@@ -1507,8 +1602,9 @@ int ava_state_select(const ava_state* s, const int32_t* idx, int32_t n, ava_stat
         if (idx[i] < 0 || idx[i] >= s->rows) return e->fail(AVA_ERR_ARG, "select: row %d of %d", idx[i], s->rows);
     CK(cudaSetDevice(e->device));
     ava_state* o = nullptr;
-    int rc = alloc_state(e, n, s->ring, s->keep, &o);
+    int rc = flush_pending(e, const_cast<ava_state*>(s));  // the copy takes the fast weights as they are in memory
     if (rc) return rc;
+    if ((rc = alloc_state(e, n, s->ring, s->keep, &o))) return rc;
     for (int i = 0; i < n && !rc; ++i) rc = copy_row(e, s, idx[i], o, i);
     if (!rc) rc = push_counts(e, o);
     if (rc) {
@@ -1530,8 +1626,10 @@ int ava_state_cat(const ava_state* const* parts, int32_t n, ava_state** out) {
     }
     CK(cudaSetDevice(e->device));
     ava_state* o = nullptr;
-    int rc = alloc_state(e, rows, parts[0]->ring, parts[0]->keep, &o);
+    int rc = AVA_OK;
+    for (int i = 0; i < n && !rc; ++i) rc = flush_pending(e, const_cast<ava_state*>(parts[i]));
     if (rc) return rc;
+    if ((rc = alloc_state(e, rows, parts[0]->ring, parts[0]->keep, &o))) return rc;
     int at = 0;
     for (int i = 0; i < n && !rc; ++i)
         for (int r = 0; r < parts[i]->rows && !rc; ++r) rc = copy_row(e, parts[i], r, o, at++);
@@ -1566,6 +1664,10 @@ int ava_state_export(const ava_state* s, int32_t row, const char* name, float* o
     StateSlice sl;
     if (row < 0 || row >= s->rows || !locate(s, row, name, &sl)) return e->fail(AVA_ERR_ARG, "no state tensor %s of row %d", name, row);
     CK(cudaSetDevice(e->device));
+    if (sl.tiled) {
+        const int frc = flush_pending(e, const_cast<ava_state*>(s));
+        if (frc) return frc;
+    }
     CK(cudaStreamSynchronize(e->stream));
     if (sl.tiled) {
         Dev tmp;
@@ -1601,6 +1703,10 @@ int ava_state_import(ava_state* s, int32_t row, const char* name, const float* i
     StateSlice sl;
     if (row < 0 || row >= s->rows || !locate(s, row, name, &sl)) return e->fail(AVA_ERR_ARG, "no state tensor %s of row %d", name, row);
     CK(cudaSetDevice(e->device));
+    if (sl.tiled) {
+        const int frc = flush_pending(e, s);  // the other rows' pending updates must not be lost, nor applied to what is written now
+        if (frc) return frc;
+    }
     CK(cudaStreamSynchronize(e->stream));
     if (!sl.eng) {
         if ((int64_t)sl.count != n) return e->fail(AVA_ERR_ARG, "%s: %lld values, want %lld", name, (long long)n, (long long)sl.count);
@@ -1862,6 +1968,12 @@ int ava_engine_set_segmented_read(ava_engine* e, int32_t seg_len) {
 
 const ava_config* ava_engine_config(const ava_engine* e) { return e ? &e->cfg : nullptr; }
 int ava_engine_device(const ava_engine* e) { return e ? e->device : -1; }
+
+int ava_engine_set_lanes(ava_engine* e, int32_t lanes) {
+    if (!e || lanes < 1 || lanes > 8) return AVA_ERR_ARG;
+    e->n_lanes = lanes;
+    return AVA_OK;
+}
 
 int ava_engine_set_fast_products(ava_engine* e, int32_t on) {
     if (!e) return AVA_ERR_ARG;

@@ -1,4 +1,6 @@
-// The fast-weight memory's update + read for one token (sm_100a): the kernel that streams the carried state.
+// The fast-weight memory's update + read with a block's slice of the state resident in shared memory (sm_100a): the form for
+// a chunk of T tokens (prompt reading) and for the memory with momentum.  One token of the plain memory takes the streaming
+// pass of k_stream.cu.
 //
 // Per head, F [hs, hs] f32 (row = key dimension, column = value dimension), as the reference's `head_rows`
 // (design-tests/nn/gpu/src/model/fstep/arch.rs:256-337) without momentum:
@@ -9,9 +11,8 @@
 // Columns are independent, so one block of threads owns a slice of CW columns of one head.  The state is kept
 // SLICE-MAJOR in HBM: [row][head][slice][hs][CW], so a block's slice is one contiguous run of hs * CW * 4 bytes.  It
 // comes into shared memory as a few large bulk copies (cp.async.bulk, one mbarrier per chunk of rows), the column sums
-// run down the rows as the chunks land, the slice is updated in place in shared memory and each chunk is written back
-// with a bulk store as soon as it is done.  Per token the state is read once and written once: 8 bytes per state
-// element is the kernel's whole DRAM traffic apart from the per-head vectors.
+// run down the rows, the slice is updated in place in shared memory token after token, and it goes back with bulk stores
+// once the chunk's last token is done: the state is read once and written once per CHUNK.
 #include "ava_math.h"
 #include "kernels.cuh"
 
@@ -86,156 +87,17 @@ __device__ __forceinline__ void bulk_store(void* dst, const void* src, uint32_t 
     asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)), "r"(bytes) : "memory");
 }
 
-// One block: row m, head e, slice s.  Shared memory: the slice [hs][CW], then e, qg, ex, w, ah [hs] each, then v, rr,
-// t1 [CW] each, then the barriers.
-// DBG: the testing form, whose waits take the caller's poll limit and whose byte count for one chunk can be over-stated
-// so that the wait on it runs out; the production form keeps the limit a compile-time constant.
-template <int CW, bool DBG>
-__global__ void __launch_bounds__(THREADS) mem_heads_kernel(const MemHeadsArgs a) {
-    pdl_enter();
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    const int hs = a.hs, cr = a.chunk_rows, nchunk = hs / cr;
-    float* tile = reinterpret_cast<float*>(smem_raw);
-    float* ve = tile + (size_t)hs * CW;
-    float* vqg = ve + hs;
-    float* vex = vqg + hs;
-    float* vw = vex + hs;
-    float* vah = vw + hs;
-    float* vv = vah + hs;
-    float* rr = vv + CW;
-    float* t1 = rr + CW;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(t1 + CW);
-
-    const int tid = threadIdx.x;
-    const int slices = hs / CW;
-    const int slice = blockIdx.x % slices;
-    const int head = (blockIdx.x / slices) % a.nh;
-    const int m = blockIdx.x / (slices * a.nh);
-    const int c0 = slice * CW;
-    const size_t vo = ((size_t)m * a.nh + head) * hs;  // offset of this head's vectors
-    float* gslice = a.f + (vo * hs) + (size_t)slice * hs * CW;  // this block's contiguous slice in HBM
-    const uint32_t chunk_bytes = (uint32_t)(cr * CW * sizeof(float));
-    // optional phase clock of thread 0 (nanoseconds, 6 marks per block) for tuning; nullptr in normal runs
-    unsigned long long* tl = a.timeline ? a.timeline + (size_t)blockIdx.x * 6 : nullptr;
-    auto mark = [&](int i) {
-        if (tl && tid == 0) {
-            unsigned long long t;
-            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-            tl[i] = t;
-        }
-    };
-    mark(0);
-    auto wait = [&](uint64_t* bar) { return DBG ? mbar_wait_lim(bar, 0, a.wait_limit ? a.wait_limit : WAIT_LIMIT) : mbar_wait(bar, 0); };
-
-    uint64_t* vbar = &bars[nchunk];  // the per-head vectors arrive on their own barrier
-    if (tid == 0) {
-        for (int c = 0; c <= nchunk; ++c) mbar_init(&bars[c], 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    if (tid == 0) {
-        const uint32_t vb = (uint32_t)(hs * sizeof(float));
-        mbar_expect_tx(vbar, 5 * vb + (uint32_t)(CW * sizeof(float)));
-        bulk_load(ve, a.e + vo, vb, vbar);
-        bulk_load(vqg, a.qg + vo, vb, vbar);
-        for (int c = 0; c < nchunk; ++c) {
-            mbar_expect_tx(&bars[c], chunk_bytes + ((DBG && a.fault_chunk_plus1 == c + 1) ? 16u : 0u));
-            bulk_load(tile + (size_t)c * cr * CW, gslice + (size_t)c * cr * CW, chunk_bytes, &bars[c]);
-        }
-        bulk_load(vex, a.ex + vo, vb, vbar);
-        bulk_load(vw, a.w + vo, vb, vbar);
-        bulk_load(vah, a.ah + vo, vb, vbar);
-        bulk_load(vv, a.v + vo + c0, (uint32_t)(CW * sizeof(float)), vbar);
-    }
-    bool ok = wait(vbar);
-    mark(1);
-
-    // pass 1: the column sums, rows in order as their chunks land (the first CW threads, one column each).  The chain
-    // starts from -0: fma(f, e, -0) is the rounded product with its own sign, i.e. row 0's plain product.
-    if (tid < CW) {
-        float r = -0.0f, t = -0.0f;
-        for (int c = 0; c < nchunk; ++c) {
-            ok = wait(&bars[c]) && ok;
-            const float* p = tile + (size_t)c * cr * CW + tid;
-            const int end = (c + 1) * cr;
-            for (int row = c * cr; row < end; row += 8, p += 8 * CW) {
-                float f[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) f[i] = p[i * CW];
-                const float4 e0 = *reinterpret_cast<const float4*>(ve + row), e1 = *reinterpret_cast<const float4*>(ve + row + 4);
-                const float4 g0 = *reinterpret_cast<const float4*>(vqg + row), g1 = *reinterpret_cast<const float4*>(vqg + row + 4);
-                const float ev[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
-                const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    r = fma(f[i], ev[i], r);
-                    t = fma(f[i], gv[i], t);
-                }
-            }
-        }
-        // the recall's term from inside the one-token chunk is an exact zero (arch.rs:277-280): kept for the sign of zero
-        r = add(r, mul(1.0f, mul(0.0f, vv[tid])));
-        rr[tid] = r;
-        t1[tid] = t;
-    }
-    mark(2);
-    __syncthreads();
-    // a wait that succeeded makes the copied bytes visible to its own thread only: every other thread waits too
-    if (tid >= CW)
-        for (int c = 0; c < nchunk; ++c) ok = wait(&bars[c]) && ok;
-    // a wait ran out somewhere in the block: flag it and leave the state as it was (no read, no update, no store)
-    if (__syncthreads_or(!ok)) {
-        if (tid == 0) atomicOr(a.status, ST_WAIT_TIMEOUT);
-        return;
-    }
-
-    // the read
-    if (tid < CW) {
-        const float qw = a.qw[(size_t)m * a.nh + head], qa = a.qa[(size_t)m * a.nh + head];
-        a.y[vo + c0 + tid] = sub(add(t1[tid], mul(qw, vv[tid])), mul(qa, rr[tid]));
-    }
-    // pass 2: the update in place, four columns per thread, chunk by chunk; each chunk goes back to HBM as soon as
-    // it is done
-    {
-        constexpr int QW = CW / 4, RPP = THREADS / QW;  // threads per row, rows per sweep
-        const int q4 = tid % QW, rg = tid / QW;
-        const float4 vb = *reinterpret_cast<const float4*>(vv + 4 * q4), rb4 = *reinterpret_cast<const float4*>(rr + 4 * q4);
-        for (int c = 0; c < nchunk; ++c) {
-            const int end = (c + 1) * cr;
-#pragma unroll 2
-            for (int row = c * cr + rg; row < end; row += RPP) {
-                float4* p = reinterpret_cast<float4*>(tile + (size_t)row * CW) + q4;
-                float4 f = *p;
-                const float x = vex[row], w = vw[row], ah = vah[row];
-                f.x = sub(add(mul(f.x, x), mul(w, vb.x)), mul(ah, rb4.x));
-                f.y = sub(add(mul(f.y, x), mul(w, vb.y)), mul(ah, rb4.y));
-                f.z = sub(add(mul(f.z, x), mul(w, vb.z)), mul(ah, rb4.z));
-                f.w = sub(add(mul(f.w, x), mul(w, vb.w)), mul(ah, rb4.w));
-                *p = f;
-            }
-            // generic-proxy writes must be visible to the bulk-copy engine before it reads the chunk
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncthreads();
-            if (tid == 0) {
-                bulk_store(gslice + (size_t)c * cr * CW, tile + (size_t)c * cr * CW, chunk_bytes);
-                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-            }
-        }
-    }
-    mark(3);
-    // the shared memory must stay until the engine has read it
-    if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-    mark(4);
-}
-
-// The same update + read for T tokens in a row (chunked prompt reading): the block's slice comes into shared memory
+// The update + read for T tokens in a row (chunked prompt reading, and the memory with momentum): one block owns row m, head e,
+// slice s; the block's slice comes into shared memory
 // once, every token of the chunk updates it there in order, and it goes back to HBM once: the state traffic of a chunk
 // is that of one token.  Per token the block needs the head's vectors (time-major [T][M][nh * hs]), all brought by
 // bulk copies that overlap the other pass: alpha, w and ah of token t land while its column sums run; e, q*alpha of
 // token t + 1 land while token t's update runs (the value slice is double-buffered: both passes read it).
 // MOM: the memory's momentum (second matrix S, src/model/fstep/arch.rs:281-323): rr gains p2 S (an exact zero kept for
 // the sign of zero), y gains (q M) S, F' = ((F alpha + w v^T) - ah rr^T) + S M, S' = ((S M + 0) + w v^T) - ah rr^T.
-template <int CW, bool MOM>
+// DBG: the testing form, whose waits take the caller's poll limit and whose byte count for one chunk can be over-stated
+// so that the wait on it runs out; the production form keeps the limit a compile-time constant.
+template <int CW, bool MOM, bool DBG>
 __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsArgs a, int T) {
     pdl_enter();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -295,22 +157,27 @@ __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsAr
     if (tid == 0) {
         fetch_a(0);
         for (int c = 0; c < nchunk; ++c) {
-            mbar_expect_tx(&bars[c], (MOM ? 2 : 1) * chunk_bytes);
+            mbar_expect_tx(&bars[c], (MOM ? 2 : 1) * chunk_bytes + ((DBG && a.fault_chunk_plus1 == c + 1) ? 16u : 0u));
             bulk_load(tile + (size_t)c * cr * CW, gslice + (size_t)c * cr * CW, chunk_bytes, &bars[c]);
             if (MOM) bulk_load(tileS + (size_t)c * cr * CW, gsliceS + (size_t)c * cr * CW, chunk_bytes, &bars[c]);
         }
     }
     bool ok = true;
+    auto wait = [&](uint64_t* bar, uint32_t par) { return DBG ? mbar_wait_lim(bar, par, a.wait_limit ? a.wait_limit : WAIT_LIMIT) : mbar_wait(bar, par); };
     const float mf = a.mom;
     const float gsx = add(mul(0.0f, mf), 0.0f);  // the factor of the recall's zero row p2 = e * (0 * M + 0)
-    for (int c = 0; c < nchunk; ++c) ok = mbar_wait(&bars[c], 0) && ok;  // the slice is resident from here on
+    for (int c = 0; c < nchunk; ++c) ok = wait(&bars[c], 0) && ok;  // the slice is resident from here on
+    if (__syncthreads_or(!ok)) {  // not even the slice arrived: nothing is computed, nothing stored
+        if (tid == 0) atomicOr(a.status, ST_WAIT_TIMEOUT);
+        return;
+    }
     constexpr int QW = CW / 4, RPP = THREADS / QW;
     const int q4 = tid % QW, rg = tid / QW;
     for (int t = 0; t < T; ++t) {
         const uint32_t par = (uint32_t)(t & 1);
         // alpha, w, ah of this token: their buffers were last read by the update of token t - 1 (barrier at its end)
         if (tid == 0) fetch_b(t);
-        ok = mbar_wait(barA, par) && ok;
+        ok = wait(barA, par) && ok;
         const float* vv = vvb + (t & 1) * CW;
         if (tid < CW) {
             // the column sums, eight rows fetched one batch ahead of the two chains (chains start from -0: see above)
@@ -369,7 +236,7 @@ __global__ void __launch_bounds__(THREADS) mem_heads_seq_kernel(const MemHeadsAr
             if (MOM) yv = add(yv, tqv[tid]);
             a.y[ro + c0 + tid] = yv;
         }
-        ok = mbar_wait(barB, par) && ok;
+        ok = wait(barB, par) && ok;
         {
             const float4 vb4 = *reinterpret_cast<const float4*>(vv + 4 * q4), rb4 = *reinterpret_cast<const float4*>(rr + 4 * q4);
 #pragma unroll 4
@@ -423,7 +290,7 @@ size_t smem_bytes_seq(int hs, int cw, bool mom = false) {
     return ((size_t)hs * cw * (mom ? 2 : 1) + (mom ? 6 : 5) * (size_t)hs + 5 * (size_t)cw) * sizeof(float) + (MAX_CHUNKS + 2) * sizeof(uint64_t);
 }
 
-size_t smem_bytes(int hs, int cw) { return ((size_t)hs * cw + 5 * (size_t)hs + 3 * (size_t)cw) * sizeof(float) + (MAX_CHUNKS + 1) * sizeof(uint64_t); }
+size_t smem_bytes(int hs, int cw) { return ((size_t)hs * cw + 5 * (size_t)hs + 3 * (size_t)cw) * sizeof(float) + (MAX_CHUNKS + 1) * sizeof(uint64_t); }  // (the two-blocks-per-SM rule of the tiling below)
 
 }  // namespace
 
@@ -448,27 +315,15 @@ bool mem_heads_tiling(int hs, int* cw, int* chunk_rows, bool momentum) {
     return true;
 }
 
-template <int CW, bool DBG>
-static void launch_one(cudaStream_t st, const MemHeadsArgs& a, size_t smem, unsigned grid) {
-    cudaFuncSetAttribute(mem_heads_kernel<CW, DBG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch_k(mem_heads_kernel<CW, DBG>, dim3(grid), dim3(THREADS), smem, st, a);
-}
-
-void launch_mem_heads(cudaStream_t st, const MemHeadsArgs& a) {
-    const size_t smem = smem_bytes(a.hs, a.cw);
-    const unsigned grid = (unsigned)((size_t)a.M * a.nh * (a.hs / a.cw));
-    const bool dbg = a.wait_limit != 0 || a.fault_chunk_plus1 != 0;
-    if (a.cw == 32) {
-        if (dbg) launch_one<32, true>(st, a, smem, grid); else launch_one<32, false>(st, a, smem, grid);
-    } else {
-        if (dbg) launch_one<16, true>(st, a, smem, grid); else launch_one<16, false>(st, a, smem, grid);
-    }
-}
-
 template <int CW, bool MOM>
 void launch_seq(cudaStream_t st, const MemHeadsArgs& a, int T, size_t smem, unsigned grid) {
-    cudaFuncSetAttribute(mem_heads_seq_kernel<CW, MOM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch_k(mem_heads_seq_kernel<CW, MOM>, dim3(grid), dim3(THREADS), smem, st, a, T);
+    if (a.wait_limit != 0 || a.fault_chunk_plus1 != 0) {
+        cudaFuncSetAttribute(mem_heads_seq_kernel<CW, MOM, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch_k(mem_heads_seq_kernel<CW, MOM, true>, dim3(grid), dim3(THREADS), smem, st, a, T);
+        return;
+    }
+    cudaFuncSetAttribute(mem_heads_seq_kernel<CW, MOM, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_k(mem_heads_seq_kernel<CW, MOM, false>, dim3(grid), dim3(THREADS), smem, st, a, T);
 }
 
 void launch_mem_heads_seq(cudaStream_t st, const MemHeadsArgs& a, int T) {

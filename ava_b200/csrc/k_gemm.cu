@@ -6,6 +6,8 @@
 // model down another path, so this kernel keeps that order: each thread owns a 4x4 block of outputs and walks k
 // upwards, never splitting K.  The int8 tile is widened to f32 once when it is staged in shared memory and reused by
 // every row of the tile.
+#include <cstdlib>
+
 #include "ava_math.h"
 #include "kernels.cuh"
 
@@ -611,6 +613,25 @@ int g_gemm_force = 0;  // tuning override (0: choose by shape)
 int g_resident_max_rows = 16;  // up to this many rows the resident-tile kernel takes the dense products (measured: 19-21 us
                                 // against 23 us for the tiled kernel at 1-8 rows, slower from 32 rows on)
 int g_pdl = 1;         // programmatic dependent launch on every kernel of the step (kernels.cuh)
+
+void prefer_max_shared(const void* kernel) {
+    // once per kernel and device (a handful of kernels: a linear scan of a small table)
+    struct Seen { const void* k; int dev; };
+    static Seen seen[512];
+    static int n = 0;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    for (int i = 0; i < n; ++i)
+        if (seen[i].k == kernel && seen[i].dev == dev) return;
+    // half of it as shared memory: measured best for the step as a whole (all of it starves the kernels that lean on L1)
+    static int percent = -2;
+    if (percent == -2) {
+        percent = 50;
+        if (const char* v = std::getenv("AVA_CARVEOUT")) percent = std::atoi(v);
+    }
+    if (percent >= 0) cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, percent);
+    if (n < 512) seen[n++] = {kernel, dev};
+}
 
 void launch_q8_gemm(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int sm_count) {
     switch (g_gemm_force) {

@@ -788,7 +788,12 @@ void launch_relay_res(cudaStream_t st, float* x, const float* x_in, const float*
 }
 
 void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a) {
-    const int nh = a.d / a.hs;
+    launch_mem_gates(st, a);
+    launch_mem_prep_rows(st, a);
+}
+
+// the gates' two projection stages (they read the normed input only, so they can run beside the q|k|v|e|g product)
+void launch_mem_gates(cudaStream_t st, const MemPrepArgs& a) {
     // stage one
     launch_chain_gemv(st, a.h, a.gate_w, a.M, a.d, a.gate_cols, a.gate_chunk, a.z);
     // stage two
@@ -803,6 +808,11 @@ void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a) {
             launch_k(lowrank_kernel<0>, grid, block, smem, st, a.z, a.gate_cols, 0, a.rank, a.rank, a.wa2, a.wb2, a.M, a.d, a.lra, a.lrb);
         }
     }
+}
+
+// everything per row once the projections and the gates' stages exist
+void launch_mem_prep_rows(cudaStream_t st, const MemPrepArgs& a) {
+    const int nh = a.d / a.hs;
     const size_t smem = ((size_t)5 * a.d + 3 * nh + 4) * sizeof(float);
     opt_in_smem(mem_prep_kernel, smem);
     launch_k(mem_prep_kernel, dim3(a.M), dim3(256), smem, st, a);

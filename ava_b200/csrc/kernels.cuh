@@ -23,8 +23,16 @@ __device__ __forceinline__ void pdl_enter() {
 
 extern int g_pdl;  // 1: launch with the programmatic-serialization attribute (default; AVA_PDL=0 in the environment turns it off)
 
+// Every kernel asks for the same split of an SM's on-chip memory between shared memory and L1.  An SM cannot change the
+// split while blocks are resident on it, so kernels that ask for different splits do not run side by side on one SM: a
+// kernel of another stream then waits until the SM has drained, however much room is left (measured: a lane's RMS norm
+// waited 116 us for another lane's state pass to end).  With one preference for all, a lane's small kernels start beside
+// another lane's state pass.  A kernel that needs more than the preferred share still gets it.
+void prefer_max_shared(const void* kernel);
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    prefer_max_shared(reinterpret_cast<const void*>(kernel));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -182,6 +190,9 @@ void launch_relay(cudaStream_t st, const float* thr, float* acc, bool first, int
 void launch_relay_res(cudaStream_t st, float* x, const float* x_in, const float* g, int M, int d);
 // three launches: the gates' first projection, their low-rank second stage, then everything per row
 void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a);
+// the same in its two parts: the gates' projection stages (need only a.h), then the per-row kernel (needs a.proj too)
+void launch_mem_gates(cudaStream_t st, const MemPrepArgs& a);
+void launch_mem_prep_rows(cudaStream_t st, const MemPrepArgs& a);
 
 struct MemHeadsArgs {
     float* f;            // this block's fast weights, slice-major: [M][nh][hs / cw][hs][cw] f32, updated in place
@@ -193,15 +204,32 @@ struct MemHeadsArgs {
     const float *qw, *qa;                    // [M, nh]
     float* y;                                // [M, nh * hs]
     uint32_t* status;
-    unsigned long long* timeline;            // nullptr, or [blocks][6] phase marks in ns (tuning aid)
     uint32_t wait_limit;                     // polls before a bounded wait gives up (0: the kernel's default)
     int fault_chunk_plus1;                   // testing aid: c + 1 makes every block expect 16 bytes too many for chunk c of its
                                              // first item, so that barrier never completes and the wait runs out (0: off)
 };
-void launch_mem_heads(cudaStream_t st, const MemHeadsArgs& a);
-// The same for T tokens in time order with the slice resident in shared memory between them: the vectors and y are
-// time-major [T][M][nh * hs], qw/qa [T][M][nh]; the state is read and written once for the whole chunk.
+// T tokens in time order with a block's slice of the state resident in shared memory between them: the vectors and y
+// are time-major [T][M][nh * hs], qw/qa [T][M][nh]; the state is read and written once for the whole chunk.
 void launch_mem_heads_seq(cudaStream_t st, const MemHeadsArgs& a, int T);
+
+// One token as a single streaming pass (k_stream.cu): the token's read, while the update the token BEFORE it left
+// pending is applied to the rows as they stream by; this token's own update stays pending (its alpha, w, ah per row
+// and value, rr per column).  The state in HBM is therefore one update behind until launch_mem_flush applies the
+// pending update alone.  Same bits as the resident form.
+struct MemStreamArgs {
+    float* f;                       // this block's fast weights, slice-major [M][nh][hs / cw][hs][cw]
+    int M, nh, hs, cw;
+    int parts;                      // set by the launcher: blocks a head's columns are split over
+    const float *e, *qg, *v;        // this token: [M, nh * hs]
+    const float *qw, *qa;           // this token: [M, nh]
+    float* y;                       // [M, nh * hs]
+    float* rr_out;                  // [M, nh * hs]: this token's rr (part of its pending update)
+    const float *px, *pw, *pah;     // the pending update's alpha, w, ah per row [M, nh * hs]; px == nullptr: none pending
+    const float *pv, *prr;          // the pending update's value and rr per column [M, nh * hs]
+};
+bool launch_mem_stream(cudaStream_t st, const MemStreamArgs& a);
+void launch_mem_flush(cudaStream_t st, float* f, const float* px, const float* pw, const float* pah, const float* pv, const float* prr, int64_t heads,
+                      int hs, int cw);
 // the column-slice width and the rows per bulk copy the kernel uses for a head size; false: head size not covered
 bool mem_heads_tiling(int hs, int* cw, int* chunk_rows, bool momentum = false);
 // natural [heads][hs][hs] to slice-major [heads][hs / cw][hs][cw] (to_slices 1) or back (0)

@@ -214,14 +214,18 @@ int ava_op_mem_heads(int device, int32_t m, int32_t hs, const float* e, const fl
     OCK(up(dy, nullptr, vb));
     OCK(up(dst, nullptr, 4));
     OCK(cudaMemset(dst.p, 0, 4));
-    MemHeadsArgs a{};
-    Tmp dft;  // the slice-major copy the kernel works on
+    Tmp dft, drr;  // the slice-major copy the kernels work on; the token's rr
     OCK(up(dft, nullptr, fb));
+    OCK(up(drr, nullptr, vb));
     launch_retile(0, df.as<float>(), dft.as<float>(), m, hs, cw, 1);
-    a.f = dft.as<float>(); a.s = nullptr; a.qs = nullptr; a.mom = 0.0f; a.M = m; a.nh = 1; a.hs = hs; a.cw = cw; a.chunk_rows = rb;
-    a.e = de.as<float>(); a.v = dv.as<float>(); a.w = dw.as<float>(); a.ah = dah.as<float>(); a.qg = dqg.as<float>(); a.ex = dex.as<float>();
-    a.qw = dqw.as<float>(); a.qa = dqa.as<float>(); a.y = dy.as<float>(); a.status = dst.as<uint32_t>();
-    launch_mem_heads(0, a);
+    // what a decode step runs: the streaming pass (here with no update pending), which leaves the token's own update
+    // pending, then that update applied alone, as every reader of the state other than the next pass would first do
+    MemStreamArgs a{};
+    a.f = dft.as<float>(); a.M = m; a.nh = 1; a.hs = hs; a.cw = cw;
+    a.e = de.as<float>(); a.qg = dqg.as<float>(); a.v = dv.as<float>(); a.qw = dqw.as<float>(); a.qa = dqa.as<float>();
+    a.y = dy.as<float>(); a.rr_out = drr.as<float>();
+    if (!launch_mem_stream(0, a)) return AVA_NOT_APPLICABLE;
+    launch_mem_flush(0, dft.as<float>(), dex.as<float>(), dw.as<float>(), dah.as<float>(), dv.as<float>(), drr.as<float>(), m, hs, cw);
     launch_retile(0, dft.as<float>(), df.as<float>(), m, hs, cw, 0);
     if ((rc = end_())) return rc;
     uint32_t st = 0;
@@ -255,39 +259,13 @@ int ava_debug_mem_heads_wait_runs_out(int device, int32_t m, int32_t hs, int32_t
     a.e = a.v = a.w = a.ah = a.qg = a.ex = dv.as<float>(); a.qw = a.qa = dq.as<float>(); a.y = dy.as<float>(); a.status = dst.as<uint32_t>();
     a.wait_limit = poll_limit;
     a.fault_chunk_plus1 = chunk + 1;
-    launch_mem_heads(0, a);
+    launch_mem_heads_seq(0, a, 1);
     if ((rc = end_())) return rc;
     uint32_t st = 0;
     OCK(cudaMemcpy(&st, dst.p, 4, cudaMemcpyDeviceToHost));
     OCK(cudaMemcpy(back.data(), df.p, fn * 4, cudaMemcpyDeviceToHost));
     *state_changed = std::memcmp(back.data(), hf.data(), fn * 4) != 0;
     return (st & ST_WAIT_TIMEOUT) ? AVA_ERR_CUDA : AVA_OK;
-}
-
-/* Tuning aid: the fast-weight kernel on m zeroed heads of size hs with the phase clock on; out [blocks][6] ns marks
- * (start, vectors staged, column sums done, update done and stores issued, stores read out), returns the block count. */
-int ava_debug_mem_heads_timeline(int device, int32_t m, int32_t hs, uint64_t* out, int64_t cap) {
-    int cw, rb;
-    if (!out || m <= 0 || hs % 16 || !mem_heads_tiling(hs, &cw, &rb)) return AVA_ERR_ARG;
-    int rc = begin(device);
-    if (rc) return rc;
-    const int64_t blocks = (int64_t)m * (hs / cw);
-    if (cap < blocks * 6) return AVA_ERR_ARG;
-    const size_t vb = (size_t)m * hs * 4, fb = (size_t)m * hs * hs * 4;
-    Tmp dv, dq, df, dy, dst, dtl;
-    OCK(up(dv, nullptr, vb)); OCK(up(dq, nullptr, (size_t)m * 4)); OCK(up(df, nullptr, fb)); OCK(up(dy, nullptr, vb)); OCK(up(dst, nullptr, 4));
-    OCK(up(dtl, nullptr, (size_t)blocks * 6 * 8));
-    OCK(cudaMemset(dv.p, 0, vb)); OCK(cudaMemset(dq.p, 0, (size_t)m * 4)); OCK(cudaMemset(df.p, 0, fb)); OCK(cudaMemset(dst.p, 0, 4));
-    MemHeadsArgs a{};
-    a.f = df.as<float>(); a.s = nullptr; a.qs = nullptr; a.mom = 0.0f; a.M = m; a.nh = 1; a.hs = hs; a.cw = cw; a.chunk_rows = rb;
-    a.e = a.v = a.w = a.ah = a.qg = a.ex = dv.as<float>(); a.qw = a.qa = dq.as<float>(); a.y = dy.as<float>(); a.status = dst.as<uint32_t>();
-    launch_mem_heads(0, a);  // warm
-    a.timeline = dtl.as<unsigned long long>();
-    OCK(cudaMemset(dtl.p, 0, (size_t)blocks * 6 * 8));
-    launch_mem_heads(0, a);
-    if ((rc = end_())) return rc;
-    OCK(cudaMemcpy(out, dtl.p, (size_t)blocks * 6 * 8, cudaMemcpyDeviceToHost));
-    return (int)blocks;
 }
 
 int ava_op_attend(int device, int32_t m, int32_t n, int32_t hs, int32_t bf16_store, const float* q, const float* kc, const float* vc, float* out) {

@@ -117,8 +117,7 @@ int ava_mem_heads_static(int device, void* stream, int32_t m, int32_t hs, const 
     a.e = e; a.v = v; a.w = w; a.ah = ah; a.qg = qg; a.ex = ex; a.qw = qw; a.qa = qa;
     a.y = y;
     a.status = d->status;
-    a.timeline = nullptr;
-    launch_mem_heads(st, a);
+    launch_mem_heads_seq(st, a, 1);
     launch_retile(st, d->scratch, f, m, hs, cw, 0);
     if ((ce = cudaGetLastError()) != cudaSuccess) return fail(AVA_ERR_CUDA, std::string("launch: ") + cudaGetErrorString(ce));
     uint32_t status = 0;

@@ -181,6 +181,11 @@ int64_t ava_state_bytes(const ava_state* s);
  * bit. */
 int ava_engine_set_segmented_read(ava_engine* e, int32_t seg_len);
 
+/* No counterpart in the reference (its step runs one row on the host's threads).  A decode step of a large batch runs
+ * as `lanes` lanes (1..8, default 2): contiguous windows of the state's rows, each with work buffers and a stream of its
+ * own, forked from and joined back into the engine's stream, so that one lane's state pass (HBM-bound) runs beside the
+ * other lanes' products (bound by latency).  Rows are independent (src/state.rs:13-15): the bits do not depend on it. */
+int ava_engine_set_lanes(ava_engine* e, int32_t lanes);
 /* Fast products (no counterpart in the reference; off by default).  on != 0: the dense int8-weight products of the step
  * (W_in, the q|k|v|e|g projection, W_o, the engram's projections, W_1 and the output head) run on the tensor cores:
  * every product exact (the f32 activation as three bf16 limbs, the int8 weight exact in bf16), the f32 sum in the
@@ -384,9 +389,6 @@ const char* ava_static_last_error(void);
 int ava_op_attend(int device, int32_t m, int32_t n, int32_t hs, int32_t bf16_store, const float* q, const float* kc,
                   const float* vc, float* out);
 
-/* Tuning aid with no counterpart in the reference: the fast-weight kernel on m zeroed heads of size hs with its phase
- * clock on; out [blocks][6] nanosecond marks, returns the number of blocks (or < 0). */
-int ava_debug_mem_heads_timeline(int device, int32_t m, int32_t hs, uint64_t* out, int64_t cap);
 /* Testing aid for the kernels' bounded waits; no counterpart in the reference (its waits are host-side joins).  Runs
  * the fast-weight kernel on m pattern-filled heads of size hs with the byte count of row chunk `chunk` over-stated by
  * 16 on every block's first item and a poll limit of `poll_limit`, so that wait runs out without any copy failing.
