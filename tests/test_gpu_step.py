@@ -440,3 +440,34 @@ def test_streamed_engram_read_bits(orc_same_math, cap):
     for name in ("eng.k", "eng.v", "lif.1.v"):
         assert np.array_equal(bits(gs.get(1, name)), bits(os_.get(1, name))), name
     assert gs.get(0, "eng.k").size == (cap if cap else T) * cfg["d"]
+
+
+def test_lanes_of_rows_give_the_same_bits(orc_same_math):
+    """A decode step of a large batch runs as lanes: windows of the rows on streams of their own, so that one lane's
+    state pass runs beside another's products.  Rows are independent (src/state.rs:13-15), so logits and state must not
+    depend on the number of lanes, windows that do not divide the rows included; and they are the oracle's bits.  The
+    fast weights are read back through the export, which first applies the update the last step left pending."""
+    cfg = config.tiny(head_size=128, eng_head_size=64, eng_store_bf16=1)
+    rows, steps = 203, 5
+    gm, om = pair(orc_same_math, cfg, seed=3)
+    ids = synth.token_ids(cfg["vocab"], rows, steps, seed0=7)
+    os_ = om.state(rows)
+    for t in range(steps):
+        want = os_.step(ids[:, t])
+    names = ["lif.2.v", "lif.0.s", "mem.0.f", "mem.2.f", "eng.k", "eng.v"]
+    for lanes in (1, 2, 4, 3):
+        gm.set_lanes(lanes)
+        gs = gm.state(rows, 16)
+        for t in range(steps):
+            got = gm.step(gs, ids[:, t])
+        assert np.array_equal(bits(got), bits(want)), lanes
+        for r in (0, 50, 51, 101, 102, 135, 152, 202):      # rows at and around every window's edge
+            for name in names:
+                assert np.array_equal(bits(gs.get(r, name)), bits(os_.get(r, name))), (lanes, r, name)
+        # a selection taken while an update is pending carries the updated weights, and continues like the original
+        pick = gs.select([202, 0, 101])
+        a = gm.step(pick, ids[[202, 0, 101], 0])
+        b = gm.step(gs, ids[:, 0])
+        assert np.array_equal(bits(a), bits(b[[202, 0, 101]])), lanes
+        gs.close()
+        pick.close()
