@@ -165,6 +165,21 @@ int64_t orc_trace_len(const char* name, int block);
 int orc_trace_get(const char* name, int block, float* out);
 void orc_trace_enable(int on);
 
+/* ---- the chunk-parallel forms of the fast-weight memory (ava_chunk.cpp), one head each ------------------------------
+ * (I + A)^-1 of a strictly lower-triangular A [c, c] by block doubling (src/model.rs:720-742). */
+void orc_inv_unit_lower(const float* a, int c, float* t);
+/* The plain (v0.2) delta rule in its chunk-64 WY form (src/model.rs:744-799): q, k, v [t, hs], log alpha and beta [t],
+ * f0 [hs, hs] or NULL; y [t, hs], f1 [hs, hs]. */
+void orc_delta_rule_from(int t, int hs, const float* q, const float* k, const float* v, const float* la, const float* beta, const float* f0,
+                         float* y, float* f1);
+/* The Ava-0.4 rule token by token (src/arch.rs:1091-1136): q, k, e, v [t, hs]; la, b [t, g] (g 1 or hs); momentum m;
+ * f0, s0 [hs, hs] or NULL; cap bounds the state (1e5 in the reference).  y [t, hs], f1, s1 [hs, hs] (s1 may be NULL). */
+void orc_delta_rec(int t, int hs, int g, const float* q, const float* k, const float* e, const float* v, const float* la, const float* b, float m,
+                   const float* f0, const float* s0, float cap, float* y, float* f1, float* s1);
+/* The same rule in chunks (src/arch.rs:1151-1173, 1243-1327), same arguments without the cap. */
+void orc_delta_chunk(int t, int hs, int g, const float* q, const float* k, const float* e, const float* v, const float* la, const float* b, float m,
+                     const float* f0, const float* s0, float* y, float* f1, float* s1);
+
 #ifdef __cplusplus
 }
 #endif

@@ -26,10 +26,8 @@ class OrcConfig(C.Structure):
 
 def build(force: bool = False) -> str:
     """Compile the oracle with the recipe beside it (g++ only) and return the library's path."""
-    src = os.path.join(_HERE, "ava_oracle.cpp")
-    hdr = os.path.join(_HERE, "ava_oracle.h")
-    stale = (not os.path.exists(_LIB_PATH)) or any(
-        os.path.getmtime(p) > os.path.getmtime(_LIB_PATH) for p in (src, hdr))
+    srcs = [os.path.join(_HERE, n) for n in ("ava_oracle.cpp", "ava_chunk.cpp", "ava_oracle.h", "Makefile")]
+    stale = (not os.path.exists(_LIB_PATH)) or any(os.path.getmtime(p) > os.path.getmtime(_LIB_PATH) for p in srcs)
     if force or stale:
         subprocess.check_call(["make", "-C", _HERE, "-s", "clean"])
         subprocess.check_call(["make", "-C", _HERE, "-s"])
@@ -78,6 +76,10 @@ def lib() -> C.CDLL:
     L.orc_head_rows.argtypes = [C.c_int, fp, fp, fp, fp, fp, fp, C.c_float, C.c_float, C.c_float, C.c_float,
                                 C.c_float, fp, fp, fp, fp, fp, fp, fp]
     L.orc_delta_plain.argtypes = [C.c_int, fp, fp, fp, fp, C.c_float, C.c_float, fp, fp]
+    L.orc_inv_unit_lower.argtypes = [fp, C.c_int, fp]
+    L.orc_delta_rule_from.argtypes = [C.c_int, C.c_int, fp, fp, fp, fp, fp, fp, fp, fp]
+    L.orc_delta_rec.argtypes = [C.c_int, C.c_int, C.c_int, fp, fp, fp, fp, fp, fp, C.c_float, fp, fp, C.c_float, fp, fp, fp]
+    L.orc_delta_chunk.argtypes = [C.c_int, C.c_int, C.c_int, fp, fp, fp, fp, fp, fp, C.c_float, fp, fp, fp, fp, fp]
     L.orc_bf16_round.argtypes = [C.c_float]
     L.orc_bf16_round.restype = C.c_float
     L.orc_model_new.argtypes = [C.POINTER(OrcConfig)]
@@ -246,6 +248,56 @@ def head_rows(e, v, w, ah, qg, ex, qw, qa, f0, ke=0.0, tinv=1.0, mom=0.0, qs=Non
     lib().orc_head_rows(hs, _fp(e), _fp(v), _fp(w), _fp(ah), _fp(qg), _fp(ex), qw, qa, ke, tinv, mom, _fp(qs), _fp(p2),
                         _fp(f0), _fp(s0), _fp(y), _fp(f1), _fp(s1))
     return y, f1, s1
+
+
+def inv_unit_lower(a):
+    """(I + A)^-1 for strictly lower-triangular A [c, c] (src/model.rs:720-742)."""
+    a = np.ascontiguousarray(a, np.float32)
+    c = a.shape[0]
+    out = np.empty((c, c), np.float32)
+    lib().orc_inv_unit_lower(_fp(a), c, _fp(out))
+    return out
+
+
+def delta_rule_from(q, k, v, la, beta, f0=None):
+    """One head of `delta_rule_from` (src/model.rs:761-799): y [t, hs] and the fast weights after the window."""
+    q, k, v = (np.ascontiguousarray(x, np.float32) for x in (q, k, v))
+    la, beta = np.ascontiguousarray(la, np.float32), np.ascontiguousarray(beta, np.float32)
+    t, hs = q.shape
+    y, f1 = np.empty((t, hs), np.float32), np.empty((hs, hs), np.float32)
+    f0 = None if f0 is None else np.ascontiguousarray(f0, np.float32)
+    lib().orc_delta_rule_from(t, hs, _fp(q), _fp(k), _fp(v), _fp(la), _fp(beta), _fp(f0) if f0 is not None else None, _fp(y), _fp(f1))
+    return y, f1
+
+
+def _delta_args(q, k, e, v, la, b, f0, s0):
+    q, k, e, v = (np.ascontiguousarray(x, np.float32) for x in (q, k, e, v))
+    t, hs = q.shape
+    la = np.ascontiguousarray(la, np.float32).reshape(t, -1)
+    b = np.ascontiguousarray(b, np.float32).reshape(t, -1)
+    g = la.shape[1]
+    assert g in (1, hs) and b.shape[1] == g
+    f0 = None if f0 is None else np.ascontiguousarray(f0, np.float32)
+    s0 = None if s0 is None else np.ascontiguousarray(s0, np.float32)
+    return q, k, e, v, la, b, f0, s0, t, hs, g
+
+
+def delta_rec(q, k, e, v, la, b, m=0.0, f0=None, s0=None, cap=1e5):
+    """One head of `delta_rec` (src/arch.rs:1091-1136), the token loop: y, F and (with momentum) S."""
+    q, k, e, v, la, b, f0, s0, t, hs, g = _delta_args(q, k, e, v, la, b, f0, s0)
+    y, f1, s1 = np.empty((t, hs), np.float32), np.empty((hs, hs), np.float32), np.zeros((hs, hs), np.float32)
+    lib().orc_delta_rec(t, hs, g, _fp(q), _fp(k), _fp(e), _fp(v), _fp(la), _fp(b), m, _fp(f0) if f0 is not None else None,
+                        _fp(s0) if s0 is not None else None, cap, _fp(y), _fp(f1), _fp(s1))
+    return y, f1, (s1 if m > 0 else None)
+
+
+def delta_chunk(q, k, e, v, la, b, m=0.0, f0=None, s0=None):
+    """One head of `delta_chunk` / `chunk_core` (src/arch.rs:1151-1173, 1243-1327): the same rule in chunks."""
+    q, k, e, v, la, b, f0, s0, t, hs, g = _delta_args(q, k, e, v, la, b, f0, s0)
+    y, f1, s1 = np.empty((t, hs), np.float32), np.empty((hs, hs), np.float32), np.zeros((hs, hs), np.float32)
+    lib().orc_delta_chunk(t, hs, g, _fp(q), _fp(k), _fp(e), _fp(v), _fp(la), _fp(b), m, _fp(f0) if f0 is not None else None,
+                          _fp(s0) if s0 is not None else None, _fp(y), _fp(f1), _fp(s1))
+    return y, f1, (s1 if m > 0 else None)
 
 
 def delta_plain(f0, k, v, q, al, b):
