@@ -1,0 +1,267 @@
+// Batched f32-accurate products on the tensor cores (sm_100a: TMA + tcgen05.mma + tensor memory) for the chunk-parallel
+// form of the fast-weight memory (k_chunk.cu).
+//
+//   C[b] (M x N, f32) = A[b] (M x K) . B[b]^T (N x K)          b = 0 .. batch - 1
+//
+// Both operands are f32 values carried as bf16 LIMBS (hi = bf16(x), mid = bf16(x - hi), lo = bf16(x - hi - mid): their
+// sum is x exactly, and a bf16 x bf16 product is exact in f32), stored K-major as planes [limb][batch * rows][K].  The
+// kernel issues the limb products A_i . B_j with i + j below the larger limb count (six for three limbs each: hi.hi,
+// hi.mid, mid.hi, hi.lo, mid.mid, lo.hi), all into one f32 accumulator in tensor memory, so the result carries the
+// operands to about 2^-24 each: an f32 product with the tensor core's summation order.
+//
+// One block of 128 threads per 128 x BN tile of one batch item; k-tiles of 64 in a ring of stages.  Thread 0 brings the
+// limb tiles in by TMA (2-D tiled, 128-byte swizzle; no cluster multicast), thread 32 issues the multiply-adds and
+// commits each stage's "empty" barrier, all four warps read the accumulator back (tcgen05.ld) for the epilogue:
+//   TCB_STORE   C = acc
+//   TCB_DECAY   C = colscale[b][n] * C + acc, and the three limbs of the new C written beside it (the state update of the
+//               chunked memory: the next step multiplies by this state, so its limbs are made where it is produced)
+// Every wait is bounded; a wait that runs out sets ST_WAIT_TIMEOUT and the tile is not written.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "ava_math.h"
+#include "kernels.cuh"
+
+namespace ava {
+
+namespace {
+
+constexpr int B_BM = 128, B_BK = 64, B_THREADS = 128;
+constexpr uint32_t B_WAIT_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void bar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void bar_expect(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = s32(bar);
+    for (uint32_t i = 0; i < B_WAIT_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if (i > 1024) __nanosleep(32);
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(s32(dst)),
+                 "l"(map), "r"(x), "r"(y), "r"(s32(bar))
+                 : "memory");
+}
+// K-major tile of 64 bf16 (128 bytes) per row, 128-byte swizzle: start address / 16, 1024 bytes between 8-row groups,
+// descriptor version 1 (sm_100), layout 2 (SWIZZLE_128B)
+__device__ __forceinline__ uint64_t operand_desc(const void* tile) {
+    uint64_t d = 0;
+    d |= (uint64_t)((s32(tile) & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(1024u >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// kind::f16: f32 accumulate, bf16 x bf16, both K-major, M 128, N n
+__host__ __device__ constexpr uint32_t instr_desc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(B_BM >> 4) << 24);
+}
+
+template <int BN, int LA, int LB, int STAGES, int EPI>
+__global__ void __launch_bounds__(B_THREADS) tc_bgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                                                             const TcbArgs a) {
+    pdl_enter();
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (s32(smem_raw) & 1023u)) & 1023u);  // swizzled tiles want a 1024-byte boundary
+    constexpr uint32_t A_BYTES = B_BM * B_BK * 2, B_BYTES = BN * B_BK * 2, STAGE_BYTES = LA * A_BYTES + LB * B_BYTES;
+    constexpr int PMAX = (LA > LB ? LA : LB) - 1;  // limb products A_i . B_j with i + j <= PMAX
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* accbar = empty + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accbar + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.y * B_BM, n0 = blockIdx.x * BN, bz = blockIdx.z;
+    const int kt = a.K / B_BK;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            bar_init(&full[s], 1);
+            bar_init(&empty[s], 1);
+        }
+        bar_init(accbar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (tid == 0) {
+        bool ok = true;
+        const int ya = bz * a.M + m0, yb = bz * a.N + n0;
+        for (int it = 0; it < kt && ok; ++it) {
+            const int s = it % STAGES, n = it / STAGES;
+            if (n > 0) ok = bar_wait(&empty[s], (uint32_t)((n - 1) & 1));
+            if (!ok) break;
+            unsigned char* st = smem + (size_t)s * STAGE_BYTES;
+            bar_expect(&full[s], STAGE_BYTES);
+#pragma unroll
+            for (int l = 0; l < LA; ++l) tma_load(st + l * A_BYTES, &map_a, it * B_BK, (int)(l * a.rows_a) + ya, &full[s]);
+#pragma unroll
+            for (int l = 0; l < LB; ++l) tma_load(st + LA * A_BYTES + l * B_BYTES, &map_b, it * B_BK, (int)(l * a.rows_b) + yb, &full[s]);
+        }
+        if (!ok) atomicOr(a.status, ST_WAIT_TIMEOUT);
+    } else if (tid == 32) {
+        bool ok = true;
+        constexpr uint32_t idesc = instr_desc(BN);
+        for (int it = 0; it < kt && ok; ++it) {
+            const int s = it % STAGES, n = it / STAGES;
+            ok = bar_wait(&full[s], (uint32_t)(n & 1));
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            unsigned char* st = smem + (size_t)s * STAGE_BYTES;
+            bool first = it == 0;
+#pragma unroll
+            for (int i = 0; i < LA; ++i)
+#pragma unroll
+                for (int j = 0; j < LB; ++j) {
+                    if (i + j > PMAX) continue;
+                    const uint64_t da = operand_desc(st + i * A_BYTES), db = operand_desc(st + LA * A_BYTES + j * B_BYTES);
+#pragma unroll
+                    for (int k16 = 0; k16 < B_BK / 16; ++k16) {
+                        const uint32_t acc = first ? 0u : 1u;  // the very first multiply-add of the tile overwrites the accumulator
+                        first = false;
+                        asm volatile(
+                            "{\n\t.reg .pred p;\n\t"
+                            "setp.ne.b32 p, %4, 0;\n\t"
+                            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                            ::"r"(tmem), "l"(da + 2u * k16), "l"(db + 2u * k16), "r"(idesc), "r"(acc)
+                            : "memory");
+                    }
+                }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&empty[s])) : "memory");
+        }
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(accbar)) : "memory");
+        if (!ok) atomicOr(a.status, ST_WAIT_TIMEOUT);
+    }
+    __syncwarp();
+    const bool acc_ok = bar_wait(accbar, 0);
+    if (!acc_ok && lane == 0) atomicOr(a.status, ST_WAIT_TIMEOUT);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+    // epilogue: warp w reads lanes 32 w .. 32 w + 31 (one output row per thread), 32 columns per instruction
+    const int row = m0 + warp * 32 + lane;
+    float* crow = a.C + (size_t)bz * a.c_batch_stride + (size_t)row * a.ldc;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+              "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+              "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+              "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < a.M && acc_ok) {
+            float4 prev[8];
+            if (EPI == TCB_DECAY) {  // the old values are read before any new one is written
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    const int c = n0 + c0 + j;
+                    prev[j / 4] = c < a.N ? *reinterpret_cast<const float4*>(crow + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                const int c = n0 + c0 + j;
+                if (c >= a.N) continue;  // N is a multiple of 4
+                float4 o = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                if (EPI == TCB_DECAY) {
+                    const float4 g = *reinterpret_cast<const float4*>(a.colscale + (size_t)bz * a.colscale_batch_stride + c);
+                    const float4 x = prev[j / 4];
+                    o = make_float4(add(mul(x.x, g.x), o.x), add(mul(x.y, g.y), o.y), add(mul(x.z, g.z), o.z), add(mul(x.w, g.w), o.w));
+                }
+                *reinterpret_cast<float4*>(crow + c) = o;
+                if (EPI == TCB_DECAY) {
+                    // the new value's three limbs, in the operand layout of the product that reads it next: [limb][batch * M][N]
+                    const float ov[4] = {o.x, o.y, o.z, o.w};
+                    uint16_t l0[4], l1[4], l2[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        l0[q] = f_to_bf16(ov[q]);
+                        const float r1 = sub(ov[q], bf16_to_f(l0[q]));
+                        l1[q] = f_to_bf16(r1);
+                        l2[q] = f_to_bf16(sub(r1, bf16_to_f(l1[q])));
+                    }
+                    const size_t at = ((size_t)bz * a.M + row) * a.N + c;
+                    *reinterpret_cast<uint2*>(a.c_limbs + at) = make_uint2(l0[0] | ((uint32_t)l0[1] << 16), l0[2] | ((uint32_t)l0[3] << 16));
+                    *reinterpret_cast<uint2*>(a.c_limbs + a.c_limb_plane + at) = make_uint2(l1[0] | ((uint32_t)l1[1] << 16), l1[2] | ((uint32_t)l1[3] << 16));
+                    *reinterpret_cast<uint2*>(a.c_limbs + 2 * a.c_limb_plane + at) = make_uint2(l2[0] | ((uint32_t)l2[1] << 16), l2[2] | ((uint32_t)l2[3] << 16));
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)BN) : "memory");
+}
+
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                             const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn encode_fn() {
+    static EncodeFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(p);
+    }
+    return fn;
+}
+// bf16 [rows][cols] row-major, boxes of [64 columns, box_rows rows], 128-byte swizzle
+bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {B_BK, box_rows};
+    const cuuint32_t es[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int LA, int LB, int STAGES, int EPI>
+bool launch_one(cudaStream_t st, const TcbArgs& a) {
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, a.a, (uint64_t)LA * a.rows_a, a.K, B_BM) || !make_map(&mb, a.b, (uint64_t)LB * a.rows_b, a.K, BN)) return false;
+    const size_t smem = (size_t)STAGES * (LA * B_BM * B_BK * 2 + LB * BN * B_BK * 2) + (2 * STAGES + 1) * sizeof(uint64_t) + 16 + 1024;
+    cudaFuncSetAttribute(tc_bgemm_kernel<BN, LA, LB, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    dim3 grid((a.N + BN - 1) / BN, (a.M + B_BM - 1) / B_BM, a.batch);
+    return launch_k(tc_bgemm_kernel<BN, LA, LB, STAGES, EPI>, grid, dim3(B_THREADS), smem, st, ma, mb, a) == cudaSuccess;
+}
+
+}  // namespace
+
+// false: shape not covered (K a multiple of 64, M a multiple of 128, N a multiple of 4) or no tensor-map encoder
+bool launch_tc_bgemm(cudaStream_t st, const TcbArgs& a, int epi) {
+    if (a.K % B_BK || a.M % B_BM || a.N % 4 || a.batch < 1) return false;
+    if (a.N % 128 == 0) return epi == TCB_DECAY ? launch_one<128, 3, 3, 2, TCB_DECAY>(st, a) : launch_one<128, 3, 3, 2, TCB_STORE>(st, a);
+    return epi == TCB_DECAY ? launch_one<64, 3, 3, 3, TCB_DECAY>(st, a) : launch_one<64, 3, 3, 3, TCB_STORE>(st, a);
+}
+
+}  // namespace ava

@@ -115,6 +115,26 @@ struct TcGemmArgs {
 // false: shape or epilogue not covered (K % 64, N % 4, EPI_LIF) or no tensor-map encoder; nothing was launched
 bool launch_tc_gemm(cudaStream_t st, const TcGemmArgs& a, GemmEpilogue epi);
 void launch_split3(cudaStream_t st, const float* x, int64_t n, uint16_t* out);
+
+// Batched f32-accurate products on the tensor cores (k_tcb.cu): C[b] = A[b] . B[b]^T with both operands as three bf16
+// limbs, K-major planes [limb][batch * rows][K].
+enum { TCB_STORE = 0, TCB_DECAY = 1 };
+struct TcbArgs {
+    const uint16_t* a;        // [3][rows_a][K], rows_a = batch * M
+    const uint16_t* b;        // [3][rows_b][K], rows_b = batch * N
+    int64_t rows_a, rows_b;
+    float* C;                 // [batch][M][ldc]
+    int ldc;
+    int64_t c_batch_stride;   // floats between batch items of C
+    int M, N, K, batch;       // M a multiple of 128, K of 64, N of 4
+    // TCB_DECAY: C = colscale[b][n] * C + A . B^T, and the new C's limbs into c_limbs [3][batch * M][N]
+    const float* colscale;
+    int64_t colscale_batch_stride;
+    uint16_t* c_limbs;
+    int64_t c_limb_plane;     // elements between limb planes
+    uint32_t* status;
+};
+bool launch_tc_bgemm(cudaStream_t st, const TcbArgs& a, int epi);
 void launch_widen_transpose(cudaStream_t st, const int8_t* q, int K, int N, uint16_t* out);
 
 // ---- row kernels ----------------------------------------------------------------------------------------------

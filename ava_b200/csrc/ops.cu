@@ -236,6 +236,44 @@ int ava_op_mem_heads(int device, int32_t m, int32_t hs, const float* e, const fl
     return AVA_OK;
 }
 
+/* The batched limb product of the chunked memory alone: C[b] = A[b] . B[b]^T (+ colscale[b][n] * C_in when colscale is
+ * given), A [batch][M][K], B [batch][N][K], C [batch][M][N] f32 on the host; limbs [3][batch * M][N] of the result are
+ * returned as their exact sum in c_limb_sum when it is not NULL (TCB_DECAY only). */
+int ava_op_tc_bgemm(int device, int32_t batch, int32_t m, int32_t n, int32_t k, const float* a, const float* b, const float* colscale, float* c,
+                    float* c_limb_sum) {
+    if (!a || !b || !c || batch <= 0 || m <= 0 || n <= 0 || k <= 0) return AVA_ERR_ARG;
+    if (m % 128 || k % 64 || n % 4) return AVA_NOT_APPLICABLE;
+    int rc = begin(device);
+    if (rc) return rc;
+    const size_t na = (size_t)batch * m * k, nb = (size_t)batch * n * k, nc = (size_t)batch * m * n;
+    Tmp da, db, dc, dla, dlb, dcs, dcl, dst;
+    OCK(up(da, a, na * 4)); OCK(up(db, b, nb * 4)); OCK(up(dc, c, nc * 4));
+    OCK(up(dla, nullptr, na * 6)); OCK(up(dlb, nullptr, nb * 6)); OCK(up(dst, nullptr, 4));
+    OCK(cudaMemset(dst.p, 0, 4));
+    launch_split3(0, da.as<float>(), (int64_t)na, dla.as<uint16_t>());
+    launch_split3(0, db.as<float>(), (int64_t)nb, dlb.as<uint16_t>());
+    TcbArgs t{};
+    t.a = dla.as<uint16_t>(); t.b = dlb.as<uint16_t>(); t.rows_a = (int64_t)batch * m; t.rows_b = (int64_t)batch * n;
+    t.C = dc.as<float>(); t.ldc = n; t.c_batch_stride = (int64_t)m * n; t.M = m; t.N = n; t.K = k; t.batch = batch; t.status = dst.as<uint32_t>();
+    if (colscale) {
+        OCK(up(dcs, colscale, (size_t)batch * n * 4));
+        OCK(up(dcl, nullptr, nc * 6));
+        t.colscale = dcs.as<float>(); t.colscale_batch_stride = n; t.c_limbs = dcl.as<uint16_t>(); t.c_limb_plane = (int64_t)nc;
+    }
+    if (!launch_tc_bgemm(0, t, colscale ? TCB_DECAY : TCB_STORE)) return AVA_NOT_APPLICABLE;
+    if ((rc = end_())) return rc;
+    uint32_t st = 0;
+    OCK(cudaMemcpy(&st, dst.p, 4, cudaMemcpyDeviceToHost));
+    if (st) return AVA_ERR_CUDA;
+    OCK(cudaMemcpy(c, dc.p, nc * 4, cudaMemcpyDeviceToHost));
+    if (colscale && c_limb_sum) {
+        std::vector<uint16_t> l(nc * 3);
+        OCK(cudaMemcpy(l.data(), dcl.p, nc * 6, cudaMemcpyDeviceToHost));
+        for (size_t i = 0; i < nc; ++i) c_limb_sum[i] = (bf16_to_f(l[i]) + bf16_to_f(l[nc + i])) + bf16_to_f(l[2 * nc + i]);
+    }
+    return AVA_OK;
+}
+
 /* Testing aid for the kernels' bounded waits (no GPU fault involved: every copy completes, only a barrier is told to
  * expect 16 bytes more than will ever arrive).  Runs the fast-weight update + read on m heads of size hs whose state
  * is filled with a pattern, with chunk `chunk` of every block's first item mis-counted and a poll limit of

