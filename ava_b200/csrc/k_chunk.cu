@@ -1,0 +1,368 @@
+// The fast-weight memory over a chunk of tokens in its chunk-parallel form, the big products on the tensor cores
+// (sm_100a).  Optional, for prompt reading in the tolerance mode: it follows the reference's `delta_chunk` /
+// `chunk_core` (design-tests/nn/gpu/src/arch.rs:1151-1173, 1243-1327) for per-channel gates without momentum, and like
+// it agrees with the token loop to rounding only (the reference's own bound for this form: 1e-4 of max(1, max|ref|),
+// src/arch/tests.rs:700-753), not bit for bit.
+//
+// Per head and chunk of C = 64 tokens (positions i, j inside the chunk; cum = inclusive sums of log alpha per channel,
+// cumex = the sums before a position; q, e unit; w = k b the write key, ah = e (b alpha) the erase key):
+//     qs = q exp(cum)        es = e exp(cumex)        ws = w exp(-cum)        as = ah exp(-cum)
+//     Qw = tril(qs ws^T)     Qa = tril(qs as^T)       Ke = stril(es ws^T)     Ae = stril(es as^T)       one 128x128xhs product
+//     T  = (I + Ae)^-1       p1 = T es                r0 = (T Ke) v           qwv = Qw v
+//     wl = w exp(cum_C - cum)   al = ah exp(cum_C - cum)   gc = exp(cum_C)
+// then, chunk after chunk with the state F [key, value]:
+//     [rr0; yq] = [p1; qs] F                           128 x hs x hs on the tensor cores
+//     rr = rr0 + r0        y = yq + qwv - Qa rr
+//     F' = diag(gc) F + wl^T v - al^T rr               hs x hs x 128 on the tensor cores
+// The pairwise decays exp(cum_i - cum_j) are formed as products exp(cum_i) exp(-cum_j) so that the Gram matrices are
+// plain products; that is safe while the sums stay within the f32 exponent range over one chunk.  The scaling kernel
+// raises a flag when a chunk's sum of log rates falls below -60 (forgetting by a factor 1e-26 inside 64 tokens); the
+// caller then reads that chunk of tokens with the exact kernels instead.
+//
+// The state is worked on transposed, Ft [value, key] with its three bf16 limbs beside it, because both big products
+// want their operands K-major: the first sums over keys (rows of Ft are K-major as they lie), the second over the
+// chunk's 128 token slots.  All f32 operands of the tensor-core products are carried as three bf16 limbs (k_tcb.cu).
+#include <cuda_runtime.h>
+
+#include <algorithm>
+
+#include "ava_math.h"
+#include "kernels.cuh"
+
+namespace ava {
+
+namespace {
+
+constexpr int CC = 64;  // tokens per chunk
+
+__device__ __forceinline__ void limbs3(float x, uint16_t& l0, uint16_t& l1, uint16_t& l2) {
+    l0 = f_to_bf16(x);
+    const float r1 = x - bf16_to_f(l0);
+    l1 = f_to_bf16(r1);
+    l2 = f_to_bf16(r1 - bf16_to_f(l1));
+}
+
+// ---- scaling: one thread per (chunk, head, channel), the chunk's 64 tokens in order ------------------------------
+__global__ void __launch_bounds__(256) chunk_scale_kernel(const ChunkArgs a) {
+    pdl_enter();
+    const int H = a.hs, ch = blockIdx.x * blockDim.x + threadIdx.x;
+    if (ch >= H) return;
+    const int u = blockIdx.y, j = u / a.HB, hb = u % a.HB;  // u = j * HB + hb
+    const size_t in0 = (size_t)j * CC * a.tok_stride + (size_t)hb * H + ch;
+    const size_t P128 = (size_t)a.nC * a.HB * 128 * H;     // plane of QE / WA / A3
+    const size_t PT = (size_t)a.nC * a.HB * H * 128;       // plane of A5 / B5
+    const size_t row128 = (size_t)u * 128, rowT = ((size_t)u * H + ch) * 128;
+    float cum = 0.0f, mincum = 0.0f;
+    for (int i = 0; i < CC; ++i) {
+        const size_t at = in0 + (size_t)i * a.tok_stride;
+        const float la = a.la[at], cumex = cum;
+        cum += la;
+        mincum = fminf(mincum, cum);
+        const float up = __expf(cum), upx = __expf(cumex), dn = __expf(-cum);
+        const float qs = a.qn[at] * up, es = a.e[at] * upx, ws = a.w[at] * dn, as = a.ah[at] * dn;
+        uint16_t l0, l1, l2;
+        const size_t o_top = (row128 + i) * H + ch, o_bot = (row128 + 64 + i) * H + ch;
+        limbs3(qs, l0, l1, l2);
+        a.QE[o_top] = l0; a.QE[P128 + o_top] = l1; a.QE[2 * P128 + o_top] = l2;
+        a.A3[o_bot] = l0; a.A3[P128 + o_bot] = l1; a.A3[2 * P128 + o_bot] = l2;
+        limbs3(es, l0, l1, l2);
+        a.QE[o_bot] = l0; a.QE[P128 + o_bot] = l1; a.QE[2 * P128 + o_bot] = l2;
+        a.ES[((size_t)u * 64 + i) * H + ch] = es;
+        limbs3(ws, l0, l1, l2);
+        a.WA[o_top] = l0; a.WA[P128 + o_top] = l1; a.WA[2 * P128 + o_top] = l2;
+        limbs3(as, l0, l1, l2);
+        a.WA[o_bot] = l0; a.WA[P128 + o_bot] = l1; a.WA[2 * P128 + o_bot] = l2;
+    }
+    if (mincum < -60.0f || !(cum == cum)) atomicOr(a.flags, 1u);
+    const float cl = cum;
+    a.gc[(size_t)u * H + ch] = __expf(cl);
+    // the keys decayed to the chunk's end, and the values, as rows of 128 token slots (this channel's row)
+    cum = 0.0f;
+    for (int i8 = 0; i8 < CC; i8 += 8) {
+        uint16_t wl[3][8], al[3][8], vv[3][8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const size_t at = in0 + (size_t)(i8 + q) * a.tok_stride;
+            cum += a.la[at];
+            const float kk = __expf(cl - cum);
+            limbs3(a.w[at] * kk, wl[0][q], wl[1][q], wl[2][q]);
+            limbs3(a.ah[at] * kk, al[0][q], al[1][q], al[2][q]);
+            limbs3(a.v[at], vv[0][q], vv[1][q], vv[2][q]);
+        }
+#pragma unroll
+        for (int p = 0; p < 3; ++p) {
+            auto pack = [](const uint16_t* s) { return make_uint4(s[0] | ((uint32_t)s[1] << 16), s[2] | ((uint32_t)s[3] << 16), s[4] | ((uint32_t)s[5] << 16), s[6] | ((uint32_t)s[7] << 16)); };
+            *reinterpret_cast<uint4*>(a.B5 + p * PT + rowT + i8) = pack(wl[p]);
+            *reinterpret_cast<uint4*>(a.B5 + p * PT + rowT + 64 + i8) = pack(al[p]);
+            *reinterpret_cast<uint4*>(a.A5 + p * PT + rowT + i8) = pack(vv[p]);
+        }
+    }
+}
+
+// ---- the four 64x64 matrices of a chunk and the inverse: one block of 256 threads per (chunk, head) --------------
+__global__ void __launch_bounds__(256) chunk_solve_kernel(const ChunkArgs a) {
+    pdl_enter();
+    extern __shared__ __align__(16) float sm[];
+    float* Ae = sm;               // [64][65]
+    float* Ke = Ae + 64 * 65;     // [64][65]
+    float* X = Ke + 64 * 65;      // [64][65] the inverse
+    const int u = blockIdx.x, tid = threadIdx.x;
+    const float* G = a.Gm + (size_t)u * 128 * 128;
+    float* Qw = a.Qw + (size_t)u * 4096;
+    float* Qa = a.Qa + (size_t)u * 4096;
+    for (int n = tid; n < 4096; n += 256) {
+        const int i = n >> 6, jj = n & 63;
+        Qw[n] = jj <= i ? G[(size_t)i * 128 + jj] : 0.0f;
+        Qa[n] = jj <= i ? G[(size_t)i * 128 + 64 + jj] : 0.0f;
+        Ke[i * 65 + jj] = jj < i ? G[(size_t)(64 + i) * 128 + jj] : 0.0f;
+        Ae[i * 65 + jj] = jj < i ? G[(size_t)(64 + i) * 128 + 64 + jj] : 0.0f;
+    }
+    __syncthreads();
+    // X = (I + Ae)^-1 by forward substitution, one thread per column: x_i = [i == c] - sum_{k < i} Ae[i][k] x_k
+    if (tid < 64) {
+        const int c = tid;
+        for (int i = 0; i < 64; ++i) {
+            float s = i == c ? 1.0f : 0.0f;
+            for (int k = c; k < i; ++k) s = fmaf(-Ae[i * 65 + k], X[k * 65 + c], s);  // x_k = 0 for k < c
+            X[i * 65 + c] = i < c ? 0.0f : s;
+        }
+    }
+    __syncthreads();
+    float* Ti = a.Tinv + (size_t)u * 4096;
+    float* TK = a.TK + (size_t)u * 4096;
+    for (int n = tid; n < 4096; n += 256) {
+        const int i = n >> 6, c = n & 63;
+        Ti[n] = X[i * 65 + c];
+        float s = 0.0f;
+        for (int k = 0; k <= i; ++k) s = fmaf(X[i * 65 + k], Ke[k * 65 + c], s);  // X is lower triangular
+        TK[n] = s;
+    }
+}
+
+// ---- D [64 x cols] = Mx [64 x 64] . Xin [64 x cols] per (chunk, head): p1 = T es (as limbs), r0 = (T Ke) v, qwv = Qw v -----
+// grid (H / 128, nC * HB, 3); 256 threads: thread (r4, c8) owns rows r4 * 4 .. + 3 and columns c8 * 8 .. + 7 of the tile
+__global__ void __launch_bounds__(256) chunk_small_kernel(const ChunkArgs a) {
+    pdl_enter();
+    __shared__ __align__(16) float Mt[64][64];  // transposed: [k][row]
+    __shared__ __align__(16) float Xs[64][128];
+    const int H = a.hs, u = blockIdx.y, j = u / a.HB, hb = u % a.HB, which = blockIdx.z, c0 = blockIdx.x * 128, tid = threadIdx.x;
+    const float* Mx = (which == 0 ? a.Tinv : which == 1 ? a.TK : a.Qw) + (size_t)u * 4096;
+    for (int n = tid; n < 4096; n += 256) Mt[n & 63][n >> 6] = Mx[n];
+    for (int n = tid; n < 64 * 32; n += 256) {
+        const int i = n >> 5, q = (n & 31) * 4;
+        const float* src = which == 0 ? a.ES + ((size_t)u * 64 + i) * H + c0 + q
+                                      : a.v + (size_t)(j * CC + i) * a.tok_stride + (size_t)hb * H + c0 + q;
+        *reinterpret_cast<float4*>(&Xs[i][q]) = *reinterpret_cast<const float4*>(src);
+    }
+    __syncthreads();
+    const int r4 = tid >> 4, c8 = tid & 15;
+    float acc[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[i][q] = 0.0f;
+    for (int k = 0; k < 64; ++k) {
+        const float4 x0 = *reinterpret_cast<const float4*>(&Xs[k][c8 * 8]), x1 = *reinterpret_cast<const float4*>(&Xs[k][c8 * 8 + 4]);
+        const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        const float4 m4 = *reinterpret_cast<const float4*>(&Mt[k][r4 * 4]);
+        const float mv[4] = {m4.x, m4.y, m4.z, m4.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc[i][q] = fmaf(mv[i], xv[q], acc[i][q]);
+    }
+    const size_t P128 = (size_t)a.nC * a.HB * 128 * H;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int row = r4 * 4 + i;
+        if (which == 0) {  // p1: the top rows of the state product's left operand, as limbs
+            const size_t o = ((size_t)u * 128 + row) * H + c0 + c8 * 8;
+            uint16_t l[3][8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) limbs3(acc[i][q], l[0][q], l[1][q], l[2][q]);
+#pragma unroll
+            for (int p = 0; p < 3; ++p)
+                *reinterpret_cast<uint4*>(a.A3 + p * P128 + o) =
+                    make_uint4(l[p][0] | ((uint32_t)l[p][1] << 16), l[p][2] | ((uint32_t)l[p][3] << 16), l[p][4] | ((uint32_t)l[p][5] << 16), l[p][6] | ((uint32_t)l[p][7] << 16));
+        } else {
+            float* dst = (which == 1 ? a.r0 : a.qwv) + ((size_t)u * 64 + row) * H + c0 + c8 * 8;
+            *reinterpret_cast<float4*>(dst) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+            *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+        }
+    }
+}
+
+// ---- one chunk's reads: rr = rr0 + r0, y = yq + qwv - Qa rr; -rr^T into the update's left operand ---------------
+// grid (H / 128, HB); 256 threads
+__global__ void __launch_bounds__(256) chunk_read_kernel(const ChunkArgs a, int j) {
+    pdl_enter();
+    __shared__ __align__(16) float Mt[64][64];  // Qa transposed: [k][row]
+    __shared__ __align__(16) float Rs[64][128];
+    const int H = a.hs, hb = blockIdx.y, u = j * a.HB + hb, c0 = blockIdx.x * 128, tid = threadIdx.x;
+    const float* Qa = a.Qa + (size_t)u * 4096;
+    for (int n = tid; n < 4096; n += 256) Mt[n & 63][n >> 6] = Qa[n];
+    const float* RY = a.RY + (size_t)hb * 128 * H;
+    for (int n = tid; n < 64 * 32; n += 256) {
+        const int i = n >> 5, q = (n & 31) * 4;
+        const float4 x = *reinterpret_cast<const float4*>(RY + (size_t)i * H + c0 + q);
+        const float4 r = *reinterpret_cast<const float4*>(a.r0 + ((size_t)u * 64 + i) * H + c0 + q);
+        *reinterpret_cast<float4*>(&Rs[i][q]) = make_float4(x.x + r.x, x.y + r.y, x.z + r.z, x.w + r.w);
+    }
+    __syncthreads();
+    const int r4 = tid >> 4, c8 = tid & 15;
+    float acc[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[i][q] = 0.0f;
+    for (int k = 0; k < 64; ++k) {
+        const float4 x0 = *reinterpret_cast<const float4*>(&Rs[k][c8 * 8]), x1 = *reinterpret_cast<const float4*>(&Rs[k][c8 * 8 + 4]);
+        const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        const float4 m4 = *reinterpret_cast<const float4*>(&Mt[k][r4 * 4]);
+        const float mv[4] = {m4.x, m4.y, m4.z, m4.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc[i][q] = fmaf(mv[i], xv[q], acc[i][q]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int row = r4 * 4 + i;
+        const float* yq = RY + (size_t)(64 + row) * H + c0 + c8 * 8;
+        const float* qv = a.qwv + ((size_t)u * 64 + row) * H + c0 + c8 * 8;
+        float* dst = a.y + (size_t)(j * CC + row) * a.tok_stride + (size_t)hb * H + c0 + c8 * 8;
+        float o[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) o[q] = (yq[q] + qv[q]) - acc[i][q];
+        *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(o[4], o[5], o[6], o[7]);
+    }
+    // -rr transposed: row (value) of the update's left operand, token slots 64 .. 127; thread = (value, half of the tokens)
+    const size_t PT = (size_t)a.nC * a.HB * H * 128;
+    const int val = tid & 127, half = tid >> 7;
+    const size_t rowT = ((size_t)u * H + c0 + val) * 128 + 64 + half * 32;
+#pragma unroll
+    for (int i8 = 0; i8 < 32; i8 += 8) {
+        uint16_t l[3][8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) limbs3(-Rs[half * 32 + i8 + q][val], l[0][q], l[1][q], l[2][q]);
+#pragma unroll
+        for (int p = 0; p < 3; ++p)
+            *reinterpret_cast<uint4*>(a.A5 + p * PT + rowT + i8) =
+                make_uint4(l[p][0] | ((uint32_t)l[p][1] << 16), l[p][2] | ((uint32_t)l[p][3] << 16), l[p][4] | ((uint32_t)l[p][5] << 16), l[p][6] | ((uint32_t)l[p][7] << 16));
+    }
+}
+
+// ---- the state between its layouts: slice-major F [hb][hs / cw][key][cw] <-> transposed Ft [hb][value][key] (+ limbs) -----
+// grid (H / 32, H / 32, HB), 32 x 8 threads: a 32 x 32 tile through shared memory
+__global__ void chunk_state_kernel(const ChunkArgs a, int to_ft) {
+    pdl_enter();
+    __shared__ float tile[32][33];
+    const int H = a.hs, cw = a.cw, hb = blockIdx.z, k0 = blockIdx.x * 32, v0 = blockIdx.y * 32;
+    float* F = a.F + (size_t)hb * H * H;
+    float* Ft = a.Ft + (size_t)hb * H * H;
+    const size_t PF = (size_t)a.HB * H * H;
+    auto fidx = [&](int key, int val) { return (size_t)(val / cw) * H * cw + (size_t)key * cw + (val % cw); };
+    if (to_ft) {
+        for (int r = threadIdx.y; r < 32; r += 8) tile[r][threadIdx.x] = F[fidx(k0 + r, v0 + threadIdx.x)];  // [key][value]
+        __syncthreads();
+        for (int r = threadIdx.y; r < 32; r += 8) {
+            const float x = tile[threadIdx.x][r];  // key = k0 + x-thread, value = v0 + r
+            const size_t o = (size_t)(v0 + r) * H + k0 + threadIdx.x;
+            Ft[o] = x;
+            uint16_t l0, l1, l2;
+            limbs3(x, l0, l1, l2);
+            const size_t ol = (size_t)hb * H * H + o;
+            a.Ft_limbs[ol] = l0; a.Ft_limbs[PF + ol] = l1; a.Ft_limbs[2 * PF + ol] = l2;
+        }
+    } else {
+        for (int r = threadIdx.y; r < 32; r += 8) tile[r][threadIdx.x] = Ft[(size_t)(v0 + r) * H + k0 + threadIdx.x];  // [value][key]
+        __syncthreads();
+        for (int r = threadIdx.y; r < 32; r += 8) F[fidx(k0 + r, v0 + threadIdx.x)] = tile[threadIdx.x][r];
+    }
+}
+
+}  // namespace
+
+size_t mem_chunk_workspace_bytes(int HB, int hs, int nC) {
+    const size_t H = hs, U = (size_t)nC * HB;
+    size_t b = 0;
+    b += 3 * (3 * U * 128 * H * 2);   // QE, WA, A3 limbs
+    b += 2 * (3 * U * H * 128 * 2);   // A5, B5 limbs
+    b += 3 * (U * 64 * H * 4);        // ES, r0, qwv
+    b += U * H * 4;                   // gc
+    b += U * 128 * 128 * 4;           // Gm
+    b += 4 * (U * 4096 * 4);          // Qw, Qa, Tinv, TK
+    b += (size_t)HB * 128 * H * 4;    // RY
+    b += (size_t)HB * H * H * 4;      // Ft
+    b += 3 * (size_t)HB * H * H * 2;  // Ft limbs
+    return b + 4096;
+}
+
+void mem_chunk_carve(ChunkArgs& a, void* ws) {
+    const size_t H = a.hs, U = (size_t)a.nC * a.HB;
+    unsigned char* p = static_cast<unsigned char*>(ws);
+    auto take = [&](size_t bytes) { void* q = p; p += (bytes + 255) & ~(size_t)255; return q; };
+    a.QE = (uint16_t*)take(3 * U * 128 * H * 2);
+    a.WA = (uint16_t*)take(3 * U * 128 * H * 2);
+    a.A3 = (uint16_t*)take(3 * U * 128 * H * 2);
+    a.A5 = (uint16_t*)take(3 * U * H * 128 * 2);
+    a.B5 = (uint16_t*)take(3 * U * H * 128 * 2);
+    a.ES = (float*)take(U * 64 * H * 4);
+    a.r0 = (float*)take(U * 64 * H * 4);
+    a.qwv = (float*)take(U * 64 * H * 4);
+    a.gc = (float*)take(U * H * 4);
+    a.Gm = (float*)take(U * 128 * 128 * 4);
+    a.Qw = (float*)take(U * 4096 * 4);
+    a.Qa = (float*)take(U * 4096 * 4);
+    a.Tinv = (float*)take(U * 4096 * 4);
+    a.TK = (float*)take(U * 4096 * 4);
+    a.RY = (float*)take((size_t)a.HB * 128 * H * 4);
+    a.Ft = (float*)take((size_t)a.HB * H * H * 4);
+    a.Ft_limbs = (uint16_t*)take(3 * (size_t)a.HB * H * H * 2);
+}
+
+bool mem_chunk_covers(int hs, int T, float momentum) { return hs % 128 == 0 && T % CC == 0 && T > 0 && !(momentum > 0.0f); }
+
+// Stage 1: scaling (sets *a.flags when a chunk's rates are too strong for this form).  The caller checks the flag
+// before stage 2.
+bool launch_mem_chunk_scale(cudaStream_t st, const ChunkArgs& a) {
+    if (!mem_chunk_covers(a.hs, a.nC * CC, 0.0f)) return false;
+    launch_k(chunk_scale_kernel, dim3((a.hs + 255) / 256, a.nC * a.HB), dim3(256), 0, st, a);
+    return true;
+}
+
+// Stage 2: everything else; the state F (slice-major) is read at the start and written back at the end.
+bool launch_mem_chunk_rest(cudaStream_t st, const ChunkArgs& a) {
+    const int H = a.hs, U = a.nC * a.HB;
+    launch_k(chunk_state_kernel, dim3(H / 32, H / 32, a.HB), dim3(32, 8), 0, st, a, 1);
+    TcbArgs g{};
+    g.a = a.QE; g.b = a.WA; g.rows_a = g.rows_b = (int64_t)U * 128; g.C = a.Gm; g.ldc = 128; g.c_batch_stride = 128 * 128;
+    g.M = 128; g.N = 128; g.K = H; g.batch = U; g.status = a.status;
+    if (!launch_tc_bgemm(st, g, TCB_STORE)) return false;
+    const size_t solve_smem = 3 * 64 * 65 * sizeof(float);
+    cudaFuncSetAttribute(chunk_solve_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)solve_smem);
+    launch_k(chunk_solve_kernel, dim3(U), dim3(256), solve_smem, st, a);
+    launch_k(chunk_small_kernel, dim3(H / 128, U, 3), dim3(256), 0, st, a);
+    for (int j = 0; j < a.nC; ++j) {
+        TcbArgs s3{};
+        s3.a = a.A3; s3.a_row0 = (int64_t)j * a.HB * 128; s3.rows_a = (int64_t)U * 128;
+        s3.b = a.Ft_limbs; s3.rows_b = (int64_t)a.HB * H;
+        s3.C = a.RY; s3.ldc = H; s3.c_batch_stride = (int64_t)128 * H; s3.M = 128; s3.N = H; s3.K = H; s3.batch = a.HB; s3.status = a.status;
+        if (!launch_tc_bgemm(st, s3, TCB_STORE)) return false;
+        launch_k(chunk_read_kernel, dim3(H / 128, a.HB), dim3(256), 0, st, a, j);
+        TcbArgs s5{};
+        s5.a = a.A5; s5.a_row0 = (int64_t)j * a.HB * H; s5.rows_a = (int64_t)U * H;
+        s5.b = a.B5; s5.b_row0 = (int64_t)j * a.HB * H; s5.rows_b = (int64_t)U * H;
+        s5.C = a.Ft; s5.ldc = H; s5.c_batch_stride = (int64_t)H * H; s5.M = H; s5.N = H; s5.K = 128; s5.batch = a.HB;
+        s5.colscale = a.gc + (size_t)j * a.HB * H; s5.colscale_batch_stride = H;
+        s5.c_limbs = a.Ft_limbs; s5.c_limb_plane = (int64_t)a.HB * H * H; s5.status = a.status;
+        if (!launch_tc_bgemm(st, s5, TCB_DECAY)) return false;
+    }
+    launch_k(chunk_state_kernel, dim3(H / 32, H / 32, a.HB), dim3(32, 8), 0, st, a, 0);
+    return true;
+}
+
+int mem_chunk_launches(int nC) { return 5 + 3 * nC + 1; }
+
+}  // namespace ava

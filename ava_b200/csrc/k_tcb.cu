@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(B_THREADS) tc_bgemm_kernel(const __grid_consta
 
     if (tid == 0) {
         bool ok = true;
-        const int ya = bz * a.M + m0, yb = bz * a.N + n0;
+        const int ya = (int)a.a_row0 + bz * a.M + m0, yb = (int)a.b_row0 + bz * a.N + n0;
         for (int it = 0; it < kt && ok; ++it) {
             const int s = it % STAGES, n = it / STAGES;
             if (n > 0) ok = bar_wait(&empty[s], (uint32_t)((n - 1) & 1));

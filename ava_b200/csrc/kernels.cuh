@@ -123,6 +123,7 @@ struct TcbArgs {
     const uint16_t* a;        // [3][rows_a][K], rows_a = batch * M
     const uint16_t* b;        // [3][rows_b][K], rows_b = batch * N
     int64_t rows_a, rows_b;
+    int64_t a_row0, b_row0;   // first row of batch item 0 inside a plane (a window of a longer buffer)
     float* C;                 // [batch][M][ldc]
     int ldc;
     int64_t c_batch_stride;   // floats between batch items of C
@@ -135,6 +136,28 @@ struct TcbArgs {
     uint32_t* status;
 };
 bool launch_tc_bgemm(cudaStream_t st, const TcbArgs& a, int epi);
+
+// The fast-weight memory over chunks of 64 tokens in its chunk-parallel form (k_chunk.cu), per-channel gates without
+// momentum.  Inputs are time-major: element (token t, head-row hb, channel c) at [t * tok_stride + hb * hs + c], t in
+// [0, 64 nC); HB = rows * heads.  F is the state in the step kernels' slice-major layout.
+struct ChunkArgs {
+    int HB, hs, nC, cw;
+    int64_t tok_stride;
+    const float *qn, *e, *w, *ah, *v, *la;  // unit query, unit erase direction, write key, erase key, value, log rate
+    float* y;                                // reads, time-major like the inputs
+    float* F;
+    uint32_t* flags;                         // bit 0: a chunk's rates are outside this form's range
+    uint32_t* status;
+    // workspace (mem_chunk_carve)
+    uint16_t *QE, *WA, *A3, *A5, *B5, *Ft_limbs;
+    float *ES, *r0, *qwv, *gc, *Gm, *Qw, *Qa, *Tinv, *TK, *RY, *Ft;
+};
+size_t mem_chunk_workspace_bytes(int HB, int hs, int nC);
+void mem_chunk_carve(ChunkArgs& a, void* ws);
+bool mem_chunk_covers(int hs, int T, float momentum);
+bool launch_mem_chunk_scale(cudaStream_t st, const ChunkArgs& a);
+bool launch_mem_chunk_rest(cudaStream_t st, const ChunkArgs& a);
+int mem_chunk_launches(int nC);
 void launch_widen_transpose(cudaStream_t st, const int8_t* q, int K, int N, uint16_t* out);
 
 // ---- row kernels ----------------------------------------------------------------------------------------------

@@ -274,6 +274,42 @@ int ava_op_tc_bgemm(int device, int32_t batch, int32_t m, int32_t n, int32_t k, 
     return AVA_OK;
 }
 
+/* The chunk-parallel form of the fast-weight memory alone (tensor-core products; agrees with the token loop to
+ * rounding, not bit for bit).  t tokens (a multiple of 64) of hb head-rows of size hs (a multiple of 128), inputs
+ * time-major [t][hb][hs]: unit query qn, unit erase direction e, write key w, erase key ah, value v, log rate la; the
+ * state f [hb][hs(key)][hs(value)] is advanced in place, y [t][hb][hs] receives the reads.  *out_of_range is set to 1
+ * (and nothing else is written) when a chunk's rates are too strong for this form; the caller then uses the token loop. */
+int ava_op_mem_chunk(int device, int32_t t, int32_t hb, int32_t hs, const float* qn, const float* e, const float* w, const float* ah, const float* v,
+                     const float* la, float* f, float* y, int32_t* out_of_range) {
+    if (!qn || !e || !w || !ah || !v || !la || !f || !y || !out_of_range || t <= 0 || hb <= 0 || hs <= 0) return AVA_ERR_ARG;
+    if (!mem_chunk_covers(hs, t, 0.0f)) return AVA_NOT_APPLICABLE;
+    int rc = begin(device);
+    if (rc) return rc;
+    const size_t vn = (size_t)t * hb * hs, fn = (size_t)hb * hs * hs;
+    Tmp dq, de, dw, da, dv, dl, df, dy, dws, dfl;
+    OCK(up(dq, qn, vn * 4)); OCK(up(de, e, vn * 4)); OCK(up(dw, w, vn * 4)); OCK(up(da, ah, vn * 4)); OCK(up(dv, v, vn * 4)); OCK(up(dl, la, vn * 4));
+    OCK(up(df, f, fn * 4)); OCK(up(dy, nullptr, vn * 4)); OCK(up(dfl, nullptr, 8));
+    OCK(cudaMemset(dfl.p, 0, 8));
+    ChunkArgs c{};
+    c.HB = hb; c.hs = hs; c.nC = t / 64; c.cw = hs; c.tok_stride = (int64_t)hb * hs;
+    c.qn = dq.as<float>(); c.e = de.as<float>(); c.w = dw.as<float>(); c.ah = da.as<float>(); c.v = dv.as<float>(); c.la = dl.as<float>();
+    c.y = dy.as<float>(); c.F = df.as<float>(); c.flags = dfl.as<uint32_t>(); c.status = dfl.as<uint32_t>() + 1;
+    OCK(up(dws, nullptr, mem_chunk_workspace_bytes(hb, hs, c.nC)));
+    mem_chunk_carve(c, dws.p);
+    if (!launch_mem_chunk_scale(0, c)) return AVA_NOT_APPLICABLE;
+    uint32_t fl[2] = {0, 0};
+    OCK(cudaMemcpy(fl, dfl.p, 8, cudaMemcpyDeviceToHost));
+    *out_of_range = (int32_t)(fl[0] & 1u);
+    if (*out_of_range) return end_();
+    if (!launch_mem_chunk_rest(0, c)) return AVA_NOT_APPLICABLE;
+    if ((rc = end_())) return rc;
+    OCK(cudaMemcpy(fl, dfl.p, 8, cudaMemcpyDeviceToHost));
+    if (fl[1]) return AVA_ERR_CUDA;
+    OCK(cudaMemcpy(f, df.p, fn * 4, cudaMemcpyDeviceToHost));
+    OCK(cudaMemcpy(y, dy.p, vn * 4, cudaMemcpyDeviceToHost));
+    return AVA_OK;
+}
+
 /* Testing aid for the kernels' bounded waits (no GPU fault involved: every copy completes, only a barrier is told to
  * expect 16 bytes more than will ever arrive).  Runs the fast-weight update + read on m heads of size hs whose state
  * is filled with a pattern, with chunk `chunk` of every block's first item mis-counted and a poll limit of

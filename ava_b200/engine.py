@@ -135,6 +135,7 @@ def lib() -> C.CDLL:
         "ava_op_lif": ([C.c_int, fp, fp, fp, fp, fp, C.c_int32, fp, fp, fp, C.c_int32, C.c_int32, fp, fp, fp], C.c_int),
         "ava_op_kwta": ([C.c_int, fp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, fp], C.c_int),
         "ava_op_mem_heads": ([C.c_int, C.c_int32, C.c_int32, fp, fp, fp, fp, fp, fp, fp, fp, fp, fp], C.c_int),
+        "ava_op_mem_chunk": ([C.c_int, C.c_int32, C.c_int32, C.c_int32, fp, fp, fp, fp, fp, fp, fp, fp, C.POINTER(C.c_int32)], C.c_int),
         "ava_op_tc_bgemm": ([C.c_int, C.c_int32, C.c_int32, C.c_int32, C.c_int32, fp, fp, fp, fp, fp], C.c_int),
         "ava_debug_mem_heads_wait_runs_out": ([C.c_int, C.c_int32, C.c_int32, C.c_int32, C.c_uint32, C.POINTER(C.c_int32)], C.c_int),
         "ava_mem_heads_static": ([C.c_int, vp, C.c_int32, C.c_int32] + [vp] * 10, C.c_int),
@@ -160,7 +161,7 @@ EXPORTS = ("ava_engine_create ava_engine_destroy ava_last_error ava_engine_set_f
            "ava_state_rows ava_state_select ava_state_cat ava_state_seen ava_state_len ava_state_export "
            "ava_state_import ava_step ava_step_greedy ava_forward_with_state ava_step_device ava_prefill_device ava_state_set_kv_shard ava_shard_parts ava_split_step_begin ava_shard_partial ava_split_step_end ava_sync "
            "ava_engine_stream ava_engine_launches ava_engine_bytes ava_state_bytes ava_debug_keep ava_debug_width "
-           "ava_debug_get ava_engine_set_segmented_read ava_engine_set_fast_products ava_engine_set_lanes ava_prof_enable ava_prof_read ava_prof_names ava_engine_fingerprint ava_state_engine ava_state_set_seen ava_state_save ava_state_load ava_ckpt_read_u32 ava_conv_path ava_conv_save ava_conv_load ava_step_sample ava_generate_sampled ava_op_sample ava_engine_device ava_engine_config ava_splitmix64_next ava_pick ava_generate ava_loader_error ava_ckpt_open ava_ckpt_close ava_ckpt_count ava_ckpt_find ava_ckpt_tensor ava_ckpt_read_f32 ava_arch_flags ava_config_from_ckpt ava_engine_load_ckpt ava_op_q8_matmul ava_op_q8_event_matmul ava_op_q8_tc_matmul ava_debug_mem_heads_wait_runs_out ava_op_tc_bgemm ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
+           "ava_debug_get ava_engine_set_segmented_read ava_engine_set_fast_products ava_engine_set_lanes ava_prof_enable ava_prof_read ava_prof_names ava_engine_fingerprint ava_state_engine ava_state_set_seen ava_state_save ava_state_load ava_ckpt_read_u32 ava_conv_path ava_conv_save ava_conv_load ava_step_sample ava_generate_sampled ava_op_sample ava_engine_device ava_engine_config ava_splitmix64_next ava_pick ava_generate ava_loader_error ava_ckpt_open ava_ckpt_close ava_ckpt_count ava_ckpt_find ava_ckpt_tensor ava_ckpt_read_f32 ava_arch_flags ava_config_from_ckpt ava_engine_load_ckpt ava_op_q8_matmul ava_op_q8_event_matmul ava_op_q8_tc_matmul ava_debug_mem_heads_wait_runs_out ava_op_tc_bgemm ava_op_mem_chunk ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
            "ava_host_expf ava_host_logf ava_host_rsqrtf ava_host_sinf ava_host_cosf ava_op_math ava_step_trace ava_trace_get ava_trace_free").split()
 
 
@@ -706,6 +707,17 @@ def op_tc_bgemm(a, b, colscale=None, c_in=None, device=0):
     cs = None if colscale is None else _f32(colscale)
     _rc(lib().ava_op_tc_bgemm(device, batch, m, n, k, _p(a), _p(b), _p(cs) if cs is not None else None, _p(c), _p(limb_sum) if limb_sum is not None else None))
     return (c, limb_sum) if colscale is not None else c
+
+
+def op_mem_chunk(qn, e, w, ah, v, la, f, device=0):
+    """The chunk-parallel fast-weight memory over t tokens: inputs [t][hb][hs], f [hb][hs][hs]; returns (y, f', out_of_range)."""
+    qn, e, w, ah, v, la = map(_f32, (qn, e, w, ah, v, la))
+    t, hb, hs = qn.shape
+    f = np.array(f, np.float32, copy=True).reshape(hb, hs, hs)
+    y = np.zeros((t, hb, hs), np.float32)
+    oor = C.c_int32(0)
+    _rc(lib().ava_op_mem_chunk(device, t, hb, hs, _p(qn), _p(e), _p(w), _p(ah), _p(v), _p(la), _p(f), _p(y), C.byref(oor)))
+    return y, f, bool(oor.value)
 
 
 def op_mem_heads(e, v, w, ah, qg, ex, qw, qa, f, device=0):

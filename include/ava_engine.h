@@ -396,6 +396,15 @@ int ava_op_attend(int device, int32_t m, int32_t n, int32_t hs, int32_t bf16_sto
  * else AVA_NOT_APPLICABLE. */
 int ava_op_tc_bgemm(int device, int32_t batch, int32_t m, int32_t n, int32_t k, const float* a, const float* b, const float* colscale, float* c,
                     float* c_limb_sum);
+/* The chunk-parallel form of the fast-weight memory alone, on host buffers: `delta_chunk` / `chunk_core`
+ * (src/arch.rs:1151-1173, 1243-1327) with per-channel gates and no momentum, the big products on the tensor cores.
+ * Like the reference's it agrees with the token loop to rounding (1e-4 of max(1, max|ref|), src/arch/tests.rs:700-753),
+ * not bit for bit.  t tokens (a multiple of 64) of hb head-rows of size hs (a multiple of 128, else
+ * AVA_NOT_APPLICABLE), inputs [t][hb][hs]: qn unit query, e unit erase direction, w write key, ah erase key, v value,
+ * la log rate (<= 0).  f [hb][hs key][hs value] is advanced in place, y [t][hb][hs] gets the reads.  When a chunk's
+ * log rates sum below -60 the form is out of its range: *out_of_range = 1, f and y untouched, AVA_OK. */
+int ava_op_mem_chunk(int device, int32_t t, int32_t hb, int32_t hs, const float* qn, const float* e, const float* w, const float* ah, const float* v,
+                     const float* la, float* f, float* y, int32_t* out_of_range);
 /* Testing aid for the kernels' bounded waits; no counterpart in the reference (its waits are host-side joins).  Runs
  * the fast-weight kernel on m pattern-filled heads of size hs with the byte count of row chunk `chunk` over-stated by
  * 16 on every block's first item and a poll limit of `poll_limit`, so that wait runs out without any copy failing.

@@ -33,3 +33,42 @@ def test_batched_limb_product_is_an_f32_product(batch, m, n, k):
     want1 = g[:, None, :].astype(np.float64) * c0 + want
     assert float((np.abs(c1 - want1) / (mag + np.abs(c0))).max()) < 1e-5
     assert np.array_equal(limb_sum.view(np.uint32), c1.view(np.uint32))
+
+
+def _chunk_case(rng, t, hb, hs, rate_bias):
+    unit = lambda x: (x / np.linalg.norm(x, axis=-1, keepdims=True)).astype(np.float32)
+    q, k, e = (unit(rng.normal(size=(t, hb, hs))) for _ in range(3))
+    v = rng.normal(size=(t, hb, hs)).astype(np.float32)
+    la = (-np.log1p(np.exp(-(rng.normal(size=(t, hb, hs)) + rate_bias)))).astype(np.float32)  # log sigmoid
+    b = (1.0 / (1.0 + np.exp(-rng.normal(size=(t, hb, hs))))).astype(np.float32)
+    f0 = (0.1 * rng.normal(size=(hb, hs, hs))).astype(np.float32)
+    return q, k, e, v, la, b, f0
+
+
+@pytest.mark.parametrize("t,hb,hs,rate_bias", [(64, 1, 128, 3.0), (128, 3, 128, 2.0), (256, 2, 256, 4.0), (128, 2, 768, 3.0)])
+def test_chunked_memory_agrees_with_the_token_loop(t, hb, hs, rate_bias):
+    """y and the state after t tokens from the chunk-parallel kernels (64-token chunks, state carried from chunk to
+    chunk and from a non-zero start) against the oracle's token loop, at the reference's bound for its own chunked
+    form: 1e-4 of max(1, max|ref|)."""
+    from oracle import oracle
+
+    rng = np.random.default_rng(t + hb + hs)
+    q, k, e, v, la, b, f0 = _chunk_case(rng, t, hb, hs, rate_bias)
+    w = (k * b).astype(np.float32)
+    ah = (e * (b * np.exp(la))).astype(np.float32)
+    y, f1, oor = engine.op_mem_chunk(q, e, w, ah, v, la, f0)
+    assert not oor
+    for h in range(hb):
+        yr, fr, _ = oracle.delta_rec(q[:, h], k[:, h], e[:, h], v[:, h], la[:, h], b[:, h], f0=f0[h])
+        assert float(np.abs(y[:, h] - yr).max()) <= 1e-4 * max(1.0, float(np.abs(yr).max())), h
+        assert float(np.abs(f1[h] - fr).max()) <= 1e-4 * max(1.0, float(np.abs(fr).max())), h
+
+
+def test_chunked_memory_refuses_rates_outside_its_range():
+    """Rates that forget by more than e^-60 inside one chunk cannot be written as products of per-token scalings in
+    f32; the pass says so and touches nothing."""
+    rng = np.random.default_rng(5)
+    q, k, e, v, la, b, f0 = _chunk_case(rng, 64, 1, 128, -3.0)  # log rates near -3 per token: -190 over the chunk
+    y, f1, oor = engine.op_mem_chunk(q, e, k * b, e * (b * np.exp(la)), v, la, f0)
+    assert oor
+    assert np.array_equal(f1, f0) and not y.any()
