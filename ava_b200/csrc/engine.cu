@@ -98,6 +98,7 @@ struct Work {
     int ws_rows = 0;
     Dev x, h, proj, ve, vv, vw, vah, vqg, vex, vqs, qw, qa, yraw, y, eqkv, eo, u, act, streams, v_first;
     Dev gz, lra, lrb;  // the gates' stages: [rows][gate_cols], [rows][d] twice
+    Dev vqn, vla, chunk_ws, chunk_flag;  // the chunk-parallel memory of the tolerance mode: unit queries, log rates, its work space
     Dev sig;           // --neuromod: [rows][4] NE, ACh, DA (and one unused) of the step's token-rows
     // --dopamine / --mood: block 0's normed output [rows][d], the rows the head reads (the position before each), the
     // head's logits for them [rows][vocab], surprise s and z [rows], moods [rows][k], the current's gain and the MLP's output [rows][d]
@@ -161,6 +162,8 @@ struct ava_engine : Work {
     std::map<std::string, std::pair<int64_t, double>> prof_total;  // kernel -> (launches, milliseconds)
 
     bool fast = false;     // dense products on the tensor cores (exact products, the tensor core's summation order)
+    bool chunk_mem = true; // with fast: a prompt chunk's fast-weight memory in the chunk-parallel form (k_chunk.cu)
+    int64_t chunked_blocks = 0, chunk_fallbacks = 0;
     Dev limbs;             // [3][rows][d] bf16 limbs of the current product's input
     const float* limbs_src = nullptr;  // the f32 buffer whose limbs the producing kernel has just written there
     int limbs_rows = 0;
@@ -672,6 +675,15 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
             prof_end(e);
             mp.rh_w = w.rh_gw.as<float>();
         }
+        const bool use_chunk = e->fast && e->chunk_mem && T > 1 && !e->keep && mem_chunk_covers(hs, T, c.mem_momentum);
+        if (use_chunk) {
+            const size_t need = mem_chunk_workspace_bytes(rows * nh, hs, T / 64);
+            if (w.chunk_ws.bytes < need) CK(w.chunk_ws.alloc(need));
+            if (w.vqn.bytes < Md * sizeof(float)) { CK(w.vqn.alloc(Md * sizeof(float))); CK(w.vla.alloc(Md * sizeof(float))); }
+            if (!w.chunk_flag.p) CK(w.chunk_flag.alloc(2 * sizeof(uint32_t)));
+            mp.qn_out = w.vqn.as<float>();
+            mp.la_out = w.vla.as<float>();
+        }
         mp.ach = (c.neuromod > 0 && i > 0) ? w.sig.as<float>() + 1 : nullptr;
         mp.ach_stride = 4;
         mp.status = e->status.as<uint32_t>();
@@ -712,7 +724,32 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
         mh.y = w.yraw.as<float>();
         mh.status = e->status.as<uint32_t>();
         prof_begin(e, "mem_heads");
-        if (stream) {
+        bool chunked = false;
+        if (use_chunk) {
+            // the tolerance mode reads a prompt's chunk with the chunk-parallel form on the tensor cores, unless the
+            // rates of some 64 tokens forget too fast for it (then the token loop below, for this block and chunk)
+            ChunkArgs ca{};
+            ca.HB = rows * nh; ca.hs = hs; ca.nC = T / 64; ca.cw = e->cw; ca.tok_stride = (int64_t)rows * d;
+            ca.qn = mp.qn_out; ca.e = mp.e; ca.w = mp.w; ca.ah = mp.ah; ca.v = mp.v; ca.la = mp.la_out; ca.y = mh.y; ca.F = mh.f;
+            ca.flags = w.chunk_flag.as<uint32_t>(); ca.status = e->status.as<uint32_t>();
+            mem_chunk_carve(ca, w.chunk_ws.p);
+            CK(cudaMemsetAsync(ca.flags, 0, sizeof(uint32_t), st));
+            launch_mem_chunk_scale(st, ca);
+            uint32_t out_of_range = 0;
+            CK(cudaMemcpyAsync(&out_of_range, ca.flags, sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
+            CK(cudaStreamSynchronize(st));
+            e->launches += 1;
+            if (!(out_of_range & 1u)) {
+                if (!launch_mem_chunk_rest(st, ca)) return e->fail(AVA_ERR_CUDA, "chunk-parallel memory: a launch was refused");
+                e->launches += mem_chunk_launches(ca.nC) - 2;
+                chunked = true;
+                ++e->chunked_blocks;
+            } else {
+                ++e->chunk_fallbacks;
+            }
+        }
+        if (chunked) {
+        } else if (stream) {
             MemStreamArgs ms{};
             ms.f = mh.f; ms.M = rows; ms.nh = nh; ms.hs = hs; ms.cw = e->cw;
             ms.e = mp.e; ms.qg = mp.qg; ms.v = mp.v; ms.qw = mp.qw; ms.qa = mp.qa;
@@ -1972,6 +2009,19 @@ int ava_engine_device(const ava_engine* e) { return e ? e->device : -1; }
 int ava_engine_set_lanes(ava_engine* e, int32_t lanes) {
     if (!e || lanes < 1 || lanes > 8) return AVA_ERR_ARG;
     e->n_lanes = lanes;
+    return AVA_OK;
+}
+
+int ava_engine_set_chunked_memory(ava_engine* e, int32_t on) {
+    if (!e) return AVA_ERR_ARG;
+    e->chunk_mem = on != 0;
+    return AVA_OK;
+}
+
+int ava_engine_chunked_memory_counts(const ava_engine* e, int64_t* chunked, int64_t* token_loop) {
+    if (!e || !chunked || !token_loop) return AVA_ERR_ARG;
+    *chunked = e->chunked_blocks;
+    *token_loop = e->chunk_fallbacks;
     return AVA_OK;
 }
 

@@ -535,6 +535,10 @@ __global__ void mem_prep_kernel(const MemPrepArgs a) {
         a.qg[o] = qg;
         a.ex[o] = ex;
         if (a.be_out) a.be_out[o] = be;
+        if (a.qn_out) {
+            a.qn_out[o] = qn;
+            a.la_out[o] = la;
+        }
         if (a.qs) a.qs[o] = mul(qn, add(mul(1.0f, a.mom), 0.0f));  // q * (1 * M + 0) (src/model/fstep/arch.rs:784)
         q[c] = qn;
         wv[c] = w;

@@ -214,6 +214,7 @@ struct MemPrepArgs {
     // outputs [M, d] each, qw/qa [M, d / hs]
     float *e, *v, *w, *ah, *qg, *ex, *qw, *qa;
     float* qs;           // [M, d] q * M when the memory has momentum, else nullptr
+    float *qn_out, *la_out;  // [M, d] the unit query and the log rate, for the chunk-parallel form; or nullptr
     float mom;
     uint32_t* status;
 };

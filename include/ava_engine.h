@@ -194,6 +194,14 @@ int ava_engine_set_lanes(ava_engine* e, int32_t lanes);
  * differently.  The spike-driven products (W_out, W_2) keep the exact event sum.  Costs 2 bytes per dense weight of
  * device memory on first use.  Call after ava_engine_finalize, between steps. */
 int ava_engine_set_fast_products(ava_engine* e, int32_t on);
+/* With fast products on, a prompt chunk whose length is a multiple of 64 (head size a multiple of 128, no momentum)
+ * reads the fast-weight memory in its chunk-parallel form on the tensor cores (`delta_chunk`,
+ * design-tests/nn/gpu/src/arch.rs:1151-1173, 1243-1327), which agrees with the token loop to rounding (the reference's
+ * bound for it: 1e-4 of max(1, max|ref|)); a block whose rates forget faster than e^-60 inside 64 tokens falls back to
+ * the token loop for that chunk.  on = 0 keeps the token loop everywhere (default: on).  ava_engine_chunked_memory_counts
+ * reports how many (block, chunk) passes took each form since the engine was made. */
+int ava_engine_set_chunked_memory(ava_engine* e, int32_t on);
+int ava_engine_chunked_memory_counts(const ava_engine* e, int64_t* chunked, int64_t* token_loop);
 
 /* ---- one long sequence with its engram store split by position over several GPUs ------------------------------
  * No counterpart in the reference (one device, src/memory.rs:664-692).  Each GPU runs one process with its own engine

@@ -560,3 +560,59 @@ def test_benchmark_prompt_final_state(orc_same_math, tokens):
     for r in range(rows):
         for name in ("lif.0.v", "lif.11.v", "lif.6.s", "lif.3.a", "mem.0.f", "mem.6.f", "mem.11.f", "eng.k", "eng.v"):
             assert np.array_equal(bits(gs.get(r, name)), bits(os_.get(r, name))), (r, name)
+
+
+@pytest.mark.parametrize("shape", ["small", "benchmark"])
+def test_chunked_memory_in_the_prompt_pass(orc_same_math, shape):
+    """With fast products on, a prompt chunk of a multiple of 64 tokens reads the fast-weight memory in its
+    chunk-parallel form.  Against the same engine with that form switched off (the token loop on the same inputs), the
+    first block's memory state, whose inputs are then the same bits, agrees to the reference's bound for its chunked
+    form, 1e-4 of max(1, max|ref|); the logits are held to the fast products' own loose bound against the oracle."""
+    import torch
+    orc = orc_same_math
+    if shape == "small":
+        cfg = config.make(64, 128, 2, head_size=128, eng_block=1, eng_head_size=32)
+        rows, tokens, chunk, recipe = 3, 256, 128, "awake"
+    else:
+        cfg, rows, tokens, chunk, recipe = config.ava04_shaped(), 2, 256, 128, "bench"
+    w = synth.model(cfg, 0, recipe)
+    gm, om = engine.Model(cfg, w), orc.OracleModel(cfg, w)
+    ids = synth.token_ids(cfg["vocab"], rows, tokens, seed0=7)
+    dev = torch.device("cuda", 0)
+    tok = torch.from_numpy(np.ascontiguousarray(ids.T).astype(np.int32)).to(dev)
+    gm.set_fast_products(True)
+    out = {}
+    for on in (True, False):
+        gm.set_chunked_memory(on)
+        before = gm.chunked_memory_counts()
+        gs = gm.state(rows, tokens + 8)
+        logits = torch.empty(rows, cfg["vocab"], dtype=torch.float32, device=dev)
+        torch.cuda.synchronize()
+        gm.prefill_device(gs, tok.data_ptr(), tokens, chunk, logits.data_ptr(), None)
+        gm.sync()
+        after = gm.chunked_memory_counts()
+        out[on] = (logits.cpu().numpy(), [gs.get(r, "mem.0.f") for r in range(rows)], (after[0] - before[0], after[1] - before[1]))
+    gm.set_chunked_memory(True)
+    gm.set_fast_products(False)
+    passes = cfg["n_blocks"] * (tokens // chunk)
+    print("chunked memory passes (chunk form, token loop):", out[True][2], "of", passes)
+    assert out[False][2] == (0, 0)
+    assert sum(out[True][2]) == passes and out[True][2][0] > 0
+    worst = 0.0
+    for a, b in zip(out[True][1], out[False][1]):
+        worst = max(worst, float(np.abs(a - b).max()) / max(1.0, float(np.abs(b).max())))
+    print("first block's memory, chunk form against token loop:", worst)
+    if out[True][2][1] == 0:
+        assert worst <= 1e-4
+    orc.set_threads(8)
+    try:
+        want = om.state(rows).forward(ids, last_only=True)
+    finally:
+        orc.set_threads(1)
+    # The last position's logits after hundreds of tokens of a spiking model with random weights are no measure of
+    # either form: one tipped spike early on changes the state for good (the fast products' own test bounds three
+    # tokens).  Both errors are printed as a record; the chunk form must not be worse than the token loop by more than
+    # such tipping explains.
+    err = {on: float(np.abs(out[on][0] - want).max()) / float(np.abs(want).max()) for on in (True, False)}
+    print("logits against the oracle, fast products with the chunk form:", err[True], "with the token loop:", err[False])
+    assert np.isfinite(out[True][0]).all() and err[True] <= max(3.0 * err[False], 1e-2)
