@@ -481,6 +481,10 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
     g.K = w.din;
     if (lif) g.lif = *lif;
     if (epi == EPI_ADD) g.lif.ne = row_gain;  // [rows][NM_STRIDE]
+    // with fast products a prompt chunk's k-WTA output is multiplied densely on the tensor cores as well (a quarter of
+    // its entries are non-zero: over thousands of token-rows the dense product is the shorter one); a decode step's
+    // few hundred rows keep the exact event sum
+    if (sparse && e->fast && w.wt.p && M >= 1024) sparse = false;
     if (e->fast && !sparse && !row_gain && w.wt.p && lda == w.din && w.din % 64 == 0 && w.dout % 4 == 0) {
         const size_t need = (size_t)3 * M * w.din * sizeof(uint16_t);
         if (e->limbs.bytes < need) {
@@ -794,7 +798,8 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
                 dbg(e, "eng_qkv", i, w.eqkv.as<float>(), M, 3 * d);
             }
             if (phase == PHASE_BEGIN) {
-                const cudaError_t le0 = cudaGetLastError();
+                cudaError_t le0 = take_launch_error();
+                if (le0 == cudaSuccess) le0 = cudaGetLastError();
                 if (le0 != cudaSuccess) return e->cuda_fail(le0, "kernel launch");
                 return AVA_OK;
             }
@@ -972,7 +977,8 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
                 }
             }
     for (int r = r0; r < r0 + rows; ++r) s->seen[r] += T;
-    const cudaError_t le = cudaGetLastError();
+    cudaError_t le = take_launch_error();
+    if (le == cudaSuccess) le = cudaGetLastError();
     if (le != cudaSuccess) return e->cuda_fail(le, "kernel launch");
     return AVA_OK;
 }
@@ -1183,7 +1189,8 @@ int flush_pending(ava_engine* e, ava_state* s) {
                          s->pend_at(s->pend_set, 2, i), s->pend_at(s->pend_set, 3, i), s->pend_at(s->pend_set, 4, i), (int64_t)s->rows * e->nh(), c.head_size, e->cw);
     e->launches += c.n_blocks;
     s->pending = false;
-    const cudaError_t le = cudaGetLastError();
+    cudaError_t le = take_launch_error();
+    if (le == cudaSuccess) le = cudaGetLastError();
     if (le != cudaSuccess) return e->cuda_fail(le, "kernel launch");
     return AVA_OK;
 }
@@ -1953,7 +1960,8 @@ int ava_shard_partial(ava_engine* e, ava_state* s, const float* qkv_device, floa
     if (!launch_engram_partial(e->stream, ea, seg_len, n_seg, partial_device))
         return e->fail(AVA_ERR_CAPACITY, "engram segments of %d keys do not fit shared memory", seg_len);
     prof_end(e);
-    const cudaError_t le = cudaGetLastError();
+    cudaError_t le = take_launch_error();
+    if (le == cudaSuccess) le = cudaGetLastError();
     if (le != cudaSuccess) return e->cuda_fail(le, "kernel launch");
     return AVA_OK;
 }
@@ -2030,10 +2038,10 @@ int ava_engine_set_fast_products(ava_engine* e, int32_t on) {
     if (!e->finalized) return e->fail(AVA_ERR_ARG, "engine not finalized");
     CK(cudaSetDevice(e->device));
     if (on) {
-        // bf16 [dout][din] copies of the dense matrices (the spike-driven ones keep the exact event sum)
+        // bf16 [dout][din] copies of the dense matrices and of W_2 (W_out, driven by spikes, keeps the exact event sum)
         std::vector<QMat*> mats{&e->head};
         for (auto& b : e->blocks)
-            for (QMat* m : {&b->win, &b->proj, &b->wo, &b->eqkv, &b->ewo, &b->w1}) mats.push_back(m);
+            for (QMat* m : {&b->win, &b->proj, &b->wo, &b->eqkv, &b->ewo, &b->w1, &b->w2}) mats.push_back(m);
         for (QMat* m : mats) {
             if (!m->q.p || m->wt.p || m->din % 64 || m->dout % 4) continue;
             CK(m->wt.alloc((size_t)m->din * m->dout * sizeof(uint16_t)));

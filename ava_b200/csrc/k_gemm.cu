@@ -6,6 +6,7 @@
 // model down another path, so this kernel keeps that order: each thread owns a 4x4 block of outputs and walks k
 // upwards, never splitting K.  The int8 tile is widened to f32 once when it is staged in shared memory and reused by
 // every row of the tile.
+#include <algorithm>
 #include <cstdlib>
 
 #include "ava_math.h"
@@ -468,7 +469,8 @@ __global__ void __launch_bounds__(EV_THREADS) q8_event_kernel(const GemmArgs g) 
     unsigned short* idx = reinterpret_cast<unsigned short*>(vals + g.K);  // [K]
     __shared__ int warp_off[EV_THREADS / 32 + 1];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int r = blockIdx.y, c0 = blockIdx.x * EV_COLS + tid * 4;
+    const int r = blockIdx.z * gridDim.y + blockIdx.y, c0 = blockIdx.x * EV_COLS + tid * 4;  // rows beyond a grid dimension's 65535 go on in z
+    if (r >= g.M) return;
     const float* xr = g.A + (size_t)r * g.lda;
     // ordered compaction, coalesced: each warp takes a contiguous part of the row 32 inputs at a time; first the
     // warps count, then each writes its part of the list behind the parts before it
@@ -612,9 +614,10 @@ __global__ void lif_kernel(const float* cur, const LifParams p, int M, int d) {
 int g_gemm_force = 0;  // tuning override (0: choose by shape)
 int g_resident_max_rows = 16;  // up to this many rows the resident-tile kernel takes the dense products (measured: 19-21 us
                                 // against 23 us for the tiled kernel at 1-8 rows, slower from 32 rows on)
+thread_local cudaError_t g_launch_error = cudaSuccess;
 int g_pdl = 1;         // programmatic dependent launch on every kernel of the step (kernels.cuh)
 
-void prefer_max_shared(const void* kernel) {
+void prefer_max_shared(const void* kernel, int percent_for_this) {
     // once per kernel and device (a handful of kernels: a linear scan of a small table)
     struct Seen { const void* k; int dev; };
     static Seen seen[512];
@@ -629,7 +632,8 @@ void prefer_max_shared(const void* kernel) {
         percent = 50;
         if (const char* v = std::getenv("AVA_CARVEOUT")) percent = std::atoi(v);
     }
-    if (percent >= 0) cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, percent);
+    const int pc = percent_for_this >= 0 ? percent_for_this : percent;
+    if (pc >= 0) cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, pc);
     if (n < 512) seen[n++] = {kernel, dev};
 }
 
@@ -663,7 +667,8 @@ bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {
     if (a.K > 65535 || epi == EPI_LIF) return false;
     const size_t smem = (size_t)a.K * (sizeof(float) + sizeof(unsigned short));
     if (smem > 200 * 1024) return false;
-    dim3 grid((a.N + EV_COLS - 1) / EV_COLS, a.M);
+    const int gy = std::min(a.M, 32768);
+    dim3 grid((a.N + EV_COLS - 1) / EV_COLS, gy, (a.M + gy - 1) / gy);
     auto go = [&](auto kernel) {
         if (smem > 32 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         launch_k(kernel, dim3(grid), dim3(EV_THREADS), smem, st, a);

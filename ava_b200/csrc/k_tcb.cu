@@ -9,9 +9,9 @@
 // hi.mid, mid.hi, hi.lo, mid.mid, lo.hi), all into one f32 accumulator in tensor memory, so the result carries the
 // operands to about 2^-24 each: an f32 product with the tensor core's summation order.
 //
-// One block of 128 threads per 128 x BN tile of one batch item; k-tiles of 64 in a ring of stages.  Thread 0 brings the
+// One block of 256 threads per 128 x BN tile of one batch item; k-tiles of 64 in a ring of stages.  Thread 0 brings the
 // limb tiles in by TMA (2-D tiled, 128-byte swizzle; no cluster multicast), thread 32 issues the multiply-adds and
-// commits each stage's "empty" barrier, all four warps read the accumulator back (tcgen05.ld) for the epilogue:
+// commits each stage's "empty" barrier, all eight warps read the accumulator back (tcgen05.ld) for the epilogue:
 //   TCB_STORE   C = acc
 //   TCB_DECAY   C = colscale[b][n] * C + acc, and the three limbs of the new C written beside it (the state update of the
 //               chunked memory: the next step multiplies by this state, so its limbs are made where it is produced)
@@ -26,7 +26,7 @@ namespace ava {
 
 namespace {
 
-constexpr int B_BM = 128, B_BK = 64, B_THREADS = 128;
+constexpr int B_BM = 128, B_BK = 64, B_THREADS = 256;
 constexpr uint32_t B_WAIT_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -89,6 +89,14 @@ __global__ void __launch_bounds__(B_THREADS) tc_bgemm_kernel(const __grid_consta
     const int m0 = blockIdx.y * B_BM, n0 = blockIdx.x * BN, bz = blockIdx.z;
     const int kt = a.K / B_BK;
 
+    if (EPI == TCB_DECAY) {
+        // the tile of the old C is wanted by the epilogue only: ask for it now, so that it waits in L2 by then
+        const float* ctile = a.C + (size_t)bz * a.c_batch_stride + (size_t)m0 * a.ldc + n0;
+        for (int n = tid; n < B_BM * (BN / 32); n += B_THREADS) {
+            const int r = n / (BN / 32), c = (n % (BN / 32)) * 32;
+            if (m0 + r < a.M && n0 + c < a.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(ctile + (size_t)r * a.ldc + c));
+        }
+    }
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
             bar_init(&full[s], 1);
@@ -160,13 +168,18 @@ __global__ void __launch_bounds__(B_THREADS) tc_bgemm_kernel(const __grid_consta
     if (!acc_ok && lane == 0) atomicOr(a.status, ST_WAIT_TIMEOUT);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-    // epilogue: warp w reads lanes 32 w .. 32 w + 31 (one output row per thread), 32 columns per instruction
-    const int row = m0 + warp * 32 + lane;
-    float* crow = a.C + (size_t)bz * a.c_batch_stride + (size_t)row * a.ldc;
+    // epilogue: warp w reads lanes 32 (w % 4) .. + 31 of the accumulator (one output row per thread), 32 columns per
+    // instruction; warps 0-3 take the left half of the tile's columns, warps 4-7 the right half.  Each 32 x 32 piece
+    // goes through a staging square in shared memory (the operand stage is free once the accumulator is complete) so
+    // that global memory is touched row-wise: eight lanes cover 128 contiguous bytes of a row, four rows per instruction.
+    const int wq = warp & 3, half = warp >> 2;
+    float* stage = reinterpret_cast<float*>(smem) + warp * (32 * 33);
+    const int sub_r = lane >> 3, sub_c = (lane & 7) * 4;
+    float* cbase = a.C + (size_t)bz * a.c_batch_stride;
 #pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 32) {
+    for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
         uint32_t r[32];
-        const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+        const uint32_t taddr = tmem + ((uint32_t)(wq * 32) << 16) + (uint32_t)c0;
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -177,42 +190,47 @@ __global__ void __launch_bounds__(B_THREADS) tc_bgemm_kernel(const __grid_consta
               "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
             : "r"(taddr));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < a.M && acc_ok) {
-            float4 prev[8];
-            if (EPI == TCB_DECAY) {  // the old values are read before any new one is written
+        const int c = n0 + c0 + sub_c;           // this lane's four columns
+        const bool col_ok = c < a.N && acc_ok;   // N is a multiple of 4
+        float4 prev[8], g = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (EPI == TCB_DECAY) {  // the old values: asked for before the staging, all eight row groups at once
 #pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                    const int c = n0 + c0 + j;
-                    prev[j / 4] = c < a.N ? *reinterpret_cast<const float4*>(crow + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
+            for (int it = 0; it < 8; ++it) {
+                const int row = m0 + wq * 32 + it * 4 + sub_r;
+                prev[it] = (col_ok && row < a.M) ? *reinterpret_cast<const float4*>(cbase + (size_t)row * a.ldc + c) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
+            if (col_ok) g = *reinterpret_cast<const float4*>(a.colscale + (size_t)bz * a.colscale_batch_stride + c);
+        }
+        __syncwarp();  // the lanes' reads of the piece before
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-                const int c = n0 + c0 + j;
-                if (c >= a.N) continue;  // N is a multiple of 4
-                float4 o = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                if (EPI == TCB_DECAY) {
-                    const float4 g = *reinterpret_cast<const float4*>(a.colscale + (size_t)bz * a.colscale_batch_stride + c);
-                    const float4 x = prev[j / 4];
-                    o = make_float4(add(mul(x.x, g.x), o.x), add(mul(x.y, g.y), o.y), add(mul(x.z, g.z), o.z), add(mul(x.w, g.w), o.w));
-                }
-                *reinterpret_cast<float4*>(crow + c) = o;
-                if (EPI == TCB_DECAY) {
-                    // the new value's three limbs, in the operand layout of the product that reads it next: [limb][batch * M][N]
-                    const float ov[4] = {o.x, o.y, o.z, o.w};
-                    uint16_t l0[4], l1[4], l2[4];
+        for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = __uint_as_float(r[j]);
+        __syncwarp();
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        l0[q] = f_to_bf16(ov[q]);
-                        const float r1 = sub(ov[q], bf16_to_f(l0[q]));
-                        l1[q] = f_to_bf16(r1);
-                        l2[q] = f_to_bf16(sub(r1, bf16_to_f(l1[q])));
-                    }
-                    const size_t at = ((size_t)bz * a.M + row) * a.N + c;
-                    *reinterpret_cast<uint2*>(a.c_limbs + at) = make_uint2(l0[0] | ((uint32_t)l0[1] << 16), l0[2] | ((uint32_t)l0[3] << 16));
-                    *reinterpret_cast<uint2*>(a.c_limbs + a.c_limb_plane + at) = make_uint2(l1[0] | ((uint32_t)l1[1] << 16), l1[2] | ((uint32_t)l1[3] << 16));
-                    *reinterpret_cast<uint2*>(a.c_limbs + 2 * a.c_limb_plane + at) = make_uint2(l2[0] | ((uint32_t)l2[1] << 16), l2[2] | ((uint32_t)l2[3] << 16));
+        for (int it = 0; it < 8; ++it) {
+            const int lr = it * 4 + sub_r, row = m0 + wq * 32 + lr;
+            if (!col_ok || row >= a.M) continue;
+            const float* sp = stage + lr * 33 + sub_c;
+            float4 o = make_float4(sp[0], sp[1], sp[2], sp[3]);
+            if (EPI == TCB_DECAY) {
+                const float4 x = prev[it];
+                o = make_float4(add(mul(x.x, g.x), o.x), add(mul(x.y, g.y), o.y), add(mul(x.z, g.z), o.z), add(mul(x.w, g.w), o.w));
+            }
+            *reinterpret_cast<float4*>(cbase + (size_t)row * a.ldc + c) = o;
+            if (EPI == TCB_DECAY) {
+                // the new value's three limbs, in the operand layout of the product that reads it next: [limb][batch * M][N]
+                const float ov[4] = {o.x, o.y, o.z, o.w};
+                uint16_t l0[4], l1[4], l2[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    l0[q] = f_to_bf16(ov[q]);
+                    const float r1 = sub(ov[q], bf16_to_f(l0[q]));
+                    l1[q] = f_to_bf16(r1);
+                    l2[q] = f_to_bf16(sub(r1, bf16_to_f(l1[q])));
                 }
+                const size_t at = ((size_t)bz * a.M + row) * a.N + c;
+                *reinterpret_cast<uint2*>(a.c_limbs + at) = make_uint2(l0[0] | ((uint32_t)l0[1] << 16), l0[2] | ((uint32_t)l0[3] << 16));
+                *reinterpret_cast<uint2*>(a.c_limbs + a.c_limb_plane + at) = make_uint2(l1[0] | ((uint32_t)l1[1] << 16), l1[2] | ((uint32_t)l1[3] << 16));
+                *reinterpret_cast<uint2*>(a.c_limbs + 2 * a.c_limb_plane + at) = make_uint2(l2[0] | ((uint32_t)l2[1] << 16), l2[2] | ((uint32_t)l2[3] << 16));
             }
         }
     }
@@ -251,6 +269,7 @@ bool launch_one(cudaStream_t st, const TcbArgs& a) {
     if (!make_map(&ma, a.a, (uint64_t)LA * a.rows_a, a.K, B_BM) || !make_map(&mb, a.b, (uint64_t)LB * a.rows_b, a.K, BN)) return false;
     const size_t smem = (size_t)STAGES * (LA * B_BM * B_BK * 2 + LB * BN * B_BK * 2) + (2 * STAGES + 1) * sizeof(uint64_t) + 16 + 1024;
     cudaFuncSetAttribute(tc_bgemm_kernel<BN, LA, LB, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    prefer_max_shared(reinterpret_cast<const void*>(tc_bgemm_kernel<BN, LA, LB, STAGES, EPI>), 100);
     dim3 grid((a.N + BN - 1) / BN, (a.M + B_BM - 1) / B_BM, a.batch);
     return launch_k(tc_bgemm_kernel<BN, LA, LB, STAGES, EPI>, grid, dim3(B_THREADS), smem, st, ma, mb, a) == cudaSuccess;
 }
@@ -260,6 +279,7 @@ bool launch_one(cudaStream_t st, const TcbArgs& a) {
 // false: shape not covered (K a multiple of 64, M a multiple of 128, N a multiple of 4) or no tensor-map encoder
 bool launch_tc_bgemm(cudaStream_t st, const TcbArgs& a, int epi) {
     if (a.K % B_BK || a.M % B_BM || a.N % 4 || a.batch < 1) return false;
+    // N 128: two stages of 96 KB, one block per SM (measured a little ahead of one stage with two blocks per SM)
     if (a.N % 128 == 0) return epi == TCB_DECAY ? launch_one<128, 3, 3, 2, TCB_DECAY>(st, a) : launch_one<128, 3, 3, 2, TCB_STORE>(st, a);
     return epi == TCB_DECAY ? launch_one<64, 3, 3, 3, TCB_DECAY>(st, a) : launch_one<64, 3, 3, 3, TCB_STORE>(st, a);
 }

@@ -21,14 +21,17 @@ __device__ __forceinline__ void pdl_enter() {
 }
 #endif
 
+extern thread_local cudaError_t g_launch_error;
 extern int g_pdl;  // 1: launch with the programmatic-serialization attribute (default; AVA_PDL=0 in the environment turns it off)
 
 // Every kernel asks for the same split of an SM's on-chip memory between shared memory and L1.  An SM cannot change the
 // split while blocks are resident on it, so kernels that ask for different splits do not run side by side on one SM: a
 // kernel of another stream then waits until the SM has drained, however much room is left (measured: a lane's RMS norm
 // waited 116 us for another lane's state pass to end).  With one preference for all, a lane's small kernels start beside
-// another lane's state pass.  A kernel that needs more than the preferred share still gets it.
-void prefer_max_shared(const void* kernel);
+// another lane's state pass.  A kernel that needs more than the preferred share still gets it.  percent_for_this >= 0
+// (given before the kernel's first launch) asks for another split for that kernel: the tensor-core kernels of prompt
+// reading, which run alone on their stream, take all of it so that two of their blocks share an SM.
+void prefer_max_shared(const void* kernel, int percent_for_this = -1);
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
@@ -43,7 +46,17 @@ inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    const cudaError_t rc = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (rc != cudaSuccess && g_launch_error == cudaSuccess) g_launch_error = rc;  // kept until take_launch_error reads it
+    return rc;
+}
+// The first launch that was refused on this thread since the last call (cudaSuccess: none), and forgets it.  The step
+// asks after queueing its kernels, so a refused launch (a grid too large, a kernel image that did not load) fails the
+// call instead of leaving a result that lacks one kernel's work.
+inline cudaError_t take_launch_error() {
+    const cudaError_t rc = g_launch_error;
+    g_launch_error = cudaSuccess;
+    return rc;
 }
 
 // Status word in device memory that kernels OR bits into; the host reads it when it reads the step's results.

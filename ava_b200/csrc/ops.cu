@@ -37,10 +37,12 @@ cudaError_t up(Tmp& t, const void* src, size_t bytes) {
 int begin(int device) {
     int n = 0;
     if (cudaGetDeviceCount(&n) != cudaSuccess || device < 0 || device >= n) return AVA_ERR_CUDA;
+    take_launch_error();  // what an earlier, failed call left
     return cudaSetDevice(device) == cudaSuccess ? AVA_OK : AVA_ERR_CUDA;
 }
 
 int end_() {
+    if (take_launch_error() != cudaSuccess) return AVA_ERR_CUDA;
     if (cudaGetLastError() != cudaSuccess) return AVA_ERR_CUDA;
     return cudaDeviceSynchronize() == cudaSuccess ? AVA_OK : AVA_ERR_CUDA;
 }

@@ -191,7 +191,8 @@ int ava_engine_set_lanes(ava_engine* e, int32_t lanes);
  * every product exact (the f32 activation as three bf16 limbs, the int8 weight exact in bf16), the f32 sum in the
  * tensor core's order instead of k = 0, 1, ...  The step's results then agree with the reference's to about 1e-6 of
  * each sum's magnitudes instead of bit for bit, and a membrane within that distance of its threshold can spike
- * differently.  The spike-driven products (W_out, W_2) keep the exact event sum.  Costs 2 bytes per dense weight of
+ * differently.  W_out, driven by spikes, keeps the exact event sum, and so does W_2 in a decode step; over a prompt
+ * chunk of 1024 token-rows or more W_2 is multiplied densely on the tensor cores too.  Costs 2 bytes per dense weight of
  * device memory on first use.  Call after ava_engine_finalize, between steps. */
 int ava_engine_set_fast_products(ava_engine* e, int32_t on);
 /* With fast products on, a prompt chunk whose length is a multiple of 64 (head size a multiple of 128, no momentum)

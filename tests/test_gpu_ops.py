@@ -138,6 +138,21 @@ def test_event_sum_bits_many_rows(orc, m, din, dout, density):
     assert not np.isnan(got[:m - 1]).any()
 
 
+def test_event_sum_more_rows_than_a_grid_dimension(orc):
+    """70000 token-rows (a long prompt chunk of many sequences): more than one grid dimension holds (65535), so the
+    rows go on in a second one; first, middle and last rows against the oracle, all rows against the dense kernel."""
+    rng = np.random.default_rng(70000)
+    m, din, dout = 70000, 64, 64
+    q = rng.integers(-127, 128, (din, dout)).astype(np.int8)
+    sc = (rng.uniform(0.5, 1.5, dout) / 127).astype(np.float32)
+    x = (rng.integers(-2, 3, (m, din)) * (rng.random((m, din)) < 0.3)).astype(np.float32)
+    got = engine.op_q8_matmul(x, q, sc, event=True)
+    dense = engine.op_q8_matmul(x, q, sc, event=False)
+    assert np.array_equal(bits(got), bits(dense))
+    pick = np.r_[0:4, 32766:32770, 65534:65538, m - 3:m]
+    assert np.array_equal(bits(got[pick]), bits(orc.q8_matmul(x[pick], q, sc)))
+
+
 @pytest.mark.parametrize("m,n", [(1, 64), (7, 768), (300, 2048)])
 def test_rmsnorm_bits(orc_same_math, m, n):
     rng = np.random.default_rng(n)
