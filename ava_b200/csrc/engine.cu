@@ -163,7 +163,7 @@ struct ava_engine : Work {
 
     bool fast = false;     // dense products on the tensor cores (exact products, the tensor core's summation order)
     bool chunk_mem = true; // with fast: a prompt chunk's fast-weight memory in the chunk-parallel form (k_chunk.cu)
-    int64_t chunked_blocks = 0, chunk_fallbacks = 0;
+    int64_t chunked_blocks = 0, chunk_fallbacks = 0, chunked_reads = 0;
     Dev limbs;             // [3][rows][d] bf16 limbs of the current product's input
     const float* limbs_src = nullptr;  // the f32 buffer whose limbs the producing kernel has just written there
     int limbs_rows = 0;
@@ -821,7 +821,24 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
                 const size_t need = (size_t)rows * enh * n_seg * (2 + c.eng_head_size) * sizeof(float);
                 if (w.eng_partial.bytes < need) CK(w.eng_partial.alloc(need));
             }
-            for (int t = 0; t < T && phase == PHASE_ALL; ++t) {
+            // the tolerance mode reads a prompt chunk in one causal pass on the tensor cores, when the store neither wraps
+            // nor trims inside the chunk (head size 64, bf16 store)
+            bool chunk_read = e->fast && e->chunk_mem && T > 1 && phase == PHASE_ALL && !e->keep && c.eng_store_bf16 && c.eng_head_size == 64 &&
+                              s->keep == s->ring;
+            for (int r = r0; r < r0 + rows && chunk_read; ++r) chunk_read = s->start_host[r] + s->n_host[r] + T <= s->ring;
+            if (chunk_read) {
+                EngramChunkArgs ca{};
+                ca.qkv = w.eqkv.as<float>(); ca.o = w.eo.as<float>(); ca.k = ea.k; ca.v = ea.v; ca.n = ea.n; ca.start = ea.start;
+                ca.M = rows; ca.d = d; ca.hs = c.eng_head_size; ca.cap = s->ring; ca.T = T; ca.bf16 = 1; ca.status = ea.status;
+                prof_begin(e, "engram.chunk");
+                chunk_read = launch_engram_chunk(st, ca);
+                prof_end(e);
+                if (chunk_read) {
+                    e->launches += 2;
+                    ++e->chunked_reads;
+                }
+            }
+            for (int t = 0; t < T && phase == PHASE_ALL && !chunk_read; ++t) {
                 ea.qkv = w.eqkv.as<float>() + (size_t)t * rows * 3 * d;
                 ea.o = w.eo.as<float>() + (size_t)t * Rd;
                 if (!segmented) {
@@ -2026,10 +2043,11 @@ int ava_engine_set_chunked_memory(ava_engine* e, int32_t on) {
     return AVA_OK;
 }
 
-int ava_engine_chunked_memory_counts(const ava_engine* e, int64_t* chunked, int64_t* token_loop) {
-    if (!e || !chunked || !token_loop) return AVA_ERR_ARG;
+int ava_engine_chunked_memory_counts(const ava_engine* e, int64_t* chunked, int64_t* token_loop, int64_t* engram_chunks) {
+    if (!e || !chunked || !token_loop || !engram_chunks) return AVA_ERR_ARG;
     *chunked = e->chunked_blocks;
     *token_loop = e->chunk_fallbacks;
+    *engram_chunks = e->chunked_reads;
     return AVA_OK;
 }
 

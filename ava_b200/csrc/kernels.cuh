@@ -324,6 +324,21 @@ bool engram_fits_one_block(int d, int hs, int n_max);
 bool launch_engram_partial(cudaStream_t st, const EngramArgs& a, int seg_len, int n_seg, float* partial);
 void launch_engram_combine(cudaStream_t st, const float* partial, int M, int nh, int hs, int n_part, float* o, int n_groups = 1);
 
+// The engram over a whole prompt chunk on the tensor cores (k_eattn.cu): the chunk's T keys and values join the store,
+// every token's causal read, the counts move on by T.  qkv [T][M][3 d] and o [T][M][d] are time-major; the store must
+// not wrap or trim inside the chunk (start + n + T <= cap for every row: the caller checks on its mirror of the counts).
+struct EngramChunkArgs {
+    const float* qkv;
+    float* o;
+    void* k;             // [M, heads, cap, hs] bf16
+    void* v;
+    int32_t* n;
+    int32_t* start;
+    int M, d, hs, cap, T, bf16;
+    uint32_t* status;
+};
+bool launch_engram_chunk(cudaStream_t st, const EngramChunkArgs& a);
+
 void launch_kwta(cudaStream_t st, const float* u, int M, int n, int k, int relu2, float* a);
 // x <- x + sum_j streams[j] * w[j] over the n_streams streams (the last one is x itself, stored first)
 void launch_dense_mix(cudaStream_t st, float* x, float* streams, const float* w, int n_streams, int64_t MD);

@@ -344,6 +344,49 @@ int ava_debug_mem_heads_wait_runs_out(int device, int32_t m, int32_t hs, int32_t
     return (st & ST_WAIT_TIMEOUT) ? AVA_ERR_CUDA : AVA_OK;
 }
 
+/* The engram's causal read over a whole chunk on the tensor cores, alone (head size 64, bf16 store).  rows stores, each
+ * holding n0 tokens already (k_prev, v_prev [rows][d / 64][n0][64], rounded to bf16 as the store keeps them) from ring
+ * slot `start` on; then t tokens whose q | k | v are qkv [t][rows][3 d]: their keys and values join the store and
+ * o [t][rows][d] gets every token's read over the keys up to and including its own. */
+int ava_op_engram_chunk(int device, int32_t rows, int32_t t, int32_t n0, int32_t start, int32_t d, const float* qkv, const float* k_prev,
+                        const float* v_prev, float* o) {
+    if (!qkv || !o || rows <= 0 || t <= 0 || n0 < 0 || start < 0 || d <= 0 || (n0 > 0 && (!k_prev || !v_prev))) return AVA_ERR_ARG;
+    if (d % 64) return AVA_NOT_APPLICABLE;
+    int rc = begin(device);
+    if (rc) return rc;
+    const int nh = d / 64, cap = start + n0 + t + 5;  // a few slots never written: their bytes must not matter
+    const size_t store = (size_t)rows * nh * cap * 64;
+    std::vector<uint16_t> ks(store, 0x7fc0), vs(store, 0x7fc0);  // NaN patterns wherever nothing is stored
+    for (int r = 0; r < rows; ++r)
+        for (int hh = 0; hh < nh; ++hh)
+            for (int j = 0; j < n0; ++j)
+                for (int x = 0; x < 64; ++x) {
+                    const size_t src = (((size_t)r * nh + hh) * n0 + j) * 64 + x, dst = (((size_t)r * nh + hh) * cap + start + j) * 64 + x;
+                    ks[dst] = f_to_bf16(k_prev[src]);
+                    vs[dst] = f_to_bf16(v_prev[src]);
+                }
+    std::vector<int32_t> hn(rows, n0), hs_(rows, start);
+    Tmp dq, dk, dv, dn, dstart, dout, dst;
+    OCK(up(dq, qkv, (size_t)t * rows * 3 * d * 4));
+    OCK(up(dk, ks.data(), store * 2)); OCK(up(dv, vs.data(), store * 2));
+    OCK(up(dn, hn.data(), rows * 4)); OCK(up(dstart, hs_.data(), rows * 4));
+    OCK(up(dout, nullptr, (size_t)t * rows * d * 4)); OCK(up(dst, nullptr, 4));
+    OCK(cudaMemset(dst.p, 0, 4));
+    EngramChunkArgs a{};
+    a.qkv = dq.as<float>(); a.o = dout.as<float>(); a.k = dk.p; a.v = dv.p; a.n = dn.as<int32_t>(); a.start = dstart.as<int32_t>();
+    a.M = rows; a.d = d; a.hs = 64; a.cap = cap; a.T = t; a.bf16 = 1; a.status = dst.as<uint32_t>();
+    if (!launch_engram_chunk(0, a)) return AVA_NOT_APPLICABLE;
+    if ((rc = end_())) return rc;
+    uint32_t st = 0;
+    OCK(cudaMemcpy(&st, dst.p, 4, cudaMemcpyDeviceToHost));
+    if (st) return AVA_ERR_CUDA;
+    OCK(cudaMemcpy(hn.data(), dn.p, rows * 4, cudaMemcpyDeviceToHost));
+    for (int r = 0; r < rows; ++r)
+        if (hn[r] != n0 + t) return AVA_ERR_CUDA;
+    OCK(cudaMemcpy(o, dout.p, (size_t)t * rows * d * 4, cudaMemcpyDeviceToHost));
+    return AVA_OK;
+}
+
 int ava_op_attend(int device, int32_t m, int32_t n, int32_t hs, int32_t bf16_store, const float* q, const float* kc, const float* vc, float* out) {
     if (!q || !kc || !vc || !out || m <= 0 || n <= 0 || hs <= 0) return AVA_ERR_ARG;
     int rc = begin(device);

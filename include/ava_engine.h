@@ -195,14 +195,19 @@ int ava_engine_set_lanes(ava_engine* e, int32_t lanes);
  * chunk of 1024 token-rows or more W_2 is multiplied densely on the tensor cores too.  Costs 2 bytes per dense weight of
  * device memory on first use.  Call after ava_engine_finalize, between steps. */
 int ava_engine_set_fast_products(ava_engine* e, int32_t on);
-/* With fast products on, a prompt chunk whose length is a multiple of 64 (head size a multiple of 128, no momentum)
- * reads the fast-weight memory in its chunk-parallel form on the tensor cores (`delta_chunk`,
- * design-tests/nn/gpu/src/arch.rs:1151-1173, 1243-1327), which agrees with the token loop to rounding (the reference's
- * bound for it: 1e-4 of max(1, max|ref|)); a block whose rates forget faster than e^-60 inside 64 tokens falls back to
- * the token loop for that chunk.  on = 0 keeps the token loop everywhere (default: on).  ava_engine_chunked_memory_counts
- * reports how many (block, chunk) passes took each form since the engine was made. */
+/* With fast products on, a prompt chunk reads its two recurrent memories in chunk-parallel forms on the tensor cores
+ * (on = 0 keeps the token loops; default on):
+ *   the fast-weight memory, when the chunk's length is a multiple of 64, the head size a multiple of 128 and there is no
+ *     momentum: `delta_chunk` (design-tests/nn/gpu/src/arch.rs:1151-1173, 1243-1327), which agrees with the token loop
+ *     to rounding (the reference's bound for it: 1e-4 of max(1, max|ref|)); a block whose rates forget faster than e^-60
+ *     inside 64 tokens falls back to the token loop for that chunk;
+ *   the engram, when its head size is 64, the store is bf16 and neither wraps nor trims inside the chunk: the chunk's
+ *     keys and values join the store, then one causal pass reads every token (no counterpart in the reference, which
+ *     reads once per token: src/model/fstep.rs:303-356); agrees with the one-token read to rounding.
+ * ava_engine_chunked_memory_counts reports, since the engine was made, the (block, chunk) passes of the fast-weight memory
+ * that took the chunk form and that fell back, and the chunks whose engram read took the causal pass. */
 int ava_engine_set_chunked_memory(ava_engine* e, int32_t on);
-int ava_engine_chunked_memory_counts(const ava_engine* e, int64_t* chunked, int64_t* token_loop);
+int ava_engine_chunked_memory_counts(const ava_engine* e, int64_t* chunked, int64_t* token_loop, int64_t* engram_chunks);
 
 /* ---- one long sequence with its engram store split by position over several GPUs ------------------------------
  * No counterpart in the reference (one device, src/memory.rs:664-692).  Each GPU runs one process with its own engine
@@ -398,6 +403,13 @@ const char* ava_static_last_error(void);
 int ava_op_attend(int device, int32_t m, int32_t n, int32_t hs, int32_t bf16_store, const float* q, const float* kc,
                   const float* vc, float* out);
 
+/* No counterpart in the reference (it reads the engram once per token, src/model/fstep.rs:303-356).  The causal read of
+ * a whole chunk on the tensor cores, alone, on host buffers: `rows` stores of head size 64 kept in bf16, each holding n0
+ * tokens (k_prev, v_prev [rows][d / 64][n0][64]) from ring slot `start` on; t tokens with qkv [t][rows][3 d] join them and
+ * o [t][rows][d] gets each token's softmax(K q / 8) V over the keys up to and including its own.  Agrees with the
+ * one-token read to rounding.  d % 64 != 0: AVA_NOT_APPLICABLE. */
+int ava_op_engram_chunk(int device, int32_t rows, int32_t t, int32_t n0, int32_t start, int32_t d, const float* qkv, const float* k_prev,
+                        const float* v_prev, float* o);
 /* No counterpart in the reference (its chunked memory multiplies with its tensor library's matmul,
  * src/arch.rs:1243-1327).  The batched limb product of the chunked memory alone, on host buffers: c[b] = a[b] . b[b]^T
  * (a [batch][m][k], b [batch][n][k], c [batch][m][n]); with colscale [batch][n], c = colscale[b][n] * c + a . b^T and

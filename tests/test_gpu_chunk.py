@@ -72,3 +72,37 @@ def test_chunked_memory_refuses_rates_outside_its_range():
     y, f1, oor = engine.op_mem_chunk(q, e, k * b, e * (b * np.exp(la)), v, la, f0)
     assert oor
     assert np.array_equal(f1, f0) and not y.any()
+
+
+def _bf16_round(x):
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    return u.astype(np.uint32).view(np.float32)
+
+
+@pytest.mark.parametrize("rows,t,n0,start,heads", [(1, 64, 0, 0, 1), (2, 200, 37, 3, 2), (1, 256, 300, 0, 3), (3, 130, 1000, 11, 1)])
+def test_engram_chunk_read_is_the_causal_softmax(rows, t, n0, start, heads):
+    """The causal read of a whole chunk (tensor cores, two passes, keys in tiles of 64) against float64: token i sees
+    the n0 keys held before the chunk and the chunk's keys 0 .. i, all as the store keeps them (bf16).  Chunk lengths
+    that do and do not fill a tile of 128 queries, stores that start inside the ring, never-written slots full of NaN."""
+    rng = np.random.default_rng(rows + t + n0 + heads)
+    d = 64 * heads
+    qkv = rng.normal(size=(t, rows, 3 * d)).astype(np.float32)
+    qkv[:, :, :d] *= 3.0   # sharp scores: a few keys carry most of a row's weight
+    kp = rng.normal(size=(rows, heads, n0, 64)).astype(np.float32)
+    vp = rng.normal(size=(rows, heads, n0, 64)).astype(np.float32)
+    got = engine.op_engram_chunk(qkv, kp, vp, start=start)
+    worst = 0.0
+    for r in range(rows):
+        for h in range(heads):
+            q = qkv[:, r, h * 64:(h + 1) * 64].astype(np.float64)
+            k = np.concatenate([_bf16_round(kp[r, h]), _bf16_round(qkv[:, r, d + h * 64:d + (h + 1) * 64])]).astype(np.float64)
+            v = np.concatenate([_bf16_round(vp[r, h]), _bf16_round(qkv[:, r, 2 * d + h * 64:2 * d + (h + 1) * 64])]).astype(np.float64)
+            s = q @ k.T / 8.0
+            vis = np.arange(n0 + t)[None, :] <= (n0 + np.arange(t))[:, None]
+            s = np.where(vis, s, -np.inf)
+            p = np.exp(s - s.max(axis=1, keepdims=True))
+            want = (p / p.sum(axis=1, keepdims=True)) @ v
+            worst = max(worst, float(np.abs(got[:, r, h * 64:(h + 1) * 64] - want).max()) / max(1.0, float(np.abs(want).max())))
+    print("engram chunk read against float64:", worst)
+    assert worst <= 2e-5

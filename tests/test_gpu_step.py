@@ -571,7 +571,7 @@ def test_chunked_memory_in_the_prompt_pass(orc_same_math, shape):
     import torch
     orc = orc_same_math
     if shape == "small":
-        cfg = config.make(64, 128, 2, head_size=128, eng_block=1, eng_head_size=32)
+        cfg = config.make(64, 128, 2, head_size=128, eng_block=1, eng_head_size=64, eng_store_bf16=1)
         rows, tokens, chunk, recipe = 3, 256, 128, "awake"
     else:
         cfg, rows, tokens, chunk, recipe = config.ava04_shaped(), 2, 256, 128, "bench"
@@ -591,12 +591,17 @@ def test_chunked_memory_in_the_prompt_pass(orc_same_math, shape):
         gm.prefill_device(gs, tok.data_ptr(), tokens, chunk, logits.data_ptr(), None)
         gm.sync()
         after = gm.chunked_memory_counts()
-        out[on] = (logits.cpu().numpy(), [gs.get(r, "mem.0.f") for r in range(rows)], (after[0] - before[0], after[1] - before[1]))
+        out[on] = (logits.cpu().numpy(), [gs.get(r, "mem.0.f") for r in range(rows)], (after[0] - before[0], after[1] - before[1]), after[2] - before[2],
+                   [gs.get(r, "eng.k") for r in range(rows)])
     gm.set_chunked_memory(True)
     gm.set_fast_products(False)
     passes = cfg["n_blocks"] * (tokens // chunk)
     print("chunked memory passes (chunk form, token loop):", out[True][2], "of", passes)
-    assert out[False][2] == (0, 0)
+    assert out[False][2] == (0, 0) and out[False][3] == 0
+    assert out[True][3] == tokens // chunk   # every chunk's engram read took the causal pass
+    for a, b in zip(out[True][4], out[False][4]):
+        if shape == "small":   # same inputs up to the engram's block when no spike tipped: the stored keys are the same bf16
+            assert float(np.abs(a - b).max()) <= 1e-2 * max(1.0, float(np.abs(b).max()))
     assert sum(out[True][2]) == passes and out[True][2][0] > 0
     worst = 0.0
     for a, b in zip(out[True][1], out[False][1]):
