@@ -666,6 +666,7 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
         mp.qg = w.vqg.as<float>(); mp.ex = w.vex.as<float>(); mp.qw = w.qw.as<float>(); mp.qa = w.qa.as<float>();
         mp.qs = c.mem_momentum > 0.0f ? w.vqs.as<float>() : nullptr;
         mp.mom = c.mem_momentum;
+        mp.fast = e->fast && !e->keep;
         // One token of the plain memory takes the streaming pass: this token's alpha, w, ah and values go straight into
         // the state's pending set (the one this step writes), the pass reads the set the step before wrote.
         const bool stream = T == 1 && !(c.mem_momentum > 0.0f);
@@ -742,10 +743,10 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
             uint32_t out_of_range = 0;
             CK(cudaMemcpyAsync(&out_of_range, ca.flags, sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
             CK(cudaStreamSynchronize(st));
-            e->launches += 1;
+            e->launches += 3;
             if (!(out_of_range & 1u)) {
                 if (!launch_mem_chunk_rest(st, ca)) return e->fail(AVA_ERR_CUDA, "chunk-parallel memory: a launch was refused");
-                e->launches += mem_chunk_launches(ca.nC) - 2;
+                e->launches += mem_chunk_launches(ca.nC) - 4;
                 chunked = true;
                 ++e->chunked_blocks;
             } else {

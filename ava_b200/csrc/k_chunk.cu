@@ -42,61 +42,115 @@ __device__ __forceinline__ void limbs3(float x, uint16_t& l0, uint16_t& l1, uint
     l2 = f_to_bf16(r1 - bf16_to_f(l1));
 }
 
-// ---- scaling: one thread per (chunk, head, channel), the chunk's 64 tokens in order ------------------------------
-__global__ void __launch_bounds__(256) chunk_scale_kernel(const ChunkArgs a) {
+// ---- scaling, in three kernels ------------------------------------------------------------------------------------
+// (1) the running sums of the log rates: one thread per (chunk, head, channel), the chunk's 64 tokens in order
+__global__ void __launch_bounds__(256) chunk_scan_kernel(const ChunkArgs a) {
     pdl_enter();
     const int H = a.hs, ch = blockIdx.x * blockDim.x + threadIdx.x;
     if (ch >= H) return;
     const int u = blockIdx.y, j = u / a.HB, hb = u % a.HB;  // u = j * HB + hb
     const size_t in0 = (size_t)j * CC * a.tok_stride + (size_t)hb * H + ch;
-    const size_t P128 = (size_t)a.nC * a.HB * 128 * H;     // plane of QE / WA / A3
-    const size_t PT = (size_t)a.nC * a.HB * H * 128;       // plane of A5 / B5
-    const size_t row128 = (size_t)u * 128, rowT = ((size_t)u * H + ch) * 128;
     float cum = 0.0f, mincum = 0.0f;
-    for (int i = 0; i < CC; ++i) {
-        const size_t at = in0 + (size_t)i * a.tok_stride;
-        const float la = a.la[at], cumex = cum;
-        cum += la;
-        mincum = fminf(mincum, cum);
-        const float up = __expf(cum), upx = __expf(cumex), dn = __expf(-cum);
-        const float qs = a.qn[at] * up, es = a.e[at] * upx, ws = a.w[at] * dn, as = a.ah[at] * dn;
-        uint16_t l0, l1, l2;
-        const size_t o_top = (row128 + i) * H + ch, o_bot = (row128 + 64 + i) * H + ch;
-        limbs3(qs, l0, l1, l2);
-        a.QE[o_top] = l0; a.QE[P128 + o_top] = l1; a.QE[2 * P128 + o_top] = l2;
-        a.A3[o_bot] = l0; a.A3[P128 + o_bot] = l1; a.A3[2 * P128 + o_bot] = l2;
-        limbs3(es, l0, l1, l2);
-        a.QE[o_bot] = l0; a.QE[P128 + o_bot] = l1; a.QE[2 * P128 + o_bot] = l2;
-        a.ES[((size_t)u * 64 + i) * H + ch] = es;
-        limbs3(ws, l0, l1, l2);
-        a.WA[o_top] = l0; a.WA[P128 + o_top] = l1; a.WA[2 * P128 + o_top] = l2;
-        limbs3(as, l0, l1, l2);
-        a.WA[o_bot] = l0; a.WA[P128 + o_bot] = l1; a.WA[2 * P128 + o_bot] = l2;
-    }
-    if (mincum < -60.0f || !(cum == cum)) atomicOr(a.flags, 1u);
-    const float cl = cum;
-    a.gc[(size_t)u * H + ch] = __expf(cl);
-    // the keys decayed to the chunk's end, and the values, as rows of 128 token slots (this channel's row)
-    cum = 0.0f;
     for (int i8 = 0; i8 < CC; i8 += 8) {
-        uint16_t wl[3][8], al[3][8], vv[3][8];
+        float la[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) la[q] = __ldg(a.la + in0 + (size_t)(i8 + q) * a.tok_stride);
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
-            const size_t at = in0 + (size_t)(i8 + q) * a.tok_stride;
-            cum += a.la[at];
-            const float kk = __expf(cl - cum);
-            limbs3(a.w[at] * kk, wl[0][q], wl[1][q], wl[2][q]);
-            limbs3(a.ah[at] * kk, al[0][q], al[1][q], al[2][q]);
-            limbs3(a.v[at], vv[0][q], vv[1][q], vv[2][q]);
-        }
-#pragma unroll
-        for (int p = 0; p < 3; ++p) {
-            auto pack = [](const uint16_t* s) { return make_uint4(s[0] | ((uint32_t)s[1] << 16), s[2] | ((uint32_t)s[3] << 16), s[4] | ((uint32_t)s[5] << 16), s[6] | ((uint32_t)s[7] << 16)); };
-            *reinterpret_cast<uint4*>(a.B5 + p * PT + rowT + i8) = pack(wl[p]);
-            *reinterpret_cast<uint4*>(a.B5 + p * PT + rowT + 64 + i8) = pack(al[p]);
-            *reinterpret_cast<uint4*>(a.A5 + p * PT + rowT + i8) = pack(vv[p]);
+            cum += la[q];
+            mincum = fminf(mincum, cum);
+            a.CUM[((size_t)u * 64 + i8 + q) * H + ch] = cum;
         }
     }
+    if (mincum < -60.0f || !(cum == cum)) atomicOr(a.flags, 1u);
+    a.gc[(size_t)u * H + ch] = __expf(cum);
+}
+
+__device__ __forceinline__ void limbs3x4(const float4 x, uint2& p0, uint2& p1, uint2& p2) {
+    uint16_t l[3][4];
+    limbs3(x.x, l[0][0], l[1][0], l[2][0]);
+    limbs3(x.y, l[0][1], l[1][1], l[2][1]);
+    limbs3(x.z, l[0][2], l[1][2], l[2][2]);
+    limbs3(x.w, l[0][3], l[1][3], l[2][3]);
+    p0 = make_uint2(l[0][0] | ((uint32_t)l[0][1] << 16), l[0][2] | ((uint32_t)l[0][3] << 16));
+    p1 = make_uint2(l[1][0] | ((uint32_t)l[1][1] << 16), l[1][2] | ((uint32_t)l[1][3] << 16));
+    p2 = make_uint2(l[2][0] | ((uint32_t)l[2][1] << 16), l[2][2] | ((uint32_t)l[2][3] << 16));
+}
+
+// (2) the scaled rows, token-major: one thread per (chunk, head, token, four channels)
+__global__ void __launch_bounds__(256) chunk_scale_kernel(const ChunkArgs a) {
+    pdl_enter();
+    const int H = a.hs, H4 = H / 4;
+    const size_t n = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= (size_t)a.nC * a.HB * 64 * H4) return;
+    const int c4 = (int)(n % H4) * 4, i = (int)((n / H4) % 64), u = (int)(n / ((size_t)H4 * 64)), j = u / a.HB, hb = u % a.HB;
+    const size_t at = (size_t)(j * CC + i) * a.tok_stride + (size_t)hb * H + c4;
+    const float4 q = *reinterpret_cast<const float4*>(a.qn + at), e = *reinterpret_cast<const float4*>(a.e + at);
+    const float4 w = *reinterpret_cast<const float4*>(a.w + at), ah = *reinterpret_cast<const float4*>(a.ah + at);
+    const float4 cum = *reinterpret_cast<const float4*>(a.CUM + ((size_t)u * 64 + i) * H + c4);
+    const float4 cumex = i > 0 ? *reinterpret_cast<const float4*>(a.CUM + ((size_t)u * 64 + i - 1) * H + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 up = make_float4(__expf(cum.x), __expf(cum.y), __expf(cum.z), __expf(cum.w));
+    const float4 upx = make_float4(__expf(cumex.x), __expf(cumex.y), __expf(cumex.z), __expf(cumex.w));
+    const float4 dn = make_float4(__expf(-cum.x), __expf(-cum.y), __expf(-cum.z), __expf(-cum.w));
+    const float4 qs = make_float4(q.x * up.x, q.y * up.y, q.z * up.z, q.w * up.w), es = make_float4(e.x * upx.x, e.y * upx.y, e.z * upx.z, e.w * upx.w);
+    const float4 ws = make_float4(w.x * dn.x, w.y * dn.y, w.z * dn.z, w.w * dn.w), as = make_float4(ah.x * dn.x, ah.y * dn.y, ah.z * dn.z, ah.w * dn.w);
+    const size_t P128 = (size_t)a.nC * a.HB * 128 * H;
+    const size_t o_top = ((size_t)u * 128 + i) * H + c4, o_bot = ((size_t)u * 128 + 64 + i) * H + c4;
+    uint2 p0, p1, p2;
+    limbs3x4(qs, p0, p1, p2);
+    *reinterpret_cast<uint2*>(a.QE + o_top) = p0; *reinterpret_cast<uint2*>(a.QE + P128 + o_top) = p1; *reinterpret_cast<uint2*>(a.QE + 2 * P128 + o_top) = p2;
+    *reinterpret_cast<uint2*>(a.A3 + o_bot) = p0; *reinterpret_cast<uint2*>(a.A3 + P128 + o_bot) = p1; *reinterpret_cast<uint2*>(a.A3 + 2 * P128 + o_bot) = p2;
+    limbs3x4(es, p0, p1, p2);
+    *reinterpret_cast<uint2*>(a.QE + o_bot) = p0; *reinterpret_cast<uint2*>(a.QE + P128 + o_bot) = p1; *reinterpret_cast<uint2*>(a.QE + 2 * P128 + o_bot) = p2;
+    *reinterpret_cast<float4*>(a.ES + ((size_t)u * 64 + i) * H + c4) = es;
+    limbs3x4(ws, p0, p1, p2);
+    *reinterpret_cast<uint2*>(a.WA + o_top) = p0; *reinterpret_cast<uint2*>(a.WA + P128 + o_top) = p1; *reinterpret_cast<uint2*>(a.WA + 2 * P128 + o_top) = p2;
+    limbs3x4(as, p0, p1, p2);
+    *reinterpret_cast<uint2*>(a.WA + o_bot) = p0; *reinterpret_cast<uint2*>(a.WA + P128 + o_bot) = p1; *reinterpret_cast<uint2*>(a.WA + 2 * P128 + o_bot) = p2;
+}
+
+// (3) the keys decayed to the chunk's end, and the values, channel-major (rows of the 128 token slots): one block per
+// (chunk, head, 64 channels), the 64 x 64 pieces turned round in shared memory.  grid (H / 64, nC * HB), 256 threads
+__global__ void __launch_bounds__(256) chunk_keys_kernel(const ChunkArgs a) {
+    pdl_enter();
+    __shared__ float Ws[64][65], As[64][65];
+    const int H = a.hs, u = blockIdx.y, j = u / a.HB, hb = u % a.HB, c0 = blockIdx.x * 64, tid = threadIdx.x;
+    const int ch = tid >> 2, i0 = (tid & 3) * 16;   // when writing: thread = (channel, sixteen tokens)
+    const size_t PT = (size_t)a.nC * a.HB * H * 128;
+    const size_t rowT = ((size_t)u * H + c0 + ch) * 128 + i0;
+    auto put = [&](const float (*S)[65], uint16_t* dst) {
+#pragma unroll
+        for (int h8 = 0; h8 < 16; h8 += 8) {
+            uint16_t l[3][8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) limbs3(S[i0 + h8 + q][ch], l[0][q], l[1][q], l[2][q]);
+#pragma unroll
+            for (int p = 0; p < 3; ++p)
+                *reinterpret_cast<uint4*>(dst + p * PT + h8) =
+                    make_uint4(l[p][0] | ((uint32_t)l[p][1] << 16), l[p][2] | ((uint32_t)l[p][3] << 16), l[p][4] | ((uint32_t)l[p][5] << 16), l[p][6] | ((uint32_t)l[p][7] << 16));
+        }
+    };
+    for (int n = tid; n < 64 * 16; n += 256) {
+        const int i = n >> 4, c4 = (n & 15) * 4;
+        const size_t at = (size_t)(j * CC + i) * a.tok_stride + (size_t)hb * H + c0 + c4;
+        const float4 w = *reinterpret_cast<const float4*>(a.w + at), ah = *reinterpret_cast<const float4*>(a.ah + at);
+        const float4 cum = *reinterpret_cast<const float4*>(a.CUM + ((size_t)u * 64 + i) * H + c0 + c4);
+        const float4 cl = *reinterpret_cast<const float4*>(a.CUM + ((size_t)u * 64 + 63) * H + c0 + c4);
+        const float k0 = __expf(cl.x - cum.x), k1 = __expf(cl.y - cum.y), k2 = __expf(cl.z - cum.z), k3 = __expf(cl.w - cum.w);
+        Ws[i][c4] = w.x * k0; Ws[i][c4 + 1] = w.y * k1; Ws[i][c4 + 2] = w.z * k2; Ws[i][c4 + 3] = w.w * k3;
+        As[i][c4] = ah.x * k0; As[i][c4 + 1] = ah.y * k1; As[i][c4 + 2] = ah.z * k2; As[i][c4 + 3] = ah.w * k3;
+    }
+    __syncthreads();
+    put(Ws, a.B5 + rowT);
+    put(As, a.B5 + rowT + 64);
+    __syncthreads();
+    for (int n = tid; n < 64 * 16; n += 256) {   // the values, through the first square again
+        const int i = n >> 4, c4 = (n & 15) * 4;
+        const float4 v = *reinterpret_cast<const float4*>(a.v + (size_t)(j * CC + i) * a.tok_stride + (size_t)hb * H + c0 + c4);
+        Ws[i][c4] = v.x; Ws[i][c4 + 1] = v.y; Ws[i][c4 + 2] = v.z; Ws[i][c4 + 3] = v.w;
+    }
+    __syncthreads();
+    put(Ws, a.A5 + rowT);
 }
 
 // ---- the four 64x64 matrices of a chunk and the inverse: one block of 256 threads per (chunk, head) --------------
@@ -140,41 +194,47 @@ __global__ void __launch_bounds__(256) chunk_solve_kernel(const ChunkArgs a) {
 }
 
 // ---- D [64 x cols] = Mx [64 x 64] . Xin [64 x cols] per (chunk, head): p1 = T es (as limbs), r0 = (T Ke) v, qwv = Qw v -----
-// grid (H / 128, nC * HB, 3); 256 threads: thread (r4, c8) owns rows r4 * 4 .. + 3 and columns c8 * 8 .. + 7 of the tile
-__global__ void __launch_bounds__(256) chunk_small_kernel(const ChunkArgs a) {
+// grid (H / 128, nC * HB, 3); 128 threads: thread (r8, c8) owns rows r8 * 8 .. + 7 and columns c8 * 8 .. + 7 of the tile
+// (an 8 x 8 register tile: four 16-byte reads of shared memory per 64 multiply-adds)
+__device__ __forceinline__ void tile_mm_8x8(const float (*Mt)[64], const float (*Xs)[128], int r8, int c8, float (&acc)[8][8]) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[i][q] = 0.0f;
+#pragma unroll 4
+    for (int k = 0; k < 64; ++k) {
+        const float4 x0 = *reinterpret_cast<const float4*>(&Xs[k][c8 * 8]), x1 = *reinterpret_cast<const float4*>(&Xs[k][c8 * 8 + 4]);
+        const float4 m0 = *reinterpret_cast<const float4*>(&Mt[k][r8 * 8]), m1 = *reinterpret_cast<const float4*>(&Mt[k][r8 * 8 + 4]);
+        const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        const float mv[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc[i][q] = fmaf(mv[i], xv[q], acc[i][q]);
+    }
+}
+
+__global__ void __launch_bounds__(128) chunk_small_kernel(const ChunkArgs a) {
     pdl_enter();
     __shared__ __align__(16) float Mt[64][64];  // transposed: [k][row]
     __shared__ __align__(16) float Xs[64][128];
     const int H = a.hs, u = blockIdx.y, j = u / a.HB, hb = u % a.HB, which = blockIdx.z, c0 = blockIdx.x * 128, tid = threadIdx.x;
     const float* Mx = (which == 0 ? a.Tinv : which == 1 ? a.TK : a.Qw) + (size_t)u * 4096;
-    for (int n = tid; n < 4096; n += 256) Mt[n & 63][n >> 6] = Mx[n];
-    for (int n = tid; n < 64 * 32; n += 256) {
+    for (int n = tid; n < 4096; n += 128) Mt[n & 63][n >> 6] = Mx[n];
+    for (int n = tid; n < 64 * 32; n += 128) {
         const int i = n >> 5, q = (n & 31) * 4;
         const float* src = which == 0 ? a.ES + ((size_t)u * 64 + i) * H + c0 + q
                                       : a.v + (size_t)(j * CC + i) * a.tok_stride + (size_t)hb * H + c0 + q;
         *reinterpret_cast<float4*>(&Xs[i][q]) = *reinterpret_cast<const float4*>(src);
     }
     __syncthreads();
-    const int r4 = tid >> 4, c8 = tid & 15;
-    float acc[4][8];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int q = 0; q < 8; ++q) acc[i][q] = 0.0f;
-    for (int k = 0; k < 64; ++k) {
-        const float4 x0 = *reinterpret_cast<const float4*>(&Xs[k][c8 * 8]), x1 = *reinterpret_cast<const float4*>(&Xs[k][c8 * 8 + 4]);
-        const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-        const float4 m4 = *reinterpret_cast<const float4*>(&Mt[k][r4 * 4]);
-        const float mv[4] = {m4.x, m4.y, m4.z, m4.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-            for (int q = 0; q < 8; ++q) acc[i][q] = fmaf(mv[i], xv[q], acc[i][q]);
-    }
+    const int r8 = tid >> 4, c8 = tid & 15;
+    float acc[8][8];
+    tile_mm_8x8(Mt, Xs, r8, c8, acc);
     const size_t P128 = (size_t)a.nC * a.HB * 128 * H;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int row = r4 * 4 + i;
+    for (int i = 0; i < 8; ++i) {
+        const int row = r8 * 8 + i;
         if (which == 0) {  // p1: the top rows of the state product's left operand, as limbs
             const size_t o = ((size_t)u * 128 + row) * H + c0 + c8 * 8;
             uint16_t l[3][8];
@@ -193,59 +253,44 @@ __global__ void __launch_bounds__(256) chunk_small_kernel(const ChunkArgs a) {
 }
 
 // ---- one chunk's reads: rr = rr0 + r0, y = yq + qwv - Qa rr; -rr^T into the update's left operand ---------------
-// grid (H / 128, HB); 256 threads
-__global__ void __launch_bounds__(256) chunk_read_kernel(const ChunkArgs a, int j) {
+// grid (H / 128, HB); 128 threads, the same 8 x 8 register tile
+__global__ void __launch_bounds__(128) chunk_read_kernel(const ChunkArgs a, int j) {
     pdl_enter();
     __shared__ __align__(16) float Mt[64][64];  // Qa transposed: [k][row]
     __shared__ __align__(16) float Rs[64][128];
     const int H = a.hs, hb = blockIdx.y, u = j * a.HB + hb, c0 = blockIdx.x * 128, tid = threadIdx.x;
     const float* Qa = a.Qa + (size_t)u * 4096;
-    for (int n = tid; n < 4096; n += 256) Mt[n & 63][n >> 6] = Qa[n];
+    for (int n = tid; n < 4096; n += 128) Mt[n & 63][n >> 6] = Qa[n];
     const float* RY = a.RY + (size_t)hb * 128 * H;
-    for (int n = tid; n < 64 * 32; n += 256) {
+    for (int n = tid; n < 64 * 32; n += 128) {
         const int i = n >> 5, q = (n & 31) * 4;
         const float4 x = *reinterpret_cast<const float4*>(RY + (size_t)i * H + c0 + q);
         const float4 r = *reinterpret_cast<const float4*>(a.r0 + ((size_t)u * 64 + i) * H + c0 + q);
         *reinterpret_cast<float4*>(&Rs[i][q]) = make_float4(x.x + r.x, x.y + r.y, x.z + r.z, x.w + r.w);
     }
     __syncthreads();
-    const int r4 = tid >> 4, c8 = tid & 15;
-    float acc[4][8];
+    const int r8 = tid >> 4, c8 = tid & 15;
+    float acc[8][8];
+    tile_mm_8x8(Mt, Rs, r8, c8, acc);
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int q = 0; q < 8; ++q) acc[i][q] = 0.0f;
-    for (int k = 0; k < 64; ++k) {
-        const float4 x0 = *reinterpret_cast<const float4*>(&Rs[k][c8 * 8]), x1 = *reinterpret_cast<const float4*>(&Rs[k][c8 * 8 + 4]);
-        const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-        const float4 m4 = *reinterpret_cast<const float4*>(&Mt[k][r4 * 4]);
-        const float mv[4] = {m4.x, m4.y, m4.z, m4.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-            for (int q = 0; q < 8; ++q) acc[i][q] = fmaf(mv[i], xv[q], acc[i][q]);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int row = r4 * 4 + i;
+    for (int i = 0; i < 8; ++i) {
+        const int row = r8 * 8 + i;
         const float* yq = RY + (size_t)(64 + row) * H + c0 + c8 * 8;
         const float* qv = a.qwv + ((size_t)u * 64 + row) * H + c0 + c8 * 8;
         float* dst = a.y + (size_t)(j * CC + row) * a.tok_stride + (size_t)hb * H + c0 + c8 * 8;
-        float o[8];
-#pragma unroll
-        for (int q = 0; q < 8; ++q) o[q] = (yq[q] + qv[q]) - acc[i][q];
-        *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
-        *reinterpret_cast<float4*>(dst + 4) = make_float4(o[4], o[5], o[6], o[7]);
+        const float4 y0 = *reinterpret_cast<const float4*>(yq), y1 = *reinterpret_cast<const float4*>(yq + 4);
+        const float4 q0 = *reinterpret_cast<const float4*>(qv), q1 = *reinterpret_cast<const float4*>(qv + 4);
+        *reinterpret_cast<float4*>(dst) = make_float4((y0.x + q0.x) - acc[i][0], (y0.y + q0.y) - acc[i][1], (y0.z + q0.z) - acc[i][2], (y0.w + q0.w) - acc[i][3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4((y1.x + q1.x) - acc[i][4], (y1.y + q1.y) - acc[i][5], (y1.z + q1.z) - acc[i][6], (y1.w + q1.w) - acc[i][7]);
     }
-    // -rr transposed: row (value) of the update's left operand, token slots 64 .. 127; thread = (value, half of the tokens)
+    // -rr transposed: row (value) of the update's left operand, token slots 64 .. 127; thread = value
     const size_t PT = (size_t)a.nC * a.HB * H * 128;
-    const int val = tid & 127, half = tid >> 7;
-    const size_t rowT = ((size_t)u * H + c0 + val) * 128 + 64 + half * 32;
-#pragma unroll
-    for (int i8 = 0; i8 < 32; i8 += 8) {
+    const size_t rowT = ((size_t)u * H + c0 + tid) * 128 + 64;
+#pragma unroll 2
+    for (int i8 = 0; i8 < 64; i8 += 8) {
         uint16_t l[3][8];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) limbs3(-Rs[half * 32 + i8 + q][val], l[0][q], l[1][q], l[2][q]);
+        for (int q = 0; q < 8; ++q) limbs3(-Rs[i8 + q][tid], l[0][q], l[1][q], l[2][q]);
 #pragma unroll
         for (int p = 0; p < 3; ++p)
             *reinterpret_cast<uint4*>(a.A5 + p * PT + rowT + i8) =
@@ -289,7 +334,7 @@ size_t mem_chunk_workspace_bytes(int HB, int hs, int nC) {
     size_t b = 0;
     b += 3 * (3 * U * 128 * H * 2);   // QE, WA, A3 limbs
     b += 2 * (3 * U * H * 128 * 2);   // A5, B5 limbs
-    b += 3 * (U * 64 * H * 4);        // ES, r0, qwv
+    b += 4 * (U * 64 * H * 4);        // ES, r0, qwv, CUM
     b += U * H * 4;                   // gc
     b += U * 128 * 128 * 4;           // Gm
     b += 4 * (U * 4096 * 4);          // Qw, Qa, Tinv, TK
@@ -311,6 +356,7 @@ void mem_chunk_carve(ChunkArgs& a, void* ws) {
     a.ES = (float*)take(U * 64 * H * 4);
     a.r0 = (float*)take(U * 64 * H * 4);
     a.qwv = (float*)take(U * 64 * H * 4);
+    a.CUM = (float*)take(U * 64 * H * 4);
     a.gc = (float*)take(U * H * 4);
     a.Gm = (float*)take(U * 128 * 128 * 4);
     a.Qw = (float*)take(U * 4096 * 4);
@@ -328,7 +374,10 @@ bool mem_chunk_covers(int hs, int T, float momentum) { return hs % 128 == 0 && T
 // before stage 2.
 bool launch_mem_chunk_scale(cudaStream_t st, const ChunkArgs& a) {
     if (!mem_chunk_covers(a.hs, a.nC * CC, 0.0f)) return false;
-    launch_k(chunk_scale_kernel, dim3((a.hs + 255) / 256, a.nC * a.HB), dim3(256), 0, st, a);
+    launch_k(chunk_scan_kernel, dim3((a.hs + 255) / 256, a.nC * a.HB), dim3(256), 0, st, a);
+    const size_t n = (size_t)a.nC * a.HB * 64 * (a.hs / 4);
+    launch_k(chunk_scale_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, a);
+    launch_k(chunk_keys_kernel, dim3(a.hs / 64, a.nC * a.HB), dim3(256), 0, st, a);
     return true;
 }
 
@@ -343,14 +392,14 @@ bool launch_mem_chunk_rest(cudaStream_t st, const ChunkArgs& a) {
     const size_t solve_smem = 3 * 64 * 65 * sizeof(float);
     cudaFuncSetAttribute(chunk_solve_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)solve_smem);
     launch_k(chunk_solve_kernel, dim3(U), dim3(256), solve_smem, st, a);
-    launch_k(chunk_small_kernel, dim3(H / 128, U, 3), dim3(256), 0, st, a);
+    launch_k(chunk_small_kernel, dim3(H / 128, U, 3), dim3(128), 0, st, a);
     for (int j = 0; j < a.nC; ++j) {
         TcbArgs s3{};
         s3.a = a.A3; s3.a_row0 = (int64_t)j * a.HB * 128; s3.rows_a = (int64_t)U * 128;
         s3.b = a.Ft_limbs; s3.rows_b = (int64_t)a.HB * H;
         s3.C = a.RY; s3.ldc = H; s3.c_batch_stride = (int64_t)128 * H; s3.M = 128; s3.N = H; s3.K = H; s3.batch = a.HB; s3.status = a.status;
         if (!launch_tc_bgemm(st, s3, TCB_STORE)) return false;
-        launch_k(chunk_read_kernel, dim3(H / 128, a.HB), dim3(256), 0, st, a, j);
+        launch_k(chunk_read_kernel, dim3(H / 128, a.HB), dim3(128), 0, st, a, j);
         TcbArgs s5{};
         s5.a = a.A5; s5.a_row0 = (int64_t)j * a.HB * H; s5.rows_a = (int64_t)U * H;
         s5.b = a.B5; s5.b_row0 = (int64_t)j * a.HB * H; s5.rows_b = (int64_t)U * H;
@@ -363,6 +412,6 @@ bool launch_mem_chunk_rest(cudaStream_t st, const ChunkArgs& a) {
     return true;
 }
 
-int mem_chunk_launches(int nC) { return 5 + 3 * nC + 1; }
+int mem_chunk_launches(int nC) { return 5 + 3 * nC + 3; }
 
 }  // namespace ava

@@ -450,6 +450,9 @@ __global__ void relay_res_kernel(float* x, const float* __restrict__ x_in, const
 
 // ---------------------------------------------------------------------------------------------------- memory: gates
 // src/model/fstep/arch.rs:685-803 for one row per block of threads, after the two stages of the gate projections.
+// FAST (the tolerance mode): the sums of squares and the two dot products are summed by a warp each (another order) and
+// the gates use the CUDA library's exp and log; everything else is the same.
+template <bool FAST>
 __global__ void mem_prep_kernel(const MemPrepArgs a) {
     pdl_enter();
     extern __shared__ __align__(16) float sm[];
@@ -493,11 +496,23 @@ __global__ void mem_prep_kernel(const MemPrepArgs a) {
         p_v0[u] = (in && !a.first && a.vres) ? a.v_first[o] : 0.0f;
     }
     // the three sums of squares per head, each in order by one thread; spread over the warps
+    if (FAST) {
+        for (int it = tid >> 5; it < 3 * nh; it += T >> 5) {
+            const int which = it / nh, e = it % nh;
+            const float* src = (which == 0 ? q : which == 1 ? kr : ek) + e * hs;
+            float s = 0.0f;
+            for (int i = tid & 31; i < hs; i += 32) s = fmaf(src[i], src[i], s);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if ((tid & 31) == 0) (which == 0 ? inv_q : which == 1 ? inv_k : inv_e)[e] = rsqrtf_(s + (float)1e-6);
+        }
+    } else {
     for (int it = tid; it < 3 * nh * 32; it += T) {
         if (it & 31) continue;
         const int which = (it >> 5) / nh, e = (it >> 5) % nh;
         const float* src = (which == 0 ? q : which == 1 ? kr : ek) + e * hs;
         (which == 0 ? inv_q : which == 1 ? inv_k : inv_e)[e] = inv_l2_seq(src, hs);
+    }
     }
     __syncthreads();
     bool bad = false;
@@ -505,15 +520,22 @@ __global__ void mem_prep_kernel(const MemPrepArgs a) {
     auto gates = [&](int c, float in_lra, float in_lrb, float in_off, float v, float v0, float za, float zb) {
         const int e = c / hs;
         const size_t o = (size_t)r * d + c;
-        const float la = log_sigmoid(add(add(za, in_off), in_lra));
-        float be = add(mul(sigmoid(add(zb, in_lrb)), 2.0f), 0.0f);
+        float la, be;
+        if (FAST) {
+            const float xa = (za + in_off) + in_lra, xb = zb + in_lrb;
+            la = -(fmaxf(-xa, 0.0f) + ::log1pf(::expf(-fabsf(xa))));
+            be = 2.0f / (1.0f + ::expf(-xb));
+        } else {
+            la = log_sigmoid(add(add(za, in_off), in_lra));
+            be = add(mul(sigmoid(add(zb, in_lrb)), 2.0f), 0.0f);
+        }
         if (a.rh_w) be = mul(be, a.rh_w[(size_t)r * nh + e]);  // --rhythm: the write gate, before ACh's clamp
         if (a.ach) {  // --neuromod ACh: times its signal, kept in [0, 2] (maximum, then minimum: src/model/fstep/arch.rs:1121-1129)
             be = mul(be, ach);
             be = be < 0.0f ? 0.0f : be;
             be = be > 2.0f ? 2.0f : be;
         }
-        const float ex = expf_(la);
+        const float ex = FAST ? ::expf(la) : expf_(la);
         const float qn = mul(q[c], inv_q[e]);
         const float kn = mul(kr[c], inv_k[e]);
         const float en = mul(ek[c], inv_e[e]);
@@ -558,6 +580,18 @@ __global__ void mem_prep_kernel(const MemPrepArgs a) {
     if (bad) atomicOr(a.status, ST_NONFINITE);
     __syncthreads();
     // q.w and q.ah, each summed in order from 0 (src/model/fstep/arch.rs:789-797); one thread per sum, in separate warps
+    if (FAST) {
+        for (int role = tid >> 5; role < 2 * nh; role += T >> 5) {
+            const int e = role % nh;
+            const float *av = q + e * hs, *bvec = (role < nh ? wv : ahv) + e * hs;
+            float s = 0.0f;
+            for (int i = tid & 31; i < hs; i += 32) s = fmaf(av[i], bvec[i], s);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if ((tid & 31) == 0) (role < nh ? a.qw : a.qa)[(size_t)r * nh + e] = s;
+        }
+        return;
+    }
     for (int it = tid; it < 2 * nh * 32; it += T) {
         if (it & 31) continue;
         const int role = it >> 5, e = role % nh;
@@ -818,8 +852,13 @@ void launch_mem_gates(cudaStream_t st, const MemPrepArgs& a) {
 void launch_mem_prep_rows(cudaStream_t st, const MemPrepArgs& a) {
     const int nh = a.d / a.hs;
     const size_t smem = ((size_t)5 * a.d + 3 * nh + 4) * sizeof(float);
-    opt_in_smem(mem_prep_kernel, smem);
-    launch_k(mem_prep_kernel, dim3(a.M), dim3(256), smem, st, a);
+    if (a.fast) {
+        opt_in_smem(mem_prep_kernel<true>, smem);
+        launch_k(mem_prep_kernel<true>, dim3(a.M), dim3(256), smem, st, a);
+    } else {
+        opt_in_smem(mem_prep_kernel<false>, smem);
+        launch_k(mem_prep_kernel<false>, dim3(a.M), dim3(256), smem, st, a);
+    }
 }
 
 void launch_mem_post(cudaStream_t st, const float* y_raw, const float* gate, int ldg, int M, int d, int hs, float* y, uint16_t* limbs,

@@ -163,7 +163,7 @@ struct ChunkArgs {
     uint32_t* status;
     // workspace (mem_chunk_carve)
     uint16_t *QE, *WA, *A3, *A5, *B5, *Ft_limbs;
-    float *ES, *r0, *qwv, *gc, *Gm, *Qw, *Qa, *Tinv, *TK, *RY, *Ft;
+    float *ES, *r0, *qwv, *CUM, *gc, *Gm, *Qw, *Qa, *Tinv, *TK, *RY, *Ft;
 };
 size_t mem_chunk_workspace_bytes(int HB, int hs, int nC);
 void mem_chunk_carve(ChunkArgs& a, void* ws);
@@ -228,6 +228,7 @@ struct MemPrepArgs {
     float *e, *v, *w, *ah, *qg, *ex, *qw, *qa;
     float* qs;           // [M, d] q * M when the memory has momentum, else nullptr
     float *qn_out, *la_out;  // [M, d] the unit query and the log rate, for the chunk-parallel form; or nullptr
+    int fast;            // 1 (the tolerance mode): norms and dot products summed by a warp each, the library's exp and log
     float mom;
     uint32_t* status;
 };
