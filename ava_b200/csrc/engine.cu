@@ -73,6 +73,7 @@ struct BlockDev {
     Dev dend_a, dend_b;                // --dendrite: A [d][32], B [32][hidden]
     Dev rh_w, rh_r;                    // --rhythm: the write strength's and the read's gates [4][heads]
     Dev da_w, da_c, mood_g;            // --dopamine: gate [d] twice; --mood: gain [k][d] (blocks after the first)
+    Dev gate_wl;                       // fast products: the three bf16 limbs of gate_w transposed, [3][gate_cols][d]
     QMat win, wout, proj, wo, eqkv, ewo, w1, w2;
 };
 
@@ -698,7 +699,22 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
         }
         // the gates' two projection stages read the normed input alone: on the lane's side stream they run beside the
         // q|k|v|e|g product (both are short of warps on their own); the per-row kernel then needs both
-        const bool fork = w.side_stream != nullptr && !e->prof && !e->keep;
+        // with fast products the first stage is a product of limbs on the tensor cores (the norm has left the limbs of h)
+        bool tc_gates = false;
+        if (e->fast && !e->keep && b.gate_wl.p && M % 128 == 0 && d % 64 == 0 && e->limbs_src == h && e->limbs_rows == M) {
+            TcbArgs g{};
+            g.a = e->limbs.as<uint16_t>(); g.rows_a = M; g.b = b.gate_wl.as<uint16_t>(); g.rows_b = e->gate_cols;
+            g.C = mp.z; g.ldc = e->gate_cols; g.c_batch_stride = 0; g.M = M; g.N = e->gate_cols; g.K = d; g.batch = 1;
+            g.status = e->status.as<uint32_t>();
+            prof_begin(e, "gate_z");
+            tc_gates = launch_tc_bgemm(st, g, TCB_STORE);
+            prof_end(e);
+            if (tc_gates) {
+                launch_mem_gates_low(st, mp);
+                e->launches++;
+            }
+        }
+        const bool fork = !tc_gates && w.side_stream != nullptr && !e->prof && !e->keep;
         if (fork) {
             CK(cudaEventRecord(w.side_go, st));
             CK(cudaStreamWaitEvent(w.side_stream, w.side_go, 0));
@@ -708,7 +724,10 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
         gemm(e, "gemm.qkveg", h, d, b.proj, w.proj.as<float>(), pw, M, EPI_STORE);
         dbg(e, "qkveg", i, w.proj.as<float>(), M, pw);
         prof_begin(e, "mem_prep");
-        if (fork) {
+        if (tc_gates) {
+            launch_mem_prep_rows(st, mp);
+            e->launches -= 2;  // counted where they were queued
+        } else if (fork) {
             CK(cudaStreamWaitEvent(st, w.side_done, 0));
             launch_mem_prep_rows(st, mp);
         } else {
@@ -2065,6 +2084,21 @@ int ava_engine_set_fast_products(ava_engine* e, int32_t on) {
             if (!m->q.p || m->wt.p || m->din % 64 || m->dout % 4) continue;
             CK(m->wt.alloc((size_t)m->din * m->dout * sizeof(uint16_t)));
             launch_widen_transpose(e->stream, m->qp(), m->din, m->dout, m->wt.as<uint16_t>());
+        }
+        // the gates' first-stage matrix [d][gate_cols] f32, transposed and split into limbs
+        for (auto& b : e->blocks) {
+            if (!b->gate_w.p || b->gate_wl.p || e->cfg.d % 64) continue;
+            const size_t n = (size_t)e->cfg.d * e->gate_cols;
+            std::vector<float> hw(n), ht(n);
+            CK(cudaMemcpy(hw.data(), b->gate_w.p, n * sizeof(float), cudaMemcpyDeviceToHost));
+            for (int k = 0; k < e->cfg.d; ++k)
+                for (int c = 0; c < e->gate_cols; ++c) ht[(size_t)c * e->cfg.d + k] = hw[(size_t)k * e->gate_cols + c];
+            Dev tmp;
+            CK(tmp.alloc(n * sizeof(float)));
+            CK(cudaMemcpy(tmp.p, ht.data(), n * sizeof(float), cudaMemcpyHostToDevice));
+            CK(b->gate_wl.alloc(3 * n * sizeof(uint16_t)));
+            launch_split3(e->stream, tmp.as<float>(), (int64_t)n, b->gate_wl.as<uint16_t>());
+            CK(cudaStreamSynchronize(e->stream));
         }
         CK(cudaStreamSynchronize(e->stream));
     }

@@ -834,7 +834,11 @@ void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a) {
 void launch_mem_gates(cudaStream_t st, const MemPrepArgs& a) {
     // stage one
     launch_chain_gemv(st, a.h, a.gate_w, a.M, a.d, a.gate_cols, a.gate_chunk, a.z);
-    // stage two
+    launch_mem_gates_low(st, a);
+}
+
+// stage two alone (stage one's products a.z exist already)
+void launch_mem_gates_low(cudaStream_t st, const MemPrepArgs& a) {
     {
         const size_t smem = (size_t)std::min(a.M, LR_ROWS) * 2 * a.rank * sizeof(float);
         const dim3 grid((a.d + LR_COLS - 1) / LR_COLS, (a.M + LR_ROWS - 1) / LR_ROWS), block(LR_COLS * LR_LANES);

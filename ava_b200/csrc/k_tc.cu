@@ -10,13 +10,13 @@
 //
 //   C[M, N] = (A_hi + A_mid + A_lo)[M, K] . W[K, N] * scale[N]      A limbs bf16 [3][M][K], W as bf16 [N][K] (K-major)
 //
-// One block of 128 threads per 128 x BN output tile, a 3-stage ring of k-tiles.  Thread 0 is the producer: per k-tile
+// One block of 256 threads per 128 x BN output tile, a 3-stage ring of k-tiles.  Thread 0 is the producer: per k-tile
 // TMA (2-D tiled, 128-byte swizzle) brings the 128 x 64 tiles of the three A limbs and one BN x 64 tile of W into
 // shared memory and signals the stage's "full" mbarrier.  Thread 32 issues the multiply-adds: twelve tcgen05.mma per
 // stage (three limbs x four steps of K 16; M 128, N BN, bf16 in, f32 accumulate in tensor memory), then tcgen05.commit
 // on the stage's "empty" mbarrier, which the producer waits on before it refills the stage.  After the last commit all
-// four warps read the accumulator back (tcgen05.ld, 32 lanes x 32 columns per warp and instruction), scale it and
-// store or add it.  Every wait is bounded.
+// eight warps read the accumulator back (tcgen05.ld, 32 lanes x 32 columns per warp and instruction), scale it and
+// store or add it, row-wise through a staging square in shared memory.  Every wait is bounded.
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -27,7 +27,7 @@ namespace ava {
 
 namespace {
 
-constexpr int TC_BM = 128, TC_BK = 64, TC_STAGES = 3, TC_THREADS = 128;
+constexpr int TC_BM = 128, TC_BK = 64, TC_STAGES = 3, TC_THREADS = 256;
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -112,6 +112,13 @@ __global__ void __launch_bounds__(TC_THREADS) tc_gemm_kernel(const __grid_consta
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
+    if (EPI == EPI_ADD) {
+        // the tile the products are added to is wanted by the epilogue only: ask for it now, so that it waits in L2 by then
+        for (int n = tid; n < TC_BM * (BN / 32); n += TC_THREADS) {
+            const int r = n / (BN / 32), c = (n % (BN / 32)) * 32;
+            if (m0 + r < M && n0 + c < N) asm volatile("prefetch.global.L2 [%0];" ::"l"(C + (size_t)(m0 + r) * ldc + n0 + c));
+        }
+    }
 
     if (tid == 0) {
         // producer: one k-tile per stage, the weight tile shared by the three limbs
@@ -165,12 +172,17 @@ __global__ void __launch_bounds__(TC_THREADS) tc_gemm_kernel(const __grid_consta
     if (!acc_ok && lane == 0) atomicOr(status, ST_WAIT_TIMEOUT);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-    // epilogue: warp w reads lanes 32 w .. 32 w + 31 (one output row per thread), 32 columns per instruction
-    const int row = m0 + warp * 32 + lane;
+    // epilogue: warp w reads lanes 32 (w % 4) .. + 31 of the accumulator (one output row per thread), 32 columns per
+    // instruction; warps 0-3 take the left half of the tile's columns, warps 4-7 the right half.  Each 32 x 32 piece
+    // goes through a staging square in shared memory (the first stage is free once the accumulator is complete) so
+    // that global memory is touched row-wise: eight lanes cover 128 contiguous bytes of a row, four rows per instruction.
+    const int wq = warp & 3, half = warp >> 2;
+    float* stage = reinterpret_cast<float*>(smem) + warp * (32 * 33);
+    const int sub_r = lane >> 3, sub_c = (lane & 7) * 4;
 #pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 32) {
+    for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
         uint32_t r[32];
-        const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+        const uint32_t taddr = tmem + ((uint32_t)(wq * 32) << 16) + (uint32_t)c0;
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -181,31 +193,32 @@ __global__ void __launch_bounds__(TC_THREADS) tc_gemm_kernel(const __grid_consta
               "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
             : "r"(taddr));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < M && acc_ok) {
-            // EPI_ADD: the 32 values the products are added to are read before any is written (a store would fence the
-            // loads after it, one memory round trip per group of four)
-            float4 prev[8];
+        const int c = n0 + c0 + sub_c;           // this lane's four columns
+        const bool col_ok = c < N && acc_ok;     // N is a multiple of 4
+        float4 prev[8], sc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (EPI == EPI_ADD) {  // the values the products are added to: asked for before the staging, all eight row groups at once
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                const int row = m0 + wq * 32 + it * 4 + sub_r;
+                prev[it] = (col_ok && row < M) ? *reinterpret_cast<const float4*>(C + (size_t)row * ldc + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        if (col_ok) sc = *reinterpret_cast<const float4*>(scale + c);
+        __syncwarp();  // the lanes' reads of the piece before
+#pragma unroll
+        for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = __uint_as_float(r[j]);
+        __syncwarp();
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int lr = it * 4 + sub_r, row = m0 + wq * 32 + lr;
+            if (!col_ok || row >= M) continue;
+            const float* sp = stage + lr * 33 + sub_c;
+            float4 o = make_float4(mul(sp[0], sc.x), mul(sp[1], sc.y), mul(sp[2], sc.z), mul(sp[3], sc.w));
             if (EPI == EPI_ADD) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                    const int c = n0 + c0 + j;
-                    prev[j / 4] = c < N ? *reinterpret_cast<const float4*>(C + (size_t)row * ldc + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
+                const float4 x = prev[it];
+                o = make_float4(add(x.x, o.x), add(x.y, o.y), add(x.z, o.z), add(x.w, o.w));
             }
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-                const int c = n0 + c0 + j;
-                if (c < N) {  // N is a multiple of 4
-                    const float4 sc = *reinterpret_cast<const float4*>(scale + c);
-                    float4 o = make_float4(mul(__uint_as_float(r[j]), sc.x), mul(__uint_as_float(r[j + 1]), sc.y),
-                                           mul(__uint_as_float(r[j + 2]), sc.z), mul(__uint_as_float(r[j + 3]), sc.w));
-                    if (EPI == EPI_ADD) {
-                        const float4 x = prev[j / 4];
-                        o = make_float4(add(x.x, o.x), add(x.y, o.y), add(x.z, o.z), add(x.w, o.w));
-                    }
-                    *reinterpret_cast<float4*>(C + (size_t)row * ldc + c) = o;
-                }
-            }
+            *reinterpret_cast<float4*>(C + (size_t)row * ldc + c) = o;
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -272,11 +285,11 @@ bool launch_bn(cudaStream_t st, const TcGemmArgs& a, GemmEpilogue epi) {
     if (!make_map(&ma, a.a_limbs, (uint64_t)3 * a.M, a.K, TC_BM) || !make_map(&mw, a.w_bf16, a.N, a.K, BN)) return false;
     dim3 grid((a.N + BN - 1) / BN, (a.M + TC_BM - 1) / TC_BM);
     const size_t smem = tc_smem<BN>();
-    static bool opted = false;  // per process; the attribute is per function and device-independent in effect here
-    if (!opted) {
-        cudaFuncSetAttribute(tc_gemm_kernel<BN, EPI_ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaFuncSetAttribute(tc_gemm_kernel<BN, EPI_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        opted = true;
+    // the attribute belongs to the function on the current device: set on every launch (a table lookup in the runtime)
+    if (epi == EPI_ADD) {
+        if (cudaFuncSetAttribute(tc_gemm_kernel<BN, EPI_ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
+    } else {
+        if (cudaFuncSetAttribute(tc_gemm_kernel<BN, EPI_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
     }
     if (epi == EPI_ADD) {
         launch_k(tc_gemm_kernel<BN, EPI_ADD>, dim3(grid), dim3(TC_THREADS), smem, st, ma, mw, a.scale, a.C, a.ldc, a.M, a.N, a.K, a.status);

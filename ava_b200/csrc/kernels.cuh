@@ -250,6 +250,7 @@ void launch_relay_res(cudaStream_t st, float* x, const float* x_in, const float*
 void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a);
 // the same in its two parts: the gates' projection stages (need only a.h), then the per-row kernel (needs a.proj too)
 void launch_mem_gates(cudaStream_t st, const MemPrepArgs& a);
+void launch_mem_gates_low(cudaStream_t st, const MemPrepArgs& a);  // stage two alone, when a.z was made elsewhere
 void launch_mem_prep_rows(cudaStream_t st, const MemPrepArgs& a);
 
 struct MemHeadsArgs {
