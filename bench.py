@@ -30,6 +30,7 @@ sys.path.insert(0, ROOT)
 METRIC = "decode tokens/s (batch 256 per GPU, Ava-0.4-shaped int8 model)"
 UNIT = "tokens/s"
 ROWS_PER_GPU = 256
+TRAFFIC_PER_STATE_BYTE = 1154.7e6 / 1207959552.0  # ncu: DRAM read + write per algorithmic byte of the state pass (profiles/)
 MEAN_CTX = 1536  # mean KV length of the decode phase of configuration 1 (1024 prompt + 1024 decode)
 
 
@@ -42,22 +43,68 @@ def peaks():
 
 
 class Clocks:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples the SM clock and the throttle reasons while the steps run: NVML from a thread every 10 ms (reading only),
+    or nvidia-smi's own loop when the NVML module is missing.  start() before the warm-up steps, mark() when the timed
+    region begins: the summary is over the samples from the mark on (over all of them when the region was too short
+    to hold three)."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    BITS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
 
     def __init__(self, gpu_index: int):
         self.gpu = gpu_index
         self.p = None
+        self.thread = None
+        self.samples = []   # (time, sm MHz, reasons bitmask)
+        self.t_mark = None
+        self.stop_flag = False
+        self.max_mhz = None
+
+    def _loop(self, nv, h):
+        while not self.stop_flag:
+            try:
+                self.samples.append((time.perf_counter(), float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)),
+                                     int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(h))))
+            except Exception:
+                pass
+            time.sleep(0.01)
 
     def start(self):
         try:
-            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.gpu)],
+            import threading
+            import pynvml as nv
+            nv.nvmlInit()
+            # NVML counts physical GPUs; CUDA_VISIBLE_DEVICES may renumber them for this process
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            ent = vis.split(",")[self.gpu].strip() if vis else str(self.gpu)
+            h = nv.nvmlDeviceGetHandleByUUID(ent) if ent.startswith("GPU-") else nv.nvmlDeviceGetHandleByIndex(int(ent))
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._loop, args=(nv, h), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(self.gpu)],
                                       stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.p = None
 
+    def mark(self):
+        self.t_mark = time.perf_counter()
+
     def stop(self) -> dict:
+        if self.thread is not None:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+            timed = [x for x in self.samples if self.t_mark is not None and x[0] >= self.t_mark]
+            use, window = (timed, "timed steps") if len(timed) >= 3 else (self.samples, "warm-up and timed steps")
+            mask = 0
+            for x in use:
+                mask |= x[2]
+            reasons = sorted(name for bit, name in self.BITS.items() if mask & bit)
+            return {"sm_mhz": float(np.median([x[1] for x in use])) if use else None, "sm_max_mhz": self.max_mhz, "samples": len(use),
+                    "window": window, "source": "NVML, every 10 ms", "reasons": reasons}
         if self.p is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.p.terminate()
@@ -80,7 +127,7 @@ class Clocks:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "window": "warm-up and timed steps", "source": "nvidia-smi, every 50 ms", "reasons": sorted(reasons)}
 
 
 # ------------------------------------------------------------------------------------------------- CPU baseline
@@ -123,6 +170,32 @@ def run_reference(args, cfg, rank):
     print(json.dumps(line), flush=True)
 
 
+def prefill_tensor_flops(cfg, tokens):
+    """Tensor-core FLOPs per prompt token of the tolerance mode's chunked pass: (executed, algorithmic).  Executed counts
+    every limb product the kernels issue (3 per dense product: three activation limbs x one exact bf16 weight; 6 per
+    product of the chunk-parallel memory: three limbs each side, i + j <= 2; the engram's scores 3 twice and its mix 2);
+    algorithmic counts each product once (and the scores once)."""
+    d, H, L, hs = cfg["d"], cfg["hidden"], cfg["n_blocks"], cfg["head_size"]
+    nh = d // hs
+    dense = d * d * (1 + 4 + (1 if cfg["out_gate"] else 0) + 1) + 2 * d * H          # W_in, q|k|v|e(|g), W_o, W_1, W_2 (W_out is the event sum)
+    gate_cols = 2 * cfg["gate_rank"] + 2 * nh
+    mem = nh * (128 * 128 * hs + 2 * 128 * hs * hs) / 64.0                           # per token: the Gram, the state read and the state update of a 64-token chunk
+    eng_dense = 4 * d * d if cfg["eng_block"] >= 0 else 0
+    mean_keys = (tokens + 1) / 2.0 + 32                                              # causal, in tiles of 64 keys
+    attn = d * mean_keys if cfg["eng_block"] >= 0 else 0                             # one product of a query with its keys, all heads
+    algorithmic = 2.0 * (L * (dense + d * gate_cols + mem) + eng_dense + 2 * attn)
+    executed = 2.0 * (L * (3 * dense + 6 * d * gate_cols + 6 * mem) + 3 * eng_dense + 8 * attn)
+    return executed, algorithmic
+
+
+def tensor_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["bf16_tflops_sustained"]), "measured (MEASURED_PEAKS.json bf16_tflops_sustained: the pass runs for seconds)"
+    return 1400.0, "fallback (1.4 PFLOP/s sustained, earlier measurement on this pool)"
+
+
 def measure_prefill(model, cfg, local, world, dist, rows, tokens, chunk, seed0, fast=False):
     """Chunked prompt reading through ava_prefill_device: tokens/s over all ranks, device-timed, ids resident."""
     import torch
@@ -140,6 +213,7 @@ def measure_prefill(model, cfg, local, world, dist, rows, tokens, chunk, seed0, 
     if world > 1:
         dist.barrier()
     l0 = model.launches
+    c0 = model.chunked_memory_counts()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record(stream)
     model.prefill_device(st, tok.data_ptr(), tokens, chunk, logits.data_ptr(), None)
@@ -153,7 +227,18 @@ def measure_prefill(model, cfg, local, world, dist, rows, tokens, chunk, seed0, 
         ms = float(t.item())
     st.close()
     if fast:
-        return {"value": world * rows * tokens / (ms * 1e-3), "unit": "tokens/s", "ms": ms, "gpu_launches": int(model.launches - l0)}
+        executed, algorithmic = prefill_tensor_flops(cfg, tokens)
+        tps = rows * tokens / (ms * 1e-3)   # per GPU
+        peak, src = tensor_peak()
+        after = model.chunked_memory_counts()
+        return {"value": world * tps, "unit": "tokens/s", "rows_per_gpu": rows, "tokens_per_row": tokens, "chunk": chunk, "ms": ms,
+                "gpu_launches": int(model.launches - l0),
+                "what": "benchmark configuration 2 in the tolerance mode: dense products, the chunk-parallel fast-weight memory (chunks of 64) and "
+                        "the engram's causal read on tcgen05 tensor cores; agrees with the sequential reference to rounding, not bit for bit",
+                "memory_passes": {"chunk_form": after[0] - c0[0], "token_loop": after[1] - c0[1], "engram_chunks": after[2] - c0[2]},
+                "roofline": {"bound": "tensor", "achieved": executed * tps / 1e12, "peak": peak, "unit": "TFLOP/s", "frac": executed * tps / 1e12 / peak,
+                             "of": src, "counts": "limb products issued (executed FLOPs)", "algorithmic_tflops": algorithmic * tps / 1e12,
+                             "flops_per_token": {"executed": executed, "algorithmic": algorithmic}, "traffic": None}}
     return {"value": world * rows * tokens / (ms * 1e-3), "unit": "tokens/s", "rows_per_gpu": rows, "tokens_per_row": tokens, "chunk": chunk,
             "ms": ms, "gpu_launches": int(model.launches - l0),
             "what": "chunked prompt reading, bit-identical to stepping (CUDA-core products in k order, LIF time scan, fast-weight slice "
@@ -173,7 +258,8 @@ def main():
     ap.add_argument("--scaled", action="store_true", help="benchmark configuration 3: 24 blocks, d 2048, wide 8192, vocab 32768 (use --rows 128: an 8-GPU share of 1024 sequences)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--parts", action="store_true", help="the same workload with the nine Ava-0.4 parts switched on (their cost; not the headline configuration)")
-    ap.add_argument("--prefill-tokens", type=int, default=1024, help="tokens per row of the prompt-reading sample (config 2: 8192)")
+    ap.add_argument("--prefill-tokens", type=int, default=1024, help="tokens per row of the exact prompt-reading sample (config 2 is 8192: about half a minute)")
+    ap.add_argument("--fast-prefill-tokens", type=int, default=8192, help="tokens per row of the tolerance mode's prompt-reading leg (config 2: 8192)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
 
@@ -235,13 +321,16 @@ def main():
             cur ^= 1
         return cur
 
+    # the clock sampler starts before the warm-up steps (a short timed region would otherwise end before its first
+    # sample): its samples cover warm-up and timed steps, both under the same load
+    clocks = Clocks(local)
+    clocks.start()
     cur = decode(W, 0)
     model.sync()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    clocks = Clocks(local)
-    clocks.start()
+    clocks.mark()
     l0 = model.launches
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record(stream)
@@ -327,9 +416,10 @@ def main():
     state_bytes = rows * 2 * 4 * cfg["d"] * cfg["head_size"]        # read once + written once, f32, per launch
     peak, peak_src = peaks()
     achieved = state_bytes / (ms_mh / max(n_mh, 1) * 1e-3) / 1e9 if n_mh else 0.0
-    # DRAM bytes one launch moved under ncu (dram__bytes_read.sum + dram__bytes_write.sum, 256 rows of one 768x768
-    # matrix: profiles/mem_heads_bulk_slice_major_small_case.md); it grows in proportion to the state a launch streams
-    traffic = 1154.7e6 * state_bytes / 1207959552.0
+    # DRAM bytes one launch moved under ncu (dram__bytes_read.sum + dram__bytes_write.sum of the state pass over 256 rows
+    # of one 768x768 matrix, from the capture summarised under profiles/): a constant of that profile, scaled by the
+    # state a launch streams, not something this run measures
+    traffic = TRAFFIC_PER_STATE_BYTE * state_bytes
     # the whole step against the HBM roofline: algorithmic bytes per decoded token (state + weights/rows + KV + LIF)
     kv_bytes = args.ctx * 2 * cfg["d"] * 2 if cfg["eng_block"] >= 0 else 0
     tok_bytes = (2 * 4 * cfg["n_blocks"] * cfg["d"] * cfg["head_size"] + synth.weight_bytes(cfg) / rows + kv_bytes
@@ -354,7 +444,7 @@ def main():
         "gpu_launches": int(launches),
         "clocks": clk,
         "roofline": {"bound": "hbm", "kernel": "mem_heads (fast-weight state pass)", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "of": peak_src, "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram read + write)",
+                     "frac": achieved / peak, "of": peak_src, "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram read + write)", "traffic_source": "profile constant (ncu capture under profiles/), scaled by the bytes a launch streams; not measured in this run",
                      "bytes_per_launch": state_bytes,
                      "mean_launch_ms": ms_mh / max(n_mh, 1), "launches_timed": n_mh,
                      "step_bytes_per_token": tok_bytes, "step_frac_of_hbm_roofline": step_frac},
@@ -387,7 +477,7 @@ def main():
     model.prof_enable(False)
     fast_prefill = None
     if not args.small and not args.scaled:
-        fast_prefill = measure_prefill(model, cfg, local, world, dist, rows=64, tokens=args.prefill_tokens, chunk=256, seed0=50_000 + first, fast=True)
+        fast_prefill = measure_prefill(model, cfg, local, world, dist, rows=64, tokens=args.fast_prefill_tokens, chunk=1024, seed0=50_000 + first, fast=True)
     model.set_fast_products(False)
     line["fast_products"] = {"prefill": fast_prefill, "value": world * rows * K / (fast_ms * 1e-3), "unit": UNIT, "ms_per_step": fast_ms / K, "gpu_launches": int(fast_launches),
                              "parity": "dense products on tcgen05 tensor cores: exact products (3 bf16 limbs x bf16 weights), f32 sums in the "
@@ -399,7 +489,15 @@ def main():
     if rank == 0 and not args.no_cpu and not args.small:
         threads = os.cpu_count() or 1
         val, _, sample = cpu_reference(cfg, weights, 128, 4, 16, threads)
-        line["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
+        # the same sample at fewer threads (bounded: a few seconds each), and configuration 0's own case: one sequence
+        sweep = {str(threads): val}
+        for th in (1, 4, 8):
+            if th < threads:
+                sweep[str(th)] = cpu_reference(cfg, weights, 8 * th, 2, 16, th)[0]
+        one, one_ms, one_sample = cpu_reference(cfg, weights, 64, 4, 1, threads)
+        line["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample,
+                                "by_threads": sweep,
+                                "config0_batch1": {"value": one, "unit": UNIT, "ms_per_token": one_ms, "sample": one_sample}}
     elif rank == 0:
         line["cpu_baseline"] = None
     if rank == 0:
