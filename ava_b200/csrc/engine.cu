@@ -158,6 +158,7 @@ struct ava_engine : Work {
     uint32_t* status_host = nullptr;  // pinned
 
     bool prof = false;
+    bool prof_lanes = std::getenv("AVA_TIMELINE") != nullptr;  // tuning aid: keep the lanes under the section clock (its per-kernel sums then overlap)
     struct Pending { const char* cls; cudaEvent_t a, b; cudaStream_t st; };
     std::vector<Pending> prof_pending;
     std::map<std::string, std::pair<int64_t, double>> prof_total;  // kernel -> (launches, milliseconds)
@@ -535,8 +536,10 @@ enum StepPhase { PHASE_ALL = 0, PHASE_BEGIN = 1, PHASE_END = 2 };  // BEGIN stop
 
 // One lane: rows [r0, r0 + rows) of the state, with the lane's work buffers, queued on stream st.  tok, logits and next
 // are the caller's whole buffers (a lane reads and writes its own rows of them).
+// blk0, blk1: the blocks [blk0, blk1) queued by this call (with what precedes block 0 when blk0 == 0, and the head and the
+// host's bookkeeping when blk1 reaches the last block), so that a step's lanes can be queued block by block in turn.
 int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int rows, const uint32_t* tok, float* logits, uint32_t* next, bool want_logits,
-              int T, bool all_logits, StepPhase phase) {
+              int T, bool all_logits, StepPhase phase, int blk0 = 0, int blk1 = 1 << 30) {
     const ava_config& c = e->cfg;
     const int d = c.d, L = c.n_blocks, nh = e->nh(), hs = c.head_size, H = c.hidden;
     e->cur = st;
@@ -560,7 +563,8 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
         }
     }
 
-    if (phase != PHASE_END) {
+    const bool head_part = blk0 == 0, tail_part = blk1 >= L;
+    if (phase != PHASE_END && head_part) {
         prof_begin(e, "embed");
         launch_embed(st, e->tok_emb.as<float>(), tok, M, d, c.vocab, x, streams, e->status.as<uint32_t>(), c.letters ? e->letters.as<float>() : nullptr);
         prof_end(e);
@@ -578,7 +582,7 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
         e->launches += 2;
         dbg(e, "th_g", j, w.th_g.as<float>(), M, 4);
     };
-    if (c.rhythm && phase != PHASE_END) {
+    if (c.rhythm && phase != PHASE_END && head_part) {
         // Y: the clocks at every token of the chunk, from the input (after the letters): reset read-out, times, phase features
         prof_begin(e, "rhythm");
         launch_rmsnorm(st, x, e->ones.as<float>(), M, d, h);
@@ -588,8 +592,8 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
         e->launches += 2;
         dbg(e, "rh_f", -1, w.rh_f.as<float>(), M, 4);
     }
-    if (c.thalamus && phase != PHASE_END) relay_read(0);
-    for (int i = phase == PHASE_END ? c.eng_block : 0; i < L; ++i) {
+    if (c.thalamus && phase != PHASE_END && head_part) relay_read(0);
+    for (int i = std::max(phase == PHASE_END ? c.eng_block : 0, blk0); i < std::min(L, blk1); ++i) {
         BlockDev& b = *e->blocks[i];
         if (c.thalamus && !(phase == PHASE_END && i == c.eng_block))
             CK(cudaMemcpyAsync(w.x_in.p, x, Md * sizeof(float), cudaMemcpyDeviceToDevice, st));  // the residual rule's x_in
@@ -714,7 +718,7 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
                 e->launches++;
             }
         }
-        const bool fork = !tc_gates && w.side_stream != nullptr && !e->prof && !e->keep;
+        const bool fork = !tc_gates && w.side_stream != nullptr && (!e->prof || e->prof_lanes) && !e->keep;
         if (fork) {
             CK(cudaEventRecord(w.side_go, st));
             CK(cudaStreamWaitEvent(w.side_stream, w.side_go, 0));
@@ -972,6 +976,12 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
             dbg(e, "nm_sig", 0, w.sig.as<float>(), M, 4);
         }
     }
+    if (!tail_part) {
+        cudaError_t le = take_launch_error();
+        if (le == cudaSuccess) le = cudaGetLastError();
+        if (le != cudaSuccess) return e->cuda_fail(le, "kernel launch");
+        return AVA_OK;
+    }
     if (want_logits || next) {
         // the head reads the last token's rows only, unless every position's logits were asked for
         const int first_row = all_logits ? 0 : (T - 1) * rows, head_rows = all_logits ? M : rows;
@@ -1035,7 +1045,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         if (frc) return frc;
     }
     int lanes = 1;
-    if (e->n_lanes > 1 && T == 1 && phase == PHASE_ALL && !e->keep && !e->fast && !e->prof) lanes = std::max(1, std::min(e->n_lanes, s->rows / 48));  // a lane of fewer rows gains nothing
+    if (e->n_lanes > 1 && T == 1 && phase == PHASE_ALL && !e->keep && !e->fast && (!e->prof || e->prof_lanes)) lanes = std::max(1, std::min(e->n_lanes, s->rows / 48));  // a lane of fewer rows gains nothing
     if (lanes == 1) {
         const int rc1 = step_rows(e, *e, e->stream, s, 0, s->rows, tok, logits, next, want_logits, T, all_logits, phase);
         if (rc1 == AVA_OK && streams_state) {
@@ -1063,17 +1073,23 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
     }
     CK(cudaEventRecord(e->fork_ev, e->stream));
     int rc = AVA_OK;
-    for (int l = 0; l < lanes && rc == AVA_OK; ++l) {
-        const int r0 = l * per, n = std::min(per, s->rows - r0);
-        if (n <= 0) break;
-        Work& w = l == 0 ? static_cast<Work&>(*e) : *e->more_lanes[l - 1];
-        cudaStream_t st = l == 0 ? e->stream : w.lane_stream;
-        if (l > 0) CK(cudaStreamWaitEvent(st, e->fork_ev, 0));
-        rc = step_rows(e, w, st, s, r0, n, tok, logits, next, want_logits, T, all_logits, phase);
-        if (l > 0) {
-            CK(cudaEventRecord(w.lane_done, st));
-            CK(cudaStreamWaitEvent(e->stream, w.lane_done, 0));
+    for (int l = 1; l < lanes; ++l)
+        if (l * per < s->rows) CK(cudaStreamWaitEvent(e->more_lanes[l - 1]->lane_stream, e->fork_ev, 0));
+    // the lanes are queued block by block in turn: queued one whole lane after the other, the second lane would start
+    // only when the host has queued all of the first (a millisecond of a five-millisecond step)
+    const int L = e->cfg.n_blocks;
+    for (int b = 0; b < L && rc == AVA_OK; ++b)
+        for (int l = 0; l < lanes && rc == AVA_OK; ++l) {
+            const int r0 = l * per, n = std::min(per, s->rows - r0);
+            if (n <= 0) break;
+            Work& w = l == 0 ? static_cast<Work&>(*e) : *e->more_lanes[l - 1];
+            rc = step_rows(e, w, l == 0 ? e->stream : w.lane_stream, s, r0, n, tok, logits, next, want_logits, T, all_logits, phase, b, b + 1 == L ? 1 << 30 : b + 1);
         }
+    for (int l = 1; l < lanes; ++l) {
+        if (l * per >= s->rows) break;
+        Work& w = *e->more_lanes[l - 1];
+        CK(cudaEventRecord(w.lane_done, w.lane_stream));
+        CK(cudaStreamWaitEvent(e->stream, w.lane_done, 0));
     }
     e->cur = e->stream;
     if (rc == AVA_OK && streams_state) {

@@ -81,10 +81,9 @@ class Clocks:
             self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
             self.thread = threading.Thread(target=self._loop, args=(nv, h), daemon=True)
             self.thread.start()
-            return
         except Exception:
             self.thread = None
-        try:
+        try:  # nvidia-smi's own loop beside it: the summary falls back to it when the thread got too few samples
             self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(self.gpu)],
                                       stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
@@ -103,8 +102,12 @@ class Clocks:
             for x in use:
                 mask |= x[2]
             reasons = sorted(name for bit, name in self.BITS.items() if mask & bit)
-            return {"sm_mhz": float(np.median([x[1] for x in use])) if use else None, "sm_max_mhz": self.max_mhz, "samples": len(use),
-                    "window": window, "source": "NVML, every 10 ms", "reasons": reasons}
+            if len(use) >= 3:
+                if self.p is not None:
+                    self.p.terminate()
+                    self.p.communicate()
+                return {"sm_mhz": float(np.median([x[1] for x in use])) if use else None, "sm_max_mhz": self.max_mhz, "samples": len(use),
+                        "window": window, "source": "NVML, every 10 ms", "reasons": reasons}
         if self.p is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.p.terminate()
