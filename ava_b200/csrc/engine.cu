@@ -22,6 +22,7 @@
 #include "../../include/ava_engine.h"
 #include "ava_math.h"
 #include "kernels.cuh"
+#include "nccl_dl.h"
 
 namespace {
 
@@ -2198,6 +2199,74 @@ int ava_prof_names(ava_engine* e, char* out, int32_t cap) {
     for (auto& p : e->prof_pending) e->prof_total[p.cls];
     for (auto& kv : e->prof_total) all += kv.first + "\n";
     snprintf(out, cap, "%s", all.c_str());
+    return AVA_OK;
+}
+
+// ---- the split step's exchange behind the boundary: NCCL reached by dlopen, the caller's (or our own) communicator ----
+int ava_nccl_version(int32_t* version) {
+    const NcclApi* n = nccl_api();
+    if (!n || !version) return AVA_NOT_APPLICABLE;
+    int v = 0;
+    if (n->GetVersion(&v) != 0) return AVA_ERR_CUDA;
+    *version = v;
+    return AVA_OK;
+}
+
+int ava_nccl_unique_id(unsigned char* id128) {
+    const NcclApi* n = nccl_api();
+    if (!id128) return AVA_ERR_ARG;
+    if (!n) return AVA_NOT_APPLICABLE;
+    NcclUniqueId id;
+    if (n->GetUniqueId(&id) != 0) return AVA_ERR_CUDA;
+    std::memcpy(id128, id.internal, 128);
+    return AVA_OK;
+}
+
+int ava_nccl_comm_init(ava_engine* e, int32_t world, int32_t rank, const unsigned char* id128, void** comm) {
+    if (!e || !id128 || !comm || world < 1 || rank < 0 || rank >= world) return AVA_ERR_ARG;
+    const NcclApi* n = nccl_api();
+    if (!n) return e->fail(AVA_NOT_APPLICABLE, "no NCCL library: %s", nccl_dl_error());
+    CK(cudaSetDevice(e->device));
+    NcclUniqueId id;
+    std::memcpy(id.internal, id128, 128);
+    void* c = nullptr;
+    const int rc = n->CommInitRank(&c, world, id, rank);
+    if (rc != 0) return e->fail(AVA_ERR_CUDA, "ncclCommInitRank: %s", n->GetErrorString(rc));
+    *comm = c;
+    return AVA_OK;
+}
+
+int ava_nccl_comm_destroy(void* comm) {
+    const NcclApi* n = nccl_api();
+    if (!n || !comm) return AVA_ERR_ARG;
+    return n->CommDestroy(comm) == 0 ? AVA_OK : AVA_ERR_CUDA;
+}
+
+int ava_split_step(ava_engine* e, ava_state* s, void* nccl_comm, int32_t rank, int32_t world, const uint32_t* tok_device, float* qkv_device,
+                   float* partial_device, float* gathered_device, float* logits_device, uint32_t* next_device) {
+    int rc = check_pair(e, s);
+    if (rc) return rc;
+    if (!qkv_device || !partial_device || !gathered_device || world < 1 || rank < 0 || rank >= world || (rank == 0 && !tok_device) || (world > 1 && !nccl_comm))
+        return e->fail(AVA_ERR_ARG, "bad arguments");
+    const bool use_nccl = nccl_comm != nullptr;  // one rank with a communicator still goes through NCCL
+    const NcclApi* n = use_nccl ? nccl_api() : nullptr;
+    if (use_nccl && !n) return e->fail(AVA_NOT_APPLICABLE, "no NCCL library: %s", nccl_dl_error());
+    const ava_config& c = e->cfg;
+    const size_t qkv_n = (size_t)s->rows * 3 * c.d;
+    const size_t part_n = (size_t)s->rows * (c.d / c.eng_head_size) * ava_shard_parts(e, s) * (2 + c.eng_head_size);
+    if (rank == 0 && (rc = ava_split_step_begin(e, s, tok_device, qkv_device))) return rc;
+    if (use_nccl) {
+        const int nrc = n->Broadcast(qkv_device, qkv_device, qkv_n, NCCL_FLOAT32, 0, nccl_comm, e->stream);
+        if (nrc != 0) return e->fail(AVA_ERR_CUDA, "ncclBroadcast: %s", n->GetErrorString(nrc));
+    }
+    if ((rc = ava_shard_partial(e, s, qkv_device, partial_device))) return rc;
+    if (use_nccl) {
+        const int nrc = n->AllGather(partial_device, gathered_device, part_n, NCCL_FLOAT32, nccl_comm, e->stream);
+        if (nrc != 0) return e->fail(AVA_ERR_CUDA, "ncclAllGather: %s", n->GetErrorString(nrc));
+    } else {
+        CK(cudaMemcpyAsync(gathered_device, partial_device, part_n * sizeof(float), cudaMemcpyDeviceToDevice, e->stream));
+    }
+    if (rank == 0) return ava_split_step_end(e, s, gathered_device, world, logits_device, next_device);
     return AVA_OK;
 }
 

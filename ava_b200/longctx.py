@@ -66,6 +66,31 @@ class SplitKV:
         """rank 0, after the partials were gathered: merge in position order and finish the step."""
         self.m._check(engine.lib().ava_split_step_end(self.m.h, self.state.h, self.gathered.data_ptr(), self.world, logits_ptr, next_ptr))
 
+    # ---- the exchange behind the C ABI: a communicator of the engine's own, NCCL loaded by the library itself
+    def make_comm(self):
+        """Collective over `dist` (any backend): rank 0 draws the id, everyone joins.  After it, step_c is the whole token."""
+        ident = C.create_string_buffer(128)
+        if self.rank == 0:
+            self.m._check(engine.lib().ava_nccl_unique_id(ident))
+        if self.world > 1:
+            box = [ident.raw if self.rank == 0 else None]
+            self.dist.broadcast_object_list(box, src=0)
+            ident = C.create_string_buffer(box[0], 128)
+        comm = C.c_void_p()
+        self.m._check(engine.lib().ava_nccl_comm_init(self.m.h, self.world, self.rank, ident, C.byref(comm)))
+        self.comm = comm
+
+    def close_comm(self):
+        if getattr(self, "comm", None):
+            engine.lib().ava_nccl_comm_destroy(self.comm)
+            self.comm = None
+
+    def step_c(self, tok_ptr: int | None, logits_ptr=None, next_ptr=None):
+        """One token as one call of the library (ava_split_step): both collectives inside, on the engine's stream."""
+        comm = getattr(self, "comm", None)
+        self.m._check(engine.lib().ava_split_step(self.m.h, self.state.h, comm, self.rank, self.world, tok_ptr, self.qkv.data_ptr(),
+                                                  self.partial.data_ptr(), self.gathered.data_ptr(), logits_ptr, next_ptr))
+
     def step(self, tok_ptr: int | None, logits_ptr=None, next_ptr=None):
         """One token with torch.distributed doing the exchange on the engine's stream."""
         torch, dist = self.torch, self.dist

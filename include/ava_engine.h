@@ -227,6 +227,24 @@ int ava_split_step_begin(ava_engine* e, ava_state* s, const uint32_t* tok_device
 int ava_shard_partial(ava_engine* e, ava_state* s, const float* qkv_device, float* partial_device);
 int ava_split_step_end(ava_engine* e, ava_state* s, const float* gathered_device, int32_t world, float* logits_device, uint32_t* next_device);
 
+/* The same token as ONE call, the two collectives included: rank 0 runs ava_split_step_begin, q,k,v are broadcast from
+ * rank 0, every rank runs ava_shard_partial, the partials are all-gathered, rank 0 runs ava_split_step_end; all of it
+ * queued on the engine's stream.  nccl_comm is an ncclComm_t of `world` ranks whose rank numbers are the shard's (the
+ * caller's own communicator, or one made by ava_nccl_comm_init); NCCL is reached with dlopen at the first call
+ * (libnccl.so.2, or the library AVA_NCCL_LIB names), the engine's library does not link against it.  The buffers are the
+ * caller's device memory: qkv [rows, 3 d], partial [rows][heads][ava_shard_parts()][2 + head size], gathered `world`
+ * times that; tok_device, logits_device and next_device are read on rank 0 only.  world == 1 needs no communicator
+ * (NULL: the gather is a copy; given one, the two collectives run through it all the same).
+ * AVA_NOT_APPLICABLE when no NCCL library can be loaded.
+ * ava_nccl_unique_id fills 128 bytes on one rank (the caller carries them to the others by any means it has);
+ * ava_nccl_comm_init makes the communicator on the engine's device; ava_nccl_version reports the loaded library's. */
+int ava_split_step(ava_engine* e, ava_state* s, void* nccl_comm, int32_t rank, int32_t world, const uint32_t* tok_device, float* qkv_device,
+                   float* partial_device, float* gathered_device, float* logits_device, uint32_t* next_device);
+int ava_nccl_unique_id(unsigned char* id128);
+int ava_nccl_comm_init(ava_engine* e, int32_t world, int32_t rank, const unsigned char* id128, void** comm);
+int ava_nccl_comm_destroy(void* comm);
+int ava_nccl_version(int32_t* version);
+
 /* One traced token of a one-row state: `Model::step_trace` (src/model.rs, record built in src/model/fstep/arch.rs:420-476,
  * the chat app's event feed).  The step is the plain one (same logits, same state); the record holds copies of what it
  * computed and sizes taken from those copies on the host.  ava_trace_get(name, block): per block "spikes" [d] as they reach

@@ -76,3 +76,46 @@ def test_split_store_decode_matches_the_oracle(orc, world, parts):
         assert counts[-1] >= decode
     finally:
         orc.reset_math()
+
+
+def test_split_step_as_one_call_with_its_own_communicator():
+    """ava_split_step on one rank: NCCL loaded by the library (dlopen), a communicator of one rank made through the C
+    ABI, the token stepped as one call; the logits are the bits of the three-call form on a twin state (with one rank
+    the all-gather is a copy either way), and the communicator's broadcast and all-gather ran on the engine's stream."""
+    import ctypes as C
+    import torch
+    build.build()
+    ver = C.c_int32(0)
+    if engine.lib().ava_nccl_version(C.byref(ver)) != 0:
+        pytest.skip("no NCCL library to load")
+    cfg = config.tiny(eng_head_size=64, eng_store_bf16=1)
+    w = synth.model(cfg, 0, "awake")
+    ids = synth.token_ids(cfg["vocab"], 1, 24, seed0=5)
+    dev = torch.device("cuda", 0)
+    outs = []
+    for one_call in (False, True):
+        sk = longctx.SplitKV(engine.Model(cfg, w), 1, 64, 0, 1, dist=None, seg_len=8)
+        engine.lib().ava_state_set_kv_shard(sk.state.h, 0, 1, 64, 0)
+        if one_call:
+            sk.make_comm()
+        logits = torch.empty(1, cfg["vocab"], dtype=torch.float32, device=dev)
+        got = []
+        for t in range(24):
+            tok = torch.tensor([int(ids[0, t])], dtype=torch.int32, device=dev)
+            torch.cuda.synchronize()
+            if one_call:
+                sk.step_c(tok.data_ptr(), logits.data_ptr(), None)
+            else:
+                sk.begin(tok.data_ptr())
+                sk.partial_read()
+                sk.m.sync()
+                sk.gathered.copy_(sk.partial.unsqueeze(0))
+                torch.cuda.synchronize()
+                sk.end(logits.data_ptr(), None)
+            sk.m.sync()
+            got.append(logits.cpu().numpy().copy())
+        if one_call:
+            sk.close_comm()
+        outs.append(np.stack(got))
+    assert ver.value >= 20000
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
