@@ -54,14 +54,16 @@ pub struct AvaEngine { _p: [u8; 0] }
 pub struct AvaState { _p: [u8; 0] }
 #[repr(C)]
 pub struct AvaCkpt { _p: [u8; 0] }
+#[repr(C)]
+pub struct AvaTrace { _p: [u8; 0] }
 
 #[link(name = "ava_engine")]
 extern "C" {
+    // ---- begin: generated from include/ava_engine.h by bindings/gen_extern.py
     pub fn ava_engine_create(cfg: *const AvaConfig, device: c_int, out: *mut *mut AvaEngine) -> c_int;
     pub fn ava_engine_destroy(e: *mut AvaEngine);
     pub fn ava_last_error(e: *const AvaEngine) -> *const c_char;
     pub fn ava_engine_set_f32(e: *mut AvaEngine, name: *const c_char, data: *const f32, n: i64) -> c_int;
-    /// --letters: every token's spelling, bytes[offsets[t]..offsets[t + 1]] (vocab + 1 offsets), before finalize
     pub fn ava_engine_set_token_bytes(e: *mut AvaEngine, bytes: *const u8, offsets: *const i64) -> c_int;
     pub fn ava_engine_set_q8(e: *mut AvaEngine, name: *const c_char, q: *const i8, scale: *const f32, din: i32, dout: i32) -> c_int;
     pub fn ava_engine_set_q8_from_f32(e: *mut AvaEngine, name: *const c_char, w: *const f32, din: i32, dout: i32) -> c_int;
@@ -75,38 +77,89 @@ extern "C" {
     pub fn ava_state_seen(s: *const AvaState, row: i32) -> i64;
     pub fn ava_state_len(s: *const AvaState, row: i32, name: *const c_char) -> i64;
     pub fn ava_state_export(s: *const AvaState, row: i32, name: *const c_char, out: *mut f32) -> c_int;
-    pub fn ava_state_import(s: *mut AvaState, row: i32, name: *const c_char, data: *const f32, n: i64) -> c_int;
+    pub fn ava_state_import(s: *mut AvaState, row: i32, name: *const c_char, in_: *const f32, n: i64) -> c_int;
     pub fn ava_step(e: *mut AvaEngine, s: *mut AvaState, tok: *const u32, logits: *mut f32) -> c_int;
     pub fn ava_step_greedy(e: *mut AvaEngine, s: *mut AvaState, tok: *const u32, next: *mut u32) -> c_int;
     pub fn ava_forward_with_state(e: *mut AvaEngine, s: *mut AvaState, ids: *const u32, t: i32, last_only: i32, logits: *mut f32) -> c_int;
-    pub fn ava_step_device(e: *mut AvaEngine, s: *mut AvaState, tok: *const u32, logits: *mut f32, next: *mut u32) -> c_int;
+    pub fn ava_step_device(e: *mut AvaEngine, s: *mut AvaState, tok_device: *const u32, logits_device: *mut f32, next_device: *mut u32) -> c_int;
+    pub fn ava_prefill_device(e: *mut AvaEngine, s: *mut AvaState, tok_device: *const u32, t: i32, chunk: i32, logits_device: *mut f32, next_device: *mut u32) -> c_int;
     pub fn ava_sync(e: *mut AvaEngine) -> c_int;
     pub fn ava_engine_stream(e: *mut AvaEngine) -> *mut c_void;
+    pub fn ava_engine_launches(e: *const AvaEngine) -> i64;
+    pub fn ava_engine_bytes(e: *const AvaEngine) -> i64;
+    pub fn ava_state_bytes(s: *const AvaState) -> i64;
+    pub fn ava_engine_set_segmented_read(e: *mut AvaEngine, seg_len: i32) -> c_int;
+    pub fn ava_engine_set_lanes(e: *mut AvaEngine, lanes: i32) -> c_int;
     pub fn ava_engine_set_fast_products(e: *mut AvaEngine, on: i32) -> c_int;
-    pub fn ava_engine_config(e: *const AvaEngine) -> *const AvaConfig;
-    pub fn ava_engine_fingerprint(e: *const AvaEngine) -> u64;
-    // files: src/ckpt.rs, src/arch.rs `from_flags`
+    pub fn ava_engine_set_chunked_memory(e: *mut AvaEngine, on: i32) -> c_int;
+    pub fn ava_engine_chunked_memory_counts(e: *const AvaEngine, chunked: *mut i64, token_loop: *mut i64, engram_chunks: *mut i64) -> c_int;
+    pub fn ava_state_set_kv_shard(s: *mut AvaState, rank: i32, world: i32, block: i64, position: i64) -> c_int;
+    pub fn ava_shard_parts(e: *const AvaEngine, s: *const AvaState) -> i32;
+    pub fn ava_split_step_begin(e: *mut AvaEngine, s: *mut AvaState, tok_device: *const u32, qkv_device: *mut f32) -> c_int;
+    pub fn ava_shard_partial(e: *mut AvaEngine, s: *mut AvaState, qkv_device: *const f32, partial_device: *mut f32) -> c_int;
+    pub fn ava_split_step_end(e: *mut AvaEngine, s: *mut AvaState, gathered_device: *const f32, world: i32, logits_device: *mut f32, next_device: *mut u32) -> c_int;
+    pub fn ava_split_step(e: *mut AvaEngine, s: *mut AvaState, nccl_comm: *mut c_void, rank: i32, world: i32, tok_device: *const u32, qkv_device: *mut f32, partial_device: *mut f32, gathered_device: *mut f32, logits_device: *mut f32, next_device: *mut u32) -> c_int;
+    pub fn ava_nccl_unique_id(id128: *mut u8) -> c_int;
+    pub fn ava_nccl_comm_init(e: *mut AvaEngine, world: i32, rank: i32, id128: *const u8, comm: *mut *mut c_void) -> c_int;
+    pub fn ava_nccl_comm_destroy(comm: *mut c_void) -> c_int;
+    pub fn ava_nccl_version(version: *mut i32) -> c_int;
+    pub fn ava_step_trace(e: *mut AvaEngine, s: *mut AvaState, tok: u32, logits: *mut f32, out: *mut *mut AvaTrace) -> c_int;
+    pub fn ava_trace_get(t: *const AvaTrace, name: *const c_char, block: i32, out: *mut f32, cap: i64) -> i64;
+    pub fn ava_trace_free(t: *mut AvaTrace);
+    pub fn ava_prof_enable(e: *mut AvaEngine, on: i32) -> c_int;
+    pub fn ava_prof_read(e: *mut AvaEngine, kernel: *const c_char, launches: *mut i64, ms: *mut f64) -> c_int;
+    pub fn ava_prof_names(e: *mut AvaEngine, out: *mut c_char, cap: i32) -> c_int;
+    pub fn ava_debug_keep(e: *mut AvaEngine, on: i32) -> c_int;
+    pub fn ava_debug_width(e: *const AvaEngine, name: *const c_char) -> i64;
+    pub fn ava_debug_get(e: *mut AvaEngine, name: *const c_char, block: i32, out: *mut f32) -> c_int;
     pub fn ava_loader_error() -> *const c_char;
     pub fn ava_ckpt_open(path: *const c_char, out: *mut *mut AvaCkpt) -> c_int;
     pub fn ava_ckpt_close(c: *mut AvaCkpt);
     pub fn ava_ckpt_count(c: *const AvaCkpt) -> i32;
     pub fn ava_ckpt_find(c: *const AvaCkpt, name: *const c_char) -> i32;
+    pub fn ava_ckpt_tensor(c: *const AvaCkpt, i: i32, name: *mut *const c_char, dtype: *mut *const c_char, rank: *mut i32, dims: *mut i64) -> c_int;
     pub fn ava_ckpt_read_f32(c: *const AvaCkpt, i: i32, out: *mut f32, n: i64) -> c_int;
+    pub fn ava_ckpt_read_u32(c: *const AvaCkpt, i: i32, out: *mut u32, n: i64) -> c_int;
     pub fn ava_arch_flags(flags: *const c_char, cfg: *mut AvaConfig) -> c_int;
     pub fn ava_config_from_ckpt(c: *const AvaCkpt, kind: *const c_char, arch_flags: *const c_char, out: *mut AvaConfig) -> c_int;
     pub fn ava_engine_load_ckpt(e: *mut AvaEngine, c: *const AvaCkpt) -> c_int;
-    // carried state on disk: `State::save` / `State::load`, `ConvStore`
+    pub fn ava_engine_fingerprint(e: *const AvaEngine) -> u64;
+    pub fn ava_state_engine(s: *const AvaState) -> *mut AvaEngine;
+    pub fn ava_state_set_seen(s: *mut AvaState, row: i32, seen: i64) -> c_int;
     pub fn ava_state_save(s: *const AvaState, path: *const c_char) -> c_int;
     pub fn ava_state_load(e: *mut AvaEngine, path: *const c_char, max_ctx: i32, out: *mut *mut AvaState) -> c_int;
+    pub fn ava_conv_path(dir: *const c_char, id: *const c_char, out: *mut c_char, n: i64) -> c_int;
     pub fn ava_conv_save(dir: *const c_char, id: *const c_char, s: *const AvaState) -> c_int;
     pub fn ava_conv_load(e: *mut AvaEngine, dir: *const c_char, id: *const c_char, max_ctx: i32, out: *mut *mut AvaState, found: *mut i32) -> c_int;
-    // `diary::pick`, `state::generate`
-    pub fn ava_pick(logits: *const f32, vocab: i32, temperature: f32, top_k: i32, rng_state: *mut u64, token: *mut u32, logp: *mut f32,
-                    sample_logp: *mut f32) -> c_int;
-    pub fn ava_generate(e: *mut AvaEngine, prompts: *const u32, prompt_len: *const i32, n_prompts: i32, max_new: i32, batch_rows: i32, max_ctx: i32,
-                        eos: u32, pick: Option<extern "C" fn(*mut c_void, i32, *const f32, i32) -> u32>,
-                        stop: Option<extern "C" fn(*mut c_void, i32, *const u32, i32) -> c_int>, user: *mut c_void, out: *mut u32,
-                        out_len: *mut i32) -> c_int;
+    pub fn ava_engine_config(e: *const AvaEngine) -> *const AvaConfig;
+    pub fn ava_engine_device(e: *const AvaEngine) -> c_int;
+    pub fn ava_splitmix64_next(state: *mut u64) -> u64;
+    pub fn ava_pick(logits: *const f32, vocab: i32, temperature: f32, top_k: i32, rng_state: *mut u64, token: *mut u32, logp: *mut f32, sample_logp: *mut f32) -> c_int;
+    pub fn ava_step_sample(e: *mut AvaEngine, s: *mut AvaState, tok: *const u32, temperature: f32, top_k: i32, uniform: *const f64, next: *mut u32) -> c_int;
+    pub fn ava_generate(e: *mut AvaEngine, prompts: *const u32, prompt_len: *const i32, n_prompts: i32, max_new: i32, batch_rows: i32, max_ctx: i32, eos: u32, pick: Option<extern "C" fn(*mut c_void, i32, *const f32, i32) -> u32>, stop: Option<extern "C" fn(*mut c_void, i32, *const u32, i32) -> c_int>, user: *mut c_void, out: *mut u32, out_len: *mut i32) -> c_int;
+    pub fn ava_generate_sampled(e: *mut AvaEngine, prompts: *const u32, prompt_len: *const i32, n_prompts: i32, max_new: i32, batch_rows: i32, max_ctx: i32, eos: u32, temperature: f32, top_k: i32, rng_state: *mut u64, stop: Option<extern "C" fn(*mut c_void, i32, *const u32, i32) -> c_int>, user: *mut c_void, out: *mut u32, out_len: *mut i32) -> c_int;
+    pub fn ava_op_q8_matmul(device: c_int, x: *const f32, m: i32, q: *const i8, scale: *const f32, din: i32, dout: i32, y: *mut f32) -> c_int;
+    pub fn ava_op_q8_event_matmul(device: c_int, x: *const f32, m: i32, q: *const i8, scale: *const f32, din: i32, dout: i32, y: *mut f32) -> c_int;
+    pub fn ava_op_q8_tc_matmul(device: c_int, x: *const f32, m: i32, q: *const i8, scale: *const f32, din: i32, dout: i32, y: *mut f32, reps: i32, ms_per_launch: *mut f32) -> c_int;
+    pub fn ava_op_sample(device: c_int, logits: *const f32, m: i32, vocab: i32, temperature: f32, top_k: i32, uniform: *const f64, next: *mut u32) -> c_int;
+    pub fn ava_op_rmsnorm(device: c_int, x: *const f32, gain: *const f32, m: i32, n: i32, y: *mut f32) -> c_int;
+    pub fn ava_op_lif(device: c_int, cur: *const f32, beta: *const f32, theta: *const f32, rho: *const f32, gain: *const f32, spikes: i32, v0: *const f32, s0: *const f32, a0: *const f32, m: i32, d: i32, s1: *mut f32, v1: *mut f32, a1: *mut f32) -> c_int;
+    pub fn ava_op_kwta(device: c_int, u: *const f32, m: i32, n: i32, k: i32, relu2: i32, a: *mut f32) -> c_int;
+    pub fn ava_op_mem_heads(device: c_int, m: i32, hs: i32, e: *const f32, v: *const f32, w: *const f32, ah: *const f32, qg: *const f32, ex: *const f32, qw: *const f32, qa: *const f32, f: *mut f32, y: *mut f32) -> c_int;
+    pub fn ava_mem_heads_static(device: c_int, stream: *mut c_void, m: i32, hs: i32, e: *const f32, v: *const f32, w: *const f32, ah: *const f32, qg: *const f32, ex: *const f32, qw: *const f32, qa: *const f32, f: *mut f32, y: *mut f32) -> c_int;
+    pub fn ava_static_last_error() -> *const c_char;
+    pub fn ava_op_attend(device: c_int, m: i32, n: i32, hs: i32, bf16_store: i32, q: *const f32, kc: *const f32, vc: *const f32, out: *mut f32) -> c_int;
+    pub fn ava_op_engram_chunk(device: c_int, rows: i32, t: i32, n0: i32, start: i32, d: i32, qkv: *const f32, k_prev: *const f32, v_prev: *const f32, o: *mut f32) -> c_int;
+    pub fn ava_op_tc_bgemm(device: c_int, batch: i32, m: i32, n: i32, k: i32, a: *const f32, b: *const f32, colscale: *const f32, c: *mut f32, c_limb_sum: *mut f32) -> c_int;
+    pub fn ava_op_mem_chunk(device: c_int, t: i32, hb: i32, hs: i32, qn: *const f32, e: *const f32, w: *const f32, ah: *const f32, v: *const f32, la: *const f32, f: *mut f32, y: *mut f32, out_of_range: *mut i32) -> c_int;
+    pub fn ava_debug_mem_heads_wait_runs_out(device: c_int, m: i32, hs: i32, chunk: i32, poll_limit: u32, state_changed: *mut i32) -> c_int;
+    pub fn ava_host_expf(x: f32) -> f32;
+    pub fn ava_host_logf(x: f32) -> f32;
+    pub fn ava_host_rsqrtf(x: f32) -> f32;
+    pub fn ava_host_sinf(x: f32) -> f32;
+    pub fn ava_host_cosf(x: f32) -> f32;
+    pub fn ava_op_math(device: c_int, which: i32, x: *const f32, n: i64, y: *mut f32) -> c_int;
+    // ---- end: generated
 }
 
 #[derive(Debug)]

@@ -119,3 +119,16 @@ def test_static_entry_refuses_an_unaligned_vector_before_any_launch(L):
         args = [ok] * 10
         args[i] = off2
         assert L.ava_mem_heads_static(0, None, 1, 64, *args) == engine.ERR_ARG
+
+
+def test_rust_binding_declares_exactly_the_headers_entry_points():
+    """bindings/ava_engine.rs: the names in its extern "C" block are the header's, and the block is what
+    bindings/gen_extern.py writes from the header today (so a new entry point cannot be forgotten there)."""
+    import subprocess
+    import sys
+    rs = open(os.path.join(ROOT, "bindings", "ava_engine.rs")).read()
+    block = rs[rs.index('extern "C" {'):]
+    block = block[:block.index("\n}\n")]
+    in_rs = sorted(set(re.findall(r"pub fn (ava_[a-z0-9_]+)\s*\(", block)))
+    assert in_rs == declared_symbols()
+    assert subprocess.run([sys.executable, os.path.join(ROOT, "bindings", "gen_extern.py"), "--check"]).returncode == 0
