@@ -173,6 +173,15 @@ def run_reference(args, cfg, rank):
     print(json.dumps(line), flush=True)
 
 
+def waves_note(total: int, world: int, rows: int) -> dict:
+    """Sequences are independent, so a job larger than the GPUs' memory runs as waves of world x rows resident sequences,
+    each wave from its prompt to its last token before the next starts; tokens/s is that of one wave."""
+    if total <= 0:
+        return {}
+    return {"sequences_total": total, "waves": -(-total // (world * rows)), "wave_schedule": "waves of gpus x rows_per_gpu resident sequences run one after "
+            "another (no state leaves the GPU); value is the rate while a wave runs"}
+
+
 def prefill_tensor_flops(cfg, tokens):
     """Tensor-core FLOPs per prompt token of the tolerance mode's chunked pass: (executed, algorithmic).  Executed counts
     every limb product the kernels issue (3 per dense product: three activation limbs x one exact bf16 weight; 6 per
@@ -260,6 +269,8 @@ def main():
     ap.add_argument("--small", action="store_true", help="a small model and batch (profiling captures, not a bench value)")
     ap.add_argument("--scaled", action="store_true", help="benchmark configuration 3: 24 blocks, d 2048, wide 8192, vocab 32768 (use --rows 128: an 8-GPU share of 1024 sequences)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--total-sequences", type=int, default=0, help="the job's sequences over all GPUs when they do not all fit at once (configuration 3 "
+                    "on 1 or 2 GPUs): they run as waves of gpus x rows resident sequences, one wave after another; the line states the waves")
     ap.add_argument("--parts", action="store_true", help="the same workload with the nine Ava-0.4 parts switched on (their cost; not the headline configuration)")
     ap.add_argument("--prefill-tokens", type=int, default=1024, help="tokens per row of the exact prompt-reading sample (config 2 is 8192: about half a minute)")
     ap.add_argument("--fast-prefill-tokens", type=int, default=8192, help="tokens per row of the tolerance mode's prompt-reading leg (config 2: 8192)")
@@ -438,7 +449,7 @@ def main():
                    ("small profiling case" if args.small else "benchmark configuration 3: scaled Ava (24 blocks, d 2048, wide 8192, kWTA 2048, vocab 32768, one "
                     "2048x2048 f32 fast-synapse matrix per block)"),
                    "parts": "the nine Ava-0.4 parts on (stp, neuromod 3, dendrite, letters, dopamine, mood, rhythm, thalamus, cerebellum head 12288)" if args.parts else "none",
-                   "rows_per_gpu": rows, "kv_len_timed": [prompt + W, prompt + W + K], "l2": "per-step inputs (state "
+                   "rows_per_gpu": rows, **waves_note(args.total_sequences, world, rows), "kv_len_timed": [prompt + W, prompt + W + K], "l2": "per-step inputs (state "
                    f"{state.nbytes / 1e9:.2f} GB per GPU) are larger than L2", "sequences": "independent, sharded by rank, no collective"},
         "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": rows * 4, "d2h_bytes_per_step": rows * cfg["vocab"] * 4,
                 "steps": e2e_steps, "call": "ava_step (host token ids in, host logits out, pinned buffers)",
