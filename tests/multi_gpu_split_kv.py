@@ -27,6 +27,7 @@ def main():
     ap.add_argument("--decode", type=int, default=32)
     ap.add_argument("--full", action="store_true", help="the Ava-0.4-shaped model instead of the small one")
     ap.add_argument("--no-check", action="store_true")
+    ap.add_argument("--seg-len", type=int, default=512, help="keys per segment of the partial read (one block of threads sums a segment in key order)")
     ap.add_argument("--import-keys", type=int, default=0, help="no prompt is read: the store starts with this many positions of seeded random keys and "
                     "values (bf16-exact), dealt out by position, and the membranes and fast weights start fresh (benchmark configuration 4 at its full 131072)")
     ap.add_argument("--torch-exchange", action="store_true", help="the two collectives through torch.distributed instead of the library's own call")
@@ -45,7 +46,7 @@ def main():
     P, D = (args.import_keys or args.prompt), args.decode
     block = -(-P // world)
     cap = block + D + 8
-    sk = longctx.SplitKV(model, 1, cap, rank, world, dist=dist)
+    sk = longctx.SplitKV(model, 1, cap, rank, world, dist=dist, seg_len=args.seg_len)
     if not args.torch_exchange:
         sk.make_comm()   # a communicator made through the C ABI; every token is then one call of the library
     ids = synth.token_ids(cfg["vocab"], 1, P + D, seed0=7)
@@ -101,7 +102,7 @@ def main():
     dist.all_gather_object(counts, sk.state.get(0, "eng.k").size // cfg["d"])
     if rank == 0:
         line = {"what": "one sequence, engram store split by position", "world": world, "prompt": P, "decode": D,
-                "tokens_per_rank": counts, "ms_per_token": float(t_ms.item()) / D, "exchange": "torch.distributed" if args.torch_exchange else "ava_split_step (NCCL by dlopen, own communicator)", "prompt_read_s": prompt_s, "checked": not args.no_check}
+                "tokens_per_rank": counts, "ms_per_token": float(t_ms.item()) / D, "seg_len": args.seg_len, "exchange": "torch.distributed" if args.torch_exchange else "ava_split_step (NCCL by dlopen, own communicator)", "prompt_read_s": prompt_s, "checked": not args.no_check}
         assert sum(counts) == P + D, counts
         if not args.no_check:
             from oracle import oracle
