@@ -2,7 +2,7 @@
  *
  * The reference (nochallenge/ava, crate design-tests/nn/gpu) has no FFI of its own: its seams are Rust-internal.
  * Each entry point below names the reference interface it stands in for (file:line inside the reference project),
- * so that a Rust `extern "C"` block can bind them one to one (see bindings/ava_engine.rs and INTEGRATION.md).
+ * so that a Rust `extern "C"` block can bind them one to one (bindings/ava_engine.rs is that block).
  *
  * Conventions
  *   - plain pointers and sizes only; every buffer is HOST memory unless the name says `_device`;
