@@ -30,7 +30,7 @@ sys.path.insert(0, ROOT)
 METRIC = "decode tokens/s (batch 256 per GPU, Ava-0.4-shaped int8 model)"
 UNIT = "tokens/s"
 ROWS_PER_GPU = 256
-TRAFFIC_PER_STATE_BYTE = 1154.7e6 / 1207959552.0  # ncu: DRAM read + write per algorithmic byte of the state pass (profiles/)
+TRAFFIC_PER_STATE_BYTE = 0.813  # ncu: DRAM bytes moved per algorithmic byte of the state pass (capture of a 64-row lane, profiles/)
 MEAN_CTX = 1536  # mean KV length of the decode phase of configuration 1 (1024 prompt + 1024 decode)
 
 
@@ -430,9 +430,9 @@ def main():
     state_bytes = rows * 2 * 4 * cfg["d"] * cfg["head_size"]        # read once + written once, f32, per launch
     peak, peak_src = peaks()
     achieved = state_bytes / (ms_mh / max(n_mh, 1) * 1e-3) / 1e9 if n_mh else 0.0
-    # DRAM bytes one launch moved under ncu (dram__bytes_read.sum + dram__bytes_write.sum of the state pass over 256 rows
-    # of one 768x768 matrix, from the capture summarised under profiles/): a constant of that profile, scaled by the
-    # state a launch streams, not something this run measures
+    # DRAM bytes one launch moved under ncu (the state pass over a 64-row lane of 768x768 matrices, from the capture
+    # summarised under profiles/): a constant of that profile, scaled by the state a launch streams, not something this
+    # run measures
     traffic = TRAFFIC_PER_STATE_BYTE * state_bytes
     # the whole step against the HBM roofline: algorithmic bytes per decoded token (state + weights/rows + KV + LIF)
     kv_bytes = args.ctx * 2 * cfg["d"] * 2 if cfg["eng_block"] >= 0 else 0
