@@ -206,6 +206,11 @@ struct ava_state {
     // other, the step before's, is applied).  mem_f is one update behind while `pending` is set; flush_pending()
     // brings it up to date for every other reader.
     Dev pend;
+    // Commit at the end (ava_state_set_commit_at_end): a second copy of the fast weights that a one-token step writes while
+    // it reads the first (the two change places when the call has succeeded), and room for a copy of the small carried
+    // tensors taken before a call.
+    bool commit_at_end = false, txn_pingpong = false;
+    Dev mem_f_alt, snap;
     bool pending = false;
     int pend_set = 0;         // the set the LAST step wrote
     float* pend_at(int set, int what, int block) { return pend.as<float>() + ((((size_t)set * 5 + what) * e->cfg.n_blocks + block) * rows) * e->cfg.d; }
@@ -781,6 +786,7 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
         } else if (stream) {
             MemStreamArgs ms{};
             ms.f = mh.f; ms.M = rows; ms.nh = nh; ms.hs = hs; ms.cw = e->cw;
+            if (s->txn_pingpong && s->pending) ms.f_out = s->mem_f_alt.as<float>() + ((size_t)i * Sd + so) * hs;
             ms.e = mp.e; ms.qg = mp.qg; ms.v = mp.v; ms.qw = mp.qw; ms.qa = mp.qa;
             ms.y = mh.y;
             ms.rr_out = s->pend_at(wset, 4, i) + so;
@@ -1856,16 +1862,120 @@ int ava_sync(ava_engine* e) {
     return finish(e);
 }
 
+// ---- commit at the end (src/model/fstep/arch.rs:1059-1069: "everything computed: the State moves on") ----------------
+// The kernels update the carried state as they go.  For a state with commit_at_end set, a host-facing call brackets its
+// work: the small carried tensors (membranes, traces, the parts' states, the engram's counts) are copied aside first;
+// the fast weights, the bulk of the state, are not copied for a one-token step: the streaming pass reads one copy and
+// writes the other, and the two change places only when the call has succeeded (no extra traffic, twice the memory).
+// A prompt (several tokens per row) or a memory with momentum works in place, so the fast weights are copied aside
+// whole for such a call.  The engram's keys and values need no copy: a token only ever fills a free slot, and the
+// counts say which slots hold tokens.  When the call fails after work was queued (a non-finite gate, a full store, a
+// wait that ran out), everything is put back and the state is as it was before the call.
+struct Txn {
+    bool active = false, pingpong = false, whole = false, was_pending = false;
+    int pend_set = 0;
+    int64_t shard_pos = 0;
+    std::vector<int32_t> n_host, start_host;
+    std::vector<int64_t> seen;
+    Dev whole_f, whole_s, whole_pend;
+};
+
+std::vector<Dev*> small_carried(ava_state* s) {
+    return {&s->lif_v, &s->lif_s, &s->lif_a, &s->stp_u, &s->stp_x, &s->rh, &s->sur_prev, &s->sur_valid, &s->sur_last, &s->mood, &s->eng_n, &s->eng_start};
+}
+
+int txn_begin(ava_engine* e, ava_state* s, bool one_token, Txn& t) {
+    if (!s->commit_at_end) return AVA_OK;
+    const ava_config& c = e->cfg;
+    t.active = true;
+    t.was_pending = s->pending;
+    t.pend_set = s->pend_set;
+    t.shard_pos = s->shard_pos;
+    t.n_host = s->n_host; t.start_host = s->start_host; t.seen = s->seen;
+    size_t need = 0;
+    for (Dev* d : small_carried(s)) need += (d->bytes + 255) & ~(size_t)255;
+    if (s->snap.bytes < need) CK(s->snap.alloc(need));
+    size_t at = 0;
+    for (Dev* d : small_carried(s)) {
+        if (d->bytes) CK(cudaMemcpyAsync((char*)s->snap.p + at, d->p, d->bytes, cudaMemcpyDeviceToDevice, e->stream));
+        at += (d->bytes + 255) & ~(size_t)255;
+    }
+    t.pingpong = one_token && c.fast_mem && !(c.mem_momentum > 0.0f);
+    if (t.pingpong) {
+        if (!s->mem_f_alt.p) CK(s->mem_f_alt.alloc(s->mem_f.bytes));
+        s->txn_pingpong = true;
+    } else if (c.fast_mem) {
+        t.whole = true;
+        CK(t.whole_f.alloc(s->mem_f.bytes));
+        CK(cudaMemcpyAsync(t.whole_f.p, s->mem_f.p, s->mem_f.bytes, cudaMemcpyDeviceToDevice, e->stream));
+        if (s->mem_s.bytes) {
+            CK(t.whole_s.alloc(s->mem_s.bytes));
+            CK(cudaMemcpyAsync(t.whole_s.p, s->mem_s.p, s->mem_s.bytes, cudaMemcpyDeviceToDevice, e->stream));
+        }
+        if (s->pend.bytes) {
+            CK(t.whole_pend.alloc(s->pend.bytes));
+            CK(cudaMemcpyAsync(t.whole_pend.p, s->pend.p, s->pend.bytes, cudaMemcpyDeviceToDevice, e->stream));
+        }
+    }
+    return AVA_OK;
+}
+
+// rc: what the call is about to return.  Success: the second copy of the fast weights becomes the state's.  Failure:
+// everything goes back (the stream is idle by then: finish() has waited, or nothing was queued after an early refusal).
+int txn_end(ava_engine* e, ava_state* s, Txn& t, int rc) {
+    if (!t.active) return rc;
+    s->txn_pingpong = false;
+    if (rc == AVA_OK) {
+        if (t.pingpong && t.was_pending) {   // the pass wrote the new weights there
+            std::swap(s->mem_f.p, s->mem_f_alt.p);
+            std::swap(s->mem_f.bytes, s->mem_f_alt.bytes);
+        }
+        return rc;
+    }
+    cudaStreamSynchronize(e->stream);
+    size_t at = 0;
+    for (Dev* d : small_carried(s)) {
+        if (d->bytes) cudaMemcpyAsync(d->p, (char*)s->snap.p + at, d->bytes, cudaMemcpyDeviceToDevice, e->stream);
+        at += (d->bytes + 255) & ~(size_t)255;
+    }
+    if (t.whole) {
+        cudaMemcpyAsync(s->mem_f.p, t.whole_f.p, s->mem_f.bytes, cudaMemcpyDeviceToDevice, e->stream);
+        if (s->mem_s.bytes) cudaMemcpyAsync(s->mem_s.p, t.whole_s.p, s->mem_s.bytes, cudaMemcpyDeviceToDevice, e->stream);
+        if (s->pend.bytes) cudaMemcpyAsync(s->pend.p, t.whole_pend.p, s->pend.bytes, cudaMemcpyDeviceToDevice, e->stream);
+    }
+    cudaStreamSynchronize(e->stream);
+    s->pending = t.was_pending;
+    s->pend_set = t.pend_set;
+    s->shard_pos = t.shard_pos;
+    s->n_host = t.n_host; s->start_host = t.start_host; s->seen = t.seen;
+    return rc;
+}
+
+int ava_state_set_commit_at_end(ava_state* s, int32_t on) {
+    if (!s) return AVA_ERR_ARG;
+    s->commit_at_end = on != 0;
+    if (!on) {
+        s->mem_f_alt.release();
+        s->snap.release();
+    }
+    return AVA_OK;
+}
+
 int ava_step(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits) {
     int rc = check_pair(e, s);
     if (rc) return rc;
     if (!tok || !logits) return e->fail(AVA_ERR_ARG, "null buffer");
     for (int r = 0; r < s->rows; ++r)
         if (tok[r] >= (uint32_t)e->cfg.vocab) return e->fail(AVA_ERR_ARG, "token %u of row %d outside the vocabulary", tok[r], r);
-    CK(cudaMemcpyAsync(e->tok.p, tok, s->rows * sizeof(uint32_t), cudaMemcpyHostToDevice, e->stream));
-    if ((rc = step_device(e, s, e->tok.as<uint32_t>(), e->logits.as<float>(), nullptr, true))) return rc;
-    CK(cudaMemcpyAsync(logits, e->logits.p, (size_t)s->rows * e->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost, e->stream));
-    return finish(e);
+    Txn txn;
+    if ((rc = txn_begin(e, s, true, txn))) return rc;
+    auto body = [&]() -> int {
+        CK(cudaMemcpyAsync(e->tok.p, tok, s->rows * sizeof(uint32_t), cudaMemcpyHostToDevice, e->stream));
+        if (const int rs = step_device(e, s, e->tok.as<uint32_t>(), e->logits.as<float>(), nullptr, true)) return rs;
+        CK(cudaMemcpyAsync(logits, e->logits.p, (size_t)s->rows * e->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost, e->stream));
+        return finish(e);
+    };
+    return txn_end(e, s, txn, body());
 }
 
 int ava_step_greedy(ava_engine* e, ava_state* s, const uint32_t* tok, uint32_t* next) {
@@ -1874,10 +1984,15 @@ int ava_step_greedy(ava_engine* e, ava_state* s, const uint32_t* tok, uint32_t* 
     if (!tok || !next) return e->fail(AVA_ERR_ARG, "null buffer");
     for (int r = 0; r < s->rows; ++r)
         if (tok[r] >= (uint32_t)e->cfg.vocab) return e->fail(AVA_ERR_ARG, "token %u of row %d outside the vocabulary", tok[r], r);
-    CK(cudaMemcpyAsync(e->tok.p, tok, s->rows * sizeof(uint32_t), cudaMemcpyHostToDevice, e->stream));
-    if ((rc = step_device(e, s, e->tok.as<uint32_t>(), nullptr, e->next.as<uint32_t>(), false))) return rc;
-    CK(cudaMemcpyAsync(next, e->next.p, s->rows * sizeof(uint32_t), cudaMemcpyDeviceToHost, e->stream));
-    return finish(e);
+    Txn txn;
+    if ((rc = txn_begin(e, s, true, txn))) return rc;
+    auto body = [&]() -> int {
+        CK(cudaMemcpyAsync(e->tok.p, tok, s->rows * sizeof(uint32_t), cudaMemcpyHostToDevice, e->stream));
+        if (const int rs = step_device(e, s, e->tok.as<uint32_t>(), nullptr, e->next.as<uint32_t>(), false)) return rs;
+        CK(cudaMemcpyAsync(next, e->next.p, s->rows * sizeof(uint32_t), cudaMemcpyDeviceToHost, e->stream));
+        return finish(e);
+    };
+    return txn_end(e, s, txn, body());
 }
 
 int ava_step_sample(ava_engine* e, ava_state* s, const uint32_t* tok, float temperature, int32_t top_k, const double* uniform, uint32_t* next) {
@@ -1890,14 +2005,19 @@ int ava_step_sample(ava_engine* e, ava_state* s, const uint32_t* tok, float temp
     // asked before anything moves: a refusal leaves the state as it was
     if (!sample_covered(e->cfg.vocab, top_k))
         return e->fail(AVA_NOT_APPLICABLE, "the device sampler does not cover this vocabulary or top_k (top_k above 1024, or a vocabulary beyond its shared memory): pick on the host (ava_step + ava_pick)");
-    CK(cudaMemcpyAsync(e->tok.p, tok, s->rows * sizeof(uint32_t), cudaMemcpyHostToDevice, e->stream));
-    CK(cudaMemcpyAsync(e->uniform.p, uniform, s->rows * sizeof(double), cudaMemcpyHostToDevice, e->stream));
-    if ((rc = step_device(e, s, e->tok.as<uint32_t>(), e->logits.as<float>(), nullptr, true))) return rc;
-    if (!launch_sample(e->stream, e->logits.as<float>(), s->rows, e->cfg.vocab, temperature, top_k, e->uniform.as<double>(), e->next.as<uint32_t>()))
-        return e->fail(AVA_NOT_APPLICABLE, "the sampler does not cover this vocabulary or top_k: pick on the host (ava_step + ava_pick)");
-    e->launches++;
-    CK(cudaMemcpyAsync(next, e->next.p, s->rows * sizeof(uint32_t), cudaMemcpyDeviceToHost, e->stream));
-    return finish(e);
+    Txn txn;
+    if ((rc = txn_begin(e, s, true, txn))) return rc;
+    auto body = [&]() -> int {
+        CK(cudaMemcpyAsync(e->tok.p, tok, s->rows * sizeof(uint32_t), cudaMemcpyHostToDevice, e->stream));
+        CK(cudaMemcpyAsync(e->uniform.p, uniform, s->rows * sizeof(double), cudaMemcpyHostToDevice, e->stream));
+        if (const int rs = step_device(e, s, e->tok.as<uint32_t>(), e->logits.as<float>(), nullptr, true)) return rs;
+        if (!launch_sample(e->stream, e->logits.as<float>(), s->rows, e->cfg.vocab, temperature, top_k, e->uniform.as<double>(), e->next.as<uint32_t>()))
+            return e->fail(AVA_NOT_APPLICABLE, "the sampler does not cover this vocabulary or top_k: pick on the host (ava_step + ava_pick)");
+        e->launches++;
+        CK(cudaMemcpyAsync(next, e->next.p, s->rows * sizeof(uint32_t), cudaMemcpyDeviceToHost, e->stream));
+        return finish(e);
+    };
+    return txn_end(e, s, txn, body());
 }
 
 int ava_forward_with_state(ava_engine* e, ava_state* s, const uint32_t* ids, int32_t t, int32_t last_only, float* logits) {
@@ -1911,6 +2031,10 @@ int ava_forward_with_state(ava_engine* e, ava_state* s, const uint32_t* ids, int
     std::vector<uint32_t> col((size_t)t * M);
     for (int r = 0; r < M; ++r)
         for (int j = 0; j < t; ++j) col[(size_t)j * M + r] = ids[(size_t)r * t + j];
+    Txn txn;
+    if ((rc = txn_begin(e, s, false, txn))) return rc;
+    auto body = [&]() -> int {
+    int rc = AVA_OK;
     Dev dcol;
     CK(dcol.alloc(col.size() * sizeof(uint32_t)));
     CK(cudaMemcpyAsync(dcol.p, col.data(), col.size() * sizeof(uint32_t), cudaMemcpyHostToDevice, e->stream));
@@ -1937,6 +2061,8 @@ int ava_forward_with_state(ava_engine* e, ava_state* s, const uint32_t* ids, int
         }
     }
     return finish(e);
+    };
+    return txn_end(e, s, txn, body());
 }
 
 int ava_prefill_device(ava_engine* e, ava_state* s, const uint32_t* tok_device, int32_t t, int32_t chunk, float* logits_device, uint32_t* next_device) {

@@ -83,7 +83,9 @@ __global__ void __launch_bounds__(256) mem_stream_kernel(const MemStreamArgs a) 
     const int c = part * (int)blockDim.x * 4 + (threadIdx.x >> 5) * 128 + (threadIdx.x & 31) * 4;  // first of this lane's four columns
     if (c >= hs) return;
     // slice-major state: [slice][row][cw]; four neighbouring columns lie in one slice
-    float* fp = a.f + vo * hs + (size_t)(c / cw) * hs * cw + (c % cw);
+    const size_t fo = vo * hs + (size_t)(c / cw) * hs * cw + (c % cw);
+    float* fp = a.f + fo;
+    float* fq = (a.f_out ? a.f_out : a.f) + fo;   // where the updated state goes: in place, or the state's second copy
     float4 pv = make_float4(0.f, 0.f, 0.f, 0.f), prr = pv;
     if (PEND) {
         pv = *reinterpret_cast<const float4*>(a.pv + vo + c);
@@ -96,6 +98,7 @@ __global__ void __launch_bounds__(256) mem_stream_kernel(const MemStreamArgs a) 
     for (int i = 0; i < SD; ++i) buf[i] = ldg_stream<MODE>(fp + (size_t)i * cw);
     for (int row = 0; row < hs; row += SD) {
         float* rp = fp + (size_t)row * cw;
+        float* wp = fq + (size_t)row * cw;
 #pragma unroll
         for (int i4 = 0; i4 < SD; i4 += 4) {
             const float4 e4 = *reinterpret_cast<const float4*>(ve + row + i4), g4 = *reinterpret_cast<const float4*>(vqg + row + i4);
@@ -114,7 +117,7 @@ __global__ void __launch_bounds__(256) mem_stream_kernel(const MemStreamArgs a) 
                 if (row + SD < hs) buf[i] = ldg_stream<MODE>(rp + (size_t)(SD + i) * cw);  // the row sixteen ahead takes the freed register
                 if (PEND) {
                     f = pending_update(f, xx[j], ww[j], hh[j], pv, prr);
-                    stg_stream<MODE>(rp + (size_t)i * cw, f);
+                    stg_stream<MODE>(wp + (size_t)i * cw, f);
                 }
                 r.x = fma(f.x, ee[j], r.x); r.y = fma(f.y, ee[j], r.y); r.z = fma(f.z, ee[j], r.z); r.w = fma(f.w, ee[j], r.w);
                 t.x = fma(f.x, gg[j], t.x); t.y = fma(f.y, gg[j], t.y); t.z = fma(f.z, gg[j], t.z); t.w = fma(f.w, gg[j], t.w);

@@ -277,6 +277,7 @@ void launch_mem_heads_seq(cudaStream_t st, const MemHeadsArgs& a, int T);
 // pending update alone.  Same bits as the resident form.
 struct MemStreamArgs {
     float* f;                       // this block's fast weights, slice-major [M][nh][hs / cw][hs][cw]
+    float* f_out;                   // where the updated weights are written (nullptr: in place); used only with a pending update
     int M, nh, hs, cw;
     int parts;                      // set by the launcher: blocks a head's columns are split over
     const float *e, *qg, *v;        // this token: [M, nh * hs]

@@ -81,6 +81,7 @@ extern "C" {
     pub fn ava_step(e: *mut AvaEngine, s: *mut AvaState, tok: *const u32, logits: *mut f32) -> c_int;
     pub fn ava_step_greedy(e: *mut AvaEngine, s: *mut AvaState, tok: *const u32, next: *mut u32) -> c_int;
     pub fn ava_forward_with_state(e: *mut AvaEngine, s: *mut AvaState, ids: *const u32, t: i32, last_only: i32, logits: *mut f32) -> c_int;
+    pub fn ava_state_set_commit_at_end(s: *mut AvaState, on: i32) -> c_int;
     pub fn ava_step_device(e: *mut AvaEngine, s: *mut AvaState, tok_device: *const u32, logits_device: *mut f32, next_device: *mut u32) -> c_int;
     pub fn ava_prefill_device(e: *mut AvaEngine, s: *mut AvaState, tok_device: *const u32, t: i32, chunk: i32, logits_device: *mut f32, next_device: *mut u32) -> c_int;
     pub fn ava_sync(e: *mut AvaEngine) -> c_int;

@@ -157,6 +157,16 @@ int ava_step_greedy(ava_engine* e, ava_state* s, const uint32_t* tok, uint32_t* 
  * vocab], or [rows, vocab] of the last position when last_only (what `Model::feed` keeps, src/model.rs:1218-1227). */
 int ava_forward_with_state(ava_engine* e, ava_state* s, const uint32_t* ids, int32_t t, int32_t last_only, float* logits);
 
+/* Commit at the end, as the reference has it (src/model/fstep/arch.rs:1059-1069: the State moves on only once everything
+ * is computed; a refusal at :780-783, 861-864 leaves nothing changed).  The kernels update the carried state as they go;
+ * with this set (off by default), ava_step, ava_step_greedy, ava_step_sample and ava_forward_with_state put the state
+ * back as it was when they fail after work was queued (AVA_ERR_NONFINITE, a full engram store, a wait that ran out): the
+ * small carried tensors are copied aside before the call; the fast weights are not copied for a one-token step: the
+ * streaming pass reads one copy and writes a second, and the two change places on success (no extra traffic, twice the
+ * fast-weight memory).  A prompt, or a memory with momentum, works in place and copies the fast weights aside whole
+ * for the call.  The device-queued calls (ava_step_device, ava_prefill_device) report no status and commit as they go. */
+int ava_state_set_commit_at_end(ava_state* s, int32_t on);
+
 /* Device-resident forms for callers that keep tokens and logits in GPU memory (no host copies, no synchronise):
  * tok_device [rows] u32, logits_device [rows, vocab] f32 or NULL, next_device [rows] u32 or NULL.  Work is queued on
  * the engine's stream; ava_sync waits for it and returns the step's status. */

@@ -325,6 +325,63 @@ def test_nonfinite_gate_is_reported(orc):
     assert os_.last_status == 1 and os_.seen(0) == 0
 
 
+@pytest.mark.parametrize("parts", [False, True])
+def test_commit_at_end_puts_the_state_back(orc_same_math, parts):
+    """A state made to commit at the end: a step (and a prompt) that fails half-way, here on a token whose embedding
+    row is NaN, so that the gates of the first block are not finite after its membranes have already moved, leaves
+    every carried tensor as it was before the call, bit for bit, as the reference's step does (it commits last:
+    src/model/fstep/arch.rs:1059-1069; the oracle reports the refusal and does not move).  The steps before and after it
+    are the oracle's bits, so the second copy of the fast weights changes places correctly on success."""
+    orc = orc_same_math
+    extra = dict(stp=1, neuromod=3, dopamine=1, mood=4, rhythm=1) if parts else {}
+    cfg = config.tiny(eng_head_size=64, eng_store_bf16=1, **extra)
+    w = synth.model(cfg, 0, "awake")
+    bad = 7
+    emb = np.array(w["tok_emb"], np.float32, copy=True).reshape(cfg["vocab"], cfg["d"])
+    emb[bad] = np.nan
+    w["tok_emb"] = emb
+    gm, om = engine.Model(cfg, w), orc.OracleModel(cfg, w)
+    rows = 2
+    gs, os_ = gm.state(rows, 64), om.state(rows)
+    gs.set_commit_at_end(True)
+    ids = synth.token_ids(cfg["vocab"], rows, 12, seed0=2)
+    ids[ids == bad] = bad + 1
+    names = STATE_NAMES(cfg) + ["eng.k", "eng.v"]
+    for t in range(5):
+        assert np.array_equal(bits(gm.step(gs, ids[:, t])), bits(os_.step(ids[:, t]))), t
+    before = {(r, n): gs.get(r, n).copy() for r in range(rows) for n in names}
+    seen = [gs.seen(r) for r in range(rows)]
+    with pytest.raises(engine.EngineError) as ei:
+        gm.step(gs, np.array([ids[0, 5], bad], np.uint32))
+    assert ei.value.code == engine.ERR_NONFINITE
+    for (r, n), a in before.items():
+        b = gs.get(r, n)
+        assert a.shape == b.shape and np.array_equal(bits(a), bits(b)), (r, n)
+    assert [gs.seen(r) for r in range(rows)] == seen
+    # a prompt with the bad token in its middle: the same
+    prompt = np.array(ids[:, 5:11], np.uint32, copy=True)
+    prompt[1, 3] = bad
+    with pytest.raises(engine.EngineError):
+        gm.forward_with_state(prompt, gs, last_only=True)
+    for (r, n), a in before.items():
+        assert np.array_equal(bits(a), bits(gs.get(r, n))), (r, n)
+    assert [gs.seen(r) for r in range(rows)] == seen
+    # and the state goes on from where it was
+    for t in range(5, 9):
+        assert np.array_equal(bits(gm.step(gs, ids[:, t])), bits(os_.step(ids[:, t]))), t
+    last = gm.forward_with_state(ids[:, 9:12], gs, last_only=True)
+    want = os_.forward(ids[:, 9:12], last_only=True)
+    assert np.array_equal(bits(last), bits(want))
+    assert_same_state(cfg, gs, os_, rows)
+    # without the flag the same failure leaves a moved state behind (stated in the header)
+    gs2 = gm.state(rows, 64)
+    gm.step(gs2, ids[:, 0])
+    v0 = gs2.get(1, "lif.0.v").copy()
+    with pytest.raises(engine.EngineError):
+        gm.step(gs2, np.array([ids[0, 1], bad], np.uint32))
+    assert not np.array_equal(bits(v0), bits(gs2.get(1, "lif.0.v")))
+
+
 def test_scaled_block_bits(orc_same_math):
     """One block of the scaled model (d 2048, wide 8192, kWTA 2048, one 2048x2048 fast-synapse matrix, vocab cut to 2048):
     the 64-byte column slices and the 16-chunk bulk copies of the big head, every bit."""
