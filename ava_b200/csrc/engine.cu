@@ -914,7 +914,9 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
         gemm(e, "gemm.w1", h, d, b.w1, w.u.as<float>(), H, M, EPI_STORE);
         dbg(e, "u", i, w.u.as<float>(), M, H);
         prof_begin(e, "kwta");
-        launch_kwta(st, w.u.as<float>(), M, H, c.kwta_k, c.relu2, w.act.as<float>());
+        // a prompt chunk in the tolerance mode multiplies the k-WTA's output densely on the tensor cores: its limbs are made here
+        launch_kwta(st, w.u.as<float>(), M, H, c.kwta_k, c.relu2, w.act.as<float>(),
+                    (M >= 1024 && b.w2.wt.p && !c.dendrite) ? limbs_for(e, w.act.as<float>(), M, H) : nullptr);
         prof_end(e);
         dbg(e, "a", i, w.act.as<float>(), M, H);
         if (c.dendrite && c.fast_mem) {

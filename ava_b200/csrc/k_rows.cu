@@ -165,8 +165,17 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     for (int i = lane; i < n; i += 32) xs[i] = xr[i];
     __syncwarp();
     float inv = 0.0f;
-    if (lane == 0) inv = inv_rms_seq(xs, n);
-    inv = __shfl_sync(0xffffffffu, inv, 0);
+    if (limbs) {
+        // the tolerance mode (its consumer is a tensor-core product): the squares summed by the whole warp, another order
+        float sq = 0.0f;
+        for (int i = lane; i < n; i += 32) sq = fmaf(xs[i], xs[i], sq);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        inv = rsqrtf_(sq * (float)(1.0 / (double)n) + NORM_EPS);
+    } else {
+        if (lane == 0) inv = inv_rms_seq(xs, n);
+        inv = __shfl_sync(0xffffffffu, inv, 0);
+    }
     float* yr = y + (size_t)r * n;
     for (int i = lane; i < n; i += 32) {
         const float v = mul(mul(xs[i], inv), gain[i]);
@@ -612,7 +621,17 @@ __global__ void mem_post_kernel(const float* __restrict__ y_raw, const float* __
     float* inv = sm + d;
     for (int c = tid; c < d; c += T) ys[c] = y_raw[(size_t)r * d + c];
     __syncthreads();
-    for (int e = tid; e < nh; e += T) inv[e] = inv_rms_seq(ys + e * hs, hs);
+    if (limbs) {  // the tolerance mode: a warp sums a head's squares (another order)
+        for (int e = tid >> 5; e < nh; e += T >> 5) {
+            float sq = 0.0f;
+            for (int i = tid & 31; i < hs; i += 32) sq = fmaf(ys[e * hs + i], ys[e * hs + i], sq);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            if ((tid & 31) == 0) inv[e] = rsqrtf_(sq * (float)(1.0 / (double)hs) + NORM_EPS);
+        }
+    } else {
+        for (int e = tid; e < nh; e += T) inv[e] = inv_rms_seq(ys + e * hs, hs);
+    }
     __syncthreads();
     for (int c = tid; c < d; c += T) {
         float v = mul(ys[c], inv[c / hs]);
@@ -636,7 +655,7 @@ __device__ __forceinline__ uint32_t order_key(float f) {
 }
 __device__ __forceinline__ float key_value(uint32_t k) { return bits_to_f((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k); }
 
-__global__ void kwta_kernel(const float* __restrict__ u, int M, int n, int k, int relu2, float* __restrict__ out) {
+__global__ void kwta_kernel(const float* __restrict__ u, int M, int n, int k, int relu2, float* __restrict__ out, uint16_t* __restrict__ limbs) {
     pdl_enter();
     extern __shared__ uint32_t keys[];  // [n] keys
     const int r = blockIdx.x, tid = threadIdx.x, T = blockDim.x, lane = tid & 31, warp = tid >> 5;
@@ -645,7 +664,9 @@ __global__ void kwta_kernel(const float* __restrict__ u, int M, int n, int k, in
     if (k >= n) {
         for (int i = tid; i < n; i += T) {
             float v = fmaxf(mul(ur[i], 1.0f), 0.0f);
-            orow[i] = relu2 ? mul(v, v) : v;
+            v = relu2 ? mul(v, v) : v;
+            orow[i] = v;
+            if (limbs) store_limbs(limbs, (int64_t)M * n, (int64_t)r * n + i, v);
         }
         return;
     }
@@ -688,7 +709,9 @@ __global__ void kwta_kernel(const float* __restrict__ u, int M, int n, int k, in
     for (int i = tid; i < n; i += T) {
         const float v = ur[i];
         float o = fmaxf(mul(v, sub(v, kth) >= 0.0f ? 1.0f : 0.0f), 0.0f);
-        orow[i] = relu2 ? mul(o, o) : o;
+        const float ov = relu2 ? mul(o, o) : o;
+        orow[i] = ov;
+        if (limbs) store_limbs(limbs, (int64_t)M * n, (int64_t)r * n + i, ov);
     }
 }
 
@@ -872,10 +895,10 @@ void launch_mem_post(cudaStream_t st, const float* y_raw, const float* gate, int
     launch_k(mem_post_kernel, dim3(M), dim3(256), smem, st, y_raw, gate, ldg, M, d, hs, y, limbs, rh_r);
 }
 
-void launch_kwta(cudaStream_t st, const float* u, int M, int n, int k, int relu2, float* a) {
+void launch_kwta(cudaStream_t st, const float* u, int M, int n, int k, int relu2, float* a, uint16_t* limbs) {
     const size_t smem = (size_t)n * sizeof(uint32_t);
     opt_in_smem(kwta_kernel, smem);
-    launch_k(kwta_kernel, dim3(M), dim3(256), smem, st, u, M, n, k, relu2, a);
+    launch_k(kwta_kernel, dim3(M), dim3(256), smem, st, u, M, n, k, relu2, a, limbs);
 }
 
 void launch_dense_mix(cudaStream_t st, float* x, float* streams, const float* w, int n_streams, int64_t MD) {

@@ -342,7 +342,8 @@ struct EngramChunkArgs {
 };
 bool launch_engram_chunk(cudaStream_t st, const EngramChunkArgs& a);
 
-void launch_kwta(cudaStream_t st, const float* u, int M, int n, int k, int relu2, float* a);
+// limbs (may be null): also the three bf16 limbs of the output, planes [3][M * n], for launch_tc_gemm
+void launch_kwta(cudaStream_t st, const float* u, int M, int n, int k, int relu2, float* a, uint16_t* limbs = nullptr);
 // x <- x + sum_j streams[j] * w[j] over the n_streams streams (the last one is x itself, stored first)
 void launch_dense_mix(cudaStream_t st, float* x, float* streams, const float* w, int n_streams, int64_t MD);
 // `diary::pick` for every row: softmax(logits / temperature), the top_k most likely, one draw with the row's uniform
