@@ -8,11 +8,11 @@
 // cumex = the sums before a position; q, e unit; w = k b the write key, ah = e (b alpha) the erase key):
 //     qs = q exp(cum)        es = e exp(cumex)        ws = w exp(-cum)        as = ah exp(-cum)
 //     Qw = tril(qs ws^T)     Qa = tril(qs as^T)       Ke = stril(es ws^T)     Ae = stril(es as^T)       one 128x128xhs product
-//     T  = (I + Ae)^-1       p1 = T es                r0 = (T Ke) v           qwv = Qw v
+//     T  = (I + Ae)^-1       p1 = T es                r0 = (T Ke) v           qwv = Qw v      (r0 and qwv inside the state read, below)
 //     wl = w exp(cum_C - cum)   al = ah exp(cum_C - cum)   gc = exp(cum_C)
 // then, chunk after chunk with the state F [key, value]:
-//     [rr0; yq] = [p1; qs] F                           128 x hs x hs on the tensor cores
-//     rr = rr0 + r0        y = yq + qwv - Qa rr
+//     [rr; yw] = [p1 | T Ke; qs | Qw] [F; v]           128 x (hs + 64) x hs on the tensor cores: rr = p1 F + r0, yw = qs F + qwv
+//     y = yw - Qa rr
 //     F' = diag(gc) F + wl^T v - al^T rr               hs x hs x 128 on the tensor cores
 // The pairwise decays exp(cum_i - cum_j) are formed as products exp(cum_i) exp(-cum_j) so that the Gram matrices are
 // plain products; that is safe while the sums stay within the f32 exponent range over one chunk.  The scaling kernel
@@ -162,11 +162,16 @@ __global__ void __launch_bounds__(256) chunk_solve_kernel(const ChunkArgs a) {
     float* X = Ke + 64 * 65;      // [64][65] the inverse
     const int u = blockIdx.x, tid = threadIdx.x;
     const float* G = a.Gm + (size_t)u * 128 * 128;
-    float* Qw = a.Qw + (size_t)u * 4096;
     float* Qa = a.Qa + (size_t)u * 4096;
+    const size_t PX = (size_t)a.nC * a.HB * 128 * 64;      // plane of XL
+    uint16_t* XL = a.XL + (size_t)u * 128 * 64;            // rows 0..63: T Ke, rows 64..127: Qw
     for (int n = tid; n < 4096; n += 256) {
         const int i = n >> 6, jj = n & 63;
-        Qw[n] = jj <= i ? G[(size_t)i * 128 + jj] : 0.0f;
+        {
+            uint16_t l0, l1, l2;
+            limbs3(jj <= i ? G[(size_t)i * 128 + jj] : 0.0f, l0, l1, l2);
+            XL[4096 + n] = l0; XL[PX + 4096 + n] = l1; XL[2 * PX + 4096 + n] = l2;
+        }
         Qa[n] = jj <= i ? G[(size_t)i * 128 + 64 + jj] : 0.0f;
         Ke[i * 65 + jj] = jj < i ? G[(size_t)(64 + i) * 128 + jj] : 0.0f;
         Ae[i * 65 + jj] = jj < i ? G[(size_t)(64 + i) * 128 + 64 + jj] : 0.0f;
@@ -183,18 +188,19 @@ __global__ void __launch_bounds__(256) chunk_solve_kernel(const ChunkArgs a) {
     }
     __syncthreads();
     float* Ti = a.Tinv + (size_t)u * 4096;
-    float* TK = a.TK + (size_t)u * 4096;
     for (int n = tid; n < 4096; n += 256) {
         const int i = n >> 6, c = n & 63;
         Ti[n] = X[i * 65 + c];
         float s = 0.0f;
         for (int k = 0; k <= i; ++k) s = fmaf(X[i * 65 + k], Ke[k * 65 + c], s);  // X is lower triangular
-        TK[n] = s;
+        uint16_t l0, l1, l2;
+        limbs3(s, l0, l1, l2);
+        XL[n] = l0; XL[PX + n] = l1; XL[2 * PX + n] = l2;
     }
 }
 
-// ---- D [64 x cols] = Mx [64 x 64] . Xin [64 x cols] per (chunk, head): p1 = T es (as limbs), r0 = (T Ke) v, qwv = Qw v -----
-// grid (H / 128, nC * HB, 3); 128 threads: thread (r8, c8) owns rows r8 * 8 .. + 7 and columns c8 * 8 .. + 7 of the tile
+// ---- p1 [64 x hs] = T [64 x 64] . es [64 x hs] per (chunk, head), written as limbs into the state read's left operand -----
+// grid (H / 128, nC * HB); 128 threads: thread (r8, c8) owns rows r8 * 8 .. + 7 and columns c8 * 8 .. + 7 of the tile
 // (an 8 x 8 register tile: four 16-byte reads of shared memory per 64 multiply-adds)
 __device__ __forceinline__ void tile_mm_8x8(const float (*Mt)[64], const float (*Xs)[128], int r8, int c8, float (&acc)[8][8]) {
 #pragma unroll
@@ -218,14 +224,12 @@ __global__ void __launch_bounds__(128) chunk_small_kernel(const ChunkArgs a) {
     pdl_enter();
     __shared__ __align__(16) float Mt[64][64];  // transposed: [k][row]
     __shared__ __align__(16) float Xs[64][128];
-    const int H = a.hs, u = blockIdx.y, j = u / a.HB, hb = u % a.HB, which = blockIdx.z, c0 = blockIdx.x * 128, tid = threadIdx.x;
-    const float* Mx = (which == 0 ? a.Tinv : which == 1 ? a.TK : a.Qw) + (size_t)u * 4096;
+    const int H = a.hs, u = blockIdx.y, c0 = blockIdx.x * 128, tid = threadIdx.x;
+    const float* Mx = a.Tinv + (size_t)u * 4096;
     for (int n = tid; n < 4096; n += 128) Mt[n & 63][n >> 6] = Mx[n];
     for (int n = tid; n < 64 * 32; n += 128) {
         const int i = n >> 5, q = (n & 31) * 4;
-        const float* src = which == 0 ? a.ES + ((size_t)u * 64 + i) * H + c0 + q
-                                      : a.v + (size_t)(j * CC + i) * a.tok_stride + (size_t)hb * H + c0 + q;
-        *reinterpret_cast<float4*>(&Xs[i][q]) = *reinterpret_cast<const float4*>(src);
+        *reinterpret_cast<float4*>(&Xs[i][q]) = *reinterpret_cast<const float4*>(a.ES + ((size_t)u * 64 + i) * H + c0 + q);
     }
     __syncthreads();
     const int r8 = tid >> 4, c8 = tid & 15;
@@ -235,24 +239,18 @@ __global__ void __launch_bounds__(128) chunk_small_kernel(const ChunkArgs a) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int row = r8 * 8 + i;
-        if (which == 0) {  // p1: the top rows of the state product's left operand, as limbs
-            const size_t o = ((size_t)u * 128 + row) * H + c0 + c8 * 8;
-            uint16_t l[3][8];
+        const size_t o = ((size_t)u * 128 + row) * H + c0 + c8 * 8;
+        uint16_t l[3][8];
 #pragma unroll
-            for (int q = 0; q < 8; ++q) limbs3(acc[i][q], l[0][q], l[1][q], l[2][q]);
+        for (int q = 0; q < 8; ++q) limbs3(acc[i][q], l[0][q], l[1][q], l[2][q]);
 #pragma unroll
-            for (int p = 0; p < 3; ++p)
-                *reinterpret_cast<uint4*>(a.A3 + p * P128 + o) =
-                    make_uint4(l[p][0] | ((uint32_t)l[p][1] << 16), l[p][2] | ((uint32_t)l[p][3] << 16), l[p][4] | ((uint32_t)l[p][5] << 16), l[p][6] | ((uint32_t)l[p][7] << 16));
-        } else {
-            float* dst = (which == 1 ? a.r0 : a.qwv) + ((size_t)u * 64 + row) * H + c0 + c8 * 8;
-            *reinterpret_cast<float4*>(dst) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-            *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
-        }
+        for (int p = 0; p < 3; ++p)
+            *reinterpret_cast<uint4*>(a.A3 + p * P128 + o) =
+                make_uint4(l[p][0] | ((uint32_t)l[p][1] << 16), l[p][2] | ((uint32_t)l[p][3] << 16), l[p][4] | ((uint32_t)l[p][5] << 16), l[p][6] | ((uint32_t)l[p][7] << 16));
     }
 }
 
-// ---- one chunk's reads: rr = rr0 + r0, y = yq + qwv - Qa rr; -rr^T into the update's left operand ---------------
+// ---- one chunk's reads: y = yw - Qa rr (rr and yw come from the state read); -rr^T into the update's left operand ----
 // grid (H / 128, HB); 128 threads, the same 8 x 8 register tile
 __global__ void __launch_bounds__(128) chunk_read_kernel(const ChunkArgs a, int j) {
     pdl_enter();
@@ -264,9 +262,7 @@ __global__ void __launch_bounds__(128) chunk_read_kernel(const ChunkArgs a, int 
     const float* RY = a.RY + (size_t)hb * 128 * H;
     for (int n = tid; n < 64 * 32; n += 128) {
         const int i = n >> 5, q = (n & 31) * 4;
-        const float4 x = *reinterpret_cast<const float4*>(RY + (size_t)i * H + c0 + q);
-        const float4 r = *reinterpret_cast<const float4*>(a.r0 + ((size_t)u * 64 + i) * H + c0 + q);
-        *reinterpret_cast<float4*>(&Rs[i][q]) = make_float4(x.x + r.x, x.y + r.y, x.z + r.z, x.w + r.w);
+        *reinterpret_cast<float4*>(&Rs[i][q]) = *reinterpret_cast<const float4*>(RY + (size_t)i * H + c0 + q);
     }
     __syncthreads();
     const int r8 = tid >> 4, c8 = tid & 15;
@@ -276,12 +272,10 @@ __global__ void __launch_bounds__(128) chunk_read_kernel(const ChunkArgs a, int 
     for (int i = 0; i < 8; ++i) {
         const int row = r8 * 8 + i;
         const float* yq = RY + (size_t)(64 + row) * H + c0 + c8 * 8;
-        const float* qv = a.qwv + ((size_t)u * 64 + row) * H + c0 + c8 * 8;
         float* dst = a.y + (size_t)(j * CC + row) * a.tok_stride + (size_t)hb * H + c0 + c8 * 8;
         const float4 y0 = *reinterpret_cast<const float4*>(yq), y1 = *reinterpret_cast<const float4*>(yq + 4);
-        const float4 q0 = *reinterpret_cast<const float4*>(qv), q1 = *reinterpret_cast<const float4*>(qv + 4);
-        *reinterpret_cast<float4*>(dst) = make_float4((y0.x + q0.x) - acc[i][0], (y0.y + q0.y) - acc[i][1], (y0.z + q0.z) - acc[i][2], (y0.w + q0.w) - acc[i][3]);
-        *reinterpret_cast<float4*>(dst + 4) = make_float4((y1.x + q1.x) - acc[i][4], (y1.y + q1.y) - acc[i][5], (y1.z + q1.z) - acc[i][6], (y1.w + q1.w) - acc[i][7]);
+        *reinterpret_cast<float4*>(dst) = make_float4(y0.x - acc[i][0], y0.y - acc[i][1], y0.z - acc[i][2], y0.w - acc[i][3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(y1.x - acc[i][4], y1.y - acc[i][5], y1.z - acc[i][6], y1.w - acc[i][7]);
     }
     // -rr transposed: row (value) of the update's left operand, token slots 64 .. 127; thread = value
     const size_t PT = (size_t)a.nC * a.HB * H * 128;
@@ -334,10 +328,11 @@ size_t mem_chunk_workspace_bytes(int HB, int hs, int nC) {
     size_t b = 0;
     b += 3 * (3 * U * 128 * H * 2);   // QE, WA, A3 limbs
     b += 2 * (3 * U * H * 128 * 2);   // A5, B5 limbs
-    b += 4 * (U * 64 * H * 4);        // ES, r0, qwv, CUM
+    b += 2 * (U * 64 * H * 4);        // ES, CUM
+    b += 3 * U * 128 * 64 * 2;        // XL
     b += U * H * 4;                   // gc
     b += U * 128 * 128 * 4;           // Gm
-    b += 4 * (U * 4096 * 4);          // Qw, Qa, Tinv, TK
+    b += 2 * (U * 4096 * 4);          // Qa, Tinv
     b += (size_t)HB * 128 * H * 4;    // RY
     b += (size_t)HB * H * H * 4;      // Ft
     b += 3 * (size_t)HB * H * H * 2;  // Ft limbs
@@ -354,15 +349,12 @@ void mem_chunk_carve(ChunkArgs& a, void* ws) {
     a.A5 = (uint16_t*)take(3 * U * H * 128 * 2);
     a.B5 = (uint16_t*)take(3 * U * H * 128 * 2);
     a.ES = (float*)take(U * 64 * H * 4);
-    a.r0 = (float*)take(U * 64 * H * 4);
-    a.qwv = (float*)take(U * 64 * H * 4);
     a.CUM = (float*)take(U * 64 * H * 4);
     a.gc = (float*)take(U * H * 4);
     a.Gm = (float*)take(U * 128 * 128 * 4);
-    a.Qw = (float*)take(U * 4096 * 4);
     a.Qa = (float*)take(U * 4096 * 4);
     a.Tinv = (float*)take(U * 4096 * 4);
-    a.TK = (float*)take(U * 4096 * 4);
+    a.XL = (uint16_t*)take(3 * U * 128 * 64 * 2);
     a.RY = (float*)take((size_t)a.HB * 128 * H * 4);
     a.Ft = (float*)take((size_t)a.HB * H * H * 4);
     a.Ft_limbs = (uint16_t*)take(3 * (size_t)a.HB * H * H * 2);
@@ -392,11 +384,13 @@ bool launch_mem_chunk_rest(cudaStream_t st, const ChunkArgs& a) {
     const size_t solve_smem = 3 * 64 * 65 * sizeof(float);
     cudaFuncSetAttribute(chunk_solve_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)solve_smem);
     launch_k(chunk_solve_kernel, dim3(U), dim3(256), solve_smem, st, a);
-    launch_k(chunk_small_kernel, dim3(H / 128, U, 3), dim3(128), 0, st, a);
+    launch_k(chunk_small_kernel, dim3(H / 128, U), dim3(128), 0, st, a);
     for (int j = 0; j < a.nC; ++j) {
         TcbArgs s3{};
         s3.a = a.A3; s3.a_row0 = (int64_t)j * a.HB * 128; s3.rows_a = (int64_t)U * 128;
         s3.b = a.Ft_limbs; s3.rows_b = (int64_t)a.HB * H;
+        s3.a2 = a.XL; s3.rows_a2 = (int64_t)U * 128; s3.a2_row0 = (int64_t)j * a.HB * 128; s3.lda2 = 64;      // [T Ke; Qw] ...
+        s3.b2 = a.A5; s3.rows_b2 = (int64_t)U * H; s3.b2_row0 = (int64_t)j * a.HB * H; s3.ldb2 = 128; s3.K2 = 64;  // ... times the chunk's values
         s3.C = a.RY; s3.ldc = H; s3.c_batch_stride = (int64_t)128 * H; s3.M = 128; s3.N = H; s3.K = H; s3.batch = a.HB; s3.status = a.status;
         if (!launch_tc_bgemm(st, s3, TCB_STORE)) return false;
         launch_k(chunk_read_kernel, dim3(H / 128, a.HB), dim3(128), 0, st, a, j);

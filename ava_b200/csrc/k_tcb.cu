@@ -31,6 +31,7 @@ using namespace tcc;
 constexpr int B_THREADS = 256;
 template <int BN, int LA, int LB, int STAGES, int EPI>
 __global__ void __launch_bounds__(B_THREADS) tc_bgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                                                             const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
                                                              const TcbArgs a) {
     pdl_enter();
     extern __shared__ unsigned char smem_raw[];
@@ -44,7 +45,7 @@ __global__ void __launch_bounds__(B_THREADS) tc_bgemm_kernel(const __grid_consta
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int m0 = blockIdx.y * B_BM, n0 = blockIdx.x * BN, bz = blockIdx.z;
-    const int kt = a.K / B_BK;
+    const int kt1 = a.K / B_BK, kt = kt1 + a.K2 / B_BK;   // k-tiles of the operands proper, then of the second stretch
 
     if (EPI == TCB_DECAY) {
         // the tile of the old C is wanted by the epilogue only: ask for it now, so that it waits in L2 by then
@@ -81,10 +82,18 @@ __global__ void __launch_bounds__(B_THREADS) tc_bgemm_kernel(const __grid_consta
             if (!ok) break;
             unsigned char* st = smem + (size_t)s * STAGE_BYTES;
             bar_expect(&full[s], STAGE_BYTES);
+            if (it < kt1) {
 #pragma unroll
-            for (int l = 0; l < LA; ++l) tma_load(st + l * A_BYTES, &map_a, it * B_BK, (int)(l * a.rows_a) + ya, &full[s]);
+                for (int l = 0; l < LA; ++l) tma_load(st + l * A_BYTES, &map_a, it * B_BK, (int)(l * a.rows_a) + ya, &full[s]);
 #pragma unroll
-            for (int l = 0; l < LB; ++l) tma_load(st + LA * A_BYTES + l * B_BYTES, &map_b, it * B_BK, (int)(l * a.rows_b) + yb, &full[s]);
+                for (int l = 0; l < LB; ++l) tma_load(st + LA * A_BYTES + l * B_BYTES, &map_b, it * B_BK, (int)(l * a.rows_b) + yb, &full[s]);
+            } else {
+                const int ya2 = (int)a.a2_row0 + bz * a.M + m0, yb2 = (int)a.b2_row0 + bz * a.N + n0;
+#pragma unroll
+                for (int l = 0; l < LA; ++l) tma_load(st + l * A_BYTES, &map_a2, (it - kt1) * B_BK, (int)(l * a.rows_a2) + ya2, &full[s]);
+#pragma unroll
+                for (int l = 0; l < LB; ++l) tma_load(st + LA * A_BYTES + l * B_BYTES, &map_b2, (it - kt1) * B_BK, (int)(l * a.rows_b2) + yb2, &full[s]);
+            }
         }
         if (!ok) atomicOr(a.status, ST_WAIT_TIMEOUT);
     } else if (tid == 32) {
@@ -198,20 +207,27 @@ __global__ void __launch_bounds__(B_THREADS) tc_bgemm_kernel(const __grid_consta
 
 template <int BN, int LA, int LB, int STAGES, int EPI>
 bool launch_one(cudaStream_t st, const TcbArgs& a) {
-    CUtensorMap ma, mb;
+    CUtensorMap ma, mb, ma2, mb2;
     if (!make_map(&ma, a.a, (uint64_t)LA * a.rows_a, a.K, B_BM) || !make_map(&mb, a.b, (uint64_t)LB * a.rows_b, a.K, BN)) return false;
+    if (a.K2 > 0) {
+        if (!make_map(&ma2, a.a2, (uint64_t)LA * a.rows_a2, a.lda2, B_BM) || !make_map(&mb2, a.b2, (uint64_t)LB * a.rows_b2, a.ldb2, BN)) return false;
+    } else {
+        ma2 = ma;
+        mb2 = mb;
+    }
     const size_t smem = (size_t)STAGES * (LA * B_BM * B_BK * 2 + LB * BN * B_BK * 2) + (2 * STAGES + 1) * sizeof(uint64_t) + 16 + 1024;
     cudaFuncSetAttribute(tc_bgemm_kernel<BN, LA, LB, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     prefer_max_shared(reinterpret_cast<const void*>(tc_bgemm_kernel<BN, LA, LB, STAGES, EPI>), 100);
     dim3 grid((a.N + BN - 1) / BN, (a.M + B_BM - 1) / B_BM, a.batch);
-    return launch_k(tc_bgemm_kernel<BN, LA, LB, STAGES, EPI>, grid, dim3(B_THREADS), smem, st, ma, mb, a) == cudaSuccess;
+    return launch_k(tc_bgemm_kernel<BN, LA, LB, STAGES, EPI>, grid, dim3(B_THREADS), smem, st, ma, mb, ma2, mb2, a) == cudaSuccess;
 }
 
 }  // namespace
 
 // false: shape not covered (K a multiple of 64, M a multiple of 128, N a multiple of 4) or no tensor-map encoder
 bool launch_tc_bgemm(cudaStream_t st, const TcbArgs& a, int epi) {
-    if (a.K % B_BK || a.M % B_BM || a.N % 4 || a.batch < 1) return false;
+    if (a.K % B_BK || a.K2 % B_BK || a.K2 < 0 || a.M % B_BM || a.N % 4 || a.batch < 1) return false;
+    if (a.K2 > 0 && (!a.a2 || !a.b2 || a.lda2 < a.K2 || a.ldb2 < a.K2 || a.lda2 % 8 || a.ldb2 % 8)) return false;
     // N 128: two stages of 96 KB, one block per SM (measured a little ahead of one stage with two blocks per SM)
     if (a.N % 128 == 0) return epi == TCB_DECAY ? launch_one<128, 3, 3, 2, TCB_DECAY>(st, a) : launch_one<128, 3, 3, 2, TCB_STORE>(st, a);
     return epi == TCB_DECAY ? launch_one<64, 3, 3, 3, TCB_DECAY>(st, a) : launch_one<64, 3, 3, 3, TCB_STORE>(st, a);

@@ -146,6 +146,12 @@ struct TcbArgs {
     int64_t colscale_batch_stride;
     uint16_t* c_limbs;
     int64_t c_limb_plane;     // elements between limb planes
+    // An optional second stretch of K from other buffers: C += A2[b] . B2[b]^T over K2 more columns (a multiple of 64), as if
+    // [A | A2] and [B | B2] were single operands.  Rows of width lda2 / ldb2 elements, of which the first K2 are read.
+    const uint16_t* a2;       // [3][rows_a2][lda2]
+    const uint16_t* b2;       // [3][rows_b2][ldb2]
+    int64_t rows_a2, rows_b2, a2_row0, b2_row0;
+    int K2, lda2, ldb2;
     uint32_t* status;
 };
 bool launch_tc_bgemm(cudaStream_t st, const TcbArgs& a, int epi);
@@ -163,7 +169,8 @@ struct ChunkArgs {
     uint32_t* status;
     // workspace (mem_chunk_carve)
     uint16_t *QE, *WA, *A3, *A5, *B5, *Ft_limbs;
-    float *ES, *r0, *qwv, *CUM, *gc, *Gm, *Qw, *Qa, *Tinv, *TK, *RY, *Ft;
+    float *ES, *CUM, *gc, *Gm, *Qa, *Tinv, *RY, *Ft;
+    uint16_t* XL;   // [3][nC * HB * 128][64]: per chunk the limbs of [T Ke; Qw], the second stretch of the state read's left operand
 };
 size_t mem_chunk_workspace_bytes(int HB, int hs, int nC);
 void mem_chunk_carve(ChunkArgs& a, void* ws);
