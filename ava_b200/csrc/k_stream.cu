@@ -57,7 +57,8 @@ __device__ __forceinline__ float4 pending_update(float4 f, float x, float w, flo
 // warp of the launch is resident from the start (registers are the limit, and they hold the rows in flight), so all
 // slices stream side by side at the pace of HBM and end together, whatever the count of (row, head) pairs against SMs.
 // SD: rows a lane keeps in flight (16, or 32 when the launch has too few warps to keep HBM busy with 16)
-template <bool PEND, int MODE, int SD>
+// ALT: the updated state goes to a.f_out (a state that commits at the end) instead of back in place
+template <bool PEND, int MODE, int SD, bool ALT = false>
 __global__ void __launch_bounds__(256) mem_stream_kernel(const MemStreamArgs a) {
     pdl_enter();
     extern __shared__ __align__(16) float vs[];
@@ -85,7 +86,7 @@ __global__ void __launch_bounds__(256) mem_stream_kernel(const MemStreamArgs a) 
     // slice-major state: [slice][row][cw]; four neighbouring columns lie in one slice
     const size_t fo = vo * hs + (size_t)(c / cw) * hs * cw + (c % cw);
     float* fp = a.f + fo;
-    float* fq = (a.f_out ? a.f_out : a.f) + fo;   // where the updated state goes: in place, or the state's second copy
+    float* fq = ALT ? a.f_out + fo : fp;   // where the updated state goes: in place, or the state's second copy
     float4 pv = make_float4(0.f, 0.f, 0.f, 0.f), prr = pv;
     if (PEND) {
         pv = *reinterpret_cast<const float4*>(a.pv + vo + c);
@@ -184,6 +185,10 @@ bool launch_mem_stream(cudaStream_t st, const MemStreamArgs& a) {
     }
     const bool deep = (long)a.M * a.nh * warps_head < deep_below;
     if (!pend) { go(mem_stream_kernel<false, 7, 16>); return true; }
+    if (a.f_out) {
+        if (deep) go(mem_stream_kernel<true, 7, 32, true>); else go(mem_stream_kernel<true, 7, 16, true>);
+        return true;
+    }
     if (deep) go(mem_stream_kernel<true, 7, 32>); else go(mem_stream_kernel<true, 7, 16>);
     return true;
 }
