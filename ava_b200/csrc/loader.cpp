@@ -283,7 +283,15 @@ int ava_ckpt_open(const char* path, ava_ckpt** out) {
         if (e.shape.size() > 4) return fail(AVA_NOT_APPLICABLE, e.name + ": more than 4 dimensions");
         for (int64_t s : e.shape)
             if (s < 0) return fail(AVA_ERR_ARG, e.name + ": negative dimension");
-        if (e.end > dlen || e.end - e.begin != (uint64_t)e.count() * es) return fail(AVA_ERR_ARG, e.name + ": data offsets do not match its shape");
+        // the element count with every step checked: a shape whose product wraps must not pass as a small tensor
+        uint64_t count = 1;
+        bool wraps = false;
+        for (int64_t s : e.shape) {
+            if (s != 0 && count > (dlen / (uint64_t)es + 1) / (uint64_t)s + 1) wraps = true;
+            if (!wraps) count *= (uint64_t)s;
+        }
+        if (wraps || e.begin > e.end || e.end > dlen || e.end - e.begin != count * (uint64_t)es)
+            return fail(AVA_ERR_ARG, e.name + ": data offsets do not match its shape");
         if (!c->index.emplace(e.name, (int)i).second) return fail(AVA_ERR_ARG, e.name + ": named twice");
     }
     c->data.resize((size_t)dlen);

@@ -103,7 +103,7 @@ def test_f16_and_bf16_tensors_widen_exactly(tmp_path):
     assert ck.info(1)[2] == (2, 2) or ck.info(0)[2] == (2, 2)
 
 
-@pytest.mark.parametrize("damage", ["short", "header_len", "offsets", "dtype", "json", "twice"])
+@pytest.mark.parametrize("damage", ["short", "header_len", "offsets", "dtype", "json", "twice", "shape_wraps", "begin_after_end"])
 def test_damaged_files_are_refused(tmp_path, damage):
     path = str(tmp_path / "bad.safetensors")
     good = '{"t":{"dtype":"F32","shape":[2],"data_offsets":[0,8]}}'
@@ -119,6 +119,13 @@ def test_damaged_files_are_refused(tmp_path, damage):
         blob = struct.pack("<Q", len(h)) + h.encode() + data
     elif damage == "json":
         h = good[:-3]
+        blob = struct.pack("<Q", len(h)) + h.encode() + data
+    elif damage == "shape_wraps":
+        # 2^31 x 2^31 x 4 elements of 4 bytes: the byte count wraps to 0 in 64 bits, so a naive product matches [0,0]
+        h = good.replace("[2]", "[2147483648,2147483648,4]").replace("[0,8]", "[0,0]")
+        blob = struct.pack("<Q", len(h)) + h.encode() + data
+    elif damage == "begin_after_end":
+        h = good.replace("[0,8]", "[8,0]")
         blob = struct.pack("<Q", len(h)) + h.encode() + data
     else:
         h = '{"t":{"dtype":"F32","shape":[1],"data_offsets":[0,4]},"t":{"dtype":"F32","shape":[1],"data_offsets":[4,8]}}'
