@@ -500,6 +500,26 @@ def main():
     # ---- prompt reading (benchmark configuration 2's shape: 64 rows per GPU, chunks of 256 tokens), a bounded sample of it
     if not args.small and not args.scaled:
         line["prefill"] = measure_prefill(model, cfg, local, world, dist, rows=64, tokens=args.prefill_tokens, chunk=256, seed0=50_000 + first)
+    # ---- configuration 0's shape on the GPU: one sequence alone (256-token prompt, then decode), exact mode
+    if rank == 0 and not args.small and not args.scaled:
+        one = model.state(1, 512)
+        ids1 = torch.from_numpy(np.ascontiguousarray(synth.token_ids(cfg["vocab"], 1, 256 + 3, seed0=0).T).astype(np.int32)).to(f"cuda:{local}")
+        lg1 = torch.empty(1, cfg["vocab"], dtype=torch.float32, device=f"cuda:{local}")
+        nx = [torch.zeros(1, dtype=torch.int32, device=f"cuda:{local}") for _ in range(2)]
+        for t in range(256):
+            model.step_device(one, ids1[t].data_ptr(), lg1.data_ptr(), nx[0].data_ptr())
+        model.sync()
+        ev0.record(stream)
+        for t in range(64):
+            model.step_device(one, nx[t & 1].data_ptr(), lg1.data_ptr(), nx[(t & 1) ^ 1].data_ptr())
+        ev1.record(stream)
+        model.sync()
+        torch.cuda.synchronize()
+        one_ms = ev0.elapsed_time(ev1) / 64
+        line["config0_batch1"] = {"value": 1e3 / one_ms, "unit": UNIT, "ms_per_token": one_ms,
+                                  "what": "one sequence alone on the GPU (greedy feedback on the device, KV length 256..320), exact mode; the CPU's figure "
+                                          "for the same case is cpu_baseline.config0_batch1"}
+        one.close()
     if rank == 0 and not args.no_cpu and not args.small:
         threads = os.cpu_count() or 1
         val, _, sample = cpu_reference(cfg, weights, 128, 4, 16, threads)
