@@ -101,6 +101,7 @@ struct Work {
     Dev x, h, proj, ve, vv, vw, vah, vqg, vex, vqs, qw, qa, yraw, y, eqkv, eo, u, act, streams, v_first;
     Dev gz, lra, lrb;  // the gates' stages: [rows][gate_cols], [rows][d] twice
     Dev vqn, vla, chunk_ws, chunk_flag;  // the chunk-parallel memory of the tolerance mode: unit queries, log rates, its work space
+    Dev vrr;                             // a chunk of tokens through the streaming pass: every token's rr [T][rows][d]
     Dev sig;           // --neuromod: [rows][4] NE, ACh, DA (and one unused) of the step's token-rows
     // --dopamine / --mood: block 0's normed output [rows][d], the rows the head reads (the position before each), the
     // head's logits for them [rows][vocab], surprise s and z [rows], moods [rows][k], the current's gain and the MLP's output [rows][d]
@@ -540,6 +541,12 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
 // with its slice resident in shared memory, the engram read token by token.  Every value is the one T single steps give.
 enum StepPhase { PHASE_ALL = 0, PHASE_BEGIN = 1, PHASE_END = 2 };  // BEGIN stops once the engram's q,k,v exist; END resumes after its read
 
+// whether a chunk of T tokens takes the chunk-parallel (tensor-core) form of the memory: then the state itself is worked on
+bool chunk_form_applies(const ava_engine* e, int T) {
+    return e->fast && e->chunk_mem && T > 1 && !e->keep && mem_chunk_covers(e->cfg.head_size, T, e->cfg.mem_momentum);
+}
+
+
 // One lane: rows [r0, r0 + rows) of the state, with the lane's work buffers, queued on stream st.  tok, logits and next
 // are the caller's whole buffers (a lane reads and writes its own rows of them).
 // blk0, blk1: the blocks [blk0, blk1) queued by this call (with what precedes block 0 when blk0 == 0, and the head and the
@@ -681,6 +688,7 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
         // One token of the plain memory takes the streaming pass: this token's alpha, w, ah and values go straight into
         // the state's pending set (the one this step writes), the pass reads the set the step before wrote.
         const bool stream = T == 1 && !(c.mem_momentum > 0.0f);
+        const bool stream_chunk = T > 1 && !(c.mem_momentum > 0.0f) && !chunk_form_applies(e, T);
         const int wset = s->pend_set ^ 1;
         if (stream) {
             mp.ex = s->pend_at(wset, 0, i) + so; mp.w = s->pend_at(wset, 1, i) + so; mp.ah = s->pend_at(wset, 2, i) + so; mp.v = s->pend_at(wset, 3, i) + so;
@@ -691,7 +699,7 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
             prof_end(e);
             mp.rh_w = w.rh_gw.as<float>();
         }
-        const bool use_chunk = e->fast && e->chunk_mem && T > 1 && !e->keep && mem_chunk_covers(hs, T, c.mem_momentum);
+        const bool use_chunk = chunk_form_applies(e, T);
         if (use_chunk) {
             const size_t need = mem_chunk_workspace_bytes(rows * nh, hs, T / 64);
             if (w.chunk_ws.bytes < need) CK(w.chunk_ws.alloc(need));
@@ -783,6 +791,34 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
             }
         }
         if (chunked) {
+        } else if (stream_chunk) {
+            // a chunk of tokens, one streaming pass per token: token t's pass applies token t - 1's update (the vectors
+            // of the whole chunk lie in the work buffers; the first token takes what the state has pending) and leaves
+            // its own rr beside them; the last token's update stays pending in the state.  One read and one write of
+            // the state per token, as in decoding; the same bits.
+            if (w.vrr.bytes < Md * sizeof(float)) CK(w.vrr.alloc(Md * sizeof(float)));
+            for (int t = 0; t < T; ++t) {
+                const size_t at = (size_t)t * Rd, ah_ = (size_t)t * rows * nh;
+                MemStreamArgs ms{};
+                ms.f = mh.f; ms.M = rows; ms.nh = nh; ms.hs = hs; ms.cw = e->cw;
+                ms.e = mp.e + at; ms.qg = mp.qg + at; ms.v = mp.v + at; ms.qw = mp.qw + ah_; ms.qa = mp.qa + ah_;
+                ms.y = mh.y + at;
+                ms.rr_out = w.vrr.as<float>() + at;
+                if (t > 0) {
+                    const size_t pr = at - Rd;
+                    ms.px = mp.ex + pr; ms.pw = mp.w + pr; ms.pah = mp.ah + pr; ms.pv = mp.v + pr; ms.prr = w.vrr.as<float>() + pr;
+                } else if (s->pending) {
+                    const int rset = s->pend_set;
+                    ms.px = s->pend_at(rset, 0, i) + so; ms.pw = s->pend_at(rset, 1, i) + so; ms.pah = s->pend_at(rset, 2, i) + so;
+                    ms.pv = s->pend_at(rset, 3, i) + so; ms.prr = s->pend_at(rset, 4, i) + so;
+                }
+                if (!launch_mem_stream(st, ms)) return e->fail(AVA_ERR_CAPACITY, "memory head size not covered by the streaming pass");
+            }
+            const size_t last = (size_t)(T - 1) * Rd;
+            const float* srcs[5] = {mp.ex + last, mp.w + last, mp.ah + last, mp.v + last, w.vrr.as<float>() + last};
+            for (int k = 0; k < 5; ++k)
+                CK(cudaMemcpyAsync(s->pend_at(wset, k, i) + so, srcs[k], Rd * sizeof(float), cudaMemcpyDeviceToDevice, st));
+            e->launches += T - 1;
         } else if (stream) {
             MemStreamArgs ms{};
             ms.f = mh.f; ms.M = rows; ms.nh = nh; ms.hs = hs; ms.cw = e->cw;
@@ -1048,7 +1084,8 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
                 StepPhase phase = PHASE_ALL) {
     // a token's pending set is complete once its last block is through: a step split in two (BEGIN, END) writes one set
     // across both halves, so the sets change places after ALL or END only
-    const bool streams_state = e->cfg.fast_mem && T == 1 && !(e->cfg.mem_momentum > 0.0f) && phase != PHASE_BEGIN;
+    // (a chunk of tokens of the plain memory streams too, token after token, unless it takes the chunk-parallel form)
+    const bool streams_state = e->cfg.fast_mem && !(e->cfg.mem_momentum > 0.0f) && phase != PHASE_BEGIN && !(T > 1 && chunk_form_applies(e, T));
     if (!streams_state && T > 1) {
         const int frc = flush_pending(e, s);  // a chunk of tokens works on the state itself
         if (frc) return frc;

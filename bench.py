@@ -253,8 +253,8 @@ def measure_prefill(model, cfg, local, world, dist, rows, tokens, chunk, seed0, 
                              "flops_per_token": {"executed": executed, "algorithmic": algorithmic}, "traffic": None}}
     return {"value": world * rows * tokens / (ms * 1e-3), "unit": "tokens/s", "rows_per_gpu": rows, "tokens_per_row": tokens, "chunk": chunk,
             "ms": ms, "gpu_launches": int(model.launches - l0),
-            "what": "chunked prompt reading, bit-identical to stepping (CUDA-core products in k order, LIF time scan, fast-weight slice "
-                    "resident in shared memory per chunk, engram read token by token); config 2 is 8192 tokens per row, this is its first part"}
+            "what": "chunked prompt reading, bit-identical to stepping (CUDA-core products in k order, LIF time scan, one streaming pass of the "
+                    "fast weights per token, engram read token by token); config 2 is 8192 tokens per row, this is its first part"}
 
 
 # ------------------------------------------------------------------------------------------------- GPU arm
