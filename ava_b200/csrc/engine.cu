@@ -1372,14 +1372,9 @@ int ava_engine_create(const ava_config* cfg, int device, ava_engine** out) {
         return AVA_ERR_CUDA;
     }
     e->cur = e->stream;
-    if (!std::getenv("AVA_NO_SIDE")) {
-        cudaStreamCreateWithFlags(&e->side_stream, cudaStreamNonBlocking);
-        cudaEventCreateWithFlags(&e->side_go, cudaEventDisableTiming);
-        cudaEventCreateWithFlags(&e->side_done, cudaEventDisableTiming);
-    }
-    if (const char* v = std::getenv("AVA_PDL")) g_pdl = std::atoi(v) != 0;
-    if (const char* v = std::getenv("AVA_LANES")) e->n_lanes = std::max(1, std::min(8, std::atoi(v)));
-    if (const char* v = std::getenv("AVA_GEMM2")) e->gemm2 = std::atoi(v) != 0;
+    cudaStreamCreateWithFlags(&e->side_stream, cudaStreamNonBlocking);
+    cudaEventCreateWithFlags(&e->side_go, cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&e->side_done, cudaEventDisableTiming);
     const char* why = find_blocker(e->cfg, &e->cw, &e->rb);
     if (why) e->blocker = why;
     if (!why) {

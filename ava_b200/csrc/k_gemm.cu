@@ -627,13 +627,8 @@ void prefer_max_shared(const void* kernel, int percent_for_this) {
     for (int i = 0; i < n; ++i)
         if (seen[i].k == kernel && seen[i].dev == dev) return;
     // half of it as shared memory: measured best for the step as a whole (all of it starves the kernels that lean on L1)
-    static int percent = -2;
-    if (percent == -2) {
-        percent = 50;
-        if (const char* v = std::getenv("AVA_CARVEOUT")) percent = std::atoi(v);
-    }
-    const int pc = percent_for_this >= 0 ? percent_for_this : percent;
-    if (pc >= 0) cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, pc);
+    const int percent = 50;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, percent_for_this >= 0 ? percent_for_this : percent);
     if (n < 512) seen[n++] = {kernel, dev};
 }
 

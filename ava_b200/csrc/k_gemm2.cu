@@ -267,8 +267,7 @@ int g_gemm2_force = 0;  // tuning override (0: choose by shape)
 bool launch_q8_gemm2(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int sm_count) {
     if (a.K % G2_BK || a.N % 16 || a.ldw % 16 || a.lda % 4 || a.ldc % 4 || a.M < 1) return false;
     if ((reinterpret_cast<uintptr_t>(a.A) | reinterpret_cast<uintptr_t>(a.W) | reinterpret_cast<uintptr_t>(a.C) | reinterpret_cast<uintptr_t>(a.scale)) & 15) return false;
-    static const int env_force = std::getenv("AVA_GEMM2_FORCE") ? std::atoi(std::getenv("AVA_GEMM2_FORCE")) : 0;  // tuning aid
-    switch (g_gemm2_force ? g_gemm2_force : env_force) {
+    switch (g_gemm2_force) {
         case 1: launch_tile2<64, 64, 8, 4>(st, a, epi); return true;
         case 2: launch_tile2<128, 64, 8, 4>(st, a, epi); return true;
         case 3: launch_tile2<64, 128, 8, 8>(st, a, epi); return true;

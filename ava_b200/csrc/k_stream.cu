@@ -29,20 +29,10 @@ namespace ava {
 namespace {
 
 
-template <int MODE>
-__device__ __forceinline__ float4 ldg_stream(const float* p) {
-    if ((MODE & 3) == 0) return __ldcs(reinterpret_cast<const float4*>(p));
-    if ((MODE & 3) == 1) return __ldcg(reinterpret_cast<const float4*>(p));
-    if ((MODE & 3) == 2) return __ldlu(reinterpret_cast<const float4*>(p));
-    return *reinterpret_cast<const float4*>(p);
-}
-template <int MODE>
-__device__ __forceinline__ void stg_stream(float* p, float4 v) {
-    if ((MODE >> 2) == 0) __stcs(reinterpret_cast<float4*>(p), v);
-    else if ((MODE >> 2) == 1) __stcg(reinterpret_cast<float4*>(p), v);
-    else if ((MODE >> 2) == 2) __stwt(reinterpret_cast<float4*>(p), v);
-    else *reinterpret_cast<float4*>(p) = v;
-}
+// loads through the default path, stores that stay out of L1 (st.global.cg): measured best of the pairings of cache
+// hints tried (0.92 of the copy bandwidth against 0.86 with streaming hints on both)
+__device__ __forceinline__ float4 ldg_stream(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ void stg_stream(float* p, float4 v) { __stcg(reinterpret_cast<float4*>(p), v); }
 
 __device__ __forceinline__ float4 pending_update(float4 f, float x, float w, float ah, float4 pv, float4 prr) {
     f.x = sub(add(mul(f.x, x), mul(w, pv.x)), mul(ah, prr.x));
@@ -58,7 +48,7 @@ __device__ __forceinline__ float4 pending_update(float4 f, float x, float w, flo
 // slices stream side by side at the pace of HBM and end together, whatever the count of (row, head) pairs against SMs.
 // SD: rows a lane keeps in flight (16, or 32 when the launch has too few warps to keep HBM busy with 16)
 // ALT: the updated state goes to a.f_out (a state that commits at the end) instead of back in place
-template <bool PEND, int MODE, int SD, bool ALT = false>
+template <bool PEND, int SD, bool ALT = false>
 __global__ void __launch_bounds__(256) mem_stream_kernel(const MemStreamArgs a) {
     pdl_enter();
     extern __shared__ __align__(16) float vs[];
@@ -96,7 +86,7 @@ __global__ void __launch_bounds__(256) mem_stream_kernel(const MemStreamArgs a) 
     float4 r = make_float4(-0.0f, -0.0f, -0.0f, -0.0f), t = r;
     float4 buf[SD];
 #pragma unroll
-    for (int i = 0; i < SD; ++i) buf[i] = ldg_stream<MODE>(fp + (size_t)i * cw);
+    for (int i = 0; i < SD; ++i) buf[i] = ldg_stream(fp + (size_t)i * cw);
     for (int row = 0; row < hs; row += SD) {
         float* rp = fp + (size_t)row * cw;
         float* wp = fq + (size_t)row * cw;
@@ -115,10 +105,10 @@ __global__ void __launch_bounds__(256) mem_stream_kernel(const MemStreamArgs a) 
             for (int j = 0; j < 4; ++j) {
                 const int i = i4 + j;
                 float4 f = buf[i];
-                if (row + SD < hs) buf[i] = ldg_stream<MODE>(rp + (size_t)(SD + i) * cw);  // the row sixteen ahead takes the freed register
+                if (row + SD < hs) buf[i] = ldg_stream(rp + (size_t)(SD + i) * cw);  // the row sixteen ahead takes the freed register
                 if (PEND) {
                     f = pending_update(f, xx[j], ww[j], hh[j], pv, prr);
-                    stg_stream<MODE>(wp + (size_t)i * cw, f);
+                    stg_stream(wp + (size_t)i * cw, f);
                 }
                 r.x = fma(f.x, ee[j], r.x); r.y = fma(f.y, ee[j], r.y); r.z = fma(f.z, ee[j], r.z); r.w = fma(f.w, ee[j], r.w);
                 t.x = fma(f.x, gg[j], t.x); t.y = fma(f.y, gg[j], t.y); t.z = fma(f.z, gg[j], t.z); t.w = fma(f.w, gg[j], t.w);
@@ -161,12 +151,7 @@ __global__ void mem_flush_kernel(float* f, const float* __restrict__ px, const f
 bool launch_mem_stream(cudaStream_t st, const MemStreamArgs& a) {
     const bool pend = a.px != nullptr;
     const size_t smem = (size_t)(pend ? 5 : 2) * a.hs * sizeof(float);
-    static int wpb = 2;  // warps per block (AVA_STREAM_WPB in the environment overrides: tuning)
-    static bool read_env = false, read_env2 = false;
-    if (!read_env) {
-        read_env = true;
-        if (const char* v = std::getenv("AVA_STREAM_WPB")) wpb = std::max(1, std::min(8, std::atoi(v)));
-    }
+    const int wpb = 2;  // warps per block: small blocks, so that every warp of the launch is resident from the start
     const int warps_head = (a.hs + 127) / 128, warps = std::min(wpb, warps_head);
     if (a.hs % 16 || a.cw % 4 || smem > 64 * 1024) return false;
     MemStreamArgs b = a;
@@ -176,20 +161,16 @@ bool launch_mem_stream(cudaStream_t st, const MemStreamArgs& a) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         launch_k(kernel, dim3(grid), dim3(warps * 32), smem, st, b);
     };
-    // loads through the default path, stores that stay out of L1 (measured best of the sixteen pairings: 0.92 of the copy
-    // bandwidth against 0.86 with streaming hints on both); rows in flight: about 10 MB over the whole GPU are needed
-    static int deep_below = 1200;  // warps (AVA_STREAM_DEEP in the environment overrides: tuning)
-    if (!read_env2) {
-        read_env2 = true;
-        if (const char* v = std::getenv("AVA_STREAM_DEEP")) deep_below = std::atoi(v);
-    }
+    // rows in flight per lane: sixteen, or thirty-two when the launch has too few warps to keep HBM busy with sixteen (about 10 MB
+    // in flight over the whole GPU are needed)
+    const int deep_below = 1200;  // warps
     const bool deep = (long)a.M * a.nh * warps_head < deep_below;
-    if (!pend) { go(mem_stream_kernel<false, 7, 16>); return true; }
+    if (!pend) { go(mem_stream_kernel<false, 16>); return true; }
     if (a.f_out) {
-        if (deep) go(mem_stream_kernel<true, 7, 32, true>); else go(mem_stream_kernel<true, 7, 16, true>);
+        if (deep) go(mem_stream_kernel<true, 32, true>); else go(mem_stream_kernel<true, 16, true>);
         return true;
     }
-    if (deep) go(mem_stream_kernel<true, 7, 32>); else go(mem_stream_kernel<true, 7, 16>);
+    if (deep) go(mem_stream_kernel<true, 32>); else go(mem_stream_kernel<true, 16>);
     return true;
 }
 

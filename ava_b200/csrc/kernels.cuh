@@ -22,7 +22,7 @@ __device__ __forceinline__ void pdl_enter() {
 #endif
 
 extern thread_local cudaError_t g_launch_error;
-extern int g_pdl;  // 1: launch with the programmatic-serialization attribute (default; AVA_PDL=0 in the environment turns it off)
+extern int g_pdl;  // 1: launch with the programmatic-serialization attribute (the default)
 
 // Every kernel asks for the same split of an SM's on-chip memory between shared memory and L1.  An SM cannot change the
 // split while blocks are resident on it, so kernels that ask for different splits do not run side by side on one SM: a
