@@ -159,15 +159,22 @@ def run_reference(args, cfg, rank):
     if rank != 0:
         return
     from ava_b200 import synth
-    threads = os.cpu_count() or 1
     rows = 16
     w = synth.model(cfg, 0, "bench")
+    # the port's threading does not always gain from every core of a large host: a short trial at all, 16 and 8 threads
+    # picks the count the timed run uses (the fastest), and the line says which
+    allc = os.cpu_count() or 1
+    tried = {}
+    for th in sorted({allc, min(allc, 16), min(allc, 8)}, reverse=True):
+        tried[th] = cpu_reference(cfg, w, 6, 2, rows, th)[0]
+    threads = max(tried, key=tried.get)
     val, ms, sample = cpu_reference(cfg, w, args.steps, args.warmup, rows, threads)
     line = {"metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations x int8 weights",
             "data": "synthetic", "impl": "reference",
             "config": {"workload": "benchmark configuration 1 (Ava-0.4-shaped decode), bounded CPU sample", "rows": rows},
-            "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample,
+                             "threads_tried": {str(k): v for k, v in tried.items()}, "host_cores": allc},
             "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
@@ -529,7 +536,8 @@ def main():
             if th < threads:
                 sweep[str(th)] = cpu_reference(cfg, weights, 8 * th, 2, 16, th)[0]
         one, one_ms, one_sample = cpu_reference(cfg, weights, 64, 4, 1, threads)
-        line["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample,
+        best = max(sweep, key=sweep.get)
+        line["cpu_baseline"] = {"value": sweep[best], "unit": UNIT, "cores": int(best), "kind": "port", "sample": sample.replace(f"{threads} threads", f"{best} threads (the fastest of those tried)"),
                                 "by_threads": sweep,
                                 "config0_batch1": {"value": one, "unit": UNIT, "ms_per_token": one_ms, "sample": one_sample}}
     elif rank == 0:
