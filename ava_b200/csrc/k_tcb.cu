@@ -10,7 +10,7 @@
 // operands to about 2^-24 each: an f32 product with the tensor core's summation order.
 //
 // One block of 256 threads per 128 x BN tile of one batch item; k-tiles of 64 in a ring of stages.  Thread 0 brings the
-// limb tiles in by TMA (2-D tiled, 128-byte swizzle; no cluster multicast), thread 32 issues the multiply-adds and
+// limb tiles in by TMA (2-D tiled, 128-byte swizzle; every block fetches its own tiles), thread 32 issues the multiply-adds and
 // commits each stage's "empty" barrier, all eight warps read the accumulator back (tcgen05.ld) for the epilogue:
 //   TCB_STORE   C = acc
 //   TCB_DECAY   C = colscale[b][n] * C + acc, and the three limbs of the new C written beside it (the state update of the
