@@ -476,7 +476,7 @@ uint16_t* limbs_for(ava_engine* e, const float* dst, int M, int K) {
 }
 
 int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w, float* C, int ldc, int M, GemmEpilogue epi, const LifParams* lif = nullptr, bool sparse = false,
-         const float* row_gain = nullptr) {
+         const float* row_gain = nullptr, bool int_rows = false) {
     GemmArgs g{};
     g.A = A;
     g.lda = lda;
@@ -490,6 +490,26 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
     g.K = w.din;
     if (lif) g.lif = *lif;
     if (epi == EPI_ADD) g.lif.ne = row_gain;  // [rows][NM_STRIDE]
+    // Rows of small integers (spikes) times int8 weights on the tensor cores, one bf16 limb each side: every product and
+    // partial sum is an integer below 2^24, so the f32 accumulator is exact in any order and the result is the event
+    // sum's bits.  Taken for a prompt chunk when the bf16 copy of the weights exists (fast products on).
+    if (int_rows && e->fast && w.wt.p && M >= 1024 && M % 128 == 0 && epi == EPI_ADD && !row_gain && lda == w.din && ldc == w.dout && w.din % 64 == 0 &&
+        w.dout % 4 == 0) {
+        const size_t need = (size_t)M * w.din * sizeof(uint16_t);
+        if (e->limbs.bytes < need) CK(e->limbs.alloc(need));
+        e->limbs_src = nullptr;
+        prof_begin(e, "tc.round");
+        launch_round_bf16(e->cur, A, (int64_t)M * w.din, e->limbs.as<uint16_t>());
+        prof_end(e);
+        TcbArgs t{};
+        t.a = e->limbs.as<uint16_t>(); t.rows_a = M; t.b = w.wt.as<uint16_t>(); t.rows_b = w.dout;
+        t.C = C; t.ldc = ldc; t.M = M; t.N = w.dout; t.K = w.din; t.batch = 1;
+        t.colscale = w.sp(); t.status = e->status.as<uint32_t>();
+        prof_begin(e, cls);
+        const bool launched = launch_tc_bgemm(e->cur, t, TCB_SCALE_ADD);
+        prof_end(e);
+        if (launched) return AVA_OK;
+    }
     // with fast products a prompt chunk's k-WTA output is multiplied densely on the tensor cores as well (a quarter of
     // its entries are non-zero: over thousands of token-rows the dense product is the shorter one); a decode step's
     // few hundred rows keep the exact event sum
@@ -658,7 +678,7 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
             spikes = w.eo.as<float>();
             dbg(e, "stp_out", i, spikes, M, d);
         }
-        gemm(e, "gemm.wout", spikes, d, b.wout, x, d, M, EPI_ADD, nullptr, true);
+        gemm(e, "gemm.wout", spikes, d, b.wout, x, d, M, EPI_ADD, nullptr, true, nullptr, !c.stp);
         dbg(e, "x_lif", i, x, M, d);
 
         // ---- the fast-weight memory (kinds D and A; a kind-S block goes on to its MLP)
@@ -2253,10 +2273,10 @@ int ava_engine_set_fast_products(ava_engine* e, int32_t on) {
     if (!e->finalized) return e->fail(AVA_ERR_ARG, "engine not finalized");
     CK(cudaSetDevice(e->device));
     if (on) {
-        // bf16 [dout][din] copies of the dense matrices and of W_2 (W_out, driven by spikes, keeps the exact event sum)
+        // bf16 [dout][din] copies of the matrices (exact: int8 values)
         std::vector<QMat*> mats{&e->head};
         for (auto& b : e->blocks)
-            for (QMat* m : {&b->win, &b->proj, &b->wo, &b->eqkv, &b->ewo, &b->w1, &b->w2}) mats.push_back(m);
+            for (QMat* m : {&b->win, &b->wout, &b->proj, &b->wo, &b->eqkv, &b->ewo, &b->w1, &b->w2}) mats.push_back(m);
         for (QMat* m : mats) {
             if (!m->q.p || m->wt.p || m->din % 64 || m->dout % 4) continue;
             CK(m->wt.alloc((size_t)m->din * m->dout * sizeof(uint16_t)));

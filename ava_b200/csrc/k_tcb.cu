@@ -13,6 +13,9 @@
 // limb tiles in by TMA (2-D tiled, 128-byte swizzle; every block fetches its own tiles), thread 32 issues the multiply-adds and
 // commits each stage's "empty" barrier, all eight warps read the accumulator back (tcgen05.ld) for the epilogue:
 //   TCB_STORE   C = acc
+//   TCB_SCALE_ADD  C = C + acc * colscale[b][n]: the int8-weight product of integer-valued rows (spikes), one limb each side:
+//               every product and every partial sum is an integer below 2^24, so the accumulator is exact whatever the
+//               order, and the result is the ordered sum's bits
 //   TCB_DECAY   C = colscale[b][n] * C + acc, and the three limbs of the new C written beside it (the state update of the
 //               chunked memory: the next step multiplies by this state, so its limbs are made where it is produced)
 // Every wait is bounded; a wait that runs out sets ST_WAIT_TIMEOUT and the tile is not written.
@@ -47,7 +50,7 @@ __global__ void __launch_bounds__(B_THREADS) tc_bgemm_kernel(const __grid_consta
     const int m0 = blockIdx.y * B_BM, n0 = blockIdx.x * BN, bz = blockIdx.z;
     const int kt1 = a.K / B_BK, kt = kt1 + a.K2 / B_BK;   // k-tiles of the operands proper, then of the second stretch
 
-    if (EPI == TCB_DECAY) {
+    if (EPI == TCB_DECAY || EPI == TCB_SCALE_ADD) {
         // the tile of the old C is wanted by the epilogue only: ask for it now, so that it waits in L2 by then
         const float* ctile = a.C + (size_t)bz * a.c_batch_stride + (size_t)m0 * a.ldc + n0;
         for (int n = tid; n < B_BM * (BN / 32); n += B_THREADS) {
@@ -159,7 +162,7 @@ __global__ void __launch_bounds__(B_THREADS) tc_bgemm_kernel(const __grid_consta
         const int c = n0 + c0 + sub_c;           // this lane's four columns
         const bool col_ok = c < a.N && acc_ok;   // N is a multiple of 4
         float4 prev[8], g = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (EPI == TCB_DECAY) {  // the old values: asked for before the staging, all eight row groups at once
+        if (EPI == TCB_DECAY || EPI == TCB_SCALE_ADD) {  // the old values: asked for before the staging, all eight row groups at once
 #pragma unroll
             for (int it = 0; it < 8; ++it) {
                 const int row = m0 + wq * 32 + it * 4 + sub_r;
@@ -180,6 +183,10 @@ __global__ void __launch_bounds__(B_THREADS) tc_bgemm_kernel(const __grid_consta
             if (EPI == TCB_DECAY) {
                 const float4 x = prev[it];
                 o = make_float4(add(mul(x.x, g.x), o.x), add(mul(x.y, g.y), o.y), add(mul(x.z, g.z), o.z), add(mul(x.w, g.w), o.w));
+            }
+            if (EPI == TCB_SCALE_ADD) {  // the int8 product's epilogue: the sum times the column's scale, added to what is there
+                const float4 x = prev[it];
+                o = make_float4(add(x.x, mul(o.x, g.x)), add(x.y, mul(o.y, g.y)), add(x.z, mul(o.z, g.z)), add(x.w, mul(o.w, g.w)));
             }
             *reinterpret_cast<float4*>(cbase + (size_t)row * a.ldc + c) = o;
             if (EPI == TCB_DECAY) {
@@ -229,6 +236,11 @@ bool launch_tc_bgemm(cudaStream_t st, const TcbArgs& a, int epi) {
     if (a.K % B_BK || a.K2 % B_BK || a.K2 < 0 || a.M % B_BM || a.N % 4 || a.batch < 1) return false;
     if (a.K2 > 0 && (!a.a2 || !a.b2 || a.lda2 < a.K2 || a.ldb2 < a.K2 || a.lda2 % 8 || a.ldb2 % 8)) return false;
     // N 128: two stages of 96 KB, one block per SM (measured a little ahead of one stage with two blocks per SM)
+    if (epi == TCB_SCALE_ADD) {
+        // one limb each side (operands exact in bf16: spikes and int8 weights), four stages of 32 KB
+        if (a.K2 > 0) return false;
+        return a.N % 128 == 0 ? launch_one<128, 1, 1, 4, TCB_SCALE_ADD>(st, a) : launch_one<64, 1, 1, 4, TCB_SCALE_ADD>(st, a);
+    }
     if (a.N % 128 == 0) return epi == TCB_DECAY ? launch_one<128, 3, 3, 2, TCB_DECAY>(st, a) : launch_one<128, 3, 3, 2, TCB_STORE>(st, a);
     return epi == TCB_DECAY ? launch_one<64, 3, 3, 3, TCB_DECAY>(st, a) : launch_one<64, 3, 3, 3, TCB_STORE>(st, a);
 }

@@ -131,7 +131,7 @@ void launch_split3(cudaStream_t st, const float* x, int64_t n, uint16_t* out);
 
 // Batched f32-accurate products on the tensor cores (k_tcb.cu): C[b] = A[b] . B[b]^T with both operands as three bf16
 // limbs, K-major planes [limb][batch * rows][K].
-enum { TCB_STORE = 0, TCB_DECAY = 1 };
+enum { TCB_STORE = 0, TCB_DECAY = 1, TCB_SCALE_ADD = 2 };
 struct TcbArgs {
     const uint16_t* a;        // [3][rows_a][K], rows_a = batch * M
     const uint16_t* b;        // [3][rows_b][K], rows_b = batch * N

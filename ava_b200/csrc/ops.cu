@@ -129,6 +129,36 @@ int ava_op_q8_tc_matmul(int device, const float* x, int32_t m, const int8_t* q, 
     return AVA_OK;
 }
 
+/* Rows of small integers (spikes) times int8 weights on the tensor cores, added to y: y += (x . q) * scale.  Every product
+ * and partial sum is an integer below 2^24, so the result is the ordered sum's bits (checked against the event sum). */
+int ava_op_q8_spike_tc_matmul(int device, const float* x, int32_t m, const int8_t* q, const float* scale, int32_t din, int32_t dout, float* y) {
+    if (!x || !q || !scale || !y || m <= 0 || din <= 0 || dout <= 0) return AVA_ERR_ARG;
+    if (din % 64 || dout % 4 || m % 128) return AVA_NOT_APPLICABLE;
+    int rc = begin(device);
+    if (rc) return rc;
+    Tmp dx, dq, ds, dy, dl, dw, dst;
+    OCK(up(dx, x, (size_t)m * din * 4));
+    OCK(up(dq, q, (size_t)din * dout));
+    OCK(up(ds, scale, (size_t)dout * 4));
+    OCK(up(dy, y, (size_t)m * dout * 4));
+    OCK(up(dl, nullptr, (size_t)m * din * 2));
+    OCK(up(dw, nullptr, (size_t)din * dout * 2));
+    OCK(up(dst, nullptr, 4));
+    OCK(cudaMemset(dst.p, 0, 4));
+    launch_widen_transpose(0, dq.as<int8_t>(), din, dout, dw.as<uint16_t>());
+    launch_round_bf16(0, dx.as<float>(), (int64_t)m * din, dl.as<uint16_t>());
+    TcbArgs t{};
+    t.a = dl.as<uint16_t>(); t.rows_a = m; t.b = dw.as<uint16_t>(); t.rows_b = dout;
+    t.C = dy.as<float>(); t.ldc = dout; t.M = m; t.N = dout; t.K = din; t.batch = 1; t.colscale = ds.as<float>(); t.status = dst.as<uint32_t>();
+    if (!launch_tc_bgemm(0, t, TCB_SCALE_ADD)) return AVA_NOT_APPLICABLE;
+    if ((rc = end_())) return rc;
+    uint32_t st = 0;
+    OCK(cudaMemcpy(&st, dst.p, 4, cudaMemcpyDeviceToHost));
+    if (st) return AVA_ERR_STATE;
+    OCK(cudaMemcpy(y, dy.p, (size_t)m * dout * 4, cudaMemcpyDeviceToHost));
+    return AVA_OK;
+}
+
 int ava_op_sample(int device, const float* logits, int32_t m, int32_t vocab, float temperature, int32_t top_k, const double* uniform, uint32_t* next) {
     if (!logits || !uniform || !next || m <= 0 || vocab <= 0) return AVA_ERR_ARG;
     int rc = begin(device);

@@ -147,6 +147,7 @@ extern "C" {
     pub fn ava_op_lif(device: c_int, cur: *const f32, beta: *const f32, theta: *const f32, rho: *const f32, gain: *const f32, spikes: i32, v0: *const f32, s0: *const f32, a0: *const f32, m: i32, d: i32, s1: *mut f32, v1: *mut f32, a1: *mut f32) -> c_int;
     pub fn ava_op_kwta(device: c_int, u: *const f32, m: i32, n: i32, k: i32, relu2: i32, a: *mut f32) -> c_int;
     pub fn ava_op_mem_heads(device: c_int, m: i32, hs: i32, e: *const f32, v: *const f32, w: *const f32, ah: *const f32, qg: *const f32, ex: *const f32, qw: *const f32, qa: *const f32, f: *mut f32, y: *mut f32) -> c_int;
+    pub fn ava_op_q8_spike_tc_matmul(device: c_int, x: *const f32, m: i32, q: *const i8, scale: *const f32, din: i32, dout: i32, y: *mut f32) -> c_int;
     pub fn ava_mem_heads_static(device: c_int, stream: *mut c_void, m: i32, hs: i32, e: *const f32, v: *const f32, w: *const f32, ah: *const f32, qg: *const f32, ex: *const f32, qw: *const f32, qa: *const f32, f: *mut f32, y: *mut f32) -> c_int;
     pub fn ava_static_last_error() -> *const c_char;
     pub fn ava_op_attend(device: c_int, m: i32, n: i32, hs: i32, bf16_store: i32, q: *const f32, kc: *const f32, vc: *const f32, out: *mut f32) -> c_int;

@@ -201,8 +201,9 @@ int ava_engine_set_lanes(ava_engine* e, int32_t lanes);
  * every product exact (the f32 activation as three bf16 limbs, the int8 weight exact in bf16), the f32 sum in the
  * tensor core's order instead of k = 0, 1, ...  The step's results then agree with the reference's to about 1e-6 of
  * each sum's magnitudes instead of bit for bit, and a membrane within that distance of its threshold can spike
- * differently.  W_out, driven by spikes, keeps the exact event sum, and so does W_2 in a decode step; over a prompt
- * chunk of 1024 token-rows or more W_2 is multiplied densely on the tensor cores too.  Costs 2 bytes per dense weight of
+ * differently.  In a decode step W_out and W_2 keep the exact event sum; over a prompt chunk of 1024 token-rows or more
+ * W_2 is multiplied densely on the tensor cores too, and W_out (rows of spikes: small integers) with one bf16 limb each
+ * side, which is exact (integer partial sums below 2^24): that product is still the event sum's bits.  Costs 2 bytes per dense weight of
  * device memory on first use.  Call after ava_engine_finalize, between steps. */
 int ava_engine_set_fast_products(ava_engine* e, int32_t on);
 /* With fast products on, a prompt chunk reads its two recurrent memories in chunk-parallel forms on the tensor cores
@@ -411,6 +412,11 @@ int ava_op_kwta(int device, const float* u, int32_t m, int32_t n, int32_t k, int
  * e, v, w, ah, qg, ex [m, hs]; qw, qa [m]; f [m, hs, hs] updated in place; y [m, hs]. */
 int ava_op_mem_heads(int device, int32_t m, int32_t hs, const float* e, const float* v, const float* w, const float* ah,
                      const float* qg, const float* ex, const float* qw, const float* qa, float* f, float* y);
+/* The same product for rows of small integers (spikes in {-2..2}) on the tensor cores, added to y: y += (x . q) * scale
+ * (no counterpart in the reference).  One bf16 limb each side is exact for such operands, and every partial sum is an
+ * integer below 2^24, so the f32 accumulator is exact whatever its order: the result is the ordered sum's bits
+ * (src/int8.rs:315-331).  m % 128, din % 64, dout % 4, else AVA_NOT_APPLICABLE. */
+int ava_op_q8_spike_tc_matmul(int device, const float* x, int32_t m, const int8_t* q, const float* scale, int32_t din, int32_t dout, float* y);
 /* No counterpart in the reference.  ava_op_mem_heads for callers that cannot allocate device memory (a latency-critical
  * thread that must not take the allocator's device-wide lock, a process whose GPU memory was handed out in full at
  * start-up): every pointer is DEVICE memory, `stream` is a cudaStream_t (NULL: the default stream), f [m, hs, hs] is

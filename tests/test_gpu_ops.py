@@ -138,6 +138,28 @@ def test_event_sum_bits_many_rows(orc, m, din, dout, density):
     assert not np.isnan(got[:m - 1]).any()
 
 
+@pytest.mark.parametrize("m,din,dout", [(128, 64, 64), (256, 768, 768), (1024, 768, 128), (128, 3072, 68)])
+def test_spike_rows_on_the_tensor_cores_are_the_event_sums_bits(orc, m, din, dout):
+    """Rows of spikes (integers in -2..2) times int8 weights with one bf16 limb each side on tcgen05: every partial sum is
+    an integer below 2^24, so the accumulator is exact in any order; times the scale and added to what is there, the
+    result is the bits of the ordered sum followed by the same multiply and add."""
+    rng = np.random.default_rng(m + din + dout)
+    q = rng.integers(-127, 128, (din, dout)).astype(np.int8)
+    sc = (rng.uniform(0.5, 1.5, dout) / 127).astype(np.float32)
+    x = (rng.integers(-2, 3, (m, din)) * (rng.random((m, din)) < 0.3)).astype(np.float32)
+    x[0] = 2.0   # the largest sums a row can make
+    x[1] = -2.0
+    y0 = rng.normal(size=(m, dout)).astype(np.float32)
+    got = engine.op_q8_spike_tc_matmul(x, q, sc, y0)
+    orc.set_threads(8)
+    try:
+        prod = orc.q8_matmul(x, q, sc)
+    finally:
+        orc.set_threads(1)
+    want = (y0 + prod).astype(np.float32)   # one rounding, as the residual add has
+    assert np.array_equal(bits(got), bits(want))
+
+
 def test_event_sum_more_rows_than_a_grid_dimension(orc):
     """70000 token-rows (a long prompt chunk of many sequences): more than one grid dimension holds (65535), so the
     rows go on in a second one; first, middle and last rows against the oracle, all rows against the dense kernel."""
