@@ -102,6 +102,9 @@ struct Work {
     Dev gz, lra, lrb;  // the gates' stages: [rows][gate_cols], [rows][d] twice
     Dev vqn, vla, chunk_ws, chunk_flag;  // the chunk-parallel memory of the tolerance mode: unit queries, log rates, its work space
     Dev vrr;                             // a chunk of tokens through the streaming pass: every token's rr [T][rows][d]
+    Dev limbs;                           // fast products: [3][rows][K] bf16 limbs of the current product's input
+    const float* limbs_src = nullptr;    // the f32 buffer whose limbs the producing kernel has just written there
+    int limbs_rows = 0;
     Dev sig;           // --neuromod: [rows][4] NE, ACh, DA (and one unused) of the step's token-rows
     // --dopamine / --mood: block 0's normed output [rows][d], the rows the head reads (the position before each), the
     // head's logits for them [rows][vocab], surprise s and z [rows], moods [rows][k], the current's gain and the MLP's output [rows][d]
@@ -168,9 +171,7 @@ struct ava_engine : Work {
     bool fast = false;     // dense products on the tensor cores (exact products, the tensor core's summation order)
     bool chunk_mem = true; // with fast: a prompt chunk's fast-weight memory in the chunk-parallel form (k_chunk.cu)
     int64_t chunked_blocks = 0, chunk_fallbacks = 0, chunked_reads = 0;
-    Dev limbs;             // [3][rows][d] bf16 limbs of the current product's input
-    const float* limbs_src = nullptr;  // the f32 buffer whose limbs the producing kernel has just written there
-    int limbs_rows = 0;
+    Work* cur_w = nullptr; // the lane being queued (its work buffers; set with `cur`)
 
     int long_seg = 0;      // > 0: the engram is always read in segments of this many keys (else only when it must be)
 
@@ -469,10 +470,10 @@ void dbg(ava_engine* e, const char* name, int block, const float* src, int rows,
 uint16_t* limbs_for(ava_engine* e, const float* dst, int M, int K) {
     if (!e->fast || K % 64) return nullptr;
     const size_t need = (size_t)3 * M * K * sizeof(uint16_t);
-    if (e->limbs.bytes < need && e->limbs.alloc(need) != cudaSuccess) return nullptr;
-    e->limbs_src = dst;
-    e->limbs_rows = M;
-    return e->limbs.as<uint16_t>();
+    if (e->cur_w->limbs.bytes < need && e->cur_w->limbs.alloc(need) != cudaSuccess) return nullptr;
+    e->cur_w->limbs_src = dst;
+    e->cur_w->limbs_rows = M;
+    return e->cur_w->limbs.as<uint16_t>();
 }
 
 int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w, float* C, int ldc, int M, GemmEpilogue epi, const LifParams* lif = nullptr, bool sparse = false,
@@ -496,13 +497,13 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
     if (int_rows && e->fast && w.wt.p && M >= 1024 && M % 128 == 0 && epi == EPI_ADD && !row_gain && lda == w.din && ldc == w.dout && w.din % 64 == 0 &&
         w.dout % 4 == 0) {
         const size_t need = (size_t)M * w.din * sizeof(uint16_t);
-        if (e->limbs.bytes < need) CK(e->limbs.alloc(need));
-        e->limbs_src = nullptr;
+        if (e->cur_w->limbs.bytes < need) CK(e->cur_w->limbs.alloc(need));
+        e->cur_w->limbs_src = nullptr;
         prof_begin(e, "tc.round");
-        launch_round_bf16(e->cur, A, (int64_t)M * w.din, e->limbs.as<uint16_t>());
+        launch_round_bf16(e->cur, A, (int64_t)M * w.din, e->cur_w->limbs.as<uint16_t>());
         prof_end(e);
         TcbArgs t{};
-        t.a = e->limbs.as<uint16_t>(); t.rows_a = M; t.b = w.wt.as<uint16_t>(); t.rows_b = w.dout;
+        t.a = e->cur_w->limbs.as<uint16_t>(); t.rows_a = M; t.b = w.wt.as<uint16_t>(); t.rows_b = w.dout;
         t.C = C; t.ldc = ldc; t.M = M; t.N = w.dout; t.K = w.din; t.batch = 1;
         t.colscale = w.sp(); t.status = e->status.as<uint32_t>();
         prof_begin(e, cls);
@@ -516,21 +517,21 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
     if (sparse && e->fast && w.wt.p && M >= 1024) sparse = false;
     if (e->fast && !sparse && !row_gain && w.wt.p && lda == w.din && w.din % 64 == 0 && w.dout % 4 == 0) {
         const size_t need = (size_t)3 * M * w.din * sizeof(uint16_t);
-        if (e->limbs.bytes < need) {
-            CK(e->limbs.alloc(need));
-            e->limbs_src = nullptr;
+        if (e->cur_w->limbs.bytes < need) {
+            CK(e->cur_w->limbs.alloc(need));
+            e->cur_w->limbs_src = nullptr;
         }
-        if (!(e->limbs_src == A && e->limbs_rows == M)) {  // the producer did not leave them
+        if (!(e->cur_w->limbs_src == A && e->cur_w->limbs_rows == M)) {  // the producer did not leave them
             prof_begin(e, "tc.split3");
-            launch_split3(e->cur, A, (int64_t)M * w.din, e->limbs.as<uint16_t>());
+            launch_split3(e->cur, A, (int64_t)M * w.din, e->cur_w->limbs.as<uint16_t>());
             prof_end(e);
         }
-        e->limbs_src = nullptr;  // one product per set of limbs
+        e->cur_w->limbs_src = nullptr;  // one product per set of limbs
         TcGemmArgs t{};
-        t.a_limbs = e->limbs.as<uint16_t>();
+        t.a_limbs = e->cur_w->limbs.as<uint16_t>();
         t.w_bf16 = w.wt.as<uint16_t>();
         t.scale = w.sp();
-        t.C = epi == EPI_LIF ? e->yraw.as<float>() : C;  // the currents' buffer is free while the LIF layer runs
+        t.C = epi == EPI_LIF ? e->cur_w->yraw.as<float>() : C;  // the currents' buffer is free while the LIF layer runs
         t.ldc = epi == EPI_LIF ? w.dout : ldc;
         t.M = M;
         t.N = w.dout;
@@ -542,7 +543,7 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
         if (launched) {
             if (epi == EPI_LIF) {
                 prof_begin(e, "lif");
-                launch_lif(e->cur, e->yraw.as<float>(), *lif, M, w.dout);
+                launch_lif(e->cur, e->cur_w->yraw.as<float>(), *lif, M, w.dout);
                 prof_end(e);
             }
             return AVA_OK;
@@ -576,6 +577,7 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
     const ava_config& c = e->cfg;
     const int d = c.d, L = c.n_blocks, nh = e->nh(), hs = c.head_size, H = c.hidden;
     e->cur = st;
+    e->cur_w = &w;
     tok += r0;  // a lane other than the first exists only for T == 1: its tokens are rows r0.. of the one token
     const size_t Sd = (size_t)s->rows * d;  // one block's carried LIF state over ALL rows of the state
     const size_t so = (size_t)r0 * d;       // this lane's first row inside a block's state
@@ -739,9 +741,9 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
         // q|k|v|e|g product (both are short of warps on their own); the per-row kernel then needs both
         // with fast products the first stage is a product of limbs on the tensor cores (the norm has left the limbs of h)
         bool tc_gates = false;
-        if (e->fast && !e->keep && b.gate_wl.p && M % 128 == 0 && d % 64 == 0 && e->limbs_src == h && e->limbs_rows == M) {
+        if (e->fast && !e->keep && b.gate_wl.p && M % 128 == 0 && d % 64 == 0 && e->cur_w->limbs_src == h && e->cur_w->limbs_rows == M) {
             TcbArgs g{};
-            g.a = e->limbs.as<uint16_t>(); g.rows_a = M; g.b = b.gate_wl.as<uint16_t>(); g.rows_b = e->gate_cols;
+            g.a = e->cur_w->limbs.as<uint16_t>(); g.rows_a = M; g.b = b.gate_wl.as<uint16_t>(); g.rows_b = e->gate_cols;
             g.C = mp.z; g.ldc = e->gate_cols; g.c_batch_stride = 0; g.M = M; g.N = e->gate_cols; g.K = d; g.batch = 1;
             g.status = e->status.as<uint32_t>();
             prof_begin(e, "gate_z");
@@ -1111,7 +1113,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         if (frc) return frc;
     }
     int lanes = 1;
-    if (e->n_lanes > 1 && T == 1 && phase == PHASE_ALL && !e->keep && !e->fast && (!e->prof || e->prof_lanes)) lanes = std::max(1, std::min(e->n_lanes, s->rows / 48));  // a lane of fewer rows gains nothing
+    if (e->n_lanes > 1 && T == 1 && phase == PHASE_ALL && !e->keep && !e->fast && (!e->prof || e->prof_lanes))  // (with fast products lanes measured no gain: 4.52 ms either way) lanes = std::max(1, std::min(e->n_lanes, s->rows / 48));  // a lane of fewer rows gains nothing
     if (lanes == 1) {
         const int rc1 = step_rows(e, *e, e->stream, s, 0, s->rows, tok, logits, next, want_logits, T, all_logits, phase);
         if (rc1 == AVA_OK && streams_state) {
@@ -1158,6 +1160,7 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         CK(cudaStreamWaitEvent(e->stream, w.lane_done, 0));
     }
     e->cur = e->stream;
+    e->cur_w = e;
     if (rc == AVA_OK && streams_state) {
         s->pend_set ^= 1;
         s->pending = true;
@@ -1392,6 +1395,7 @@ int ava_engine_create(const ava_config* cfg, int device, ava_engine** out) {
         return AVA_ERR_CUDA;
     }
     e->cur = e->stream;
+    e->cur_w = e.get();
     cudaStreamCreateWithFlags(&e->side_stream, cudaStreamNonBlocking);
     cudaEventCreateWithFlags(&e->side_go, cudaEventDisableTiming);
     cudaEventCreateWithFlags(&e->side_done, cudaEventDisableTiming);
