@@ -27,6 +27,7 @@
 #include <algorithm>
 
 #include "ava_math.h"
+#include "bf16_hw.cuh"
 #include "kernels.cuh"
 
 namespace ava {
@@ -35,12 +36,7 @@ namespace {
 
 constexpr int CC = 64;  // tokens per chunk
 
-__device__ __forceinline__ void limbs3(float x, uint16_t& l0, uint16_t& l1, uint16_t& l2) {
-    l0 = f_to_bf16(x);
-    const float r1 = x - bf16_to_f(l0);
-    l1 = f_to_bf16(r1);
-    l2 = f_to_bf16(r1 - bf16_to_f(l1));
-}
+__device__ __forceinline__ void limbs3(float x, uint16_t& l0, uint16_t& l1, uint16_t& l2) { limbs3_hw(x, l0, l1, l2); }
 
 // ---- scaling, in three kernels ------------------------------------------------------------------------------------
 // (1) the running sums of the log rates: one thread per (chunk, head, channel), the chunk's 64 tokens in order

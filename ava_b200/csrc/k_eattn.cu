@@ -22,6 +22,7 @@
 #include <cuda_runtime.h>
 
 #include "ava_math.h"
+#include "bf16_hw.cuh"
 #include "kernels.cuh"
 #include "tc_common.cuh"
 
@@ -37,12 +38,7 @@ constexpr uint32_t EA_TILE_K = EA_KEYS * EA_HS * 2;    // 8 KB
 constexpr uint32_t EA_OFF_P = 3 * EA_TILE_Q, EA_OFF_K = EA_OFF_P + 2 * EA_TILE_Q, EA_OFF_VT = EA_OFF_K + EA_TILE_K, EA_OFF_V = EA_OFF_VT + EA_TILE_K,
                    EA_OFF_BAR = EA_OFF_V + EA_TILE_K, EA_SMEM = EA_OFF_BAR + 64 + 1024;
 
-__device__ __forceinline__ void limbs3(float x, uint16_t& l0, uint16_t& l1, uint16_t& l2) {
-    l0 = f_to_bf16(x);
-    const float r1 = x - bf16_to_f(l0);
-    l1 = f_to_bf16(r1);
-    l2 = f_to_bf16(r1 - bf16_to_f(l1));
-}
+__device__ __forceinline__ void limbs3(float x, uint16_t& l0, uint16_t& l1, uint16_t& l2) { limbs3_hw(x, l0, l1, l2); }
 __device__ __forceinline__ uint32_t pack2(uint16_t a, uint16_t b) { return a | ((uint32_t)b << 16); }
 __device__ __forceinline__ void bar_arrive(uint64_t* bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(bar)) : "memory"); }
 __device__ __forceinline__ void fence_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -213,8 +209,8 @@ __global__ void __launch_bounds__(EA_THREADS) engram_chunk_attn_kernel(const __g
                 for (int i = 0; i < 8; ++i) {
                     const int j = ch * 8 + i;
                     const float p = (k0 + j < lim) ? __expf(__uint_as_float(s[j]) - m) * inv_l : 0.0f;
-                    p0[i] = f_to_bf16(p);
-                    p1[i] = f_to_bf16(p - bf16_to_f(p0[i]));
+                    p0[i] = bf16_rn_hw(p);
+                    p1[i] = bf16_rn_hw(p - bf16_widen(p0[i]));
                 }
                 const uint32_t off = swz128(tid, ch * 8);
                 *reinterpret_cast<uint4*>(sP + off) = make_uint4(pack2(p0[0], p0[1]), pack2(p0[2], p0[3]), pack2(p0[4], p0[5]), pack2(p0[6], p0[7]));

@@ -8,6 +8,7 @@
 #include <algorithm>
 
 #include "ava_math.h"
+#include "bf16_hw.cuh"
 #include "kernels.cuh"
 
 namespace ava {
@@ -144,12 +145,11 @@ __global__ void embed_kernel(const float* __restrict__ tok_emb, const uint32_t* 
 // ---------------------------------------------------------------------------------------------------- RMS norm
 // three bf16 limbs of v (their sum is v exactly) into planes [3][plane], for the tensor-core products
 __device__ __forceinline__ void store_limbs(uint16_t* limbs, int64_t plane, int64_t i, float v) {
-    const uint16_t hi = f_to_bf16(v);
-    const float r1 = sub(v, bf16_to_f(hi));
-    const uint16_t mid = f_to_bf16(r1);
+    uint16_t hi, mid, lo;
+    limbs3_hw(v, hi, mid, lo);
     limbs[i] = hi;
     limbs[plane + i] = mid;
-    limbs[2 * plane + i] = f_to_bf16(sub(r1, bf16_to_f(mid)));
+    limbs[2 * plane + i] = lo;
 }
 
 // One warp per row: the row is staged in shared memory, lane 0 takes the ordered sum, every lane scales.

@@ -23,6 +23,7 @@
 #include <cuda_runtime.h>
 
 #include "ava_math.h"
+#include "bf16_hw.cuh"
 #include "kernels.cuh"
 #include "tc_common.cuh"
 
@@ -194,12 +195,7 @@ __global__ void __launch_bounds__(B_THREADS) tc_bgemm_kernel(const __grid_consta
                 const float ov[4] = {o.x, o.y, o.z, o.w};
                 uint16_t l0[4], l1[4], l2[4];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    l0[q] = f_to_bf16(ov[q]);
-                    const float r1 = sub(ov[q], bf16_to_f(l0[q]));
-                    l1[q] = f_to_bf16(r1);
-                    l2[q] = f_to_bf16(sub(r1, bf16_to_f(l1[q])));
-                }
+                for (int q = 0; q < 4; ++q) limbs3_hw(ov[q], l0[q], l1[q], l2[q]);
                 const size_t at = ((size_t)bz * a.M + row) * a.N + c;
                 *reinterpret_cast<uint2*>(a.c_limbs + at) = make_uint2(l0[0] | ((uint32_t)l0[1] << 16), l0[2] | ((uint32_t)l0[3] << 16));
                 *reinterpret_cast<uint2*>(a.c_limbs + a.c_limb_plane + at) = make_uint2(l1[0] | ((uint32_t)l1[1] << 16), l1[2] | ((uint32_t)l1[3] << 16));
