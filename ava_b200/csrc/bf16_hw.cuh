@@ -1,6 +1,6 @@
 // bf16 limbs of an f32 value with the hardware's conversion (cvt.rn.bf16.f32: round to nearest even, one instruction
 // instead of the seven of the portable form in ava_math.h).  For the tolerance mode's kernels only: the exact paths
-// (the engram's bf16 store) keep f_to_bf16, whose treatment of NaN payloads the oracle shares.
+// (the engram's bf16 store) keep f_to_bf16, whose treatment of NaN payloads is part of the bit contract.
 #pragma once
 #include <cuda_runtime.h>
 

@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <chrono>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -17,6 +18,7 @@
 #include <map>
 #include <memory>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "../../include/ava_engine.h"
@@ -1113,7 +1115,9 @@ int step_device(ava_engine* e, ava_state* s, const uint32_t* tok, float* logits,
         if (frc) return frc;
     }
     int lanes = 1;
-    if (e->n_lanes > 1 && T == 1 && phase == PHASE_ALL && !e->keep && !e->fast && (!e->prof || e->prof_lanes))  // (with fast products lanes measured no gain: 4.52 ms either way) lanes = std::max(1, std::min(e->n_lanes, s->rows / 48));  // a lane of fewer rows gains nothing
+    // (with fast products lanes measured no gain: 4.52 ms per step either way, so that mode keeps one lane)
+    if (e->n_lanes > 1 && T == 1 && phase == PHASE_ALL && !e->keep && !e->fast && (!e->prof || e->prof_lanes))
+        lanes = std::max(1, std::min(e->n_lanes, s->rows / 48));  // a lane of fewer rows gains nothing
     if (lanes == 1) {
         const int rc1 = step_rows(e, *e, e->stream, s, 0, s->rows, tok, logits, next, want_logits, T, all_logits, phase);
         if (rc1 == AVA_OK && streams_state) {
@@ -2451,6 +2455,45 @@ int ava_split_step(ava_engine* e, ava_state* s, void* nccl_comm, int32_t rank, i
         CK(cudaMemcpyAsync(gathered_device, partial_device, part_n * sizeof(float), cudaMemcpyDeviceToDevice, e->stream));
     }
     if (rank == 0) return ava_split_step_end(e, s, gathered_device, world, logits_device, next_device);
+    return AVA_OK;
+}
+
+int ava_split_wait(ava_engine* e, void* nccl_comm, int32_t timeout_ms) {
+    if (!e || timeout_ms < 0) return AVA_ERR_ARG;
+    const NcclApi* n = nccl_comm ? nccl_api() : nullptr;
+    if (nccl_comm && !n) return e->fail(AVA_NOT_APPLICABLE, "no NCCL library: %s", nccl_dl_error());
+    CK(cudaSetDevice(e->device));
+    cudaEvent_t done;
+    CK(cudaEventCreateWithFlags(&done, cudaEventDisableTiming));
+    cudaError_t ce = cudaEventRecord(done, e->stream);
+    const auto t0 = std::chrono::steady_clock::now();
+    int why = 0;  // 1: NCCL reported an error, 2: the time ran out
+    int async_error = 0;
+    while (ce == cudaSuccess) {
+        ce = cudaEventQuery(done);
+        if (ce != cudaErrorNotReady) break;
+        ce = cudaSuccess;
+        if (n && n->CommGetAsyncError && n->CommGetAsyncError(nccl_comm, &async_error) == 0 && async_error != 0 && async_error != NCCL_IN_PROGRESS) {
+            why = 1;
+            break;
+        }
+        if (std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count() >= timeout_ms) {
+            why = 2;
+            break;
+        }
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+    if (why != 0) {
+        // The collective's kernel is waiting for a rank that will not come: only an abort ends it.  The communicator is
+        // gone after it, whatever the abort answers.
+        const bool aborted = n && n->CommAbort && n->CommAbort(nccl_comm) == 0;
+        if (aborted) cudaStreamSynchronize(e->stream);
+        cudaEventDestroy(done);
+        if (why == 1) return e->fail(AVA_ERR_CUDA, "NCCL: %s%s", n->GetErrorString(async_error), aborted ? " (communicator aborted)" : "");
+        return e->fail(AVA_ERR_CUDA, "the split step did not finish within %d ms%s", (int)timeout_ms, aborted ? " (communicator aborted)" : "");
+    }
+    cudaEventDestroy(done);
+    if (ce != cudaSuccess) return e->fail(AVA_ERR_CUDA, "%s", cudaGetErrorString(ce));
     return AVA_OK;
 }
 

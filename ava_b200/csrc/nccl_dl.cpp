@@ -39,6 +39,8 @@ void load() {
     g_api.AllGather = reinterpret_cast<decltype(g_api.AllGather)>(sym("ncclAllGather"));
     g_api.GetErrorString = reinterpret_cast<decltype(g_api.GetErrorString)>(sym("ncclGetErrorString"));
     g_api.GetVersion = reinterpret_cast<decltype(g_api.GetVersion)>(sym("ncclGetVersion"));
+    g_api.CommGetAsyncError = reinterpret_cast<decltype(g_api.CommGetAsyncError)>(dlsym(h, "ncclCommGetAsyncError"));
+    g_api.CommAbort = reinterpret_cast<decltype(g_api.CommAbort)>(dlsym(h, "ncclCommAbort"));
     g_ok = g_api.GetUniqueId && g_api.CommInitRank && g_api.CommDestroy && g_api.Broadcast && g_api.AllGather && g_api.GetErrorString && g_api.GetVersion;
 }
 }  // namespace

@@ -19,7 +19,12 @@ struct NcclApi {
     int (*AllGather)(const void* send, void* recv, size_t sendcount, int dtype, void* comm, cudaStream_t st);
     const char* (*GetErrorString)(int);
     int (*GetVersion)(int*);
+    // Optional (null when the library has none): the communicator's asynchronous error state, and the abort that ends
+    // its kernels in flight.
+    int (*CommGetAsyncError)(void* comm, int* async_error);
+    int (*CommAbort)(void* comm);
 };
+constexpr int NCCL_IN_PROGRESS = 7;
 constexpr int NCCL_FLOAT32 = 7;
 
 // nullptr when no NCCL library could be loaded (why: nccl_dl_error()).  The library named by AVA_NCCL_LIB is tried

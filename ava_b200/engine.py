@@ -96,6 +96,7 @@ def lib() -> C.CDLL:
         "ava_nccl_comm_init": ([vp, C.c_int32, C.c_int32, C.c_char_p, C.POINTER(vp)], C.c_int),
         "ava_nccl_comm_destroy": ([vp], C.c_int),
         "ava_nccl_version": ([C.POINTER(C.c_int32)], C.c_int),
+        "ava_split_wait": ([vp, vp, C.c_int32], C.c_int),
         "ava_engine_set_chunked_memory": ([vp, C.c_int32], C.c_int),
         "ava_engine_chunked_memory_counts": ([vp, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64)], C.c_int),
         "ava_step_trace": ([vp, vp, C.c_uint32, fp, C.POINTER(vp)], C.c_int),
@@ -171,7 +172,7 @@ EXPORTS = ("ava_engine_create ava_engine_destroy ava_last_error ava_engine_set_f
            "ava_state_rows ava_state_select ava_state_cat ava_state_seen ava_state_len ava_state_export "
            "ava_state_import ava_step ava_step_greedy ava_forward_with_state ava_step_device ava_prefill_device ava_state_set_kv_shard ava_shard_parts ava_split_step_begin ava_shard_partial ava_split_step_end ava_sync "
            "ava_engine_stream ava_engine_launches ava_engine_bytes ava_state_bytes ava_debug_keep ava_debug_width "
-           "ava_debug_get ava_engine_set_segmented_read ava_engine_set_fast_products ava_engine_set_lanes ava_state_set_commit_at_end ava_split_step ava_nccl_unique_id ava_nccl_comm_init ava_nccl_comm_destroy ava_nccl_version ava_engine_set_chunked_memory ava_engine_chunked_memory_counts ava_prof_enable ava_prof_read ava_prof_names ava_engine_fingerprint ava_state_engine ava_state_set_seen ava_state_save ava_state_load ava_ckpt_read_u32 ava_conv_path ava_conv_save ava_conv_load ava_step_sample ava_generate_sampled ava_op_sample ava_engine_device ava_engine_config ava_splitmix64_next ava_pick ava_generate ava_loader_error ava_ckpt_open ava_ckpt_close ava_ckpt_count ava_ckpt_find ava_ckpt_tensor ava_ckpt_read_f32 ava_arch_flags ava_config_from_ckpt ava_engine_load_ckpt ava_op_q8_matmul ava_op_q8_event_matmul ava_op_q8_tc_matmul ava_debug_mem_heads_wait_runs_out ava_op_tc_bgemm ava_op_q8_spike_tc_matmul ava_op_engram_chunk ava_op_mem_chunk ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
+           "ava_debug_get ava_engine_set_segmented_read ava_engine_set_fast_products ava_engine_set_lanes ava_state_set_commit_at_end ava_split_step ava_nccl_unique_id ava_nccl_comm_init ava_nccl_comm_destroy ava_nccl_version ava_split_wait ava_engine_set_chunked_memory ava_engine_chunked_memory_counts ava_prof_enable ava_prof_read ava_prof_names ava_engine_fingerprint ava_state_engine ava_state_set_seen ava_state_save ava_state_load ava_ckpt_read_u32 ava_conv_path ava_conv_save ava_conv_load ava_step_sample ava_generate_sampled ava_op_sample ava_engine_device ava_engine_config ava_splitmix64_next ava_pick ava_generate ava_loader_error ava_ckpt_open ava_ckpt_close ava_ckpt_count ava_ckpt_find ava_ckpt_tensor ava_ckpt_read_f32 ava_arch_flags ava_config_from_ckpt ava_engine_load_ckpt ava_op_q8_matmul ava_op_q8_event_matmul ava_op_q8_tc_matmul ava_debug_mem_heads_wait_runs_out ava_op_tc_bgemm ava_op_q8_spike_tc_matmul ava_op_engram_chunk ava_op_mem_chunk ava_op_rmsnorm ava_op_lif ava_op_kwta ava_op_mem_heads ava_mem_heads_static ava_static_last_error ava_op_attend "
            "ava_host_expf ava_host_logf ava_host_rsqrtf ava_host_sinf ava_host_cosf ava_op_math ava_step_trace ava_trace_get ava_trace_free").split()
 
 

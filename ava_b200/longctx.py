@@ -91,6 +91,15 @@ class SplitKV:
         self.m._check(engine.lib().ava_split_step(self.m.h, self.state.h, comm, self.rank, self.world, tok_ptr, self.qkv.data_ptr(),
                                                   self.partial.data_ptr(), self.gathered.data_ptr(), logits_ptr, next_ptr))
 
+    def wait(self, timeout_ms: int = 10000):
+        """Bounded host wait for the token (ava_split_wait).  On a NCCL error or when the time runs out the library has
+        aborted the communicator: it is dropped here, and the error is raised."""
+        comm = getattr(self, "comm", None)
+        rc = engine.lib().ava_split_wait(self.m.h, comm, timeout_ms)
+        if rc != 0:
+            self.comm = None
+        self.m._check(rc)
+
     def step(self, tok_ptr: int | None, logits_ptr=None, next_ptr=None):
         """One token with torch.distributed doing the exchange on the engine's stream."""
         torch, dist = self.torch, self.dist

@@ -104,6 +104,7 @@ extern "C" {
     pub fn ava_nccl_comm_init(e: *mut AvaEngine, world: i32, rank: i32, id128: *const u8, comm: *mut *mut c_void) -> c_int;
     pub fn ava_nccl_comm_destroy(comm: *mut c_void) -> c_int;
     pub fn ava_nccl_version(version: *mut i32) -> c_int;
+    pub fn ava_split_wait(e: *mut AvaEngine, nccl_comm: *mut c_void, timeout_ms: i32) -> c_int;
     pub fn ava_step_trace(e: *mut AvaEngine, s: *mut AvaState, tok: u32, logits: *mut f32, out: *mut *mut AvaTrace) -> c_int;
     pub fn ava_trace_get(t: *const AvaTrace, name: *const c_char, block: i32, out: *mut f32, cap: i64) -> i64;
     pub fn ava_trace_free(t: *mut AvaTrace);

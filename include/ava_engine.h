@@ -256,6 +256,15 @@ int ava_nccl_comm_init(ava_engine* e, int32_t world, int32_t rank, const unsigne
 int ava_nccl_comm_destroy(void* comm);
 int ava_nccl_version(int32_t* version);
 
+/* A bounded host wait for what is queued on the engine's stream (the split step's collectives among it): returns AVA_OK
+ * once the stream has drained.  While it waits it asks NCCL for the communicator's asynchronous error
+ * (ncclCommGetAsyncError); on an error, or when timeout_ms have passed (a rank that never joined its collective), it
+ * aborts the communicator (ncclCommAbort, which ends the collective's kernel in flight), drains the stream and returns
+ * AVA_ERR_CUDA with the reason in ava_last_error: the communicator must not be used or destroyed afterwards, the engine
+ * and the state stay usable.  nccl_comm NULL: the same wait without the NCCL queries.  The reference has no
+ * counterpart (its sequence never leaves one device). */
+int ava_split_wait(ava_engine* e, void* nccl_comm, int32_t timeout_ms);
+
 /* One traced token of a one-row state: `Model::step_trace` (src/model.rs, record built in src/model/fstep/arch.rs:420-476,
  * the chat app's event feed).  The step is the plain one (same logits, same state); the record holds copies of what it
  * computed and sizes taken from those copies on the host.  ava_trace_get(name, block): per block "spikes" [d] as they reach

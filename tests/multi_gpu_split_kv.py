@@ -93,6 +93,8 @@ def main():
             model.sync()
             out.append(logits.cpu().numpy().copy())
     ev1.record(sk.stream)
+    if not args.torch_exchange:
+        sk.wait(60000)
     model.sync()
     torch.cuda.synchronize()
     ms = ev0.elapsed_time(ev1)

@@ -81,7 +81,8 @@ def test_split_store_decode_matches_the_oracle(orc, world, parts):
 def test_split_step_as_one_call_with_its_own_communicator():
     """ava_split_step on one rank: NCCL loaded by the library (dlopen), a communicator of one rank made through the C
     ABI, the token stepped as one call; the logits are the bits of the three-call form on a twin state (with one rank
-    the all-gather is a copy either way), and the communicator's broadcast and all-gather ran on the engine's stream."""
+    the all-gather is a copy either way), and the communicator's broadcast and all-gather ran on the engine's stream.  Each token is
+    waited for with ava_split_wait (the bounded wait that asks NCCL for its asynchronous error)."""
     import ctypes as C
     import torch
     build.build()
@@ -112,6 +113,9 @@ def test_split_step_as_one_call_with_its_own_communicator():
                 sk.gathered.copy_(sk.partial.unsqueeze(0))
                 torch.cuda.synchronize()
                 sk.end(logits.data_ptr(), None)
+            if one_call:
+                sk.wait(20000)  # the bounded wait: stream drained, no asynchronous NCCL error, communicator kept
+                assert sk.comm is not None
             sk.m.sync()
             got.append(logits.cpu().numpy().copy())
         if one_call:
