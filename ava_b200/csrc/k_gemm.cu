@@ -454,6 +454,96 @@ bool launch_resident(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {
     return true;
 }
 
+// ------------------------------------------------------------------------------------------- a few rows (one sequence)
+// With one sequence (or a handful) a product is a chain of K dependent multiply-adds per output and nothing else, so the
+// kernel is laid out for latency: a block owns 32 output columns, all its threads request the [K][32] strip of weights
+// at once (the weights do not depend on the kernel before, so they are requested BEFORE the wait for it), and then one
+// warp per row walks k with one column per lane: one shared-memory byte, one conversion, one multiply-add per step.
+constexpr int GV_COLS = 32, GV_THREADS = 256, GV_ROWS = GV_THREADS / 32;
+
+__device__ __forceinline__ float lds_s8(const int8_t* p) {
+    int w;
+    asm volatile("ld.shared.s8 %0, [%1];" : "=r"(w) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+    return (float)w;
+}
+__device__ __forceinline__ float4 lds_f4(const float* p) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+    return v;
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(GV_THREADS) q8_gemv_kernel(const GemmArgs g) {
+    extern __shared__ __align__(16) unsigned char gv_smem[];
+    int8_t* wt = reinterpret_cast<int8_t*>(gv_smem);                          // [K][32]
+    float* xs = reinterpret_cast<float*>(gv_smem + (size_t)g.K * GV_COLS);    // [rows][K]
+    const int tid = threadIdx.x;
+    const int n0 = blockIdx.x * GV_COLS, m0 = blockIdx.y * GV_ROWS;
+    const int rows = min(GV_ROWS, g.M - m0);
+    for (int i = tid; i < g.K * 2; i += GV_THREADS) {
+        const int k = i >> 1, q = i & 1;
+        if (n0 + q * 16 < g.N)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(wt + (size_t)k * GV_COLS + q * 16)),
+                         "l"(g.W + (size_t)k * g.ldw + n0 + q * 16)
+                         : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    pdl_enter();
+    for (int i = tid; i < rows * (g.K / 4); i += GV_THREADS) {
+        const int r = i / (g.K / 4), k4 = i - r * (g.K / 4);
+        reinterpret_cast<float4*>(xs + (size_t)r * g.K)[k4] = *reinterpret_cast<const float4*>(g.A + (size_t)(m0 + r) * g.lda + 4 * k4);
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    const int cl = tid & 31, rl = tid >> 5, c = n0 + cl;
+    if (c >= g.N || rl >= rows) return;
+    const float* x = xs + (size_t)rl * g.K;
+    const int8_t* wp = wt + cl;
+    float acc = 0.f;
+    // four k at a time, the next four on their way
+    float4 xv = lds_f4(x);
+    float w0 = lds_s8(wp), w1 = lds_s8(wp + GV_COLS), w2 = lds_s8(wp + 2 * GV_COLS), w3 = lds_s8(wp + 3 * GV_COLS);
+    for (int k = 0; k < g.K; k += 4) {
+        const int kn = k + 4 < g.K ? k + 4 : k;
+        const float4 nx = lds_f4(x + kn);
+        const int8_t* wn = wp + (size_t)kn * GV_COLS;
+        const float n0w = lds_s8(wn), n1w = lds_s8(wn + GV_COLS), n2w = lds_s8(wn + 2 * GV_COLS), n3w = lds_s8(wn + 3 * GV_COLS);
+        acc = fma(xv.x, w0, acc);
+        acc = fma(xv.y, w1, acc);
+        acc = fma(xv.z, w2, acc);
+        acc = fma(xv.w, w3, acc);
+        xv = nx; w0 = n0w; w1 = n1w; w2 = n2w; w3 = n3w;
+    }
+    const int r = m0 + rl;
+    float o = mul(acc, g.scale[c]);
+    if (EPI == EPI_ADD && g.lif.ne) o = mul(o, g.lif.ne[(size_t)r * NM_STRIDE]);
+    if (EPI == EPI_LIF) {
+        lif_update(g.lif, r, c, g.N, o);
+    } else {
+        float* dst = g.C + (size_t)r * g.ldc + c;
+        if (EPI == EPI_ADD) o = add(*dst, o);
+        *dst = o;
+    }
+}
+
+// false: shape not covered (the strip and the rows must fit shared memory; N a multiple of 16; 16-byte aligned rows)
+bool launch_gemv(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {
+    const int rows = a.M < GV_ROWS ? a.M : GV_ROWS;
+    const size_t smem = (size_t)a.K * GV_COLS + (size_t)rows * a.K * sizeof(float);
+    if (smem > 200 * 1024 || a.N % 16 || a.K % 4 || a.ldw % 16 || a.lda % 4 || (reinterpret_cast<uintptr_t>(a.W) & 15) || (reinterpret_cast<uintptr_t>(a.A) & 15)) return false;
+    dim3 grid((a.N + GV_COLS - 1) / GV_COLS, (a.M + GV_ROWS - 1) / GV_ROWS);
+    auto go = [&](auto kernel) {
+        if (smem > 32 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch_k(kernel, grid, dim3(GV_THREADS), smem, st, a);
+    };
+    switch (epi) {
+        case EPI_STORE: go(q8_gemv_kernel<EPI_STORE>); break;
+        case EPI_ADD: go(q8_gemv_kernel<EPI_ADD>); break;
+        case EPI_LIF: go(q8_gemv_kernel<EPI_LIF>); break;
+    }
+    return true;
+}
+
 // ---------------------------------------------------------------------------------------------------- event sums
 // A mostly-zero row (the LIF spikes, the k-WTA'd MLP units) sums over its non-zero inputs only, in increasing order:
 // fma(0, q, acc) = acc exactly, so this is the dense sum bit for bit (src/int8.rs:10-13; -0 counts as zero, NaN does
@@ -556,6 +646,81 @@ __global__ void __launch_bounds__(EV_THREADS) q8_event_kernel(const GemmArgs g) 
     *dst = make_float4(o[0], o[1], o[2], o[3]);
 }
 
+// The event sum for a few rows: one block per (row, 32 output columns).  The block lists the row's non-zero inputs in
+// order (eight warps, a contiguous part of the row each), requests the listed weight rows' 32 bytes all at once into
+// shared memory (one latency for the whole list instead of one per 32 events), and one warp then walks the list with a
+// column per lane.
+constexpr int EVS_COLS = 32, EVS_THREADS = 256;
+
+template <int EPI, bool GAIN>
+__global__ void __launch_bounds__(EVS_THREADS) q8_event_small_kernel(const GemmArgs g) {
+    pdl_enter();
+    extern __shared__ __align__(16) unsigned char evs_smem[];
+    int8_t* wt = reinterpret_cast<int8_t*>(evs_smem);                                   // [K][32], the first nnz rows used
+    float* vals = reinterpret_cast<float*>(evs_smem + (size_t)g.K * EVS_COLS);          // [K]
+    unsigned short* idx = reinterpret_cast<unsigned short*>(vals + g.K);                // [K]
+    constexpr int NW = EVS_THREADS / 32;
+    __shared__ int warp_off[NW + 1];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int r = blockIdx.y, n0 = blockIdx.x * EVS_COLS;
+    const float* xr = g.A + (size_t)r * g.lda;
+    const int part = ((g.K + NW * 32 - 1) / (NW * 32)) * 32;  // inputs per warp, a multiple of 32
+    const int j0 = min(g.K, warp * part), j1 = min(g.K, j0 + part);
+    int cnt = 0;
+    for (int j = j0 + lane; j < j1; j += 32) cnt += xr[j] != 0.0f;
+    for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+    if (lane == 0) warp_off[warp + 1] = cnt;
+    __syncthreads();
+    if (tid == 0) {
+        warp_off[0] = 0;
+        for (int w = 1; w <= NW; ++w) warp_off[w] += warp_off[w - 1];
+    }
+    __syncthreads();
+    int at = warp_off[warp];
+    for (int j = j0; j < j1; j += 32) {
+        const float v = (j + lane < j1) ? xr[j + lane] : 0.0f;
+        const unsigned m = __ballot_sync(0xffffffffu, v != 0.0f);
+        if (v != 0.0f) {
+            const int pos = at + __popc(m & ((1u << lane) - 1u));
+            vals[pos] = v;
+            idx[pos] = (unsigned short)(j + lane);
+        }
+        at += __popc(m);
+    }
+    __syncthreads();
+    const int nnz = warp_off[NW];
+    for (int i = tid; i < nnz * 2; i += EVS_THREADS) {
+        const int ev = i >> 1, q = i & 1;
+        if (n0 + q * 16 < g.N)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(wt + (size_t)ev * EVS_COLS + q * 16)),
+                         "l"(g.W + (size_t)idx[ev] * g.ldw + n0 + q * 16)
+                         : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    const int c = n0 + lane;
+    if (warp != 0 || c >= g.N) return;
+    const int8_t* wp = wt + lane;
+    float acc = 0.f;
+    int i = 0;
+    for (; i + 4 <= nnz; i += 4) {
+        const float4 xv = lds_f4(vals + i);
+        const float w0 = lds_s8(wp + (size_t)i * EVS_COLS), w1 = lds_s8(wp + (size_t)(i + 1) * EVS_COLS);
+        const float w2 = lds_s8(wp + (size_t)(i + 2) * EVS_COLS), w3 = lds_s8(wp + (size_t)(i + 3) * EVS_COLS);
+        acc = fma(xv.x, w0, acc);
+        acc = fma(xv.y, w1, acc);
+        acc = fma(xv.z, w2, acc);
+        acc = fma(xv.w, w3, acc);
+    }
+    for (; i < nnz; ++i) acc = fma(vals[i], lds_s8(wp + (size_t)i * EVS_COLS), acc);
+    float o = mul(acc, g.scale[c]);
+    if (GAIN) o = mul(o, g.lif.ne[(size_t)r * NM_STRIDE]);
+    float* dst = g.C + (size_t)r * g.ldc + c;
+    if (EPI == EPI_ADD) o = add(*dst, o);
+    *dst = o;
+}
+
 template <int BM, int BN, int TM, int TN>
 void launch_tile(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {
     dim3 grid((a.N + BN - 1) / BN, (a.M + BM - 1) / BM);
@@ -612,6 +777,7 @@ __global__ void lif_kernel(const float* cur, const LifParams p, int M, int d) {
 }  // namespace
 
 int g_gemm_force = 0;  // tuning override (0: choose by shape)
+int g_gemv_max_rows = 8;       // up to this many rows the one-column-per-lane kernel takes the dense products
 int g_resident_max_rows = 16;  // up to this many rows the resident-tile kernel takes the dense products (measured: 19-21 us
                                 // against 23 us for the tiled kernel at 1-8 rows, slower from 32 rows on)
 thread_local cudaError_t g_launch_error = cudaSuccess;
@@ -643,6 +809,8 @@ void launch_q8_gemm(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int sm
             break;
         default: break;
     }
+    // one sequence or a handful: a column per lane, the weights' strip requested before the wait for the kernel before
+    if (g_gemm_force == 0 && a.M <= g_gemv_max_rows && launch_gemv(st, a, epi)) return;
     // a few rows: the whole-K tile in shared memory, one latency instead of one per k-tile
     if (g_gemm_force == 0 && a.M <= g_resident_max_rows && launch_resident(st, a, epi)) return;
     // Measured on B200 at 256 rows (the machine is short of warps at this batch, so the choice is about filling SMs):
@@ -662,6 +830,21 @@ bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {
     if (a.K > 65535 || epi == EPI_LIF) return false;
     const size_t smem = (size_t)a.K * (sizeof(float) + sizeof(unsigned short));
     if (smem > 200 * 1024) return false;
+    const size_t smem_small = smem + (size_t)a.K * EVS_COLS;
+    if (a.M <= g_gemv_max_rows && smem_small <= 200 * 1024 && a.N % 16 == 0 && a.ldw % 16 == 0 && a.K % 4 == 0 && !(reinterpret_cast<uintptr_t>(a.W) & 15)) {
+        dim3 grid((a.N + EVS_COLS - 1) / EVS_COLS, a.M);
+        auto go = [&](auto kernel) {
+            if (smem_small > 32 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_small);
+            launch_k(kernel, dim3(grid), dim3(EVS_THREADS), smem_small, st, a);
+        };
+        if (epi == EPI_ADD && a.lif.ne)
+            go(q8_event_small_kernel<EPI_ADD, true>);
+        else if (epi == EPI_ADD)
+            go(q8_event_small_kernel<EPI_ADD, false>);
+        else
+            go(q8_event_small_kernel<EPI_STORE, false>);
+        return true;
+    }
     const int gy = std::min(a.M, 32768);
     dim3 grid((a.N + EV_COLS - 1) / EV_COLS, gy, (a.M + gy - 1) / gy);
     auto go = [&](auto kernel) {

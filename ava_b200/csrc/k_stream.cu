@@ -129,6 +129,83 @@ __global__ void __launch_bounds__(256) mem_stream_kernel(const MemStreamArgs a) 
     *reinterpret_cast<float4*>(a.rr_out + vo + c) = rr;
 }
 
+// The same pass for a FEW sequences (one talking, or a handful): the streaming kernel above keeps a lane's rows in
+// registers, which needs thousands of warps to keep HBM busy; with one sequence it has a few warps and a lane waits a
+// memory latency per 32 rows of its 768.  Here a block owns a strip of eight columns of one head: all its threads bring
+// the strip [hs][8] into shared memory at once (one latency), all of them apply the pending update element by element
+// (the same three roundings) and write the state back, and then sixteen lanes run the sixteen ordered column sums
+// (eight columns times rr and t1) over the rows from shared memory, one multiply-add per row each.  Same operations
+// per element in the same order, so the same bits.
+constexpr int MS_COLS = 8, MS_THREADS = 256;
+
+template <bool PEND, bool ALT>
+__global__ void __launch_bounds__(MS_THREADS) mem_stream_small_kernel(const MemStreamArgs a) {
+    pdl_enter();
+    extern __shared__ __align__(16) float ss[];
+    const int hs = a.hs, cw = a.cw;
+    float* fs = ss;                       // [hs][8]
+    float* ve = fs + (size_t)hs * MS_COLS;
+    float* vqg = ve + hs;
+    float* vpx = vqg + hs;
+    float* vpw = vpx + (PEND ? hs : 0);
+    float* vpa = vpw + (PEND ? hs : 0);
+    const int strips = hs / MS_COLS, strip = blockIdx.x % strips;
+    const int head = (blockIdx.x / strips) % a.nh, m = blockIdx.x / (strips * a.nh);
+    const size_t vo = ((size_t)m * a.nh + head) * hs;
+    const int c = strip * MS_COLS;
+    const size_t fo = vo * hs + (size_t)(c / cw) * hs * cw + (c % cw);   // slice-major: row r of the strip at fo + r * cw
+    const float* fp = a.f + fo;
+    float* fq = ALT ? a.f_out + fo : a.f + fo;
+    const int tid = threadIdx.x;
+    for (int i = tid; i < hs * 2; i += MS_THREADS) {
+        const int r = i >> 1, q = i & 1;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(fs + (size_t)r * MS_COLS + q * 4)),
+                     "l"(fp + (size_t)r * cw + q * 4)
+                     : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    for (int i = tid * 4; i < hs; i += MS_THREADS * 4) {
+        *reinterpret_cast<float4*>(ve + i) = *reinterpret_cast<const float4*>(a.e + vo + i);
+        *reinterpret_cast<float4*>(vqg + i) = *reinterpret_cast<const float4*>(a.qg + vo + i);
+        if (PEND) {
+            *reinterpret_cast<float4*>(vpx + i) = *reinterpret_cast<const float4*>(a.px + vo + i);
+            *reinterpret_cast<float4*>(vpw + i) = *reinterpret_cast<const float4*>(a.pw + vo + i);
+            *reinterpret_cast<float4*>(vpa + i) = *reinterpret_cast<const float4*>(a.pah + vo + i);
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    if (PEND) {
+        // every thread the same half row (four columns) of every 128th row: its value and rr columns stay in registers
+        const int q = tid & 1;
+        const float4 pv = *reinterpret_cast<const float4*>(a.pv + vo + c + q * 4), prr = *reinterpret_cast<const float4*>(a.prr + vo + c + q * 4);
+        for (int r = tid >> 1; r < hs; r += MS_THREADS / 2) {
+            float4* sp = reinterpret_cast<float4*>(fs + (size_t)r * MS_COLS + q * 4);
+            const float4 f = pending_update(*sp, vpx[r], vpw[r], vpa[r], pv, prr);
+            *sp = f;
+            stg_stream(fq + (size_t)r * cw + q * 4, f);
+        }
+        __syncthreads();
+    }
+    if (tid >= 2 * MS_COLS) return;
+    // lane j < 8: rr of column j (the rows times e); lane 8 + j: t1 of column j (the rows times q alpha)
+    const int j = tid & (MS_COLS - 1);
+    const float* vec = tid < MS_COLS ? ve : vqg;
+    // the chains start from -0: fma(f, e, -0) is the rounded product with its own sign, i.e. row 0's plain product
+    float sum = -0.0f;
+    const float* col = fs + j;
+#pragma unroll 8
+    for (int r = 0; r < hs; ++r) sum = fma(col[(size_t)r * MS_COLS], vec[r], sum);
+    const float t1 = __shfl_down_sync(0x0000ffffu, sum, MS_COLS, 16);
+    if (tid >= MS_COLS) return;
+    const float v = a.v[vo + c + j];
+    const float qw = a.qw[(size_t)m * a.nh + head], qa = a.qa[(size_t)m * a.nh + head];
+    // the recall's term from inside the one-token chunk is an exact zero (arch.rs:277-280): kept for the sign of zero
+    const float rr = add(sum, mul(1.0f, mul(0.0f, v)));
+    a.y[vo + c + j] = sub(add(t1, mul(qw, v)), mul(qa, rr));
+    a.rr_out[vo + c + j] = rr;
+}
+
 // The pending update alone: f = (f * alpha[row] + w[row] v[col]) - ah[row] rr[col] over the whole slice-major state of
 // one block of the model.  One thread per four neighbouring columns of a row.
 __global__ void mem_flush_kernel(float* f, const float* __restrict__ px, const float* __restrict__ pw, const float* __restrict__ pah,
@@ -147,9 +224,26 @@ __global__ void mem_flush_kernel(float* f, const float* __restrict__ px, const f
 
 }  // namespace
 
+long g_mem_stream_small_max = 8 * 768;  // up to this many (sequence, head, row) triples the strip kernel takes the pass
+
 // false: head size not covered (a multiple of 16; the head's five vectors must fit shared memory)
 bool launch_mem_stream(cudaStream_t st, const MemStreamArgs& a) {
     const bool pend = a.px != nullptr;
+    // a few sequences: strips of eight columns staged in shared memory (the register-streaming kernel would have a handful of warps)
+    if ((long)a.M * a.nh * a.hs <= g_mem_stream_small_max && a.hs % 16 == 0 && a.cw % MS_COLS == 0) {
+        const size_t sm = (size_t)(MS_COLS + (pend ? 5 : 2)) * a.hs * sizeof(float);
+        if (sm <= 200 * 1024) {
+            const unsigned grid = (unsigned)((size_t)a.M * a.nh * (a.hs / MS_COLS));
+            auto go = [&](auto kernel) {
+                if (sm > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+                launch_k(kernel, dim3(grid), dim3(MS_THREADS), sm, st, a);
+            };
+            if (!pend) go(mem_stream_small_kernel<false, false>);
+            else if (a.f_out) go(mem_stream_small_kernel<true, true>);
+            else go(mem_stream_small_kernel<true, false>);
+            return true;
+        }
+    }
     const size_t smem = (size_t)(pend ? 5 : 2) * a.hs * sizeof(float);
     const int wpb = 2;  // warps per block: small blocks, so that every warp of the launch is resident from the start
     const int warps_head = (a.hs + 127) / 128, warps = std::min(wpb, warps_head);

@@ -45,7 +45,7 @@ def test_device_math_equals_host_math():
     assert np.array_equal(bits(got[:3000]), bits(want))
 
 
-@pytest.mark.parametrize("m,din,dout", [(1, 128, 64), (5, 768, 768), (70, 768, 3840), (256, 3072, 768), (33, 128, 320), (256, 768, 4112)])
+@pytest.mark.parametrize("m,din,dout", [(1, 128, 64), (5, 768, 768), (1, 768, 3072), (8, 3072, 784), (3, 192, 48), (70, 768, 3840), (256, 3072, 768), (33, 128, 320), (256, 768, 4112)])
 def test_q8_matmul_bits(orc, m, din, dout):
     rng = np.random.default_rng(m * 7 + dout)
     q = rng.integers(-127, 128, (din, dout)).astype(np.int8)
@@ -96,10 +96,11 @@ def test_tensor_core_product_agrees_to_rounding(orc, m, din, dout):
 
 @pytest.mark.parametrize("density", [0.0, 0.02, 0.25, 0.6, 1.0])
 @pytest.mark.parametrize("din,dout", [(768, 768), (3072, 768), (128, 320)])
-def test_event_sum_bits(orc, density, din, dout):
-    """The event-sum kernel (non-zero inputs only, in order) gives the dense sum's bits at any density."""
+@pytest.mark.parametrize("m", [9, 3])
+def test_event_sum_bits(orc, density, din, dout, m):
+    """The event-sum kernel (non-zero inputs only, in order) gives the dense sum's bits at any density; nine rows take
+    the kernel for batches, three the one for a few sequences."""
     rng = np.random.default_rng(int(density * 100) + din)
-    m = 9
     q = rng.integers(-127, 128, (din, dout)).astype(np.int8)
     sc = (rng.uniform(0.5, 1.5, dout) / 127).astype(np.float32)
     x = np.zeros((m, din), np.float32)

@@ -407,7 +407,7 @@ def test_scaled_block_bits(orc_same_math):
         orc.set_threads(1)
 
 
-@pytest.mark.parametrize("rows", [1, 40])
+@pytest.mark.parametrize("rows", [1, 6, 40])
 def test_benchmark_shape_bits(orc_same_math, rows):
     """The Ava-0.4-shaped benchmark model itself (12 blocks, d 768, one 768x768 fast-synapse matrix per block, engram of
     12 x 64 in bf16), a few tokens, every bit."""
