@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libava_engine.so")
 SOURCES = ["engine.cu", "ops.cu", "k_gemm.cu", "k_gemm2.cu", "k_stream.cu", "k_rows.cu", "k_delta.cu", "k_engram.cu", "k_tc.cu", "k_tcb.cu", "k_chunk.cu", "k_eattn.cu", "k_sample.cu", "k_parts.cu", "k_cb.cu", "static_entry.cu", "nccl_dl.cpp", "loader.cpp", "generate.cpp", "state_io.cpp", "trace.cpp"]
-HEADERS = ["ava_math.h", "kernels.cuh", os.path.join("..", "..", "include", "ava_engine.h")]
+HEADERS = sorted(f for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))) + [os.path.join("..", "..", "include", "ava_engine.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-fmad=false",
               "-Xcompiler", "-fPIC,-ffp-contract=off,-O2", "-ccbin", "g++"]
 

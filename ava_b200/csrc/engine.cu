@@ -479,7 +479,7 @@ uint16_t* limbs_for(ava_engine* e, const float* dst, int M, int K) {
 }
 
 int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w, float* C, int ldc, int M, GemmEpilogue epi, const LifParams* lif = nullptr, bool sparse = false,
-         const float* row_gain = nullptr, bool int_rows = false) {
+         const float* row_gain = nullptr, bool int_rows = false, const GemvPro* pro = nullptr) {
     GemmArgs g{};
     g.A = A;
     g.lda = lda;
@@ -493,6 +493,16 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
     g.K = w.din;
     if (lif) g.lif = *lif;
     if (epi == EPI_ADD) g.lif.ne = row_gain;  // [rows][NM_STRIDE]
+    if (pro && pro->kind != PRO_NONE) {
+        // a few rows, the input's norm taken inside the product: AVA_NOT_APPLICABLE (nothing queued) sends the caller
+        // to the norm's own kernel and the plain product
+        if (e->fast || sparse || M > gemv_max_rows()) return AVA_NOT_APPLICABLE;
+        prof_begin(e, cls);
+        const bool queued = launch_q8_gemv_pro(e->cur, g, epi, *pro);
+        prof_end(e);
+        if (!queued) e->launches--;
+        return queued ? AVA_OK : AVA_NOT_APPLICABLE;
+    }
     // Rows of small integers (spikes) times int8 weights on the tensor cores, one bf16 limb each side: every product and
     // partial sum is an integer below 2^24, so the f32 accumulator is exact in any order and the result is the event
     // sum's bits.  Taken for a prompt chunk when the bf16 copy of the weights exists (fast products on).
@@ -637,9 +647,14 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
         const float* th_mem = c.thalamus ? w.th_g.as<float>() + 1 : nullptr;
         if (!(phase == PHASE_END && i == c.eng_block)) {
         // ---- the spiking memory
+        // one sequence or a handful: the norm is taken inside the product that reads it (one kernel fewer per norm)
+        const bool few = T == 1 && !e->fast && !e->keep && M <= gemv_max_rows();
+        bool h_lif_fused = few && !(c.mood > 0 && i > 0);
+        if (!h_lif_fused) {
         prof_begin(e, "rmsnorm");
         launch_rmsnorm(st, x, b.mem_norm.as<float>(), M, d, h, limbs_for(e, h, M, d));
         prof_end(e);
+        }
         dbg(e, "h_lif", i, h, M, d);
         LifParams lp{};
         lp.beta = b.beta.as<float>();
@@ -662,7 +677,19 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
             prof_end(e);
             cur_gain = w.mood_gain.as<float>();
         }
-        if (T == 1 && !cur_gain) {
+        if (h_lif_fused) {
+            GemvPro pn;
+            pn.kind = PRO_RMS;
+            pn.gain = b.mem_norm.as<float>();
+            if (gemm(e, "gemm.win_lif", x, d, b.win, nullptr, 0, M, EPI_LIF, &lp, false, nullptr, false, &pn) != AVA_OK) {
+                h_lif_fused = false;
+                prof_begin(e, "rmsnorm");
+                launch_rmsnorm(st, x, b.mem_norm.as<float>(), M, d, h, nullptr);
+                prof_end(e);
+            }
+        }
+        if (h_lif_fused) {
+        } else if (T == 1 && !cur_gain) {
             gemm(e, "gemm.win_lif", h, d, b.win, nullptr, 0, M, EPI_LIF, &lp);
         } else {
             // currents of the whole chunk, then the scan in time (buffers free at this point of the block are borrowed)
@@ -861,12 +888,24 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
         }
         prof_end(e);
         dbg(e, "y_raw", i, mh.y, M, d);
+        bool post_fused = false;
+        if (few && !c.dendrite && !c.rhythm) {
+            GemvPro pp;
+            pp.kind = PRO_POST;
+            pp.gate = c.out_gate ? w.proj.as<float>() + 4 * d : nullptr;
+            pp.ldg = pw;
+            pp.hs = hs;
+            post_fused = gemm(e, "gemm.wo", mh.y, d, b.wo, x, d, M, EPI_ADD, nullptr, false, th_mem, false, &pp) == AVA_OK;
+        }
+        if (!post_fused) {
         prof_begin(e, "mem_post");
         launch_mem_post(st, mh.y, c.out_gate ? w.proj.as<float>() + 4 * d : nullptr, pw, M, d, hs, w.y.as<float>(), limbs_for(e, w.y.as<float>(), M, d),
                         c.rhythm ? w.rh_gr.as<float>() : nullptr);
         prof_end(e);
+        }
         dbg(e, "y", i, w.y.as<float>(), M, d);
-        if (c.dendrite) {
+        if (post_fused) {
+        } else if (c.dendrite) {
             // P: the read after W_o is kept, the context of this block's dendrites
             gemm(e, "gemm.wo", w.y.as<float>(), d, b.wo, w.ctx.as<float>(), d, M, EPI_STORE);
             prof_begin(e, "add");
@@ -882,10 +921,19 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
         // ---- the engram
         if (i == c.eng_block) {
             if (phase != PHASE_END) {
+                bool eng_fused = false;
+                if (T == 1 && !e->fast && !e->keep && M <= gemv_max_rows()) {
+                    GemvPro pn;
+                    pn.kind = PRO_RMS;
+                    pn.gain = b.eng_norm.as<float>();
+                    eng_fused = gemm(e, "gemm.eng_qkv", x, d, b.eqkv, w.eqkv.as<float>(), 3 * d, M, EPI_STORE, nullptr, false, nullptr, false, &pn) == AVA_OK;
+                }
+                if (!eng_fused) {
                 prof_begin(e, "rmsnorm");
                 launch_rmsnorm(st, x, b.eng_norm.as<float>(), M, d, h, limbs_for(e, h, M, d));
                 prof_end(e);
                 gemm(e, "gemm.eng_qkv", h, d, b.eqkv, w.eqkv.as<float>(), 3 * d, M, EPI_STORE);
+                }
                 dbg(e, "eng_qkv", i, w.eqkv.as<float>(), M, 3 * d);
             }
             if (phase == PHASE_BEGIN) {
@@ -968,10 +1016,19 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
         }
 
         // ---- the sparse MLP
+        bool mlp_fused = false;
+        if (T == 1 && !e->fast && !e->keep && M <= gemv_max_rows()) {
+            GemvPro pn;
+            pn.kind = PRO_RMS;
+            pn.gain = b.mlp_norm.as<float>();
+            mlp_fused = gemm(e, "gemm.w1", x, d, b.w1, w.u.as<float>(), H, M, EPI_STORE, nullptr, false, nullptr, false, &pn) == AVA_OK;
+        }
+        if (!mlp_fused) {
         prof_begin(e, "rmsnorm");
         launch_rmsnorm(st, x, b.mlp_norm.as<float>(), M, d, h, limbs_for(e, h, M, d));
         prof_end(e);
         gemm(e, "gemm.w1", h, d, b.w1, w.u.as<float>(), H, M, EPI_STORE);
+        }
         dbg(e, "u", i, w.u.as<float>(), M, H);
         prof_begin(e, "kwta");
         // a prompt chunk in the tolerance mode multiplies the k-WTA's output densely on the tensor cores: its limbs are made here
@@ -1054,9 +1111,19 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
     if (want_logits || next) {
         // the head reads the last token's rows only, unless every position's logits were asked for
         const int first_row = all_logits ? 0 : (T - 1) * rows, head_rows = all_logits ? M : rows;
+        float* lg = (logits ? logits : e->logits.as<float>()) + (size_t)r0 * c.vocab;
+        bool head_fused = false;
+        if (T == 1 && !e->fast && !e->keep && c.cb_units == 0 && head_rows <= gemv_max_rows()) {
+            GemvPro pn;
+            pn.kind = PRO_RMS;
+            pn.gain = e->final_norm.as<float>();
+            head_fused = gemm(e, "gemm.head", x + (size_t)first_row * d, d, e->head, lg, c.vocab, head_rows, EPI_STORE, nullptr, false, nullptr, false, &pn) == AVA_OK;
+        }
+        if (!head_fused) {
         prof_begin(e, "rmsnorm");
         launch_rmsnorm(st, x + (size_t)first_row * d, e->final_norm.as<float>(), head_rows, d, h, c.cb_units > 0 ? nullptr : limbs_for(e, h, head_rows, d));
         prof_end(e);
+        }
         dbg(e, "x_final", -1, h, head_rows, d);
         if (c.cb_units > 0) {
             // CB: the final normed state plus the read-out of the sparse code of it and the token's embedding
@@ -1071,9 +1138,8 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
             e->launches += 5;
             dbg(e, "x_cb", -1, h, head_rows, d);
         }
-        float* lg = (logits ? logits : e->logits.as<float>()) + (size_t)r0 * c.vocab;
         if (next) next += r0;
-        gemm(e, "gemm.head", h, d, e->head, lg, c.vocab, head_rows, EPI_STORE);
+        if (!head_fused) gemm(e, "gemm.head", h, d, e->head, lg, c.vocab, head_rows, EPI_STORE);
         if (next) {
             prof_begin(e, "argmax");
             launch_argmax(st, lg + (all_logits ? (size_t)(T - 1) * rows * c.vocab : 0), rows, c.vocab, next);

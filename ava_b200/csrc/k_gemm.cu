@@ -11,6 +11,7 @@
 
 #include "ava_math.h"
 #include "kernels.cuh"
+#include "row_sums.cuh"
 
 namespace ava {
 
@@ -461,19 +462,8 @@ bool launch_resident(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {
 // warp per row walks k with one column per lane: one shared-memory byte, one conversion, one multiply-add per step.
 constexpr int GV_COLS = 32, GV_THREADS = 256, GV_ROWS = GV_THREADS / 32;
 
-__device__ __forceinline__ float lds_s8(const int8_t* p) {
-    int w;
-    asm volatile("ld.shared.s8 %0, [%1];" : "=r"(w) : "r"((uint32_t)__cvta_generic_to_shared(p)));
-    return (float)w;
-}
-__device__ __forceinline__ float4 lds_f4(const float* p) {
-    float4 v;
-    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"((uint32_t)__cvta_generic_to_shared(p)));
-    return v;
-}
-
 template <int EPI>
-__global__ void __launch_bounds__(GV_THREADS) q8_gemv_kernel(const GemmArgs g) {
+__global__ void __launch_bounds__(GV_THREADS) q8_gemv_kernel(const GemmArgs g, const GemvPro pro) {
     extern __shared__ __align__(16) unsigned char gv_smem[];
     int8_t* wt = reinterpret_cast<int8_t*>(gv_smem);                          // [K][32]
     float* xs = reinterpret_cast<float*>(gv_smem + (size_t)g.K * GV_COLS);    // [rows][K]
@@ -493,27 +483,55 @@ __global__ void __launch_bounds__(GV_THREADS) q8_gemv_kernel(const GemmArgs g) {
         const int r = i / (g.K / 4), k4 = i - r * (g.K / 4);
         reinterpret_cast<float4*>(xs + (size_t)r * g.K)[k4] = *reinterpret_cast<const float4*>(g.A + (size_t)(m0 + r) * g.lda + 4 * k4);
     }
+    // the prologue's own vectors come in with the rows (one latency for all): the norm's gain [K], or the rows' gates [rows][K]
+    float* aux = xs + (size_t)rows * g.K;
+    if (pro.kind == PRO_RMS) {
+        for (int i = tid; i < g.K / 4; i += GV_THREADS) reinterpret_cast<float4*>(aux)[i] = reinterpret_cast<const float4*>(pro.gain)[i];
+    } else if (pro.kind == PRO_POST && pro.gate) {
+        for (int i = tid; i < rows * (g.K / 4); i += GV_THREADS) {
+            const int r = i / (g.K / 4), k4 = i - r * (g.K / 4);
+            reinterpret_cast<float4*>(aux + (size_t)r * g.K)[k4] = *reinterpret_cast<const float4*>(pro.gate + (size_t)(m0 + r) * pro.ldg + 4 * k4);
+        }
+    }
+    const int cl = tid & 31, rl = tid >> 5, c = n0 + cl;
+    if (pro.kind != PRO_NONE) {
+        // one thread per ordered sum (a row's, or a head's of a row), all of them side by side; then every thread of the
+        // block scales its share of the elements.  The weights are still arriving meanwhile.
+        float* inv_sh = aux + (pro.kind == PRO_RMS ? g.K : (pro.gate ? (size_t)rows * g.K : 0));   // [rows] or [rows][heads]
+        __syncthreads();
+        if (pro.kind == PRO_RMS) {
+            if (cl == 0 && rl < rows) inv_sh[rl] = inv_rms_seq(xs + (size_t)rl * g.K, g.K);
+            __syncthreads();
+            for (int i = tid; i < rows * g.K; i += GV_THREADS) {
+                const int r = i / g.K, col = i - r * g.K;
+                const float v = mul(mul(xs[i], inv_sh[r]), aux[col]);
+                xs[i] = v;
+                if (pro.out && blockIdx.x == 0) pro.out[(size_t)(m0 + r) * g.K + col] = v;
+            }
+        } else {
+            const int nh = g.K / pro.hs;
+            // lane 0 of each warp takes a sum at a time (sums side by side in one warp would meet in one shared-memory bank)
+            for (int p = rl; p < rows * nh; p += GV_THREADS / 32)
+                if (cl == 0) inv_sh[p] = inv_rms_seq(xs + (size_t)p * pro.hs, pro.hs);   // row p / nh, head p % nh
+            __syncthreads();
+            for (int i = tid; i < rows * g.K; i += GV_THREADS) {
+                const int r = i / g.K, col = i - r * g.K;
+                float v = mul(xs[i], inv_sh[i / pro.hs]);
+                if (pro.gate) {
+                    const float gt = aux[i];
+                    v = mul(v, div(gt, add(1.0f, expf_(-gt))));
+                }
+                xs[i] = v;
+                if (pro.out && blockIdx.x == 0) pro.out[(size_t)(m0 + r) * g.K + col] = v;
+            }
+        }
+    }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    const int cl = tid & 31, rl = tid >> 5, c = n0 + cl;
     if (c >= g.N || rl >= rows) return;
     const float* x = xs + (size_t)rl * g.K;
     const int8_t* wp = wt + cl;
-    float acc = 0.f;
-    // four k at a time, the next four on their way
-    float4 xv = lds_f4(x);
-    float w0 = lds_s8(wp), w1 = lds_s8(wp + GV_COLS), w2 = lds_s8(wp + 2 * GV_COLS), w3 = lds_s8(wp + 3 * GV_COLS);
-    for (int k = 0; k < g.K; k += 4) {
-        const int kn = k + 4 < g.K ? k + 4 : k;
-        const float4 nx = lds_f4(x + kn);
-        const int8_t* wn = wp + (size_t)kn * GV_COLS;
-        const float n0w = lds_s8(wn), n1w = lds_s8(wn + GV_COLS), n2w = lds_s8(wn + 2 * GV_COLS), n3w = lds_s8(wn + 3 * GV_COLS);
-        acc = fma(xv.x, w0, acc);
-        acc = fma(xv.y, w1, acc);
-        acc = fma(xv.z, w2, acc);
-        acc = fma(xv.w, w3, acc);
-        xv = nx; w0 = n0w; w1 = n1w; w2 = n2w; w3 = n3w;
-    }
+    const float acc = chain_s8<GV_COLS>(x, wp, g.K, 0.f);
     const int r = m0 + rl;
     float o = mul(acc, g.scale[c]);
     if (EPI == EPI_ADD && g.lif.ne) o = mul(o, g.lif.ne[(size_t)r * NM_STRIDE]);
@@ -527,14 +545,21 @@ __global__ void __launch_bounds__(GV_THREADS) q8_gemv_kernel(const GemmArgs g) {
 }
 
 // false: shape not covered (the strip and the rows must fit shared memory; N a multiple of 16; 16-byte aligned rows)
-bool launch_gemv(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {
+bool launch_gemv(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, const GemvPro& pro = GemvPro()) {
     const int rows = a.M < GV_ROWS ? a.M : GV_ROWS;
-    const size_t smem = (size_t)a.K * GV_COLS + (size_t)rows * a.K * sizeof(float);
+    if (pro.kind == PRO_POST && (pro.hs <= 0 || a.K % pro.hs || pro.hs % 4)) return false;
+    size_t aux = pro.kind == PRO_RMS ? (size_t)a.K * sizeof(float) : (pro.kind == PRO_POST && pro.gate) ? (size_t)rows * a.K * sizeof(float) : 0;
+    if (pro.kind == PRO_RMS) aux += (size_t)rows * sizeof(float);                       // the rows' norms
+    if (pro.kind == PRO_POST) aux += (size_t)rows * (a.K / pro.hs) * sizeof(float);    // the heads' norms
+    aux = (aux + 15) & ~(size_t)15;
+    const size_t smem = (size_t)a.K * GV_COLS + (size_t)rows * a.K * sizeof(float) + aux;
+    if (pro.kind == PRO_RMS && (reinterpret_cast<uintptr_t>(pro.gain) & 15)) return false;
+    if (pro.kind == PRO_POST && pro.gate && ((reinterpret_cast<uintptr_t>(pro.gate) & 15) || pro.ldg % 4)) return false;
     if (smem > 200 * 1024 || a.N % 16 || a.K % 4 || a.ldw % 16 || a.lda % 4 || (reinterpret_cast<uintptr_t>(a.W) & 15) || (reinterpret_cast<uintptr_t>(a.A) & 15)) return false;
     dim3 grid((a.N + GV_COLS - 1) / GV_COLS, (a.M + GV_ROWS - 1) / GV_ROWS);
     auto go = [&](auto kernel) {
         if (smem > 32 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_k(kernel, grid, dim3(GV_THREADS), smem, st, a);
+        launch_k(kernel, grid, dim3(GV_THREADS), smem, st, a, pro);
     };
     switch (epi) {
         case EPI_STORE: go(q8_gemv_kernel<EPI_STORE>); break;
@@ -702,18 +727,7 @@ __global__ void __launch_bounds__(EVS_THREADS) q8_event_small_kernel(const GemmA
     const int c = n0 + lane;
     if (warp != 0 || c >= g.N) return;
     const int8_t* wp = wt + lane;
-    float acc = 0.f;
-    int i = 0;
-    for (; i + 4 <= nnz; i += 4) {
-        const float4 xv = lds_f4(vals + i);
-        const float w0 = lds_s8(wp + (size_t)i * EVS_COLS), w1 = lds_s8(wp + (size_t)(i + 1) * EVS_COLS);
-        const float w2 = lds_s8(wp + (size_t)(i + 2) * EVS_COLS), w3 = lds_s8(wp + (size_t)(i + 3) * EVS_COLS);
-        acc = fma(xv.x, w0, acc);
-        acc = fma(xv.y, w1, acc);
-        acc = fma(xv.z, w2, acc);
-        acc = fma(xv.w, w3, acc);
-    }
-    for (; i < nnz; ++i) acc = fma(vals[i], lds_s8(wp + (size_t)i * EVS_COLS), acc);
+    const float acc = chain_s8<EVS_COLS>(vals, wp, nnz, 0.f);
     float o = mul(acc, g.scale[c]);
     if (GAIN) o = mul(o, g.lif.ne[(size_t)r * NM_STRIDE]);
     float* dst = g.C + (size_t)r * g.ldc + c;
@@ -796,6 +810,12 @@ void prefer_max_shared(const void* kernel, int percent_for_this) {
     const int percent = 50;
     cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, percent_for_this >= 0 ? percent_for_this : percent);
     if (n < 512) seen[n++] = {kernel, dev};
+}
+
+int gemv_max_rows() { return g_gemm_force == 0 ? g_gemv_max_rows : 0; }
+
+bool launch_q8_gemv_pro(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, const GemvPro& pro) {
+    return a.M <= gemv_max_rows() && launch_gemv(st, a, epi, pro);
 }
 
 void launch_q8_gemm(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int sm_count) {

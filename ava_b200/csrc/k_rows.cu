@@ -10,91 +10,11 @@
 #include "ava_math.h"
 #include "bf16_hw.cuh"
 #include "kernels.cuh"
+#include "row_sums.cuh"
 
 namespace ava {
 
 namespace {
-
-constexpr float NORM_EPS = 1e-5f;  // src/model.rs:36
-
-// Shared-memory loads that stay where they are written: the compiler otherwise sinks a prefetch down to its use and the
-// ordered chains below then wait for every load in turn.
-__device__ __forceinline__ float lds1(const float* p) {
-    float v;
-    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"((uint32_t)__cvta_generic_to_shared(p)));
-    return v;
-}
-__device__ __forceinline__ float4 lds4(const float* p) {
-    float4 v;
-    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"((uint32_t)__cvta_generic_to_shared(p)));
-    return v;
-}
-
-// sum of x[i]^2 one after another from 0; x in shared memory, 16-byte aligned.  Eight values are fetched ahead of the
-// chain so that the loads overlap; the order of the additions is the reference's.
-__device__ __forceinline__ float sumsq_seq(const float* x, int n) {
-    float s = 0.0f;
-    int i = 0;
-    if (n >= 8) {
-        float4 a = lds4(x), b = lds4(x + 4);
-        for (; i + 16 <= n; i += 8) {
-            const float4 na = lds4(x + i + 8), nb = lds4(x + i + 12);
-            const float p[8] = {mul(a.x, a.x), mul(a.y, a.y), mul(a.z, a.z), mul(a.w, a.w), mul(b.x, b.x), mul(b.y, b.y), mul(b.z, b.z), mul(b.w, b.w)};
-#pragma unroll
-            for (int k = 0; k < 8; ++k) s = add(s, p[k]);
-            a = na;
-            b = nb;
-        }
-        const float p[8] = {mul(a.x, a.x), mul(a.y, a.y), mul(a.z, a.z), mul(a.w, a.w), mul(b.x, b.x), mul(b.y, b.y), mul(b.z, b.z), mul(b.w, b.w)};
-#pragma unroll
-        for (int k = 0; k < 8; ++k) s = add(s, p[k]);
-        i += 8;
-    }
-    for (; i < n; ++i) s = add(s, mul(x[i], x[i]));
-    return s;
-}
-
-// sum of a[i] * b[i] one after another from 0 (shared memory, 16-byte aligned); the next eight products are formed
-// while the chain adds the eight before
-__device__ __forceinline__ float dot_seq(const float* a, const float* b, int n) {
-    float s = 0.0f;
-    int i = 0;
-    if (n >= 8) {
-        auto prods = [&](int at, float* p) {
-            const float4 a0 = lds4(a + at), a1 = lds4(a + at + 4), b0 = lds4(b + at), b1 = lds4(b + at + 4);
-            p[0] = mul(a0.x, b0.x); p[1] = mul(a0.y, b0.y); p[2] = mul(a0.z, b0.z); p[3] = mul(a0.w, b0.w);
-            p[4] = mul(a1.x, b1.x); p[5] = mul(a1.y, b1.y); p[6] = mul(a1.z, b1.z); p[7] = mul(a1.w, b1.w);
-        };
-        float p[8];
-        prods(0, p);
-        for (; i + 16 <= n; i += 8) {
-            float np[8];
-            prods(i + 8, np);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) s = add(s, p[k]);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) p[k] = np[k];
-        }
-#pragma unroll
-        for (int k = 0; k < 8; ++k) s = add(s, p[k]);
-        i += 8;
-    }
-    for (; i < n; ++i) s = add(s, mul(a[i], b[i]));
-    return s;
-}
-
-// (mean(x^2) + eps)^-1/2 with the squares summed in order (src/model/fstep.rs:212-220); x in shared memory
-__device__ __forceinline__ float inv_rms_seq(const float* x, int n) {
-    const float s = sumsq_seq(x, n);
-    const float ms = add(mul(s, (float)(1.0 / (double)n)), 0.0f);
-    return rsqrtf_(add(mul(ms, 1.0f), NORM_EPS));
-}
-
-// (sum(x^2) + 1e-6)^-1/2 (src/model/fstep.rs:271-282)
-__device__ __forceinline__ float inv_l2_seq(const float* x, int n) {
-    const float s = sumsq_seq(x, n);
-    return rsqrtf_(add(mul(s, 1.0f), (float)1e-6));
-}
 
 // gemm's one-row product for one output: x [k] (shared), w[j * stride] the column's weights (global).  The weights are
 // fetched sixteen at a time ahead of the chain so that their latency overlaps; the chain's order is untouched.
@@ -649,12 +569,6 @@ __global__ void mem_post_kernel(const float* __restrict__ y_raw, const float* __
 // The k-th largest value found exactly, one byte of its order-preserving key per round (256 threads, one per
 // histogram bin): the result is the largest key T with count(keys >= T) >= k.  Every unit at or above it is kept (ties included), negatives dropped, squared on request
 // (src/model/fstep.rs:295-299, src/model/fstep/arch.rs:982-989).
-__device__ __forceinline__ uint32_t order_key(float f) {
-    const uint32_t u = f_to_bits(f);
-    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
-__device__ __forceinline__ float key_value(uint32_t k) { return bits_to_f((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k); }
-
 __global__ void kwta_kernel(const float* __restrict__ u, int M, int n, int k, int relu2, float* __restrict__ out, uint16_t* __restrict__ limbs) {
     pdl_enter();
     extern __shared__ uint32_t keys[];  // [n] keys

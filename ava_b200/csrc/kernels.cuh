@@ -101,9 +101,28 @@ struct GemmArgs {
 };
 static_assert(sizeof(GemmArgs) == 128, "parameter block of the product kernels");
 
+// What a product for a few rows does to its input rows in shared memory before the chains start, instead of a kernel of
+// its own in front of it (one sequence talking is bound by the count of kernels, not by their work):
+//   PRO_RMS   the block's RMS norm: x (mean(x^2) + eps)^-1/2 gain (src/model/fstep.rs:212-220)
+//   PRO_POST  the memory's head norm and silu output gate (src/model/fstep/arch.rs:842-852)
+// Every block of the product takes the row's ordered sum itself, while its strip of weights is on the way.
+enum GemvPrologue { PRO_NONE = 0, PRO_RMS = 1, PRO_POST = 2 };
+struct GemvPro {
+    int kind = PRO_NONE;
+    const float* gain = nullptr;   // PRO_RMS: [K]
+    const float* gate = nullptr;   // PRO_POST: the output gate's pre-activation [M, ldg], or nullptr
+    int ldg = 0;
+    int hs = 0;                    // PRO_POST: head size (K is a multiple)
+    float* out = nullptr;          // not null: the rows after the prologue [M, K], written by the first block of columns
+};
+
 // C = A . W with f32 activations, int8 weights, one fused multiply-add per term in the order k = 0, 1, ... from +0,
 // the sum then times scale[n]: the bits of the reference's int8 product (src/int8.rs:315-331).  K % 16 == 0, N % 4 == 0.
 void launch_q8_gemm(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int sm_count);
+// The product for a few rows with a prologue on its input rows; false: shape or row count not covered (nothing queued).
+bool launch_q8_gemv_pro(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, const GemvPro& pro);
+// the most rows launch_q8_gemv_pro takes
+int gemv_max_rows();
 
 // The same product, same bits, with packed weights and packed multiply-adds (k_gemm2.cu).  false: shape not covered.
 bool launch_q8_gemm2(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int sm_count);
