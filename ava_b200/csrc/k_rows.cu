@@ -176,6 +176,78 @@ __global__ void gate_z_kernel(const float* __restrict__ hin, const float* __rest
     if (live) z[(size_t)(row0 + rb) * ncp + col] = out;
 }
 
+// Stage one for a few rows: with one sequence the kernel above is ONE block that pulls the whole [d][ncp] weight matrix
+// through its ring.  Here a block owns four columns: all its threads request the [d][4] strip at once (16 bytes per row),
+// and one thread per (row, column) walks the same chain from shared memory, sixteen terms fetched ahead.
+constexpr int GZF_ROWS = 8, GZF_THREADS = 128;
+__global__ void __launch_bounds__(GZF_THREADS) gate_z_few_kernel(const float* __restrict__ hin, const float* __restrict__ gate_w, int M, int d, int ncp,
+                                                                 float* __restrict__ z) {
+    extern __shared__ __align__(16) float sm[];
+    float* ws = sm;                      // [d][4]
+    float* h = sm + (size_t)d * 4;       // [rows][d]
+    const int tid = threadIdx.x, c0 = blockIdx.x * 4, row0 = blockIdx.y * GZF_ROWS, rows = min(GZF_ROWS, M - row0);
+    for (int k = tid; k < d; k += GZF_THREADS)   // the weights depend on nothing before: requested ahead of the wait
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(ws + 4 * k)), "l"(gate_w + (size_t)k * ncp + c0) : "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    pdl_enter();
+    for (int i = tid; i < rows * d / 4; i += GZF_THREADS)
+        reinterpret_cast<float4*>(h)[i] = reinterpret_cast<const float4*>(hin + (size_t)row0 * d)[i];
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    const int rb = tid >> 2, col = tid & 3;
+    if (rb >= rows) return;
+    const float* hx = h + (size_t)rb * d;
+    const float* wc = ws + col;
+    float out = -0.0f;  // fma(w, x, -0) is the plain rounded product: the chain's first term
+    float wa[16], wb[16];
+    float4 xa[4], xb[4];
+    auto load_a = [&](int g) {
+#pragma unroll
+        for (int u = 0; u < 16; ++u) wa[u] = lds1(wc + (size_t)(16 * g + u) * 4);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) xa[u] = lds4(hx + 16 * g + 4 * u);
+    };
+    auto load_b = [&](int g) {
+#pragma unroll
+        for (int u = 0; u < 16; ++u) wb[u] = lds1(wc + (size_t)(16 * g + u) * 4);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) xb[u] = lds4(hx + 16 * g + 4 * u);
+    };
+    const int G = d / 16;
+    int g = 0;
+    if (G > 0) load_a(0);
+    while (g + 2 <= G) {
+        load_b(g + 1);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            out = fma(wa[4 * u], xa[u].x, out);
+            out = fma(wa[4 * u + 1], xa[u].y, out);
+            out = fma(wa[4 * u + 2], xa[u].z, out);
+            out = fma(wa[4 * u + 3], xa[u].w, out);
+        }
+        if (g + 2 < G) load_a(g + 2);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            out = fma(wb[4 * u], xb[u].x, out);
+            out = fma(wb[4 * u + 1], xb[u].y, out);
+            out = fma(wb[4 * u + 2], xb[u].z, out);
+            out = fma(wb[4 * u + 3], xb[u].w, out);
+        }
+        g += 2;
+    }
+    if (g < G) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            out = fma(wa[4 * u], xa[u].x, out);
+            out = fma(wa[4 * u + 1], xa[u].y, out);
+            out = fma(wa[4 * u + 2], xa[u].z, out);
+            out = fma(wa[4 * u + 3], xa[u].w, out);
+        }
+    }
+    for (int k = 16 * G; k < d; ++k) out = fma(lds1(wc + (size_t)k * 4), lds1(hx + k), out);
+    z[(size_t)(row0 + rb) * ncp + c0 + col] = out;
+}
+
 // gemm's one-row product of k terms, the terms given by functions of j (src/model/fstep.rs:222-257)
 template <typename W, typename X>
 __device__ __forceinline__ float chain_k(int k, W w, X x) {
@@ -721,6 +793,15 @@ void launch_rmsnorm(cudaStream_t st, const float* x, const float* gain, int M, i
 }
 
 void launch_chain_gemv(cudaStream_t st, const float* x, const float* W, int M, int d, int n, int chunk_rows, float* out) {
+    // a few rows: the columns spread over blocks of four
+    if (M <= 2 * GZF_ROWS && n % 4 == 0 && d % 4 == 0 && !((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(x)) & 15)) {
+        const size_t sm = ((size_t)d * 4 + (size_t)std::min(M, GZF_ROWS) * d) * sizeof(float);
+        if (sm <= 200 * 1024) {
+            opt_in_smem(gate_z_few_kernel, sm);
+            launch_k(gate_z_few_kernel, dim3(n / 4, (M + GZF_ROWS - 1) / GZF_ROWS), dim3(GZF_THREADS), sm, st, x, W, M, d, n, out);
+            return;
+        }
+    }
     // a few rows per block share the staged weights
     // rows per block: one thread per (row, column), the rows' inputs within about 96 KB of shared memory
     const int RB = std::max(1, std::min(256 / n, (int)((96 * 1024) / ((size_t)d * sizeof(float))))), threads = ((RB * n + 31) / 32) * 32;
