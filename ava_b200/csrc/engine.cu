@@ -479,7 +479,7 @@ uint16_t* limbs_for(ava_engine* e, const float* dst, int M, int K) {
 }
 
 int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w, float* C, int ldc, int M, GemmEpilogue epi, const LifParams* lif = nullptr, bool sparse = false,
-         const float* row_gain = nullptr, bool int_rows = false, const GemvPro* pro = nullptr) {
+         const float* row_gain = nullptr, bool int_rows = false, const GemvPro* pro = nullptr, MixArgs* mix = nullptr) {
     GemmArgs g{};
     g.A = A;
     g.lda = lda;
@@ -562,7 +562,12 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
         }
     }
     prof_begin(e, cls);
-    if (!(sparse && launch_q8_event(e->cur, g, epi)) && !(e->gemm2 && M > 16 && launch_q8_gemm2(e->cur, g, epi, e->sm_count))) launch_q8_gemm(e->cur, g, epi, e->sm_count);
+    // a few rows: the event sum takes the dense mix that follows it along (mix->streams is cleared to say so)
+    const bool with_mix = mix && mix->streams && sparse && event_takes_mix(g, epi, mix->n_streams);
+    if (!(sparse && launch_q8_event(e->cur, g, epi, with_mix ? mix : nullptr)) && !(e->gemm2 && M > 16 && launch_q8_gemm2(e->cur, g, epi, e->sm_count)))
+        launch_q8_gemm(e->cur, g, epi, e->sm_count);
+    else if (with_mix)
+        mix->streams = nullptr;
     prof_end(e);
     return AVA_OK;
 }
@@ -874,6 +879,7 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
             MemStreamArgs ms{};
             ms.f = mh.f; ms.M = rows; ms.nh = nh; ms.hs = hs; ms.cw = e->cw;
             if (s->txn_pingpong && s->pending) ms.f_out = s->mem_f_alt.as<float>() + ((size_t)i * Sd + so) * hs;
+            ms.early_state = 1;   // the kernel queued just before (the gates' per-row part) does not write the state
             ms.e = mp.e; ms.qg = mp.qg; ms.v = mp.v; ms.qw = mp.qw; ms.qa = mp.qa;
             ms.y = mh.y;
             ms.rr_out = s->pend_at(wset, 4, i) + so;
@@ -1047,6 +1053,13 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
             dbg(e, "a_dend", i, w.act.as<float>(), M, H);
         }
         const float* nm_da = (c.neuromod > 0 && i > 0) ? w.sig.as<float>() + 2 : nullptr;
+        MixArgs mixa;   // one sequence or a handful: W2's event sum takes the dense mix along
+        if (c.dense && !c.thalamus && T == 1 && !e->fast && !e->keep) {
+            mixa.streams = streams;
+            mixa.w = b.dense.as<float>();
+            mixa.n_streams = i + 2;
+        }
+        const bool mix_asked = mixa.streams != nullptr;
         if (c.dopamine && i > 0) {
             // DA: the MLP's output times 1 + tanh(z w + c), z the token's surprise / ln V, before the nucleus's DA signal
             gemm(e, "gemm.w2", w.act.as<float>(), H, b.w2, w.y2.as<float>(), d, M, EPI_STORE, nullptr, true);
@@ -1054,14 +1067,14 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
             launch_da_add(st, x, w.y2.as<float>(), w.sur_z.as<float>(), b.da_w.as<float>(), b.da_c.as<float>(), nm_da, M, d);
             prof_end(e);
         } else {
-            gemm(e, "gemm.w2", w.act.as<float>(), H, b.w2, x, d, M, EPI_ADD, nullptr, true, nm_da);
+            gemm(e, "gemm.w2", w.act.as<float>(), H, b.w2, x, d, M, EPI_ADD, nullptr, true, nm_da, false, nullptr, &mixa);
         }
         if (c.thalamus) {
             prof_begin(e, "relay");
             launch_relay_res(st, x, w.x_in.as<float>(), w.th_g.as<float>(), M, d);
             prof_end(e);
         }
-        if (c.dense) {
+        if (c.dense && !(mix_asked && !mixa.streams)) {
             prof_begin(e, "dense_mix");
             launch_dense_mix(st, x, streams, b.dense.as<float>(), i + 2, (int64_t)Md);
             prof_end(e);

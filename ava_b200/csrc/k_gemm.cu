@@ -678,7 +678,7 @@ __global__ void __launch_bounds__(EV_THREADS) q8_event_kernel(const GemmArgs g) 
 constexpr int EVS_COLS = 32, EVS_THREADS = 256;
 
 template <int EPI, bool GAIN>
-__global__ void __launch_bounds__(EVS_THREADS) q8_event_small_kernel(const GemmArgs g) {
+__global__ void __launch_bounds__(EVS_THREADS) q8_event_small_kernel(const GemmArgs g, const MixArgs mx) {
     pdl_enter();
     extern __shared__ __align__(16) unsigned char evs_smem[];
     int8_t* wt = reinterpret_cast<int8_t*>(evs_smem);                                   // [K][32], the first nnz rows used
@@ -727,11 +727,30 @@ __global__ void __launch_bounds__(EVS_THREADS) q8_event_small_kernel(const GemmA
     const int c = n0 + lane;
     if (warp != 0 || c >= g.N) return;
     const int8_t* wp = wt + lane;
+    // the mix's stream values of this element are requested before the chain, so that their latency passes under it
+    constexpr int MIX_PRE = 16;
+    float sv[MIX_PRE];
+    if (EPI == EPI_ADD && mx.streams) {
+        const int64_t MD = (int64_t)g.M * g.N, i = (int64_t)r * g.N + c;
+#pragma unroll
+        for (int j = 0; j < MIX_PRE; ++j) sv[j] = j < mx.n_streams - 1 ? mx.streams[(int64_t)j * MD + i] : 0.0f;
+    }
     const float acc = chain_s8<EVS_COLS>(vals, wp, nnz, 0.f);
     float o = mul(acc, g.scale[c]);
     if (GAIN) o = mul(o, g.lif.ne[(size_t)r * NM_STRIDE]);
     float* dst = g.C + (size_t)r * g.ldc + c;
     if (EPI == EPI_ADD) o = add(*dst, o);
+    if (EPI == EPI_ADD && mx.streams) {
+        // the dense mix (dense_mix_kernel): x + sum_j stream_j w_j in order, the block's output joining the streams
+        const int64_t MD = (int64_t)g.M * g.N, i = (int64_t)r * g.N + c;
+        float mix = o;
+#pragma unroll
+        for (int j = 0; j < MIX_PRE; ++j)
+            if (j < mx.n_streams - 1) mix = add(mix, mul(sv[j], mx.w[j]));
+        mix = add(mix, mul(o, mx.w[mx.n_streams - 1]));
+        mx.streams[(int64_t)(mx.n_streams - 1) * MD + i] = o;
+        o = mix;
+    }
     *dst = o;
 }
 
@@ -846,16 +865,24 @@ void launch_q8_gemm(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int sm
         launch_tile<32, 64, 4, 2>(st, a, epi);
 }
 
-bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi) {
+bool event_takes_mix(const GemmArgs& a, GemmEpilogue epi, int n_streams) {
+    const size_t smem_small = (size_t)a.K * (sizeof(float) + sizeof(unsigned short) + EVS_COLS);
+    return epi == EPI_ADD && n_streams >= 1 && n_streams - 1 <= 16 && a.K <= 65535 && a.M <= g_gemv_max_rows && smem_small <= 200 * 1024 && a.N % 16 == 0 && a.ldw % 16 == 0 && a.K % 4 == 0 &&
+           !(reinterpret_cast<uintptr_t>(a.W) & 15) && a.ldc == a.N;
+}
+
+bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, const MixArgs* mix) {
     if (a.K > 65535 || epi == EPI_LIF) return false;
     const size_t smem = (size_t)a.K * (sizeof(float) + sizeof(unsigned short));
     if (smem > 200 * 1024) return false;
     const size_t smem_small = smem + (size_t)a.K * EVS_COLS;
     if (a.M <= g_gemv_max_rows && smem_small <= 200 * 1024 && a.N % 16 == 0 && a.ldw % 16 == 0 && a.K % 4 == 0 && !(reinterpret_cast<uintptr_t>(a.W) & 15)) {
         dim3 grid((a.N + EVS_COLS - 1) / EVS_COLS, a.M);
+        MixArgs mx;
+        if (mix && mix->streams && event_takes_mix(a, epi, mix->n_streams)) mx = *mix;
         auto go = [&](auto kernel) {
             if (smem_small > 32 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_small);
-            launch_k(kernel, dim3(grid), dim3(EVS_THREADS), smem_small, st, a);
+            launch_k(kernel, dim3(grid), dim3(EVS_THREADS), smem_small, st, a, mx);
         };
         if (epi == EPI_ADD && a.lif.ne)
             go(q8_event_small_kernel<EPI_ADD, true>);

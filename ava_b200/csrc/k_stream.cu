@@ -140,7 +140,6 @@ constexpr int MS_COLS = 8, MS_THREADS = 256;
 
 template <bool PEND, bool ALT>
 __global__ void __launch_bounds__(MS_THREADS) mem_stream_small_kernel(const MemStreamArgs a) {
-    pdl_enter();
     extern __shared__ __align__(16) float ss[];
     const int hs = a.hs, cw = a.cw;
     float* fs = ss;                       // [hs][8]
@@ -157,6 +156,9 @@ __global__ void __launch_bounds__(MS_THREADS) mem_stream_small_kernel(const MemS
     const float* fp = a.f + fo;
     float* fq = ALT ? a.f_out + fo : a.f + fo;
     const int tid = threadIdx.x;
+    // In a decode step the state was last written a whole step ago (by this block's pass of the token before), and the
+    // kernel just before this one does not touch it: the strip is then requested before the wait for that kernel.
+    if (!a.early_state) pdl_enter();
     for (int i = tid; i < hs * 2; i += MS_THREADS) {
         const int r = i >> 1, q = i & 1;
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(fs + (size_t)r * MS_COLS + q * 4)),
@@ -164,6 +166,7 @@ __global__ void __launch_bounds__(MS_THREADS) mem_stream_small_kernel(const MemS
                      : "memory");
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
+    if (a.early_state) pdl_enter();
     for (int i = tid * 4; i < hs; i += MS_THREADS * 4) {
         *reinterpret_cast<float4*>(ve + i) = *reinterpret_cast<const float4*>(a.e + vo + i);
         *reinterpret_cast<float4*>(vqg + i) = *reinterpret_cast<const float4*>(a.qg + vo + i);

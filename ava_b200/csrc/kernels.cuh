@@ -129,7 +129,16 @@ bool launch_q8_gemm2(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int s
 
 // The same product for rows that are mostly zeros (spikes, k-WTA'd units): summed over the non-zero inputs only, in
 // order, which gives the dense sum's bits (src/int8.rs:10-13).  false: shape not covered, use launch_q8_gemm.
-bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi);
+// mix (may be null; a few rows and EPI_ADD only, else ignored with false returned by event_takes_mix): after the add the
+// row's dense mix of the streams (launch_dense_mix) is taken in the same kernel, element by element.
+struct MixArgs {
+    float* streams = nullptr;      // [n_streams][M * d]
+    const float* w = nullptr;      // [n_streams]
+    int n_streams = 0;
+};
+bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, const MixArgs* mix = nullptr);
+// whether launch_q8_event would take the mix along for this shape (asked first: the mix then has no kernel of its own)
+bool event_takes_mix(const GemmArgs& a, GemmEpilogue epi, int n_streams);
 
 // The dense product on the tensor cores (tcgen05, f32 accumulate in tensor memory), for the optional fast-products
 // mode: exact products (three bf16 limbs of each activation times a bf16 copy of the int8 weight), the sum in the
@@ -312,6 +321,8 @@ struct MemStreamArgs {
     float* rr_out;                  // [M, nh * hs]: this token's rr (part of its pending update)
     const float *px, *pw, *pah;     // the pending update's alpha, w, ah per row [M, nh * hs]; px == nullptr: none pending
     const float *pv, *prr;          // the pending update's value and rr per column [M, nh * hs]
+    int early_state;                // 1: nothing queued just before this pass writes the state (a decode step), so the few-row kernel may request it before
+                                    // its wait for the kernel before
 };
 bool launch_mem_stream(cudaStream_t st, const MemStreamArgs& a);
 void launch_mem_flush(cudaStream_t st, float* f, const float* px, const float* pw, const float* pah, const float* pv, const float* prr, int64_t heads,
