@@ -82,12 +82,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     if (r >= M) return;
     float* xs = sm + (size_t)warp * n;
     const float* xr = x + (size_t)r * n;
-    const bool vec4 = n % 4 == 0 && !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(gain)) & 15);
-    if (vec4) {
-        for (int i = lane; i < n / 4; i += 32) reinterpret_cast<float4*>(xs)[i] = reinterpret_cast<const float4*>(xr)[i];
-    } else {
-        for (int i = lane; i < n; i += 32) xs[i] = xr[i];
-    }
+    for (int i = lane; i < n; i += 32) xs[i] = xr[i];
     __syncwarp();
     float inv = 0.0f;
     if (limbs) {
@@ -102,13 +97,6 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
         inv = __shfl_sync(0xffffffffu, inv, 0);
     }
     float* yr = y + (size_t)r * n;
-    if (vec4 && !limbs) {
-        for (int i = lane; i < n / 4; i += 32) {
-            const float4 a = reinterpret_cast<const float4*>(xs)[i], gn = reinterpret_cast<const float4*>(gain)[i];
-            reinterpret_cast<float4*>(yr)[i] = make_float4(mul(mul(a.x, inv), gn.x), mul(mul(a.y, inv), gn.y), mul(mul(a.z, inv), gn.z), mul(mul(a.w, inv), gn.w));
-        }
-        return;
-    }
     for (int i = lane; i < n; i += 32) {
         const float v = mul(mul(xs[i], inv), gain[i]);
         yr[i] = v;
