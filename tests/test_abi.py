@@ -85,6 +85,15 @@ def test_no_gpu_means_an_error_not_a_fallback(L):
         engine.op_q8_matmul(x, np.zeros((16, 4), np.int8), np.ones(4, np.float32))
 
 
+def test_split_step_calls_refuse_missing_arguments_before_any_cuda_call(L):
+    """The split step's entry points check their arguments first (no engine, a negative time limit): an error code, no
+    CUDA call, so this runs without a GPU."""
+    ERR_ARG = -1
+    assert L.ava_split_wait(None, None, 10) == ERR_ARG
+    assert L.ava_nccl_unique_id(None) == ERR_ARG
+    assert L.ava_nccl_comm_destroy(None) == ERR_ARG
+
+
 def test_product_does_not_touch_the_oracle():
     """Nothing under the package may import, link or name the oracle."""
     pkg = os.path.join(ROOT, "ava_b200")
