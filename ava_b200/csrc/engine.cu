@@ -562,12 +562,13 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
         }
     }
     prof_begin(e, cls);
-    // a few rows: the event sum takes the dense mix that follows it along (mix->streams is cleared to say so)
+    // the event sum takes the dense mix that follows it along (mix->streams is cleared to say so)
     const bool with_mix = mix && mix->streams && sparse && event_takes_mix(g, epi, mix->n_streams);
-    if (!(sparse && launch_q8_event(e->cur, g, epi, with_mix ? mix : nullptr)) && !(e->gemm2 && M > 16 && launch_q8_gemm2(e->cur, g, epi, e->sm_count)))
+    if (sparse && launch_q8_event(e->cur, g, epi, with_mix ? mix : nullptr)) {
+        if (with_mix) mix->streams = nullptr;
+    } else if (!(e->gemm2 && M > 16 && launch_q8_gemm2(e->cur, g, epi, e->sm_count))) {
         launch_q8_gemm(e->cur, g, epi, e->sm_count);
-    else if (with_mix)
-        mix->streams = nullptr;
+    }
     prof_end(e);
     return AVA_OK;
 }
@@ -1053,8 +1054,8 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
             dbg(e, "a_dend", i, w.act.as<float>(), M, H);
         }
         const float* nm_da = (c.neuromod > 0 && i > 0) ? w.sig.as<float>() + 2 : nullptr;
-        MixArgs mixa;   // one sequence or a handful: W2's event sum takes the dense mix along
-        if (c.dense && !c.thalamus && T == 1 && !e->fast && !e->keep) {
+        MixArgs mixa;   // W2's event sum takes the dense mix along in its epilogue (one kernel fewer in the block's chain)
+        if (c.dense && !c.thalamus && !e->fast && !e->keep) {
             mixa.streams = streams;
             mixa.w = b.dense.as<float>();
             mixa.n_streams = i + 2;

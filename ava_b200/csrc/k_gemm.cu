@@ -577,7 +577,7 @@ bool launch_gemv(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, const Gem
 constexpr int EV_THREADS = 64, EV_COLS = EV_THREADS * 4;
 
 template <int EPI, bool GAIN>
-__global__ void __launch_bounds__(EV_THREADS) q8_event_kernel(const GemmArgs g) {
+__global__ void __launch_bounds__(EV_THREADS) q8_event_kernel(const GemmArgs g, const MixArgs mx) {
     pdl_enter();
     extern __shared__ unsigned char ev_smem[];
     float* vals = reinterpret_cast<float*>(ev_smem);                  // [K]
@@ -667,6 +667,26 @@ __global__ void __launch_bounds__(EV_THREADS) q8_event_kernel(const GemmArgs g) 
         o[1] = add(x.y, o[1]);
         o[2] = add(x.z, o[2]);
         o[3] = add(x.w, o[3]);
+    }
+    if (EPI == EPI_ADD && mx.streams) {
+        // the dense mix (dense_mix_kernel) of these four elements: x + sum_j stream_j w_j in order, the block's output
+        // joining the streams; every load before the first store
+        const int64_t MD = (int64_t)g.M * g.N, i = (int64_t)r * g.N + c0;
+        float mix[4] = {o[0], o[1], o[2], o[3]};
+        for (int j = 0; j < mx.n_streams - 1; ++j) {
+            const float4 sj = *reinterpret_cast<const float4*>(mx.streams + (int64_t)j * MD + i);
+            const float wj = mx.w[j];
+            mix[0] = add(mix[0], mul(sj.x, wj));
+            mix[1] = add(mix[1], mul(sj.y, wj));
+            mix[2] = add(mix[2], mul(sj.z, wj));
+            mix[3] = add(mix[3], mul(sj.w, wj));
+        }
+        const float wl = mx.w[mx.n_streams - 1];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mix[j] = add(mix[j], mul(o[j], wl));
+        *reinterpret_cast<float4*>(mx.streams + (int64_t)(mx.n_streams - 1) * MD + i) = make_float4(o[0], o[1], o[2], o[3]);
+        *dst = make_float4(mix[0], mix[1], mix[2], mix[3]);
+        return;
     }
     *dst = make_float4(o[0], o[1], o[2], o[3]);
 }
@@ -866,9 +886,13 @@ void launch_q8_gemm(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int sm
 }
 
 bool event_takes_mix(const GemmArgs& a, GemmEpilogue epi, int n_streams) {
-    const size_t smem_small = (size_t)a.K * (sizeof(float) + sizeof(unsigned short) + EVS_COLS);
-    return epi == EPI_ADD && n_streams >= 1 && n_streams - 1 <= 16 && a.K <= 65535 && a.M <= g_gemv_max_rows && smem_small <= 200 * 1024 && a.N % 16 == 0 && a.ldw % 16 == 0 && a.K % 4 == 0 &&
-           !(reinterpret_cast<uintptr_t>(a.W) & 15) && a.ldc == a.N;
+    // either event kernel takes it: the few-row one keeps up to 16 stream values in registers, the other walks the streams
+    if (epi != EPI_ADD || n_streams < 1 || a.K > 65535 || a.ldc != a.N || a.N % 4) return false;
+    const size_t smem = (size_t)a.K * (sizeof(float) + sizeof(unsigned short));
+    if (smem > 200 * 1024) return false;
+    const bool few = a.M <= g_gemv_max_rows && smem + (size_t)a.K * EVS_COLS <= 200 * 1024 && a.N % 16 == 0 && a.ldw % 16 == 0 && a.K % 4 == 0 &&
+                     !(reinterpret_cast<uintptr_t>(a.W) & 15);
+    return few ? n_streams - 1 <= 16 : true;
 }
 
 bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, const MixArgs* mix) {
@@ -894,9 +918,11 @@ bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, const
     }
     const int gy = std::min(a.M, 32768);
     dim3 grid((a.N + EV_COLS - 1) / EV_COLS, gy, (a.M + gy - 1) / gy);
+    MixArgs mx;
+    if (mix && mix->streams && event_takes_mix(a, epi, mix->n_streams)) mx = *mix;
     auto go = [&](auto kernel) {
         if (smem > 32 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_k(kernel, dim3(grid), dim3(EV_THREADS), smem, st, a);
+        launch_k(kernel, dim3(grid), dim3(EV_THREADS), smem, st, a, mx);
     };
     if (epi == EPI_ADD && a.lif.ne)
         go(q8_event_kernel<EPI_ADD, true>);

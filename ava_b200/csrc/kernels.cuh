@@ -129,8 +129,8 @@ bool launch_q8_gemm2(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int s
 
 // The same product for rows that are mostly zeros (spikes, k-WTA'd units): summed over the non-zero inputs only, in
 // order, which gives the dense sum's bits (src/int8.rs:10-13).  false: shape not covered, use launch_q8_gemm.
-// mix (may be null; a few rows and EPI_ADD only, else ignored with false returned by event_takes_mix): after the add the
-// row's dense mix of the streams (launch_dense_mix) is taken in the same kernel, element by element.
+// mix (may be null; EPI_ADD only, and only where event_takes_mix says so): after the add the row's dense mix of the
+// streams (launch_dense_mix) is taken in the same kernel, element by element.
 struct MixArgs {
     float* streams = nullptr;      // [n_streams][M * d]
     const float* w = nullptr;      // [n_streams]
