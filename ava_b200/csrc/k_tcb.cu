@@ -237,6 +237,7 @@ bool launch_tc_bgemm(cudaStream_t st, const TcbArgs& a, int epi) {
         if (a.K2 > 0) return false;
         return a.N % 128 == 0 ? launch_one<128, 1, 1, 4, TCB_SCALE_ADD>(st, a) : launch_one<64, 1, 1, 4, TCB_SCALE_ADD>(st, a);
     }
+    if (a.N % 128 == 0 && epi == TCB_DECAY && a.K + a.K2 <= 2 * B_BK) return launch_one<128, 3, 3, 1, TCB_DECAY>(st, a);
     if (a.N % 128 == 0) return epi == TCB_DECAY ? launch_one<128, 3, 3, 2, TCB_DECAY>(st, a) : launch_one<128, 3, 3, 2, TCB_STORE>(st, a);
     return epi == TCB_DECAY ? launch_one<64, 3, 3, 3, TCB_DECAY>(st, a) : launch_one<64, 3, 3, 3, TCB_STORE>(st, a);
 }
