@@ -564,7 +564,12 @@ int gemm(ava_engine* e, const char* cls, const float* A, int lda, const QMat& w,
     prof_begin(e, cls);
     // the event sum takes the dense mix that follows it along (mix->streams is cleared to say so)
     const bool with_mix = mix && mix->streams && sparse && event_takes_mix(g, epi, mix->n_streams);
-    if (sparse && launch_q8_event(e->cur, g, epi, with_mix ? mix : nullptr)) {
+    const bool with_kw = mix && mix->kw_u;   // the k winners made inside the event kernel (a few rows): checked by the caller
+    MixArgs pass;
+    if (with_mix) pass = *mix;
+    if (with_kw) { pass.kw_u = mix->kw_u; pass.kw_k = mix->kw_k; pass.kw_relu2 = mix->kw_relu2; }
+    if (with_kw && !(sparse && event_small_covers(g, epi))) return e->fail(AVA_ERR_ARG, "the k winners inside the event sum: shape not covered");
+    if (sparse && launch_q8_event(e->cur, g, epi, (with_mix || with_kw) ? &pass : nullptr)) {
         if (with_mix) mix->streams = nullptr;
     } else if (!(e->gemm2 && M > 16 && launch_q8_gemm2(e->cur, g, epi, e->sm_count))) {
         launch_q8_gemm(e->cur, g, epi, e->sm_count);
@@ -1037,11 +1042,21 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
         gemm(e, "gemm.w1", h, d, b.w1, w.u.as<float>(), H, M, EPI_STORE);
         }
         dbg(e, "u", i, w.u.as<float>(), M, H);
+        // one sequence or a handful: W2's event kernel makes the k winners itself (each of its blocks selects them from
+        // the 3072 pre-activations while nothing else runs anyway), so they need no kernel of their own
+        bool kw_inside = false;
+        if (T == 1 && !e->fast && !e->keep && !c.dendrite && !(c.dopamine && i > 0) && M <= gemv_max_rows()) {
+            GemmArgs gq{};
+            gq.W = b.w2.qp(); gq.ldw = b.w2.dout; gq.M = M; gq.N = b.w2.dout; gq.K = b.w2.din; gq.ldc = d;
+            kw_inside = event_small_covers(gq, EPI_ADD);
+        }
+        if (!kw_inside) {
         prof_begin(e, "kwta");
         // a prompt chunk in the tolerance mode multiplies the k-WTA's output densely on the tensor cores: its limbs are made here
         launch_kwta(st, w.u.as<float>(), M, H, c.kwta_k, c.relu2, w.act.as<float>(),
                     (M >= 1024 && b.w2.wt.p && !c.dendrite) ? limbs_for(e, w.act.as<float>(), M, H) : nullptr);
         prof_end(e);
+        }
         dbg(e, "a", i, w.act.as<float>(), M, H);
         if (c.dendrite && c.fast_mem) {
             // P: the units times 1 + tanh(head_norm(ctx) A B); h is free here
@@ -1061,6 +1076,11 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
             mixa.n_streams = i + 2;
         }
         const bool mix_asked = mixa.streams != nullptr;
+        if (kw_inside) {
+            mixa.kw_u = w.u.as<float>();
+            mixa.kw_k = c.kwta_k;
+            mixa.kw_relu2 = c.relu2;
+        }
         if (c.dopamine && i > 0) {
             // DA: the MLP's output times 1 + tanh(z w + c), z the token's surprise / ln V, before the nucleus's DA signal
             gemm(e, "gemm.w2", w.act.as<float>(), H, b.w2, w.y2.as<float>(), d, M, EPI_STORE, nullptr, true);

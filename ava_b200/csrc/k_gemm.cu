@@ -709,6 +709,63 @@ __global__ void __launch_bounds__(EVS_THREADS) q8_event_small_kernel(const GemmA
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int r = blockIdx.y, n0 = blockIdx.x * EVS_COLS;
     const float* xr = g.A + (size_t)r * g.lda;
+    if (mx.kw_u) {
+        // the row is the k winners of the pre-activations (kwta_kernel's selection and arithmetic), made here
+        float* us = reinterpret_cast<float*>(idx + g.K);   // [K]
+        uint32_t* keys = reinterpret_cast<uint32_t*>(vals);  // [K], free until the list is written
+        __shared__ int hist[256];
+        __shared__ int warp_sum[8];
+        __shared__ uint32_t sel_prefix;
+        __shared__ int sel_k;
+        const int n = g.K, k = mx.kw_k;
+        const float* ur = mx.kw_u + (size_t)r * n;
+        for (int i = tid; i < n; i += EVS_THREADS) us[i] = ur[i];
+        __syncthreads();
+        if (k >= n) {
+            for (int i = tid; i < n; i += EVS_THREADS) {
+                const float v = fmaxf(mul(us[i], 1.0f), 0.0f);
+                us[i] = mx.kw_relu2 ? mul(v, v) : v;
+            }
+        } else {
+            for (int i = tid; i < n; i += EVS_THREADS) keys[i] = order_key(us[i]);
+            uint32_t thr = 0;
+            int k_rem = k;
+            for (int shift = 24; shift >= 0; shift -= 8) {
+                hist[tid] = 0;
+                __syncthreads();
+                const uint32_t mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+                for (int i = tid; i < n; i += EVS_THREADS) {
+                    const uint32_t key = keys[i];
+                    if ((key & mask) == thr) atomicAdd(&hist[(key >> shift) & 255u], 1);
+                }
+                __syncthreads();
+                const int h = hist[tid];
+                int sfx = h;  // keys in bins tid .. 255
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int up = __shfl_down_sync(0xffffffffu, sfx, o);
+                    if (lane + o < 32) sfx += up;
+                }
+                if (lane == 0) warp_sum[warp] = sfx;
+                __syncthreads();
+                for (int w = warp + 1; w < 8; ++w) sfx += warp_sum[w];
+                if (sfx >= k_rem && sfx - h < k_rem) {  // exactly one bin: the suffix sums fall as the bin index rises
+                    sel_prefix = thr | ((uint32_t)tid << shift);
+                    sel_k = k_rem - (sfx - h);
+                }
+                __syncthreads();
+                thr = sel_prefix;
+                k_rem = sel_k;
+            }
+            const float kth = key_value(thr);
+            for (int i = tid; i < n; i += EVS_THREADS) {
+                const float v = us[i];
+                const float o = fmaxf(mul(v, sub(v, kth) >= 0.0f ? 1.0f : 0.0f), 0.0f);
+                us[i] = mx.kw_relu2 ? mul(o, o) : o;
+            }
+        }
+        __syncthreads();
+        xr = us;
+    }
     const int part = ((g.K + NW * 32 - 1) / (NW * 32)) * 32;  // inputs per warp, a multiple of 32
     const int j0 = min(g.K, warp * part), j1 = min(g.K, j0 + part);
     int cnt = 0;
@@ -885,25 +942,38 @@ void launch_q8_gemm(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, int sm
         launch_tile<32, 64, 4, 2>(st, a, epi);
 }
 
+bool event_small_covers(const GemmArgs& a, GemmEpilogue epi) {
+    // (the k winners' copy of the row is counted in: K * 4 bytes more)
+    const size_t smem_small = (size_t)a.K * (2 * sizeof(float) + sizeof(unsigned short) + EVS_COLS);
+    return epi != EPI_LIF && a.K <= 65535 && a.M <= g_gemv_max_rows && smem_small <= 200 * 1024 && a.N % 16 == 0 && a.ldw % 16 == 0 && a.K % 4 == 0 &&
+           !(reinterpret_cast<uintptr_t>(a.W) & 15);
+}
+
 bool event_takes_mix(const GemmArgs& a, GemmEpilogue epi, int n_streams) {
     // either event kernel takes it: the few-row one keeps up to 16 stream values in registers, the other walks the streams
     if (epi != EPI_ADD || n_streams < 1 || a.K > 65535 || a.ldc != a.N || a.N % 4) return false;
     const size_t smem = (size_t)a.K * (sizeof(float) + sizeof(unsigned short));
     if (smem > 200 * 1024) return false;
-    const bool few = a.M <= g_gemv_max_rows && smem + (size_t)a.K * EVS_COLS <= 200 * 1024 && a.N % 16 == 0 && a.ldw % 16 == 0 && a.K % 4 == 0 &&
-                     !(reinterpret_cast<uintptr_t>(a.W) & 15);
-    return few ? n_streams - 1 <= 16 : true;
+    return event_small_covers(a, epi) ? n_streams - 1 <= 16 : true;
 }
 
 bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, const MixArgs* mix) {
     if (a.K > 65535 || epi == EPI_LIF) return false;
     const size_t smem = (size_t)a.K * (sizeof(float) + sizeof(unsigned short));
     if (smem > 200 * 1024) return false;
-    const size_t smem_small = smem + (size_t)a.K * EVS_COLS;
-    if (a.M <= g_gemv_max_rows && smem_small <= 200 * 1024 && a.N % 16 == 0 && a.ldw % 16 == 0 && a.K % 4 == 0 && !(reinterpret_cast<uintptr_t>(a.W) & 15)) {
+    const size_t smem_small = smem + (size_t)a.K * EVS_COLS + (mix && mix->kw_u ? (size_t)a.K * sizeof(float) : 0);
+    if (mix && mix->kw_u && !event_small_covers(a, epi)) return false;   // only the kernel for a few rows makes the k winners itself
+    if (event_small_covers(a, epi)) {
         dim3 grid((a.N + EVS_COLS - 1) / EVS_COLS, a.M);
         MixArgs mx;
         if (mix && mix->streams && event_takes_mix(a, epi, mix->n_streams)) mx = *mix;
+        if (mix && mix->kw_u) {
+            mx.kw_u = mix->kw_u;
+            mx.kw_k = mix->kw_k;
+            mx.kw_relu2 = mix->kw_relu2;
+        } else {
+            mx.kw_u = nullptr;
+        }
         auto go = [&](auto kernel) {
             if (smem_small > 32 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_small);
             launch_k(kernel, dim3(grid), dim3(EVS_THREADS), smem_small, st, a, mx);

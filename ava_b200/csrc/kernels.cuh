@@ -135,10 +135,17 @@ struct MixArgs {
     float* streams = nullptr;      // [n_streams][M * d]
     const float* w = nullptr;      // [n_streams]
     int n_streams = 0;
+    // A few rows only (event_small_covers): the input row is not read from A but made in the kernel as the k winners of
+    // kw_u's row (launch_kwta's arithmetic: the units at or above the k-th largest, negatives dropped, squared on
+    // request), so the k winners need no kernel of their own.  kw_u == nullptr: the row comes from A as usual.
+    const float* kw_u = nullptr;   // [M, K] pre-activations
+    int kw_k = 0, kw_relu2 = 0;
 };
 bool launch_q8_event(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, const MixArgs* mix = nullptr);
 // whether launch_q8_event would take the mix along for this shape (asked first: the mix then has no kernel of its own)
 bool event_takes_mix(const GemmArgs& a, GemmEpilogue epi, int n_streams);
+// whether the event kernel for a few rows takes this product (only it can make the k winners itself)
+bool event_small_covers(const GemmArgs& a, GemmEpilogue epi);
 
 // The dense product on the tensor cores (tcgen05, f32 accumulate in tensor memory), for the optional fast-products
 // mode: exact products (three bf16 limbs of each activation times a bf16 copy of the int8 weight), the sum in the
