@@ -725,13 +725,28 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
 
         // ---- the fast-weight memory (kinds D and A; a kind-S block goes on to its MLP)
         if (c.fast_mem) {
+        const int pw = e->proj_w();
+        // one sequence or a handful: the norm in front of q|k|v|e|g and the gates is taken by both of its readers
+        // themselves (each while its weights arrive), so it needs no kernel of its own
+        GemvPro hebb_pro;
+        hebb_pro.kind = PRO_RMS;
+        hebb_pro.gain = b.hebb_norm.as<float>();
+        bool norm_inside = false;
+        if (few) {
+            GemmArgs gq{};
+            gq.A = x; gq.lda = d; gq.W = b.proj.qp(); gq.ldw = b.proj.dout; gq.M = M; gq.N = b.proj.dout; gq.K = b.proj.din; gq.ldc = pw;
+            norm_inside = b.proj.din == d && q8_gemv_pro_covers(gq, hebb_pro) && gate_z_few_covers(x, b.gate_w.as<float>(), M, d, e->gate_cols) &&
+                          !(reinterpret_cast<uintptr_t>(hebb_pro.gain) & 15);
+        }
+        if (!norm_inside) {
         prof_begin(e, "rmsnorm");
         launch_rmsnorm(st, x, b.hebb_norm.as<float>(), M, d, h, limbs_for(e, h, M, d));
         prof_end(e);
+        }
         dbg(e, "h_mem", i, h, M, d);
-        const int pw = e->proj_w();
         MemPrepArgs mp{};
-        mp.h = h;
+        mp.h = norm_inside ? x : h;
+        mp.h_gain = norm_inside ? hebb_pro.gain : nullptr;
         mp.proj = w.proj.as<float>();
         mp.ldp = pw;
         mp.gate_w = b.gate_w.as<float>(); mp.gate_cols = e->gate_cols; mp.gate_chunk = e->gate_chunk;
@@ -801,7 +816,12 @@ int step_rows(ava_engine* e, Work& w, cudaStream_t st, ava_state* s, int r0, int
             launch_mem_gates(w.side_stream, mp);
             CK(cudaEventRecord(w.side_done, w.side_stream));
         }
-        gemm(e, "gemm.qkveg", h, d, b.proj, w.proj.as<float>(), pw, M, EPI_STORE);
+        if (norm_inside) {
+            const int prc = gemm(e, "gemm.qkveg", x, d, b.proj, w.proj.as<float>(), pw, M, EPI_STORE, nullptr, false, nullptr, false, &hebb_pro);
+            if (prc != AVA_OK) return e->fail(AVA_ERR_CUDA, "the q|k|v|e|g product with its norm inside was refused after it had been accepted");
+        } else {
+            gemm(e, "gemm.qkveg", h, d, b.proj, w.proj.as<float>(), pw, M, EPI_STORE);
+        }
         dbg(e, "qkveg", i, w.proj.as<float>(), M, pw);
         prof_begin(e, "mem_prep");
         if (tc_gates) {

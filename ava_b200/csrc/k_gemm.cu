@@ -545,17 +545,24 @@ __global__ void __launch_bounds__(GV_THREADS) q8_gemv_kernel(const GemmArgs g, c
 }
 
 // false: shape not covered (the strip and the rows must fit shared memory; N a multiple of 16; 16-byte aligned rows)
-bool launch_gemv(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, const GemvPro& pro = GemvPro()) {
+// the shared-memory size of the launch, or 0 when the shape is not covered
+size_t gemv_smem(const GemmArgs& a, const GemvPro& pro) {
     const int rows = a.M < GV_ROWS ? a.M : GV_ROWS;
-    if (pro.kind == PRO_POST && (pro.hs <= 0 || a.K % pro.hs || pro.hs % 4)) return false;
+    if (pro.kind == PRO_POST && (pro.hs <= 0 || a.K % pro.hs || pro.hs % 4)) return 0;
     size_t aux = pro.kind == PRO_RMS ? (size_t)a.K * sizeof(float) : (pro.kind == PRO_POST && pro.gate) ? (size_t)rows * a.K * sizeof(float) : 0;
     if (pro.kind == PRO_RMS) aux += (size_t)rows * sizeof(float);                       // the rows' norms
     if (pro.kind == PRO_POST) aux += (size_t)rows * (a.K / pro.hs) * sizeof(float);    // the heads' norms
     aux = (aux + 15) & ~(size_t)15;
     const size_t smem = (size_t)a.K * GV_COLS + (size_t)rows * a.K * sizeof(float) + aux;
-    if (pro.kind == PRO_RMS && (reinterpret_cast<uintptr_t>(pro.gain) & 15)) return false;
-    if (pro.kind == PRO_POST && pro.gate && ((reinterpret_cast<uintptr_t>(pro.gate) & 15) || pro.ldg % 4)) return false;
-    if (smem > 200 * 1024 || a.N % 16 || a.K % 4 || a.ldw % 16 || a.lda % 4 || (reinterpret_cast<uintptr_t>(a.W) & 15) || (reinterpret_cast<uintptr_t>(a.A) & 15)) return false;
+    if (pro.kind == PRO_RMS && (reinterpret_cast<uintptr_t>(pro.gain) & 15)) return 0;
+    if (pro.kind == PRO_POST && pro.gate && ((reinterpret_cast<uintptr_t>(pro.gate) & 15) || pro.ldg % 4)) return 0;
+    if (smem > 200 * 1024 || a.N % 16 || a.K % 4 || a.ldw % 16 || a.lda % 4 || (reinterpret_cast<uintptr_t>(a.W) & 15) || (reinterpret_cast<uintptr_t>(a.A) & 15)) return 0;
+    return smem;
+}
+
+bool launch_gemv(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, const GemvPro& pro = GemvPro()) {
+    const size_t smem = gemv_smem(a, pro);
+    if (!smem) return false;
     dim3 grid((a.N + GV_COLS - 1) / GV_COLS, (a.M + GV_ROWS - 1) / GV_ROWS);
     auto go = [&](auto kernel) {
         if (smem > 32 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -909,6 +916,8 @@ void prefer_max_shared(const void* kernel, int percent_for_this) {
 }
 
 int gemv_max_rows() { return g_gemm_force == 0 ? g_gemv_max_rows : 0; }
+
+bool q8_gemv_pro_covers(const GemmArgs& a, const GemvPro& pro) { return a.M <= gemv_max_rows() && gemv_smem(a, pro) != 0; }
 
 bool launch_q8_gemv_pro(cudaStream_t st, const GemmArgs& a, GemmEpilogue epi, const GemvPro& pro) {
     return a.M <= gemv_max_rows() && launch_gemv(st, a, epi, pro);

@@ -181,10 +181,11 @@ __global__ void gate_z_kernel(const float* __restrict__ hin, const float* __rest
 // and one thread per (row, column) walks the same chain from shared memory, sixteen terms fetched ahead.
 constexpr int GZF_ROWS = 8, GZF_THREADS = 128;
 __global__ void __launch_bounds__(GZF_THREADS) gate_z_few_kernel(const float* __restrict__ hin, const float* __restrict__ gate_w, int M, int d, int ncp,
-                                                                 float* __restrict__ z) {
+                                                                 float* __restrict__ z, const float* __restrict__ norm_gain) {
     extern __shared__ __align__(16) float sm[];
     float* ws = sm;                      // [d][4]
     float* h = sm + (size_t)d * 4;       // [rows][d]
+    float* gn = h + (size_t)GZF_ROWS * d;  // [d] the norm's gain, then [GZF_ROWS] the rows' norms (norm_gain only)
     const int tid = threadIdx.x, c0 = blockIdx.x * 4, row0 = blockIdx.y * GZF_ROWS, rows = min(GZF_ROWS, M - row0);
     for (int k = tid; k < d; k += GZF_THREADS)   // the weights depend on nothing before: requested ahead of the wait
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(ws + 4 * k)), "l"(gate_w + (size_t)k * ncp + c0) : "memory");
@@ -192,6 +193,20 @@ __global__ void __launch_bounds__(GZF_THREADS) gate_z_few_kernel(const float* __
     pdl_enter();
     for (int i = tid; i < rows * d / 4; i += GZF_THREADS)
         reinterpret_cast<float4*>(h)[i] = reinterpret_cast<const float4*>(hin + (size_t)row0 * d)[i];
+    if (norm_gain) {
+        // the rows came as the block's input: their RMS norm is taken here (rmsnorm_kernel's arithmetic), a row's
+        // ordered sum by lane 0 of a warp, the scaling by everyone, while the weights arrive
+        for (int i = tid; i < d / 4; i += GZF_THREADS) reinterpret_cast<float4*>(gn)[i] = reinterpret_cast<const float4*>(norm_gain)[i];
+        __syncthreads();
+        float* inv_sh = gn + d;
+        for (int r = tid >> 5; r < rows; r += GZF_THREADS / 32)
+            if ((tid & 31) == 0) inv_sh[r] = inv_rms_seq(h + (size_t)r * d, d);
+        __syncthreads();
+        for (int i = tid; i < rows * d; i += GZF_THREADS) {
+            const int r = i / d;
+            h[i] = mul(mul(h[i], inv_sh[r]), gn[i - r * d]);
+        }
+    }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     const int rb = tid >> 2, col = tid & 3;
@@ -792,15 +807,23 @@ void launch_rmsnorm(cudaStream_t st, const float* x, const float* gain, int M, i
     launch_k(rmsnorm_kernel, dim3((M + warps - 1) / warps), dim3(warps * 32), smem, st, x, gain, M, n, y, limbs);
 }
 
-void launch_chain_gemv(cudaStream_t st, const float* x, const float* W, int M, int d, int n, int chunk_rows, float* out) {
+bool gate_z_few_covers(const float* x, const float* W, int M, int d, int n) {
+    const size_t sm = ((size_t)d * 4 + (size_t)GZF_ROWS * d + d + GZF_ROWS) * sizeof(float);
+    return M <= 2 * GZF_ROWS && n % 4 == 0 && d % 4 == 0 && !((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(x)) & 15) && sm <= 200 * 1024;
+}
+
+// norm_gain (a few rows only: ask gate_z_few_covers first): x is not normed yet, the kernel takes its RMS norm with this gain
+void launch_chain_gemv(cudaStream_t st, const float* x, const float* W, int M, int d, int n, int chunk_rows, float* out, const float* norm_gain) {
     // a few rows: the columns spread over blocks of four
-    if (M <= 2 * GZF_ROWS && n % 4 == 0 && d % 4 == 0 && !((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(x)) & 15)) {
-        const size_t sm = ((size_t)d * 4 + (size_t)std::min(M, GZF_ROWS) * d) * sizeof(float);
-        if (sm <= 200 * 1024) {
-            opt_in_smem(gate_z_few_kernel, sm);
-            launch_k(gate_z_few_kernel, dim3(n / 4, (M + GZF_ROWS - 1) / GZF_ROWS), dim3(GZF_THREADS), sm, st, x, W, M, d, n, out);
-            return;
-        }
+    if (gate_z_few_covers(x, W, M, d, n) && !(reinterpret_cast<uintptr_t>(norm_gain) & 15)) {
+        const size_t sm = ((size_t)d * 4 + (size_t)GZF_ROWS * d + d + GZF_ROWS) * sizeof(float);
+        opt_in_smem(gate_z_few_kernel, sm);
+        launch_k(gate_z_few_kernel, dim3(n / 4, (M + GZF_ROWS - 1) / GZF_ROWS), dim3(GZF_THREADS), sm, st, x, W, M, d, n, out, norm_gain);
+        return;
+    }
+    if (norm_gain) {   // never: the caller asked first
+        if (g_launch_error == cudaSuccess) g_launch_error = cudaErrorInvalidValue;
+        return;
     }
     // a few rows per block share the staged weights
     // rows per block: one thread per (row, column), the rows' inputs within about 96 KB of shared memory
@@ -851,7 +874,7 @@ void launch_mem_prep(cudaStream_t st, const MemPrepArgs& a) {
 // the gates' two projection stages (they read the normed input only, so they can run beside the q|k|v|e|g product)
 void launch_mem_gates(cudaStream_t st, const MemPrepArgs& a) {
     // stage one
-    launch_chain_gemv(st, a.h, a.gate_w, a.M, a.d, a.gate_cols, a.gate_chunk, a.z);
+    launch_chain_gemv(st, a.h, a.gate_w, a.M, a.d, a.gate_cols, a.gate_chunk, a.z, a.h_gain);
     launch_mem_gates_low(st, a);
 }
 

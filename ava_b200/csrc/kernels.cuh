@@ -273,10 +273,16 @@ struct MemPrepArgs {
     int fast;            // 1 (the tolerance mode): norms and dot products summed by a warp each, the library's exp and log
     float mom;
     uint32_t* status;
+    const float* h_gain = nullptr;  // not null (a few rows only, gate_z_few_covers): h is the block's input as it came and stage one takes
+                                    // its RMS norm with this gain itself, so the norm needs no kernel of its own
 };
 // out [M][n] = x [M][d] . W [d][n] in gemm's one-row order (an fma chain down the rows from the first product), the weights
 // staged through shared memory for a few rows at a time; n a multiple of 4 (at most 224), d a multiple of chunk
-void launch_chain_gemv(cudaStream_t st, const float* x, const float* W, int M, int d, int n, int chunk, float* out);
+void launch_chain_gemv(cudaStream_t st, const float* x, const float* W, int M, int d, int n, int chunk, float* out, const float* norm_gain = nullptr);
+// whether the kernel for a few rows takes this projection (only it can take the input's norm itself)
+bool gate_z_few_covers(const float* x, const float* W, int M, int d, int n);
+// whether launch_q8_gemv_pro would take this product (asked before anything is queued)
+bool q8_gemv_pro_covers(const GemmArgs& a, const GemvPro& pro);
 // --dendrite (src/model/fstep/arch_f4.rs:120-141): act [M][H] *= 1 + tanh(z1 [M][rank] . B [rank][H]), the product in gemm's
 // one-row order
 void launch_dend_gain(cudaStream_t st, const float* z1, int rank, const float* B, int M, int H, float* act);
