@@ -531,15 +531,19 @@ __global__ void __launch_bounds__(GV_THREADS) q8_gemv_kernel(const GemmArgs g, c
     if (c >= g.N || rl >= rows) return;
     const float* x = xs + (size_t)rl * g.K;
     const int8_t* wp = wt + cl;
-    const float acc = chain_s8<GV_COLS>(x, wp, g.K, 0.f);
+    // what the epilogue reads from global memory is requested before the chain: its latency passes under it
     const int r = m0 + rl;
-    float o = mul(acc, g.scale[c]);
-    if (EPI == EPI_ADD && g.lif.ne) o = mul(o, g.lif.ne[(size_t)r * NM_STRIDE]);
+    const float sc = g.scale[c];
+    float* dst = EPI == EPI_LIF ? nullptr : g.C + (size_t)r * g.ldc + c;
+    const float before = EPI == EPI_ADD ? *dst : 0.0f;
+    const float row_gain = (EPI == EPI_ADD && g.lif.ne) ? g.lif.ne[(size_t)r * NM_STRIDE] : 1.0f;
+    const float acc = chain_s8<GV_COLS>(x, wp, g.K, 0.f);
+    float o = mul(acc, sc);
+    if (EPI == EPI_ADD && g.lif.ne) o = mul(o, row_gain);
     if (EPI == EPI_LIF) {
         lif_update(g.lif, r, c, g.N, o);
     } else {
-        float* dst = g.C + (size_t)r * g.ldc + c;
-        if (EPI == EPI_ADD) o = add(*dst, o);
+        if (EPI == EPI_ADD) o = add(before, o);
         *dst = o;
     }
 }
@@ -819,19 +823,32 @@ __global__ void __launch_bounds__(EVS_THREADS) q8_event_small_kernel(const GemmA
 #pragma unroll
         for (int j = 0; j < MIX_PRE; ++j) sv[j] = j < mx.n_streams - 1 ? mx.streams[(int64_t)j * MD + i] : 0.0f;
     }
-    const float acc = chain_s8<EVS_COLS>(vals, wp, nnz, 0.f);
-    float o = mul(acc, g.scale[c]);
-    if (GAIN) o = mul(o, g.lif.ne[(size_t)r * NM_STRIDE]);
+    // so is everything else the epilogue reads
+    const float sc = g.scale[c];
+    const float row_gain = GAIN ? g.lif.ne[(size_t)r * NM_STRIDE] : 1.0f;
     float* dst = g.C + (size_t)r * g.ldc + c;
-    if (EPI == EPI_ADD) o = add(*dst, o);
+    const float before = EPI == EPI_ADD ? *dst : 0.0f;
+    float mw[MIX_PRE + 1];
+    if (EPI == EPI_ADD && mx.streams) {
+#pragma unroll
+        for (int j = 0; j <= MIX_PRE; ++j) mw[j] = j < mx.n_streams ? mx.w[j] : 0.0f;
+    }
+    const float acc = chain_s8<EVS_COLS>(vals, wp, nnz, 0.f);
+    float o = mul(acc, sc);
+    if (GAIN) o = mul(o, row_gain);
+    if (EPI == EPI_ADD) o = add(before, o);
     if (EPI == EPI_ADD && mx.streams) {
         // the dense mix (dense_mix_kernel): x + sum_j stream_j w_j in order, the block's output joining the streams
         const int64_t MD = (int64_t)g.M * g.N, i = (int64_t)r * g.N + c;
         float mix = o;
+        float w_last = 0.0f;
 #pragma unroll
         for (int j = 0; j < MIX_PRE; ++j)
-            if (j < mx.n_streams - 1) mix = add(mix, mul(sv[j], mx.w[j]));
-        mix = add(mix, mul(o, mx.w[mx.n_streams - 1]));
+            if (j < mx.n_streams - 1) mix = add(mix, mul(sv[j], mw[j]));
+#pragma unroll
+        for (int j = 0; j <= MIX_PRE; ++j)
+            if (j == mx.n_streams - 1) w_last = mw[j];
+        mix = add(mix, mul(o, w_last));
         mx.streams[(int64_t)(mx.n_streams - 1) * MD + i] = o;
         o = mix;
     }

@@ -194,6 +194,9 @@ __global__ void __launch_bounds__(MS_THREADS) mem_stream_small_kernel(const MemS
     // lane j < 8: rr of column j (the rows times e); lane 8 + j: t1 of column j (the rows times q alpha)
     const int j = tid & (MS_COLS - 1);
     const float* vec = tid < MS_COLS ? ve : vqg;
+    // what the read's tail takes from global memory is requested before the chains
+    const float v = a.v[vo + c + j];
+    const float qw = a.qw[(size_t)m * a.nh + head], qa = a.qa[(size_t)m * a.nh + head];
     // the chains start from -0: fma(f, e, -0) is the rounded product with its own sign, i.e. row 0's plain product
     float sum = -0.0f;
     const float* col = fs + j;
@@ -201,8 +204,6 @@ __global__ void __launch_bounds__(MS_THREADS) mem_stream_small_kernel(const MemS
     for (int r = 0; r < hs; ++r) sum = fma(col[(size_t)r * MS_COLS], vec[r], sum);
     const float t1 = __shfl_down_sync(0x0000ffffu, sum, MS_COLS, 16);
     if (tid >= MS_COLS) return;
-    const float v = a.v[vo + c + j];
-    const float qw = a.qw[(size_t)m * a.nh + head], qa = a.qa[(size_t)m * a.nh + head];
     // the recall's term from inside the one-token chunk is an exact zero (arch.rs:277-280): kept for the sign of zero
     const float rr = add(sum, mul(1.0f, mul(0.0f, v)));
     a.y[vo + c + j] = sub(add(t1, mul(qw, v)), mul(qa, rr));
