@@ -537,11 +537,29 @@ __global__ void __launch_bounds__(GV_THREADS) q8_gemv_kernel(const GemmArgs g, c
     float* dst = EPI == EPI_LIF ? nullptr : g.C + (size_t)r * g.ldc + c;
     const float before = EPI == EPI_ADD ? *dst : 0.0f;
     const float row_gain = (EPI == EPI_ADD && g.lif.ne) ? g.lif.ne[(size_t)r * NM_STRIDE] : 1.0f;
+    // (the LIF update's state and parameters of this channel too: lif_update's loads, made early)
+    const size_t li = (size_t)r * g.N + c;
+    float lv = 0.f, ls = 0.f, la = 0.f, l_beta = 0.f, l_th = 1.0f, l_rho = 0.f, l_gain = 0.f, l_ne = 1.0f;
+    if (EPI == EPI_LIF) {
+        const LifParams& p = g.lif;
+        lv = p.v[li];
+        ls = p.s[li];
+        la = p.rho ? p.a[li] : 0.0f;
+        l_beta = p.beta[c];
+        l_th = p.theta ? p.theta[c] : 1.0f;
+        l_rho = p.rho ? p.rho[c] : 0.0f;
+        l_gain = p.rho ? p.gain[c] : 0.0f;
+        l_ne = p.ne ? p.ne[(size_t)r * NM_STRIDE] : 1.0f;
+    }
     const float acc = chain_s8<GV_COLS>(x, wp, g.K, 0.f);
     float o = mul(acc, sc);
     if (EPI == EPI_ADD && g.lif.ne) o = mul(o, row_gain);
     if (EPI == EPI_LIF) {
-        lif_update(g.lif, r, c, g.N, o);
+        const LifParams& p = g.lif;
+        lif_math(p.spikes, p.lif_scale, p.rho != nullptr, l_beta, l_th, l_rho, l_gain, l_ne, o, lv, ls, la);
+        p.v[li] = lv;
+        p.s[li] = ls;
+        if (p.rho) p.a[li] = la;
     } else {
         if (EPI == EPI_ADD) o = add(before, o);
         *dst = o;

@@ -484,11 +484,27 @@ __global__ void mem_prep_kernel(const MemPrepArgs a) {
     float* inv_e = inv_k + nh;
 
     const float* pr = a.proj + (size_t)r * a.ldp;
-    for (int c = tid; c < d; c += T) {
-        q[c] = pr[c];
-        const float kk = pr[d + c];
-        kr[c] = kk;
-        ek[c] = add(kk, pr[3 * d + c]);
+    // (all of a thread's loads before its first store: the compiler cannot move a load above a store it cannot tell apart)
+    constexpr int LD = 4;
+    for (int c0 = tid; c0 < d; c0 += T * LD) {
+        float lq[LD], lk[LD], le[LD];
+#pragma unroll
+        for (int u = 0; u < LD; ++u) {
+            const int c = c0 + u * T;
+            const bool in = c < d;
+            lq[u] = in ? pr[c] : 0.0f;
+            lk[u] = in ? pr[d + c] : 0.0f;
+            le[u] = in ? pr[3 * d + c] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < LD; ++u) {
+            const int c = c0 + u * T;
+            if (c < d) {
+                q[c] = lq[u];
+                kr[c] = lk[u];
+                ek[c] = add(lk[u], le[u]);
+            }
+        }
     }
     __syncthreads();
     // the gate phase's inputs for this thread's first channels are requested now, so that their latency passes while the
