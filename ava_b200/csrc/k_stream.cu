@@ -62,12 +62,21 @@ __global__ void __launch_bounds__(256) mem_stream_kernel(const MemStreamArgs a) 
     const int head = (blockIdx.x / parts) % a.nh, m = blockIdx.x / (parts * a.nh);
     const size_t vo = ((size_t)m * a.nh + head) * hs;
     for (int i = threadIdx.x * 4; i < hs; i += blockDim.x * 4) {
-        *reinterpret_cast<float4*>(ve + i) = *reinterpret_cast<const float4*>(a.e + vo + i);
-        *reinterpret_cast<float4*>(vqg + i) = *reinterpret_cast<const float4*>(a.qg + vo + i);
+        // the five loads before the first store (the compiler cannot move a load above a store it cannot tell apart,
+        // and five latencies one after another at the start of every block are not nothing)
+        const float4 le = *reinterpret_cast<const float4*>(a.e + vo + i), lq = *reinterpret_cast<const float4*>(a.qg + vo + i);
+        float4 lx = le, lw = le, la = le;
         if (PEND) {
-            *reinterpret_cast<float4*>(vpx + i) = *reinterpret_cast<const float4*>(a.px + vo + i);
-            *reinterpret_cast<float4*>(vpw + i) = *reinterpret_cast<const float4*>(a.pw + vo + i);
-            *reinterpret_cast<float4*>(vpa + i) = *reinterpret_cast<const float4*>(a.pah + vo + i);
+            lx = *reinterpret_cast<const float4*>(a.px + vo + i);
+            lw = *reinterpret_cast<const float4*>(a.pw + vo + i);
+            la = *reinterpret_cast<const float4*>(a.pah + vo + i);
+        }
+        *reinterpret_cast<float4*>(ve + i) = le;
+        *reinterpret_cast<float4*>(vqg + i) = lq;
+        if (PEND) {
+            *reinterpret_cast<float4*>(vpx + i) = lx;
+            *reinterpret_cast<float4*>(vpw + i) = lw;
+            *reinterpret_cast<float4*>(vpa + i) = la;
         }
     }
     __syncthreads();
@@ -168,12 +177,20 @@ __global__ void __launch_bounds__(MS_THREADS) mem_stream_small_kernel(const MemS
     asm volatile("cp.async.commit_group;" ::: "memory");
     if (a.early_state) pdl_enter();
     for (int i = tid * 4; i < hs; i += MS_THREADS * 4) {
-        *reinterpret_cast<float4*>(ve + i) = *reinterpret_cast<const float4*>(a.e + vo + i);
-        *reinterpret_cast<float4*>(vqg + i) = *reinterpret_cast<const float4*>(a.qg + vo + i);
+        // the five loads before the first store
+        const float4 le = *reinterpret_cast<const float4*>(a.e + vo + i), lq = *reinterpret_cast<const float4*>(a.qg + vo + i);
+        float4 lx = le, lw = le, la = le;
         if (PEND) {
-            *reinterpret_cast<float4*>(vpx + i) = *reinterpret_cast<const float4*>(a.px + vo + i);
-            *reinterpret_cast<float4*>(vpw + i) = *reinterpret_cast<const float4*>(a.pw + vo + i);
-            *reinterpret_cast<float4*>(vpa + i) = *reinterpret_cast<const float4*>(a.pah + vo + i);
+            lx = *reinterpret_cast<const float4*>(a.px + vo + i);
+            lw = *reinterpret_cast<const float4*>(a.pw + vo + i);
+            la = *reinterpret_cast<const float4*>(a.pah + vo + i);
+        }
+        *reinterpret_cast<float4*>(ve + i) = le;
+        *reinterpret_cast<float4*>(vqg + i) = lq;
+        if (PEND) {
+            *reinterpret_cast<float4*>(vpx + i) = lx;
+            *reinterpret_cast<float4*>(vpw + i) = lw;
+            *reinterpret_cast<float4*>(vpa + i) = la;
         }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
